@@ -1,0 +1,58 @@
+// C ABI of liborinfer_kernels.so.  Every entry point takes raw device pointers and
+// the CUDA stream to launch on, returns 0 on success, a negative value for a
+// rejected argument, or the cudaError_t of the launch.  None of them synchronises.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- runtime
+int orinfer_init(void);                      // per-device tables + status word (idempotent)
+int orinfer_read_status(int* out4);          // synchronises the device; copies 4 ints
+int orinfer_clear_status(void);
+const void* orinfer_e8p_tables_device(void); // device address of the decode tables
+int orinfer_e8p_basis_host(int8_t* out256x8);
+
+// ---- row kernels
+int orinfer_embed_w8(const int* ids, const int8_t* table, const __half* scales, __half* out,
+                     int rows, int hidden, int vocab, cudaStream_t stream);
+int orinfer_act_prep(const __half* x, float* resid, const __half* norm_w, const int8_t* signs,
+                     int8_t* q_out, float* scale_out, __half* y_out, int rows, int K, float eps,
+                     int zero_centered, int swiglu, cudaStream_t stream);
+int orinfer_rope_table(const int* positions, float* cosb, float* sinb, int rows, int head_dim,
+                       double theta, cudaStream_t stream);
+int orinfer_qk_rope_kv(const __half* qkv, const __half* wq, const __half* wk, const float* cosb,
+                       const float* sinb, const int* row_req, const int* row_pos,
+                       const int* page_table, int max_pages, int rows, int qh, int kvh,
+                       int head_dim, int gated, float eps, int zero_centered, __half* q_out,
+                       __half* gate_out, int8_t* kcache, int8_t* vcache, __half* kscale,
+                       __half* vscale, int num_pages, cudaStream_t stream);
+int orinfer_argmax_parts(int vocab);
+int orinfer_argmax(const float* logits, int rows, int vocab, float* scratch_val, int* scratch_idx,
+                   int* token, cudaStream_t stream);
+
+// ---- quantised GEMM.  fmt: 0 = W8 [N,K] int8, 1 = E8P Q4 U32 [K/128,N,16], 2 = E8P Q2 U16
+// [K/128,N,16].  out is fp16 [M,N] (out_f32 = 0) or fp32.  out[m,n] = acc * s_w[n] * s_a[m].
+int orinfer_qgemm(int fmt, const int8_t* a, const float* a_scale, const void* w,
+                  const __half* w_scale, void* out, int M, int N, int K, int out_f32,
+                  int force_path, cudaStream_t stream);
+
+// ---- attention over the paged INT8 KV cache
+size_t orinfer_attention_scratch_bytes(int rows, int qh, int head_dim, int splits);
+int orinfer_attention(const __half* q, const __half* gate, const int* row_req, const int* row_pos,
+                      const int* page_table, int max_pages, const int8_t* kcache,
+                      const int8_t* vcache, const __half* kscale, const __half* vscale,
+                      __half* out, int rows, int qh, int kvh, int head_dim, int splits,
+                      float* scratch, cudaStream_t stream);
+
+// ---- E8P nearest-codeword encoder: x fp32 [V,8] -> int32 codes [V]
+int orinfer_e8p_encode(const float* x, int* codes, long long vectors, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

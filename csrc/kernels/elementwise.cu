@@ -1,0 +1,458 @@
+// Bandwidth-bound row kernels: W8 embedding gather, the fused
+// residual-add / RMSNorm / SwiGLU / block-128 Hadamard rotation / per-token INT8
+// quantiser, RoPE tables, q/k head-norm + RoPE + paged INT8 KV write, and greedy
+// argmax.  They replace the reference's residual_norm_rotate_a8 /
+// rotate_activation_a8 (kernels/cuda/model/rotation_a8.py:267,608),
+// activation_quantization (kernels/cuda/operators/op30_activation_quantization.py:22),
+// full_prepare_mrope_int8 (kernels/cuda/model/kv_int8.py:63) and greedy_partials /
+// greedy_merge (kernels/cuda/model/greedy.py:11,83).
+#include "common.cuh"
+#include "api.h"
+
+namespace orinfer {
+
+// ------------------------------------------------------------------ embedding
+__global__ void embed_w8_kernel(const int* __restrict__ ids, const int8_t* __restrict__ table,
+                                const __half* __restrict__ scales, __half* __restrict__ out,
+                                int hidden, int vocab, int* status) {
+  const int row = blockIdx.x;
+  int id = ids[row];
+  if (id < 0 || id >= vocab) {
+    report_status(status, STATUS_BAD_INDEX, 1);
+    id = 0;
+  }
+  const float s = __half2float(scales[id]);
+  const int8_t* src = table + static_cast<size_t>(id) * hidden;
+  __half* dst = out + static_cast<size_t>(row) * hidden;
+  for (int i = threadIdx.x * 16; i < hidden; i += blockDim.x * 16) {
+    const int4 raw = *reinterpret_cast<const int4*>(src + i);
+    const int8_t* b = reinterpret_cast<const int8_t*>(&raw);
+    __align__(16) __half h[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) h[j] = __float2half_rn(static_cast<float>(b[j]) * s);
+    *reinterpret_cast<int4*>(dst + i) = *reinterpret_cast<const int4*>(h);
+    *reinterpret_cast<int4*>(dst + i + 8) = *reinterpret_cast<const int4*>(h + 8);
+  }
+}
+
+// ------------------------------------------------------------------ act_prep
+__device__ __forceinline__ float block_reduce(float v, float* red, bool is_max) {
+  v = is_max ? warp_max(v) : warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = (lane < nw) ? red[lane] : (is_max ? 0.f : 0.f);
+  r = is_max ? warp_max(r) : warp_sum(r);
+  return r;
+}
+
+// One CTA per row.  row buffer (K floats) lives in dynamic shared memory.
+//   SWIGLU: x is [M, 2K] (gate | up);   otherwise x is [M, K] (may be null when resid given).
+template <bool SWIGLU>
+__global__ void __launch_bounds__(256) act_prep_kernel(
+    const __half* __restrict__ x, float* __restrict__ resid, const __half* __restrict__ norm_w,
+    const int8_t* __restrict__ signs, int8_t* __restrict__ q_out, float* __restrict__ scale_out,
+    __half* __restrict__ y_out, int K, float eps, int zero_centered) {
+  extern __shared__ float rowbuf[];
+  __shared__ float red[32];
+  const int row = blockIdx.x, tid = threadIdx.x;
+  float sumsq = 0.f;
+  if (SWIGLU) {
+    const __half* g = x + static_cast<size_t>(row) * 2 * K;
+    const __half* u = g + K;
+    for (int i = tid * 8; i < K; i += blockDim.x * 8) {
+      const int4 gr = *reinterpret_cast<const int4*>(g + i);
+      const int4 ur = *reinterpret_cast<const int4*>(u + i);
+      const __half* gh = reinterpret_cast<const __half*>(&gr);
+      const __half* uh = reinterpret_cast<const __half*>(&ur);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float gv = __half2float(gh[j]);
+        const float sg = __fdiv_rn(1.f, 1.f + expf(-gv));
+        rowbuf[i + j] = round_f16(__fmul_rn(__fmul_rn(gv, sg), __half2float(uh[j])));
+      }
+    }
+  } else {
+    const __half* xr = x ? x + static_cast<size_t>(row) * K : nullptr;
+    float* rr = resid ? resid + static_cast<size_t>(row) * K : nullptr;
+    for (int i = tid * 8; i < K; i += blockDim.x * 8) {
+      float v[8];
+      if (xr) {
+        const int4 raw = *reinterpret_cast<const int4*>(xr + i);
+        const __half* h = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __half2float(h[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = 0.f;
+      }
+      if (rr) {
+        const float4 r0 = *reinterpret_cast<const float4*>(rr + i);
+        const float4 r1 = *reinterpret_cast<const float4*>(rr + i + 4);
+        v[0] += r0.x; v[1] += r0.y; v[2] += r0.z; v[3] += r0.w;
+        v[4] += r1.x; v[5] += r1.y; v[6] += r1.z; v[7] += r1.w;
+        *reinterpret_cast<float4*>(rr + i) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(rr + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        rowbuf[i + j] = v[j];
+        sumsq += v[j] * v[j];
+      }
+    }
+    if (norm_w) {
+      const float total = block_reduce(sumsq, red, false);
+      const float r = rsqrtf(total / static_cast<float>(K) + eps);
+      const float add = zero_centered ? 1.f : 0.f;
+      for (int i = tid * 8; i < K; i += blockDim.x * 8) {
+        const int4 wr = *reinterpret_cast<const int4*>(norm_w + i);
+        const __half* wh = reinterpret_cast<const __half*>(&wr);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          rowbuf[i + j] =
+              round_f16(__fmul_rn(__fmul_rn(rowbuf[i + j], r), __half2float(wh[j]) + add));
+      }
+    } else {
+      for (int i = tid * 8; i < K; i += blockDim.x * 8)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) rowbuf[i + j] = round_f16(rowbuf[i + j]);
+    }
+  }
+  __syncthreads();
+  if (y_out) {
+    __half* yr = y_out + static_cast<size_t>(row) * K;
+    for (int i = tid * 8; i < K; i += blockDim.x * 8) {
+      __align__(16) __half h[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(rowbuf[i + j]);
+      *reinterpret_cast<int4*>(yr + i) = *reinterpret_cast<const int4*>(h);
+    }
+  }
+  float amax = 0.f;
+  if (signs) {
+    // Each warp transforms whole 128-blocks; lane holds 4 consecutive values.
+    const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+    for (int b = warp; b < K / 128; b += nw) {
+      float* p = rowbuf + b * 128 + lane * 4;
+      const char4 sg = *reinterpret_cast<const char4*>(signs + b * 128 + lane * 4);
+      float v0 = p[0] * sg.x, v1 = p[1] * sg.y, v2 = p[2] * sg.z, v3 = p[3] * sg.w;
+      float t0 = v0 + v1, t1 = v0 - v1, t2 = v2 + v3, t3 = v2 - v3;      // h = 1
+      v0 = t0 + t2; v2 = t0 - t2; v1 = t1 + t3; v3 = t1 - t3;            // h = 2
+#pragma unroll
+      for (int m = 1; m < 32; m <<= 1) {                                   // h = 4 .. 64
+        const float o0 = __shfl_xor_sync(0xffffffffu, v0, m);
+        const float o1 = __shfl_xor_sync(0xffffffffu, v1, m);
+        const float o2 = __shfl_xor_sync(0xffffffffu, v2, m);
+        const float o3 = __shfl_xor_sync(0xffffffffu, v3, m);
+        const bool hi = (lane & m) != 0;
+        v0 = hi ? o0 - v0 : v0 + o0;
+        v1 = hi ? o1 - v1 : v1 + o1;
+        v2 = hi ? o2 - v2 : v2 + o2;
+        v3 = hi ? o3 - v3 : v3 + o3;
+      }
+      const float c = 0.08838834764831845f;                                // 128^-1/2
+      v0 *= c; v1 *= c; v2 *= c; v3 *= c;
+      p[0] = v0; p[1] = v1; p[2] = v2; p[3] = v3;
+      amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3))));
+    }
+  } else {
+    for (int i = tid; i < K; i += blockDim.x) amax = fmaxf(amax, fabsf(rowbuf[i]));
+  }
+  amax = block_reduce(amax, red, true);
+  const float scale = a8_scale(amax);
+  if (tid == 0) scale_out[row] = scale;
+  int8_t* qr = q_out + static_cast<size_t>(row) * K;
+  for (int i = tid * 4; i < K; i += blockDim.x * 4) {
+    char4 c;
+    c.x = static_cast<signed char>(a8_code(rowbuf[i + 0], scale));
+    c.y = static_cast<signed char>(a8_code(rowbuf[i + 1], scale));
+    c.z = static_cast<signed char>(a8_code(rowbuf[i + 2], scale));
+    c.w = static_cast<signed char>(a8_code(rowbuf[i + 3], scale));
+    *reinterpret_cast<char4*>(qr + i) = c;
+  }
+}
+
+// ------------------------------------------------------------------ RoPE tables
+__global__ void rope_table_kernel(const int* __restrict__ positions, float* __restrict__ cosb,
+                                  float* __restrict__ sinb, int rows, int half_dim, double theta) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * half_dim) return;
+  const int r = idx / half_dim, j = idx % half_dim;
+  const double inv = pow(theta, -static_cast<double>(2 * j) / static_cast<double>(2 * half_dim));
+  const double ang = static_cast<double>(positions[r]) * inv;
+  double s, c;
+  sincos(ang, &s, &c);
+  cosb[idx] = static_cast<float>(c);
+  sinb[idx] = static_cast<float>(s);
+}
+
+// ------------------------------------------------------------------ q/k norm + RoPE + KV write
+// One warp per (row, head).  Heads are ordered q[0..QH), k[0..KVH), v[0..KVH).
+// Input row layout: q heads (D each, or 2D = query|gate when GATED), then K, then V.
+template <int D, bool GATED>
+__global__ void __launch_bounds__(256) qk_rope_kv_kernel(
+    const __half* __restrict__ qkv, const __half* __restrict__ wq, const __half* __restrict__ wk,
+    const float* __restrict__ cosb, const float* __restrict__ sinb,
+    const int* __restrict__ row_req, const int* __restrict__ row_pos,
+    const int* __restrict__ page_table, int max_pages, int qh, int kvh, float eps,
+    int zero_centered, __half* __restrict__ q_out, __half* __restrict__ gate_out,
+    int8_t* __restrict__ kcache, int8_t* __restrict__ vcache, __half* __restrict__ kscale,
+    __half* __restrict__ vscale, int num_pages, int* status) {
+  constexpr int HALF = D / 2;
+  constexpr int PER = HALF / 32;          // pairs per lane
+  constexpr int GROUPS = D / 64;
+  const int row = blockIdx.x;
+  const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int heads = qh + 2 * kvh;
+  if (head >= heads) return;
+  const int qstride = GATED ? 2 * D : D;
+  const int width = qh * qstride + 2 * kvh * D;
+  const __half* src;
+  const bool is_q = head < qh, is_k = !is_q && head < qh + kvh;
+  if (is_q) src = qkv + static_cast<size_t>(row) * width + head * qstride;
+  else src = qkv + static_cast<size_t>(row) * width + qh * qstride + (head - qh) * D;
+  float a[PER], b[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    a[i] = __half2float(src[lane + 32 * i]);
+    b[i] = __half2float(src[HALF + lane + 32 * i]);
+  }
+  if (is_q || is_k) {
+    const __half* w = is_q ? wq : wk;
+    if (w) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) ss += a[i] * a[i] + b[i] * b[i];
+      ss = warp_sum(ss);
+      const float r = rsqrtf(ss / static_cast<float>(D) + eps);
+      const float add = zero_centered ? 1.f : 0.f;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        a[i] = round_f16(__fmul_rn(__fmul_rn(a[i], r), __half2float(w[lane + 32 * i]) + add));
+        b[i] = round_f16(
+            __fmul_rn(__fmul_rn(b[i], r), __half2float(w[HALF + lane + 32 * i]) + add));
+      }
+    }
+    const float* cr = cosb + static_cast<size_t>(row) * HALF;
+    const float* sr = sinb + static_cast<size_t>(row) * HALF;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const float c = cr[lane + 32 * i], s = sr[lane + 32 * i];
+      const float na = round_f16(__fsub_rn(__fmul_rn(a[i], c), __fmul_rn(b[i], s)));
+      const float nb = round_f16(__fadd_rn(__fmul_rn(b[i], c), __fmul_rn(a[i], s)));
+      a[i] = na;
+      b[i] = nb;
+    }
+  }
+  if (is_q) {
+    __half* dst = q_out + (static_cast<size_t>(row) * qh + head) * D;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      dst[lane + 32 * i] = __float2half_rn(a[i]);
+      dst[HALF + lane + 32 * i] = __float2half_rn(b[i]);
+    }
+    if (GATED) {
+      __half* gd = gate_out + (static_cast<size_t>(row) * qh + head) * D;
+      for (int i = lane; i < D; i += 32) gd[i] = src[D + i];
+    }
+    return;
+  }
+  // K or V: quantise per 64-channel group and write into the paged cache.
+  const int req = row_req[row], pos = row_pos[row];
+  const int page = page_table[static_cast<size_t>(req) * max_pages + (pos >> 7)];
+  if (page < 0 || page >= num_pages) {
+    if (lane == 0) report_status(status, STATUS_BAD_INDEX, 2);
+    return;
+  }
+  const int kvhead = is_k ? head - qh : head - qh - kvh;
+  const size_t slot = static_cast<size_t>(page) * 128 + (pos & 127);
+  float gmax[GROUPS];
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) gmax[g] = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int ja = lane + 32 * i, jb = HALF + ja;
+#pragma unroll
+    for (int g = 0; g < GROUPS; ++g) {
+      if (ja / 64 == g) gmax[g] = fmaxf(gmax[g], fabsf(a[i]));
+      if (jb / 64 == g) gmax[g] = fmaxf(gmax[g], fabsf(b[i]));
+    }
+  }
+  float gscale[GROUPS];
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) {
+    const float m = warp_max(gmax[g]);
+    gscale[g] = round_f16(fmaxf(__fdiv_rn(m, 127.f), 5.9604644775390625e-08f));
+  }
+  int8_t* cdst = (is_k ? kcache : vcache) + (slot * kvh + kvhead) * D;
+  __half* sdst = (is_k ? kscale : vscale) + (slot * kvh + kvhead) * GROUPS;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int ja = lane + 32 * i, jb = HALF + ja;
+    float sa = gscale[0], sb = gscale[0];
+#pragma unroll
+    for (int g = 1; g < GROUPS; ++g) {
+      if (ja / 64 == g) sa = gscale[g];
+      if (jb / 64 == g) sb = gscale[g];
+    }
+    cdst[ja] = static_cast<int8_t>(a8_code(a[i], sa));
+    cdst[jb] = static_cast<int8_t>(a8_code(b[i], sb));
+  }
+  if (lane < GROUPS) {
+    float s = gscale[0];
+#pragma unroll
+    for (int g = 1; g < GROUPS; ++g)
+      if (lane == g) s = gscale[g];
+    sdst[lane] = __float2half_rn(s);
+  }
+}
+
+// ------------------------------------------------------------------ argmax
+// Pass 1: each block scans a slice of one row; pass 2 merges the partials.  Ties go
+// to the lowest index; a non-finite maximum marks the row invalid (token -1).
+__global__ void argmax_partial_kernel(const float* __restrict__ logits, int vocab, int parts,
+                                      float* __restrict__ pval, int* __restrict__ pidx) {
+  const int row = blockIdx.y, part = blockIdx.x;
+  const int chunk = (vocab + parts - 1) / parts;
+  const int lo = part * chunk, hi = min(vocab, lo + chunk);
+  const float* r = logits + static_cast<size_t>(row) * vocab;
+  float best = -INFINITY;
+  int bidx = 0x7fffffff;
+  bool bad = false;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v = r[i];
+    if (!(fabsf(v) <= 3.4e38f)) bad = true;
+    if (v > best) { best = v; bidx = i; }
+  }
+  __shared__ float sv[256];
+  __shared__ int si[256];
+  __shared__ int sbad;
+  if (threadIdx.x == 0) sbad = 0;
+  __syncthreads();
+  if (bad) sbad = 1;
+  sv[threadIdx.x] = best;
+  si[threadIdx.x] = bidx;
+  __syncthreads();
+  for (int s = blockDim.x / 2; s > 0; s >>= 1) {
+    if (threadIdx.x < s) {
+      const float ov = sv[threadIdx.x + s];
+      const int oi = si[threadIdx.x + s];
+      if (ov > sv[threadIdx.x] || (ov == sv[threadIdx.x] && oi < si[threadIdx.x])) {
+        sv[threadIdx.x] = ov;
+        si[threadIdx.x] = oi;
+      }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    pval[row * parts + part] = sbad ? NAN : sv[0];
+    pidx[row * parts + part] = si[0];
+  }
+}
+
+__global__ void argmax_merge_kernel(const float* __restrict__ pval, const int* __restrict__ pidx,
+                                    int parts, int* __restrict__ token) {
+  const int row = blockIdx.x;
+  if (threadIdx.x != 0) return;
+  float best = -INFINITY;
+  int bidx = 0x7fffffff;
+  bool bad = false;
+  for (int p = 0; p < parts; ++p) {
+    const float v = pval[row * parts + p];
+    const int i = pidx[row * parts + p];
+    if (v != v) bad = true;
+    if (v > best || (v == best && i < bidx)) { best = v; bidx = i; }
+  }
+  token[row] = bad ? -1 : bidx;
+}
+
+}  // namespace orinfer
+
+using namespace orinfer;
+
+extern "C" {
+
+int orinfer_embed_w8(const int* ids, const int8_t* table, const __half* scales, __half* out,
+                     int rows, int hidden, int vocab, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (hidden % 16) return -1;
+  if (runtime_ensure_init() != cudaSuccess) return -2;
+  embed_w8_kernel<<<rows, 128, 0, stream>>>(ids, table, scales, out, hidden, vocab,
+                                            runtime_status_ptr());
+  return static_cast<int>(cudaGetLastError());
+}
+
+int orinfer_act_prep(const __half* x, float* resid, const __half* norm_w, const int8_t* signs,
+                     int8_t* q_out, float* scale_out, __half* y_out, int rows, int K, float eps,
+                     int zero_centered, int swiglu, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (K % 128) return -1;
+  const size_t smem = static_cast<size_t>(K) * sizeof(float);
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(act_prep_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         200 * 1024);
+    cudaFuncSetAttribute(act_prep_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         200 * 1024);
+    attr_set = true;
+  }
+  if (smem > 200 * 1024) return -1;
+  if (swiglu)
+    act_prep_kernel<true><<<rows, 256, smem, stream>>>(x, nullptr, nullptr, signs, q_out,
+                                                       scale_out, y_out, K, eps, zero_centered);
+  else
+    act_prep_kernel<false><<<rows, 256, smem, stream>>>(x, resid, norm_w, signs, q_out, scale_out,
+                                                        y_out, K, eps, zero_centered);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int orinfer_rope_table(const int* positions, float* cosb, float* sinb, int rows, int head_dim,
+                       double theta, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int total = rows * (head_dim / 2);
+  rope_table_kernel<<<(total + 255) / 256, 256, 0, stream>>>(positions, cosb, sinb, rows,
+                                                             head_dim / 2, theta);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int orinfer_qk_rope_kv(const __half* qkv, const __half* wq, const __half* wk, const float* cosb,
+                       const float* sinb, const int* row_req, const int* row_pos,
+                       const int* page_table, int max_pages, int rows, int qh, int kvh,
+                       int head_dim, int gated, float eps, int zero_centered, __half* q_out,
+                       __half* gate_out, int8_t* kcache, int8_t* vcache, __half* kscale,
+                       __half* vscale, int num_pages, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (runtime_ensure_init() != cudaSuccess) return -2;
+  const int heads = qh + 2 * kvh;
+  dim3 grid(rows, (heads + 7) / 8);
+  int* st = runtime_status_ptr();
+#define LAUNCH(DD, GG)                                                                          \
+  qk_rope_kv_kernel<DD, GG><<<grid, 256, 0, stream>>>(                                          \
+      qkv, wq, wk, cosb, sinb, row_req, row_pos, page_table, max_pages, qh, kvh, eps,           \
+      zero_centered, q_out, gate_out, kcache, vcache, kscale, vscale, num_pages, st)
+  if (head_dim == 64 && !gated) LAUNCH(64, false);
+  else if (head_dim == 64 && gated) LAUNCH(64, true);
+  else if (head_dim == 128 && !gated) LAUNCH(128, false);
+  else if (head_dim == 128 && gated) LAUNCH(128, true);
+  else if (head_dim == 256 && !gated) LAUNCH(256, false);
+  else if (head_dim == 256 && gated) LAUNCH(256, true);
+  else return -1;
+#undef LAUNCH
+  return static_cast<int>(cudaGetLastError());
+}
+
+int orinfer_argmax_parts(int vocab) { return vocab >= 65536 ? 64 : (vocab >= 4096 ? 8 : 1); }
+
+int orinfer_argmax(const float* logits, int rows, int vocab, float* scratch_val, int* scratch_idx,
+                   int* token, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int parts = orinfer_argmax_parts(vocab);
+  argmax_partial_kernel<<<dim3(parts, rows), 256, 0, stream>>>(logits, vocab, parts, scratch_val,
+                                                               scratch_idx);
+  argmax_merge_kernel<<<rows, 32, 0, stream>>>(scratch_val, scratch_idx, parts, token);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"

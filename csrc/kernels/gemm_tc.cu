@@ -1,0 +1,279 @@
+// Quantised GEMM on the 5th-generation tensor cores: out[M,N] = (A8[M,K] . W[N,K]^T) * s_w * s_a.
+//
+// One CTA computes a 128 x 128 output tile.  Warp 0 streams operand tiles with TMA
+// (activations always; INT8 weights for W8; the packed E8P codes as one contiguous
+// bulk copy per k-block for Q4/Q2).  Warps 2-5 expand the lattice codes into an INT8
+// weight tile in the 128-byte-swizzled K-major layout the tensor core reads, warp 1
+// issues tcgen05.mma kind::i8 into a TMEM accumulator, and warps 2-5 finally read
+// TMEM back, apply the two scales and store FP16/FP32.  INT4 tensor-core MMA (the
+// reference's fastest path, kernels/cuda/model/e8p_core.py:15-33) does not exist on
+// tcgen05, so both E8P formats go through INT8 operands.  Replaces e8p_q4.projection
+// (kernels/cuda/model/e8p_q4.py:144-265), integer_vq (kernels/cuda/model/integer_vq.py:263)
+// and int8_projection (kernels/cuda/model/int8_projection.py:15).
+#include <cuda.h>
+
+#include "api.h"
+#include "common.cuh"
+#include "tma.h"
+
+namespace orinfer {
+
+int qgemv_dispatch(int fmt, const int8_t* a, const float* as, const void* w, const __half* ws,
+                   void* out, int M, int N, int K, int out_f32, cudaStream_t stream);
+
+namespace tc {
+
+constexpr int BM = 128, BN = 128, BK = 128, STAGES = 4;
+constexpr int TILE_BYTES = 128 * 128;        // one INT8 operand tile
+constexpr int THREADS = 192;
+
+template <int FMT>
+struct Layout {
+  static constexpr int ROW_CODE_BYTES = FMT == 1 ? 64 : (FMT == 2 ? 32 : 0);
+  static constexpr int CODE_BYTES = BN * ROW_CODE_BYTES;
+  static constexpr int LUT_BYTES = FMT == 1 ? 16384 : (FMT == 2 ? 8192 : 0);
+  static constexpr int A_OFF = 0;
+  static constexpr int B_OFF = A_OFF + STAGES * TILE_BYTES;
+  static constexpr int CODE_OFF = B_OFF + STAGES * TILE_BYTES;
+  static constexpr int LUT_OFF = CODE_OFF + STAGES * CODE_BYTES;
+  static constexpr int BAR_OFF = LUT_OFF + LUT_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;   // barriers + alignment slack
+};
+
+template <int FMT, bool OUT_F32>
+__global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
+    const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+    const unsigned char* __restrict__ w, const float* __restrict__ a_scale,
+    const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K,
+    const E8pTables* __restrict__ tables, int* status) {
+  using L = Layout<FMT>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* a_s = smem + L::A_OFF;
+  unsigned char* b_s = smem + L::B_OFF;
+  unsigned char* code_s = smem + L::CODE_OFF;
+  uint4* lut = reinterpret_cast<uint4*>(smem + L::LUT_OFF);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* tma_full = bars;                 // [STAGES]
+  uint64_t* b_full = bars + STAGES;          // [STAGES]
+  uint64_t* empty = bars + 2 * STAGES;       // [STAGES]
+  uint64_t* tmem_full = bars + 3 * STAGES;   // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int kblocks = K / BK;
+  const int rows_valid = min(BN, N - n0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&tma_full[s], 1);
+      mbar_init(&b_full[s], 128);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(tmem_full, 1);
+    mbar_fence_init();
+    prefetch_tmap(&tmap_a);
+    if (FMT == 0) prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, BN);
+    tmem_relinquish();
+  }
+  if (FMT != 0 && warp >= 2) {
+    const int t = threadIdx.x - 64;
+    const uint4* src = reinterpret_cast<const uint4*>(tables);
+    // fine table first, then (Q4 only) the coarse one: same order as E8pTables.
+    for (int i = t; i < L::LUT_BYTES / 16; i += 128) lut[i] = src[i];
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int issued = 0;
+      for (int kb = 0; kb < kblocks; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, status, STATUS_TMA_WAIT, kb)) break;
+        const uint32_t bytes =
+            TILE_BYTES + (FMT == 0 ? TILE_BYTES : rows_valid * L::ROW_CODE_BYTES);
+        mbar_expect_tx(&tma_full[s], bytes);
+        tma_load_2d(a_s + s * TILE_BYTES, &tmap_a, &tma_full[s], kb * BK, m0);
+        if (FMT == 0) {
+          tma_load_2d(b_s + s * TILE_BYTES, &tmap_b, &tma_full[s], kb * BK, n0);
+        } else {
+          const unsigned char* src =
+              w + (static_cast<size_t>(kb) * N + n0) * L::ROW_CODE_BYTES;
+          bulk_load(code_s + s * L::CODE_BYTES, src, rows_valid * L::ROW_CODE_BYTES, &tma_full[s]);
+        }
+        issued = kb + 1;
+      }
+      // Never leave the CTA with a copy of ours in flight: wait (bounded) for the
+      // last copies issued into each stage.
+      for (int kb = max(0, issued - STAGES); kb < issued; ++kb)
+        mbar_wait(&tma_full[kb % STAGES], (kb / STAGES) & 1, status, STATUS_TMA_WAIT, 0x4000 | kb);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(2, 1, 1, 0, 0, BM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < kblocks && ok; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1;
+        ok = mbar_wait(&tma_full[s], ph, status, STATUS_MMA_WAIT, kb);
+        if (ok && FMT != 0) ok = mbar_wait(&b_full[s], ph, status, STATUS_MMA_WAIT, 0x2000 | kb);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(a_s + s * TILE_BYTES);
+        const uint32_t b_addr = smem_u32(b_s + s * TILE_BYTES);
+#pragma unroll
+        for (int j = 0; j < BK / 32; ++j) {
+          mma_i8_ss(tmem_base, umma_desc(a_addr + j * 32, 16, 1024),
+                    umma_desc(b_addr + j * 32, 16, 1024), idesc, (kb | j) != 0 ? 1u : 0u);
+        }
+        tc_commit(&empty[s]);
+      }
+      if (ok) tc_commit(tmem_full);
+    }
+  } else {
+    const int t = threadIdx.x - 64;                     // 0..127
+    bool ok = true;
+    if (FMT != 0) {
+      const uint4* fine = lut;
+      const uint4* coarse = lut + 512;
+      const int chunk = t & 7, rbase = t >> 3;          // 16 rows per pass
+      for (int kb = 0; kb < kblocks; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1;
+        ok = mbar_wait(&tma_full[s], ph, status, STATUS_DECODE_WAIT, kb);
+        if (!ok) break;
+        const unsigned char* cs = code_s + s * L::CODE_BYTES;
+        unsigned char* bs = b_s + s * TILE_BYTES;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int row = rbase + 16 * i;
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (row < rows_valid) {
+            if (FMT == 1) {
+              const uint2 wd = *reinterpret_cast<const uint2*>(cs + row * 64 + chunk * 8);
+              const uint2 q0 = e8p_decode_q4(wd.x, coarse, fine);
+              const uint2 q1 = e8p_decode_q4(wd.y, coarse, fine);
+              v = make_uint4(q0.x, q0.y, q1.x, q1.y);
+            } else {
+              const uint32_t wd = *reinterpret_cast<const uint32_t*>(cs + row * 32 + chunk * 4);
+              const uint2 q0 = e8p_decode8(wd & 0xffffu, fine);
+              const uint2 q1 = e8p_decode8(wd >> 16, fine);
+              v = make_uint4(q0.x, q0.y, q1.x, q1.y);
+            }
+          }
+          *reinterpret_cast<uint4*>(bs + swz128(row, chunk)) = v;
+        }
+        fence_proxy_async();
+        mbar_arrive(&b_full[s]);
+      }
+    }
+    if (ok) ok = mbar_wait(tmem_full, 0, status, STATUS_EPILOGUE_WAIT, 0);
+    ok = __all_sync(0xffffffffu, ok);        // tcgen05.ld needs the whole warp
+    if (ok) {
+      tc_fence_after();
+      const int quad = warp & 3;
+      const int row = quad * 32 + lane;
+      const int m = m0 + row;
+      const float sa = m < M ? a_scale[m] : 0.f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + c0, r);
+        tc_wait_ld();
+        if (m < M) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int n = n0 + c0 + g * 8;
+            if (n + 8 <= N) {
+              float v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                v[j] = (static_cast<float>(static_cast<int>(r[g * 8 + j])) *
+                        __half2float(w_scale[n + j])) * sa;
+              if (OUT_F32) {
+                float* o = reinterpret_cast<float*>(out) + static_cast<size_t>(m) * N + n;
+                *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+              } else {
+                __align__(16) __half h[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
+                __half* o = reinterpret_cast<__half*>(out) + static_cast<size_t>(m) * N + n;
+                *reinterpret_cast<int4*>(o) = *reinterpret_cast<const int4*>(h);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, BN);
+}
+
+template <int FMT, bool OUT_F32>
+int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale, void* out,
+           int M, int N, int K, cudaStream_t stream) {
+  using L = Layout<FMT>;
+  CUtensorMap ta, tb;
+  if (!make_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BM, BK)) return -3;
+  if (FMT == 0) {
+    if (!make_tmap_2d(&tb, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, BN, BK)) return -3;
+  } else {
+    tb = ta;
+    if (reinterpret_cast<uintptr_t>(w) % 16) return -1;
+  }
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(qgemm_tc_kernel<FMT, OUT_F32>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr = true;
+  }
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  qgemm_tc_kernel<FMT, OUT_F32><<<grid, THREADS, L::TOTAL, stream>>>(
+      ta, tb, reinterpret_cast<const unsigned char*>(w), a_scale, w_scale, out, M, N, K,
+      runtime_e8p_tables(), runtime_status_ptr());
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace tc
+}  // namespace orinfer
+
+using namespace orinfer;
+
+extern "C" int orinfer_qgemm(int fmt, const int8_t* a, const float* a_scale, const void* w,
+                             const __half* w_scale, void* out, int M, int N, int K, int out_f32,
+                             int force_path, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 128 || N % 8 || fmt < 0 || fmt > 2) return -1;
+  if (runtime_ensure_init() != cudaSuccess) return -2;
+  const bool simt = force_path == 1 || (force_path == 0 && M <= 8);
+  if (simt) {
+    // The SIMT kernel takes at most 8 rows per launch.
+    for (int m = 0; m < M; m += 8) {
+      const int rows = M - m < 8 ? M - m : 8;
+      void* o = out_f32 ? static_cast<void*>(reinterpret_cast<float*>(out) + (size_t)m * N)
+                        : static_cast<void*>(reinterpret_cast<__half*>(out) + (size_t)m * N);
+      int r = qgemv_dispatch(fmt, a + (size_t)m * K, a_scale + m, w, w_scale, o, rows, N, K,
+                             out_f32, stream);
+      if (r) return r;
+    }
+    return 0;
+  }
+#define GO(F) (out_f32 ? tc::launch<F, true>(a, a_scale, w, w_scale, out, M, N, K, stream) \
+                       : tc::launch<F, false>(a, a_scale, w, w_scale, out, M, N, K, stream))
+  if (fmt == 0) return GO(0);
+  if (fmt == 1) return GO(1);
+  return GO(2);
+#undef GO
+}

@@ -1,0 +1,208 @@
+// Small-M quantised GEMM (decode path, M <= 8): weight-bandwidth bound.  Each CTA
+// owns a few output rows and streams their codes once; warps split K, lanes decode
+// E8P codes through a shared-memory value table and accumulate with dp4a against
+// the INT8 activations staged in shared memory.  Replaces the reference's dp4a /
+// gemv projections (kernels/cuda/model/integer_core.py:275,
+// kernels/cuda/model/integer_vq.py:381 integer_e8p_gemv,
+// kernels/cuda/model/int8_projection.py:66).
+#include "api.h"
+#include "common.cuh"
+
+namespace orinfer {
+
+constexpr int GEMV_WARPS = 8;
+
+template <int MT>
+__device__ __forceinline__ void stage_activations(int8_t* dst, const int8_t* __restrict__ a, int M,
+                                                  int K) {
+  const int chunks = MT * K / 16;
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    const int m = (c * 16) / K;
+    int4 v = make_int4(0, 0, 0, 0);
+    if (m < M) v = *reinterpret_cast<const int4*>(a + static_cast<size_t>(c) * 16);
+    *reinterpret_cast<int4*>(dst + static_cast<size_t>(c) * 16) = v;
+  }
+}
+
+template <int MT>
+__device__ __forceinline__ void store_row(void* out, int out_f32, int m, int n, int N, int acc,
+                                          float sw, float sa) {
+  const float v = (static_cast<float>(acc) * sw) * sa;
+  if (out_f32) reinterpret_cast<float*>(out)[static_cast<size_t>(m) * N + n] = v;
+  else reinterpret_cast<__half*>(out)[static_cast<size_t>(m) * N + n] = __float2half_rn(v);
+}
+
+// FMT 1: Q4 (U32 codes, 8 rows per CTA, 4 lanes per row); FMT 2: Q2 (U16 codes, 16 rows, 2 lanes).
+template <int FMT, int MT>
+__global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
+    const int8_t* __restrict__ a, const float* __restrict__ a_scale, const uint4* __restrict__ w,
+    const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K, int out_f32,
+    const E8pTables* __restrict__ tables) {
+  constexpr int ROWS = FMT == 1 ? 8 : 16;
+  constexpr int LPR = 32 / ROWS;                 // lanes per row
+  constexpr int WPL = 128 / LPR;                 // weights per lane per k-block
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint4* fine = reinterpret_cast<uint4*>(smem_raw);
+  uint4* coarse = fine + 512;
+  int8_t* act = reinterpret_cast<int8_t*>(smem_raw) + (FMT == 1 ? 16384 : 8192);
+  __shared__ int red[GEMV_WARPS][ROWS][MT];
+
+  for (int i = threadIdx.x; i < 512; i += blockDim.x) {
+    fine[i] = tables->fine[i];
+    if (FMT == 1) coarse[i] = tables->coarse[i];
+  }
+  stage_activations<MT>(act, a, M, K);
+  __syncthreads();
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = lane / LPR, part = lane % LPR;
+  const int n0 = blockIdx.x * ROWS;
+  const int n = min(n0 + row, N - 1);
+  const int kblocks = K / 128;
+  int acc[MT];
+#pragma unroll
+  for (int m = 0; m < MT; ++m) acc[m] = 0;
+
+  // uint4 index of (kb, n, part): Q4 row = 16 words = 4 uint4; Q2 row = 16 halves = 2 uint4.
+  auto widx = [&](int kb) { return (static_cast<size_t>(kb) * N + n) * LPR + part; };
+  uint4 cur = make_uint4(0, 0, 0, 0);
+  if (warp < kblocks) cur = __ldg(w + widx(warp));
+  for (int kb = warp; kb < kblocks; kb += GEMV_WARPS) {
+    uint4 nxt = make_uint4(0, 0, 0, 0);
+    if (kb + GEMV_WARPS < kblocks) nxt = __ldg(w + widx(kb + GEMV_WARPS));
+    const int8_t* abase = act + kb * 128 + part * WPL;
+    const uint32_t words[4] = {cur.x, cur.y, cur.z, cur.w};
+    if (FMT == 1) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint2 q = e8p_decode_q4(words[j], coarse, fine);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          const int2 av = *reinterpret_cast<const int2*>(abase + m * K + j * 8);
+          acc[m] = __dp4a(static_cast<int>(q.x), av.x, acc[m]);
+          acc[m] = __dp4a(static_cast<int>(q.y), av.y, acc[m]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t code = (words[j >> 1] >> ((j & 1) * 16)) & 0xffffu;
+        const uint2 q = e8p_decode8(code, fine);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          const int2 av = *reinterpret_cast<const int2*>(abase + m * K + j * 8);
+          acc[m] = __dp4a(static_cast<int>(q.x), av.x, acc[m]);
+          acc[m] = __dp4a(static_cast<int>(q.y), av.y, acc[m]);
+        }
+      }
+    }
+    cur = nxt;
+  }
+#pragma unroll
+  for (int m = 0; m < MT; ++m) {
+#pragma unroll
+    for (int o = 1; o < LPR; o <<= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
+    if (part == 0) red[warp][row][m] = acc[m];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < ROWS * MT; i += blockDim.x) {
+    const int r = i / MT, m = i % MT;
+    if (n0 + r < N && m < M) {
+      int total = 0;
+#pragma unroll
+      for (int wv = 0; wv < GEMV_WARPS; ++wv) total += red[wv][r][m];
+      store_row<MT>(out, out_f32, m, n0 + r, N, total, __half2float(w_scale[n0 + r]), a_scale[m]);
+    }
+  }
+}
+
+// W8: one warp per output row, 16 weights per lane per step.
+template <int MT>
+__global__ void __launch_bounds__(GEMV_WARPS * 32) w8_gemv_kernel(
+    const int8_t* __restrict__ a, const float* __restrict__ a_scale, const int8_t* __restrict__ w,
+    const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K, int out_f32) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  int8_t* act = reinterpret_cast<int8_t*>(smem_raw);
+  stage_activations<MT>(act, a, M, K);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * GEMV_WARPS + warp;
+  if (n >= N) return;
+  const int8_t* wr = w + static_cast<size_t>(n) * K;
+  int acc[MT];
+#pragma unroll
+  for (int m = 0; m < MT; ++m) acc[m] = 0;
+#pragma unroll 4
+  for (int k = lane * 16; k < K; k += 512) {
+    const int4 wv = __ldg(reinterpret_cast<const int4*>(wr + k));
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      const int4 av = *reinterpret_cast<const int4*>(act + m * K + k);
+      acc[m] = __dp4a(wv.x, av.x, acc[m]);
+      acc[m] = __dp4a(wv.y, av.y, acc[m]);
+      acc[m] = __dp4a(wv.z, av.z, acc[m]);
+      acc[m] = __dp4a(wv.w, av.w, acc[m]);
+    }
+  }
+  const float sw = __half2float(w_scale[n]);
+#pragma unroll
+  for (int m = 0; m < MT; ++m) {
+    int v = acc[m];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0 && m < M) store_row<MT>(out, out_f32, m, n, N, v, sw, a_scale[m]);
+  }
+}
+
+template <int FMT, int MT>
+static int launch_e8p(const int8_t* a, const float* as, const void* w, const __half* ws, void* out,
+                      int M, int N, int K, int out_f32, cudaStream_t stream) {
+  constexpr int ROWS = FMT == 1 ? 8 : 16;
+  const size_t smem = (FMT == 1 ? 16384 : 8192) + static_cast<size_t>(MT) * K;
+  if (smem > 200 * 1024) return -1;
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(e8p_gemv_kernel<FMT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         200 * 1024);
+    attr = true;
+  }
+  e8p_gemv_kernel<FMT, MT><<<(N + ROWS - 1) / ROWS, GEMV_WARPS * 32, smem, stream>>>(
+      a, as, reinterpret_cast<const uint4*>(w), ws, out, M, N, K, out_f32, runtime_e8p_tables());
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int MT>
+static int launch_w8(const int8_t* a, const float* as, const void* w, const __half* ws, void* out,
+                     int M, int N, int K, int out_f32, cudaStream_t stream) {
+  const size_t smem = static_cast<size_t>(MT) * K;
+  if (smem > 200 * 1024) return -1;
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(w8_gemv_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         200 * 1024);
+    attr = true;
+  }
+  w8_gemv_kernel<MT><<<(N + GEMV_WARPS - 1) / GEMV_WARPS, GEMV_WARPS * 32, smem, stream>>>(
+      a, as, reinterpret_cast<const int8_t*>(w), ws, out, M, N, K, out_f32);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int qgemv_dispatch(int fmt, const int8_t* a, const float* as, const void* w, const __half* ws,
+                   void* out, int M, int N, int K, int out_f32, cudaStream_t stream) {
+  if (M < 1 || M > 8 || K % 128) return -1;
+#define BY_M(FN, ...)                                            \
+  (M == 1 ? FN<__VA_ARGS__ 1>(a, as, w, ws, out, M, N, K, out_f32, stream)  \
+   : M == 2 ? FN<__VA_ARGS__ 2>(a, as, w, ws, out, M, N, K, out_f32, stream) \
+   : M <= 4 ? FN<__VA_ARGS__ 4>(a, as, w, ws, out, M, N, K, out_f32, stream) \
+            : FN<__VA_ARGS__ 8>(a, as, w, ws, out, M, N, K, out_f32, stream))
+  if (fmt == 0) {
+    if (K % 16) return -1;
+    return BY_M(launch_w8, );
+  }
+  if (fmt == 1) return BY_M(launch_e8p, 1, );
+  if (fmt == 2) return BY_M(launch_e8p, 2, );
+#undef BY_M
+  return -1;
+}
+
+}  // namespace orinfer

@@ -1,0 +1,215 @@
+"""Device model runner: one packed-row forward pass over the CUDA kernels.
+
+A *packet* is a set of token rows from any mix of requests (decode rows and
+prefill chunks).  Shared ops (projections, norms) run once over all rows;
+request-private ops (KV write, attention, GDN state) are natively batched
+through ``row_req`` / ``row_pos`` / the page table, so no per-request launches
+exist.  This mirrors the packet structure of the reference's row adapter
+(crates/orinfer-models/src/qwen3_5/rows.rs:1137-1463) with page-table
+indirection in place of its pointer tables; op order follows
+python/orinfer_build/models/qwen35/build.py:802-1116.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config import KV_GROUP, PAGE_TOKENS, ModelConfig
+from ..ops import functional as F
+from .weights import LayerWeights, ModelWeights, QLinear
+
+
+@dataclass
+class KVPool:
+    """Paged INT8 KV storage for every full-attention layer. Page 0 is a dummy
+    target for padded rows and is never handed out."""
+    k: List[torch.Tensor]
+    v: List[torch.Tensor]
+    ks: List[torch.Tensor]
+    vs: List[torch.Tensor]
+    pages: int
+
+    @classmethod
+    def allocate(cls, cfg: ModelConfig, pages: int, device, extra_layers: int = 0) -> "KVPool":
+        n = sum(cfg.is_full_attention(i) for i in range(cfg.layers)) + extra_layers
+        mk = lambda last, dt: [torch.zeros(pages, PAGE_TOKENS, cfg.kv_heads, last, dtype=dt,
+                                           device=device) for _ in range(n)]
+        g = cfg.head_dim // KV_GROUP
+        return cls(mk(cfg.head_dim, torch.int8), mk(cfg.head_dim, torch.int8),
+                   mk(g, torch.float16), mk(g, torch.float16), pages)
+
+    @staticmethod
+    def bytes_per_page(cfg: ModelConfig, extra_layers: int = 0) -> int:
+        n = sum(cfg.is_full_attention(i) for i in range(cfg.layers)) + extra_layers
+        per_tok = 2 * cfg.kv_dim + 2 * 2 * (cfg.kv_dim // KV_GROUP)
+        return n * per_tok * PAGE_TOKENS
+
+
+class Workspace:
+    """Static activation buffers sized for ``max_rows`` packed rows."""
+
+    def __init__(self, cfg: ModelConfig, max_rows: int, device):
+        self.max_rows = max_rows
+        f16, f32, i8 = torch.float16, torch.float32, torch.int8
+        e = lambda *s, dt=f16: torch.empty(*s, dtype=dt, device=device)
+        h = cfg.hidden
+        self.hidden = e(max_rows, h)
+        self.resid = e(max_rows, h, dt=f32)
+        self.scale = e(max_rows, dt=f32)
+        self.q8: Dict[int, torch.Tensor] = {}
+        widths = {h, cfg.q_heads * cfg.head_dim}
+        ffn_w = cfg.ffn or 0
+        if ffn_w:
+            widths.add(ffn_w)
+        if cfg.experts:
+            widths.update({cfg.expert_ffn, cfg.shared_expert_ffn or cfg.expert_ffn})
+        if cfg.arch == "hybrid":
+            widths.add(cfg.gdn_v_heads * cfg.gdn_head_dim)
+        if cfg.mtp_layers:
+            widths.add(2 * h)
+            widths.add(cfg.ffn or max(cfg.expert_ffn * 4, 512))
+        for w in widths:
+            if w:
+                self.q8[w] = e(max_rows, w, dt=i8)
+        self.qkv = e(max_rows, cfg.q_dim + 2 * cfg.kv_dim)
+        self.q = e(max_rows, cfg.q_heads, cfg.head_dim)
+        self.gate = e(max_rows, cfg.q_heads, cfg.head_dim) if cfg.gated_attention else None
+        self.attn = e(max_rows, cfg.q_heads * cfg.head_dim)
+        mtp_f = (cfg.ffn or max(cfg.expert_ffn * 4, 512)) if cfg.mtp_layers else 0
+        self.gate_up = e(max_rows, 2 * max(ffn_w, cfg.shared_expert_ffn, mtp_f, 64))
+        self.cos = e(max_rows, cfg.head_dim // 2, dt=f32)
+        self.sin = e(max_rows, cfg.head_dim // 2, dt=f32)
+        self.attn_scratch: Optional[torch.Tensor] = None
+
+    def scratch(self, floats: int, device) -> torch.Tensor:
+        if self.attn_scratch is None or self.attn_scratch.numel() < floats:
+            self.attn_scratch = torch.empty(floats, dtype=torch.float32, device=device)
+        return self.attn_scratch
+
+
+@dataclass
+class Packet:
+    """Device-side description of one forward pass (all int32, on the GPU)."""
+    ids: torch.Tensor            # [rows]
+    row_req: torch.Tensor        # [rows] index into page_table
+    row_pos: torch.Tensor        # [rows] absolute position of the row in its request
+    page_table: torch.Tensor     # [requests, max_pages]
+    rows: int
+    max_kv_len: int              # host-side bound used to pick the split count
+    logit_rows: Optional[torch.Tensor] = None   # int64 rows whose logits are needed (None = all)
+
+
+class ModelRunner:
+    def __init__(self, weights: ModelWeights, kv: KVPool, max_rows: int):
+        self.w = weights
+        self.cfg = weights.config
+        self.kv = kv
+        self.device = weights.embed_q.device
+        self.ws = Workspace(self.cfg, max_rows, self.device)
+        self._attn_index = {}
+        n = 0
+        for i in range(self.cfg.layers):
+            if self.cfg.is_full_attention(i):
+                self._attn_index[i] = n
+                n += 1
+        self.mtp_kv_index = n
+        self._argmax_scratch = None
+        self.layer_hooks = {}
+
+    # ---------------------------------------------------------------- helpers
+    def _signs(self, lin: QLinear):
+        return lin.signs
+
+    def _linear(self, lin: QLinear, q8, scale, rows, out, out_f32=False):
+        return F.qgemm(q8, scale, lin.codes, lin.scale, lin.fmt, lin.n, out=out, out_f32=out_f32,
+                       rows=rows)
+
+    def _attention_block(self, lw: LayerWeights, kv_slot: int, x, p: Packet, rows: int,
+                         first: bool):
+        cfg, ws = self.cfg, self.ws
+        h = cfg.hidden
+        q8, sc = F.act_prep(x, ws.resid, lw.in_norm,
+                            self._signs(lw.qkv), eps=cfg.eps, zero_centered=cfg.zero_centered_norm,
+                            rows=rows, q_out=ws.q8[h], scale_out=ws.scale)
+        qkv = self._linear(lw.qkv, q8, sc, rows, ws.qkv)
+        F.qk_rope_kv(qkv, lw.q_norm if cfg.qk_norm else None, lw.k_norm if cfg.qk_norm else None,
+                     ws.cos, ws.sin, p.row_req, p.row_pos, p.page_table, self.kv.k[kv_slot],
+                     self.kv.v[kv_slot], self.kv.ks[kv_slot], self.kv.vs[kv_slot],
+                     qh=cfg.q_heads, kvh=cfg.kv_heads, head_dim=cfg.head_dim,
+                     gated=cfg.gated_attention and lw.qkv.n == cfg.q_dim + 2 * cfg.kv_dim,
+                     eps=cfg.eps, zero_centered=cfg.zero_centered_norm, q_out=ws.q,
+                     gate_out=ws.gate, rows=rows)
+        splits = F.attention_splits(p.max_kv_len, rows, cfg.kv_heads)
+        scratch = None
+        if splits > 1:
+            scratch = ws.scratch(ws.max_rows * cfg.q_heads * splits * (cfg.head_dim + 2),
+                                 self.device)
+        gated = cfg.gated_attention and lw.qkv.n == cfg.q_dim + 2 * cfg.kv_dim
+        F.attention(ws.q, ws.gate if gated else None, p.row_req, p.row_pos, p.page_table,
+                    self.kv.k[kv_slot], self.kv.v[kv_slot], self.kv.ks[kv_slot],
+                    self.kv.vs[kv_slot], splits=splits, scratch=scratch, out=ws.attn, rows=rows)
+        qd = cfg.q_heads * cfg.head_dim
+        q8, sc = F.act_prep(ws.attn, None, None, self._signs(lw.o), rows=rows, q_out=ws.q8[qd],
+                            scale_out=ws.scale)
+        return self._linear(lw.o, q8, sc, rows, ws.hidden)
+
+    def _dense_ffn(self, lw: LayerWeights, x, rows: int):
+        cfg, ws = self.cfg, self.ws
+        h = cfg.hidden
+        q8, sc = F.act_prep(x, ws.resid, lw.post_norm, self._signs(lw.gate_up), eps=cfg.eps,
+                            zero_centered=cfg.zero_centered_norm, rows=rows, q_out=ws.q8[h],
+                            scale_out=ws.scale)
+        f = lw.gate_up.n // 2
+        gu = self._linear(lw.gate_up, q8, sc, rows, ws.gate_up.view(-1)[: ws.max_rows * 2 * f]
+                          .view(ws.max_rows, 2 * f))
+        q8, sc = F.act_prep(gu, None, None, self._signs(lw.down), swiglu=True, rows=rows,
+                            q_out=ws.q8[f], scale_out=ws.scale)
+        return self._linear(lw.down, q8, sc, rows, ws.hidden)
+
+    # ---------------------------------------------------------------- forward
+    def forward_hidden(self, p: Packet):
+        """Runs embedding + all layers; leaves the last branch output in ws.hidden and
+        the running residual in ws.resid (final residual = resid + hidden)."""
+        cfg, ws, rows = self.cfg, self.ws, p.rows
+        if rows > ws.max_rows:
+            raise ValueError(f"packet of {rows} rows exceeds workspace ({ws.max_rows})")
+        x = F.embed_w8(p.ids, self.w.embed_q, self.w.embed_s, out=ws.hidden)
+        ws.resid[:rows].zero_()
+        F.rope_table(p.row_pos, cfg.head_dim, cfg.rope_theta, ws.cos, ws.sin, rows=rows)
+        for i, lw in enumerate(self.w.layers):
+            if lw.kind == "attn":
+                x = self._attention_block(lw, self._attn_index[i], x, p, rows, True)
+            else:
+                x = self.layer_hooks["gdn"](self, lw, i, x, p, rows)
+            if cfg.experts:
+                x = self.layer_hooks["moe"](self, lw, i, x, p, rows)
+            else:
+                x = self._dense_ffn(lw, x, rows)
+        return x
+
+    def logits(self, p: Packet, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """fp32 logits [n_sel, vocab] of the selected rows (final norm + W8 head)."""
+        cfg, ws = self.cfg, self.ws
+        x = self.forward_hidden(p)
+        rows = p.rows
+        if p.logit_rows is not None:
+            sel = p.logit_rows
+            xs = x[:rows].index_select(0, sel).contiguous()
+            rs = ws.resid[:rows].index_select(0, sel).contiguous()
+            rows = sel.shape[0]
+        else:
+            xs, rs = x, ws.resid
+        q8, sc = F.act_prep(xs, rs, self.w.final_norm, self.w.head.signs, eps=cfg.eps,
+                            zero_centered=cfg.zero_centered_norm, rows=rows,
+                            q_out=ws.q8[cfg.hidden], scale_out=ws.scale)
+        if out is None:
+            out = torch.empty(rows, self.w.head.n, dtype=torch.float32, device=self.device)
+        return F.qgemm(q8, sc, self.w.head.codes, self.w.head.scale, self.w.head.fmt,
+                       self.w.head.n, out=out, out_f32=True, rows=rows)
+
+    def greedy(self, p: Packet, logits_out=None, token_out=None):
+        lg = self.logits(p, logits_out)
+        return F.argmax(lg, out=token_out), lg

@@ -1,0 +1,170 @@
+"""Tensor-level wrappers of the CUDA kernels (one function per device op).
+
+Every wrapper validates shapes/dtypes, takes optional preallocated outputs (so a
+captured CUDA graph owns static buffers) and launches on the current stream.
+The matching fp32 PyTorch statement of each op lives in ``orinfer_b200.ref.ops_ref``.
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import native
+from .native import FMT, check, count_launches, ptr, stream
+
+
+def _cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise native.KernelError("device op called with a CPU tensor")
+
+
+def embed_w8(ids: torch.Tensor, table_q: torch.Tensor, table_s: torch.Tensor,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _cuda(ids, table_q, table_s)
+    rows, hidden = ids.shape[0], table_q.shape[1]
+    assert ids.dtype == torch.int32 and table_q.dtype == torch.int8 and table_s.dtype == torch.float16
+    if out is None:
+        out = torch.empty(rows, hidden, dtype=torch.float16, device=ids.device)
+    check(native.lib().orinfer_embed_w8(ptr(ids), ptr(table_q), ptr(table_s), ptr(out), rows,
+                                        hidden, table_q.shape[0], stream()), "embed_w8")
+    count_launches(1)
+    return out
+
+
+def act_prep(x: Optional[torch.Tensor], resid: Optional[torch.Tensor],
+             norm_w: Optional[torch.Tensor], signs: Optional[torch.Tensor], *, eps: float = 1e-6,
+             zero_centered: bool = False, swiglu: bool = False, rows: Optional[int] = None,
+             q_out: Optional[torch.Tensor] = None, scale_out: Optional[torch.Tensor] = None,
+             y_out: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """residual add (in place into ``resid``) -> RMSNorm -> (SwiGLU) -> rotation -> A8."""
+    _cuda(x, resid, norm_w, signs)
+    ref = x if x is not None else resid
+    rows = ref.shape[0] if rows is None else rows
+    k = ref.shape[1] // 2 if swiglu else ref.shape[1]
+    if x is not None:
+        assert x.dtype == torch.float16 and x.is_contiguous()
+    if resid is not None:
+        assert resid.dtype == torch.float32 and resid.is_contiguous() and not swiglu
+    if q_out is None:
+        q_out = torch.empty(ref.shape[0], k, dtype=torch.int8, device=ref.device)
+    if scale_out is None:
+        scale_out = torch.empty(ref.shape[0], dtype=torch.float32, device=ref.device)
+    check(native.lib().orinfer_act_prep(ptr(x), ptr(resid), ptr(norm_w), ptr(signs), ptr(q_out),
+                                        ptr(scale_out), ptr(y_out), rows, k, float(eps),
+                                        int(zero_centered), int(swiglu), stream()), "act_prep")
+    count_launches(1)
+    return q_out, scale_out
+
+
+def rope_table(positions: torch.Tensor, head_dim: int, theta: float,
+               cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
+               rows: Optional[int] = None):
+    _cuda(positions)
+    assert positions.dtype == torch.int32
+    n = positions.shape[0]
+    if cos is None:
+        cos = torch.empty(n, head_dim // 2, dtype=torch.float32, device=positions.device)
+        sin = torch.empty_like(cos)
+    check(native.lib().orinfer_rope_table(ptr(positions), ptr(cos), ptr(sin),
+                                          n if rows is None else rows, head_dim, float(theta),
+                                          stream()), "rope_table")
+    count_launches(1)
+    return cos, sin
+
+
+def qk_rope_kv(qkv: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor],
+               cos: torch.Tensor, sin: torch.Tensor, row_req: torch.Tensor, row_pos: torch.Tensor,
+               page_table: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+               kscale: torch.Tensor, vscale: torch.Tensor, *, qh: int, kvh: int, head_dim: int,
+               gated: bool = False, eps: float = 1e-6, zero_centered: bool = False,
+               q_out: Optional[torch.Tensor] = None, gate_out: Optional[torch.Tensor] = None,
+               rows: Optional[int] = None):
+    """Per-head RMSNorm of q/k, NeoX RoPE, and the INT8 group-64 write of K/V into
+    the paged cache ``[pages, 128, kvh, D]`` (scales ``[pages, 128, kvh, D/64]``)."""
+    _cuda(qkv, cos, row_req, page_table, kcache)
+    n = qkv.shape[0]
+    assert qkv.dtype == torch.float16 and qkv.is_contiguous()
+    assert row_req.dtype == torch.int32 and row_pos.dtype == torch.int32
+    assert page_table.dtype == torch.int32 and page_table.dim() == 2
+    if q_out is None:
+        q_out = torch.empty(n, qh, head_dim, dtype=torch.float16, device=qkv.device)
+    if gated and gate_out is None:
+        gate_out = torch.empty_like(q_out)
+    check(native.lib().orinfer_qk_rope_kv(
+        ptr(qkv), ptr(wq), ptr(wk), ptr(cos), ptr(sin), ptr(row_req), ptr(row_pos),
+        ptr(page_table), page_table.shape[1], n if rows is None else rows, qh, kvh, head_dim,
+        int(gated), float(eps), int(zero_centered), ptr(q_out), ptr(gate_out), ptr(kcache),
+        ptr(vcache), ptr(kscale), ptr(vscale), kcache.shape[0], stream()), "qk_rope_kv")
+    count_launches(1)
+    return q_out, gate_out
+
+
+def qgemm(a: torch.Tensor, a_scale: torch.Tensor, codes: torch.Tensor, w_scale: torch.Tensor,
+          fmt: str, n: int, *, out: Optional[torch.Tensor] = None, out_f32: bool = False,
+          rows: Optional[int] = None, path: int = 0) -> torch.Tensor:
+    """out[m, n] = (sum_k a[m,k] * W[n,k]) * w_scale[n] * a_scale[m].
+
+    ``path``: 0 auto, 1 SIMT dp4a kernel, 2 tcgen05 tensor-core kernel."""
+    _cuda(a, a_scale, codes, w_scale)
+    m, k = a.shape
+    assert a.dtype == torch.int8 and a.is_contiguous() and a_scale.dtype == torch.float32
+    assert w_scale.dtype == torch.float16 and codes.is_contiguous()
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.float32 if out_f32 else torch.float16, device=a.device)
+    else:
+        assert out.dtype == (torch.float32 if out_f32 else torch.float16)
+    mm = m if rows is None else rows
+    check(native.lib().orinfer_qgemm(FMT[fmt], ptr(a), ptr(a_scale), ptr(codes), ptr(w_scale),
+                                     ptr(out), mm, n, k, int(out_f32), path, stream()), "qgemm")
+    count_launches(1 if (path == 2 or (path == 0 and mm > 8)) else (mm + 7) // 8)
+    return out
+
+
+def attention_splits(max_kv_len: int, rows: int, kvh: int) -> int:
+    """Split the key axis when there are too few (row, kv head) CTAs to fill 148 SMs."""
+    if max_kv_len <= 256:
+        return 1
+    want = max(1, (148 * 2) // max(rows * kvh, 1))
+    return int(max(1, min(want, (max_kv_len + 255) // 256, 32)))
+
+
+def attention(q: torch.Tensor, gate: Optional[torch.Tensor], row_req: torch.Tensor,
+              row_pos: torch.Tensor, page_table: torch.Tensor, kcache: torch.Tensor,
+              vcache: torch.Tensor, kscale: torch.Tensor, vscale: torch.Tensor, *, splits: int = 1,
+              scratch: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+              rows: Optional[int] = None) -> torch.Tensor:
+    _cuda(q, row_req, page_table, kcache)
+    n, qh, d = q.shape
+    kvh = kcache.shape[2]
+    if out is None:
+        out = torch.empty(n, qh * d, dtype=torch.float16, device=q.device)
+    if splits > 1 and scratch is None:
+        need = native.lib().orinfer_attention_scratch_bytes(n, qh, d, splits)
+        scratch = torch.empty(need // 4, dtype=torch.float32, device=q.device)
+    check(native.lib().orinfer_attention(
+        ptr(q), ptr(gate), ptr(row_req), ptr(row_pos), ptr(page_table), page_table.shape[1],
+        ptr(kcache), ptr(vcache), ptr(kscale), ptr(vscale), ptr(out), n if rows is None else rows,
+        qh, kvh, d, splits, ptr(scratch), stream()), "attention")
+    count_launches(2 if splits > 1 else 1)
+    return out
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None,
+           scratch: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+           rows: Optional[int] = None) -> torch.Tensor:
+    _cuda(logits)
+    m, v = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    parts = native.lib().orinfer_argmax_parts(v)
+    if scratch is None:
+        scratch = (torch.empty(m * parts, dtype=torch.float32, device=logits.device),
+                   torch.empty(m * parts, dtype=torch.int32, device=logits.device))
+    if out is None:
+        out = torch.empty(m, dtype=torch.int32, device=logits.device)
+    check(native.lib().orinfer_argmax(ptr(logits), m if rows is None else rows, v, ptr(scratch[0]),
+                                      ptr(scratch[1]), ptr(out), stream()), "argmax")
+    count_launches(2)
+    return out

@@ -1,0 +1,129 @@
+"""ctypes binding of ``liborinfer_kernels.so`` (the sm_100a kernel library).
+
+Kernels take raw device pointers plus the current CUDA stream, so launches made
+inside ``torch.cuda.graph`` capture are recorded like any other.  There is no
+PyTorch fallback: on a machine with a GPU a missing library is an error.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_double, c_float, c_int, c_longlong, c_size_t, c_void_p
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parents[1] / "_native" / "liborinfer_kernels.so"
+_lib: Optional[ctypes.CDLL] = None
+_launches = 0           # kernels launched through this binding (for benchmark accounting)
+
+FMT = {"w8": 0, "q4": 1, "q2": 2}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _load() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _LIB_PATH.exists():
+        raise KernelError(
+            f"{_LIB_PATH} is missing: run `python -m orinfer_b200.ops.build` "
+            "(there is no non-CUDA fallback for the device ops)")
+    lib = ctypes.CDLL(str(_LIB_PATH))
+    P, I = c_void_p, c_int
+    sig = {
+        "orinfer_init": ([], I),
+        "orinfer_read_status": ([P], I),
+        "orinfer_clear_status": ([], I),
+        "orinfer_e8p_basis_host": ([P], I),
+        "orinfer_embed_w8": ([P, P, P, P, I, I, I, P], I),
+        "orinfer_act_prep": ([P, P, P, P, P, P, P, I, I, c_float, I, I, P], I),
+        "orinfer_rope_table": ([P, P, P, I, I, c_double, P], I),
+        "orinfer_qk_rope_kv": ([P, P, P, P, P, P, P, P, I, I, I, I, I, I, c_float, I, P, P, P, P,
+                                P, P, I, P], I),
+        "orinfer_argmax_parts": ([I], I),
+        "orinfer_argmax": ([P, I, I, P, P, P, P], I),
+        "orinfer_qgemm": ([I, P, P, P, P, P, I, I, I, I, I, P], I),
+        "orinfer_attention_scratch_bytes": ([I, I, I, I], c_size_t),
+        "orinfer_attention": ([P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, P, P], I),
+        "orinfer_e8p_encode": ([P, P, c_longlong, P], I),
+    }
+    for name, (args, res) in sig.items():
+        if hasattr(lib, name):
+            fn = getattr(lib, name)
+            fn.argtypes, fn.restype = args, res
+    _lib = lib
+    return lib
+
+
+def loaded() -> bool:
+    try:
+        _load()
+        return True
+    except (KernelError, OSError):
+        return False
+
+
+def has(symbol: str) -> bool:
+    return loaded() and hasattr(_lib, symbol)
+
+
+def lib() -> ctypes.CDLL:
+    return _load()
+
+
+def launches() -> int:
+    return _launches
+
+
+def count_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
+def ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        detail = "invalid argument" if code < 0 else f"cudaError {code}"
+        raise KernelError(f"{what} failed: {detail} ({code})")
+
+
+def init() -> None:
+    check(_load().orinfer_init(), "orinfer_init")
+
+
+def read_status() -> int:
+    """Synchronise and return the device status word (0 = no bounded wait ran out)."""
+    buf = (c_int * 4)()
+    check(_load().orinfer_read_status(buf), "orinfer_read_status")
+    return int(buf[0])
+
+
+def clear_status() -> None:
+    check(_load().orinfer_clear_status(), "orinfer_clear_status")
+
+
+def basis_host() -> torch.Tensor:
+    out = torch.empty(256, 8, dtype=torch.int8)
+    check(_load().orinfer_e8p_basis_host(out.data_ptr()), "orinfer_e8p_basis_host")
+    return out
+
+
+def e8p_encode(x: torch.Tensor) -> torch.Tensor:
+    assert x.is_cuda and x.dtype == torch.float32 and x.shape[-1] == 8 and x.is_contiguous()
+    codes = torch.empty(x.shape[0], dtype=torch.int32, device=x.device)
+    check(_load().orinfer_e8p_encode(x.data_ptr(), codes.data_ptr(), x.shape[0], stream()),
+          "orinfer_e8p_encode")
+    count_launches(1)
+    return codes

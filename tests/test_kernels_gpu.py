@@ -1,0 +1,248 @@
+"""CUDA kernels against the plain PyTorch fp32 statement of the same op."""
+import math
+
+import pytest
+import torch
+
+from orinfer_b200.quant import e8p_torch
+from orinfer_b200.ref import ops_ref as R
+
+pytestmark = pytest.mark.gpu
+
+
+def _signs(k, dev, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return (1 - 2 * torch.randint(0, 2, (k,), generator=g)).to(torch.int8).to(dev)
+
+
+def _codes_close(q, q_ref, frac=0.01):
+    d = (q.int() - q_ref.int()).abs()
+    assert int(d.max()) <= 1, f"max code diff {int(d.max())}"
+    assert float((d > 0).float().mean()) <= frac
+
+
+def test_basis_matches_python(cuda):
+    from orinfer_b200.ops import native
+    from orinfer_b200.quant import e8p
+    assert torch.equal(native.basis_host(), torch.from_numpy(e8p.basis().copy()))
+
+
+def test_embed_w8(cuda):
+    from orinfer_b200.ops import functional as F
+    g = torch.Generator().manual_seed(0)
+    table = torch.randint(-127, 128, (300, 256), generator=g, dtype=torch.int8).to(cuda)
+    scale = (torch.rand(300, generator=g) * 0.01 + 1e-3).half().to(cuda)
+    ids = torch.randint(0, 300, (37,), generator=g, dtype=torch.int32).to(cuda)
+    out = F.embed_w8(ids, table, scale)
+    assert torch.equal(out.float(), R.embed_w8(ids, table, scale))
+
+
+@pytest.mark.parametrize("k", [128, 256, 2560])
+@pytest.mark.parametrize("mode", ["norm_rot", "rot", "norm", "plain", "zero"])
+def test_act_prep(cuda, k, mode):
+    from orinfer_b200.ops import functional as F
+    g = torch.Generator().manual_seed(k)
+    m = 19
+    x = (torch.randn(m, k, generator=g) * 0.5).half().to(cuda)
+    if mode == "zero":
+        x.zero_()
+    resid = torch.randn(m, k, generator=g).to(cuda) if mode in ("norm_rot", "norm") else None
+    w = (1 + 0.1 * torch.randn(k, generator=g)).half().to(cuda) if "norm" in mode else None
+    sg = _signs(k, cuda) if "rot" in mode else None
+    r_in = None if resid is None else resid.clone()
+    y_out = torch.empty(m, k, dtype=torch.float16, device=cuda)
+    q, s = F.act_prep(x, resid, w, sg, eps=1e-6, y_out=y_out)
+    q_ref, s_ref, r_ref, y_ref = R.act_prep(x, r_in, w, sg, 1e-6)
+    assert torch.allclose(s, s_ref, rtol=2e-3, atol=0)
+    if resid is not None:
+        assert torch.allclose(resid, r_ref, atol=1e-6)
+    assert float((y_out.float() - y_ref).abs().max()) <= 2e-3 * max(1.0, float(y_ref.abs().max()))
+    _codes_close(q, q_ref, 0.02)
+
+
+def test_act_prep_swiglu(cuda):
+    from orinfer_b200.ops import functional as F
+    g = torch.Generator().manual_seed(3)
+    m, f = 11, 512
+    gu = torch.randn(m, 2 * f, generator=g).half().to(cuda)
+    sg = _signs(f, cuda)
+    q, s = F.act_prep(gu, None, None, sg, swiglu=True)
+    q_ref, s_ref, _, _ = R.act_prep(gu, None, None, sg, swiglu=True)
+    assert torch.allclose(s, s_ref, rtol=2e-3)
+    _codes_close(q, q_ref, 0.02)
+
+
+def _rand_weight(fmt, n, k, dev, seed):
+    g = torch.Generator().manual_seed(seed)
+    ws = (torch.rand(n, generator=g) * 0.01 + 1e-3).half().to(dev)
+    if fmt == "w8":
+        codes = torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8).to(dev)
+        return codes, ws, codes
+    if fmt == "q4":
+        codes = torch.randint(-2 ** 31, 2 ** 31 - 1, (k // 128, n, 16), generator=g,
+                              dtype=torch.int64).to(torch.int32).to(dev)
+        rows = codes.permute(1, 0, 2).reshape(n, k // 8).to(torch.int64) & 0xFFFFFFFF
+        w_int = (4 * e8p_torch.decode_t(rows & 0xFFFF).to(torch.int32)
+                 + e8p_torch.decode_t(rows >> 16).to(torch.int32)).reshape(n, k).to(torch.int8)
+        return codes, ws, w_int
+    codes = torch.randint(-2 ** 15, 2 ** 15 - 1, (k // 128, n, 16), generator=g,
+                          dtype=torch.int64).to(torch.int16).to(dev)
+    rows = codes.permute(1, 0, 2).reshape(n, k // 8).to(torch.int64) & 0xFFFF
+    return codes, ws, e8p_torch.decode_t(rows).reshape(n, k)
+
+
+@pytest.mark.parametrize("fmt", ["w8", "q4", "q2"])
+@pytest.mark.parametrize("m,n,k,path", [
+    (1, 256, 256, 1), (3, 136, 128, 1), (8, 2560, 1024, 1), (5, 256, 512, 2),
+    (16, 128, 128, 2), (128, 384, 1024, 2), (200, 2560, 2560, 2), (512, 1536, 1280, 0),
+])
+def test_qgemm(cuda, fmt, m, n, k, path):
+    from orinfer_b200.ops import functional as F
+    g = torch.Generator().manual_seed(m * 7 + n)
+    a = torch.randint(-127, 128, (m, k), generator=g, dtype=torch.int8).to(cuda)
+    sa = (torch.rand(m, generator=g) * 0.05 + 1e-3).to(cuda)
+    codes, ws, w_int = _rand_weight(fmt, n, k, cuda, seed=k + n)
+    for f32 in (False, True):
+        out = F.qgemm(a, sa, codes, ws, fmt, n, out_f32=f32, path=path)
+        ref = R.qgemm(a, sa, w_int, ws, out_f32=f32)
+        torch.cuda.synchronize()
+        assert torch.equal(out.float(), ref), \
+            f"max diff {float((out.float() - ref).abs().max())}"
+
+
+def test_qgemm_graph_replay_changed_inputs(cuda):
+    """Capture once, replay with different activation contents."""
+    from orinfer_b200.ops import functional as F
+    m, n, k = 64, 256, 512
+    a = torch.zeros(m, k, dtype=torch.int8, device=cuda)
+    sa = torch.ones(m, device=cuda)
+    codes, ws, w_int = _rand_weight("q4", n, k, cuda, 5)
+    out = torch.empty(m, n, dtype=torch.float16, device=cuda)
+    F.qgemm(a, sa, codes, ws, "q4", n, out=out)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        F.qgemm(a, sa, codes, ws, "q4", n, out=out)
+    for seed in (1, 2):
+        g = torch.Generator().manual_seed(seed)
+        a.copy_(torch.randint(-127, 128, (m, k), generator=g, dtype=torch.int8))
+        sa.copy_(torch.rand(m, generator=g) * 0.1 + 0.01)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out.float(), R.qgemm(a, sa, w_int, ws))
+
+
+def _paged_setup(cuda, lens, kvh, d, seed=0):
+    """Random INT8 KV for requests of the given lengths, scattered over pages."""
+    g = torch.Generator().manual_seed(seed)
+    n_req = len(lens)
+    pages_per = [(l + 127) // 128 for l in lens]
+    total = sum(pages_per) + 1
+    perm = (torch.randperm(total - 1, generator=g) + 1).tolist()
+    table = torch.zeros(n_req, max(pages_per), dtype=torch.int32)
+    it = iter(perm)
+    for r, npg in enumerate(pages_per):
+        for j in range(npg):
+            table[r, j] = next(it)
+    kc = torch.randint(-127, 128, (total, 128, kvh, d), generator=g, dtype=torch.int8)
+    vc = torch.randint(-127, 128, (total, 128, kvh, d), generator=g, dtype=torch.int8)
+    ks = (torch.rand(total, 128, kvh, d // 64, generator=g) * 0.02 + 1e-3).half()
+    vs = (torch.rand(total, 128, kvh, d // 64, generator=g) * 0.02 + 1e-3).half()
+    return table.to(cuda), kc.to(cuda), vc.to(cuda), ks.to(cuda), vs.to(cuda)
+
+
+def _gather_kv(table, cache, scale, req, length):
+    pos = torch.arange(length, device=cache.device)
+    pages = table[req, pos // 128].long()
+    return R.kv_dequant(cache[pages, pos % 128], scale[pages, pos % 128])
+
+
+@pytest.mark.parametrize("qh,kvh,d", [(4, 2, 64), (32, 8, 128), (40, 8, 128), (16, 2, 256)])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_attention_rows(cuda, qh, kvh, d, splits):
+    from orinfer_b200.ops import functional as F
+    lens = [1, 130, 300]
+    table, kc, vc, ks, vs = _paged_setup(cuda, lens, kvh, d)
+    g = torch.Generator().manual_seed(1)
+    # rows: last row of request 0, last 3 rows of request 1, rows 100..101 of request 2
+    row_req = torch.tensor([0, 1, 1, 1, 2, 2], dtype=torch.int32, device=cuda)
+    row_pos = torch.tensor([0, 127, 128, 129, 100, 299], dtype=torch.int32, device=cuda)
+    q = torch.randn(6, qh, d, generator=g).half().to(cuda)
+    gate = torch.randn(6, qh, d, generator=g).half().to(cuda) if d == 256 else None
+    out = F.attention(q, gate, row_req, row_pos, table, kc, vc, ks, vs, splits=splits)
+    for i in range(6):
+        r, pos = int(row_req[i]), int(row_pos[i])
+        k = _gather_kv(table, kc, ks, r, pos + 1)
+        v = _gather_kv(table, vc, vs, r, pos + 1)
+        ref = R.causal_gqa(q[i:i + 1], k, v, pos, None if gate is None else gate[i:i + 1])
+        assert torch.allclose(out[i].float(), ref[0], atol=2e-3, rtol=2e-3), \
+            f"row {i}: {float((out[i].float() - ref[0]).abs().max())}"
+
+
+@pytest.mark.parametrize("qh,kvh,d,gated", [(4, 2, 64, False), (32, 8, 128, False),
+                                             (16, 2, 256, True)])
+def test_qk_rope_kv(cuda, qh, kvh, d, gated):
+    from orinfer_b200.ops import functional as F
+    g = torch.Generator().manual_seed(2)
+    rows = 9
+    width = qh * d * (2 if gated else 1) + 2 * kvh * d
+    qkv = torch.randn(rows, width, generator=g).half().to(cuda)
+    wq = (1 + 0.1 * torch.randn(d, generator=g)).half().to(cuda)
+    wk = (1 + 0.1 * torch.randn(d, generator=g)).half().to(cuda)
+    row_req = torch.tensor([0, 0, 0, 1, 1, 1, 1, 1, 1], dtype=torch.int32, device=cuda)
+    row_pos = torch.tensor([126, 127, 128, 0, 1, 2, 3, 4, 5], dtype=torch.int32, device=cuda)
+    table = torch.tensor([[3, 1], [2, 0]], dtype=torch.int32, device=cuda)
+    kc = torch.zeros(4, 128, kvh, d, dtype=torch.int8, device=cuda)
+    vc = torch.zeros_like(kc)
+    ks = torch.zeros(4, 128, kvh, d // 64, dtype=torch.float16, device=cuda)
+    vs = torch.zeros_like(ks)
+    cos, sin = F.rope_table(row_pos, d, 1e6)
+    cos_r, sin_r = R.rope_tables(row_pos, d, 1e6)
+    assert torch.allclose(cos, cos_r, atol=1e-6) and torch.allclose(sin, sin_r, atol=1e-6)
+    q_out, gate_out = F.qk_rope_kv(qkv, wq, wk, cos, sin, row_req, row_pos, table, kc, vc, ks, vs,
+                                   qh=qh, kvh=kvh, head_dim=d, gated=gated)
+    qs = d * (2 if gated else 1)
+    qraw = qkv[:, :qh * qs].reshape(rows, qh, qs)
+    q_ref = R.qk_norm_rope(qraw[..., :d], wq, cos_r, sin_r, 1e-6, False)
+    assert float((q_out.float() - q_ref).abs().max()) <= 4e-3
+    if gated:
+        assert torch.equal(gate_out, qraw[..., d:].contiguous())
+    kraw = qkv[:, qh * qs:qh * qs + kvh * d].reshape(rows, kvh, d)
+    vraw = qkv[:, qh * qs + kvh * d:].reshape(rows, kvh, d)
+    k_ref = R.qk_norm_rope(kraw, wk, cos_r, sin_r, 1e-6, False)
+    kq_ref, ks_ref = R.kv_quant(k_ref)
+    vq_ref, vs_ref = R.kv_quant(R.f16(vraw.float()))
+    for i in range(rows):
+        page = int(table[int(row_req[i]), int(row_pos[i]) // 128])
+        slot = int(row_pos[i]) % 128
+        assert torch.equal(vc[page, slot], vq_ref[i])
+        assert torch.equal(vs[page, slot].float(), vs_ref[i])
+        assert torch.allclose(ks[page, slot].float(), ks_ref[i], rtol=2e-3)
+        deq = R.kv_dequant(kc[page, slot], ks[page, slot])
+        assert float((deq - k_ref[i]).abs().max()) <= 1.5 * float(ks_ref[i].max()) + 4e-3
+
+
+def test_argmax(cuda):
+    from orinfer_b200.ops import functional as F
+    g = torch.Generator().manual_seed(4)
+    for vocab in (1024, 5000, 151936):
+        lg = torch.randn(5, vocab, generator=g).to(cuda)
+        lg[1, 7] = lg[1, 900] = 50.0          # tie -> lowest index
+        lg[2, vocab - 1] = 99.0
+        tok = F.argmax(lg)
+        assert torch.equal(tok, R.argmax_lowest(lg))
+        assert int(tok[1]) == 7 and int(tok[2]) == vocab - 1
+    lg[3, 5] = float("nan")
+    assert int(F.argmax(lg)[3]) == -1
+
+
+def test_e8p_encode_kernel(cuda):
+    from orinfer_b200.ops import native
+    g = torch.Generator().manual_seed(6)
+    x = (torch.randn(5000, 8, generator=g) * 4).to(cuda)
+    codes = native.e8p_encode(x)
+    ref = e8p_torch.encode_nearest_t(x)
+    d_mine = ((x - e8p_torch.decode_t(codes).float()) ** 2).sum(1)
+    d_ref = ((x - e8p_torch.decode_t(ref).float()) ** 2).sum(1)
+    assert float((d_mine - d_ref).abs().max()) < 1e-3
+    assert float((codes == ref).float().mean()) > 0.995
