@@ -1,0 +1,469 @@
+"""Continuous-batching engine: admission, chunked prefill, mixed packets, decode
+CUDA graphs, prefix reuse and per-request sampling.
+
+One iteration (``step``) is one forward packet, as in the reference's
+``advance_requests_with`` (crates/orinfer-engine/src/runtime/requests.rs:1386-1658):
+
+1. retire finished / cancelled requests (store their prefix, free pages);
+2. admit waiting requests while slots, pages and the memory reserve allow
+   (``can_admit``: prospective KV for prompt + max_new, requests.rs:392-459),
+   evicting cached prefixes under pressure;
+3. select work: decode rows of every running request plus prefill chunks up to
+   the packet budget (latency policy keeps chunks within the prefill budget;
+   throughput policy fills the packet);
+4. run the packet (captured CUDA graph when it is pure decode and graphs are on);
+5. commit: greedy rows read tokens written by the device argmax in one readback,
+   other rows go through the host sampling law with counter RNG keyed by
+   (seed, committed position).
+
+Requests never share mutable state: KV pages are private except for read-only
+full prefix pages, and sampling depends only on the request's own history.
+"""
+
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..config import PAGE_TOKENS, GraphMode, LoadOptions, ModelConfig, Phase as ExecPhase, Policy, \
+    SchedulerOptions
+from ..core import sampling as S
+from ..core.prefix import RadixPrefixCache
+from ..models.runner import KVPool, Packet
+from ..models.weights import ModelWeights
+from .pages import OutOfPages, PagePool
+from .request import Phase, Request
+
+DECODE_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128)
+
+
+@dataclass
+class EngineStatistics:
+    iterations: int = 0
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    graph_hits: int = 0
+    graph_captures: int = 0
+    direct_packets: int = 0
+    admitted: int = 0
+    deferred_admissions: int = 0
+    finished: int = 0
+    cancelled: int = 0
+    capture_s: float = 0.0
+    replay_s: float = 0.0
+    direct_s: float = 0.0
+    batch_inputs_s: float = 0.0
+    batch_commit_s: float = 0.0
+    evicted_pages: int = 0
+
+    def as_dict(self) -> dict:
+        return dict(self.__dict__)
+
+
+class _DecodeGraph:
+    """Static buffers + captured graph of a pure-decode packet of ``rows`` rows."""
+
+    def __init__(self, engine: "Engine", rows: int):
+        dev = engine.device
+        z = lambda *s, dt=torch.int32: torch.zeros(*s, dtype=dt, device=dev)
+        self.rows = rows
+        self.ids, self.req, self.pos = z(rows), z(rows), z(rows)
+        self.tokens = z(rows)
+        self.logits = torch.zeros(rows, engine.cfg.vocab, dtype=torch.float32, device=dev)
+        self.packet = Packet(self.ids, self.req, self.pos, engine.page_table_dev, rows,
+                             engine.max_context)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.trials = 0
+
+
+class Engine:
+    def __init__(self, weights: ModelWeights, *, load: Optional[LoadOptions] = None,
+                 sched: Optional[SchedulerOptions] = None, kv_pages: Optional[int] = None,
+                 max_context: Optional[int] = None, max_rows: Optional[int] = None,
+                 runner=None):
+        self.w = weights
+        self.cfg: ModelConfig = weights.config
+        self.load = load or LoadOptions()
+        self.sched = sched or SchedulerOptions()
+        self.load.validate()
+        self.sched.validate()
+        self.device = weights.embed_q.device
+        self.on_gpu = self.device.type == "cuda"
+        self.max_context = max_context or min(self.cfg.max_context, 32768)
+        self.max_pages_per_req = (self.max_context + PAGE_TOKENS - 1) // PAGE_TOKENS
+        self.max_rows = max_rows or max(self.sched.prefill_chunk + self.sched.max_active, 256)
+        extra = self.cfg.mtp_layers
+        if kv_pages is None:
+            kv_pages = self._auto_pages(extra)
+        self.pool = PagePool(kv_pages)
+        self.kv = KVPool.allocate(self.cfg, kv_pages, self.device, extra_layers=extra)
+        if runner is not None:
+            self.runner = runner(weights, self.kv, self.max_rows)
+        elif self.on_gpu:
+            from ..models.runner import ModelRunner
+            self.runner = ModelRunner(weights, self.kv, self.max_rows)
+        else:
+            from ..models.torch_runner import TorchRunner
+            self.runner = TorchRunner(weights, self.kv, self.max_rows)
+        slots = self.sched.max_active + 1                      # last slot = padding target
+        self.page_table_host = np.zeros((slots, self.max_pages_per_req), np.int32)
+        self.page_table_dev = torch.zeros(slots, self.max_pages_per_req, dtype=torch.int32,
+                                          device=self.device)
+        self.free_slots: List[int] = list(range(self.sched.max_active - 1, -1, -1))
+        self.pad_slot = self.sched.max_active
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []
+        self.prefix = RadixPrefixCache(PAGE_TOKENS) if self.load.prefix_cache_bytes > 0 else None
+        self._prefix_nodes: Dict[int, List[int]] = {}
+        self.stats = EngineStatistics()
+        self._graphs: Dict[int, _DecodeGraph] = {}
+        self._next_rid = 1
+        self._pin = {}
+        self.tpot_ewma: Optional[float] = None
+
+    # ------------------------------------------------------------------ sizing
+    def _auto_pages(self, extra_layers: int) -> int:
+        per_page = KVPool.bytes_per_page(self.cfg, extra_layers)
+        if self.on_gpu:
+            free, _total = torch.cuda.mem_get_info(self.device)
+            budget = max(free - self.sched.memory_reserve_bytes - (8 << 30), per_page * 64)
+            budget = min(budget, 64 << 30)
+        else:
+            budget = 64 << 20
+        want = self.sched.max_active * self.max_pages_per_req + 1
+        return int(max(4, min(budget // per_page, want)))
+
+    # ------------------------------------------------------------------ public API
+    def submit(self, prompt: Sequence[int], max_new: int = 16,
+               sampling: Optional[S.SamplingOptions] = None, **kw) -> Request:
+        if len(prompt) == 0:
+            raise ValueError("empty prompt")
+        if len(prompt) + max_new > self.max_context:
+            raise ValueError(
+                f"request of {len(prompt)} + {max_new} tokens exceeds the context window "
+                f"({self.max_context})")
+        sampling = sampling or S.SamplingOptions(temperature=0.0)
+        sampling.validate()
+        req = Request(self._next_rid, list(map(int, prompt)), int(max_new), sampling, **kw)
+        self._next_rid += 1
+        self.waiting.append(req)
+        return req
+
+    def cancel(self, req: Request) -> None:
+        req.cancelled = True
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def generate(self, prompts: Sequence[Sequence[int]], max_new: int = 16,
+                 sampling: Optional[S.SamplingOptions] = None, **kw) -> List[List[int]]:
+        reqs = [self.submit(p, max_new, sampling, **kw) for p in prompts]
+        while any(not r.finished for r in reqs):
+            self.step()
+        return [r.generated for r in reqs]
+
+    # ------------------------------------------------------------------ admission
+    def _pages_needed(self, req: Request) -> int:
+        return (req.context_needed() + PAGE_TOKENS - 1) // PAGE_TOKENS
+
+    def can_admit(self, req: Request, shared_pages: int = 0) -> bool:
+        return bool(self.free_slots) and \
+            self._pages_needed(req) - shared_pages <= self.pool.available
+
+    def _reclaim(self, pages: int) -> None:
+        """Evict cached prefixes (lowest utility first) until ``pages`` are free."""
+        if self.prefix is None:
+            return
+        short = pages - self.pool.available
+        if short <= 0:
+            return
+        victims = self.prefix.evict(short, to_host=False)
+        self.pool.release([p for _, p in victims])
+        self.stats.evicted_pages += len(victims)
+
+    def _admit(self) -> None:
+        started = time.monotonic()
+        admitted = 0
+        while self.waiting and len(self.running) < self.sched.max_active:
+            req = self.waiting[0]
+            if req.cancelled:
+                self.waiting.popleft()
+                self._finish(req, "cancelled")
+                continue
+            node_ids, pages = [], []
+            if self.prefix is not None and req.cache_prompt:
+                node_ids, pages = self.prefix.match(req.prompt, limit_tokens=len(req.prompt) - 1)
+                if any(pg < 0 for pg in pages):              # host-resident tail: not restored here
+                    cut = next(i for i, pg in enumerate(pages) if pg < 0)
+                    self.prefix.release(node_ids[cut:])
+                    node_ids, pages = node_ids[:cut], pages[:cut]
+            need = self._pages_needed(req) - len(pages)
+            if need > self.pool.available:
+                self._reclaim(need)
+            if not self.free_slots or need > self.pool.available:
+                if node_ids:
+                    self.prefix.release(node_ids)
+                self.stats.deferred_admissions += 1
+                break
+            self.waiting.popleft()
+            for pg in pages:
+                self.pool.share(pg)
+            req.pages = list(pages) + self.pool.take(need)
+            req.slot = self.free_slots.pop()
+            req.offset = req.cached_tokens = len(pages) * PAGE_TOKENS
+            req.phase = Phase.PREFILL
+            self._prefix_nodes[req.rid] = node_ids
+            row = self.page_table_host[req.slot]
+            row[:] = 0
+            row[:len(req.pages)] = req.pages
+            self.page_table_dev[req.slot].copy_(torch.from_numpy(row), non_blocking=True)
+            self.running.append(req)
+            self.stats.admitted += 1
+            admitted += 1
+            if self._should_yield(admitted, time.monotonic() - started):
+                break
+
+    def _should_yield(self, admitted: int, elapsed: float) -> bool:
+        has_decoders = any(r.phase is Phase.DECODE for r in self.running)
+        if has_decoders:
+            return admitted >= 8 or elapsed >= 0.100
+        return admitted >= 32 or elapsed >= 3.0
+
+    # ------------------------------------------------------------------ retirement
+    def _finish(self, req: Request, reason: str) -> None:
+        req.finish_reason = req.finish_reason or reason
+        req.phase = Phase.FINISHED
+        req.finished_at = time.monotonic()
+        if req.slot >= 0:
+            if self.prefix is not None and req.cache_prompt and reason != "error":
+                # index the full pages of prompt + generated tokens whose KV is in the cache
+                toks = req.history[:req.offset]
+                adopted, _ids = self.prefix.insert(toks, req.pages[:len(toks) // PAGE_TOKENS])
+                for pg, took in zip(req.pages, adopted):
+                    if took:
+                        self.pool.share(pg)
+            if self.prefix is not None:
+                self.prefix.release(self._prefix_nodes.pop(req.rid, []))
+            self.pool.release(req.pages)
+            req.pages = []
+            self.free_slots.append(req.slot)
+            req.slot = -1
+        if reason == "cancelled":
+            self.stats.cancelled += 1
+        else:
+            self.stats.finished += 1
+        if req in self.running:
+            self.running.remove(req)
+
+    # ------------------------------------------------------------------ work selection
+    def _select(self):
+        decoders = [r for r in self.running if r.phase is Phase.DECODE]
+        prefills = [r for r in self.running if r.phase is Phase.PREFILL]
+        budget = max(self.max_rows - len(decoders), 0)
+        budget = min(budget, self.sched.prefill_chunk)
+        chunks = []
+        if self.sched.policy is Policy.LATENCY and decoders and self.tpot_ewma is not None:
+            # keep prompt progress within the prefill budget while decoders are live
+            rate = self._prefill_rate()
+            if rate:
+                budget = min(budget, max(int(rate * self.sched.prefill_budget_ms / 1e3), 16))
+        prefills.sort(key=lambda r: (r.last_prefill_at or r.arrived))
+        for r in prefills:
+            if budget <= 0:
+                break
+            n = min(r.remaining_prefill, budget)
+            chunks.append((r, n))
+            budget -= n
+        return decoders, chunks
+
+    def _prefill_rate(self) -> Optional[float]:
+        return getattr(self, "_prefill_tok_s", None)
+
+    # ------------------------------------------------------------------ one iteration
+    def step(self) -> List[Request]:
+        """Run one packet; returns the requests that produced tokens."""
+        for r in list(self.running):
+            if r.cancelled:
+                self._finish(r, "cancelled")
+        self._admit()
+        decoders, chunks = self._select()
+        if not decoders and not chunks:
+            return []
+        self.stats.iterations += 1
+        t0 = time.monotonic()
+        pure_decode = not chunks
+        use_graph = (self.on_gpu and pure_decode and
+                     self.load.cuda_graph.uses_graph(ExecPhase.DECODE) and
+                     len(decoders) <= DECODE_BUCKETS[-1])
+        if use_graph:
+            tokens, logits, order = self._run_decode_graph(decoders)
+        else:
+            tokens, logits, order = self._run_direct(decoders, chunks)
+        t1 = time.monotonic()
+        produced = self._commit(order, tokens, logits)
+        t2 = time.monotonic()
+        self.stats.batch_commit_s += t2 - t1
+        if pure_decode:
+            dt = t2 - t0
+            self.tpot_ewma = dt if self.tpot_ewma is None else 0.8 * self.tpot_ewma + 0.2 * dt
+        elif chunks:
+            toks = sum(n for _, n in chunks)
+            rate = toks / max(t2 - t0, 1e-6)
+            prev = getattr(self, "_prefill_tok_s", None)
+            self._prefill_tok_s = rate if prev is None else 0.8 * prev + 0.2 * rate
+        return produced
+
+    # ------------------------------------------------------------------ execution
+    def _pinned(self, name: str, n: int) -> torch.Tensor:
+        buf = self._pin.get(name)
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 1024), dtype=torch.int32)
+            if self.on_gpu:
+                buf = buf.pin_memory()
+            self._pin[name] = buf
+        return buf
+
+    def _upload(self, name: str, values: List[int]) -> torch.Tensor:
+        n = len(values)
+        host = self._pinned(name, n)
+        host[:n] = torch.tensor(values, dtype=torch.int32)
+        if not self.on_gpu:
+            return host[:n].clone()
+        return host[:n].to(self.device, non_blocking=True)
+
+    def _run_direct(self, decoders: List[Request], chunks):
+        t0 = time.monotonic()
+        ids, req_rows, pos, logit_rows, order = [], [], [], [], []
+        max_kv = 1
+        for r in decoders:
+            ids.append(r.pending)
+            req_rows.append(r.slot)
+            pos.append(r.offset)
+            logit_rows.append(len(ids) - 1)
+            order.append((r, 1, True))
+            max_kv = max(max_kv, r.offset + 1)
+        for r, n in chunks:
+            ids += r.prompt[r.offset:r.offset + n]
+            req_rows += [r.slot] * n
+            pos += list(range(r.offset, r.offset + n))
+            last = r.offset + n == len(r.prompt)
+            if last:
+                logit_rows.append(len(ids) - 1)
+            order.append((r, n, last))
+            max_kv = max(max_kv, r.offset + n)
+        rows = len(ids)
+        if not logit_rows:
+            logit_rows = [rows - 1]                 # keep shapes simple; result unused
+            dummy_logits = True
+        else:
+            dummy_logits = False
+        packet = Packet(self._upload("ids", ids), self._upload("req", req_rows),
+                        self._upload("pos", pos), self.page_table_dev, rows, max_kv,
+                        self._upload("sel", logit_rows).long())
+        t1 = time.monotonic()
+        self.stats.batch_inputs_s += t1 - t0
+        tok, lg = self.runner.greedy(packet)
+        tokens = tok.cpu()                           # one readback (synchronises)
+        self.stats.direct_packets += 1
+        self.stats.direct_s += time.monotonic() - t1
+        self.stats.prefill_tokens += sum(n for _, n in chunks)
+        if dummy_logits:
+            return None, None, order
+        return tokens, lg, order
+
+    def _run_decode_graph(self, decoders: List[Request]):
+        t0 = time.monotonic()
+        n = len(decoders)
+        bucket = next(b for b in DECODE_BUCKETS if b >= n)
+        g = self._graphs.get(bucket)
+        if g is None:
+            g = self._graphs[bucket] = _DecodeGraph(self, bucket)
+        pad = bucket - n
+        ids = [r.pending for r in decoders] + [0] * pad
+        slots = [r.slot for r in decoders] + [self.pad_slot] * pad
+        pos = [r.offset for r in decoders] + [0] * pad
+        g.ids.copy_(self._upload("ids", ids), non_blocking=True)
+        g.req.copy_(self._upload("req", slots), non_blocking=True)
+        g.pos.copy_(self._upload("pos", pos), non_blocking=True)
+        t1 = time.monotonic()
+        self.stats.batch_inputs_s += t1 - t0
+        if g.graph is None:
+            g.trials += 1
+            self.runner.greedy(g.packet, g.logits, g.tokens)        # warm (lazy inits)
+            if g.trials >= 2:
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    self.runner.greedy(g.packet, g.logits, g.tokens)
+                g.graph = graph
+                self.stats.graph_captures += 1
+                self.stats.capture_s += time.monotonic() - t1
+        else:
+            g.graph.replay()
+            self.stats.graph_hits += 1
+        tokens = g.tokens[:n].cpu()
+        self.stats.replay_s += time.monotonic() - t1
+        order = [(r, 1, True) for r in decoders]
+        return tokens, g.logits, order
+
+    # ------------------------------------------------------------------ commit
+    def _commit(self, order, tokens, logits) -> List[Request]:
+        produced = []
+        sel = 0
+        now = time.monotonic()
+        for r, n, has_logits in order:
+            was_decode = r.phase is Phase.DECODE
+            r.offset += n
+            if not was_decode:
+                r.last_prefill_at = now
+            if not has_logits:
+                continue
+            row = sel
+            sel += 1
+            if was_decode:
+                self.stats.decode_tokens += 1
+            tok = self._sample(r, tokens, logits, row)
+            r.pending = tok
+            r.generated.append(tok)
+            if r.first_token_at is None:
+                r.first_token_at = now
+            r.phase = Phase.DECODE
+            if r.on_token is not None:
+                r.on_token(r, tok)
+            produced.append(r)
+            if tok in r.stop_ids and not r.ignore_eos:
+                self._finish(r, "stop")
+            elif len(r.generated) >= r.max_new:
+                self._finish(r, "length")
+            elif r.constraint is not None and getattr(r.constraint, "finished", lambda: False)():
+                self._finish(r, "stop")
+        return produced
+
+    def _sample(self, r: Request, tokens, logits, row: int) -> int:
+        plain = (r.sampling.is_greedy and r.constraint is None and not r.want_logprobs
+                 and r.sampling.top_logprobs is None)
+        if plain:
+            tok = int(tokens[row])
+            if tok < 0:
+                r.error = "non-finite logits"
+                return 0
+            return tok
+        lg = logits[row].float().cpu().numpy()
+        mask = None
+        if r.constraint is not None:
+            mask = r.constraint.mask(self.cfg.vocab)
+        step = len(r.generated)
+        u = S.counter_uniform(r.sampling.seed, 0, step)
+        tok = S.sample(lg, r.history, r.sampling, u, mask)
+        if r.want_logprobs or r.sampling.top_logprobs is not None:
+            lp, top = S.logprobs(lg, r.history, r.sampling, tok, r.sampling.top_logprobs or 0,
+                                 mask)
+            r.logprobs.append((tok, lp, top))
+        if r.constraint is not None:
+            r.constraint.consume(tok)
+        return tok

@@ -82,12 +82,11 @@ class Workspace:
         self.gate_up = e(max_rows, 2 * max(ffn_w, cfg.shared_expert_ffn, mtp_f, 64))
         self.cos = e(max_rows, cfg.head_dim // 2, dt=f32)
         self.sin = e(max_rows, cfg.head_dim // 2, dt=f32)
-        self.attn_scratch: Optional[torch.Tensor] = None
+        # split-KV partial records: (rows * splits) <= SPLIT_ROWS by construction, and the
+        # buffer never moves, so captured graphs may keep its address.
+        self.attn_scratch = e(self.SPLIT_ROWS * cfg.q_heads * (cfg.head_dim + 2), dt=f32)
 
-    def scratch(self, floats: int, device) -> torch.Tensor:
-        if self.attn_scratch is None or self.attn_scratch.numel() < floats:
-            self.attn_scratch = torch.empty(floats, dtype=torch.float32, device=device)
-        return self.attn_scratch
+    SPLIT_ROWS = 512
 
 
 @dataclass
@@ -142,11 +141,9 @@ class ModelRunner:
                      gated=cfg.gated_attention and lw.qkv.n == cfg.q_dim + 2 * cfg.kv_dim,
                      eps=cfg.eps, zero_centered=cfg.zero_centered_norm, q_out=ws.q,
                      gate_out=ws.gate, rows=rows)
-        splits = F.attention_splits(p.max_kv_len, rows, cfg.kv_heads)
-        scratch = None
-        if splits > 1:
-            scratch = ws.scratch(ws.max_rows * cfg.q_heads * splits * (cfg.head_dim + 2),
-                                 self.device)
+        splits = min(F.attention_splits(p.max_kv_len, rows, cfg.kv_heads),
+                     max(ws.SPLIT_ROWS // rows, 1))
+        scratch = ws.attn_scratch if splits > 1 else None
         gated = cfg.gated_attention and lw.qkv.n == cfg.q_dim + 2 * cfg.kv_dim
         F.attention(ws.q, ws.gate if gated else None, p.row_req, p.row_pos, p.page_table,
                     self.kv.k[kv_slot], self.kv.v[kv_slot], self.kv.ks[kv_slot],

@@ -1,0 +1,134 @@
+"""Packed-row forward in plain PyTorch over the same paged INT8 KV layout.
+
+Drop-in stand-in for :class:`ModelRunner` on machines without a GPU (engine tests,
+the timed CPU baseline) and the batch-invariance oracle for the CUDA path: it is
+built from ``ops_ref`` only, so it computes what the kernels are specified to
+compute.  Plays the role of the reference's single-request generation path used as
+isolation oracle (crates/orinfer-engine/src/runtime/reference_generation.rs:5-6).
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..config import ModelConfig
+from ..ref import ops_ref as R
+from .runner import KVPool, Packet
+from .weights import LayerWeights, ModelWeights, QLinear
+
+
+class TorchRunner:
+    def __init__(self, weights: ModelWeights, kv: KVPool, max_rows: int):
+        self.w, self.cfg, self.kv = weights, weights.config, kv
+        self.device = weights.embed_q.device
+        self.max_rows = max_rows
+        self._ints = {}
+        self._attn_index = {}
+        n = 0
+        for i in range(self.cfg.layers):
+            if self.cfg.is_full_attention(i):
+                self._attn_index[i] = n
+                n += 1
+        self.mtp_kv_index = n
+        self.layer_hooks = {}
+
+    def _w(self, lin: QLinear) -> torch.Tensor:
+        key = id(lin.codes)
+        if key not in self._ints:
+            self._ints[key] = lin.integers()
+        return self._ints[key]
+
+    def _linear(self, lin: QLinear, y: torch.Tensor, out_f32: bool = False) -> torch.Tensor:
+        z = R.hadamard_rotate(y, lin.signs) if lin.signs is not None else y
+        q, s = R.a8(z)
+        return R.qgemm(q, s, self._w(lin), lin.scale, out_f32)
+
+    def _attention(self, lw: LayerWeights, slot: int, y: torch.Tensor, p: Packet, cos, sin):
+        cfg = self.cfg
+        rows, d, qh, kvh = p.rows, cfg.head_dim, cfg.q_heads, cfg.kv_heads
+        proj = self._linear(lw.qkv, y)
+        gated = cfg.gated_attention and lw.qkv.n == cfg.q_dim + 2 * cfg.kv_dim
+        qw = qh * d * (2 if gated else 1)
+        gate = None
+        if gated:
+            qg = proj[:, :qw].reshape(rows, qh, 2 * d)
+            q, gate = qg[..., :d], qg[..., d:]
+        else:
+            q = proj[:, :qw].reshape(rows, qh, d)
+        k = proj[:, qw:qw + kvh * d].reshape(rows, kvh, d)
+        v = proj[:, qw + kvh * d:].reshape(rows, kvh, d)
+        qn = R.qk_norm_rope(q, lw.q_norm if cfg.qk_norm else None, cos, sin, cfg.eps,
+                            cfg.zero_centered_norm)
+        kn = R.qk_norm_rope(k, lw.k_norm if cfg.qk_norm else None, cos, sin, cfg.eps,
+                            cfg.zero_centered_norm)
+        kq, ks = R.kv_quant(kn)
+        vq, vs = R.kv_quant(R.f16(v.float()))
+        req, pos = p.row_req[:rows].long(), p.row_pos[:rows].long()
+        page = p.page_table[req, pos // 128].long()
+        off = pos % 128
+        self.kv.k[slot][page, off] = kq
+        self.kv.v[slot][page, off] = vq
+        self.kv.ks[slot][page, off] = ks.to(torch.float16)
+        self.kv.vs[slot][page, off] = vs.to(torch.float16)
+        out = torch.empty(rows, qh * d)
+        for r in torch.unique(req).tolist():
+            idx = (req == r).nonzero().flatten()
+            rp = pos[idx]
+            kv_len = int(rp.max()) + 1
+            allpos = torch.arange(kv_len)
+            pg = p.page_table[r, allpos // 128].long()
+            kk = R.kv_dequant(self.kv.k[slot][pg, allpos % 128], self.kv.ks[slot][pg, allpos % 128])
+            vv = R.kv_dequant(self.kv.v[slot][pg, allpos % 128], self.kv.vs[slot][pg, allpos % 128])
+            for j, i in enumerate(idx.tolist()):
+                n = int(rp[j]) + 1
+                out[i] = R.causal_gqa(qn[i:i + 1], kk[:n], vv[:n], n - 1,
+                                      None if gate is None else gate[i:i + 1])[0]
+        return out
+
+    def _ffn(self, lw: LayerWeights, y: torch.Tensor) -> torch.Tensor:
+        gu = self._linear(lw.gate_up, y)
+        f = gu.shape[-1] // 2
+        return self._linear(lw.down, R.silu_mul(gu[:, :f], gu[:, f:]))
+
+    def forward_hidden(self, p: Packet):
+        cfg = self.cfg
+        rows = p.rows
+        x = R.embed_w8(p.ids[:rows], self.w.embed_q, self.w.embed_s)
+        resid = torch.zeros(rows, cfg.hidden)
+        cos, sin = R.rope_tables(p.row_pos[:rows], cfg.head_dim, cfg.rope_theta)
+        zc = cfg.zero_centered_norm
+        for i, lw in enumerate(self.w.layers):
+            resid = resid + x
+            y = R.rms_norm(resid, lw.in_norm, cfg.eps, zc)
+            if lw.kind == "attn":
+                mix = self._attention(lw, self._attn_index[i], y, p, cos, sin)
+                x = self._linear(lw.o, mix)
+            else:
+                x = self.layer_hooks["gdn"](self, lw, i, y, p)
+            resid = resid + x
+            y = R.rms_norm(resid, lw.post_norm, cfg.eps, zc)
+            if cfg.experts:
+                x = self.layer_hooks["moe"](self, lw, i, y, p)
+            else:
+                x = self._ffn(lw, y)
+        return x, resid
+
+    def logits(self, p: Packet, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        x, resid = self.forward_hidden(p)
+        final = resid + x
+        if p.logit_rows is not None:
+            final = final.index_select(0, p.logit_rows.long())
+        h = R.rms_norm(final, self.w.final_norm, self.cfg.eps, self.cfg.zero_centered_norm)
+        lg = self._linear(self.w.head, h, out_f32=True)
+        if out is not None:
+            out[:lg.shape[0]].copy_(lg)
+        return lg
+
+    def greedy(self, p: Packet, logits_out=None, token_out=None):
+        lg = self.logits(p, logits_out)
+        tok = R.argmax_lowest(lg)
+        if token_out is not None:
+            token_out[:tok.shape[0]].copy_(tok)
+        return tok, lg

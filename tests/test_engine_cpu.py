@@ -1,0 +1,125 @@
+"""Continuous engine on the CPU reference runner (tiny model)."""
+import pytest
+import torch
+
+from orinfer_b200.config import PRESETS, LoadOptions, SchedulerOptions
+from orinfer_b200.core.sampling import SamplingOptions
+from orinfer_b200.engine.engine import Engine
+from orinfer_b200.engine.request import Phase
+from orinfer_b200.models.weights import random_model
+from orinfer_b200.ref import cpu_forward as ref
+
+
+@pytest.fixture(scope="module")
+def weights():
+    return random_model(PRESETS["tiny"], seed=0)
+
+
+def _prompts(n, length, seed=1, vocab=1024):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (length,), generator=g).tolist() for _ in range(n)]
+
+
+def _engine(weights, **kw):
+    sched = SchedulerOptions(max_active=kw.pop("max_active", 4),
+                             prefill_chunk=kw.pop("prefill_chunk", 64))
+    return Engine(weights, sched=sched, kv_pages=kw.pop("kv_pages", 24), max_context=512,
+                  load=kw.pop("load", LoadOptions()), **kw)
+
+
+def test_greedy_matches_single_request_reference(weights):
+    prompts = _prompts(2, 32)
+    eng = _engine(weights)
+    out = eng.generate(prompts, max_new=8)
+    for p, o in zip(prompts, out):
+        want, _ = ref.generate_greedy(weights, torch.tensor(p), 8, quantized=True)
+        assert o == want
+    assert eng.stats.finished == 2 and eng.pool.available == 23 - eng.prefix.statistics().device_pages
+
+
+def test_continuous_batching_is_batch_invariant(weights):
+    prompts = _prompts(3, 20, seed=2)
+    solo = [_engine(weights).generate([p], max_new=6)[0] for p in prompts]
+    eng = _engine(weights, prefill_chunk=8)          # chunked prefill + staggered arrivals
+    r0 = eng.submit(prompts[0], 6)
+    eng.step(); eng.step()
+    r1 = eng.submit(prompts[1], 6)
+    eng.step()
+    r2 = eng.submit(prompts[2], 6)
+    while eng.has_work():
+        eng.step()
+    assert [r0.generated, r1.generated, r2.generated] == solo
+    assert eng.stats.prefill_tokens == 60
+
+
+def test_prefix_cache_reuses_pages_and_keeps_output(weights):
+    base = _prompts(1, 140, seed=3)[0]
+    eng = _engine(weights, prefill_chunk=256)
+    first = eng.generate([base + [5, 6, 7]], max_new=4)[0]
+    r = eng.submit(base + [5, 6, 7], 4)
+    while not r.finished:
+        eng.step()
+    assert r.cached_tokens == 128 and r.generated == first
+    other = eng.submit(base[:130] + [9, 9], 4)
+    while not other.finished:
+        eng.step()
+    assert other.cached_tokens == 128
+    st = eng.prefix.statistics()
+    assert st.hit_tokens >= 256 and st.device_pages >= 1
+    cold = _engine(weights, prefill_chunk=256, load=LoadOptions(prefix_cache_bytes=0))
+    assert cold.generate([base[:130] + [9, 9]], max_new=4)[0] == other.generated
+
+
+def test_admission_waits_for_pages_and_evicts_prefixes(weights):
+    prompts = _prompts(4, 100, seed=4)
+    eng = _engine(weights, kv_pages=4, max_active=4)       # 3 usable pages, 1 page per request
+    reqs = [eng.submit(p, 8) for p in prompts]
+    steps = 0
+    while eng.has_work():
+        eng.step()
+        steps += 1
+        assert steps < 200
+    assert all(len(r.generated) == 8 for r in reqs)
+    assert eng.stats.deferred_admissions > 0
+    solo = _engine(weights).generate([prompts[3]], max_new=8)[0]
+    assert reqs[3].generated == solo
+
+
+def test_seeded_sampling_is_independent_of_batch(weights):
+    prompts = _prompts(2, 16, seed=5)
+    opt = SamplingOptions(temperature=0.9, top_p=0.95, seed=1234)
+    alone = _engine(weights).generate([prompts[0]], max_new=6, sampling=opt)[0]
+    both = _engine(weights).generate(prompts, max_new=6, sampling=opt)
+    assert both[0] == alone
+    again = _engine(weights).generate([prompts[0]], max_new=6, sampling=opt)[0]
+    assert again == alone
+    other_seed = _engine(weights).generate(
+        [prompts[0]], max_new=6, sampling=SamplingOptions(temperature=0.9, top_p=0.95, seed=99))[0]
+    assert other_seed != alone
+
+
+def test_cancel_stop_and_logprobs(weights):
+    prompts = _prompts(2, 12, seed=6)
+    eng = _engine(weights)
+    a = eng.submit(prompts[0], 50)
+    b = eng.submit(prompts[1], 5, SamplingOptions(temperature=0.0, top_logprobs=3))
+    eng.step(); eng.step()
+    eng.cancel(a)
+    while eng.has_work():
+        eng.step()
+    assert a.finish_reason == "cancelled" and a.phase is Phase.FINISHED
+    assert b.finish_reason == "length" and len(b.logprobs) == 5
+    tok, lp, top = b.logprobs[0]
+    assert top[0][0] == tok and abs(top[0][1] - lp) < 1e-12 and lp <= 0
+    first = b.generated[0]
+    c = eng.submit(prompts[1], 5, stop_ids=(first,))
+    while eng.has_work():
+        eng.step()
+    assert c.generated == [first] and c.finish_reason == "stop"
+    assert eng.pool.available + eng.prefix.statistics().device_pages == 23
+
+
+def test_context_limit_is_rejected(weights):
+    eng = _engine(weights)
+    with pytest.raises(ValueError, match="exceeds the context window"):
+        eng.submit([1] * 500, 100)
