@@ -154,7 +154,9 @@ def main() -> int:
             ids = torch.randint(0, cfg.vocab, (n_tokens,), generator=gen, dtype=torch.int32).to(dev)
             packets.append(Packet(ids, torch.zeros(n_tokens, dtype=torch.int32, device=dev),
                                   torch.arange(n_tokens, dtype=torch.int32, device=dev), table,
-                                  n_tokens, n_tokens, torch.tensor([n_tokens - 1], device=dev)))
+                                  n_tokens, n_tokens, torch.tensor([n_tokens - 1], device=dev),
+                                  chunks=torch.tensor([[0, n_tokens, 0, 0]], dtype=torch.int32,
+                                                      device=dev), max_q_len=n_tokens))
         for p in packets[:warmup]:
             runner.greedy(p)
         barrier()

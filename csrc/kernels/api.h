@@ -50,6 +50,15 @@ int orinfer_attention(const __half* q, const __half* gate, const int* row_req, c
                       __half* out, int rows, int qh, int kvh, int head_dim, int splits,
                       float* scratch, cudaStream_t stream);
 
+// Prefill chunks on tensor cores.  chunks: device int32 [n_chunks, 4] =
+// (first packed row, rows, absolute position of the first row, page-table row).
+// Returns -4 for a head size it does not implement (use orinfer_attention instead).
+int orinfer_attention_prefill(const __half* q, const __half* gate, const int* chunks, int n_chunks,
+                              int max_q_len, int total_rows, const int* page_table, int max_pages,
+                              const int8_t* kcache, const int8_t* vcache, const __half* kscale,
+                              const __half* vscale, __half* out, int qh, int kvh, int head_dim,
+                              int num_pages, cudaStream_t stream);
+
 // ---- E8P nearest-codeword encoder: x fp32 [V,8] -> int32 codes [V]
 int orinfer_e8p_encode(const float* x, int* codes, long long vectors, cudaStream_t stream);
 

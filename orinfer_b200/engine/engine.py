@@ -338,7 +338,7 @@ class Engine:
 
     def _run_direct(self, decoders: List[Request], chunks):
         t0 = time.monotonic()
-        ids, req_rows, pos, logit_rows, order = [], [], [], [], []
+        ids, req_rows, pos, logit_rows, order, chunk_rows = [], [], [], [], [], []
         max_kv = 1
         for r in decoders:
             ids.append(r.pending)
@@ -347,7 +347,9 @@ class Engine:
             logit_rows.append(len(ids) - 1)
             order.append((r, 1, True))
             max_kv = max(max_kv, r.offset + 1)
+        n_decode = len(ids)
         for r, n in chunks:
+            chunk_rows.append([len(ids), n, r.offset, r.slot])
             ids += r.prompt[r.offset:r.offset + n]
             req_rows += [r.slot] * n
             pos += list(range(r.offset, r.offset + n))
@@ -365,6 +367,11 @@ class Engine:
         packet = Packet(self._upload("ids", ids), self._upload("req", req_rows),
                         self._upload("pos", pos), self.page_table_dev, rows, max_kv,
                         self._upload("sel", logit_rows).long())
+        if chunk_rows and self.on_gpu:
+            flat = [v for c in chunk_rows for v in c]
+            packet.chunks = self._upload("chunks", flat).view(-1, 4)
+            packet.max_q_len = max(c[1] for c in chunk_rows)
+            packet.decode_rows = n_decode
         t1 = time.monotonic()
         self.stats.batch_inputs_s += t1 - t0
         tok, lg = self.runner.greedy(packet)

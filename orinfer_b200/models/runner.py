@@ -99,6 +99,12 @@ class Packet:
     rows: int
     max_kv_len: int              # host-side bound used to pick the split count
     logit_rows: Optional[torch.Tensor] = None   # int64 rows whose logits are needed (None = all)
+    # Prefill chunks for the tensor-core attention kernel: int32 [C, 4] = (first row, rows,
+    # position of the first row, page-table row).  Rows [0, decode_rows) are single-row
+    # requests handled by the row kernel; None = every row goes through the row kernel.
+    chunks: Optional[torch.Tensor] = None
+    max_q_len: int = 0
+    decode_rows: int = 0
 
 
 class ModelRunner:
@@ -141,13 +147,23 @@ class ModelRunner:
                      gated=cfg.gated_attention and lw.qkv.n == cfg.q_dim + 2 * cfg.kv_dim,
                      eps=cfg.eps, zero_centered=cfg.zero_centered_norm, q_out=ws.q,
                      gate_out=ws.gate, rows=rows)
-        splits = min(F.attention_splits(p.max_kv_len, rows, cfg.kv_heads),
-                     max(ws.SPLIT_ROWS // rows, 1))
-        scratch = ws.attn_scratch if splits > 1 else None
         gated = cfg.gated_attention and lw.qkv.n == cfg.q_dim + 2 * cfg.kv_dim
-        F.attention(ws.q, ws.gate if gated else None, p.row_req, p.row_pos, p.page_table,
-                    self.kv.k[kv_slot], self.kv.v[kv_slot], self.kv.ks[kv_slot],
-                    self.kv.vs[kv_slot], splits=splits, scratch=scratch, out=ws.attn, rows=rows)
+        gate = ws.gate if gated else None
+        row_rows = rows
+        if p.chunks is not None and cfg.head_dim in (64, 128):
+            done = F.attention_prefill(ws.q, gate, p.chunks, p.max_q_len, p.page_table,
+                                       self.kv.k[kv_slot], self.kv.v[kv_slot],
+                                       self.kv.ks[kv_slot], self.kv.vs[kv_slot], out=ws.attn,
+                                       total_rows=rows)
+            if done:
+                row_rows = p.decode_rows
+        if row_rows > 0:
+            splits = min(F.attention_splits(p.max_kv_len, row_rows, cfg.kv_heads),
+                         max(ws.SPLIT_ROWS // row_rows, 1))
+            scratch = ws.attn_scratch if splits > 1 else None
+            F.attention(ws.q, gate, p.row_req, p.row_pos, p.page_table, self.kv.k[kv_slot],
+                        self.kv.v[kv_slot], self.kv.ks[kv_slot], self.kv.vs[kv_slot],
+                        splits=splits, scratch=scratch, out=ws.attn, rows=row_rows)
         qd = cfg.q_heads * cfg.head_dim
         q8, sc = F.act_prep(ws.attn, None, None, self._signs(lw.o), rows=rows, q_out=ws.q8[qd],
                             scale_out=ws.scale)

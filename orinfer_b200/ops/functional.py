@@ -152,6 +152,30 @@ def attention(q: torch.Tensor, gate: Optional[torch.Tensor], row_req: torch.Tens
     return out
 
 
+def attention_prefill(q: torch.Tensor, gate: Optional[torch.Tensor], chunks: torch.Tensor,
+                      max_q_len: int, page_table: torch.Tensor, kcache: torch.Tensor,
+                      vcache: torch.Tensor, kscale: torch.Tensor, vscale: torch.Tensor, *,
+                      out: Optional[torch.Tensor] = None, total_rows: Optional[int] = None) -> bool:
+    """tcgen05 flash attention over prefill chunks.  ``chunks`` is int32 [C, 4] =
+    (first row, rows, position of the first row, page-table row).  Returns False when the
+    head size is not implemented by the tensor-core kernel (nothing was launched)."""
+    _cuda(q, chunks, page_table, kcache)
+    n, qh, d = q.shape
+    assert chunks.dtype == torch.int32 and chunks.dim() == 2 and chunks.shape[1] == 4
+    if out is None:
+        raise native.KernelError("attention_prefill needs a preallocated output")
+    rc = native.lib().orinfer_attention_prefill(
+        ptr(q), ptr(gate), ptr(chunks), chunks.shape[0], max_q_len,
+        n if total_rows is None else total_rows, ptr(page_table), page_table.shape[1],
+        ptr(kcache), ptr(vcache), ptr(kscale), ptr(vscale), ptr(out), qh, kcache.shape[2], d,
+        kcache.shape[0], stream())
+    if rc == -4:
+        return False
+    check(rc, "attention_prefill")
+    count_launches(1)
+    return True
+
+
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None,
            scratch: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
            rows: Optional[int] = None) -> torch.Tensor:

@@ -246,3 +246,42 @@ def test_e8p_encode_kernel(cuda):
     d_ref = ((x - e8p_torch.decode_t(ref).float()) ** 2).sum(1)
     assert float((d_mine - d_ref).abs().max()) < 1e-3
     assert float((codes == ref).float().mean()) > 0.995
+
+
+@pytest.mark.parametrize("qh,kvh,d", [(32, 8, 128), (40, 8, 128), (4, 2, 64), (8, 1, 128)])
+def test_attention_prefill_tensor_core(cuda, qh, kvh, d):
+    """Two chunks: a fresh 300-token prompt and a 130-row continuation at position 200."""
+    from orinfer_b200.ops import functional as F
+    lens = [300, 330]
+    table, kc, vc, ks, vs = _paged_setup(cuda, lens, kvh, d, seed=7)
+    g = torch.Generator().manual_seed(8)
+    rows = 300 + 130
+    q = torch.randn(rows, qh, d, generator=g).half().to(cuda)
+    chunks = torch.tensor([[0, 300, 0, 0], [300, 130, 200, 1]], dtype=torch.int32, device=cuda)
+    out = torch.zeros(rows, qh * d, dtype=torch.float16, device=cuda)
+    assert F.attention_prefill(q, None, chunks, 300, table, kc, vc, ks, vs, out=out)
+    torch.cuda.synchronize()
+    for (r0, n, pos0, req) in chunks.tolist():
+        k = _gather_kv(table, kc, ks, req, pos0 + n)
+        v = _gather_kv(table, vc, vs, req, pos0 + n)
+        ref = R.causal_gqa(q[r0:r0 + n], k, v, pos0)
+        err = (out[r0:r0 + n].float() - ref).abs()
+        assert float(err.max()) < 2e-2 * max(1.0, float(ref.abs().max())), float(err.max())
+        assert float(err.mean()) < 2e-3 * max(1.0, float(ref.abs().mean()) * 10)
+
+
+def test_attention_prefill_matches_row_kernel(cuda):
+    from orinfer_b200.ops import functional as F
+    qh, kvh, d = 32, 8, 128
+    table, kc, vc, ks, vs = _paged_setup(cuda, [700], kvh, d, seed=9)
+    g = torch.Generator().manual_seed(10)
+    n, pos0 = 200, 500
+    q = torch.randn(n, qh, d, generator=g).half().to(cuda)
+    gate = torch.randn(n, qh, d, generator=g).half().to(cuda)
+    chunks = torch.tensor([[0, n, pos0, 0]], dtype=torch.int32, device=cuda)
+    out = torch.zeros(n, qh * d, dtype=torch.float16, device=cuda)
+    assert F.attention_prefill(q, gate, chunks, n, table, kc, vc, ks, vs, out=out)
+    req = torch.zeros(n, dtype=torch.int32, device=cuda)
+    pos = torch.arange(pos0, pos0 + n, dtype=torch.int32, device=cuda)
+    rows = F.attention(q, gate, req, pos, table, kc, vc, ks, vs)
+    assert float((out.float() - rows.float()).abs().max()) < 2e-2
