@@ -223,45 +223,50 @@ __device__ __forceinline__ uint32_t swz128(uint32_t row, uint32_t chunk) {
 }
 
 // ---------------------------------------------------------------- E8P decode
-// Value table: entry (parity << 8 | index) = {pos_lo, neg_lo, pos_hi, neg_hi},
-// four packed INT8 each, where pos = mult * (basis + shift), neg = mult * (-basis + shift)
-// and shift = 1 - 2 * parity.  mult is 4 for the coarse stage of Q4, else 1.
+// Value table (4 KiB): entry[index] = {pos_lo, neg_lo, pos_hi, neg_hi}, four packed bytes
+// each, holding basis + 24 and -basis + 24 (so every byte is in 14..34 and whole-word
+// arithmetic never carries between bytes).  A code's sign byte picks pos/neg per
+// coordinate with one PRMT per half; the +/-1 parity shift and the re-centring are one
+// constant added afterwards, and XOR 0x80 turns the biased byte into two's complement.
 struct E8pTables {
-  uint4 fine[512];
-  uint4 coarse[512];
+  uint4 pairs[256];
 };
-
 
 // Host-side runtime singletons (runtime.cu): device status word and decode tables.
 int* runtime_status_ptr();
 const E8pTables* runtime_e8p_tables();
 cudaError_t runtime_ensure_init();
 
-__device__ __forceinline__ uint2 e8p_decode8(uint32_t code, const uint4* __restrict__ table) {
+// -> biased coordinate bytes (+/-basis + 24) and the parity bit of one 16-bit code
+__device__ __forceinline__ void e8p_select(uint32_t code, const uint4* __restrict__ table,
+                                           uint32_t& lo, uint32_t& hi, uint32_t& par) {
   const uint32_t s = code & 0xffu;
-  const uint32_t par = __popc(s) & 1u;
+  par = __popc(s) & 1u;
   const uint32_t t = s ^ par;
-  const uint4 e = table[(par << 8) | ((code >> 8) & 0xffu)];
+  const uint4 e = table[(code >> 8) & 0xffu];
   const uint32_t t2 = t >> 2;
-  const uint32_t sel_lo = 0x3210u | ((t & 0x11u) << 2) | ((t & 0x22u) << 9);
-  const uint32_t sel_hi = 0x3210u | ((t2 & 0x11u) << 2) | ((t2 & 0x22u) << 9);
-  uint2 out;
-  out.x = __byte_perm(e.x, e.y, sel_lo);
-  out.y = __byte_perm(e.z, e.w, sel_hi);
-  return out;
+  // coordinate i flips with bit {0,4,1,5,2,6,3,7}[i]; nibble j of a PRMT selector is
+  // j (take the "pos" byte) or j + 4 (take the "neg" byte)
+  lo = __byte_perm(e.x, e.y, 0x3210u | ((t & 0x11u) << 2) | ((t & 0x22u) << 9));
+  hi = __byte_perm(e.z, e.w, 0x3210u | ((t2 & 0x11u) << 2) | ((t2 & 0x22u) << 9));
 }
 
-// Per-byte two's-complement add (no carries between bytes).
-__device__ __forceinline__ uint32_t add_bytes(uint32_t a, uint32_t b) {
-  return ((a & 0x7f7f7f7fu) + (b & 0x7f7f7f7fu)) ^ ((a ^ b) & 0x80808080u);
+// One 16-bit code -> eight INT8 weights  (+/-basis) + (1 - 2*parity).
+__device__ __forceinline__ uint2 e8p_decode8(uint32_t code, const uint4* __restrict__ table) {
+  uint32_t lo, hi, par;
+  e8p_select(code, table, lo, hi, par);
+  const uint32_t cw = 0x69696969u - par * 0x02020202u;          // 128 - 24 + shift
+  return make_uint2((lo + cw) ^ 0x80808080u, (hi + cw) ^ 0x80808080u);
 }
 
 // One Q4 word (coarse U16 low, residual U16 high) -> eight INT8 weights 4*q0 + q1.
-__device__ __forceinline__ uint2 e8p_decode_q4(uint32_t word, const uint4* __restrict__ coarse,
-                                               const uint4* __restrict__ fine) {
-  const uint2 a = e8p_decode8(word & 0xffffu, coarse);
-  const uint2 b = e8p_decode8(word >> 16, fine);
-  return make_uint2(add_bytes(a.x, b.x), add_bytes(a.y, b.y));
+__device__ __forceinline__ uint2 e8p_decode_q4(uint32_t word, const uint4* __restrict__ table) {
+  uint32_t l0, h0, p0, l1, h1, p1;
+  e8p_select(word & 0xffffu, table, l0, h0, p0);
+  e8p_select(word >> 16, table, l1, h1, p1);
+  // 4*(b0+24) + (b1+24) + c = 4*q0 + q1 + 128  with  c = 128 - 120 + 4*s0 + s1
+  const uint32_t cw = 0x0d0d0d0du - p0 * 0x08080808u - p1 * 0x02020202u;
+  return make_uint2(((l0 << 2) + l1 + cw) ^ 0x80808080u, ((h0 << 2) + h1 + cw) ^ 0x80808080u);
 }
 
 // ---------------------------------------------------------------- math

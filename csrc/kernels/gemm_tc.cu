@@ -1,15 +1,16 @@
 // Quantised GEMM on the 5th-generation tensor cores: out[M,N] = (A8[M,K] . W[N,K]^T) * s_w * s_a.
 //
-// One CTA computes a 128 x 128 output tile.  Warp 0 streams operand tiles with TMA
-// (activations always; INT8 weights for W8; the packed E8P codes as one contiguous
-// bulk copy per k-block for Q4/Q2).  Warps 2-5 expand the lattice codes into an INT8
-// weight tile in the 128-byte-swizzled K-major layout the tensor core reads, warp 1
-// issues tcgen05.mma kind::i8 into a TMEM accumulator, and warps 2-5 finally read
-// TMEM back, apply the two scales and store FP16/FP32.  INT4 tensor-core MMA (the
-// reference's fastest path, kernels/cuda/model/e8p_core.py:15-33) does not exist on
-// tcgen05, so both E8P formats go through INT8 operands.  Replaces e8p_q4.projection
-// (kernels/cuda/model/e8p_q4.py:144-265), integer_vq (kernels/cuda/model/integer_vq.py:263)
-// and int8_projection (kernels/cuda/model/int8_projection.py:15).
+// One CTA computes a (MT*128) x 128 output tile, MT = 1 or 2 accumulators in TMEM that
+// share every decoded weight tile.  Warp 0 streams operand tiles with TMA (activations
+// always; INT8 weights for W8; the packed E8P codes as one contiguous bulk copy per
+// k-block for Q4/Q2).  Warps 2-9 expand the lattice codes into an INT8 weight tile in the
+// 128-byte-swizzled K-major layout the tensor core reads, warp 1 issues tcgen05.mma
+// kind::i8 into TMEM, and warps 2-9 finally read TMEM back, apply the two scales and
+// store FP16/FP32.  INT4 tensor-core MMA (the reference's fastest path,
+// kernels/cuda/model/e8p_core.py:15-33) does not exist on tcgen05, so both E8P formats go
+// through INT8 operands.  Replaces e8p_q4.projection (kernels/cuda/model/e8p_q4.py:144-265),
+// integer_vq (kernels/cuda/model/integer_vq.py:263) and int8_projection
+// (kernels/cuda/model/int8_projection.py:15).
 #include <cuda.h>
 
 #include "api.h"
@@ -23,30 +24,33 @@ int qgemv_dispatch(int fmt, const int8_t* a, const float* as, const void* w, con
 
 namespace tc {
 
-constexpr int BM = 128, BN = 128, BK = 128, STAGES = 4;
+constexpr int BM = 128, BN = 128, BK = 128;
 constexpr int TILE_BYTES = 128 * 128;        // one INT8 operand tile
-constexpr int THREADS = 192;
+constexpr int PRODUCERS = 256;               // warps 2..9
+constexpr int THREADS = 64 + PRODUCERS;
 
-template <int FMT>
+template <int FMT, int MT>
 struct Layout {
+  static constexpr int STAGES = MT == 1 ? 4 : 3;
   static constexpr int ROW_CODE_BYTES = FMT == 1 ? 64 : (FMT == 2 ? 32 : 0);
   static constexpr int CODE_BYTES = BN * ROW_CODE_BYTES;
-  static constexpr int LUT_BYTES = FMT == 1 ? 16384 : (FMT == 2 ? 8192 : 0);
+  static constexpr int LUT_BYTES = FMT == 0 ? 0 : 4096;
   static constexpr int A_OFF = 0;
-  static constexpr int B_OFF = A_OFF + STAGES * TILE_BYTES;
+  static constexpr int B_OFF = A_OFF + STAGES * MT * TILE_BYTES;
   static constexpr int CODE_OFF = B_OFF + STAGES * TILE_BYTES;
   static constexpr int LUT_OFF = CODE_OFF + STAGES * CODE_BYTES;
   static constexpr int BAR_OFF = LUT_OFF + LUT_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;   // barriers + alignment slack
 };
 
-template <int FMT, bool OUT_F32>
+template <int FMT, bool OUT_F32, int MT>
 __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
     const unsigned char* __restrict__ w, const float* __restrict__ a_scale,
     const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K,
     const E8pTables* __restrict__ tables, int* status) {
-  using L = Layout<FMT>;
+  using L = Layout<FMT, MT>;
+  constexpr int STAGES = L::STAGES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* a_s = smem + L::A_OFF;
@@ -61,14 +65,15 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM * MT;
   const int kblocks = K / BK;
   const int rows_valid = min(BN, N - n0);
+  constexpr uint32_t TMEM_COLS = MT * BN;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&tma_full[s], 1);
-      mbar_init(&b_full[s], 128);
+      mbar_init(&b_full[s], PRODUCERS);
       mbar_init(&empty[s], 1);
     }
     mbar_init(tmem_full, 1);
@@ -77,14 +82,12 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     if (FMT == 0) prefetch_tmap(&tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, BN);
+    tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
   if (FMT != 0 && warp >= 2) {
     const int t = threadIdx.x - 64;
-    const uint4* src = reinterpret_cast<const uint4*>(tables);
-    // fine table first, then (Q4 only) the coarse one: same order as E8pTables.
-    for (int i = t; i < L::LUT_BYTES / 16; i += 128) lut[i] = src[i];
+    lut[t] = tables->pairs[t];               // 256 producer threads, 256 entries
   }
   tc_fence_before();
   __syncthreads();
@@ -99,9 +102,12 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
         const uint32_t ph = (kb / STAGES) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, status, STATUS_TMA_WAIT, kb)) break;
         const uint32_t bytes =
-            TILE_BYTES + (FMT == 0 ? TILE_BYTES : rows_valid * L::ROW_CODE_BYTES);
+            MT * TILE_BYTES + (FMT == 0 ? TILE_BYTES : rows_valid * L::ROW_CODE_BYTES);
         mbar_expect_tx(&tma_full[s], bytes);
-        tma_load_2d(a_s + s * TILE_BYTES, &tmap_a, &tma_full[s], kb * BK, m0);
+#pragma unroll
+        for (int t = 0; t < MT; ++t)
+          tma_load_2d(a_s + (s * MT + t) * TILE_BYTES, &tmap_a, &tma_full[s], kb * BK,
+                      m0 + t * BM);
         if (FMT == 0) {
           tma_load_2d(b_s + s * TILE_BYTES, &tmap_b, &tma_full[s], kb * BK, n0);
         } else {
@@ -127,45 +133,49 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
         if (ok && FMT != 0) ok = mbar_wait(&b_full[s], ph, status, STATUS_MMA_WAIT, 0x2000 | kb);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(a_s + s * TILE_BYTES);
         const uint32_t b_addr = smem_u32(b_s + s * TILE_BYTES);
 #pragma unroll
         for (int j = 0; j < BK / 32; ++j) {
-          mma_i8_ss(tmem_base, umma_desc(a_addr + j * 32, 16, 1024),
-                    umma_desc(b_addr + j * 32, 16, 1024), idesc, (kb | j) != 0 ? 1u : 0u);
+          const uint64_t bdesc = umma_desc(b_addr + j * 32, 16, 1024);
+#pragma unroll
+          for (int t = 0; t < MT; ++t) {
+            const uint32_t a_addr = smem_u32(a_s + (s * MT + t) * TILE_BYTES);
+            mma_i8_ss(tmem_base + t * BN, umma_desc(a_addr + j * 32, 16, 1024), bdesc, idesc,
+                      (kb | j) != 0 ? 1u : 0u);
+          }
         }
         tc_commit(&empty[s]);
       }
       if (ok) tc_commit(tmem_full);
     }
   } else {
-    const int t = threadIdx.x - 64;                     // 0..127
+    const int t = threadIdx.x - 64;                     // 0..255
     bool ok = true;
     if (FMT != 0) {
-      const uint4* fine = lut;
-      const uint4* coarse = lut + 512;
-      const int chunk = t & 7, rbase = t >> 3;          // 16 rows per pass
+      const int chunk = t & 7, rbase = t >> 3;          // 32 rows per pass, 4 passes
       for (int kb = 0; kb < kblocks; ++kb) {
         const int s = kb % STAGES;
         const uint32_t ph = (kb / STAGES) & 1;
+        // the copy for this phase is only issued after the stage was released, so its
+        // arrival also means the INT8 tile of this stage is free to overwrite
         ok = mbar_wait(&tma_full[s], ph, status, STATUS_DECODE_WAIT, kb);
         if (!ok) break;
         const unsigned char* cs = code_s + s * L::CODE_BYTES;
         unsigned char* bs = b_s + s * TILE_BYTES;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int row = rbase + 16 * i;
+        for (int i = 0; i < 4; ++i) {
+          const int row = rbase + 32 * i;
           uint4 v = make_uint4(0, 0, 0, 0);
           if (row < rows_valid) {
             if (FMT == 1) {
               const uint2 wd = *reinterpret_cast<const uint2*>(cs + row * 64 + chunk * 8);
-              const uint2 q0 = e8p_decode_q4(wd.x, coarse, fine);
-              const uint2 q1 = e8p_decode_q4(wd.y, coarse, fine);
+              const uint2 q0 = e8p_decode_q4(wd.x, lut);
+              const uint2 q1 = e8p_decode_q4(wd.y, lut);
               v = make_uint4(q0.x, q0.y, q1.x, q1.y);
             } else {
               const uint32_t wd = *reinterpret_cast<const uint32_t*>(cs + row * 32 + chunk * 4);
-              const uint2 q0 = e8p_decode8(wd & 0xffffu, fine);
-              const uint2 q1 = e8p_decode8(wd >> 16, fine);
+              const uint2 q0 = e8p_decode8(wd & 0xffffu, lut);
+              const uint2 q1 = e8p_decode8(wd >> 16, lut);
               v = make_uint4(q0.x, q0.y, q1.x, q1.y);
             }
           }
@@ -179,35 +189,39 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     ok = __all_sync(0xffffffffu, ok);        // tcgen05.ld needs the whole warp
     if (ok) {
       tc_fence_after();
-      const int quad = warp & 3;
+      const int quad = warp & 3;                          // TMEM lane quadrant of this warp
+      const int half = (warp - 2) >> 2;                   // which 64 columns of each tile
       const int row = quad * 32 + lane;
-      const int m = m0 + row;
-      const float sa = m < M ? a_scale[m] : 0.f;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + c0, r);
-        tc_wait_ld();
-        if (m < M) {
+      for (int mt = 0; mt < MT; ++mt) {
+        const int m = m0 + mt * BM + row;
+        const float sa = m < M ? a_scale[m] : 0.f;
+#pragma unroll 1
+        for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + mt * BN + c0, r);
+          tc_wait_ld();
+          if (m < M) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int n = n0 + c0 + g * 8;
-            if (n + 8 <= N) {
-              float v[8];
+            for (int g = 0; g < 4; ++g) {
+              const int n = n0 + c0 + g * 8;
+              if (n + 8 <= N) {
+                float v[8];
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
-                v[j] = (static_cast<float>(static_cast<int>(r[g * 8 + j])) *
-                        __half2float(w_scale[n + j])) * sa;
-              if (OUT_F32) {
-                float* o = reinterpret_cast<float*>(out) + static_cast<size_t>(m) * N + n;
-                *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
-                *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
-              } else {
-                __align__(16) __half h[8];
+                for (int j = 0; j < 8; ++j)
+                  v[j] = (static_cast<float>(static_cast<int>(r[g * 8 + j])) *
+                          __half2float(w_scale[n + j])) * sa;
+                if (OUT_F32) {
+                  float* o = reinterpret_cast<float*>(out) + static_cast<size_t>(m) * N + n;
+                  *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+                  *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+                } else {
+                  __align__(16) __half h[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
-                __half* o = reinterpret_cast<__half*>(out) + static_cast<size_t>(m) * N + n;
-                *reinterpret_cast<int4*>(o) = *reinterpret_cast<const int4*>(h);
+                  for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
+                  __half* o = reinterpret_cast<__half*>(out) + static_cast<size_t>(m) * N + n;
+                  *reinterpret_cast<int4*>(o) = *reinterpret_cast<const int4*>(h);
+                }
               }
             }
           }
@@ -217,13 +231,13 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, BN);
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-template <int FMT, bool OUT_F32>
+template <int FMT, bool OUT_F32, int MT>
 int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale, void* out,
            int M, int N, int K, cudaStream_t stream) {
-  using L = Layout<FMT>;
+  using L = Layout<FMT, MT>;
   CUtensorMap ta, tb;
   if (!make_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BM, BK)) return -3;
   if (FMT == 0) {
@@ -234,16 +248,26 @@ int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w
   }
   static bool attr = false;
   if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(qgemm_tc_kernel<FMT, OUT_F32>,
+    cudaError_t e = cudaFuncSetAttribute(qgemm_tc_kernel<FMT, OUT_F32, MT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return static_cast<int>(e);
     attr = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  qgemm_tc_kernel<FMT, OUT_F32><<<grid, THREADS, L::TOTAL, stream>>>(
+  dim3 grid((N + BN - 1) / BN, (M + BM * MT - 1) / (BM * MT));
+  qgemm_tc_kernel<FMT, OUT_F32, MT><<<grid, THREADS, L::TOTAL, stream>>>(
       ta, tb, reinterpret_cast<const unsigned char*>(w), a_scale, w_scale, out, M, N, K,
       runtime_e8p_tables(), runtime_status_ptr());
   return static_cast<int>(cudaGetLastError());
+}
+
+template <int FMT>
+int launch_fmt(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale,
+               void* out, int M, int N, int K, int out_f32, cudaStream_t stream) {
+  if (M > BM)
+    return out_f32 ? launch<FMT, true, 2>(a, a_scale, w, w_scale, out, M, N, K, stream)
+                   : launch<FMT, false, 2>(a, a_scale, w, w_scale, out, M, N, K, stream);
+  return out_f32 ? launch<FMT, true, 1>(a, a_scale, w, w_scale, out, M, N, K, stream)
+                 : launch<FMT, false, 1>(a, a_scale, w, w_scale, out, M, N, K, stream);
 }
 
 }  // namespace tc
@@ -270,10 +294,7 @@ extern "C" int orinfer_qgemm(int fmt, const int8_t* a, const float* a_scale, con
     }
     return 0;
   }
-#define GO(F) (out_f32 ? tc::launch<F, true>(a, a_scale, w, w_scale, out, M, N, K, stream) \
-                       : tc::launch<F, false>(a, a_scale, w, w_scale, out, M, N, K, stream))
-  if (fmt == 0) return GO(0);
-  if (fmt == 1) return GO(1);
-  return GO(2);
-#undef GO
+  if (fmt == 0) return tc::launch_fmt<0>(a, a_scale, w, w_scale, out, M, N, K, out_f32, stream);
+  if (fmt == 1) return tc::launch_fmt<1>(a, a_scale, w, w_scale, out, M, N, K, out_f32, stream);
+  return tc::launch_fmt<2>(a, a_scale, w, w_scale, out, M, N, K, out_f32, stream);
 }

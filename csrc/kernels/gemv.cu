@@ -42,15 +42,11 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
   constexpr int LPR = 32 / ROWS;                 // lanes per row
   constexpr int WPL = 128 / LPR;                 // weights per lane per k-block
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  uint4* fine = reinterpret_cast<uint4*>(smem_raw);
-  uint4* coarse = fine + 512;
-  int8_t* act = reinterpret_cast<int8_t*>(smem_raw) + (FMT == 1 ? 16384 : 8192);
+  uint4* table = reinterpret_cast<uint4*>(smem_raw);
+  int8_t* act = reinterpret_cast<int8_t*>(smem_raw) + 4096;
   __shared__ int red[GEMV_WARPS][ROWS][MT];
 
-  for (int i = threadIdx.x; i < 512; i += blockDim.x) {
-    fine[i] = tables->fine[i];
-    if (FMT == 1) coarse[i] = tables->coarse[i];
-  }
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) table[i] = tables->pairs[i];
   stage_activations<MT>(act, a, M, K);
   __syncthreads();
 
@@ -75,7 +71,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
     if (FMT == 1) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const uint2 q = e8p_decode_q4(words[j], coarse, fine);
+        const uint2 q = e8p_decode_q4(words[j], table);
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
           const int2 av = *reinterpret_cast<const int2*>(abase + m * K + j * 8);
@@ -87,7 +83,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const uint32_t code = (words[j >> 1] >> ((j & 1) * 16)) & 0xffffu;
-        const uint2 q = e8p_decode8(code, fine);
+        const uint2 q = e8p_decode8(code, table);
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
           const int2 av = *reinterpret_cast<const int2*>(abase + m * K + j * 8);
@@ -158,7 +154,7 @@ template <int FMT, int MT>
 static int launch_e8p(const int8_t* a, const float* as, const void* w, const __half* ws, void* out,
                       int M, int N, int K, int out_f32, cudaStream_t stream) {
   constexpr int ROWS = FMT == 1 ? 8 : 16;
-  const size_t smem = (FMT == 1 ? 16384 : 8192) + static_cast<size_t>(MT) * K;
+  const size_t smem = 4096 + static_cast<size_t>(MT) * K;
   if (smem > 200 * 1024) return -1;
   static bool attr = false;
   if (!attr) {

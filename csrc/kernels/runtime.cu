@@ -30,26 +30,18 @@ cudaError_t runtime_ensure_init() {
   if (g_ready) return cudaSuccess;
   build_e8p_basis(g_basis);
   static E8pTables host;
-  for (int par = 0; par < 2; ++par) {
-    const int shift = 1 - 2 * par;
-    for (int i = 0; i < 256; ++i) {
-      int pos[8], neg[8];
-      for (int d = 0; d < 8; ++d) {
-        pos[d] = g_basis[i][d] + shift;
-        neg[d] = -g_basis[i][d] + shift;
-      }
-      uint4 f, c;
-      f.x = pack4(pos[0], pos[1], pos[2], pos[3]);
-      f.y = pack4(neg[0], neg[1], neg[2], neg[3]);
-      f.z = pack4(pos[4], pos[5], pos[6], pos[7]);
-      f.w = pack4(neg[4], neg[5], neg[6], neg[7]);
-      c.x = pack4(4 * pos[0], 4 * pos[1], 4 * pos[2], 4 * pos[3]);
-      c.y = pack4(4 * neg[0], 4 * neg[1], 4 * neg[2], 4 * neg[3]);
-      c.z = pack4(4 * pos[4], 4 * pos[5], 4 * pos[6], 4 * pos[7]);
-      c.w = pack4(4 * neg[4], 4 * neg[5], 4 * neg[6], 4 * neg[7]);
-      host.fine[par * 256 + i] = f;
-      host.coarse[par * 256 + i] = c;
+  for (int i = 0; i < 256; ++i) {
+    int pos[8], neg[8];
+    for (int d = 0; d < 8; ++d) {
+      pos[d] = g_basis[i][d] + 24;
+      neg[d] = -g_basis[i][d] + 24;
     }
+    uint4 f;
+    f.x = pack4(pos[0], pos[1], pos[2], pos[3]);
+    f.y = pack4(neg[0], neg[1], neg[2], neg[3]);
+    f.z = pack4(pos[4], pos[5], pos[6], pos[7]);
+    f.w = pack4(neg[4], neg[5], neg[6], neg[7]);
+    host.pairs[i] = f;
   }
   cudaError_t e = cudaMalloc(&g_status, 4 * sizeof(int));
   if (e != cudaSuccess) return e;
