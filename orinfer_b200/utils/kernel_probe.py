@@ -1,0 +1,131 @@
+"""Micro-benchmarks of single kernels with CUDA-event timing and roofline fractions.
+
+    python -m orinfer_b200.utils.kernel_probe gemm --m 512 --n 19456 --k 2560 --fmt q4
+    python -m orinfer_b200.utils.kernel_probe attn --tokens 2048
+    python -m orinfer_b200.utils.kernel_probe gemv --m 1 --n 19456 --k 2560 --fmt q4
+
+Each run does warm-up launches, then times ``--iters`` launches between two events on
+the launching stream (synchronised on both sides); with ``--rotate`` buffers larger than
+L2 are cycled so every launch reads its operands from HBM.  Peaks come from
+``MEASURED_PEAKS.json`` at the repository root when present.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+from ..ops import functional as F
+from ..ops import native
+
+ROOT = Path(__file__).resolve().parents[2]
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "measured"
+    return 6.65e12, 1.59e15, "fallback"
+
+
+def timed(fn, iters, warm=3):
+    for _ in range(warm):
+        fn(0)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(iters):
+        fn(i)
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters * 1e-3
+
+
+def weights(fmt, n, k, dev, copies):
+    out = []
+    for _ in range(copies):
+        if fmt == "w8":
+            c = torch.randint(-127, 128, (n, k), dtype=torch.int8, device=dev)
+        elif fmt == "q4":
+            c = torch.randint(-2 ** 31, 2 ** 31 - 1, (k // 128, n, 16), dtype=torch.int64,
+                              device=dev).to(torch.int32)
+        else:
+            c = torch.randint(-2 ** 15, 2 ** 15 - 1, (k // 128, n, 16), dtype=torch.int64,
+                              device=dev).to(torch.int16)
+        out.append(c)
+    return out
+
+
+def gemm(args, dev):
+    m, n, k = args.m, args.n, args.k
+    wbytes = n * k * {"w8": 1.0, "q4": 0.5, "q2": 0.25}[args.fmt]
+    copies = max(1, int(256e6 // wbytes) + 1) if args.rotate else 1
+    ws = weights(args.fmt, n, k, dev, copies)
+    a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device=dev)
+    sa = torch.rand(m, device=dev) * 0.01
+    sw = (torch.rand(n, device=dev) * 0.01).half()
+    out = torch.empty(m, n, dtype=torch.float16, device=dev)
+    path = {"auto": 0, "simt": 1, "tc": 2}[args.path]
+    t = timed(lambda i: F.qgemm(a, sa, ws[i % copies], sw, args.fmt, n, out=out, path=path),
+              args.iters)
+    hbm, flops, tag = peaks()
+    ops = 2.0 * m * n * k
+    byts = wbytes + m * k + m * n * 2
+    print(json.dumps({"kernel": "qgemm", "fmt": args.fmt, "m": m, "n": n, "k": k, "us": t * 1e6,
+                      "tops": ops / t / 1e12, "gbs": byts / t / 1e9,
+                      "frac_int8_peak": ops / t / (2 * flops), "frac_hbm": byts / t / hbm,
+                      "peaks": tag, "int8_peak_assumed": "2 x bf16 cuBLAS burst"}))
+
+
+def attn(args, dev):
+    qh, kvh, d, n = args.qh, args.kvh, args.d, args.tokens
+    pages = (n + 127) // 128
+    table = torch.arange(1, pages + 1, dtype=torch.int32, device=dev).view(1, -1)
+    kc = torch.randint(-127, 128, (pages + 1, 128, kvh, d), dtype=torch.int8, device=dev)
+    vc = torch.randint(-127, 128, (pages + 1, 128, kvh, d), dtype=torch.int8, device=dev)
+    ks = (torch.rand(pages + 1, 128, kvh, d // 64, device=dev) * 0.02).half()
+    vs = (torch.rand(pages + 1, 128, kvh, d // 64, device=dev) * 0.02).half()
+    q = torch.randn(n, qh, d, device=dev).half()
+    out = torch.empty(n, qh * d, dtype=torch.float16, device=dev)
+    chunks = torch.tensor([[0, n, 0, 0]], dtype=torch.int32, device=dev)
+    t = timed(lambda i: F.attention_prefill(q, None, chunks, n, table, kc, vc, ks, vs, out=out),
+              args.iters)
+    _, flops, tag = peaks()
+    ops = 4.0 * qh * d * n * (n + 1) / 2
+    print(json.dumps({"kernel": "attention_prefill", "tokens": n, "qh": qh, "kvh": kvh, "d": d,
+                      "us": t * 1e6, "tflops_causal": ops / t / 1e12,
+                      "frac_f16_peak": ops / t / flops, "peaks": tag}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=512)
+    g.add_argument("--n", type=int, default=19456)
+    g.add_argument("--k", type=int, default=2560)
+    g.add_argument("--fmt", default="q4", choices=["q4", "q2", "w8"])
+    g.add_argument("--path", default="auto", choices=["auto", "simt", "tc"])
+    g.add_argument("--rotate", action="store_true")
+    g.add_argument("--iters", type=int, default=20)
+    a = sub.add_parser("attn")
+    a.add_argument("--tokens", type=int, default=2048)
+    a.add_argument("--qh", type=int, default=32)
+    a.add_argument("--kvh", type=int, default=8)
+    a.add_argument("--d", type=int, default=128)
+    a.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    dev = torch.device("cuda:0")
+    native.init()
+    (gemm if args.cmd == "gemm" else attn)(args, dev)
+    st = native.read_status()
+    if st:
+        raise SystemExit(f"kernel status {st:#x}")
+
+
+if __name__ == "__main__":
+    main()
