@@ -223,13 +223,21 @@ __device__ __forceinline__ uint32_t swz128(uint32_t row, uint32_t chunk) {
 }
 
 // ---------------------------------------------------------------- E8P decode
-// Value table (4 KiB): entry[index] = {pos_lo, neg_lo, pos_hi, neg_hi}, four packed bytes
-// each, holding basis + 24 and -basis + 24 (so every byte is in 14..34 and whole-word
-// arithmetic never carries between bytes).  A code's sign byte picks pos/neg per
-// coordinate with one PRMT per half; the +/-1 parity shift and the re-centring are one
+// Global table (2 KiB): pos[index] = {lo, hi}, four packed bytes each, holding basis + 24,
+// so every byte is in 14..34 and whole-word arithmetic never carries between bytes; the
+// negated coordinates are 48 - pos, again without borrows.  A code's sign byte picks
+// pos/neg per coordinate with one PRMT per half; the selectors come from a 256-entry
+// table indexed by the sign byte.  The +/-1 parity shift and the re-centring are one
 // constant added afterwards, and XOR 0x80 turns the biased byte into two's complement.
 struct E8pTables {
-  uint4 pairs[256];
+  uint2 pos[256];
+};
+
+// Shared-memory working copy: the value table plus PRMT selectors per sign byte
+// (low half-word: coordinates 0-3, high half-word: coordinates 4-7).
+struct E8pSmem {
+  uint2 pos[256];
+  uint32_t sel[256];
 };
 
 // Host-side runtime singletons (runtime.cu): device status word and decode tables.
@@ -237,33 +245,43 @@ int* runtime_status_ptr();
 const E8pTables* runtime_e8p_tables();
 cudaError_t runtime_ensure_init();
 
+__device__ __forceinline__ void e8p_smem_init(E8pSmem* sm, const E8pTables* __restrict__ g,
+                                              int tid, int nthreads) {
+  for (int i = tid; i < 256; i += nthreads) {
+    sm->pos[i] = g->pos[i];
+    const uint32_t t = static_cast<uint32_t>(i) ^ (__popc(i) & 1u), t2 = t >> 2;
+    // coordinate c flips with bit {0,4,1,5,2,6,3,7}[c]; nibble j of a PRMT selector is
+    // j (take the "pos" byte) or j + 4 (take the "neg" byte)
+    const uint32_t lo = 0x3210u | ((t & 0x11u) << 2) | ((t & 0x22u) << 9);
+    const uint32_t hi = 0x3210u | ((t2 & 0x11u) << 2) | ((t2 & 0x22u) << 9);
+    sm->sel[i] = lo | (hi << 16);
+  }
+}
+
 // -> biased coordinate bytes (+/-basis + 24) and the parity bit of one 16-bit code
-__device__ __forceinline__ void e8p_select(uint32_t code, const uint4* __restrict__ table,
+__device__ __forceinline__ void e8p_select(uint32_t code, const E8pSmem* __restrict__ sm,
                                            uint32_t& lo, uint32_t& hi, uint32_t& par) {
   const uint32_t s = code & 0xffu;
   par = __popc(s) & 1u;
-  const uint32_t t = s ^ par;
-  const uint4 e = table[(code >> 8) & 0xffu];
-  const uint32_t t2 = t >> 2;
-  // coordinate i flips with bit {0,4,1,5,2,6,3,7}[i]; nibble j of a PRMT selector is
-  // j (take the "pos" byte) or j + 4 (take the "neg" byte)
-  lo = __byte_perm(e.x, e.y, 0x3210u | ((t & 0x11u) << 2) | ((t & 0x22u) << 9));
-  hi = __byte_perm(e.z, e.w, 0x3210u | ((t2 & 0x11u) << 2) | ((t2 & 0x22u) << 9));
+  const uint2 e = sm->pos[(code >> 8) & 0xffu];
+  const uint32_t sl = sm->sel[s];
+  lo = __byte_perm(e.x, 0x30303030u - e.x, sl);
+  hi = __byte_perm(e.y, 0x30303030u - e.y, sl >> 16);
 }
 
 // One 16-bit code -> eight INT8 weights  (+/-basis) + (1 - 2*parity).
-__device__ __forceinline__ uint2 e8p_decode8(uint32_t code, const uint4* __restrict__ table) {
+__device__ __forceinline__ uint2 e8p_decode8(uint32_t code, const E8pSmem* __restrict__ sm) {
   uint32_t lo, hi, par;
-  e8p_select(code, table, lo, hi, par);
+  e8p_select(code, sm, lo, hi, par);
   const uint32_t cw = 0x69696969u - par * 0x02020202u;          // 128 - 24 + shift
   return make_uint2((lo + cw) ^ 0x80808080u, (hi + cw) ^ 0x80808080u);
 }
 
 // One Q4 word (coarse U16 low, residual U16 high) -> eight INT8 weights 4*q0 + q1.
-__device__ __forceinline__ uint2 e8p_decode_q4(uint32_t word, const uint4* __restrict__ table) {
+__device__ __forceinline__ uint2 e8p_decode_q4(uint32_t word, const E8pSmem* __restrict__ sm) {
   uint32_t l0, h0, p0, l1, h1, p1;
-  e8p_select(word & 0xffffu, table, l0, h0, p0);
-  e8p_select(word >> 16, table, l1, h1, p1);
+  e8p_select(word & 0xffffu, sm, l0, h0, p0);
+  e8p_select(word >> 16, sm, l1, h1, p1);
   // 4*(b0+24) + (b1+24) + c = 4*q0 + q1 + 128  with  c = 128 - 120 + 4*s0 + s1
   const uint32_t cw = 0x0d0d0d0du - p0 * 0x08080808u - p1 * 0x02020202u;
   return make_uint2(((l0 << 2) + l1 + cw) ^ 0x80808080u, ((h0 << 2) + h1 + cw) ^ 0x80808080u);

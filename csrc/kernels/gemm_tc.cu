@@ -3,9 +3,9 @@
 // One CTA computes a (MT*128) x 128 output tile, MT = 1 or 2 accumulators in TMEM that
 // share every decoded weight tile.  Warp 0 streams operand tiles with TMA (activations
 // always; INT8 weights for W8; the packed E8P codes as one contiguous bulk copy per
-// k-block for Q4/Q2).  Warps 2-9 expand the lattice codes into an INT8 weight tile in the
+// k-block for Q4/Q2).  Warps 2-17 expand the lattice codes into an INT8 weight tile in the
 // 128-byte-swizzled K-major layout the tensor core reads, warp 1 issues tcgen05.mma
-// kind::i8 into TMEM, and warps 2-9 finally read TMEM back, apply the two scales and
+// kind::i8 into TMEM, and warps 2-17 finally read TMEM back, apply the two scales and
 // store FP16/FP32.  INT4 tensor-core MMA (the reference's fastest path,
 // kernels/cuda/model/e8p_core.py:15-33) does not exist on tcgen05, so both E8P formats go
 // through INT8 operands.  Replaces e8p_q4.projection (kernels/cuda/model/e8p_q4.py:144-265),
@@ -26,7 +26,7 @@ namespace tc {
 
 constexpr int BM = 128, BN = 128, BK = 128;
 constexpr int TILE_BYTES = 128 * 128;        // one INT8 operand tile
-constexpr int PRODUCERS = 256;               // warps 2..9
+constexpr int PRODUCERS = 512;               // warps 2..17
 constexpr int THREADS = 64 + PRODUCERS;
 
 template <int FMT, int MT>
@@ -56,7 +56,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   unsigned char* a_s = smem + L::A_OFF;
   unsigned char* b_s = smem + L::B_OFF;
   unsigned char* code_s = smem + L::CODE_OFF;
-  uint4* lut = reinterpret_cast<uint4*>(smem + L::LUT_OFF);
+  E8pSmem* lut = reinterpret_cast<E8pSmem*>(smem + L::LUT_OFF);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* tma_full = bars;                 // [STAGES]
   uint64_t* b_full = bars + STAGES;          // [STAGES]
@@ -86,8 +86,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     tmem_relinquish();
   }
   if (FMT != 0 && warp >= 2) {
-    const int t = threadIdx.x - 64;
-    lut[t] = tables->pairs[t];               // 256 producer threads, 256 entries
+    e8p_smem_init(lut, tables, threadIdx.x - 64, PRODUCERS);
   }
   tc_fence_before();
   __syncthreads();
@@ -149,10 +148,10 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
       if (ok) tc_commit(tmem_full);
     }
   } else {
-    const int t = threadIdx.x - 64;                     // 0..255
+    const int t = threadIdx.x - 64;                     // 0..511
     bool ok = true;
     if (FMT != 0) {
-      const int chunk = t & 7, rbase = t >> 3;          // 32 rows per pass, 4 passes
+      const int chunk = t & 7, rbase = t >> 3;          // 64 rows per pass, 2 passes
       for (int kb = 0; kb < kblocks; ++kb) {
         const int s = kb % STAGES;
         const uint32_t ph = (kb / STAGES) & 1;
@@ -163,8 +162,8 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
         const unsigned char* cs = code_s + s * L::CODE_BYTES;
         unsigned char* bs = b_s + s * TILE_BYTES;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int row = rbase + 32 * i;
+        for (int i = 0; i < 2; ++i) {
+          const int row = rbase + 64 * i;
           uint4 v = make_uint4(0, 0, 0, 0);
           if (row < rows_valid) {
             if (FMT == 1) {
@@ -190,14 +189,14 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     if (ok) {
       tc_fence_after();
       const int quad = warp & 3;                          // TMEM lane quadrant of this warp
-      const int half = (warp - 2) >> 2;                   // which 64 columns of each tile
+      const int part = (warp - 2) >> 2;                   // which 32 columns of each tile
       const int row = quad * 32 + lane;
 #pragma unroll 1
       for (int mt = 0; mt < MT; ++mt) {
         const int m = m0 + mt * BM + row;
         const float sa = m < M ? a_scale[m] : 0.f;
 #pragma unroll 1
-        for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
+        for (int c0 = part * 32; c0 < part * 32 + 32; c0 += 32) {
           uint32_t r[32];
           tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + mt * BN + c0, r);
           tc_wait_ld();
@@ -263,7 +262,10 @@ int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w
 template <int FMT>
 int launch_fmt(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale,
                void* out, int M, int N, int K, int out_f32, cudaStream_t stream) {
-  if (M > BM)
+  // two accumulators halve the decode work per MAC, but only pay off once the grid
+  // still covers the 148 SMs
+  const long ctas2 = static_cast<long>((N + BN - 1) / BN) * ((M + 2 * BM - 1) / (2 * BM));
+  if (M > BM && ctas2 >= 120)
     return out_f32 ? launch<FMT, true, 2>(a, a_scale, w, w_scale, out, M, N, K, stream)
                    : launch<FMT, false, 2>(a, a_scale, w, w_scale, out, M, N, K, stream);
   return out_f32 ? launch<FMT, true, 1>(a, a_scale, w, w_scale, out, M, N, K, stream)

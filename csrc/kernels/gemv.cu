@@ -32,7 +32,10 @@ __device__ __forceinline__ void store_row(void* out, int out_f32, int m, int n, 
   else reinterpret_cast<__half*>(out)[static_cast<size_t>(m) * N + n] = __float2half_rn(v);
 }
 
-// FMT 1: Q4 (U32 codes, 8 rows per CTA, 4 lanes per row); FMT 2: Q2 (U16 codes, 16 rows, 2 lanes).
+// FMT 1: Q4 (U32 codes, 8 rows per group, 4 lanes per row); FMT 2: Q2 (U16 codes, 16 rows,
+// 2 lanes).  CTAs are persistent over row groups (decode tables and activations are staged
+// once); inside a group the 8 warps split the k-blocks, and every lane keeps DEPTH 16-byte
+// code loads of the next batch in flight while it decodes the current one.
 template <int FMT, int MT>
 __global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
     const int8_t* __restrict__ a, const float* __restrict__ a_scale, const uint4* __restrict__ w,
@@ -41,74 +44,104 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
   constexpr int ROWS = FMT == 1 ? 8 : 16;
   constexpr int LPR = 32 / ROWS;                 // lanes per row
   constexpr int WPL = 128 / LPR;                 // weights per lane per k-block
+  constexpr int DEPTH = 4;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  uint4* table = reinterpret_cast<uint4*>(smem_raw);
+  E8pSmem* table = reinterpret_cast<E8pSmem*>(smem_raw);
   int8_t* act = reinterpret_cast<int8_t*>(smem_raw) + 4096;
-  __shared__ int red[GEMV_WARPS][ROWS][MT];
+  __shared__ int red[2][GEMV_WARPS][ROWS][MT];
 
-  for (int i = threadIdx.x; i < 256; i += blockDim.x) table[i] = tables->pairs[i];
+  e8p_smem_init(table, tables, threadIdx.x, blockDim.x);
   stage_activations<MT>(act, a, M, K);
   __syncthreads();
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = lane / LPR, part = lane % LPR;
-  const int n0 = blockIdx.x * ROWS;
-  const int n = min(n0 + row, N - 1);
   const int kblocks = K / 128;
+  const int groups = (N + ROWS - 1) / ROWS;
   int acc[MT];
 #pragma unroll
   for (int m = 0; m < MT; ++m) acc[m] = 0;
 
-  // uint4 index of (kb, n, part): Q4 row = 16 words = 4 uint4; Q2 row = 16 halves = 2 uint4.
-  auto widx = [&](int kb) { return (static_cast<size_t>(kb) * N + n) * LPR + part; };
-  uint4 cur = make_uint4(0, 0, 0, 0);
-  if (warp < kblocks) cur = __ldg(w + widx(warp));
-  for (int kb = warp; kb < kblocks; kb += GEMV_WARPS) {
-    uint4 nxt = make_uint4(0, 0, 0, 0);
-    if (kb + GEMV_WARPS < kblocks) nxt = __ldg(w + widx(kb + GEMV_WARPS));
-    const int8_t* abase = act + kb * 128 + part * WPL;
-    const uint32_t words[4] = {cur.x, cur.y, cur.z, cur.w};
-    if (FMT == 1) {
+  // position of this warp in its (group, k-block batch) sequence
+  int g = blockIdx.x, kb0 = warp, parity = 0;
+  auto load_batch = [&](int gg, int kk, uint4 (&dst)[DEPTH]) {
+    const int n = min(gg * ROWS + row, N - 1);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint2 q = e8p_decode_q4(words[j], table);
+    for (int i = 0; i < DEPTH; ++i) {
+      const int kb = kk + GEMV_WARPS * i;
+      dst[i] = make_uint4(0, 0, 0, 0);
+      if (gg < groups && kb < kblocks)
+        dst[i] = __ldg(w + (static_cast<size_t>(kb) * N + n) * LPR + part);
+    }
+  };
+  uint4 cur[DEPTH], nxt[DEPTH];
+  load_batch(g, kb0, cur);
+  while (g < groups) {
+    int ng = g, nkb = kb0 + GEMV_WARPS * DEPTH;
+    if (nkb >= kblocks) {
+      ng = g + gridDim.x;
+      nkb = warp;
+    }
+    load_batch(ng, nkb, nxt);
 #pragma unroll
-        for (int m = 0; m < MT; ++m) {
-          const int2 av = *reinterpret_cast<const int2*>(abase + m * K + j * 8);
-          acc[m] = __dp4a(static_cast<int>(q.x), av.x, acc[m]);
-          acc[m] = __dp4a(static_cast<int>(q.y), av.y, acc[m]);
-        }
-      }
-    } else {
+    for (int i = 0; i < DEPTH; ++i) {
+      const int kb = kb0 + GEMV_WARPS * i;
+      if (kb < kblocks) {
+        const int8_t* abase = act + kb * 128 + part * WPL;
+        const uint32_t words[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
+        if (FMT == 1) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint32_t code = (words[j >> 1] >> ((j & 1) * 16)) & 0xffffu;
-        const uint2 q = e8p_decode8(code, table);
+          for (int j = 0; j < 4; ++j) {
+            const uint2 q = e8p_decode_q4(words[j], table);
 #pragma unroll
-        for (int m = 0; m < MT; ++m) {
-          const int2 av = *reinterpret_cast<const int2*>(abase + m * K + j * 8);
-          acc[m] = __dp4a(static_cast<int>(q.x), av.x, acc[m]);
-          acc[m] = __dp4a(static_cast<int>(q.y), av.y, acc[m]);
+            for (int m = 0; m < MT; ++m) {
+              const int2 av = *reinterpret_cast<const int2*>(abase + m * K + j * 8);
+              acc[m] = __dp4a(static_cast<int>(q.x), av.x, acc[m]);
+              acc[m] = __dp4a(static_cast<int>(q.y), av.y, acc[m]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t code = (words[j >> 1] >> ((j & 1) * 16)) & 0xffffu;
+            const uint2 q = e8p_decode8(code, table);
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+              const int2 av = *reinterpret_cast<const int2*>(abase + m * K + j * 8);
+              acc[m] = __dp4a(static_cast<int>(q.x), av.x, acc[m]);
+              acc[m] = __dp4a(static_cast<int>(q.y), av.y, acc[m]);
+            }
+          }
         }
       }
     }
-    cur = nxt;
-  }
+    if (ng != g) {
+      // group finished: combine lanes, then warps (double-buffered, one barrier per group)
 #pragma unroll
-  for (int m = 0; m < MT; ++m) {
+      for (int m = 0; m < MT; ++m) {
 #pragma unroll
-    for (int o = 1; o < LPR; o <<= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
-    if (part == 0) red[warp][row][m] = acc[m];
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i < ROWS * MT; i += blockDim.x) {
-    const int r = i / MT, m = i % MT;
-    if (n0 + r < N && m < M) {
-      int total = 0;
+        for (int o = 1; o < LPR; o <<= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
+        if (part == 0) red[parity][warp][row][m] = acc[m];
+        acc[m] = 0;
+      }
+      __syncthreads();
+      const int n0 = g * ROWS;
+      for (int i = threadIdx.x; i < ROWS * MT; i += blockDim.x) {
+        const int r = i / MT, m = i % MT;
+        if (n0 + r < N && m < M) {
+          int total = 0;
 #pragma unroll
-      for (int wv = 0; wv < GEMV_WARPS; ++wv) total += red[wv][r][m];
-      store_row<MT>(out, out_f32, m, n0 + r, N, total, __half2float(w_scale[n0 + r]), a_scale[m]);
+          for (int wv = 0; wv < GEMV_WARPS; ++wv) total += red[parity][wv][r][m];
+          store_row<MT>(out, out_f32, m, n0 + r, N, total, __half2float(w_scale[n0 + r]),
+                        a_scale[m]);
+        }
+      }
+      parity ^= 1;
     }
+    g = ng;
+    kb0 = nkb;
+#pragma unroll
+    for (int i = 0; i < DEPTH; ++i) cur[i] = nxt[i];
   }
 }
 
@@ -162,7 +195,10 @@ static int launch_e8p(const int8_t* a, const float* as, const void* w, const __h
                          200 * 1024);
     attr = true;
   }
-  e8p_gemv_kernel<FMT, MT><<<(N + ROWS - 1) / ROWS, GEMV_WARPS * 32, smem, stream>>>(
+  const int groups = (N + ROWS - 1) / ROWS;
+  const int per_sm = smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4);
+  const int grid = groups < 148 * per_sm ? groups : 148 * per_sm;
+  e8p_gemv_kernel<FMT, MT><<<grid, GEMV_WARPS * 32, smem, stream>>>(
       a, as, reinterpret_cast<const uint4*>(w), ws, out, M, N, K, out_f32, runtime_e8p_tables());
   return static_cast<int>(cudaGetLastError());
 }

@@ -31,17 +31,10 @@ cudaError_t runtime_ensure_init() {
   build_e8p_basis(g_basis);
   static E8pTables host;
   for (int i = 0; i < 256; ++i) {
-    int pos[8], neg[8];
-    for (int d = 0; d < 8; ++d) {
-      pos[d] = g_basis[i][d] + 24;
-      neg[d] = -g_basis[i][d] + 24;
-    }
-    uint4 f;
-    f.x = pack4(pos[0], pos[1], pos[2], pos[3]);
-    f.y = pack4(neg[0], neg[1], neg[2], neg[3]);
-    f.z = pack4(pos[4], pos[5], pos[6], pos[7]);
-    f.w = pack4(neg[4], neg[5], neg[6], neg[7]);
-    host.pairs[i] = f;
+    int pos[8];
+    for (int d = 0; d < 8; ++d) pos[d] = g_basis[i][d] + 24;
+    host.pos[i] = make_uint2(pack4(pos[0], pos[1], pos[2], pos[3]),
+                             pack4(pos[4], pos[5], pos[6], pos[7]));
   }
   cudaError_t e = cudaMalloc(&g_status, 4 * sizeof(int));
   if (e != cudaSuccess) return e;

@@ -32,10 +32,27 @@ def peaks():
     return 6.65e12, 1.59e15, "fallback"
 
 
+GRAPH = False
+
+
 def timed(fn, iters, warm=3):
     for _ in range(warm):
         fn(0)
     torch.cuda.synchronize()
+    if GRAPH:
+        # one graph holding `iters` launches: removes host launch overhead from the timing
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(iters):
+                fn(i)
+        g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / iters * 1e-3
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for i in range(iters):
@@ -103,6 +120,8 @@ def attn(args, dev):
 
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--graph", action="store_true",
+                    help="time the launches inside one CUDA graph (no host launch overhead)")
     sub = ap.add_subparsers(dest="cmd", required=True)
     g = sub.add_parser("gemm")
     g.add_argument("--m", type=int, default=512)
@@ -119,6 +138,8 @@ def main():
     a.add_argument("--d", type=int, default=128)
     a.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
+    global GRAPH
+    GRAPH = args.graph
     dev = torch.device("cuda:0")
     native.init()
     (gemm if args.cmd == "gemm" else attn)(args, dev)
