@@ -18,6 +18,33 @@ int orinfer_clear_status(void);
 const void* orinfer_e8p_tables_device(void); // device address of the decode tables
 int orinfer_e8p_basis_host(int8_t* out256x8);
 
+// ---- fused tensor-parallel plumbing (all pointers are device addresses; peers' buffers
+// are peer-mapped into this process).  tp <= 8.
+typedef struct OrinferPeerOut {
+  void* inbox[8];              // every rank's inbox for this op: fp16 [tp][rows_cap][n]
+  int* flag[8];                // every rank's flag array for this op: int32 [tp]
+  int* sent;                   // local sequence counter (device memory)
+  unsigned int* ticket;        // local CTA counter (device memory, zero)
+  int tp, rank, rows_cap;
+} OrinferPeerOut;
+
+typedef struct OrinferInbox {
+  const void* inbox;           // local inbox: fp16 [tp][rows_cap][n]
+  const int* flag;             // local flag array: int32 [tp]
+  int* seen;                   // local sequence counter (device memory)
+  unsigned int* ticket;        // local CTA counter (device memory, zero)
+  int tp, rows_cap;
+} OrinferInbox;
+
+int orinfer_act_prep_inbox(const OrinferInbox* inbox, float* resid, const __half* norm_w,
+                           const int8_t* signs, int8_t* q_out, float* scale_out, __half* y_out,
+                           int rows, int K, float eps, int zero_centered, cudaStream_t stream);
+// Row-parallel projection whose FP16 partial result goes to slot [rank] of every peer's
+// inbox instead of a local matrix (GEMM fused with the scatter half of an all-reduce).
+int orinfer_qgemm_peer(int fmt, const int8_t* a, const float* a_scale, const void* w,
+                       const __half* w_scale, const OrinferPeerOut* peer, int M, int N, int K,
+                       int force_path, cudaStream_t stream);
+
 // ---- row kernels
 int orinfer_embed_w8(const int* ids, const int8_t* table, const __half* scales, __half* out,
                      int rows, int hidden, int vocab, cudaStream_t stream);

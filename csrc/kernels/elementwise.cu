@@ -9,6 +9,7 @@
 #include "common.cuh"
 #include "api.h"
 #include "argmax_kernels.cuh"
+#include "tp_comm.cuh"
 
 namespace orinfer {
 
@@ -54,7 +55,7 @@ template <bool SWIGLU>
 __global__ void __launch_bounds__(256) act_prep_kernel(
     const __half* __restrict__ x, float* __restrict__ resid, const __half* __restrict__ norm_w,
     const int8_t* __restrict__ signs, int8_t* __restrict__ q_out, float* __restrict__ scale_out,
-    __half* __restrict__ y_out, int K, float eps, int zero_centered) {
+    __half* __restrict__ y_out, int K, float eps, int zero_centered, InboxIn in, int* status) {
   extern __shared__ float rowbuf[];
   __shared__ float red[32];
   const int row = blockIdx.x, tid = threadIdx.x;
@@ -77,9 +78,25 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
   } else {
     const __half* xr = x ? x + static_cast<size_t>(row) * K : nullptr;
     float* rr = resid ? resid + static_cast<size_t>(row) * K : nullptr;
+    const bool from_inbox = in.inbox != nullptr;
+    if (from_inbox) inbox_wait(in, status);       // a timed-out wait is reported; data may be stale
     for (int i = tid * 8; i < K; i += blockDim.x * 8) {
       float v[8];
-      if (xr) {
+      if (from_inbox) {
+        // sum the tp partial rows in fixed source order; bypass L1 (peers wrote this memory)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = 0.f;
+        for (int s = 0; s < in.tp; ++s) {
+          const __half* src =
+              in.inbox + (static_cast<size_t>(s) * in.rows_cap + row) * K + i;
+          const int4 raw = __ldcg(reinterpret_cast<const int4*>(src));
+          const __half* h = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] += __half2float(h[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = round_f16(v[j]);
+      } else if (xr) {
         const int4 raw = *reinterpret_cast<const int4*>(xr + i);
         const __half* h = reinterpret_cast<const __half*>(&raw);
 #pragma unroll
@@ -172,6 +189,7 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
     c.w = static_cast<signed char>(a8_code(rowbuf[i + 3], scale));
     *reinterpret_cast<char4*>(qr + i) = c;
   }
+  if (!SWIGLU && in.inbox != nullptr) inbox_consumed(in, gridDim.x);
 }
 
 // ------------------------------------------------------------------ RoPE tables
@@ -314,6 +332,11 @@ __global__ void __launch_bounds__(256) qk_rope_kv_kernel(
 
 using namespace orinfer;
 
+static int act_prep_launch(const __half* x, float* resid, const __half* norm_w, const int8_t* signs,
+                           int8_t* q_out, float* scale_out, __half* y_out, int rows, int K,
+                           float eps, int zero_centered, int swiglu, InboxIn in,
+                           cudaStream_t stream);
+
 extern "C" {
 
 int orinfer_embed_w8(const int* ids, const int8_t* table, const __half* scales, __half* out,
@@ -329,7 +352,36 @@ int orinfer_embed_w8(const int* ids, const int8_t* table, const __half* scales, 
 int orinfer_act_prep(const __half* x, float* resid, const __half* norm_w, const int8_t* signs,
                      int8_t* q_out, float* scale_out, __half* y_out, int rows, int K, float eps,
                      int zero_centered, int swiglu, cudaStream_t stream) {
+  InboxIn none{};
+  return act_prep_launch(x, resid, norm_w, signs, q_out, scale_out, y_out, rows, K, eps,
+                         zero_centered, swiglu, none, stream);
+}
+
+// Same, but the branch input is the sum of the tp partial rows in the local inbox.
+int orinfer_act_prep_inbox(const OrinferInbox* inbox, float* resid, const __half* norm_w,
+                           const int8_t* signs, int8_t* q_out, float* scale_out, __half* y_out,
+                           int rows, int K, float eps, int zero_centered, cudaStream_t stream) {
+  if (inbox == nullptr || inbox->tp < 1 || inbox->tp > TP_MAX || rows > inbox->rows_cap) return -1;
+  InboxIn in;
+  in.inbox = reinterpret_cast<const __half*>(inbox->inbox);
+  in.flag = inbox->flag;
+  in.seen = inbox->seen;
+  in.ticket = inbox->ticket;
+  in.tp = inbox->tp;
+  in.rows_cap = inbox->rows_cap;
+  return act_prep_launch(nullptr, resid, norm_w, signs, q_out, scale_out, y_out, rows, K, eps,
+                         zero_centered, 0, in, stream);
+}
+
+}  // extern "C"
+
+static int act_prep_launch(const __half* x, float* resid, const __half* norm_w, const int8_t* signs,
+                           int8_t* q_out, float* scale_out, __half* y_out, int rows, int K,
+                           float eps, int zero_centered, int swiglu, InboxIn in,
+                           cudaStream_t stream) {
   if (rows <= 0) return 0;
+  if (runtime_ensure_init() != cudaSuccess) return -2;
+  int* status = runtime_status_ptr();
   if (K % 128) return -1;
   const size_t smem = static_cast<size_t>(K) * sizeof(float);
   static bool attr_set = false;
@@ -343,12 +395,15 @@ int orinfer_act_prep(const __half* x, float* resid, const __half* norm_w, const 
   if (smem > 200 * 1024) return -1;
   if (swiglu)
     act_prep_kernel<true><<<rows, 256, smem, stream>>>(x, nullptr, nullptr, signs, q_out,
-                                                       scale_out, y_out, K, eps, zero_centered);
+                                                       scale_out, y_out, K, eps, zero_centered,
+                                                       in, status);
   else
     act_prep_kernel<false><<<rows, 256, smem, stream>>>(x, resid, norm_w, signs, q_out, scale_out,
-                                                        y_out, K, eps, zero_centered);
+                                                        y_out, K, eps, zero_centered, in, status);
   return static_cast<int>(cudaGetLastError());
 }
+
+extern "C" {
 
 int orinfer_rope_table(const int* positions, float* cosb, float* sinb, int rows, int head_dim,
                        double theta, cudaStream_t stream) {

@@ -16,11 +16,13 @@
 #include "api.h"
 #include "common.cuh"
 #include "tma.h"
+#include "tp_comm.cuh"
 
 namespace orinfer {
 
 int qgemv_dispatch(int fmt, const int8_t* a, const float* as, const void* w, const __half* ws,
-                   void* out, int M, int N, int K, int out_f32, cudaStream_t stream);
+                   void* out, int M, int N, int K, int out_f32, cudaStream_t stream,
+                   const PeerOut* peer);
 
 namespace tc {
 
@@ -48,7 +50,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
     const unsigned char* __restrict__ w, const float* __restrict__ a_scale,
     const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K,
-    const E8pTables* __restrict__ tables, int* status) {
+    const E8pTables* __restrict__ tables, int* status, PeerOut po) {
   using L = Layout<FMT, MT>;
   constexpr int STAGES = L::STAGES;
   extern __shared__ unsigned char smem_raw[];
@@ -210,7 +212,16 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
                 for (int j = 0; j < 8; ++j)
                   v[j] = (static_cast<float>(static_cast<int>(r[g * 8 + j])) *
                           __half2float(w_scale[n + j])) * sa;
-                if (OUT_F32) {
+                if (po.tp > 0) {
+                  // fused scatter: FP16 partial tile -> slot [rank] of every rank's inbox
+                  __align__(16) __half h[8];
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
+                  const size_t off =
+                      (static_cast<size_t>(po.rank) * po.rows_cap + m) * N + n;
+                  for (int d = 0; d < po.tp; ++d)
+                    *reinterpret_cast<int4*>(po.inbox[d] + off) = *reinterpret_cast<const int4*>(h);
+                } else if (OUT_F32) {
                   float* o = reinterpret_cast<float*>(out) + static_cast<size_t>(m) * N + n;
                   *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
                   *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
@@ -231,11 +242,12 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (po.tp > 0) peer_signal_done(po, gridDim.x * gridDim.y);
 }
 
 template <int FMT, bool OUT_F32, int MT>
 int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale, void* out,
-           int M, int N, int K, cudaStream_t stream) {
+           int M, int N, int K, cudaStream_t stream, const PeerOut& po) {
   using L = Layout<FMT, MT>;
   CUtensorMap ta, tb;
   if (!make_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BM, BK)) return -3;
@@ -255,21 +267,22 @@ int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w
   dim3 grid((N + BN - 1) / BN, (M + BM * MT - 1) / (BM * MT));
   qgemm_tc_kernel<FMT, OUT_F32, MT><<<grid, THREADS, L::TOTAL, stream>>>(
       ta, tb, reinterpret_cast<const unsigned char*>(w), a_scale, w_scale, out, M, N, K,
-      runtime_e8p_tables(), runtime_status_ptr());
+      runtime_e8p_tables(), runtime_status_ptr(), po);
   return static_cast<int>(cudaGetLastError());
 }
 
 template <int FMT>
 int launch_fmt(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale,
-               void* out, int M, int N, int K, int out_f32, cudaStream_t stream) {
+               void* out, int M, int N, int K, int out_f32, cudaStream_t stream,
+               const PeerOut& po) {
   // two accumulators halve the decode work per MAC, but only pay off once the grid
   // still covers the 148 SMs
   const long ctas2 = static_cast<long>((N + BN - 1) / BN) * ((M + 2 * BM - 1) / (2 * BM));
   if (M > BM && ctas2 >= 120)
-    return out_f32 ? launch<FMT, true, 2>(a, a_scale, w, w_scale, out, M, N, K, stream)
-                   : launch<FMT, false, 2>(a, a_scale, w, w_scale, out, M, N, K, stream);
-  return out_f32 ? launch<FMT, true, 1>(a, a_scale, w, w_scale, out, M, N, K, stream)
-                 : launch<FMT, false, 1>(a, a_scale, w, w_scale, out, M, N, K, stream);
+    return out_f32 ? launch<FMT, true, 2>(a, a_scale, w, w_scale, out, M, N, K, stream, po)
+                   : launch<FMT, false, 2>(a, a_scale, w, w_scale, out, M, N, K, stream, po);
+  return out_f32 ? launch<FMT, true, 1>(a, a_scale, w, w_scale, out, M, N, K, stream, po)
+                 : launch<FMT, false, 1>(a, a_scale, w, w_scale, out, M, N, K, stream, po);
 }
 
 }  // namespace tc
@@ -277,26 +290,56 @@ int launch_fmt(const int8_t* a, const float* a_scale, const void* w, const __hal
 
 using namespace orinfer;
 
-extern "C" int orinfer_qgemm(int fmt, const int8_t* a, const float* a_scale, const void* w,
-                             const __half* w_scale, void* out, int M, int N, int K, int out_f32,
-                             int force_path, cudaStream_t stream) {
+static int qgemm_any(int fmt, const int8_t* a, const float* a_scale, const void* w,
+                     const __half* w_scale, void* out, int M, int N, int K, int out_f32,
+                     int force_path, cudaStream_t stream, const PeerOut* peer) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 128 || N % 8 || fmt < 0 || fmt > 2) return -1;
   if (runtime_ensure_init() != cudaSuccess) return -2;
   const bool simt = force_path == 1 || (force_path == 0 && M <= 8);
   if (simt) {
-    // The SIMT kernel takes at most 8 rows per launch.
+    // The SIMT kernel takes at most 8 rows per launch (one launch when fused with peers,
+    // because every launch bumps the peers' sequence flags).
+    if (peer != nullptr && M > 8) return -1;
     for (int m = 0; m < M; m += 8) {
       const int rows = M - m < 8 ? M - m : 8;
       void* o = out_f32 ? static_cast<void*>(reinterpret_cast<float*>(out) + (size_t)m * N)
                         : static_cast<void*>(reinterpret_cast<__half*>(out) + (size_t)m * N);
       int r = qgemv_dispatch(fmt, a + (size_t)m * K, a_scale + m, w, w_scale, o, rows, N, K,
-                             out_f32, stream);
+                             out_f32, stream, peer);
       if (r) return r;
     }
     return 0;
   }
-  if (fmt == 0) return tc::launch_fmt<0>(a, a_scale, w, w_scale, out, M, N, K, out_f32, stream);
-  if (fmt == 1) return tc::launch_fmt<1>(a, a_scale, w, w_scale, out, M, N, K, out_f32, stream);
-  return tc::launch_fmt<2>(a, a_scale, w, w_scale, out, M, N, K, out_f32, stream);
+  PeerOut po{};
+  if (peer != nullptr) po = *peer;
+  if (fmt == 0)
+    return tc::launch_fmt<0>(a, a_scale, w, w_scale, out, M, N, K, out_f32, stream, po);
+  if (fmt == 1)
+    return tc::launch_fmt<1>(a, a_scale, w, w_scale, out, M, N, K, out_f32, stream, po);
+  return tc::launch_fmt<2>(a, a_scale, w, w_scale, out, M, N, K, out_f32, stream, po);
+}
+
+extern "C" int orinfer_qgemm(int fmt, const int8_t* a, const float* a_scale, const void* w,
+                             const __half* w_scale, void* out, int M, int N, int K, int out_f32,
+                             int force_path, cudaStream_t stream) {
+  return qgemm_any(fmt, a, a_scale, w, w_scale, out, M, N, K, out_f32, force_path, stream,
+                   nullptr);
+}
+
+extern "C" int orinfer_qgemm_peer(int fmt, const int8_t* a, const float* a_scale, const void* w,
+                                  const __half* w_scale, const OrinferPeerOut* peer, int M, int N,
+                                  int K, int force_path, cudaStream_t stream) {
+  if (peer == nullptr || peer->tp < 1 || peer->tp > TP_MAX || M > peer->rows_cap) return -1;
+  PeerOut po;
+  for (int i = 0; i < TP_MAX; ++i) {
+    po.inbox[i] = reinterpret_cast<__half*>(peer->inbox[i]);
+    po.flag[i] = peer->flag[i];
+  }
+  po.sent = peer->sent;
+  po.ticket = peer->ticket;
+  po.tp = peer->tp;
+  po.rank = peer->rank;
+  po.rows_cap = peer->rows_cap;
+  return qgemm_any(fmt, a, a_scale, w, w_scale, nullptr, M, N, K, 0, force_path, stream, &po);
 }

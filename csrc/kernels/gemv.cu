@@ -7,6 +7,7 @@
 // kernels/cuda/model/int8_projection.py:66).
 #include "api.h"
 #include "common.cuh"
+#include "tp_comm.cuh"
 
 namespace orinfer {
 
@@ -26,8 +27,15 @@ __device__ __forceinline__ void stage_activations(int8_t* dst, const int8_t* __r
 
 template <int MT>
 __device__ __forceinline__ void store_row(void* out, int out_f32, int m, int n, int N, int acc,
-                                          float sw, float sa) {
+                                          float sw, float sa, const PeerOut* po = nullptr) {
   const float v = (static_cast<float>(acc) * sw) * sa;
+  if (po != nullptr) {
+    // partial result -> slot [rank] of every rank's inbox (plain peer stores over NVLink)
+    const __half hv = __float2half_rn(v);
+    const size_t off = (static_cast<size_t>(po->rank) * po->rows_cap + m) * N + n;
+    for (int d = 0; d < po->tp; ++d) po->inbox[d][off] = hv;
+    return;
+  }
   if (out_f32) reinterpret_cast<float*>(out)[static_cast<size_t>(m) * N + n] = v;
   else reinterpret_cast<__half*>(out)[static_cast<size_t>(m) * N + n] = __float2half_rn(v);
 }
@@ -40,11 +48,12 @@ template <int FMT, int MT>
 __global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
     const int8_t* __restrict__ a, const float* __restrict__ a_scale, const uint4* __restrict__ w,
     const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K, int out_f32,
-    const E8pTables* __restrict__ tables) {
+    const E8pTables* __restrict__ tables, PeerOut po) {
   constexpr int ROWS = FMT == 1 ? 8 : 16;
   constexpr int LPR = 32 / ROWS;                 // lanes per row
   constexpr int WPL = 128 / LPR;                 // weights per lane per k-block
   constexpr int DEPTH = 4;
+  const PeerOut* peer = po.tp > 0 ? &po : nullptr;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   E8pSmem* table = reinterpret_cast<E8pSmem*>(smem_raw);
   int8_t* act = reinterpret_cast<int8_t*>(smem_raw) + 4096;
@@ -133,7 +142,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
 #pragma unroll
           for (int wv = 0; wv < GEMV_WARPS; ++wv) total += red[parity][wv][r][m];
           store_row<MT>(out, out_f32, m, n0 + r, N, total, __half2float(w_scale[n0 + r]),
-                        a_scale[m]);
+                        a_scale[m], peer);
         }
       }
       parity ^= 1;
@@ -143,20 +152,23 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
 #pragma unroll
     for (int i = 0; i < DEPTH; ++i) cur[i] = nxt[i];
   }
+  if (peer != nullptr) peer_signal_done(po, gridDim.x);
 }
 
 // W8: one warp per output row, 16 weights per lane per step.
 template <int MT>
 __global__ void __launch_bounds__(GEMV_WARPS * 32) w8_gemv_kernel(
     const int8_t* __restrict__ a, const float* __restrict__ a_scale, const int8_t* __restrict__ w,
-    const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K, int out_f32) {
+    const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K, int out_f32,
+    PeerOut po) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int8_t* act = reinterpret_cast<int8_t*>(smem_raw);
+  const PeerOut* peer = po.tp > 0 ? &po : nullptr;
   stage_activations<MT>(act, a, M, K);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * GEMV_WARPS + warp;
-  if (n >= N) return;
+  if (n < N) {
   const int8_t* wr = w + static_cast<size_t>(n) * K;
   int acc[MT];
 #pragma unroll
@@ -179,13 +191,15 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) w8_gemv_kernel(
     int v = acc[m];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    if (lane == 0 && m < M) store_row<MT>(out, out_f32, m, n, N, v, sw, a_scale[m]);
+    if (lane == 0 && m < M) store_row<MT>(out, out_f32, m, n, N, v, sw, a_scale[m], peer);
   }
+  }
+  if (peer != nullptr) peer_signal_done(po, gridDim.x);
 }
 
 template <int FMT, int MT>
 static int launch_e8p(const int8_t* a, const float* as, const void* w, const __half* ws, void* out,
-                      int M, int N, int K, int out_f32, cudaStream_t stream) {
+                      int M, int N, int K, int out_f32, cudaStream_t stream, const PeerOut& po) {
   constexpr int ROWS = FMT == 1 ? 8 : 16;
   const size_t smem = 4096 + static_cast<size_t>(MT) * K;
   if (smem > 200 * 1024) return -1;
@@ -199,13 +213,14 @@ static int launch_e8p(const int8_t* a, const float* as, const void* w, const __h
   const int per_sm = smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4);
   const int grid = groups < 148 * per_sm ? groups : 148 * per_sm;
   e8p_gemv_kernel<FMT, MT><<<grid, GEMV_WARPS * 32, smem, stream>>>(
-      a, as, reinterpret_cast<const uint4*>(w), ws, out, M, N, K, out_f32, runtime_e8p_tables());
+      a, as, reinterpret_cast<const uint4*>(w), ws, out, M, N, K, out_f32, runtime_e8p_tables(),
+      po);
   return static_cast<int>(cudaGetLastError());
 }
 
 template <int MT>
 static int launch_w8(const int8_t* a, const float* as, const void* w, const __half* ws, void* out,
-                     int M, int N, int K, int out_f32, cudaStream_t stream) {
+                     int M, int N, int K, int out_f32, cudaStream_t stream, const PeerOut& po) {
   const size_t smem = static_cast<size_t>(MT) * K;
   if (smem > 200 * 1024) return -1;
   static bool attr = false;
@@ -215,18 +230,21 @@ static int launch_w8(const int8_t* a, const float* as, const void* w, const __ha
     attr = true;
   }
   w8_gemv_kernel<MT><<<(N + GEMV_WARPS - 1) / GEMV_WARPS, GEMV_WARPS * 32, smem, stream>>>(
-      a, as, reinterpret_cast<const int8_t*>(w), ws, out, M, N, K, out_f32);
+      a, as, reinterpret_cast<const int8_t*>(w), ws, out, M, N, K, out_f32, po);
   return static_cast<int>(cudaGetLastError());
 }
 
 int qgemv_dispatch(int fmt, const int8_t* a, const float* as, const void* w, const __half* ws,
-                   void* out, int M, int N, int K, int out_f32, cudaStream_t stream) {
+                   void* out, int M, int N, int K, int out_f32, cudaStream_t stream,
+                   const PeerOut* peer) {
+  PeerOut po{};
+  if (peer != nullptr) po = *peer;
   if (M < 1 || M > 8 || K % 128) return -1;
 #define BY_M(FN, ...)                                            \
-  (M == 1 ? FN<__VA_ARGS__ 1>(a, as, w, ws, out, M, N, K, out_f32, stream)  \
-   : M == 2 ? FN<__VA_ARGS__ 2>(a, as, w, ws, out, M, N, K, out_f32, stream) \
-   : M <= 4 ? FN<__VA_ARGS__ 4>(a, as, w, ws, out, M, N, K, out_f32, stream) \
-            : FN<__VA_ARGS__ 8>(a, as, w, ws, out, M, N, K, out_f32, stream))
+  (M == 1 ? FN<__VA_ARGS__ 1>(a, as, w, ws, out, M, N, K, out_f32, stream, po)  \
+   : M == 2 ? FN<__VA_ARGS__ 2>(a, as, w, ws, out, M, N, K, out_f32, stream, po) \
+   : M <= 4 ? FN<__VA_ARGS__ 4>(a, as, w, ws, out, M, N, K, out_f32, stream, po) \
+            : FN<__VA_ARGS__ 8>(a, as, w, ws, out, M, N, K, out_f32, stream, po))
   if (fmt == 0) {
     if (K % 16) return -1;
     return BY_M(launch_w8, );

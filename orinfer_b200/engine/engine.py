@@ -104,6 +104,14 @@ class Engine:
         self.kv = KVPool.allocate(self.cfg, kv_pages, self.device, extra_layers=extra)
         if runner is not None:
             self.runner = runner(weights, self.kv, self.max_rows)
+        elif getattr(weights, "tp", None) is not None:
+            from ..parallel.tp_runner import TPRunner, TPTorchRunner
+            from ..parallel import fused
+            if self.on_gpu:
+                cls = fused.FusedTPRunner if fused.enabled() else TPRunner
+            else:
+                cls = TPTorchRunner
+            self.runner = cls(weights, self.kv, self.max_rows)
         elif self.on_gpu:
             from ..models.runner import ModelRunner
             self.runner = ModelRunner(weights, self.kv, self.max_rows)
@@ -374,7 +382,8 @@ class Engine:
             packet.decode_rows = n_decode
         t1 = time.monotonic()
         self.stats.batch_inputs_s += t1 - t0
-        tok, lg = self.runner.greedy(packet)
+        need = any(not self._plain(r) for r, _n, has in order if has)
+        tok, lg = self.runner.greedy(packet, need_logits=need)
         tokens = tok.cpu()                           # one readback (synchronises)
         self.stats.direct_packets += 1
         self.stats.direct_s += time.monotonic() - t1
@@ -387,9 +396,10 @@ class Engine:
         t0 = time.monotonic()
         n = len(decoders)
         bucket = next(b for b in DECODE_BUCKETS if b >= n)
-        g = self._graphs.get(bucket)
+        need = any(not self._plain(r) for r in decoders)
+        g = self._graphs.get((bucket, need))
         if g is None:
-            g = self._graphs[bucket] = _DecodeGraph(self, bucket)
+            g = self._graphs[(bucket, need)] = _DecodeGraph(self, bucket)
         pad = bucket - n
         ids = [r.pending for r in decoders] + [0] * pad
         slots = [r.slot for r in decoders] + [self.pad_slot] * pad
@@ -401,12 +411,12 @@ class Engine:
         self.stats.batch_inputs_s += t1 - t0
         if g.graph is None:
             g.trials += 1
-            self.runner.greedy(g.packet, g.logits, g.tokens)        # warm (lazy inits)
+            self.runner.greedy(g.packet, g.logits, g.tokens, need_logits=need)   # warm
             if g.trials >= 2:
                 torch.cuda.synchronize()
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph):
-                    self.runner.greedy(g.packet, g.logits, g.tokens)
+                    self.runner.greedy(g.packet, g.logits, g.tokens, need_logits=need)
                 g.graph = graph
                 self.stats.graph_captures += 1
                 self.stats.capture_s += time.monotonic() - t1
@@ -451,10 +461,14 @@ class Engine:
                 self._finish(r, "stop")
         return produced
 
+    @staticmethod
+    def _plain(r: Request) -> bool:
+        """Greedy, unconstrained, no probability report: the device argmax is the answer."""
+        return (r.sampling.is_greedy and r.constraint is None and not r.want_logprobs
+                and r.sampling.top_logprobs is None)
+
     def _sample(self, r: Request, tokens, logits, row: int) -> int:
-        plain = (r.sampling.is_greedy and r.constraint is None and not r.want_logprobs
-                 and r.sampling.top_logprobs is None)
-        if plain:
+        if self._plain(r):
             tok = int(tokens[row])
             if tok < 0:
                 r.error = "non-finite logits"

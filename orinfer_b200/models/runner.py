@@ -88,6 +88,13 @@ class Workspace:
 
     SPLIT_ROWS = 512
 
+    def attn_norm(self, rows: int, hidden: int) -> torch.Tensor:
+        """fp16 scratch [max_rows, hidden] for normalised hidden states (final norm)."""
+        if getattr(self, "_norm_buf", None) is None:
+            self._norm_buf = torch.empty(self.max_rows, hidden, dtype=torch.float16,
+                                         device=self.hidden.device)
+        return self._norm_buf
+
 
 @dataclass
 class Packet:
@@ -136,9 +143,7 @@ class ModelRunner:
                          first: bool):
         cfg, ws = self.cfg, self.ws
         h = cfg.hidden
-        q8, sc = F.act_prep(x, ws.resid, lw.in_norm,
-                            self._signs(lw.qkv), eps=cfg.eps, zero_centered=cfg.zero_centered_norm,
-                            rows=rows, q_out=ws.q8[h], scale_out=ws.scale)
+        q8, sc = self._prep(x, lw.in_norm, self._signs(lw.qkv), rows)
         qkv = self._linear(lw.qkv, q8, sc, rows, ws.qkv)
         F.qk_rope_kv(qkv, lw.q_norm if cfg.qk_norm else None, lw.k_norm if cfg.qk_norm else None,
                      ws.cos, ws.sin, p.row_req, p.row_pos, p.page_table, self.kv.k[kv_slot],
@@ -167,20 +172,34 @@ class ModelRunner:
         qd = cfg.q_heads * cfg.head_dim
         q8, sc = F.act_prep(ws.attn, None, None, self._signs(lw.o), rows=rows, q_out=ws.q8[qd],
                             scale_out=ws.scale)
-        return self._linear(lw.o, q8, sc, rows, ws.hidden)
+        return self._row_parallel("o", lw.o, q8, sc, rows)
+
+    def _reduce(self, x, rows: int):
+        """Completes a row-parallel projection (no-op without tensor parallelism)."""
+        return x
+
+    def _prep(self, x, norm_w, signs, rows: int, y_out=None):
+        """Residual add + RMSNorm + rotation + A8 of a branch output ``x`` (a tensor here;
+        tensor-parallel runners may hand over a pending all-reduce instead)."""
+        cfg, ws = self.cfg, self.ws
+        return F.act_prep(x, ws.resid, norm_w, signs, eps=cfg.eps,
+                          zero_centered=cfg.zero_centered_norm, rows=rows,
+                          q_out=ws.q8[cfg.hidden], scale_out=ws.scale, y_out=y_out)
+
+    def _row_parallel(self, name: str, lin: QLinear, q8, sc, rows: int):
+        """Row-parallel projection into the hidden buffer (then reduced across ranks)."""
+        return self._reduce(self._linear(lin, q8, sc, rows, self.ws.hidden), rows)
 
     def _dense_ffn(self, lw: LayerWeights, x, rows: int):
         cfg, ws = self.cfg, self.ws
         h = cfg.hidden
-        q8, sc = F.act_prep(x, ws.resid, lw.post_norm, self._signs(lw.gate_up), eps=cfg.eps,
-                            zero_centered=cfg.zero_centered_norm, rows=rows, q_out=ws.q8[h],
-                            scale_out=ws.scale)
+        q8, sc = self._prep(x, lw.post_norm, self._signs(lw.gate_up), rows)
         f = lw.gate_up.n // 2
         gu = self._linear(lw.gate_up, q8, sc, rows, ws.gate_up.view(-1)[: ws.max_rows * 2 * f]
                           .view(ws.max_rows, 2 * f))
         q8, sc = F.act_prep(gu, None, None, self._signs(lw.down), swiglu=True, rows=rows,
                             q_out=ws.q8[f], scale_out=ws.scale)
-        return self._linear(lw.down, q8, sc, rows, ws.hidden)
+        return self._row_parallel("down", lw.down, q8, sc, rows)
 
     # ---------------------------------------------------------------- forward
     def forward_hidden(self, p: Packet):
@@ -208,21 +227,22 @@ class ModelRunner:
         cfg, ws = self.cfg, self.ws
         x = self.forward_hidden(p)
         rows = p.rows
-        if p.logit_rows is not None:
-            sel = p.logit_rows
-            xs = x[:rows].index_select(0, sel).contiguous()
-            rs = ws.resid[:rows].index_select(0, sel).contiguous()
-            rows = sel.shape[0]
+        if p.logit_rows is not None or not isinstance(x, torch.Tensor):
+            # final norm over every row (fp16 result), then pick the rows that need logits
+            self._prep(x, self.w.final_norm, None, rows, y_out=ws.attn_norm(rows, cfg.hidden))
+            y = ws.attn_norm(rows, cfg.hidden)[:rows]
+            if p.logit_rows is not None:
+                y = y.index_select(0, p.logit_rows).contiguous()
+                rows = p.logit_rows.shape[0]
+            q8, sc = F.act_prep(y, None, None, self.w.head.signs, rows=rows,
+                                q_out=ws.q8[cfg.hidden], scale_out=ws.scale)
         else:
-            xs, rs = x, ws.resid
-        q8, sc = F.act_prep(xs, rs, self.w.final_norm, self.w.head.signs, eps=cfg.eps,
-                            zero_centered=cfg.zero_centered_norm, rows=rows,
-                            q_out=ws.q8[cfg.hidden], scale_out=ws.scale)
+            q8, sc = self._prep(x, self.w.final_norm, self.w.head.signs, rows)
         if out is None:
             out = torch.empty(rows, self.w.head.n, dtype=torch.float32, device=self.device)
         return F.qgemm(q8, sc, self.w.head.codes, self.w.head.scale, self.w.head.fmt,
                        self.w.head.n, out=out, out_f32=True, rows=rows)
 
-    def greedy(self, p: Packet, logits_out=None, token_out=None):
+    def greedy(self, p: Packet, logits_out=None, token_out=None, need_logits: bool = True):
         lg = self.logits(p, logits_out)
         return F.argmax(lg, out=token_out), lg

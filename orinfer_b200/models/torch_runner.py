@@ -87,10 +87,13 @@ class TorchRunner:
                                       None if gate is None else gate[i:i + 1])[0]
         return out
 
+    def _reduce(self, x: torch.Tensor) -> torch.Tensor:
+        return x
+
     def _ffn(self, lw: LayerWeights, y: torch.Tensor) -> torch.Tensor:
         gu = self._linear(lw.gate_up, y)
         f = gu.shape[-1] // 2
-        return self._linear(lw.down, R.silu_mul(gu[:, :f], gu[:, f:]))
+        return self._reduce(self._linear(lw.down, R.silu_mul(gu[:, :f], gu[:, f:])))
 
     def forward_hidden(self, p: Packet):
         cfg = self.cfg
@@ -104,7 +107,7 @@ class TorchRunner:
             y = R.rms_norm(resid, lw.in_norm, cfg.eps, zc)
             if lw.kind == "attn":
                 mix = self._attention(lw, self._attn_index[i], y, p, cos, sin)
-                x = self._linear(lw.o, mix)
+                x = self._reduce(self._linear(lw.o, mix))
             else:
                 x = self.layer_hooks["gdn"](self, lw, i, y, p)
             resid = resid + x
@@ -126,7 +129,7 @@ class TorchRunner:
             out[:lg.shape[0]].copy_(lg)
         return lg
 
-    def greedy(self, p: Packet, logits_out=None, token_out=None):
+    def greedy(self, p: Packet, logits_out=None, token_out=None, need_logits: bool = True):
         lg = self.logits(p, logits_out)
         tok = R.argmax_lowest(lg)
         if token_out is not None:

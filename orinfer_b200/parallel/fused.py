@@ -1,0 +1,135 @@
+"""Fused compute+collective tensor-parallel path over NVLink peer memory.
+
+Every row-parallel projection (o_proj, down_proj) is ONE kernel that multiplies on the
+tensor cores (or dp4a for decode batches) and, from its epilogue, stores its FP16 partial
+tile straight into slot ``[rank]`` of every peer's inbox with plain peer stores; the last
+CTA publishes a sequence number to the peers (release, system scope).  The all-reduce's
+reduction is fused into the consumer: the following residual-add/RMSNorm/rotate/quantise
+kernel waits (bounded) for the tp sequence flags and sums the tp partial rows in fixed
+source order.  No NCCL call and no separate reduction kernel remains on that path; NCCL
+(``TPRunner``) is kept as the baseline arm and for the tiny head merge.
+
+Buffers come from ``torch.distributed._symmetric_memory`` (cuMem handles exchanged once
+at start-up, every rank maps every peer's inbox).  Counters live in device memory, so a
+captured CUDA graph replays the protocol unchanged.  No TMA multicast is used anywhere;
+peers are only ever written with ordinary ``st.global``.
+
+Replaces collective call sites C1/C2 of the reference's TP8 plans (AllReduce after
+``wo_b`` and after the FFN: python/orinfer_build/models/deepseek_v41/build.py:1086-1110,
+1355-1364).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_int, c_uint, c_void_p
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..models.runner import KVPool
+from ..models.weights import ModelWeights, QLinear
+from ..ops import native
+from ..ops.native import FMT, check, count_launches, ptr, stream
+from .tp_runner import TPRunner
+
+
+def enabled() -> bool:
+    return os.environ.get("ORINFER_TP_FUSED", "1") != "0"
+
+
+class _PeerOut(ctypes.Structure):
+    _fields_ = [("inbox", c_void_p * 8), ("flag", c_void_p * 8), ("sent", c_void_p),
+                ("ticket", c_void_p), ("tp", c_int), ("rank", c_int), ("rows_cap", c_int)]
+
+
+class _Inbox(ctypes.Structure):
+    _fields_ = [("inbox", c_void_p), ("flag", c_void_p), ("seen", c_void_p),
+                ("ticket", c_void_p), ("tp", c_int), ("rows_cap", c_int)]
+
+
+OPS = ("o", "down")
+
+
+class PeerMemory:
+    """Symmetric allocation holding, per fused op, an inbox ``fp16 [tp][rows_cap][hidden]``
+    and a flag array ``int32 [tp]``; plus local sequence / ticket counters."""
+
+    def __init__(self, hidden: int, rows_cap: int, group, device):
+        import torch.distributed._symmetric_memory as symm
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.rows_cap = rows_cap
+        inbox_bytes = self.world * rows_cap * hidden * 2
+        inbox_bytes = (inbox_bytes + 255) // 256 * 256
+        flag_bytes = 256
+        total = len(OPS) * (inbox_bytes + flag_bytes)
+        self.buf = symm.empty(total, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        torch.cuda.synchronize()
+        self.handle = symm.rendezvous(self.buf, group=group if group is not None
+                                      else dist.group.WORLD)
+        bases = [int(p) for p in self.handle.buffer_ptrs]
+        self.local = torch.zeros(64, dtype=torch.int32, device=device)   # sent/seen/tickets
+        lp = self.local.data_ptr()
+        self.peer_out: Dict[str, _PeerOut] = {}
+        self.inbox: Dict[str, _Inbox] = {}
+        for i, op in enumerate(OPS):
+            off_inbox = i * (inbox_bytes + flag_bytes)
+            off_flag = off_inbox + inbox_bytes
+            po = _PeerOut()
+            for r in range(8):
+                po.inbox[r] = bases[r] + off_inbox if r < self.world else None
+                po.flag[r] = bases[r] + off_flag if r < self.world else None
+            po.sent = lp + (4 * i + 0) * 4
+            po.ticket = lp + (4 * i + 1) * 4
+            po.tp, po.rank, po.rows_cap = self.world, self.rank, rows_cap
+            ib = _Inbox(bases[self.rank] + off_inbox, bases[self.rank] + off_flag,
+                        lp + (4 * i + 2) * 4, lp + (4 * i + 3) * 4, self.world, rows_cap)
+            self.peer_out[op], self.inbox[op] = po, ib
+        dist.barrier(group=group)
+
+
+def _setup_lib():
+    lib = native.lib()
+    P, I = c_void_p, c_int
+    lib.orinfer_qgemm_peer.argtypes = [I, P, P, P, P, ctypes.POINTER(_PeerOut), I, I, I, I, P]
+    lib.orinfer_qgemm_peer.restype = I
+    lib.orinfer_act_prep_inbox.argtypes = [ctypes.POINTER(_Inbox), P, P, P, P, P, P, I, I,
+                                           ctypes.c_float, I, P]
+    lib.orinfer_act_prep_inbox.restype = I
+    return lib
+
+
+class FusedTPRunner(TPRunner):
+    """Tensor-parallel runner whose row-parallel projections scatter their partial results
+    to the peers from the GEMM epilogue and whose norm kernels reduce them."""
+
+    def __init__(self, weights: ModelWeights, kv: KVPool, max_rows: int, group=None):
+        super().__init__(weights, kv, max_rows, group)
+        self.lib = _setup_lib()
+        self.mem = PeerMemory(self.cfg.hidden, max_rows, group, self.device)
+
+    def _row_parallel(self, name: str, lin: QLinear, q8, sc, rows: int):
+        po = self.mem.peer_out[name]
+        check(self.lib.orinfer_qgemm_peer(FMT[lin.fmt], ptr(q8), ptr(sc), ptr(lin.codes),
+                                          ptr(lin.scale), ctypes.byref(po), rows, lin.n, lin.k, 0,
+                                          stream()), "qgemm_peer")
+        count_launches(1)
+        return name                         # a pending all-reduce, completed by _prep
+
+    def _prep(self, x, norm_w, signs, rows: int, y_out=None):
+        if isinstance(x, torch.Tensor):
+            return super()._prep(x, norm_w, signs, rows, y_out)
+        cfg, ws = self.cfg, self.ws
+        ib = self.mem.inbox[x]
+        q8, sc = ws.q8[cfg.hidden], ws.scale
+        check(self.lib.orinfer_act_prep_inbox(ctypes.byref(ib), ptr(ws.resid), ptr(norm_w),
+                                              ptr(signs), ptr(q8), ptr(sc), ptr(y_out), rows,
+                                              cfg.hidden, float(cfg.eps),
+                                              int(cfg.zero_centered_norm), stream()),
+              "act_prep_inbox")
+        count_launches(1)
+        return q8, sc

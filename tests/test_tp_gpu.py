@@ -1,0 +1,104 @@
+"""Fused GEMM + peer-memory all-reduce path against the NCCL-only arm and the unsharded
+model.  world_size 1 exercises the kernels' inbox / flag protocol on a single GPU (the rank
+is its own peer); world_size 2 runs when two GPUs are visible."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from orinfer_b200.config import PRESETS
+    from orinfer_b200.models.runner import KVPool, ModelRunner, Packet
+    from orinfer_b200.models.weights import random_model
+    from orinfer_b200.ops import native
+    from orinfer_b200.parallel.fused import FusedTPRunner
+    from orinfer_b200.parallel.tp import shard_model
+    from orinfer_b200.parallel.tp_runner import TPRunner
+    native.init()
+    cfg = PRESETS["tiny"]
+    full = random_model(cfg, seed=0).to(dev)
+    shard = shard_model(full, rank, world)
+    t = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    g = torch.Generator().manual_seed(1)
+    res = {}
+    for name, cls in (("nccl", TPRunner), ("fused", FusedTPRunner)):
+        runner = cls(shard, KVPool.allocate(shard.config, 6, dev), 256)
+        outs = []
+        gg = torch.Generator().manual_seed(1)
+        n = 150                                          # tensor-core GEMM path
+        ids = torch.randint(0, cfg.vocab, (n,), generator=gg, dtype=torch.int32).to(dev)
+        p = Packet(ids, t([0] * n), t(list(range(n))), t([[1, 2]]), n, n,
+                   torch.tensor([n - 1], device=dev))
+        tok, lg = runner.greedy(p)
+        outs.append((tok.cpu(), lg.cpu()))
+        for step in range(3):                            # dp4a decode path, twice-used inboxes
+            p = Packet(tok.clone(), t([0]), t([n + step]), t([[1, 2]]), 1, n + step + 1)
+            tok, lg = runner.greedy(p)
+            outs.append((tok.cpu(), lg.cpu()))
+        # graph replay of the decode step with changed inputs
+        if name == "fused":
+            ids1, pos1 = t([5]), t([n + 3])
+            pk = Packet(ids1, t([0]), pos1, t([[1, 2]]), 1, 256)
+            lgb = torch.empty(1, cfg.vocab, device=dev)
+            tkb = torch.empty(1, dtype=torch.int32, device=dev)
+            runner.greedy(pk, lgb, tkb)
+            torch.cuda.synchronize()
+            dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                runner.greedy(pk, lgb, tkb)
+            for tokv in (7, 11):
+                ids1.fill_(tokv)
+                graph.replay()
+                torch.cuda.synchronize()
+                eager_tok, eager_lg = runner.greedy(pk)
+                assert torch.equal(eager_tok, tkb) and torch.allclose(eager_lg, lgb)
+        res[name] = outs
+        torch.cuda.synchronize()
+        assert native.read_status() == 0
+    if rank == 0:
+        single = ModelRunner(full, KVPool.allocate(cfg, 6, dev), 256)
+        n = 150
+        gg = torch.Generator().manual_seed(1)
+        ids = torch.randint(0, cfg.vocab, (n,), generator=gg, dtype=torch.int32).to(dev)
+        p = Packet(ids, t([0] * n), t(list(range(n))), t([[1, 2]]), n, n,
+                   torch.tensor([n - 1], device=dev))
+        _, lg = single.greedy(p)
+        res["single"] = lg.cpu()
+        torch.save(res, os.path.join(out_dir, "res.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _check(tmp_path, world):
+    port = 29600 + os.getpid() % 1000 + world
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    res = torch.load(tmp_path / "res.pt")
+    for (tn, ln), (tf, lf) in zip(res["nccl"], res["fused"]):
+        cos = torch.nn.functional.cosine_similarity(ln.flatten(), lf.flatten(), dim=0)
+        assert cos > 0.9995, cos
+    cos = torch.nn.functional.cosine_similarity(res["fused"][0][1].flatten(),
+                                                res["single"].flatten(), dim=0)
+    assert cos > 0.995, cos
+
+
+def test_fused_tp_world1(cuda, tmp_path):
+    _check(tmp_path, 1)
+
+
+def test_fused_tp_world2(cuda, tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _check(tmp_path, 2)
