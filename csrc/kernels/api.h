@@ -45,6 +45,14 @@ int orinfer_qgemm_peer(int fmt, const int8_t* a, const float* a_scale, const voi
                        const __half* w_scale, const OrinferPeerOut* peer, int M, int N, int K,
                        int force_path, cudaStream_t stream);
 
+// ---- peer-mapped buffers (CUDA IPC, one node)
+void* orinfer_peer_alloc(size_t bytes);
+int orinfer_peer_free(void* p);
+int orinfer_peer_export(void* p, unsigned char* handle64);
+int orinfer_peer_import(const unsigned char* handle64, void** out);
+int orinfer_peer_unmap(void* p);
+int orinfer_peer_copy(void* dst, const void* src, size_t bytes);
+
 // ---- row kernels
 int orinfer_embed_w8(const int* ids, const int8_t* table, const __half* scales, __half* out,
                      int rows, int hidden, int vocab, cudaStream_t stream);

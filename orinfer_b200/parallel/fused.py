@@ -9,8 +9,8 @@ kernel waits (bounded) for the tp sequence flags and sums the tp partial rows in
 source order.  No NCCL call and no separate reduction kernel remains on that path; NCCL
 (``TPRunner``) is kept as the baseline arm and for the tiny head merge.
 
-Buffers come from ``torch.distributed._symmetric_memory`` (cuMem handles exchanged once
-at start-up, every rank maps every peer's inbox).  Counters live in device memory, so a
+Buffers are cudaMalloc'd per rank and mapped into every peer with CUDA IPC handles
+exchanged once at start-up (``csrc/kernels/peer_mem.cu``).  Counters live in device memory, so a
 captured CUDA graph replays the protocol unchanged.  No TMA multicast is used anywhere;
 peers are only ever written with ordinary ``st.global``.
 
@@ -54,11 +54,19 @@ OPS = ("o", "down")
 
 
 class PeerMemory:
-    """Symmetric allocation holding, per fused op, an inbox ``fp16 [tp][rows_cap][hidden]``
-    and a flag array ``int32 [tp]``; plus local sequence / ticket counters."""
+    """One peer-mapped allocation per rank holding, per fused op, an inbox
+    ``fp16 [tp][rows_cap][hidden]`` and a flag array ``int32 [tp]``; plus local sequence
+    and ticket counters.  Handles are CUDA IPC handles exchanged with an object gather."""
 
     def __init__(self, hidden: int, rows_cap: int, group, device):
-        import torch.distributed._symmetric_memory as symm
+        lib = native.lib()
+        lib.orinfer_peer_alloc.restype = c_void_p
+        lib.orinfer_peer_alloc.argtypes = [ctypes.c_size_t]
+        lib.orinfer_peer_export.argtypes = [c_void_p, c_void_p]
+        lib.orinfer_peer_import.argtypes = [c_void_p, ctypes.POINTER(c_void_p)]
+        lib.orinfer_peer_unmap.argtypes = [c_void_p]
+        lib.orinfer_peer_free.argtypes = [c_void_p]
+        self.lib = lib
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.rows_cap = rows_cap
@@ -66,12 +74,25 @@ class PeerMemory:
         inbox_bytes = (inbox_bytes + 255) // 256 * 256
         flag_bytes = 256
         total = len(OPS) * (inbox_bytes + flag_bytes)
-        self.buf = symm.empty(total, dtype=torch.uint8, device=device)
-        self.buf.zero_()
-        torch.cuda.synchronize()
-        self.handle = symm.rendezvous(self.buf, group=group if group is not None
-                                      else dist.group.WORLD)
-        bases = [int(p) for p in self.handle.buffer_ptrs]
+        self.base = lib.orinfer_peer_alloc(total)
+        if not self.base:
+            raise native.KernelError(f"cannot allocate {total} bytes of peer memory")
+        handle = (ctypes.c_ubyte * 64)()
+        check(lib.orinfer_peer_export(self.base, handle), "peer_export")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=group)
+        bases = []
+        self._mapped = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                bases.append(int(self.base))
+                continue
+            out = c_void_p()
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+            check(lib.orinfer_peer_import(buf, ctypes.byref(out)), "peer_import")
+            bases.append(int(out.value))
+            self._mapped.append(out.value)
+        self.bases = bases
         self.local = torch.zeros(64, dtype=torch.int32, device=device)   # sent/seen/tickets
         lp = self.local.data_ptr()
         self.peer_out: Dict[str, _PeerOut] = {}
@@ -89,7 +110,16 @@ class PeerMemory:
             ib = _Inbox(bases[self.rank] + off_inbox, bases[self.rank] + off_flag,
                         lp + (4 * i + 2) * 4, lp + (4 * i + 3) * 4, self.world, rows_cap)
             self.peer_out[op], self.inbox[op] = po, ib
+        torch.cuda.synchronize()
         dist.barrier(group=group)
+
+    def close(self) -> None:
+        for p in self._mapped:
+            self.lib.orinfer_peer_unmap(p)
+        self._mapped = []
+        if self.base:
+            self.lib.orinfer_peer_free(self.base)
+            self.base = None
 
 
 def _setup_lib():

@@ -3,6 +3,7 @@ model.  world_size 1 exercises the kernels' inbox / flag protocol on a single GP
 is its own peer); world_size 2 runs when two GPUs are visible."""
 import os
 import sys
+import time
 
 import pytest
 import torch
@@ -84,7 +85,14 @@ def _worker(rank, world, port, out_dir):
 
 def _check(tmp_path, world):
     port = 29600 + os.getpid() % 1000 + world
-    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    ctx = mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=False)
+    deadline = time.time() + 240
+    while not ctx.join(timeout=5):
+        if time.time() > deadline:                 # never leave ranks behind a hung test
+            for proc in ctx.processes:
+                if proc.is_alive():
+                    proc.kill()
+            pytest.fail("tensor-parallel ranks did not finish within 240 s")
     res = torch.load(tmp_path / "res.pt")
     for (tn, ln), (tf, lf) in zip(res["nccl"], res["fused"]):
         cos = torch.nn.functional.cosine_similarity(ln.flatten(), lf.flatten(), dim=0)
