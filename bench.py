@@ -121,7 +121,7 @@ def main() -> int:
     native.init()
     cfg = PRESETS[args.model]
     if world > 1:
-        from orinfer_b200.parallel.tp import shard_model, tp_engine
+        from orinfer_b200.parallel.tp import shard_model
         weights = shard_model(random_model(cfg, seed=0, device=dev), rank, world)
     else:
         weights = random_model(cfg, seed=0, device=dev)
@@ -246,9 +246,15 @@ def main() -> int:
             "gpu_launches": int(launches), "clocks": clocks, "extra": extra,
             "kernel_status": status, "impl": "native",
         }
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Captured decode graphs hold NCCL work; tearing the communicator down under them
+        # can block for minutes.  Everything is flushed, so leave without the teardown.
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     return 0
 
 

@@ -1,0 +1,347 @@
+"""Chat request decoding: validation, defaults, template rendering, tokenisation.
+
+Behavioural contract follows the reference's codec
+(crates/orinfer-api/src/server/chat.rs:97-142 request fields with unknown fields
+rejected, :341-830 prepare; crates/orinfer-api/src/server/defaults.rs:23-110 defaults
+merging: request > deployment > model, explicit null clears a deployment default,
+grouped fields override as a group).
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import secrets
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import jinja2
+
+from ..core.sampling import SamplingOptions
+
+MAX_STOPS = 4
+MAX_TOOLS = 128
+
+
+class RequestError(ValueError):
+    """A client error: becomes an OpenAI-style error body."""
+
+    def __init__(self, message: str, param: Optional[str] = None, code: Optional[str] = None,
+                 status: int = 400, err_type: str = "invalid_request_error"):
+        super().__init__(message)
+        self.message, self.param, self.code, self.status, self.type = \
+            message, param, code, status, err_type
+
+    def body(self) -> dict:
+        return {"error": {"message": self.message, "type": self.type, "param": self.param,
+                          "code": self.code}}
+
+
+# --------------------------------------------------------------------------- tokenizers
+class ByteTokenizer:
+    """Fallback for random-init models without tokenizer assets: UTF-8 bytes are ids
+    0..255, followed by the control tokens."""
+
+    SPECIALS = ["<|endoftext|>", "<|im_start|>", "<|im_end|>", "<think>", "</think>",
+                "<tool_call>", "</tool_call>"]
+
+    def __init__(self, vocab: int):
+        if vocab < 256 + len(self.SPECIALS):
+            raise ValueError("vocabulary too small for the byte tokenizer")
+        self.vocab = vocab
+        self.special_ids = {s: 256 + i for i, s in enumerate(self.SPECIALS)}
+        self.eos_ids = (self.special_ids["<|im_end|>"], self.special_ids["<|endoftext|>"])
+
+    def encode(self, text: str) -> List[int]:
+        out: List[int] = []
+        i = 0
+        while i < len(text):
+            hit = next((s for s in self.SPECIALS if text.startswith(s, i)), None)
+            if hit:
+                out.append(self.special_ids[hit])
+                i += len(hit)
+            else:
+                out.extend(text[i].encode("utf-8"))
+                i += 1
+        return out
+
+    def token_bytes(self, tok: int) -> bytes:
+        if tok < 256:
+            return bytes([tok])
+        idx = tok - 256
+        return self.SPECIALS[idx].encode() if idx < len(self.SPECIALS) else b""
+
+    def decode(self, ids: Sequence[int]) -> str:
+        return b"".join(self.token_bytes(t) for t in ids).decode("utf-8", errors="replace")
+
+    def token_id(self, text: str) -> Optional[int]:
+        return self.special_ids.get(text)
+
+
+class HFTokenizer:
+    """``tokenizer.json`` through the ``tokenizers`` library."""
+
+    def __init__(self, path: Path, eos: Sequence[int] = ()):
+        from tokenizers import Tokenizer
+        self.tk = Tokenizer.from_file(str(path))
+        self.vocab = self.tk.get_vocab_size()
+        self.eos_ids = tuple(eos)
+
+    def encode(self, text: str) -> List[int]:
+        return self.tk.encode(text, add_special_tokens=False).ids
+
+    def decode(self, ids: Sequence[int]) -> str:
+        return self.tk.decode(list(ids), skip_special_tokens=False)
+
+    def token_bytes(self, tok: int) -> bytes:
+        return self.decode([tok]).encode("utf-8")
+
+    def token_id(self, text: str) -> Optional[int]:
+        return self.tk.token_to_id(text)
+
+
+DEFAULT_TEMPLATE = (
+    "{%- if tools %}<|im_start|>system\n# Tools\n{{ tools | tojson }}<|im_end|>\n{%- endif %}"
+    "{%- for m in messages %}<|im_start|>{{ m.role }}\n"
+    "{%- if m.content is string %}{{ m.content }}{%- else %}"
+    "{%- for part in m.content %}{%- if part.type == 'text' %}{{ part.text }}{%- endif %}"
+    "{%- endfor %}{%- endif %}"
+    "{%- if m.tool_calls %}{%- for c in m.tool_calls %}\n<tool_call>\n"
+    "{{ {'name': c.function.name, 'arguments': c.function.arguments} | tojson }}\n</tool_call>"
+    "{%- endfor %}{%- endif %}<|im_end|>\n{%- endfor %}"
+    "{%- if add_generation_prompt %}<|im_start|>assistant\n"
+    "{%- if enable_thinking %}<think>\n{%- endif %}{%- endif %}")
+
+
+def _tojson(value, indent=None):
+    # Python's default separators, as chat templates written for transformers expect
+    return json.dumps(value, ensure_ascii=False, indent=indent)
+
+
+# --------------------------------------------------------------------------- request model
+ALLOWED_FIELDS = {
+    "model", "messages", "temperature", "top_p", "top_k", "n", "stream", "stream_options",
+    "stop", "max_tokens", "max_completion_tokens", "presence_penalty", "frequency_penalty",
+    "repetition_penalty", "logit_bias", "logprobs", "top_logprobs", "seed", "user", "tools",
+    "tool_choice", "parallel_tool_calls", "response_format", "enable_thinking",
+    "chat_template_kwargs", "reasoning_effort", "thinking_token_budget", "prompt_cache_key",
+    "prompt_cache_retention", "ignore_eos", "image_processing", "store", "metadata",
+    "min_tokens", "cache_prompt",
+}
+GROUPS = [("enable_thinking", "reasoning_effort"), ("max_tokens", "max_completion_tokens")]
+
+
+def merge_defaults(request: Dict[str, Any], deployment: Dict[str, Any]) -> Dict[str, Any]:
+    """request > deployment; an explicit null in the request clears the deployment
+    default; grouped fields override as a group."""
+    out = dict(deployment)
+    for group in GROUPS:
+        if any(k in request for k in group):
+            for k in group:
+                out.pop(k, None)
+    for k, v in request.items():
+        if v is None:
+            out.pop(k, None)
+        else:
+            out[k] = v
+    return out
+
+
+@dataclass
+class ModelDefaults:
+    thinking: bool = False
+    temperature: float = 0.0
+    top_p: float = 1.0
+    top_k: int = 0
+    presence_penalty: float = 0.0
+    max_tokens: int = 1024
+
+
+@dataclass
+class Prepared:
+    """A validated request ready for the engine."""
+    prompt_ids: List[int]
+    sampling: SamplingOptions
+    max_new: int
+    stream: bool
+    include_usage: bool
+    stop_ids: Tuple[int, ...]
+    stop_strings: List[str]
+    ignore_eos: bool
+    want_logprobs: bool
+    thinking: bool
+    thinking_budget: Optional[int]
+    json_schema: Optional[dict]
+    json_object: bool
+    tools: List[dict]
+    tool_choice: Any
+    parallel_tool_calls: bool
+    model: str
+    prompt_text: str = ""
+    cache_prompt: bool = True
+
+
+class ChatCodec:
+    def __init__(self, tokenizer, template: Optional[str] = None,
+                 defaults: Optional[ModelDefaults] = None, context: int = 32768,
+                 model_name: str = "orinfer"):
+        self.tokenizer = tokenizer
+        self.env = jinja2.Environment(trim_blocks=False, lstrip_blocks=False)
+        self.env.filters["tojson"] = _tojson
+        self.template = self.env.from_string(template or DEFAULT_TEMPLATE)
+        self.defaults = defaults or ModelDefaults()
+        self.context = context
+        self.model_name = model_name
+
+    @classmethod
+    def load(cls, model_dir: Path, vocab: int, context: int, model_name: str) -> "ChatCodec":
+        model_dir = Path(model_dir)
+        template = None
+        tpl = model_dir / "chat_template.jinja"
+        if tpl.exists():
+            template = tpl.read_text()
+        eos: List[int] = []
+        gen = model_dir / "generation_config.json"
+        if gen.exists():
+            e = json.loads(gen.read_text()).get("eos_token_id", [])
+            eos = [e] if isinstance(e, int) else list(e)
+        tok_file = model_dir / "tokenizer.json"
+        tokenizer = HFTokenizer(tok_file, eos) if tok_file.exists() else ByteTokenizer(vocab)
+        if tokenizer.vocab > vocab:
+            raise ValueError("tokenizer vocabulary exceeds the model vocabulary")
+        return cls(tokenizer, template, None, context, model_name)
+
+    # ----------------------------------------------------------------- validation
+    def prepare(self, body: Dict[str, Any], deployment_defaults: Optional[dict] = None) -> Prepared:
+        if not isinstance(body, dict):
+            raise RequestError("request body must be a JSON object")
+        unknown = sorted(set(body) - ALLOWED_FIELDS)
+        if unknown:
+            raise RequestError(f"unknown field `{unknown[0]}`", param=unknown[0])
+        req = merge_defaults(body, deployment_defaults or {})
+        messages = req.get("messages")
+        if not isinstance(messages, list) or not messages:
+            raise RequestError("`messages` must be a non-empty array", param="messages")
+        for i, m in enumerate(messages):
+            if not isinstance(m, dict) or m.get("role") not in ("system", "user", "assistant",
+                                                                "tool", "developer"):
+                raise RequestError("invalid message role", param=f"messages[{i}].role")
+        if req.get("n", 1) != 1:
+            raise RequestError("only n = 1 is supported", param="n")
+        if req.get("store") is True:
+            raise RequestError("`store` is not supported", param="store")
+        meta = req.get("metadata")
+        if meta is not None and (not isinstance(meta, dict) or len(meta) > 16):
+            raise RequestError("`metadata` accepts at most 16 string pairs", param="metadata")
+        tools = req.get("tools") or []
+        if len(tools) > MAX_TOOLS:
+            raise RequestError(f"at most {MAX_TOOLS} tools", param="tools")
+        stop = req.get("stop")
+        stops = [stop] if isinstance(stop, str) else list(stop or [])
+        if len(stops) > MAX_STOPS or any(not isinstance(s, str) or not s for s in stops):
+            raise RequestError(f"`stop` accepts up to {MAX_STOPS} non-empty strings", param="stop")
+
+        kwargs = dict(req.get("chat_template_kwargs") or {})
+        effort = req.get("reasoning_effort", kwargs.get("reasoning_effort"))
+        thinking = req.get("enable_thinking", kwargs.get("enable_thinking",
+                                                         kwargs.get("thinking")))
+        if thinking is None:
+            thinking = (effort not in (None, "none")) if effort is not None \
+                else self.defaults.thinking
+        budget = req.get("thinking_token_budget", kwargs.get("thinking_budget"))
+        if budget is not None and (not isinstance(budget, int) or budget < 0):
+            raise RequestError("`thinking_token_budget` must be >= 0",
+                               param="thinking_token_budget")
+
+        d = self.defaults
+        seed = req.get("seed")
+        if seed is None:
+            seed = secrets.randbits(64)
+        elif not isinstance(seed, int) or not -2 ** 63 <= seed < 2 ** 64:
+            raise RequestError("`seed` must be a 64-bit integer", param="seed")
+        top_k = req.get("top_k", d.top_k)
+        if top_k in (-1, None):
+            top_k = 0
+        bias_in = req.get("logit_bias") or {}
+        try:
+            bias = {int(k): float(v) for k, v in bias_in.items()}
+        except (TypeError, ValueError):
+            raise RequestError("`logit_bias` maps token ids to numbers", param="logit_bias")
+        want_lp = bool(req.get("logprobs", False))
+        top_lp = req.get("top_logprobs")
+        if top_lp is not None and not want_lp:
+            raise RequestError("`top_logprobs` requires `logprobs`", param="top_logprobs")
+        sampling = SamplingOptions(
+            temperature=float(req.get("temperature", d.temperature)),
+            top_p=float(req.get("top_p", d.top_p)), top_k=int(top_k),
+            presence_penalty=float(req.get("presence_penalty", d.presence_penalty)),
+            frequency_penalty=float(req.get("frequency_penalty", 0.0)),
+            repetition_penalty=float(req.get("repetition_penalty", 1.0)),
+            seed=seed & (2 ** 64 - 1), logit_bias=bias,
+            top_logprobs=(top_lp if top_lp is not None else (0 if want_lp else None)))
+        try:
+            sampling.validate()
+        except ValueError as e:
+            name = str(e).split(":")[0]
+            raise RequestError(str(e), param=name)
+
+        rf = req.get("response_format") or {"type": "text"}
+        schema, json_object = None, False
+        if rf.get("type") == "json_schema":
+            js = rf.get("json_schema") or {}
+            schema = js.get("schema")
+            if not isinstance(schema, dict):
+                raise RequestError("`json_schema.schema` must be an object",
+                                   param="response_format")
+            _check_depth(schema)
+        elif rf.get("type") == "json_object":
+            json_object = True
+        elif rf.get("type") != "text":
+            raise RequestError("unknown response_format type", param="response_format")
+        constrained = schema is not None or json_object
+        if constrained and stops:
+            raise RequestError("`stop` cannot be combined with a constrained response",
+                               param="stop")
+
+        text = self.render(messages, tools, bool(thinking), kwargs)
+        ids = self.tokenizer.encode(text)
+        max_new = req.get("max_completion_tokens", req.get("max_tokens", d.max_tokens))
+        if not isinstance(max_new, int) or max_new < 1:
+            raise RequestError("`max_tokens` must be a positive integer", param="max_tokens")
+        if len(ids) >= self.context:
+            raise RequestError(
+                f"the prompt of {len(ids)} tokens exceeds the context window of "
+                f"{self.context} tokens", param="messages", code="context_length_exceeded")
+        max_new = min(max_new, self.context - len(ids))
+        stream_opts = req.get("stream_options") or {}
+        return Prepared(
+            prompt_ids=ids, sampling=sampling, max_new=max_new, stream=bool(req.get("stream")),
+            include_usage=bool(stream_opts.get("include_usage")),
+            stop_ids=tuple(self.tokenizer.eos_ids), stop_strings=stops,
+            ignore_eos=bool(req.get("ignore_eos", False)), want_logprobs=want_lp,
+            thinking=bool(thinking), thinking_budget=budget, json_schema=schema,
+            json_object=json_object, tools=tools, tool_choice=req.get("tool_choice", "auto"),
+            parallel_tool_calls=bool(req.get("parallel_tool_calls", True)),
+            model=req.get("model") or self.model_name, prompt_text=text,
+            cache_prompt=bool(req.get("cache_prompt", True)))
+
+    def render(self, messages, tools, thinking: bool, kwargs: Optional[dict] = None) -> str:
+        ctx = dict(kwargs or {})
+        ctx.update(messages=messages, tools=tools or None, add_generation_prompt=True,
+                   enable_thinking=thinking)
+        try:
+            return self.template.render(**ctx)
+        except jinja2.TemplateError as e:
+            raise RequestError(f"chat template failed: {e}", param="messages")
+
+
+def _check_depth(schema, depth: int = 0, limit: int = 64) -> None:
+    if depth > limit:
+        raise RequestError("JSON schema nests too deeply", param="response_format")
+    if isinstance(schema, dict):
+        for v in schema.values():
+            _check_depth(v, depth + 1, limit)
+    elif isinstance(schema, list):
+        for v in schema:
+            _check_depth(v, depth + 1, limit)
