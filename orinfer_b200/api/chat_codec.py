@@ -102,16 +102,17 @@ class HFTokenizer:
 
 
 DEFAULT_TEMPLATE = (
-    "{%- if tools %}<|im_start|>system\n# Tools\n{{ tools | tojson }}<|im_end|>\n{%- endif %}"
-    "{%- for m in messages %}<|im_start|>{{ m.role }}\n"
-    "{%- if m.content is string %}{{ m.content }}{%- else %}"
-    "{%- for part in m.content %}{%- if part.type == 'text' %}{{ part.text }}{%- endif %}"
-    "{%- endfor %}{%- endif %}"
-    "{%- if m.tool_calls %}{%- for c in m.tool_calls %}\n<tool_call>\n"
-    "{{ {'name': c.function.name, 'arguments': c.function.arguments} | tojson }}\n</tool_call>"
-    "{%- endfor %}{%- endif %}<|im_end|>\n{%- endfor %}"
-    "{%- if add_generation_prompt %}<|im_start|>assistant\n"
-    "{%- if enable_thinking %}<think>\n{%- endif %}{%- endif %}")
+    "{%- if tools -%}<|im_start|>system{{ '\\n' }}# Tools{{ '\\n' }}{{ tools | tojson }}"
+    "<|im_end|>{{ '\\n' }}{%- endif -%}"
+    "{%- for m in messages -%}<|im_start|>{{ m.role }}{{ '\\n' }}"
+    "{%- if m.content is string -%}{{ m.content }}{%- elif m.content -%}"
+    "{%- for part in m.content -%}{%- if part.type == 'text' -%}{{ part.text }}{%- endif -%}"
+    "{%- endfor -%}{%- endif -%}"
+    "{%- if m.tool_calls -%}{%- for c in m.tool_calls -%}{{ '\\n' }}<tool_call>{{ '\\n' }}"
+    "{{ {'name': c.function.name, 'arguments': c.function.arguments} | tojson }}"
+    "{{ '\\n' }}</tool_call>{%- endfor -%}{%- endif -%}<|im_end|>{{ '\\n' }}{%- endfor -%}"
+    "{%- if add_generation_prompt -%}<|im_start|>assistant{{ '\\n' }}"
+    "{%- if enable_thinking -%}<think>{{ '\\n' }}{%- endif -%}{%- endif -%}")
 
 
 def _tojson(value, indent=None):

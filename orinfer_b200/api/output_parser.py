@@ -1,0 +1,160 @@
+"""Incremental output parser: token text -> OpenAI deltas.
+
+Splits generated text into ``reasoning_content`` (inside ``<think>...</think>``),
+``content`` and ``tool_calls`` (``<tool_call>...</tool_call>`` holding either JSON
+``{"name":..., "arguments":...}`` or the XML form
+``<function=NAME><parameter=KEY>VALUE</parameter></function>``), applies stop strings,
+and withholds the longest suffix that could still become a marker or a stop string so a
+client never sees half a tag.  Finish reasons rank ``length`` > ``tool_calls`` > ``stop``.
+Behaviour follows crates/orinfer-api/src/server/output.rs:154-343,382-475 of the reference.
+"""
+
+from __future__ import annotations
+
+import json
+import re
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+THINK_OPEN, THINK_CLOSE = "<think>", "</think>"
+TOOL_OPEN, TOOL_CLOSE = "<tool_call>", "</tool_call>"
+
+
+@dataclass
+class Delta:
+    content: str = ""
+    reasoning: str = ""
+    tool_calls: List[dict] = field(default_factory=list)
+
+    def empty(self) -> bool:
+        return not (self.content or self.reasoning or self.tool_calls)
+
+
+def _partial_suffix(text: str, markers: List[str]) -> int:
+    """Length of the longest suffix of ``text`` that is a proper prefix of a marker."""
+    best = 0
+    for m in markers:
+        for n in range(min(len(m) - 1, len(text)), 0, -1):
+            if text.endswith(m[:n]):
+                best = max(best, n)
+                break
+    return best
+
+
+def parse_tool_call(body: str) -> Optional[dict]:
+    body = body.strip()
+    if body.startswith("{"):
+        try:
+            obj = json.loads(body)
+        except json.JSONDecodeError:
+            return None
+        if not isinstance(obj, dict) or "name" not in obj:
+            return None
+        args = obj.get("arguments", {})
+        return {"name": str(obj["name"]),
+                "arguments": args if isinstance(args, str) else json.dumps(args,
+                                                                           ensure_ascii=False)}
+    m = re.match(r"<function=([^>]+)>(.*)</function>\s*$", body, re.S)
+    if not m:
+        return None
+    args: Dict[str, object] = {}
+    for key, val in re.findall(r"<parameter=([^>]+)>\n?(.*?)\n?</parameter>", m.group(2), re.S):
+        try:
+            args[key] = json.loads(val)
+        except json.JSONDecodeError:
+            args[key] = val
+    return {"name": m.group(1).strip(), "arguments": json.dumps(args, ensure_ascii=False)}
+
+
+class OutputParser:
+    def __init__(self, thinking: bool = False, stops: Optional[List[str]] = None,
+                 json_mode: bool = False, tools: bool = True):
+        self.in_think = thinking            # template already opened <think>
+        self.stops = list(stops or [])
+        self.json_mode = json_mode          # tags inside a JSON body are data
+        self.tools_enabled = tools and not json_mode
+        self.buffer = ""
+        self.in_tool = False
+        self.tool_text = ""
+        self.tool_index = 0
+        self.stopped = False
+        self.saw_tool_call = False
+        self.reasoning_chars = 0
+
+    def _markers(self) -> List[str]:
+        if self.in_think:
+            return [THINK_CLOSE]
+        if self.in_tool:
+            return [TOOL_CLOSE]
+        m = list(self.stops)
+        if not self.json_mode:
+            m.append(THINK_OPEN)
+            if self.tools_enabled:
+                m.append(TOOL_OPEN)
+        return m
+
+    def feed(self, text: str, final: bool = False) -> Delta:
+        """Consume generated text; returns what may be shown now."""
+        delta = Delta()
+        if self.stopped:
+            return delta
+        self.buffer += text
+        while True:
+            markers = self._markers()
+            hit_pos, hit = -1, None
+            for m in markers:
+                p = self.buffer.find(m)
+                if p >= 0 and (hit_pos < 0 or p < hit_pos):
+                    hit_pos, hit = p, m
+            if hit is None:
+                hold = 0 if final else _partial_suffix(self.buffer, markers)
+                emit, self.buffer = self.buffer[:len(self.buffer) - hold], \
+                    self.buffer[len(self.buffer) - hold:]
+                self._emit(delta, emit)
+                break
+            self._emit(delta, self.buffer[:hit_pos])
+            self.buffer = self.buffer[hit_pos + len(hit):]
+            if hit == THINK_CLOSE:
+                self.in_think = False
+            elif hit == THINK_OPEN:
+                self.in_think = True
+            elif hit == TOOL_OPEN:
+                self.in_tool, self.tool_text = True, ""
+            elif hit == TOOL_CLOSE:
+                self.in_tool = False
+                call = parse_tool_call(self.tool_text)
+                if call is not None:
+                    self.saw_tool_call = True
+                    delta.tool_calls.append({
+                        "index": self.tool_index, "id": f"call_{self.tool_index}",
+                        "type": "function", "function": call})
+                    self.tool_index += 1
+                else:                       # malformed call is shown as text
+                    delta.content += TOOL_OPEN + self.tool_text + TOOL_CLOSE
+            else:                           # a stop string
+                self.stopped = True
+                self.buffer = ""
+                break
+        if final and self.in_tool:
+            # an unfinished call at the end of generation is returned as plain text
+            delta.content += TOOL_OPEN + self.tool_text
+            self.in_tool = False
+        return delta
+
+    def _emit(self, delta: Delta, text: str) -> None:
+        if not text:
+            return
+        if self.in_tool:
+            self.tool_text += text
+        elif self.in_think:
+            delta.reasoning += text
+            self.reasoning_chars += len(text)
+        else:
+            delta.content += text
+
+    def finish_reason(self, engine_reason: str) -> str:
+        if engine_reason == "length":
+            return "length"
+        if self.saw_tool_call:
+            return "tool_calls"
+        return "stop"

@@ -1,0 +1,100 @@
+"""Chat codec, output parser, grammar and thinking-budget units (CPU)."""
+import json
+
+import numpy as np
+import pytest
+
+from orinfer_b200.api.chat_codec import ByteTokenizer, ChatCodec, RequestError, merge_defaults
+from orinfer_b200.api.grammar import GrammarConstraint, ThinkingBudget
+from orinfer_b200.api.output_parser import OutputParser, parse_tool_call
+
+
+def _codec():
+    return ChatCodec(ByteTokenizer(1024), context=512, model_name="tiny")
+
+
+def test_defaults_merge_rules():
+    dep = {"temperature": 0.7, "enable_thinking": True, "max_tokens": 64}
+    assert merge_defaults({"temperature": None}, dep) == {"enable_thinking": True, "max_tokens": 64}
+    got = merge_defaults({"reasoning_effort": "high", "max_completion_tokens": 9}, dep)
+    assert got == {"temperature": 0.7, "reasoning_effort": "high", "max_completion_tokens": 9}
+
+
+def test_prepare_validates_and_tokenises():
+    c = _codec()
+    p = c.prepare({"messages": [{"role": "user", "content": "hi"}], "seed": -5, "top_k": -1,
+                   "max_tokens": 7, "stream": True, "stream_options": {"include_usage": True}})
+    assert p.max_new == 7 and p.stream and p.include_usage and p.sampling.top_k == 0
+    assert p.sampling.seed == (-5) & (2 ** 64 - 1)
+    assert c.tokenizer.decode(p.prompt_ids).endswith("<|im_start|>assistant\n")
+    for body, param in [({"messages": []}, "messages"), ({"messages": [{"role": "x"}]}, "messages[0].role"),
+                        ({"messages": [{"role": "user", "content": "a"}], "n": 2}, "n"),
+                        ({"messages": [{"role": "user", "content": "a"}], "bogus": 1}, "bogus"),
+                        ({"messages": [{"role": "user", "content": "a"}], "temperature": 3}, "temperature"),
+                        ({"messages": [{"role": "user", "content": "a"}], "stop": ["a"] * 5}, "stop"),
+                        ({"messages": [{"role": "user", "content": "a"}], "store": True}, "store")]:
+        with pytest.raises(RequestError) as e:
+            c.prepare(body)
+        assert e.value.param == param
+    with pytest.raises(RequestError) as e:
+        c.prepare({"messages": [{"role": "user", "content": "x" * 600}]})
+    assert e.value.code == "context_length_exceeded" and e.value.status == 400
+
+
+def test_parser_thinking_tools_and_withholding_every_split():
+    text = ("plan</think>Hello <tool_call>\n{\"name\": \"f\", \"arguments\": {\"a\": 1}}\n</tool_call>"
+            " bye STOP tail")
+    want = None
+    for cut in range(1, len(text)):
+        p = OutputParser(thinking=True, stops=["STOP"])
+        parts = [p.feed(text[:cut]), p.feed(text[cut:], final=True)]
+        got = ("".join(d.reasoning for d in parts), "".join(d.content for d in parts),
+               [c["function"] for d in parts for c in d.tool_calls], p.stopped)
+        want = want or got
+        assert got == want, cut
+    assert want[0] == "plan" and want[1] == "Hello  bye " and want[3]
+    assert want[2] == [{"name": "f", "arguments": "{\"a\": 1}"}]
+    assert OutputParser().finish_reason("length") == "length"
+
+
+def test_parser_xml_tool_call_and_json_mode():
+    call = parse_tool_call("<function=get_weather><parameter=city>\nParis\n</parameter>"
+                           "<parameter=days>3</parameter></function>")
+    assert call["name"] == "get_weather" and json.loads(call["arguments"]) == {"city": "Paris", "days": 3}
+    p = OutputParser(json_mode=True)
+    d = p.feed('{"a": "<think>x</think><tool_call>"}', final=True)
+    assert d.content == '{"a": "<think>x</think><tool_call>"}' and not d.tool_calls
+
+
+def test_grammar_constraint_masks_and_forks():
+    tok = ByteTokenizer(1024)
+    schema = {"type": "object", "properties": {"answer": {"type": "integer"}},
+              "required": ["answer"], "additionalProperties": False}
+    g = GrammarConstraint(tok, 1024, schema, tok.eos_ids)
+    allowed = lambda m, t: bool(m[t // 32] >> (t % 32) & 1)
+    m = g.mask(1024)
+    assert allowed(m, ord("{")) and not allowed(m, ord("x")) and not allowed(m, tok.eos_ids[0])
+    fork = g.fork()
+    for ch in b'{"answer":42}':
+        assert allowed(g.mask(1024), ch), chr(ch)
+        g.consume(ch)
+    m = g.mask(1024)
+    assert allowed(m, tok.eos_ids[0]) and not allowed(m, ord("a"))
+    g.consume(tok.eos_ids[0])
+    assert g.finished() and not fork.finished()
+    assert allowed(fork.mask(1024), ord("{"))
+
+
+def test_thinking_budget_forces_close():
+    tok = ByteTokenizer(1024)
+    close = tok.encode("</think>")
+    tb = ThinkingBudget(close, budget=3, max_new=20)
+    for t in (65, 66, 67):
+        assert tb.mask(1024) is None
+        tb.consume(t)
+    m = tb.mask(1024)
+    assert m is not None and int(np.unpackbits(m.view(np.uint8)).sum()) == 1
+    tb.consume(close[0])
+    assert tb.closed and tb.mask(1024) is None
+    # the budget always leaves room for the answer
+    assert ThinkingBudget(close, budget=100, max_new=10).budget == 8
