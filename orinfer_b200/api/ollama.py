@@ -1,0 +1,259 @@
+"""Ollama-compatible routes: requests are translated to the native chat request, responses
+to Ollama's NDJSON stream (``stream`` defaults to true) with nanosecond durations.
+
+Routes and semantics follow crates/orinfer-api/src/manager/ollama/mod.rs:47-59,
+ollama/request.rs:9-75,76-280 (``think``, ``format``, ``tools``, ``options``,
+``keep_alive`` forms) and ollama/response.rs:19-350; registry operations
+(``pull``/``push``/``create``), raw prompts and template overrides answer explicit errors.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import datetime as _dt
+import json
+import re
+import time
+from typing import Any, Dict, Optional
+
+from fastapi import FastAPI, Request as HttpRequest
+from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
+from .chat_codec import RequestError
+
+VERSION = "0.12.0"
+OPTION_MAP = {"temperature": "temperature", "top_p": "top_p", "top_k": "top_k", "seed": "seed",
+              "presence_penalty": "presence_penalty", "frequency_penalty": "frequency_penalty",
+              "repeat_penalty": "repetition_penalty", "num_predict": "max_tokens",
+              "stop": "stop"}
+
+
+def parse_keep_alive(value) -> Optional[float]:
+    """Seconds; None = default, negative = keep, 0 = unload now.  Accepts numbers and
+    duration strings such as ``"1h30m"`` or ``"60s"``."""
+    if value is None:
+        return None
+    if isinstance(value, (int, float)):
+        return float(value)
+    if isinstance(value, str):
+        s = value.strip()
+        if re.fullmatch(r"-?\d+(\.\d+)?", s):
+            return float(s)
+        total, pos = 0.0, 0
+        sign = -1.0 if s.startswith("-") else 1.0
+        s = s.lstrip("+-")
+        units = {"ns": 1e-9, "us": 1e-6, "ms": 1e-3, "s": 1, "m": 60, "h": 3600}
+        for m in re.finditer(r"(\d+(?:\.\d+)?)(ns|us|ms|s|m|h)", s):
+            if m.start() != pos:
+                raise RequestError("invalid keep_alive duration", param="keep_alive")
+            total += float(m.group(1)) * units[m.group(2)]
+            pos = m.end()
+        if pos != len(s) or pos == 0:
+            raise RequestError("invalid keep_alive duration", param="keep_alive")
+        return sign * total
+    raise RequestError("invalid keep_alive", param="keep_alive")
+
+
+def translate(body: Dict[str, Any], generate: bool) -> Dict[str, Any]:
+    """Ollama request -> native chat request."""
+    if not isinstance(body, dict):
+        raise RequestError("request body must be a JSON object")
+    if body.get("raw"):
+        raise RequestError("raw prompts are not supported", param="raw")
+    if body.get("template"):
+        raise RequestError("template overrides are not supported", param="template")
+    out: Dict[str, Any] = {"model": body.get("model")}
+    if generate:
+        msgs = []
+        if body.get("system"):
+            msgs.append({"role": "system", "content": body["system"]})
+        msgs.append({"role": "user", "content": body.get("prompt", "")})
+        if body.get("suffix"):
+            raise RequestError("suffix is not supported", param="suffix")
+        out["messages"] = msgs
+    else:
+        out["messages"] = body.get("messages") or []
+    opts = body.get("options") or {}
+    for k, v in opts.items():
+        if k in OPTION_MAP:
+            out[OPTION_MAP[k]] = v
+        elif k in ("num_ctx", "num_keep", "num_gpu", "num_thread", "num_batch", "min_p",
+                   "typical_p", "mirostat", "mirostat_tau", "mirostat_eta", "repeat_last_n",
+                   "tfs_z", "penalize_newline", "use_mmap", "numa", "main_gpu", "low_vram"):
+            continue                                  # accepted, no native equivalent
+        else:
+            raise RequestError(f"unknown option `{k}`", param=f"options.{k}")
+    if out.get("max_tokens") is not None and out["max_tokens"] < 0:
+        out.pop("max_tokens")
+    think = body.get("think")
+    if think is not None:
+        if isinstance(think, str):
+            out["reasoning_effort"] = think
+        else:
+            out["enable_thinking"] = bool(think)
+    fmt = body.get("format")
+    if fmt == "json":
+        out["response_format"] = {"type": "json_object"}
+    elif isinstance(fmt, dict):
+        out["response_format"] = {"type": "json_schema",
+                                  "json_schema": {"name": "format", "schema": fmt}}
+    elif fmt not in (None, ""):
+        raise RequestError("format must be \"json\" or a JSON schema", param="format")
+    if body.get("tools"):
+        out["tools"] = body["tools"]
+    if body.get("logprobs"):
+        out["logprobs"] = True
+        if body.get("top_logprobs") is not None:
+            out["top_logprobs"] = body["top_logprobs"]
+    parse_keep_alive(body.get("keep_alive"))
+    out["stream"] = body.get("stream", True)
+    return out
+
+
+def _now() -> str:
+    return _dt.datetime.now(_dt.timezone.utc).isoformat().replace("+00:00", "Z")
+
+
+def install(app: FastAPI, service) -> None:
+    def model_entry() -> dict:
+        return {"name": service.model_name, "model": service.model_name,
+                "modified_at": _now(), "size": 0, "digest": "",
+                "details": {"format": "orinfer-e8p", "family": "orinfer",
+                            "parameter_size": "", "quantization_level": "E8P-Q4A8"}}
+
+    @app.get("/")
+    async def root():
+        return PlainTextResponse("Orinfer is running")
+
+    @app.get("/api/version")
+    async def version():
+        return {"version": VERSION}
+
+    @app.get("/api/tags")
+    async def tags():
+        return {"models": [model_entry()]}
+
+    @app.get("/api/ps")
+    async def ps():
+        entry = model_entry()
+        entry["expires_at"] = _now()
+        entry["size_vram"] = 0
+        return {"models": [entry]}
+
+    @app.post("/api/show")
+    async def show(request: HttpRequest):
+        body = json.loads(await request.body() or b"{}")
+        name = body.get("model") or body.get("name")
+        if name not in (service.model_name, None):
+            return JSONResponse({"error": f"model '{name}' not found"}, status_code=404)
+        eng = service.worker.engine
+        info = {} if eng is None else {"general.architecture": eng.cfg.arch,
+                                       "context_length": eng.max_context}
+        return {"details": model_entry()["details"], "model_info": info,
+                "capabilities": ["completion", "tools", "thinking"], "template": "",
+                "parameters": ""}
+
+    async def run(request: HttpRequest, generate: bool):
+        started = time.perf_counter_ns()
+        try:
+            body = json.loads(await request.body() or b"{}")
+            if not generate and not body.get("messages") or generate and not body.get("prompt"):
+                # an empty request only loads (or unloads) the model
+                key = "response" if generate else "message"
+                val = "" if generate else {"role": "assistant", "content": ""}
+                return {"model": body.get("model"), "created_at": _now(), key: val,
+                        "done": True, "done_reason": "load"}
+            native = translate(body, generate)
+            stream = native.pop("stream")
+            native["stream"] = False
+            job = service.submit(native, asyncio.get_running_loop())
+        except RequestError as e:
+            return JSONResponse({"error": e.message}, status_code=e.status)
+        except json.JSONDecodeError:
+            return JSONResponse({"error": "invalid JSON"}, status_code=400)
+        model = body.get("model") or service.model_name
+        first_token_ns: Optional[int] = None
+
+        def frame(content="", thinking="", calls=None, done=False, final=None) -> dict:
+            out: Dict[str, Any] = {"model": model, "created_at": _now()}
+            if generate:
+                out["response"] = content
+                if thinking:
+                    out["thinking"] = thinking
+            else:
+                msg: Dict[str, Any] = {"role": "assistant", "content": content}
+                if thinking:
+                    msg["thinking"] = thinking
+                if calls:
+                    msg["tool_calls"] = [{"function": {
+                        "name": c["function"]["name"],
+                        "arguments": json.loads(c["function"]["arguments"] or "{}")}}
+                        for c in calls]
+                out["message"] = msg
+            out["done"] = done
+            if final:
+                out.update(final)
+            return out
+
+        def finals(ev) -> dict:
+            now = time.perf_counter_ns()
+            u = ev["usage"]
+            first = first_token_ns or now
+            return {"done_reason": "length" if ev["finish_reason"] == "length" else "stop",
+                    "total_duration": now - started, "load_duration": 0,
+                    "prompt_eval_count": u["prompt_tokens"],
+                    "prompt_eval_duration": first - started,
+                    "eval_count": u["completion_tokens"], "eval_duration": now - first}
+
+        if stream:
+            async def ndjson():
+                nonlocal first_token_ns
+                try:
+                    async for ev in service.events(job):
+                        if ev["type"] == "delta":
+                            first_token_ns = first_token_ns or time.perf_counter_ns()
+                            d = ev["delta"]
+                            yield json.dumps(frame(d.content, d.reasoning, d.tool_calls),
+                                             ensure_ascii=False) + "\n"
+                        elif ev["type"] == "done":
+                            yield json.dumps(frame(done=True, final=finals(ev))) + "\n"
+                        elif ev["type"] == "error":
+                            yield json.dumps({"error": ev["message"]}) + "\n"
+                finally:
+                    job.cancelled = True
+            return StreamingResponse(ndjson(), media_type="application/x-ndjson")
+        content, thinking, calls = "", "", []
+        async for ev in service.events(job):
+            if ev["type"] == "delta":
+                first_token_ns = first_token_ns or time.perf_counter_ns()
+                content += ev["delta"].content
+                thinking += ev["delta"].reasoning
+                calls += ev["delta"].tool_calls
+            elif ev["type"] == "error":
+                return JSONResponse({"error": ev["message"]}, status_code=ev.get("status", 500))
+            elif ev["type"] == "done":
+                return frame(content, thinking, calls, True, finals(ev))
+        return JSONResponse({"error": "request ended without a result"}, status_code=500)
+
+    @app.post("/api/chat")
+    async def chat(request: HttpRequest):
+        return await run(request, False)
+
+    @app.post("/api/generate")
+    async def generate(request: HttpRequest):
+        return await run(request, True)
+
+    @app.post("/api/copy")
+    async def copy(request: HttpRequest):
+        return JSONResponse({"error": "aliases need the model manager (orinfer serve "
+                                      "without a model path)"}, status_code=501)
+
+    @app.delete("/api/delete")
+    async def delete(request: HttpRequest):
+        return JSONResponse({"error": "unregistering needs the model manager"}, status_code=501)
+
+    @app.api_route("/api/{path:path}", methods=["GET", "POST", "PUT", "DELETE", "HEAD"])
+    async def unsupported(path: str):
+        return JSONResponse({"error": f"/api/{path} is not supported by orinfer (registry "
+                                      "operations such as pull, push and create are "
+                                      "unavailable)"}, status_code=501)

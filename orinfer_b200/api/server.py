@@ -1,0 +1,230 @@
+"""HTTP surface: OpenAI ``/v1/chat/completions`` (+ ``/render``), ``/v1/models``,
+``/health``, ``/metrics`` and the Ollama routes, on FastAPI.
+
+Route set, error body shape (``error.{message,type,param,code}``), 429 +
+``Retry-After: 1`` on a full queue, 503 while not ready, the SSE chunk sequence (role
+chunk, deltas, finish chunk, optional usage chunk, ``[DONE]``) and the request-id header
+follow crates/orinfer-api/src/server/mod.rs:126-163,250-343,350-556 and
+server/continuous.rs:424-449,774-776 of the reference.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import json
+import time
+import uuid
+from typing import Any, Callable, Dict, Optional
+
+from fastapi import FastAPI, Request as HttpRequest
+from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
+from .chat_codec import ChatCodec, RequestError
+from .metrics import Metrics
+from .worker import EngineWorker, Job, Lifecycle
+
+BODY_LIMIT = 32 << 20
+
+
+def _error(status: int, message: str, code: Optional[str] = None, param: Optional[str] = None,
+           err_type: str = "invalid_request_error", headers: Optional[dict] = None):
+    return JSONResponse({"error": {"message": message, "type": err_type, "param": param,
+                                   "code": code}}, status_code=status, headers=headers)
+
+
+class Service:
+    def __init__(self, engine_factory: Callable, codec: ChatCodec, model_name: str,
+                 default_request_params: Optional[dict] = None, queue_timeout_ms: int = 0,
+                 output_timeout_ms: int = 60000):
+        self.codec = codec
+        self.model_name = model_name
+        self.defaults = default_request_params or {}
+        self.metrics = Metrics()
+        self.lifecycle = Lifecycle()
+        self.worker = EngineWorker(engine_factory, codec, self.metrics, self.lifecycle,
+                                   queue_timeout_ms)
+        self.output_timeout_s = output_timeout_ms / 1e3
+        self.started = time.time()
+
+    def start(self, wait: bool = True) -> None:
+        self.worker.start()
+        if wait:
+            self.worker.ready.wait()
+
+    def stop(self, drain_ms: int = 30000) -> None:
+        self.worker.stop(drain_ms / 1e3)
+
+    # ------------------------------------------------------------------ chat
+    def submit(self, body: dict, loop) -> Job:
+        prepared = self.codec.prepare(body, self.defaults)
+        job = Job(prepared, "chatcmpl-" + uuid.uuid4().hex[:24], loop, asyncio.Queue())
+        if self.lifecycle.state != Lifecycle.READY:
+            raise RequestError("server is not ready", status=503, code="not_ready",
+                               err_type="server_error")
+        if not self.worker.try_submit(job):
+            raise RequestError("request queue is full", status=429, code="queue_full",
+                               err_type="rate_limit_error")
+        return job
+
+    async def events(self, job: Job):
+        while True:
+            try:
+                ev = await asyncio.wait_for(job.events.get(), timeout=self.output_timeout_s)
+            except asyncio.TimeoutError:
+                job.cancelled = True
+                yield {"type": "error", "status": 504, "message": "output stalled",
+                       "code": "client_output_timeout"}
+                return
+            yield ev
+            if ev["type"] in ("done", "error"):
+                return
+
+    def health(self) -> dict:
+        eng = self.worker.engine
+        out = {"status": self.lifecycle.state, "model": self.model_name,
+               "uptime_s": round(time.time() - self.started, 3),
+               "continuous_batching": True,
+               "chat_capabilities": {"chat_template_kwargs": True, "tools": True,
+                                     "json_schema": True, "logprobs": True}}
+        if self.lifecycle.reason:
+            out["reason"] = self.lifecycle.reason
+        if eng is not None:
+            out["scheduler"] = eng.stats.as_dict()
+            out["active"] = len(eng.running)
+            out["queued"] = len(eng.waiting) + self.worker.jobs.qsize()
+            if eng.prefix is not None:
+                out["prefix_cache"] = eng.prefix.statistics().__dict__
+            out["context"] = eng.max_context
+        return out
+
+
+def _chunk(job: Job, model: str, delta: dict, finish: Optional[str] = None,
+           logprobs=None, usage=None) -> str:
+    choice: Dict[str, Any] = {"index": 0, "delta": delta, "finish_reason": finish}
+    if logprobs:
+        choice["logprobs"] = {"content": logprobs}
+    body = {"id": job.rid, "object": "chat.completion.chunk", "created": int(time.time()),
+            "model": model, "choices": [choice] if delta is not None else []}
+    if usage is not None:
+        body["usage"] = usage
+    return "data: " + json.dumps(body, ensure_ascii=False) + "\n\n"
+
+
+def _delta_dict(d) -> dict:
+    out: Dict[str, Any] = {}
+    if d.content:
+        out["content"] = d.content
+    if d.reasoning:
+        out["reasoning_content"] = d.reasoning
+    if d.tool_calls:
+        out["tool_calls"] = d.tool_calls
+    return out
+
+
+def create_app(service: Service) -> FastAPI:
+    app = FastAPI(title="orinfer-b200", docs_url=None, redoc_url=None)
+
+    @app.middleware("http")
+    async def request_id(request: HttpRequest, call_next):
+        rid = request.headers.get("x-request-id") or uuid.uuid4().hex
+        size = int(request.headers.get("content-length") or 0)
+        if size > BODY_LIMIT:
+            resp = _error(413, "request body too large", code="body_too_large")
+        else:
+            resp = await call_next(request)
+        resp.headers["x-request-id"] = rid
+        return resp
+
+    @app.get("/health")
+    async def health():
+        body = service.health()
+        ok = service.lifecycle.state in (Lifecycle.READY, Lifecycle.DRAINING)
+        return JSONResponse(body, status_code=200 if ok else 503)
+
+    @app.get("/metrics")
+    async def metrics():
+        return PlainTextResponse(service.metrics.render(),
+                                 media_type="text/plain; version=0.0.4")
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": service.model_name, "object": "model",
+                                            "created": int(service.started),
+                                            "owned_by": "orinfer"}]}
+
+    async def _json(request: HttpRequest):
+        try:
+            return json.loads(await request.body())
+        except (json.JSONDecodeError, UnicodeDecodeError):
+            raise RequestError("request body is not valid JSON")
+
+    @app.post("/v1/chat/completions/render")
+    async def render(request: HttpRequest):
+        try:
+            p = service.codec.prepare(await _json(request), service.defaults)
+        except RequestError as e:
+            return JSONResponse(e.body(), status_code=e.status)
+        return {"prompt": p.prompt_text, "prompt_token_ids": p.prompt_ids,
+                "prompt_tokens": len(p.prompt_ids), "max_tokens": p.max_new}
+
+    @app.post("/v1/chat/completions")
+    async def completions(request: HttpRequest):
+        try:
+            job = service.submit(await _json(request), asyncio.get_running_loop())
+        except RequestError as e:
+            headers = {"Retry-After": "1"} if e.status == 429 else None
+            return JSONResponse(e.body(), status_code=e.status, headers=headers)
+        model = job.prepared.model
+        if job.prepared.stream:
+            async def sse():
+                try:
+                    async for ev in service.events(job):
+                        if ev["type"] == "start":
+                            yield _chunk(job, model, {"role": "assistant", "content": ""})
+                        elif ev["type"] == "delta":
+                            yield _chunk(job, model, _delta_dict(ev["delta"]),
+                                         logprobs=ev.get("logprobs"))
+                        elif ev["type"] == "done":
+                            yield _chunk(job, model, {}, finish=ev["finish_reason"])
+                            if job.prepared.include_usage:
+                                yield _chunk(job, model, None, usage=ev["usage"])
+                            yield "data: [DONE]\n\n"
+                        else:
+                            yield "data: " + json.dumps({"error": {
+                                "message": ev["message"], "type": "server_error", "param": None,
+                                "code": ev.get("code")}}) + "\n\n"
+                            yield "data: [DONE]\n\n"
+                finally:
+                    job.cancelled = True          # client went away or stream ended
+            return StreamingResponse(sse(), media_type="text/event-stream")
+        content, reasoning, calls, lps = "", "", [], []
+        async for ev in service.events(job):
+            if ev["type"] == "delta":
+                content += ev["delta"].content
+                reasoning += ev["delta"].reasoning
+                calls += ev["delta"].tool_calls
+                lps += ev.get("logprobs") or []
+            elif ev["type"] == "error":
+                return _error(ev.get("status", 500), ev["message"], ev.get("code"),
+                              err_type="server_error" if ev.get("status", 500) >= 500
+                              else "invalid_request_error")
+            elif ev["type"] == "done":
+                msg: Dict[str, Any] = {"role": "assistant", "content": content or None
+                                       if calls else content}
+                if reasoning:
+                    msg["reasoning_content"] = reasoning
+                if calls:
+                    msg["tool_calls"] = [{k: v for k, v in c.items() if k != "index"}
+                                         for c in calls]
+                choice: Dict[str, Any] = {"index": 0, "message": msg,
+                                          "finish_reason": ev["finish_reason"]}
+                if job.prepared.want_logprobs:
+                    choice["logprobs"] = {"content": lps}
+                return {"id": job.rid, "object": "chat.completion",
+                        "created": int(time.time()), "model": model, "choices": [choice],
+                        "usage": ev["usage"]}
+        return _error(500, "request ended without a result", err_type="server_error")
+
+    from .ollama import install as install_ollama
+    install_ollama(app, service)
+    return app

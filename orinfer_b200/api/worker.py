@@ -1,0 +1,258 @@
+"""The serving loop: one OS thread owns the engine (and its CUDA context); HTTP handlers
+hand it jobs through a bounded queue and receive events on per-request mailboxes.
+
+Per iteration, like the reference's continuous worker
+(crates/orinfer-api/src/server/continuous.rs:470-1009): receive waiting jobs (queue
+deadline), mark cancelled ones, admit, advance the engine one packet, deliver tokens
+through the output parser, publish statistics.  A fatal engine error flips the
+lifecycle to ``failed`` (``/health`` answers 503) and fails every open request;
+request-level errors fail only that request.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import queue
+import threading
+import time
+import traceback
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional
+
+from ..engine.engine import Engine
+from ..engine.request import Request
+from .chat_codec import ChatCodec, Prepared, RequestError
+from .grammar import GrammarConstraint, GrammarError, ThinkingBudget
+from .metrics import Metrics
+from .output_parser import Delta, OutputParser
+
+QUEUE_CAPACITY = 128
+
+
+class Lifecycle:
+    STARTING, READY, DRAINING, FAILED = "starting", "ready", "draining", "failed"
+
+    def __init__(self):
+        self.state = self.STARTING
+        self.reason: Optional[str] = None
+        self._lock = threading.Lock()
+
+    def set(self, state: str, reason: Optional[str] = None) -> None:
+        with self._lock:
+            if self.state != self.FAILED:
+                self.state, self.reason = state, reason
+
+
+@dataclass
+class Job:
+    prepared: Prepared
+    rid: str
+    loop: Optional[asyncio.AbstractEventLoop] = None
+    events: Any = None                           # asyncio.Queue or queue.Queue
+    created: float = field(default_factory=time.monotonic)
+    cancelled: bool = False
+    request: Optional[Request] = None
+    parser: Optional[OutputParser] = None
+    pending_bytes: bytes = b""
+    text_tokens: List[int] = field(default_factory=list)
+    first_token_at: Optional[float] = None
+    logprob_entries: List[dict] = field(default_factory=list)
+
+    def post(self, event: dict) -> None:
+        if self.loop is not None:
+            self.loop.call_soon_threadsafe(self.events.put_nowait, event)
+        else:
+            self.events.put_nowait(event)
+
+
+class EngineWorker(threading.Thread):
+    def __init__(self, engine_factory: Callable[[], Engine], codec: ChatCodec, metrics: Metrics,
+                 lifecycle: Lifecycle, queue_timeout_ms: int = 0):
+        super().__init__(name="orinfer-gpu", daemon=True)
+        self.engine_factory = engine_factory
+        self.engine: Optional[Engine] = None
+        self.codec = codec
+        self.metrics = metrics
+        self.lifecycle = lifecycle
+        self.jobs: "queue.Queue[Job]" = queue.Queue(maxsize=QUEUE_CAPACITY)
+        self.active: Dict[int, Job] = {}
+        self.queue_timeout_s = queue_timeout_ms / 1e3 if queue_timeout_ms else None
+        self._stop = threading.Event()
+        self.ready = threading.Event()
+
+    # ------------------------------------------------------------------ submission
+    def try_submit(self, job: Job) -> bool:
+        if self.lifecycle.state != Lifecycle.READY:
+            return False
+        try:
+            self.jobs.put_nowait(job)
+        except queue.Full:
+            return False
+        self.metrics.set("requests_waiting", self.jobs.qsize())
+        return True
+
+    def stop(self, drain_s: float = 30.0) -> None:
+        self.lifecycle.set(Lifecycle.DRAINING)
+        deadline = time.monotonic() + drain_s
+        while (self.active or not self.jobs.empty()) and time.monotonic() < deadline:
+            time.sleep(0.01)
+        self._stop.set()
+
+    # ------------------------------------------------------------------ the loop
+    def run(self) -> None:
+        try:
+            self.engine = self.engine_factory()
+            self._warmup()
+            self.lifecycle.set(Lifecycle.READY)
+            self.ready.set()
+            while not self._stop.is_set():
+                self._receive()
+                if not self.engine.has_work():
+                    try:
+                        job = self.jobs.get(timeout=0.05)
+                        self._start(job)
+                    except queue.Empty:
+                        pass
+                    continue
+                t0 = time.monotonic()
+                self.engine.step()
+                self.metrics.add("compute_seconds_total", time.monotonic() - t0)
+                self._reap()
+                self.metrics.set("requests_running", len(self.active))
+                self.metrics.set("requests_waiting", self.jobs.qsize())
+        except Exception as exc:                     # fatal: fail closed
+            self.lifecycle.set(Lifecycle.FAILED, f"{type(exc).__name__}: {exc}")
+            self.metrics.set("backend_healthy", 0)
+            traceback.print_exc()
+            for job in list(self.active.values()):
+                job.post({"type": "error", "status": 500, "message": "engine failure",
+                          "code": "engine_failure"})
+            self.ready.set()
+
+    def _warmup(self) -> None:
+        self.engine.generate([[0]], max_new=1)
+
+    def _receive(self) -> None:
+        for _ in range(QUEUE_CAPACITY):
+            try:
+                job = self.jobs.get_nowait()
+            except queue.Empty:
+                return
+            self._start(job)
+
+    def _start(self, job: Job) -> None:
+        now = time.monotonic()
+        if job.cancelled:
+            return
+        if self.queue_timeout_s is not None and now - job.created > self.queue_timeout_s:
+            job.post({"type": "error", "status": 408, "message": "request waited too long",
+                      "code": "request_queue_timeout", "retryable": True})
+            return
+        p = job.prepared
+        try:
+            constraint = self._constraint(p)
+            job.parser = OutputParser(thinking=p.thinking, stops=p.stop_strings,
+                                      json_mode=p.json_schema is not None or p.json_object,
+                                      tools=bool(p.tools))
+            req = self.engine.submit(p.prompt_ids, p.max_new, p.sampling, stop_ids=p.stop_ids,
+                                     ignore_eos=p.ignore_eos, want_logprobs=p.want_logprobs,
+                                     constraint=constraint, cache_prompt=p.cache_prompt,
+                                     on_token=lambda r, tok, j=job: self._on_token(j, r, tok))
+        except (RequestError, GrammarError, ValueError) as exc:
+            job.post({"type": "error", "status": 400, "message": str(exc),
+                      "code": getattr(exc, "code", None)})
+            self.metrics.add("request_errors_total")
+            return
+        job.request = req
+        self.active[req.rid] = job
+        self.metrics.observe("queue", now - job.created)
+        job.post({"type": "start"})
+
+    def _constraint(self, p: Prepared):
+        tok = self.codec.tokenizer
+        inner = None
+        if p.json_schema is not None or p.json_object:
+            inner = GrammarConstraint(tok, self.engine.cfg.vocab, p.json_schema, p.stop_ids)
+        if p.thinking and p.thinking_budget is not None:
+            return ThinkingBudget(tok.encode("</think>"), p.thinking_budget, p.max_new, inner)
+        if p.thinking and inner is not None:
+            return ThinkingBudget(tok.encode("</think>"), p.max_new, p.max_new, inner)
+        return inner
+
+    # ------------------------------------------------------------------ token delivery
+    def _on_token(self, job: Job, req: Request, tok: int) -> None:
+        if job.cancelled:
+            self.engine.cancel(req)
+            return
+        if job.first_token_at is None:
+            job.first_token_at = time.monotonic()
+            self.metrics.observe("time_to_first_token", job.first_token_at - job.created)
+        is_stop = tok in req.stop_ids and not req.ignore_eos
+        piece = b"" if is_stop else self.codec.tokenizer.token_bytes(tok)
+        job.pending_bytes += piece
+        text, job.pending_bytes = _utf8_prefix(job.pending_bytes)
+        if req.logprobs and job.prepared.want_logprobs and not is_stop:
+            _t, lp, top = req.logprobs[-1]
+            job.logprob_entries.append({
+                "token": piece.decode("utf-8", errors="replace"), "logprob": lp,
+                "bytes": list(piece),
+                "top_logprobs": [{"token": self.codec.tokenizer.token_bytes(i).decode(
+                    "utf-8", errors="replace"), "logprob": l,
+                    "bytes": list(self.codec.tokenizer.token_bytes(i))} for i, l in top]})
+        delta = job.parser.feed(text)
+        if not delta.empty():
+            job.post({"type": "delta", "delta": delta, "logprobs": self._take_logprobs(job)})
+        if job.parser.stopped:
+            self.engine.cancel(req)
+            req.finish_reason = "stop"
+
+    @staticmethod
+    def _take_logprobs(job: Job):
+        out, job.logprob_entries = job.logprob_entries, []
+        return out
+
+    def _reap(self) -> None:
+        for rid, job in list(self.active.items()):
+            req = job.request
+            if job.cancelled and not req.finished:
+                self.engine.cancel(req)
+            if not req.finished:
+                continue
+            del self.active[rid]
+            tail = job.parser.feed(job.pending_bytes.decode("utf-8", errors="replace"),
+                                   final=True)
+            if not tail.empty() or job.logprob_entries:
+                job.post({"type": "delta", "delta": tail, "logprobs": self._take_logprobs(job)})
+            reason = req.finish_reason or "stop"
+            if reason == "cancelled":
+                reason = "stop"
+            now = time.monotonic()
+            self.metrics.observe("latency", now - job.created)
+            if job.first_token_at:
+                self.metrics.observe("decode", now - job.first_token_at)
+            self.metrics.add("requests_total")
+            self.metrics.add("prompt_tokens_total", len(req.prompt))
+            self.metrics.add("completion_tokens_total", len(req.generated))
+            self.metrics.add("cached_tokens_total", req.cached_tokens)
+            reasoning = 0
+            if job.prepared.thinking:
+                close = self.codec.tokenizer.encode("</think>")
+                gen = req.generated
+                reasoning = next((i for i in range(len(gen)) if gen[i:i + len(close)] == close),
+                                 len(gen))
+            job.post({"type": "done", "finish_reason": job.parser.finish_reason(reason),
+                      "usage": {"prompt_tokens": len(req.prompt),
+                                "completion_tokens": len(req.generated),
+                                "total_tokens": len(req.prompt) + len(req.generated),
+                                "completion_tokens_details": {"reasoning_tokens": reasoning},
+                                "prompt_tokens_details": {"cached_tokens": req.cached_tokens}}})
+
+
+def _utf8_prefix(data: bytes):
+    """Longest prefix that is complete UTF-8, and the withheld remainder."""
+    for cut in range(len(data), max(len(data) - 4, -1), -1):
+        try:
+            return data[:cut].decode("utf-8"), data[cut:]
+        except UnicodeDecodeError:
+            continue
+    return data.decode("utf-8", errors="replace"), b""

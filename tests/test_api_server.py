@@ -1,0 +1,129 @@
+"""HTTP surface on the tiny CPU model: OpenAI chat (JSON + SSE), errors, logprobs,
+JSON-schema constraint, Ollama routes, health and metrics."""
+import json
+
+import pytest
+from fastapi.testclient import TestClient
+
+from orinfer_b200.api.chat_codec import ByteTokenizer, ChatCodec
+from orinfer_b200.api.server import Service, create_app
+from orinfer_b200.config import PRESETS, LoadOptions, SchedulerOptions
+from orinfer_b200.engine.engine import Engine
+from orinfer_b200.models.weights import random_model
+
+
+@pytest.fixture(scope="module")
+def client():
+    weights = random_model(PRESETS["tiny"], seed=0)
+
+    def factory():
+        return Engine(weights, sched=SchedulerOptions(max_active=4, prefill_chunk=64),
+                      kv_pages=24, max_context=512)
+
+    codec = ChatCodec(ByteTokenizer(1024), context=512, model_name="tiny")
+    svc = Service(factory, codec, "tiny")
+    svc.start()
+    with TestClient(create_app(svc)) as c:
+        yield c
+    svc.stop(1000)
+
+
+MSG = [{"role": "user", "content": "hello"}]
+
+
+def test_health_models_metrics(client):
+    h = client.get("/health").json()
+    assert h["status"] == "ready" and h["continuous_batching"] and "scheduler" in h
+    assert client.get("/v1/models").json()["data"][0]["id"] == "tiny"
+    r = client.get("/metrics")
+    assert "orinfer_request_latency_seconds_bucket" in r.text
+    assert "x-request-id" in r.headers
+
+
+def test_chat_completion_json_and_determinism(client):
+    body = {"messages": MSG, "max_tokens": 6, "temperature": 0, "ignore_eos": True}
+    a = client.post("/v1/chat/completions", json=body).json()
+    b = client.post("/v1/chat/completions", json=body).json()
+    assert a["object"] == "chat.completion" and a["choices"][0]["finish_reason"] == "length"
+    assert a["usage"]["completion_tokens"] == 6 and a["usage"]["prompt_tokens"] > 5
+    assert a["choices"][0]["message"]["content"] == b["choices"][0]["message"]["content"]
+    seeded = dict(body, temperature=1.0, seed=7)
+    s1 = client.post("/v1/chat/completions", json=seeded).json()
+    s2 = client.post("/v1/chat/completions", json=seeded).json()
+    assert s1["choices"][0]["message"] == s2["choices"][0]["message"]
+
+
+def test_streaming_chunk_sequence_and_usage(client):
+    body = {"messages": MSG, "max_tokens": 5, "temperature": 0, "stream": True, "ignore_eos": True,
+            "stream_options": {"include_usage": True}}
+    with client.stream("POST", "/v1/chat/completions", json=body) as r:
+        lines = [l for l in r.iter_lines() if l.startswith("data: ")]
+    assert lines[-1] == "data: [DONE]"
+    chunks = [json.loads(l[6:]) for l in lines[:-1]]
+    assert chunks[0]["choices"][0]["delta"] == {"role": "assistant", "content": ""}
+    assert chunks[-1]["choices"] == [] and chunks[-1]["usage"]["completion_tokens"] == 5
+    assert chunks[-2]["choices"][0]["finish_reason"] == "length"
+
+
+def test_validation_errors_and_context_overflow(client):
+    r = client.post("/v1/chat/completions", json={"messages": MSG, "bogus": 1})
+    assert r.status_code == 400 and r.json()["error"]["param"] == "bogus"
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user",
+                                                                "content": "x" * 600}]})
+    assert r.status_code == 400 and r.json()["error"]["code"] == "context_length_exceeded"
+    r = client.post("/v1/chat/completions", content=b"{not json")
+    assert r.status_code == 400
+    r = client.post("/v1/chat/completions/render", json={"messages": MSG})
+    assert r.json()["prompt"].endswith("<|im_start|>assistant\n")
+
+
+def test_logprobs_report(client):
+    body = {"messages": MSG, "max_tokens": 4, "temperature": 0, "logprobs": True,
+            "top_logprobs": 2, "ignore_eos": True}
+    out = client.post("/v1/chat/completions", json=body).json()
+    entries = out["choices"][0]["logprobs"]["content"]
+    assert len(entries) == 4
+    for e in entries:
+        assert e["logprob"] <= 0 and len(e["top_logprobs"]) == 2
+        assert e["top_logprobs"][0]["logprob"] >= e["top_logprobs"][1]["logprob"]
+        assert bytes(e["bytes"]).decode("utf-8", errors="replace") == e["token"]
+
+
+def test_json_schema_constrained_output(client):
+    schema = {"type": "object", "properties": {"n": {"type": "integer"}}, "required": ["n"],
+              "additionalProperties": False}
+    body = {"messages": MSG, "max_tokens": 40, "temperature": 0,
+            "response_format": {"type": "json_schema", "json_schema": {"name": "x",
+                                                                       "schema": schema}}}
+    out = client.post("/v1/chat/completions", json=body).json()
+    choice = out["choices"][0]
+    if choice["finish_reason"] == "stop":
+        assert isinstance(json.loads(choice["message"]["content"])["n"], int)
+    else:                                              # truncated JSON prefix
+        assert choice["message"]["content"].startswith("{")
+
+
+def test_ollama_routes(client):
+    assert client.get("/api/version").json()["version"]
+    assert client.get("/api/tags").json()["models"][0]["name"] == "tiny"
+    assert client.get("/").text == "Orinfer is running"
+    r = client.post("/api/chat", json={"model": "tiny", "messages": MSG, "stream": False,
+                                       "options": {"num_predict": 4, "temperature": 0}})
+    out = r.json()
+    assert out["done"] and out["eval_count"] <= 4 and "content" in out["message"]
+    with client.stream("POST", "/api/generate", json={"model": "tiny", "prompt": "hi",
+                                                      "options": {"num_predict": 3}}) as r:
+        frames = [json.loads(l) for l in r.iter_lines() if l]
+    assert frames[-1]["done"] and frames[-1]["total_duration"] > 0
+    assert client.post("/api/pull", json={}).status_code == 501
+    assert client.post("/api/chat", json={"model": "tiny", "messages": MSG,
+                                          "options": {"bogus": 1}}).status_code == 400
+    assert client.post("/api/generate", json={"model": "tiny"}).json()["done_reason"] == "load"
+
+
+def test_keep_alive_forms():
+    from orinfer_b200.api.ollama import parse_keep_alive
+    assert parse_keep_alive("1h30m") == 5400 and parse_keep_alive(-1) == -1
+    assert parse_keep_alive("60s") == 60 and parse_keep_alive("0") == 0
+    with pytest.raises(ValueError):
+        parse_keep_alive("soon")
