@@ -1,0 +1,340 @@
+"""``orinfer`` command line: serve, batch, validate-model, plan-model, run-model,
+score-model, make-model, devices, info, validate-nccl.
+
+Verbs, flags and defaults mirror the reference's CLI (crates/orinfer-cli/src/args.rs:7-111,
+serve.rs:48-260, diag.rs:8-101; flag table docs/serving.md:229-263): listen ``[::]:8088``,
+``--scheduler-policy latency|throughput``, ``--cuda-graph decode_only|full|off``,
+``--mtp-drafts auto|0..31``, ``--prefix-cache-mib 4096``, ``--kv-offload-mib 0``,
+``--max-active-requests 32``, ``--prefill-budget-ms 200``, ``--target-tpot-ms 400``,
+``--memory-reserve-mib 1024``, queue / output / drain timeouts 0 / 60000 / 30000 ms.
+``--tp N`` is this build's addition (the reference has no multi-GPU CUDA path).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import signal
+import sys
+import time
+from pathlib import Path
+
+from .config import PRESETS, GraphMode, LoadOptions, Policy, SchedulerOptions
+
+
+def _load_args(p: argparse.ArgumentParser, batch: bool = False) -> None:
+    p.add_argument("model_dir", nargs="?", help="model directory (with cache/model.json)")
+    p.add_argument("--preset", choices=sorted(PRESETS), help="random-init model of a named "
+                   "geometry instead of a model directory")
+    p.add_argument("--model", default="qwen3.8-27b", help="API model id")
+    p.add_argument("--default-request-params", default="{}")
+    p.add_argument("--scheduler-policy", default="throughput" if batch else "latency",
+                   choices=["latency", "throughput"])
+    p.add_argument("--cuda-graph", "--graph", dest="cuda_graph", default="decode_only",
+                   choices=["decode_only", "full", "off"])
+    p.add_argument("--mtp-drafts", default="auto")
+    p.add_argument("--prompt-lookup", action="store_true")
+    p.add_argument("--resident-experts", default="full")
+    p.add_argument("--verify-weights", action="store_true")
+    p.add_argument("--load-workers", type=int, default=0)
+    p.add_argument("--prefix-cache-mib", type=int, default=4096)
+    p.add_argument("--kv-offload-mib", type=int, default=0)
+    p.add_argument("--max-active-requests", type=int, default=32)
+    p.add_argument("--max-batch-tokens", type=int, default=128)
+    p.add_argument("--max-speculative-tokens", type=int, default=0)
+    p.add_argument("--prefill-budget-ms", type=float, default=200.0)
+    p.add_argument("--target-tpot-ms", type=float, default=400.0)
+    p.add_argument("--memory-reserve-mib", type=int, default=1024)
+    p.add_argument("--prefill-chunk", type=int, default=4096)
+    p.add_argument("--max-context", type=int, default=None)
+    p.add_argument("--tp", type=int, default=1)
+    p.add_argument("--device", default="cuda")
+
+
+def _options(a):
+    drafts = None if a.mtp_drafts == "auto" else int(a.mtp_drafts)
+    load = LoadOptions(cuda_graph=GraphMode(a.cuda_graph), verify_weights=a.verify_weights,
+                       load_workers=a.load_workers, prefix_cache_bytes=a.prefix_cache_mib << 20,
+                       kv_offload_bytes=a.kv_offload_mib << 20, mtp_drafts=drafts,
+                       prompt_lookup=a.prompt_lookup,
+                       resident_experts=0 if a.resident_experts == "full"
+                       else int(a.resident_experts), tp=a.tp)
+    sched = SchedulerOptions(policy=Policy(a.scheduler_policy), max_active=a.max_active_requests,
+                             max_batch_tokens=a.max_batch_tokens,
+                             max_speculative_tokens=a.max_speculative_tokens,
+                             prefill_budget_ms=a.prefill_budget_ms,
+                             target_tpot_ms=a.target_tpot_ms,
+                             memory_reserve_bytes=a.memory_reserve_mib << 20,
+                             prefill_chunk=a.prefill_chunk)
+    load.validate()
+    sched.validate()
+    return load, sched
+
+
+def _weights(a):
+    import torch
+    from .models.weights import random_model
+    dev = a.device if (a.device != "cuda" or torch.cuda.is_available()) else "cpu"
+    if a.preset:
+        return random_model(PRESETS[a.preset], seed=0, device=dev), a.preset
+    if not a.model_dir:
+        raise SystemExit("a model directory or --preset is required")
+    from .engine.checkpoint import load_model, read_descriptor
+    t0 = time.time()
+    w = load_model(a.model_dir, dev, verify=a.verify_weights)
+    print(f"MODEL READY after {time.time() - t0:.2f}s", file=sys.stderr)
+    return w, read_descriptor(a.model_dir)["name"]
+
+
+def _engine_factory(a, weights, load, sched):
+    from .engine.engine import Engine
+
+    def factory():
+        return Engine(weights, load=load, sched=sched, max_context=a.max_context)
+    return factory
+
+
+def _codec(a, weights, name):
+    from .api.chat_codec import ChatCodec
+    ctx = a.max_context or min(weights.config.max_context, 32768)
+    if a.model_dir:
+        return ChatCodec.load(Path(a.model_dir), weights.config.vocab, ctx, name)
+    from .api.chat_codec import ByteTokenizer
+    return ChatCodec(ByteTokenizer(weights.config.vocab), context=ctx, model_name=name)
+
+
+def cmd_serve(a) -> int:
+    import uvicorn
+    from .api.server import Service, create_app
+    load, sched = _options(a)
+    host, _, port = a.listen.rpartition(":")
+    host = host.strip("[]") or "::"
+    # bind first: a port conflict must fail before the GPU load starts
+    import socket
+    probe = socket.socket(socket.AF_INET6 if ":" in host else socket.AF_INET)
+    probe.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+    try:
+        probe.bind((host, int(port)))
+    except OSError as e:
+        print(f"cannot bind {a.listen}: {e}", file=sys.stderr)
+        return 2
+    probe.close()
+    weights, name = _weights(a)
+    name = a.model if a.model != "qwen3.8-27b" or not a.preset else name
+    service = Service(_engine_factory(a, weights, load, sched), _codec(a, weights, name), name,
+                      json.loads(a.default_request_params), a.queue_timeout_ms,
+                      a.output_timeout_ms)
+    service.start()
+    if service.lifecycle.state != "ready":
+        print(f"worker failed: {service.lifecycle.reason}", file=sys.stderr)
+        return 1
+    print("WARMUP READY", file=sys.stderr)
+    print(f"API READY http://{a.listen}/v1; context {service.worker.engine.max_context}; "
+          f"continuous_batching=true", file=sys.stderr)
+    server = uvicorn.Server(uvicorn.Config(create_app(service), host=host, port=int(port),
+                                           log_level="warning"))
+
+    def drain(*_):
+        service.lifecycle.set("draining")
+        server.should_exit = True
+    signal.signal(signal.SIGINT, drain)
+    signal.signal(signal.SIGTERM, drain)
+    server.run()
+    service.stop(a.drain_timeout_ms)
+    print("SCHEDULER " + json.dumps(service.worker.engine.stats.as_dict()), file=sys.stderr)
+    return 1 if service.lifecycle.state == "failed" else 0
+
+
+def cmd_batch(a) -> int:
+    from .api.batch_jsonl import BatchError, run_batch
+    load, sched = _options(a)
+    weights, name = _weights(a)
+    engine = _engine_factory(a, weights, load, sched)()
+    try:
+        counts = run_batch(engine, _codec(a, weights, name), a.input, a.output, resume=a.resume,
+                           order=a.batch_order,
+                           default_request_params=json.loads(a.default_request_params),
+                           model_id=name)
+    except BatchError as e:
+        print(f"batch failed: {e}", file=sys.stderr)
+        return 2
+    print(json.dumps(counts))
+    print("SCHEDULER " + json.dumps(engine.stats.as_dict()), file=sys.stderr)
+    return 0 if counts["failed"] == 0 else 3
+
+
+def cmd_validate_model(a) -> int:
+    from .engine.checkpoint import CheckpointError, validate_model
+    try:
+        print(json.dumps(validate_model(a.model_dir)))
+        return 0
+    except CheckpointError as e:
+        print(f"invalid model: {e}", file=sys.stderr)
+        return 1
+
+
+def cmd_plan_model(a) -> int:
+    """Static plan: geometry, per-layer projections and formats, weight / KV bytes."""
+    from .engine.checkpoint import read_descriptor
+    from .config import ModelConfig
+    from .models.runner import KVPool
+    if a.preset:
+        cfg = PRESETS[a.preset]
+    else:
+        read_descriptor(a.model_dir)
+        cfg = ModelConfig.from_json((Path(a.model_dir) / "config.json").read_text())
+    layers = [{"layer": i, "kind": "attention" if cfg.is_full_attention(i) else "gdn",
+               "ffn": "moe" if cfg.experts else "dense"} for i in range(cfg.layers)]
+    print(json.dumps({"model": cfg.name, "target": "sm_100a", "layers": layers,
+                      "kv_bytes_per_token": cfg.kv_bytes_per_token(),
+                      "kv_bytes_per_page": KVPool.bytes_per_page(cfg, cfg.mtp_layers),
+                      "programs": ["prefill", "decode", "mixed", "verify"],
+                      "graph_modes": ["decode_only", "full", "off"]}, indent=1))
+    return 0
+
+
+def cmd_run_model(a) -> int:
+    """Token-id requests from a JSON file ``{"requests":[{"id", "input_tokens",
+    "max_new_tokens"}]}``; reports prefill / decode timings per request
+    (crates/orinfer-engine/src/runtime/benchmark.rs:57-212)."""
+    import torch
+    load, sched = _options(a)
+    weights, _ = _weights(a)
+    engine = _engine_factory(a, weights, load, sched)()
+    spec = json.loads(Path(a.requests).read_text())
+    report = []
+    for item in spec["requests"]:
+        t0 = time.perf_counter()
+        req = engine.submit(item["input_tokens"], item.get("max_new_tokens", 16),
+                            ignore_eos=True)
+        while not req.generated:
+            engine.step()
+        ttft = time.perf_counter() - t0
+        while not req.finished:
+            engine.step()
+        total = time.perf_counter() - t0
+        n_in, n_new = len(req.prompt), len(req.generated)
+        report.append({"id": item.get("id"), "ttft_s": ttft, "decode_s": total - ttft,
+                       "prefill_tps": n_in / ttft,
+                       "decode_tps": (n_new - 1) / max(total - ttft, 1e-9),
+                       "tokens": req.generated})
+    print(json.dumps({"timing_scope": "no MTP, fixed output length", "requests": report}))
+    return 0
+
+
+def cmd_score_model(a) -> int:
+    """Teacher-forced next-token log-probabilities of ``--tokens`` (prefix cache and MTP off)."""
+    import numpy as np
+    import torch
+    from .core import sampling as S
+    from .models.runner import Packet
+    load, sched = _options(a)
+    load.prefix_cache_bytes = 0
+    weights, _ = _weights(a)
+    engine = _engine_factory(a, weights, load, sched)()
+    ids = [int(x) for x in a.tokens.split(",")]
+    dev = engine.device
+    t = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    pages = engine.pool.take((len(ids) + 127) // 128)
+    table = torch.zeros(1, engine.max_pages_per_req, dtype=torch.int32, device=dev)
+    table[0, :len(pages)] = t(pages)
+    p = Packet(t(ids), t([0] * len(ids)), t(list(range(len(ids)))), table, len(ids), len(ids))
+    _, logits = engine.runner.greedy(p)
+    logits = logits.float().cpu().numpy()
+    out = []
+    opts = S.SamplingOptions()
+    for i in range(len(ids) - 1):
+        lp, top = S.logprobs(logits[i], [], opts, ids[i + 1], 3)
+        out.append({"position": i + 1, "token": ids[i + 1], "logprob": lp, "top3": top})
+    print(json.dumps({"nll": -float(np.mean([o["logprob"] for o in out])), "probes": out}))
+    return 0
+
+
+def cmd_make_model(a) -> int:
+    """Random-init weights of a preset geometry quantised to the checkpoint format."""
+    import torch
+    from .engine.checkpoint import save_model
+    from .models.weights import random_model
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    w = random_model(PRESETS[a.preset], seed=a.seed, device=dev)
+    print(save_model(w, a.output, a.preset))
+    return 0
+
+
+def cmd_devices(a) -> int:
+    import torch
+    devs = []
+    for i in range(torch.cuda.device_count()):
+        pr = torch.cuda.get_device_properties(i)
+        devs.append({"index": i, "name": pr.name, "sm": f"{pr.major}{pr.minor}",
+                     "memory_bytes": pr.total_memory, "multiprocessors": pr.multi_processor_count,
+                     "supported": (pr.major, pr.minor) == (10, 0)})
+    print(json.dumps({"target": "sm_100a", "devices": devs}))
+    return 0
+
+
+def cmd_info(a) -> int:
+    from . import __version__
+    from .ops import native
+    print(json.dumps({"version": __version__, "target": "sm_100a",
+                      "kernel_library": native.loaded(), "presets": sorted(PRESETS)}))
+    return 0
+
+
+def cmd_validate_nccl(a) -> int:
+    from .parallel.selftest import main as selftest
+    return selftest(a.world)
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="orinfer")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    s = sub.add_parser("serve")
+    _load_args(s)
+    s.add_argument("--listen", default="[::]:8088")
+    s.add_argument("--queue-timeout-ms", type=int, default=0)
+    s.add_argument("--output-timeout-ms", type=int, default=60000)
+    s.add_argument("--drain-timeout-ms", type=int, default=30000)
+    s.set_defaults(fn=cmd_serve)
+    b = sub.add_parser("batch")
+    _load_args(b, batch=True)
+    b.add_argument("--input", required=True)
+    b.add_argument("--output", required=True)
+    b.add_argument("--resume", action="store_true")
+    b.add_argument("--batch-order", default="auto", choices=["input", "auto"])
+    b.set_defaults(fn=cmd_batch)
+    v = sub.add_parser("validate-model")
+    v.add_argument("model_dir")
+    v.set_defaults(fn=cmd_validate_model)
+    pm = sub.add_parser("plan-model")
+    pm.add_argument("model_dir", nargs="?")
+    pm.add_argument("--preset", choices=sorted(PRESETS))
+    pm.set_defaults(fn=cmd_plan_model)
+    r = sub.add_parser("run-model")
+    _load_args(r)
+    r.add_argument("--requests", required=True)
+    r.set_defaults(fn=cmd_run_model)
+    sc = sub.add_parser("score-model")
+    _load_args(sc)
+    sc.add_argument("--tokens", required=True, help="comma-separated token ids")
+    sc.set_defaults(fn=cmd_score_model)
+    mk = sub.add_parser("make-model")
+    mk.add_argument("--preset", required=True, choices=sorted(PRESETS))
+    mk.add_argument("--output", required=True)
+    mk.add_argument("--seed", type=int, default=0)
+    mk.set_defaults(fn=cmd_make_model)
+    sub.add_parser("devices").set_defaults(fn=cmd_devices)
+    sub.add_parser("info").set_defaults(fn=cmd_info)
+    vn = sub.add_parser("validate-nccl")
+    vn.add_argument("--world", type=int, default=0, help="ranks (0 = all visible GPUs)")
+    vn.set_defaults(fn=cmd_validate_nccl)
+    return ap
+
+
+def main(argv=None) -> int:
+    args = build_parser().parse_args(argv)
+    return int(args.fn(args) or 0)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
