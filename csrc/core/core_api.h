@@ -48,6 +48,64 @@ int orinfer_sampled_commit(const uint32_t* drafts, int n_drafts, const double* d
                            int history_len, const OrinferSamplingOptions* o, uint64_t step,
                            uint32_t* committed);
 
+// ---- scheduler policy
+typedef struct OrinferWaiting {
+  double age_s, remaining_s, restore_s, startup_s;
+  long long remaining_tokens;
+} OrinferWaiting;
+int orinfer_select_waiting(const OrinferWaiting* reqs, int n);
+void orinfer_rank_throughput_waiting(const OrinferWaiting* reqs, const double* expected, int n,
+                                     int has_cohort, double cohort_remaining, int* order);
+void orinfer_replenish(double* credits, int n, double quantum_s);
+double orinfer_prefill_window(double slack_s, double decode_s, double ceiling_ms);
+int orinfer_joint_prefill_worthwhile(int loses_large_tile, int measured, double joint_s,
+                                     double native_s);
+double orinfer_decode_quantum_s(double prefill_s, double prefill_budget_ms, double tpot_ms);
+int orinfer_admission_should_yield(int has_decoders, int admitted, double elapsed_s,
+                                   int batchable_start);
+long long orinfer_usable_host_bytes(long long total_kb, long long available_kb);
+void* orinfer_timing_create(void);
+void orinfer_timing_destroy(void* h);
+void orinfer_timing_observe(void* h, double seconds);
+double orinfer_timing_mean(void* h);
+double orinfer_timing_upper(void* h);
+long long orinfer_timing_samples(void* h);
+void* orinfer_lengths_create(void);
+void orinfer_lengths_destroy(void* h);
+void orinfer_lengths_observe(void* h, long long input, long long output);
+double orinfer_lengths_estimate(void* h, long long input, long long limit);
+int orinfer_error_is_fatal(int kind);
+
+// ---- adaptive MTP control and prompt lookup
+typedef struct OrinferMtpCandidate {
+  int id, width;
+  double expected_tokens, maximum_tokens;
+  long long remaining_tokens;
+  double mean_s, upper_s, transition_s;
+  int warm_ready, review_acceptance, samples;
+  long long last;                 // call index of the last use, -1 = never
+} OrinferMtpCandidate;
+typedef struct OrinferMtpSelection {
+  double normal_s, fixed_s;
+  int batch;
+  double slack_s, available_s, calibration_s;
+  int allow_exploration;
+  long long calls, normal_last;   // normal_last -1 = never
+} OrinferMtpSelection;
+void* orinfer_acceptance_create(void);
+void orinfer_acceptance_destroy(void* h);
+void orinfer_acceptance_observe(void* h, const int* proposed, const int* accepted, int n);
+double orinfer_acceptance_rate(void* h, int position, double prior);
+double orinfer_acceptance_expected(void* h, int drafts);
+double orinfer_mtp_progress(const double* yields, int n, int batch, int latency);
+int orinfer_mtp_select(const OrinferMtpSelection* in, const OrinferMtpCandidate* cands, int n,
+                       int* flags);
+void* orinfer_lookup_create(void);
+void orinfer_lookup_destroy(void* h);
+int orinfer_lookup_propose(void* h, const uint32_t* history, int n, int count, int confident,
+                           uint32_t* out);
+void orinfer_lookup_observe(void* h, int accepted, int proposed, int progress);
+
 // ---- radix prefix cache (page granular)
 void* orinfer_prefix_create(int page_tokens);
 void orinfer_prefix_destroy(void* handle);
