@@ -132,6 +132,8 @@ class Engine:
         self._graphs: Dict[int, _DecodeGraph] = {}
         self._next_rid = 1
         self._pin = {}
+        from .speculation import Speculator
+        self.spec = Speculator(self, self.load.mtp_drafts, self.load.prompt_lookup)
         self.tpot_ewma: Optional[float] = None
 
     # ------------------------------------------------------------------ sizing
@@ -267,6 +269,7 @@ class Engine:
             self.stats.finished += 1
         if req in self.running:
             self.running.remove(req)
+        self.spec.forget(req)
 
     # ------------------------------------------------------------------ work selection
     def _select(self):
@@ -305,6 +308,10 @@ class Engine:
         self.stats.iterations += 1
         t0 = time.monotonic()
         pure_decode = not chunks
+        if pure_decode and self.spec.enabled:
+            produced = self.spec.run(decoders)
+            if produced is not None:
+                return produced
         use_graph = (self.on_gpu and pure_decode and
                      self.load.cuda_graph.uses_graph(ExecPhase.DECODE) and
                      len(decoders) <= DECODE_BUCKETS[-1])
@@ -445,21 +452,28 @@ class Engine:
             if was_decode:
                 self.stats.decode_tokens += 1
             tok = self._sample(r, tokens, logits, row)
-            r.pending = tok
-            r.generated.append(tok)
-            if r.first_token_at is None:
-                r.first_token_at = now
-            r.phase = Phase.DECODE
-            if r.on_token is not None:
-                r.on_token(r, tok)
+            self._deliver(r, tok)
             produced.append(r)
-            if tok in r.stop_ids and not r.ignore_eos:
-                self._finish(r, "stop")
-            elif len(r.generated) >= r.max_new:
-                self._finish(r, "length")
-            elif r.constraint is not None and getattr(r.constraint, "finished", lambda: False)():
-                self._finish(r, "stop")
         return produced
+
+    def _deliver(self, r: Request, tok: int) -> None:
+        """Commit one sampled token: history, callbacks, stop conditions."""
+        r.pending = tok
+        r.generated.append(tok)
+        if r.first_token_at is None:
+            r.first_token_at = time.monotonic()
+        r.phase = Phase.DECODE
+        if r.on_token is not None:
+            r.on_token(r, tok)
+        if tok in r.stop_ids and not r.ignore_eos:
+            self._finish(r, "stop")
+        elif len(r.generated) >= r.max_new:
+            self._finish(r, "length")
+        elif r.constraint is not None and getattr(r.constraint, "finished", lambda: False)():
+            self._finish(r, "stop")
+
+    def runner_has_mtp(self) -> bool:
+        return False
 
     @staticmethod
     def _plain(r: Request) -> bool:

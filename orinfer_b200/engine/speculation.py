@@ -1,0 +1,161 @@
+"""Speculative decoding rounds: draft -> verify -> commit, distribution preserving.
+
+Drafts come from request-local prompt lookup (copies of an earlier continuation) and, when
+the model carries one, the MTP draft head.  One verification packet runs the target model
+over ``[pending, d1, ..., dk]`` of every speculating request (plain decoders ride along
+with one row); greedy requests commit the longest matching prefix plus the target's own
+next token, sampled requests use exact rejection sampling with separate counter streams,
+so the committed text never depends on whether speculation ran.  Rejected rows need no
+rollback: their KV sits beyond the request's cursor and is overwritten later.  The width
+of a round is chosen by the adaptive controller from measured round costs and
+per-position acceptance.  Mirrors crates/orinfer-engine/src/runtime/requests/speculation.rs
+:243-403,1361-1906 and mtp.rs:10-22,48-97 of the reference.
+"""
+
+from __future__ import annotations
+
+import os
+import time
+from typing import Dict, List, Optional, Tuple
+
+import numpy as np
+
+from ..config import MAX_MTP_DRAFTS
+from ..core import policy as P
+from ..core import sampling as S
+from .request import Phase, Request
+
+WIDTHS = (2, 3, 4, 6, 8, 12, 16, 32)
+
+
+class Speculator:
+    def __init__(self, engine, max_drafts: Optional[int], prompt_lookup: bool):
+        self.engine = engine
+        self.max_drafts = MAX_MTP_DRAFTS if max_drafts is None else max_drafts
+        if max_drafts is None:
+            self.max_drafts = 3                        # "auto": up to three drafts
+        self.prompt_lookup = prompt_lookup
+        self.lookups: Dict[int, P.PromptLookup] = {}
+        self.acceptance = P.Acceptance()
+        self.costs: Dict[int, P.Timing] = {}          # verification width -> round cost
+        self.last_used: Dict[int, int] = {}
+        self.calls = 0
+        self.rounds = self.proposed = self.accepted = self.committed = 0
+        self.trace = os.environ.get("ORINFER_MTP_TRACE") == "1"
+        self.policy = os.environ.get("ORINFER_SINGLE_MTP_POLICY", "auto")
+
+    @property
+    def enabled(self) -> bool:
+        return self.max_drafts > 0 and (self.prompt_lookup or self.engine.runner_has_mtp())
+
+    # ------------------------------------------------------------------ width selection
+    def choose_width(self, batch: int, remaining: int) -> int:
+        """Verification width (rows per speculating request); 1 = plain decode."""
+        if self.policy.startswith("fixed"):
+            return 1 + min(int(self.policy[5:] or 0), self.max_drafts)
+        normal = self.engine.tpot_ewma
+        if normal is None:
+            return 1
+        cands = []
+        for w in WIDTHS:
+            if w - 1 > self.max_drafts:
+                break
+            t = self.costs.get(w)
+            exp = self.acceptance.expected(w - 1)
+            mean = t.mean if t and t.samples else normal * (1 + 0.05 * (w - 1))
+            upper = t.upper if t and t.samples else mean * 1.5
+            cands.append(P.Candidate(w, w, exp * batch, w * batch, remaining, mean, upper,
+                                     samples=t.samples if t else 0,
+                                     last=self.last_used.get(w)))
+        cid, exploring, calibrating = P.mtp_select(
+            normal, batch, self.engine.sched.target_tpot_ms / 1e3, cands,
+            available_s=normal, calibration_s=4 * normal, calls=self.calls)
+        if self.trace:
+            print(f"MTP choose batch={batch} normal={normal:.5f} -> {cid} "
+                  f"exploring={exploring} calibrating={calibrating}", flush=True)
+        return cid or 1
+
+    # ------------------------------------------------------------------ drafting
+    def drafts_for(self, r: Request, count: int) -> List[int]:
+        if count <= 0 or r.constraint is not None:
+            return []
+        if self.prompt_lookup:
+            lk = self.lookups.setdefault(r.rid, P.PromptLookup())
+            got = lk.propose(r.history, count, confident=not r.sampling.is_greedy)
+            if got:
+                return got
+        return []
+
+    def forget(self, r: Request) -> None:
+        self.lookups.pop(r.rid, None)
+
+    # ------------------------------------------------------------------ one round
+    def run(self, decoders: List[Request]) -> Optional[List[Request]]:
+        """Runs one verification packet; None when no request had a draft (caller falls
+        back to the ordinary decode path)."""
+        eng = self.engine
+        remaining = min(r.max_new - len(r.generated) for r in decoders)
+        width = self.choose_width(len(decoders), remaining)
+        self.calls += 1
+        if width < 2:
+            return None
+        plans: List[Tuple[Request, List[int]]] = []
+        for r in decoders:
+            room = r.max_new - len(r.generated) - 1
+            plans.append((r, self.drafts_for(r, min(width - 1, room))))
+        if not any(d for _, d in plans):
+            return None
+        t0 = time.monotonic()
+        ids, rows_req, pos, max_kv = [], [], [], 1
+        for r, drafts in plans:
+            toks = [r.pending] + drafts
+            ids += toks
+            rows_req += [r.slot] * len(toks)
+            pos += list(range(r.offset, r.offset + len(toks)))
+            max_kv = max(max_kv, r.offset + len(toks))
+        from ..models.runner import Packet
+        packet = Packet(eng._upload("ids", ids), eng._upload("req", rows_req),
+                        eng._upload("pos", pos), eng.page_table_dev, len(ids), max_kv)
+        need = any(not eng._plain(r) for r, _ in plans)
+        tok_dev, logits = eng.runner.greedy(packet, need_logits=need)
+        tokens = tok_dev.cpu().tolist()
+        produced, row = [], 0
+        counts = []
+        for r, drafts in plans:
+            n = 1 + len(drafts)
+            if eng._plain(r):
+                commit = S.greedy_commit(drafts, tokens[row:row + n]) if drafts else [tokens[row]]
+            elif drafts:
+                lg = logits[row:row + n].float().cpu().numpy()
+                commit = S.sampled_commit(drafts, None, lg, r.history, r.sampling,
+                                          len(r.generated))
+            else:
+                commit = [eng._sample(r, tokens, logits, row)]
+            accepted = len(commit) - 1
+            if drafts:
+                counts.append((len(drafts), accepted))
+                if r.rid in self.lookups:
+                    self.lookups[r.rid].observe(accepted, len(drafts), len(r.history))
+            r.offset += 1 + accepted
+            for tok in commit:
+                if r.finished:
+                    break
+                eng._deliver(r, int(tok))
+            produced.append(r)
+            row += n
+        if counts:
+            self.acceptance.observe(counts)
+            self.rounds += 1
+            self.proposed += sum(c[0] for c in counts)
+            self.accepted += sum(c[1] for c in counts)
+        self.committed += sum(1 for _ in produced)
+        dt = time.monotonic() - t0
+        self.costs.setdefault(width, P.Timing()).observe(dt)
+        self.last_used[width] = self.calls
+        eng.stats.decode_tokens += len(ids)
+        return produced
+
+    def statistics(self) -> dict:
+        return {"rounds": self.rounds, "proposed_tokens": self.proposed,
+                "accepted_draft_tokens": self.accepted,
+                "acceptance_rate": self.accepted / self.proposed if self.proposed else 0.0}

@@ -123,3 +123,46 @@ def test_context_limit_is_rejected(weights):
     eng = _engine(weights)
     with pytest.raises(ValueError, match="exceeds the context window"):
         eng.submit([1] * 500, 100)
+
+
+def test_speculation_preserves_output(weights):
+    """Verification rounds commit exactly the tokens plain decoding produces, whether the
+    drafts are all right (oracle), all wrong, or come from prompt lookup; greedy and seeded
+    sampling (exact rejection sampling with point-mass proposals)."""
+    import os
+    base = [5, 6, 7, 8, 9, 10, 11, 12] * 6
+    for opt in (None, SamplingOptions(temperature=0.8, seed=3)):
+        ref_eng = _engine(weights)
+        plain = ref_eng.generate([base], max_new=24, sampling=opt)[0]
+        os.environ["ORINFER_SINGLE_MTP_POLICY"] = "fixed3"
+        try:
+            for kind in ("oracle", "wrong", "lookup"):
+                eng = _engine(weights, load=LoadOptions(prompt_lookup=True, mtp_drafts=3))
+                if kind == "oracle":
+                    eng.spec.drafts_for = lambda r, c: plain[len(r.generated):len(r.generated) + c]
+                elif kind == "wrong":
+                    eng.spec.drafts_for = lambda r, c: [(t + 1) % 1024 for t in
+                                                        plain[len(r.generated):len(r.generated) + c]]
+                out = eng.generate([base], max_new=24, sampling=opt)[0]
+                if opt is None:
+                    assert out == plain, kind
+                else:
+                    # sampled rounds preserve the law, not the sample path; they must be
+                    # reproducible for a fixed seed
+                    eng2 = _engine(weights, load=LoadOptions(prompt_lookup=True, mtp_drafts=3))
+                    eng2.spec.drafts_for = eng.spec.drafts_for
+                    assert eng2.generate([base], max_new=24, sampling=opt)[0] == out
+                    assert len(out) == 24
+                    continue
+                st = eng.spec.statistics()
+                if kind == "oracle":
+                    assert st["acceptance_rate"] == 1.0 and eng.stats.iterations < ref_eng.stats.iterations
+                if kind == "wrong":
+                    assert st["rounds"] > 0 and st["accepted_draft_tokens"] == 0
+        finally:
+            del os.environ["ORINFER_SINGLE_MTP_POLICY"]
+    # adaptive controller path (width chosen from measured costs and acceptance)
+    eng = _engine(weights, load=LoadOptions(prompt_lookup=True))
+    greedy = _engine(weights).generate([base], max_new=24)[0]
+    eng.spec.drafts_for = lambda r, c: greedy[len(r.generated):len(r.generated) + c]
+    assert eng.generate([base], max_new=24)[0] == greedy
