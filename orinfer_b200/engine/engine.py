@@ -392,6 +392,12 @@ class Engine:
         need = any(not self._plain(r) for r, _n, has in order if has)
         tok, lg = self.runner.greedy(packet, need_logits=need)
         tokens = tok.cpu()                           # one readback (synchronises)
+        if self.spec.enabled and self.runner_has_mtp():
+            info, row0 = [], 0
+            for r, n, _has in order:
+                info.append((r, row0, n, r.offset))
+                row0 += n
+            self.spec.capture(info, self.runner.final_hidden(rows))
         self.stats.direct_packets += 1
         self.stats.direct_s += time.monotonic() - t1
         self.stats.prefill_tokens += sum(n for _, n in chunks)
@@ -431,6 +437,9 @@ class Engine:
             g.graph.replay()
             self.stats.graph_hits += 1
         tokens = g.tokens[:n].cpu()
+        if self.spec.enabled and self.runner_has_mtp():
+            self.spec.capture([(r, i, 1, r.offset) for i, r in enumerate(decoders)],
+                              self.runner.final_hidden(n))
         self.stats.replay_s += time.monotonic() - t1
         order = [(r, 1, True) for r in decoders]
         return tokens, g.logits, order
@@ -473,7 +482,8 @@ class Engine:
             self._finish(r, "stop")
 
     def runner_has_mtp(self) -> bool:
-        return False
+        return (self.w.mtp is not None and hasattr(self.runner, "mtp_rows")
+                and self.load.mtp_drafts != 0 and getattr(self.w, "tp", None) is None)
 
     @staticmethod
     def _plain(r: Request) -> bool:

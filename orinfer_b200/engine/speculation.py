@@ -36,6 +36,7 @@ class Speculator:
             self.max_drafts = 3                        # "auto": up to three drafts
         self.prompt_lookup = prompt_lookup
         self.lookups: Dict[int, P.PromptLookup] = {}
+        self.backlog: Dict[int, list] = {}            # rid -> [(first pos, hidden rows)]
         self.acceptance = P.Acceptance()
         self.costs: Dict[int, P.Timing] = {}          # verification width -> round cost
         self.last_used: Dict[int, int] = {}
@@ -88,6 +89,55 @@ class Speculator:
 
     def forget(self, r: Request) -> None:
         self.lookups.pop(r.rid, None)
+        self.backlog.pop(r.rid, None)
+
+    # ------------------------------------------------------------------ MTP draft head
+    def capture(self, rows_info, hidden) -> None:
+        """Remember the target hidden states of freshly computed rows: the draft head must
+        see (next token, hidden) of every position before it can draft past it."""
+        if not self.engine.runner_has_mtp() or self.max_drafts <= 0:
+            return
+        for r, row0, n, pos0 in rows_info:
+            if n > 0 and not r.finished and r.constraint is None:
+                self.backlog.setdefault(r.rid, []).append((pos0, hidden[row0:row0 + n].clone()))
+
+    def mtp_drafts(self, reqs: List[Request], count: int) -> Dict[int, List[int]]:
+        """Batched draft loop: one head pass over the backlog rows (catch-up + first draft),
+        then ``count - 1`` single-row passes feeding the head's own hidden state back."""
+        import torch
+        from ..models.runner import Packet
+        eng = self.engine
+        live = [r for r in reqs if self.backlog.get(r.rid)]
+        if not live or count <= 0:
+            return {}
+        toks, hids, rreq, rpos, last = [], [], [], [], []
+        for r in live:
+            hist = r.history
+            for pos0, h in self.backlog.pop(r.rid):
+                n = h.shape[0]
+                toks += [hist[pos0 + i + 1] for i in range(n)]
+                hids.append(h)
+                rreq += [r.slot] * n
+                rpos += list(range(pos0, pos0 + n))
+            last.append(len(toks) - 1)
+        rows = len(toks)
+        if rows > eng.max_rows:
+            return {}
+        p = Packet(eng._upload("mids", toks), eng._upload("mreq", rreq), eng._upload("mpos", rpos),
+                   eng.page_table_dev, rows, max(rpos) + 1)
+        dtok, dhid = eng.runner.mtp_rows(p.ids, torch.cat(hids, dim=0), p)
+        sel = torch.tensor(last, device=dtok.device)
+        cur_tok, cur_hid = dtok[sel], dhid[sel]
+        out = {r.rid: [int(t)] for r, t in zip(live, cur_tok.cpu().tolist())}
+        for j in range(1, count):
+            pos = [r.offset - 1 + j for r in live]
+            p = Packet(cur_tok.to(torch.int32).contiguous(),
+                       eng._upload("mreq", [r.slot for r in live]), eng._upload("mpos", pos),
+                       eng.page_table_dev, len(live), max(pos) + 1)
+            cur_tok, cur_hid = eng.runner.mtp_rows(p.ids, cur_hid, p)
+            for r, t in zip(live, cur_tok.cpu().tolist()):
+                out[r.rid].append(int(t))
+        return out
 
     # ------------------------------------------------------------------ one round
     def run(self, decoders: List[Request]) -> Optional[List[Request]]:
@@ -103,6 +153,11 @@ class Speculator:
         for r in decoders:
             room = r.max_new - len(r.generated) - 1
             plans.append((r, self.drafts_for(r, min(width - 1, room))))
+        if eng.runner_has_mtp():
+            need = [r for r, d in plans if not d and r.constraint is None]
+            room = min([r.max_new - len(r.generated) - 1 for r in need], default=0)
+            got = self.mtp_drafts(need, min(width - 1, room))
+            plans = [(r, d or got.get(r.rid, [])) for r, d in plans]
         if not any(d for _, d in plans):
             return None
         t0 = time.monotonic()
@@ -121,6 +176,7 @@ class Speculator:
         tokens = tok_dev.cpu().tolist()
         produced, row = [], 0
         counts = []
+        hidden = eng.runner.final_hidden(len(ids)) if eng.runner_has_mtp() else None
         for r, drafts in plans:
             n = 1 + len(drafts)
             if eng._plain(r):
@@ -136,6 +192,8 @@ class Speculator:
                 counts.append((len(drafts), accepted))
                 if r.rid in self.lookups:
                     self.lookups[r.rid].observe(accepted, len(drafts), len(r.history))
+            if hidden is not None:
+                self.capture([(r, row, 1 + accepted, r.offset)], hidden)
             r.offset += 1 + accepted
             for tok in commit:
                 if r.finished:

@@ -246,3 +246,47 @@ class ModelRunner:
     def greedy(self, p: Packet, logits_out=None, token_out=None, need_logits: bool = True):
         lg = self.logits(p, logits_out)
         return F.argmax(lg, out=token_out), lg
+
+    # ---------------------------------------------------------------- MTP draft head
+    def final_hidden(self, rows: int) -> torch.Tensor:
+        """Residual stream entering the final norm, for the rows of the last packet."""
+        return self.ws.resid[:rows]
+
+    def mtp_rows(self, tokens: torch.Tensor, hidden: torch.Tensor, p: Packet):
+        """One pass of the draft head over ``p.rows`` rows: row i combines the embedding of
+        ``tokens[i]`` (the token that FOLLOWS position ``p.row_pos[i]``) with the target
+        model's hidden state at that position, writes the draft layer's KV at that position
+        and predicts the token after next.  Returns (draft tokens, draft hidden fp32).
+        concat(norm_e(embed), norm_h(hidden)) -> fc -> one decoder layer -> norm -> shared head
+        (kernels/cuda/model/speculation.py:31 mtp_norm_concat of the reference)."""
+        cfg, ws, m, rows = self.cfg, self.ws, self.w.mtp, p.rows
+        h = cfg.hidden
+        if getattr(ws, "mtp_buf", None) is None:
+            e = lambda *s, dt=torch.float16: torch.empty(*s, dtype=dt, device=self.device)
+            ws.mtp_buf = dict(e=e(ws.max_rows, h), ye=e(ws.max_rows, h), yh=e(ws.max_rows, h),
+                              r=e(ws.max_rows, h, dt=torch.float32),
+                              resid=e(ws.max_rows, h, dt=torch.float32))
+        b = ws.mtp_buf
+        F.embed_w8(tokens, self.w.embed_q, self.w.embed_s, out=b["e"])
+        F.act_prep(b["e"], None, m.norm_e, None, eps=cfg.eps, rows=rows, q_out=ws.q8[h],
+                   scale_out=ws.scale, y_out=b["ye"])
+        b["r"][:rows].copy_(hidden[:rows])
+        F.act_prep(None, b["r"], m.norm_h, None, eps=cfg.eps, rows=rows, q_out=ws.q8[h],
+                   scale_out=ws.scale, y_out=b["yh"])
+        cat = torch.cat([b["ye"][:rows], b["yh"][:rows]], dim=1).contiguous()
+        q8, sc = F.act_prep(cat, None, None, m.fc.signs, rows=rows)
+        x = F.qgemm(q8, sc, m.fc.codes, m.fc.scale, m.fc.fmt, m.fc.n, out=ws.hidden, rows=rows)
+        saved = ws.resid
+        ws.resid = b["resid"]
+        try:
+            ws.resid[:rows].zero_()
+            F.rope_table(p.row_pos, cfg.head_dim, cfg.rope_theta, ws.cos, ws.sin, rows=rows)
+            x = self._attention_block(m.layer, self.mtp_kv_index, x, p, rows, True)
+            x = self._dense_ffn(m.layer, x, rows)
+            q8, sc = self._prep(x, m.final_norm, self.w.head.signs, rows)
+            lg = F.qgemm(q8, sc, self.w.head.codes, self.w.head.scale, self.w.head.fmt,
+                         self.w.head.n, out_f32=True, rows=rows)
+            hid = ws.resid[:rows].clone()
+        finally:
+            ws.resid = saved
+        return F.argmax(lg[:rows]), hid

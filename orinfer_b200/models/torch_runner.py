@@ -121,6 +121,7 @@ class TorchRunner:
     def logits(self, p: Packet, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         x, resid = self.forward_hidden(p)
         final = resid + x
+        self._final = final
         if p.logit_rows is not None:
             final = final.index_select(0, p.logit_rows.long())
         h = R.rms_norm(final, self.w.final_norm, self.cfg.eps, self.cfg.zero_centered_norm)
@@ -135,3 +136,27 @@ class TorchRunner:
         if token_out is not None:
             token_out[:tok.shape[0]].copy_(tok)
         return tok, lg
+
+    # ---------------------------------------------------------------- MTP draft head
+    def final_hidden(self, rows: int) -> torch.Tensor:
+        return self._final[:rows]
+
+    def mtp_rows(self, tokens: torch.Tensor, hidden: torch.Tensor, p: Packet):
+        """Same contract as ModelRunner.mtp_rows, in plain PyTorch."""
+        cfg, m, rows = self.cfg, self.w.mtp, p.rows
+        zc = cfg.zero_centered_norm
+        e = R.embed_w8(tokens[:rows], self.w.embed_q, self.w.embed_s)
+        ye = R.rms_norm(e, m.norm_e, cfg.eps, zc)
+        yh = R.rms_norm(hidden[:rows].float(), m.norm_h, cfg.eps, zc)
+        x = self._linear(m.fc, torch.cat([ye, yh], dim=1))
+        cos, sin = R.rope_tables(p.row_pos[:rows], cfg.head_dim, cfg.rope_theta)
+        resid = x
+        y = R.rms_norm(resid, m.layer.in_norm, cfg.eps, zc)
+        mix = self._attention(m.layer, self.mtp_kv_index, y, p, cos, sin)
+        x = self._linear(m.layer.o, mix)
+        resid = resid + x
+        y = R.rms_norm(resid, m.layer.post_norm, cfg.eps, zc)
+        x = self._ffn(m.layer, y)
+        final = resid + x
+        lg = self._linear(self.w.head, R.rms_norm(final, m.final_norm, cfg.eps, zc), out_f32=True)
+        return R.argmax_lowest(lg), final

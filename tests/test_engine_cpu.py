@@ -166,3 +166,23 @@ def test_speculation_preserves_output(weights):
     greedy = _engine(weights).generate([base], max_new=24)[0]
     eng.spec.drafts_for = lambda r, c: greedy[len(r.generated):len(r.generated) + c]
     assert eng.generate([base], max_new=24)[0] == greedy
+
+
+def test_mtp_head_speculation_preserves_greedy_output():
+    """Draft-head rounds (catch-up over the prompt, draft loop, verify, commit) leave the
+    greedy text unchanged; the head of a random-init model rarely guesses right."""
+    import dataclasses, os
+    cfg = dataclasses.replace(PRESETS["tiny"], mtp_layers=1)
+    w = random_model(cfg, seed=4)
+    prompts = _prompts(2, 20, seed=8)
+    plain = _engine(w, load=LoadOptions(mtp_drafts=0)).generate(prompts, max_new=10)
+    os.environ["ORINFER_SINGLE_MTP_POLICY"] = "fixed2"
+    try:
+        eng = _engine(w, load=LoadOptions(mtp_drafts=2))
+        assert eng.runner_has_mtp() and eng.spec.enabled
+        out = eng.generate(prompts, max_new=10)
+    finally:
+        del os.environ["ORINFER_SINGLE_MTP_POLICY"]
+    assert out == plain
+    st = eng.spec.statistics()
+    assert st["rounds"] > 0 and st["proposed_tokens"] >= 2 * st["rounds"]
