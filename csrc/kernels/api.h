@@ -77,6 +77,21 @@ int orinfer_qgemm(int fmt, const int8_t* a, const float* a_scale, const void* w,
                   const __half* w_scale, void* out, int M, int N, int K, int out_f32,
                   int force_path, cudaStream_t stream);
 
+// ---- mixture of experts
+int orinfer_router_topk(const __half* x, const __half* w, int rows, int hidden, int experts,
+                        int has_shared, int top_k, int renorm, int* ids, float* probs,
+                        float* shared_gate, cudaStream_t stream);
+int orinfer_moe_dispatch(const int* ids, int rows, int top_k, int experts, const int8_t* q8,
+                         const float* scale, int K, int* counts, int* offsets, int* tiles,
+                         int* meta, int max_tiles, int* slots, int8_t* q8_sorted,
+                         float* scale_sorted, cudaStream_t stream);
+int orinfer_moe_combine(const __half* expert_out, const int* slots, const float* probs, int rows,
+                        int top_k, const __half* shared_out, const float* shared_gate,
+                        __half* out, int hidden, cudaStream_t stream);
+int orinfer_qgemm_grouped(int fmt, const int8_t* a, const float* a_scale, const void* w,
+                          const __half* w_scale, void* out, int S, int N, int K, int experts,
+                          const int* tiles, const int* meta, int max_tiles, cudaStream_t stream);
+
 // ---- attention over the paged INT8 KV cache
 size_t orinfer_attention_scratch_bytes(int rows, int qh, int head_dim, int splits);
 int orinfer_attention(const __half* q, const __half* gate, const int* row_req, const int* row_pos,

@@ -45,12 +45,21 @@ struct Layout {
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;   // barriers + alignment slack
 };
 
+// Grouped (mixture-of-experts) launch: blockIdx.y walks a device-side tile table
+// (expert, first row, valid rows); each expert has its own weight bank and row scales.
+struct GroupDesc {
+  const int* tiles;            // int32 [max_tiles, 4]; nullptr = ordinary GEMM
+  const int* meta;             // meta[0] = number of tiles
+  long long w_stride;          // bytes between consecutive experts' weight banks
+  int n_per_expert;            // rows of one expert's bank (= N)
+};
+
 template <int FMT, bool OUT_F32, int MT>
 __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
     const unsigned char* __restrict__ w, const float* __restrict__ a_scale,
     const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K,
-    const E8pTables* __restrict__ tables, int* status, PeerOut po) {
+    const E8pTables* __restrict__ tables, int* status, PeerOut po, GroupDesc grp) {
   using L = Layout<FMT, MT>;
   constexpr int STAGES = L::STAGES;
   extern __shared__ unsigned char smem_raw[];
@@ -67,7 +76,17 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM * MT;
+  const int n0 = blockIdx.x * BN;
+  int m0 = blockIdx.y * BM * MT, m_limit = M, b_row0 = n0;
+  if (grp.tiles != nullptr) {
+    if (static_cast<int>(blockIdx.y) >= grp.meta[0]) return;
+    const int expert = grp.tiles[blockIdx.y * 4];
+    m0 = grp.tiles[blockIdx.y * 4 + 1];
+    m_limit = m0 + grp.tiles[blockIdx.y * 4 + 2];
+    w += static_cast<long long>(expert) * grp.w_stride;
+    w_scale += static_cast<long long>(expert) * grp.n_per_expert;
+    b_row0 = expert * grp.n_per_expert + n0;
+  }
   const int kblocks = K / BK;
   const int rows_valid = min(BN, N - n0);
   constexpr uint32_t TMEM_COLS = MT * BN;
@@ -110,7 +129,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
           tma_load_2d(a_s + (s * MT + t) * TILE_BYTES, &tmap_a, &tma_full[s], kb * BK,
                       m0 + t * BM);
         if (FMT == 0) {
-          tma_load_2d(b_s + s * TILE_BYTES, &tmap_b, &tma_full[s], kb * BK, n0);
+          tma_load_2d(b_s + s * TILE_BYTES, &tmap_b, &tma_full[s], kb * BK, b_row0);
         } else {
           const unsigned char* src =
               w + (static_cast<size_t>(kb) * N + n0) * L::ROW_CODE_BYTES;
@@ -196,13 +215,13 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
 #pragma unroll 1
       for (int mt = 0; mt < MT; ++mt) {
         const int m = m0 + mt * BM + row;
-        const float sa = m < M ? a_scale[m] : 0.f;
+        const float sa = m < m_limit ? a_scale[m] : 0.f;
 #pragma unroll 1
         for (int c0 = part * 32; c0 < part * 32 + 32; c0 += 32) {
           uint32_t r[32];
           tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + mt * BN + c0, r);
           tc_wait_ld();
-          if (m < M) {
+          if (m < m_limit) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               const int n = n0 + c0 + g * 8;
@@ -247,12 +266,16 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
 
 template <int FMT, bool OUT_F32, int MT>
 int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale, void* out,
-           int M, int N, int K, cudaStream_t stream, const PeerOut& po) {
+           int M, int N, int K, cudaStream_t stream, const PeerOut& po,
+           const GroupDesc& grp = GroupDesc{nullptr, nullptr, 0, 0}, int experts = 1,
+           int max_tiles = 0) {
   using L = Layout<FMT, MT>;
   CUtensorMap ta, tb;
   if (!make_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BM, BK)) return -3;
   if (FMT == 0) {
-    if (!make_tmap_2d(&tb, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, BN, BK)) return -3;
+    if (!make_tmap_2d(&tb, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1,
+                      static_cast<uint64_t>(N) * experts, K, K, BN, BK))
+      return -3;
   } else {
     tb = ta;
     if (reinterpret_cast<uintptr_t>(w) % 16) return -1;
@@ -264,10 +287,10 @@ int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w
     if (e != cudaSuccess) return static_cast<int>(e);
     attr = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + BM * MT - 1) / (BM * MT));
+  dim3 grid((N + BN - 1) / BN, grp.tiles ? max_tiles : (M + BM * MT - 1) / (BM * MT));
   qgemm_tc_kernel<FMT, OUT_F32, MT><<<grid, THREADS, L::TOTAL, stream>>>(
       ta, tb, reinterpret_cast<const unsigned char*>(w), a_scale, w_scale, out, M, N, K,
-      runtime_e8p_tables(), runtime_status_ptr(), po);
+      runtime_e8p_tables(), runtime_status_ptr(), po, grp);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -342,4 +365,27 @@ extern "C" int orinfer_qgemm_peer(int fmt, const int8_t* a, const float* a_scale
   po.rank = peer->rank;
   po.rows_cap = peer->rows_cap;
   return qgemm_any(fmt, a, a_scale, w, w_scale, nullptr, M, N, K, 0, force_path, stream, &po);
+}
+
+// Grouped expert GEMM: rows of `a` are sorted by expert; tile t of the table covers rows
+// [first, first + valid) of expert e, multiplied with that expert's bank.  out is fp16 [S, N].
+extern "C" int orinfer_qgemm_grouped(int fmt, const int8_t* a, const float* a_scale, const void* w,
+                                     const __half* w_scale, void* out, int S, int N, int K,
+                                     int experts, const int* tiles, const int* meta,
+                                     int max_tiles, cudaStream_t stream) {
+  if (S <= 0 || max_tiles <= 0) return 0;
+  if (K <= 0 || K % 128 || N % 128 || fmt < 0 || fmt > 2 || experts < 1) return -1;
+  if (runtime_ensure_init() != cudaSuccess) return -2;
+  const long long bank = fmt == 0 ? static_cast<long long>(N) * K
+                                  : static_cast<long long>(K / 128) * N * (fmt == 1 ? 64 : 32);
+  tc::GroupDesc g{tiles, meta, bank, N};
+  PeerOut po{};
+  if (fmt == 0)
+    return tc::launch<0, false, 1>(a, a_scale, w, w_scale, out, S, N, K, stream, po, g, experts,
+                                   max_tiles);
+  if (fmt == 1)
+    return tc::launch<1, false, 1>(a, a_scale, w, w_scale, out, S, N, K, stream, po, g, experts,
+                                   max_tiles);
+  return tc::launch<2, false, 1>(a, a_scale, w, w_scale, out, S, N, K, stream, po, g, experts,
+                                 max_tiles);
 }

@@ -217,10 +217,47 @@ class ModelRunner:
             else:
                 x = self.layer_hooks["gdn"](self, lw, i, x, p, rows)
             if cfg.experts:
-                x = self.layer_hooks["moe"](self, lw, i, x, p, rows)
+                x = self._moe_ffn(lw, x, rows)
             else:
                 x = self._dense_ffn(lw, x, rows)
         return x
+
+    def _moe_ffn(self, lw: LayerWeights, x, rows: int):
+        """norm+rotate+quantise once -> router top-k -> dispatch rows to expert-contiguous
+        slots -> grouped gate_up GEMM -> SwiGLU+rotate+quantise -> grouped down GEMM ->
+        weighted combine (+ sigmoid-gated shared expert)."""
+        cfg, ws = self.cfg, self.ws
+        h, f = cfg.hidden, cfg.expert_ffn
+        if getattr(ws, "moe", None) is None:
+            ws.moe = F.MoeScratch(ws.max_rows, cfg.top_k, cfg.experts, h, f, self.device)
+            ws.moe_out = torch.empty(ws.max_rows, h, dtype=torch.float16, device=self.device)
+            ws.shared_out = torch.empty(ws.max_rows, h, dtype=torch.float16, device=self.device)
+        sc = ws.moe
+        bank_up, bank_dn = lw.expert_gate_up, lw.expert_down
+        y16 = ws.attn_norm(rows, h)
+        q8, s8 = self._prep(x, lw.post_norm, bank_up.signs, rows, y_out=y16)
+        F.router_topk(y16, lw.router, cfg.experts, cfg.top_k, renorm=cfg.renormalize, rows=rows,
+                      ids=sc.ids, probs=sc.probs, gate=sc.gate)
+        F.moe_dispatch(sc.ids, q8, s8, cfg.experts, sc, rows)
+        total = rows * cfg.top_k
+        F.qgemm_grouped(sc.q8, sc.scale, bank_up.codes, bank_up.scale, bank_up.fmt, 2 * f,
+                        sc.gate_up, sc, total)
+        F.act_prep(sc.gate_up, None, None, bank_dn.signs, swiglu=True, rows=total,
+                   q_out=sc.q8_mid, scale_out=sc.scale_mid)
+        F.qgemm_grouped(sc.q8_mid, sc.scale_mid, bank_dn.codes, bank_dn.scale, bank_dn.fmt, h,
+                        sc.down, sc, total)
+        shared = None
+        if lw.shared_gate_up is not None:
+            fs = lw.shared_gate_up.n // 2
+            gu = self._linear(lw.shared_gate_up, q8, s8, rows,
+                              ws.gate_up.view(-1)[: ws.max_rows * 2 * fs].view(ws.max_rows, 2 * fs))
+            q8s, s8s = F.act_prep(gu, None, None, self._signs(lw.shared_down), swiglu=True,
+                                  rows=rows, q_out=ws.q8[fs], scale_out=ws.scale)
+            shared = self._linear(lw.shared_down, q8s, s8s, rows, ws.shared_out)
+        has_gate = lw.router.shape[0] == cfg.experts + 1
+        F.moe_combine(sc.down, sc.slots, sc.probs, shared, sc.gate if has_gate else None,
+                      ws.hidden, rows)
+        return ws.hidden
 
     def logits(self, p: Packet, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """fp32 logits [n_sel, vocab] of the selected rows (final norm + W8 head)."""

@@ -192,3 +192,80 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None,
                                       ptr(scratch[1]), ptr(out), stream()), "argmax")
     count_launches(2)
     return out
+
+
+# ---------------------------------------------------------------------------- MoE
+def router_topk(y: torch.Tensor, router_w: torch.Tensor, experts: int, top_k: int, *,
+                renorm: bool = True, rows: Optional[int] = None, ids=None, probs=None,
+                gate=None):
+    """Router projection + softmax + top-k (ties to the lower expert id).  ``router_w`` has
+    ``experts`` rows plus an optional shared-expert gate row.  Returns (ids int32 [M,k],
+    probs fp32 [M,k], sigmoid shared gate fp32 [M] or None)."""
+    _cuda(y, router_w)
+    m, h = y.shape
+    has_shared = router_w.shape[0] == experts + 1
+    dev = y.device
+    ids = torch.empty(m, top_k, dtype=torch.int32, device=dev) if ids is None else ids
+    probs = torch.empty(m, top_k, dtype=torch.float32, device=dev) if probs is None else probs
+    if has_shared and gate is None:
+        gate = torch.empty(m, dtype=torch.float32, device=dev)
+    check(native.lib().orinfer_router_topk(ptr(y), ptr(router_w), m if rows is None else rows, h,
+                                           experts, int(has_shared), top_k, int(renorm), ptr(ids),
+                                           ptr(probs), ptr(gate), stream()), "router_topk")
+    count_launches(1)
+    return ids, probs, gate
+
+
+class MoeScratch:
+    """Static buffers of one MoE layer evaluation for up to ``max_rows`` tokens."""
+
+    def __init__(self, max_rows: int, top_k: int, experts: int, hidden: int, ffn: int, device):
+        s = max_rows * top_k
+        e = lambda *shape, dt: torch.empty(*shape, dtype=dt, device=device)
+        self.max_tiles = (s + 127) // 128 + experts
+        self.ids = e(max_rows, top_k, dt=torch.int32)
+        self.probs = e(max_rows, top_k, dt=torch.float32)
+        self.gate = e(max_rows, dt=torch.float32)
+        self.counts = e(experts, dt=torch.int32)
+        self.offsets = e(experts + 1, dt=torch.int32)
+        self.tiles = torch.zeros(self.max_tiles, 4, dtype=torch.int32, device=device)
+        self.meta = torch.zeros(4, dtype=torch.int32, device=device)
+        self.slots = e(s, dt=torch.int32)
+        self.q8 = e(s, hidden, dt=torch.int8)
+        self.scale = e(s, dt=torch.float32)
+        self.gate_up = e(s, 2 * ffn, dt=torch.float16)
+        self.q8_mid = e(s, ffn, dt=torch.int8)
+        self.scale_mid = e(s, dt=torch.float32)
+        self.down = e(s, hidden, dt=torch.float16)
+
+
+def moe_dispatch(ids: torch.Tensor, q8: torch.Tensor, scale: torch.Tensor, experts: int,
+                 sc: MoeScratch, rows: int) -> None:
+    top_k = ids.shape[1]
+    check(native.lib().orinfer_moe_dispatch(
+        ptr(ids), rows, top_k, experts, ptr(q8), ptr(scale), q8.shape[1], ptr(sc.counts),
+        ptr(sc.offsets), ptr(sc.tiles), ptr(sc.meta), sc.max_tiles, ptr(sc.slots), ptr(sc.q8),
+        ptr(sc.scale), stream()), "moe_dispatch")
+    count_launches(3)
+
+
+def qgemm_grouped(a: torch.Tensor, a_scale: torch.Tensor, codes: torch.Tensor,
+                  w_scale: torch.Tensor, fmt: str, n: int, out: torch.Tensor, sc: MoeScratch,
+                  total_rows: int) -> torch.Tensor:
+    experts = codes.shape[0]
+    check(native.lib().orinfer_qgemm_grouped(
+        FMT[fmt], ptr(a), ptr(a_scale), ptr(codes), ptr(w_scale), ptr(out), total_rows, n,
+        a.shape[1], experts, ptr(sc.tiles), ptr(sc.meta), sc.max_tiles, stream()),
+        "qgemm_grouped")
+    count_launches(1)
+    return out
+
+
+def moe_combine(expert_out: torch.Tensor, slots: torch.Tensor, probs: torch.Tensor,
+                shared_out: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                out: torch.Tensor, rows: int) -> torch.Tensor:
+    check(native.lib().orinfer_moe_combine(ptr(expert_out), ptr(slots), ptr(probs), rows,
+                                           probs.shape[1], ptr(shared_out), ptr(gate), ptr(out),
+                                           out.shape[1], stream()), "moe_combine")
+    count_launches(1)
+    return out

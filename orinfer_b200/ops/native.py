@@ -51,6 +51,10 @@ def _load() -> ctypes.CDLL:
         "orinfer_attention_scratch_bytes": ([I, I, I, I], c_size_t),
         "orinfer_attention": ([P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, P, P], I),
         "orinfer_e8p_encode": ([P, P, c_longlong, P], I),
+        "orinfer_router_topk": ([P, P, I, I, I, I, I, I, P, P, P, P], I),
+        "orinfer_moe_dispatch": ([P, I, I, I, P, P, I, P, P, P, P, I, P, P, P, P], I),
+        "orinfer_moe_combine": ([P, P, P, I, I, P, P, P, I, P], I),
+        "orinfer_qgemm_grouped": ([I, P, P, P, P, P, I, I, I, I, P, P, I, P], I),
         "orinfer_attention_prefill": ([P, P, P, I, I, I, P, I, P, P, P, P, P, I, I, I, I, P], I),
     }
     for name, (args, res) in sig.items():

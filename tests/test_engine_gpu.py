@@ -65,3 +65,16 @@ def test_sampled_rows_use_host_law(cuda):
     a = _engine(w).generate(prompts, max_new=8, sampling=opt)
     b = _engine(w).generate(prompts[:1], max_new=8, sampling=opt)
     assert a[0] == b[0]
+
+
+def test_mtp_head_speculation_on_device(cuda, monkeypatch):
+    import dataclasses
+    cfg = dataclasses.replace(PRESETS["tiny"], mtp_layers=1)
+    w = random_model(cfg, seed=4).to(cuda)
+    prompts = _prompts(2, 20, seed=8)
+    plain = _engine(w, load=dict(mtp_drafts=0)).generate(prompts, max_new=10)
+    monkeypatch.setenv("ORINFER_SINGLE_MTP_POLICY", "fixed2")
+    eng = _engine(w, load=dict(mtp_drafts=2))
+    assert eng.runner_has_mtp()
+    assert eng.generate(prompts, max_new=10) == plain
+    assert eng.spec.statistics()["rounds"] > 0

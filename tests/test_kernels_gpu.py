@@ -285,3 +285,65 @@ def test_attention_prefill_matches_row_kernel(cuda):
     pos = torch.arange(pos0, pos0 + n, dtype=torch.int32, device=cuda)
     rows = F.attention(q, gate, req, pos, table, kc, vc, ks, vs)
     assert float((out.float() - rows.float()).abs().max()) < 2e-2
+
+
+@pytest.mark.parametrize("experts,top_k,shared", [(8, 2, False), (128, 8, False), (512, 10, True)])
+def test_router_topk(cuda, experts, top_k, shared):
+    from orinfer_b200.ops import functional as F
+    g = torch.Generator().manual_seed(experts)
+    m, h = 37, 256
+    y = torch.randn(m, h, generator=g).half().to(cuda)
+    w = (torch.randn(experts + int(shared), h, generator=g) * 0.1).half().to(cuda)
+    w[3] = w[1]                                             # exact tie -> lower id first
+    ids, probs, gate = F.router_topk(y, w, experts, top_k, renorm=True)
+    logits = y.float() @ w.float().t()
+    p = torch.softmax(logits[:, :experts], -1)
+    order = torch.sort(p, dim=-1, descending=True, stable=True).indices[:, :top_k]
+    ref_p = torch.gather(p, 1, order)
+    ref_p = ref_p / ref_p.sum(-1, keepdim=True)
+    same = (ids.long() == order).float().mean()
+    assert same > 0.98, same                                # fp32 sum order can swap near-ties
+    assert torch.allclose(probs.sum(-1), torch.ones(m, device=cuda), atol=1e-5)
+    agree = ids.long() == order
+    assert torch.allclose(probs[agree], ref_p[agree], atol=2e-4)
+    if shared:
+        assert torch.allclose(gate, torch.sigmoid(logits[:, experts]), atol=2e-4)
+
+
+@pytest.mark.parametrize("fmt", ["q4", "q2", "w8"])
+def test_moe_dispatch_grouped_gemm_combine(cuda, fmt):
+    """Dispatch -> grouped GEMM -> combine against per-assignment dense arithmetic."""
+    from orinfer_b200.ops import functional as F
+    g = torch.Generator().manual_seed(11)
+    m, h, n, experts, top_k = 300, 256, 384, 8, 2
+    ids = torch.stack([torch.randperm(experts, generator=g)[:top_k] for _ in range(m)]) \
+        .to(torch.int32).to(cuda)
+    ids[:40] = torch.tensor([5, 2], dtype=torch.int32)      # one expert with > 128 rows
+    probs = torch.rand(m, top_k, generator=g).to(cuda)
+    q8 = torch.randint(-127, 128, (m, h), generator=g, dtype=torch.int8).to(cuda)
+    sa = (torch.rand(m, generator=g) * 0.05 + 1e-3).to(cuda)
+    banks = [_rand_weight(fmt, n, h, cuda, seed=100 + e) for e in range(experts)]
+    codes = torch.stack([b[0] for b in banks]).contiguous()
+    wscale = torch.stack([b[1] for b in banks]).contiguous()
+    sc = F.MoeScratch(m, top_k, experts, h, n // 2, cuda)
+    F.moe_dispatch(ids, q8, sa, experts, sc, m)
+    out = torch.zeros(m * top_k, n, dtype=torch.float16, device=cuda)
+    F.qgemm_grouped(sc.q8, sc.scale, codes, wscale, fmt, n, out, sc, m * top_k)
+    torch.cuda.synchronize()
+    counts = torch.bincount(ids.flatten().long(), minlength=experts)
+    assert torch.equal(sc.counts.long(), counts)
+    slots = sc.slots.view(m, top_k).long()
+    assert sorted(slots.flatten().tolist()) == list(range(m * top_k))
+    for r in (0, 1, 39, 40, 150, 299):
+        for j in range(top_k):
+            e = int(ids[r, j])
+            ref = R.qgemm(q8[r:r + 1], sa[r:r + 1], banks[e][2], banks[e][1])
+            assert torch.equal(out[slots[r, j]].float(), ref[0]), (r, j)
+    # stable slots: within an expert, slots follow (row, k) order
+    for e in range(experts):
+        s = slots.flatten()[ids.flatten().long() == e]
+        assert torch.equal(s, torch.sort(s).values)
+    hidden_out = torch.zeros(m, n, dtype=torch.float16, device=cuda)
+    F.moe_combine(out, sc.slots, probs, None, None, hidden_out, m)
+    ref = (out[slots].float() * probs[..., None]).sum(1)
+    assert torch.allclose(hidden_out.float(), ref, atol=2e-2, rtol=2e-3)

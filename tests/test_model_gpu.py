@@ -78,3 +78,20 @@ def test_batch_invariance(cuda):
     alone = alone.clone()
     _, both = runner.greedy(_packet(runner, [b, a], [0, 0], cuda, [[2], [3]]))
     assert torch.equal(alone[0], both[1])
+
+
+def test_tiny_moe_matches_torch_runner(cuda):
+    """MoE decoder (router top-k, dispatch, grouped expert GEMM, combine) against the
+    PyTorch packed-row runner."""
+    from orinfer_b200.models.runner import KVPool, ModelRunner
+    from orinfer_b200.models.torch_runner import TorchRunner
+    cfg = PRESETS["tiny-moe"]
+    w_cpu = random_model(cfg, seed=5)
+    dev_runner = ModelRunner(w_cpu.to(cuda), KVPool.allocate(cfg, 6, cuda), 256)
+    cpu_runner = TorchRunner(w_cpu, KVPool.allocate(cfg, 6, "cpu"), 256)
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, cfg.vocab, (150,), generator=g).tolist()]
+    _, lg = dev_runner.greedy(_packet(dev_runner, prompts, [0], cuda, [[1, 2]]))
+    _, lr = cpu_runner.greedy(_packet(cpu_runner, prompts, [0], "cpu", [[1, 2]]))
+    cos = torch.nn.functional.cosine_similarity(lg[0].cpu(), lr[0], dim=0)
+    assert cos > 0.998, cos
