@@ -109,6 +109,20 @@ int orinfer_attention_prefill(const __half* q, const __half* gate, const int* ch
                               const __half* vscale, __half* out, int qh, int kvh, int head_dim,
                               int num_pages, cudaStream_t stream);
 
+// ---- gated-delta-rule linear attention (segments: int32 [n,4] = first row, rows, 0, 0;
+// the state slot of a row is row_slot[row]; a segment starting at position 0 starts fresh)
+int orinfer_small_proj(const __half* x, const __half* w, float* out, int rows, int hidden, int n,
+                       cudaStream_t stream);
+int orinfer_gdn_conv(const __half* x, int x_stride, const __half* weight, __half* hist,
+                     const int* row_first, const int* row_slot, const int* row_pos,
+                     const int* segs, int n_segs, int rows, int hk, int hv, int head_dim, __half* y, cudaStream_t stream);
+int orinfer_gdn_scan(const __half* qkv, const float* ab, const float* a_log, const float* dt_bias,
+                     const int* segs, int n_segs, const int* row_slot, const int* row_pos, int hk,
+                     int hv, int head_dim, float* state, float* out, cudaStream_t stream);
+int orinfer_gdn_gated_norm(const float* o, const __half* z, int z_stride, const __half* w,
+                           float eps, int sigmoid_gate, int rows, int hv, int head_dim,
+                           __half* y, cudaStream_t stream);
+
 // ---- E8P nearest-codeword encoder: x fp32 [V,8] -> int32 codes [V]
 int orinfer_e8p_encode(const float* x, int* codes, long long vectors, cudaStream_t stream);
 

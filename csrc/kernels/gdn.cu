@@ -1,0 +1,280 @@
+// Gated-delta-rule linear attention kernels, natively batched over the requests of a packet
+// through a segment table (first row, rows, state slot):
+//   small_proj   : fp32 out[M,N] = x[M,H] . W[N,H]^T for narrow N (the a/b gate projection)
+//   gdn_conv     : width-4 causal depthwise conv over q|k|v channels with a 3-row per-request
+//                  history, SiLU, per-head L2 norm of q and k; then the history update
+//   gdn_scan     : exact sequential recurrence on the FP32 state (one CTA per segment and
+//                  value head; the 128x128 state lives in registers across the segment)
+//   gdn_gated_norm : per-head RMSNorm(o) * w * SiLU(z) (or sigmoid(z))
+// Replace gdn_ab_tensorcore (kernels/cuda/operators/op07_gdn_ab.py:16), gdn_conv_prep
+// (op08_gdn_conv_prep.py:23-278), gdn_gates (op09_gdn_gates.py:26-76), gdn_sequence
+// (kernels/cuda/model/gdn_sequence.py:19-250) and gated_norm (op17_gdn_gated_norm.py:15-71).
+#include "api.h"
+#include "common.cuh"
+
+namespace orinfer {
+
+// The state slot of a segment is row_slot[row_start]; a segment whose first row sits at
+// position 0 of its request starts from a zero state and a zero history, so a reused slot
+// needs no reset.
+struct Segment {
+  int row_start, rows, pad0, pad1;
+};
+
+// ---------------------------------------------------------------- small projection
+__global__ void __launch_bounds__(256) small_proj_kernel(const __half* __restrict__ x,
+                                                         const __half* __restrict__ w,
+                                                         float* __restrict__ out, int hidden,
+                                                         int n) {
+  const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const __half* xr = x + static_cast<size_t>(row) * hidden;
+  for (int e = warp; e < n; e += blockDim.x >> 5) {
+    const __half* wr = w + static_cast<size_t>(e) * hidden;
+    float acc = 0.f;
+    for (int i = lane * 8; i < hidden; i += 256) {
+      const int4 xa = *reinterpret_cast<const int4*>(xr + i);
+      const int4 wa = *reinterpret_cast<const int4*>(wr + i);
+      const __half2* xh = reinterpret_cast<const __half2*>(&xa);
+      const __half2* wh = reinterpret_cast<const __half2*>(&wa);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 a = __half22float2(xh[j]), b = __half22float2(wh[j]);
+        acc = fmaf(a.x, b.x, acc);
+        acc = fmaf(a.y, b.y, acc);
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) out[static_cast<size_t>(row) * n + e] = acc;
+  }
+}
+
+// ---------------------------------------------------------------- conv + SiLU + L2 norm
+// grid (rows, heads) with heads = 2*HK + HV of D channels each; block = D threads.
+// x row layout: q | k | v | z  (z untouched).  hist: fp16 [slots, 3, conv_dim], oldest first.
+template <int D>
+__global__ void __launch_bounds__(D) gdn_conv_kernel(
+    const __half* __restrict__ x, int x_stride, const __half* __restrict__ weight,
+    const __half* __restrict__ hist, const int* __restrict__ row_first,
+    const int* __restrict__ row_slot, const int* __restrict__ row_pos, int conv_dim,
+    int qk_heads, __half* __restrict__ y) {
+  const int row = blockIdx.x, head = blockIdx.y, c = head * D + threadIdx.x;
+  const int first = row_first[row], slot = row_slot[row];
+  const bool fresh = row_pos[first] == 0;
+  const __half* wc = weight + static_cast<size_t>(c) * 4;
+  float acc = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int src = row - 3 + j;                       // tap j reads the row 3-j steps back
+    float v;
+    if (src >= first) {
+      v = __half2float(x[static_cast<size_t>(src) * x_stride + c]);
+    } else {
+      // rows before the chunk come from the history: index 3 - (first - src) from its end
+      const int back = first - src;                    // 1..3
+      v = fresh ? 0.f
+                : __half2float(hist[(static_cast<size_t>(slot) * 3 + (3 - back)) * conv_dim + c]);
+    }
+    acc = fmaf(v, __half2float(wc[j]), acc);
+  }
+  float val = round_f16(acc * __fdiv_rn(1.f, 1.f + expf(-acc)));
+  if (head < qk_heads) {
+    __shared__ float red[D / 32];
+    float ss = warp_sum(val * val);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) tot += red[i];
+    val = round_f16(val * rsqrtf(tot + 1e-6f));
+  }
+  y[static_cast<size_t>(row) * conv_dim + c] = __float2half_rn(val);
+}
+
+// One CTA per segment: new history = last three pre-conv rows of (old history ++ chunk).
+__global__ void __launch_bounds__(256) gdn_history_kernel(const __half* __restrict__ x,
+                                                          int x_stride,
+                                                          const Segment* __restrict__ segs,
+                                                          const int* __restrict__ row_slot,
+                                                          const int* __restrict__ row_pos,
+                                                          int conv_dim,
+                                                          __half* __restrict__ hist) {
+  const Segment s = segs[blockIdx.x];
+  const bool fresh = row_pos[s.row_start] == 0;
+  __half* h = hist + static_cast<size_t>(row_slot[s.row_start]) * 3 * conv_dim;
+  for (int c = threadIdx.x; c < conv_dim; c += blockDim.x) {
+    __half v[3];
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      const int idx = s.rows - 3 + j;                  // index into the chunk, < 0 = history
+      v[j] = idx >= 0 ? x[static_cast<size_t>(s.row_start + idx) * x_stride + c]
+                      : (fresh ? __float2half(0.f) : h[static_cast<size_t>(3 + idx) * conv_dim + c]);
+    }
+#pragma unroll
+    for (int j = 0; j < 3; ++j) h[static_cast<size_t>(j) * conv_dim + c] = v[j];
+  }
+}
+
+// ---------------------------------------------------------------- sequential scan
+// grid (HV, segments); 256 threads: thread t owns value column dv = t % D and key rows
+// [ROWS*(t/D), +ROWS) of the DxD state, kept in registers for the whole segment.
+template <int D>
+__global__ void __launch_bounds__(256) gdn_scan_kernel(
+    const __half* __restrict__ qkv, int conv_dim, const float* __restrict__ ab,
+    const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+    const Segment* __restrict__ segs, const int* __restrict__ row_slot,
+    const int* __restrict__ row_pos, int hk, int hv, float* __restrict__ state,
+    float* __restrict__ out) {
+  constexpr int PARTS = 256 / D, ROWS = D / PARTS;
+  const int vh = blockIdx.x;
+  const Segment seg = segs[blockIdx.y];
+  const int kh = vh / (hv / hk);
+  const int dv = threadIdx.x % D, part_id = threadIdx.x / D;
+  const int slot = row_slot[seg.row_start];
+  const bool fresh = row_pos[seg.row_start] == 0;
+  float* sp = state + ((static_cast<size_t>(slot) * hv + vh) * D + part_id * ROWS) * D + dv;
+  float s[ROWS];
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) s[i] = fresh ? 0.f : sp[static_cast<size_t>(i) * D];
+  __shared__ float ks[D], qs[D], part[PARTS][D], opart[PARTS][D];
+  const float alog = expf(a_log[vh]), bias = dt_bias[vh];
+  const float scale = rsqrtf(static_cast<float>(D));
+  const int dk_total = hk * D;
+  for (int t = 0; t < seg.rows; ++t) {
+    const size_t row = static_cast<size_t>(seg.row_start + t);
+    const __half* base = qkv + row * conv_dim;
+    if (threadIdx.x < D) {
+      qs[threadIdx.x] = __half2float(base[kh * D + threadIdx.x]) * scale;
+    } else if (threadIdx.x < 2 * D) {
+      ks[threadIdx.x - D] = __half2float(base[dk_total + kh * D + threadIdx.x - D]);
+    }
+    const float a = ab[row * 2 * hv + vh], b = ab[row * 2 * hv + hv + vh];
+    const float xg = a + bias;
+    const float softplus = xg > 20.f ? xg : log1pf(expf(xg));
+    const float decay = expf(-alog * softplus);
+    const float beta = __fdiv_rn(1.f, 1.f + expf(-b));
+    const float v = __half2float(base[2 * dk_total + vh * D + dv]);
+    __syncthreads();
+    float pred = 0.f;
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) {
+      s[i] *= decay;
+      pred = fmaf(s[i], ks[part_id * ROWS + i], pred);
+    }
+    part[part_id][dv] = pred;
+    __syncthreads();
+    float full = 0.f;
+#pragma unroll
+    for (int i = 0; i < PARTS; ++i) full += part[i][dv];
+    const float delta = beta * (v - full);
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) {
+      s[i] = fmaf(ks[part_id * ROWS + i], delta, s[i]);
+      o = fmaf(s[i], qs[part_id * ROWS + i], o);
+    }
+    opart[part_id][dv] = o;
+    __syncthreads();
+    if (part_id == 0) {
+      float tot = 0.f;
+#pragma unroll
+      for (int i = 0; i < PARTS; ++i) tot += opart[i][dv];
+      out[(row * hv + vh) * D + dv] = tot;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) sp[static_cast<size_t>(i) * D] = s[i];
+}
+
+// ---------------------------------------------------------------- gated norm
+// grid (rows, HV), D threads: y = rmsnorm(o) * w * silu(z)  (sigmoid(z) when sigmoid_gate)
+template <int D>
+__global__ void __launch_bounds__(D) gdn_gated_norm_kernel(
+    const float* __restrict__ o, const __half* __restrict__ z, int z_stride,
+    const __half* __restrict__ w, float eps, int sigmoid_gate, int hv,
+    __half* __restrict__ y) {
+  const int row = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  const float v = o[(static_cast<size_t>(row) * hv + h) * D + d];
+  __shared__ float red[D / 32];
+  const float ss = warp_sum(v * v);
+  if ((d & 31) == 0) red[d >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) tot += red[i];
+  const float n = v * rsqrtf(tot / D + eps) * __half2float(w[d]);
+  const float zf = __half2float(z[static_cast<size_t>(row) * z_stride + h * D + d]);
+  const float sg = __fdiv_rn(1.f, 1.f + expf(-zf));
+  const float gate = sigmoid_gate ? sg : zf * sg;
+  y[(static_cast<size_t>(row) * hv + h) * D + d] = __float2half_rn(n * gate);
+}
+
+}  // namespace orinfer
+
+using namespace orinfer;
+
+extern "C" {
+
+int orinfer_small_proj(const __half* x, const __half* w, float* out, int rows, int hidden, int n,
+                       cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (hidden % 8) return -1;
+  small_proj_kernel<<<rows, 256, 0, stream>>>(x, w, out, hidden, n);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// x: fp16 [rows, x_stride] with q|k|v in the first conv_dim channels; y: fp16 [rows, conv_dim].
+// segs: int32 [n_segs, 4] = (first row, rows, 0, 0).  Updates hist in place.
+int orinfer_gdn_conv(const __half* x, int x_stride, const __half* weight, __half* hist,
+                     const int* row_first, const int* row_slot, const int* row_pos,
+                     const int* segs, int n_segs,
+                     int rows, int hk, int hv, int head_dim, __half* y, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (head_dim != 128 && head_dim != 64) return -1;
+  const int conv_dim = (2 * hk + hv) * head_dim;
+  dim3 grid(rows, 2 * hk + hv);
+  if (head_dim == 128)
+    gdn_conv_kernel<128><<<grid, 128, 0, stream>>>(x, x_stride, weight, hist, row_first, row_slot,
+                                                   row_pos, conv_dim, 2 * hk, y);
+  else
+    gdn_conv_kernel<64><<<grid, 64, 0, stream>>>(x, x_stride, weight, hist, row_first, row_slot,
+                                                 row_pos, conv_dim, 2 * hk, y);
+  gdn_history_kernel<<<n_segs, 256, 0, stream>>>(x, x_stride,
+                                                 reinterpret_cast<const Segment*>(segs), row_slot,
+                                                 row_pos, conv_dim, hist);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// qkv: conv output fp16 [rows, conv_dim]; ab fp32 [rows, 2*HV]; state fp32 (below);
+// out fp32 [rows, HV, D].  head_dim D is 64 or 128; state is [slots, HV, D, D].
+int orinfer_gdn_scan(const __half* qkv, const float* ab, const float* a_log, const float* dt_bias,
+                     const int* segs, int n_segs, const int* row_slot, const int* row_pos, int hk,
+                     int hv, int head_dim, float* state, float* out, cudaStream_t stream) {
+  if (n_segs <= 0) return 0;
+  if ((head_dim != 128 && head_dim != 64) || hv % hk) return -1;
+  const Segment* sg = reinterpret_cast<const Segment*>(segs);
+  const int conv_dim = (2 * hk + hv) * head_dim;
+  if (head_dim == 128)
+    gdn_scan_kernel<128><<<dim3(hv, n_segs), 256, 0, stream>>>(
+        qkv, conv_dim, ab, a_log, dt_bias, sg, row_slot, row_pos, hk, hv, state, out);
+  else
+    gdn_scan_kernel<64><<<dim3(hv, n_segs), 256, 0, stream>>>(
+        qkv, conv_dim, ab, a_log, dt_bias, sg, row_slot, row_pos, hk, hv, state, out);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int orinfer_gdn_gated_norm(const float* o, const __half* z, int z_stride, const __half* w,
+                           float eps, int sigmoid_gate, int rows, int hv, int head_dim,
+                           __half* y, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (head_dim == 128)
+    gdn_gated_norm_kernel<128><<<dim3(rows, hv), 128, 0, stream>>>(o, z, z_stride, w, eps,
+                                                                   sigmoid_gate, hv, y);
+  else if (head_dim == 64)
+    gdn_gated_norm_kernel<64><<<dim3(rows, hv), 64, 0, stream>>>(o, z, z_stride, w, eps,
+                                                                 sigmoid_gate, hv, y);
+  else
+    return -1;
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -22,6 +22,8 @@ full prefix pages, and sampling depends only on the request's own history.
 
 from __future__ import annotations
 
+import dataclasses
+
 import time
 from collections import deque
 from dataclasses import dataclass, field
@@ -77,6 +79,13 @@ class _DecodeGraph:
         self.logits = torch.zeros(rows, engine.cfg.vocab, dtype=torch.float32, device=dev)
         self.packet = Packet(self.ids, self.req, self.pos, engine.page_table_dev, rows,
                              engine.max_context)
+        if engine.recurrent:
+            # every decode row is its own run; the state slot is read from ``req`` on the device
+            ar = torch.arange(rows, dtype=torch.int32, device=dev)
+            self.packet.row_first = ar
+            self.packet.segments = torch.stack(
+                [ar, torch.ones_like(ar), torch.zeros_like(ar), torch.zeros_like(ar)], 1).contiguous()
+            self.packet.n_segments = rows
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.trials = 0
 
@@ -94,6 +103,13 @@ class Engine:
         self.sched.validate()
         self.device = weights.embed_q.device
         self.on_gpu = self.device.type == "cuda"
+        # Recurrent (GDN) layers keep per-request state that cannot be rebuilt from KV pages:
+        # prefix reuse would start a request without its state and a rejected draft would
+        # leave the state ahead of the committed text, so both stay off for hybrid models.
+        self.recurrent = self.cfg.arch == "hybrid"
+        if self.recurrent:
+            self.load = dataclasses.replace(self.load, prefix_cache_bytes=0, mtp_drafts=0,
+                                            prompt_lookup=False)
         self.max_context = max_context or min(self.cfg.max_context, 32768)
         self.max_pages_per_req = (self.max_context + PAGE_TOKENS - 1) // PAGE_TOKENS
         self.max_rows = max_rows or max(self.sched.prefill_chunk + self.sched.max_active, 256)
@@ -382,6 +398,12 @@ class Engine:
         packet = Packet(self._upload("ids", ids), self._upload("req", req_rows),
                         self._upload("pos", pos), self.page_table_dev, rows, max_kv,
                         self._upload("sel", logit_rows).long())
+        if self.recurrent:
+            segs = [[i, 1, 0, 0] for i in range(n_decode)] + [[c[0], c[1], 0, 0] for c in chunk_rows]
+            first = list(range(n_decode)) + [c[0] for c in chunk_rows for _ in range(c[1])]
+            packet.segments = self._upload("segs", [v for g in segs for v in g]).view(-1, 4)
+            packet.row_first = self._upload("first", first)
+            packet.n_segments = len(segs)
         if chunk_rows and self.on_gpu:
             flat = [v for c in chunk_rows for v in c]
             packet.chunks = self._upload("chunks", flat).view(-1, 4)

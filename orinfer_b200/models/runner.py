@@ -112,6 +112,27 @@ class Packet:
     chunks: Optional[torch.Tensor] = None
     max_q_len: int = 0
     decode_rows: int = 0
+    # Runs of consecutive rows of one request, for the recurrent (GDN) layers: int32 [S, 4] =
+    # (first row, rows, 0, 0) and, per row, the first row of its run.  Derived from row_req on
+    # the host when absent (one readback), so graph-captured packets must carry them.
+    segments: Optional[torch.Tensor] = None
+    n_segments: int = 0
+    row_first: Optional[torch.Tensor] = None
+
+    def ensure_segments(self) -> None:
+        if self.segments is not None:
+            return
+        req = self.row_req[: self.rows].cpu().tolist()
+        segs, first, start = [], [], 0
+        for i in range(self.rows + 1):
+            if i == self.rows or (i > 0 and req[i] != req[i - 1]):
+                segs.append([start, i - start, 0, 0])
+                first += [start] * (i - start)
+                start = i
+        dev = self.row_req.device
+        self.segments = torch.tensor(segs, dtype=torch.int32, device=dev)
+        self.row_first = torch.tensor(first, dtype=torch.int32, device=dev)
+        self.n_segments = len(segs)
 
 
 class ModelRunner:
@@ -174,6 +195,53 @@ class ModelRunner:
                             scale_out=ws.scale)
         return self._row_parallel("o", lw.o, q8, sc, rows)
 
+    def _gdn_state(self, slots: int):
+        """Recurrent pools, one entry per page-table row: FP32 state [slots, HV, D, D] and the
+        FP16 three-row convolution history [slots, 3, conv_dim] of every GDN layer."""
+        st = getattr(self, "_gdn", None)
+        if st is None or st["slots"] < slots:
+            cfg = self.cfg
+            hk, hv, d = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim
+            conv_dim = (2 * hk + hv) * d
+            n = sum(lw.kind == "gdn" for lw in self.w.layers)
+            ws, dev = self.ws, self.device
+            st = self._gdn = dict(
+                slots=slots,
+                index={i: j for j, i in enumerate(i for i, lw in enumerate(self.w.layers)
+                                                  if lw.kind == "gdn")},
+                state=torch.zeros(n, slots, hv, d, d, dtype=torch.float32, device=dev),
+                hist=torch.zeros(n, slots, 3, conv_dim, dtype=torch.float16, device=dev),
+                proj=torch.empty(ws.max_rows, conv_dim + hv * d, dtype=torch.float16, device=dev),
+                conv=torch.empty(ws.max_rows, conv_dim, dtype=torch.float16, device=dev),
+                ab=torch.empty(ws.max_rows, 2 * hv, dtype=torch.float32, device=dev),
+                o=torch.empty(ws.max_rows, hv, d, dtype=torch.float32, device=dev),
+                mix=torch.empty(ws.max_rows, hv * d, dtype=torch.float16, device=dev))
+        return st
+
+    def _gdn_block(self, lw: LayerWeights, layer: int, x, p: Packet, rows: int):
+        """Gated-delta-rule mixer: norm+rotate+A8 -> q|k|v|z projection (tensor cores) and the
+        fp16 a/b gate projection -> conv4+SiLU+L2 with per-request history -> sequential FP32
+        recurrence -> gated RMSNorm -> rotate+A8 -> output projection."""
+        cfg = self.cfg
+        hk, hv, d = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim
+        conv_dim = (2 * hk + hv) * d
+        p.ensure_segments()
+        st = self._gdn_state(p.page_table.shape[0])
+        j = st["index"][layer]
+        y16 = self.ws.attn_norm(rows, cfg.hidden)
+        q8, sc = self._prep(x, lw.in_norm, self._signs(lw.gdn_qkvz), rows, y_out=y16)
+        proj = self._linear(lw.gdn_qkvz, q8, sc, rows, st["proj"])
+        F.small_proj(y16, lw.gdn_ab, rows=rows, out=st["ab"])
+        F.gdn_conv(proj, lw.gdn_conv, st["hist"][j], p.row_first, p.row_req, p.row_pos,
+                   p.segments, p.n_segments, rows, hk, hv, d, out=st["conv"])
+        F.gdn_scan(st["conv"], st["ab"], lw.gdn_a_log, lw.gdn_dt_bias, p.segments, p.n_segments,
+                   p.row_req, p.row_pos, hk, hv, d, st["state"][j], out=st["o"])
+        F.gdn_gated_norm(st["o"], proj[:, conv_dim:], lw.gdn_norm, cfg.eps, rows, hv, d,
+                         out=st["mix"])
+        q8, sc = F.act_prep(st["mix"], None, None, self._signs(lw.gdn_out), rows=rows,
+                            q_out=self.ws.q8[hv * d], scale_out=self.ws.scale)
+        return self._row_parallel("gdn_out", lw.gdn_out, q8, sc, rows)
+
     def _reduce(self, x, rows: int):
         """Completes a row-parallel projection (no-op without tensor parallelism)."""
         return x
@@ -215,7 +283,7 @@ class ModelRunner:
             if lw.kind == "attn":
                 x = self._attention_block(lw, self._attn_index[i], x, p, rows, True)
             else:
-                x = self.layer_hooks["gdn"](self, lw, i, x, p, rows)
+                x = self._gdn_block(lw, i, x, p, rows)
             if cfg.experts:
                 x = self._moe_ffn(lw, x, rows)
             else:

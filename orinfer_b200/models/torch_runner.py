@@ -87,6 +87,35 @@ class TorchRunner:
                                       None if gate is None else gate[i:i + 1])[0]
         return out
 
+    def _gdn(self, lw: LayerWeights, layer: int, y: torch.Tensor, p: Packet) -> torch.Tensor:
+        """Gated-delta-rule mixer per run of rows of one request; the recurrent state and the
+        convolution history live per page-table row and restart when a run begins at
+        position 0."""
+        from ..ref import gdn_ref as G
+        cfg = self.cfg
+        hk, hv, d = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim
+        dk, conv_dim = hk * d, (2 * hk + hv) * d
+        if not hasattr(self, "_gdn_pool"):
+            self._gdn_pool = {}
+        proj = self._linear(lw.gdn_qkvz, y)
+        ab = R.f16(y).float() @ lw.gdn_ab.float().t()
+        g, beta = G.gates(ab, lw.gdn_a_log, lw.gdn_dt_bias)
+        p.ensure_segments()
+        out = torch.empty(p.rows, hv * d)
+        for start, n, _a, _b in p.segments.tolist():
+            slot, pos0 = int(p.row_req[start]), int(p.row_pos[start])
+            key = (layer, slot)
+            if pos0 == 0 or key not in self._gdn_pool:
+                self._gdn_pool[key] = (torch.zeros(hv, d, d), torch.zeros(3, conv_dim))
+            state, hist = self._gdn_pool[key]
+            sl = slice(start, start + n)
+            yc, hist = G.conv_silu_l2(proj[sl, :conv_dim], hist, lw.gdn_conv, dk, d)
+            o, state = G.recurrence(yc[:, :dk].reshape(n, hk, d), yc[:, dk:2 * dk].reshape(n, hk, d),
+                                    yc[:, 2 * dk:].reshape(n, hv, d), g[sl], beta[sl], state)
+            self._gdn_pool[key] = (state, hist)
+            out[sl] = G.gated_norm(o, proj[sl, conv_dim:].reshape(n, hv, d), lw.gdn_norm, cfg.eps)
+        return out
+
     def _reduce(self, x: torch.Tensor) -> torch.Tensor:
         return x
 
@@ -109,7 +138,7 @@ class TorchRunner:
                 mix = self._attention(lw, self._attn_index[i], y, p, cos, sin)
                 x = self._reduce(self._linear(lw.o, mix))
             else:
-                x = self.layer_hooks["gdn"](self, lw, i, y, p)
+                x = self._reduce(self._linear(lw.gdn_out, self._gdn(lw, i, y, p)))
             resid = resid + x
             y = R.rms_norm(resid, lw.post_norm, cfg.eps, zc)
             if cfg.experts:

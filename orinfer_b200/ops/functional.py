@@ -269,3 +269,71 @@ def moe_combine(expert_out: torch.Tensor, slots: torch.Tensor, probs: torch.Tens
                                            out.shape[1], stream()), "moe_combine")
     count_launches(1)
     return out
+
+
+# ---------------------------------------------------------------- gated delta rule
+def small_proj(x: torch.Tensor, w: torch.Tensor, rows: Optional[int] = None,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 ``x[rows, H] @ w[N, H]^T`` for a narrow fp16 weight (the GDN a/b gates)."""
+    _cuda(x, w)
+    assert x.dtype == torch.float16 and w.dtype == torch.float16 and x.is_contiguous()
+    rows = x.shape[0] if rows is None else rows
+    if out is None:
+        out = torch.empty(x.shape[0], w.shape[0], dtype=torch.float32, device=x.device)
+    check(native.lib().orinfer_small_proj(ptr(x), ptr(w), ptr(out), rows, x.shape[1], w.shape[0],
+                                          stream()), "small_proj")
+    count_launches(1)
+    return out
+
+
+def gdn_conv(x: torch.Tensor, weight: torch.Tensor, hist: torch.Tensor, row_first: torch.Tensor,
+             row_slot: torch.Tensor, row_pos: torch.Tensor, segs: torch.Tensor, n_segs: int,
+             rows: int, hk: int, hv: int, head_dim: int,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal conv4 + SiLU + L2(q, k) over the q|k|v channels of ``x`` [rows, >= conv_dim];
+    ``hist`` fp16 [slots, 3, conv_dim] is read, then advanced in place per segment."""
+    _cuda(x, weight, hist, row_first, row_slot, row_pos, segs)
+    conv_dim = (2 * hk + hv) * head_dim
+    assert x.dtype == torch.float16 and x.stride(1) == 1 and hist.shape[-1] == conv_dim
+    assert weight.shape == (conv_dim, 4) and weight.is_contiguous()
+    if out is None:
+        out = torch.empty(x.shape[0], conv_dim, dtype=torch.float16, device=x.device)
+    check(native.lib().orinfer_gdn_conv(ptr(x), x.stride(0), ptr(weight), ptr(hist),
+                                        ptr(row_first), ptr(row_slot), ptr(row_pos), ptr(segs),
+                                        n_segs, rows,
+                                        hk, hv, head_dim, ptr(out), stream()), "gdn_conv")
+    count_launches(2)
+    return out
+
+
+def gdn_scan(qkv: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+             segs: torch.Tensor, n_segs: int, row_slot: torch.Tensor, row_pos: torch.Tensor,
+             hk: int, hv: int, head_dim: int, state: torch.Tensor,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Sequential gated-delta recurrence; ``state`` fp32 [slots, HV, D, D] updated in place."""
+    _cuda(qkv, ab, a_log, dt_bias, segs, state, row_slot, row_pos)
+    assert ab.dtype == torch.float32 and state.dtype == torch.float32 and state.is_contiguous()
+    assert a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32
+    if out is None:
+        out = torch.empty(qkv.shape[0], hv, head_dim, dtype=torch.float32, device=qkv.device)
+    check(native.lib().orinfer_gdn_scan(ptr(qkv), ptr(ab), ptr(a_log), ptr(dt_bias), ptr(segs),
+                                        n_segs, ptr(row_slot), ptr(row_pos), hk, hv, head_dim,
+                                        ptr(state), ptr(out), stream()),
+          "gdn_scan")
+    count_launches(1)
+    return out
+
+
+def gdn_gated_norm(o: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, rows: int,
+                   hv: int, head_dim: int, sigmoid_gate: bool = False,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``rmsnorm(o) * w * silu(z)`` per head; ``z`` may be a column view of the projection."""
+    _cuda(o, z, weight)
+    assert o.dtype == torch.float32 and z.dtype == torch.float16 and z.stride(1) == 1
+    if out is None:
+        out = torch.empty(o.shape[0], hv * head_dim, dtype=torch.float16, device=o.device)
+    check(native.lib().orinfer_gdn_gated_norm(ptr(o), ptr(z), z.stride(0), ptr(weight), float(eps),
+                                              int(sigmoid_gate), rows, hv, head_dim, ptr(out),
+                                              stream()), "gdn_gated_norm")
+    count_launches(1)
+    return out

@@ -55,6 +55,10 @@ def _load() -> ctypes.CDLL:
         "orinfer_moe_dispatch": ([P, I, I, I, P, P, I, P, P, P, P, I, P, P, P, P], I),
         "orinfer_moe_combine": ([P, P, P, I, I, P, P, P, I, P], I),
         "orinfer_qgemm_grouped": ([I, P, P, P, P, P, I, I, I, I, P, P, I, P], I),
+        "orinfer_small_proj": ([P, P, P, I, I, I, P], I),
+        "orinfer_gdn_conv": ([P, I, P, P, P, P, P, P, I, I, I, I, I, P, P], I),
+        "orinfer_gdn_scan": ([P, P, P, P, P, I, P, P, I, I, I, P, P, P], I),
+        "orinfer_gdn_gated_norm": ([P, P, I, P, c_float, I, I, I, I, P, P], I),
         "orinfer_attention_prefill": ([P, P, P, I, I, I, P, I, P, P, P, P, P, I, I, I, I, P], I),
     }
     for name, (args, res) in sig.items():
