@@ -88,6 +88,15 @@ int orinfer_moe_dispatch(const int* ids, int rows, int top_k, int experts, const
 int orinfer_moe_combine(const __half* expert_out, const int* slots, const float* probs, int rows,
                         int top_k, const __half* shared_out, const float* shared_gate,
                         __half* out, int hidden, cudaStream_t stream);
+int orinfer_moe_dispatch_ep(const int* ids, int rows, int top_k, int base_expert,
+                            int local_experts, const int8_t* q8, const float* scale, int K,
+                            int* counts, int* offsets, int* tiles, int* meta, int max_tiles,
+                            int* slots, int8_t* q8_sorted, float* scale_sorted,
+                            cudaStream_t stream);
+int orinfer_moe_combine_peer(const __half* expert_out, const int* slots, const float* probs,
+                             int rows, int top_k, const __half* shared_out,
+                             const float* shared_gate, const OrinferPeerOut* peers, int hidden,
+                             cudaStream_t stream);
 int orinfer_qgemm_grouped(int fmt, const int8_t* a, const float* a_scale, const void* w,
                           const __half* w_scale, void* out, int S, int N, int K, int experts,
                           const int* tiles, const int* meta, int max_tiles, cudaStream_t stream);

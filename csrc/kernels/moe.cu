@@ -6,6 +6,7 @@
 // expert_dispatch (moe.py:286) and moe_combine (moe.py:498-557) of the reference.
 #include "api.h"
 #include "common.cuh"
+#include "tp_comm.cuh"
 
 namespace orinfer {
 
@@ -79,11 +80,14 @@ __global__ void __launch_bounds__(256) router_topk_kernel(
 }
 
 // ---------------------------------------------------------------- counts (one CTA per expert)
+// Under expert parallelism a rank owns experts [base, base + gridDim.x): ids outside that
+// range are left to their owners (their slot stays -1 and the combine skips them).
 __global__ void __launch_bounds__(256) moe_count_kernel(const int* __restrict__ ids, int assigns,
+                                                        int base_expert,
                                                         int* __restrict__ counts) {
   const int e = blockIdx.x;
   int c = 0;
-  for (int i = threadIdx.x; i < assigns; i += blockDim.x) c += ids[i] == e;
+  for (int i = threadIdx.x; i < assigns; i += blockDim.x) c += ids[i] == e + base_expert;
   __shared__ int red[8];
   c = static_cast<int>(warp_sum(static_cast<float>(c)));       // counts < 2^24: exact
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = c;
@@ -121,9 +125,10 @@ __global__ void moe_offsets_kernel(const int* __restrict__ counts, int experts,
 // slot[i] = offsets[e] + rank of assignment i among the assignments of expert e (stable in
 // (row, k) order); also copies the quantised row and its scale into that slot.
 __global__ void __launch_bounds__(256) moe_dispatch_kernel(
-    const int* __restrict__ ids, int assigns, int top_k, const int* __restrict__ offsets,
-    const int8_t* __restrict__ q8, const float* __restrict__ scale, int K,
-    int* __restrict__ slots, int8_t* __restrict__ q8_sorted, float* __restrict__ scale_sorted) {
+    const int* __restrict__ ids, int assigns, int top_k, int base_expert,
+    const int* __restrict__ offsets, const int8_t* __restrict__ q8,
+    const float* __restrict__ scale, int K, int* __restrict__ slots,
+    int8_t* __restrict__ q8_sorted, float* __restrict__ scale_sorted) {
   const int e = blockIdx.x;
   __shared__ int wsum[8];
   __shared__ int base;
@@ -132,7 +137,7 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int start = 0; start < assigns; start += 256) {
     const int i = start + threadIdx.x;
-    const bool mine = i < assigns && ids[i] == e;
+    const bool mine = i < assigns && ids[i] == e + base_expert;
     const unsigned ballot = __ballot_sync(0xffffffffu, mine);
     if (lane == 0) wsum[warp] = __popc(ballot);
     __syncthreads();
@@ -159,13 +164,15 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(
 __global__ void __launch_bounds__(256) moe_combine_kernel(
     const __half* __restrict__ expert_out, const int* __restrict__ slots,
     const float* __restrict__ probs, int top_k, const __half* __restrict__ shared_out,
-    const float* __restrict__ shared_gate, __half* __restrict__ out, int hidden) {
+    const float* __restrict__ shared_gate, __half* __restrict__ out, int hidden,
+    const PeerOut peers) {
   const int row = blockIdx.x;
   for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int k = 0; k < top_k; ++k) {
       const float p = probs[row * top_k + k];
       const int slot = slots[row * top_k + k];
+      if (slot < 0) continue;                        // routed to an expert of another rank
       const int4 raw =
           *reinterpret_cast<const int4*>(expert_out + static_cast<size_t>(slot) * hidden + i);
       const __half* h = reinterpret_cast<const __half*>(&raw);
@@ -183,9 +190,18 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(
     __align__(16) __half o[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) o[j] = __float2half_rn(acc[j]);
-    *reinterpret_cast<int4*>(out + static_cast<size_t>(row) * hidden + i) =
-        *reinterpret_cast<const int4*>(o);
+    if (peers.tp == 0) {
+      *reinterpret_cast<int4*>(out + static_cast<size_t>(row) * hidden + i) =
+          *reinterpret_cast<const int4*>(o);
+    } else {
+      // expert-parallel combine: this rank's partial row goes straight into slot [rank] of
+      // every rank's inbox; the consumer norm kernel sums the tp partials
+      const size_t off = (static_cast<size_t>(peers.rank) * peers.rows_cap + row) * hidden + i;
+      for (int d = 0; d < peers.tp; ++d)
+        *reinterpret_cast<int4*>(peers.inbox[d] + off) = *reinterpret_cast<const int4*>(o);
+    }
   }
+  if (peers.tp != 0) peer_signal_done(peers, gridDim.x);
 }
 
 }  // namespace orinfer
@@ -213,10 +229,55 @@ int orinfer_moe_dispatch(const int* ids, int rows, int top_k, int experts, const
   if (rows <= 0) return 0;
   if (K % 16) return -1;
   const int assigns = rows * top_k;
-  moe_count_kernel<<<experts, 256, 0, stream>>>(ids, assigns, counts);
+  moe_count_kernel<<<experts, 256, 0, stream>>>(ids, assigns, 0, counts);
   moe_offsets_kernel<<<1, 32, 0, stream>>>(counts, experts, offsets, tiles, meta, max_tiles);
-  moe_dispatch_kernel<<<experts, 256, 0, stream>>>(ids, assigns, top_k, offsets, q8, scale, K,
+  moe_dispatch_kernel<<<experts, 256, 0, stream>>>(ids, assigns, top_k, 0, offsets, q8, scale, K,
                                                    slots, q8_sorted, scale_sorted);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Expert-parallel dispatch: this rank owns experts [base_expert, base_expert + local_experts);
+// only rows routed there are counted and copied, every other slot is -1.
+int orinfer_moe_dispatch_ep(const int* ids, int rows, int top_k, int base_expert,
+                            int local_experts, const int8_t* q8, const float* scale, int K,
+                            int* counts, int* offsets, int* tiles, int* meta, int max_tiles,
+                            int* slots, int8_t* q8_sorted, float* scale_sorted,
+                            cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (K % 16) return -1;
+  const int assigns = rows * top_k;
+  cudaMemsetAsync(slots, 0xFF, sizeof(int) * assigns, stream);
+  moe_count_kernel<<<local_experts, 256, 0, stream>>>(ids, assigns, base_expert, counts);
+  moe_offsets_kernel<<<1, 32, 0, stream>>>(counts, local_experts, offsets, tiles, meta,
+                                           max_tiles);
+  moe_dispatch_kernel<<<local_experts, 256, 0, stream>>>(ids, assigns, top_k, base_expert,
+                                                         offsets, q8, scale, K, slots, q8_sorted,
+                                                         scale_sorted);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Combine whose result rows are pushed into every rank's inbox (slot [rank]) over NVLink and
+// signalled, instead of being written locally: the all-reduce of the expert-parallel partial
+// sums is completed by the consumer norm kernel.
+int orinfer_moe_combine_peer(const __half* expert_out, const int* slots, const float* probs,
+                             int rows, int top_k, const __half* shared_out,
+                             const float* shared_gate, const OrinferPeerOut* peers, int hidden,
+                             cudaStream_t stream) {
+  if (rows <= 0 || peers == nullptr) return -1;
+  if (hidden % 8 || rows > peers->rows_cap) return -1;
+  if (peers->tp < 1 || peers->tp > TP_MAX) return -1;
+  PeerOut po;
+  for (int i = 0; i < TP_MAX; ++i) {
+    po.inbox[i] = reinterpret_cast<__half*>(peers->inbox[i]);
+    po.flag[i] = peers->flag[i];
+  }
+  po.sent = peers->sent;
+  po.ticket = peers->ticket;
+  po.tp = peers->tp;
+  po.rank = peers->rank;
+  po.rows_cap = peers->rows_cap;
+  moe_combine_kernel<<<rows, 256, 0, stream>>>(expert_out, slots, probs, top_k, shared_out,
+                                               shared_gate, nullptr, hidden, po);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -226,7 +287,7 @@ int orinfer_moe_combine(const __half* expert_out, const int* slots, const float*
   if (rows <= 0) return 0;
   if (hidden % 8) return -1;
   moe_combine_kernel<<<rows, 256, 0, stream>>>(expert_out, slots, probs, top_k, shared_out,
-                                               shared_gate, out, hidden);
+                                               shared_gate, out, hidden, PeerOut{});
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -306,7 +306,7 @@ class ModelRunner:
         q8, s8 = self._prep(x, lw.post_norm, bank_up.signs, rows, y_out=y16)
         F.router_topk(y16, lw.router, cfg.experts, cfg.top_k, renorm=cfg.renormalize, rows=rows,
                       ids=sc.ids, probs=sc.probs, gate=sc.gate)
-        F.moe_dispatch(sc.ids, q8, s8, cfg.experts, sc, rows)
+        F.moe_dispatch(sc.ids, q8, s8, cfg.experts, sc, rows, bank_up.base, bank_up.experts)
         total = rows * cfg.top_k
         F.qgemm_grouped(sc.q8, sc.scale, bank_up.codes, bank_up.scale, bank_up.fmt, 2 * f,
                         sc.gate_up, sc, total)
@@ -323,9 +323,14 @@ class ModelRunner:
                                   rows=rows, q_out=ws.q8[fs], scale_out=ws.scale)
             shared = self._linear(lw.shared_down, q8s, s8s, rows, ws.shared_out)
         has_gate = lw.router.shape[0] == cfg.experts + 1
-        F.moe_combine(sc.down, sc.slots, sc.probs, shared, sc.gate if has_gate else None,
-                      ws.hidden, rows)
-        return ws.hidden
+        return self._moe_combine(sc, shared, sc.gate if has_gate and shared is not None else None,
+                                 rows)
+
+    def _moe_combine(self, sc, shared, gate, rows: int):
+        """Weighted sum of the routed expert rows (+ gated shared expert) into the hidden
+        buffer; expert-parallel runners complete it across ranks."""
+        F.moe_combine(sc.down, sc.slots, sc.probs, shared, gate, self.ws.hidden, rows)
+        return self._reduce(self.ws.hidden, rows)
 
     def logits(self, p: Packet, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """fp32 logits [n_sel, vocab] of the selected rows (final norm + W8 head)."""

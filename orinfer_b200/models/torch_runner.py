@@ -143,7 +143,7 @@ class TorchRunner:
             y = R.rms_norm(resid, lw.post_norm, cfg.eps, zc)
             if cfg.experts:
                 from ..ref.cpu_forward import moe_ffn
-                x = moe_ffn(cfg, lw, y, True)
+                x = self._reduce(moe_ffn(cfg, lw, y, True))
             else:
                 x = self._ffn(lw, y)
         return x, resid

@@ -94,15 +94,21 @@ class ExpertBank:
     scale: torch.Tensor               # fp16 [E, N]
     signs: Optional[torch.Tensor]
     dense: Optional[torch.Tensor] = None
+    base: int = 0                     # global id of local expert 0 (expert parallelism)
 
     def expert(self, e: int) -> QLinear:
+        """Projection of GLOBAL expert ``e`` (must be one of this bank's experts)."""
+        e -= self.base
         return QLinear(self.fmt, self.n, self.k, self.codes[e], self.scale[e], self.signs,
                        None if self.dense is None else self.dense[e])
+
+    def owns(self, e: int) -> bool:
+        return self.base <= e < self.base + self.experts
 
     def to(self, device) -> "ExpertBank":
         mv = lambda t: None if t is None else t.to(device)
         return ExpertBank(self.fmt, self.experts, self.n, self.k, mv(self.codes), mv(self.scale),
-                          mv(self.signs), self.dense)
+                          mv(self.signs), self.dense, self.base)
 
 
 @dataclass

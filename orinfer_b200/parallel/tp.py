@@ -21,7 +21,7 @@ from typing import List, Optional, Tuple
 import torch
 
 from ..config import ModelConfig
-from ..models.weights import LayerWeights, ModelWeights, MtpWeights, QLinear
+from ..models.weights import ExpertBank, LayerWeights, ModelWeights, MtpWeights, QLinear
 
 
 def split_blocks(total_blocks: int, world: int) -> List[Tuple[int, int]]:
@@ -102,24 +102,83 @@ def _shard_ffn(lw: LayerWeights, lay: TPLayout, dev) -> None:
     lw.down = _cols(lw.down, lo, hi)
 
 
+def _shard_gdn(cfg: ModelConfig, lw: LayerWeights, lay: TPLayout, dev) -> None:
+    """Linear-attention heads are split over the ranks (no collective inside the mixer):
+    q|k|v|z projection rows, gate rows, convolution channels and per-head scalars follow
+    their heads; the output projection is row-parallel."""
+    w, r = lay.world, lay.rank
+    hk, hv, d = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim
+    if hk % w or hv % w or (hv // w * d) % 128:
+        raise ValueError(f"GDN heads ({hk} key, {hv} value) do not split over {w} ranks")
+    lk, lv = hk // w, hv // w
+    ar = lambda a, n: torch.arange(a, a + n, device=dev)
+    q_i = ar(r * lk * d, lk * d)
+    k_i = ar(hk * d + r * lk * d, lk * d)
+    v_i = ar(2 * hk * d + r * lv * d, lv * d)
+    z_i = ar(2 * hk * d + hv * d + r * lv * d, lv * d)
+    lw.gdn_qkvz = _rows(lw.gdn_qkvz, torch.cat([q_i, k_i, v_i, z_i]))
+    conv_i = torch.cat([q_i, k_i, v_i]).to(lw.gdn_conv.device)
+    lw.gdn_conv = lw.gdn_conv.index_select(0, conv_i).contiguous()
+    heads = torch.arange(r * lv, (r + 1) * lv, device=lw.gdn_ab.device)
+    lw.gdn_ab = lw.gdn_ab.index_select(0, torch.cat([heads, hv + heads])).contiguous()
+    lw.gdn_a_log = lw.gdn_a_log[r * lv:(r + 1) * lv].contiguous()
+    lw.gdn_dt_bias = lw.gdn_dt_bias[r * lv:(r + 1) * lv].contiguous()
+    lw.gdn_out = _cols(lw.gdn_out, r * lv * d, (r + 1) * lv * d)
+
+
+def _slice_bank(bank: ExpertBank, lo: int, hi: int) -> ExpertBank:
+    dense = None if bank.dense is None else bank.dense[lo:hi]
+    return ExpertBank(bank.fmt, hi - lo, bank.n, bank.k, bank.codes[lo:hi].contiguous(),
+                      bank.scale[lo:hi].contiguous(), bank.signs, dense, base=lo)
+
+
+def _shard_moe(cfg: ModelConfig, lw: LayerWeights, layer: int, lay: TPLayout, dev) -> None:
+    """Expert parallelism: a contiguous range of experts per rank; tokens and the router stay
+    replicated, so every rank computes its own experts' share of each token and the partial
+    sums meet in the all-reduce that follows (the reference's TP8 plans do the same:
+    python/orinfer_build/models/deepseek_v41/build.py:1199-1226,1355-1364).  The shared expert
+    is split like a dense FFN when its width allows, else whole layers alternate owners."""
+    w, r = lay.world, lay.rank
+    lo, hi = split_blocks(cfg.experts, w)[r]
+    lw.expert_gate_up = _slice_bank(lw.expert_gate_up, lo, hi)
+    lw.expert_down = _slice_bank(lw.expert_down, lo, hi)
+    if lw.shared_gate_up is not None:
+        f = lw.shared_gate_up.n // 2
+        if (f // 128) % w == 0:
+            a, b = split_blocks(f // 128, w)[r]
+            a, b = a * 128, b * 128
+            idx = torch.cat([torch.arange(a, b, device=dev), torch.arange(f + a, f + b, device=dev)])
+            lw.shared_gate_up = _rows(lw.shared_gate_up, idx)
+            lw.shared_down = _cols(lw.shared_down, a, b)
+        elif layer % w != r:
+            lw.shared_gate_up = lw.shared_down = None
+
+
 def shard_model(weights: ModelWeights, rank: int, world: int) -> ModelWeights:
     """Returns this rank's shard; ``weights.config`` becomes the *local* geometry
-    (local head counts, local FFN width) while ``vocab`` stays global."""
+    (local head counts, local FFN width) while ``vocab`` and the expert count stay global."""
     cfg = weights.config
-    if cfg.arch != "dense":
-        raise NotImplementedError("tensor parallelism is implemented for dense decoders")
     lay = layout(cfg, rank, world)
     dev = weights.embed_q.device
     layers = []
-    for lw in weights.layers:
+    for i, lw in enumerate(weights.layers):
         lw = dataclasses.replace(lw)
-        _shard_attention(cfg, lw, lay, dev)
-        _shard_ffn(lw, lay, dev)
+        if lw.kind == "attn":
+            _shard_attention(cfg, lw, lay, dev)
+        else:
+            _shard_gdn(cfg, lw, lay, dev)
+        if cfg.experts:
+            _shard_moe(cfg, lw, i, lay, dev)
+        else:
+            _shard_ffn(lw, lay, dev)
         layers.append(lw)
     v0, v1 = lay.vocab
     head = _rows(weights.head, torch.arange(v0, v1, device=dev))
     local = dataclasses.replace(cfg, q_heads=lay.q_heads, kv_heads=lay.kv_heads,
-                                ffn=lay.ffn[1] - lay.ffn[0], mtp_layers=0)
+                                ffn=(lay.ffn[1] - lay.ffn[0]) if cfg.ffn else cfg.ffn,
+                                gdn_k_heads=cfg.gdn_k_heads // world if cfg.gdn_k_heads else 0,
+                                gdn_v_heads=cfg.gdn_v_heads // world if cfg.gdn_v_heads else 0,
+                                mtp_layers=0)
     out = ModelWeights(local, weights.embed_q, weights.embed_s, layers, weights.final_norm, head,
                        weights.signs, None, weights.embed_dense)
     out.tp = lay                       # type: ignore[attr-defined]

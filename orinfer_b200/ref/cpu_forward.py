@@ -130,6 +130,8 @@ def moe_ffn(cfg: ModelConfig, lw: LayerWeights, y: torch.Tensor, quantized: bool
     for tok in range(y.shape[0]):
         for j in range(cfg.top_k):
             ex = int(order[tok, j])
+            if not lw.expert_gate_up.owns(ex):        # another rank's expert
+                continue
             gu_l, dn_l = lw.expert_gate_up.expert(ex), lw.expert_down.expert(ex)
             row = y[tok:tok + 1]
             if quantized:

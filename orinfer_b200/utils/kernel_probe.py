@@ -118,6 +118,28 @@ def attn(args, dev):
                       "frac_f16_peak": ops / t / flops, "peaks": tag}))
 
 
+def gdn(args, dev):
+    """Sequential gated-delta scan: ``segs`` requests of ``tokens`` rows each."""
+    hk, hv, d, n, segs = args.hk, args.hv, args.d, args.tokens, args.segs
+    rows = n * segs
+    conv_dim = (2 * hk + hv) * d
+    qkv = (torch.randn(rows, conv_dim, device=dev) * 0.1).half()
+    ab = torch.randn(rows, 2 * hv, device=dev)
+    a_log, dt = torch.zeros(hv, device=dev), torch.zeros(hv, device=dev)
+    state = torch.zeros(segs, hv, d, d, device=dev)
+    seg = torch.tensor([[i * n, n, 0, 0] for i in range(segs)], dtype=torch.int32, device=dev)
+    slot = torch.arange(segs, dtype=torch.int32, device=dev).repeat_interleave(n)
+    pos = torch.arange(1, n + 1, dtype=torch.int32, device=dev).repeat(segs)
+    out = torch.empty(rows, hv, d, device=dev)
+    t = timed(lambda i: F.gdn_scan(qkv, ab, a_log, dt, seg, segs, slot, pos, hk, hv, d, state,
+                                   out=out), args.iters)
+    bw, _, tag = peaks()
+    moved = 2.0 * segs * hv * d * d * 4 + rows * (conv_dim * 2 + hv * d * 4)
+    print(json.dumps({"kernel": "gdn_scan", "tokens": n, "segments": segs, "hk": hk, "hv": hv,
+                      "d": d, "us": t * 1e6, "us_per_token": t * 1e6 / n,
+                      "gbs": moved / t / 1e9, "frac_hbm": moved / t / bw, "peaks": tag}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--graph", action="store_true",
@@ -137,12 +159,19 @@ def main():
     a.add_argument("--kvh", type=int, default=8)
     a.add_argument("--d", type=int, default=128)
     a.add_argument("--iters", type=int, default=10)
+    r = sub.add_parser("gdn")
+    r.add_argument("--tokens", type=int, default=1)
+    r.add_argument("--segs", type=int, default=128)
+    r.add_argument("--hk", type=int, default=16)
+    r.add_argument("--hv", type=int, default=32)
+    r.add_argument("--d", type=int, default=128)
+    r.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
     global GRAPH
     GRAPH = args.graph
     dev = torch.device("cuda:0")
     native.init()
-    (gemm if args.cmd == "gemm" else attn)(args, dev)
+    {"gemm": gemm, "attn": attn, "gdn": gdn}[args.cmd](args, dev)
     st = native.read_status()
     if st:
         raise SystemExit(f"kernel status {st:#x}")
