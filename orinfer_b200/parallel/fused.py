@@ -130,6 +130,8 @@ def _setup_lib():
     lib.orinfer_act_prep_inbox.argtypes = [ctypes.POINTER(_Inbox), P, P, P, P, P, P, I, I,
                                            ctypes.c_float, I, P]
     lib.orinfer_act_prep_inbox.restype = I
+    lib.orinfer_moe_combine_peer.argtypes = [P, P, P, I, I, P, P, ctypes.POINTER(_PeerOut), I, P]
+    lib.orinfer_moe_combine_peer.restype = I
     return lib
 
 
@@ -142,7 +144,21 @@ class FusedTPRunner(TPRunner):
         self.lib = _setup_lib()
         self.mem = PeerMemory(self.cfg.hidden, max_rows, group, self.device)
 
+    _SLOT = {"o": "o", "gdn_out": "o", "down": "down"}
+
+    def _moe_combine(self, sc, shared, gate, rows: int):
+        """Expert-parallel combine fused with the scatter half of the all-reduce: the kernel
+        that sums this rank's expert rows stores the partial row into every peer's inbox."""
+        po = self.mem.peer_out["down"]
+        check(self.lib.orinfer_moe_combine_peer(ptr(sc.down), ptr(sc.slots), ptr(sc.probs), rows,
+                                                sc.probs.shape[1], ptr(shared), ptr(gate),
+                                                ctypes.byref(po), self.cfg.hidden, stream()),
+              "moe_combine_peer")
+        count_launches(1)
+        return "down"
+
     def _row_parallel(self, name: str, lin: QLinear, q8, sc, rows: int):
+        name = self._SLOT[name]
         po = self.mem.peer_out[name]
         check(self.lib.orinfer_qgemm_peer(FMT[lin.fmt], ptr(q8), ptr(sc), ptr(lin.codes),
                                           ptr(lin.scale), ctypes.byref(po), rows, lin.n, lin.k, 0,

@@ -347,3 +347,36 @@ def test_moe_dispatch_grouped_gemm_combine(cuda, fmt):
     F.moe_combine(out, sc.slots, probs, None, None, hidden_out, m)
     ref = (out[slots].float() * probs[..., None]).sum(1)
     assert torch.allclose(hidden_out.float(), ref, atol=2e-2, rtol=2e-3)
+
+
+def test_moe_expert_parallel_partials_sum_to_full(cuda):
+    """Two expert-parallel halves (experts [0,4) and [4,8)): each dispatches only its own
+    rows (other slots -1), and their combined partial sums equal the single-rank result."""
+    from orinfer_b200.ops import functional as F
+    g = torch.Generator().manual_seed(12)
+    m, h, n, experts, top_k = 200, 256, 256, 8, 2
+    ids = torch.stack([torch.randperm(experts, generator=g)[:top_k] for _ in range(m)]) \
+        .to(torch.int32).to(cuda)
+    probs = torch.rand(m, top_k, generator=g).to(cuda)
+    q8 = torch.randint(-127, 128, (m, h), generator=g, dtype=torch.int8).to(cuda)
+    sa = (torch.rand(m, generator=g) * 0.05 + 1e-3).to(cuda)
+    banks = [_rand_weight("q4", n, h, cuda, seed=200 + e) for e in range(experts)]
+    codes = torch.stack([b[0] for b in banks]).contiguous()
+    wscale = torch.stack([b[1] for b in banks]).contiguous()
+
+    def run(base, local):
+        sc = F.MoeScratch(m, top_k, experts, h, n // 2, cuda)
+        F.moe_dispatch(ids, q8, sa, experts, sc, m, base, local)
+        out = torch.zeros(m * top_k, n, dtype=torch.float16, device=cuda)
+        F.qgemm_grouped(sc.q8, sc.scale, codes[base:base + local].contiguous(),
+                        wscale[base:base + local].contiguous(), "q4", n, out, sc, m * top_k)
+        res = torch.zeros(m, n, dtype=torch.float16, device=cuda)
+        F.moe_combine(out, sc.slots, probs, None, None, res, m)
+        torch.cuda.synchronize()
+        return res.float(), sc.slots.view(m, top_k).clone()
+
+    full, _ = run(0, experts)
+    lo, slots_lo = run(0, 4)
+    hi, slots_hi = run(4, 4)
+    assert torch.equal(slots_lo < 0, ids >= 4) and torch.equal(slots_hi < 0, ids < 4)
+    assert torch.allclose(lo + hi, full, atol=3e-2, rtol=3e-3)

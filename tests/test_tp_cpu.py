@@ -11,7 +11,7 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, preset):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -21,10 +21,15 @@ def _worker(rank, world, port, out_dir):
     from orinfer_b200.models.weights import random_model
     from orinfer_b200.parallel.tp import shard_model
     from orinfer_b200.parallel.tp_runner import TPTorchRunner
-    cfg = PRESETS["tiny"]
+    cfg = PRESETS[preset]
     full = random_model(cfg, seed=0)
     shard = shard_model(full, rank, world)
-    assert shard.config.q_heads == cfg.q_heads // world and shard.config.ffn == cfg.ffn // world
+    assert shard.config.q_heads == cfg.q_heads // world
+    if cfg.experts:
+        assert shard.layers[0].expert_gate_up.experts == cfg.experts // world
+        assert shard.layers[0].expert_gate_up.base == rank * (cfg.experts // world)
+    else:
+        assert shard.config.ffn == cfg.ffn // world
     runner = TPTorchRunner(shard, KVPool.allocate(shard.config, 4, "cpu"), 64)
     g = torch.Generator().manual_seed(1)
     ids = torch.randint(0, cfg.vocab, (24,), generator=g, dtype=torch.int32)
@@ -35,16 +40,19 @@ def _worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-def test_tp2_matches_unsharded(tmp_path):
+@pytest.mark.parametrize("preset", ["tiny", "tiny-moe", "tiny-hybrid"])
+def test_tp2_matches_unsharded(tmp_path, preset):
+    """Dense: Megatron sharding.  MoE: experts split over the ranks (expert parallelism with
+    replicated tokens).  Hybrid: linear-attention heads split over the ranks."""
     from orinfer_b200.config import PRESETS
     from orinfer_b200.models.weights import random_model
     from orinfer_b200.ref import cpu_forward as ref
     port = 29500 + os.getpid() % 2000
-    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, str(tmp_path), preset), nprocs=2, join=True)
     r0 = torch.load(tmp_path / "r0.pt")
     r1 = torch.load(tmp_path / "r1.pt")
     assert torch.equal(r0["logits"], r1["logits"]) and torch.equal(r0["tok"], r1["tok"])
-    cfg = PRESETS["tiny"]
+    cfg = PRESETS[preset]
     full = random_model(cfg, seed=0)
     g = torch.Generator().manual_seed(1)
     ids = torch.randint(0, cfg.vocab, (24,), generator=g, dtype=torch.int32)

@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, preset):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -28,7 +28,7 @@ def _worker(rank, world, port, out_dir):
     from orinfer_b200.parallel.tp import shard_model
     from orinfer_b200.parallel.tp_runner import TPRunner
     native.init()
-    cfg = PRESETS["tiny"]
+    cfg = PRESETS[preset]
     full = random_model(cfg, seed=0).to(dev)
     shard = shard_model(full, rank, world)
     t = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
@@ -84,9 +84,9 @@ def _worker(rank, world, port, out_dir):
     os._exit(0)          # skip communicator teardown under live captured graphs
 
 
-def _check(tmp_path, world):
+def _check(tmp_path, world, preset="tiny"):
     port = 29600 + os.getpid() % 1000 + world
-    ctx = mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=False)
+    ctx = mp.spawn(_worker, args=(world, port, str(tmp_path), preset), nprocs=world, join=False)
     deadline = time.time() + 240
     while not ctx.join(timeout=5):
         if time.time() > deadline:                 # never leave ranks behind a hung test
@@ -103,11 +103,18 @@ def _check(tmp_path, world):
     assert cos > 0.995, cos
 
 
-def test_fused_tp_world1(cuda, tmp_path):
-    _check(tmp_path, 1)
+PRESET_NAMES = ["tiny", "tiny-moe", "tiny-hybrid"]
 
 
-def test_fused_tp_world2(cuda, tmp_path):
+@pytest.mark.parametrize("preset", PRESET_NAMES)
+def test_fused_tp_world1(cuda, tmp_path, preset):
+    _check(tmp_path, 1, preset)
+
+
+@pytest.mark.parametrize("preset", PRESET_NAMES)
+def test_fused_tp_world2(cuda, tmp_path, preset):
+    """Dense: tensor parallel.  MoE: expert parallel with the combine pushing partial rows to
+    the peers.  Hybrid: linear-attention heads split over the ranks."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    _check(tmp_path, 2)
+    _check(tmp_path, 2, preset)
