@@ -26,7 +26,27 @@ typedef struct OrinferPeerOut {
   int* sent;                   // local sequence counter (device memory)
   unsigned int* ticket;        // local CTA counter (device memory, zero)
   int tp, rank, rows_cap;
+  int rows_per;                // 0: push every row to every rank (all-reduce);
+                               // > 0: row m only to rank m / rows_per (reduce-scatter)
 } OrinferPeerOut;
+
+// Sequence-parallel all-gather by push (see tp_comm.cuh).
+typedef struct OrinferAgOut {
+  void* q[8];                  // every rank's activation buffer: int8 [rows_cap][K]
+  float* scale[8];             // every rank's row scales: fp32 [rows_cap]
+  int* flag[8];                // every rank's all-gather flags: int32 [tp]
+  int* sent;                   // local sequence counter (device memory)
+  unsigned int* ticket;        // local CTA counter (device memory, zero)
+  int tp, rank, rows_per;
+} OrinferAgOut;
+
+typedef struct OrinferAgIn {
+  const int* flag;             // local all-gather flags
+  const int* sent;             // local sequence counter of the producing norm kernel
+  int tp, rows_per;
+} OrinferAgIn;
+
+
 
 typedef struct OrinferInbox {
   const void* inbox;           // local inbox: fp16 [tp][rows_cap][n]
@@ -35,6 +55,21 @@ typedef struct OrinferInbox {
   unsigned int* ticket;        // local CTA counter (device memory, zero)
   int tp, rows_cap;
 } OrinferInbox;
+
+// Owner rows [rank*rows_per, ...) only: sum the tp partial rows of the inbox, add the
+// residual, normalise, rotate, quantise, store the INT8 row + scale into every rank's
+// activation buffer and publish the all-gather flag.
+int orinfer_act_prep_sp(const OrinferInbox* inbox, const OrinferAgOut* ag, float* resid,
+                        const __half* norm_w, const int8_t* signs, int rows, int K, float eps,
+                        int zero_centered, cudaStream_t stream);
+// Column-parallel GEMM whose A operand (and row scales) is the all-gathered activation
+// buffer: waits per M tile for the source ranks' flags before loading.
+int orinfer_qgemm_ag(int fmt, const int8_t* a, const float* a_scale, const void* w,
+                     const __half* w_scale, void* out, const OrinferAgIn* ag, int M, int N, int K,
+                     int out_f32, cudaStream_t stream);
+// Waits (bounded) for every source of the current all-gather; later kernels on the stream
+// may then read the activation buffer with ordinary loads.
+int orinfer_ag_wait(const OrinferAgIn* ag, int rows, cudaStream_t stream);
 
 int orinfer_act_prep_inbox(const OrinferInbox* inbox, float* resid, const __half* norm_w,
                            const int8_t* signs, int8_t* q_out, float* scale_out, __half* y_out,

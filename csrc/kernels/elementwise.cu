@@ -55,10 +55,19 @@ template <bool SWIGLU>
 __global__ void __launch_bounds__(256) act_prep_kernel(
     const __half* __restrict__ x, float* __restrict__ resid, const __half* __restrict__ norm_w,
     const int8_t* __restrict__ signs, int8_t* __restrict__ q_out, float* __restrict__ scale_out,
-    __half* __restrict__ y_out, int K, float eps, int zero_centered, InboxIn in, int* status) {
+    __half* __restrict__ y_out, int K, float eps, int zero_centered, InboxIn in, int* status,
+    AgOut ag, int rows) {
   extern __shared__ float rowbuf[];
   __shared__ float red[32];
-  const int row = blockIdx.x, tid = threadIdx.x;
+  const int tid = threadIdx.x;
+  // sequence-parallel form: this rank handles only the rows it owns and pushes the result
+  const bool sp = !SWIGLU && ag.tp > 0;
+  const int row = sp ? ag.rank * ag.rows_per + blockIdx.x : blockIdx.x;
+  if (sp && row >= rows) {                 // tail of the last owner: nothing to do but count
+    inbox_consumed(in, gridDim.x);
+    ag_signal_done(ag, gridDim.x);
+    return;
+  }
   float sumsq = 0.f;
   if (SWIGLU) {
     const __half* g = x + static_cast<size_t>(row) * 2 * K;
@@ -179,6 +188,21 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
   }
   amax = block_reduce(amax, red, true);
   const float scale = a8_scale(amax);
+  if (sp) {
+    // all-gather by push: the INT8 row and its scale go to every rank's activation buffer
+    if (tid < ag.tp) ag.scale[tid][row] = scale;
+    for (int i = tid * 16; i < K; i += blockDim.x * 16) {
+      __align__(16) signed char c[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) c[j] = static_cast<signed char>(a8_code(rowbuf[i + j], scale));
+      for (int d = 0; d < ag.tp; ++d)
+        *reinterpret_cast<int4*>(ag.q[d] + static_cast<size_t>(row) * K + i) =
+            *reinterpret_cast<const int4*>(c);
+    }
+    inbox_consumed(in, gridDim.x);
+    ag_signal_done(ag, gridDim.x);
+    return;
+  }
   if (tid == 0) scale_out[row] = scale;
   int8_t* qr = q_out + static_cast<size_t>(row) * K;
   for (int i = tid * 4; i < K; i += blockDim.x * 4) {
@@ -190,6 +214,10 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
     *reinterpret_cast<char4*>(qr + i) = c;
   }
   if (!SWIGLU && in.inbox != nullptr) inbox_consumed(in, gridDim.x);
+}
+
+__global__ void ag_wait_kernel(AgIn in, int rows, int* status) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) ag_wait(in, 0, rows - 1, status);
 }
 
 // ------------------------------------------------------------------ RoPE tables
@@ -335,7 +363,7 @@ using namespace orinfer;
 static int act_prep_launch(const __half* x, float* resid, const __half* norm_w, const int8_t* signs,
                            int8_t* q_out, float* scale_out, __half* y_out, int rows, int K,
                            float eps, int zero_centered, int swiglu, InboxIn in,
-                           cudaStream_t stream);
+                           cudaStream_t stream, AgOut ag = AgOut{});
 
 extern "C" {
 
@@ -373,12 +401,49 @@ int orinfer_act_prep_inbox(const OrinferInbox* inbox, float* resid, const __half
                          zero_centered, 0, in, stream);
 }
 
+int orinfer_act_prep_sp(const OrinferInbox* inbox, const OrinferAgOut* agp, float* resid,
+                        const __half* norm_w, const int8_t* signs, int rows, int K, float eps,
+                        int zero_centered, cudaStream_t stream) {
+  if (inbox == nullptr || agp == nullptr || inbox->tp < 1 || inbox->tp > TP_MAX ||
+      agp->tp != inbox->tp || rows > inbox->rows_cap || agp->rows_per < 1 || K % 16 ||
+      static_cast<long long>(agp->rows_per) * agp->tp < rows)
+    return -1;
+  InboxIn in;
+  in.inbox = reinterpret_cast<const __half*>(inbox->inbox);
+  in.flag = inbox->flag;
+  in.seen = inbox->seen;
+  in.ticket = inbox->ticket;
+  in.tp = inbox->tp;
+  in.rows_cap = inbox->rows_cap;
+  AgOut ag;
+  for (int i = 0; i < TP_MAX; ++i) {
+    ag.q[i] = reinterpret_cast<int8_t*>(agp->q[i]);
+    ag.scale[i] = agp->scale[i];
+    ag.flag[i] = agp->flag[i];
+  }
+  ag.sent = agp->sent;
+  ag.ticket = agp->ticket;
+  ag.tp = agp->tp;
+  ag.rank = agp->rank;
+  ag.rows_per = agp->rows_per;
+  return act_prep_launch(nullptr, resid, norm_w, signs, nullptr, nullptr, nullptr, rows, K, eps,
+                         zero_centered, 0, in, stream, ag);
+}
+
+int orinfer_ag_wait(const OrinferAgIn* agp, int rows, cudaStream_t stream) {
+  if (agp == nullptr || agp->tp < 1 || agp->tp > TP_MAX || agp->rows_per < 1 || rows < 1) return -1;
+  if (runtime_ensure_init() != cudaSuccess) return -2;
+  AgIn in{agp->flag, agp->sent, agp->tp, agp->rows_per};
+  ag_wait_kernel<<<1, 32, 0, stream>>>(in, rows, runtime_status_ptr());
+  return static_cast<int>(cudaGetLastError());
+}
+
 }  // extern "C"
 
 static int act_prep_launch(const __half* x, float* resid, const __half* norm_w, const int8_t* signs,
                            int8_t* q_out, float* scale_out, __half* y_out, int rows, int K,
                            float eps, int zero_centered, int swiglu, InboxIn in,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, AgOut ag) {
   if (rows <= 0) return 0;
   if (runtime_ensure_init() != cudaSuccess) return -2;
   int* status = runtime_status_ptr();
@@ -396,10 +461,11 @@ static int act_prep_launch(const __half* x, float* resid, const __half* norm_w, 
   if (swiglu)
     act_prep_kernel<true><<<rows, 256, smem, stream>>>(x, nullptr, nullptr, signs, q_out,
                                                        scale_out, y_out, K, eps, zero_centered,
-                                                       in, status);
+                                                       in, status, AgOut{}, rows);
   else
-    act_prep_kernel<false><<<rows, 256, smem, stream>>>(x, resid, norm_w, signs, q_out, scale_out,
-                                                        y_out, K, eps, zero_centered, in, status);
+    act_prep_kernel<false><<<ag.tp > 0 ? ag.rows_per : rows, 256, smem, stream>>>(
+        x, resid, norm_w, signs, q_out, scale_out, y_out, K, eps, zero_centered, in, status, ag,
+        rows);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
     const unsigned char* __restrict__ w, const float* __restrict__ a_scale,
     const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K,
-    const E8pTables* __restrict__ tables, int* status, PeerOut po, GroupDesc grp) {
+    const E8pTables* __restrict__ tables, int* status, PeerOut po, GroupDesc grp, AgIn ag) {
   using L = Layout<FMT, MT>;
   constexpr int STAGES = L::STAGES;
   extern __shared__ unsigned char smem_raw[];
@@ -117,7 +117,14 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   if (warp == 0) {
     if (lane == 0) {
       int issued = 0;
-      for (int kb = 0; kb < kblocks; ++kb) {
+      bool a_ready = true;
+      if (ag.tp > 0) {
+        // all-gather fused into the GEMM: A rows of this M tile were pushed by their owner
+        // ranks; wait for exactly those sources, then order the async-proxy loads after it
+        a_ready = ag_wait(ag, m0, min(m0 + MT * BM, M) - 1, status);
+        fence_proxy_async_all();
+      }
+      for (int kb = 0; a_ready && kb < kblocks; ++kb) {
         const int s = kb % STAGES;
         const uint32_t ph = (kb / STAGES) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, status, STATUS_TMA_WAIT, kb)) break;
@@ -215,7 +222,8 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
 #pragma unroll 1
       for (int mt = 0; mt < MT; ++mt) {
         const int m = m0 + mt * BM + row;
-        const float sa = m < m_limit ? a_scale[m] : 0.f;
+        // gathered row scales were written by peers: read them past L1
+        const float sa = m < m_limit ? (ag.tp > 0 ? __ldcg(a_scale + m) : a_scale[m]) : 0.f;
 #pragma unroll 1
         for (int c0 = part * 32; c0 < part * 32 + 32; c0 += 32) {
           uint32_t r[32];
@@ -238,8 +246,15 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
                   for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
                   const size_t off =
                       (static_cast<size_t>(po.rank) * po.rows_cap + m) * N + n;
-                  for (int d = 0; d < po.tp; ++d)
-                    *reinterpret_cast<int4*>(po.inbox[d] + off) = *reinterpret_cast<const int4*>(h);
+                  if (po.rows_per > 0) {
+                    // reduce-scatter: only the owner of row m receives this partial
+                    *reinterpret_cast<int4*>(po.inbox[min(m / po.rows_per, po.tp - 1)] + off) =
+                        *reinterpret_cast<const int4*>(h);
+                  } else {
+                    for (int d = 0; d < po.tp; ++d)
+                      *reinterpret_cast<int4*>(po.inbox[d] + off) =
+                          *reinterpret_cast<const int4*>(h);
+                  }
                 } else if (OUT_F32) {
                   float* o = reinterpret_cast<float*>(out) + static_cast<size_t>(m) * N + n;
                   *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
@@ -268,7 +283,7 @@ template <int FMT, bool OUT_F32, int MT>
 int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale, void* out,
            int M, int N, int K, cudaStream_t stream, const PeerOut& po,
            const GroupDesc& grp = GroupDesc{nullptr, nullptr, 0, 0}, int experts = 1,
-           int max_tiles = 0) {
+           int max_tiles = 0, const AgIn& ag = AgIn{nullptr, nullptr, 0, 0}) {
   using L = Layout<FMT, MT>;
   CUtensorMap ta, tb;
   if (!make_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BM, BK)) return -3;
@@ -290,22 +305,25 @@ int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w
   dim3 grid((N + BN - 1) / BN, grp.tiles ? max_tiles : (M + BM * MT - 1) / (BM * MT));
   qgemm_tc_kernel<FMT, OUT_F32, MT><<<grid, THREADS, L::TOTAL, stream>>>(
       ta, tb, reinterpret_cast<const unsigned char*>(w), a_scale, w_scale, out, M, N, K,
-      runtime_e8p_tables(), runtime_status_ptr(), po, grp);
+      runtime_e8p_tables(), runtime_status_ptr(), po, grp, ag);
   return static_cast<int>(cudaGetLastError());
 }
 
 template <int FMT>
 int launch_fmt(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale,
                void* out, int M, int N, int K, int out_f32, cudaStream_t stream,
-               const PeerOut& po) {
+               const PeerOut& po, const AgIn& ag = AgIn{nullptr, nullptr, 0, 0}) {
   // two accumulators halve the decode work per MAC, but only pay off once the grid
   // still covers the 148 SMs
   const long ctas2 = static_cast<long>((N + BN - 1) / BN) * ((M + 2 * BM - 1) / (2 * BM));
+  const GroupDesc none{nullptr, nullptr, 0, 0};
   if (M > BM && ctas2 >= 120)
-    return out_f32 ? launch<FMT, true, 2>(a, a_scale, w, w_scale, out, M, N, K, stream, po)
-                   : launch<FMT, false, 2>(a, a_scale, w, w_scale, out, M, N, K, stream, po);
-  return out_f32 ? launch<FMT, true, 1>(a, a_scale, w, w_scale, out, M, N, K, stream, po)
-                 : launch<FMT, false, 1>(a, a_scale, w, w_scale, out, M, N, K, stream, po);
+    return out_f32
+               ? launch<FMT, true, 2>(a, a_scale, w, w_scale, out, M, N, K, stream, po, none, 1, 0, ag)
+               : launch<FMT, false, 2>(a, a_scale, w, w_scale, out, M, N, K, stream, po, none, 1, 0, ag);
+  return out_f32
+             ? launch<FMT, true, 1>(a, a_scale, w, w_scale, out, M, N, K, stream, po, none, 1, 0, ag)
+             : launch<FMT, false, 1>(a, a_scale, w, w_scale, out, M, N, K, stream, po, none, 1, 0, ag);
 }
 
 }  // namespace tc
@@ -364,7 +382,25 @@ extern "C" int orinfer_qgemm_peer(int fmt, const int8_t* a, const float* a_scale
   po.tp = peer->tp;
   po.rank = peer->rank;
   po.rows_cap = peer->rows_cap;
+  po.rows_per = peer->rows_per;
+  if (po.rows_per < 0 || (po.rows_per > 0 && (M <= 8 || force_path == 1))) return -1;
   return qgemm_any(fmt, a, a_scale, w, w_scale, nullptr, M, N, K, 0, force_path, stream, &po);
+}
+
+extern "C" int orinfer_qgemm_ag(int fmt, const int8_t* a, const float* a_scale, const void* w,
+                                const __half* w_scale, void* out, const OrinferAgIn* agp, int M,
+                                int N, int K, int out_f32, cudaStream_t stream) {
+  if (agp == nullptr || agp->tp < 1 || agp->tp > TP_MAX || agp->rows_per < 1) return -1;
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 128 || N % 8 || fmt < 0 || fmt > 2) return -1;
+  if (runtime_ensure_init() != cudaSuccess) return -2;
+  const AgIn ag{agp->flag, agp->sent, agp->tp, agp->rows_per};
+  const PeerOut po{};
+  if (fmt == 0)
+    return tc::launch_fmt<0>(a, a_scale, w, w_scale, out, M, N, K, out_f32, stream, po, ag);
+  if (fmt == 1)
+    return tc::launch_fmt<1>(a, a_scale, w, w_scale, out, M, N, K, out_f32, stream, po, ag);
+  return tc::launch_fmt<2>(a, a_scale, w, w_scale, out, M, N, K, out_f32, stream, po, ag);
 }
 
 // Grouped expert GEMM: rows of `a` are sorted by expert; tile t of the table covers rows

@@ -276,6 +276,7 @@ int orinfer_moe_combine_peer(const __half* expert_out, const int* slots, const f
   po.tp = peers->tp;
   po.rank = peers->rank;
   po.rows_cap = peers->rows_cap;
+  po.rows_per = 0;
   moe_combine_kernel<<<rows, 256, 0, stream>>>(expert_out, slots, probs, top_k, shared_out,
                                                shared_gate, nullptr, hidden, po);
   return static_cast<int>(cudaGetLastError());

@@ -9,6 +9,15 @@
 //     source order (bit-reproducible) with L1-bypassing loads; its last CTA bumps `seen`.
 // Every rank runs the same sequence of fused ops, so the counters stay aligned without
 // any reset, also across CUDA-graph replays (all counters live in device memory).
+//
+// Sequence-parallel form of the same step (prefill packets), bytes over NVLink cut by tp:
+//   reduce-scatter: rows are split into contiguous ranges of `rows_per`; the GEMM epilogue
+//     stores row m only into the inbox of its owner rank m / rows_per;
+//   the owner's norm kernel sums the tp partials of ITS rows, adds its residual slice,
+//     normalises, rotates, quantises and
+//   all-gathers by push: stores the INT8 row + scale into every rank's activation buffer and
+//     publishes a second sequence flag; the next column-parallel GEMM waits (bounded) on the
+//     flags of the source ranks covering its M tile before its first TMA load of A.
 #pragma once
 
 #include "common.cuh"
@@ -23,6 +32,23 @@ struct PeerOut {                 // producer side
   int* sent;                     // local: sequence number of the last completed send
   unsigned int* ticket;          // local: CTA completion counter
   int tp, rank, rows_cap;
+  int rows_per;                  // 0: all-reduce push to every rank; > 0: row m -> rank m / rows_per
+};
+
+struct AgOut {                   // all-gather by push (producer: the owner's norm kernel)
+  int8_t* q[TP_MAX];             // every rank's activation buffer, int8 [rows_cap][K]
+  float* scale[TP_MAX];          // every rank's row scales, fp32 [rows_cap]
+  int* flag[TP_MAX];             // every rank's all-gather flag array, [tp]
+  int* sent;                     // local sequence counter
+  unsigned int* ticket;          // local CTA counter
+  int tp, rank, rows_per;        // tp == 0: not sequence-parallel
+};
+
+struct AgIn {                    // consumer: the column-parallel GEMM
+  const int* flag;               // local all-gather flag array, [tp]
+  const int* sent;               // local counter written by the norm kernel that ran just
+                                 // before on this stream: the sequence number to wait for
+  int tp, rows_per;              // tp == 0: operand is local, no wait
 };
 
 struct InboxIn {                 // consumer side
@@ -44,19 +70,44 @@ __device__ __forceinline__ void st_release_sys(int* p, int v) {
 
 // Called by every thread of a producer CTA after its peer stores.  Returns after the
 // last CTA of the grid has published the new sequence number to all peers.
-__device__ __forceinline__ void peer_signal_done(const PeerOut& po, unsigned int total_ctas) {
+__device__ __forceinline__ void signal_done(int* const* flag, int* sent, unsigned int* ticket,
+                                            int tp, int rank, unsigned int total_ctas) {
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
-    const unsigned int t = atomicAdd(po.ticket, 1u);
+    const unsigned int t = atomicAdd(ticket, 1u);
     if (t == total_ctas - 1) {
-      *po.ticket = 0;
+      *ticket = 0;
       __threadfence_system();
-      const int v = *po.sent + 1;
-      *po.sent = v;
-      for (int d = 0; d < po.tp; ++d) st_release_sys(po.flag[d] + po.rank, v);
+      const int v = *sent + 1;
+      *sent = v;
+      for (int d = 0; d < tp; ++d) st_release_sys(flag[d] + rank, v);
     }
   }
+}
+__device__ __forceinline__ void peer_signal_done(const PeerOut& po, unsigned int total_ctas) {
+  signal_done(po.flag, po.sent, po.ticket, po.tp, po.rank, total_ctas);
+}
+__device__ __forceinline__ void ag_signal_done(const AgOut& ag, unsigned int total_ctas) {
+  signal_done(ag.flag, ag.sent, ag.ticket, ag.tp, ag.rank, total_ctas);
+}
+
+// One thread: wait (bounded) until the source ranks owning rows [m_lo, m_hi] have published
+// the current all-gather; false when a wait ran out.
+__device__ __forceinline__ bool ag_wait(const AgIn& in, int m_lo, int m_hi, int* status) {
+  const int want = *reinterpret_cast<const volatile int*>(in.sent);
+  const int s_hi = min(m_hi / in.rows_per, in.tp - 1);
+  for (int s = m_lo / in.rows_per; s <= s_hi; ++s) {
+    if (ld_acquire_sys(in.flag + s) >= want) continue;
+    const long long start = clock64();
+    while (ld_acquire_sys(in.flag + s) < want) {
+      if (clock64() - start > WAIT_LIMIT_CYCLES) {
+        report_status(status, STATUS_PEER_WAIT, 0x100 | s);
+        return false;
+      }
+    }
+  }
+  return true;
 }
 
 // Thread 0 of a consumer CTA waits for every source; false when a wait ran out.

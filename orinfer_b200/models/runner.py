@@ -334,8 +334,10 @@ class ModelRunner:
 
     def logits(self, p: Packet, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """fp32 logits [n_sel, vocab] of the selected rows (final norm + W8 head)."""
+        return self._head(self.forward_hidden(p), p, out)
+
+    def _head(self, x, p: Packet, out: Optional[torch.Tensor]) -> torch.Tensor:
         cfg, ws = self.cfg, self.ws
-        x = self.forward_hidden(p)
         rows = p.rows
         if p.logit_rows is not None or not isinstance(x, torch.Tensor):
             # final norm over every row (fp16 result), then pick the rows that need logits

@@ -9,6 +9,13 @@ kernel waits (bounded) for the tp sequence flags and sums the tp partial rows in
 source order.  No NCCL call and no separate reduction kernel remains on that path; NCCL
 (``TPRunner``) is kept as the baseline arm and for the tiny head merge.
 
+Prefill packets (``rows >= SP_MIN_ROWS``, dense models) run sequence-parallel instead: the
+GEMM epilogue stores each partial row only into its owner's inbox (reduce-scatter, 1/tp of
+the bytes), the owner's norm kernel reduces, normalises, rotates and quantises ITS rows and
+stores the INT8 rows + scales into every rank's activation buffer (all-gather by push, one
+byte per element), and the following column-parallel GEMM waits per M tile for the source
+ranks it needs before its first TMA load.  The FP32 residual stream stays row-sharded.
+
 Buffers are cudaMalloc'd per rank and mapped into every peer with CUDA IPC handles
 exchanged once at start-up (``csrc/kernels/peer_mem.cu``).  Counters live in device memory, so a
 captured CUDA graph replays the protocol unchanged.  No TMA multicast is used anywhere;
@@ -42,7 +49,29 @@ def enabled() -> bool:
 
 class _PeerOut(ctypes.Structure):
     _fields_ = [("inbox", c_void_p * 8), ("flag", c_void_p * 8), ("sent", c_void_p),
-                ("ticket", c_void_p), ("tp", c_int), ("rank", c_int), ("rows_cap", c_int)]
+                ("ticket", c_void_p), ("tp", c_int), ("rank", c_int), ("rows_cap", c_int),
+                ("rows_per", c_int)]
+
+
+class _AgOut(ctypes.Structure):
+    _fields_ = [("q", c_void_p * 8), ("scale", c_void_p * 8), ("flag", c_void_p * 8),
+                ("sent", c_void_p), ("ticket", c_void_p), ("tp", c_int), ("rank", c_int),
+                ("rows_per", c_int)]
+
+
+class _AgIn(ctypes.Structure):
+    _fields_ = [("flag", c_void_p), ("sent", c_void_p), ("tp", c_int), ("rows_per", c_int)]
+
+
+class _DeviceView:
+    """Exposes a raw device range to torch through the CUDA array interface."""
+
+    def __init__(self, address: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr,
+                                         "data": (address, False), "version": 2}
+
+
+SP_MIN_ROWS = int(os.environ.get("ORINFER_TP_SP_MIN_ROWS", "256"))
 
 
 class _Inbox(ctypes.Structure):
@@ -73,7 +102,10 @@ class PeerMemory:
         inbox_bytes = self.world * rows_cap * hidden * 2
         inbox_bytes = (inbox_bytes + 255) // 256 * 256
         flag_bytes = 256
-        total = len(OPS) * (inbox_bytes + flag_bytes)
+        ag_q_bytes = (rows_cap * hidden + 255) // 256 * 256
+        ag_s_bytes = (rows_cap * 4 + 255) // 256 * 256
+        ag_off = len(OPS) * (inbox_bytes + flag_bytes)
+        total = ag_off + ag_q_bytes + ag_s_bytes + flag_bytes
         self.base = lib.orinfer_peer_alloc(total)
         if not self.base:
             raise native.KernelError(f"cannot allocate {total} bytes of peer memory")
@@ -110,6 +142,22 @@ class PeerMemory:
             ib = _Inbox(bases[self.rank] + off_inbox, bases[self.rank] + off_flag,
                         lp + (4 * i + 2) * 4, lp + (4 * i + 3) * 4, self.world, rows_cap)
             self.peer_out[op], self.inbox[op] = po, ib
+        # all-gather activation buffer (INT8 rows + scales) and its flags
+        ag = _AgOut()
+        for r in range(8):
+            ag.q[r] = bases[r] + ag_off if r < self.world else None
+            ag.scale[r] = bases[r] + ag_off + ag_q_bytes if r < self.world else None
+            ag.flag[r] = bases[r] + ag_off + ag_q_bytes + ag_s_bytes if r < self.world else None
+        ag.sent, ag.ticket = lp + 32 * 4, lp + 33 * 4
+        ag.tp, ag.rank, ag.rows_per = self.world, self.rank, 0
+        self.ag_out = ag
+        mine = bases[self.rank] + ag_off
+        self.ag_in = _AgIn(mine + ag_q_bytes + ag_s_bytes, lp + 32 * 4, self.world, 0)
+        self.ag_q = torch.as_tensor(_DeviceView(mine, (rows_cap, hidden), "|i1"), device=device)
+        self.ag_scale = torch.as_tensor(_DeviceView(mine + ag_q_bytes, (rows_cap,), "<f4"),
+                                        device=device)
+        if self.ag_q.data_ptr() != mine:
+            raise native.KernelError("activation buffer view does not alias peer memory")
         torch.cuda.synchronize()
         dist.barrier(group=group)
 
@@ -132,6 +180,13 @@ def _setup_lib():
     lib.orinfer_act_prep_inbox.restype = I
     lib.orinfer_moe_combine_peer.argtypes = [P, P, P, I, I, P, P, ctypes.POINTER(_PeerOut), I, P]
     lib.orinfer_moe_combine_peer.restype = I
+    lib.orinfer_act_prep_sp.argtypes = [ctypes.POINTER(_Inbox), ctypes.POINTER(_AgOut), P, P, P,
+                                        I, I, ctypes.c_float, I, P]
+    lib.orinfer_act_prep_sp.restype = I
+    lib.orinfer_qgemm_ag.argtypes = [I, P, P, P, P, P, ctypes.POINTER(_AgIn), I, I, I, I, P]
+    lib.orinfer_qgemm_ag.restype = I
+    lib.orinfer_ag_wait.argtypes = [ctypes.POINTER(_AgIn), I, P]
+    lib.orinfer_ag_wait.restype = I
     return lib
 
 
@@ -143,8 +198,20 @@ class FusedTPRunner(TPRunner):
         super().__init__(weights, kv, max_rows, group)
         self.lib = _setup_lib()
         self.mem = PeerMemory(self.cfg.hidden, max_rows, group, self.device)
+        self._sp_rows_per, self._sp_total = 0, 0
 
     _SLOT = {"o": "o", "gdn_out": "o", "down": "down"}
+
+    def forward_hidden(self, p):
+        # sequence-parallel for prefill-sized packets of dense models; decode-sized packets
+        # keep the one-hop all-reduce form (latency, not bytes, is what matters there)
+        cfg = self.cfg
+        self._sp_rows_per = 0
+        if self.world > 1 or os.environ.get("ORINFER_TP_SP_WORLD1") == "1":
+            if p.rows >= SP_MIN_ROWS and not cfg.experts and cfg.arch == "dense":
+                self._sp_rows_per = (p.rows + self.world - 1) // self.world
+        self._sp_total = p.rows
+        return super().forward_hidden(p)
 
     def _moe_combine(self, sc, shared, gate, rows: int):
         """Expert-parallel combine fused with the scatter half of the all-reduce: the kernel
@@ -160,17 +227,30 @@ class FusedTPRunner(TPRunner):
     def _row_parallel(self, name: str, lin: QLinear, q8, sc, rows: int):
         name = self._SLOT[name]
         po = self.mem.peer_out[name]
+        po.rows_per = self._sp_rows_per if rows == self._sp_total else 0
         check(self.lib.orinfer_qgemm_peer(FMT[lin.fmt], ptr(q8), ptr(sc), ptr(lin.codes),
                                           ptr(lin.scale), ctypes.byref(po), rows, lin.n, lin.k, 0,
                                           stream()), "qgemm_peer")
         count_launches(1)
-        return name                         # a pending all-reduce, completed by _prep
+        return (name, po.rows_per)          # a pending reduction, completed by _prep
 
     def _prep(self, x, norm_w, signs, rows: int, y_out=None):
         if isinstance(x, torch.Tensor):
             return super()._prep(x, norm_w, signs, rows, y_out)
         cfg, ws = self.cfg, self.ws
-        ib = self.mem.inbox[x]
+        name, rows_per = x if isinstance(x, tuple) else (x, 0)
+        ib = self.mem.inbox[name]
+        if rows_per:
+            if y_out is not None:
+                raise native.KernelError("sequence-parallel norm has no fp16 output")
+            ag = self.mem.ag_out
+            ag.rows_per = rows_per
+            check(self.lib.orinfer_act_prep_sp(ctypes.byref(ib), ctypes.byref(ag), ptr(ws.resid),
+                                               ptr(norm_w), ptr(signs), rows, cfg.hidden,
+                                               float(cfg.eps), int(cfg.zero_centered_norm),
+                                               stream()), "act_prep_sp")
+            count_launches(1)
+            return self.mem.ag_q, self.mem.ag_scale       # gathered; consumers must wait
         q8, sc = ws.q8[cfg.hidden], ws.scale
         check(self.lib.orinfer_act_prep_inbox(ctypes.byref(ib), ptr(ws.resid), ptr(norm_w),
                                               ptr(signs), ptr(q8), ptr(sc), ptr(y_out), rows,
@@ -179,3 +259,40 @@ class FusedTPRunner(TPRunner):
               "act_prep_inbox")
         count_launches(1)
         return q8, sc
+
+    def _linear(self, lin: QLinear, q8, scale, rows, out, out_f32=False):
+        if q8 is not self.mem.ag_q:
+            return super()._linear(lin, q8, scale, rows, out, out_f32)
+        # all-gather fused into the GEMM: its TMA warp waits for the source ranks of each tile
+        ai = self.mem.ag_in
+        ai.rows_per = self._sp_rows_per
+        check(self.lib.orinfer_qgemm_ag(FMT[lin.fmt], ptr(q8), ptr(scale), ptr(lin.codes),
+                                        ptr(lin.scale), ptr(out), ctypes.byref(ai), rows, lin.n,
+                                        lin.k, int(out_f32), stream()), "qgemm_ag")
+        count_launches(1)
+        return out
+
+    def _head(self, x, p, out):
+        if isinstance(x, torch.Tensor) or not (isinstance(x, tuple) and x[1]):
+            return super()._head(x, p, out)
+        # sequence-parallel: owners normalise + rotate + quantise their rows and push them to
+        # every rank; wait for all sources, pick the rows that need logits, run the local
+        # vocabulary shard of the head
+        head, rows = self.w.head, p.rows
+        q8, sc = self._prep(x, self.w.final_norm, head.signs, rows)
+        ai = self.mem.ag_in
+        ai.rows_per = self._sp_rows_per
+        check(self.lib.orinfer_ag_wait(ctypes.byref(ai), rows, stream()), "ag_wait")
+        count_launches(1)
+        q8, sc = q8[:rows], sc[:rows]
+        if p.logit_rows is not None:
+            q8 = q8.index_select(0, p.logit_rows).contiguous()
+            sc = sc.index_select(0, p.logit_rows).contiguous()
+            rows = p.logit_rows.shape[0]
+        else:
+            q8, sc = q8.clone(), sc.clone()
+        if out is None:
+            out = torch.empty(rows, head.n, dtype=torch.float32, device=self.device)
+        from ..ops import functional as F
+        return F.qgemm(q8, sc, head.codes, head.scale, head.fmt, head.n, out=out, out_f32=True,
+                       rows=rows)
