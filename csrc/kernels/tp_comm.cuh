@@ -72,9 +72,12 @@ __device__ __forceinline__ void st_release_sys(int* p, int v) {
 // last CTA of the grid has published the new sequence number to all peers.
 __device__ __forceinline__ void signal_done(int* const* flag, int* sent, unsigned int* ticket,
                                             int tp, int rank, unsigned int total_ctas) {
-  __threadfence_system();
+  // The barrier orders every thread's peer stores before thread 0; its system-scope fence
+  // is cumulative over them, so one fence per CTA is enough (a fence per thread costs
+  // microseconds on a grid of hundreds of CTAs).
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const unsigned int t = atomicAdd(ticket, 1u);
     if (t == total_ctas - 1) {
       *ticket = 0;
