@@ -167,6 +167,11 @@ int orinfer_gdn_gated_norm(const float* o, const __half* z, int z_stride, const 
                            float eps, int sigmoid_gate, int rows, int hv, int head_dim,
                            __half* y, cudaStream_t stream);
 
+// ---- device top-k / top-p sampler (rows it cannot serve exactly get flag = 1)
+int orinfer_sample_topk(const float* logits, int rows, int vocab, long long row_stride,
+                        const int* top_k, const double* temperature, const double* top_p,
+                        const double* uniform, int* token, int* flag, cudaStream_t stream);
+
 // ---- E8P nearest-codeword encoder: x fp32 [V,8] -> int32 codes [V]
 int orinfer_e8p_encode(const float* x, int* codes, long long vectors, cudaStream_t stream);
 

@@ -63,6 +63,14 @@ class SamplingOptions:
         return bool(lib().orinfer_sampling_is_greedy(ctypes.byref(c)))
 
     @property
+    def device_topk(self) -> bool:
+        """Servable by the device top-k sampler: no host state (penalties, bias, report)."""
+        return (self.temperature >= 1e-5 and 1 <= self.top_k <= 64 and 0.0 < self.top_p <= 1.0
+                and self.presence_penalty == 0.0 and self.frequency_penalty == 0.0
+                and self.repetition_penalty == 1.0 and not self.logit_bias
+                and self.top_logprobs is None)
+
+    @property
     def device_categorical(self) -> bool:
         c, _keep = self._c()
         return bool(lib().orinfer_sampling_device_categorical(ctypes.byref(c)))

@@ -62,6 +62,9 @@ class EngineStatistics:
     batch_inputs_s: float = 0.0
     batch_commit_s: float = 0.0
     evicted_pages: int = 0
+    device_samples: int = 0
+    offloaded_pages: int = 0
+    restored_pages: int = 0
 
     def as_dict(self) -> dict:
         return dict(self.__dict__)
@@ -144,6 +147,12 @@ class Engine:
         self.running: List[Request] = []
         self.prefix = RadixPrefixCache(PAGE_TOKENS) if self.load.prefix_cache_bytes > 0 else None
         self._prefix_nodes: Dict[int, List[int]] = {}
+        self.host_kv = None
+        if self.prefix is not None and self.load.kv_offload_bytes > 0:
+            from .offload import HostKvStore
+            self.host_kv = HostKvStore(self.kv, self.load.kv_offload_bytes)
+            if self.host_kv.slots == 0:
+                self.host_kv = None
         self.stats = EngineStatistics()
         self._graphs: Dict[int, _DecodeGraph] = {}
         self._next_rid = 1
@@ -208,9 +217,51 @@ class Engine:
         short = pages - self.pool.available
         if short <= 0:
             return
+        if self.host_kv is not None:
+            # move the least useful pages to pinned host memory; their nodes stay indexed
+            if self.host_kv.available < short:
+                for h in self.prefix.drop_host(short - self.host_kv.available):
+                    self.host_kv.free(h)
+            victims = self.prefix.evict(min(short, self.host_kv.available), to_host=True)
+            for node, page in victims:
+                self.prefix.set_host(node, self.host_kv.save(page))
+            if victims:
+                self.host_kv.sync()                 # pages are reused right after this
+            self.pool.release([p for _, p in victims])
+            self.stats.evicted_pages += len(victims)
+            self.stats.offloaded_pages += len(victims)
+            short -= len(victims)
+            if short <= 0:
+                return
         victims = self.prefix.evict(short, to_host=False)
         self.pool.release([p for _, p in victims])
         self.stats.evicted_pages += len(victims)
+
+    def _restore_host_pages(self, node_ids: List[int], pages: List[int]) -> int:
+        """Brings the host-resident nodes of a matched prefix back into device pages, in
+        order; returns how many leading nodes are usable (device-resident) afterwards."""
+        for i, (node, page) in enumerate(zip(node_ids, pages)):
+            if page >= 0:
+                continue
+            if self.host_kv is None:
+                return i
+            if self.pool.available == 0:
+                self._reclaim(1)
+            if self.pool.available == 0:
+                return i
+            handle = self.prefix.host_handle(node)
+            if handle < 0:
+                return i
+            new = self.pool.take(1)[0]
+            self.host_kv.load(handle, new)
+            if not self.prefix.restore(node, new):
+                self.pool.release([new])
+                return i
+            self.prefix.set_host(node, -1)
+            self.host_kv.free(handle)
+            pages[i] = new
+            self.stats.restored_pages += 1
+        return len(pages)
 
     def _admit(self) -> None:
         started = time.monotonic()
@@ -224,8 +275,8 @@ class Engine:
             node_ids, pages = [], []
             if self.prefix is not None and req.cache_prompt:
                 node_ids, pages = self.prefix.match(req.prompt, limit_tokens=len(req.prompt) - 1)
-                if any(pg < 0 for pg in pages):              # host-resident tail: not restored here
-                    cut = next(i for i, pg in enumerate(pages) if pg < 0)
+                if any(pg < 0 for pg in pages):              # host-resident nodes: restore or cut
+                    cut = self._restore_host_pages(node_ids, pages)
                     self.prefix.release(node_ids[cut:])
                     node_ids, pages = node_ids[:cut], pages[:cut]
             need = self._pages_needed(req) - len(pages)
@@ -467,10 +518,41 @@ class Engine:
         return tokens, g.logits, order
 
     # ------------------------------------------------------------------ commit
+    def _device_samples(self, order, logits) -> Dict[int, int]:
+        """Rows whose sampling options need no host state are drawn by one launch of the
+        device top-k sampler (same counter-RNG uniform as the host law); only their tokens
+        cross PCIe instead of a full row of logits each."""
+        if not self.on_gpu or logits is None or not logits.is_cuda:
+            return {}
+        rows, reqs, sel = [], [], 0
+        for r, _n, has_logits in order:
+            if not has_logits:
+                continue
+            if (not self._plain(r) and r.constraint is None and not r.want_logprobs
+                    and r.sampling.device_topk):
+                rows.append(sel)
+                reqs.append(r)
+            sel += 1
+        if not rows:
+            return {}
+        from ..ops import functional as F
+        dev = self.device
+        f64 = lambda v: torch.tensor(v, dtype=torch.float64, device=dev)
+        idx = torch.tensor(rows, dtype=torch.int64, device=dev)
+        tok, flag = F.sample_topk(
+            logits.index_select(0, idx).float().contiguous(),
+            torch.tensor([r.sampling.top_k for r in reqs], dtype=torch.int32, device=dev),
+            f64([r.sampling.temperature for r in reqs]), f64([r.sampling.top_p for r in reqs]),
+            f64([S.counter_uniform(r.sampling.seed, 0, len(r.generated)) for r in reqs]))
+        tok, flag = tok.cpu().tolist(), flag.cpu().tolist()
+        self.stats.device_samples += len(rows)
+        return {row: t for row, t, f in zip(rows, tok, flag) if not f}
+
     def _commit(self, order, tokens, logits) -> List[Request]:
         produced = []
         sel = 0
         now = time.monotonic()
+        drawn = self._device_samples(order, logits)
         for r, n, has_logits in order:
             was_decode = r.phase is Phase.DECODE
             r.offset += n
@@ -482,7 +564,7 @@ class Engine:
             sel += 1
             if was_decode:
                 self.stats.decode_tokens += 1
-            tok = self._sample(r, tokens, logits, row)
+            tok = drawn[row] if row in drawn else self._sample(r, tokens, logits, row)
             self._deliver(r, tok)
             produced.append(r)
         return produced

@@ -348,3 +348,23 @@ def gdn_gated_norm(o: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: 
                                               stream()), "gdn_gated_norm")
     count_launches(1)
     return out
+
+
+# ---------------------------------------------------------------- sampling
+def sample_topk(logits: torch.Tensor, top_k: torch.Tensor, temperature: torch.Tensor,
+                top_p: torch.Tensor, uniform: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-row top-k/top-p categorical draw on the device.  ``logits`` fp32 [rows, vocab];
+    ``top_k`` int32, ``temperature`` / ``top_p`` / ``uniform`` fp64, all [rows].  Returns
+    (tokens int32, flags int32); a set flag means the host law must serve that row."""
+    _cuda(logits, top_k, temperature, top_p, uniform)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and top_k.dtype == torch.int32
+    assert temperature.dtype == torch.float64 and top_p.dtype == torch.float64
+    assert uniform.dtype == torch.float64
+    rows, vocab = logits.shape
+    tok = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    flag = torch.zeros(rows, dtype=torch.int32, device=logits.device)
+    check(native.lib().orinfer_sample_topk(ptr(logits), rows, vocab, logits.stride(0), ptr(top_k),
+                                           ptr(temperature), ptr(top_p), ptr(uniform), ptr(tok),
+                                           ptr(flag), stream()), "sample_topk")
+    count_launches(1)
+    return tok, flag

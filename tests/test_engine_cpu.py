@@ -186,3 +186,20 @@ def test_mtp_head_speculation_preserves_greedy_output():
     assert out == plain
     st = eng.spec.statistics()
     assert st["rounds"] > 0 and st["proposed_tokens"] >= 2 * st["rounds"]
+
+
+def test_host_kv_offload_restores_evicted_prefix(weights):
+    """With a host tier, prefixes evicted under page pressure come back from pinned host memory
+    instead of being recomputed, and the restored KV gives the same tokens."""
+    base = _prompts(3, 130, seed=11)
+    load = LoadOptions(kv_offload_bytes=64 << 20)
+    eng = _engine(weights, kv_pages=4, max_active=1, prefill_chunk=256, load=load)
+    first = [eng.generate([p], max_new=4)[0] for p in base]       # 3 usable pages: must evict
+    assert eng.stats.offloaded_pages >= 1 and eng.prefix.statistics().host_pages >= 1
+    r = eng.submit(base[0], 4)
+    while not r.finished:
+        eng.step()
+    assert eng.stats.restored_pages >= 1 and r.cached_tokens == 128
+    assert r.generated == first[0]
+    cold = _engine(weights, load=LoadOptions(prefix_cache_bytes=0))
+    assert cold.generate([base[0]], max_new=4)[0] == first[0]

@@ -62,9 +62,32 @@ def test_sampled_rows_use_host_law(cuda):
     w = random_model(PRESETS["tiny"], seed=3).to(cuda)
     prompts = _prompts(2, 24, seed=4)
     opt = SamplingOptions(temperature=0.8, top_k=20, seed=7)
-    a = _engine(w).generate(prompts, max_new=8, sampling=opt)
+    eng = _engine(w)
+    a = eng.generate(prompts, max_new=8, sampling=opt)
     b = _engine(w).generate(prompts[:1], max_new=8, sampling=opt)
     assert a[0] == b[0]
+    assert eng.stats.device_samples == 16              # drawn by the device top-k sampler
+    host = _engine(w)
+    host._device_samples = lambda order, logits: {}    # same steps through the host law
+    assert host.generate(prompts, max_new=8, sampling=opt) == a
+    pen = SamplingOptions(temperature=0.8, top_k=20, seed=7, presence_penalty=0.5)
+    eng2 = _engine(w)
+    eng2.generate(prompts, max_new=4, sampling=pen)    # penalties need history: host law
+    assert eng2.stats.device_samples == 0
+
+
+def test_host_kv_offload_on_device(cuda):
+    w = random_model(PRESETS["tiny"], seed=3).to(cuda)
+    base = _prompts(3, 130, seed=11)
+    eng = Engine(w, load=LoadOptions(cuda_graph=GraphMode.OFF, kv_offload_bytes=64 << 20),
+                 sched=SchedulerOptions(max_active=1, prefill_chunk=256), kv_pages=4,
+                 max_context=512)
+    first = [eng.generate([p], max_new=4)[0] for p in base]
+    assert eng.stats.offloaded_pages >= 1
+    r = eng.submit(base[0], 4)
+    while not r.finished:
+        eng.step()
+    assert eng.stats.restored_pages >= 1 and r.cached_tokens == 128 and r.generated == first[0]
 
 
 def test_mtp_head_speculation_on_device(cuda, monkeypatch):

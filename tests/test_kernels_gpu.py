@@ -380,3 +380,32 @@ def test_moe_expert_parallel_partials_sum_to_full(cuda):
     hi, slots_hi = run(4, 4)
     assert torch.equal(slots_lo < 0, ids >= 4) and torch.equal(slots_hi < 0, ids < 4)
     assert torch.allclose(lo + hi, full, atol=3e-2, rtol=3e-3)
+
+
+def test_device_topk_sampler_matches_host_law(cuda):
+    """Same uniform, same law: the device draw equals the host law's draw row by row,
+    including ties at the top-k threshold (lowest ids win) and a nucleus cut."""
+    from orinfer_b200.core import sampling as S
+    from orinfer_b200.ops import functional as F
+    g = torch.Generator().manual_seed(21)
+    rows, vocab = 48, 5000
+    logits = torch.randn(rows, vocab, generator=g) * 3
+    logits[5, 100:140] = logits[5].max() + 1.0          # 40 equal maxima: ties inside the top-k
+    logits[6] = torch.round(logits[6])                   # many exact ties everywhere
+    ks = [1 + (7 * i) % 64 for i in range(rows)]
+    temps = [0.3 + 0.05 * i for i in range(rows)]
+    tops = [1.0 if i % 3 else 0.8 for i in range(rows)]
+    us = [S.counter_uniform(1234, 0, i) for i in range(rows)]
+    dev = lambda v, dt: torch.tensor(v, dtype=dt, device=cuda)
+    tok, flag = F.sample_topk(logits.to(cuda), dev(ks, torch.int32), dev(temps, torch.float64),
+                              dev(tops, torch.float64), dev(us, torch.float64))
+    assert flag.sum().item() == 0
+    want = [S.sample(logits[i].numpy(), [], S.SamplingOptions(temperature=temps[i], top_p=tops[i],
+                                                              top_k=ks[i]), us[i])
+            for i in range(rows)]
+    assert tok.cpu().tolist() == want
+    # a row of all-equal logits has more ties than the shortlist holds: handed to the host
+    flat = torch.zeros(1, vocab)
+    _, flag = F.sample_topk(flat.to(cuda), dev([8], torch.int32), dev([1.0], torch.float64),
+                            dev([1.0], torch.float64), dev([0.5], torch.float64))
+    assert flag.item() == 1
