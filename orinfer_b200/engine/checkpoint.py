@@ -169,26 +169,30 @@ def read_descriptor(directory) -> dict:
     return d
 
 
-def load_model(directory, device="cpu", verify: bool = False) -> ModelWeights:
+def load_model(directory, device="cpu", verify: bool = False,
+               workers: Optional[int] = None) -> ModelWeights:
+    """Reads the checkpoint with the C++ parallel reader (``workers`` threads, pinned staging
+    when the target is a GPU, per-tensor SHA-256 when ``verify``) and uploads it."""
+    from .weight_io import WeightReadError, read_tensors
     directory = Path(directory)
     desc = read_descriptor(directory)
     cfg = ModelConfig.from_json((directory / "config.json").read_text())
-    t: Dict[str, torch.Tensor] = {}
-    with safe_open(str(directory / "model.safetensors"), framework="pt") as f:
-        meta = f.metadata() or {}
-        for key in ("codec", "layout", "rotation"):
-            if meta.get(key) != QUANT_METADATA[key]:
-                raise CheckpointError(f"quantisation contract mismatch on {key}")
-        for k in f.keys():
-            t[k] = f.get_tensor(k)
+    to_gpu = torch.device(device).type == "cuda"
+    try:
+        t, meta = read_tensors(directory / "model.safetensors", workers=workers, pin=to_gpu,
+                               digests=desc["tensors"] if verify else None)
+    except WeightReadError as e:
+        raise CheckpointError(str(e)) from e
+    for key in ("codec", "layout", "rotation"):
+        if meta.get(key) != QUANT_METADATA[key]:
+            raise CheckpointError(f"quantisation contract mismatch on {key}")
+    if verify and set(desc["tensors"]) - set(t):
+        raise CheckpointError(f"tensors missing: {sorted(set(desc['tensors']) - set(t))[:3]}")
     if not np.array_equal(t["orinfer.e8p_q4.basis"].numpy(), np.array(e8p.basis())):
         raise CheckpointError("E8P basis in the checkpoint differs from the codec's")
-    if verify:
-        for k, v in t.items():
-            if hashlib.sha256(v.contiguous().numpy().tobytes()).hexdigest() != \
-                    desc["tensors"].get(k):
-                raise CheckpointError(f"SHA-256 mismatch for tensor {k}")
-    t = {k: v.to(device) for k, v in t.items()}
+    t = {k: v.to(device, non_blocking=to_gpu) for k, v in t.items()}
+    if to_gpu:
+        torch.cuda.synchronize()
     signs = {int(k.split(".k")[1].split(".")[0]): v for k, v in t.items()
              if k.startswith("orinfer.rotation.")}
     layers = [_load_layer(t, f"layers.{i}", "attn" if cfg.is_full_attention(i) else "gdn", signs)
