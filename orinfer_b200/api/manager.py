@@ -1,0 +1,267 @@
+"""Multi-model manager: a persistent registry of named models (with aliases), runners
+started on demand and shared by every name that resolves to the same runner key, leases
+that count requests in flight, a memory budget with idle eviction, a keep-alive sweep and a
+short negative cache for failed starts.
+
+The reference runs one child ``orinfer serve`` process per runner key behind a gateway
+(crates/orinfer-api/src/manager/mod.rs:32-96,159-372,430-560,674-727; behaviour pinned by
+manager/tests.rs:18-43).  Here a runner is an in-process ``Service`` (one engine thread each,
+all sharing the GPU's one CUDA context), which keeps start-up at weight-load time and lets
+runners share the process-wide kernel library; the registry, lease, budget and keep-alive
+semantics are the same.  ``install`` adds the gateway routes that need the registry
+(``/api/copy``, ``/api/delete``, ``/api/tags``, ``/api/ps``, model-dispatching chat).
+"""
+
+from __future__ import annotations
+
+import json
+import threading
+import time
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Callable, Dict, List, Optional
+
+from fastapi import Request as HttpRequest
+from fastapi.responses import JSONResponse
+
+NEGATIVE_CACHE_S = 10.0
+DEFAULT_KEEP_ALIVE_S = 300.0
+
+
+class ManagerError(ValueError):
+    def __init__(self, message: str, status: int = 400):
+        super().__init__(message)
+        self.status = status
+
+
+@dataclass
+class Entry:
+    name: str
+    path: str
+    options: Dict[str, object] = field(default_factory=dict)     # execution-affecting options
+    defaults: Dict[str, object] = field(default_factory=dict)    # sampling defaults (no fork)
+
+    def runner_key(self) -> str:
+        return json.dumps([str(Path(self.path).resolve()), self.options], sort_keys=True)
+
+
+@dataclass
+class Runner:
+    key: str
+    service: object
+    bytes: int
+    leases: int = 0
+    last_used: float = field(default_factory=time.monotonic)
+    keep_alive_s: float = DEFAULT_KEEP_ALIVE_S
+
+
+class ModelManager:
+    """``start(entry) -> (service, bytes)`` builds and starts a runner; ``stop(service)``
+    retires it.  Both run under the transition lock, so starts and stops are serialised while
+    models that are already up keep serving."""
+
+    def __init__(self, state_dir, start: Callable[[Entry], tuple], stop: Callable[[object], None],
+                 memory_budget_bytes: int = 0, clock: Callable[[], float] = time.monotonic):
+        self.state = Path(state_dir)
+        self.state.mkdir(parents=True, exist_ok=True)
+        self._start, self._stop = start, stop
+        self.budget = memory_budget_bytes
+        self.clock = clock
+        self._lock = threading.Lock()              # registry + runner table
+        self._transition = threading.Lock()        # serialises starts / stops
+        self.entries: Dict[str, Entry] = {}
+        self.runners: Dict[str, Runner] = {}
+        self._failed: Dict[str, tuple] = {}        # runner key -> (time, message)
+        self._load()
+
+    # ------------------------------------------------------------------ registry
+    def _file(self) -> Path:
+        return self.state / "registry.json"
+
+    def _load(self) -> None:
+        if self._file().exists():
+            for e in json.loads(self._file().read_text()):
+                self.entries[e["name"]] = Entry(**e)
+
+    def _save(self) -> None:
+        tmp = self._file().with_suffix(".tmp")
+        tmp.write_text(json.dumps([e.__dict__ for e in self.entries.values()], indent=1))
+        tmp.replace(self._file())
+
+    def register(self, name: str, path, options=None, defaults=None) -> Entry:
+        if not name or "/" in name.strip("/") and name.startswith("/"):
+            raise ManagerError("invalid model name")
+        with self._lock:
+            e = Entry(name, str(path), dict(options or {}), dict(defaults or {}))
+            self.entries[name] = e
+            self._save()
+            return e
+
+    def copy(self, source: str, destination: str) -> Entry:
+        """An alias: same path and options (so the same runner), its own name."""
+        with self._lock:
+            if source not in self.entries:
+                raise ManagerError(f"model '{source}' not found", 404)
+            src = self.entries[source]
+            e = Entry(destination, src.path, dict(src.options), dict(src.defaults))
+            self.entries[destination] = e
+            self._save()
+            return e
+
+    def remove(self, name: str) -> None:
+        with self._lock:
+            if name not in self.entries:
+                raise ManagerError(f"model '{name}' not found", 404)
+            key = self.entries.pop(name).runner_key()
+            self._save()
+            orphan = all(e.runner_key() != key for e in self.entries.values())
+        if orphan:
+            self._retire(key, force=False)
+
+    def list(self) -> List[Entry]:
+        with self._lock:
+            return sorted(self.entries.values(), key=lambda e: e.name)
+
+    def show(self, name: str) -> Entry:
+        with self._lock:
+            if name not in self.entries:
+                raise ManagerError(f"model '{name}' not found", 404)
+            return self.entries[name]
+
+    # ------------------------------------------------------------------ runners
+    def acquire(self, name: str, keep_alive_s: Optional[float] = None) -> Runner:
+        """Lease on the runner serving ``name`` (started if needed).  Pair with ``release``."""
+        entry = self.show(name)
+        key = entry.runner_key()
+        with self._lock:
+            r = self.runners.get(key)
+            if r is not None:
+                r.leases += 1
+                r.last_used = self.clock()
+                if keep_alive_s is not None:
+                    r.keep_alive_s = keep_alive_s
+                return r
+            failed = self._failed.get(key)
+            if failed and self.clock() - failed[0] < NEGATIVE_CACHE_S:
+                raise ManagerError(f"model '{name}' failed to start: {failed[1]}", 503)
+        with self._transition:
+            with self._lock:                        # someone else may have started it meanwhile
+                r = self.runners.get(key)
+                if r is not None:
+                    r.leases += 1
+                    r.last_used = self.clock()
+                    return r
+            try:
+                service, nbytes = self._start(entry)
+            except Exception as exc:                # noqa: BLE001 - reported to the client
+                with self._lock:
+                    self._failed[key] = (self.clock(), str(exc))
+                raise ManagerError(f"model '{name}' failed to start: {exc}", 503) from exc
+            self._make_room(nbytes)
+            r = Runner(key, service, nbytes, leases=1, last_used=self.clock(),
+                       keep_alive_s=DEFAULT_KEEP_ALIVE_S if keep_alive_s is None else keep_alive_s)
+            with self._lock:
+                self.runners[key] = r
+                self._failed.pop(key, None)
+            return r
+
+    def release(self, runner: Runner) -> None:
+        with self._lock:
+            runner.leases = max(runner.leases - 1, 0)
+            runner.last_used = self.clock()
+
+    def _make_room(self, nbytes: int) -> None:
+        """Idle eviction under the memory budget: least recently used idle runners go first."""
+        if self.budget <= 0:
+            return
+        while True:
+            with self._lock:
+                used = sum(r.bytes for r in self.runners.values())
+                if used + nbytes <= self.budget:
+                    return
+                idle = sorted((r for r in self.runners.values() if r.leases == 0),
+                              key=lambda r: r.last_used)
+                if not idle:
+                    raise ManagerError("memory budget exhausted by models in use", 503)
+                victim = idle[0].key
+            self._retire(victim, force=True, locked=True)
+
+    def _retire(self, key: str, force: bool, locked: bool = False) -> bool:
+        def go():
+            with self._lock:
+                r = self.runners.get(key)
+                if r is None or (r.leases > 0 and not force):
+                    return False
+                if r.leases > 0:
+                    return False
+                del self.runners[key]
+            self._stop(r.service)
+            return True
+        if locked:
+            return go()
+        with self._transition:
+            return go()
+
+    def sweep(self) -> List[str]:
+        """Retires idle runners whose keep-alive has run out (0 = retire as soon as idle;
+        negative = keep forever).  Returns the retired runner keys."""
+        now = self.clock()
+        with self._lock:
+            due = [r.key for r in self.runners.values()
+                   if r.leases == 0 and r.keep_alive_s >= 0 and now - r.last_used >= r.keep_alive_s]
+        return [k for k in due if self._retire(k, force=False)]
+
+    def running(self) -> List[dict]:
+        with self._lock:
+            names = {}
+            for e in self.entries.values():
+                names.setdefault(e.runner_key(), []).append(e.name)
+            return [{"names": sorted(names.get(r.key, [])), "bytes": r.bytes, "leases": r.leases,
+                     "idle_s": round(self.clock() - r.last_used, 3),
+                     "keep_alive_s": r.keep_alive_s} for r in self.runners.values()]
+
+    def shutdown(self) -> None:
+        with self._transition:
+            with self._lock:
+                rs, self.runners = list(self.runners.values()), {}
+            for r in rs:
+                self._stop(r.service)
+
+
+def install(app, manager: ModelManager) -> None:
+    """Registry routes of the Ollama surface on a gateway app."""
+    def fail(e: ManagerError):
+        return JSONResponse({"error": str(e)}, status_code=e.status)
+
+    @app.get("/api/tags")
+    async def tags():
+        return {"models": [{"name": e.name, "model": e.name, "details": {"path": e.path}}
+                           for e in manager.list()]}
+
+    @app.get("/api/ps")
+    async def ps():
+        return {"models": [{"name": n, "size": r["bytes"], "leases": r["leases"]}
+                           for r in manager.running() for n in r["names"]]}
+
+    @app.post("/api/copy")
+    async def copy(request: HttpRequest):
+        body = await request.json()
+        try:
+            manager.copy(body.get("source", ""), body.get("destination", ""))
+        except ManagerError as e:
+            return fail(e)
+        return JSONResponse({}, status_code=200)
+
+    @app.delete("/api/delete")
+    async def delete(request: HttpRequest):
+        body = await request.json()
+        try:
+            manager.remove(body.get("model") or body.get("name") or "")
+        except ManagerError as e:
+            return fail(e)
+        return JSONResponse({}, status_code=200)
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": e.name, "object": "model", "owned_by": "orinfer"}
+                                           for e in manager.list()]}

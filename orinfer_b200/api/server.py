@@ -225,6 +225,8 @@ def create_app(service: Service) -> FastAPI:
                         "usage": ev["usage"]}
         return _error(500, "request ended without a result", err_type="server_error")
 
+    from .encoders import install as install_encoders
     from .ollama import install as install_ollama
+    install_encoders(app, service)
     install_ollama(app, service)
     return app

@@ -65,6 +65,17 @@ class Job:
             self.events.put_nowait(event)
 
 
+class CallJob:
+    """A function to run on the engine thread between two engine steps (encoder passes,
+    introspection); the result comes back through ``future``."""
+
+    def __init__(self, fn: Callable[[Engine], Any]):
+        import concurrent.futures
+        self.fn = fn
+        self.future: "concurrent.futures.Future" = concurrent.futures.Future()
+        self.cancelled = False
+
+
 class EngineWorker(threading.Thread):
     def __init__(self, engine_factory: Callable[[], Engine], codec: ChatCodec, metrics: Metrics,
                  lifecycle: Lifecycle, queue_timeout_ms: int = 0):
@@ -140,7 +151,21 @@ class EngineWorker(threading.Thread):
                 return
             self._start(job)
 
-    def _start(self, job: Job) -> None:
+    def call(self, fn: Callable[[Engine], Any], timeout: Optional[float] = 60.0):
+        """Runs ``fn(engine)`` on the engine thread and returns its result."""
+        job = CallJob(fn)
+        if not self.try_submit(job):
+            raise RequestError("request queue is full", status=429, code="queue_full",
+                               err_type="rate_limit_error")
+        return job.future.result(timeout=timeout)
+
+    def _start(self, job) -> None:
+        if isinstance(job, CallJob):
+            try:
+                job.future.set_result(job.fn(self.engine))
+            except Exception as exc:                 # noqa: BLE001 - belongs to the caller
+                job.future.set_exception(exc)
+            return
         now = time.monotonic()
         if job.cancelled:
             return

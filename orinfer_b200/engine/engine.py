@@ -189,6 +189,42 @@ class Engine:
         self.waiting.append(req)
         return req
 
+    def encode(self, tokens: Sequence[int]):
+        """One bidirectional-free encoder pass of the decoder over ``tokens`` outside the
+        request queue: returns (mean-pooled, L2-normalised final hidden state fp32 [hidden],
+        fp32 logits of the last position).  Used by the embeddings and rerank endpoints.
+        Needs one free request slot and enough free KV pages (evicting cached prefixes)."""
+        n = len(tokens)
+        if n == 0 or n > min(self.max_context, self.max_rows):
+            raise ValueError(f"encoder input of {n} tokens is outside 1..{min(self.max_context, self.max_rows)}")
+        need = (n + PAGE_TOKENS - 1) // PAGE_TOKENS
+        if need > self.pool.available:
+            self._reclaim(need)
+        if not self.free_slots or need > self.pool.available:
+            raise MemoryError("no free slot or KV pages for an encoder pass")
+        slot = self.free_slots.pop()
+        pages = self.pool.take(need)
+        try:
+            row = self.page_table_host[slot]
+            row[:] = 0
+            row[:need] = pages
+            self.page_table_dev[slot].copy_(torch.from_numpy(row))
+            packet = Packet(self._upload("ids", list(tokens)), self._upload("req", [slot] * n),
+                            self._upload("pos", list(range(n))), self.page_table_dev, n, n,
+                            self._upload("sel", [n - 1]).long())
+            if self.on_gpu and n > 1:
+                packet.chunks = self._upload("chunks", [0, n, 0, slot]).view(-1, 4)
+                packet.max_q_len = n
+            _tok, lg = self.runner.greedy(packet, need_logits=True)
+            hidden = (self.runner.final_hidden(n) if hasattr(self.runner, "final_hidden")
+                      else self.runner._final[:n]).float()
+            pooled = hidden.mean(0)
+            pooled = pooled / pooled.norm().clamp_min(1e-12)
+            return pooled.cpu(), lg[0].float().cpu()
+        finally:
+            self.pool.release(pages)
+            self.free_slots.append(slot)
+
     def cancel(self, req: Request) -> None:
         req.cancelled = True
 

@@ -1,0 +1,141 @@
+"""Model manager semantics (registry, aliases, leases, budget eviction, keep-alive, negative
+cache) with fake runners, and the embeddings / rerank endpoints on the tiny CPU model."""
+import base64
+import struct
+
+import pytest
+from fastapi import FastAPI
+from fastapi.testclient import TestClient
+
+from orinfer_b200.api import manager as M
+
+
+class Clock:
+    def __init__(self):
+        self.t = 0.0
+
+    def __call__(self):
+        return self.t
+
+
+def _manager(tmp_path, budget=0, fail=()):
+    started, stopped, clock = [], [], Clock()
+
+    def start(entry):
+        if entry.name in fail:
+            raise RuntimeError("boom")
+        started.append(entry.name)
+        return f"svc:{entry.path}", 100
+
+    m = M.ModelManager(tmp_path, start, stopped.append, budget, clock)
+    return m, started, stopped, clock
+
+
+def test_aliases_share_a_runner_and_registry_persists(tmp_path):
+    m, started, stopped, _ = _manager(tmp_path)
+    m.register("a", "/models/a", options={"tp": 2}, defaults={"temperature": 0.2})
+    m.copy("a", "a-alias")
+    m.register("a-fast", "/models/a", options={"tp": 4})          # different runner key
+    r1, r2, r3 = m.acquire("a"), m.acquire("a-alias"), m.acquire("a-fast")
+    assert r1 is r2 and r3 is not r1 and started == ["a", "a-fast"] and r1.leases == 2
+    again = M.ModelManager(tmp_path, lambda e: ("x", 1), lambda s: None)
+    assert [e.name for e in again.list()] == ["a", "a-alias", "a-fast"]
+    assert again.show("a-alias").options == {"tp": 2}
+    with pytest.raises(M.ManagerError):
+        m.copy("missing", "x")
+    m.release(r1); m.release(r2)
+    m.remove("a")
+    assert stopped == []                                          # alias still needs the runner
+    m.remove("a-alias")
+    assert stopped == ["svc:/models/a"]
+
+
+def test_budget_evicts_idle_lru_and_refuses_when_all_in_use(tmp_path):
+    m, started, stopped, clock = _manager(tmp_path, budget=250)
+    for n in "abc":
+        m.register(n, f"/models/{n}")
+    ra = m.acquire("a"); clock.t = 1
+    rb = m.acquire("b"); clock.t = 2
+    with pytest.raises(M.ManagerError) as err:
+        m.acquire("c")                                            # 300 > 250, nothing idle
+    assert err.value.status == 503
+    m.release(ra); clock.t = 3
+    m.acquire("c")
+    assert stopped == ["svc:/models/a"] and {r["names"][0] for r in m.running()} == {"b", "c"}
+    m.release(rb)
+
+
+def test_keep_alive_sweep_and_negative_cache(tmp_path):
+    m, started, stopped, clock = _manager(tmp_path, fail={"bad"})
+    m.register("a", "/models/a"); m.register("bad", "/models/bad")
+    r = m.acquire("a", keep_alive_s=5)
+    assert m.sweep() == []                                        # leased
+    m.release(r); clock.t = 4.9
+    assert m.sweep() == []
+    clock.t = 5.1
+    assert len(m.sweep()) == 1 and stopped == ["svc:/models/a"]
+    with pytest.raises(M.ManagerError):
+        m.acquire("bad")
+    started_before = list(started)
+    with pytest.raises(M.ManagerError, match="failed to start"):
+        m.acquire("bad")                                          # served from the negative cache
+    assert started == started_before
+    clock.t += M.NEGATIVE_CACHE_S + 1
+    with pytest.raises(M.ManagerError):
+        m.acquire("bad")                                          # retried after the window
+
+
+def test_gateway_registry_routes(tmp_path):
+    m, *_ = _manager(tmp_path)
+    m.register("a", "/models/a")
+    app = FastAPI()
+    M.install(app, m)
+    c = TestClient(app)
+    assert c.post("/api/copy", json={"source": "a", "destination": "b"}).status_code == 200
+    assert [x["name"] for x in c.get("/api/tags").json()["models"]] == ["a", "b"]
+    assert c.post("/api/copy", json={"source": "zz", "destination": "b"}).status_code == 404
+    assert c.request("DELETE", "/api/delete", json={"model": "a"}).status_code == 200
+    assert [x["id"] for x in c.get("/v1/models").json()["data"]] == ["b"]
+
+
+@pytest.fixture(scope="module")
+def client():
+    from orinfer_b200.api.chat_codec import ByteTokenizer, ChatCodec
+    from orinfer_b200.api.server import Service, create_app
+    from orinfer_b200.config import PRESETS, SchedulerOptions
+    from orinfer_b200.engine.engine import Engine
+    from orinfer_b200.models.weights import random_model
+    weights = random_model(PRESETS["tiny"], seed=0)
+    svc = Service(lambda: Engine(weights, sched=SchedulerOptions(max_active=4, prefill_chunk=64),
+                                 kv_pages=24, max_context=512),
+                  ChatCodec(ByteTokenizer(1024), context=512, model_name="tiny"), "tiny")
+    svc.start()
+    with TestClient(create_app(svc)) as c:
+        yield c
+    svc.stop(1000)
+
+
+def test_embeddings_endpoint(client):
+    r = client.post("/v1/embeddings", json={"input": ["hello world", "hello world", "other"]}).json()
+    assert r["object"] == "list" and len(r["data"]) == 3 and r["usage"]["prompt_tokens"] > 0
+    a, b, c = (d["embedding"] for d in r["data"])
+    assert a == b and a != c and len(a) == 256
+    assert abs(sum(x * x for x in a) - 1.0) < 1e-4
+    q = client.post("/v1/embeddings", json={"input": "hello world", "input_type": "query",
+                                            "dimensions": 64, "encoding_format": "base64"}).json()
+    vec = struct.unpack("<64f", base64.b64decode(q["data"][0]["embedding"]))
+    assert abs(sum(x * x for x in vec) - 1.0) < 1e-4
+    bad = client.post("/v1/embeddings", json={"input": [], "input_type": "document"})
+    assert bad.status_code == 400 and bad.json()["error"]["param"] == "input"
+    assert client.post("/v1/embeddings", json={"input": "x", "dimensions": 9999}).status_code == 400
+
+
+def test_rerank_endpoint(client):
+    body = {"query": "capital of France", "documents": ["Paris", {"text": "bananas"}, "Lyon"],
+            "top_n": 2, "return_documents": True}
+    r = client.post("/v1/rerank", json=body).json()
+    assert len(r["results"]) == 2
+    assert r["results"][0]["relevance_score"] >= r["results"][1]["relevance_score"]
+    assert {x["index"] for x in r["results"]} <= {0, 1, 2} and "document" in r["results"][0]
+    assert client.post("/rerank", json=body).json()["results"] == r["results"]
+    assert client.post("/v1/rerank", json={"query": "", "documents": ["a"]}).status_code == 400
