@@ -393,7 +393,7 @@ def test_device_topk_sampler_matches_host_law(cuda):
     logits[5, 100:140] = logits[5].max() + 1.0          # 40 equal maxima: ties inside the top-k
     logits[6] = torch.round(logits[6])                   # many exact ties everywhere
     ks = [1 + (7 * i) % 64 for i in range(rows)]
-    temps = [0.3 + 0.05 * i for i in range(rows)]
+    temps = [0.3 + 0.03 * i for i in range(rows)]
     tops = [1.0 if i % 3 else 0.8 for i in range(rows)]
     us = [S.counter_uniform(1234, 0, i) for i in range(rows)]
     dev = lambda v, dt: torch.tensor(v, dtype=dt, device=cuda)
