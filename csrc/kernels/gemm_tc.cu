@@ -1,7 +1,9 @@
 // Quantised GEMM on the 5th-generation tensor cores: out[M,N] = (A8[M,K] . W[N,K]^T) * s_w * s_a.
 //
-// One CTA computes a (MT*128) x 128 output tile, MT = 1 or 2 accumulators in TMEM that
-// share every decoded weight tile.  Warp 0 streams operand tiles with TMA (activations
+// One CTA computes a (MT*128) x NB output tile: MT = 1, 2 or 4 accumulators in TMEM share
+// every decoded weight tile (the lattice decode, not the MMA, is the scarce resource, so a
+// weight tile should be decoded once and multiplied against as many rows as the packet has),
+// and NB = 128, 64 or 32 weight rows per CTA spreads narrow projections over the 148 SMs.  Warp 0 streams operand tiles with TMA (activations
 // always; INT8 weights for W8; the packed E8P codes as one contiguous bulk copy per
 // k-block for Q4/Q2).  Warps 2-17 expand the lattice codes into an INT8 weight tile in the
 // 128-byte-swizzled K-major layout the tensor core reads, warp 1 issues tcgen05.mma
@@ -26,20 +28,23 @@ int qgemv_dispatch(int fmt, const int8_t* a, const float* as, const void* w, con
 
 namespace tc {
 
-constexpr int BM = 128, BN = 128, BK = 128;
-constexpr int TILE_BYTES = 128 * 128;        // one INT8 operand tile
+constexpr int BM = 128, BK = 128;
+constexpr int TILE_BYTES = 128 * 128;        // one INT8 activation tile (128 rows x 128 k)
 constexpr int PRODUCERS = 512;               // warps 2..17
 constexpr int THREADS = 64 + PRODUCERS;
 
-template <int FMT, int MT>
+template <int FMT, int MT, int NB>
 struct Layout {
-  static constexpr int STAGES = MT == 1 ? 4 : 3;
   static constexpr int ROW_CODE_BYTES = FMT == 1 ? 64 : (FMT == 2 ? 32 : 0);
-  static constexpr int CODE_BYTES = BN * ROW_CODE_BYTES;
+  static constexpr int CODE_BYTES = NB * ROW_CODE_BYTES;
+  static constexpr int B_BYTES = NB * BK;     // INT8 weight tile, 128-byte rows
+  static constexpr int STAGE_BYTES = MT * TILE_BYTES + B_BYTES + CODE_BYTES;
+  static constexpr int STAGES = (222 * 1024) / STAGE_BYTES >= 4 ? 4 : (222 * 1024) / STAGE_BYTES;
+  static_assert(STAGES >= 2, "at least double buffering");
   static constexpr int LUT_BYTES = FMT == 0 ? 0 : 4096;
   static constexpr int A_OFF = 0;
   static constexpr int B_OFF = A_OFF + STAGES * MT * TILE_BYTES;
-  static constexpr int CODE_OFF = B_OFF + STAGES * TILE_BYTES;
+  static constexpr int CODE_OFF = B_OFF + STAGES * B_BYTES;
   static constexpr int LUT_OFF = CODE_OFF + STAGES * CODE_BYTES;
   static constexpr int BAR_OFF = LUT_OFF + LUT_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;   // barriers + alignment slack
@@ -54,14 +59,15 @@ struct GroupDesc {
   int n_per_expert;            // rows of one expert's bank (= N)
 };
 
-template <int FMT, bool OUT_F32, int MT>
+template <int FMT, bool OUT_F32, int MT, int NB>
 __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
     const unsigned char* __restrict__ w, const float* __restrict__ a_scale,
     const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K,
     const E8pTables* __restrict__ tables, int* status, PeerOut po, GroupDesc grp, AgIn ag) {
-  using L = Layout<FMT, MT>;
+  using L = Layout<FMT, MT, NB>;
   constexpr int STAGES = L::STAGES;
+  constexpr int BN = NB;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* a_s = smem + L::A_OFF;
@@ -129,14 +135,14 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
         const uint32_t ph = (kb / STAGES) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, status, STATUS_TMA_WAIT, kb)) break;
         const uint32_t bytes =
-            MT * TILE_BYTES + (FMT == 0 ? TILE_BYTES : rows_valid * L::ROW_CODE_BYTES);
+            MT * TILE_BYTES + (FMT == 0 ? L::B_BYTES : rows_valid * L::ROW_CODE_BYTES);
         mbar_expect_tx(&tma_full[s], bytes);
 #pragma unroll
         for (int t = 0; t < MT; ++t)
           tma_load_2d(a_s + (s * MT + t) * TILE_BYTES, &tmap_a, &tma_full[s], kb * BK,
                       m0 + t * BM);
         if (FMT == 0) {
-          tma_load_2d(b_s + s * TILE_BYTES, &tmap_b, &tma_full[s], kb * BK, b_row0);
+          tma_load_2d(b_s + s * L::B_BYTES, &tmap_b, &tma_full[s], kb * BK, b_row0);
         } else {
           const unsigned char* src =
               w + (static_cast<size_t>(kb) * N + n0) * L::ROW_CODE_BYTES;
@@ -160,7 +166,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
         if (ok && FMT != 0) ok = mbar_wait(&b_full[s], ph, status, STATUS_MMA_WAIT, 0x2000 | kb);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t b_addr = smem_u32(b_s + s * TILE_BYTES);
+        const uint32_t b_addr = smem_u32(b_s + s * L::B_BYTES);
 #pragma unroll
         for (int j = 0; j < BK / 32; ++j) {
           const uint64_t bdesc = umma_desc(b_addr + j * 32, 16, 1024);
@@ -179,7 +185,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     const int t = threadIdx.x - 64;                     // 0..511
     bool ok = true;
     if (FMT != 0) {
-      const int chunk = t & 7, rbase = t >> 3;          // 64 rows per pass, 2 passes
+      const int chunk = t & 7, rbase = t >> 3;          // 64 weight rows per pass
       for (int kb = 0; kb < kblocks; ++kb) {
         const int s = kb % STAGES;
         const uint32_t ph = (kb / STAGES) & 1;
@@ -188,10 +194,11 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
         ok = mbar_wait(&tma_full[s], ph, status, STATUS_DECODE_WAIT, kb);
         if (!ok) break;
         const unsigned char* cs = code_s + s * L::CODE_BYTES;
-        unsigned char* bs = b_s + s * TILE_BYTES;
+        unsigned char* bs = b_s + s * L::B_BYTES;
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < (BN + 63) / 64; ++i) {
           const int row = rbase + 64 * i;
+          if (BN < 64 && row >= BN) break;
           uint4 v = make_uint4(0, 0, 0, 0);
           if (row < rows_valid) {
             if (FMT == 1) {
@@ -217,55 +224,53 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     if (ok) {
       tc_fence_after();
       const int quad = warp & 3;                          // TMEM lane quadrant of this warp
-      const int part = (warp - 2) >> 2;                   // which 32 columns of each tile
+      const int part = (warp - 2) >> 2;                   // 0..3: which 32-column chunks
       const int row = quad * 32 + lane;
+      constexpr int CHUNKS = BN / 32;                     // 32-column chunks per accumulator
 #pragma unroll 1
-      for (int mt = 0; mt < MT; ++mt) {
+      for (int item = part; item < MT * CHUNKS; item += 4) {
+        const int mt = item / CHUNKS, c0 = (item % CHUNKS) * 32;
         const int m = m0 + mt * BM + row;
         // gathered row scales were written by peers: read them past L1
         const float sa = m < m_limit ? (ag.tp > 0 ? __ldcg(a_scale + m) : a_scale[m]) : 0.f;
-#pragma unroll 1
-        for (int c0 = part * 32; c0 < part * 32 + 32; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + mt * BN + c0, r);
-          tc_wait_ld();
-          if (m < m_limit) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + mt * BN + c0, r);
+        tc_wait_ld();
+        if (m < m_limit) {
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const int n = n0 + c0 + g * 8;
-              if (n + 8 <= N) {
-                float v[8];
+          for (int g = 0; g < 4; ++g) {
+            const int n = n0 + c0 + g * 8;
+            if (n + 8 <= N) {
+              float v[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  v[j] = (static_cast<float>(static_cast<int>(r[g * 8 + j])) *
-                          __half2float(w_scale[n + j])) * sa;
-                if (po.tp > 0) {
-                  // fused scatter: FP16 partial tile -> slot [rank] of every rank's inbox
-                  __align__(16) __half h[8];
+              for (int j = 0; j < 8; ++j)
+                v[j] = (static_cast<float>(static_cast<int>(r[g * 8 + j])) *
+                        __half2float(w_scale[n + j])) * sa;
+              if (po.tp > 0) {
+                // fused scatter: FP16 partial tile -> slot [rank] of the peers' inboxes
+                __align__(16) __half h[8];
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
-                  const size_t off =
-                      (static_cast<size_t>(po.rank) * po.rows_cap + m) * N + n;
-                  if (po.rows_per > 0) {
-                    // reduce-scatter: only the owner of row m receives this partial
-                    *reinterpret_cast<int4*>(po.inbox[min(m / po.rows_per, po.tp - 1)] + off) =
-                        *reinterpret_cast<const int4*>(h);
-                  } else {
-                    for (int d = 0; d < po.tp; ++d)
-                      *reinterpret_cast<int4*>(po.inbox[d] + off) =
-                          *reinterpret_cast<const int4*>(h);
-                  }
-                } else if (OUT_F32) {
-                  float* o = reinterpret_cast<float*>(out) + static_cast<size_t>(m) * N + n;
-                  *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
-                  *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+                for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
+                const size_t off = (static_cast<size_t>(po.rank) * po.rows_cap + m) * N + n;
+                if (po.rows_per > 0) {
+                  // reduce-scatter: only the owner of row m receives this partial
+                  *reinterpret_cast<int4*>(po.inbox[min(m / po.rows_per, po.tp - 1)] + off) =
+                      *reinterpret_cast<const int4*>(h);
                 } else {
-                  __align__(16) __half h[8];
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
-                  __half* o = reinterpret_cast<__half*>(out) + static_cast<size_t>(m) * N + n;
-                  *reinterpret_cast<int4*>(o) = *reinterpret_cast<const int4*>(h);
+                  for (int d = 0; d < po.tp; ++d)
+                    *reinterpret_cast<int4*>(po.inbox[d] + off) =
+                        *reinterpret_cast<const int4*>(h);
                 }
+              } else if (OUT_F32) {
+                float* o = reinterpret_cast<float*>(out) + static_cast<size_t>(m) * N + n;
+                *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+              } else {
+                __align__(16) __half h[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
+                __half* o = reinterpret_cast<__half*>(out) + static_cast<size_t>(m) * N + n;
+                *reinterpret_cast<int4*>(o) = *reinterpret_cast<const int4*>(h);
               }
             }
           }
@@ -279,17 +284,17 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   if (po.tp > 0) peer_signal_done(po, gridDim.x * gridDim.y);
 }
 
-template <int FMT, bool OUT_F32, int MT>
+template <int FMT, bool OUT_F32, int MT, int NB>
 int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale, void* out,
            int M, int N, int K, cudaStream_t stream, const PeerOut& po,
            const GroupDesc& grp = GroupDesc{nullptr, nullptr, 0, 0}, int experts = 1,
            int max_tiles = 0, const AgIn& ag = AgIn{nullptr, nullptr, 0, 0}) {
-  using L = Layout<FMT, MT>;
+  using L = Layout<FMT, MT, NB>;
   CUtensorMap ta, tb;
   if (!make_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BM, BK)) return -3;
   if (FMT == 0) {
     if (!make_tmap_2d(&tb, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1,
-                      static_cast<uint64_t>(N) * experts, K, K, BN, BK))
+                      static_cast<uint64_t>(N) * experts, K, K, NB, BK))
       return -3;
   } else {
     tb = ta;
@@ -297,33 +302,53 @@ int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w
   }
   static bool attr = false;
   if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(qgemm_tc_kernel<FMT, OUT_F32, MT>,
+    cudaError_t e = cudaFuncSetAttribute(qgemm_tc_kernel<FMT, OUT_F32, MT, NB>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return static_cast<int>(e);
     attr = true;
   }
-  dim3 grid((N + BN - 1) / BN, grp.tiles ? max_tiles : (M + BM * MT - 1) / (BM * MT));
-  qgemm_tc_kernel<FMT, OUT_F32, MT><<<grid, THREADS, L::TOTAL, stream>>>(
+  dim3 grid((N + NB - 1) / NB, grp.tiles ? max_tiles : (M + BM * MT - 1) / (BM * MT));
+  qgemm_tc_kernel<FMT, OUT_F32, MT, NB><<<grid, THREADS, L::TOTAL, stream>>>(
       ta, tb, reinterpret_cast<const unsigned char*>(w), a_scale, w_scale, out, M, N, K,
       runtime_e8p_tables(), runtime_status_ptr(), po, grp, ag);
   return static_cast<int>(cudaGetLastError());
 }
 
+// Tile choice.  Rows: as many accumulators as the packet fills (each decoded weight tile is
+// then multiplied against up to 512 rows).  Weight rows per CTA: the widest tile that still
+// gives the grid about one CTA per SM, so narrow projections (N = hidden) do not leave most
+// of the machine idle.  FP32 output is only used by the (very wide) vocabulary head.
 template <int FMT>
 int launch_fmt(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale,
                void* out, int M, int N, int K, int out_f32, cudaStream_t stream,
                const PeerOut& po, const AgIn& ag = AgIn{nullptr, nullptr, 0, 0}) {
-  // two accumulators halve the decode work per MAC, but only pay off once the grid
-  // still covers the 148 SMs
-  const long ctas2 = static_cast<long>((N + BN - 1) / BN) * ((M + 2 * BM - 1) / (2 * BM));
   const GroupDesc none{nullptr, nullptr, 0, 0};
-  if (M > BM && ctas2 >= 120)
-    return out_f32
-               ? launch<FMT, true, 2>(a, a_scale, w, w_scale, out, M, N, K, stream, po, none, 1, 0, ag)
-               : launch<FMT, false, 2>(a, a_scale, w, w_scale, out, M, N, K, stream, po, none, 1, 0, ag);
-  return out_f32
-             ? launch<FMT, true, 1>(a, a_scale, w, w_scale, out, M, N, K, stream, po, none, 1, 0, ag)
-             : launch<FMT, false, 1>(a, a_scale, w, w_scale, out, M, N, K, stream, po, none, 1, 0, ag);
+  const int mt = M > 2 * BM ? 4 : (M > BM ? 2 : 1);
+  const long mtiles = (M + BM * mt - 1) / (BM * mt);
+  auto ctas = [&](int nb) { return mtiles * ((N + nb - 1) / nb); };
+  const int nb = (out_f32 || ctas(128) >= 120) ? 128 : (ctas(64) >= 120 ? 64 : 32);
+#define ORINFER_GO(F32, MTV, NBV)                                                              \
+  return launch<FMT, F32, MTV, NBV>(a, a_scale, w, w_scale, out, M, N, K, stream, po, none, 1, \
+                                    0, ag)
+  if (out_f32) {
+    if (mt == 4) ORINFER_GO(true, 4, 128);
+    if (mt == 2) ORINFER_GO(true, 2, 128);
+    ORINFER_GO(true, 1, 128);
+  }
+  if (mt == 4) {
+    if (nb == 128) ORINFER_GO(false, 4, 128);
+    if (nb == 64) ORINFER_GO(false, 4, 64);
+    ORINFER_GO(false, 4, 32);
+  }
+  if (mt == 2) {
+    if (nb == 128) ORINFER_GO(false, 2, 128);
+    if (nb == 64) ORINFER_GO(false, 2, 64);
+    ORINFER_GO(false, 2, 32);
+  }
+  if (nb == 128) ORINFER_GO(false, 1, 128);
+  if (nb == 64) ORINFER_GO(false, 1, 64);
+  ORINFER_GO(false, 1, 32);
+#undef ORINFER_GO
 }
 
 }  // namespace tc
@@ -417,11 +442,11 @@ extern "C" int orinfer_qgemm_grouped(int fmt, const int8_t* a, const float* a_sc
   tc::GroupDesc g{tiles, meta, bank, N};
   PeerOut po{};
   if (fmt == 0)
-    return tc::launch<0, false, 1>(a, a_scale, w, w_scale, out, S, N, K, stream, po, g, experts,
+    return tc::launch<0, false, 1, 128>(a, a_scale, w, w_scale, out, S, N, K, stream, po, g, experts,
                                    max_tiles);
   if (fmt == 1)
-    return tc::launch<1, false, 1>(a, a_scale, w, w_scale, out, S, N, K, stream, po, g, experts,
+    return tc::launch<1, false, 1, 128>(a, a_scale, w, w_scale, out, S, N, K, stream, po, g, experts,
                                    max_tiles);
-  return tc::launch<2, false, 1>(a, a_scale, w, w_scale, out, S, N, K, stream, po, g, experts,
+  return tc::launch<2, false, 1, 128>(a, a_scale, w, w_scale, out, S, N, K, stream, po, g, experts,
                                  max_tiles);
 }

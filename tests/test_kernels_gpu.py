@@ -95,6 +95,9 @@ def _rand_weight(fmt, n, k, dev, seed):
 @pytest.mark.parametrize("m,n,k,path", [
     (1, 256, 256, 1), (3, 136, 128, 1), (8, 2560, 1024, 1), (5, 256, 512, 2),
     (16, 128, 128, 2), (128, 384, 1024, 2), (200, 2560, 2560, 2), (512, 1536, 1280, 0),
+    # tile variants: 4 / 2 / 1 accumulators x 128 / 64 / 32 weight rows per CTA, ragged N
+    (600, 19456, 256, 0), (1000, 6400, 128, 0), (250, 12800, 128, 0), (100, 12800, 256, 0),
+    (700, 8200, 256, 0), (50, 1000, 128, 0), (513, 2560, 1024, 0),
 ])
 def test_qgemm(cuda, fmt, m, n, k, path):
     from orinfer_b200.ops import functional as F
