@@ -184,9 +184,14 @@ def main() -> int:
         barrier()
         return max_over_ranks(ms) / steps
 
-    def decode_rate(batch: int, context: int, new_tokens: int):
+    def decode_rate(batch: int, context: int, new_tokens: int, mtp: bool = False):
         """Aggregate decode tokens/s of `batch` concurrent requests through the Engine
-        (CUDA-graph decode, greedy, one token readback per step)."""
+        (CUDA-graph decode, greedy, one token readback per step).  ``mtp`` keeps the adaptive
+        draft-head speculation on; random-init weights give it almost nothing to accept, so
+        that number shows the controller's cost of finding that out, not a speed-up."""
+        saved_drafts = engine.spec.max_drafts
+        if not mtp:
+            engine.spec.max_drafts = 0
         prompts = [torch.randint(0, cfg.vocab, (context,), generator=gen).tolist()
                    for _ in range(batch)]
         reqs = [engine.submit(p, new_tokens + 8, ignore_eos=True) for p in prompts]
@@ -208,6 +213,7 @@ def main() -> int:
             engine.cancel(r)
         while engine.has_work():
             engine.step()
+        engine.spec.max_drafts = saved_drafts
         return produced / dt, dt / max(steps, 1) * 1e3
 
     sampler = ClockSampler(local) if rank == 0 else None
@@ -222,6 +228,9 @@ def main() -> int:
             rate, ms = decode_rate(b, 512, 64)
             extra[f"decode_tok_s_bs{b}"] = round(rate, 1)
             extra[f"decode_ms_per_step_bs{b}"] = round(ms, 3)
+        if engine.spec.enabled:
+            rate, ms = decode_rate(1, 512, 256, mtp=True)
+            extra["decode_tok_s_bs1_mtp_adaptive_random_weights"] = round(rate, 1)
     status = native.read_status()
     if rank == 0:
         value = PROMPT / ms_dev * 1e3

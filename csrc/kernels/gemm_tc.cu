@@ -38,16 +38,25 @@ struct Layout {
   static constexpr int ROW_CODE_BYTES = FMT == 1 ? 64 : (FMT == 2 ? 32 : 0);
   static constexpr int CODE_BYTES = NB * ROW_CODE_BYTES;
   static constexpr int B_BYTES = NB * BK;     // INT8 weight tile, 128-byte rows
-  static constexpr int STAGE_BYTES = MT * TILE_BYTES + B_BYTES + CODE_BYTES;
-  static constexpr int STAGES = (222 * 1024) / STAGE_BYTES >= 4 ? 4 : (222 * 1024) / STAGE_BYTES;
-  static_assert(STAGES >= 2, "at least double buffering");
+  // Two rings of different depth: activation tiles are large (MT x 16 KiB per k-block), so
+  // they get what is left after the weight side (codes + decoded INT8 tile) is 3-4 deep;
+  // the decode then runs ahead of the tensor core while the next activation tiles land.
+  static constexpr int A_BYTES = MT * TILE_BYTES;
+  static constexpr int BC_BYTES = B_BYTES + CODE_BYTES;
+  static constexpr int BUDGET = 221 * 1024;
+  static constexpr int SB_FIT = (BUDGET - 2 * A_BYTES) / BC_BYTES;
+  static constexpr int SB = SB_FIT >= 4 ? 4 : SB_FIT;
+  static constexpr int SA_FIT = (BUDGET - SB * BC_BYTES) / A_BYTES;
+  static constexpr int SA = SA_FIT >= 4 ? 4 : SA_FIT;
+  static_assert(SA >= 2 && SB >= 2, "at least double buffering");
   static constexpr int LUT_BYTES = FMT == 0 ? 0 : 4096;
   static constexpr int A_OFF = 0;
-  static constexpr int B_OFF = A_OFF + STAGES * MT * TILE_BYTES;
-  static constexpr int CODE_OFF = B_OFF + STAGES * B_BYTES;
-  static constexpr int LUT_OFF = CODE_OFF + STAGES * CODE_BYTES;
+  static constexpr int B_OFF = A_OFF + SA * A_BYTES;
+  static constexpr int CODE_OFF = B_OFF + SB * B_BYTES;
+  static constexpr int LUT_OFF = CODE_OFF + SB * CODE_BYTES;
   static constexpr int BAR_OFF = LUT_OFF + LUT_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;   // barriers + alignment slack
+  static_assert(TOTAL <= 227 * 1024, "exceeds the shared memory of one CTA");
 };
 
 // Grouped (mixture-of-experts) launch: blockIdx.y walks a device-side tile table
@@ -66,7 +75,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K,
     const E8pTables* __restrict__ tables, int* status, PeerOut po, GroupDesc grp, AgIn ag) {
   using L = Layout<FMT, MT, NB>;
-  constexpr int STAGES = L::STAGES;
+  constexpr int SA = L::SA, SB = L::SB;
   constexpr int BN = NB;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -75,11 +84,13 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   unsigned char* code_s = smem + L::CODE_OFF;
   E8pSmem* lut = reinterpret_cast<E8pSmem*>(smem + L::LUT_OFF);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
-  uint64_t* tma_full = bars;                 // [STAGES]
-  uint64_t* b_full = bars + STAGES;          // [STAGES]
-  uint64_t* empty = bars + 2 * STAGES;       // [STAGES]
-  uint64_t* tmem_full = bars + 3 * STAGES;   // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 1);
+  uint64_t* a_full = bars;                   // [SA] activation tiles landed (TMA)
+  uint64_t* a_empty = bars + SA;             // [SA] tensor core done with the tiles
+  uint64_t* c_full = bars + 2 * SA;          // [SB] packed codes landed (bulk copy)
+  uint64_t* b_full = c_full + SB;            // [SB] INT8 weight tile ready (decode or TMA)
+  uint64_t* b_empty = c_full + 2 * SB;       // [SB] tensor core done with the weight tile
+  uint64_t* tmem_full = c_full + 3 * SB;     // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN;
@@ -98,10 +109,14 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   constexpr uint32_t TMEM_COLS = MT * BN;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&tma_full[s], 1);
-      mbar_init(&b_full[s], PRODUCERS);
-      mbar_init(&empty[s], 1);
+    for (int s = 0; s < SA; ++s) {
+      mbar_init(&a_full[s], 1);
+      mbar_init(&a_empty[s], 1);
+    }
+    for (int s = 0; s < SB; ++s) {
+      mbar_init(&c_full[s], 1);
+      mbar_init(&b_full[s], FMT == 0 ? 1 : PRODUCERS);
+      mbar_init(&b_empty[s], 1);
     }
     mbar_init(tmem_full, 1);
     mbar_fence_init();
@@ -122,6 +137,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
 
   if (warp == 0) {
     if (lane == 0) {
+      // activation loader
       int issued = 0;
       bool a_ready = true;
       if (ag.tp > 0) {
@@ -131,53 +147,64 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
         fence_proxy_async_all();
       }
       for (int kb = 0; a_ready && kb < kblocks; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        if (!mbar_wait(&empty[s], ph ^ 1, status, STATUS_TMA_WAIT, kb)) break;
-        const uint32_t bytes =
-            MT * TILE_BYTES + (FMT == 0 ? L::B_BYTES : rows_valid * L::ROW_CODE_BYTES);
-        mbar_expect_tx(&tma_full[s], bytes);
+        const int s = kb % SA;
+        if (!mbar_wait(&a_empty[s], ((kb / SA) & 1) ^ 1, status, STATUS_TMA_WAIT, kb)) break;
+        mbar_expect_tx(&a_full[s], MT * TILE_BYTES);
 #pragma unroll
         for (int t = 0; t < MT; ++t)
-          tma_load_2d(a_s + (s * MT + t) * TILE_BYTES, &tmap_a, &tma_full[s], kb * BK,
+          tma_load_2d(a_s + (s * MT + t) * TILE_BYTES, &tmap_a, &a_full[s], kb * BK,
                       m0 + t * BM);
-        if (FMT == 0) {
-          tma_load_2d(b_s + s * L::B_BYTES, &tmap_b, &tma_full[s], kb * BK, b_row0);
-        } else {
-          const unsigned char* src =
-              w + (static_cast<size_t>(kb) * N + n0) * L::ROW_CODE_BYTES;
-          bulk_load(code_s + s * L::CODE_BYTES, src, rows_valid * L::ROW_CODE_BYTES, &tma_full[s]);
-        }
         issued = kb + 1;
       }
       // Never leave the CTA with a copy of ours in flight: wait (bounded) for the
       // last copies issued into each stage.
-      for (int kb = max(0, issued - STAGES); kb < issued; ++kb)
-        mbar_wait(&tma_full[kb % STAGES], (kb / STAGES) & 1, status, STATUS_TMA_WAIT, 0x4000 | kb);
+      for (int kb = max(0, issued - SA); kb < issued; ++kb)
+        mbar_wait(&a_full[kb % SA], (kb / SA) & 1, status, STATUS_TMA_WAIT, 0x4000 | kb);
+    } else if (lane == 1) {
+      // weight loader: INT8 tiles by TMA (W8) or the packed codes as one bulk copy
+      int issued = 0;
+      uint64_t* landed = FMT == 0 ? b_full : c_full;
+      for (int kb = 0; kb < kblocks; ++kb) {
+        const int s = kb % SB;
+        if (!mbar_wait(&b_empty[s], ((kb / SB) & 1) ^ 1, status, STATUS_TMA_WAIT, 0x1000 | kb))
+          break;
+        if (FMT == 0) {
+          mbar_expect_tx(&b_full[s], L::B_BYTES);
+          tma_load_2d(b_s + s * L::B_BYTES, &tmap_b, &b_full[s], kb * BK, b_row0);
+        } else {
+          const unsigned char* src =
+              w + (static_cast<size_t>(kb) * N + n0) * L::ROW_CODE_BYTES;
+          mbar_expect_tx(&c_full[s], rows_valid * L::ROW_CODE_BYTES);
+          bulk_load(code_s + s * L::CODE_BYTES, src, rows_valid * L::ROW_CODE_BYTES, &c_full[s]);
+        }
+        issued = kb + 1;
+      }
+      for (int kb = max(0, issued - SB); kb < issued; ++kb)
+        mbar_wait(&landed[kb % SB], (kb / SB) & 1, status, STATUS_TMA_WAIT, 0x5000 | kb);
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc(2, 1, 1, 0, 0, BM, BN);
       bool ok = true;
       for (int kb = 0; kb < kblocks && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        ok = mbar_wait(&tma_full[s], ph, status, STATUS_MMA_WAIT, kb);
-        if (ok && FMT != 0) ok = mbar_wait(&b_full[s], ph, status, STATUS_MMA_WAIT, 0x2000 | kb);
+        const int sa = kb % SA, sb = kb % SB;
+        ok = mbar_wait(&a_full[sa], (kb / SA) & 1, status, STATUS_MMA_WAIT, kb);
+        if (ok) ok = mbar_wait(&b_full[sb], (kb / SB) & 1, status, STATUS_MMA_WAIT, 0x2000 | kb);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t b_addr = smem_u32(b_s + s * L::B_BYTES);
+        const uint32_t b_addr = smem_u32(b_s + sb * L::B_BYTES);
 #pragma unroll
         for (int j = 0; j < BK / 32; ++j) {
           const uint64_t bdesc = umma_desc(b_addr + j * 32, 16, 1024);
 #pragma unroll
           for (int t = 0; t < MT; ++t) {
-            const uint32_t a_addr = smem_u32(a_s + (s * MT + t) * TILE_BYTES);
+            const uint32_t a_addr = smem_u32(a_s + (sa * MT + t) * TILE_BYTES);
             mma_i8_ss(tmem_base + t * BN, umma_desc(a_addr + j * 32, 16, 1024), bdesc, idesc,
                       (kb | j) != 0 ? 1u : 0u);
           }
         }
-        tc_commit(&empty[s]);
+        tc_commit(&a_empty[sa]);
+        tc_commit(&b_empty[sb]);
       }
       if (ok) tc_commit(tmem_full);
     }
@@ -187,11 +214,10 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     if (FMT != 0) {
       const int chunk = t & 7, rbase = t >> 3;          // 64 weight rows per pass
       for (int kb = 0; kb < kblocks; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        // the copy for this phase is only issued after the stage was released, so its
-        // arrival also means the INT8 tile of this stage is free to overwrite
-        ok = mbar_wait(&tma_full[s], ph, status, STATUS_DECODE_WAIT, kb);
+        const int s = kb % SB;
+        // the codes of this phase are only requested after the tensor core released the
+        // stage, so their arrival also means the INT8 tile of this stage may be overwritten
+        ok = mbar_wait(&c_full[s], (kb / SB) & 1, status, STATUS_DECODE_WAIT, kb);
         if (!ok) break;
         const unsigned char* cs = code_s + s * L::CODE_BYTES;
         unsigned char* bs = b_s + s * L::B_BYTES;

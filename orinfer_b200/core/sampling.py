@@ -59,8 +59,12 @@ class SamplingOptions:
 
     @property
     def is_greedy(self) -> bool:
-        c, _keep = self._c()
-        return bool(lib().orinfer_sampling_is_greedy(ctypes.byref(c)))
+        """Temperature 0 and nothing that rewrites the scores: the arg-max is the answer.
+        (Same predicate as ``orinfer_sampling_is_greedy``; evaluated here because the engine
+        asks it for every row of every step.)"""
+        return (self.temperature == 0.0 and self.presence_penalty == 0.0
+                and self.frequency_penalty == 0.0 and self.repetition_penalty == 1.0
+                and not self.logit_bias)
 
     @property
     def device_topk(self) -> bool:
