@@ -132,6 +132,7 @@ int orinfer_moe_combine_peer(const __half* expert_out, const int* slots, const f
                              int rows, int top_k, const __half* shared_out,
                              const float* shared_gate, const OrinferPeerOut* peers, int hidden,
                              cudaStream_t stream);
+int orinfer_qgemm_launches(int M, int N, int K, int out_f32, int force_path);
 int orinfer_qgemm_grouped(int fmt, const int8_t* a, const float* a_scale, const void* w,
                           const __half* w_scale, void* out, int S, int N, int K, int experts,
                           const int* tiles, const int* meta, int max_tiles, cudaStream_t stream);

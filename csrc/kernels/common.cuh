@@ -248,6 +248,10 @@ struct E8pSmem {
 
 // Host-side runtime singletons (runtime.cu): device status word and decode tables.
 int* runtime_status_ptr();
+// INT32 partial accumulators of split-K GEMMs: [splits][M][N], allocated once at start-up so
+// that no launch ever allocates (captured graphs keep the address).
+constexpr size_t SPLITK_WORKSPACE_BYTES = 96ull << 20;
+int* runtime_splitk_workspace();
 const E8pTables* runtime_e8p_tables();
 cudaError_t runtime_ensure_init();
 

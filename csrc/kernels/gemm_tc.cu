@@ -73,7 +73,8 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
     const unsigned char* __restrict__ w, const float* __restrict__ a_scale,
     const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K,
-    const E8pTables* __restrict__ tables, int* status, PeerOut po, GroupDesc grp, AgIn ag) {
+    const E8pTables* __restrict__ tables, int* status, PeerOut po, GroupDesc grp, AgIn ag,
+    int* __restrict__ partial) {
   using L = Layout<FMT, MT, NB>;
   constexpr int SA = L::SA, SB = L::SB;
   constexpr int BN = NB;
@@ -104,7 +105,11 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     w_scale += static_cast<long long>(expert) * grp.n_per_expert;
     b_row0 = expert * grp.n_per_expert + n0;
   }
-  const int kblocks = K / BK;
+  // split-K: blockIdx.z owns k-blocks [kb0, kb0 + kblocks) and stores raw INT32 accumulators
+  // into partial[z][M][N]; a finalize kernel adds the splits and applies the scales
+  const int kb_all = K / BK, kb_per = (kb_all + gridDim.z - 1) / gridDim.z;
+  const int kb0 = blockIdx.z * kb_per;
+  const int kblocks = max(0, min(kb_all, kb0 + kb_per) - kb0);
   const int rows_valid = min(BN, N - n0);
   constexpr uint32_t TMEM_COLS = MT * BN;
 
@@ -152,7 +157,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
         mbar_expect_tx(&a_full[s], MT * TILE_BYTES);
 #pragma unroll
         for (int t = 0; t < MT; ++t)
-          tma_load_2d(a_s + (s * MT + t) * TILE_BYTES, &tmap_a, &a_full[s], kb * BK,
+          tma_load_2d(a_s + (s * MT + t) * TILE_BYTES, &tmap_a, &a_full[s], (kb0 + kb) * BK,
                       m0 + t * BM);
         issued = kb + 1;
       }
@@ -170,10 +175,10 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
           break;
         if (FMT == 0) {
           mbar_expect_tx(&b_full[s], L::B_BYTES);
-          tma_load_2d(b_s + s * L::B_BYTES, &tmap_b, &b_full[s], kb * BK, b_row0);
+          tma_load_2d(b_s + s * L::B_BYTES, &tmap_b, &b_full[s], (kb0 + kb) * BK, b_row0);
         } else {
           const unsigned char* src =
-              w + (static_cast<size_t>(kb) * N + n0) * L::ROW_CODE_BYTES;
+              w + (static_cast<size_t>(kb0 + kb) * N + n0) * L::ROW_CODE_BYTES;
           mbar_expect_tx(&c_full[s], rows_valid * L::ROW_CODE_BYTES);
           bulk_load(code_s + s * L::CODE_BYTES, src, rows_valid * L::ROW_CODE_BYTES, &c_full[s]);
         }
@@ -206,7 +211,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
         tc_commit(&a_empty[sa]);
         tc_commit(&b_empty[sb]);
       }
-      if (ok) tc_commit(tmem_full);
+      if (ok && kblocks > 0) tc_commit(tmem_full);
     }
   } else {
     const int t = threadIdx.x - 64;                     // 0..511
@@ -245,7 +250,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
         mbar_arrive(&b_full[s]);
       }
     }
-    if (ok) ok = mbar_wait(tmem_full, 0, status, STATUS_EPILOGUE_WAIT, 0);
+    if (ok && kblocks > 0) ok = mbar_wait(tmem_full, 0, status, STATUS_EPILOGUE_WAIT, 0);
     ok = __all_sync(0xffffffffu, ok);        // tcgen05.ld needs the whole warp
     if (ok) {
       tc_fence_after();
@@ -260,8 +265,24 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
         // gathered row scales were written by peers: read them past L1
         const float sa = m < m_limit ? (ag.tp > 0 ? __ldcg(a_scale + m) : a_scale[m]) : 0.f;
         uint32_t r[32];
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + mt * BN + c0, r);
-        tc_wait_ld();
+        if (kblocks > 0) {
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + mt * BN + c0, r);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0;           // an empty k range contributes zero
+        }
+        if (partial != nullptr) {
+          if (m < m_limit) {
+            int* dst = partial + (static_cast<size_t>(blockIdx.z) * M + m) * N + n0 + c0;
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              if (n0 + c0 + g * 4 + 4 <= N)
+                *reinterpret_cast<int4*>(dst + g * 4) =
+                    make_int4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+          }
+          continue;
+        }
         if (m < m_limit) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
@@ -307,14 +328,56 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
-  if (po.tp > 0) peer_signal_done(po, gridDim.x * gridDim.y);
+  if (po.tp > 0 && partial == nullptr) peer_signal_done(po, gridDim.x * gridDim.y);
+}
+
+// out[m][n] = (float(sum_z partial[z][m][n]) * w_scale[n]) * a_scale[m], as FP16 into `out`
+// or, with peers, into the inboxes (all ranks, or the row's owner when rows_per > 0).
+// One thread per 8 columns; the arithmetic is the GEMM epilogue's, so a split GEMM returns
+// bit for bit what the unsplit one does.
+__global__ void __launch_bounds__(256) splitk_finalize_kernel(
+    const int* __restrict__ partial, int splits, const float* __restrict__ a_scale,
+    const __half* __restrict__ w_scale, __half* __restrict__ out, int M, int N, PeerOut po,
+    int ag_scales) {
+  const int groups = N / 8;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx < static_cast<long long>(M) * groups) {
+    const int m = static_cast<int>(idx / groups), n = static_cast<int>(idx % groups) * 8;
+    int acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int z = 0; z < splits; ++z) {
+      const int4* src =
+          reinterpret_cast<const int4*>(partial + (static_cast<size_t>(z) * M + m) * N + n);
+      const int4 a = src[0], b = src[1];
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    const float sa = ag_scales ? __ldcg(a_scale + m) : a_scale[m];
+    __align__(16) __half h[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      h[j] = __float2half_rn((static_cast<float>(acc[j]) * __half2float(w_scale[n + j])) * sa);
+    if (po.tp > 0) {
+      const size_t off = (static_cast<size_t>(po.rank) * po.rows_cap + m) * N + n;
+      if (po.rows_per > 0) {
+        *reinterpret_cast<int4*>(po.inbox[min(m / po.rows_per, po.tp - 1)] + off) =
+            *reinterpret_cast<const int4*>(h);
+      } else {
+        for (int d = 0; d < po.tp; ++d)
+          *reinterpret_cast<int4*>(po.inbox[d] + off) = *reinterpret_cast<const int4*>(h);
+      }
+    } else {
+      *reinterpret_cast<int4*>(out + static_cast<size_t>(m) * N + n) =
+          *reinterpret_cast<const int4*>(h);
+    }
+  }
+  if (po.tp > 0) peer_signal_done(po, gridDim.x);
 }
 
 template <int FMT, bool OUT_F32, int MT, int NB>
 int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale, void* out,
            int M, int N, int K, cudaStream_t stream, const PeerOut& po,
            const GroupDesc& grp = GroupDesc{nullptr, nullptr, 0, 0}, int experts = 1,
-           int max_tiles = 0, const AgIn& ag = AgIn{nullptr, nullptr, 0, 0}) {
+           int max_tiles = 0, const AgIn& ag = AgIn{nullptr, nullptr, 0, 0}, int splits = 1) {
   using L = Layout<FMT, MT, NB>;
   CUtensorMap ta, tb;
   if (!make_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BM, BK)) return -3;
@@ -333,10 +396,17 @@ int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w
     if (e != cudaSuccess) return static_cast<int>(e);
     attr = true;
   }
-  dim3 grid((N + NB - 1) / NB, grp.tiles ? max_tiles : (M + BM * MT - 1) / (BM * MT));
+  dim3 grid((N + NB - 1) / NB, grp.tiles ? max_tiles : (M + BM * MT - 1) / (BM * MT), splits);
+  int* partial = splits > 1 ? runtime_splitk_workspace() : nullptr;
   qgemm_tc_kernel<FMT, OUT_F32, MT, NB><<<grid, THREADS, L::TOTAL, stream>>>(
       ta, tb, reinterpret_cast<const unsigned char*>(w), a_scale, w_scale, out, M, N, K,
-      runtime_e8p_tables(), runtime_status_ptr(), po, grp, ag);
+      runtime_e8p_tables(), runtime_status_ptr(), po, grp, ag, partial);
+  if (splits > 1) {
+    const long long items = static_cast<long long>(M) * (N / 8);
+    splitk_finalize_kernel<<<static_cast<unsigned>((items + 255) / 256), 256, 0, stream>>>(
+        partial, splits, a_scale, w_scale, reinterpret_cast<__half*>(out), M, N, po,
+        ag.tp > 0 ? 1 : 0);
+  }
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -344,6 +414,20 @@ int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w
 // then multiplied against up to 512 rows).  Weight rows per CTA: the widest tile that still
 // gives the grid about one CTA per SM, so narrow projections (N = hidden) do not leave most
 // of the machine idle.  FP32 output is only used by the (very wide) vocabulary head.
+inline int plan_splits(int M, int N, int K, int out_f32) {
+  const int mt = M > 2 * BM ? 4 : (M > BM ? 2 : 1);
+  const long c128 = static_cast<long>((M + BM * mt - 1) / (BM * mt)) * ((N + 127) / 128);
+  int splits = 1;
+  if (!out_f32 && c128 <= 74 && K / BK >= 8 && N % 8 == 0) {
+    splits = static_cast<int>(148 / c128);
+    splits = splits > K / BK / 8 ? K / BK / 8 : splits;          // at least 8 k-blocks each
+    splits = splits > 8 ? 8 : splits;
+    while (splits > 1 && static_cast<size_t>(splits) * M * N * 4 > SPLITK_WORKSPACE_BYTES)
+      --splits;
+  }
+  return splits < 1 ? 1 : splits;
+}
+
 template <int FMT>
 int launch_fmt(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale,
                void* out, int M, int N, int K, int out_f32, cudaStream_t stream,
@@ -352,10 +436,15 @@ int launch_fmt(const int8_t* a, const float* a_scale, const void* w, const __hal
   const int mt = M > 2 * BM ? 4 : (M > BM ? 2 : 1);
   const long mtiles = (M + BM * mt - 1) / (BM * mt);
   auto ctas = [&](int nb) { return mtiles * ((N + nb - 1) / nb); };
-  const int nb = (out_f32 || ctas(128) >= 120) ? 128 : (ctas(64) >= 120 ? 64 : 32);
+  // A projection too narrow to give every SM a CTA is split along K instead of into thinner
+  // weight tiles: thin tiles make every CTA stream the whole activation matrix, while K
+  // splits share it.  Partials are INT32, so the result does not depend on the split.
+  const long c128 = ctas(128);
+  const int splits = plan_splits(M, N, K, out_f32);
+  const int nb = (out_f32 || splits > 1 || c128 >= 120) ? 128 : (ctas(64) >= 120 ? 64 : 32);
 #define ORINFER_GO(F32, MTV, NBV)                                                              \
   return launch<FMT, F32, MTV, NBV>(a, a_scale, w, w_scale, out, M, N, K, stream, po, none, 1, \
-                                    0, ag)
+                                    0, ag, splits)
   if (out_f32) {
     if (mt == 4) ORINFER_GO(true, 4, 128);
     if (mt == 2) ORINFER_GO(true, 2, 128);
@@ -410,6 +499,12 @@ static int qgemm_any(int fmt, const int8_t* a, const float* a_scale, const void*
   if (fmt == 1)
     return tc::launch_fmt<1>(a, a_scale, w, w_scale, out, M, N, K, out_f32, stream, po);
   return tc::launch_fmt<2>(a, a_scale, w, w_scale, out, M, N, K, out_f32, stream, po);
+}
+
+// Number of kernel launches orinfer_qgemm makes for this shape (1, or 2 with split-K).
+extern "C" int orinfer_qgemm_launches(int M, int N, int K, int out_f32, int force_path) {
+  if (force_path == 1 || (force_path == 0 && M <= 8)) return (M + 7) / 8;
+  return tc::plan_splits(M, N, K, out_f32) > 1 ? 2 : 1;
 }
 
 extern "C" int orinfer_qgemm(int fmt, const int8_t* a, const float* a_scale, const void* w,

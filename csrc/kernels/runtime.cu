@@ -18,6 +18,7 @@ int* g_status = nullptr;
 E8pTables* g_tables = nullptr;
 PFN_encodeTiled g_encode = nullptr;
 int8_t g_basis[256][8];
+int* g_splitk = nullptr;
 
 uint32_t pack4(int a, int b, int c, int d) {
   return (static_cast<uint32_t>(a & 0xff)) | (static_cast<uint32_t>(b & 0xff) << 8) |
@@ -44,6 +45,8 @@ cudaError_t runtime_ensure_init() {
   if (e != cudaSuccess) return e;
   e = cudaMemcpy(g_tables, &host, sizeof(E8pTables), cudaMemcpyHostToDevice);
   if (e != cudaSuccess) return e;
+  e = cudaMalloc(&g_splitk, SPLITK_WORKSPACE_BYTES);
+  if (e != cudaSuccess) return e;
   void* fn = nullptr;
   cudaDriverEntryPointQueryResult qres;
   e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
@@ -55,6 +58,7 @@ cudaError_t runtime_ensure_init() {
 }
 
 int* runtime_status_ptr() { return g_status; }
+int* runtime_splitk_workspace() { return g_splitk; }
 const E8pTables* runtime_e8p_tables() { return g_tables; }
 PFN_encodeTiled runtime_tma_encoder() { return g_encode; }
 

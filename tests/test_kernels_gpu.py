@@ -98,6 +98,8 @@ def _rand_weight(fmt, n, k, dev, seed):
     # tile variants: 4 / 2 / 1 accumulators x 128 / 64 / 32 weight rows per CTA, ragged N
     (600, 19456, 256, 0), (1000, 6400, 128, 0), (250, 12800, 128, 0), (100, 12800, 256, 0),
     (700, 8200, 256, 0), (50, 1000, 128, 0), (513, 2560, 1024, 0),
+    # split-K (narrow N, long K): INT32 partials + finalize must equal the unsplit result
+    (512, 2560, 9728, 0), (100, 2560, 4096, 0), (300, 1024, 2560, 0), (512, 6144, 2560, 0),
 ])
 def test_qgemm(cuda, fmt, m, n, k, path):
     from orinfer_b200.ops import functional as F
