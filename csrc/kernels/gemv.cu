@@ -44,6 +44,69 @@ __device__ __forceinline__ void store_row(void* out, int out_f32, int m, int n, 
 // 2 lanes).  CTAs are persistent over row groups (decode tables and activations are staged
 // once); inside a group the 8 warps split the k-blocks, and every lane keeps DEPTH 16-byte
 // code loads of the next batch in flight while it decodes the current one.
+// Decode tables replicated COPIES times with the copies interleaved word by word, so that
+// lane l always reads copy l % COPIES.  The lookups of a warp are random in the entry index;
+// with one copy they collide on the 32 banks about 3.5-fold, which made the kernel
+// shared-memory bound.  With 16 interleaved copies only the two lanes sharing a copy can
+// collide (entry parity equal), so a lookup costs ~1.5 wavefronts instead of ~3.5.
+// A single row (MT = 1) keeps one copy: its launch is so short that filling 48 KiB of tables
+// per CTA costs more than the conflicts it removes (measured: 19.9 us vs 22.2 us at
+// N = 19456, K = 2560), while 8 rows gain 20 % (38 us -> 30 us).
+template <int COPIES>
+struct E8pBanked {
+  uint32_t posx[256 * COPIES], posy[256 * COPIES], sel[256 * COPIES];
+};
+
+template <int COPIES>
+__device__ __forceinline__ void banked_init(E8pBanked<COPIES>* sm,
+                                            const E8pTables* __restrict__ g, int tid,
+                                            int nthreads) {
+  for (int j = tid; j < 256 * COPIES; j += nthreads) {
+    const int i = j / COPIES;
+    const uint2 p = g->pos[i];
+    sm->posx[j] = p.x;
+    sm->posy[j] = p.y;
+    const uint32_t t = static_cast<uint32_t>(i) ^ (__popc(i) & 1u), t2 = t >> 2;
+    const uint32_t lo = 0x3210u | ((t & 0x11u) << 2) | ((t & 0x22u) << 9);
+    const uint32_t hi = 0x3210u | ((t2 & 0x11u) << 2) | ((t2 & 0x22u) << 9);
+    sm->sel[j] = lo | (hi << 16);
+  }
+}
+
+template <int COPIES>
+__device__ __forceinline__ void banked_select(uint32_t code,
+                                              const E8pBanked<COPIES>* __restrict__ sm, int copy,
+                                              uint32_t& lo, uint32_t& hi, uint32_t& par) {
+  const uint32_t s = code & 0xffu;
+  par = __popc(s) & 1u;
+  const uint32_t at = ((code >> 8) & 0xffu) * COPIES + copy;
+  const uint32_t ex = sm->posx[at], ey = sm->posy[at];
+  const uint32_t sl = sm->sel[s * COPIES + copy];
+  lo = __byte_perm(ex, 0x30303030u - ex, sl);
+  hi = __byte_perm(ey, 0x30303030u - ey, sl >> 16);
+}
+
+template <int COPIES>
+__device__ __forceinline__ uint2 banked_decode8(uint32_t code,
+                                                const E8pBanked<COPIES>* __restrict__ sm,
+                                                int copy) {
+  uint32_t lo, hi, par;
+  banked_select(code, sm, copy, lo, hi, par);
+  const uint32_t cw = 0x69696969u - par * 0x02020202u;
+  return make_uint2((lo + cw) ^ 0x80808080u, (hi + cw) ^ 0x80808080u);
+}
+
+template <int COPIES>
+__device__ __forceinline__ uint2 banked_decode_q4(uint32_t word,
+                                                  const E8pBanked<COPIES>* __restrict__ sm,
+                                                  int copy) {
+  uint32_t l0, h0, p0, l1, h1, p1;
+  banked_select(word & 0xffffu, sm, copy, l0, h0, p0);
+  banked_select(word >> 16, sm, copy, l1, h1, p1);
+  const uint32_t cw = 0x0d0d0d0du - p0 * 0x08080808u - p1 * 0x02020202u;
+  return make_uint2(((l0 << 2) + l1 + cw) ^ 0x80808080u, ((h0 << 2) + h1 + cw) ^ 0x80808080u);
+}
+
 template <int FMT, int MT>
 __global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
     const int8_t* __restrict__ a, const float* __restrict__ a_scale, const uint4* __restrict__ w,
@@ -55,11 +118,14 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
   constexpr int DEPTH = 4;
   const PeerOut* peer = po.tp > 0 ? &po : nullptr;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  E8pSmem* table = reinterpret_cast<E8pSmem*>(smem_raw);
-  int8_t* act = reinterpret_cast<int8_t*>(smem_raw) + 4096;
+  constexpr int COPIES = MT == 1 ? 1 : 16;
+  using Table = E8pBanked<COPIES>;
+  Table* table = reinterpret_cast<Table*>(smem_raw);
+  int8_t* act = reinterpret_cast<int8_t*>(smem_raw) + sizeof(Table);
   __shared__ int red[2][GEMV_WARPS][ROWS][MT];
 
-  e8p_smem_init(table, tables, threadIdx.x, blockDim.x);
+  banked_init(table, tables, threadIdx.x, blockDim.x);
+  const int copy = threadIdx.x & (COPIES - 1);
   stage_activations<MT>(act, a, M, K);
   __syncthreads();
 
@@ -101,7 +167,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
         if (FMT == 1) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const uint2 q = e8p_decode_q4(words[j], table);
+            const uint2 q = banked_decode_q4(words[j], table, copy);
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
               const int2 av = *reinterpret_cast<const int2*>(abase + m * K + j * 8);
@@ -113,7 +179,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const uint32_t code = (words[j >> 1] >> ((j & 1) * 16)) & 0xffffu;
-            const uint2 q = e8p_decode8(code, table);
+            const uint2 q = banked_decode8(code, table, copy);
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
               const int2 av = *reinterpret_cast<const int2*>(abase + m * K + j * 8);
@@ -201,7 +267,7 @@ template <int FMT, int MT>
 static int launch_e8p(const int8_t* a, const float* as, const void* w, const __half* ws, void* out,
                       int M, int N, int K, int out_f32, cudaStream_t stream, const PeerOut& po) {
   constexpr int ROWS = FMT == 1 ? 8 : 16;
-  const size_t smem = 4096 + static_cast<size_t>(MT) * K;
+  const size_t smem = sizeof(E8pBanked<(MT == 1 ? 1 : 16)>) + static_cast<size_t>(MT) * K;
   if (smem > 200 * 1024) return -1;
   static bool attr = false;
   if (!attr) {
@@ -210,7 +276,7 @@ static int launch_e8p(const int8_t* a, const float* as, const void* w, const __h
     attr = true;
   }
   const int groups = (N + ROWS - 1) / ROWS;
-  const int per_sm = smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4);
+  const int per_sm = smem > 110 * 1024 ? 1 : (smem > 72 * 1024 ? 2 : (smem > 54 * 1024 ? 3 : 4));
   const int grid = groups < 148 * per_sm ? groups : 148 * per_sm;
   e8p_gemv_kernel<FMT, MT><<<grid, GEMV_WARPS * 32, smem, stream>>>(
       a, as, reinterpret_cast<const uint4*>(w), ws, out, M, N, K, out_f32, runtime_e8p_tables(),
