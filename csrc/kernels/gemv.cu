@@ -201,14 +201,38 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
       }
       __syncthreads();
       const int n0 = g * ROWS;
-      for (int i = threadIdx.x; i < ROWS * MT; i += blockDim.x) {
-        const int r = i / MT, m = i % MT;
-        if (n0 + r < N && m < M) {
-          int total = 0;
+      if (peer != nullptr && n0 + ROWS <= N) {
+        // peers get whole 16-byte segments (8 consecutive outputs of one row per store):
+        // 2-byte remote stores would each become their own NVLink write
+        for (int i = threadIdx.x; i < (ROWS / 8) * MT; i += blockDim.x) {
+          const int m = i % MT, seg = i / MT;
+          if (m < M) {
+            __align__(16) __half h[8];
+            const float sa = a_scale[m];
 #pragma unroll
-          for (int wv = 0; wv < GEMV_WARPS; ++wv) total += red[parity][wv][r][m];
-          store_row<MT>(out, out_f32, m, n0 + r, N, total, __half2float(w_scale[n0 + r]),
-                        a_scale[m], peer);
+            for (int r = 0; r < 8; ++r) {
+              int total = 0;
+#pragma unroll
+              for (int wv = 0; wv < GEMV_WARPS; ++wv) total += red[parity][wv][seg * 8 + r][m];
+              h[r] = __float2half_rn(
+                  (static_cast<float>(total) * __half2float(w_scale[n0 + seg * 8 + r])) * sa);
+            }
+            const size_t off =
+                (static_cast<size_t>(po.rank) * po.rows_cap + m) * N + n0 + seg * 8;
+            for (int d = 0; d < po.tp; ++d)
+              *reinterpret_cast<int4*>(po.inbox[d] + off) = *reinterpret_cast<const int4*>(h);
+          }
+        }
+      } else {
+        for (int i = threadIdx.x; i < ROWS * MT; i += blockDim.x) {
+          const int r = i / MT, m = i % MT;
+          if (n0 + r < N && m < M) {
+            int total = 0;
+#pragma unroll
+            for (int wv = 0; wv < GEMV_WARPS; ++wv) total += red[parity][wv][r][m];
+            store_row<MT>(out, out_f32, m, n0 + r, N, total, __half2float(w_scale[n0 + r]),
+                          a_scale[m], peer);
+          }
         }
       }
       parity ^= 1;
