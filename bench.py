@@ -125,7 +125,7 @@ def main() -> int:
         weights = shard_model(random_model(cfg, seed=0, device=dev), rank, world)
     else:
         weights = random_model(cfg, seed=0, device=dev)
-    load = LoadOptions(cuda_graph=GraphMode.DECODE_ONLY, prefix_cache_bytes=0, tp=world)
+    load = LoadOptions(cuda_graph=GraphMode.FULL, prefix_cache_bytes=0, tp=world)
     sched = SchedulerOptions(max_active=128, prefill_chunk=8192)
     engine = Engine(weights, load=load, sched=sched, kv_pages=128 * 6 + 80, max_context=8192 + 512,
                     max_rows=8192 + 128)
@@ -157,14 +157,20 @@ def main() -> int:
                                   n_tokens, n_tokens, torch.tensor([n_tokens - 1], device=dev),
                                   chunks=torch.tensor([[0, n_tokens, 0, 0]], dtype=torch.int32,
                                                       device=dev), max_q_len=n_tokens))
+        def run(p):
+            # the engine's own full-graph path: a prefill geometry is captured at its second
+            # use and replayed afterwards (inputs are copied into the graph's static buffers)
+            if engine._prefill_graph(p, (n_tokens,), False) is None:
+                runner.greedy(p)
+
         for p in packets[:warmup]:
-            runner.greedy(p)
+            run(p)
         barrier()
         l0 = native.launches()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for p in packets[warmup:]:
-            runner.greedy(p)
+            run(p)
         b.record()
         barrier()
         return max_over_ranks(a.elapsed_time(b)) / steps, (native.launches() - l0)
@@ -247,7 +253,7 @@ def main() -> int:
                        "parallelism": f"tp{world}",
                        "l2": "inputs larger than L2: every step streams 2.2 GB of packed "
                              "weights and a fresh prompt",
-                       "kv": "int8 group-64, paged"},
+                       "kv": "int8 group-64, paged", "cuda_graph": "full"},
             "e2e": {"value": round(PROMPT / ms_e2e * 1e3, 1), "unit": "tok/s",
                     "h2d_bytes_per_step": 3 * PROMPT * 4 + 8 + engine.max_pages_per_req * 4,
                     "d2h_bytes_per_step": 4,

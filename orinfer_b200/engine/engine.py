@@ -499,7 +499,13 @@ class Engine:
         t1 = time.monotonic()
         self.stats.batch_inputs_s += t1 - t0
         need = any(not self._plain(r) for r, _n, has in order if has)
-        tok, lg = self.runner.greedy(packet, need_logits=need)
+        graphed = None
+        if (self.on_gpu and n_decode == 0 and chunk_rows and not self.recurrent
+                and self.cfg.head_dim in (64, 128)
+                and self.load.cuda_graph.uses_graph(ExecPhase.PREFILL)):
+            graphed = self._prefill_graph(packet, tuple(c[1] for c in chunk_rows), need)
+        tok, lg = graphed if graphed is not None else self.runner.greedy(packet,
+                                                                         need_logits=need)
         tokens = tok.cpu()                           # one readback (synchronises)
         if self.spec.enabled and self.runner_has_mtp():
             info, row0 = [], 0
@@ -513,6 +519,53 @@ class Engine:
         if dummy_logits:
             return None, None, order
         return tokens, lg, order
+
+    PREFILL_GRAPHS = 16
+
+    def _prefill_graph(self, packet: Packet, chunk_lens: tuple, need: bool):
+        """Full-graph mode: a pure-prefill packet is replayed from a graph keyed by its launch
+        geometry (chunk lengths, selected rows); token ids, positions, page-table rows and
+        chunk offsets are data in static buffers.  A geometry is captured at its second use;
+        the least recently used of PREFILL_GRAPHS entries is dropped.  Returns (tokens,
+        logits) or None when this packet ran (or must run) directly."""
+        n_sel = packet.logit_rows.shape[0]
+        key = (chunk_lens, n_sel, need)
+        cache = self.__dict__.setdefault("_prefill_graphs", {})
+        e = cache.pop(key, None)
+        if e is None:
+            while len(cache) >= self.PREFILL_GRAPHS:
+                cache.pop(next(iter(cache)))
+            cache[key] = {"trials": 1}
+            return None
+        cache[key] = e                               # most recently used goes last
+        if "graph" not in e:
+            e["trials"] += 1
+            if e["trials"] < 2:
+                return None
+            st = Packet(packet.ids.clone(), packet.row_req.clone(), packet.row_pos.clone(),
+                        self.page_table_dev, packet.rows, packet.max_kv_len,
+                        packet.logit_rows.clone(), chunks=packet.chunks.clone(),
+                        max_q_len=packet.max_q_len, decode_rows=0)
+            self.runner.greedy(st, need_logits=need)                 # warm outside capture
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            from ..ops import native
+            before = native.launches()
+            with torch.cuda.graph(graph):
+                tok, lg = self.runner.greedy(st, need_logits=need)
+            e.update(graph=graph, packet=st, tok=tok, lg=lg, launches=native.launches() - before)
+            self.stats.graph_captures += 1
+        st = e["packet"]
+        st.ids.copy_(packet.ids, non_blocking=True)
+        st.row_req.copy_(packet.row_req, non_blocking=True)
+        st.row_pos.copy_(packet.row_pos, non_blocking=True)
+        st.logit_rows.copy_(packet.logit_rows, non_blocking=True)
+        st.chunks.copy_(packet.chunks, non_blocking=True)
+        e["graph"].replay()
+        from ..ops import native
+        native.count_launches(e["launches"])         # kernels the replay launches
+        self.stats.graph_hits += 1
+        return e["tok"], e["lg"]
 
     def _run_decode_graph(self, decoders: List[Request]):
         t0 = time.monotonic()
@@ -537,13 +590,18 @@ class Engine:
             if g.trials >= 2:
                 torch.cuda.synchronize()
                 graph = torch.cuda.CUDAGraph()
+                from ..ops import native
+                before = native.launches()
                 with torch.cuda.graph(graph):
                     self.runner.greedy(g.packet, g.logits, g.tokens, need_logits=need)
                 g.graph = graph
+                g.launches = native.launches() - before
                 self.stats.graph_captures += 1
                 self.stats.capture_s += time.monotonic() - t1
         else:
             g.graph.replay()
+            from ..ops import native
+            native.count_launches(getattr(g, "launches", 0))
             self.stats.graph_hits += 1
         tokens = g.tokens[:n].cpu()
         if self.spec.enabled and self.runner_has_mtp():

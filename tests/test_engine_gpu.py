@@ -34,6 +34,20 @@ def test_graph_modes_agree_and_replay_changed_inputs(cuda):
     assert eng.generate(more, max_new=12) == _engine(w, GraphMode.OFF).generate(more, max_new=12)
 
 
+def test_full_graph_mode_replays_prefill_geometries(cuda):
+    """FULL mode: a prefill geometry is captured at its second use and replayed with new
+    token ids; outputs equal the graph-free engine."""
+    w = random_model(PRESETS["tiny"], seed=0).to(cuda)
+    prompts = _prompts(5, 150, seed=21)
+    off = [_engine(w, GraphMode.OFF).generate([p], max_new=6)[0] for p in prompts]
+    eng = _engine(w, GraphMode.FULL)
+    on = [eng.generate([p], max_new=6)[0] for p in prompts]
+    assert on == off
+    assert len(eng._prefill_graphs) == 1 and eng.stats.graph_hits >= 3 + 5 * 3
+    other = _prompts(1, 77, seed=22)                      # a new geometry runs direct first
+    assert eng.generate(other, max_new=4) == _engine(w, GraphMode.OFF).generate(other, max_new=4)
+
+
 def test_batch_invariance_and_chunked_prefill(cuda):
     w = random_model(PRESETS["tiny"], seed=1).to(cuda)
     prompts = _prompts(4, 150, seed=2)
