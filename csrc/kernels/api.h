@@ -154,6 +154,36 @@ int orinfer_attention_prefill(const __half* q, const __half* gate, const int* ch
                               const __half* vscale, __half* out, int qh, int kvh, int head_dim,
                               int num_pages, cudaStream_t stream);
 
+// ---- expert-parallel all-to-alls over peer memory (moe_a2a.cu); cap = owned rows x top_k
+typedef struct OrinferA2aDispatch {
+  void* rows[8];               // every rank's receive buffer: int8 [tp][cap][K]
+  float* scale[8];             // fp32 [tp][cap]
+  int* expert[8];              // int32 [tp][cap]
+  int* header[8];              // int32 [tp][2] = (count, base slot at the sender)
+  int* flag[8];                // int32 [tp]
+  int* sent;                   // local sequence counter
+  unsigned int* ticket;        // local CTA counter
+  int tp, rank, cap;
+} OrinferA2aDispatch;
+
+typedef struct OrinferA2aReturn {
+  void* ret[8];                // every rank's return buffer: fp16 [cap][H]
+  int* flag[8];
+  int* sent;
+  unsigned int* ticket;
+  int tp, rank, cap;
+} OrinferA2aReturn;
+
+int orinfer_a2a_dispatch_push(const int* ids, const int* slots, const int* offsets,
+                              const int8_t* q8, const float* scale, int rows, int top_k, int K,
+                              int experts_per_rank, const OrinferA2aDispatch* d,
+                              cudaStream_t stream);
+int orinfer_a2a_recv_prepare(const int* flag, const int* sent, const int* header, int* expert,
+                             int tp, int cap, cudaStream_t stream);
+int orinfer_a2a_return_push(const __half* down, const int* slots, const int* header, int H,
+                            const OrinferA2aReturn* r, cudaStream_t stream);
+int orinfer_a2a_wait(const int* flag, const int* sent, int tp, cudaStream_t stream);
+
 // ---- gated-delta-rule linear attention (segments: int32 [n,4] = first row, rows, 0, 0;
 // the state slot of a row is row_slot[row]; a segment starting at position 0 starts fresh)
 int orinfer_small_proj(const __half* x, const __half* w, float* out, int rows, int hidden, int n,
