@@ -61,7 +61,11 @@ typedef struct OrinferInbox {
 // activation buffer and publish the all-gather flag.
 int orinfer_act_prep_sp(const OrinferInbox* inbox, const OrinferAgOut* ag, float* resid,
                         const __half* norm_w, const int8_t* signs, int rows, int K, float eps,
-                        int zero_centered, cudaStream_t stream);
+                        int zero_centered, cudaStream_t stream, const __half* x);
+int orinfer_act_prep_inbox_rows(const OrinferInbox* inbox, float* resid, const __half* norm_w,
+                                const int8_t* signs, int8_t* q_out, float* scale_out,
+                                __half* y_out, int row_base, int count, int K, float eps,
+                                int zero_centered, cudaStream_t stream);
 // Column-parallel GEMM whose A operand (and row scales) is the all-gathered activation
 // buffer: waits per M tile for the source ranks' flags before loading.
 int orinfer_qgemm_ag(int fmt, const int8_t* a, const float* a_scale, const void* w,
@@ -71,6 +75,9 @@ int orinfer_qgemm_ag(int fmt, const int8_t* a, const float* a_scale, const void*
 // may then read the activation buffer with ordinary loads.
 int orinfer_ag_wait(const OrinferAgIn* ag, int rows, cudaStream_t stream);
 
+int orinfer_act_prep_limited(const __half* x, const int8_t* signs, int8_t* q_out,
+                             float* scale_out, int rows, int K, int swiglu, const int* row_limit,
+                             cudaStream_t stream);
 int orinfer_act_prep_inbox(const OrinferInbox* inbox, float* resid, const __half* norm_w,
                            const int8_t* signs, int8_t* q_out, float* scale_out, __half* y_out,
                            int rows, int K, float eps, int zero_centered, cudaStream_t stream);

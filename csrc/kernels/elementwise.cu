@@ -56,18 +56,21 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
     const __half* __restrict__ x, float* __restrict__ resid, const __half* __restrict__ norm_w,
     const int8_t* __restrict__ signs, int8_t* __restrict__ q_out, float* __restrict__ scale_out,
     __half* __restrict__ y_out, int K, float eps, int zero_centered, InboxIn in, int* status,
-    AgOut ag, int rows) {
+    AgOut ag, int rows, const int* __restrict__ row_limit, int row_base) {
   extern __shared__ float rowbuf[];
   __shared__ float red[32];
   const int tid = threadIdx.x;
   // sequence-parallel form: this rank handles only the rows it owns and pushes the result
   const bool sp = !SWIGLU && ag.tp > 0;
-  const int row = sp ? ag.rank * ag.rows_per + blockIdx.x : blockIdx.x;
+  const int row = (sp ? ag.rank * ag.rows_per : row_base) + blockIdx.x;
   if (sp && row >= rows) {                 // tail of the last owner: nothing to do but count
-    inbox_consumed(in, gridDim.x);
+    if (in.inbox != nullptr) inbox_consumed(in, gridDim.x);
     ag_signal_done(ag, gridDim.x);
     return;
   }
+  // a device-side row count (rows routed to this rank's experts) bounds the useful work of a
+  // launch that was sized for the worst case
+  if (row_limit != nullptr && row >= *row_limit) return;
   float sumsq = 0.f;
   if (SWIGLU) {
     const __half* g = x + static_cast<size_t>(row) * 2 * K;
@@ -199,7 +202,7 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
         *reinterpret_cast<int4*>(ag.q[d] + static_cast<size_t>(row) * K + i) =
             *reinterpret_cast<const int4*>(c);
     }
-    inbox_consumed(in, gridDim.x);
+    if (in.inbox != nullptr) inbox_consumed(in, gridDim.x);
     ag_signal_done(ag, gridDim.x);
     return;
   }
@@ -363,7 +366,8 @@ using namespace orinfer;
 static int act_prep_launch(const __half* x, float* resid, const __half* norm_w, const int8_t* signs,
                            int8_t* q_out, float* scale_out, __half* y_out, int rows, int K,
                            float eps, int zero_centered, int swiglu, InboxIn in,
-                           cudaStream_t stream, AgOut ag = AgOut{});
+                           cudaStream_t stream, AgOut ag = AgOut{},
+                           const int* row_limit = nullptr, int row_base = 0);
 
 extern "C" {
 
@@ -385,6 +389,16 @@ int orinfer_act_prep(const __half* x, float* resid, const __half* norm_w, const 
                          zero_centered, swiglu, none, stream);
 }
 
+// Same as orinfer_act_prep for a launch sized for the worst case: rows at or beyond the
+// device-side count *row_limit are skipped.
+int orinfer_act_prep_limited(const __half* x, const int8_t* signs, int8_t* q_out,
+                             float* scale_out, int rows, int K, int swiglu, const int* row_limit,
+                             cudaStream_t stream) {
+  InboxIn none{};
+  return act_prep_launch(x, nullptr, nullptr, signs, q_out, scale_out, nullptr, rows, K, 1e-6f, 0,
+                         swiglu, none, stream, AgOut{}, row_limit);
+}
+
 // Same, but the branch input is the sum of the tp partial rows in the local inbox.
 int orinfer_act_prep_inbox(const OrinferInbox* inbox, float* resid, const __half* norm_w,
                            const int8_t* signs, int8_t* q_out, float* scale_out, __half* y_out,
@@ -401,12 +415,15 @@ int orinfer_act_prep_inbox(const OrinferInbox* inbox, float* resid, const __half
                          zero_centered, 0, in, stream);
 }
 
-int orinfer_act_prep_sp(const OrinferInbox* inbox, const OrinferAgOut* agp, float* resid,
-                        const __half* norm_w, const int8_t* signs, int rows, int K, float eps,
-                        int zero_centered, cudaStream_t stream) {
-  if (inbox == nullptr || agp == nullptr || inbox->tp < 1 || inbox->tp > TP_MAX ||
-      agp->tp != inbox->tp || rows > inbox->rows_cap || agp->rows_per < 1 || K % 16 ||
-      static_cast<long long>(agp->rows_per) * agp->tp < rows)
+// Rows [row_base, row_base + count) only (the rows this rank owns after a reduce-scatter):
+// sums the tp partial rows, adds the residual, normalises, rotates and quantises into the
+// LOCAL buffers at the same row indices.  Every CTA still takes part in the inbox hand-shake.
+int orinfer_act_prep_inbox_rows(const OrinferInbox* inbox, float* resid, const __half* norm_w,
+                                const int8_t* signs, int8_t* q_out, float* scale_out,
+                                __half* y_out, int row_base, int count, int K, float eps,
+                                int zero_centered, cudaStream_t stream) {
+  if (inbox == nullptr || inbox->tp < 1 || inbox->tp > TP_MAX || row_base < 0 || count < 1 ||
+      row_base + count > inbox->rows_cap)
     return -1;
   InboxIn in;
   in.inbox = reinterpret_cast<const __half*>(inbox->inbox);
@@ -415,6 +432,29 @@ int orinfer_act_prep_sp(const OrinferInbox* inbox, const OrinferAgOut* agp, floa
   in.ticket = inbox->ticket;
   in.tp = inbox->tp;
   in.rows_cap = inbox->rows_cap;
+  return act_prep_launch(nullptr, resid, norm_w, signs, q_out, scale_out, y_out, count, K, eps,
+                         zero_centered, 0, in, stream, AgOut{}, nullptr, row_base);
+}
+
+// inbox == nullptr: the branch output of the owned rows is the local matrix x (indexed by
+// global row), e.g. the combined expert output of a token-sharded MoE layer.
+int orinfer_act_prep_sp(const OrinferInbox* inbox, const OrinferAgOut* agp, float* resid,
+                        const __half* norm_w, const int8_t* signs, int rows, int K, float eps,
+                        int zero_centered, cudaStream_t stream, const __half* x) {
+  if (agp == nullptr || agp->tp < 1 || agp->tp > TP_MAX || agp->rows_per < 1 || K % 16 ||
+      static_cast<long long>(agp->rows_per) * agp->tp < rows)
+    return -1;
+  if (inbox == nullptr && x == nullptr) return -1;
+  if (inbox != nullptr && (agp->tp != inbox->tp || rows > inbox->rows_cap)) return -1;
+  InboxIn in{};
+  if (inbox != nullptr) {
+    in.inbox = reinterpret_cast<const __half*>(inbox->inbox);
+    in.flag = inbox->flag;
+    in.seen = inbox->seen;
+    in.ticket = inbox->ticket;
+    in.tp = inbox->tp;
+    in.rows_cap = inbox->rows_cap;
+  }
   AgOut ag;
   for (int i = 0; i < TP_MAX; ++i) {
     ag.q[i] = reinterpret_cast<int8_t*>(agp->q[i]);
@@ -426,8 +466,8 @@ int orinfer_act_prep_sp(const OrinferInbox* inbox, const OrinferAgOut* agp, floa
   ag.tp = agp->tp;
   ag.rank = agp->rank;
   ag.rows_per = agp->rows_per;
-  return act_prep_launch(nullptr, resid, norm_w, signs, nullptr, nullptr, nullptr, rows, K, eps,
-                         zero_centered, 0, in, stream, ag);
+  return act_prep_launch(inbox != nullptr ? nullptr : x, resid, norm_w, signs, nullptr, nullptr,
+                         nullptr, rows, K, eps, zero_centered, 0, in, stream, ag);
 }
 
 int orinfer_ag_wait(const OrinferAgIn* agp, int rows, cudaStream_t stream) {
@@ -443,7 +483,7 @@ int orinfer_ag_wait(const OrinferAgIn* agp, int rows, cudaStream_t stream) {
 static int act_prep_launch(const __half* x, float* resid, const __half* norm_w, const int8_t* signs,
                            int8_t* q_out, float* scale_out, __half* y_out, int rows, int K,
                            float eps, int zero_centered, int swiglu, InboxIn in,
-                           cudaStream_t stream, AgOut ag) {
+                           cudaStream_t stream, AgOut ag, const int* row_limit, int row_base) {
   if (rows <= 0) return 0;
   if (runtime_ensure_init() != cudaSuccess) return -2;
   int* status = runtime_status_ptr();
@@ -461,11 +501,11 @@ static int act_prep_launch(const __half* x, float* resid, const __half* norm_w, 
   if (swiglu)
     act_prep_kernel<true><<<rows, 256, smem, stream>>>(x, nullptr, nullptr, signs, q_out,
                                                        scale_out, y_out, K, eps, zero_centered,
-                                                       in, status, AgOut{}, rows);
+                                                       in, status, AgOut{}, rows, row_limit, 0);
   else
     act_prep_kernel<false><<<ag.tp > 0 ? ag.rows_per : rows, 256, smem, stream>>>(
         x, resid, norm_w, signs, q_out, scale_out, y_out, K, eps, zero_centered, in, status, ag,
-        rows);
+        rows, row_limit, row_base);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -88,6 +88,13 @@ class Workspace:
 
     SPLIT_ROWS = 512
 
+    def scale_alt(self, rows: int) -> torch.Tensor:
+        """A second row-scale buffer, for a quantisation whose input scales are still live."""
+        if getattr(self, "_scale_alt", None) is None:
+            self._scale_alt = torch.empty(self.max_rows, dtype=torch.float32,
+                                          device=self.hidden.device)
+        return self._scale_alt
+
     def attn_norm(self, rows: int, hidden: int) -> torch.Tensor:
         """fp16 scratch [max_rows, hidden] for normalised hidden states (final norm)."""
         if getattr(self, "_norm_buf", None) is None:
@@ -310,12 +317,14 @@ class ModelRunner:
         total = rows * cfg.top_k
         F.qgemm_grouped(sc.q8, sc.scale, bank_up.codes, bank_up.scale, bank_up.fmt, 2 * f,
                         sc.gate_up, sc, total)
-        F.act_prep(sc.gate_up, None, None, bank_dn.signs, swiglu=True, rows=total,
-                   q_out=sc.q8_mid, scale_out=sc.scale_mid)
+        # offsets[n_local_experts] = rows actually routed to this rank's experts
+        F.act_prep_limited(sc.gate_up, bank_dn.signs, sc.offsets[bank_up.experts:], swiglu=True,
+                           rows=total, q_out=sc.q8_mid, scale_out=sc.scale_mid)
         F.qgemm_grouped(sc.q8_mid, sc.scale_mid, bank_dn.codes, bank_dn.scale, bank_dn.fmt, h,
                         sc.down, sc, total)
         shared = None
-        if lw.shared_gate_up is not None:
+        tp = getattr(self.w, "tp", None)
+        if lw.shared_gate_up is not None and (tp is None or lw.shared_owner in (-1, tp.rank)):
             fs = lw.shared_gate_up.n // 2
             gu = self._linear(lw.shared_gate_up, q8, s8, rows,
                               ws.gate_up.view(-1)[: ws.max_rows * 2 * fs].view(ws.max_rows, 2 * fs))

@@ -143,6 +143,8 @@ class TorchRunner:
             y = R.rms_norm(resid, lw.post_norm, cfg.eps, zc)
             if cfg.experts:
                 from ..ref.cpu_forward import moe_ffn
+                tp = getattr(self.w, "tp", None)       # replicated shared expert: owner adds it
+                lw._add_shared = tp is None or lw.shared_owner in (-1, tp.rank)
                 x = self._reduce(moe_ffn(cfg, lw, y, True))
             else:
                 x = self._ffn(lw, y)

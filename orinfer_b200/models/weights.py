@@ -138,6 +138,7 @@ class LayerWeights:
     expert_down: Optional[ExpertBank] = None
     shared_gate_up: Optional[QLinear] = None
     shared_down: Optional[QLinear] = None
+    shared_owner: int = -1                        # rank adding the shared expert (-1: every rank)
 
     def to(self, device) -> "LayerWeights":
         out = {}

@@ -59,6 +59,21 @@ def act_prep(x: Optional[torch.Tensor], resid: Optional[torch.Tensor],
     return q_out, scale_out
 
 
+def act_prep_limited(x: torch.Tensor, signs: Optional[torch.Tensor], row_limit: torch.Tensor, *,
+                     swiglu: bool, rows: int, q_out: torch.Tensor,
+                     scale_out: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``act_prep`` (no residual / norm) for a launch sized for the worst case: only rows below
+    the device-side count ``row_limit[0]`` are processed."""
+    _cuda(x, signs, row_limit)
+    k = x.shape[1] // 2 if swiglu else x.shape[1]
+    assert x.dtype == torch.float16 and x.is_contiguous() and row_limit.dtype == torch.int32
+    check(native.lib().orinfer_act_prep_limited(ptr(x), ptr(signs), ptr(q_out), ptr(scale_out),
+                                                rows, k, int(swiglu), ptr(row_limit), stream()),
+          "act_prep_limited")
+    count_launches(1)
+    return q_out, scale_out
+
+
 def rope_table(positions: torch.Tensor, head_dim: int, theta: float,
                cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
                rows: Optional[int] = None):

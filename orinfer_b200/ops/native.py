@@ -58,6 +58,7 @@ def _load() -> ctypes.CDLL:
         "orinfer_moe_dispatch_ep": ([P, I, I, I, I, P, P, I, P, P, P, P, I, P, P, P, P], I),
         "orinfer_sample_topk": ([P, I, I, c_longlong, P, P, P, P, P, P, P], I),
         "orinfer_qgemm_launches": ([I, I, I, I, I], I),
+        "orinfer_act_prep_limited": ([P, P, P, P, I, I, I, P, P], I),
         "orinfer_small_proj": ([P, P, P, I, I, I, P], I),
         "orinfer_gdn_conv": ([P, I, P, P, P, P, P, P, I, I, I, I, I, P, P], I),
         "orinfer_gdn_scan": ([P, P, P, P, P, I, P, P, I, I, I, P, P, P], I),

@@ -45,6 +45,8 @@ def _align(n: int) -> int:
 class ExpertA2A:
     def __init__(self, gate_up: ExpertBank, down: ExpertBank, experts_total: int, top_k: int,
                  max_rows: int, group=None):
+        """``gate_up`` / ``down`` fix the geometry (and are the default banks of ``forward``);
+        layers sharing that geometry share one instance and pass their own banks."""
         lib = native.lib()
         lib.orinfer_peer_alloc.restype = c_void_p
         lib.orinfer_peer_alloc.argtypes = [ctypes.c_size_t]
@@ -125,11 +127,15 @@ class ExpertA2A:
 
     def forward(self, q8: torch.Tensor, scale: torch.Tensor, ids: torch.Tensor,
                 probs: torch.Tensor, out: torch.Tensor, shared: Optional[torch.Tensor] = None,
-                gate: Optional[torch.Tensor] = None, rows: Optional[int] = None) -> torch.Tensor:
+                gate: Optional[torch.Tensor] = None, rows: Optional[int] = None,
+                gate_up: Optional[ExpertBank] = None,
+                down: Optional[ExpertBank] = None) -> torch.Tensor:
         """q8 int8 [R, K] / scale fp32 [R]: the owned tokens, normalised, rotated for the
         experts' gate_up and quantised; ids int32 [R, top_k] global expert ids; probs fp32.
         Writes fp16 ``out[R, H] = sum_k probs * expert(ids)(token) (+ gate * shared)``."""
         lib, tp, cap = self.lib, self.world, self.cap
+        up = self.gate_up if gate_up is None else gate_up
+        dn = self.down if down is None else down
         rows = q8.shape[0] if rows is None else rows
         if rows * self.top_k > cap:
             raise ValueError("more owned rows than the all-to-all buffers were sized for")
@@ -147,13 +153,13 @@ class ExpertA2A:
         # 3. local experts over everything received
         be, total = self.by_expert, tp * cap
         F.moe_dispatch(self.recv_expert, self.recv_rows, self.recv_scale, self.experts_total, be,
-                       total, self.gate_up.base, self.local_experts)
-        F.qgemm_grouped(be.q8, be.scale, self.gate_up.codes, self.gate_up.scale, self.gate_up.fmt,
-                        2 * self.ffn, be.gate_up, be, total)
-        F.act_prep(be.gate_up, None, None, self.down.signs, swiglu=True, rows=total,
-                   q_out=be.q8_mid, scale_out=be.scale_mid)
-        F.qgemm_grouped(be.q8_mid, be.scale_mid, self.down.codes, self.down.scale, self.down.fmt,
-                        self.h, be.down, be, total)
+                       total, up.base, self.local_experts)
+        F.qgemm_grouped(be.q8, be.scale, up.codes, up.scale, up.fmt, 2 * self.ffn, be.gate_up, be,
+                        total)
+        F.act_prep_limited(be.gate_up, dn.signs, be.offsets[self.local_experts:], swiglu=True,
+                           rows=total, q_out=be.q8_mid, scale_out=be.scale_mid)
+        F.qgemm_grouped(be.q8_mid, be.scale_mid, dn.codes, dn.scale, dn.fmt, self.h, be.down, be,
+                        total)
         # 4. combine all-to-all
         check(lib.orinfer_a2a_return_push(ptr(be.down), ptr(be.slots), self._p["header"], self.h,
                                           ctypes.byref(self.r), s), "a2a_return_push")

@@ -181,8 +181,11 @@ def _setup_lib():
     lib.orinfer_moe_combine_peer.argtypes = [P, P, P, I, I, P, P, ctypes.POINTER(_PeerOut), I, P]
     lib.orinfer_moe_combine_peer.restype = I
     lib.orinfer_act_prep_sp.argtypes = [ctypes.POINTER(_Inbox), ctypes.POINTER(_AgOut), P, P, P,
-                                        I, I, ctypes.c_float, I, P]
+                                        I, I, ctypes.c_float, I, P, P]
     lib.orinfer_act_prep_sp.restype = I
+    lib.orinfer_act_prep_inbox_rows.argtypes = [ctypes.POINTER(_Inbox), P, P, P, P, P, P, I, I, I,
+                                                ctypes.c_float, I, P]
+    lib.orinfer_act_prep_inbox_rows.restype = I
     lib.orinfer_qgemm_ag.argtypes = [I, P, P, P, P, P, ctypes.POINTER(_AgIn), I, I, I, I, P]
     lib.orinfer_qgemm_ag.restype = I
     lib.orinfer_ag_wait.argtypes = [ctypes.POINTER(_AgIn), I, P]
@@ -208,10 +211,66 @@ class FusedTPRunner(TPRunner):
         cfg = self.cfg
         self._sp_rows_per = 0
         if self.world > 1 or os.environ.get("ORINFER_TP_SP_WORLD1") == "1":
-            if p.rows >= SP_MIN_ROWS and not cfg.experts and cfg.arch == "dense":
+            dense = not cfg.experts and cfg.arch == "dense"
+            moe = bool(cfg.experts) and cfg.arch == "moe" and cfg.experts % self.world == 0 \
+                and os.environ.get("ORINFER_EP_A2A", "1") != "0"
+            if p.rows >= SP_MIN_ROWS and (dense or moe):
                 self._sp_rows_per = (p.rows + self.world - 1) // self.world
         self._sp_total = p.rows
         return super().forward_hidden(p)
+
+    def _moe_ffn(self, lw, x, rows: int):
+        """Prefill-sized packets of MoE models keep the tokens sharded: this rank normalises
+        the rows it owns (completing the attention's reduce-scatter), routes them, sends each
+        (row, expert) to the expert's owner, runs its own experts over what it received,
+        returns the results and combines top-k rows per owned token.  The shared expert runs
+        on the owned rows with its full weights."""
+        rows_per = self._sp_rows_per if rows == self._sp_total else 0
+        if not rows_per or not isinstance(x, tuple) or x[0] == "local":
+            return super()._moe_ffn(lw, x, rows)
+        from ..ops import functional as F
+        from .ep_a2a import ExpertA2A
+        cfg, ws = self.cfg, self.ws
+        h, f = cfg.hidden, cfg.expert_ffn
+        base = self.tp.rank * rows_per
+        cnt = min(rows_per, rows - base)
+        if cnt <= 0:
+            raise native.KernelError("a rank owns no rows of a sequence-parallel packet")
+        bank_up, bank_dn = lw.expert_gate_up, lw.expert_down
+        cap_rows = (ws.max_rows + self.world - 1) // self.world
+        if getattr(self, "_a2a", None) is None:
+            self._a2a = ExpertA2A(bank_up, bank_dn, cfg.experts, cfg.top_k, cap_rows, self.group)
+            e = lambda *s_, dt: torch.empty(*s_, dtype=dt, device=self.device)
+            self._a2a_buf = dict(ids=e(cap_rows, cfg.top_k, dt=torch.int32),
+                                 probs=e(cap_rows, cfg.top_k, dt=torch.float32),
+                                 gate=e(cap_rows, dt=torch.float32),
+                                 shared=e(cap_rows, h, dt=torch.float16),
+                                 q8s=e(cap_rows, max(cfg.shared_expert_ffn, 16), dt=torch.int8))
+        b = self._a2a_buf
+        y16 = ws.attn_norm(rows, h)
+        q8, sc = ws.q8[h], ws.scale
+        ib = self.mem.inbox[x[0]]
+        check(self.lib.orinfer_act_prep_inbox_rows(
+            ctypes.byref(ib), ptr(ws.resid), ptr(lw.post_norm), ptr(bank_up.signs), ptr(q8),
+            ptr(sc), ptr(y16), base, cnt, h, float(cfg.eps), int(cfg.zero_centered_norm),
+            stream()), "act_prep_inbox_rows")
+        count_launches(1)
+        q8o, sco, y16o = q8[base:base + cnt], sc[base:base + cnt], y16[base:base + cnt]
+        F.router_topk(y16o, lw.router, cfg.experts, cfg.top_k, renorm=cfg.renormalize, rows=cnt,
+                      ids=b["ids"], probs=b["probs"], gate=b["gate"])
+        shared = None
+        if lw.shared_gate_up is not None:
+            fs = lw.shared_gate_up.n // 2
+            gu = self._linear(lw.shared_gate_up, q8o, sco, cnt,
+                              ws.gate_up.view(-1)[: ws.max_rows * 2 * fs].view(ws.max_rows, 2 * fs))
+            q8s, s8s = F.act_prep(gu, None, None, self._signs(lw.shared_down), swiglu=True,
+                                  rows=cnt, q_out=b["q8s"], scale_out=ws.scale_alt(cnt))
+            shared = self._linear(lw.shared_down, q8s, s8s, cnt, b["shared"])
+        has_gate = lw.router.shape[0] == cfg.experts + 1
+        self._a2a.forward(q8o, sco, b["ids"], b["probs"], ws.hidden[base:base + cnt], shared,
+                          b["gate"] if has_gate and shared is not None else None, rows=cnt,
+                          gate_up=bank_up, down=bank_dn)
+        return ("local", rows_per)
 
     def _moe_combine(self, sc, shared, gate, rows: int):
         """Expert-parallel combine fused with the scatter half of the all-reduce: the kernel
@@ -239,16 +298,19 @@ class FusedTPRunner(TPRunner):
             return super()._prep(x, norm_w, signs, rows, y_out)
         cfg, ws = self.cfg, self.ws
         name, rows_per = x if isinstance(x, tuple) else (x, 0)
-        ib = self.mem.inbox[name]
+        ib = self.mem.inbox[name] if name != "local" else None
         if rows_per:
             if y_out is not None:
                 raise native.KernelError("sequence-parallel norm has no fp16 output")
             ag = self.mem.ag_out
             ag.rows_per = rows_per
-            check(self.lib.orinfer_act_prep_sp(ctypes.byref(ib), ctypes.byref(ag), ptr(ws.resid),
-                                               ptr(norm_w), ptr(signs), rows, cfg.hidden,
-                                               float(cfg.eps), int(cfg.zero_centered_norm),
-                                               stream()), "act_prep_sp")
+            # "local": the owned rows' branch output sits in ws.hidden (token-sharded MoE)
+            check(self.lib.orinfer_act_prep_sp(ctypes.byref(ib) if ib is not None else None,
+                                               ctypes.byref(ag), ptr(ws.resid), ptr(norm_w),
+                                               ptr(signs), rows, cfg.hidden, float(cfg.eps),
+                                               int(cfg.zero_centered_norm), stream(),
+                                               None if ib is not None else ptr(ws.hidden)),
+                  "act_prep_sp")
             count_launches(1)
             return self.mem.ag_q, self.mem.ag_scale       # gathered; consumers must wait
         q8, sc = ws.q8[cfg.hidden], ws.scale

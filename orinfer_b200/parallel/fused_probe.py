@@ -85,7 +85,7 @@ def main():
         check(lib.orinfer_qgemm_peer(FMT["q4"], ptr(a_row), ptr(sa_row), ptr(w_row), ptr(s_row),
                                      ctypes.byref(po), m, h, k_row, 0, stream()), "gemm_rs")
         check(lib.orinfer_act_prep_sp(ctypes.byref(ib), ctypes.byref(ag), ptr(resid), ptr(norm_w),
-                                      ptr(signs), m, h, 1e-6, 0, stream()), "norm_ag")
+                                      ptr(signs), m, h, 1e-6, 0, stream(), None), "norm_ag")
         check(lib.orinfer_qgemm_ag(FMT["q4"], ptr(mem.ag_q), ptr(mem.ag_scale), ptr(w_col),
                                    ptr(s_col), ptr(out_col), ctypes.byref(ai), m, n_col, h, 0,
                                    stream()), "ag_gemm")

@@ -134,24 +134,17 @@ def _slice_bank(bank: ExpertBank, lo: int, hi: int) -> ExpertBank:
 
 def _shard_moe(cfg: ModelConfig, lw: LayerWeights, layer: int, lay: TPLayout, dev) -> None:
     """Expert parallelism: a contiguous range of experts per rank; tokens and the router stay
-    replicated, so every rank computes its own experts' share of each token and the partial
-    sums meet in the all-reduce that follows (the reference's TP8 plans do the same:
-    python/orinfer_build/models/deepseek_v41/build.py:1199-1226,1355-1364).  The shared expert
-    is split like a dense FFN when its width allows, else whole layers alternate owners."""
+    replicated for decode-sized packets, so every rank computes its own experts' share of each
+    token and the partial sums meet in the all-reduce that follows (the reference's TP8 plans
+    do the same: python/orinfer_build/models/deepseek_v41/build.py:1199-1226,1355-1364);
+    prefill-sized packets shard the tokens and exchange rows with all-to-alls."""
     w, r = lay.world, lay.rank
     lo, hi = split_blocks(cfg.experts, w)[r]
     lw.expert_gate_up = _slice_bank(lw.expert_gate_up, lo, hi)
     lw.expert_down = _slice_bank(lw.expert_down, lo, hi)
-    if lw.shared_gate_up is not None:
-        f = lw.shared_gate_up.n // 2
-        if (f // 128) % w == 0:
-            a, b = split_blocks(f // 128, w)[r]
-            a, b = a * 128, b * 128
-            idx = torch.cat([torch.arange(a, b, device=dev), torch.arange(f + a, f + b, device=dev)])
-            lw.shared_gate_up = _rows(lw.shared_gate_up, idx)
-            lw.shared_down = _cols(lw.shared_down, a, b)
-        elif layer % w != r:
-            lw.shared_gate_up = lw.shared_down = None
+    # The shared expert stays whole on every rank (it is small): with sharded tokens each rank
+    # applies it to the rows it owns; with replicated tokens only its owner rank adds it.
+    lw.shared_owner = layer % w
 
 
 def shard_model(weights: ModelWeights, rank: int, world: int) -> ModelWeights:

@@ -143,7 +143,7 @@ def moe_ffn(cfg: ModelConfig, lw: LayerWeights, y: torch.Tensor, quantized: bool
                 f = gu.shape[-1] // 2
                 o = _linear_fp(dn_l, torch.nn.functional.silu(gu[:, :f]) * gu[:, f:])
             out[tok] += w[tok, j] * o[0]
-    if lw.shared_gate_up is not None:
+    if lw.shared_gate_up is not None and getattr(lw, "_add_shared", True):
         sh = LayerWeights("attn", lw.in_norm, lw.post_norm, gate_up=lw.shared_gate_up,
                           down=lw.shared_down)
         out = out + torch.sigmoid(logits[:, e:e + 1]) * dense_ffn(sh, y, quantized)
