@@ -136,3 +136,15 @@ def test_fused_sequence_parallel_world2(cuda, tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     _check(tmp_path, 2, "tiny", sp=True)
+
+
+def test_fused_sequence_parallel_moe_world1(cuda, tmp_path):
+    """Token-sharded MoE: owned-row norm, router, expert all-to-all (dispatch push, grouped
+    GEMM, return push), local-input norm + all-gather; the rank is its own peer."""
+    _check(tmp_path, 1, "tiny-moe", sp=True)
+
+
+def test_fused_sequence_parallel_moe_world2(cuda, tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _check(tmp_path, 2, "tiny-moe", sp=True)
