@@ -122,6 +122,15 @@ int orinfer_prefix_restore(void* handle, int32_t node_id, int32_t page);
 int orinfer_prefix_drop_host(void* handle, int want, int64_t* handles);
 void orinfer_prefix_stats(void* handle, uint64_t out[10]);
 
+// ---- cost curves (cost_curves.cpp)
+typedef struct OrinferWork {
+  uint32_t tokens;          // prompt tokens in the packet
+  uint32_t context;         // longest context among its prompt chunks
+  uint32_t decode_rows;     // decode rows riding along
+  uint32_t decode_context;  // longest context among them
+  int domain;               // execution family (model / parallel layout); curves never mix
+} OrinferWork;
+
 #ifdef __cplusplus
 }
 #endif

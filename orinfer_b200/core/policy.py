@@ -283,3 +283,70 @@ class PromptLookup(_Handle):
 
     def observe(self, accepted: int, proposed: int, progress: int) -> None:
         self._l.orinfer_lookup_observe(self._h, accepted, proposed, progress)
+
+
+# ---------------------------------------------------------------- packet cost curves
+class _Work(ctypes.Structure):
+    _fields_ = [("tokens", ctypes.c_uint32), ("context", ctypes.c_uint32),
+                ("decode_rows", ctypes.c_uint32), ("decode_context", ctypes.c_uint32),
+                ("domain", ctypes.c_int)]
+
+
+DIRECT, REPLAY, SHARED = 0, 1, 2
+
+
+class CostCurves:
+    """Bounded table of measured packet times (``csrc/core/cost_curves.cpp``): exact cell,
+    then another path of the same shape, then interpolation over token counts, then the cold
+    prior.  ``fit_tokens`` sizes a prefill chunk against a time budget."""
+
+    def __init__(self, cold_tokens_per_s: float = 20000.0):
+        L = _L()
+        L.orinfer_costs_create.restype = ctypes.c_void_p
+        L.orinfer_costs_create.argtypes = [ctypes.c_double]
+        L.orinfer_costs_destroy.argtypes = [ctypes.c_void_p]
+        L.orinfer_costs_cells.argtypes = [ctypes.c_void_p]
+        L.orinfer_costs_observe.argtypes = [ctypes.c_void_p, ctypes.POINTER(_Work), ctypes.c_int,
+                                            ctypes.c_double, ctypes.c_double]
+        L.orinfer_costs_estimate.argtypes = [ctypes.c_void_p, ctypes.POINTER(_Work), ctypes.c_int,
+                                             ctypes.POINTER(ctypes.c_double)]
+        L.orinfer_costs_fit_tokens.argtypes = [ctypes.c_void_p, ctypes.POINTER(_Work),
+                                               ctypes.c_int, ctypes.c_double, ctypes.c_int,
+                                               ctypes.c_int]
+        self._h = L.orinfer_costs_create(cold_tokens_per_s)
+        if not self._h:
+            raise ValueError("cold rate must be positive")
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            _L().orinfer_costs_destroy(self._h)
+            self._h = None
+
+    @staticmethod
+    def _w(tokens, context, decode_rows=0, decode_context=0, domain=0) -> _Work:
+        return _Work(int(tokens), int(context), int(decode_rows), int(decode_context), int(domain))
+
+    def observe(self, seconds: float, *, tokens: int, context: int, decode_rows: int = 0,
+                decode_context: int = 0, domain: int = 0, path: int = DIRECT,
+                setup_s: float = 0.0) -> None:
+        w = self._w(tokens, context, decode_rows, decode_context, domain)
+        _L().orinfer_costs_observe(self._h, ctypes.byref(w), path, seconds, setup_s)
+
+    def estimate(self, *, tokens: int, context: int, decode_rows: int = 0,
+                 decode_context: int = 0, domain: int = 0, path: int = -1):
+        """-> (seconds, upper_s, samples, path)."""
+        w = self._w(tokens, context, decode_rows, decode_context, domain)
+        out = (ctypes.c_double * 4)()
+        _L().orinfer_costs_estimate(self._h, ctypes.byref(w), path, out)
+        return out[0], out[1], int(out[2]), int(out[3])
+
+    def fit_tokens(self, budget_s: float, limit: int, quantum: int = 128, *, context: int,
+                   decode_rows: int = 0, decode_context: int = 0, domain: int = 0,
+                   path: int = -1) -> int:
+        w = self._w(0, context, decode_rows, decode_context, domain)
+        return _L().orinfer_costs_fit_tokens(self._h, ctypes.byref(w), path, budget_s, limit,
+                                             quantum)
+
+    @property
+    def cells(self) -> int:
+        return _L().orinfer_costs_cells(self._h)

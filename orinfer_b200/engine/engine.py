@@ -160,6 +160,8 @@ class Engine:
         from .speculation import Speculator
         self.spec = Speculator(self, self.load.mtp_drafts, self.load.prompt_lookup)
         self.tpot_ewma: Optional[float] = None
+        from ..core.policy import CostCurves
+        self.costs = CostCurves()
 
     # ------------------------------------------------------------------ sizing
     def _auto_pages(self, extra_layers: int) -> int:
@@ -383,9 +385,20 @@ class Engine:
         chunks = []
         if self.sched.policy is Policy.LATENCY and decoders and self.tpot_ewma is not None:
             # keep prompt progress within the prefill budget while decoders are live
-            rate = self._prefill_rate()
-            if rate:
-                budget = min(budget, max(int(rate * self.sched.prefill_budget_ms / 1e3), 16))
+            # measured packet costs size the chunk against the prefill budget (cold: the
+            # running tokens/s estimate)
+            ctx = max((r.offset for r in prefills), default=0) + 1
+            dctx = max(r.offset for r in decoders) + 1
+            if self.costs.cells:
+                fit = self.costs.fit_tokens(self.sched.prefill_budget_ms / 1e3, budget, 16,
+                                            context=ctx, decode_rows=len(decoders),
+                                            decode_context=dctx)
+                budget = min(budget, max(fit, 16))
+            else:
+                rate = self._prefill_rate()
+                if rate:
+                    budget = min(budget,
+                                 max(int(rate * self.sched.prefill_budget_ms / 1e3), 16))
         prefills.sort(key=lambda r: (r.last_prefill_at or r.arrived))
         for r in prefills:
             if budget <= 0:
@@ -434,6 +447,10 @@ class Engine:
             rate = toks / max(t2 - t0, 1e-6)
             prev = getattr(self, "_prefill_tok_s", None)
             self._prefill_tok_s = rate if prev is None else 0.8 * prev + 0.2 * rate
+            self.costs.observe(t2 - t0, tokens=toks,
+                               context=max(r.offset for r, _ in chunks),
+                               decode_rows=len(decoders),
+                               decode_context=max((r.offset for r in decoders), default=0) + 1)
         return produced
 
     # ------------------------------------------------------------------ execution

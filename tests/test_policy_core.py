@@ -109,3 +109,41 @@ def test_prompt_lookup_copies_continuation_and_cools_down():
     lk.observe(0, 3, len(hist))
     lk.observe(0, 3, len(hist))                             # two misses -> cooldown
     assert lk.propose(hist, 3) == []
+
+
+def test_cost_curves_exact_interpolated_and_cold():
+    from orinfer_b200.core.policy import DIRECT, REPLAY, CostCurves
+    c = CostCurves(cold_tokens_per_s=10000.0)
+    sec, up, n, path = c.estimate(tokens=500, context=500)
+    assert abs(sec - 0.05) < 1e-9 and n == 0 and path == DIRECT          # cold prior
+    for _ in range(5):
+        c.observe(0.010, tokens=512, context=512)
+        c.observe(0.030, tokens=2048, context=512)
+        c.observe(0.018, tokens=1024, context=512)
+    sec, up, n, _ = c.estimate(tokens=512, context=512)
+    assert abs(sec - 0.010) < 1e-9 and n == 5 and up >= sec
+    sec, _, n, _ = c.estimate(tokens=768, context=512)                     # between 512 and 1024
+    assert 0.010 < sec < 0.018 and n == 0
+    sec, _, _, _ = c.estimate(tokens=4096, context=400)                    # beyond the data: linear
+    assert abs(sec - 0.060) < 1e-9
+    assert c.estimate(tokens=4096, context=4096)[2] == 0                   # another family: cold
+    # the family remembers its last path; a path without samples borrows the hot cost
+    c.observe(0.008, tokens=512, context=512, path=REPLAY)
+    assert c.estimate(tokens=512, context=512)[3] == REPLAY
+    # a sample that paid for a capture only primes the cell, a clean one replaces it
+    c.observe(0.5, tokens=256, context=256, setup_s=0.4)
+    assert abs(c.estimate(tokens=256, context=256)[0] - 0.5) < 1e-9
+    c.observe(0.004, tokens=256, context=256)
+    assert abs(c.estimate(tokens=256, context=256)[0] - 0.004) < 1e-9
+    # chunk sizing against a budget uses the upper estimate
+    assert c.fit_tokens(0.012, 4096, 128, context=512) in (512, 640)
+    assert c.fit_tokens(1e-6, 4096, 128, context=512) == 128              # never below a quantum
+
+
+def test_cost_curves_are_bounded():
+    from orinfer_b200.core.policy import CostCurves
+    c = CostCurves()
+    for t in range(1, 400):
+        c.observe(0.001 * t, tokens=t, context=64)
+    assert c.cells == 256
+    assert c.estimate(tokens=399, context=64)[2] == 1 and c.estimate(tokens=1, context=64)[2] == 0
