@@ -546,7 +546,7 @@ class Engine:
         the least recently used of PREFILL_GRAPHS entries is dropped.  Returns (tokens,
         logits) or None when this packet ran (or must run) directly."""
         n_sel = packet.logit_rows.shape[0]
-        key = (chunk_lens, n_sel, need)
+        key = (chunk_lens, n_sel, need, packet.page_table.data_ptr())
         cache = self.__dict__.setdefault("_prefill_graphs", {})
         e = cache.pop(key, None)
         if e is None:
@@ -560,7 +560,7 @@ class Engine:
             if e["trials"] < 2:
                 return None
             st = Packet(packet.ids.clone(), packet.row_req.clone(), packet.row_pos.clone(),
-                        self.page_table_dev, packet.rows, packet.max_kv_len,
+                        packet.page_table, packet.rows, packet.max_kv_len,
                         packet.logit_rows.clone(), chunks=packet.chunks.clone(),
                         max_q_len=packet.max_q_len, decode_rows=0)
             self.runner.greedy(st, need_logits=need)                 # warm outside capture
