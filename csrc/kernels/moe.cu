@@ -148,11 +148,13 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(
     if (mine) {
       const int slot = base + before + __popc(ballot & ((1u << lane) - 1u));
       slots[i] = slot;
-      const int row = i / top_k;
-      scale_sorted[slot] = scale[row];
-      const int4* src = reinterpret_cast<const int4*>(q8 + static_cast<size_t>(row) * K);
-      int4* dst = reinterpret_cast<int4*>(q8_sorted + static_cast<size_t>(slot) * K);
-      for (int c = 0; c < K / 16; ++c) dst[c] = src[c];
+      if (q8 != nullptr) {                  // nullptr: only the slot numbering is wanted
+        const int row = i / top_k;
+        scale_sorted[slot] = scale[row];
+        const int4* src = reinterpret_cast<const int4*>(q8 + static_cast<size_t>(row) * K);
+        int4* dst = reinterpret_cast<int4*>(q8_sorted + static_cast<size_t>(slot) * K);
+        for (int c = 0; c < K / 16; ++c) dst[c] = src[c];
+      }
     }
     __syncthreads();
     if (threadIdx.x == 0) base += block_total;

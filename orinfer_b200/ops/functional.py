@@ -254,22 +254,23 @@ class MoeScratch:
         self.down = e(s, hidden, dt=torch.float16)
 
 
-def moe_dispatch(ids: torch.Tensor, q8: torch.Tensor, scale: torch.Tensor, experts: int,
-                 sc: MoeScratch, rows: int, base_expert: int = 0,
+def moe_dispatch(ids: torch.Tensor, q8: Optional[torch.Tensor], scale: Optional[torch.Tensor],
+                 experts: int, sc: MoeScratch, rows: int, base_expert: int = 0,
                  local_experts: Optional[int] = None) -> None:
     """Deterministic dispatch metadata + copy of the routed rows into expert-contiguous
-    slots.  With ``local_experts`` only rows routed to experts
+    slots (``q8 = None``: numbering only).  With ``local_experts`` only rows routed to experts
     [base_expert, base_expert + local_experts) are dispatched; other slots become -1."""
     top_k = ids.shape[1]
+    width = sc.q8.shape[1] if q8 is None else q8.shape[1]
     if local_experts is not None and local_experts != experts:
         check(native.lib().orinfer_moe_dispatch_ep(
-            ptr(ids), rows, top_k, base_expert, local_experts, ptr(q8), ptr(scale), q8.shape[1],
+            ptr(ids), rows, top_k, base_expert, local_experts, ptr(q8), ptr(scale), width,
             ptr(sc.counts), ptr(sc.offsets), ptr(sc.tiles), ptr(sc.meta), sc.max_tiles,
             ptr(sc.slots), ptr(sc.q8), ptr(sc.scale), stream()), "moe_dispatch_ep")
         count_launches(3)
         return
     check(native.lib().orinfer_moe_dispatch(
-        ptr(ids), rows, top_k, experts, ptr(q8), ptr(scale), q8.shape[1], ptr(sc.counts),
+        ptr(ids), rows, top_k, experts, ptr(q8), ptr(scale), width, ptr(sc.counts),
         ptr(sc.offsets), ptr(sc.tiles), ptr(sc.meta), sc.max_tiles, ptr(sc.slots), ptr(sc.q8),
         ptr(sc.scale), stream()), "moe_dispatch")
     count_launches(3)

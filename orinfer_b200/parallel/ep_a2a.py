@@ -120,7 +120,7 @@ class ExpertA2A:
         self.recv_expert = view("expert", (tp * cap, 1), "<i4")
         self.ret = view("ret", (cap, self.h), "<f2")
         self._p = {n: mine + self.off[n] for n in ("header", "flag_d", "flag_r")}
-        self.by_dst = F.MoeScratch(max_rows, top_k, tp, self.k, 8, dev)
+        self.by_dst = F.MoeScratch(max_rows, top_k, tp, 16, 8, dev)     # numbering only
         self.by_expert = F.MoeScratch(tp * cap, 1, self.local_experts, self.k, self.ffn, dev)
         torch.cuda.synchronize()
         dist.barrier(group=group)
@@ -142,7 +142,7 @@ class ExpertA2A:
         s = stream()
         # 1. rank of every assignment among those bound for the same destination rank
         dst = torch.div(ids[:rows], self.local_experts, rounding_mode="floor").to(torch.int32)
-        F.moe_dispatch(dst.contiguous(), q8, scale, tp, self.by_dst, rows)
+        F.moe_dispatch(dst.contiguous(), None, None, tp, self.by_dst, rows)
         # 2. dispatch all-to-all
         check(lib.orinfer_a2a_dispatch_push(ptr(ids), ptr(self.by_dst.slots),
                                             ptr(self.by_dst.offsets), ptr(q8), ptr(scale), rows,
