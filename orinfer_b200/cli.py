@@ -261,6 +261,23 @@ def cmd_make_model(a) -> int:
     return 0
 
 
+def cmd_package_install(a) -> int:
+    from .engine import packages
+    try:
+        path = packages.install(a.archive, a.cache)
+    except packages.PackageError as e:
+        print(f"Package installation: {e}", file=sys.stderr)
+        return 2
+    print(json.dumps({"digest": path.name, "path": str(path)}))
+    return 0
+
+
+def cmd_package_create(a) -> int:
+    from .engine import packages
+    print(json.dumps({"digest": packages.create(a.model, a.output), "archive": a.output}))
+    return 0
+
+
 def cmd_devices(a) -> int:
     import torch
     devs = []
@@ -323,6 +340,16 @@ def build_parser() -> argparse.ArgumentParser:
     mk.add_argument("--output", required=True)
     mk.add_argument("--seed", type=int, default=0)
     mk.set_defaults(fn=cmd_make_model)
+    pk = sub.add_parser("package")
+    pks = pk.add_subparsers(dest="package_cmd", required=True)
+    pi = pks.add_parser("install")
+    pi.add_argument("archive")
+    pi.add_argument("--cache", default=None)
+    pi.set_defaults(fn=cmd_package_install)
+    pc = pks.add_parser("create")
+    pc.add_argument("model")
+    pc.add_argument("--output", required=True)
+    pc.set_defaults(fn=cmd_package_create)
     sub.add_parser("devices").set_defaults(fn=cmd_devices)
     sub.add_parser("info").set_defaults(fn=cmd_info)
     vn = sub.add_parser("validate-nccl")
