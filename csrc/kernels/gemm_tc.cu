@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     const unsigned char* __restrict__ w, const float* __restrict__ a_scale,
     const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K,
     const E8pTables* __restrict__ tables, int* status, PeerOut po, GroupDesc grp, AgIn ag,
-    int* __restrict__ partial) {
+    int* __restrict__ partial, int n_begin, int n_end) {
   using L = Layout<FMT, MT, NB>;
   constexpr int SA = L::SA, SB = L::SB;
   constexpr int BN = NB;
@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN;
+  const int n0 = n_begin + blockIdx.x * BN;    // this launch covers columns [n_begin, n_end)
   int m0 = blockIdx.y * BM * MT, m_limit = M, b_row0 = n0;
   if (grp.tiles != nullptr) {
     if (static_cast<int>(blockIdx.y) >= grp.meta[0]) return;
@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   const int kb_all = K / BK, kb_per = (kb_all + gridDim.z - 1) / gridDim.z;
   const int kb0 = blockIdx.z * kb_per;
   const int kblocks = max(0, min(kb_all, kb0 + kb_per) - kb0);
-  const int rows_valid = min(BN, N - n0);
+  const int rows_valid = min(BN, n_end - n0);
   constexpr uint32_t TMEM_COLS = MT * BN;
 
   if (threadIdx.x == 0) {
@@ -274,10 +274,13 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
         }
         if (partial != nullptr) {
           if (m < m_limit) {
-            int* dst = partial + (static_cast<size_t>(blockIdx.z) * M + m) * N + n0 + c0;
+            // the workspace is compact over this launch's columns
+            const int width = n_end - n_begin;
+            int* dst = partial + (static_cast<size_t>(blockIdx.z) * M + m) * width +
+                       (n0 - n_begin) + c0;
 #pragma unroll
             for (int g = 0; g < 8; ++g)
-              if (n0 + c0 + g * 4 + 4 <= N)
+              if (n0 + c0 + g * 4 + 4 <= n_end)
                 *reinterpret_cast<int4*>(dst + g * 4) =
                     make_int4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
           }
@@ -287,7 +290,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             const int n = n0 + c0 + g * 8;
-            if (n + 8 <= N) {
+            if (n + 8 <= n_end) {
               float v[8];
 #pragma unroll
               for (int j = 0; j < 8; ++j)
@@ -338,15 +341,16 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
 __global__ void __launch_bounds__(256) splitk_finalize_kernel(
     const int* __restrict__ partial, int splits, const float* __restrict__ a_scale,
     const __half* __restrict__ w_scale, __half* __restrict__ out, int M, int N, PeerOut po,
-    int ag_scales) {
-  const int groups = N / 8;
+    int ag_scales, int n_begin, int width) {
+  const int groups = width / 8;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx < static_cast<long long>(M) * groups) {
-    const int m = static_cast<int>(idx / groups), n = static_cast<int>(idx % groups) * 8;
+    const int m = static_cast<int>(idx / groups), c = static_cast<int>(idx % groups) * 8;
+    const int n = n_begin + c;
     int acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int z = 0; z < splits; ++z) {
-      const int4* src =
-          reinterpret_cast<const int4*>(partial + (static_cast<size_t>(z) * M + m) * N + n);
+      const int4* src = reinterpret_cast<const int4*>(
+          partial + (static_cast<size_t>(z) * M + m) * width + c);
       const int4 a = src[0], b = src[1];
       acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
       acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
@@ -377,8 +381,10 @@ template <int FMT, bool OUT_F32, int MT, int NB>
 int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale, void* out,
            int M, int N, int K, cudaStream_t stream, const PeerOut& po,
            const GroupDesc& grp = GroupDesc{nullptr, nullptr, 0, 0}, int experts = 1,
-           int max_tiles = 0, const AgIn& ag = AgIn{nullptr, nullptr, 0, 0}, int splits = 1) {
+           int max_tiles = 0, const AgIn& ag = AgIn{nullptr, nullptr, 0, 0}, int splits = 1,
+           int n_begin = 0, int n_end = -1) {
   using L = Layout<FMT, MT, NB>;
+  if (n_end < 0) n_end = N;
   CUtensorMap ta, tb;
   if (!make_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BM, BK)) return -3;
   if (FMT == 0) {
@@ -396,16 +402,19 @@ int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w
     if (e != cudaSuccess) return static_cast<int>(e);
     attr = true;
   }
-  dim3 grid((N + NB - 1) / NB, grp.tiles ? max_tiles : (M + BM * MT - 1) / (BM * MT), splits);
+  const int width = n_end - n_begin;
+  if (width <= 0) return 0;
+  dim3 grid((width + NB - 1) / NB, grp.tiles ? max_tiles : (M + BM * MT - 1) / (BM * MT), splits);
   int* partial = splits > 1 ? runtime_splitk_workspace() : nullptr;
+  if (splits > 1 && static_cast<size_t>(splits) * M * width * 4 > SPLITK_WORKSPACE_BYTES) return -1;
   qgemm_tc_kernel<FMT, OUT_F32, MT, NB><<<grid, THREADS, L::TOTAL, stream>>>(
       ta, tb, reinterpret_cast<const unsigned char*>(w), a_scale, w_scale, out, M, N, K,
-      runtime_e8p_tables(), runtime_status_ptr(), po, grp, ag, partial);
+      runtime_e8p_tables(), runtime_status_ptr(), po, grp, ag, partial, n_begin, n_end);
   if (splits > 1) {
-    const long long items = static_cast<long long>(M) * (N / 8);
+    const long long items = static_cast<long long>(M) * (width / 8);
     splitk_finalize_kernel<<<static_cast<unsigned>((items + 255) / 256), 256, 0, stream>>>(
         partial, splits, a_scale, w_scale, reinterpret_cast<__half*>(out), M, N, po,
-        ag.tp > 0 ? 1 : 0);
+        ag.tp > 0 ? 1 : 0, n_begin, width);
   }
   return static_cast<int>(cudaGetLastError());
 }
@@ -442,6 +451,30 @@ int launch_fmt(const int8_t* a, const float* a_scale, const void* w, const __hal
   const long c128 = ctas(128);
   const int splits = plan_splits(M, N, K, out_f32);
   const int nb = (out_f32 || splits > 1 || c128 >= 120) ? 128 : (ctas(64) >= 120 ? 64 : 32);
+  // Wave quantisation: a grid of one M tile that is a few CTAs larger than the machine would
+  // run a second, almost empty wave.  The full wave runs as one launch; the last few weight
+  // tiles follow as a split-K launch of their own, which occupies the SMs the tail left idle.
+  const long ntiles = (N + 127) / 128;
+  if (!out_f32 && splits == 1 && nb == 128 && mtiles == 1 && po.tp == 0 && ntiles > 148 &&
+      ntiles % 148 > 0 && ntiles % 148 <= 40 && K / BK >= 8 && N % 128 == 0) {
+    const int tail_tiles = static_cast<int>(ntiles % 148);
+    const int cut = static_cast<int>(ntiles - tail_tiles) * 128;
+    int ts = 148 / tail_tiles;
+    ts = ts > K / BK / 4 ? K / BK / 4 : ts;
+    ts = ts > 8 ? 8 : (ts < 1 ? 1 : ts);
+#define ORINFER_TWO(MTV)                                                                        \
+  {                                                                                             \
+    const int r = launch<FMT, false, MTV, 128>(a, a_scale, w, w_scale, out, M, N, K, stream, po, \
+                                               none, 1, 0, ag, 1, 0, cut);                     \
+    if (r) return r;                                                                            \
+    return launch<FMT, false, MTV, 128>(a, a_scale, w, w_scale, out, M, N, K, stream, po, none, \
+                                        1, 0, ag, ts, cut, N);                                 \
+  }
+    if (mt == 4) ORINFER_TWO(4)
+    if (mt == 2) ORINFER_TWO(2)
+    ORINFER_TWO(1)
+#undef ORINFER_TWO
+  }
 #define ORINFER_GO(F32, MTV, NBV)                                                              \
   return launch<FMT, F32, MTV, NBV>(a, a_scale, w, w_scale, out, M, N, K, stream, po, none, 1, \
                                     0, ag, splits)
@@ -504,7 +537,17 @@ static int qgemm_any(int fmt, const int8_t* a, const float* a_scale, const void*
 // Number of kernel launches orinfer_qgemm makes for this shape (1, or 2 with split-K).
 extern "C" int orinfer_qgemm_launches(int M, int N, int K, int out_f32, int force_path) {
   if (force_path == 1 || (force_path == 0 && M <= 8)) return (M + 7) / 8;
-  return tc::plan_splits(M, N, K, out_f32) > 1 ? 2 : 1;
+  if (tc::plan_splits(M, N, K, out_f32) > 1) return 2;
+  const int mt = M > 2 * tc::BM ? 4 : (M > tc::BM ? 2 : 1);
+  const long mtiles = (M + tc::BM * mt - 1) / (tc::BM * mt), ntiles = (N + 127) / 128;
+  if (!out_f32 && mtiles == 1 && ntiles > 148 && ntiles % 148 > 0 && ntiles % 148 <= 40 &&
+      K / tc::BK >= 8 &&
+      N % 128 == 0) {
+    int ts = static_cast<int>(148 / (ntiles % 148));
+    ts = ts > K / tc::BK / 4 ? K / tc::BK / 4 : ts;
+    return ts > 1 ? 3 : 2;
+  }
+  return 1;
 }
 
 extern "C" int orinfer_qgemm(int fmt, const int8_t* a, const float* a_scale, const void* w,

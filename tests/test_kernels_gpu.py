@@ -100,6 +100,8 @@ def _rand_weight(fmt, n, k, dev, seed):
     (700, 8200, 256, 0), (50, 1000, 128, 0), (513, 2560, 1024, 0),
     # split-K (narrow N, long K): INT32 partials + finalize must equal the unsplit result
     (512, 2560, 9728, 0), (100, 2560, 4096, 0), (300, 1024, 2560, 0), (512, 6144, 2560, 0),
+    # one M tile, a few weight tiles more than SMs: full wave + split-K tail launch
+    (512, 19456, 1024, 0), (100, 19968, 1024, 0),
 ])
 def test_qgemm(cuda, fmt, m, n, k, path):
     from orinfer_b200.ops import functional as F
