@@ -22,7 +22,7 @@ from pathlib import Path
 from typing import Callable, Dict, List, Optional
 
 from fastapi import Request as HttpRequest
-from fastapi.responses import JSONResponse
+from fastapi.responses import JSONResponse, Response
 
 NEGATIVE_CACHE_S = 10.0
 DEFAULT_KEEP_ALIVE_S = 300.0
@@ -265,3 +265,107 @@ def install(app, manager: ModelManager) -> None:
     async def models():
         return {"object": "list", "data": [{"id": e.name, "object": "model", "owned_by": "orinfer"}
                                            for e in manager.list()]}
+
+
+# ---------------------------------------------------------------- gateway
+class _Forward(Response):
+    """ASGI response that replays the already-read body into a runner's own app and releases
+    the runner's lease when the response (also a streamed one) has finished."""
+
+    def __init__(self, app, body: bytes, done: Callable[[], None]):
+        super().__init__()
+        self.app, self.replay, self.done = app, body, done
+
+    async def __call__(self, scope, receive, send):
+        replayed = False
+
+        async def rcv():
+            nonlocal replayed
+            if not replayed:
+                replayed = True
+                return {"type": "http.request", "body": self.replay, "more_body": False}
+            return await receive()
+
+        try:
+            await self.app(scope, rcv, send)
+        finally:
+            self.done()
+
+
+@dataclass
+class RunnerHandle:
+    service: object
+    app: object
+
+
+def create_gateway_app(manager: ModelManager, sweep_s: float = 5.0):
+    """One listener for every registered model: OpenAI and Ollama inference routes are
+    forwarded to the runner that serves the request's ``model`` (started on demand, leased for
+    the life of the response); registry routes are served here.  ``start`` of the manager must
+    return ``(RunnerHandle, bytes)``."""
+    import asyncio
+    import json as _json
+
+    from fastapi import FastAPI
+
+    app = FastAPI(title="orinfer-b200 gateway", docs_url=None, redoc_url=None)
+    install(app, manager)
+
+    def openai_error(e: ManagerError):
+        return JSONResponse({"error": {"message": str(e), "type": "invalid_request_error"
+                                       if e.status < 500 else "server_error", "param": "model",
+                                       "code": "model_not_found" if e.status == 404 else None}},
+                            status_code=e.status)
+
+    async def forward(request: HttpRequest, ollama: bool):
+        body = await request.body()
+        try:
+            payload = _json.loads(body)
+            name = payload["model"]
+        except (ValueError, KeyError, TypeError):
+            err = ManagerError("request body must be JSON with a `model` field", 400)
+            return fail_ollama(err) if ollama else openai_error(err)
+        keep = None
+        if ollama and "keep_alive" in payload:
+            from .ollama import parse_keep_alive
+            keep = parse_keep_alive(payload["keep_alive"])
+        try:
+            runner = await asyncio.get_running_loop().run_in_executor(
+                None, manager.acquire, name, keep)
+        except ManagerError as e:
+            return fail_ollama(e) if ollama else openai_error(e)
+        return _Forward(runner.service.app, body, lambda: manager.release(runner))
+
+    def fail_ollama(e: ManagerError):
+        return JSONResponse({"error": str(e)}, status_code=e.status)
+
+    def handler(ollama: bool):
+        async def route(request: HttpRequest):
+            return await forward(request, ollama)
+        return route
+
+    for path in ("/v1/chat/completions", "/v1/chat/completions/render", "/v1/embeddings",
+                 "/v1/rerank", "/rerank"):
+        app.add_api_route(path, handler(False), methods=["POST"])
+    for path in ("/api/chat", "/api/generate", "/api/show"):
+        app.add_api_route(path, handler(True), methods=["POST"])
+
+    @app.get("/health")
+    async def health():
+        return {"status": "ready", "models": [e.name for e in manager.list()],
+                "running": manager.running()}
+
+    @app.on_event("startup")
+    async def start_sweeper():
+        async def loop():
+            while True:
+                await asyncio.sleep(sweep_s)
+                await asyncio.get_running_loop().run_in_executor(None, manager.sweep)
+        app.state.sweeper = asyncio.create_task(loop())
+
+    @app.on_event("shutdown")
+    async def stop_all():
+        app.state.sweeper.cancel()
+        manager.shutdown()
+
+    return app

@@ -119,6 +119,8 @@ def cmd_serve(a) -> int:
         print(f"cannot bind {a.listen}: {e}", file=sys.stderr)
         return 2
     probe.close()
+    if not a.model_dir and not a.preset:
+        return _serve_manager(a, host, int(port), load, sched)
     weights, name = _weights(a)
     name = a.model if a.model != "qwen3.8-27b" or not a.preset else name
     service = Service(_engine_factory(a, weights, load, sched), _codec(a, weights, name), name,
@@ -143,6 +145,66 @@ def cmd_serve(a) -> int:
     service.stop(a.drain_timeout_ms)
     print("SCHEDULER " + json.dumps(service.worker.engine.stats.as_dict()), file=sys.stderr)
     return 1 if service.lifecycle.state == "failed" else 0
+
+
+def _state_dir(a) -> Path:
+    import os
+    return Path(getattr(a, "state_dir", None) or os.environ.get("ORINFER_STATE_DIR")
+                or Path.home() / ".local" / "share" / "orinfer")
+
+
+def _serve_manager(a, host: str, port: int, load, sched) -> int:
+    """`orinfer serve` without a model: every registered model behind one listener, runners
+    started on demand under the memory budget and retired by keep-alive."""
+    import copy
+
+    import uvicorn
+    from .api.manager import ModelManager, RunnerHandle, create_gateway_app
+    from .api.server import Service, create_app
+
+    def start(entry):
+        args = copy.copy(a)
+        args.model_dir, args.preset = entry.path, None
+        weights, name = _weights(args)
+        svc = Service(_engine_factory(args, weights, load, sched), _codec(args, weights, entry.name),
+                      entry.name, dict(json.loads(a.default_request_params), **entry.defaults),
+                      a.queue_timeout_ms, a.output_timeout_ms)
+        svc.start()
+        if svc.lifecycle.state != "ready":
+            raise RuntimeError(svc.lifecycle.reason or "worker failed")
+        return RunnerHandle(svc, create_app(svc)), weights.nbytes()
+
+    manager = ModelManager(_state_dir(a), start, lambda h: h.service.stop(a.drain_timeout_ms),
+                           memory_budget_bytes=getattr(a, "memory_budget_mib", 0) << 20)
+    print(f"API READY http://{a.listen}/v1; manager with {len(manager.list())} models",
+          file=sys.stderr)
+    uvicorn.Server(uvicorn.Config(create_gateway_app(manager), host=host, port=port,
+                                  log_level="warning")).run()
+    return 0
+
+
+def cmd_models(a) -> int:
+    from .api.manager import ManagerError, ModelManager
+    m = ModelManager(_state_dir(a), lambda e: (_ for _ in ()).throw(RuntimeError("offline")),
+                     lambda h: None)
+    try:
+        if a.models_cmd == "import":
+            from .engine.checkpoint import validate_model
+            validate_model(a.path)
+            e = m.register(a.name, str(Path(a.path).resolve()))
+            print(json.dumps(e.__dict__))
+        elif a.models_cmd == "list":
+            print(json.dumps([e.__dict__ for e in m.list()]))
+        elif a.models_cmd == "show":
+            print(json.dumps(m.show(a.name).__dict__))
+        elif a.models_cmd == "cp":
+            print(json.dumps(m.copy(a.name, a.destination).__dict__))
+        elif a.models_cmd == "rm":
+            m.remove(a.name)
+    except ManagerError as e:
+        print(str(e), file=sys.stderr)
+        return 2
+    return 0
 
 
 def cmd_batch(a) -> int:
@@ -312,6 +374,9 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--queue-timeout-ms", type=int, default=0)
     s.add_argument("--output-timeout-ms", type=int, default=60000)
     s.add_argument("--drain-timeout-ms", type=int, default=30000)
+    s.add_argument("--state-dir", default=None, help="manager registry (serve without a model)")
+    s.add_argument("--memory-budget-mib", type=int, default=0,
+                   help="manager mode: evict idle models beyond this many MiB of weights")
     s.set_defaults(fn=cmd_serve)
     b = sub.add_parser("batch")
     _load_args(b, batch=True)
@@ -340,6 +405,20 @@ def build_parser() -> argparse.ArgumentParser:
     mk.add_argument("--output", required=True)
     mk.add_argument("--seed", type=int, default=0)
     mk.set_defaults(fn=cmd_make_model)
+    mo = sub.add_parser("models")
+    mo.add_argument("--state-dir", default=None)
+    mos = mo.add_subparsers(dest="models_cmd", required=True)
+    mi = mos.add_parser("import")
+    mi.add_argument("name")
+    mi.add_argument("path")
+    mos.add_parser("list")
+    for verb in ("show", "rm"):
+        mv = mos.add_parser(verb)
+        mv.add_argument("name")
+    mc = mos.add_parser("cp")
+    mc.add_argument("name")
+    mc.add_argument("destination")
+    mo.set_defaults(fn=cmd_models)
     pk = sub.add_parser("package")
     pks = pk.add_subparsers(dest="package_cmd", required=True)
     pi = pks.add_parser("install")

@@ -45,3 +45,19 @@ def test_model_verbs(tmp_path, capsys):
 def test_validate_nccl_on_cpu_ranks():
     from orinfer_b200.parallel.selftest import main as selftest
     assert selftest(2, use_cuda=False) == 0
+
+
+def test_models_registry_verbs(tmp_path, capsys):
+    from orinfer_b200.cli import main
+    model = tmp_path / "m"
+    assert main(["make-model", "--preset", "tiny", "--output", str(model)]) == 0
+    st = ["--state-dir", str(tmp_path / "state")]
+    assert main(["models", *st, "import", "tiny", str(model)]) == 0
+    assert main(["models", *st, "cp", "tiny", "tiny2"]) == 0
+    capsys.readouterr()
+    assert main(["models", *st, "list"]) == 0
+    import json
+    names = [e["name"] for e in json.loads(capsys.readouterr().out)]
+    assert names == ["tiny", "tiny2"]
+    assert main(["models", *st, "rm", "tiny"]) == 0
+    assert main(["models", *st, "show", "tiny"]) == 2

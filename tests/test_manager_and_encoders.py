@@ -139,3 +139,46 @@ def test_rerank_endpoint(client):
     assert {x["index"] for x in r["results"]} <= {0, 1, 2} and "document" in r["results"][0]
     assert client.post("/rerank", json=body).json()["results"] == r["results"]
     assert client.post("/v1/rerank", json={"query": "", "documents": ["a"]}).status_code == 400
+
+
+def test_gateway_forwards_by_model_and_releases_leases(tmp_path):
+    """Two names, one runner: requests are forwarded to the runner serving the model and the
+    lease ends with the response; an unknown model is a 404 in OpenAI error shape."""
+    from orinfer_b200.api.chat_codec import ByteTokenizer, ChatCodec
+    from orinfer_b200.api.server import Service, create_app
+    from orinfer_b200.config import PRESETS, SchedulerOptions
+    from orinfer_b200.engine.engine import Engine
+    from orinfer_b200.models.weights import random_model
+    weights = random_model(PRESETS["tiny"], seed=0)
+    started, stopped = [], []
+
+    def start(entry):
+        svc = Service(lambda: Engine(weights, sched=SchedulerOptions(max_active=4, prefill_chunk=64),
+                                     kv_pages=24, max_context=512),
+                      ChatCodec(ByteTokenizer(1024), context=512, model_name=entry.name), entry.name)
+        svc.start()
+        started.append(entry.name)
+        return M.RunnerHandle(svc, create_app(svc)), weights.nbytes()
+
+    def stop(handle):
+        handle.service.stop(1000)
+        stopped.append(handle.service.model_name)
+
+    m = M.ModelManager(tmp_path, start, stop)
+    m.register("tiny", "/models/tiny")
+    m.copy("tiny", "tiny-alias")
+    with TestClient(M.create_gateway_app(m, sweep_s=3600)) as c:
+        body = {"model": "tiny-alias", "messages": [{"role": "user", "content": "hi"}],
+                "max_tokens": 4, "temperature": 0, "ignore_eos": True}
+        r = c.post("/v1/chat/completions", json=body)
+        assert r.status_code == 200 and r.json()["usage"]["completion_tokens"] == 4
+        r2 = c.post("/v1/chat/completions", json=dict(body, model="tiny"))
+        assert r2.json()["choices"][0]["message"] == r.json()["choices"][0]["message"]
+        assert started == ["tiny-alias"] and m.running()[0]["leases"] == 0
+        emb = c.post("/v1/embeddings", json={"model": "tiny", "input": "hello"})
+        assert emb.status_code == 200 and len(emb.json()["data"][0]["embedding"]) == 256
+        missing = c.post("/v1/chat/completions", json=dict(body, model="nope"))
+        assert missing.status_code == 404 and missing.json()["error"]["code"] == "model_not_found"
+        assert c.post("/api/generate", json={"model": "nope", "prompt": "x"}).status_code == 404
+        assert [x["name"] for x in c.get("/api/ps").json()["models"]] == ["tiny", "tiny-alias"]
+    assert stopped == ["tiny-alias"]                                # shutdown retired the runner
