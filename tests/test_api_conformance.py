@@ -1,0 +1,112 @@
+"""API conformance checks in the spirit of the reference's compatibility suite
+(tools/api/compatibility.py): seeds, cache hints, logit bias, JSON modes over SSE, request
+state isolation, token bytes in logprobs."""
+import json
+
+import pytest
+from fastapi.testclient import TestClient
+
+from orinfer_b200.api.chat_codec import ByteTokenizer, ChatCodec
+from orinfer_b200.api.server import Service, create_app
+from orinfer_b200.config import PRESETS, SchedulerOptions
+from orinfer_b200.engine.engine import Engine
+from orinfer_b200.models.weights import random_model
+
+MSG = [{"role": "user", "content": "hello"}]
+
+
+@pytest.fixture(scope="module")
+def client():
+    weights = random_model(PRESETS["tiny"], seed=0)
+    svc = Service(lambda: Engine(weights, sched=SchedulerOptions(max_active=4, prefill_chunk=64),
+                                 kv_pages=32, max_context=512),
+                  ChatCodec(ByteTokenizer(1024), context=512, model_name="tiny"), "tiny")
+    svc.start()
+    with TestClient(create_app(svc)) as c:
+        yield c
+    svc.stop(1000)
+
+
+def _chat(client, **kw):
+    body = dict(dict(messages=MSG, max_tokens=6, ignore_eos=True), **kw)
+    r = client.post("/v1/chat/completions", json=body)
+    assert r.status_code == 200, r.text
+    return r.json()
+
+
+def test_nullable_and_signed_seed(client):
+    a = _chat(client, temperature=1.0, seed=None)
+    assert a["choices"][0]["finish_reason"] == "length"
+    neg1 = _chat(client, temperature=1.0, seed=-5)
+    neg2 = _chat(client, temperature=1.0, seed=-5)
+    assert neg1["choices"][0]["message"] == neg2["choices"][0]["message"]
+    bad = client.post("/v1/chat/completions", json=dict(messages=MSG, seed="x"))
+    assert bad.status_code == 400 and bad.json()["error"]["param"] == "seed"
+
+
+def test_cache_hints_preserve_output(client):
+    plain = _chat(client, temperature=0)
+    hinted = _chat(client, temperature=0, prompt_cache_key="tenant-1", prompt_cache_retention="24h")
+    again = _chat(client, temperature=0, prompt_cache_key="tenant-1")
+    assert plain["choices"][0]["message"] == hinted["choices"][0]["message"] \
+        == again["choices"][0]["message"]
+
+
+def test_logit_bias_forces_and_bans_tokens(client):
+    forced = _chat(client, temperature=0, logit_bias={"65": 100})
+    assert forced["choices"][0]["message"]["content"] == "A" * 6
+    base = _chat(client, temperature=0, logprobs=True, top_logprobs=1)
+    first = base["choices"][0]["logprobs"]["content"][0]
+    tok_id = first["bytes"][0] if first.get("bytes") else None
+    if tok_id is not None and tok_id < 256:
+        banned = _chat(client, temperature=0, logit_bias={str(tok_id): -100}, logprobs=True)
+        assert banned["choices"][0]["logprobs"]["content"][0]["bytes"] != first["bytes"]
+    assert client.post("/v1/chat/completions",
+                       json=dict(messages=MSG, logit_bias={"65": 101})).status_code == 400
+
+
+def test_json_object_and_schema_over_sse(client):
+    obj = _chat(client, temperature=0, max_tokens=48, ignore_eos=False,
+                response_format={"type": "json_object"})
+    text = obj["choices"][0]["message"]["content"]
+    if obj["choices"][0]["finish_reason"] == "stop":
+        assert isinstance(json.loads(text), dict)
+    else:
+        assert text.lstrip().startswith("{")
+    schema = {"type": "object", "properties": {"ok": {"type": "boolean"}}, "required": ["ok"],
+              "additionalProperties": False}
+    body = dict(messages=MSG, max_tokens=48, temperature=0, stream=True,
+                response_format={"type": "json_schema",
+                                 "json_schema": {"name": "r", "schema": schema, "strict": True}})
+    with client.stream("POST", "/v1/chat/completions", json=body) as r:
+        chunks = [json.loads(l[6:]) for l in r.iter_lines()
+                  if l.startswith("data: ") and l != "data: [DONE]"]
+    text = "".join(c["choices"][0]["delta"].get("content") or "" for c in chunks if c["choices"])
+    assert json.loads(text)["ok"] in (True, False)
+    assert chunks[-1]["choices"][0]["finish_reason"] == "stop"
+
+
+def test_request_state_isolation(client):
+    """A request's output does not depend on what ran before it or beside it."""
+    import concurrent.futures as cf
+    solo = _chat(client, temperature=0.9, seed=11)["choices"][0]["message"]
+    others = [dict(messages=[{"role": "user", "content": f"noise {i}"}], max_tokens=9,
+                   temperature=1.0, seed=i, ignore_eos=True) for i in range(3)]
+    with cf.ThreadPoolExecutor(4) as pool:
+        futs = [pool.submit(client.post, "/v1/chat/completions", json=b) for b in others]
+        mixed = _chat(client, temperature=0.9, seed=11)["choices"][0]["message"]
+        assert all(f.result().status_code == 200 for f in futs)
+    assert mixed == solo
+
+
+def test_unicode_token_bytes_in_logprobs(client):
+    body = dict(messages=[{"role": "user", "content": "héllo ✓"}], max_tokens=5, temperature=0,
+                logprobs=True, top_logprobs=2, ignore_eos=True)
+    r = client.post("/v1/chat/completions", json=body).json()
+    entries = r["choices"][0]["logprobs"]["content"]
+    assert len(entries) == 5
+    for e in entries:
+        assert isinstance(e["bytes"], list) and all(0 <= b < 256 for b in e["bytes"])
+        assert e["logprob"] <= 0 and len(e["top_logprobs"]) == 2
+    raw = bytes(b for e in entries for b in e["bytes"])
+    assert raw.decode("utf-8", errors="replace") is not None
