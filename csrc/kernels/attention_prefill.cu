@@ -35,8 +35,8 @@ struct Smem {
   static constexpr int Q_OFF = 0;
   static constexpr int K_OFF = Q_OFF + NSUB * SUB;       // two K buffers
   static constexpr int V_OFF = K_OFF + 2 * NSUB * SUB;   // two V buffers
-  static constexpr int P_OFF = V_OFF + 2 * NSUB * SUB;   // P: 128 x 128 fp16 = 2 sub-tiles
-  static constexpr int BAR_OFF = P_OFF + 2 * SUB;
+  static constexpr int P_OFF = V_OFF + 2 * NSUB * SUB;   // two P buffers of 128 x 128 fp16
+  static constexpr int BAR_OFF = P_OFF + 2 * 2 * SUB;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
@@ -79,17 +79,17 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
   using L = Smem<D>;
   constexpr int NSUB = L::NSUB;
   constexpr int GROUPS = D / 64;
-  constexpr uint32_t TMEM_COLS = (128 + D) <= 256 ? 256 : 512;
+  constexpr uint32_t TMEM_COLS = 512;          // S0 | S1 (128 columns each) | O (D columns)
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* q_full = bars;            // Q tile landed
   uint64_t* kv_ready = bars + 1;      // [2] dequantised K/V buffer filled (128 arrivals)
-  uint64_t* s_full = bars + 3;        // S = QK^T finished
-  uint64_t* p_ready = bars + 4;       // P written, S consumed, O rescaled (128 arrivals)
-  uint64_t* o_done = bars + 5;        // O += PV finished (frees P; O may be rescaled)
-  uint64_t* kv_free = bars + 6;       // [2] the PV that read K/V buffer b finished
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* s_full = bars + 3;        // [2] S[b] = QK^T finished
+  uint64_t* p_ready = bars + 5;       // [2] P[b] written, S[b] consumed, O rescaled (128 arrivals)
+  uint64_t* o_done = bars + 7;        // O += PV finished (O may be rescaled)
+  uint64_t* kv_free = bars + 8;       // [2] the PV that read K/V buffer b finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const Chunk ch = chunks[blockIdx.z];
@@ -105,8 +105,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
     mbar_init(q_full, 1);
     mbar_init(&kv_ready[0], 128);
     mbar_init(&kv_ready[1], 128);
-    mbar_init(s_full, 1);
-    mbar_init(p_ready, 128);
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
+    mbar_init(&p_ready[0], 128);
+    mbar_init(&p_ready[1], 128);
     mbar_init(o_done, 1);
     mbar_init(&kv_free[0], 1);
     mbar_init(&kv_free[1], 1);
@@ -121,7 +123,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 256;   // S[b] at tmem_s + 128 * b
   const int* pages = page_table + static_cast<size_t>(ch.slot) * max_pages;
 
   if (warp == 0) {
@@ -139,29 +141,39 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
       const uint32_t q_addr = smem_u32(smem + L::Q_OFF);
       const uint32_t p_addr = smem_u32(smem + L::P_OFF);
       bool ok = mbar_wait(q_full, 0, status, STATUS_MMA_WAIT, 2);
-      for (int j = 0; j < n_tiles && ok; ++j) {
+      // S and P are double buffered: S(j+1) = Q K(j+1)^T is issued before O += P(j) V(j), so
+      // the tensor core works on the next scores while the softmax warps turn S(j) into P(j).
+      auto issue_qk = [&](int j) -> bool {
         const int b = j & 1;
-        const uint32_t k_addr = smem_u32(smem + L::K_OFF + b * NSUB * L::SUB);
-        const uint32_t v_addr = smem_u32(smem + L::V_OFF + b * NSUB * L::SUB);
-        ok = mbar_wait(&kv_ready[b], (j >> 1) & 1, status, STATUS_MMA_WAIT, 0x100 | j);
-        // S may only be overwritten once the softmax warps have consumed S of tile j-1
-        // (p_ready of j-1, waited below before PV of j-1), which program order guarantees.
-        if (!ok) break;
+        if (!mbar_wait(&kv_ready[b], (j >> 1) & 1, status, STATUS_MMA_WAIT, 0x100 | j))
+          return false;
         tc_fence_after();
+        const uint32_t k_addr = smem_u32(smem + L::K_OFF + b * NSUB * L::SUB);
 #pragma unroll
         for (int i = 0; i < D / 16; ++i) {
           const uint32_t off = (i / 4) * L::SUB + (i % 4) * 32;
-          mma_f16_ss(tmem_s, umma_desc(q_addr + off, 16, 1024), umma_desc(k_addr + off, 16, 1024),
-                     idesc_s, i != 0 ? 1u : 0u);
+          mma_f16_ss(tmem_s + 128 * b, umma_desc(q_addr + off, 16, 1024),
+                     umma_desc(k_addr + off, 16, 1024), idesc_s, i != 0 ? 1u : 0u);
         }
-        tc_commit(s_full);
-        ok = mbar_wait(p_ready, j & 1, status, STATUS_MMA_WAIT, 0x200 | j);
+        tc_commit(&s_full[b]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int b = j & 1;
+        // S[(j+1)&1] was last read by the softmax of tile j-1, whose p_ready this thread
+        // waited for before issuing PV(j-1): program order makes the overwrite safe.
+        if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+        if (!ok) break;
+        const uint32_t v_addr = smem_u32(smem + L::V_OFF + b * NSUB * L::SUB);
+        const uint32_t pj_addr = p_addr + b * 2 * L::SUB;
+        ok = mbar_wait(&p_ready[b], (j >> 1) & 1, status, STATUS_MMA_WAIT, 0x200 | j);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int i = 0; i < TILE / 16; ++i) {
           const uint32_t a_off = (i / 4) * L::SUB + (i % 4) * 32;
-          mma_f16_ss(tmem_o, umma_desc(p_addr + a_off, 16, 1024),
+          mma_f16_ss(tmem_o, umma_desc(pj_addr + a_off, 16, 1024),
                      umma_desc(v_addr + i * 2048, L::SUB, 1024), idesc_o, (j | i) != 0 ? 1u : 0u);
         }
         tc_commit(o_done);
@@ -179,31 +191,45 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
         report_status(status, STATUS_BAD_INDEX, 3);
         page = 0;
       }
+      unsigned char* kb = smem + L::K_OFF + b * NSUB * L::SUB;
+      unsigned char* vb = smem + L::V_OFF + b * NSUB * L::SUB;
+      constexpr int CPK = D / 16;                    // 16-byte chunks per key
+      constexpr int ITERS = TILE * CPK / 128;
+      // every load of the page is issued before the first conversion: one memory round trip
+      // per page instead of one per pair of chunks (the 128 dequant threads have no other
+      // way to hide latency)
+      uint4 kraw[ITERS], vraw[ITERS];
+      __half ksc[ITERS], vsc[ITERS];
+#pragma unroll
+      for (int it = 0; it < ITERS; ++it) {
+        const int idx = it * 128 + t;
+        const int key = idx / CPK, c = idx % CPK;
+        const size_t slot = (static_cast<size_t>(page) * 128 + key) * kvh + h;
+        kraw[it] = __ldg(reinterpret_cast<const uint4*>(kc + slot * D + c * 16));
+        vraw[it] = __ldg(reinterpret_cast<const uint4*>(vc + slot * D + c * 16));
+        ksc[it] = ks[slot * GROUPS + c / 4];
+        vsc[it] = vs[slot * GROUPS + c / 4];
+      }
       // buffer b was last read by the MMAs of tile j-2: wait for its PV to finish.  A
       // per-buffer barrier is used because a waiter two phases behind a shared barrier
       // would alias its parity.
       if (j >= 2)
         ok = mbar_wait(&kv_free[b], ((j >> 1) - 1) & 1, status, STATUS_DECODE_WAIT, j);
       if (!ok) break;
-      unsigned char* kb = smem + L::K_OFF + b * NSUB * L::SUB;
-      unsigned char* vb = smem + L::V_OFF + b * NSUB * L::SUB;
-      constexpr int CPK = D / 16;                    // 16-byte chunks per key
-#pragma unroll 2
-      for (int it = 0; it < TILE * CPK / 128; ++it) {
+#pragma unroll
+      for (int it = 0; it < ITERS; ++it) {
         const int idx = it * 128 + t;
         const int key = idx / CPK, c = idx % CPK;
-        const size_t slot = (static_cast<size_t>(page) * 128 + key) * kvh + h;
-        const uint4 kraw = __ldg(reinterpret_cast<const uint4*>(kc + slot * D + c * 16));
-        const uint4 vraw = __ldg(reinterpret_cast<const uint4*>(vc + slot * D + c * 16));
-        const __half2 ksc = __half2half2(ks[slot * GROUPS + c / 4]);
-        const __half2 vsc = __half2half2(vs[slot * GROUPS + c / 4]);
+        const __half2 k2 = __half2half2(ksc[it]), v2 = __half2half2(vsc[it]);
         const int sub = c / 4, chunk = (c % 4) * 2;
         unsigned char* kd = kb + sub * L::SUB;
         unsigned char* vd = vb + sub * L::SUB;
-        *reinterpret_cast<uint4*>(kd + swz128(key, chunk)) = dequant8(kraw.x, kraw.y, ksc);
-        *reinterpret_cast<uint4*>(kd + swz128(key, chunk + 1)) = dequant8(kraw.z, kraw.w, ksc);
-        *reinterpret_cast<uint4*>(vd + swz128(key, chunk)) = dequant8(vraw.x, vraw.y, vsc);
-        *reinterpret_cast<uint4*>(vd + swz128(key, chunk + 1)) = dequant8(vraw.z, vraw.w, vsc);
+        *reinterpret_cast<uint4*>(kd + swz128(key, chunk)) = dequant8(kraw[it].x, kraw[it].y, k2);
+        *reinterpret_cast<uint4*>(kd + swz128(key, chunk + 1)) =
+            dequant8(kraw[it].z, kraw[it].w, k2);
+        *reinterpret_cast<uint4*>(vd + swz128(key, chunk)) = dequant8(vraw[it].x, vraw[it].y, v2);
+        *reinterpret_cast<uint4*>(vd + swz128(key, chunk + 1)) =
+            dequant8(vraw[it].z, vraw[it].w, v2);
       }
       fence_proxy_async();
       mbar_arrive(&kv_ready[b]);
@@ -217,26 +243,37 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
     const int q_pos = valid ? ch.pos0 + p_first + p_rel : -1;
     const float scale = rsqrtf(static_cast<float>(D)) * 1.4426950408889634f;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    unsigned char* pb = smem + L::P_OFF;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      ok = mbar_wait(s_full, j & 1, status, STATUS_EPILOGUE_WAIT, j);
+      const int sb = j & 1;
+      const uint32_t tmem_sj = tmem_s + 128 * sb;
+      unsigned char* pb = smem + L::P_OFF + sb * 2 * L::SUB;
+      ok = mbar_wait(&s_full[sb], (j >> 1) & 1, status, STATUS_EPILOGUE_WAIT, j);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       const int key0 = j * TILE;
-      // pass 1: row maximum
-      float m_tile = -INFINITY;
+      // Only the last page of a row can hold keys beyond its position; every earlier page
+      // takes the mask-free path (one FMNMX per score here, FFMA + EX2 per score below).
+      const bool full = key0 + TILE - 1 <= q_pos;
+      // pass 1: row maximum (of the raw scores: the scale is positive)
+      float m_raw = -INFINITY;
 #pragma unroll 1
       for (int c0 = 0; c0 < TILE; c0 += 32) {
         uint32_t r[32];
-        tmem_ld_32x32(tmem_s + lane_addr + c0, r);
+        tmem_ld_32x32(tmem_sj + lane_addr + c0, r);
         tc_wait_ld();
+        if (full) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (key0 + c0 + i <= q_pos) m_tile = fmaxf(m_tile, __uint_as_float(r[i]) * scale);
+          for (int i = 0; i < 32; ++i) m_raw = fmaxf(m_raw, __uint_as_float(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (key0 + c0 + i <= q_pos) m_raw = fmaxf(m_raw, __uint_as_float(r[i]));
+        }
       }
+      const float m_tile = m_raw * scale;               // -inf stays -inf
       const float m_new = fmaxf(m_run, m_tile);
       const float corr = (m_new == -INFINITY) ? 1.f : exp2f(m_run - m_new);
       // P buffer and O are free once PV of tile j-1 has finished
@@ -263,18 +300,29 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
 #pragma unroll 1
       for (int c0 = 0; c0 < TILE; c0 += 32) {
         uint32_t r[32];
-        tmem_ld_32x32(tmem_s + lane_addr + c0, r);
+        tmem_ld_32x32(tmem_sj + lane_addr + c0, r);
         tc_wait_ld();
         uint32_t packed[16];
+        if (full) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = 0.f, p1 = 0.f;
-          if (key0 + c0 + i <= q_pos) p0 = exp2f(__uint_as_float(r[i]) * scale - m_new);
-          if (key0 + c0 + i + 1 <= q_pos) p1 = exp2f(__uint_as_float(r[i + 1]) * scale - m_new);
-          const __half2 hp = __floats2half2_rn(p0, p1);
-          // sum what the tensor core will actually multiply (the rounded values)
-          l_tile += __low2float(hp) + __high2float(hp);
-          packed[i / 2] = *reinterpret_cast<const uint32_t*>(&hp);
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = exp2f(fmaf(__uint_as_float(r[i]), scale, -m_new));
+            const float p1 = exp2f(fmaf(__uint_as_float(r[i + 1]), scale, -m_new));
+            l_tile += p0 + p1;
+            const __half2 hp = __floats2half2_rn(p0, p1);
+            packed[i / 2] = *reinterpret_cast<const uint32_t*>(&hp);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = 0.f, p1 = 0.f;
+            if (key0 + c0 + i <= q_pos) p0 = exp2f(fmaf(__uint_as_float(r[i]), scale, -m_new));
+            if (key0 + c0 + i + 1 <= q_pos)
+              p1 = exp2f(fmaf(__uint_as_float(r[i + 1]), scale, -m_new));
+            l_tile += p0 + p1;
+            const __half2 hp = __floats2half2_rn(p0, p1);
+            packed[i / 2] = *reinterpret_cast<const uint32_t*>(&hp);
+          }
         }
         // keys c0..c0+31 -> sub-tile c0/64, 16-byte chunks ((c0 % 64) / 8) .. +3
         unsigned char* dst = pb + (c0 / 64) * L::SUB;
@@ -288,7 +336,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
       m_run = m_new;
       tc_fence_before();
       fence_proxy_async();
-      mbar_arrive(p_ready);
+      mbar_arrive(&p_ready[sb]);
     }
     if (ok) {
       ok = mbar_wait(o_done, (n_tiles - 1) & 1, status, STATUS_EPILOGUE_WAIT, 0x300);
