@@ -260,17 +260,21 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
       // pass 1: row maximum (of the raw scores: the scale is positive)
       float m_raw = -INFINITY;
 #pragma unroll 1
-      for (int c0 = 0; c0 < TILE; c0 += 32) {
-        uint32_t r[32];
+      for (int c0 = 0; c0 < TILE; c0 += 64) {
+        uint32_t r[32], r2[32];                           // two TMEM loads in flight
         tmem_ld_32x32(tmem_sj + lane_addr + c0, r);
+        tmem_ld_32x32(tmem_sj + lane_addr + c0 + 32, r2);
         tc_wait_ld();
         if (full) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) m_raw = fmaxf(m_raw, __uint_as_float(r[i]));
+          for (int i = 0; i < 32; ++i)
+            m_raw = fmaxf(m_raw, fmaxf(__uint_as_float(r[i]), __uint_as_float(r2[i])));
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
+          for (int i = 0; i < 32; ++i) {
             if (key0 + c0 + i <= q_pos) m_raw = fmaxf(m_raw, __uint_as_float(r[i]));
+            if (key0 + c0 + 32 + i <= q_pos) m_raw = fmaxf(m_raw, __uint_as_float(r2[i]));
+          }
         }
       }
       const float m_tile = m_raw * scale;               // -inf stays -inf
