@@ -139,6 +139,10 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // peer epilogue staging: one padded FP16 row per output row (pad keeps 16-byte stores of
+  // 32 consecutive rows on distinct banks)
+  constexpr int STAGE_ROW = BN * 2 + 16;
+  static_assert(MT * BM * STAGE_ROW <= L::LUT_OFF, "staged tile must fit in the operand rings");
 
   if (warp == 0) {
     if (lane == 0) {
@@ -297,20 +301,13 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
                 v[j] = (static_cast<float>(static_cast<int>(r[g * 8 + j])) *
                         __half2float(w_scale[n + j])) * sa;
               if (po.tp > 0) {
-                // fused scatter: FP16 partial tile -> slot [rank] of the peers' inboxes
+                // fused scatter, step 1: the FP16 partial tile is staged in the (now idle)
+                // operand rings so that it can leave for the peers in whole rows
                 __align__(16) __half h[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
-                const size_t off = (static_cast<size_t>(po.rank) * po.rows_cap + m) * N + n;
-                if (po.rows_per > 0) {
-                  // reduce-scatter: only the owner of row m receives this partial
-                  *reinterpret_cast<int4*>(po.inbox[min(m / po.rows_per, po.tp - 1)] + off) =
-                      *reinterpret_cast<const int4*>(h);
-                } else {
-                  for (int d = 0; d < po.tp; ++d)
-                    *reinterpret_cast<int4*>(po.inbox[d] + off) =
-                        *reinterpret_cast<const int4*>(h);
-                }
+                *reinterpret_cast<int4*>(smem + static_cast<size_t>(mt * BM + row) * STAGE_ROW +
+                                         (c0 + g * 8) * 2) = *reinterpret_cast<const int4*>(h);
               } else if (OUT_F32) {
                 float* o = reinterpret_cast<float*>(out) + static_cast<size_t>(m) * N + n;
                 *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
@@ -324,6 +321,30 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
               }
             }
           }
+        }
+      }
+    }
+  }
+  if (warp >= 2 && po.tp > 0 && partial == nullptr) {
+    // fused scatter, step 2: every producer warp joins (also after a failed wait, so that
+    // nobody is left at the barrier), then whole 16-byte segments of consecutive columns go
+    // out lane by lane: a warp writes two complete 256-byte rows per instruction instead of
+    // 32 rows x 16 bytes, which is what keeps NVLink packets full.
+    asm volatile("bar.sync 1, %0;" ::"n"(PRODUCERS) : "memory");
+    constexpr int SEGS = BN / 8;                          // 16-byte segments per row
+    const int t = threadIdx.x - 64;
+    for (int idx = t; idx < MT * BM * SEGS; idx += PRODUCERS) {
+      const int r = idx / SEGS, seg = idx % SEGS;
+      const int m = m0 + r, n = n0 + seg * 8;
+      if (m < m_limit && n + 8 <= n_end) {
+        const int4 val = *reinterpret_cast<const int4*>(smem + static_cast<size_t>(r) * STAGE_ROW +
+                                                        seg * 16);
+        const size_t off = (static_cast<size_t>(po.rank) * po.rows_cap + m) * N + n;
+        if (po.rows_per > 0) {
+          // reduce-scatter: only the owner of row m receives this partial
+          *reinterpret_cast<int4*>(po.inbox[min(m / po.rows_per, po.tp - 1)] + off) = val;
+        } else {
+          for (int d = 0; d < po.tp; ++d) *reinterpret_cast<int4*>(po.inbox[d] + off) = val;
         }
       }
     }
