@@ -27,7 +27,9 @@ typedef struct OrinferPeerOut {
   unsigned int* ticket;        // local CTA counter (device memory, zero)
   int tp, rank, rows_cap;
   int rows_per;                // 0: push every row to every rank (all-reduce);
-                               // > 0: row m only to rank m / rows_per (reduce-scatter)
+                               // > 0: row m only to rank m / rows_per (reduce-scatter);
+                               // -1: low-latency all-reduce (<= 8 rows, Q4/Q2 weights): inbox[]
+                               //     are the LL regions, sent / ticket the LL counters
 } OrinferPeerOut;
 
 // Sequence-parallel all-gather by push (see tp_comm.cuh).
@@ -54,6 +56,8 @@ typedef struct OrinferInbox {
   int* seen;                   // local sequence counter (device memory)
   unsigned int* ticket;        // local CTA counter (device memory, zero)
   int tp, rows_cap;
+  const void* ll;              // non-null: low-latency form (<= 8 rows): uint2 [tp][8][n / 2]
+                               // units {2 x fp16, sequence number}; seen / ticket are its counters
 } OrinferInbox;
 
 // Owner rows [rank*rows_per, ...) only: sum the tp partial rows of the inbox, add the

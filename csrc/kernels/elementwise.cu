@@ -91,10 +91,28 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
     const __half* xr = x ? x + static_cast<size_t>(row) * K : nullptr;
     float* rr = resid ? resid + static_cast<size_t>(row) * K : nullptr;
     const bool from_inbox = in.inbox != nullptr;
-    if (from_inbox) inbox_wait(in, status);       // a timed-out wait is reported; data may be stale
+    const bool from_ll = in.ll != nullptr;
+    const int ll_seq = from_ll ? *reinterpret_cast<volatile int*>(in.seen) + 1 : 0;
+    if (from_inbox && !from_ll) inbox_wait(in, status);   // a timed-out wait is reported
     for (int i = tid * 8; i < K; i += blockDim.x * 8) {
       float v[8];
-      if (from_inbox) {
+      if (from_ll) {
+        // low-latency form: each unit carries its own sequence number; sum the sources in
+        // fixed order as soon as their units have arrived
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = 0.f;
+        for (int s = 0; s < in.tp; ++s) {
+          const uint2* src = in.ll + (static_cast<size_t>(s) * LL_ROWS + row) * (K / 2) + i / 2;
+          uint32_t w[4];
+          ll_load4(src, ll_seq, w[0], w[1], status, s);
+          ll_load4(src + 2, ll_seq, w[2], w[3], status, s);
+          const __half* h = reinterpret_cast<const __half*>(w);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] += __half2float(h[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = round_f16(v[j]);
+      } else if (from_inbox) {
         // sum the tp partial rows in fixed source order; bypass L1 (peers wrote this memory)
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = 0.f;
@@ -216,7 +234,7 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
     c.w = static_cast<signed char>(a8_code(rowbuf[i + 3], scale));
     *reinterpret_cast<char4*>(qr + i) = c;
   }
-  if (!SWIGLU && in.inbox != nullptr) inbox_consumed(in, gridDim.x);
+  if (!SWIGLU && (in.inbox != nullptr || in.ll != nullptr)) inbox_consumed(in, gridDim.x);
 }
 
 __global__ void ag_wait_kernel(AgIn in, int rows, int* status) {
@@ -404,13 +422,19 @@ int orinfer_act_prep_inbox(const OrinferInbox* inbox, float* resid, const __half
                            const int8_t* signs, int8_t* q_out, float* scale_out, __half* y_out,
                            int rows, int K, float eps, int zero_centered, cudaStream_t stream) {
   if (inbox == nullptr || inbox->tp < 1 || inbox->tp > TP_MAX || rows > inbox->rows_cap) return -1;
-  InboxIn in;
+  InboxIn in{};
   in.inbox = reinterpret_cast<const __half*>(inbox->inbox);
   in.flag = inbox->flag;
   in.seen = inbox->seen;
   in.ticket = inbox->ticket;
   in.tp = inbox->tp;
   in.rows_cap = inbox->rows_cap;
+  in.ll = nullptr;
+  if (inbox->ll != nullptr) {             // low-latency form: decode-sized packets only
+    if (rows > LL_ROWS) return -1;
+    in.ll = reinterpret_cast<const uint2*>(inbox->ll);
+    in.inbox = nullptr;
+  }
   return act_prep_launch(nullptr, resid, norm_w, signs, q_out, scale_out, y_out, rows, K, eps,
                          zero_centered, 0, in, stream);
 }
@@ -425,7 +449,7 @@ int orinfer_act_prep_inbox_rows(const OrinferInbox* inbox, float* resid, const _
   if (inbox == nullptr || inbox->tp < 1 || inbox->tp > TP_MAX || row_base < 0 || count < 1 ||
       row_base + count > inbox->rows_cap)
     return -1;
-  InboxIn in;
+  InboxIn in{};
   in.inbox = reinterpret_cast<const __half*>(inbox->inbox);
   in.flag = inbox->flag;
   in.seen = inbox->seen;

@@ -593,7 +593,8 @@ extern "C" int orinfer_qgemm_peer(int fmt, const int8_t* a, const float* a_scale
   po.rank = peer->rank;
   po.rows_cap = peer->rows_cap;
   po.rows_per = peer->rows_per;
-  if (po.rows_per < 0 || (po.rows_per > 0 && (M <= 8 || force_path == 1))) return -1;
+  if (po.rows_per < LL_MODE || (po.rows_per > 0 && (M <= 8 || force_path == 1))) return -1;
+  if (po.rows_per == LL_MODE && (M > LL_ROWS || fmt == 0 || N % 16 || force_path == 2)) return -1;
   return qgemm_any(fmt, a, a_scale, w, w_scale, nullptr, M, N, K, 0, force_path, stream, &po);
 }
 

@@ -117,6 +117,8 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
   constexpr int WPL = 128 / LPR;                 // weights per lane per k-block
   constexpr int DEPTH = 4;
   const PeerOut* peer = po.tp > 0 ? &po : nullptr;
+  const bool ll = peer != nullptr && po.rows_per == LL_MODE;
+  const int ll_seq = ll ? *reinterpret_cast<volatile int*>(po.sent) + 1 : 0;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int COPIES = MT == 1 ? 1 : 16;
   using Table = E8pBanked<COPIES>;
@@ -217,10 +219,14 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
               h[r] = __float2half_rn(
                   (static_cast<float>(total) * __half2float(w_scale[n0 + seg * 8 + r])) * sa);
             }
-            const size_t off =
-                (static_cast<size_t>(po.rank) * po.rows_cap + m) * N + n0 + seg * 8;
-            for (int d = 0; d < po.tp; ++d)
-              *reinterpret_cast<int4*>(po.inbox[d] + off) = *reinterpret_cast<const int4*>(h);
+            if (ll) {
+              ll_store8(po, ll_seq, m, n0 + seg * 8, N, h);
+            } else {
+              const size_t off =
+                  (static_cast<size_t>(po.rank) * po.rows_cap + m) * N + n0 + seg * 8;
+              for (int d = 0; d < po.tp; ++d)
+                *reinterpret_cast<int4*>(po.inbox[d] + off) = *reinterpret_cast<const int4*>(h);
+            }
           }
         }
       } else {
@@ -242,7 +248,8 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
 #pragma unroll
     for (int i = 0; i < DEPTH; ++i) cur[i] = nxt[i];
   }
-  if (peer != nullptr) peer_signal_done(po, gridDim.x);
+  if (ll) ll_done(po, ll_seq, gridDim.x);
+  else if (peer != nullptr) peer_signal_done(po, gridDim.x);
 }
 
 // W8: one warp per output row, 16 weights per lane per step.

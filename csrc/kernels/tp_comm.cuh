@@ -57,6 +57,8 @@ struct InboxIn {                 // consumer side
   int* seen;                     // local: sequence number consumed so far
   unsigned int* ticket;          // local: CTA completion counter
   int tp, rows_cap;
+  const uint2* ll;               // non-null: low-latency form, [tp][LL_ROWS][n / 2] units;
+                                 // `seen` / `ticket` are then the LL counters
 };
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
@@ -111,6 +113,64 @@ __device__ __forceinline__ bool ag_wait(const AgIn& in, int m_lo, int m_hi, int*
     }
   }
   return true;
+}
+
+// ---- low-latency form for decode-sized packets (<= 8 rows): no flag, no fence.  Every
+// 8-byte unit carries two FP16 values and the sequence number of the step, so data and
+// "ready" arrive in the same NVLink store; the consumer spins (bounded) on the units it needs.
+// PeerOut.rows_per == LL_MODE selects it; PeerOut.inbox[] then point at the LL regions
+// (uint2 [tp][LL_ROWS][n / 2], zero-initialised, sequence numbers only ever grow) and
+// `sent` / `ticket` are the LL counters.
+constexpr int LL_MODE = -1;
+constexpr int LL_ROWS = 8;
+
+__device__ __forceinline__ void ll_store8(const PeerOut& po, int seq, int m, int n, int N,
+                                          const __half* h) {
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(h);
+  const uint4 lo = make_uint4(w[0], static_cast<uint32_t>(seq), w[1], static_cast<uint32_t>(seq));
+  const uint4 hi = make_uint4(w[2], static_cast<uint32_t>(seq), w[3], static_cast<uint32_t>(seq));
+  const size_t unit = (static_cast<size_t>(po.rank) * LL_ROWS + m) * (N / 2) + n / 2;
+  for (int d = 0; d < po.tp; ++d) {
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint2*>(po.inbox[d]) + unit);
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(lo.x),
+                 "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 1), "r"(hi.x),
+                 "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
+  }
+}
+
+// Last CTA of the producer grid records the sequence number it used (local, no fence: the
+// consumer learns readiness from the data itself).
+__device__ __forceinline__ void ll_done(const PeerOut& po, int seq, unsigned int total_ctas) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int t = atomicAdd(po.ticket, 1u);
+    if (t == total_ctas - 1) {
+      *po.ticket = 0;
+      *po.sent = seq;
+    }
+  }
+}
+
+// Two units (four FP16 values) of source s; spins until both carry `seq` (bounded).
+__device__ __forceinline__ bool ll_load4(const uint2* base, int seq, uint32_t& a, uint32_t& b,
+                                         int* status, int s) {
+  const long long start = clock64();
+  for (;;) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(base) : "memory");
+    if (static_cast<int>(v.y) == seq && static_cast<int>(v.w) == seq) {
+      a = v.x;
+      b = v.z;
+      return true;
+    }
+    if (clock64() - start > WAIT_LIMIT_CYCLES) {
+      report_status(status, STATUS_PEER_WAIT, 0x400 | s);
+      a = b = 0;
+      return false;
+    }
+  }
 }
 
 // Thread 0 of a consumer CTA waits for every source; false when a wait ran out.

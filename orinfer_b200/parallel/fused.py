@@ -76,7 +76,10 @@ SP_MIN_ROWS = int(os.environ.get("ORINFER_TP_SP_MIN_ROWS", "256"))
 
 class _Inbox(ctypes.Structure):
     _fields_ = [("inbox", c_void_p), ("flag", c_void_p), ("seen", c_void_p),
-                ("ticket", c_void_p), ("tp", c_int), ("rows_cap", c_int)]
+                ("ticket", c_void_p), ("tp", c_int), ("rows_cap", c_int), ("ll", c_void_p)]
+
+
+LL_MODE, LL_ROWS = -1, 8
 
 
 OPS = ("o", "down")
@@ -105,7 +108,10 @@ class PeerMemory:
         ag_q_bytes = (rows_cap * hidden + 255) // 256 * 256
         ag_s_bytes = (rows_cap * 4 + 255) // 256 * 256
         ag_off = len(OPS) * (inbox_bytes + flag_bytes)
-        total = ag_off + ag_q_bytes + ag_s_bytes + flag_bytes
+        # low-latency regions (decode-sized packets): units of {2 x fp16, sequence number}
+        ll_bytes = (self.world * LL_ROWS * (hidden // 2) * 8 + 255) // 256 * 256
+        ll_off = ag_off + ag_q_bytes + ag_s_bytes + flag_bytes
+        total = ll_off + len(OPS) * ll_bytes
         self.base = lib.orinfer_peer_alloc(total)
         if not self.base:
             raise native.KernelError(f"cannot allocate {total} bytes of peer memory")
@@ -129,6 +135,8 @@ class PeerMemory:
         lp = self.local.data_ptr()
         self.peer_out: Dict[str, _PeerOut] = {}
         self.inbox: Dict[str, _Inbox] = {}
+        self.ll_out: Dict[str, _PeerOut] = {}
+        self.ll_in: Dict[str, _Inbox] = {}
         for i, op in enumerate(OPS):
             off_inbox = i * (inbox_bytes + flag_bytes)
             off_flag = off_inbox + inbox_bytes
@@ -140,8 +148,19 @@ class PeerMemory:
             po.ticket = lp + (4 * i + 1) * 4
             po.tp, po.rank, po.rows_cap = self.world, self.rank, rows_cap
             ib = _Inbox(bases[self.rank] + off_inbox, bases[self.rank] + off_flag,
-                        lp + (4 * i + 2) * 4, lp + (4 * i + 3) * 4, self.world, rows_cap)
+                        lp + (4 * i + 2) * 4, lp + (4 * i + 3) * 4, self.world, rows_cap, None)
             self.peer_out[op], self.inbox[op] = po, ib
+            # low-latency twin of the same op: own regions and counters
+            lo = _PeerOut()
+            for r in range(8):
+                lo.inbox[r] = bases[r] + ll_off + i * ll_bytes if r < self.world else None
+                lo.flag[r] = None
+            lo.sent = lp + (40 + 4 * i + 0) * 4
+            lo.ticket = lp + (40 + 4 * i + 1) * 4
+            lo.tp, lo.rank, lo.rows_cap, lo.rows_per = self.world, self.rank, rows_cap, LL_MODE
+            li = _Inbox(None, None, lp + (40 + 4 * i + 2) * 4, lp + (40 + 4 * i + 3) * 4,
+                        self.world, rows_cap, bases[self.rank] + ll_off + i * ll_bytes)
+            self.ll_out[op], self.ll_in[op] = lo, li
         # all-gather activation buffer (INT8 rows + scales) and its flags
         ag = _AgOut()
         for r in range(8):
@@ -202,6 +221,7 @@ class FusedTPRunner(TPRunner):
         self.lib = _setup_lib()
         self.mem = PeerMemory(self.cfg.hidden, max_rows, group, self.device)
         self._sp_rows_per, self._sp_total = 0, 0
+        self._ll = os.environ.get("ORINFER_TP_LL", "1") != "0"
 
     _SLOT = {"o": "o", "gdn_out": "o", "down": "down"}
 
@@ -285,6 +305,14 @@ class FusedTPRunner(TPRunner):
 
     def _row_parallel(self, name: str, lin: QLinear, q8, sc, rows: int):
         name = self._SLOT[name]
+        if rows <= LL_ROWS and lin.fmt != "w8" and lin.n % 16 == 0 and self._ll:
+            # decode-sized: data and readiness travel in the same 8-byte units
+            po = self.mem.ll_out[name]
+            check(self.lib.orinfer_qgemm_peer(FMT[lin.fmt], ptr(q8), ptr(sc), ptr(lin.codes),
+                                              ptr(lin.scale), ctypes.byref(po), rows, lin.n,
+                                              lin.k, 0, stream()), "qgemm_peer_ll")
+            count_launches(1)
+            return (name, LL_MODE)
         po = self.mem.peer_out[name]
         po.rows_per = self._sp_rows_per if rows == self._sp_total else 0
         check(self.lib.orinfer_qgemm_peer(FMT[lin.fmt], ptr(q8), ptr(sc), ptr(lin.codes),
@@ -298,7 +326,10 @@ class FusedTPRunner(TPRunner):
             return super()._prep(x, norm_w, signs, rows, y_out)
         cfg, ws = self.cfg, self.ws
         name, rows_per = x if isinstance(x, tuple) else (x, 0)
-        ib = self.mem.inbox[name] if name != "local" else None
+        if rows_per == LL_MODE:
+            ib, rows_per = self.mem.ll_in[name], 0
+        else:
+            ib = self.mem.inbox[name] if name != "local" else None
         if rows_per:
             if y_out is not None:
                 raise native.KernelError("sequence-parallel norm has no fp16 output")
@@ -335,7 +366,7 @@ class FusedTPRunner(TPRunner):
         return out
 
     def _head(self, x, p, out):
-        if isinstance(x, torch.Tensor) or not (isinstance(x, tuple) and x[1]):
+        if isinstance(x, torch.Tensor) or not (isinstance(x, tuple) and x[1] > 0):
             return super()._head(x, p, out)
         # sequence-parallel: owners normalise + rotate + quantise their rows and push them to
         # every rank; wait for all sources, pick the rows that need logits, run the local
