@@ -201,10 +201,18 @@ int orinfer_small_proj(const __half* x, const __half* w, float* out, int rows, i
                        cudaStream_t stream);
 int orinfer_gdn_conv(const __half* x, int x_stride, const __half* weight, __half* hist,
                      const int* row_first, const int* row_slot, const int* row_pos,
-                     const int* segs, int n_segs, int rows, int hk, int hv, int head_dim, __half* y, cudaStream_t stream);
+                     const int* segs, int n_segs, int rows, int hk, int hv, int head_dim, __half* y,
+                     cudaStream_t stream, int update_history);
 int orinfer_gdn_scan(const __half* qkv, const float* ab, const float* a_log, const float* dt_bias,
                      const int* segs, int n_segs, const int* row_slot, const int* row_pos, int hk,
-                     int hv, int head_dim, float* state, float* out, cudaStream_t stream);
+                     int hv, int head_dim, float* state, float* out, cudaStream_t stream,
+                     float* factors);
+// factors: fp32 [rows, HV, 2*D + 1] recorded by a scan with factors != NULL (which leaves the
+// state untouched); accepted: int32 [n_segs] rows of each segment to keep.
+int orinfer_gdn_commit(const __half* x, int x_stride, const float* factors, const int* segs,
+                       int n_segs, const int* accepted, const int* row_slot, const int* row_pos,
+                       int hk, int hv, int head_dim, __half* hist, float* state,
+                       cudaStream_t stream);
 int orinfer_gdn_gated_norm(const float* o, const __half* z, int z_stride, const __half* w,
                            float eps, int sigmoid_gate, int rows, int hv, int head_dim,
                            __half* y, cudaStream_t stream);

@@ -97,8 +97,13 @@ __global__ void __launch_bounds__(256) gdn_history_kernel(const __half* __restri
                                                           const int* __restrict__ row_slot,
                                                           const int* __restrict__ row_pos,
                                                           int conv_dim,
-                                                          __half* __restrict__ hist) {
-  const Segment s = segs[blockIdx.x];
+                                                          __half* __restrict__ hist,
+                                                          const int* __restrict__ accepted) {
+  Segment s = segs[blockIdx.x];
+  if (accepted != nullptr) {                 // commit of a verified prefix of the rows
+    s.rows = min(accepted[blockIdx.x], s.rows);
+    if (s.rows <= 0) return;
+  }
   const bool fresh = row_pos[s.row_start] == 0;
   __half* h = hist + static_cast<size_t>(row_slot[s.row_start]) * 3 * conv_dim;
   for (int c = threadIdx.x; c < conv_dim; c += blockDim.x) {
@@ -123,7 +128,10 @@ __global__ void __launch_bounds__(256) gdn_scan_kernel(
     const float* __restrict__ a_log, const float* __restrict__ dt_bias,
     const Segment* __restrict__ segs, const int* __restrict__ row_slot,
     const int* __restrict__ row_pos, int hk, int hv, float* __restrict__ state,
-    float* __restrict__ out) {
+    float* __restrict__ out, float* __restrict__ factors) {
+  // factors != nullptr: a verification pass.  The state is NOT written back; instead every
+  // step records (decay, k[D], delta[D]) so that gdn_commit can replay exactly the accepted
+  // prefix of the rows onto the stored state.
   constexpr int PARTS = 256 / D, ROWS = D / PARTS;
   const int vh = blockIdx.x;
   const Segment seg = segs[blockIdx.y];
@@ -166,6 +174,12 @@ __global__ void __launch_bounds__(256) gdn_scan_kernel(
 #pragma unroll
     for (int i = 0; i < PARTS; ++i) full += part[i][dv];
     const float delta = beta * (v - full);
+    if (factors != nullptr) {
+      float* f = factors + (row * hv + vh) * (2 * D + 1);
+      if (threadIdx.x == 0) f[0] = decay;
+      if (part_id == 0) f[1 + D + dv] = delta;
+      if (threadIdx.x < D) f[1 + threadIdx.x] = ks[threadIdx.x];
+    }
     float o = 0.f;
 #pragma unroll
     for (int i = 0; i < ROWS; ++i) {
@@ -180,6 +194,38 @@ __global__ void __launch_bounds__(256) gdn_scan_kernel(
       for (int i = 0; i < PARTS; ++i) tot += opart[i][dv];
       out[(row * hv + vh) * D + dv] = tot;
     }
+  }
+  if (factors == nullptr) {
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) sp[static_cast<size_t>(i) * D] = s[i];
+  }
+}
+
+// Replays the first accepted[seg] recorded steps of every segment onto the stored state:
+// S = decay * S + k (x) delta, in row order.  Same thread layout as the scan.
+template <int D>
+__global__ void __launch_bounds__(256) gdn_commit_kernel(
+    const float* __restrict__ factors, const Segment* __restrict__ segs,
+    const int* __restrict__ accepted, const int* __restrict__ row_slot,
+    const int* __restrict__ row_pos, int hv, float* __restrict__ state) {
+  constexpr int PARTS = 256 / D, ROWS = D / PARTS;
+  const int vh = blockIdx.x;
+  const Segment seg = segs[blockIdx.y];
+  const int steps = min(accepted[blockIdx.y], seg.rows);
+  if (steps <= 0) return;
+  const int dv = threadIdx.x % D, part_id = threadIdx.x / D;
+  const int slot = row_slot[seg.row_start];
+  const bool fresh = row_pos[seg.row_start] == 0;
+  float* sp = state + ((static_cast<size_t>(slot) * hv + vh) * D + part_id * ROWS) * D + dv;
+  float s[ROWS];
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) s[i] = fresh ? 0.f : sp[static_cast<size_t>(i) * D];
+  for (int t = 0; t < steps; ++t) {
+    const float* f =
+        factors + (static_cast<size_t>(seg.row_start + t) * hv + vh) * (2 * D + 1);
+    const float decay = f[0], delta = f[1 + D + dv];
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) s[i] = fmaf(f[1 + part_id * ROWS + i], delta, s[i] * decay);
   }
 #pragma unroll
   for (int i = 0; i < ROWS; ++i) sp[static_cast<size_t>(i) * D] = s[i];
@@ -227,7 +273,8 @@ int orinfer_small_proj(const __half* x, const __half* w, float* out, int rows, i
 int orinfer_gdn_conv(const __half* x, int x_stride, const __half* weight, __half* hist,
                      const int* row_first, const int* row_slot, const int* row_pos,
                      const int* segs, int n_segs,
-                     int rows, int hk, int hv, int head_dim, __half* y, cudaStream_t stream) {
+                     int rows, int hk, int hv, int head_dim, __half* y, cudaStream_t stream,
+                     int update_history) {
   if (rows <= 0) return 0;
   if (head_dim != 128 && head_dim != 64) return -1;
   const int conv_dim = (2 * hk + hv) * head_dim;
@@ -238,9 +285,32 @@ int orinfer_gdn_conv(const __half* x, int x_stride, const __half* weight, __half
   else
     gdn_conv_kernel<64><<<grid, 64, 0, stream>>>(x, x_stride, weight, hist, row_first, row_slot,
                                                  row_pos, conv_dim, 2 * hk, y);
-  gdn_history_kernel<<<n_segs, 256, 0, stream>>>(x, x_stride,
-                                                 reinterpret_cast<const Segment*>(segs), row_slot,
-                                                 row_pos, conv_dim, hist);
+  if (update_history)
+    gdn_history_kernel<<<n_segs, 256, 0, stream>>>(x, x_stride,
+                                                   reinterpret_cast<const Segment*>(segs),
+                                                   row_slot, row_pos, conv_dim, hist, nullptr);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Commit of a verification pass: advances the convolution history by the first accepted[s]
+// rows of every segment (x = the pre-convolution rows kept from the pass) and replays the
+// recorded state updates of those rows.
+int orinfer_gdn_commit(const __half* x, int x_stride, const float* factors, const int* segs,
+                       int n_segs, const int* accepted, const int* row_slot, const int* row_pos,
+                       int hk, int hv, int head_dim, __half* hist, float* state,
+                       cudaStream_t stream) {
+  if (n_segs <= 0) return 0;
+  if (head_dim != 128 && head_dim != 64) return -1;
+  const Segment* sg = reinterpret_cast<const Segment*>(segs);
+  const int conv_dim = (2 * hk + hv) * head_dim;
+  gdn_history_kernel<<<n_segs, 256, 0, stream>>>(x, x_stride, sg, row_slot, row_pos, conv_dim,
+                                                 hist, accepted);
+  if (head_dim == 128)
+    gdn_commit_kernel<128><<<dim3(hv, n_segs), 256, 0, stream>>>(factors, sg, accepted, row_slot,
+                                                                row_pos, hv, state);
+  else
+    gdn_commit_kernel<64><<<dim3(hv, n_segs), 256, 0, stream>>>(factors, sg, accepted, row_slot,
+                                                               row_pos, hv, state);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -248,17 +318,18 @@ int orinfer_gdn_conv(const __half* x, int x_stride, const __half* weight, __half
 // out fp32 [rows, HV, D].  head_dim D is 64 or 128; state is [slots, HV, D, D].
 int orinfer_gdn_scan(const __half* qkv, const float* ab, const float* a_log, const float* dt_bias,
                      const int* segs, int n_segs, const int* row_slot, const int* row_pos, int hk,
-                     int hv, int head_dim, float* state, float* out, cudaStream_t stream) {
+                     int hv, int head_dim, float* state, float* out, cudaStream_t stream,
+                     float* factors) {
   if (n_segs <= 0) return 0;
   if ((head_dim != 128 && head_dim != 64) || hv % hk) return -1;
   const Segment* sg = reinterpret_cast<const Segment*>(segs);
   const int conv_dim = (2 * hk + hv) * head_dim;
   if (head_dim == 128)
     gdn_scan_kernel<128><<<dim3(hv, n_segs), 256, 0, stream>>>(
-        qkv, conv_dim, ab, a_log, dt_bias, sg, row_slot, row_pos, hk, hv, state, out);
+        qkv, conv_dim, ab, a_log, dt_bias, sg, row_slot, row_pos, hk, hv, state, out, factors);
   else
     gdn_scan_kernel<64><<<dim3(hv, n_segs), 256, 0, stream>>>(
-        qkv, conv_dim, ab, a_log, dt_bias, sg, row_slot, row_pos, hk, hv, state, out);
+        qkv, conv_dim, ab, a_log, dt_bias, sg, row_slot, row_pos, hk, hv, state, out, factors);
   return static_cast<int>(cudaGetLastError());
 }
 

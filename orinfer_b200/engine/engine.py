@@ -107,12 +107,12 @@ class Engine:
         self.device = weights.embed_q.device
         self.on_gpu = self.device.type == "cuda"
         # Recurrent (GDN) layers keep per-request state that cannot be rebuilt from KV pages:
-        # prefix reuse would start a request without its state and a rejected draft would
-        # leave the state ahead of the committed text, so both stay off for hybrid models.
+        # prefix reuse would start a request without its state, so it stays off for hybrid
+        # models.  Speculation works: verification packets are tentative and the runner commits
+        # the accepted prefix of every request afterwards.
         self.recurrent = self.cfg.arch == "hybrid"
         if self.recurrent:
-            self.load = dataclasses.replace(self.load, prefix_cache_bytes=0, mtp_drafts=0,
-                                            prompt_lookup=False)
+            self.load = dataclasses.replace(self.load, prefix_cache_bytes=0)
         self.max_context = max_context or min(self.cfg.max_context, 32768)
         self.max_pages_per_req = (self.max_context + PAGE_TOKENS - 1) // PAGE_TOKENS
         self.max_rows = max_rows or max(self.sched.prefill_chunk + self.sched.max_active, 256)

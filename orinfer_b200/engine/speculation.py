@@ -171,11 +171,24 @@ class Speculator:
         from ..models.runner import Packet
         packet = Packet(eng._upload("ids", ids), eng._upload("req", rows_req),
                         eng._upload("pos", pos), eng.page_table_dev, len(ids), max_kv)
+        if eng.recurrent:
+            # recurrent layers must only keep the accepted prefix of each request's rows
+            segs, first, start = [], [], 0
+            for _r, drafts in plans:
+                n = 1 + len(drafts)
+                segs += [start, n, 0, 0]
+                first += [start] * n
+                start += n
+            packet.segments = eng._upload("segs", segs).view(-1, 4)
+            packet.row_first = eng._upload("first", first)
+            packet.n_segments = len(plans)
+            packet.tentative = True
         need = any(not eng._plain(r) for r, _ in plans)
         tok_dev, logits = eng.runner.greedy(packet, need_logits=need)
         tokens = tok_dev.cpu().tolist()
         produced, row = [], 0
         counts = []
+        kept_rows = []
         hidden = eng.runner.final_hidden(len(ids)) if eng.runner_has_mtp() else None
         for r, drafts in plans:
             n = 1 + len(drafts)
@@ -188,6 +201,7 @@ class Speculator:
             else:
                 commit = [eng._sample(r, tokens, logits, row)]
             accepted = len(commit) - 1
+            kept_rows.append(1 + accepted)
             if drafts:
                 counts.append((len(drafts), accepted))
                 if r.rid in self.lookups:
@@ -201,6 +215,8 @@ class Speculator:
                 eng._deliver(r, int(tok))
             produced.append(r)
             row += n
+        if packet.tentative:
+            eng.runner.gdn_commit(packet, kept_rows)
         if counts:
             self.acceptance.observe(counts)
             self.rounds += 1

@@ -125,6 +125,9 @@ class Packet:
     segments: Optional[torch.Tensor] = None
     n_segments: int = 0
     row_first: Optional[torch.Tensor] = None
+    # A verification packet of a speculative round: recurrent layers leave their state and
+    # convolution history untouched and record what ``gdn_commit`` needs to keep a prefix.
+    tentative: bool = False
 
     def ensure_segments(self) -> None:
         if self.segments is not None:
@@ -222,8 +225,36 @@ class ModelRunner:
                 conv=torch.empty(ws.max_rows, conv_dim, dtype=torch.float16, device=dev),
                 ab=torch.empty(ws.max_rows, 2 * hv, dtype=torch.float32, device=dev),
                 o=torch.empty(ws.max_rows, hv, d, dtype=torch.float32, device=dev),
-                mix=torch.empty(ws.max_rows, hv * d, dtype=torch.float16, device=dev))
+                mix=torch.empty(ws.max_rows, hv * d, dtype=torch.float16, device=dev),
+                layers=n, t_rows=0)
         return st
+
+    TENTATIVE_ROWS = 512
+
+    def _gdn_tentative(self, st):
+        """Per-layer records of a verification pass: the pre-convolution rows and the
+        (decay, k, delta) factors of every step."""
+        if "t_proj" not in st:
+            cfg = self.cfg
+            hk, hv, d = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim
+            conv_dim = (2 * hk + hv) * d
+            n, r, dev = st["layers"], self.TENTATIVE_ROWS, self.device
+            st["t_proj"] = torch.empty(n, r, conv_dim, dtype=torch.float16, device=dev)
+            st["t_fac"] = torch.empty(n, r, hv, 2 * d + 1, dtype=torch.float32, device=dev)
+        return st
+
+    def gdn_commit(self, p: Packet, accepted_rows) -> None:
+        """Keeps the first ``accepted_rows[s]`` rows of every segment of the tentative packet
+        ``p`` in every recurrent layer (state and convolution history)."""
+        st = getattr(self, "_gdn", None)
+        if st is None or "t_proj" not in st:
+            return
+        cfg = self.cfg
+        hk, hv, d = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim
+        acc = torch.tensor(list(accepted_rows), dtype=torch.int32, device=self.device)
+        for j in range(st["layers"]):
+            F.gdn_commit(st["t_proj"][j], st["t_fac"][j], p.segments, p.n_segments, acc,
+                         p.row_req, p.row_pos, hk, hv, d, st["hist"][j], st["state"][j])
 
     def _gdn_block(self, lw: LayerWeights, layer: int, x, p: Packet, rows: int):
         """Gated-delta-rule mixer: norm+rotate+A8 -> q|k|v|z projection (tensor cores) and the
@@ -239,10 +270,18 @@ class ModelRunner:
         q8, sc = self._prep(x, lw.in_norm, self._signs(lw.gdn_qkvz), rows, y_out=y16)
         proj = self._linear(lw.gdn_qkvz, q8, sc, rows, st["proj"])
         F.small_proj(y16, lw.gdn_ab, rows=rows, out=st["ab"])
+        factors = None
+        if p.tentative:
+            if rows > self.TENTATIVE_ROWS:
+                raise ValueError("verification packet larger than the recurrent journal")
+            self._gdn_tentative(st)
+            st["t_proj"][j, :rows].copy_(proj[:rows, :conv_dim])
+            factors = st["t_fac"][j]
         F.gdn_conv(proj, lw.gdn_conv, st["hist"][j], p.row_first, p.row_req, p.row_pos,
-                   p.segments, p.n_segments, rows, hk, hv, d, out=st["conv"])
+                   p.segments, p.n_segments, rows, hk, hv, d, out=st["conv"],
+                   update_history=not p.tentative)
         F.gdn_scan(st["conv"], st["ab"], lw.gdn_a_log, lw.gdn_dt_bias, p.segments, p.n_segments,
-                   p.row_req, p.row_pos, hk, hv, d, st["state"][j], out=st["o"])
+                   p.row_req, p.row_pos, hk, hv, d, st["state"][j], out=st["o"], factors=factors)
         F.gdn_gated_norm(st["o"], proj[:, conv_dim:], lw.gdn_norm, cfg.eps, rows, hv, d,
                          out=st["mix"])
         q8, sc = F.act_prep(st["mix"], None, None, self._signs(lw.gdn_out), rows=rows,

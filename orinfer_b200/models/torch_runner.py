@@ -102,19 +102,43 @@ class TorchRunner:
         g, beta = G.gates(ab, lw.gdn_a_log, lw.gdn_dt_bias)
         p.ensure_segments()
         out = torch.empty(p.rows, hv * d)
-        for start, n, _a, _b in p.segments.tolist():
+        if p.tentative:
+            self._gdn_journal = getattr(self, "_gdn_journal", {})
+        for si, (start, n, _a, _b) in enumerate(p.segments.tolist()):
             slot, pos0 = int(p.row_req[start]), int(p.row_pos[start])
             key = (layer, slot)
             if pos0 == 0 or key not in self._gdn_pool:
                 self._gdn_pool[key] = (torch.zeros(hv, d, d), torch.zeros(3, conv_dim))
             state, hist = self._gdn_pool[key]
             sl = slice(start, start + n)
+            if p.tentative:                      # verification pass: remember how to redo a prefix
+                self._gdn_journal[(layer, si)] = (key, proj[sl, :conv_dim].clone(), g[sl].clone(),
+                                                  beta[sl].clone(), lw)
             yc, hist = G.conv_silu_l2(proj[sl, :conv_dim], hist, lw.gdn_conv, dk, d)
             o, state = G.recurrence(yc[:, :dk].reshape(n, hk, d), yc[:, dk:2 * dk].reshape(n, hk, d),
                                     yc[:, 2 * dk:].reshape(n, hv, d), g[sl], beta[sl], state)
-            self._gdn_pool[key] = (state, hist)
+            if not p.tentative:
+                self._gdn_pool[key] = (state, hist)
             out[sl] = G.gated_norm(o, proj[sl, conv_dim:].reshape(n, hv, d), lw.gdn_norm, cfg.eps)
         return out
+
+    def gdn_commit(self, p: Packet, accepted_rows) -> None:
+        """Keeps the first ``accepted_rows[s]`` rows of every segment of a tentative packet."""
+        from ..ref import gdn_ref as G
+        cfg = self.cfg
+        hk, hv, d = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim
+        dk = hk * d
+        accepted_rows = list(accepted_rows)
+        for (layer, si), (key, x, g, beta, lw) in getattr(self, "_gdn_journal", {}).items():
+            a = min(accepted_rows[si], x.shape[0])
+            if a <= 0:
+                continue
+            state, hist = self._gdn_pool[key]
+            yc, hist = G.conv_silu_l2(x[:a], hist, lw.gdn_conv, dk, d)
+            _, state = G.recurrence(yc[:, :dk].reshape(a, hk, d), yc[:, dk:2 * dk].reshape(a, hk, d),
+                                    yc[:, 2 * dk:].reshape(a, hv, d), g[:a], beta[:a], state)
+            self._gdn_pool[key] = (state, hist)
+        self._gdn_journal = {}
 
     def _reduce(self, x: torch.Tensor) -> torch.Tensor:
         return x

@@ -316,9 +316,10 @@ def small_proj(x: torch.Tensor, w: torch.Tensor, rows: Optional[int] = None,
 def gdn_conv(x: torch.Tensor, weight: torch.Tensor, hist: torch.Tensor, row_first: torch.Tensor,
              row_slot: torch.Tensor, row_pos: torch.Tensor, segs: torch.Tensor, n_segs: int,
              rows: int, hk: int, hv: int, head_dim: int,
-             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+             out: Optional[torch.Tensor] = None, update_history: bool = True) -> torch.Tensor:
     """Causal conv4 + SiLU + L2(q, k) over the q|k|v channels of ``x`` [rows, >= conv_dim];
-    ``hist`` fp16 [slots, 3, conv_dim] is read, then advanced in place per segment."""
+    ``hist`` fp16 [slots, 3, conv_dim] is read, then advanced in place per segment (unless
+    ``update_history`` is off: a verification pass commits its history later)."""
     _cuda(x, weight, hist, row_first, row_slot, row_pos, segs)
     conv_dim = (2 * hk + hv) * head_dim
     assert x.dtype == torch.float16 and x.stride(1) == 1 and hist.shape[-1] == conv_dim
@@ -328,16 +329,20 @@ def gdn_conv(x: torch.Tensor, weight: torch.Tensor, hist: torch.Tensor, row_firs
     check(native.lib().orinfer_gdn_conv(ptr(x), x.stride(0), ptr(weight), ptr(hist),
                                         ptr(row_first), ptr(row_slot), ptr(row_pos), ptr(segs),
                                         n_segs, rows,
-                                        hk, hv, head_dim, ptr(out), stream()), "gdn_conv")
-    count_launches(2)
+                                        hk, hv, head_dim, ptr(out), stream(),
+                                        int(update_history)), "gdn_conv")
+    count_launches(2 if update_history else 1)
     return out
 
 
 def gdn_scan(qkv: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
              segs: torch.Tensor, n_segs: int, row_slot: torch.Tensor, row_pos: torch.Tensor,
              hk: int, hv: int, head_dim: int, state: torch.Tensor,
-             out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Sequential gated-delta recurrence; ``state`` fp32 [slots, HV, D, D] updated in place."""
+             out: Optional[torch.Tensor] = None,
+             factors: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Sequential gated-delta recurrence; ``state`` fp32 [slots, HV, D, D] updated in place.
+    With ``factors`` (fp32 [rows, HV, 2D+1]) the state is left untouched and every step's
+    (decay, k, delta) is recorded for :func:`gdn_commit`."""
     _cuda(qkv, ab, a_log, dt_bias, segs, state, row_slot, row_pos)
     assert ab.dtype == torch.float32 and state.dtype == torch.float32 and state.is_contiguous()
     assert a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32
@@ -345,10 +350,24 @@ def gdn_scan(qkv: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, dt_bias: 
         out = torch.empty(qkv.shape[0], hv, head_dim, dtype=torch.float32, device=qkv.device)
     check(native.lib().orinfer_gdn_scan(ptr(qkv), ptr(ab), ptr(a_log), ptr(dt_bias), ptr(segs),
                                         n_segs, ptr(row_slot), ptr(row_pos), hk, hv, head_dim,
-                                        ptr(state), ptr(out), stream()),
+                                        ptr(state), ptr(out), stream(), ptr(factors)),
           "gdn_scan")
     count_launches(1)
     return out
+
+
+def gdn_commit(x: torch.Tensor, factors: torch.Tensor, segs: torch.Tensor, n_segs: int,
+               accepted: torch.Tensor, row_slot: torch.Tensor, row_pos: torch.Tensor, hk: int,
+               hv: int, head_dim: int, hist: torch.Tensor, state: torch.Tensor) -> None:
+    """Keeps the first ``accepted[s]`` rows of every segment of a verification pass: advances
+    the convolution history by them and replays their recorded state updates."""
+    _cuda(x, factors, segs, accepted, row_slot, row_pos, hist, state)
+    assert accepted.dtype == torch.int32 and factors.dtype == torch.float32
+    check(native.lib().orinfer_gdn_commit(ptr(x), x.stride(0), ptr(factors), ptr(segs), n_segs,
+                                          ptr(accepted), ptr(row_slot), ptr(row_pos), hk, hv,
+                                          head_dim, ptr(hist), ptr(state), stream()),
+          "gdn_commit")
+    count_launches(2)
 
 
 def gdn_gated_norm(o: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, rows: int,

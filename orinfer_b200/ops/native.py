@@ -60,8 +60,9 @@ def _load() -> ctypes.CDLL:
         "orinfer_qgemm_launches": ([I, I, I, I, I], I),
         "orinfer_act_prep_limited": ([P, P, P, P, I, I, I, P, P], I),
         "orinfer_small_proj": ([P, P, P, I, I, I, P], I),
-        "orinfer_gdn_conv": ([P, I, P, P, P, P, P, P, I, I, I, I, I, P, P], I),
-        "orinfer_gdn_scan": ([P, P, P, P, P, I, P, P, I, I, I, P, P, P], I),
+        "orinfer_gdn_conv": ([P, I, P, P, P, P, P, P, I, I, I, I, I, P, P, I], I),
+        "orinfer_gdn_scan": ([P, P, P, P, P, I, P, P, I, I, I, P, P, P, P], I),
+        "orinfer_gdn_commit": ([P, I, P, P, I, P, P, P, I, I, I, P, P, P], I),
         "orinfer_gdn_gated_norm": ([P, P, I, P, c_float, I, I, I, I, P, P], I),
         "orinfer_attention_prefill": ([P, P, P, I, I, I, P, I, P, P, P, P, P, I, I, I, I, P], I),
     }

@@ -128,3 +128,83 @@ def test_hybrid_engine_graph_decode_matches_direct(cuda):
                      max_context=256)
         outs.append(eng.generate(prompts, max_new=10))
     assert outs[0] == outs[1]
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_tentative_scan_then_commit_is_bit_identical_to_plain_prefix(cuda, d):
+    """A verification pass records (decay, k, delta) and leaves state and history alone; the
+    commit of a[s] rows per segment gives the very bits a plain pass over those rows gives."""
+    from orinfer_b200.ops import functional as F
+    torch.manual_seed(100 + d)
+    hk, hv = 2, 4
+    conv_dim = (2 * hk + hv) * d
+    lens, slots, keep = [4, 3, 5], [1, 3, 0], [2, 0, 5]
+    rows = sum(lens)
+    w = (torch.randn(conv_dim, 4) * 0.5).half().to(cuda)
+    a_log, dt_bias = (torch.randn(hv) * 0.3).to(cuda), (torch.randn(hv) * 0.3).to(cuda)
+    hist0 = torch.randn(4, 3, conv_dim, device=cuda).half()
+    state0 = torch.randn(4, hv, d, d, device=cuda) * 0.1
+    x = torch.randn(rows, conv_dim, device=cuda).half()
+    ab = torch.randn(rows, 2 * hv, device=cuda)
+    segs, first = _segments(lens, cuda)
+    t = lambda v: torch.tensor(v, dtype=torch.int32, device=cuda)
+    row_slot = t([s for s, n in zip(slots, lens) for _ in range(n)])
+    row_pos = t([7 + i for n in lens for i in range(n)])
+
+    hist, state = hist0.clone(), state0.clone()
+    fac = torch.zeros(rows, hv, 2 * d + 1, device=cuda)
+    yc = F.gdn_conv(x, w, hist, first, row_slot, row_pos, segs, len(lens), rows, hk, hv, d,
+                    update_history=False)
+    o_t = F.gdn_scan(yc, ab, a_log, dt_bias, segs, len(lens), row_slot, row_pos, hk, hv, d, state,
+                     factors=fac)
+    torch.cuda.synchronize()
+    assert torch.equal(hist, hist0) and torch.equal(state, state0)
+    F.gdn_commit(x, fac, segs, len(lens), t(keep), row_slot, row_pos, hk, hv, d, hist, state)
+
+    # plain pass over the kept rows only
+    kept = [i for st, (n, a) in zip([0, 4, 7], zip(lens, keep)) for i in range(st, st + a)]
+    klens = [a for a in keep if a > 0]
+    kslots = [s for s, a in zip(slots, keep) if a > 0]
+    ksegs, kfirst = _segments(klens, cuda)
+    idx = torch.tensor(kept, device=cuda)
+    hist_p, state_p = hist0.clone(), state0.clone()
+    kslot = t([s for s, n in zip(kslots, klens) for _ in range(n)])
+    kpos = row_pos[idx].contiguous()
+    xk = x[idx].contiguous()
+    yk = F.gdn_conv(xk, w, hist_p, kfirst, kslot, kpos, ksegs, len(klens), len(kept), hk, hv, d)
+    o_p = F.gdn_scan(yk, ab[idx].contiguous(), a_log, dt_bias, ksegs, len(klens), kslot, kpos,
+                     hk, hv, d, state_p)
+    torch.cuda.synchronize()
+    assert torch.equal(o_t[idx], o_p)
+    assert torch.equal(hist, hist_p)
+    assert torch.equal(state, state_p)
+
+
+def test_hybrid_engine_speculation_on_device_matches_plain(cuda, monkeypatch):
+    from orinfer_b200.config import GraphMode, LoadOptions, SchedulerOptions
+    from orinfer_b200.engine.engine import Engine
+    monkeypatch.setenv("ORINFER_SINGLE_MTP_POLICY", "fixed3")
+    cfg = PRESETS["tiny-hybrid"]
+    w = random_model(cfg, seed=11).to(cuda)
+    g = torch.Generator().manual_seed(12)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (25, 9)]
+    mk = lambda **kw: Engine(w, load=LoadOptions(cuda_graph=GraphMode.OFF, **kw),
+                             sched=SchedulerOptions(max_active=4, prefill_chunk=16),
+                             kv_pages=16, max_context=256)
+    plain = mk().generate(prompts, max_new=12)
+    for kind in ("oracle", "half"):
+        eng = mk(prompt_lookup=True, mtp_drafts=3)
+        reqs = [eng.submit(p, 12) for p in prompts]
+        text = {r.rid: t for r, t in zip(reqs, plain)}
+
+        def drafts(r, c, kind=kind, text=text):
+            dr = list(text[r.rid][len(r.generated):len(r.generated) + c])
+            if kind == "half" and len(dr) > 1:
+                dr[1:] = [(x + 1) % cfg.vocab for x in dr[1:]]
+            return dr
+
+        eng.spec.drafts_for = drafts
+        while eng.has_work():
+            eng.step()
+        assert [r.generated for r in reqs] == plain, kind
+        assert eng.spec.statistics()["accepted_draft_tokens"] > 0

@@ -40,7 +40,7 @@ def test_hybrid_engine_matches_single_request_reference():
     prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (21, 9)]
     eng = Engine(w, sched=SchedulerOptions(max_active=4, prefill_chunk=8), kv_pages=12,
                  max_context=256)
-    assert eng.prefix is None and not eng.spec.enabled      # recurrent state: no reuse, no drafts
+    assert eng.prefix is None                                # recurrent state: no prefix reuse
     r0 = eng.submit(prompts[0], 5)
     eng.step()
     r1 = eng.submit(prompts[1], 5)                           # joins while r0 is mid-prefill
@@ -54,3 +54,66 @@ def test_hybrid_engine_matches_single_request_reference():
     while eng.has_work():
         eng.step()
     assert r2.generated == r1.generated
+
+
+def test_tentative_pass_then_commit_equals_plain_prefix():
+    """A verification packet leaves the recurrent state alone; committing a rows of it gives
+    what a plain pass over those a rows gives."""
+    from orinfer_b200.models.runner import Packet
+    from orinfer_b200.models.torch_runner import TorchRunner
+    cfg = PRESETS["tiny-hybrid"]
+    w = random_model(cfg, seed=3)
+    t = lambda v: torch.tensor(v, dtype=torch.int32)
+
+    def prefilled():
+        from orinfer_b200.models.runner import KVPool
+        r = TorchRunner(w, KVPool.allocate(cfg, 4, torch.device("cpu")), max_rows=64)
+        n = 6
+        r.logits(Packet(t(list(range(3, 3 + n))), t([0] * n), t(list(range(n))), t([[1, 2]]), n, n))
+        return r
+
+    toks = [11, 12, 13, 14]
+    a, b = prefilled(), prefilled()
+    p = Packet(t(toks), t([0] * 4), t([6, 7, 8, 9]), t([[1, 2]]), 4, 10)
+    p.tentative = True
+    a.logits(p)
+    a.gdn_commit(p, [2])
+    b.logits(Packet(t(toks[:2]), t([0] * 2), t([6, 7]), t([[1, 2]]), 2, 8))
+    nxt = Packet(t([20]), t([0]), t([8]), t([[1, 2]]), 1, 9)
+    assert torch.allclose(a.logits(nxt), b.logits(nxt), atol=1e-5)
+
+
+def test_hybrid_engine_speculates_and_matches_plain_greedy(monkeypatch):
+    """Right, wrong and half-right drafts: the recurrent state keeps exactly the accepted rows."""
+    from orinfer_b200.config import LoadOptions
+    monkeypatch.setenv("ORINFER_SINGLE_MTP_POLICY", "fixed3")
+    cfg = PRESETS["tiny-hybrid"]
+    w = random_model(cfg, seed=0)
+    prompts = [[5, 6, 7, 8, 9, 5, 6, 7, 8, 9, 5, 6, 7], [3, 1, 4, 1, 5, 9, 2, 6]]
+    want = [ref.generate_greedy(w, torch.tensor(p), 12, quantized=True)[0] for p in prompts]
+    for kind in ("oracle", "wrong", "half"):
+        eng = Engine(w, load=LoadOptions(prompt_lookup=True, mtp_drafts=3),
+                     sched=SchedulerOptions(max_active=2, prefill_chunk=8), kv_pages=12,
+                     max_context=256)
+        assert eng.spec.enabled
+        reqs = [eng.submit(p, 12) for p in prompts]
+        text = {r.rid: t for r, t in zip(reqs, want)}
+
+        def drafts(r, c, kind=kind, text=text):
+            d = list(text[r.rid][len(r.generated):len(r.generated) + c])
+            if kind == "wrong":
+                d = [(t + 1) % cfg.vocab for t in d]
+            elif kind == "half" and len(d) > 1:
+                d[1:] = [(t + 1) % cfg.vocab for t in d[1:]]
+            return d
+
+        eng.spec.drafts_for = drafts
+        while eng.has_work():
+            eng.step()
+        assert [r.generated for r in reqs] == want, kind
+        st = eng.spec.statistics()
+        assert st["proposed_tokens"] > 0
+        if kind == "oracle":
+            assert st["acceptance_rate"] == 1.0
+        if kind == "half":
+            assert 0 < st["accepted_draft_tokens"] < st["proposed_tokens"]
