@@ -120,9 +120,14 @@ __global__ void __launch_bounds__(256) gdn_history_kernel(const __half* __restri
 }
 
 // ---------------------------------------------------------------- sequential scan
-// grid (HV, segments); 256 threads: thread t owns value column dv = t % D and key rows
-// [ROWS*(t/D), +ROWS) of the DxD state, kept in registers for the whole segment.
-template <int D>
+// grid (HV * D/DC, segments); 256 threads.  The columns of the DxD state are independent in
+// the recurrence, so a CTA owns DC value columns of one head: thread t owns column
+// c0 + t % DC and key rows [ROWS*(t/DC), +ROWS), kept in registers for the whole segment.
+// Launched with DC = D (one CTA per head): the state is read and written in whole rows by the
+// fewest CTAs, which is what a decode step over many sequences is bound by.  The operands of
+// step t+1 are fetched into registers while step t computes.  (Few segments: see
+// gdn_scan_split_kernel below.)
+template <int D, int DC>
 __global__ void __launch_bounds__(256) gdn_scan_kernel(
     const __half* __restrict__ qkv, int conv_dim, const float* __restrict__ ab,
     const float* __restrict__ a_log, const float* __restrict__ dt_bias,
@@ -132,67 +137,246 @@ __global__ void __launch_bounds__(256) gdn_scan_kernel(
   // factors != nullptr: a verification pass.  The state is NOT written back; instead every
   // step records (decay, k[D], delta[D]) so that gdn_commit can replay exactly the accepted
   // prefix of the rows onto the stored state.
-  constexpr int PARTS = 256 / D, ROWS = D / PARTS;
-  const int vh = blockIdx.x;
+  constexpr int SPLIT = D / DC, PARTS = 256 / DC, ROWS = D / PARTS;
+  static_assert(ROWS % 4 == 0, "four independent accumulators");
+  const int vh = blockIdx.x / SPLIT, c0 = (blockIdx.x % SPLIT) * DC;
   const Segment seg = segs[blockIdx.y];
+  if (seg.rows <= 0) return;
   const int kh = vh / (hv / hk);
-  const int dv = threadIdx.x % D, part_id = threadIdx.x / D;
+  const int dv = c0 + threadIdx.x % DC, part_id = threadIdx.x / DC;
   const int slot = row_slot[seg.row_start];
   const bool fresh = row_pos[seg.row_start] == 0;
   float* sp = state + ((static_cast<size_t>(slot) * hv + vh) * D + part_id * ROWS) * D + dv;
   float s[ROWS];
 #pragma unroll
   for (int i = 0; i < ROWS; ++i) s[i] = fresh ? 0.f : sp[static_cast<size_t>(i) * D];
-  __shared__ float ks[D], qs[D], part[PARTS][D], opart[PARTS][D];
+  __shared__ float ks[2][D], qs[2][D], part[PARTS][DC], opart[PARTS][DC];
   const float alog = expf(a_log[vh]), bias = dt_bias[vh];
   const float scale = rsqrtf(static_cast<float>(D));
   const int dk_total = hk * D;
-  for (int t = 0; t < seg.rows; ++t) {
-    const size_t row = static_cast<size_t>(seg.row_start + t);
-    const __half* base = qkv + row * conv_dim;
-    if (threadIdx.x < D) {
-      qs[threadIdx.x] = __half2float(base[kh * D + threadIdx.x]) * scale;
-    } else if (threadIdx.x < 2 * D) {
-      ks[threadIdx.x - D] = __half2float(base[dk_total + kh * D + threadIdx.x - D]);
+  // which q/k element this thread stages (threads [0, D) -> q, [D, 2D) -> k)
+  const bool is_q = threadIdx.x < D, is_k = !is_q && threadIdx.x < 2 * D;
+  const int qk_col = is_q ? kh * D + threadIdx.x : dk_total + kh * D + threadIdx.x - D;
+  const int v_col = 2 * dk_total + vh * D + dv;
+  size_t row = static_cast<size_t>(seg.row_start);
+  __half n_qk = (is_q || is_k) ? qkv[row * conv_dim + qk_col] : __float2half(0.f);
+  __half n_v = qkv[row * conv_dim + v_col];
+  float n_a = ab[row * 2 * hv + vh], n_b = ab[row * 2 * hv + hv + vh];
+  for (int t = 0; t < seg.rows; ++t, ++row) {
+    const int buf = t & 1;
+    if (is_q) qs[buf][threadIdx.x] = __half2float(n_qk) * scale;
+    if (is_k) ks[buf][threadIdx.x - D] = __half2float(n_qk);
+    const float a = n_a, b = n_b, v = __half2float(n_v);
+    if (t + 1 < seg.rows) {                            // operands of the next step, in flight
+      const size_t nr = row + 1;
+      if (is_q || is_k) n_qk = qkv[nr * conv_dim + qk_col];
+      n_v = qkv[nr * conv_dim + v_col];
+      n_a = ab[nr * 2 * hv + vh];
+      n_b = ab[nr * 2 * hv + hv + vh];
     }
-    const float a = ab[row * 2 * hv + vh], b = ab[row * 2 * hv + hv + vh];
+    __syncthreads();
+    const float* kp = ks[buf] + part_id * ROWS;
+    const float* qp = qs[buf] + part_id * ROWS;
+    float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+#pragma unroll
+    for (int i = 0; i < ROWS; i += 4) {
+      p0 = fmaf(s[i], kp[i], p0);
+      p1 = fmaf(s[i + 1], kp[i + 1], p1);
+      p2 = fmaf(s[i + 2], kp[i + 2], p2);
+      p3 = fmaf(s[i + 3], kp[i + 3], p3);
+    }
     const float xg = a + bias;
     const float softplus = xg > 20.f ? xg : log1pf(expf(xg));
     const float decay = expf(-alog * softplus);
     const float beta = __fdiv_rn(1.f, 1.f + expf(-b));
-    const float v = __half2float(base[2 * dk_total + vh * D + dv]);
-    __syncthreads();
-    float pred = 0.f;
-#pragma unroll
-    for (int i = 0; i < ROWS; ++i) {
-      s[i] *= decay;
-      pred = fmaf(s[i], ks[part_id * ROWS + i], pred);
-    }
-    part[part_id][dv] = pred;
+    part[part_id][threadIdx.x % DC] = ((p0 + p1) + (p2 + p3)) * decay;
     __syncthreads();
     float full = 0.f;
 #pragma unroll
-    for (int i = 0; i < PARTS; ++i) full += part[i][dv];
+    for (int i = 0; i < PARTS; ++i) full += part[i][threadIdx.x % DC];
     const float delta = beta * (v - full);
     if (factors != nullptr) {
       float* f = factors + (row * hv + vh) * (2 * D + 1);
-      if (threadIdx.x == 0) f[0] = decay;
       if (part_id == 0) f[1 + D + dv] = delta;
-      if (threadIdx.x < D) f[1 + threadIdx.x] = ks[threadIdx.x];
+      if (c0 == 0) {
+        if (threadIdx.x == 0) f[0] = decay;
+        if (threadIdx.x < D) f[1 + threadIdx.x] = ks[buf][threadIdx.x];
+      }
     }
-    float o = 0.f;
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-    for (int i = 0; i < ROWS; ++i) {
-      s[i] = fmaf(ks[part_id * ROWS + i], delta, s[i]);
-      o = fmaf(s[i], qs[part_id * ROWS + i], o);
+    for (int i = 0; i < ROWS; i += 4) {
+      s[i] = fmaf(kp[i], delta, s[i] * decay);
+      s[i + 1] = fmaf(kp[i + 1], delta, s[i + 1] * decay);
+      s[i + 2] = fmaf(kp[i + 2], delta, s[i + 2] * decay);
+      s[i + 3] = fmaf(kp[i + 3], delta, s[i + 3] * decay);
+      o0 = fmaf(s[i], qp[i], o0);
+      o1 = fmaf(s[i + 1], qp[i + 1], o1);
+      o2 = fmaf(s[i + 2], qp[i + 2], o2);
+      o3 = fmaf(s[i + 3], qp[i + 3], o3);
     }
-    opart[part_id][dv] = o;
+    opart[part_id][threadIdx.x % DC] = (o0 + o1) + (o2 + o3);
     __syncthreads();
     if (part_id == 0) {
       float tot = 0.f;
 #pragma unroll
-      for (int i = 0; i < PARTS; ++i) tot += opart[i][dv];
+      for (int i = 0; i < PARTS; ++i) tot += opart[i][threadIdx.x % DC];
       out[(row * hv + vh) * D + dv] = tot;
+    }
+  }
+  if (factors == nullptr) {
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) sp[static_cast<size_t>(i) * D] = s[i];
+  }
+}
+
+// ---------------------------------------------------------------- sequential scan, split heads
+// The same recurrence for the case of few segments (prefill, small decode batches), where one
+// CTA per head leaves most SMs idle and every step pays its own global-memory latency.
+// grid (HV * D/32, segments): a CTA owns 32 value columns of one head.  Thread t owns column
+// t / 8 and key rows [ROWS*(t % 8), +ROWS): the eight partial dot products of a column sit in
+// neighbouring lanes and are combined with three shuffles, so a step needs no barrier.  q, k,
+// v and the gates of the next SCAN_STEPS rows are staged in shared memory with cp.async while
+// the current block computes; outputs leave in whole 128-byte rows once per block.
+constexpr int SCAN_STEPS = 16;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const unsigned a = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem) : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(256) gdn_scan_split_kernel(
+    const __half* __restrict__ qkv, int conv_dim, const float* __restrict__ ab,
+    const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+    const Segment* __restrict__ segs, const int* __restrict__ row_slot,
+    const int* __restrict__ row_pos, int hk, int hv, float* __restrict__ state,
+    float* __restrict__ out, float* __restrict__ factors) {
+  constexpr int DC = 32, SPLIT = D / DC, PARTS = 8, ROWS = D / PARTS, T = SCAN_STEPS;
+  constexpr int CH = D / 4 + DC / 8;                 // 16-byte units of one staged row
+  const int vh = blockIdx.x / SPLIT, c0 = (blockIdx.x % SPLIT) * DC;
+  const Segment seg = segs[blockIdx.y];
+  if (seg.rows <= 0) return;
+  const int kh = vh / (hv / hk);
+  const int col = threadIdx.x >> 3, part = threadIdx.x & 7;
+  const int slot = row_slot[seg.row_start];
+  const bool fresh = row_pos[seg.row_start] == 0;
+  float* sp = state + ((static_cast<size_t>(slot) * hv + vh) * D + part * ROWS) * D + c0 + col;
+  float s[ROWS];
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) s[i] = fresh ? 0.f : sp[static_cast<size_t>(i) * D];
+  __shared__ __align__(16) __half qk_s[2][T][2 * D];
+  __shared__ __align__(16) __half v_s[2][T][DC];
+  __shared__ float dec_s[2][T], beta_s[2][T], o_s[T][DC];
+  const float alog = expf(a_log[vh]), bias = dt_bias[vh];
+  const float scale = rsqrtf(static_cast<float>(D));
+  const int dk_total = hk * D;
+  const int blocks = (seg.rows + T - 1) / T;
+
+  auto stage = [&](int b) {
+    const int n = min(T, seg.rows - b * T), buf = b & 1;
+    for (int idx = threadIdx.x; idx < n * CH; idx += 256) {
+      const int t = idx / CH, c = idx % CH;
+      const __half* base = qkv + static_cast<size_t>(seg.row_start + b * T + t) * conv_dim;
+      if (c < D / 8)
+        cp_async16(&qk_s[buf][t][c * 8], base + kh * D + c * 8);
+      else if (c < D / 4)
+        cp_async16(&qk_s[buf][t][D + (c - D / 8) * 8], base + dk_total + kh * D + (c - D / 8) * 8);
+      else
+        cp_async16(&v_s[buf][t][(c - D / 4) * 8],
+                   base + 2 * dk_total + vh * D + c0 + (c - D / 4) * 8);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float n_a = 0.f, n_b = 0.f;
+  auto gates = [&](int b) {                            // threads [0, T): gate inputs of block b
+    const int t = b * T + threadIdx.x;
+    if (threadIdx.x < T && t < seg.rows) {
+      const size_t row = static_cast<size_t>(seg.row_start + t);
+      n_a = ab[row * 2 * hv + vh];
+      n_b = ab[row * 2 * hv + hv + vh];
+    }
+  };
+  stage(0);
+  gates(0);
+  for (int b = 0; b < blocks; ++b) {
+    const int buf = b & 1, n = min(T, seg.rows - b * T);
+    if (threadIdx.x < T) {
+      const float xg = n_a + bias;
+      const float softplus = xg > 20.f ? xg : log1pf(expf(xg));
+      dec_s[buf][threadIdx.x] = expf(-alog * softplus);
+      beta_s[buf][threadIdx.x] = __fdiv_rn(1.f, 1.f + expf(-n_b));
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                  // block b staged; everyone has left block b-1
+    if (b + 1 < blocks) {
+      stage(b + 1);
+      gates(b + 1);
+    }
+    for (int t = 0; t < n; ++t) {
+      const size_t row = static_cast<size_t>(seg.row_start + b * T + t);
+      float kk[ROWS], qq[ROWS];
+      const uint4* kp = reinterpret_cast<const uint4*>(&qk_s[buf][t][D + part * ROWS]);
+      const uint4* qp = reinterpret_cast<const uint4*>(&qk_s[buf][t][part * ROWS]);
+#pragma unroll
+      for (int j = 0; j < ROWS / 8; ++j) {
+        const uint4 kr = kp[j], qr = qp[j];
+        const __half2* kh2 = reinterpret_cast<const __half2*>(&kr);
+        const __half2* qh2 = reinterpret_cast<const __half2*>(&qr);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 kf = __half22float2(kh2[e]), qf = __half22float2(qh2[e]);
+          kk[j * 8 + 2 * e] = kf.x;
+          kk[j * 8 + 2 * e + 1] = kf.y;
+          qq[j * 8 + 2 * e] = qf.x;
+          qq[j * 8 + 2 * e + 1] = qf.y;
+        }
+      }
+      float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < ROWS; i += 4) {
+        p0 = fmaf(s[i], kk[i], p0);
+        p1 = fmaf(s[i + 1], kk[i + 1], p1);
+        p2 = fmaf(s[i + 2], kk[i + 2], p2);
+        p3 = fmaf(s[i + 3], kk[i + 3], p3);
+      }
+      float pred = (p0 + p1) + (p2 + p3);
+      pred += __shfl_xor_sync(0xffffffffu, pred, 1);
+      pred += __shfl_xor_sync(0xffffffffu, pred, 2);
+      pred += __shfl_xor_sync(0xffffffffu, pred, 4);
+      const float decay = dec_s[buf][t], beta = beta_s[buf][t];
+      const float v = __half2float(v_s[buf][t][col]);
+      const float delta = beta * (v - pred * decay);
+      if (factors != nullptr) {
+        float* f = factors + (row * hv + vh) * (2 * D + 1);
+        if (part == 0) f[1 + D + c0 + col] = delta;
+        if (c0 == 0) {
+          if (threadIdx.x == 0) f[0] = decay;
+          if (threadIdx.x < D) f[1 + threadIdx.x] = __half2float(qk_s[buf][t][D + threadIdx.x]);
+        }
+      }
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < ROWS; i += 4) {
+        s[i] = fmaf(kk[i], delta, s[i] * decay);
+        s[i + 1] = fmaf(kk[i + 1], delta, s[i + 1] * decay);
+        s[i + 2] = fmaf(kk[i + 2], delta, s[i + 2] * decay);
+        s[i + 3] = fmaf(kk[i + 3], delta, s[i + 3] * decay);
+        o0 = fmaf(s[i], qq[i], o0);
+        o1 = fmaf(s[i + 1], qq[i + 1], o1);
+        o2 = fmaf(s[i + 2], qq[i + 2], o2);
+        o3 = fmaf(s[i + 3], qq[i + 3], o3);
+      }
+      float o = (o0 + o1) + (o2 + o3);
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      o += __shfl_xor_sync(0xffffffffu, o, 4);
+      if (part == 0) o_s[t][col] = o * scale;
+    }
+    __syncthreads();                  // o_s complete (and re-used by the next block)
+    for (int idx = threadIdx.x; idx < n * DC; idx += 256) {
+      const int t = idx / DC, c = idx % DC;
+      out[(static_cast<size_t>(seg.row_start + b * T + t) * hv + vh) * D + c0 + c] = o_s[t][c];
     }
   }
   if (factors == nullptr) {
@@ -324,12 +508,22 @@ int orinfer_gdn_scan(const __half* qkv, const float* ab, const float* a_log, con
   if ((head_dim != 128 && head_dim != 64) || hv % hk) return -1;
   const Segment* sg = reinterpret_cast<const Segment*>(segs);
   const int conv_dim = (2 * hk + hv) * head_dim;
-  if (head_dim == 128)
-    gdn_scan_kernel<128><<<dim3(hv, n_segs), 256, 0, stream>>>(
-        qkv, conv_dim, ab, a_log, dt_bias, sg, row_slot, row_pos, hk, hv, state, out, factors);
-  else
-    gdn_scan_kernel<64><<<dim3(hv, n_segs), 256, 0, stream>>>(
-        qkv, conv_dim, ab, a_log, dt_bias, sg, row_slot, row_pos, hk, hv, state, out, factors);
+  // Few CTAs at one per head (prefill of a few long segments, small decode batches): spread
+  // each head over D/32 CTAs.  The rule depends on the segment count only, so a verification
+  // pass and the plain pass over the same requests take the same arithmetic.
+  const bool split = static_cast<long long>(hv) * n_segs < 2 * 148;
+#define ORINFER_SCAN(KERNEL, GRID_X)                                                       \
+  KERNEL<<<dim3(GRID_X, n_segs), 256, 0, stream>>>(qkv, conv_dim, ab, a_log, dt_bias, sg,  \
+                                                   row_slot, row_pos, hk, hv, state, out,  \
+                                                   factors)
+  if (head_dim == 128) {
+    if (split) ORINFER_SCAN(gdn_scan_split_kernel<128>, hv * 4);
+    else ORINFER_SCAN((gdn_scan_kernel<128, 128>), hv);
+  } else {
+    if (split) ORINFER_SCAN(gdn_scan_split_kernel<64>, hv * 2);
+    else ORINFER_SCAN((gdn_scan_kernel<64, 64>), hv);
+  }
+#undef ORINFER_SCAN
   return static_cast<int>(cudaGetLastError());
 }
 
