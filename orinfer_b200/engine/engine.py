@@ -22,6 +22,7 @@ full prefix pages, and sampling depends only on the request's own history.
 
 from __future__ import annotations
 
+import collections
 import dataclasses
 
 import time
@@ -65,6 +66,8 @@ class EngineStatistics:
     device_samples: int = 0
     offloaded_pages: int = 0
     restored_pages: int = 0
+    stored_snapshots: int = 0                 # recurrent-state endpoints kept for the prefix cache
+    restored_snapshots: int = 0
 
     def as_dict(self) -> dict:
         return dict(self.__dict__)
@@ -106,13 +109,15 @@ class Engine:
         self.sched.validate()
         self.device = weights.embed_q.device
         self.on_gpu = self.device.type == "cuda"
-        # Recurrent (GDN) layers keep per-request state that cannot be rebuilt from KV pages:
-        # prefix reuse would start a request without its state, so it stays off for hybrid
-        # models.  Speculation works: verification packets are tentative and the runner commits
+        # Recurrent (GDN) layers keep per-request state that cannot be rebuilt from KV pages.
+        # A cached prefix of a hybrid model is therefore usable only at an endpoint where the
+        # state was snapshotted (prompt end, periodic checkpoints): prefill chunks are cut at
+        # those positions and ``_snapshots`` maps the radix node of the endpoint's last page
+        # to the copy.  Speculation: verification packets are tentative and the runner commits
         # the accepted prefix of every request afterwards.
         self.recurrent = self.cfg.arch == "hybrid"
-        if self.recurrent:
-            self.load = dataclasses.replace(self.load, prefix_cache_bytes=0)
+        self._snapshots: "collections.OrderedDict[int, tuple]" = collections.OrderedDict()
+        self._snapshot_bytes = 0
         self.max_context = max_context or min(self.cfg.max_context, 32768)
         self.max_pages_per_req = (self.max_context + PAGE_TOKENS - 1) // PAGE_TOKENS
         self.max_rows = max_rows or max(self.sched.prefill_chunk + self.sched.max_active, 256)
@@ -313,8 +318,15 @@ class Engine:
             node_ids, pages = [], []
             if self.prefix is not None and req.cache_prompt:
                 node_ids, pages = self.prefix.match(req.prompt, limit_tokens=len(req.prompt) - 1)
+                snapshot = None
+                if self.recurrent and node_ids:               # usable only up to a kept endpoint
+                    cut, snapshot = self._snapshot_for(req.prompt, node_ids)
+                    self.prefix.release(node_ids[cut:])
+                    node_ids, pages = node_ids[:cut], pages[:cut]
                 if any(pg < 0 for pg in pages):              # host-resident nodes: restore or cut
                     cut = self._restore_host_pages(node_ids, pages)
+                    if self.recurrent and cut < len(pages):
+                        cut = 0                               # the endpoint itself was lost
                     self.prefix.release(node_ids[cut:])
                     node_ids, pages = node_ids[:cut], pages[:cut]
             need = self._pages_needed(req) - len(pages)
@@ -331,6 +343,9 @@ class Engine:
             req.pages = list(pages) + self.pool.take(need)
             req.slot = self.free_slots.pop()
             req.offset = req.cached_tokens = len(pages) * PAGE_TOKENS
+            if self.recurrent and pages:
+                self.runner.gdn_restore(req.slot, snapshot, self.page_table_dev.shape[0])
+                self.stats.restored_snapshots += 1
             req.phase = Phase.PREFILL
             self._prefix_nodes[req.rid] = node_ids
             row = self.page_table_host[req.slot]
@@ -358,10 +373,14 @@ class Engine:
             if self.prefix is not None and req.cache_prompt and reason != "error":
                 # index the full pages of prompt + generated tokens whose KV is in the cache
                 toks = req.history[:req.offset]
-                adopted, _ids = self.prefix.insert(toks, req.pages[:len(toks) // PAGE_TOKENS])
+                adopted, ids = self.prefix.insert(toks, req.pages[:len(toks) // PAGE_TOKENS])
                 for pg, took in zip(req.pages, adopted):
                     if took:
                         self.pool.share(pg)
+                for at, snap in req.snapshots.items():
+                    if at // PAGE_TOKENS <= len(ids):
+                        self._store_snapshot(ids[at // PAGE_TOKENS - 1], toks[:at], snap)
+            req.snapshots = {}
             if self.prefix is not None:
                 self.prefix.release(self._prefix_nodes.pop(req.rid, []))
             self.pool.release(req.pages)
@@ -404,9 +423,85 @@ class Engine:
             if budget <= 0:
                 break
             n = min(r.remaining_prefill, budget)
+            if self.recurrent and self.prefix is not None and r.cache_prompt:
+                n = min(n, self._next_endpoint(r) - r.offset)
             chunks.append((r, n))
             budget -= n
         return decoders, chunks
+
+    # ------------------------------------------------------------------ recurrent snapshots
+    CHECKPOINT_TOKENS = 8192
+
+    def _endpoints(self, prompt_len: int) -> List[int]:
+        """Positions (page multiples) at which a hybrid model's recurrent state is kept: the
+        last page boundary a later request with the same prompt may match (one token is always
+        left to compute), and every ``CHECKPOINT_TOKENS`` before it."""
+        last = (prompt_len - 1) // PAGE_TOKENS * PAGE_TOKENS
+        pts = list(range(self.CHECKPOINT_TOKENS, last, self.CHECKPOINT_TOKENS))
+        if last > 0:
+            pts.append(last)
+        return pts
+
+    def _next_endpoint(self, r: Request) -> int:
+        for at in self._endpoints(len(r.prompt)):
+            if at > r.offset:
+                return at
+        return len(r.prompt)
+
+    def _capture_snapshots(self, chunks) -> None:
+        if not (self.recurrent and self.prefix is not None):
+            return
+        for r, _n in chunks:
+            if r.cache_prompt and r.slot >= 0 and r.offset in self._endpoints(len(r.prompt)) \
+                    and r.offset > r.cached_tokens:
+                r.snapshots[r.offset] = self.runner.gdn_snapshot(r.slot)
+
+    @staticmethod
+    def _token_digest(tokens) -> bytes:
+        import hashlib
+        import numpy as np
+        return hashlib.blake2b(np.asarray(tokens, dtype=np.uint32).tobytes(),
+                               digest_size=16).digest()
+
+    @staticmethod
+    def _nbytes(snap) -> int:
+        total = 0
+        for part in snap:
+            for t in (part if isinstance(part, (list, tuple)) else [part]):
+                if torch.is_tensor(t):
+                    total += t.numel() * t.element_size()
+        return total
+
+    def _store_snapshot(self, node: int, tokens, snap) -> None:
+        """Keeps ``snap`` for the radix node ``node`` (the last page of ``tokens``); the token
+        digest guards against a node id that the tree has recycled since.  The store is an LRU
+        bounded by a quarter of the prefix-cache budget."""
+        digest = self._token_digest(tokens)
+        old = self._snapshots.pop(node, None)
+        if old is not None:
+            self._snapshot_bytes -= old[2]
+        size = self._nbytes(snap)
+        self._snapshots[node] = (digest, snap, size)
+        self._snapshot_bytes += size
+        self.stats.stored_snapshots += 1
+        limit = max(self.load.prefix_cache_bytes // 4, size)
+        while self._snapshot_bytes > limit and len(self._snapshots) > 1:
+            _node, (_d, _s, sz) = self._snapshots.popitem(last=False)
+            self._snapshot_bytes -= sz
+
+    def _snapshot_for(self, prompt, node_ids):
+        """-> (pages of the matched prefix that can be used, snapshot at that endpoint)."""
+        for i in range(len(node_ids) - 1, -1, -1):
+            hit = self._snapshots.get(node_ids[i])
+            if hit is None:
+                continue
+            if hit[0] != self._token_digest(prompt[:(i + 1) * PAGE_TOKENS]):
+                self._snapshot_bytes -= hit[2]                # recycled node id: stale entry
+                del self._snapshots[node_ids[i]]
+                continue
+            self._snapshots.move_to_end(node_ids[i])
+            return i + 1, hit[1]
+        return 0, None
 
     def _prefill_rate(self) -> Optional[float]:
         return getattr(self, "_prefill_tok_s", None)
@@ -437,6 +532,7 @@ class Engine:
             tokens, logits, order = self._run_direct(decoders, chunks)
         t1 = time.monotonic()
         produced = self._commit(order, tokens, logits)
+        self._capture_snapshots(chunks)
         t2 = time.monotonic()
         self.stats.batch_commit_s += t2 - t1
         if pure_decode:

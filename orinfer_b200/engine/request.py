@@ -41,6 +41,7 @@ class Request:
     pages: List[int] = field(default_factory=list)
     offset: int = 0                           # tokens whose KV is in the cache
     cached_tokens: int = 0                    # prefix-cache hit length
+    snapshots: dict = field(default_factory=dict)   # position -> recurrent state copy (hybrid)
     generated: List[int] = field(default_factory=list)
     logprobs: List[object] = field(default_factory=list)
     pending: int = -1                         # sampled token not yet fed to the model

@@ -243,6 +243,18 @@ class ModelRunner:
             st["t_fac"] = torch.empty(n, r, hv, 2 * d + 1, dtype=torch.float32, device=dev)
         return st
 
+    def gdn_snapshot(self, slot: int):
+        """Copy of the recurrent state of one request slot (every GDN layer): what a cached
+        prefix needs besides its KV pages."""
+        st = self._gdn
+        return st["state"][:, slot].clone(), st["hist"][:, slot].clone()
+
+    def gdn_restore(self, slot: int, snap, slots: int) -> None:
+        """``slots``: rows of the page table (sizes the pools on first use)."""
+        st = self._gdn_state(slots)
+        st["state"][:, slot].copy_(snap[0])
+        st["hist"][:, slot].copy_(snap[1])
+
     def gdn_commit(self, p: Packet, accepted_rows) -> None:
         """Keeps the first ``accepted_rows[s]`` rows of every segment of the tentative packet
         ``p`` in every recurrent layer (state and convolution history)."""

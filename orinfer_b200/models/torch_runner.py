@@ -122,6 +122,16 @@ class TorchRunner:
             out[sl] = G.gated_norm(o, proj[sl, conv_dim:].reshape(n, hv, d), lw.gdn_norm, cfg.eps)
         return out
 
+    def gdn_snapshot(self, slot: int):
+        """Copy of the recurrent state of one request slot (every GDN layer)."""
+        keys = sorted(k for k in self._gdn_pool if k[1] == slot)
+        return ([k[0] for k in keys], [self._gdn_pool[k][0].clone() for k in keys],
+                [self._gdn_pool[k][1].clone() for k in keys])
+
+    def gdn_restore(self, slot: int, snap, slots: int = 0) -> None:
+        for layer, state, hist in zip(*snap):
+            self._gdn_pool[(layer, slot)] = (state.clone(), hist.clone())
+
     def gdn_commit(self, p: Packet, accepted_rows) -> None:
         """Keeps the first ``accepted_rows[s]`` rows of every segment of a tentative packet."""
         from ..ref import gdn_ref as G

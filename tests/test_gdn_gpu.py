@@ -208,3 +208,27 @@ def test_hybrid_engine_speculation_on_device_matches_plain(cuda, monkeypatch):
             eng.step()
         assert [r.generated for r in reqs] == plain, kind
         assert eng.spec.statistics()["accepted_draft_tokens"] > 0
+
+
+def test_hybrid_prefix_reuse_restores_recurrent_state_on_device(cuda):
+    from orinfer_b200.config import PAGE_TOKENS, LoadOptions, SchedulerOptions
+    from orinfer_b200.engine.engine import Engine
+    cfg = PRESETS["tiny-hybrid"]
+    w = random_model(cfg, seed=13).to(cuda)
+    g = torch.Generator().manual_seed(14)
+    prompt = torch.randint(0, cfg.vocab, (2 * PAGE_TOKENS + 9,), generator=g).tolist()
+    longer = prompt[:2 * PAGE_TOKENS] + torch.randint(0, cfg.vocab, (20,), generator=g).tolist()
+    mk = lambda cache: Engine(w, load=LoadOptions(prefix_cache_bytes=cache),
+                              sched=SchedulerOptions(max_active=2, prefill_chunk=96),
+                              kv_pages=24, max_context=512)
+    cold = mk(0)
+    want = [cold.generate([p], max_new=6)[0] for p in (prompt, longer)]
+    eng = mk(64 << 20)
+    assert eng.generate([prompt], max_new=6)[0] == want[0]
+    assert eng.stats.stored_snapshots == 1
+    for p, text in zip((prompt, longer), want):
+        r = eng.submit(p, 6)
+        while eng.has_work():
+            eng.step()
+        assert r.generated == text and r.cached_tokens == 2 * PAGE_TOKENS
+    assert eng.stats.restored_snapshots == 2

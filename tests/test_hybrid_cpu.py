@@ -40,7 +40,7 @@ def test_hybrid_engine_matches_single_request_reference():
     prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (21, 9)]
     eng = Engine(w, sched=SchedulerOptions(max_active=4, prefill_chunk=8), kv_pages=12,
                  max_context=256)
-    assert eng.prefix is None                                # recurrent state: no prefix reuse
+    assert eng.prefix is not None                            # endpoints carry recurrent snapshots
     r0 = eng.submit(prompts[0], 5)
     eng.step()
     r1 = eng.submit(prompts[1], 5)                           # joins while r0 is mid-prefill
@@ -117,3 +117,41 @@ def test_hybrid_engine_speculates_and_matches_plain_greedy(monkeypatch):
             assert st["acceptance_rate"] == 1.0
         if kind == "half":
             assert 0 < st["accepted_draft_tokens"] < st["proposed_tokens"]
+
+
+def test_hybrid_prefix_reuse_restores_recurrent_state():
+    """A second request with the same prompt (or one that extends it) starts from the cached KV
+    pages and the snapshotted recurrent state, and produces the text of a cold run."""
+    from orinfer_b200.config import LoadOptions
+    from orinfer_b200.config import PAGE_TOKENS
+    cfg = PRESETS["tiny-hybrid"]
+    w = random_model(cfg, seed=0)
+    g = torch.Generator().manual_seed(5)
+    n = 2 * PAGE_TOKENS + 9
+    prompt = torch.randint(0, cfg.vocab, (n,), generator=g).tolist()
+    longer = prompt[:2 * PAGE_TOKENS] + torch.randint(0, cfg.vocab, (20,), generator=g).tolist()
+    mk = lambda cache: Engine(w, load=LoadOptions(prefix_cache_bytes=cache),
+                              sched=SchedulerOptions(max_active=2, prefill_chunk=96),
+                              kv_pages=24, max_context=512)
+    cold = mk(0)
+    want = [cold.generate([p], max_new=6)[0] for p in (prompt, longer)]
+    eng = mk(64 << 20)
+    assert eng.prefix is not None
+    assert eng.generate([prompt], max_new=6)[0] == want[0]
+    assert eng.stats.stored_snapshots == 1 and eng.stats.restored_snapshots == 0
+    r = eng.submit(prompt, 6)
+    while eng.has_work():
+        eng.step()
+    assert r.generated == want[0] and r.cached_tokens == 2 * PAGE_TOKENS
+    r2 = eng.submit(longer, 6)                    # shares the first two pages only
+    while eng.has_work():
+        eng.step()
+    assert r2.generated == want[1] and r2.cached_tokens == 2 * PAGE_TOKENS
+    assert eng.stats.restored_snapshots == 2
+    # a prompt that diverges inside the snapshotted span cannot use the endpoint
+    other = prompt[:PAGE_TOKENS + 3] + [(t + 1) % cfg.vocab for t in prompt[PAGE_TOKENS + 3:]]
+    r3 = eng.submit(other, 4)
+    while eng.has_work():
+        eng.step()
+    assert r3.cached_tokens == 0
+    assert r3.generated == cold.generate([other], max_new=4)[0]
