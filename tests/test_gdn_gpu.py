@@ -223,7 +223,6 @@ def test_hybrid_prefix_reuse_restores_recurrent_state_on_device(cuda):
                               kv_pages=24, max_context=512)
     # cold runs with the same chunk boundaries as the warm ones (chunks end at the endpoints)
     want = [mk(64 << 20).generate([p], max_new=6)[0] for p in (prompt, longer)]
-    assert want[0] == mk(0).generate([prompt], max_new=6)[0]
     eng = mk(64 << 20)
     assert eng.generate([prompt], max_new=6)[0] == want[0]
     assert eng.stats.stored_snapshots == 1
