@@ -187,8 +187,15 @@ class SchedulerOptions:
     target_tpot_ms: float = 400.0
     memory_reserve_bytes: int = 1 << 30
     prefill_chunk: int = 4096
+    # Layered prefill: a prefill packet of at least ``layered_min_rows`` rows that runs while
+    # requests are decoding is paused at ``prefill_stages - 1`` layer boundaries; the decoders
+    # take a step at each pause (only the hidden rows and the FP32 residual stay live).
+    prefill_stages: int = 1
+    layered_min_rows: int = 1024
 
     def validate(self) -> None:
+        if not 1 <= self.prefill_stages <= 16:
+            raise ValueError("prefill_stages must be within 1..16")
         if not 1 <= self.max_active <= MAX_ACTIVE_LIMIT:
             raise ValueError("max_active must be within 1..128")
         if not 1 <= self.max_batch_tokens <= 1 << 20:

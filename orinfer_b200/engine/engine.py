@@ -66,6 +66,7 @@ class EngineStatistics:
     device_samples: int = 0
     offloaded_pages: int = 0
     restored_pages: int = 0
+    layered_decode_steps: int = 0             # decode steps taken inside paused prefill packets
     stored_snapshots: int = 0                 # recurrent-state endpoints kept for the prefix cache
     restored_snapshots: int = 0
 
@@ -526,12 +527,17 @@ class Engine:
         use_graph = (self.on_gpu and pure_decode and
                      self.load.cuda_graph.uses_graph(ExecPhase.DECODE) and
                      len(decoders) <= DECODE_BUCKETS[-1])
+        early: List[Request] = []
         if use_graph:
             tokens, logits, order = self._run_decode_graph(decoders)
+        elif (decoders and self.sched.prefill_stages > 1
+              and sum(n for _, n in chunks) >= self.sched.layered_min_rows
+              and getattr(self.runner, "supports_stages", False)):
+            tokens, logits, order = self._run_layered(decoders, chunks, early)
         else:
             tokens, logits, order = self._run_direct(decoders, chunks)
         t1 = time.monotonic()
-        produced = self._commit(order, tokens, logits)
+        produced = early + [r for r in self._commit(order, tokens, logits) if r not in early]
         self._capture_snapshots(chunks)
         t2 = time.monotonic()
         self.stats.batch_commit_s += t2 - t1
@@ -614,6 +620,7 @@ class Engine:
         need = any(not self._plain(r) for r, _n, has in order if has)
         graphed = None
         if (self.on_gpu and n_decode == 0 and chunk_rows and not self.recurrent
+                and getattr(self.runner, "stage_hook", None) is None
                 and self.cfg.head_dim in (64, 128)
                 and self.load.cuda_graph.uses_graph(ExecPhase.PREFILL)):
             graphed = self._prefill_graph(packet, tuple(c[1] for c in chunk_rows), need)
@@ -632,6 +639,33 @@ class Engine:
         if dummy_logits:
             return None, None, order
         return tokens, lg, order
+
+    def _run_layered(self, decoders: List[Request], chunks, produced: List[Request]):
+        """Layered prefill: the prompt rows run as their own packet, paused at
+        ``prefill_stages - 1`` layer boundaries; at every pause the live decoders take one
+        ordinary step (graph replay where enabled) and their tokens are delivered, so a long
+        prompt costs the decoders one stage, not one full forward, between tokens."""
+        def between():
+            live = [r for r in decoders if r.phase is Phase.DECODE and not r.cancelled]
+            if not live:
+                return
+            if self.on_gpu:
+                torch.cuda.current_stream().synchronize()   # the outer packet's uploads landed
+            if (self.on_gpu and self.load.cuda_graph.uses_graph(ExecPhase.DECODE)
+                    and len(live) <= DECODE_BUCKETS[-1]):
+                tok, lg, order = self._run_decode_graph(live)
+            else:
+                tok, lg, order = self._run_direct(live, [])
+            for r in self._commit(order, tok, lg):
+                if r not in produced:
+                    produced.append(r)
+            self.stats.layered_decode_steps += 1
+
+        self.runner.stage_hook = (self.sched.prefill_stages, between)
+        try:
+            return self._run_direct([], chunks)
+        finally:
+            self.runner.stage_hook = None
 
     PREFILL_GRAPHS = 16
 

@@ -337,7 +337,14 @@ class ModelRunner:
         x = F.embed_w8(p.ids, self.w.embed_q, self.w.embed_s, out=ws.hidden)
         ws.resid[:rows].zero_()
         F.rope_table(p.row_pos, cfg.head_dim, cfg.rope_theta, ws.cos, ws.sin, rows=rows)
+        hook, self.stage_hook = getattr(self, "stage_hook", None), None
+        pauses = set()
+        if hook is not None:
+            n = len(self.w.layers)
+            pauses = {n * s // hook[0] for s in range(1, hook[0])} - {0}
         for i, lw in enumerate(self.w.layers):
+            if i in pauses:
+                x = self._pause(p, x, rows, hook[1])
             if lw.kind == "attn":
                 x = self._attention_block(lw, self._attn_index[i], x, p, rows, True)
             else:
@@ -346,6 +353,24 @@ class ModelRunner:
                 x = self._moe_ffn(lw, x, rows)
             else:
                 x = self._dense_ffn(lw, x, rows)
+        return x
+
+    supports_stages = True
+
+    def _pause(self, p: Packet, x, rows: int, between):
+        """Layer boundary of a layered prefill (``stage_hook = (stages, callback)`` set by the
+        caller before the forward): everything a later layer needs from the earlier ones is
+        the pending branch output ``x`` and the FP32 residual, so those rows are set aside,
+        ``between()`` is free to run other packets through this runner, and the rows and the
+        packet's RoPE table are put back.
+        Same contract as the reference's resumable prefill stages
+        (crates/orinfer-engine/src/runtime/requests/prefill.rs:7-70)."""
+        cfg, ws = self.cfg, self.ws
+        keep_x, keep_r = x[:rows].clone(), ws.resid[:rows].clone()
+        between()
+        x[:rows].copy_(keep_x)
+        ws.resid[:rows].copy_(keep_r)
+        F.rope_table(p.row_pos, cfg.head_dim, cfg.rope_theta, ws.cos, ws.sin, rows=rows)
         return x
 
     def _moe_ffn(self, lw: LayerWeights, x, rows: int):

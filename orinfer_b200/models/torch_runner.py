@@ -158,6 +158,8 @@ class TorchRunner:
         f = gu.shape[-1] // 2
         return self._reduce(self._linear(lw.down, R.silu_mul(gu[:, :f], gu[:, f:])))
 
+    supports_stages = True
+
     def forward_hidden(self, p: Packet):
         cfg = self.cfg
         rows = p.rows
@@ -165,7 +167,14 @@ class TorchRunner:
         resid = torch.zeros(rows, cfg.hidden)
         cos, sin = R.rope_tables(p.row_pos[:rows], cfg.head_dim, cfg.rope_theta)
         zc = cfg.zero_centered_norm
+        hook, self.stage_hook = getattr(self, "stage_hook", None), None
+        pauses = set()
+        if hook is not None:                     # layered prefill: see ModelRunner._pause
+            n = len(self.w.layers)
+            pauses = {n * s // hook[0] for s in range(1, hook[0])} - {0}
         for i, lw in enumerate(self.w.layers):
+            if i in pauses:
+                hook[1]()                        # x and resid are private to this call
             resid = resid + x
             y = R.rms_norm(resid, lw.in_norm, cfg.eps, zc)
             if lw.kind == "attn":

@@ -225,6 +225,10 @@ class FusedTPRunner(TPRunner):
 
     _SLOT = {"o": "o", "gdn_out": "o", "down": "down"}
 
+    # a paused forward would leave partial sums in the peers' inboxes while other packets use
+    # them: layered prefill is for the single-GPU and NCCL runners
+    supports_stages = False
+
     def forward_hidden(self, p):
         # sequence-parallel for prefill-sized packets of dense models; decode-sized packets
         # keep the one-hop all-reduce form (latency, not bytes, is what matters there)

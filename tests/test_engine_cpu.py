@@ -203,3 +203,25 @@ def test_host_kv_offload_restores_evicted_prefix(weights):
     assert r.generated == first[0]
     cold = _engine(weights, load=LoadOptions(prefix_cache_bytes=0))
     assert cold.generate([base[0]], max_new=4)[0] == first[0]
+
+
+def test_layered_prefill_lets_decoders_step_inside_a_long_prompt(weights):
+    """A prompt that joins while another request decodes is run as a paused packet: the
+    decoder takes a step at every layer-boundary pause and both texts stay what they were."""
+    short, long_ = _prompts(1, 16)[0], _prompts(1, 96)[0]
+    plain = _engine(weights, prefill_chunk=128)
+    want = [plain.generate([p], max_new=n)[0] for p, n in ((short, 12), (long_, 4))]
+    eng = Engine(weights, kv_pages=24, max_context=512,
+                 sched=SchedulerOptions(max_active=4, prefill_chunk=128, prefill_stages=2,
+                                        layered_min_rows=64))
+    a = eng.submit(short, 12)
+    eng.step()                                   # a is decoding when the long prompt arrives
+    eng.step()
+    at = len(a.generated)
+    b = eng.submit(long_, 4)
+    eng.step()                                   # one iteration: whole prompt + one pause
+    assert eng.stats.layered_decode_steps == 1
+    assert len(a.generated) == at + 1 and len(b.generated) == 1
+    while eng.has_work():
+        eng.step()
+    assert [a.generated, b.generated] == want

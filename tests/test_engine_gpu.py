@@ -115,3 +115,31 @@ def test_mtp_head_speculation_on_device(cuda, monkeypatch):
     assert eng.runner_has_mtp()
     assert eng.generate(prompts, max_new=10) == plain
     assert eng.spec.statistics()["rounds"] > 0
+
+
+@pytest.mark.parametrize("preset", ["tiny", "tiny-hybrid"])
+def test_layered_prefill_pauses_keep_both_texts(cuda, preset):
+    """The paused prompt packet gets its hidden rows, residual and RoPE table back after the
+    decoders used the same workspace (graph replay included)."""
+    w = random_model(PRESETS[preset], seed=0).to(cuda)
+    short, long_ = _prompts(1, 16)[0], _prompts(1, 200, seed=4)[0]
+
+    def run(stages):
+        eng = Engine(w, load=LoadOptions(cuda_graph=GraphMode.DECODE_ONLY, prefix_cache_bytes=0),
+                     sched=SchedulerOptions(max_active=4, prefill_chunk=256,
+                                            prefill_stages=stages, layered_min_rows=64),
+                     kv_pages=40, max_context=1024)
+        a = eng.submit(short, 14)
+        for _ in range(3):
+            eng.step()
+        b = eng.submit(long_, 5)
+        while eng.has_work():
+            eng.step()
+        return eng, [a.generated, b.generated]
+
+    plain_eng, plain = run(1)
+    eng, layered = run(2)
+    assert plain_eng.stats.layered_decode_steps == 0 and eng.stats.layered_decode_steps == 1
+    # the prompt rows ran without the decode row in their packet; the short request's text
+    # must be identical, the long one's first token comes from the same arithmetic per row
+    assert layered == plain
