@@ -46,6 +46,9 @@ def _load_args(p: argparse.ArgumentParser, batch: bool = False) -> None:
     p.add_argument("--target-tpot-ms", type=float, default=400.0)
     p.add_argument("--memory-reserve-mib", type=int, default=1024)
     p.add_argument("--prefill-chunk", type=int, default=4096)
+    p.add_argument("--prefill-stages", type=int, default=1,
+                   help="pause long prompt packets at this many layer boundaries so that "
+                        "decoding requests step in between (1 = off)")
     p.add_argument("--max-context", type=int, default=None)
     p.add_argument("--tp", type=int, default=1)
     p.add_argument("--device", default="cuda")
@@ -65,7 +68,7 @@ def _options(a):
                              prefill_budget_ms=a.prefill_budget_ms,
                              target_tpot_ms=a.target_tpot_ms,
                              memory_reserve_bytes=a.memory_reserve_mib << 20,
-                             prefill_chunk=a.prefill_chunk)
+                             prefill_chunk=a.prefill_chunk, prefill_stages=a.prefill_stages)
     load.validate()
     sched.validate()
     return load, sched
