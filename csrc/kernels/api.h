@@ -144,6 +144,11 @@ int orinfer_moe_combine_peer(const __half* expert_out, const int* slots, const f
                              const float* shared_gate, const OrinferPeerOut* peers, int hidden,
                              cudaStream_t stream);
 int orinfer_qgemm_launches(int M, int N, int K, int out_f32, int force_path);
+int orinfer_qgemm_launches_fmt(int fmt, int M, int N, int K, int out_f32, int force_path);
+int orinfer_qgemm_set_variant(int fmt, int m_lo, int m_hi, int n, int k, int mt, int nb,
+                              int splits);
+void orinfer_qgemm_clear_variants();
+void orinfer_qgemm_plan(int fmt, int M, int N, int K, int out_f32, int* out);
 int orinfer_qgemm_grouped(int fmt, const int8_t* a, const float* a_scale, const void* w,
                           const __half* w_scale, void* out, int S, int N, int K, int experts,
                           const int* tiles, const int* meta, int max_tiles, cudaStream_t stream);

@@ -458,31 +458,82 @@ inline int plan_splits(int M, int N, int K, int out_f32) {
   return splits < 1 ? 1 : splits;
 }
 
-template <int FMT>
-int launch_fmt(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale,
-               void* out, int M, int N, int K, int out_f32, cudaStream_t stream,
-               const PeerOut& po, const AgIn& ag = AgIn{nullptr, nullptr, 0, 0}) {
-  const GroupDesc none{nullptr, nullptr, 0, 0};
-  const int mt = M > 2 * BM ? 4 : (M > BM ? 2 : 1);
-  const long mtiles = (M + BM * mt - 1) / (BM * mt);
+// ---------------------------------------------------------------- launch plan
+// What launch_fmt decides for a shape: M-tile factor, weight-tile width, K splits and whether
+// the wave tail is peeled off into a split-K launch of its own.  The defaults below are the
+// heuristics; a tuned table (orinfer_qgemm_set_variant: per format, projection shape and row
+// range) overrides them.  The role of the reference's per-row-range kernel variants
+// (crates/orinfer-model-sdk/src/operators/rows.rs:10-60) and of its offline projection tuner
+// (python/orinfer_build/tuning/).
+struct Plan {
+  int mt, nb, splits, tail_splits;   // tail_splits > 0: peel ntiles % 148 weight tiles
+};
+
+struct Variant {
+  int fmt, m_lo, m_hi, n, k, mt, nb, splits;
+};
+constexpr int MAX_VARIANTS = 512;
+static Variant g_variants[MAX_VARIANTS];
+static int g_variant_count = 0;
+
+inline bool variant_valid(const Variant& v) {
+  if (v.fmt < 0 || v.fmt > 2 || v.m_lo < 1 || v.m_hi < v.m_lo || v.n < 8 || v.k < BK) return false;
+  if (v.mt != 1 && v.mt != 2 && v.mt != 4) return false;
+  if (v.nb != 128 && v.nb != 64 && v.nb != 32) return false;
+  if (v.splits < 1 || v.splits > 16 || v.splits > v.k / BK) return false;
+  if (v.splits > 1 && (v.nb != 128 || v.n % 8)) return false;
+  if (v.splits > 1 && static_cast<size_t>(v.splits) * v.m_hi * v.n * 4 > SPLITK_WORKSPACE_BYTES)
+    return false;
+  return true;
+}
+
+inline Plan make_plan(int fmt, int M, int N, int K, int out_f32, bool fused) {
+  Plan p{};
+  p.mt = M > 2 * BM ? 4 : (M > BM ? 2 : 1);
+  if (!out_f32) {
+    for (int i = 0; i < g_variant_count; ++i) {
+      const Variant& v = g_variants[i];
+      if (v.fmt == fmt && v.n == N && v.k == K && M >= v.m_lo && M <= v.m_hi) {
+        p.mt = v.mt;
+        p.nb = v.nb;
+        p.splits = v.splits;
+        return p;
+      }
+    }
+  }
+  const long mtiles = (M + BM * p.mt - 1) / (BM * p.mt);
   auto ctas = [&](int nb) { return mtiles * ((N + nb - 1) / nb); };
   // A projection too narrow to give every SM a CTA is split along K instead of into thinner
   // weight tiles: thin tiles make every CTA stream the whole activation matrix, while K
   // splits share it.  Partials are INT32, so the result does not depend on the split.
   const long c128 = ctas(128);
-  const int splits = plan_splits(M, N, K, out_f32);
-  const int nb = (out_f32 || splits > 1 || c128 >= 120) ? 128 : (ctas(64) >= 120 ? 64 : 32);
+  p.splits = plan_splits(M, N, K, out_f32);
+  p.nb = (out_f32 || p.splits > 1 || c128 >= 120) ? 128 : (ctas(64) >= 120 ? 64 : 32);
   // Wave quantisation: a grid of one M tile that is a few CTAs larger than the machine would
   // run a second, almost empty wave.  The full wave runs as one launch; the last few weight
   // tiles follow as a split-K launch of their own, which occupies the SMs the tail left idle.
   const long ntiles = (N + 127) / 128;
-  if (!out_f32 && splits == 1 && nb == 128 && mtiles == 1 && po.tp == 0 && ntiles > 148 &&
+  if (!out_f32 && p.splits == 1 && p.nb == 128 && mtiles == 1 && !fused && ntiles > 148 &&
       ntiles % 148 > 0 && ntiles % 148 <= 40 && K / BK >= 8 && N % 128 == 0) {
+    int ts = static_cast<int>(148 / (ntiles % 148));
+    ts = ts > K / BK / 4 ? K / BK / 4 : ts;
+    p.tail_splits = ts > 8 ? 8 : (ts < 1 ? 1 : ts);
+  }
+  return p;
+}
+
+template <int FMT>
+int launch_fmt(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale,
+               void* out, int M, int N, int K, int out_f32, cudaStream_t stream,
+               const PeerOut& po, const AgIn& ag = AgIn{nullptr, nullptr, 0, 0}) {
+  const GroupDesc none{nullptr, nullptr, 0, 0};
+  const Plan plan = make_plan(FMT, M, N, K, out_f32, po.tp != 0);
+  const int mt = plan.mt, nb = plan.nb, splits = plan.splits;
+  if (plan.tail_splits > 0) {
+    const long ntiles = (N + 127) / 128;
     const int tail_tiles = static_cast<int>(ntiles % 148);
     const int cut = static_cast<int>(ntiles - tail_tiles) * 128;
-    int ts = 148 / tail_tiles;
-    ts = ts > K / BK / 4 ? K / BK / 4 : ts;
-    ts = ts > 8 ? 8 : (ts < 1 ? 1 : ts);
+    const int ts = plan.tail_splits;
 #define ORINFER_TWO(MTV)                                                                        \
   {                                                                                             \
     const int r = launch<FMT, false, MTV, 128>(a, a_scale, w, w_scale, out, M, N, K, stream, po, \
@@ -555,20 +606,40 @@ static int qgemm_any(int fmt, const int8_t* a, const float* a_scale, const void*
   return tc::launch_fmt<2>(a, a_scale, w, w_scale, out, M, N, K, out_f32, stream, po);
 }
 
-// Number of kernel launches orinfer_qgemm makes for this shape (1, or 2 with split-K).
-extern "C" int orinfer_qgemm_launches(int M, int N, int K, int out_f32, int force_path) {
+// Number of kernel launches orinfer_qgemm makes for this shape and format.
+extern "C" int orinfer_qgemm_launches_fmt(int fmt, int M, int N, int K, int out_f32,
+                                          int force_path) {
   if (force_path == 1 || (force_path == 0 && M <= 8)) return (M + 7) / 8;
-  if (tc::plan_splits(M, N, K, out_f32) > 1) return 2;
-  const int mt = M > 2 * tc::BM ? 4 : (M > tc::BM ? 2 : 1);
-  const long mtiles = (M + tc::BM * mt - 1) / (tc::BM * mt), ntiles = (N + 127) / 128;
-  if (!out_f32 && mtiles == 1 && ntiles > 148 && ntiles % 148 > 0 && ntiles % 148 <= 40 &&
-      K / tc::BK >= 8 &&
-      N % 128 == 0) {
-    int ts = static_cast<int>(148 / (ntiles % 148));
-    ts = ts > K / tc::BK / 4 ? K / tc::BK / 4 : ts;
-    return ts > 1 ? 3 : 2;
-  }
-  return 1;
+  const tc::Plan p = tc::make_plan(fmt, M, N, K, out_f32, false);
+  if (p.tail_splits > 0) return p.tail_splits > 1 ? 3 : 2;
+  return p.splits > 1 ? 2 : 1;
+}
+
+extern "C" int orinfer_qgemm_launches(int M, int N, int K, int out_f32, int force_path) {
+  return orinfer_qgemm_launches_fmt(1, M, N, K, out_f32, force_path);
+}
+
+// Tuned launch variants: rows m_lo..m_hi of projection (fmt, N, K) run with M-tile factor mt
+// (1, 2, 4), weight-tile width nb (128, 64, 32) and `splits` K splits.  Earlier entries win.
+// Not thread-safe against concurrent launches: set the table before serving.
+extern "C" int orinfer_qgemm_set_variant(int fmt, int m_lo, int m_hi, int n, int k, int mt,
+                                         int nb, int splits) {
+  const tc::Variant v{fmt, m_lo, m_hi, n, k, mt, nb, splits};
+  if (!tc::variant_valid(v)) return -1;
+  if (tc::g_variant_count >= tc::MAX_VARIANTS) return -2;
+  tc::g_variants[tc::g_variant_count++] = v;
+  return 0;
+}
+
+extern "C" void orinfer_qgemm_clear_variants() { tc::g_variant_count = 0; }
+
+// The plan for a shape: out[0..3] = mt, nb, splits, tail_splits.
+extern "C" void orinfer_qgemm_plan(int fmt, int M, int N, int K, int out_f32, int* out) {
+  const tc::Plan p = tc::make_plan(fmt, M, N, K, out_f32, false);
+  out[0] = p.mt;
+  out[1] = p.nb;
+  out[2] = p.splits;
+  out[3] = p.tail_splits;
 }
 
 extern "C" int orinfer_qgemm(int fmt, const int8_t* a, const float* a_scale, const void* w,

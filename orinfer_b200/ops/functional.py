@@ -134,7 +134,7 @@ def qgemm(a: torch.Tensor, a_scale: torch.Tensor, codes: torch.Tensor, w_scale: 
     mm = m if rows is None else rows
     check(native.lib().orinfer_qgemm(FMT[fmt], ptr(a), ptr(a_scale), ptr(codes), ptr(w_scale),
                                      ptr(out), mm, n, k, int(out_f32), path, stream()), "qgemm")
-    count_launches(native.lib().orinfer_qgemm_launches(mm, n, k, int(out_f32), path))
+    count_launches(native.lib().orinfer_qgemm_launches_fmt(FMT[fmt], mm, n, k, int(out_f32), path))
     return out
 
 

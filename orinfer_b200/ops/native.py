@@ -58,6 +58,10 @@ def _load() -> ctypes.CDLL:
         "orinfer_moe_dispatch_ep": ([P, I, I, I, I, P, P, I, P, P, P, P, I, P, P, P, P], I),
         "orinfer_sample_topk": ([P, I, I, c_longlong, P, P, P, P, P, P, P], I),
         "orinfer_qgemm_launches": ([I, I, I, I, I], I),
+        "orinfer_qgemm_launches_fmt": ([I, I, I, I, I, I], I),
+        "orinfer_qgemm_set_variant": ([I, I, I, I, I, I, I, I], I),
+        "orinfer_qgemm_clear_variants": ([], None),
+        "orinfer_qgemm_plan": ([I, I, I, I, I, P], None),
         "orinfer_act_prep_limited": ([P, P, P, P, I, I, I, P, P], I),
         "orinfer_small_proj": ([P, P, P, I, I, I, P], I),
         "orinfer_gdn_conv": ([P, I, P, P, P, P, P, P, I, I, I, I, I, P, P, I], I),
@@ -115,6 +119,8 @@ def check(code: int, what: str) -> None:
 
 def init() -> None:
     check(_load().orinfer_init(), "orinfer_init")
+    from ..tuning import tables
+    tables.load_default()
 
 
 def read_status() -> int:
