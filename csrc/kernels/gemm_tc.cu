@@ -501,18 +501,42 @@ inline Plan make_plan(int fmt, int M, int N, int K, int out_f32, bool fused) {
       }
     }
   }
-  const long mtiles = (M + BM * p.mt - 1) / (BM * p.mt);
+  long mtiles = (M + BM * p.mt - 1) / (BM * p.mt);
+  const long ntiles = (N + 127) / 128;
   auto ctas = [&](int nb) { return mtiles * ((N + nb - 1) / nb); };
-  // A projection too narrow to give every SM a CTA is split along K instead of into thinner
-  // weight tiles: thin tiles make every CTA stream the whole activation matrix, while K
-  // splits share it.  Partials are INT32, so the result does not depend on the split.
+  // A projection too narrow to give every SM a CTA (at most half a wave of 128-wide tiles):
+  //  * up to 128 rows it is split along K: thin tiles would make every CTA stream the whole
+  //    activation matrix, K splits share it, and the INT32 partials make the result
+  //    independent of the split.  Two k-blocks per split are enough to pay for the finalize
+  //    pass at these row counts;
+  //  * above 128 rows the finalize pass (rows x N x splits INT32) costs more than it saves
+  //    unless K is long: thinner weight tiles under a smaller M tile win instead.
+  // (Measured over 18 projection shapes x 15 row buckets by the tuner in
+  // orinfer_b200/tuning/gemm_tuner.py; a tuned table still overrides these.)
   const long c128 = ctas(128);
-  p.splits = plan_splits(M, N, K, out_f32);
-  p.nb = (out_f32 || p.splits > 1 || c128 >= 120) ? 128 : (ctas(64) >= 120 ? 64 : 32);
+  p.splits = 1;
+  const bool narrow = !out_f32 && c128 <= 74 && K / BK >= 8 && N % 8 == 0;
+  if (narrow && M > BM && K / BK <= 48) {
+    p.mt = M <= 6 * BM ? 2 : 4;
+    p.nb = M <= 2 * BM ? 32 : 64;
+    return p;
+  }
+  if (narrow) {
+    int splits = static_cast<int>(148 / c128);
+    const int per = M <= BM ? 2 : 8;                    // k-blocks a split must keep
+    splits = splits > K / BK / per ? K / BK / per : splits;
+    splits = splits > 8 ? 8 : splits;
+    while (splits > 1 && static_cast<size_t>(splits) * M * N * 4 > SPLITK_WORKSPACE_BYTES)
+      --splits;
+    p.splits = splits < 1 ? 1 : splits;
+  }
+  // With four or more 512-row tiles, halving the weight tile doubles the activation traffic
+  // and the weight decode work for no gain: 128-wide tiles won every such case measured.
+  p.nb = (out_f32 || p.splits > 1 || c128 >= 120 || (p.mt == 4 && mtiles >= 4)) ? 128
+                                                                 : (ctas(64) >= 120 ? 64 : 32);
   // Wave quantisation: a grid of one M tile that is a few CTAs larger than the machine would
   // run a second, almost empty wave.  The full wave runs as one launch; the last few weight
   // tiles follow as a split-K launch of their own, which occupies the SMs the tail left idle.
-  const long ntiles = (N + 127) / 128;
   if (!out_f32 && p.splits == 1 && p.nb == 128 && mtiles == 1 && !fused && ntiles > 148 &&
       ntiles % 148 > 0 && ntiles % 148 <= 40 && K / BK >= 8 && N % 128 == 0) {
     int ts = static_cast<int>(148 / (ntiles % 148));
