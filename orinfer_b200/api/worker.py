@@ -131,6 +131,7 @@ class EngineWorker(threading.Thread):
                 self._reap()
                 self.metrics.set("requests_running", len(self.active))
                 self.metrics.set("requests_waiting", self.jobs.qsize())
+            self._exit_report()
         except Exception as exc:                     # fatal: fail closed
             self.lifecycle.set(Lifecycle.FAILED, f"{type(exc).__name__}: {exc}")
             self.metrics.set("backend_healthy", 0)
@@ -139,6 +140,19 @@ class EngineWorker(threading.Thread):
                 job.post({"type": "error", "status": 500, "message": "engine failure",
                           "code": "engine_failure"})
             self.ready.set()
+
+    def _exit_report(self) -> None:
+        """Telemetry lines at shutdown: ``SCHEDULER {json}`` (engine statistics, speculation,
+        prefix cache) and the device-timed spans when span profiling is on."""
+        import json
+        import sys
+        from ..utils import trace
+        eng = self.engine
+        body = {"engine": eng.stats.as_dict(), "speculation": eng.spec.statistics()}
+        if eng.prefix is not None:
+            body["prefix_cache"] = eng.prefix.statistics().__dict__
+        print(f"SCHEDULER {json.dumps(body, default=str)}", file=sys.stderr, flush=True)
+        trace.dump()
 
     def _warmup(self) -> None:
         self.engine.generate([[0]], max_new=1)

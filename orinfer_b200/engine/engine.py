@@ -37,6 +37,7 @@ from ..config import PAGE_TOKENS, GraphMode, LoadOptions, ModelConfig, Phase as 
     SchedulerOptions
 from ..core import sampling as S
 from ..core.prefix import RadixPrefixCache
+from ..utils import trace
 from ..models.runner import KVPool, Packet
 from ..models.weights import ModelWeights
 from .pages import OutOfPages, PagePool
@@ -356,6 +357,8 @@ class Engine:
             self.running.append(req)
             self.stats.admitted += 1
             admitted += 1
+            trace.line("admit", rid=req.rid, prompt=len(req.prompt), cached=req.cached_tokens,
+                       pages=len(req.pages), slot=req.slot, waiting=len(self.waiting))
             if self._should_yield(admitted, time.monotonic() - started):
                 break
 
@@ -428,6 +431,11 @@ class Engine:
                 n = min(n, self._next_endpoint(r) - r.offset)
             chunks.append((r, n))
             budget -= n
+        if chunks and trace.enabled("prefill_choose"):
+            trace.line("prefill_choose", decoders=len(decoders),
+                       chunks=[[r.rid, r.offset, n] for r, n in chunks], budget_left=budget,
+                       tpot_ms=None if self.tpot_ewma is None else round(self.tpot_ewma * 1e3, 3),
+                       cost_cells=self.costs.cells)
         return decoders, chunks
 
     # ------------------------------------------------------------------ recurrent snapshots
@@ -660,6 +668,7 @@ class Engine:
                 if r not in produced:
                     produced.append(r)
             self.stats.layered_decode_steps += 1
+            trace.line("layered", decoders=len(live), prompt_rows=sum(n for _, n in chunks))
 
         self.runner.stage_hook = (self.sched.prefill_stages, between)
         try:

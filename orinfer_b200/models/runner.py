@@ -19,6 +19,7 @@ import torch
 
 from ..config import KV_GROUP, PAGE_TOKENS, ModelConfig
 from ..ops import functional as F
+from ..utils import trace
 from .weights import LayerWeights, ModelWeights, QLinear
 
 
@@ -345,14 +346,16 @@ class ModelRunner:
         for i, lw in enumerate(self.w.layers):
             if i in pauses:
                 x = self._pause(p, x, rows, hook[1])
-            if lw.kind == "attn":
-                x = self._attention_block(lw, self._attn_index[i], x, p, rows, True)
-            else:
-                x = self._gdn_block(lw, i, x, p, rows)
-            if cfg.experts:
-                x = self._moe_ffn(lw, x, rows)
-            else:
-                x = self._dense_ffn(lw, x, rows)
+            with trace.span("attn" if lw.kind == "attn" else "gdn"):
+                if lw.kind == "attn":
+                    x = self._attention_block(lw, self._attn_index[i], x, p, rows, True)
+                else:
+                    x = self._gdn_block(lw, i, x, p, rows)
+            with trace.span("moe_ffn" if cfg.experts else "ffn"):
+                if cfg.experts:
+                    x = self._moe_ffn(lw, x, rows)
+                else:
+                    x = self._dense_ffn(lw, x, rows)
         return x
 
     supports_stages = True
