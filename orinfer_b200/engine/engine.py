@@ -67,6 +67,7 @@ class EngineStatistics:
     device_samples: int = 0
     offloaded_pages: int = 0
     restored_pages: int = 0
+    sharded_samples: int = 0                  # rows drawn from a sharded head's candidates
     layered_decode_steps: int = 0             # decode steps taken inside paused prefill packets
     stored_snapshots: int = 0                 # recurrent-state endpoints kept for the prefix cache
     restored_snapshots: int = 0
@@ -625,7 +626,7 @@ class Engine:
             packet.decode_rows = n_decode
         t1 = time.monotonic()
         self.stats.batch_inputs_s += t1 - t0
-        need = any(not self._plain(r) for r, _n, has in order if has)
+        need = any(self._needs_logits(r) for r, _n, has in order if has)
         graphed = None
         if (self.on_gpu and n_decode == 0 and chunk_rows and not self.recurrent
                 and getattr(self.runner, "stage_hook", None) is None
@@ -727,7 +728,7 @@ class Engine:
         t0 = time.monotonic()
         n = len(decoders)
         bucket = next(b for b in DECODE_BUCKETS if b >= n)
-        need = any(not self._plain(r) for r in decoders)
+        need = any(self._needs_logits(r) for r in decoders)
         g = self._graphs.get((bucket, need))
         if g is None:
             g = self._graphs[(bucket, need)] = _DecodeGraph(self, bucket)
@@ -751,11 +752,14 @@ class Engine:
                 with torch.cuda.graph(graph):
                     self.runner.greedy(g.packet, g.logits, g.tokens, need_logits=need)
                 g.graph = graph
+                g.local = getattr(self.runner, "_last_local", None)
                 g.launches = native.launches() - before
                 self.stats.graph_captures += 1
                 self.stats.capture_s += time.monotonic() - t1
         else:
             g.graph.replay()
+            if getattr(g, "local", None) is not None:
+                self.runner._last_local = g.local        # this graph's sharded logits
             from ..ops import native
             native.count_launches(getattr(g, "launches", 0))
             self.stats.graph_hits += 1
@@ -768,6 +772,31 @@ class Engine:
         return tokens, g.logits, order
 
     # ------------------------------------------------------------------ commit
+    def _sharded(self, r: Request) -> bool:
+        """Under a vocabulary-sharded head: drawn from per-rank candidates, no logit gather."""
+        return (hasattr(self.runner, "sample_sharded") and not self._plain(r)
+                and r.constraint is None and not r.want_logprobs and r.sampling.device_topk)
+
+    def _needs_logits(self, r: Request) -> bool:
+        return not self._plain(r) and not self._sharded(r)
+
+    def _sharded_samples(self, order) -> Dict[int, int]:
+        rows, reqs, sel = [], [], 0
+        for r, _n, has_logits in order:
+            if not has_logits:
+                continue
+            if self._sharded(r):
+                rows.append(sel)
+                reqs.append(r)
+            sel += 1
+        if not rows:
+            return {}
+        toks = self.runner.sample_sharded(
+            rows, [r.sampling for r in reqs],
+            [S.counter_uniform(r.sampling.seed, 0, len(r.generated)) for r in reqs])
+        self.stats.sharded_samples += len(rows)
+        return dict(zip(rows, toks))
+
     def _device_samples(self, order, logits) -> Dict[int, int]:
         """Rows whose sampling options need no host state are drawn by one launch of the
         device top-k sampler (same counter-RNG uniform as the host law); only their tokens
@@ -778,8 +807,8 @@ class Engine:
         for r, _n, has_logits in order:
             if not has_logits:
                 continue
-            if (not self._plain(r) and r.constraint is None and not r.want_logprobs
-                    and r.sampling.device_topk):
+            if (not self._plain(r) and not self._sharded(r) and r.constraint is None
+                    and not r.want_logprobs and r.sampling.device_topk):
                 rows.append(sel)
                 reqs.append(r)
             sel += 1
@@ -802,7 +831,8 @@ class Engine:
         produced = []
         sel = 0
         now = time.monotonic()
-        drawn = self._device_samples(order, logits)
+        drawn = self._sharded_samples(order)
+        drawn.update(self._device_samples(order, logits))
         for r, n, has_logits in order:
             was_decode = r.phase is Phase.DECODE
             r.offset += n

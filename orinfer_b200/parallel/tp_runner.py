@@ -55,6 +55,14 @@ class _TPMixin:
         dist.all_gather(parts, pad, group=self.group)
         return torch.cat([p[:, :w] for p, w in zip(parts, widths)], dim=1)
 
+    def sample_sharded(self, rows, options, uniforms):
+        """Tokens for the selected rows of the last forward, drawn from the sharded logits
+        (only top-k candidates cross ranks).  Collective: every rank calls it alike."""
+        from . import sharded_sampling
+        idx = torch.tensor(list(rows), dtype=torch.int64, device=self._last_local.device)
+        return sharded_sampling.sample_rows(self._last_local.index_select(0, idx), self.vocab0,
+                                            options, uniforms, self.group)
+
     def _vocab_range(self, rank: int):
         from .tp import split_blocks
         a, b = split_blocks(self.global_vocab // 128, self.world)[rank]
@@ -84,7 +92,7 @@ class TPRunner(_TPMixin, ModelRunner):
         return x
 
     def greedy(self, p: Packet, logits_out=None, token_out=None, need_logits: bool = True):
-        local = self.logits(p)                                         # [n_sel, V/tp]
+        local = self._last_local = self.logits(p)                      # [n_sel, V/tp]
         tok = self._merge_tokens(local, F.argmax(local))
         if token_out is not None:
             token_out[:tok.shape[0]].copy_(tok)
@@ -112,7 +120,7 @@ class TPTorchRunner(_TPMixin, TorchRunner):
         return R.f16(y)
 
     def greedy(self, p: Packet, logits_out=None, token_out=None, need_logits: bool = True):
-        local = self.logits(p)
+        local = self._last_local = self.logits(p)
         tok = self._merge_tokens(local, R.argmax_lowest(local))
         full = self._gather_logits(local) if need_logits else None
         return tok, full

@@ -76,3 +76,73 @@ def test_split_blocks_uneven():
     parts = split_blocks(76, 8)
     assert parts[0] == (0, 10) and parts[-1] == (67, 76)
     assert sum(b - a for a, b in parts) == 76
+
+
+def test_sharded_sampling_equals_the_host_law_on_the_full_row():
+    """World 1 (no process group): merged candidates + host law = host law on all logits,
+    ties at the top-k boundary included."""
+    from orinfer_b200.core import sampling as S
+    from orinfer_b200.parallel import sharded_sampling as SS
+    g = torch.Generator().manual_seed(3)
+    logits = torch.randn(6, 640, generator=g)
+    logits[0, [5, 300, 17]] = 4.0                      # ties inside and at the boundary
+    logits[1, 100:140] = 2.5
+    opts = [S.SamplingOptions(temperature=0.7, top_k=2, seed=1),
+            S.SamplingOptions(temperature=1.3, top_k=16, top_p=0.8, seed=2),
+            S.SamplingOptions(temperature=1.0, top_k=64, seed=3),
+            S.SamplingOptions(temperature=0.2, top_k=1, seed=4),
+            S.SamplingOptions(temperature=2.0, top_k=40, top_p=0.5, seed=5),
+            S.SamplingOptions(temperature=1.0, top_k=8, seed=6)]
+    for step in range(40):
+        us = [S.counter_uniform(o.seed, 0, step) for o in opts]
+        got = SS.sample_rows(logits, 0, opts, us)
+        want = [S.sample(logits[i].numpy(), [], o, u) for i, (o, u) in enumerate(zip(opts, us))]
+        assert got == want, step
+    # two shards merged by hand: same answer as one shard
+    a, b = logits[:, :384], logits[:, 384:]
+    va, ia = SS.local_candidates(a, 64, 0)
+    vb, ib = SS.local_candidates(b, 64, 384)
+    v, i = SS.merge_candidates(torch.cat([va, vb], 1), torch.cat([ia, ib], 1), 64)
+    v1, i1 = SS.merge_candidates(*SS.local_candidates(logits, 64, 0), 64)
+    assert torch.equal(v, v1) and torch.equal(i, i1)
+
+
+def _sampling_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from orinfer_b200.config import PRESETS, LoadOptions, SchedulerOptions
+    from orinfer_b200.core.sampling import SamplingOptions
+    from orinfer_b200.engine.engine import Engine
+    from orinfer_b200.models.runner import KVPool
+    from orinfer_b200.models.weights import random_model
+    from orinfer_b200.parallel.tp import shard_model
+    from orinfer_b200.parallel.tp_runner import TPTorchRunner
+    cfg = PRESETS["tiny"]
+    shard = shard_model(random_model(cfg, seed=0), rank, world)
+    eng = Engine(shard, kv_pages=12, max_context=256,
+                 load=LoadOptions(prefix_cache_bytes=0),
+                 sched=SchedulerOptions(max_active=4, prefill_chunk=64))
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (20, 9, 14)]
+    opts = [SamplingOptions(temperature=0.9, top_k=8, seed=11), None,
+            SamplingOptions(temperature=1.2, top_k=32, top_p=0.9, seed=12)]
+    assert isinstance(eng.runner, TPTorchRunner)
+    reqs = [eng.submit(p, 10, sampling=o) for p, o in zip(prompts, opts)]
+    while eng.has_work():
+        eng.step()
+    torch.save({"out": [r.generated for r in reqs], "sharded": eng.stats.sharded_samples},
+               os.path.join(out_dir, f"s{rank}.pt"))
+    dist.destroy_process_group()
+
+
+def test_tp2_engine_samples_from_sharded_candidates(tmp_path):
+    """Sampled requests on two ranks: both ranks commit the same tokens, drawn without
+    gathering the logits; a greedy request in the same batch is unaffected."""
+    port = 31500 + os.getpid() % 2000
+    mp.spawn(_sampling_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = torch.load(tmp_path / "s0.pt"), torch.load(tmp_path / "s1.pt")
+    assert r0["out"] == r1["out"]
+    assert all(len(o) == 10 for o in r0["out"])
+    assert r0["sharded"] == 20                       # two sampled requests x 10 tokens
