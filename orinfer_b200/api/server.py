@@ -35,7 +35,8 @@ def _error(status: int, message: str, code: Optional[str] = None, param: Optiona
 class Service:
     def __init__(self, engine_factory: Callable, codec: ChatCodec, model_name: str,
                  default_request_params: Optional[dict] = None, queue_timeout_ms: int = 0,
-                 output_timeout_ms: int = 60000):
+                 output_timeout_ms: int = 60000, preparation_workers: int = 4,
+                 preparation_memory_mib: int = 1024):
         self.codec = codec
         self.model_name = model_name
         self.defaults = default_request_params or {}
@@ -45,6 +46,8 @@ class Service:
                                    queue_timeout_ms)
         self.output_timeout_s = output_timeout_ms / 1e3
         self.started = time.time()
+        from .preparation import PreparationPool
+        self.preparation = PreparationPool(preparation_workers, preparation_memory_mib)
 
     def start(self, wait: bool = True) -> None:
         self.worker.start()
@@ -55,8 +58,17 @@ class Service:
         self.worker.stop(drain_ms / 1e3)
 
     # ------------------------------------------------------------------ chat
-    def submit(self, body: dict, loop) -> Job:
-        prepared = self.codec.prepare(body, self.defaults)
+    async def submit_async(self, body: dict, loop) -> Job:
+        """``submit`` with the preparation (template, tokeniser, grammar) on a pool thread,
+        under the pool's worker and memory budgets."""
+        from .preparation import estimate_bytes
+        prepared = await self.preparation.run(
+            lambda: self.codec.prepare(body, self.defaults), estimate_bytes(body))
+        return self.submit(body, loop, prepared)
+
+    def submit(self, body: dict, loop, prepared=None) -> Job:
+        if prepared is None:
+            prepared = self.codec.prepare(body, self.defaults)
         job = Job(prepared, "chatcmpl-" + uuid.uuid4().hex[:24], loop, asyncio.Queue())
         if self.lifecycle.state != Lifecycle.READY:
             raise RequestError("server is not ready", status=503, code="not_ready",
@@ -95,6 +107,7 @@ class Service:
             if eng.prefix is not None:
                 out["prefix_cache"] = eng.prefix.statistics().__dict__
             out["context"] = eng.max_context
+        out["preparation"] = self.preparation.snapshot()
         return out
 
 
@@ -170,7 +183,7 @@ def create_app(service: Service) -> FastAPI:
     @app.post("/v1/chat/completions")
     async def completions(request: HttpRequest):
         try:
-            job = service.submit(await _json(request), asyncio.get_running_loop())
+            job = await service.submit_async(await _json(request), asyncio.get_running_loop())
         except RequestError as e:
             headers = {"Retry-After": "1"} if e.status == 429 else None
             return JSONResponse(e.body(), status_code=e.status, headers=headers)

@@ -128,7 +128,7 @@ def cmd_serve(a) -> int:
     name = a.model if a.model != "qwen3.8-27b" or not a.preset else name
     service = Service(_engine_factory(a, weights, load, sched), _codec(a, weights, name), name,
                       json.loads(a.default_request_params), a.queue_timeout_ms,
-                      a.output_timeout_ms)
+                      a.output_timeout_ms, a.preparation_workers, a.preparation_memory_mib)
     service.start()
     if service.lifecycle.state != "ready":
         print(f"worker failed: {service.lifecycle.reason}", file=sys.stderr)
@@ -171,7 +171,8 @@ def _serve_manager(a, host: str, port: int, load, sched) -> int:
         weights, name = _weights(args)
         svc = Service(_engine_factory(args, weights, load, sched), _codec(args, weights, entry.name),
                       entry.name, dict(json.loads(a.default_request_params), **entry.defaults),
-                      a.queue_timeout_ms, a.output_timeout_ms)
+                      a.queue_timeout_ms, a.output_timeout_ms, a.preparation_workers,
+                      a.preparation_memory_mib)
         svc.start()
         if svc.lifecycle.state != "ready":
             raise RuntimeError(svc.lifecycle.reason or "worker failed")
@@ -376,6 +377,10 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--listen", default="[::]:8088")
     s.add_argument("--queue-timeout-ms", type=int, default=0)
     s.add_argument("--output-timeout-ms", type=int, default=60000)
+    s.add_argument("--preparation-workers", type=int, default=4,
+                   help="threads that render, tokenise and compile grammars for new requests")
+    s.add_argument("--preparation-memory-mib", type=int, default=1024,
+                   help="host memory that requests being prepared may hold at once")
     s.add_argument("--drain-timeout-ms", type=int, default=30000)
     s.add_argument("--state-dir", default=None, help="manager registry (serve without a model)")
     s.add_argument("--memory-budget-mib", type=int, default=0,
