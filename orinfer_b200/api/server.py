@@ -107,6 +107,9 @@ class Service:
             if eng.prefix is not None:
                 out["prefix_cache"] = eng.prefix.statistics().__dict__
             out["context"] = eng.max_context
+            pager = getattr(eng.runner, "pager", None)
+            if pager is not None:
+                out["expert_pager"] = pager.stats.as_dict()
         out["preparation"] = self.preparation.snapshot()
         return out
 

@@ -127,6 +127,19 @@ class Engine:
         extra = self.cfg.mtp_layers
         if kv_pages is None:
             kv_pages = self._auto_pages(extra)
+        # Bounded expert residency: a packet of r rows routes to at most r x top_k experts of
+        # a layer, so packets are capped at resident // top_k rows; the launch sequence depends
+        # on data read back per layer, so graphs and speculation are off.
+        self.row_cap = self.max_rows
+        self.paging = bool(self.cfg.experts) and 0 < self.load.resident_experts < self.cfg.experts
+        if self.paging:
+            if self.load.resident_experts < self.cfg.top_k:
+                raise ValueError("resident_experts must be at least top_k")
+            cap = self.row_cap = self.load.resident_experts // self.cfg.top_k
+            self.sched = dataclasses.replace(self.sched, max_active=min(self.sched.max_active, cap),
+                                             prefill_chunk=min(self.sched.prefill_chunk, cap))
+            self.load = dataclasses.replace(self.load, cuda_graph=GraphMode.OFF, mtp_drafts=0,
+                                            prompt_lookup=False)
         self.pool = PagePool(kv_pages)
         self.kv = KVPool.allocate(self.cfg, kv_pages, self.device, extra_layers=extra)
         if runner is not None:
@@ -145,6 +158,8 @@ class Engine:
         else:
             from ..models.torch_runner import TorchRunner
             self.runner = TorchRunner(weights, self.kv, self.max_rows)
+        if self.paging and hasattr(self.runner, "enable_expert_pager"):
+            self.runner.enable_expert_pager(self.load.resident_experts)
         slots = self.sched.max_active + 1                      # last slot = padding target
         self.page_table_host = np.zeros((slots, self.max_pages_per_req), np.int32)
         self.page_table_dev = torch.zeros(slots, self.max_pages_per_req, dtype=torch.int32,
@@ -404,7 +419,7 @@ class Engine:
     def _select(self):
         decoders = [r for r in self.running if r.phase is Phase.DECODE]
         prefills = [r for r in self.running if r.phase is Phase.PREFILL]
-        budget = max(self.max_rows - len(decoders), 0)
+        budget = max(min(self.max_rows, self.row_cap) - len(decoders), 0)
         budget = min(budget, self.sched.prefill_chunk)
         chunks = []
         if self.sched.policy is Policy.LATENCY and decoders and self.tpot_ewma is not None:

@@ -358,6 +358,24 @@ class ModelRunner:
                     x = self._dense_ffn(lw, x, rows)
         return x
 
+    def enable_expert_pager(self, resident: int):
+        """Keeps ``resident`` experts of every MoE layer on the device and the rest in pinned
+        host memory (see ``engine.expert_pager``).  The layers' full banks leave the device."""
+        from ..engine.expert_pager import ExpertPager
+        if getattr(self.w, "tp", None) is not None:
+            raise ValueError("expert paging and expert parallelism are exclusive")
+        banks = {}
+        for lw in self.w.layers:
+            if lw.expert_gate_up is not None:
+                banks[id(lw)] = (lw.expert_gate_up, lw.expert_down)
+        self.pager = ExpertPager(banks, resident, self.device)
+        for lw in self.w.layers:                      # free the device copies
+            if lw.expert_gate_up is not None:
+                res = self.pager.layers[id(lw)]
+                lw.expert_gate_up, lw.expert_down = res.host
+        torch.cuda.empty_cache() if self.device.type == "cuda" else None
+        return self.pager
+
     supports_stages = True
 
     def _pause(self, p: Packet, x, rows: int, between):
@@ -392,7 +410,14 @@ class ModelRunner:
         q8, s8 = self._prep(x, lw.post_norm, bank_up.signs, rows, y_out=y16)
         F.router_topk(y16, lw.router, cfg.experts, cfg.top_k, renorm=cfg.renormalize, rows=rows,
                       ids=sc.ids, probs=sc.probs, gate=sc.gate)
-        F.moe_dispatch(sc.ids, q8, s8, cfg.experts, sc, rows, bank_up.base, bank_up.experts)
+        pager = getattr(self, "pager", None)
+        if pager is not None:
+            # bounded residency: the routed experts are paged into slot banks and the ids
+            # become slot ids; everything after the router runs on the slot banks
+            bank_up, bank_dn, slot_ids = pager.page_in(id(lw), sc.ids, rows)
+            F.moe_dispatch(slot_ids, q8, s8, bank_up.experts, sc, rows, 0, bank_up.experts)
+        else:
+            F.moe_dispatch(sc.ids, q8, s8, cfg.experts, sc, rows, bank_up.base, bank_up.experts)
         total = rows * cfg.top_k
         F.qgemm_grouped(sc.q8, sc.scale, bank_up.codes, bank_up.scale, bank_up.fmt, 2 * f,
                         sc.gate_up, sc, total)
