@@ -3,9 +3,12 @@
 from __future__ import annotations
 
 import ctypes
+import os
 from pathlib import Path
 
-_PATH = Path(__file__).resolve().parents[1] / "_native" / "liborinfer_core.so"
+# ORINFER_CORE_LIB: load another build of the core (the sanitizer-instrumented ones)
+_PATH = Path(os.environ.get("ORINFER_CORE_LIB") or
+             Path(__file__).resolve().parents[1] / "_native" / "liborinfer_core.so")
 _lib = None
 
 

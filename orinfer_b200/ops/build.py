@@ -68,23 +68,38 @@ def build_kernels(verbose: bool = False) -> Path:
     return lib
 
 
-def build_core() -> Path:
+SANITIZERS = {"asan": "address,undefined", "tsan": "thread"}
+
+
+def build_core(sanitizer: str = "") -> Path:
+    """The C++ policy core.  ``sanitizer`` = "asan" (AddressSanitizer + UBSan) or "tsan"
+    builds an instrumented ``liborinfer_core_<sanitizer>.so`` beside the normal one; load it
+    with ``ORINFER_CORE_LIB`` and the matching runtime preloaded (see tests/test_sanitizers.py)."""
     OUT.mkdir(parents=True, exist_ok=True)
     OBJ.mkdir(parents=True, exist_ok=True)
     srcs = sorted((CSRC / "core").glob("*.cpp")) + sorted((CSRC / "dist").glob("*.cpp"))
-    lib = OUT / "liborinfer_core.so"
+    tag = f"_{sanitizer}" if sanitizer else ""
+    lib = OUT / f"liborinfer_core{tag}.so"
     if not srcs:
         return lib
+    flags = list(CXX_FLAGS)
+    if sanitizer:
+        flags = [f for f in flags if not f.startswith("-O")] + [
+            "-O1", "-g", "-fno-omit-frame-pointer", f"-fsanitize={SANITIZERS[sanitizer]}",
+            "-fno-sanitize-recover=undefined"]
     objs = []
     with cf.ThreadPoolExecutor(max_workers=8) as pool:
         jobs = []
         for src in srcs:
-            obj = OBJ / ("core_" + src.stem + ".o")
-            cmd = ["g++", *CXX_FLAGS, "-I", str(CSRC / "core"), "-c", str(src), "-o", str(obj)]
-            jobs.append(pool.submit(_compile, cmd, obj, _digest(src, " ".join(CXX_FLAGS)),
-                                    OBJ / ("core_" + src.stem + ".log")))
+            obj = OBJ / (f"core{tag}_" + src.stem + ".o")
+            cmd = ["g++", *flags, "-I", str(CSRC / "core"), "-c", str(src), "-o", str(obj)]
+            jobs.append(pool.submit(_compile, cmd, obj, _digest(src, " ".join(flags)),
+                                    OBJ / (f"core{tag}_" + src.stem + ".log")))
         objs = [j.result()[0] for j in jobs]
-    res = subprocess.run(["g++", "-shared", "-pthread", "-o", str(lib), *map(str, objs)],
+    link = ["g++", "-shared", "-pthread"]
+    if sanitizer:
+        link.append(f"-fsanitize={SANITIZERS[sanitizer]}")
+    res = subprocess.run([*link, "-o", str(lib), *map(str, objs)],
                          capture_output=True, text=True)
     if res.returncode:
         raise RuntimeError(res.stdout + res.stderr)
