@@ -442,7 +442,21 @@ def build_parser() -> argparse.ArgumentParser:
     vn = sub.add_parser("validate-nccl")
     vn.add_argument("--world", type=int, default=0, help="ranks (0 = all visible GPUs)")
     vn.set_defaults(fn=cmd_validate_nccl)
+    bn = sub.add_parser("bench", help="HTTP benchmark clients against a running server")
+    bn.add_argument("tool", choices=sorted(BENCH_TOOLS))
+    bn.add_argument("tool_args", nargs=argparse.REMAINDER)
+    bn.set_defaults(fn=cmd_bench)
     return ap
+
+
+BENCH_TOOLS = {"concurrency": "concurrency", "agentic": "agentic", "startup": "startup",
+               "encoders": "encoders", "scenario": "workloads"}
+
+
+def cmd_bench(a) -> int:
+    import importlib
+    mod = importlib.import_module(f".bench.{BENCH_TOOLS[a.tool]}", __package__)
+    return int(mod.main(a.tool_args) or 0)
 
 
 def main(argv=None) -> int:
