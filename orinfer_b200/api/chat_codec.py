@@ -44,7 +44,8 @@ class ByteTokenizer:
     0..255, followed by the control tokens."""
 
     SPECIALS = ["<|endoftext|>", "<|im_start|>", "<|im_end|>", "<think>", "</think>",
-                "<tool_call>", "</tool_call>"]
+                "<tool_call>", "</tool_call>", "<|vision_start|>", "<|image_pad|>",
+                "<|vision_end|>", "<|audio_start|>", "<|audio_pad|>", "<|audio_end|>"]
 
     def __init__(self, vocab: int):
         if vocab < 256 + len(self.SPECIALS):
@@ -181,6 +182,7 @@ class Prepared:
     model: str
     prompt_text: str = ""
     cache_prompt: bool = True
+    images: Optional[Any] = None      # api.images.BoundImages when the prompt holds images
 
 
 class ChatCodec:
@@ -194,6 +196,7 @@ class ChatCodec:
         self.defaults = defaults or ModelDefaults()
         self.context = context
         self.model_name = model_name
+        self.images = None            # api.images.ImageFrontend of a vision-capable model
 
     @classmethod
     def load(cls, model_dir: Path, vocab: int, context: int, model_name: str) -> "ChatCodec":
@@ -305,8 +308,24 @@ class ChatCodec:
             raise RequestError("`stop` cannot be combined with a constrained response",
                                param="stop")
 
+        bound = None
+        has_images = any(isinstance(m.get("content"), list) and any(
+            isinstance(p, dict) and p.get("type") == "image_url" for p in m["content"])
+            for m in messages)
+        if has_images and self.images is None:
+            raise RequestError("this model takes no image inputs", param="messages")
+        if self.images is not None:
+            from .images import ImageOptions
+            opts = ImageOptions.parse(req.get("image_processing"))
+            decoded = []
+            if has_images:
+                messages, decoded = self.images.extract(messages, opts)
         text = self.render(messages, tools, bool(thinking), kwargs)
         ids = self.tokenizer.encode(text)
+        if self.images is not None:
+            bound = self.images.bind(ids, decoded, opts)
+            ids = bound.prompt_ids
+            bound = bound if bound.images else None
         max_new = req.get("max_completion_tokens", req.get("max_tokens", d.max_tokens))
         if not isinstance(max_new, int) or max_new < 1:
             raise RequestError("`max_tokens` must be a positive integer", param="max_tokens")
@@ -325,7 +344,7 @@ class ChatCodec:
             json_object=json_object, tools=tools, tool_choice=req.get("tool_choice", "auto"),
             parallel_tool_calls=bool(req.get("parallel_tool_calls", True)),
             model=req.get("model") or self.model_name, prompt_text=text,
-            cache_prompt=bool(req.get("cache_prompt", True)))
+            cache_prompt=bool(req.get("cache_prompt", True)), images=bound)
 
     def render(self, messages, tools, thinking: bool, kwargs: Optional[dict] = None) -> str:
         ctx = dict(kwargs or {})

@@ -196,6 +196,7 @@ class EngineWorker(threading.Thread):
             req = self.engine.submit(p.prompt_ids, p.max_new, p.sampling, stop_ids=p.stop_ids,
                                      ignore_eos=p.ignore_eos, want_logprobs=p.want_logprobs,
                                      constraint=constraint, cache_prompt=p.cache_prompt,
+                                     **self._media(p),
                                      on_token=lambda r, tok, j=job: self._on_token(j, r, tok))
         except (RequestError, GrammarError, ValueError) as exc:
             job.post({"type": "error", "status": 400, "message": str(exc),
@@ -206,6 +207,26 @@ class EngineWorker(threading.Thread):
         self.active[req.rid] = job
         self.metrics.observe("queue", now - job.created)
         job.post({"type": "start"})
+
+    def _media(self, p: Prepared) -> dict:
+        """Engine arguments for the images of a prepared request: encoder features (cached by
+        image content) bound to their placeholder spans, and the rotary positions."""
+        bound = getattr(p, "images", None)
+        if bound is None:
+            return {}
+        from ..engine.request import MediaSpan
+        from ..models.vision import FeatureCache, VisionEncoder
+        if getattr(self, "_vision", None) is None:
+            enc = VisionEncoder(self.codec.images.spec, seed=0)
+            if self.engine.on_gpu:
+                enc = enc.to(self.engine.device).half()
+            self._vision = (enc, FeatureCache())
+        enc, cache = self._vision
+        spans = [MediaSpan(a, b, cache.get(im, enc), im.digest())
+                 for im, (a, b) in zip(bound.images, bound.spans)]
+        self.metrics.add("image_inputs_total", len(spans))
+        return {"media": spans, "rope_positions": bound.rope_positions,
+                "rope_delta": bound.rope_delta}
 
     def _constraint(self, p: Prepared):
         tok = self.codec.tokenizer

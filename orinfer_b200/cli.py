@@ -101,9 +101,14 @@ def _codec(a, weights, name):
     from .api.chat_codec import ChatCodec
     ctx = a.max_context or min(weights.config.max_context, 32768)
     if a.model_dir:
-        return ChatCodec.load(Path(a.model_dir), weights.config.vocab, ctx, name)
-    from .api.chat_codec import ByteTokenizer
-    return ChatCodec(ByteTokenizer(weights.config.vocab), context=ctx, model_name=name)
+        codec = ChatCodec.load(Path(a.model_dir), weights.config.vocab, ctx, name)
+    else:
+        from .api.chat_codec import ByteTokenizer
+        codec = ChatCodec(ByteTokenizer(weights.config.vocab), context=ctx, model_name=name)
+    if getattr(a, "vision", False):
+        from .api.images import frontend_for
+        codec.images = frontend_for(codec.tokenizer, weights.config.hidden, a.image_cache_mib)
+    return codec
 
 
 def cmd_serve(a) -> int:
@@ -382,6 +387,11 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--preparation-memory-mib", type=int, default=1024,
                    help="host memory that requests being prepared may hold at once")
     s.add_argument("--drain-timeout-ms", type=int, default=30000)
+    s.add_argument("--vision", action="store_true",
+                   help="accept image_url parts (random-init vision tower unless the model "
+                        "directory provides one)")
+    s.add_argument("--image-cache-mib", type=int, default=256,
+                   help="budget of the uuid image cache; 0 disables it")
     s.add_argument("--state-dir", default=None, help="manager registry (serve without a model)")
     s.add_argument("--memory-budget-mib", type=int, default=0,
                    help="manager mode: evict idle models beyond this many MiB of weights")

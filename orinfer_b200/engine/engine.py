@@ -210,6 +210,16 @@ class Engine:
         sampling = sampling or S.SamplingOptions(temperature=0.0)
         sampling.validate()
         req = Request(self._next_rid, list(map(int, prompt)), int(max_new), sampling, **kw)
+        if req.media or req.rope_positions is not None:
+            if not getattr(self.runner, "supports_media", False):
+                raise ValueError("this runner takes no media inputs")
+            for m in req.media:
+                if not (0 <= m.start < m.end <= len(req.prompt)) or \
+                        tuple(m.features.shape) != (m.end - m.start, self.cfg.hidden):
+                    raise ValueError("media span does not fit the prompt or the hidden size")
+            if req.rope_positions is not None and \
+                    tuple(req.rope_positions.shape) != (3, len(req.prompt)):
+                raise ValueError("rope_positions must be [3, prompt length]")
         self._next_rid += 1
         self.waiting.append(req)
         return req
@@ -335,7 +345,9 @@ class Engine:
                 continue
             node_ids, pages = [], []
             if self.prefix is not None and req.cache_prompt:
-                node_ids, pages = self.prefix.match(req.prompt, limit_tokens=len(req.prompt) - 1)
+                node_ids, pages = self.prefix.match(
+                    req.prompt, limit_tokens=len(req.prompt) - 1,
+                    media=req.page_media(PAGE_TOKENS, len(req.prompt) // PAGE_TOKENS + 1))
                 snapshot = None
                 if self.recurrent and node_ids:               # usable only up to a kept endpoint
                     cut, snapshot = self._snapshot_for(req.prompt, node_ids)
@@ -393,7 +405,9 @@ class Engine:
             if self.prefix is not None and req.cache_prompt and reason != "error":
                 # index the full pages of prompt + generated tokens whose KV is in the cache
                 toks = req.history[:req.offset]
-                adopted, ids = self.prefix.insert(toks, req.pages[:len(toks) // PAGE_TOKENS])
+                adopted, ids = self.prefix.insert(
+                    toks, req.pages[:len(toks) // PAGE_TOKENS],
+                    media=req.page_media(PAGE_TOKENS, len(toks) // PAGE_TOKENS + 1))
                 for pg, took in zip(req.pages, adopted):
                     if took:
                         self.pool.share(pg)
@@ -544,6 +558,14 @@ class Engine:
         self.stats.iterations += 1
         t0 = time.monotonic()
         pure_decode = not chunks
+        # media rows (feature overlay, shifted rotary positions) ride only in direct packets
+        has_media = any(r.media or r.rope_delta for r in decoders) or \
+            any(r.media or r.rope_delta for r, _ in chunks)
+        if has_media:
+            tokens, logits, order = self._run_direct(decoders, chunks)
+            produced = self._commit(order, tokens, logits)
+            self._capture_snapshots(chunks)
+            return produced
         if pure_decode and self.spec.enabled:
             produced = self.spec.run(decoders)
             if produced is not None:
@@ -628,6 +650,7 @@ class Engine:
         packet = Packet(self._upload("ids", ids), self._upload("req", req_rows),
                         self._upload("pos", pos), self.page_table_dev, rows, max_kv,
                         self._upload("sel", logit_rows).long())
+        has_media = self._attach_media(packet, decoders, chunks, chunk_rows, pos)
         if self.recurrent:
             segs = [[i, 1, 0, 0] for i in range(n_decode)] + [[c[0], c[1], 0, 0] for c in chunk_rows]
             first = list(range(n_decode)) + [c[0] for c in chunk_rows for _ in range(c[1])]
@@ -644,6 +667,7 @@ class Engine:
         need = any(self._needs_logits(r) for r, _n, has in order if has)
         graphed = None
         if (self.on_gpu and n_decode == 0 and chunk_rows and not self.recurrent
+                and not has_media
                 and getattr(self.runner, "stage_hook", None) is None
                 and self.cfg.head_dim in (64, 128)
                 and self.load.cuda_graph.uses_graph(ExecPhase.PREFILL)):
@@ -663,6 +687,30 @@ class Engine:
         if dummy_logits:
             return None, None, order
         return tokens, lg, order
+
+    def _attach_media(self, packet: Packet, decoders, chunks, chunk_rows, pos) -> bool:
+        """Feature overlay rows and (t, h, w) rotary positions of a direct packet."""
+        if not (any(r.media or r.rope_delta for r in decoders)
+                or any(r.media or r.rope_delta for r, _ in chunks)):
+            return False
+        rope = torch.tensor([pos, pos, pos], dtype=torch.int32)
+        rows_idx, feats = [], []
+        for i, r in enumerate(decoders):
+            rope[:, i] += r.rope_delta
+        for (r, n), (first, _n, off, _slot) in zip(chunks, chunk_rows):
+            if r.rope_positions is not None:
+                rope[:, first:first + n] = torch.as_tensor(
+                    r.rope_positions[:, off:off + n], dtype=torch.int32)
+            for m in r.media:
+                lo, hi = max(m.start, off), min(m.end, off + n)
+                if lo < hi:
+                    rows_idx += list(range(first + lo - off, first + hi - off))
+                    feats.append(m.features[lo - m.start:hi - m.start])
+        packet.mrope = rope.to(self.device)
+        if rows_idx:
+            packet.overlay_rows = torch.tensor(rows_idx, dtype=torch.int64, device=self.device)
+            packet.overlay = torch.cat(feats).to(self.device)
+        return True
 
     def _run_layered(self, decoders: List[Request], chunks, produced: List[Request]):
         """Layered prefill: the prompt rows run as their own packet, paused at

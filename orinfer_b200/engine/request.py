@@ -24,6 +24,15 @@ class Phase(enum.Enum):
 
 
 @dataclass
+class MediaSpan:
+    """Encoder features bound to the placeholder run ``[start, end)`` of a prompt."""
+    start: int
+    end: int
+    features: object                          # tensor [end - start, hidden]
+    digest: int                               # content hash (prefix-cache identity)
+
+
+@dataclass
 class Request:
     rid: int
     prompt: List[int]
@@ -35,6 +44,9 @@ class Request:
     cache_prompt: bool = True
     constraint: Optional[object] = None       # grammar / thinking-budget decoder (host)
     on_token: Optional[Callable] = None
+    media: List[MediaSpan] = field(default_factory=list)
+    rope_positions: Optional[object] = None   # int32 [3, len(prompt)] when media shift RoPE
+    rope_delta: int = 0                       # rotary position of token i >= len(prompt): i + delta
     # runtime
     phase: Phase = Phase.WAITING
     slot: int = -1                            # row of the device page table
@@ -64,6 +76,18 @@ class Request:
     @property
     def finished(self) -> bool:
         return self.phase is Phase.FINISHED
+
+    def page_media(self, page_tokens: int, pages: int) -> Optional[List[int]]:
+        """Per page, a hash of the media whose spans overlap it (0 = none); None without
+        media.  The prefix cache keys pages by (tokens, this value), so equal placeholder
+        runs of different images never share KV."""
+        if not self.media:
+            return None
+        out = [0] * pages
+        for m in self.media:
+            for pg in range(m.start // page_tokens, min(pages, (m.end - 1) // page_tokens + 1)):
+                out[pg] = (out[pg] * 0x9E3779B97F4A7C15 + m.digest + 1) & 0xFFFFFFFFFFFFFFFF
+        return out
 
     def context_needed(self) -> int:
         return len(self.prompt) + self.max_new

@@ -129,6 +129,12 @@ class Packet:
     # A verification packet of a speculative round: recurrent layers leave their state and
     # convolution history untouched and record what ``gdn_commit`` needs to keep a prefix.
     tentative: bool = False
+    # Media rows: ``overlay`` [n, hidden] replaces the embedding of rows ``overlay_rows``
+    # (int64 [n]); ``mrope`` int32 [3, rows] gives (t, h, w) rotary positions when they differ
+    # from ``row_pos`` (which always addresses the KV cache).
+    overlay_rows: Optional[torch.Tensor] = None
+    overlay: Optional[torch.Tensor] = None
+    mrope: Optional[torch.Tensor] = None
 
     def ensure_segments(self) -> None:
         if self.segments is not None:
@@ -336,8 +342,10 @@ class ModelRunner:
         if rows > ws.max_rows:
             raise ValueError(f"packet of {rows} rows exceeds workspace ({ws.max_rows})")
         x = F.embed_w8(p.ids, self.w.embed_q, self.w.embed_s, out=ws.hidden)
+        if p.overlay_rows is not None:
+            x.index_copy_(0, p.overlay_rows, p.overlay.to(x.dtype))
         ws.resid[:rows].zero_()
-        F.rope_table(p.row_pos, cfg.head_dim, cfg.rope_theta, ws.cos, ws.sin, rows=rows)
+        self._rope(p, rows)
         hook, self.stage_hook = getattr(self, "stage_hook", None), None
         pauses = set()
         if hook is not None:
@@ -391,8 +399,20 @@ class ModelRunner:
         between()
         x[:rows].copy_(keep_x)
         ws.resid[:rows].copy_(keep_r)
-        F.rope_table(p.row_pos, cfg.head_dim, cfg.rope_theta, ws.cos, ws.sin, rows=rows)
+        self._rope(p, rows)
         return x
+
+    supports_media = True
+
+    def _rope(self, p: Packet, rows: int) -> None:
+        cfg, ws = self.cfg, self.ws
+        if p.mrope is None:
+            F.rope_table(p.row_pos, cfg.head_dim, cfg.rope_theta, ws.cos, ws.sin, rows=rows)
+        else:
+            from .vision import mrope_tables
+            cos, sin = mrope_tables(p.mrope[:, :rows], cfg.head_dim, cfg.rope_theta)
+            ws.cos[:rows].copy_(cos)
+            ws.sin[:rows].copy_(sin)
 
     def _moe_ffn(self, lw: LayerWeights, x, rows: int):
         """norm+rotate+quantise once -> router top-k -> dispatch rows to expert-contiguous

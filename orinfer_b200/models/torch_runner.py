@@ -159,13 +159,20 @@ class TorchRunner:
         return self._reduce(self._linear(lw.down, R.silu_mul(gu[:, :f], gu[:, f:])))
 
     supports_stages = True
+    supports_media = True
 
     def forward_hidden(self, p: Packet):
         cfg = self.cfg
         rows = p.rows
         x = R.embed_w8(p.ids[:rows], self.w.embed_q, self.w.embed_s)
+        if p.overlay_rows is not None:
+            x = x.index_copy(0, p.overlay_rows, p.overlay.to(x.dtype))
         resid = torch.zeros(rows, cfg.hidden)
-        cos, sin = R.rope_tables(p.row_pos[:rows], cfg.head_dim, cfg.rope_theta)
+        if p.mrope is None:
+            cos, sin = R.rope_tables(p.row_pos[:rows], cfg.head_dim, cfg.rope_theta)
+        else:
+            from .vision import mrope_tables
+            cos, sin = mrope_tables(p.mrope[:, :rows], cfg.head_dim, cfg.rope_theta)
         zc = cfg.zero_centered_norm
         hook, self.stage_hook = getattr(self, "stage_hook", None), None
         pauses = set()
