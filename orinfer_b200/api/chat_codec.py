@@ -183,6 +183,7 @@ class Prepared:
     prompt_text: str = ""
     cache_prompt: bool = True
     images: Optional[Any] = None      # api.images.BoundImages when the prompt holds images
+    audio: Optional[Any] = None       # api.audio.BoundAudio of a transcription request
 
 
 class ChatCodec:

@@ -243,6 +243,8 @@ def create_app(service: Service) -> FastAPI:
 
     from .encoders import install as install_encoders
     from .ollama import install as install_ollama
+    from .audio import install as install_audio
     install_encoders(app, service)
     install_ollama(app, service)
+    install_audio(app, service)
     return app

@@ -211,10 +211,22 @@ class EngineWorker(threading.Thread):
     def _media(self, p: Prepared) -> dict:
         """Engine arguments for the images of a prepared request: encoder features (cached by
         image content) bound to their placeholder spans, and the rotary positions."""
+        from ..engine.request import MediaSpan
+        audio = getattr(p, "audio", None)
+        if audio is not None:
+            from ..models.audio import AudioEncoder
+            if getattr(self, "_audio", None) is None:
+                enc = AudioEncoder(self.engine.cfg.hidden, seed=0)
+                if self.engine.on_gpu:
+                    enc = enc.to(self.engine.device).half()
+                self._audio = enc
+            spans = [MediaSpan(a, b, self._audio.encode(x), x.digest())
+                     for x, (a, b) in zip(audio.inputs, audio.spans)]
+            self.metrics.add("audio_inputs_total", len(spans))
+            return {"media": spans}
         bound = getattr(p, "images", None)
         if bound is None:
             return {}
-        from ..engine.request import MediaSpan
         from ..models.vision import FeatureCache, VisionEncoder
         if getattr(self, "_vision", None) is None:
             enc = VisionEncoder(self.codec.images.spec, seed=0)

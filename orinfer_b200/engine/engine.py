@@ -559,8 +559,8 @@ class Engine:
         t0 = time.monotonic()
         pure_decode = not chunks
         # media rows (feature overlay, shifted rotary positions) ride only in direct packets
-        has_media = any(r.media or r.rope_delta for r in decoders) or \
-            any(r.media or r.rope_delta for r, _ in chunks)
+        has_media = any(r.rope_delta for r in decoders) or \
+            any(r.media or r.rope_positions is not None for r, _ in chunks)
         if has_media:
             tokens, logits, order = self._run_direct(decoders, chunks)
             produced = self._commit(order, tokens, logits)
@@ -690,8 +690,8 @@ class Engine:
 
     def _attach_media(self, packet: Packet, decoders, chunks, chunk_rows, pos) -> bool:
         """Feature overlay rows and (t, h, w) rotary positions of a direct packet."""
-        if not (any(r.media or r.rope_delta for r in decoders)
-                or any(r.media or r.rope_delta for r, _ in chunks)):
+        if not (any(r.rope_delta for r in decoders)
+                or any(r.media or r.rope_positions is not None for r, _ in chunks)):
             return False
         rope = torch.tensor([pos, pos, pos], dtype=torch.int32)
         rows_idx, feats = [], []
