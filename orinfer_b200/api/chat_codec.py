@@ -198,6 +198,7 @@ class ChatCodec:
         self.context = context
         self.model_name = model_name
         self.images = None            # api.images.ImageFrontend of a vision-capable model
+        self.tool_format = "xml"      # "dsml": DeepSeek-style call blocks (api/dsml.py)
 
     @classmethod
     def load(cls, model_dir: Path, vocab: int, context: int, model_name: str) -> "ChatCodec":
@@ -309,6 +310,15 @@ class ChatCodec:
             raise RequestError("`stop` cannot be combined with a constrained response",
                                param="stop")
 
+        if self.tool_format == "dsml":
+            # results follow their calls' order; past calls are shown in wire syntax
+            from . import dsml
+            messages = dsml.reorder_tool_results(messages)
+            messages = [dict(m, content=((m.get("content") or "") + "\n\n" +
+                                         dsml.render_calls(m["tool_calls"])).lstrip("\n"),
+                             tool_calls=None)
+                        if m.get("role") == "assistant" and m.get("tool_calls") else m
+                        for m in messages]
         bound = None
         has_images = any(isinstance(m.get("content"), list) and any(
             isinstance(p, dict) and p.get("type") == "image_url" for p in m["content"])

@@ -80,6 +80,20 @@ class GrammarConstraint:
         self.words = (vocab + 31) // 32
         self.done = False
 
+    @classmethod
+    def from_lark(cls, tokenizer, vocab: int, lark: str, eos_ids: Sequence[int]
+                  ) -> "GrammarConstraint":
+        """Constraint from grammar text in llguidance's Lark dialect (tool-call syntaxes)."""
+        import llguidance
+        grammar = llguidance.LLMatcher.grammar_from_lark(lark)
+        err = llguidance.LLMatcher.validate_grammar(grammar)
+        if err:
+            raise GrammarError(f"invalid grammar: {err}")
+        m = llguidance.LLMatcher(ll_tokenizer(tokenizer, vocab), grammar)
+        if m.is_error():
+            raise GrammarError(m.get_error())
+        return cls(tokenizer, vocab, None, eos_ids, _matcher=m)
+
     def needs_mask(self) -> bool:
         return True
 

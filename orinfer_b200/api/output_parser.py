@@ -18,6 +18,22 @@ from typing import Dict, List, Optional
 
 THINK_OPEN, THINK_CLOSE = "<think>", "</think>"
 TOOL_OPEN, TOOL_CLOSE = "<tool_call>", "</tool_call>"
+DSML_OPEN = "<｜DSML｜ calls>"
+
+
+def merge_tool_calls(deltas: List[dict]) -> List[dict]:
+    """Fold streamed tool-call deltas (same ``index``) into whole calls."""
+    calls: Dict[int, dict] = {}
+    for d in deltas:
+        fn = d.get("function") or {}
+        cur = calls.get(d["index"])
+        if cur is None:
+            cur = calls[d["index"]] = {"id": d.get("id"), "type": d.get("type", "function"),
+                                       "function": {"name": fn.get("name", ""), "arguments": ""}}
+        elif fn.get("name"):
+            cur["function"]["name"] = fn["name"]
+        cur["function"]["arguments"] += fn.get("arguments") or ""
+    return [calls[i] for i in sorted(calls)]
 
 
 @dataclass
@@ -68,7 +84,12 @@ def parse_tool_call(body: str) -> Optional[dict]:
 
 class OutputParser:
     def __init__(self, thinking: bool = False, stops: Optional[List[str]] = None,
-                 json_mode: bool = False, tools: bool = True):
+                 json_mode: bool = False, tools: bool = True, tool_format: str = "xml"):
+        # tool_format "dsml": calls arrive as a DSML block and their arguments are streamed
+        # as JSON fragments while the values are still being generated (api/dsml.py)
+        self.tool_format = tool_format
+        self.dsml = None
+        self.error: Optional[str] = None
         self.in_think = thinking            # template already opened <think>
         self.stops = list(stops or [])
         self.json_mode = json_mode          # tags inside a JSON body are data
@@ -90,7 +111,7 @@ class OutputParser:
         if not self.json_mode:
             m.append(THINK_OPEN)
             if self.tools_enabled:
-                m.append(TOOL_OPEN)
+                m.append(DSML_OPEN if self.tool_format == "dsml" else TOOL_OPEN)
         return m
 
     def feed(self, text: str, final: bool = False) -> Delta:
@@ -100,6 +121,10 @@ class OutputParser:
             return delta
         self.buffer += text
         while True:
+            if self.dsml is not None:
+                if not self._feed_dsml(delta):
+                    break
+                continue
             markers = self._markers()
             hit_pos, hit = -1, None
             for m in markers:
@@ -118,6 +143,9 @@ class OutputParser:
                 self.in_think = False
             elif hit == THINK_OPEN:
                 self.in_think = True
+            elif hit == DSML_OPEN and self.tool_format == "dsml":
+                from .dsml import DsmlCalls
+                self.dsml = DsmlCalls()
             elif hit == TOOL_OPEN:
                 self.in_tool, self.tool_text = True, ""
             elif hit == TOOL_CLOSE:
@@ -140,6 +168,34 @@ class OutputParser:
             delta.content += TOOL_OPEN + self.tool_text
             self.in_tool = False
         return delta
+
+    def _feed_dsml(self, delta: Delta) -> bool:
+        """Run the buffered text through the DSML state machine; True when the block closed
+        and ordinary parsing resumes."""
+        from .dsml import DsmlError
+        text, self.buffer = self.buffer, ""
+        try:
+            events = self.dsml.feed(text)
+        except DsmlError as e:
+            self.error = str(e)             # a malformed block ends the visible output
+            self.stopped = True
+            self.dsml = None
+            return False
+        for ev in events:
+            if ev[0] == "begin":
+                self.saw_tool_call = True
+                delta.tool_calls.append({"index": self.tool_index, "id": f"call_{self.tool_index}",
+                                         "type": "function",
+                                         "function": {"name": ev[1], "arguments": ""}})
+            elif ev[0] == "arguments":
+                delta.tool_calls.append({"index": self.tool_index,
+                                         "function": {"arguments": ev[1]}})
+            elif ev[0] == "end":
+                self.tool_index += 1
+            elif ev[0] == "close":
+                self.buffer, self.dsml = self.dsml.buffer, None
+                return True
+        return False
 
     def _emit(self, delta: Delta, text: str) -> None:
         if not text:

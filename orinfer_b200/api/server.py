@@ -230,8 +230,8 @@ def create_app(service: Service) -> FastAPI:
                 if reasoning:
                     msg["reasoning_content"] = reasoning
                 if calls:
-                    msg["tool_calls"] = [{k: v for k, v in c.items() if k != "index"}
-                                         for c in calls]
+                    from .output_parser import merge_tool_calls
+                    msg["tool_calls"] = merge_tool_calls(calls)
                 choice: Dict[str, Any] = {"index": 0, "message": msg,
                                           "finish_reason": ev["finish_reason"]}
                 if job.prepared.want_logprobs:

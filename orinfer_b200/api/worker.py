@@ -192,7 +192,8 @@ class EngineWorker(threading.Thread):
             constraint = self._constraint(p)
             job.parser = OutputParser(thinking=p.thinking, stops=p.stop_strings,
                                       json_mode=p.json_schema is not None or p.json_object,
-                                      tools=bool(p.tools))
+                                      tools=bool(p.tools),
+                                      tool_format=getattr(self.codec, "tool_format", "xml"))
             req = self.engine.submit(p.prompt_ids, p.max_new, p.sampling, stop_ids=p.stop_ids,
                                      ignore_eos=p.ignore_eos, want_logprobs=p.want_logprobs,
                                      constraint=constraint, cache_prompt=p.cache_prompt,
@@ -245,6 +246,12 @@ class EngineWorker(threading.Thread):
         inner = None
         if p.json_schema is not None or p.json_object:
             inner = GrammarConstraint(tok, self.engine.cfg.vocab, p.json_schema, p.stop_ids)
+        elif (getattr(self.codec, "tool_format", "xml") == "dsml" and p.tools
+              and p.tool_choice == "required"):
+            from .dsml import grammar as dsml_grammar
+            inner = GrammarConstraint.from_lark(
+                tok, self.engine.cfg.vocab,
+                dsml_grammar(p.tools, required=True, parallel=p.parallel_tool_calls), p.stop_ids)
         if p.thinking and p.thinking_budget is not None:
             return ThinkingBudget(tok.encode("</think>"), p.thinking_budget, p.max_new, inner)
         if p.thinking and inner is not None:

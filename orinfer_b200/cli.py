@@ -105,6 +105,7 @@ def _codec(a, weights, name):
     else:
         from .api.chat_codec import ByteTokenizer
         codec = ChatCodec(ByteTokenizer(weights.config.vocab), context=ctx, model_name=name)
+    codec.tool_format = getattr(a, "tool_format", "xml")
     if getattr(a, "vision", False):
         from .api.images import frontend_for
         codec.images = frontend_for(codec.tokenizer, weights.config.hidden, a.image_cache_mib)
@@ -387,6 +388,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--preparation-memory-mib", type=int, default=1024,
                    help="host memory that requests being prepared may hold at once")
     s.add_argument("--drain-timeout-ms", type=int, default=30000)
+    s.add_argument("--tool-format", choices=["xml", "dsml"], default="xml",
+                   help="tool-call wire syntax the model emits")
     s.add_argument("--vision", action="store_true",
                    help="accept image_url parts (random-init vision tower unless the model "
                         "directory provides one)")
