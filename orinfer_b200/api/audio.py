@@ -48,17 +48,24 @@ def prepare_transcription(codec, data: bytes, language: Optional[str], prompt: O
     if max_tokens is not None:
         body["max_tokens"] = max_tokens
     base = codec.prepare(body, defaults)
+    b = codec.boundary
+    ctl = b.controls if b is not None else (lambda t: t)
+    esc = b.escape if b is not None else (lambda t: t)
     text = ""
     if prompt:
-        text += f"<|im_start|>system\n{prompt}<|im_end|>\n"
-    text += f"<|im_start|>user\n{AUDIO_TEXT}<|im_end|>\n<|im_start|>assistant\n"
+        if not isinstance(prompt, str):
+            raise RequestError("`prompt` must be text", param="prompt")
+        text += ctl("<|im_start|>system\n") + esc(prompt) + ctl("<|im_end|>\n")
+    text += ctl(f"<|im_start|>user\n{AUDIO_TEXT}<|im_end|>\n<|im_start|>assistant\n")
     if language:
-        if not isinstance(language, str) or len(language) > 32 or not language.replace("-", "").isalnum():
+        if not isinstance(language, str) or len(language) > 32 or \
+                not language.replace("-", "").isalnum():
             raise RequestError("`language` must be a language name or code", param="language")
         text += f"language {language}\n"
     ids = []
-    for t in tok.encode(text):
+    for t in codec.encode_rendered(text):
         ids += [t] * n if t == pad else [t]
+    text = codec.display(text)
     start = ids.index(pad)
     if len(ids) >= codec.context:
         raise RequestError(f"the audio needs {len(ids)} prompt tokens, beyond the context window "

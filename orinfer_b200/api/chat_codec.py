@@ -67,6 +67,10 @@ class ByteTokenizer:
                 i += 1
         return out
 
+    def encode_plain(self, text: str) -> List[int]:
+        """Bytes only: control-token spellings in the text stay ordinary characters."""
+        return list(text.encode("utf-8"))
+
     def token_bytes(self, tok: int) -> bytes:
         if tok < 256:
             return bytes([tok])
@@ -189,11 +193,21 @@ class Prepared:
 class ChatCodec:
     def __init__(self, tokenizer, template: Optional[str] = None,
                  defaults: Optional[ModelDefaults] = None, context: int = 32768,
-                 model_name: str = "orinfer"):
+                 model_name: str = "orinfer", protect_controls: bool = True):
         self.tokenizer = tokenizer
         self.env = jinja2.Environment(trim_blocks=False, lstrip_blocks=False)
         self.env.filters["tojson"] = _tojson
-        self.template = self.env.from_string(template or DEFAULT_TEMPLATE)
+        # control tokens may come only from the template source or the server (token_boundary.py)
+        self.boundary = None
+        if protect_controls:
+            from .token_boundary import Boundary, BoundaryError
+            try:
+                self.boundary = Boundary(tokenizer)
+            except BoundaryError:
+                self.boundary = None
+        source = template or DEFAULT_TEMPLATE
+        self.template = self.env.from_string(
+            self.boundary.template(source) if self.boundary else source)
         self.defaults = defaults or ModelDefaults()
         self.context = context
         self.model_name = model_name
@@ -310,12 +324,19 @@ class ChatCodec:
             raise RequestError("`stop` cannot be combined with a constrained response",
                                param="stop")
 
+        if self.boundary is not None:
+            messages = self.boundary.escape_value(messages)
+            tools = self.boundary.escape_value(tools)
+            kwargs = self.boundary.escape_value(kwargs)
         if self.tool_format == "dsml":
             # results follow their calls' order; past calls are shown in wire syntax
             from . import dsml
+            mark = dsml.MARK
+            if self.boundary is not None and mark in self.boundary.tokens:
+                mark = self.boundary.control(mark)
             messages = dsml.reorder_tool_results(messages)
             messages = [dict(m, content=((m.get("content") or "") + "\n\n" +
-                                         dsml.render_calls(m["tool_calls"])).lstrip("\n"),
+                                         dsml.render_calls(m["tool_calls"], mark)).lstrip("\n"),
                              tool_calls=None)
                         if m.get("role") == "assistant" and m.get("tool_calls") else m
                         for m in messages]
@@ -330,9 +351,11 @@ class ChatCodec:
             opts = ImageOptions.parse(req.get("image_processing"))
             decoded = []
             if has_images:
-                messages, decoded = self.images.extract(messages, opts)
+                messages, decoded = self.images.extract(
+                    messages, opts, self.boundary.controls if self.boundary else None)
         text = self.render(messages, tools, bool(thinking), kwargs)
-        ids = self.tokenizer.encode(text)
+        ids = self.encode_rendered(text)
+        text = self.display(text)
         if self.images is not None:
             bound = self.images.bind(ids, decoded, opts)
             ids = bound.prompt_ids
@@ -356,6 +379,18 @@ class ChatCodec:
             parallel_tool_calls=bool(req.get("parallel_tool_calls", True)),
             model=req.get("model") or self.model_name, prompt_text=text,
             cache_prompt=bool(req.get("cache_prompt", True)), images=bound)
+
+    def encode_rendered(self, text: str) -> List[int]:
+        return self.boundary.encode(text) if self.boundary else self.tokenizer.encode(text)
+
+    def display(self, text: str) -> str:
+        """Rendered text with the private handles shown as their control-token spellings."""
+        if self.boundary is None:
+            return text
+        names = {str(i): s for s, i in self.boundary.tokens.items()}
+        return self.boundary._split.sub(
+            lambda m: self.boundary.prefix if m.group(1) == "p" else names.get(m.group(1), ""),
+            text)
 
     def render(self, messages, tools, thinking: bool, kwargs: Optional[dict] = None) -> str:
         ctx = dict(kwargs or {})

@@ -25,6 +25,7 @@ from __future__ import annotations
 import json
 from typing import Dict, List, Optional, Tuple
 
+MARK = "｜DSML｜"
 OPEN = "<｜DSML｜ calls>"
 CLOSE = "</｜DSML｜ calls>"
 INVOKE = "<｜DSML｜ invoke "
@@ -179,24 +180,26 @@ def parse_calls(text: str) -> List[dict]:
     return calls
 
 
-def render_calls(tool_calls: List[dict]) -> str:
+def render_calls(tool_calls: List[dict], mark: str = MARK) -> str:
     """Assistant history -> wire text.  String arguments are written raw with
-    ``string="true"``; everything else as JSON with ``string="false"``."""
-    out = [OPEN]
+    ``string="true"``; everything else as JSON with ``string="false"``.  ``mark`` stands for
+    the ``｜DSML｜`` control spelling (a private handle when control tokens are protected)."""
+    out = [f"<{mark} calls>"]
     for call in tool_calls:
         fn = call.get("function", call)
         args = fn.get("arguments") or {}
         if isinstance(args, str):
             args = json.loads(args) if args.strip() else {}
-        out.append(f'{INVOKE}name="{fn["name"]}">')
+        out.append(f'<{mark} invoke name="{fn["name"]}">')
         for key, value in args.items():
             if isinstance(value, str):
-                out.append(f'{PARAMETER}name="{key}" string="true">{value}{PARAMETER_END}')
+                out.append(f'<{mark} parameter name="{key}" string="true">{value}'
+                           f'</{mark} parameter>')
             else:
-                out.append(f'{PARAMETER}name="{key}" string="false">'
-                           f'{json.dumps(value, ensure_ascii=False)}{PARAMETER_END}')
-        out.append(INVOKE_END)
-    out.append(CLOSE)
+                out.append(f'<{mark} parameter name="{key}" string="false">'
+                           f'{json.dumps(value, ensure_ascii=False)}</{mark} parameter>')
+        out.append(f"</{mark} invoke>")
+    out.append(f"</{mark} calls>")
     return "\n".join(out)
 
 

@@ -131,10 +131,12 @@ class ImageFrontend:
         self.cache = ImageCache(cache_bytes)
 
     # ---- step 1: before templating -------------------------------------------------
-    def extract(self, messages: List[dict], options: ImageOptions
+    def extract(self, messages: List[dict], options: ImageOptions, controls=None
                 ) -> Tuple[List[dict], List[V.ImageInput]]:
         """Replace image parts by text parts holding one placeholder group each; returns the
-        rewritten messages and the decoded images in prompt order."""
+        rewritten messages and the decoded images in prompt order.  ``controls`` maps the
+        placeholder spelling to protected control-token handles (api/token_boundary.py)."""
+        placeholder = controls(IMAGE_TEXT) if controls else IMAGE_TEXT
         images: List[V.ImageInput] = []
         out = []
         for mi, m in enumerate(messages):
@@ -151,7 +153,7 @@ class ImageFrontend:
                 if len(images) >= options.max_images:
                     raise RequestError(f"more than {options.max_images} images", param=where)
                 images.append(self._one(part, options, where))
-                parts.append({"type": "text", "text": IMAGE_TEXT})
+                parts.append({"type": "text", "text": placeholder})
             out.append(dict(m, content=parts))
         return out, images
 

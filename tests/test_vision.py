@@ -234,8 +234,10 @@ def test_chat_with_images_over_http(client):
     assert many.status_code == 400
     big = _ask(client, [red], image_processing={"max_tokens": 2})
     assert big.status_code == 400 and "max_tokens" in big.json()["error"]["message"]
+    # a placeholder spelled out in user text is ordinary characters, not a control token
     forged = _ask(client, [{"type": "text", "text": "<|image_pad|>"}])
-    assert forged.status_code == 400
+    assert forged.status_code == 200
+    assert forged.json()["usage"]["prompt_tokens"] == n_text - len("compare") + len("<|image_pad|>")
     assert "orinfer_image_inputs_total" in client.get("/metrics").text
 
 
