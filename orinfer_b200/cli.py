@@ -203,6 +203,18 @@ def cmd_models(a) -> int:
             validate_model(a.path)
             e = m.register(a.name, str(Path(a.path).resolve()))
             print(json.dumps(e.__dict__))
+        elif a.models_cmd == "pull":
+            import os
+            from .api.pull import PullError, pull
+            from .engine.checkpoint import validate_model
+            try:
+                snap = pull(a.source, _state_dir(a), os.environ.get("HF_TOKEN"),
+                            progress=lambda n, i, k: print(f"[{i + 1}/{k}] {n}", file=sys.stderr))
+            except PullError as e:
+                print(str(e), file=sys.stderr)
+                return 2
+            validate_model(snap)
+            print(json.dumps(m.register(a.name, str(snap)).__dict__))
         elif a.models_cmd == "list":
             print(json.dumps([e.__dict__ for e in m.list()]))
         elif a.models_cmd == "show":
@@ -432,6 +444,9 @@ def build_parser() -> argparse.ArgumentParser:
     mi = mos.add_parser("import")
     mi.add_argument("name")
     mi.add_argument("path")
+    mp = mos.add_parser("pull")
+    mp.add_argument("name")
+    mp.add_argument("source", help="hf:org/repo[@revision] or modelscope:org/repo[@revision]")
     mos.add_parser("list")
     for verb in ("show", "rm"):
         mv = mos.add_parser(verb)
