@@ -334,6 +334,26 @@ def cmd_score_model(a) -> int:
     return 0
 
 
+def cmd_generate(a) -> int:
+    """One prompt through the single-request reference path (no batching, graphs, prefix cache
+    or speculation): the isolation oracle, as token ids or text."""
+    load, sched = _options(a)
+    load.prefix_cache_bytes = 0
+    weights, name = _weights(a)
+    engine = _engine_factory(a, weights, load, sched)()
+    codec = _codec(a, weights, name)
+    if a.tokens:
+        ids = [int(x) for x in a.tokens.split(",")]
+    else:
+        ids = codec.prepare({"messages": [{"role": "user", "content": a.prompt or "Hello"}],
+                             "enable_thinking": False}).prompt_ids
+    t0 = time.monotonic()
+    out = engine.generate_reference(ids, a.max_tokens)
+    print(json.dumps({"prompt_tokens": len(ids), "tokens": out,
+                      "text": codec.tokenizer.decode(out), "seconds": time.monotonic() - t0}))
+    return 0
+
+
 def cmd_make_model(a) -> int:
     """Random-init weights of a preset geometry quantised to the checkpoint format."""
     import torch
@@ -433,6 +453,12 @@ def build_parser() -> argparse.ArgumentParser:
     _load_args(sc)
     sc.add_argument("--tokens", required=True, help="comma-separated token ids")
     sc.set_defaults(fn=cmd_score_model)
+    ge = sub.add_parser("generate")
+    _load_args(ge)
+    ge.add_argument("--prompt", default=None)
+    ge.add_argument("--tokens", default=None, help="comma-separated prompt token ids")
+    ge.add_argument("--max-tokens", type=int, default=32)
+    ge.set_defaults(fn=cmd_generate)
     mk = sub.add_parser("make-model")
     mk.add_argument("--preset", required=True, choices=sorted(PRESETS))
     mk.add_argument("--output", required=True)

@@ -273,6 +273,66 @@ class Engine:
             self.step()
         return [r.generated for r in reqs]
 
+    def generate_reference(self, prompt: Sequence[int], max_new: int = 16,
+                           chunk: Optional[int] = None) -> List[int]:
+        """Greedy generation of one request on its own, outside the queue: the prompt runs as
+        full chunks of ``chunk`` tokens, its tail and every new token as single-row packets, so
+        no padding row ever enters attention, convolution or recurrent state.  This is the
+        isolation oracle that batched, chunked, graph-replayed and speculative runs are checked
+        against (the reference's crates/orinfer-engine/src/runtime/reference_generation.rs:5-6).
+        No prefix cache, no graphs, no speculation; needs an idle engine."""
+        if self.running or self.waiting:
+            raise RuntimeError("generate_reference needs an idle engine")
+        prompt = list(map(int, prompt))
+        total = len(prompt) + max_new
+        if not prompt or total > self.max_context:
+            raise ValueError("prompt is empty or prompt + max_new exceeds the context window")
+        chunk = min(chunk or self.sched.prefill_chunk, self.max_rows)
+        need = (total + PAGE_TOKENS - 1) // PAGE_TOKENS
+        if need > self.pool.available:
+            self._reclaim(need)
+        if not self.free_slots or need > self.pool.available:
+            raise MemoryError("no free slot or KV pages for a reference run")
+        slot = self.free_slots.pop()
+        pages = self.pool.take(need)
+        try:
+            row = self.page_table_host[slot]
+            row[:] = 0
+            row[:need] = pages
+            self.page_table_dev[slot].copy_(torch.from_numpy(row))
+
+            def run(tokens: List[int], start: int) -> int:
+                n = len(tokens)
+                p = Packet(self._upload("ids", tokens), self._upload("req", [slot] * n),
+                           self._upload("pos", list(range(start, start + n))),
+                           self.page_table_dev, n, start + n, self._upload("sel", [n - 1]).long())
+                if self.recurrent:
+                    p.segments = self._upload("segs", [0, n, 0, 0]).view(-1, 4)
+                    p.row_first = self._upload("first", [0] * n)
+                    p.n_segments = 1
+                if self.on_gpu and n > 1:
+                    p.chunks = self._upload("chunks", [0, n, start, slot]).view(-1, 4)
+                    p.max_q_len = n
+                tok, _ = self.runner.greedy(p, need_logits=False)
+                return int(tok[0])
+
+            at, full = 0, len(prompt) // chunk * chunk
+            last = -1
+            while at < full:
+                last = run(prompt[at:at + chunk], at)
+                at += chunk
+            for t in prompt[full:]:
+                last = run([t], at)
+                at += 1
+            out = [last]
+            while len(out) < max_new:
+                out.append(run([out[-1]], at))
+                at += 1
+            return out[:max_new]
+        finally:
+            self.pool.release(pages)
+            self.free_slots.append(slot)
+
     # ------------------------------------------------------------------ admission
     def _pages_needed(self, req: Request) -> int:
         return (req.context_needed() + PAGE_TOKENS - 1) // PAGE_TOKENS
