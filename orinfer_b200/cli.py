@@ -184,7 +184,25 @@ def _serve_manager(a, host: str, port: int, load, sched) -> int:
             raise RuntimeError(svc.lifecycle.reason or "worker failed")
         return RunnerHandle(svc, create_app(svc)), weights.nbytes()
 
-    manager = ModelManager(_state_dir(a), start, lambda h: h.service.stop(a.drain_timeout_ms),
+    def start_process(entry):
+        from .api.child_runner import ChildRunner, ProxyApp, weight_bytes
+        extra = ["--device", a.device, "--cuda-graph", str(a.cuda_graph),
+                 "--scheduler-policy", str(a.scheduler_policy),
+                 "--max-active-requests", str(a.max_active_requests),
+                 "--prefix-cache-mib", str(a.prefix_cache_mib), "--tp", str(a.tp),
+                 "--default-request-params",
+                 json.dumps(dict(json.loads(a.default_request_params), **entry.defaults))]
+        if a.max_context:
+            extra += ["--max-context", str(a.max_context)]
+        child = ChildRunner(entry.path, entry.name, extra).start()
+        return RunnerHandle(child, ProxyApp(child.base_url)), weight_bytes(entry.path)
+
+    process = getattr(a, "runners", "process") == "process"
+
+    def stop(handle):                       # ChildRunner.stop takes seconds, Service.stop ms
+        handle.service.stop(a.drain_timeout_ms / 1e3 if process else a.drain_timeout_ms)
+
+    manager = ModelManager(_state_dir(a), start_process if process else start, stop,
                            memory_budget_bytes=getattr(a, "memory_budget_mib", 0) << 20)
     print(f"API READY http://{a.listen}/v1; manager with {len(manager.list())} models",
           file=sys.stderr)
@@ -428,6 +446,9 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--image-cache-mib", type=int, default=256,
                    help="budget of the uuid image cache; 0 disables it")
     s.add_argument("--state-dir", default=None, help="manager registry (serve without a model)")
+    s.add_argument("--runners", choices=["process", "inproc"], default="process",
+                   help="manager mode: each model in its own child process (its memory returns "
+                        "on retirement) or as services inside the gateway process")
     s.add_argument("--memory-budget-mib", type=int, default=0,
                    help="manager mode: evict idle models beyond this many MiB of weights")
     s.set_defaults(fn=cmd_serve)
