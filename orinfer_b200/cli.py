@@ -343,6 +343,13 @@ def cmd_score_model(a) -> int:
     p = Packet(t(ids), t([0] * len(ids)), t(list(range(len(ids)))), table, len(ids), len(ids))
     _, logits = engine.runner.greedy(p)
     logits = logits.float().cpu().numpy()
+    if a.jsonl:
+        from .bench import quality as Q
+        query = Q.queries_from(Q.read_jsonl(a.query_from)) if a.query_from else None
+        probes = Q.probes_from_logits(logits, ids, a.case_id, "prefill", query)
+        Q.write_jsonl(a.jsonl, probes)
+        print(json.dumps({"probes": len(probes), "file": a.jsonl}))
+        return 0
     out = []
     opts = S.SamplingOptions()
     for i in range(len(ids) - 1):
@@ -473,6 +480,10 @@ def build_parser() -> argparse.ArgumentParser:
     sc = sub.add_parser("score-model")
     _load_args(sc)
     sc.add_argument("--tokens", required=True, help="comma-separated token ids")
+    sc.add_argument("--jsonl", default=None, help="write paired-probe records to this file")
+    sc.add_argument("--query-from", default=None,
+                    help="baseline probe file whose top-3 ids are also scored")
+    sc.add_argument("--case-id", default="case")
     sc.set_defaults(fn=cmd_score_model)
     ge = sub.add_parser("generate")
     _load_args(ge)
@@ -524,7 +535,7 @@ def build_parser() -> argparse.ArgumentParser:
     return ap
 
 
-BENCH_TOOLS = {"concurrency": "concurrency", "agentic": "agentic", "startup": "startup",
+BENCH_TOOLS = {"quality": "quality", "concurrency": "concurrency", "agentic": "agentic", "startup": "startup",
                "encoders": "encoders", "scenario": "workloads"}
 
 
