@@ -36,14 +36,15 @@ class Service:
     def __init__(self, engine_factory: Callable, codec: ChatCodec, model_name: str,
                  default_request_params: Optional[dict] = None, queue_timeout_ms: int = 0,
                  output_timeout_ms: int = 60000, preparation_workers: int = 4,
-                 preparation_memory_mib: int = 1024):
+                 preparation_memory_mib: int = 1024, step_timeout_ms: int = 0,
+                 exit_on_stall: bool = False):
         self.codec = codec
         self.model_name = model_name
         self.defaults = default_request_params or {}
         self.metrics = Metrics()
         self.lifecycle = Lifecycle()
         self.worker = EngineWorker(engine_factory, codec, self.metrics, self.lifecycle,
-                                   queue_timeout_ms)
+                                   queue_timeout_ms, step_timeout_ms, exit_on_stall)
         self.output_timeout_s = output_timeout_ms / 1e3
         self.started = time.time()
         from .preparation import PreparationPool

@@ -60,7 +60,10 @@ class Job:
 
     def post(self, event: dict) -> None:
         if self.loop is not None:
-            self.loop.call_soon_threadsafe(self.events.put_nowait, event)
+            try:
+                self.loop.call_soon_threadsafe(self.events.put_nowait, event)
+            except RuntimeError:            # the server's loop is gone: nobody is listening
+                self.cancelled = True
         else:
             self.events.put_nowait(event)
 
@@ -78,8 +81,13 @@ class CallJob:
 
 class EngineWorker(threading.Thread):
     def __init__(self, engine_factory: Callable[[], Engine], codec: ChatCodec, metrics: Metrics,
-                 lifecycle: Lifecycle, queue_timeout_ms: int = 0):
+                 lifecycle: Lifecycle, queue_timeout_ms: int = 0, step_timeout_ms: int = 0,
+                 exit_on_stall: bool = False):
         super().__init__(name="orinfer-gpu", daemon=True)
+        # a step that runs past step_timeout_ms fails the service closed (engine/watchdog.py)
+        self.step_timeout_s = step_timeout_ms / 1e3
+        self.exit_on_stall = exit_on_stall
+        self.watchdog = None
         self.engine_factory = engine_factory
         self.engine: Optional[Engine] = None
         self.codec = codec
@@ -112,6 +120,9 @@ class EngineWorker(threading.Thread):
     # ------------------------------------------------------------------ the loop
     def run(self) -> None:
         try:
+            if self.step_timeout_s > 0:
+                from ..engine.watchdog import StepWatchdog
+                self.watchdog = StepWatchdog(self._stalled)
             self.engine = self.engine_factory()
             self._warmup()
             self.lifecycle.set(Lifecycle.READY)
@@ -126,7 +137,13 @@ class EngineWorker(threading.Thread):
                         pass
                     continue
                 t0 = time.monotonic()
+                if self.watchdog is not None:
+                    self.watchdog.arm("engine step", self.step_timeout_s)
                 self.engine.step()
+                if self.watchdog is not None:
+                    self.watchdog.disarm()
+                    if self.watchdog.tripped:
+                        raise RuntimeError(f"{self.watchdog.tripped} ran past its deadline")
                 self.metrics.add("compute_seconds_total", time.monotonic() - t0)
                 self._reap()
                 self.metrics.set("requests_running", len(self.active))
@@ -140,6 +157,22 @@ class EngineWorker(threading.Thread):
                 job.post({"type": "error", "status": 500, "message": "engine failure",
                           "code": "engine_failure"})
             self.ready.set()
+
+    def _stalled(self, what: str, waited_s: float) -> None:
+        """Watchdog thread: the engine thread is stuck inside a step.  Fail closed, answer the
+        clients, and optionally leave the process without running exit hooks."""
+        import os
+        import sys
+        self.lifecycle.set(Lifecycle.FAILED, f"{what} exceeded {self.step_timeout_s:.1f} s")
+        self.metrics.set("backend_healthy", 0)
+        self.metrics.add("watchdog_timeouts_total")
+        print(f"WATCHDOG {what} still running after {waited_s:.1f} s; failing closed",
+              file=sys.stderr, flush=True)
+        for job in list(self.active.values()):
+            job.post({"type": "error", "status": 500, "message": "engine stalled",
+                      "code": "engine_stalled"})
+        if self.exit_on_stall:
+            os._exit(70)
 
     def _exit_report(self) -> None:
         """Telemetry lines at shutdown: ``SCHEDULER {json}`` (engine statistics, speculation,

@@ -132,13 +132,16 @@ def cmd_serve(a) -> int:
         return _serve_manager(a, host, int(port), load, sched)
     weights, name = _weights(a)
     name = a.model if a.model != "qwen3.8-27b" or not a.preset else name
+    print(f"MODEL READY {name}; {weights.nbytes() / 2 ** 20:.0f} MiB of weights", file=sys.stderr)
     service = Service(_engine_factory(a, weights, load, sched), _codec(a, weights, name), name,
                       json.loads(a.default_request_params), a.queue_timeout_ms,
-                      a.output_timeout_ms, a.preparation_workers, a.preparation_memory_mib)
+                      a.output_timeout_ms, a.preparation_workers, a.preparation_memory_mib,
+                      a.step_timeout_ms, exit_on_stall=True)
     service.start()
     if service.lifecycle.state != "ready":
         print(f"worker failed: {service.lifecycle.reason}", file=sys.stderr)
         return 1
+    print("WORKER READY", file=sys.stderr)
     print("WARMUP READY", file=sys.stderr)
     print(f"API READY http://{a.listen}/v1; context {service.worker.engine.max_context}; "
           f"continuous_batching=true", file=sys.stderr)
@@ -445,6 +448,9 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--preparation-memory-mib", type=int, default=1024,
                    help="host memory that requests being prepared may hold at once")
     s.add_argument("--drain-timeout-ms", type=int, default=30000)
+    s.add_argument("--step-timeout-ms", type=int, default=120000,
+                   help="an engine step running longer fails the server closed and exits 70 "
+                        "(0 disables the watchdog)")
     s.add_argument("--tool-format", choices=["xml", "dsml"], default="xml",
                    help="tool-call wire syntax the model emits")
     s.add_argument("--vision", action="store_true",
