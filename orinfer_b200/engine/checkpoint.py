@@ -177,6 +177,13 @@ def load_model(directory, device="cpu", verify: bool = False,
     directory = Path(directory)
     desc = read_descriptor(directory)
     cfg = ModelConfig.from_json((directory / "config.json").read_text())
+    from .. import contracts
+    try:                                      # architecture -> family, policy and target checks
+        contracts.create(desc["architecture"], desc.get("compute_policy", contracts.COMPUTE_POLICY),
+                         cfg)
+        contracts.parse_target(desc.get("target", contracts.TARGET))
+    except contracts.ContractError as e:
+        raise CheckpointError(str(e)) from e
     to_gpu = torch.device(device).type == "cuda"
     try:
         t, meta = read_tensors(directory / "model.safetensors", workers=workers, pin=to_gpu,
