@@ -67,6 +67,50 @@ def recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tenso
     return out, s
 
 
+def recurrence_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
+                       beta: torch.Tensor, state: torch.Tensor, chunk: int = 16):
+    """The same recurrence in chunkwise (WY) form: inside a chunk of ``C`` tokens everything
+    is a small matrix product, so a kernel can put it on tensor cores (the reference's
+    kernels/cuda/model/gdn_chunk.py:12,102 uses C = 16 with FP16 operands and an FP32 state).
+
+    With ``G_i`` the running sum of ``g`` inside the chunk and ``S0`` the state before it::
+
+        A[i, j] = beta_i * exp(G_i - G_j) * (k_i . k_j)          for j < i, else 0
+        B[i]    = beta_i * (v_i - exp(G_i) * S0^T k_i)
+        Delta   = (I + A)^-1 B                                   (unit lower-triangular solve)
+        o_i     = exp(G_i) * S0^T q_i + sum_{j <= i} exp(G_i - G_j) * (k_j . q_i) * Delta_j
+        S_C     = exp(G_C) * S0 + sum_j exp(G_C - G_j) * k_j (x) Delta_j
+
+    which follows from unrolling ``S_i = exp(g_i) S_{i-1} + k_i (x) delta_i``.  Same operands
+    and results as ``recurrence``; the two agree to fp32 rounding."""
+    t, hv, d = v.shape
+    rep = hv // q.shape[1]
+    qe = (q.float().repeat_interleave(rep, 1) * (d ** -0.5)).transpose(0, 1)     # [HV, T, D]
+    ke = k.float().repeat_interleave(rep, 1).transpose(0, 1)
+    ve = v.float().transpose(0, 1)
+    gt, bt = g.float().t(), beta.float().t()                                     # [HV, T]
+    s = state.float().clone()
+    out = torch.empty(hv, t, d)
+    for lo in range(0, t, chunk):
+        hi = min(t, lo + chunk)
+        c = hi - lo
+        kc, qc, vc = ke[:, lo:hi], qe[:, lo:hi], ve[:, lo:hi]
+        big_g = torch.cumsum(gt[:, lo:hi], dim=1)                                # [HV, C]
+        decay = torch.exp(big_g[:, :, None] - big_g[:, None, :])                 # e^(G_i - G_j)
+        lower = torch.tril(torch.ones(c, c), -1)
+        a = bt[:, lo:hi, None] * decay * (kc @ kc.transpose(1, 2)) * lower
+        b = bt[:, lo:hi, None] * (vc - torch.exp(big_g)[:, :, None] * (kc @ s))
+        delta = torch.linalg.solve_triangular(torch.eye(c)[None] + a, b, upper=False,
+                                              unitriangular=True)
+        causal = torch.tril(torch.ones(c, c))
+        out[:, lo:hi] = torch.exp(big_g)[:, :, None] * (qc @ s) + \
+            ((qc @ kc.transpose(1, 2)) * decay * causal) @ delta
+        tail = torch.exp(big_g[:, -1:] - big_g)                                  # e^(G_C - G_j)
+        s = torch.exp(big_g[:, -1])[:, None, None] * s + \
+            (kc * tail[:, :, None]).transpose(1, 2) @ delta
+    return out.transpose(0, 1).contiguous(), s
+
+
 def gated_norm(o: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float,
                sigmoid_gate: bool = False) -> torch.Tensor:
     """o fp32 [T, HV, D], z f16-valued [T, HV, D] -> f16-valued [T, HV*D]."""

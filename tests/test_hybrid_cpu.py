@@ -155,3 +155,28 @@ def test_hybrid_prefix_reuse_restores_recurrent_state():
         eng.step()
     assert r3.cached_tokens == 0
     assert r3.generated == cold.generate([other], max_new=4)[0]
+
+
+def test_chunked_gdn_recurrence_equals_the_sequential_one():
+    """The WY (chunkwise) form and the token-by-token scan are the same function, for any
+    chunk size, ragged last chunks, grouped heads and a non-zero starting state."""
+    import torch
+    from orinfer_b200.ref import gdn_ref as G
+    gen = torch.Generator().manual_seed(5)
+    t, hk, hv, d = 45, 2, 4, 16
+    q = torch.nn.functional.normalize(torch.randn(t, hk, d, generator=gen), dim=-1)
+    k = torch.nn.functional.normalize(torch.randn(t, hk, d, generator=gen), dim=-1)
+    v = torch.randn(t, hv, d, generator=gen)
+    g = -torch.rand(t, hv, generator=gen) * 0.5
+    beta = torch.rand(t, hv, generator=gen)
+    s0 = torch.randn(hv, d, d, generator=gen) * 0.3
+    want_o, want_s = G.recurrence(q, k, v, g, beta, s0)
+    for chunk in (1, 16, 64, 7):
+        o, s = G.recurrence_chunked(q, k, v, g, beta, s0, chunk)
+        assert torch.allclose(o, want_o, atol=2e-5, rtol=1e-5), chunk
+        assert torch.allclose(s, want_s, atol=2e-5, rtol=1e-5), chunk
+    # chunk boundaries may fall anywhere: two calls carry the state like one
+    o1, s1 = G.recurrence_chunked(q[:20], k[:20], v[:20], g[:20], beta[:20], s0)
+    o2, s2 = G.recurrence_chunked(q[20:], k[20:], v[20:], g[20:], beta[20:], s1)
+    assert torch.allclose(torch.cat([o1, o2]), want_o, atol=2e-5, rtol=1e-5)
+    assert torch.allclose(s2, want_s, atol=2e-5, rtol=1e-5)
