@@ -319,11 +319,18 @@ def create_gateway_app(manager: ModelManager, sweep_s: float = 5.0):
 
     async def forward(request: HttpRequest, ollama: bool):
         body = await request.body()
+        payload = {}
         try:
-            payload = _json.loads(body)
-            name = payload["model"]
+            if request.headers.get("content-type", "").startswith("multipart/form-data"):
+                form = await request.form()          # parsed from the body that was just cached
+                name = form["model"]
+                if not isinstance(name, str):
+                    raise TypeError("model")
+            else:
+                payload = _json.loads(body)
+                name = payload["model"]
         except (ValueError, KeyError, TypeError):
-            err = ManagerError("request body must be JSON with a `model` field", 400)
+            err = ManagerError("the request must name its `model` (JSON field or form field)", 400)
             return fail_ollama(err) if ollama else openai_error(err)
         keep = None
         if ollama and "keep_alive" in payload:
@@ -345,7 +352,7 @@ def create_gateway_app(manager: ModelManager, sweep_s: float = 5.0):
         return route
 
     for path in ("/v1/chat/completions", "/v1/chat/completions/render", "/v1/embeddings",
-                 "/v1/rerank", "/rerank"):
+                 "/v1/rerank", "/rerank", "/v1/audio/transcriptions"):
         app.add_api_route(path, handler(False), methods=["POST"])
     for path in ("/api/chat", "/api/generate", "/api/show"):
         app.add_api_route(path, handler(True), methods=["POST"])

@@ -177,6 +177,19 @@ def test_gateway_forwards_by_model_and_releases_leases(tmp_path):
         assert started == ["tiny-alias"] and m.running()[0]["leases"] == 0
         emb = c.post("/v1/embeddings", json={"model": "tiny", "input": "hello"})
         assert emb.status_code == 200 and len(emb.json()["data"][0]["embedding"]) == 256
+        import io
+        import wave
+        wav = io.BytesIO()
+        with wave.open(wav, "wb") as w:
+            w.setnchannels(1)
+            w.setsampwidth(2)
+            w.setframerate(16000)
+            w.writeframes(b"\x00\x10" * 8000)
+        tr = c.post("/v1/audio/transcriptions", files={"file": ("a.wav", wav.getvalue())},
+                    data={"model": "tiny", "max_tokens": "3"})
+        assert tr.status_code == 200 and "text" in tr.json()
+        assert c.post("/v1/audio/transcriptions", files={"file": ("a.wav", wav.getvalue())}
+                      ).status_code == 400                          # no model named
         missing = c.post("/v1/chat/completions", json=dict(body, model="nope"))
         assert missing.status_code == 404 and missing.json()["error"]["code"] == "model_not_found"
         assert c.post("/api/generate", json={"model": "nope", "prompt": "x"}).status_code == 404
