@@ -54,6 +54,36 @@ def parse_keep_alive(value) -> Optional[float]:
     raise RequestError("invalid keep_alive", param="keep_alive")
 
 
+def _content(text, images):
+    """Ollama ``images`` (bare base64 strings) -> ``image_url`` parts with a data URI whose
+    media type is read from the file signature (PNG, JPEG or WebP only)."""
+    if not images:
+        return text
+    import base64
+    import binascii
+    if not isinstance(images, list):
+        raise RequestError("`images` must be an array of base64 strings", param="images")
+    parts = [{"type": "text", "text": text or ""}]
+    for item in images:
+        try:
+            head = base64.b64decode(item[:64] + "=" * (-len(item[:64]) % 4))[:16] \
+                if isinstance(item, str) else None
+        except (binascii.Error, ValueError):
+            head = None
+        if head is None:
+            raise RequestError("invalid base64 image", param="images")
+        if head.startswith(b"\x89PNG\r\n\x1a\n"):
+            mime = "image/png"
+        elif head.startswith(b"\xff\xd8\xff"):
+            mime = "image/jpeg"
+        elif head[:4] == b"RIFF" and head[8:12] == b"WEBP":
+            mime = "image/webp"
+        else:
+            raise RequestError("images must be PNG, JPEG or WebP", param="images")
+        parts.append({"type": "image_url", "image_url": {"url": f"data:{mime};base64,{item}"}})
+    return parts
+
+
 def translate(body: Dict[str, Any], generate: bool) -> Dict[str, Any]:
     """Ollama request -> native chat request."""
     if not isinstance(body, dict):
@@ -67,12 +97,16 @@ def translate(body: Dict[str, Any], generate: bool) -> Dict[str, Any]:
         msgs = []
         if body.get("system"):
             msgs.append({"role": "system", "content": body["system"]})
-        msgs.append({"role": "user", "content": body.get("prompt", "")})
+        msgs.append({"role": "user", "content": _content(body.get("prompt", ""),
+                                                          body.get("images"))})
         if body.get("suffix"):
             raise RequestError("suffix is not supported", param="suffix")
         out["messages"] = msgs
     else:
-        out["messages"] = body.get("messages") or []
+        out["messages"] = [dict({k: v for k, v in m.items() if k != "images"},
+                                content=_content(m.get("content", ""), m["images"]))
+                           if isinstance(m, dict) and m.get("images") else m
+                           for m in body.get("messages") or []]
     opts = body.get("options") or {}
     for k, v in opts.items():
         if k in OPTION_MAP:

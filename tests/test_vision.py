@@ -247,3 +247,29 @@ def test_model_without_vision_refuses_images(weights):
     with pytest.raises(RequestError, match="no image"):
         codec.prepare({"messages": [{"role": "user", "content": [
             {"type": "image_url", "image_url": {"url": _png((1, 2, 3))}}]}]})
+
+
+def test_ollama_images_become_image_parts(client):
+    import base64
+    from PIL import Image
+    from orinfer_b200.api.chat_codec import RequestError
+    from orinfer_b200.api.ollama import translate
+    buf = io.BytesIO()
+    Image.new("RGB", (64, 64), (0, 255, 0)).save(buf, format="JPEG")
+    b64 = base64.b64encode(buf.getvalue()).decode()
+    out = translate({"model": "m", "messages": [{"role": "user", "content": "what?",
+                                                 "images": [b64]}]}, generate=False)
+    parts = out["messages"][0]["content"]
+    assert parts[0] == {"type": "text", "text": "what?"}
+    assert parts[1]["image_url"]["url"].startswith("data:image/jpeg;base64,")
+    assert "images" not in out["messages"][0]
+    gen = translate({"model": "m", "prompt": "see", "images": [_png((1, 2, 3)).split(",")[1]]},
+                    generate=True)
+    assert gen["messages"][-1]["content"][1]["image_url"]["url"].startswith("data:image/png")
+    for bad in (["!!!"], [base64.b64encode(b"GIF89a" + b"\0" * 20).decode()], "x"):
+        with pytest.raises(RequestError):
+            translate({"model": "m", "prompt": "p", "images": bad}, generate=True)
+    r = client.post("/api/chat", json={"model": "tiny", "stream": False, "options": {"num_predict": 3},
+                                       "messages": [{"role": "user", "content": "what?",
+                                                     "images": [b64]}]})
+    assert r.status_code == 200 and r.json()["prompt_eval_count"] > 6
