@@ -188,7 +188,10 @@ class EngineWorker(threading.Thread):
         trace.dump()
 
     def _warmup(self) -> None:
-        self.engine.generate([[0]], max_new=1)
+        if self.engine.cfg.bidirectional:
+            self.engine.encode([0, 1])
+        else:
+            self.engine.generate([[0]], max_new=1)
 
     def _receive(self) -> None:
         for _ in range(QUEUE_CAPACITY):

@@ -92,8 +92,16 @@ class ModelConfig:
     # MTP draft head (number of extra decoder layers, 0 = none)
     mtp_layers: int = 0
     max_context: int = 32768
+    # Encoder families (embedding models): every token attends to the whole input.  Such a
+    # model serves /v1/embeddings through ``Engine.encode``; it does not generate.
+    bidirectional: bool = False
+    pooling: str = "mean"          # "mean" | "last" | "first"
 
     def __post_init__(self):
+        if self.pooling not in ("mean", "last", "first"):
+            raise ValueError("pooling must be mean, last or first")
+        if self.bidirectional and self.arch == "hybrid":
+            raise ValueError("recurrent (gated-delta-rule) layers cannot run bidirectionally")
         if self.q_heads % max(self.kv_heads, 1):
             raise ValueError("q_heads must be a multiple of kv_heads")
         for dim in (self.hidden, self.ffn or 128, self.expert_ffn or 128,
@@ -133,6 +141,7 @@ class ModelConfig:
 # Named geometries of the benchmark configurations.
 PRESETS = {
     "tiny": ModelConfig(),
+    "tiny-embed": ModelConfig(name="tiny-embed", bidirectional=True, pooling="mean"),
     "tiny-moe": ModelConfig(name="tiny-moe", arch="moe", experts=8, top_k=2, expert_ffn=128,
                             ffn=0),
     "tiny-hybrid": ModelConfig(name="tiny-hybrid", arch="hybrid", layers=4, gdn_period=4,

@@ -203,6 +203,8 @@ class Engine:
                sampling: Optional[S.SamplingOptions] = None, **kw) -> Request:
         if len(prompt) == 0:
             raise ValueError("empty prompt")
+        if self.cfg.bidirectional:
+            raise ValueError("an encoder model embeds its input; it does not generate")
         if len(prompt) + max_new > self.max_context:
             raise ValueError(
                 f"request of {len(prompt)} + {max_new} tokens exceeds the context window "
@@ -247,13 +249,18 @@ class Engine:
             packet = Packet(self._upload("ids", list(tokens)), self._upload("req", [slot] * n),
                             self._upload("pos", list(range(n))), self.page_table_dev, n, n,
                             self._upload("sel", [n - 1]).long())
-            if self.on_gpu and n > 1:
+            if self.cfg.bidirectional:
+                # every row sees the whole input: keys are written first, then read with the
+                # last position as each row's horizon (row kernel; no causal tile kernel)
+                packet.attend_pos = self._upload("see", [n - 1] * n)
+            elif self.on_gpu and n > 1:
                 packet.chunks = self._upload("chunks", [0, n, 0, slot]).view(-1, 4)
                 packet.max_q_len = n
             _tok, lg = self.runner.greedy(packet, need_logits=True)
             hidden = (self.runner.final_hidden(n) if hasattr(self.runner, "final_hidden")
                       else self.runner._final[:n]).float()
-            pooled = hidden.mean(0)
+            pooled = {"mean": hidden.mean(0), "last": hidden[-1], "first": hidden[0]}[
+                self.cfg.pooling]
             pooled = pooled / pooled.norm().clamp_min(1e-12)
             return pooled.cpu(), lg[0].float().cpu()
         finally:

@@ -135,6 +135,9 @@ class Packet:
     overlay_rows: Optional[torch.Tensor] = None
     overlay: Optional[torch.Tensor] = None
     mrope: Optional[torch.Tensor] = None
+    # Encoder passes: row r may attend to keys 0..attend_pos[r] instead of 0..row_pos[r]
+    # (all rows of a bidirectional input carry the last position).  int32 [rows].
+    attend_pos: Optional[torch.Tensor] = None
 
     def ensure_segments(self) -> None:
         if self.segments is not None:
@@ -193,7 +196,7 @@ class ModelRunner:
         gated = cfg.gated_attention and lw.qkv.n == cfg.q_dim + 2 * cfg.kv_dim
         gate = ws.gate if gated else None
         row_rows = rows
-        if p.chunks is not None and cfg.head_dim in (64, 128):
+        if p.chunks is not None and p.attend_pos is None and cfg.head_dim in (64, 128):
             done = F.attention_prefill(ws.q, gate, p.chunks, p.max_q_len, p.page_table,
                                        self.kv.k[kv_slot], self.kv.v[kv_slot],
                                        self.kv.ks[kv_slot], self.kv.vs[kv_slot], out=ws.attn,
@@ -204,7 +207,8 @@ class ModelRunner:
             splits = min(F.attention_splits(p.max_kv_len, row_rows, cfg.kv_heads),
                          max(ws.SPLIT_ROWS // row_rows, 1))
             scratch = ws.attn_scratch if splits > 1 else None
-            F.attention(ws.q, gate, p.row_req, p.row_pos, p.page_table, self.kv.k[kv_slot],
+            see = p.row_pos if p.attend_pos is None else p.attend_pos
+            F.attention(ws.q, gate, p.row_req, see, p.page_table, self.kv.k[kv_slot],
                         self.kv.v[kv_slot], self.kv.ks[kv_slot], self.kv.vs[kv_slot],
                         splits=splits, scratch=scratch, out=ws.attn, rows=row_rows)
         qd = cfg.q_heads * cfg.head_dim

@@ -73,9 +73,10 @@ class TorchRunner:
         self.kv.ks[slot][page, off] = ks.to(torch.float16)
         self.kv.vs[slot][page, off] = vs.to(torch.float16)
         out = torch.empty(rows, qh * d)
+        see = pos if p.attend_pos is None else p.attend_pos[:rows].long()
         for r in torch.unique(req).tolist():
             idx = (req == r).nonzero().flatten()
-            rp = pos[idx]
+            rp = see[idx]
             kv_len = int(rp.max()) + 1
             allpos = torch.arange(kv_len)
             pg = p.page_table[r, allpos // 128].long()

@@ -50,3 +50,18 @@ def test_reference_generation_matches_batched_runs(cuda, preset):
     prompts = [torch.randint(1, 1000, (n,), generator=g).tolist() for n in (5, 150, 70)]
     ref = [_engine(w).generate_reference(p, max_new=6, chunk=64) for p in prompts]
     assert _engine(w, chunk=128, graph=GraphMode.OFF).generate(prompts, max_new=6) == ref
+
+
+def test_bidirectional_encoder_matches_the_cpu_runner(cuda):
+    """Encoder passes on the CUDA runner (row attention kernel with the last position as every
+    row's horizon) against the PyTorch runner on the same weights."""
+    cfg = PRESETS["tiny-embed"]
+    cpu_w = random_model(cfg, seed=3)
+    ids = torch.randint(1, 1000, (150,), generator=torch.Generator().manual_seed(8)).tolist()
+    want, want_logits = Engine(cpu_w, sched=SchedulerOptions(max_active=2, prefill_chunk=256),
+                               kv_pages=16, max_context=512).encode(ids)
+    got, got_logits = _engine(random_model(cfg, seed=3).to(cuda)).encode(ids)
+    assert torch.nn.functional.cosine_similarity(got, want, dim=0) > 0.999
+    assert torch.nn.functional.cosine_similarity(got_logits, want_logits, dim=0) > 0.995
+    causal = _engine(random_model(PRESETS["tiny"], seed=3).to(cuda)).encode(ids)[0]
+    assert torch.nn.functional.cosine_similarity(causal, want, dim=0) < 0.999   # it matters
