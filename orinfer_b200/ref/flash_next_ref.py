@@ -123,7 +123,8 @@ def qsa_index(qk: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor, 
     pos = torch.arange(first, first + t, device=qk.device)
     q = qsa_rope(rms(qk[:, :GROUP], q_weight), pos)
     groups = t // GROUP
-    pooled = qk[:groups * GROUP, GROUP].float().reshape(groups, GROUP, -1).mean(1).to(qk.dtype)
+    pooled = qk[:groups * GROUP, GROUP].float().reshape(groups, GROUP, qk.shape[-1]).mean(1).to(
+        qk.dtype)
     k = qsa_rope(rms(pooled[:, None], k_weight), pos[:groups * GROUP:GROUP])[:, 0]
     return q, k
 
