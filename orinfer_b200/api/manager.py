@@ -220,6 +220,17 @@ class ModelManager:
                      "idle_s": round(self.clock() - r.last_used, 3),
                      "keep_alive_s": r.keep_alive_s} for r in self.runners.values()]
 
+    def logs(self, name: str) -> List[str]:
+        """Recent stderr lines of the runner serving ``name`` (child-process runners keep a
+        tail; in-process ones have none); 409 when the model is not loaded."""
+        key = self.show(name).runner_key()
+        with self._lock:
+            r = self.runners.get(key)
+        if r is None:
+            raise ManagerError(f"model '{name}' is not running", 409)
+        child = getattr(r.service, "service", r.service)
+        return list(getattr(child, "tail", []))
+
     def shutdown(self) -> None:
         with self._transition:
             with self._lock:
@@ -260,6 +271,13 @@ def install(app, manager: ModelManager) -> None:
         except ManagerError as e:
             return fail(e)
         return JSONResponse({}, status_code=200)
+
+    @app.get("/api/logs")
+    async def logs(model: str = ""):
+        try:
+            return {"model": model, "lines": manager.logs(model)}
+        except ManagerError as e:
+            return fail(e)
 
     @app.get("/v1/models")
     async def models():

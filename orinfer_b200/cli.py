@@ -236,6 +236,13 @@ def cmd_models(a) -> int:
                 return 2
             validate_model(snap)
             print(json.dumps(m.register(a.name, str(snap)).__dict__))
+        elif a.models_cmd == "logs":
+            import requests
+            r = requests.get(a.url.rstrip("/") + "/api/logs", params={"model": a.name}, timeout=10)
+            if r.status_code != 200:
+                print(r.text, file=sys.stderr)
+                return 2
+            print("\n".join(r.json()["lines"]))
         elif a.models_cmd == "list":
             print(json.dumps([e.__dict__ for e in m.list()]))
         elif a.models_cmd == "show":
@@ -511,6 +518,9 @@ def build_parser() -> argparse.ArgumentParser:
     mp = mos.add_parser("pull")
     mp.add_argument("name")
     mp.add_argument("source", help="hf:org/repo[@revision] or modelscope:org/repo[@revision]")
+    ml = mos.add_parser("logs", help="recent stderr of a running model's process")
+    ml.add_argument("name")
+    ml.add_argument("--url", default="http://127.0.0.1:8088", help="address of the manager")
     mos.add_parser("list")
     for verb in ("show", "rm"):
         mv = mos.add_parser(verb)

@@ -50,6 +50,10 @@ def test_gateway_streams_through_a_child_process(model_dir, tmp_path):
         bad = c.post("/v1/chat/completions", json=dict(body, bogus=1))
         assert bad.status_code == 400 and bad.json()["error"]["param"] == "bogus"   # relayed as is
         assert len(started) == 1 and started[0].alive() and m.running()[0]["leases"] == 0
+        lines = c.get("/api/logs", params={"model": "tiny"}).json()["lines"]
+        assert any(l.startswith("API READY") for l in lines)
+        assert any(l.startswith("MODEL READY") for l in lines)
+        assert c.get("/api/logs", params={"model": "ghost"}).status_code == 404
         # a runner that died answers 502 in the OpenAI error shape, the gateway stays up
         started[0].stop(30)
         dead = c.post("/v1/chat/completions", json=body)
