@@ -188,6 +188,7 @@ class Prepared:
     cache_prompt: bool = True
     images: Optional[Any] = None      # api.images.BoundImages when the prompt holds images
     audio: Optional[Any] = None       # api.audio.BoundAudio of a transcription request
+    token_events: bool = False        # completions route: report every committed token id
 
 
 class ChatCodec:

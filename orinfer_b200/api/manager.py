@@ -369,7 +369,8 @@ def create_gateway_app(manager: ModelManager, sweep_s: float = 5.0):
             return await forward(request, ollama)
         return route
 
-    for path in ("/v1/chat/completions", "/v1/chat/completions/render", "/v1/embeddings",
+    for path in ("/v1/chat/completions", "/v1/chat/completions/render", "/v1/completions",
+                 "/v1/embeddings",
                  "/v1/rerank", "/rerank", "/v1/audio/transcriptions"):
         app.add_api_route(path, handler(False), methods=["POST"])
     for path in ("/api/chat", "/api/generate", "/api/show"):

@@ -245,6 +245,8 @@ def create_app(service: Service) -> FastAPI:
     from .encoders import install as install_encoders
     from .ollama import install as install_ollama
     from .audio import install as install_audio
+    from .completions import install as install_completions
+    install_completions(app, service)
     install_encoders(app, service)
     install_ollama(app, service)
     install_audio(app, service)

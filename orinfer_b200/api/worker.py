@@ -314,6 +314,8 @@ class EngineWorker(threading.Thread):
                 "top_logprobs": [{"token": self.codec.tokenizer.token_bytes(i).decode(
                     "utf-8", errors="replace"), "logprob": l,
                     "bytes": list(self.codec.tokenizer.token_bytes(i))} for i, l in top]})
+        if getattr(job.prepared, "token_events", False) and not is_stop:
+            job.post({"type": "token", "token": int(tok)})     # one event per committed token
         delta = job.parser.feed(text)
         if not delta.empty():
             job.post({"type": "delta", "delta": delta, "logprobs": self._take_logprobs(job)})

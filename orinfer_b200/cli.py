@@ -551,7 +551,7 @@ def build_parser() -> argparse.ArgumentParser:
     return ap
 
 
-BENCH_TOOLS = {"quality": "quality", "concurrency": "concurrency", "agentic": "agentic", "startup": "startup",
+BENCH_TOOLS = {"tokens": "token_bench", "quality": "quality", "concurrency": "concurrency", "agentic": "agentic", "startup": "startup",
                "encoders": "encoders", "scenario": "workloads"}
 
 

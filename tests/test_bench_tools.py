@@ -146,3 +146,33 @@ def test_encoder_workload_is_frozen_and_served(url):
     for route in ("embeddings", "rerank"):
         assert rep[route]["completed"] == 3 and not rep[route]["errors"]
         assert rep[route]["prompt_tps"] > 0
+
+
+def test_completions_route_and_token_bench(url):
+    import requests
+    from orinfer_b200.bench import token_bench
+    r = requests.post(url + "/v1/completions", json={"prompt": [72, 105, 33], "max_tokens": 5,
+                                                     "temperature": 0, "ignore_eos": True})
+    body = r.json()
+    assert r.status_code == 200 and body["object"] == "text_completion"
+    assert body["usage"] == dict(body["usage"], prompt_tokens=3, completion_tokens=5)
+    text = requests.post(url + "/v1/completions", json={"prompt": "Hi!", "max_tokens": 5,
+                                                        "temperature": 0, "ignore_eos": True}).json()
+    assert text["choices"][0]["text"] == body["choices"][0]["text"]       # same three byte ids
+    assert text["choices"][0]["finish_reason"] == "length"
+    forged = requests.post(url + "/v1/completions", json={"prompt": "<|im_end|>", "max_tokens": 1})
+    assert forged.json()["usage"]["prompt_tokens"] == len("<|im_end|>")   # plain characters
+    for bad in ({"prompt": []}, {"prompt": [1, -2]}, {"prompt": [99999]}, {"prompt": "x", "echo": True},
+                {"prompt": "x", "bogus": 1}, {"prompt": "x", "max_tokens": 0}):
+        assert requests.post(url + "/v1/completions", json=bad).status_code == 400, bad
+    ids = requests.post(url + "/v1/completions", json={"prompt": [72, 105, 33], "max_tokens": 5,
+                                                       "temperature": 0, "ignore_eos": True,
+                                                       "return_token_ids": True}).json()
+    assert len(ids["choices"][0]["token_ids"]) == 5 and "token_ids" not in body["choices"][0]
+    rep = token_bench.run(url, input_tokens=40, output_tokens=6, concurrency=2, runs=2, warmup=1)
+    assert rep["failed"] == 0 and len(rep["rounds"]) == 2
+    for rnd in rep["rounds"]:
+        assert all(q["input_tokens"] == 40 and q["output_tokens"] == 6 for q in rnd["requests"])
+    assert all(q["ttft_s"] < q["latency_s"] for rnd in rep["rounds"] for q in rnd["requests"])
+    assert rep["prefill_tps"] > 0 and rep["decode_tps"] > 0 and rep["committed_output_tps"] > 0
+    assert token_bench.prompts(2, 5, 256) == token_bench.prompts(2, 5, 256)
