@@ -504,6 +504,15 @@ def build_parser() -> argparse.ArgumentParser:
     ge.add_argument("--tokens", default=None, help="comma-separated prompt token ids")
     ge.add_argument("--max-tokens", type=int, default=32)
     ge.set_defaults(fn=cmd_generate)
+    cv = sub.add_parser("convert-model", help="Hugging Face Qwen3 checkpoint -> quantised model")
+    cv.add_argument("source")
+    cv.add_argument("output")
+    cv.add_argument("--device", default="cuda")
+    cv.add_argument("--exhaustive", action="store_true")
+    cv.add_argument("--name", default=None)
+    cv.set_defaults(fn=lambda a: __import__("orinfer_b200.quant.convert", fromlist=["main"]).main(
+        [a.source, a.output, "--device", a.device] + (["--exhaustive"] if a.exhaustive else [])
+        + (["--name", a.name] if a.name else [])))
     mk = sub.add_parser("make-model")
     mk.add_argument("--preset", required=True, choices=sorted(PRESETS))
     mk.add_argument("--output", required=True)

@@ -1,0 +1,132 @@
+"""Hugging Face Qwen3-style checkpoint -> quantised model directory (resumable)."""
+import json
+
+import pytest
+import torch
+from safetensors.torch import save_file
+
+from orinfer_b200.quant import convert as C
+from orinfer_b200.ref.ops_ref import hadamard_rotate
+
+H, HEADS, KV, D, FFN, V, LAYERS = 128, 2, 1, 64, 256, 300, 2
+
+
+def hf_checkpoint(path, moe=False, tied=True):
+    g = torch.Generator().manual_seed(0)
+    rnd = lambda *s: (torch.randn(*s, generator=g) * 0.05).to(torch.bfloat16)
+    cfg = {"architectures": ["Qwen3MoeForCausalLM" if moe else "Qwen3ForCausalLM"],
+           "hidden_size": H, "num_hidden_layers": LAYERS, "num_attention_heads": HEADS,
+           "num_key_value_heads": KV, "head_dim": D, "intermediate_size": FFN, "vocab_size": V,
+           "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "tie_word_embeddings": tied,
+           "max_position_embeddings": 4096}
+    if moe:
+        cfg.update(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=128,
+                   norm_topk_prob=True)
+    t = {"model.embed_tokens.weight": rnd(V, H), "model.norm.weight": torch.ones(H) * 1.5}
+    if not tied:
+        t["lm_head.weight"] = rnd(V, H)
+    for i in range(LAYERS):
+        p = f"model.layers.{i}."
+        t[p + "input_layernorm.weight"] = torch.ones(H) + 0.1 * i
+        t[p + "post_attention_layernorm.weight"] = torch.ones(H)
+        t[p + "self_attn.q_proj.weight"] = rnd(HEADS * D, H)
+        t[p + "self_attn.k_proj.weight"] = rnd(KV * D, H)
+        t[p + "self_attn.v_proj.weight"] = rnd(KV * D, H)
+        t[p + "self_attn.o_proj.weight"] = rnd(H, HEADS * D)
+        t[p + "self_attn.q_norm.weight"] = torch.ones(D)
+        t[p + "self_attn.k_norm.weight"] = torch.ones(D) * 0.5
+        if moe:
+            t[p + "mlp.gate.weight"] = rnd(4, H)
+            for e in range(4):
+                t[p + f"mlp.experts.{e}.gate_proj.weight"] = rnd(128, H)
+                t[p + f"mlp.experts.{e}.up_proj.weight"] = rnd(128, H)
+                t[p + f"mlp.experts.{e}.down_proj.weight"] = rnd(H, 128)
+        else:
+            t[p + "mlp.gate_proj.weight"] = rnd(FFN, H)
+            t[p + "mlp.up_proj.weight"] = rnd(FFN, H)
+            t[p + "mlp.down_proj.weight"] = rnd(H, FFN)
+    path.mkdir(parents=True, exist_ok=True)
+    names = sorted(t)
+    save_file({k: t[k].contiguous() for k in names[::2]}, str(path / "model-00001-of-00002.safetensors"))
+    save_file({k: t[k].contiguous() for k in names[1::2]}, str(path / "model-00002-of-00002.safetensors"))
+    (path / "config.json").write_text(json.dumps(cfg))
+    (path / "generation_config.json").write_text(json.dumps({"eos_token_id": [7]}))
+    return {k: v.float() for k, v in t.items()}
+
+
+def rel_error(lin, weight):
+    want = hadamard_rotate(weight, lin.signs)
+    got = lin.integers().float() * lin.scale.float()[:, None]
+    return float((got - want).norm() / want.norm())
+
+
+def test_dense_conversion_is_faithful_and_resumable(tmp_path):
+    from orinfer_b200.config import SchedulerOptions
+    from orinfer_b200.engine.checkpoint import load_model, validate_model
+    from orinfer_b200.engine.engine import Engine
+    src = hf_checkpoint(tmp_path / "hf", tied=False)
+    seen = []
+
+    class Stop(Exception):
+        pass
+
+    def crash_after_first(i, resumed):
+        seen.append((i, resumed))
+        if i == 0:
+            raise Stop                                    # the job dies after layer 0 is on disk
+
+    with pytest.raises(Stop):
+        C.convert(tmp_path / "hf", tmp_path / "out", on_layer=crash_after_first)
+    progress = json.loads((tmp_path / "out/.convert/progress.json").read_text())
+    assert list(progress["done"]) == ["layer.0"]
+    seen.clear()
+    out = C.convert(tmp_path / "hf", tmp_path / "out", on_layer=lambda i, r: seen.append((i, r)))
+    assert seen == [(0, True), (1, False)]                # layer 0 was kept, not recomputed
+    assert not (out / ".convert").exists() and validate_model(out)["ok"]
+    assert json.loads((out / "generation_config.json").read_text())["eos_token_id"] == [7]
+    w = load_model(out, verify=True)
+    cfg = w.config
+    assert (cfg.arch, cfg.layers, cfg.hidden, cfg.q_heads, cfg.kv_heads, cfg.head_dim, cfg.ffn,
+            cfg.vocab, cfg.tied_embeddings) == ("dense", LAYERS, H, HEADS, KV, D, FFN, V, False)
+    l1 = w.layers[1]
+    qkv = torch.cat([src[f"model.layers.1.self_attn.{x}_proj.weight"] for x in "qkv"])
+    assert l1.qkv.n == (HEADS + 2 * KV) * D and rel_error(l1.qkv, qkv) < 0.12
+    gu = torch.cat([src["model.layers.1.mlp.gate_proj.weight"],
+                    src["model.layers.1.mlp.up_proj.weight"]])
+    assert rel_error(l1.gate_up, gu) < 0.12
+    assert rel_error(l1.down, src["model.layers.1.mlp.down_proj.weight"]) < 0.12
+    assert torch.allclose(l1.in_norm.float(), torch.full((H,), 1.1), atol=1e-3)
+    assert torch.allclose(l1.k_norm.float(), torch.full((D,), 0.5))
+    assert torch.allclose(w.final_norm.float(), torch.full((H,), 1.5))
+    emb = w.embed_q.float() * w.embed_s.float()[:, None]
+    assert float((emb - src["model.embed_tokens.weight"]).norm()
+                 / src["model.embed_tokens.weight"].norm()) < 0.02
+    assert w.head.n == V and w.head.codes.data_ptr() != w.embed_q.data_ptr()
+    eng = Engine(w, sched=SchedulerOptions(max_active=2, prefill_chunk=64), kv_pages=8,
+                 max_context=256)
+    assert len(eng.generate([[1, 2, 3, 4]], max_new=4)[0]) == 4
+
+
+def test_moe_conversion_and_refusals(tmp_path):
+    from orinfer_b200.engine.checkpoint import load_model
+    src = hf_checkpoint(tmp_path / "hf", moe=True)
+    w = load_model(C.convert(tmp_path / "hf", tmp_path / "out"))
+    cfg = w.config
+    assert (cfg.arch, cfg.experts, cfg.top_k, cfg.expert_ffn, cfg.tied_embeddings) == \
+        ("moe", 4, 2, 128, True)
+    bank = w.layers[0].expert_gate_up
+    assert bank.experts == 4 and bank.n == 256 and bank.k == H
+    gu2 = torch.cat([src["model.layers.0.mlp.experts.2.gate_proj.weight"],
+                     src["model.layers.0.mlp.experts.2.up_proj.weight"]])
+    assert rel_error(bank.expert(2), gu2) < 0.12
+    assert torch.allclose(w.layers[0].router.float(), src["model.layers.0.mlp.gate.weight"],
+                          atol=1e-3)
+    bad = json.loads((tmp_path / "hf/config.json").read_text())
+    for patch, why in (({"architectures": ["LlamaForCausalLM"]}, "unsupported architecture"),
+                       ({"attention_bias": True}, "bias"),
+                       ({"mlp_only_layers": [0]}, "mixed")):
+        with pytest.raises(C.ConvertError, match=why):
+            C.config_from_hf(dict(bad, **patch))
+    (tmp_path / "hf/model-00002-of-00002.safetensors").unlink()
+    with pytest.raises(C.ConvertError, match="missing"):
+        C.convert(tmp_path / "hf", tmp_path / "out2")
