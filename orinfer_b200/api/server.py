@@ -112,6 +112,14 @@ class Service:
             if pager is not None:
                 out["expert_pager"] = pager.stats.as_dict()
         out["preparation"] = self.preparation.snapshot()
+        if getattr(self.codec, "boundary", None) is not None:
+            out["tokenization_cache"] = self.codec.boundary.cache_statistics()
+        images = getattr(self.codec, "images", None)
+        if images is not None:
+            out["image_cache"] = {"entries": len(images.cache._items), "bytes": images.cache.bytes,
+                                  "budget_bytes": images.cache.budget}
+            out["chat_capabilities"]["images"] = True
+        out["output_pipeline"] = "thread" if self.worker.pipeline is not None else "inline"
         return out
 
 

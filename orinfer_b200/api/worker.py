@@ -51,6 +51,7 @@ class Job:
     events: Any = None                           # asyncio.Queue or queue.Queue
     created: float = field(default_factory=time.monotonic)
     cancelled: bool = False
+    stop_requested: bool = False                 # the output side saw a stop string
     request: Optional[Request] = None
     parser: Optional[OutputParser] = None
     pending_bytes: bytes = b""
@@ -79,6 +80,69 @@ class CallJob:
         self.cancelled = False
 
 
+class OutputPipeline(threading.Thread):
+    """Detokenisation, parsing and event delivery on their own thread, so the engine thread goes
+    straight back to the next forward pass (the reference overlaps its output pipeline with the
+    next iteration the same way, crates/orinfer-api/src/server/continuous.rs:31-48,103-200).
+    Items arrive in commit order and are handled in that order; everything produced by one
+    drain of the queue reaches an event loop in a single ``call_soon_threadsafe``."""
+
+    def __init__(self, worker: "EngineWorker"):
+        super().__init__(name="orinfer-output", daemon=True)
+        self.worker = worker
+        self.items: "queue.SimpleQueue" = queue.SimpleQueue()
+        self.start()
+
+    def push(self, item) -> None:
+        self.items.put(item)
+
+    def close(self) -> None:
+        self.items.put(None)
+        self.join(timeout=10)
+
+    @staticmethod
+    def _deliver(pairs) -> None:                 # runs on the event loop
+        for job, event in pairs:
+            job.events.put_nowait(event)
+
+    def run(self) -> None:
+        closing = False
+        while not closing:
+            batch = [self.items.get()]
+            while True:
+                try:
+                    batch.append(self.items.get_nowait())
+                except queue.Empty:
+                    break
+            by_loop: Dict[int, list] = {}
+
+            def sink(job: Job, event: dict) -> None:
+                if job.loop is None:
+                    job.events.put_nowait(event)
+                else:
+                    by_loop.setdefault(id(job.loop), [job.loop, []])[1].append((job, event))
+
+            for item in batch:
+                if item is None:
+                    closing = True
+                    continue
+                try:
+                    if item[0] == "token":
+                        self.worker._emit_token(*item[1:], sink)
+                    else:
+                        self.worker._emit_finish(*item[1:], sink)
+                except Exception:                # noqa: BLE001 - one request, not the server
+                    traceback.print_exc()
+                    sink(item[1], {"type": "error", "status": 500,
+                                   "message": "output pipeline failure", "code": "output_failure"})
+            for loop, pairs in by_loop.values():
+                try:
+                    loop.call_soon_threadsafe(self._deliver, pairs)
+                except RuntimeError:             # the server's loop is gone
+                    for job, _ in pairs:
+                        job.cancelled = True
+
+
 class EngineWorker(threading.Thread):
     def __init__(self, engine_factory: Callable[[], Engine], codec: ChatCodec, metrics: Metrics,
                  lifecycle: Lifecycle, queue_timeout_ms: int = 0, step_timeout_ms: int = 0,
@@ -88,6 +152,10 @@ class EngineWorker(threading.Thread):
         self.step_timeout_s = step_timeout_ms / 1e3
         self.exit_on_stall = exit_on_stall
         self.watchdog = None
+        import os
+        # ORINFER_ASYNC_OUTPUT=0 keeps detokenisation and parsing on the engine thread
+        self.async_output = os.environ.get("ORINFER_ASYNC_OUTPUT", "1") != "0"
+        self.pipeline: Optional[OutputPipeline] = None
         self.engine_factory = engine_factory
         self.engine: Optional[Engine] = None
         self.codec = codec
@@ -125,6 +193,8 @@ class EngineWorker(threading.Thread):
                 self.watchdog = StepWatchdog(self._stalled)
             self.engine = self.engine_factory()
             self._warmup()
+            if self.async_output:
+                self.pipeline = OutputPipeline(self)
             self.lifecycle.set(Lifecycle.READY)
             self.ready.set()
             while not self._stop.is_set():
@@ -148,6 +218,8 @@ class EngineWorker(threading.Thread):
                 self._reap()
                 self.metrics.set("requests_running", len(self.active))
                 self.metrics.set("requests_waiting", self.jobs.qsize())
+            if self.pipeline is not None:
+                self.pipeline.close()
             self._exit_report()
         except Exception as exc:                     # fatal: fail closed
             self.lifecycle.set(Lifecycle.FAILED, f"{type(exc).__name__}: {exc}")
@@ -296,32 +368,47 @@ class EngineWorker(threading.Thread):
 
     # ------------------------------------------------------------------ token delivery
     def _on_token(self, job: Job, req: Request, tok: int) -> None:
-        if job.cancelled:
+        """Engine thread, once per committed token: the cheap part (cancellation, first-token
+        mark, stop-token test); text work goes to the output pipeline."""
+        if job.cancelled or job.stop_requested:
             self.engine.cancel(req)
+            if job.stop_requested:
+                req.finish_reason = "stop"
             return
         if job.first_token_at is None:
             job.first_token_at = time.monotonic()
             self.metrics.observe("time_to_first_token", job.first_token_at - job.created)
         is_stop = tok in req.stop_ids and not req.ignore_eos
+        lp = req.logprobs[-1] if (req.logprobs and job.prepared.want_logprobs
+                                  and not is_stop) else None
+        if self.pipeline is not None:
+            self.pipeline.push(("token", job, tok, is_stop, lp))
+            return
+        self._emit_token(job, tok, is_stop, lp, Job.post)
+        if job.stop_requested:
+            self.engine.cancel(req)
+            req.finish_reason = "stop"
+
+    def _emit_token(self, job: Job, tok: int, is_stop: bool, lp, sink) -> None:
+        """Bytes -> complete UTF-8 -> parser -> deltas.  ``sink(job, event)`` delivers."""
         piece = b"" if is_stop else self.codec.tokenizer.token_bytes(tok)
         job.pending_bytes += piece
         text, job.pending_bytes = _utf8_prefix(job.pending_bytes)
-        if req.logprobs and job.prepared.want_logprobs and not is_stop:
-            _t, lp, top = req.logprobs[-1]
+        if lp is not None:
+            _t, logprob, top = lp
             job.logprob_entries.append({
-                "token": piece.decode("utf-8", errors="replace"), "logprob": lp,
+                "token": piece.decode("utf-8", errors="replace"), "logprob": logprob,
                 "bytes": list(piece),
                 "top_logprobs": [{"token": self.codec.tokenizer.token_bytes(i).decode(
                     "utf-8", errors="replace"), "logprob": l,
                     "bytes": list(self.codec.tokenizer.token_bytes(i))} for i, l in top]})
         if getattr(job.prepared, "token_events", False) and not is_stop:
-            job.post({"type": "token", "token": int(tok)})     # one event per committed token
+            sink(job, {"type": "token", "token": int(tok)})    # one event per committed token
         delta = job.parser.feed(text)
         if not delta.empty():
-            job.post({"type": "delta", "delta": delta, "logprobs": self._take_logprobs(job)})
+            sink(job, {"type": "delta", "delta": delta, "logprobs": self._take_logprobs(job)})
         if job.parser.stopped:
-            self.engine.cancel(req)
-            req.finish_reason = "stop"
+            job.stop_requested = True                          # the engine thread cancels it
 
     @staticmethod
     def _take_logprobs(job: Job):
@@ -336,33 +423,38 @@ class EngineWorker(threading.Thread):
             if not req.finished:
                 continue
             del self.active[rid]
-            tail = job.parser.feed(job.pending_bytes.decode("utf-8", errors="replace"),
-                                   final=True)
-            if not tail.empty() or job.logprob_entries:
-                job.post({"type": "delta", "delta": tail, "logprobs": self._take_logprobs(job)})
-            reason = req.finish_reason or "stop"
-            if reason == "cancelled":
-                reason = "stop"
-            now = time.monotonic()
-            self.metrics.observe("latency", now - job.created)
-            if job.first_token_at:
-                self.metrics.observe("decode", now - job.first_token_at)
-            self.metrics.add("requests_total")
-            self.metrics.add("prompt_tokens_total", len(req.prompt))
-            self.metrics.add("completion_tokens_total", len(req.generated))
-            self.metrics.add("cached_tokens_total", req.cached_tokens)
-            reasoning = 0
-            if job.prepared.thinking:
-                close = self.codec.tokenizer.encode("</think>")
-                gen = req.generated
-                reasoning = next((i for i in range(len(gen)) if gen[i:i + len(close)] == close),
-                                 len(gen))
-            job.post({"type": "done", "finish_reason": job.parser.finish_reason(reason),
-                      "usage": {"prompt_tokens": len(req.prompt),
-                                "completion_tokens": len(req.generated),
-                                "total_tokens": len(req.prompt) + len(req.generated),
-                                "completion_tokens_details": {"reasoning_tokens": reasoning},
-                                "prompt_tokens_details": {"cached_tokens": req.cached_tokens}}})
+            if self.pipeline is not None:
+                self.pipeline.push(("finish", job, req))
+            else:
+                self._emit_finish(job, req, Job.post)
+
+    def _emit_finish(self, job: Job, req: Request, sink) -> None:
+        tail = job.parser.feed(job.pending_bytes.decode("utf-8", errors="replace"), final=True)
+        if not tail.empty() or job.logprob_entries:
+            sink(job, {"type": "delta", "delta": tail, "logprobs": self._take_logprobs(job)})
+        reason = req.finish_reason or "stop"
+        if reason == "cancelled" or job.parser.stopped:
+            reason = "stop"
+        now = time.monotonic()
+        self.metrics.observe("latency", now - job.created)
+        if job.first_token_at:
+            self.metrics.observe("decode", now - job.first_token_at)
+        self.metrics.add("requests_total")
+        self.metrics.add("prompt_tokens_total", len(req.prompt))
+        self.metrics.add("completion_tokens_total", len(req.generated))
+        self.metrics.add("cached_tokens_total", req.cached_tokens)
+        reasoning = 0
+        if job.prepared.thinking:
+            close = self.codec.tokenizer.encode("</think>")
+            gen = req.generated
+            reasoning = next((i for i in range(len(gen)) if gen[i:i + len(close)] == close),
+                             len(gen))
+        sink(job, {"type": "done", "finish_reason": job.parser.finish_reason(reason),
+                   "usage": {"prompt_tokens": len(req.prompt),
+                             "completion_tokens": len(req.generated),
+                             "total_tokens": len(req.prompt) + len(req.generated),
+                             "completion_tokens_details": {"reasoning_tokens": reasoning},
+                             "prompt_tokens_details": {"cached_tokens": req.cached_tokens}}})
 
 
 def _utf8_prefix(data: bytes):
