@@ -130,23 +130,40 @@ def cmd_serve(a) -> int:
     probe.close()
     if not a.model_dir and not a.preset:
         return _serve_manager(a, host, int(port), load, sched)
-    weights, name = _weights(a)
+    # Listen first, load behind: /health answers `starting` (503) while the weights load, a
+    # port conflict shows at once, and clients that retry on 503 need no separate readiness poll
+    # (the reference binds before loading too, crates/orinfer-api/src/server/startup.rs:44-160).
+    import threading
+    from types import SimpleNamespace
+    cfg, name = _model_identity(a)
     name = a.model if a.model != "qwen3.8-27b" or not a.preset else name
-    print(f"MODEL READY {name}; {weights.nbytes() / 2 ** 20:.0f} MiB of weights", file=sys.stderr)
-    service = Service(_engine_factory(a, weights, load, sched), _codec(a, weights, name), name,
+
+    def factory():
+        weights, _ = _weights(a)
+        if a.preset:
+            print(f"MODEL READY {name}; {weights.nbytes() / 2 ** 20:.0f} MiB of weights",
+                  file=sys.stderr, flush=True)
+        return _engine_factory(a, weights, load, sched)()
+
+    service = Service(factory, _codec(a, SimpleNamespace(config=cfg), name), name,
                       json.loads(a.default_request_params), a.queue_timeout_ms,
                       a.output_timeout_ms, a.preparation_workers, a.preparation_memory_mib,
                       a.step_timeout_ms, exit_on_stall=True)
-    service.start()
-    if service.lifecycle.state != "ready":
-        print(f"worker failed: {service.lifecycle.reason}", file=sys.stderr)
-        return 1
-    print("WORKER READY", file=sys.stderr)
-    print("WARMUP READY", file=sys.stderr)
-    print(f"API READY http://{a.listen}/v1; context {service.worker.engine.max_context}; "
-          f"continuous_batching=true", file=sys.stderr)
     server = uvicorn.Server(uvicorn.Config(create_app(service), host=host, port=int(port),
                                            log_level="warning"))
+    service.start(wait=False)
+
+    def announce():
+        service.worker.ready.wait()
+        if service.lifecycle.state != "ready":
+            print(f"worker failed: {service.lifecycle.reason}", file=sys.stderr, flush=True)
+            server.should_exit = True
+            return
+        print("WORKER READY", file=sys.stderr)
+        print("WARMUP READY", file=sys.stderr)
+        print(f"API READY http://{a.listen}/v1; context {service.worker.engine.max_context}; "
+              f"continuous_batching=true", file=sys.stderr, flush=True)
+    threading.Thread(target=announce, daemon=True).start()
 
     def drain(*_):
         service.lifecycle.set("draining")
@@ -154,9 +171,23 @@ def cmd_serve(a) -> int:
     signal.signal(signal.SIGINT, drain)
     signal.signal(signal.SIGTERM, drain)
     server.run()
+    if service.worker.engine is None:                 # never became ready
+        return 1
     service.stop(a.drain_timeout_ms)
     print("SCHEDULER " + json.dumps(service.worker.engine.stats.as_dict()), file=sys.stderr)
     return 1 if service.lifecycle.state == "failed" else 0
+
+
+def _model_identity(a):
+    """(geometry, name) of the model to serve without reading any weights."""
+    from .config import ModelConfig
+    if a.preset:
+        return PRESETS[a.preset], a.preset
+    if not a.model_dir:
+        raise SystemExit("a model directory or --preset is required")
+    from .engine.checkpoint import read_descriptor
+    cfg = ModelConfig.from_json((Path(a.model_dir) / "config.json").read_text())
+    return cfg, read_descriptor(a.model_dir)["name"]
 
 
 def _state_dir(a) -> Path:

@@ -66,3 +66,44 @@ def test_child_that_cannot_start_reports_its_stderr(tmp_path):
     with pytest.raises(RunnerStartError, match="exited with code"):
         ChildRunner(str(tmp_path / "missing"), "ghost", ["--device", "cpu"],
                     start_timeout_s=120).start()
+
+
+def test_serve_listens_while_the_model_loads():
+    """`serve` accepts connections before the weights are ready: /health says `starting`
+    (503), requests are refused with 503, then the same listener turns ready."""
+    import signal
+    import socket
+    import subprocess
+    import sys
+    import time
+
+    import requests
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    proc = subprocess.Popen([sys.executable, "-m", "orinfer_b200", "serve", "--preset", "tiny",
+                             "--device", "cpu", "--listen", f"127.0.0.1:{port}"],
+                            stderr=subprocess.DEVNULL, start_new_session=True)
+    url = f"http://127.0.0.1:{port}"
+    seen, refused = [], None
+    try:
+        deadline = time.time() + 240
+        while time.time() < deadline:
+            try:
+                r = requests.get(url + "/health", timeout=2)
+            except requests.RequestException:
+                time.sleep(0.05)
+                continue
+            seen.append((r.status_code, r.json()["status"]))
+            if r.status_code == 200:
+                break
+            if refused is None:
+                refused = requests.post(url + "/v1/chat/completions", timeout=5, json={
+                    "messages": [{"role": "user", "content": "x"}]})
+            time.sleep(0.1)
+        assert seen[0] == (503, "starting") and seen[-1] == (200, "ready")
+        assert refused is not None and refused.status_code == 503
+        assert refused.json()["error"]["code"] == "not_ready"
+    finally:
+        proc.send_signal(signal.SIGTERM)
+        assert proc.wait(timeout=60) == 0
