@@ -963,6 +963,8 @@ class Engine:
         now = time.monotonic()
         drawn = self._sharded_samples(order)
         drawn.update(self._device_samples(order, logits))
+        if isinstance(tokens, torch.Tensor):      # one conversion, not one tensor index per row
+            tokens = tokens.tolist()
         for r, n, has_logits in order:
             was_decode = r.phase is Phase.DECODE
             r.offset += n
