@@ -52,6 +52,7 @@ class Job:
     created: float = field(default_factory=time.monotonic)
     cancelled: bool = False
     stop_requested: bool = False                 # the output side saw a stop string
+    started_at: Optional[float] = None           # handed to the engine (end of queueing)
     request: Optional[Request] = None
     parser: Optional[OutputParser] = None
     pending_bytes: bytes = b""
@@ -193,6 +194,7 @@ class EngineWorker(threading.Thread):
                 self.watchdog = StepWatchdog(self._stalled)
             self.engine = self.engine_factory()
             self._warmup()
+            self._instrument()
             if self.async_output:
                 self.pipeline = OutputPipeline(self)
             self.lifecycle.set(Lifecycle.READY)
@@ -229,6 +231,29 @@ class EngineWorker(threading.Thread):
                 job.post({"type": "error", "status": 500, "message": "engine failure",
                           "code": "engine_failure"})
             self.ready.set()
+
+    def _instrument(self) -> None:
+        """Time the engine's admission pass and its prefix-cache store / host restore calls for
+        the ``admission_seconds_total`` counter and the ``prefix_store`` / ``prefix_restore``
+        histograms (wrappers on the host side; the engine itself is unchanged)."""
+        eng, metrics = self.engine, self.metrics
+
+        def timed(fn, record):
+            def call(*a, **k):
+                t0 = time.monotonic()
+                out = fn(*a, **k)
+                record(time.monotonic() - t0, a, out)
+                return out
+            return call
+
+        eng._admit = timed(eng._admit, lambda dt, a, out: metrics.add(
+            "admission_seconds_total", dt) if dt > 1e-5 else None)
+        eng._restore_host_pages = timed(
+            eng._restore_host_pages,
+            lambda dt, a, out: metrics.observe("prefix_restore", dt) if dt > 1e-5 else None)
+        if eng.prefix is not None:
+            eng.prefix.insert = timed(eng.prefix.insert,
+                                      lambda dt, a, out: metrics.observe("prefix_store", dt))
 
     def _stalled(self, what: str, waited_s: float) -> None:
         """Watchdog thread: the engine thread is stuck inside a step.  Fail closed, answer the
@@ -315,6 +340,7 @@ class EngineWorker(threading.Thread):
         job.request = req
         self.active[req.rid] = job
         self.metrics.observe("queue", now - job.created)
+        job.started_at = now
         job.post({"type": "start"})
 
     def _media(self, p: Prepared) -> dict:
@@ -378,6 +404,7 @@ class EngineWorker(threading.Thread):
         if job.first_token_at is None:
             job.first_token_at = time.monotonic()
             self.metrics.observe("time_to_first_token", job.first_token_at - job.created)
+            self.metrics.observe("prefill", job.first_token_at - (job.started_at or job.created))
         is_stop = tok in req.stop_ids and not req.ignore_eos
         lp = req.logprobs[-1] if (req.logprobs and job.prepared.want_logprobs
                                   and not is_stop) else None
@@ -437,6 +464,8 @@ class EngineWorker(threading.Thread):
             reason = "stop"
         now = time.monotonic()
         self.metrics.observe("latency", now - job.created)
+        if req.finished_at is not None:
+            self.metrics.observe("finalize", max(now - req.finished_at, 0.0))
         if job.first_token_at:
             self.metrics.observe("decode", now - job.first_token_at)
         self.metrics.add("requests_total")

@@ -80,3 +80,14 @@ def test_health_reports_the_pipeline_and_caches(client):
     assert h["output_pipeline"] in ("thread", "inline")
     assert set(h["tokenization_cache"]) == {"entries", "bytes", "hits", "misses"}
     assert h["tokenization_cache"]["misses"] >= 1
+
+
+def test_every_request_histogram_is_fed(client):
+    import re
+    client.post("/v1/chat/completions", json=forced("m", max_tokens=3))
+    text = client.get("/metrics").text
+    for name in ("queue", "prefill", "decode", "finalize", "time_to_first_token", "latency"):
+        m = re.search(rf"orinfer_request_{name}_seconds_count (\d+)", text)
+        assert m and int(m.group(1)) >= 1, name
+    assert "orinfer_request_prefix_store_seconds_count" in text
+    assert "orinfer_admission_seconds_total" in text
