@@ -380,6 +380,14 @@ class EngineWorker(threading.Thread):
         inner = None
         if p.json_schema is not None or p.json_object:
             inner = GrammarConstraint(tok, self.engine.cfg.vocab, p.json_schema, p.stop_ids)
+        elif getattr(self.codec, "tool_format", "xml") == "xml" and p.tools:
+            from . import tool_grammar
+            if tool_grammar.applies(p.tools, p.tool_choice, p.parallel_tool_calls):
+                try:
+                    text = tool_grammar.recipe(tok, p.tools, p.tool_choice, p.parallel_tool_calls)
+                except ValueError as e:
+                    raise RequestError(str(e), param="tool_choice")
+                inner = GrammarConstraint.from_lark(tok, self.engine.cfg.vocab, text, p.stop_ids)
         elif (getattr(self.codec, "tool_format", "xml") == "dsml" and p.tools
               and p.tool_choice == "required"):
             from .dsml import grammar as dsml_grammar
