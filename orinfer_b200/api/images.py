@@ -180,13 +180,17 @@ class ImageFrontend:
         if options.max_tokens_per_image:
             per = options.max_tokens_per_image * (self.spec.patch_size * self.spec.merge_size) ** 2
             limit = min(limit or per, per)
+        data = _fetch(url)
         try:
-            image = V.load_image(_fetch(url), self.spec, limit)
+            if options.max_pixels and not options.auto_resize and detail != "low":
+                # without auto_resize an oversized upload is the client's mistake, not ours to fix
+                h, w = V.image_size(data)
+                if h * w > options.max_pixels:
+                    raise RequestError(f"image of {w}x{h} pixels exceeds `max_pixels` and "
+                                       "`auto_resize` is off", param=where)
+            image = V.load_image(data, self.spec, limit)
         except V.VisionError as e:
             raise RequestError(str(e), param=where)
-        if limit and not options.auto_resize and detail != "low" and options.max_pixels and \
-                image.rgb.shape[0] * image.rgb.shape[1] > options.max_pixels:
-            raise RequestError("image exceeds `max_pixels` and `auto_resize` is off", param=where)
         if uuid:
             self.cache.put(str(uuid), image)
         return image

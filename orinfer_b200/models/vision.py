@@ -124,6 +124,16 @@ def smart_resize(height: int, width: int, factor: int, min_pixels: int, max_pixe
     return h, w
 
 
+def image_size(data: bytes) -> Tuple[int, int]:
+    """(height, width) from the file header, without decoding the pixels."""
+    from PIL import Image
+    try:
+        with Image.open(io.BytesIO(data)) as img:
+            return img.height, img.width
+    except Exception as e:                                     # PIL raises many types
+        raise VisionError(f"cannot decode image: {e}") from None
+
+
 def load_image(data: bytes, spec: VisionSpec, max_pixels: Optional[int] = None) -> ImageInput:
     """Decode PNG / JPEG / WebP bytes, convert to RGB (transparent pixels over white) and
     resize to the grid geometry."""

@@ -273,3 +273,16 @@ def test_ollama_images_become_image_parts(client):
                                        "messages": [{"role": "user", "content": "what?",
                                                      "images": [b64]}]})
     assert r.status_code == 200 and r.json()["prompt_eval_count"] > 6
+
+
+def test_max_pixels_refuses_or_resizes(client):
+    big = {"type": "image_url", "image_url": {"url": _png((9, 9, 9), (256, 128))}}
+    refused = _ask(client, [big], image_processing={"max_pixels": 64 * 64})
+    assert refused.status_code == 400 and "auto_resize" in refused.json()["error"]["message"]
+    resized = _ask(client, [big], image_processing={"max_pixels": 64 * 64, "auto_resize": True})
+    assert resized.status_code == 200
+    n_text = _ask(client, [{"type": "text", "text": ""}]).json()["usage"]["prompt_tokens"]
+    assert resized.json()["usage"]["prompt_tokens"] - n_text <= 4 + 2      # at most 64x64 -> 4 features
+    per_image = _ask(client, [big], image_processing={"max_tokens_per_image": 2})
+    assert per_image.status_code == 200
+    assert per_image.json()["usage"]["prompt_tokens"] - n_text <= 2 + 2
