@@ -105,3 +105,34 @@ def test_variants_do_not_change_the_gemm_result(cuda):
         assert native.read_status() == 0
     finally:
         lib.orinfer_qgemm_clear_variants()
+
+
+def test_launch_plan_is_valid_over_the_whole_row_domain():
+    """Offline validation of the launch geometry, the way the reference validates its dynamic
+    row contracts for every live row count (crates/orinfer-model-sdk/src/operators/dynamic.rs:
+    75-146): for each projection shape of the benchmark models, at every tensor-parallel
+    degree and with the packaged table loaded, every row count 1..4096 yields a plan the
+    launcher has a kernel instance for and whose split-K partials fit the workspace."""
+    from orinfer_b200.ops import native
+    lib = native.lib()
+    out = (ctypes.c_int * 4)()
+    formats = tables.FORMATS
+    workspace = 96 << 20                                   # split-K partials buffer
+    checked = 0
+    for table in (False, True):
+        lib.orinfer_qgemm_clear_variants()
+        if table:
+            assert tables.load_default(lib) > 0
+        for preset, degrees in (("qwen3.5-4b-class", (1, 2, 4, 8)), ("27b-class", (1, 8))):
+            for tp in degrees:
+                for fmt, n, k in gemm_tuner.model_shapes(PRESETS[preset], tp):
+                    for m in list(range(1, 513)) + list(range(513, 4097, 7)) + [4096]:
+                        lib.orinfer_qgemm_plan(formats[fmt], m, n, k, 0, out)
+                        mt, nb, splits, tail = list(out)
+                        assert mt in (1, 2, 4) and nb in (32, 64, 128), (fmt, m, n, k, list(out))
+                        assert 1 <= splits <= 8 and splits <= max(k // 128, 1)
+                        assert 0 <= tail <= 8 and (tail == 0 or (splits == 1 and nb == 128))
+                        assert splits == 1 or splits * m * n * 4 <= workspace
+                        checked += 1
+    lib.orinfer_qgemm_clear_variants()
+    assert checked > 40_000
