@@ -195,6 +195,7 @@ class EngineWorker(threading.Thread):
             self.engine = self.engine_factory()
             self._warmup()
             self._instrument()
+            self._gauges()
             if self.async_output:
                 self.pipeline = OutputPipeline(self)
             self.lifecycle.set(Lifecycle.READY)
@@ -220,6 +221,8 @@ class EngineWorker(threading.Thread):
                 self._reap()
                 self.metrics.set("requests_running", len(self.active))
                 self.metrics.set("requests_waiting", self.jobs.qsize())
+                if self.engine.stats.iterations % 32 == 0:
+                    self._gauges()
             if self.pipeline is not None:
                 self.pipeline.close()
             self._exit_report()
@@ -231,6 +234,21 @@ class EngineWorker(threading.Thread):
                 job.post({"type": "error", "status": 500, "message": "engine failure",
                           "code": "engine_failure"})
             self.ready.set()
+
+    def _gauges(self) -> None:
+        """Slow-moving engine state for dashboards: free KV pages, prefix-cache hit rate and
+        pages, speculation acceptance, graph replays."""
+        eng, m = self.engine, self.metrics
+        m.set("kv_pages_free", eng.pool.available)
+        m.set("graph_replays_total", eng.stats.graph_hits)
+        spec = eng.spec.statistics()
+        m.set("speculation_acceptance_rate", spec.get("acceptance_rate", 0.0))
+        m.set("speculation_rounds_total", spec.get("rounds", 0))
+        if eng.prefix is not None:
+            st = eng.prefix.statistics()
+            m.set("prefix_cache_hit_rate", st.hit_rate)
+            m.set("prefix_cache_device_pages", st.device_pages)
+            m.set("prefix_cache_host_pages", st.host_pages)
 
     def _instrument(self) -> None:
         """Time the engine's admission pass and its prefix-cache store / host restore calls for

@@ -91,3 +91,5 @@ def test_every_request_histogram_is_fed(client):
         assert m and int(m.group(1)) >= 1, name
     assert "orinfer_request_prefix_store_seconds_count" in text
     assert "orinfer_admission_seconds_total" in text
+    for gauge in ("kv_pages_free", "speculation_acceptance_rate", "graph_replays_total"):
+        assert re.search(rf"orinfer_{gauge} [0-9.]+", text), gauge
