@@ -220,6 +220,27 @@ class ModelManager:
                      "idle_s": round(self.clock() - r.last_used, 3),
                      "keep_alive_s": r.keep_alive_s} for r in self.runners.values()]
 
+    def load(self, name: str, keep_alive_s: Optional[float] = None) -> dict:
+        """Start the runner of ``name`` ahead of its first request (optionally setting its
+        keep-alive) and return its entry of ``running()``."""
+        self.release(self.acquire(name, keep_alive_s))
+        return next(r for r in self.running() if name in r["names"])
+
+    def unload(self, name: str, force: bool = False) -> bool:
+        """Stop the runner of ``name`` and keep its registration.  A runner with requests in
+        flight is refused (409) unless ``force``, which ends them.  False when not loaded."""
+        key = self.show(name).runner_key()
+        with self._transition:
+            with self._lock:
+                r = self.runners.get(key)
+                if r is None:
+                    return False
+                if r.leases > 0 and not force:
+                    raise ManagerError(f"model '{name}' has {r.leases} requests in flight", 409)
+                del self.runners[key]
+            self._stop(r.service)
+            return True
+
     def logs(self, name: str) -> List[str]:
         """Recent stderr lines of the runner serving ``name`` (child-process runners keep a
         tail; in-process ones have none); 409 when the model is not loaded."""
@@ -271,6 +292,31 @@ def install(app, manager: ModelManager) -> None:
         except ManagerError as e:
             return fail(e)
         return JSONResponse({}, status_code=200)
+
+    @app.post("/api/load")
+    async def load(request: HttpRequest):
+        import asyncio
+        body = await request.json()
+        keep = body.get("keep_alive")
+        if keep is not None:
+            from .ollama import parse_keep_alive
+            keep = parse_keep_alive(keep)
+        try:
+            return await asyncio.get_running_loop().run_in_executor(
+                None, manager.load, body.get("model") or "", keep)
+        except ManagerError as e:
+            return fail(e)
+
+    @app.post("/api/stop")
+    async def stop(request: HttpRequest):
+        import asyncio
+        body = await request.json()
+        try:
+            stopped = await asyncio.get_running_loop().run_in_executor(
+                None, manager.unload, body.get("model") or "", bool(body.get("force")))
+        except ManagerError as e:
+            return fail(e)
+        return {"model": body.get("model"), "stopped": stopped}
 
     @app.get("/api/logs")
     async def logs(model: str = ""):

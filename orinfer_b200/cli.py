@@ -584,11 +584,128 @@ def build_parser() -> argparse.ArgumentParser:
     vn = sub.add_parser("validate-nccl")
     vn.add_argument("--world", type=int, default=0, help="ranks (0 = all visible GPUs)")
     vn.set_defaults(fn=cmd_validate_nccl)
+    for verb, help_text in (("ps", "loaded models of a running manager"),
+                            ("load", "start a model's runner before its first request"),
+                            ("stop", "drain and unload a model, keeping its files"),
+                            ("run", "send one prompt (argument or stdin) or chat interactively"),
+                            ("transcribe", "transcribe an audio file")):
+        c = sub.add_parser(verb, help=help_text)
+        c.add_argument("--url", default="http://127.0.0.1:8088", help="server or manager")
+        if verb != "ps":
+            c.add_argument("name", help="model name")
+        if verb == "load":
+            c.add_argument("--keep-alive", default=None, help="seconds or a duration like 30m")
+        if verb == "stop":
+            c.add_argument("--force", action="store_true", help="end requests in flight")
+        if verb == "run":
+            c.add_argument("prompt", nargs="?", default=None)
+            c.add_argument("--params", default="{}", help="JSON merged into every request")
+        if verb == "transcribe":
+            c.add_argument("input")
+            c.add_argument("--language", default=None)
+            c.add_argument("--prompt", default=None)
+            c.add_argument("--max-tokens", dest="max_tokens", default=None)
+        c.set_defaults(fn=cmd_client, verb=verb)
     bn = sub.add_parser("bench", help="HTTP benchmark clients against a running server")
     bn.add_argument("tool", choices=sorted(BENCH_TOOLS))
     bn.add_argument("tool_args", nargs=argparse.REMAINDER)
     bn.set_defaults(fn=cmd_bench)
     return ap
+
+
+def cmd_client(a) -> int:
+    """Verbs that talk to a running server or manager over HTTP: ``ps``, ``load``, ``stop``,
+    ``run`` (one prompt, piped stdin, or an interactive chat) and ``transcribe``."""
+    import requests
+    url = a.url.rstrip("/")
+
+    def fail(r) -> int:
+        print(r.text.strip(), file=sys.stderr)
+        return 2
+
+    try:
+        if a.verb == "ps":
+            r = requests.get(url + "/api/ps", timeout=10)
+            if r.status_code != 200:
+                return fail(r)
+            print(json.dumps(r.json()["models"], indent=1))
+        elif a.verb == "load":
+            body = {"model": a.name}
+            if a.keep_alive is not None:
+                body["keep_alive"] = a.keep_alive
+            r = requests.post(url + "/api/load", json=body, timeout=3600)
+            if r.status_code != 200:
+                return fail(r)
+            print(json.dumps(r.json()))
+        elif a.verb == "stop":
+            r = requests.post(url + "/api/stop", json={"model": a.name, "force": a.force},
+                              timeout=600)
+            if r.status_code != 200:
+                return fail(r)
+            print(json.dumps(r.json()))
+        elif a.verb == "transcribe":
+            data = {"model": a.name}
+            for key in ("language", "prompt", "max_tokens"):
+                if getattr(a, key):
+                    data[key] = getattr(a, key)
+            with open(a.input, "rb") as f:
+                r = requests.post(url + "/v1/audio/transcriptions", data=data, timeout=3600,
+                                  files={"file": (Path(a.input).name, f)})
+            if r.status_code != 200:
+                return fail(r)
+            print(r.json()["text"])
+        else:
+            return _client_run(a, url)
+    except requests.RequestException as e:
+        print(f"cannot reach {url}: {e}", file=sys.stderr)
+        return 3
+    return 0
+
+
+def _client_run(a, url: str) -> int:
+    import requests
+    params = json.loads(a.params)
+    history = []
+
+    def turn(text: str) -> int:
+        history.append({"role": "user", "content": text})
+        body = dict(params, model=a.name, messages=history, stream=True)
+        reply = ""
+        with requests.post(url + "/v1/chat/completions", json=body, stream=True,
+                           timeout=3600) as r:
+            if r.status_code != 200:
+                print(r.text.strip(), file=sys.stderr)
+                return 2
+            for raw in r.iter_lines():
+                if not raw.startswith(b"data: ") or raw == b"data: [DONE]":
+                    continue
+                ev = json.loads(raw[6:])
+                if "error" in ev:
+                    print(json.dumps(ev["error"]), file=sys.stderr)
+                    return 2
+                for choice in ev.get("choices") or []:
+                    piece = (choice.get("delta") or {}).get("content") or ""
+                    reply += piece
+                    sys.stdout.write(piece)
+                    sys.stdout.flush()
+        sys.stdout.write("\n")
+        history.append({"role": "assistant", "content": reply})
+        return 0
+
+    if a.prompt is not None:
+        return turn(a.prompt)
+    if not sys.stdin.isatty():
+        return turn(sys.stdin.read())
+    while True:                                   # interactive chat; an empty line or EOF ends it
+        try:
+            line = input(">>> ")
+        except EOFError:
+            return 0
+        if not line.strip():
+            return 0
+        code = turn(line)
+        if code:
+            return code
 
 
 BENCH_TOOLS = {"tokens": "token_bench", "quality": "quality", "concurrency": "concurrency", "agentic": "agentic", "startup": "startup",
