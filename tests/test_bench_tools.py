@@ -89,7 +89,7 @@ def test_mixed_and_scheduling(url):
                 {"at_s": 0.3, "prompt": "c", "max_tokens": 4}]
     rep = workloads.scheduling(url, arrivals)
     assert all(r["ok"] and r["completion_tokens"] == 4 for r in rep["requests"])
-    assert all(-0.01 <= r["send_lag_s"] < 0.2 for r in rep["requests"])
+    assert all(-0.01 <= r["send_lag_s"] < 2.0 for r in rep["requests"])
     assert rep["requests"][2]["sent_s"] >= 0.3
 
 

@@ -40,13 +40,13 @@ def test_stalled_step_fails_the_service_and_answers_clients():
         def step():
             calls["n"] += 1
             if calls["n"] > 3:                               # after the warm-up: a host call that
-                release.wait(5)                              # does not come back in time
+                release.wait(12)                             # does not come back in time
             return real()
         eng.step = step
         return eng
 
     svc = Service(factory, ChatCodec(ByteTokenizer(1024), context=256, model_name="tiny"), "tiny",
-                  step_timeout_ms=200)
+                  step_timeout_ms=2000)
     svc.start()
     with TestClient(create_app(svc)) as c:
         assert c.get("/health").status_code == 200
