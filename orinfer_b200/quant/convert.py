@@ -48,17 +48,26 @@ def config_from_hf(hf: dict, name: Optional[str] = None) -> ModelConfig:
     if hf.get("attention_bias"):
         raise ConvertError("attention projections with bias are not supported")
     heads = hf["num_attention_heads"]
+    # older configs carry `rope_theta` (+ `rope_scaling`), newer ones a `rope_parameters` object
+    rope = dict(hf.get("rope_parameters") or hf.get("rope_scaling") or {})
+    kind = rope.get("rope_type") or rope.get("type") or "default"
+    if kind != "default":
+        raise ConvertError(f"rotary scaling `{kind}` is not supported (plain RoPE only)")
+    theta = hf.get("rope_theta") or rope.get("rope_theta") or 1e6
     common = dict(
         name=name or hf.get("_name_or_path") or arch, layers=hf["num_hidden_layers"],
         hidden=hf["hidden_size"], q_heads=heads, kv_heads=hf.get("num_key_value_heads", heads),
         head_dim=hf.get("head_dim") or hf["hidden_size"] // heads, vocab=hf["vocab_size"],
-        eps=hf.get("rms_norm_eps", 1e-6), rope_theta=float(hf.get("rope_theta", 1e6)),
+        eps=hf.get("rms_norm_eps", 1e-6), rope_theta=float(theta),
         tied_embeddings=bool(hf.get("tie_word_embeddings", False)),
         max_context=int(hf.get("max_position_embeddings", 32768)))
     if arch == "Qwen3MoeForCausalLM":
         if hf.get("mlp_only_layers") or hf.get("decoder_sparse_step", 1) != 1:
             raise ConvertError("mixed dense / sparse layer stacks are not supported")
-        return ModelConfig(arch="moe", ffn=0, experts=hf["num_experts"],
+        experts = hf.get("num_experts") or hf.get("num_local_experts")
+        if not experts:
+            raise ConvertError("the configuration does not say how many experts there are")
+        return ModelConfig(arch="moe", ffn=0, experts=experts,
                            top_k=hf["num_experts_per_tok"], expert_ffn=hf["moe_intermediate_size"],
                            renormalize=bool(hf.get("norm_topk_prob", True)), **common)
     return ModelConfig(arch="dense", ffn=hf["intermediate_size"], **common)
@@ -98,17 +107,27 @@ def _atomic_json(path: Path, obj) -> None:
 
 
 def convert(source, output, device: str = "cpu", fast: bool = True, name: Optional[str] = None,
-            on_layer: Optional[Callable[[int, bool], None]] = None) -> Path:
+            on_layer: Optional[Callable[[int, bool], None]] = None,
+            formats: Optional[Dict[str, str]] = None) -> Path:
     """Returns the model directory.  ``on_layer(i, resumed)`` is called after layer ``i`` is on
-    disk (freshly quantised or found in the progress record)."""
+    disk (freshly quantised or found in the progress record).  ``formats`` overrides the
+    weight formats of the geometry (``attn_format``, ``proj_format``, ``expert_format``,
+    ``head_format``: ``q4`` | ``q2`` | ``w8``)."""
     from ..engine.checkpoint import _layer_tensors, _load_layer, save_model
     source, output = Path(source), Path(output)
     config_text = (source / "config.json").read_text()
     cfg = config_from_hf(json.loads(config_text), name)
+    if formats:
+        import dataclasses
+        unknown = set(formats) - {"attn_format", "proj_format", "expert_format", "head_format"}
+        if unknown or any(v not in ("q4", "q2", "w8") for v in formats.values()):
+            raise ConvertError("formats maps attn / proj / expert / head_format to q4, q2 or w8")
+        cfg = dataclasses.replace(cfg, **formats)
     src = _Source(source)
     work = output / ".convert"
     work.mkdir(parents=True, exist_ok=True)
-    identity = src.identity(config_text + f"|{cfg.attn_format}|{cfg.proj_format}|{fast}")
+    identity = src.identity(config_text + f"|{cfg.attn_format}|{cfg.proj_format}"
+                            f"|{cfg.expert_format}|{cfg.head_format}|{fast}")
     record_path = work / "progress.json"
     record = {"source": identity, "done": {}}
     if record_path.exists():
@@ -149,8 +168,16 @@ def convert(source, output, device: str = "cpu", fast: bool = True, name: Option
         if cfg.experts:
             lw.router = f16(src.get(p + "mlp.gate.weight"))
             gu, dn = [], []
+            fused = p + "mlp.experts.gate_up_proj" in src.where     # [E, 2F, H] / [E, H, F]
+            if fused:
+                all_gu, all_dn = src.get(p + "mlp.experts.gate_up_proj"), \
+                    src.get(p + "mlp.experts.down_proj")
             for e in range(cfg.experts):
                 q = p + f"mlp.experts.{e}."
+                if fused:
+                    gu.append(lin(all_gu[e], cfg.expert_format))
+                    dn.append(lin(all_dn[e], cfg.expert_format))
+                    continue
                 gu.append(lin(torch.cat([src.get(q + "gate_proj.weight"),
                                          src.get(q + "up_proj.weight")]), cfg.expert_format))
                 dn.append(lin(src.get(q + "down_proj.weight"), cfg.expert_format))
@@ -203,9 +230,12 @@ def main(argv=None) -> int:
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--exhaustive", action="store_true", help="slower search, lower error")
     ap.add_argument("--name", default=None)
+    ap.add_argument("--format", action="append", default=[], metavar="KEY=FMT",
+                    help="e.g. --format attn_format=w8 (q4 | q2 | w8)")
     a = ap.parse_args(argv)
     try:
         out = convert(a.source, a.output, a.device, fast=not a.exhaustive, name=a.name,
+                      formats=dict(x.split("=", 1) for x in a.format) or None,
                       on_layer=lambda i, resumed: print(
                           f"layer {i} {'kept' if resumed else 'quantised'}", flush=True))
     except ConvertError as e:

@@ -130,3 +130,46 @@ def test_moe_conversion_and_refusals(tmp_path):
     (tmp_path / "hf/model-00002-of-00002.safetensors").unlink()
     with pytest.raises(C.ConvertError, match="missing"):
         C.convert(tmp_path / "hf", tmp_path / "out2")
+
+
+@pytest.mark.parametrize("moe", [False, True], ids=["dense", "moe"])
+def test_converted_model_reproduces_the_transformers_implementation(tmp_path, moe):
+    """Independent check of the whole decoder semantics (norm convention, q/k head norms,
+    rotary pairing, grouped-query attention, SwiGLU, expert routing, head): a random-init
+    Qwen3 model of the `transformers` library is saved, converted with 8-bit weights (so that
+    quantisation noise stays small) and run through this repository's forward; the logits must
+    match the library's."""
+    transformers = pytest.importorskip("transformers")
+    from orinfer_b200.engine.checkpoint import load_model
+    from orinfer_b200.ref.cpu_forward import RefKV, forward_request
+    torch.manual_seed(0)
+    common = dict(hidden_size=H, num_hidden_layers=2, num_attention_heads=HEADS,
+                  num_key_value_heads=KV, head_dim=D, vocab_size=V, rms_norm_eps=1e-6,
+                  rope_theta=10000.0, tie_word_embeddings=False, max_position_embeddings=512,
+                  attention_bias=False)
+    if moe:
+        cfg = transformers.Qwen3MoeConfig(intermediate_size=FFN, moe_intermediate_size=128,
+                                          num_experts=4, num_experts_per_tok=2, norm_topk_prob=True,
+                                          decoder_sparse_step=1, mlp_only_layers=[], **common)
+        model = transformers.Qwen3MoeForCausalLM(cfg)
+    else:
+        cfg = transformers.Qwen3Config(intermediate_size=FFN, **common)
+        model = transformers.Qwen3ForCausalLM(cfg)
+    model = model.float().eval()
+    with torch.no_grad():                         # norms away from 1 so their convention matters
+        for name, p in model.named_parameters():
+            if name.endswith("norm.weight") or "layernorm" in name:
+                p.copy_(1.0 + 0.3 * torch.randn_like(p))
+    model.save_pretrained(tmp_path / "hf", safe_serialization=True)
+    fmts = {"attn_format": "w8", "proj_format": "w8", "expert_format": "w8"}
+    w = load_model(C.convert(tmp_path / "hf", tmp_path / "out", formats=fmts))
+    ids = torch.randint(0, V, (24,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = model(ids[None]).logits[0].float()
+    got = forward_request(w, ids.int(), 0, RefKV(w.config.layers), quantized=True)
+    cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
+    assert float(cos.min()) > 0.99, cos
+    agree = (got.argmax(-1) == want.argmax(-1)).float().mean()
+    assert float(agree) >= 0.8
+    with pytest.raises(C.ConvertError, match="formats"):
+        C.convert(tmp_path / "hf", tmp_path / "bad", formats={"attn_format": "fp8"})
