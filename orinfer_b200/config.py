@@ -67,6 +67,7 @@ class ModelConfig:
     vocab: int = 1024
     eps: float = 1e-6
     rope_theta: float = 1e6
+    rotary_dim: int = 0            # channels of a head that rotate (0 = all of them)
     tied_embeddings: bool = True
     zero_centered_norm: bool = False
     qk_norm: bool = True

@@ -409,14 +409,20 @@ class ModelRunner:
     supports_media = True
 
     def _rope(self, p: Packet, rows: int) -> None:
+        """Fill the rotary tables of the packet: the table kernel for ordinary positions,
+        PyTorch for (t, h, w) positions and for partially rotated heads."""
         cfg, ws = self.cfg, self.ws
-        if p.mrope is None:
+        if p.mrope is None and not cfg.rotary_dim:
             F.rope_table(p.row_pos, cfg.head_dim, cfg.rope_theta, ws.cos, ws.sin, rows=rows)
-        else:
+            return
+        if p.mrope is not None:
             from .vision import mrope_tables
             cos, sin = mrope_tables(p.mrope[:, :rows], cfg.head_dim, cfg.rope_theta)
-            ws.cos[:rows].copy_(cos)
-            ws.sin[:rows].copy_(sin)
+        else:
+            from ..ref.ops_ref import rope_tables
+            cos, sin = rope_tables(p.row_pos[:rows], cfg.head_dim, cfg.rope_theta, cfg.rotary_dim)
+        ws.cos[:rows].copy_(cos)
+        ws.sin[:rows].copy_(sin)
 
     def _moe_ffn(self, lw: LayerWeights, x, rows: int):
         """norm+rotate+quantise once -> router top-k -> dispatch rows to expert-contiguous
@@ -529,7 +535,7 @@ class ModelRunner:
         ws.resid = b["resid"]
         try:
             ws.resid[:rows].zero_()
-            F.rope_table(p.row_pos, cfg.head_dim, cfg.rope_theta, ws.cos, ws.sin, rows=rows)
+            self._rope(p, rows)
             x = self._attention_block(m.layer, self.mtp_kv_index, x, p, rows, True)
             x = self._dense_ffn(m.layer, x, rows)
             q8, sc = self._prep(x, m.final_norm, self.w.head.signs, rows)

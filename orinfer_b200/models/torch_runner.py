@@ -170,7 +170,7 @@ class TorchRunner:
             x = x.index_copy(0, p.overlay_rows, p.overlay.to(x.dtype))
         resid = torch.zeros(rows, cfg.hidden)
         if p.mrope is None:
-            cos, sin = R.rope_tables(p.row_pos[:rows], cfg.head_dim, cfg.rope_theta)
+            cos, sin = R.rope_tables(p.row_pos[:rows], cfg.head_dim, cfg.rope_theta, cfg.rotary_dim)
         else:
             from .vision import mrope_tables
             cos, sin = mrope_tables(p.mrope[:, :rows], cfg.head_dim, cfg.rope_theta)
@@ -232,7 +232,7 @@ class TorchRunner:
         ye = R.rms_norm(e, m.norm_e, cfg.eps, zc)
         yh = R.rms_norm(hidden[:rows].float(), m.norm_h, cfg.eps, zc)
         x = self._linear(m.fc, torch.cat([ye, yh], dim=1))
-        cos, sin = R.rope_tables(p.row_pos[:rows], cfg.head_dim, cfg.rope_theta)
+        cos, sin = R.rope_tables(p.row_pos[:rows], cfg.head_dim, cfg.rope_theta, cfg.rotary_dim)
         resid = x
         y = R.rms_norm(resid, m.layer.in_norm, cfg.eps, zc)
         mix = self._attention(m.layer, self.mtp_kv_index, y, p, cos, sin)

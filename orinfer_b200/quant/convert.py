@@ -43,8 +43,9 @@ class ConvertError(ValueError):
 
 def config_from_hf(hf: dict, name: Optional[str] = None) -> ModelConfig:
     arch = (hf.get("architectures") or [""])[0]
-    if arch not in ("Qwen3ForCausalLM", "Qwen3MoeForCausalLM"):
-        raise ConvertError(f"unsupported architecture `{arch}` (Qwen3 dense and MoE are converted)")
+    if arch not in ("Qwen3ForCausalLM", "Qwen3MoeForCausalLM", "Qwen3NextForCausalLM"):
+        raise ConvertError(f"unsupported architecture `{arch}` (Qwen3 dense, MoE and the hybrid "
+                           "gated-delta-rule family are converted)")
     if hf.get("attention_bias"):
         raise ConvertError("attention projections with bias are not supported")
     heads = hf["num_attention_heads"]
@@ -61,6 +62,30 @@ def config_from_hf(hf: dict, name: Optional[str] = None) -> ModelConfig:
         eps=hf.get("rms_norm_eps", 1e-6), rope_theta=float(theta),
         tied_embeddings=bool(hf.get("tie_word_embeddings", False)),
         max_context=int(hf.get("max_position_embeddings", 32768)))
+    if arch == "Qwen3NextForCausalLM":
+        period = hf.get("full_attention_interval") or 4
+        types = hf.get("layer_types")
+        want = ["full_attention" if i % period == period - 1 else "linear_attention"
+                for i in range(hf["num_hidden_layers"])]
+        if types is not None and list(types) != want:
+            raise ConvertError("layer_types must repeat (period - 1) linear layers and one "
+                               "full-attention layer")
+        if hf.get("linear_key_head_dim") != hf.get("linear_value_head_dim"):
+            raise ConvertError("key and value head sizes of the linear layers must be equal")
+        if hf.get("mlp_only_layers") or hf.get("decoder_sparse_step", 1) != 1:
+            raise ConvertError("mixed dense / sparse layer stacks are not supported")
+        factor = hf.get("partial_rotary_factor") or rope.get("partial_rotary_factor") or 1.0
+        rotary = int(common["head_dim"] * factor)
+        return ModelConfig(
+            arch="hybrid", ffn=0, gdn_period=period, gdn_k_heads=hf["linear_num_key_heads"],
+            gdn_v_heads=hf["linear_num_value_heads"], gdn_head_dim=hf["linear_key_head_dim"],
+            gdn_conv=hf.get("linear_conv_kernel_dim", 4),
+            experts=hf.get("num_experts") or hf.get("num_local_experts"),
+            top_k=hf["num_experts_per_tok"], expert_ffn=hf["moe_intermediate_size"],
+            shared_expert_ffn=hf.get("shared_expert_intermediate_size", 0),
+            renormalize=bool(hf.get("norm_topk_prob", True)), gated_attention=True,
+            zero_centered_norm=True, rotary_dim=0 if rotary == common["head_dim"] else rotary,
+            **common)
     if arch == "Qwen3MoeForCausalLM":
         if hf.get("mlp_only_layers") or hf.get("decoder_sparse_step", 1) != 1:
             raise ConvertError("mixed dense / sparse layer stacks are not supported")
@@ -98,6 +123,19 @@ class _Source:
             raise ConvertError(f"tensor `{name}` is missing from the source checkpoint")
         with safe_open(str(f), "pt") as h:
             return h.get_tensor(name).float()
+
+
+def rotary_permutation(head_dim: int, rotary_dim: int) -> torch.Tensor:
+    """Channel order that turns "rotate the first ``rotary_dim`` channels in pairs
+    ``(i, i + rotary_dim / 2)``" into this engine's pairing ``(i, i + head_dim / 2)``:
+    ``new[j] = old[perm[j]]``.  Applied alike to q rows, k rows and their head-norm weights it
+    leaves every attention score unchanged."""
+    if not rotary_dim or rotary_dim == head_dim:
+        return torch.arange(head_dim)
+    half, r2 = head_dim // 2, rotary_dim // 2
+    rest = torch.arange(rotary_dim, head_dim)
+    fill = half - r2
+    return torch.cat([torch.arange(0, r2), rest[:fill], torch.arange(r2, rotary_dim), rest[fill:]])
 
 
 def _atomic_json(path: Path, obj) -> None:
@@ -158,15 +196,48 @@ def convert(source, output, device: str = "cpu", fast: bool = True, name: Option
                 on_layer(i, True)
             continue
         p = f"model.layers.{i}."
-        lw = LayerWeights("attn", f16(src.get(p + "input_layernorm.weight")),
+        full = cfg.is_full_attention(i)
+        lw = LayerWeights("attn" if full else "gdn", f16(src.get(p + "input_layernorm.weight")),
                           f16(src.get(p + "post_attention_layernorm.weight")))
-        lw.qkv = lin(torch.cat([src.get(p + f"self_attn.{x}_proj.weight") for x in "qkv"]),
-                     cfg.attn_format)
-        lw.q_norm = f16(src.get(p + "self_attn.q_norm.weight"))
-        lw.k_norm = f16(src.get(p + "self_attn.k_norm.weight"))
-        lw.o = lin(src.get(p + "self_attn.o_proj.weight"), cfg.attn_format)
+        if full:
+            d, perm = cfg.head_dim, rotary_permutation(cfg.head_dim, cfg.rotary_dim)
+            q = src.get(p + "self_attn.q_proj.weight")
+            k = src.get(p + "self_attn.k_proj.weight").reshape(cfg.kv_heads, d, -1)[:, perm]
+            if cfg.gated_attention:                # per head: d query rows, then d gate rows
+                q = q.reshape(cfg.q_heads, 2, d, -1)
+                q = torch.cat([q[:, 0][:, perm], q[:, 1]], dim=1)
+            else:
+                q = q.reshape(cfg.q_heads, d, -1)[:, perm]
+            lw.qkv = lin(torch.cat([q.reshape(-1, cfg.hidden), k.reshape(-1, cfg.hidden),
+                                    src.get(p + "self_attn.v_proj.weight")]), cfg.attn_format)
+            lw.q_norm = f16(src.get(p + "self_attn.q_norm.weight")[perm])
+            lw.k_norm = f16(src.get(p + "self_attn.k_norm.weight")[perm])
+            lw.o = lin(src.get(p + "self_attn.o_proj.weight"), cfg.attn_format)
+        else:
+            hk, hv, gd = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim
+            rep = hv // hk
+            # source rows are grouped per key head: q | k | v of its value heads | z of them
+            w = src.get(p + "linear_attn.in_proj_qkvz.weight").reshape(hk, 2 * gd + 2 * rep * gd, -1)
+            parts = torch.split(w, [gd, gd, rep * gd, rep * gd], dim=1)
+            lw.gdn_qkvz = lin(torch.cat([x.reshape(-1, cfg.hidden) for x in parts]),
+                              cfg.attn_format)
+            ba = src.get(p + "linear_attn.in_proj_ba.weight").reshape(hk, 2 * rep, -1)
+            lw.gdn_ab = f16(torch.cat([ba[:, rep:].reshape(hv, -1), ba[:, :rep].reshape(hv, -1)]))
+            lw.gdn_conv = f16(src.get(p + "linear_attn.conv1d.weight")[:, 0, :])
+            lw.gdn_a_log = src.get(p + "linear_attn.A_log").float().contiguous()
+            lw.gdn_dt_bias = src.get(p + "linear_attn.dt_bias").float().contiguous()
+            lw.gdn_norm = f16(src.get(p + "linear_attn.norm.weight"))
+            lw.gdn_out = lin(src.get(p + "linear_attn.out_proj.weight"), cfg.attn_format)
         if cfg.experts:
-            lw.router = f16(src.get(p + "mlp.gate.weight"))
+            router = src.get(p + "mlp.gate.weight")
+            if cfg.shared_expert_ffn:
+                router = torch.cat([router, src.get(p + "mlp.shared_expert_gate.weight")])
+                lw.shared_gate_up = lin(torch.cat([
+                    src.get(p + "mlp.shared_expert.gate_proj.weight"),
+                    src.get(p + "mlp.shared_expert.up_proj.weight")]), cfg.proj_format)
+                lw.shared_down = lin(src.get(p + "mlp.shared_expert.down_proj.weight"),
+                                     cfg.proj_format)
+            lw.router = f16(router)
             gu, dn = [], []
             fused = p + "mlp.experts.gate_up_proj" in src.where     # [E, 2F, H] / [E, H, F]
             if fused:
@@ -201,12 +272,14 @@ def convert(source, output, device: str = "cpu", fast: bool = True, name: Option
             on_layer(i, False)
 
     # ---- assemble -----------------------------------------------------------------------
-    for k in {cfg.hidden, cfg.q_heads * cfg.head_dim, cfg.ffn or cfg.expert_ffn}:
+    for k in {cfg.hidden, cfg.q_heads * cfg.head_dim, cfg.ffn or cfg.expert_ffn,
+              cfg.shared_expert_ffn or cfg.hidden, (cfg.gdn_v_heads * cfg.gdn_head_dim) or cfg.hidden}:
         sign(k)
     layers: List[LayerWeights] = []
     for i in range(cfg.layers):
         t = load_file(str(work / f"layer_{i:05d}.safetensors"))
-        layers.append(_load_layer(t, f"layers.{i}", "attn", signs))
+        layers.append(_load_layer(t, f"layers.{i}",
+                                  "attn" if cfg.is_full_attention(i) else "gdn", signs))
     emb = quantize_linear(src.get("model.embed_tokens.weight"), "w8", None)
     if cfg.tied_embeddings:
         head = QLinear("w8", cfg.vocab, cfg.hidden, emb.codes, emb.scale, None)

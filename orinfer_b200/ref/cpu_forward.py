@@ -64,7 +64,7 @@ def attention_layer(cfg: ModelConfig, lw: LayerWeights, y: torch.Tensor, positio
     """y: normed input [T, H] for ONE request; returns mixer output [T, QH*D]."""
     t = y.shape[0]
     d, qh, kvh = cfg.head_dim, cfg.q_heads, cfg.kv_heads
-    cos, sin = R.rope_tables(positions, d, cfg.rope_theta)
+    cos, sin = R.rope_tables(positions, d, cfg.rope_theta, cfg.rotary_dim)
     proj = _linear_q(lw.qkv, y) if quantized else _linear_fp(lw.qkv, y)
     qw = cfg.q_dim
     gate = None

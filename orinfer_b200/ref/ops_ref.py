@@ -91,9 +91,18 @@ def embed_w8(ids: torch.Tensor, table_q: torch.Tensor, table_s: torch.Tensor) ->
     return f16(table_q[ids.long()].float() * table_s.float()[ids.long()][:, None])
 
 
-def rope_tables(positions: torch.Tensor, dim: int, theta: float):
-    """cos/sin [M, dim/2] in fp32 for NeoX-style rotary embedding."""
-    inv = theta ** (-torch.arange(0, dim, 2, dtype=torch.float64, device=positions.device) / dim)
+def rope_tables(positions: torch.Tensor, dim: int, theta: float, rotary_dim: int = 0):
+    """cos/sin [M, dim/2] in fp32 for NeoX-style rotary embedding (pairs ``(i, i + dim/2)``).
+
+    ``rotary_dim`` (0 = the whole head) turns only ``rotary_dim / 2`` pairs, with frequencies
+    ``theta ** (-2i / rotary_dim)``; the other pairs get angle 0.  A checkpoint whose partial
+    rotary acts on the first ``rotary_dim`` channels in pairs ``(i, i + rotary_dim/2)`` is
+    brought to this pairing by permuting its q / k channels at conversion time."""
+    half = dim // 2
+    r = rotary_dim or dim
+    inv = torch.zeros(half, dtype=torch.float64, device=positions.device)
+    inv[: r // 2] = theta ** (-torch.arange(0, r, 2, dtype=torch.float64,
+                                            device=positions.device) / r)
     ang = positions.double()[:, None] * inv[None, :]
     return ang.cos().float(), ang.sin().float()
 

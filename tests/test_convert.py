@@ -173,3 +173,45 @@ def test_converted_model_reproduces_the_transformers_implementation(tmp_path, mo
     assert float(agree) >= 0.8
     with pytest.raises(C.ConvertError, match="formats"):
         C.convert(tmp_path / "hf", tmp_path / "bad", formats={"attn_format": "fp8"})
+
+
+def test_hybrid_family_reproduces_the_transformers_implementation(tmp_path):
+    """Gated-delta-rule layers (grouped q|k|v|z rows, b|a gates, depthwise convolution, gated
+    norm), gated attention with zero-centred head norms and a partially rotated head, routed
+    experts with a gated shared expert: converted from a random-init `transformers` model and
+    compared with it."""
+    transformers = pytest.importorskip("transformers")
+    if not hasattr(transformers, "Qwen3NextForCausalLM"):
+        pytest.skip("this transformers has no Qwen3-Next")
+    from orinfer_b200.engine.checkpoint import load_model
+    from orinfer_b200.ref.cpu_forward import RefKV, forward_request
+    torch.manual_seed(0)
+    cfg = transformers.Qwen3NextConfig(
+        hidden_size=H, num_hidden_layers=4, num_attention_heads=HEADS, num_key_value_heads=KV,
+        head_dim=D, vocab_size=V, intermediate_size=FFN, moe_intermediate_size=128,
+        shared_expert_intermediate_size=128, num_experts=4, num_experts_per_tok=2,
+        linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=64,
+        linear_value_head_dim=64, partial_rotary_factor=0.25, rope_theta=10000.0,
+        tie_word_embeddings=False, max_position_embeddings=512)
+    model = transformers.Qwen3NextForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if name.endswith("norm.weight") or "layernorm" in name:
+                p.copy_((0.0 if "linear_attn.norm" not in name else 1.0) + 0.3 * torch.randn_like(p))
+            if name.endswith("A_log") or name.endswith("dt_bias"):
+                p.copy_(0.5 * torch.randn_like(p))
+    model.save_pretrained(tmp_path / "hf", safe_serialization=True)
+    fmts = {"attn_format": "w8", "proj_format": "w8", "expert_format": "w8"}
+    w = load_model(C.convert(tmp_path / "hf", tmp_path / "out", formats=fmts))
+    c = w.config
+    assert (c.arch, c.gdn_period, c.rotary_dim, c.zero_centered_norm, c.gated_attention,
+            c.shared_expert_ffn) == ("hybrid", 4, 16, True, True, 128)
+    assert [lw.kind for lw in w.layers] == ["gdn", "gdn", "gdn", "attn"]
+    ids = torch.randint(0, V, (24,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = model(ids[None]).logits[0].float()
+    got = forward_request(w, ids.int(), 0, RefKV(c.layers), quantized=True)
+    cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
+    assert float(cos.min()) > 0.99, cos
+    perm = C.rotary_permutation(8, 4)
+    assert perm.tolist() == [0, 1, 4, 5, 2, 3, 6, 7] and C.rotary_permutation(8, 0).tolist() == list(range(8))
