@@ -541,9 +541,10 @@ def build_parser() -> argparse.ArgumentParser:
     cv.add_argument("--device", default="cuda")
     cv.add_argument("--exhaustive", action="store_true")
     cv.add_argument("--name", default=None)
+    cv.add_argument("--format", action="append", default=[], metavar="KEY=FMT")
     cv.set_defaults(fn=lambda a: __import__("orinfer_b200.quant.convert", fromlist=["main"]).main(
         [a.source, a.output, "--device", a.device] + (["--exhaustive"] if a.exhaustive else [])
-        + (["--name", a.name] if a.name else [])))
+        + (["--name", a.name] if a.name else []) + [x for f in a.format for x in ("--format", f)]))
     mk = sub.add_parser("make-model")
     mk.add_argument("--preset", required=True, choices=sorted(PRESETS))
     mk.add_argument("--output", required=True)
