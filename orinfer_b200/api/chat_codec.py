@@ -196,8 +196,13 @@ class ChatCodec:
                  defaults: Optional[ModelDefaults] = None, context: int = 32768,
                  model_name: str = "orinfer", protect_controls: bool = True):
         self.tokenizer = tokenizer
-        self.env = jinja2.Environment(trim_blocks=False, lstrip_blocks=False)
+        self.env = jinja2.Environment(trim_blocks=False, lstrip_blocks=False,
+                                      extensions=["jinja2.ext.loopcontrols"])
         self.env.filters["tojson"] = _tojson
+
+        def raise_exception(message):          # templates written for transformers call this
+            raise jinja2.TemplateError(message)
+        self.env.globals["raise_exception"] = raise_exception
         # control tokens may come only from the template source or the server (token_boundary.py)
         self.boundary = None
         if protect_controls:
@@ -222,6 +227,11 @@ class ChatCodec:
         tpl = model_dir / "chat_template.jinja"
         if tpl.exists():
             template = tpl.read_text()
+        elif (model_dir / "tokenizer_config.json").exists():
+            # older checkpoints keep the template inside the tokenizer configuration
+            held = json.loads((model_dir / "tokenizer_config.json").read_text()).get("chat_template")
+            if isinstance(held, str) and held.strip():
+                template = held
         eos: List[int] = []
         gen = model_dir / "generation_config.json"
         if gen.exists():

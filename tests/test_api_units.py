@@ -98,3 +98,24 @@ def test_thinking_budget_forces_close():
     assert tb.closed and tb.mask(1024) is None
     # the budget always leaves room for the answer
     assert ThinkingBudget(close, budget=100, max_new=10).budget == 8
+
+
+def test_codec_loads_templates_kept_in_the_tokenizer_configuration(tmp_path):
+    import json
+    from orinfer_b200.api.chat_codec import ChatCodec, RequestError
+    template = ("{% for m in messages %}{% if m.role == 'tool' %}{{ raise_exception('no tools') }}"
+                "{% endif %}{% if loop.index > 2 %}{% break %}{% endif %}"
+                "<|im_start|>{{ m.role }}: {{ m.content }}<|im_end|>{% endfor %}")
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps({"chat_template": template}))
+    codec = ChatCodec.load(tmp_path, 1024, 512, "m")
+    msgs = [{"role": "user", "content": str(i)} for i in range(4)]
+    text = codec.prepare({"messages": msgs}).prompt_text
+    assert text == "<|im_start|>user: 0<|im_end|><|im_start|>user: 1<|im_end|>"     # break honoured
+    try:
+        codec.prepare({"messages": [{"role": "tool", "content": "x"}]})
+    except RequestError as e:
+        assert "no tools" in e.message
+    else:
+        raise AssertionError("the template's own refusal must surface as a request error")
+    (tmp_path / "chat_template.jinja").write_text("{{ messages[0].content }}!")
+    assert ChatCodec.load(tmp_path, 1024, 512, "m").prepare({"messages": msgs}).prompt_text == "0!"
