@@ -463,8 +463,21 @@ def cmd_devices(a) -> int:
 def cmd_info(a) -> int:
     from . import __version__
     from .ops import native
-    print(json.dumps({"version": __version__, "target": "sm_100a",
-                      "kernel_library": native.loaded(), "presets": sorted(PRESETS)}))
+    from . import contracts
+    from .core._lib import lib as core_lib
+    try:
+        core_lib()
+        core = True
+    except OSError:
+        core = False
+    print(json.dumps({
+        "version": __version__, "target": contracts.TARGET,
+        "compute_policy": contracts.COMPUTE_POLICY, "kernel_library": native.loaded(),
+        "policy_core": core, "architectures": contracts.architectures(),
+        "convertible": ["Qwen3ForCausalLM", "Qwen3MoeForCausalLM", "Qwen3NextForCausalLM"],
+        "routes": ["/v1/chat/completions", "/v1/completions", "/v1/embeddings", "/v1/rerank",
+                   "/v1/audio/transcriptions", "/api/chat", "/api/generate"],
+        "presets": sorted(PRESETS)}))
     return 0
 
 
