@@ -213,5 +213,13 @@ def test_hybrid_family_reproduces_the_transformers_implementation(tmp_path):
     got = forward_request(w, ids.int(), 0, RefKV(c.layers), quantized=True)
     cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
     assert float(cos.min()) > 0.99, cos
+    # the serving engine (paged KV, chunked prefill) walks the same arithmetic as the
+    # single-request forward, partial rotary included
+    from orinfer_b200.config import SchedulerOptions
+    from orinfer_b200.engine.engine import Engine
+    from orinfer_b200.ref.cpu_forward import generate_greedy
+    eng = Engine(w, sched=SchedulerOptions(max_active=2, prefill_chunk=16), kv_pages=8,
+                 max_context=256)
+    assert eng.generate([ids.tolist()], max_new=5)[0] == generate_greedy(w, ids.int(), 5)[0]
     perm = C.rotary_permutation(8, 4)
     assert perm.tolist() == [0, 1, 4, 5, 2, 3, 6, 7] and C.rotary_permutation(8, 0).tolist() == list(range(8))
