@@ -474,7 +474,8 @@ def cmd_info(a) -> int:
         "version": __version__, "target": contracts.TARGET,
         "compute_policy": contracts.COMPUTE_POLICY, "kernel_library": native.loaded(),
         "policy_core": core, "architectures": contracts.architectures(),
-        "convertible": ["Qwen3ForCausalLM", "Qwen3MoeForCausalLM", "Qwen3NextForCausalLM"],
+        "convertible": ["Qwen3ForCausalLM", "Qwen3MoeForCausalLM", "Qwen3NextForCausalLM",
+                        "LlamaForCausalLM", "MistralForCausalLM"],
         "routes": ["/v1/chat/completions", "/v1/completions", "/v1/embeddings", "/v1/rerank",
                    "/v1/audio/transcriptions", "/api/chat", "/api/generate"],
         "presets": sorted(PRESETS)}))

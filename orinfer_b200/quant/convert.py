@@ -43,9 +43,12 @@ class ConvertError(ValueError):
 
 def config_from_hf(hf: dict, name: Optional[str] = None) -> ModelConfig:
     arch = (hf.get("architectures") or [""])[0]
-    if arch not in ("Qwen3ForCausalLM", "Qwen3MoeForCausalLM", "Qwen3NextForCausalLM"):
+    plain = ("LlamaForCausalLM", "MistralForCausalLM")       # same decoder without head norms
+    if arch not in ("Qwen3ForCausalLM", "Qwen3MoeForCausalLM", "Qwen3NextForCausalLM") + plain:
         raise ConvertError(f"unsupported architecture `{arch}` (Qwen3 dense, MoE and the hybrid "
-                           "gated-delta-rule family are converted)")
+                           "gated-delta-rule family, Llama and Mistral are converted)")
+    if hf.get("mlp_bias") or hf.get("sliding_window"):
+        raise ConvertError("MLP biases and sliding-window attention are not supported")
     if hf.get("attention_bias"):
         raise ConvertError("attention projections with bias are not supported")
     heads = hf["num_attention_heads"]
@@ -95,7 +98,8 @@ def config_from_hf(hf: dict, name: Optional[str] = None) -> ModelConfig:
         return ModelConfig(arch="moe", ffn=0, experts=experts,
                            top_k=hf["num_experts_per_tok"], expert_ffn=hf["moe_intermediate_size"],
                            renormalize=bool(hf.get("norm_topk_prob", True)), **common)
-    return ModelConfig(arch="dense", ffn=hf["intermediate_size"], **common)
+    return ModelConfig(arch="dense", ffn=hf["intermediate_size"], qk_norm=arch not in plain,
+                       **common)
 
 
 class _Source:
@@ -210,8 +214,9 @@ def convert(source, output, device: str = "cpu", fast: bool = True, name: Option
                 q = q.reshape(cfg.q_heads, d, -1)[:, perm]
             lw.qkv = lin(torch.cat([q.reshape(-1, cfg.hidden), k.reshape(-1, cfg.hidden),
                                     src.get(p + "self_attn.v_proj.weight")]), cfg.attn_format)
-            lw.q_norm = f16(src.get(p + "self_attn.q_norm.weight")[perm])
-            lw.k_norm = f16(src.get(p + "self_attn.k_norm.weight")[perm])
+            if cfg.qk_norm:
+                lw.q_norm = f16(src.get(p + "self_attn.q_norm.weight")[perm])
+                lw.k_norm = f16(src.get(p + "self_attn.k_norm.weight")[perm])
             lw.o = lin(src.get(p + "self_attn.o_proj.weight"), cfg.attn_format)
         else:
             hk, hv, gd = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim

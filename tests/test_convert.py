@@ -223,3 +223,29 @@ def test_hybrid_family_reproduces_the_transformers_implementation(tmp_path):
     assert eng.generate([ids.tolist()], max_new=5)[0] == generate_greedy(w, ids.int(), 5)[0]
     perm = C.rotary_permutation(8, 4)
     assert perm.tolist() == [0, 1, 4, 5, 2, 3, 6, 7] and C.rotary_permutation(8, 0).tolist() == list(range(8))
+
+
+def test_llama_style_checkpoints_convert_too(tmp_path):
+    """The same decoder without per-head q / k norms (Llama, Mistral)."""
+    transformers = pytest.importorskip("transformers")
+    from orinfer_b200.engine.checkpoint import load_model
+    from orinfer_b200.ref.cpu_forward import RefKV, forward_request
+    torch.manual_seed(0)
+    cfg = transformers.LlamaConfig(hidden_size=H, num_hidden_layers=2, num_attention_heads=HEADS,
+                                   num_key_value_heads=KV, head_dim=D, vocab_size=V,
+                                   intermediate_size=FFN, rms_norm_eps=1e-6, rope_theta=10000.0,
+                                   tie_word_embeddings=True, max_position_embeddings=512,
+                                   attention_bias=False, mlp_bias=False)
+    model = transformers.LlamaForCausalLM(cfg).float().eval()
+    model.save_pretrained(tmp_path / "hf", safe_serialization=True)
+    w = load_model(C.convert(tmp_path / "hf", tmp_path / "out",
+                             formats={"attn_format": "w8", "proj_format": "w8"}))
+    assert not w.config.qk_norm and w.config.tied_embeddings and w.layers[0].q_norm is None
+    ids = torch.randint(0, V, (24,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = model(ids[None]).logits[0].float()
+    got = forward_request(w, ids.int(), 0, RefKV(2), quantized=True)
+    assert float(torch.nn.functional.cosine_similarity(got, want, dim=-1).min()) > 0.99
+    with pytest.raises(C.ConvertError, match="sliding-window"):
+        C.config_from_hf({"architectures": ["MistralForCausalLM"], "sliding_window": 4096,
+                          "num_attention_heads": 2})
