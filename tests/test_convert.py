@@ -122,7 +122,7 @@ def test_moe_conversion_and_refusals(tmp_path):
     assert torch.allclose(w.layers[0].router.float(), src["model.layers.0.mlp.gate.weight"],
                           atol=1e-3)
     bad = json.loads((tmp_path / "hf/config.json").read_text())
-    for patch, why in (({"architectures": ["LlamaForCausalLM"]}, "unsupported architecture"),
+    for patch, why in (({"architectures": ["GPT2LMHeadModel"]}, "unsupported architecture"),
                        ({"attention_bias": True}, "bias"),
                        ({"mlp_only_layers": [0]}, "mixed")):
         with pytest.raises(C.ConvertError, match=why):
