@@ -10,7 +10,7 @@ accepted and echoed.  The front end runs on the preparation pool, like chat temp
 from __future__ import annotations
 
 import dataclasses
-from typing import Any, List, Optional, Tuple
+from typing import List, Optional, Tuple
 
 from fastapi import FastAPI
 from fastapi import Request as HttpRequest

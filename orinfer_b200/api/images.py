@@ -17,7 +17,7 @@ import binascii
 import threading
 from collections import OrderedDict
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, List, Optional, Tuple
 
 from ..models import vision as V
 from .chat_codec import RequestError

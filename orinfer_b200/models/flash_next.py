@@ -13,7 +13,6 @@ python/orinfer_build/models/flash_next/reference/teacher.py): streams -> [PLE at
 
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
