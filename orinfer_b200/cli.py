@@ -723,7 +723,7 @@ def _client_run(a, url: str) -> int:
             return code
 
 
-BENCH_TOOLS = {"tokens": "token_bench", "quality": "quality", "concurrency": "concurrency", "agentic": "agentic", "startup": "startup",
+BENCH_TOOLS = {"hf-reference": "hf_reference", "tokens": "token_bench", "quality": "quality", "concurrency": "concurrency", "agentic": "agentic", "startup": "startup",
                "encoders": "encoders", "scenario": "workloads"}
 
 

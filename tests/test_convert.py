@@ -249,3 +249,28 @@ def test_llama_style_checkpoints_convert_too(tmp_path):
     with pytest.raises(C.ConvertError, match="sliding-window"):
         C.config_from_hf({"architectures": ["MistralForCausalLM"], "sliding_window": 4096,
                           "num_attention_heads": 2})
+
+
+def test_quality_probes_pair_the_library_with_the_converted_model(tmp_path, capsys):
+    """The whole comparison as a user runs it: baseline probes from transformers, candidate
+    probes from the converted model through the CLI, paired analysis."""
+    transformers = pytest.importorskip("transformers")
+    from orinfer_b200 import cli
+    torch.manual_seed(0)
+    cfg = transformers.Qwen3Config(hidden_size=H, num_hidden_layers=2, num_attention_heads=HEADS,
+                                   num_key_value_heads=KV, head_dim=D, vocab_size=V,
+                                   intermediate_size=FFN, tie_word_embeddings=False,
+                                   max_position_embeddings=512)
+    transformers.Qwen3ForCausalLM(cfg).save_pretrained(tmp_path / "hf", safe_serialization=True)
+    C.convert(tmp_path / "hf", tmp_path / "out", formats={"attn_format": "w8", "proj_format": "w8"})
+    toks = ",".join(str((7 * i + 3) % V) for i in range(20))
+    base, cand = str(tmp_path / "b.jsonl"), str(tmp_path / "c.jsonl")
+    assert cli.main(["bench", "hf-reference", str(tmp_path / "hf"), "--tokens", toks,
+                     "--jsonl", base]) == 0
+    assert cli.main(["score-model", str(tmp_path / "out"), "--device", "cpu", "--tokens", toks,
+                     "--jsonl", cand, "--query-from", base]) == 0
+    capsys.readouterr()
+    assert cli.main(["bench", "quality", "--baseline", base, "--candidate", cand]) == 0
+    rep = json.loads(capsys.readouterr().out)["aggregate"]
+    assert rep["positions"] == 19 and rep["mean_abs_probability_error"] < 0.002
+    assert rep["top3_overlap"] > 0.6 and abs(rep["delta_target_nll"]) < 0.05
