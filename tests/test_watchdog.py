@@ -46,7 +46,7 @@ def test_stalled_step_fails_the_service_and_answers_clients():
         return eng
 
     svc = Service(factory, ChatCodec(ByteTokenizer(1024), context=256, model_name="tiny"), "tiny",
-                  step_timeout_ms=2000)
+                  step_timeout_ms=4000)
     svc.start()
     with TestClient(create_app(svc)) as c:
         assert c.get("/health").status_code == 200
