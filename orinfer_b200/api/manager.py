@@ -419,7 +419,7 @@ def create_gateway_app(manager: ModelManager, sweep_s: float = 5.0):
                  "/v1/embeddings",
                  "/v1/rerank", "/rerank", "/v1/audio/transcriptions"):
         app.add_api_route(path, handler(False), methods=["POST"])
-    for path in ("/api/chat", "/api/generate", "/api/show"):
+    for path in ("/api/chat", "/api/generate", "/api/show", "/api/embed", "/api/embeddings"):
         app.add_api_route(path, handler(True), methods=["POST"])
 
     @app.get("/health")

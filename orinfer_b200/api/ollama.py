@@ -277,6 +277,41 @@ def install(app: FastAPI, service) -> None:
     async def generate(request: HttpRequest):
         return await run(request, True)
 
+    async def _embed(request: HttpRequest, legacy: bool):
+        """Ollama embedding routes on top of the native encoder pass: ``/api/embed`` takes
+        ``input`` (string or array) and answers ``embeddings`` (one vector per input);
+        the older ``/api/embeddings`` takes ``prompt`` and answers one ``embedding``."""
+        import asyncio
+        from .encoders import embeddings as native_embeddings
+        started = time.perf_counter_ns()
+        try:
+            body = await request.json()
+            if not isinstance(body, dict):
+                raise RequestError("request body must be a JSON object")
+            value = body.get("prompt") if legacy else body.get("input")
+            out = await asyncio.get_running_loop().run_in_executor(
+                None, native_embeddings, service,
+                {"input": value, "input_type": "document",
+                 **({"dimensions": body["dimensions"]} if "dimensions" in body else {})})
+        except RequestError as e:
+            return JSONResponse({"error": e.message}, status_code=e.status)
+        except (MemoryError, ValueError) as e:
+            return JSONResponse({"error": str(e)}, status_code=400)
+        vectors = [d["embedding"] for d in out["data"]]
+        if legacy:
+            return {"embedding": vectors[0]}
+        return {"model": body.get("model") or service.model_name, "embeddings": vectors,
+                "total_duration": time.perf_counter_ns() - started, "load_duration": 0,
+                "prompt_eval_count": out["usage"]["prompt_tokens"]}
+
+    @app.post("/api/embed")
+    async def embed(request: HttpRequest):
+        return await _embed(request, legacy=False)
+
+    @app.post("/api/embeddings")
+    async def embeddings_legacy(request: HttpRequest):
+        return await _embed(request, legacy=True)
+
     @app.post("/api/copy")
     async def copy(request: HttpRequest):
         return JSONResponse({"error": "aliases need the model manager (orinfer serve "

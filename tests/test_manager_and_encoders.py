@@ -190,6 +190,13 @@ def test_gateway_forwards_by_model_and_releases_leases(tmp_path):
         assert tr.status_code == 200 and "text" in tr.json()
         assert c.post("/v1/audio/transcriptions", files={"file": ("a.wav", wav.getvalue())}
                       ).status_code == 400                          # no model named
+        one = c.post("/api/embed", json={"model": "tiny", "input": ["alpha", "beta gamma"]})
+        assert one.status_code == 200 and len(one.json()["embeddings"]) == 2
+        assert len(one.json()["embeddings"][0]) == 256 and one.json()["prompt_eval_count"] > 5
+        old = c.post("/api/embeddings", json={"model": "tiny", "prompt": "alpha"})
+        assert old.status_code == 200
+        assert old.json()["embedding"] == pytest.approx(one.json()["embeddings"][0], abs=1e-6)
+        assert c.post("/api/embed", json={"model": "tiny", "input": []}).status_code == 400
         missing = c.post("/v1/chat/completions", json=dict(body, model="nope"))
         assert missing.status_code == 404 and missing.json()["error"]["code"] == "model_not_found"
         assert c.post("/api/generate", json={"model": "nope", "prompt": "x"}).status_code == 404
