@@ -177,6 +177,14 @@ def create_app(service: Service) -> FastAPI:
                                             "created": int(service.started),
                                             "owned_by": "orinfer"}]}
 
+    @app.get("/v1/models/{model_id:path}")
+    async def model(model_id: str):
+        if model_id != service.model_name:
+            return _error(404, f"model `{model_id}` is not served here", code="model_not_found",
+                          param="model")
+        return {"id": service.model_name, "object": "model", "created": int(service.started),
+                "owned_by": "orinfer"}
+
     async def _json(request: HttpRequest):
         try:
             return json.loads(await request.body())

@@ -35,6 +35,9 @@ def test_health_models_metrics(client):
     h = client.get("/health").json()
     assert h["status"] == "ready" and h["continuous_batching"] and "scheduler" in h
     assert client.get("/v1/models").json()["data"][0]["id"] == "tiny"
+    assert client.get("/v1/models/tiny").json()["object"] == "model"
+    gone = client.get("/v1/models/other")
+    assert gone.status_code == 404 and gone.json()["error"]["code"] == "model_not_found"
     r = client.get("/metrics")
     assert "orinfer_request_latency_seconds_bucket" in r.text
     assert "x-request-id" in r.headers
