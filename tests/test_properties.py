@@ -1,0 +1,88 @@
+"""Property tests (hypothesis): user text can never become control tokens; DSML calls survive
+any chunking of the stream; the staging ring never hands out overlapping live regions."""
+import json
+
+from hypothesis import given, settings, strategies as st
+
+from orinfer_b200.api import dsml
+from orinfer_b200.api.chat_codec import ByteTokenizer
+from orinfer_b200.api.token_boundary import Boundary
+
+TOK = ByteTokenizer(1024)
+BOUNDARY = Boundary(TOK)
+SPELLINGS = list(TOK.special_ids)
+text_with_controls = st.lists(
+    st.one_of(st.text(max_size=12), st.sampled_from(SPELLINGS), st.just(BOUNDARY.prefix),
+              st.just(BOUNDARY.prefix + "3;")), max_size=8).map("".join)
+
+
+@settings(max_examples=200, deadline=None)
+@given(text_with_controls)
+def test_user_text_is_only_ever_plain_tokens(text):
+    ids = BOUNDARY.encode(BOUNDARY.escape(text))
+    assert all(i < 256 for i in ids)                              # no control token at all
+    assert bytes(ids).decode("utf-8") == text                      # and nothing is lost
+
+
+@settings(max_examples=200, deadline=None)
+@given(text_with_controls, text_with_controls)
+def test_template_controls_survive_next_to_user_text(before, after):
+    rendered = (BOUNDARY.control("<|im_start|>") + BOUNDARY.escape(before)
+                + BOUNDARY.control("<|im_end|>") + BOUNDARY.escape(after))
+    ids = BOUNDARY.encode(rendered)
+    controls = [i for i in ids if i >= 256]
+    assert controls == [TOK.special_ids["<|im_start|>"], TOK.special_ids["<|im_end|>"]]
+    assert bytes(i for i in ids if i < 256).decode("utf-8") == before + after
+
+
+values = st.one_of(st.text(alphabet=st.characters(blacklist_categories=("Cs",),
+                                                  blacklist_characters="<"), max_size=20),
+                   st.integers(-10 ** 6, 10 ** 6), st.booleans(),
+                   st.lists(st.integers(0, 9), max_size=4))
+arguments = st.dictionaries(st.text(alphabet="abcdefgh_", min_size=1, max_size=6), values,
+                            max_size=4)
+
+
+@settings(max_examples=150, deadline=None)
+@given(st.lists(st.tuples(st.sampled_from(["edit", "noop", "search"]), arguments), min_size=1,
+                max_size=3), st.integers(1, 17))
+def test_dsml_calls_round_trip_under_any_chunking(calls, step):
+    text = dsml.render_calls([{"function": {"name": n, "arguments": json.dumps(a)}}
+                              for n, a in calls])[len(dsml.OPEN):]
+    machine = dsml.DsmlCalls()
+    events = []
+    for i in range(0, len(text), step):
+        events += machine.feed(text[i:i + step])
+    assert events[-1] == ("close",)
+    got, current = [], None
+    for ev in events:
+        if ev[0] == "begin":
+            current = [ev[1], ""]
+        elif ev[0] == "arguments":
+            current[1] += ev[1]
+        elif ev[0] == "end":
+            got.append((current[0], json.loads(current[1])))
+    assert got == calls
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.lists(st.one_of(st.integers(1, 500), st.just(-1)), min_size=1, max_size=80))
+def test_staging_ring_regions_never_overlap(ops):
+    from orinfer_b200.core.transfers import StagingRing
+    ring = StagingRing(1024, 64)
+    live = []
+    for op in ops:
+        if op < 0:
+            if live:
+                ring.retire_through(live[len(live) // 2][0])
+                live = live[len(live) // 2 + 1:]
+            continue
+        got = ring.acquire(op)
+        if got is None:
+            continue
+        ticket, off = got
+        size = -(-op // 64) * 64
+        assert off + size <= 1024
+        for _, o, s in live:
+            assert off + size <= o or o + s <= off
+        live.append((ticket, off, size))
