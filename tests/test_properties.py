@@ -86,3 +86,37 @@ def test_staging_ring_regions_never_overlap(ops):
         for _, o, s in live:
             assert off + size <= o or o + s <= off
         live.append((ticket, off, size))
+
+
+@settings(max_examples=150, deadline=None)
+@given(st.integers(1, 500), st.integers(1, 9), st.data())
+def test_row_plans_partition_unique_rows_by_owner(table_rows, ranks, data):
+    import numpy as np
+    from orinfer_b200.core.host_rows import RowPlan, row_shard
+    ids = data.draw(st.lists(st.integers(0, table_rows - 1), max_size=60))
+    plan = RowPlan.build(ids, table_rows, ranks)
+    assert plan.rows[plan.restore].tolist() == ids if ids else plan.rows.size == 0
+    assert len(set(plan.rows.tolist())) == plan.rows.size == len(set(ids))
+    seen = []
+    for r in range(ranks):
+        first, count = row_shard(table_rows, ranks, r)
+        mine = plan.for_rank(r).tolist()
+        assert all(first <= x < first + count for x in mine)
+        seen += mine
+    assert seen == plan.rows.tolist()
+
+
+@settings(max_examples=100, deadline=None)
+@given(st.lists(st.integers(0, 15), min_size=1, max_size=30), st.integers(0, 29))
+def test_ngram_addresses_do_not_depend_on_the_chunk_cut(tokens, cut):
+    import numpy as np
+    from orinfer_b200.core.host_rows import HashLayer, NgramHasher
+    h = NgramHasher(list(range(16)), 0, [15], 2, [HashLayer(0, 5 + 7 + 11 + 13 + 17 + 19,
+                                                            [3, 5, 7, 9], [5, 7, 11, 13, 17, 19])])
+    cut = min(cut, len(tokens))
+    whole, valid = h.hash([], tokens)
+    a, va = h.hash([], tokens[:cut])
+    b, vb = h.hash(tokens[:cut], tokens[cut:])
+    assert np.array_equal(np.concatenate([a, b]), whole)
+    assert np.array_equal(np.concatenate([va, vb]), valid)
+    assert valid.tolist() == [t != 15 for t in tokens]
