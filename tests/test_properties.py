@@ -120,3 +120,46 @@ def test_ngram_addresses_do_not_depend_on_the_chunk_cut(tokens, cut):
     assert np.array_equal(np.concatenate([a, b]), whole)
     assert np.array_equal(np.concatenate([va, vb]), valid)
     assert valid.tolist() == [t != 15 for t in tokens]
+
+
+@settings(max_examples=200, deadline=None)
+@given(st.integers(8, 4000), st.integers(8, 4000))
+def test_resize_geometry_stays_on_the_grid_and_in_budget(h, w):
+    from orinfer_b200.models import vision as V
+    if max(h, w) / min(h, w) > 200:
+        return
+    lo, hi = 64 * 64, 1024 * 1024
+    nh, nw = V.smart_resize(h, w, 32, lo, hi)
+    assert nh % 32 == 0 and nw % 32 == 0 and nh >= 32 and nw >= 32
+    assert nh * nw <= hi or min(nh, nw) == 32              # very thin images keep one row of patches
+    assert nh * nw >= lo
+    assert abs((nh / nw) / (h / w) - 1) < 0.35 or min(nh, nw) <= 64    # rounding to the grid
+
+
+@settings(max_examples=100, deadline=None)
+@given(st.lists(st.tuples(st.integers(0, 6), st.integers(1, 4), st.integers(1, 4)), max_size=4),
+       st.integers(0, 6))
+def test_rotary_positions_of_prompts_with_images(images, tail):
+    """(text run, merged grid height, merged grid width) per image, then a text tail."""
+    import numpy as np
+    from orinfer_b200.models import vision as V
+    spec = V.VisionSpec(hidden=8, image_token_id=9, vision_start_token_id=7, vision_end_token_id=8)
+    tokens, spans, grids = [], [], []
+    for run, gh, gw in images:
+        tokens += [1] * run
+        spans.append((len(tokens), len(tokens) + gh * gw))
+        tokens += [9] * (gh * gw)
+        grids.append((gh * 2, gw * 2))
+    tokens += [1] * tail
+    pos, delta = V.mrope_positions(spec, tokens, spans, grids)
+    assert pos.shape == (3, len(tokens)) and delta <= 0
+    assert np.all(np.diff(pos[0]) >= 0)                           # time never runs backwards
+    text = np.array([t != 9 for t in tokens], dtype=bool)
+    assert np.all(pos[0][text] == pos[1][text]) and np.all(pos[1][text] == pos[2][text])
+    if not images:
+        assert pos[0].tolist() == list(range(len(tokens))) and delta == 0
+    for (a, b), (gh, gw) in zip(spans, grids):
+        assert len(set(pos[0, a:b].tolist())) == 1                # one time step per image
+        cells = set(zip(pos[1, a:b].tolist(), pos[2, a:b].tolist()))
+        assert len(cells) == b - a                                # every feature its own cell
+    assert int(pos.max(initial=-1)) + 1 == len(tokens) + delta    # where decoding continues
