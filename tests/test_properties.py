@@ -163,3 +163,22 @@ def test_rotary_positions_of_prompts_with_images(images, tail):
         cells = set(zip(pos[1, a:b].tolist(), pos[2, a:b].tolist()))
         assert len(cells) == b - a                                # every feature its own cell
     assert int(pos.max(initial=-1)) + 1 == len(tokens) + delta    # where decoding continues
+
+
+@settings(max_examples=25, deadline=None)
+@given(st.integers(1, 40), st.sampled_from([(1, 1), (1, 2), (2, 4)]), st.sampled_from([8, 16]),
+       st.integers(1, 20), st.integers(0, 2 ** 31 - 1))
+def test_chunkwise_gated_delta_rule_is_the_sequential_one(t, heads, d, chunk, seed):
+    import torch
+    from orinfer_b200.ref import gdn_ref as G
+    g = torch.Generator().manual_seed(seed)
+    hk, hv = heads
+    q = torch.nn.functional.normalize(torch.randn(t, hk, d, generator=g), dim=-1)
+    k = torch.nn.functional.normalize(torch.randn(t, hk, d, generator=g), dim=-1)
+    v = torch.randn(t, hv, d, generator=g)
+    decay = -torch.rand(t, hv, generator=g)
+    beta = torch.rand(t, hv, generator=g)
+    s0 = torch.randn(hv, d, d, generator=g) * 0.2
+    o1, s1 = G.recurrence(q, k, v, decay, beta, s0)
+    o2, s2 = G.recurrence_chunked(q, k, v, decay, beta, s0, chunk)
+    assert torch.allclose(o1, o2, atol=5e-5, rtol=1e-4) and torch.allclose(s1, s2, atol=5e-5, rtol=1e-4)
