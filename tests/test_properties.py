@@ -182,3 +182,51 @@ def test_chunkwise_gated_delta_rule_is_the_sequential_one(t, heads, d, chunk, se
     o1, s1 = G.recurrence(q, k, v, decay, beta, s0)
     o2, s2 = G.recurrence_chunked(q, k, v, decay, beta, s0, chunk)
     assert torch.allclose(o1, o2, atol=5e-5, rtol=1e-4) and torch.allclose(s1, s2, atol=5e-5, rtol=1e-4)
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.lists(st.tuples(st.sampled_from(["insert", "match", "release", "evict"]),
+                          st.integers(0, 5), st.integers(1, 4)), min_size=1, max_size=60))
+def test_prefix_cache_never_evicts_a_page_in_use_and_matches_what_it_indexed(ops):
+    """Random traffic on the radix prefix cache (4-token pages, six prompt families that share
+    prefixes): a page handed out by a match is never evicted while held, a match returns pages
+    that were indexed for exactly those tokens, and every adopted page is evicted at most once."""
+    from orinfer_b200.core.prefix import RadixPrefixCache
+    cache = RadixPrefixCache(page_tokens=4)
+    family = lambda f, pages: [(f % 3) * 100 + i // 4 if i < 4 else f * 1000 + i // 4
+                               for i in range(pages * 4)]     # families share their first page
+    page_of = {}                      # (tuple of tokens up to a page end) -> page id
+    held = {}                         # node id -> leases
+    handles = []                      # node-id lists still to release
+    evicted, next_page = set(), [1]
+    for op, f, pages in ops:
+        toks = family(f, pages)
+        if op == "insert":
+            ids = list(range(next_page[0], next_page[0] + pages))
+            next_page[0] += pages
+            adopted, _nodes = cache.insert(toks, ids)
+            for i, (took, pg) in enumerate(zip(adopted, ids)):
+                if took:
+                    page_of[tuple(toks[:(i + 1) * 4])] = pg
+        elif op == "match":
+            nodes, got = cache.match(toks)
+            for i, pg in enumerate(got):
+                assert page_of[tuple(toks[:(i + 1) * 4])] == pg
+                assert pg not in evicted
+            for n in nodes:
+                held[n] = held.get(n, 0) + 1
+            if nodes:
+                handles.append(nodes)
+        elif op == "release" and handles:
+            nodes = handles.pop(f % len(handles))
+            cache.release(nodes)
+            for n in nodes:
+                held[n] -= 1
+        elif op == "evict":
+            for node, pg in cache.evict(pages):
+                assert held.get(node, 0) == 0, "evicted a page that a request still reads"
+                assert pg not in evicted
+                evicted.add(pg)
+                page_of = {k: v for k, v in page_of.items() if v != pg}
+    st_ = cache.statistics()
+    assert st_.device_pages == len(page_of) and st_.evicted == len(evicted)

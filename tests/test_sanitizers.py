@@ -33,7 +33,7 @@ def test_policy_core_is_clean_under_asan_and_ubsan():
     res = _run("asan", runtime,
                ["tests/test_sampling_core.py", "tests/test_prefix_cache.py",
                 "tests/test_policy_core.py", "tests/test_weight_io.py",
-                "tests/test_host_rows.py", "tests/test_transfers.py"],
+                "tests/test_host_rows.py", "tests/test_transfers.py", "tests/test_properties.py"],
                {"ASAN_OPTIONS": "detect_leaks=0:halt_on_error=1:exitcode=97",
                 "UBSAN_OPTIONS": "halt_on_error=1:print_stacktrace=1"})
     tail = (res.stdout + res.stderr)[-3000:]
