@@ -14,78 +14,137 @@ namespace orinfer {
 
 constexpr int ATTN_WARPS = 4;
 
-template <int D, int REP>
+__device__ __forceinline__ void unpack16(const int4& raw, float (&f)[16]) {
+  const int w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[4 * i + 0] = static_cast<float>(static_cast<signed char>(w[i] & 0xff));
+    f[4 * i + 1] = static_cast<float>(static_cast<signed char>((w[i] >> 8) & 0xff));
+    f[4 * i + 2] = static_cast<float>(static_cast<signed char>((w[i] >> 16) & 0xff));
+    f[4 * i + 3] = static_cast<float>(w[i] >> 24);
+  }
+}
+
+// One CTA per (row, group of RPC query heads sharing a KV head, key split).  A key's D INT8
+// channels are covered by D/16 lanes with one 16-byte load each, so a warp takes 32/(D/16)
+// keys per step (4 at D = 128) and the four warps interleave; every lane group keeps its own
+// online-softmax state, merged by shuffles and then across warps in shared memory.
+template <int D, int RPC>
 __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_rows_kernel(
     const __half* __restrict__ q, const __half* __restrict__ gate, const int* __restrict__ row_req,
     const int* __restrict__ row_pos, const int* __restrict__ page_table, int max_pages,
     const int8_t* __restrict__ kc, const int8_t* __restrict__ vc, const __half* __restrict__ ks,
     const __half* __restrict__ vs, __half* __restrict__ out, int qh, int kvh, int splits,
-    float* __restrict__ scratch) {
-  constexpr int EPL = D / 32;
+    float* __restrict__ scratch, int rep) {
+  constexpr int LPK = D / 16;                  // lanes per key
+  constexpr int KPW = 32 / LPK;                // keys per warp step
   constexpr int GROUPS = D / 64;
-  const int row = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
+  const int row = blockIdx.x, split = blockIdx.z;
+  const int hgroups = rep / RPC;               // CTAs per KV head
+  const int h = blockIdx.y / hgroups;          // KV head
+  const int head0 = h * rep + (blockIdx.y % hgroups) * RPC;   // first query head of this CTA
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane % LPK, kslot = lane / LPK;
   const int req = row_req[row];
   const int kv_len = row_pos[row] + 1;
   const int per = (kv_len + splits - 1) / splits;
   const int k_lo = split * per, k_hi = min(kv_len, k_lo + per);
-  const int group = (lane * EPL) / 64;
+  const int group = (sub * 16) / 64;
   const float qscale = rsqrtf(static_cast<float>(D)) * 1.4426950408889634f;
 
-  float qv[REP][EPL], acc[REP][EPL], mx[REP], sum[REP];
+  // query heads (pre-scaled, FP32) in shared memory: every lane group reads the same slice,
+  // so the loads are broadcasts, and the registers go to the accumulators
+  __shared__ __align__(16) float s_q[RPC][D];
+  for (int i = threadIdx.x; i < RPC * D; i += blockDim.x)
+    s_q[i / D][i % D] =
+        __half2float(q[(static_cast<size_t>(row) * qh + head0 + i / D) * D + i % D]) * qscale;
+  float acc[RPC][16], mx[RPC], sum[RPC];
 #pragma unroll
-  for (int r = 0; r < REP; ++r) {
-    const __half* qp = q + (static_cast<size_t>(row) * qh + h * REP + r) * D + lane * EPL;
+  for (int r = 0; r < RPC; ++r) {
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) {
-      qv[r][e] = __half2float(qp[e]) * qscale;
-      acc[r][e] = 0.f;
-    }
+    for (int e = 0; e < 16; ++e) acc[r][e] = 0.f;
     mx[r] = -INFINITY;
     sum[r] = 0.f;
   }
+  __syncthreads();
   const int* pages = page_table + static_cast<size_t>(req) * max_pages;
-  for (int key = k_lo + warp; key < k_hi; key += ATTN_WARPS) {
-    const int page = pages[key >> 7];
-    const size_t slot = (static_cast<size_t>(page) * 128 + (key & 127)) * kvh + h;
-    const int8_t* kp = kc + slot * D + lane * EPL;
-    const int8_t* vp = vc + slot * D + lane * EPL;
-    const float ksc = __half2float(ks[slot * GROUPS + group]);
-    const float vsc = __half2float(vs[slot * GROUPS + group]);
-    float kf[EPL], vf[EPL];
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) {
-      kf[e] = static_cast<float>(kp[e]) * ksc;
-      vf[e] = static_cast<float>(vp[e]) * vsc;
+  // software pipeline: the loads of the next key are in flight while this one is used
+  int4 kraw = make_int4(0, 0, 0, 0), vraw = kraw;
+  float ksc = 0.f, vsc = 0.f;
+  auto fetch = [&](int key) {
+    if (key < k_hi) {
+      const int page = pages[key >> 7];
+      const size_t slot = (static_cast<size_t>(page) * 128 + (key & 127)) * kvh + h;
+      kraw = __ldg(reinterpret_cast<const int4*>(kc + slot * D + sub * 16));
+      vraw = __ldg(reinterpret_cast<const int4*>(vc + slot * D + sub * 16));
+      ksc = __half2float(ks[slot * GROUPS + group]);
+      vsc = __half2float(vs[slot * GROUPS + group]);
     }
+  };
+  int key = k_lo + warp * KPW + kslot;
+  fetch(key);
+  for (; key < k_hi; key += ATTN_WARPS * KPW) {
+    float kf[16], vf[16];
+    unpack16(kraw, kf);
+    unpack16(vraw, vf);
+    const float kscale = ksc, vscale = vsc;
+    fetch(key + ATTN_WARPS * KPW);
 #pragma unroll
-    for (int r = 0; r < REP; ++r) {
+    for (int r = 0; r < RPC; ++r) {
       float d = 0.f;
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) d += qv[r][e] * kf[e];
-      d = warp_sum(d);
+      for (int e4 = 0; e4 < 4; ++e4) {
+        const float4 qq = *reinterpret_cast<const float4*>(&s_q[r][sub * 16 + e4 * 4]);
+        d += qq.x * kf[e4 * 4] + qq.y * kf[e4 * 4 + 1] + qq.z * kf[e4 * 4 + 2] +
+             qq.w * kf[e4 * 4 + 3];
+      }
+      d *= kscale;
+#pragma unroll
+      for (int o = 1; o < LPK; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
       const float mnew = fmaxf(mx[r], d);
       const float corr = exp2f(mx[r] - mnew);
       const float p = exp2f(d - mnew);
       sum[r] = sum[r] * corr + p;
+      const float pv = p * vscale;
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) acc[r][e] = acc[r][e] * corr + p * vf[e];
+      for (int e = 0; e < 16; ++e) acc[r][e] = acc[r][e] * corr + pv * vf[e];
       mx[r] = mnew;
     }
   }
-  __shared__ float s_m[ATTN_WARPS][REP], s_l[ATTN_WARPS][REP];
-  __shared__ float s_o[ATTN_WARPS][REP][D];
+  // lanes that only differ in kslot hold states of disjoint key sets: merge them
 #pragma unroll
-  for (int r = 0; r < REP; ++r) {
-    if (lane == 0) {
-      s_m[warp][r] = mx[r];
-      s_l[warp][r] = sum[r];
+  for (int o = LPK; o < 32; o <<= 1) {
+#pragma unroll
+    for (int r = 0; r < RPC; ++r) {
+      const float mo = __shfl_xor_sync(0xffffffffu, mx[r], o);
+      const float lo = __shfl_xor_sync(0xffffffffu, sum[r], o);
+      const float mnew = fmaxf(mx[r], mo);
+      const float fa = mx[r] == -INFINITY ? 0.f : exp2f(mx[r] - mnew);
+      const float fb = mo == -INFINITY ? 0.f : exp2f(mo - mnew);
+      sum[r] = sum[r] * fa + lo * fb;
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const float ao = __shfl_xor_sync(0xffffffffu, acc[r][e], o);
+        acc[r][e] = acc[r][e] * fa + ao * fb;
+      }
+      mx[r] = mnew;
     }
+  }
+  __shared__ float s_m[ATTN_WARPS][RPC], s_l[ATTN_WARPS][RPC];
+  __shared__ float s_o[ATTN_WARPS][RPC][D];
+  if (kslot == 0) {
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) s_o[warp][r][lane * EPL + e] = acc[r][e];
+    for (int r = 0; r < RPC; ++r) {
+      if (sub == 0) {
+        s_m[warp][r] = mx[r];
+        s_l[warp][r] = sum[r];
+      }
+#pragma unroll
+      for (int e = 0; e < 16; ++e) s_o[warp][r][sub * 16 + e] = acc[r][e];
+    }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < REP * D; i += blockDim.x) {
+  for (int i = threadIdx.x; i < RPC * D; i += blockDim.x) {
     const int r = i / D, d = i % D;
     float m = -INFINITY;
 #pragma unroll
@@ -97,7 +156,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_rows_kernel(
       l += s_l[w][r] * f;
       o += s_o[w][r][d] * f;
     }
-    const int head = h * REP + r;
+    const int head = head0 + r;
     if (splits == 1) {
       float v = l > 0.f ? o / l : 0.f;
       if (gate) {
@@ -141,15 +200,15 @@ __global__ void attn_merge_kernel(const float* __restrict__ scratch,
   }
 }
 
-template <int D, int REP>
+template <int D, int RPC>
 static int launch_attn(const __half* q, const __half* gate, const int* row_req, const int* row_pos,
                        const int* page_table, int max_pages, const int8_t* kc, const int8_t* vc,
                        const __half* ks, const __half* vs, __half* out, int rows, int qh, int kvh,
-                       int splits, float* scratch, cudaStream_t stream) {
-  dim3 grid(rows, kvh, splits);
-  attn_rows_kernel<D, REP><<<grid, ATTN_WARPS * 32, 0, stream>>>(
+                       int rep, int splits, float* scratch, cudaStream_t stream) {
+  dim3 grid(rows, kvh * (rep / RPC), splits);
+  attn_rows_kernel<D, RPC><<<grid, ATTN_WARPS * 32, 0, stream>>>(
       q, gate, row_req, row_pos, page_table, max_pages, kc, vc, ks, vs, out, qh, kvh, splits,
-      scratch);
+      scratch, rep);
   if (splits > 1)
     attn_merge_kernel<D><<<dim3(rows, qh), D < 128 ? 64 : 128, 0, stream>>>(scratch, gate, out, qh,
                                                                            splits);
@@ -173,13 +232,15 @@ extern "C" int orinfer_attention(const __half* q, const __half* gate, const int*
   if (rows <= 0) return 0;
   if (splits < 1 || (splits > 1 && scratch == nullptr) || kvh <= 0 || qh % kvh) return -1;
   const int rep = qh / kvh;
-#define CASE(DD, RR)                                                                         \
-  if (head_dim == DD && rep == RR)                                                           \
-    return launch_attn<DD, RR>(q, gate, row_req, row_pos, page_table, max_pages, kc, vc, ks, \
-                               vs, out, rows, qh, kvh, splits, scratch, stream);
-  CASE(64, 1) CASE(64, 2) CASE(64, 4) CASE(64, 8)
-  CASE(128, 1) CASE(128, 2) CASE(128, 4) CASE(128, 5) CASE(128, 8)
-  CASE(256, 4) CASE(256, 8)
+  // query heads per CTA: all heads of a KV head up to 5; 8 run as two groups of 4 (their
+  // accumulators would not fit the register file)
+#define CASE(DD, RR, RPC)                                                                     \
+  if (head_dim == DD && rep == RR)                                                            \
+    return launch_attn<DD, RPC>(q, gate, row_req, row_pos, page_table, max_pages, kc, vc, ks, \
+                                vs, out, rows, qh, kvh, rep, splits, scratch, stream);
+  CASE(64, 1, 1) CASE(64, 2, 2) CASE(64, 4, 4) CASE(64, 8, 4)
+  CASE(128, 1, 1) CASE(128, 2, 2) CASE(128, 4, 4) CASE(128, 5, 5) CASE(128, 8, 4)
+  CASE(256, 1, 1) CASE(256, 2, 2) CASE(256, 4, 4) CASE(256, 8, 4)
 #undef CASE
   return -1;
 }

@@ -15,7 +15,17 @@ namespace orinfer {
 // can wait): 0 = ok, otherwise (code << 16) | detail of the first failed bounded
 // wait or rejected index.  Read back with orinfer_read_status().
 
+// Bounded waits give up after status[2] * 1024 clock cycles (set at start-up and by
+// orinfer_set_wait_limit_us; about one second by default); kernels that get no status pointer
+// use the default.
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;   // about one second
+constexpr int STATUS_LIMIT_WORD = 2;
+
+__device__ __forceinline__ long long wait_limit(const int* status) {
+  if (status == nullptr) return WAIT_LIMIT_CYCLES;
+  const int k = *reinterpret_cast<const volatile int*>(status + STATUS_LIMIT_WORD);
+  return k > 0 ? static_cast<long long>(k) << 10 : WAIT_LIMIT_CYCLES;
+}
 
 enum StatusCode : int {
   STATUS_OK = 0,
@@ -65,10 +75,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code,
                                           int detail) {
   if (mbar_try_wait(bar, parity)) return true;
-  const long long start = clock64();
+  const long long start = clock64(), limit = wait_limit(status);
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - start > WAIT_LIMIT_CYCLES) {
+    if (clock64() - start > limit) {
       report_status(status, code, detail);
+      return false;
+    }
+  }
+  return true;
+}
+// Same, for kernels whose roles must all leave when one of them gave up: `abort` is a word
+// in shared memory that the first failed wait sets and every other wait polls.
+__device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, int* status,
+                                                    int code, int detail, volatile int* abort) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64(), limit = wait_limit(status);
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort != 0) return false;
+    if (clock64() - start > limit) {
+      report_status(status, code, detail);
+      *abort = 1;
       return false;
     }
   }
@@ -229,73 +255,96 @@ __device__ __forceinline__ uint32_t swz128(uint32_t row, uint32_t chunk) {
 }
 
 // ---------------------------------------------------------------- E8P decode
-// Global table (2 KiB): pos[index] = {lo, hi}, four packed bytes each, holding basis + 24,
-// so every byte is in 14..34 and whole-word arithmetic never carries between bytes; the
-// negated coordinates are 48 - pos, again without borrows.  A code's sign byte picks
-// pos/neg per coordinate with one PRMT per half; the selectors come from a 256-entry
-// table indexed by the sign byte.  The +/-1 parity shift and the re-centring are one
-// constant added afterwards, and XOR 0x80 turns the biased byte into two's complement.
+// A 16-bit code is (basis index << 8) | sign byte.  Two 256-entry tables of 32-bit words hold
+// eight 4-bit fields each, one per coordinate: field 2j is coordinate j, field 2j+1 is
+// coordinate 4+j, so that `v & 0x0f0f0f0f` and `(v >> 4) & 0x0f0f0f0f` are the two groups
+// of four coordinates as bytes in k order.
+//   e2[index]: 2*u per coordinate, u = (basis + 14) / 4 in 1..6; negating a coordinate is
+//              u -> 7 - u = u ^ 7
+//   sg[signs]: 0xE per flipped coordinate, plus (1 - parity) in bit 0 of every field
+//   v = e2[index] ^ sg[signs] = 2*(u ^ 7*flip) + (1 - parity)   and the decoded coordinate
+//   is 2*v - 15 (the +/-1 parity shift is folded into bit 0).
+// One lookup pair and one XOR decode a code; the formats then combine whole words:
+//   Q4 weight 4*c0 + c1 = 8*v0 + 2*v1 - 75,   Q2 weight = 2*v - 15.
 struct E8pTables {
-  uint2 pos[256];
+  uint32_t e2[256];
+  uint32_t sg[256];
 };
 
-// Shared-memory working copy: the value table plus PRMT selectors per sign byte
-// (low half-word: coordinates 0-3, high half-word: coordinates 4-7).
-struct E8pSmem {
-  uint2 pos[256];
-  uint32_t sel[256];
+// Shared-memory working copy: COPIES replicas interleaved word by word, lane l reads replica
+// l % COPIES.  The lookups of a warp are random in the entry index; with one copy they
+// collide on the 32 banks about 3.5-fold, with 8 copies about 2-fold, with 32 copies never.
+template <int COPIES>
+struct E8pLut {
+  uint32_t e2[256 * COPIES];
+  uint32_t sg[256 * COPIES];
 };
 
-// Host-side runtime singletons (runtime.cu): device status word and decode tables.
-int* runtime_status_ptr();
-// INT32 partial accumulators of split-K GEMMs: [splits][M][N], allocated once at start-up so
-// that no launch ever allocates (captured graphs keep the address).
-constexpr size_t SPLITK_WORKSPACE_BYTES = 96ull << 20;
-int* runtime_splitk_workspace();
-const E8pTables* runtime_e8p_tables();
-cudaError_t runtime_ensure_init();
-
-__device__ __forceinline__ void e8p_smem_init(E8pSmem* sm, const E8pTables* __restrict__ g,
-                                              int tid, int nthreads) {
-  for (int i = tid; i < 256; i += nthreads) {
-    sm->pos[i] = g->pos[i];
-    const uint32_t t = static_cast<uint32_t>(i) ^ (__popc(i) & 1u), t2 = t >> 2;
-    // coordinate c flips with bit {0,4,1,5,2,6,3,7}[c]; nibble j of a PRMT selector is
-    // j (take the "pos" byte) or j + 4 (take the "neg" byte)
-    const uint32_t lo = 0x3210u | ((t & 0x11u) << 2) | ((t & 0x22u) << 9);
-    const uint32_t hi = 0x3210u | ((t2 & 0x11u) << 2) | ((t2 & 0x22u) << 9);
-    sm->sel[i] = lo | (hi << 16);
+template <int COPIES>
+__device__ __forceinline__ void e8p_lut_init(E8pLut<COPIES>* sm, const E8pTables* __restrict__ g,
+                                             int tid, int nthreads) {
+  static_assert(COPIES % 4 == 0, "filled with 16-byte stores");
+  constexpr int PER = COPIES / 4;                       // 16-byte stores per entry
+  for (int j = tid; j < 256 * PER; j += nthreads) {
+    const int i = j / PER;
+    const uint32_t a = g->e2[i], b = g->sg[i];
+    reinterpret_cast<uint4*>(sm->e2)[j] = make_uint4(a, a, a, a);
+    reinterpret_cast<uint4*>(sm->sg)[j] = make_uint4(b, b, b, b);
   }
 }
 
-// -> biased coordinate bytes (+/-basis + 24) and the parity bit of one 16-bit code
-__device__ __forceinline__ void e8p_select(uint32_t code, const E8pSmem* __restrict__ sm,
-                                           uint32_t& lo, uint32_t& hi, uint32_t& par) {
-  const uint32_t s = code & 0xffu;
-  par = __popc(s) & 1u;
-  const uint2 e = sm->pos[(code >> 8) & 0xffu];
-  const uint32_t sl = sm->sel[s];
-  lo = __byte_perm(e.x, 0x30303030u - e.x, sl);
-  hi = __byte_perm(e.y, 0x30303030u - e.y, sl >> 16);
+// The 4-bit fields v of the code in the low (HALF = 0) or high (HALF = 1) half of `word`.
+template <int COPIES, int HALF>
+__device__ __forceinline__ uint32_t e8p_fields(uint32_t word, const E8pLut<COPIES>* __restrict__ sm,
+                                               int copy) {
+  const uint32_t idx = __byte_perm(word, 0, HALF ? 0x4443 : 0x4441);
+  const uint32_t sgn = __byte_perm(word, 0, HALF ? 0x4442 : 0x4440);
+  return sm->e2[idx * COPIES + copy] ^ sm->sg[sgn * COPIES + copy];
 }
 
-// One 16-bit code -> eight INT8 weights  (+/-basis) + (1 - 2*parity).
-__device__ __forceinline__ uint2 e8p_decode8(uint32_t code, const E8pSmem* __restrict__ sm) {
-  uint32_t lo, hi, par;
-  e8p_select(code, sm, lo, hi, par);
-  const uint32_t cw = 0x69696969u - par * 0x02020202u;          // 128 - 24 + shift
-  return make_uint2((lo + cw) ^ 0x80808080u, (hi + cw) ^ 0x80808080u);
+constexpr uint32_t E8P_NIB = 0x0f0f0f0fu;
+
+// One Q4 word (coarse U16 low, residual U16 high) -> eight INT8 weights 4*c0 + c1.
+template <int COPIES>
+__device__ __forceinline__ uint2 e8p_decode_q4(uint32_t word, const E8pLut<COPIES>* __restrict__ sm,
+                                               int copy) {
+  const uint32_t v0 = e8p_fields<COPIES, 0>(word, sm, copy);
+  const uint32_t v1 = e8p_fields<COPIES, 1>(word, sm, copy);
+  // biased byte 8*v0 + 2*v1 + (128 - 75) is in 73..183: no carries; XOR 0x80 -> two's complement
+  uint32_t lo = (v0 & E8P_NIB) * 8u + 0x35353535u;
+  lo = ((v1 & E8P_NIB) * 2u + lo) ^ 0x80808080u;
+  uint32_t hi = ((v0 >> 4) & E8P_NIB) * 8u + 0x35353535u;
+  hi = (((v1 >> 4) & E8P_NIB) * 2u + hi) ^ 0x80808080u;
+  return make_uint2(lo, hi);
 }
 
-// One Q4 word (coarse U16 low, residual U16 high) -> eight INT8 weights 4*q0 + q1.
-__device__ __forceinline__ uint2 e8p_decode_q4(uint32_t word, const E8pSmem* __restrict__ sm) {
-  uint32_t l0, h0, p0, l1, h1, p1;
-  e8p_select(word & 0xffffu, sm, l0, h0, p0);
-  e8p_select(word >> 16, sm, l1, h1, p1);
-  // 4*(b0+24) + (b1+24) + c = 4*q0 + q1 + 128  with  c = 128 - 120 + 4*s0 + s1
-  const uint32_t cw = 0x0d0d0d0du - p0 * 0x08080808u - p1 * 0x02020202u;
-  return make_uint2(((l0 << 2) + l1 + cw) ^ 0x80808080u, ((h0 << 2) + h1 + cw) ^ 0x80808080u);
+// One Q2 code (HALF of `word`) -> eight INT8 weights 2*v - 15.
+template <int COPIES, int HALF>
+__device__ __forceinline__ uint2 e8p_decode8(uint32_t word, const E8pLut<COPIES>* __restrict__ sm,
+                                             int copy) {
+  const uint32_t v = e8p_fields<COPIES, HALF>(word, sm, copy);
+  return make_uint2(((v & E8P_NIB) * 2u + 0x71717171u) ^ 0x80808080u,
+                    (((v >> 4) & E8P_NIB) * 2u + 0x71717171u) ^ 0x80808080u);
 }
+
+// Host-side runtime state, one set per device (runtime.cu): the status word that bounded
+// waits report into, the decode tables, and start-up workspaces (no launch ever allocates,
+// so captured graphs keep the addresses).  The accessors return the current device's set.
+int* runtime_status_ptr();
+// INT32 partial accumulators of split-K GEMMs: [splits][M][N].
+constexpr size_t SPLITK_WORKSPACE_BYTES = 96ull << 20;
+int* runtime_splitk_workspace();
+// Zero-initialised INT32 accumulators [8][GEMV_WS_COLS] + tickets of the K-split GEMV; every
+// launch leaves them zero again.
+constexpr int GEMV_WS_COLS = 1 << 18;
+constexpr int GEMV_WS_TICKETS = 1024;
+int* runtime_gemv_workspace();
+const E8pTables* runtime_e8p_tables();
+cudaError_t runtime_ensure_init();
+// True the first time it is called for (current device, slot); kernels use it to set their
+// dynamic shared-memory attribute once per device.
+bool runtime_first_use(int slot);
+int runtime_new_slot();
 
 // ---------------------------------------------------------------- math
 __device__ __forceinline__ float warp_sum(float v) {

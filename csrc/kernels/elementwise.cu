@@ -6,10 +6,14 @@
 // activation_quantization (kernels/cuda/operators/op30_activation_quantization.py:22),
 // full_prepare_mrope_int8 (kernels/cuda/model/kv_int8.py:63) and greedy_partials /
 // greedy_merge (kernels/cuda/model/greedy.py:11,83).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "api.h"
 #include "argmax_kernels.cuh"
 #include "tp_comm.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace orinfer {
 
@@ -49,20 +53,44 @@ __device__ __forceinline__ float block_reduce(float v, float* red, bool is_max) 
   return r;
 }
 
-// One CTA per row.  row buffer (K floats) lives in dynamic shared memory.
+// One CTA per row, or (CL > 1, launches of a few rows) a thread-block cluster of CL CTAs per
+// row: each CTA of the cluster takes a contiguous run of 128-channel blocks, and the two
+// row-wide reductions (sum of squares, absolute maximum) meet through distributed shared
+// memory, summed in rank order.  The row buffer (this CTA's channels as floats) lives in
+// dynamic shared memory.
 //   SWIGLU: x is [M, 2K] (gate | up);   otherwise x is [M, K] (may be null when resid given).
-template <bool SWIGLU>
+template <int CL>
+__device__ __forceinline__ float cluster_reduce(float v, float* slot, bool is_max) {
+  if (CL == 1) return v;
+  cg::cluster_group cluster = cg::this_cluster();
+  if (threadIdx.x == 0) *slot = v;
+  cluster.sync();
+  float r = 0.f;
+#pragma unroll
+  for (int c = 0; c < CL; ++c) {
+    const float o = *cluster.map_shared_rank(slot, c);
+    r = is_max ? fmaxf(r, o) : r + o;
+  }
+  return r;
+}
+
+template <bool SWIGLU, int CL>
 __global__ void __launch_bounds__(256) act_prep_kernel(
     const __half* __restrict__ x, float* __restrict__ resid, const __half* __restrict__ norm_w,
     const int8_t* __restrict__ signs, int8_t* __restrict__ q_out, float* __restrict__ scale_out,
     __half* __restrict__ y_out, int K, float eps, int zero_centered, InboxIn in, int* status,
     AgOut ag, int rows, const int* __restrict__ row_limit, int row_base) {
-  extern __shared__ float rowbuf[];
+  extern __shared__ float rowbuf_raw[];
   __shared__ float red[32];
+  __shared__ float cl_slot[2];
   const int tid = threadIdx.x;
+  const int crank = CL > 1 ? static_cast<int>(blockIdx.x) % CL : 0;
+  const int nblk = K / 128;
+  const int k_lo = (nblk * crank / CL) * 128, k_hi = (nblk * (crank + 1) / CL) * 128;
+  float* rowbuf = rowbuf_raw - k_lo;           // indexed by the channel number
   // sequence-parallel form: this rank handles only the rows it owns and pushes the result
   const bool sp = !SWIGLU && ag.tp > 0;
-  const int row = (sp ? ag.rank * ag.rows_per : row_base) + blockIdx.x;
+  const int row = (sp ? ag.rank * ag.rows_per : row_base) + static_cast<int>(blockIdx.x) / CL;
   if (sp && row >= rows) {                 // tail of the last owner: nothing to do but count
     if (in.inbox != nullptr) inbox_consumed(in, gridDim.x);
     ag_signal_done(ag, gridDim.x);
@@ -75,7 +103,7 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
   if (SWIGLU) {
     const __half* g = x + static_cast<size_t>(row) * 2 * K;
     const __half* u = g + K;
-    for (int i = tid * 8; i < K; i += blockDim.x * 8) {
+    for (int i = k_lo + tid * 8; i < k_hi; i += blockDim.x * 8) {
       const int4 gr = *reinterpret_cast<const int4*>(g + i);
       const int4 ur = *reinterpret_cast<const int4*>(u + i);
       const __half* gh = reinterpret_cast<const __half*>(&gr);
@@ -94,7 +122,7 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
     const bool from_ll = in.ll != nullptr;
     const int ll_seq = from_ll ? *reinterpret_cast<volatile int*>(in.seen) + 1 : 0;
     if (from_inbox && !from_ll) inbox_wait(in, status);   // a timed-out wait is reported
-    for (int i = tid * 8; i < K; i += blockDim.x * 8) {
+    for (int i = k_lo + tid * 8; i < k_hi; i += blockDim.x * 8) {
       float v[8];
       if (from_ll) {
         // low-latency form: each unit carries its own sequence number; sum the sources in
@@ -150,10 +178,10 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
       }
     }
     if (norm_w) {
-      const float total = block_reduce(sumsq, red, false);
+      const float total = cluster_reduce<CL>(block_reduce(sumsq, red, false), &cl_slot[0], false);
       const float r = rsqrtf(total / static_cast<float>(K) + eps);
       const float add = zero_centered ? 1.f : 0.f;
-      for (int i = tid * 8; i < K; i += blockDim.x * 8) {
+      for (int i = k_lo + tid * 8; i < k_hi; i += blockDim.x * 8) {
         const int4 wr = *reinterpret_cast<const int4*>(norm_w + i);
         const __half* wh = reinterpret_cast<const __half*>(&wr);
 #pragma unroll
@@ -162,7 +190,7 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
               round_f16(__fmul_rn(__fmul_rn(rowbuf[i + j], r), __half2float(wh[j]) + add));
       }
     } else {
-      for (int i = tid * 8; i < K; i += blockDim.x * 8)
+      for (int i = k_lo + tid * 8; i < k_hi; i += blockDim.x * 8)
 #pragma unroll
         for (int j = 0; j < 8; ++j) rowbuf[i + j] = round_f16(rowbuf[i + j]);
     }
@@ -170,7 +198,7 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
   __syncthreads();
   if (y_out) {
     __half* yr = y_out + static_cast<size_t>(row) * K;
-    for (int i = tid * 8; i < K; i += blockDim.x * 8) {
+    for (int i = k_lo + tid * 8; i < k_hi; i += blockDim.x * 8) {
       __align__(16) __half h[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(rowbuf[i + j]);
@@ -181,7 +209,7 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
   if (signs) {
     // Each warp transforms whole 128-blocks; lane holds 4 consecutive values.
     const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
-    for (int b = warp; b < K / 128; b += nw) {
+    for (int b = k_lo / 128 + warp; b < k_hi / 128; b += nw) {
       float* p = rowbuf + b * 128 + lane * 4;
       const char4 sg = *reinterpret_cast<const char4*>(signs + b * 128 + lane * 4);
       float v0 = p[0] * sg.x, v1 = p[1] * sg.y, v2 = p[2] * sg.z, v3 = p[3] * sg.w;
@@ -205,14 +233,14 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
       amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3))));
     }
   } else {
-    for (int i = tid; i < K; i += blockDim.x) amax = fmaxf(amax, fabsf(rowbuf[i]));
+    for (int i = k_lo + tid; i < k_hi; i += blockDim.x) amax = fmaxf(amax, fabsf(rowbuf[i]));
   }
-  amax = block_reduce(amax, red, true);
+  amax = cluster_reduce<CL>(block_reduce(amax, red, true), &cl_slot[1], true);
   const float scale = a8_scale(amax);
   if (sp) {
     // all-gather by push: the INT8 row and its scale go to every rank's activation buffer
     if (tid < ag.tp) ag.scale[tid][row] = scale;
-    for (int i = tid * 16; i < K; i += blockDim.x * 16) {
+    for (int i = k_lo + tid * 16; i < k_hi; i += blockDim.x * 16) {
       __align__(16) signed char c[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) c[j] = static_cast<signed char>(a8_code(rowbuf[i + j], scale));
@@ -224,9 +252,9 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
     ag_signal_done(ag, gridDim.x);
     return;
   }
-  if (tid == 0) scale_out[row] = scale;
+  if (tid == 0 && crank == 0) scale_out[row] = scale;
   int8_t* qr = q_out + static_cast<size_t>(row) * K;
-  for (int i = tid * 4; i < K; i += blockDim.x * 4) {
+  for (int i = k_lo + tid * 4; i < k_hi; i += blockDim.x * 4) {
     char4 c;
     c.x = static_cast<signed char>(a8_code(rowbuf[i + 0], scale));
     c.y = static_cast<signed char>(a8_code(rowbuf[i + 1], scale));
@@ -235,6 +263,8 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
     *reinterpret_cast<char4*>(qr + i) = c;
   }
   if (!SWIGLU && (in.inbox != nullptr || in.ll != nullptr)) inbox_consumed(in, gridDim.x);
+  // a CTA's shared memory must outlive the cluster's reads of it
+  if (CL > 1) cg::this_cluster().sync();
 }
 
 __global__ void ag_wait_kernel(AgIn in, int rows, int* status) {
@@ -513,21 +543,53 @@ static int act_prep_launch(const __half* x, float* resid, const __half* norm_w, 
   int* status = runtime_status_ptr();
   if (K % 128) return -1;
   const size_t smem = static_cast<size_t>(K) * sizeof(float);
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(act_prep_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  static const int slot = runtime_new_slot();
+  if (runtime_first_use(slot)) {
+    cudaFuncSetAttribute(act_prep_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          200 * 1024);
-    cudaFuncSetAttribute(act_prep_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(act_prep_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          200 * 1024);
-    attr_set = true;
   }
   if (smem > 200 * 1024) return -1;
+  // A few rows (decode steps): one row would keep a single SM busy, so a cluster of CTAs
+  // shares each row.  Not for the sequence-parallel and count-limited forms, whose CTAs may
+  // leave early.
+  constexpr int CL = 8;
+  if (rows <= 16 && ag.tp == 0 && row_limit == nullptr && K / 128 >= CL) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows * CL);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = (static_cast<size_t>(K / 128 + CL - 1) / CL) * 128 * sizeof(float);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CL;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const AgOut no_ag{};
+    const int* no_limit = nullptr;
+    cudaError_t e;
+    if (swiglu) {
+      float* no_resid = nullptr;
+      const __half* no_norm = nullptr;
+      e = cudaLaunchKernelEx(&cfg, act_prep_kernel<true, CL>, x, no_resid, no_norm, signs, q_out,
+                             scale_out, y_out, K, eps, zero_centered, in, status, no_ag, rows,
+                             no_limit, 0);
+    } else {
+      e = cudaLaunchKernelEx(&cfg, act_prep_kernel<false, CL>, x, resid, norm_w, signs, q_out,
+                             scale_out, y_out, K, eps, zero_centered, in, status, no_ag, rows,
+                             no_limit, row_base);
+    }
+    return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
+  }
   if (swiglu)
-    act_prep_kernel<true><<<rows, 256, smem, stream>>>(x, nullptr, nullptr, signs, q_out,
-                                                       scale_out, y_out, K, eps, zero_centered,
-                                                       in, status, AgOut{}, rows, row_limit, 0);
+    act_prep_kernel<true, 1><<<rows, 256, smem, stream>>>(x, nullptr, nullptr, signs, q_out,
+                                                          scale_out, y_out, K, eps, zero_centered,
+                                                          in, status, AgOut{}, rows, row_limit, 0);
   else
-    act_prep_kernel<false><<<ag.tp > 0 ? ag.rows_per : rows, 256, smem, stream>>>(
+    act_prep_kernel<false, 1><<<ag.tp > 0 ? ag.rows_per : rows, 256, smem, stream>>>(
         x, resid, norm_w, signs, q_out, scale_out, y_out, K, eps, zero_centered, in, status, ag,
         rows, row_limit, row_base);
   return static_cast<int>(cudaGetLastError());

@@ -31,6 +31,7 @@ namespace tc {
 constexpr int BM = 128, BK = 128;
 constexpr int TILE_BYTES = 128 * 128;        // one INT8 activation tile (128 rows x 128 k)
 constexpr int PRODUCERS = 512;               // warps 2..17
+constexpr int PWARPS = PRODUCERS / 32;
 constexpr int THREADS = 64 + PRODUCERS;
 
 template <int FMT, int MT, int NB>
@@ -43,13 +44,14 @@ struct Layout {
   // the decode then runs ahead of the tensor core while the next activation tiles land.
   static constexpr int A_BYTES = MT * TILE_BYTES;
   static constexpr int BC_BYTES = B_BYTES + CODE_BYTES;
-  static constexpr int BUDGET = 221 * 1024;
+  static constexpr int BUDGET = 216 * 1024;
   static constexpr int SB_FIT = (BUDGET - 2 * A_BYTES) / BC_BYTES;
   static constexpr int SB = SB_FIT >= 4 ? 4 : SB_FIT;
   static constexpr int SA_FIT = (BUDGET - SB * BC_BYTES) / A_BYTES;
   static constexpr int SA = SA_FIT >= 4 ? 4 : SA_FIT;
   static_assert(SA >= 2 && SB >= 2, "at least double buffering");
-  static constexpr int LUT_BYTES = FMT == 0 ? 0 : 4096;
+  static constexpr int LUT_COPIES = 4;
+  static constexpr int LUT_BYTES = FMT == 0 ? 0 : static_cast<int>(sizeof(E8pLut<LUT_COPIES>));
   static constexpr int A_OFF = 0;
   static constexpr int B_OFF = A_OFF + SA * A_BYTES;
   static constexpr int CODE_OFF = B_OFF + SB * B_BYTES;
@@ -83,7 +85,8 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   unsigned char* a_s = smem + L::A_OFF;
   unsigned char* b_s = smem + L::B_OFF;
   unsigned char* code_s = smem + L::CODE_OFF;
-  E8pSmem* lut = reinterpret_cast<E8pSmem*>(smem + L::LUT_OFF);
+  using Lut = E8pLut<L::LUT_COPIES>;
+  Lut* lut = reinterpret_cast<Lut*>(smem + L::LUT_OFF);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* a_full = bars;                   // [SA] activation tiles landed (TMA)
   uint64_t* a_empty = bars + SA;             // [SA] tensor core done with the tiles
@@ -133,7 +136,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     tmem_relinquish();
   }
   if (FMT != 0 && warp >= 2) {
-    e8p_smem_init(lut, tables, threadIdx.x - 64, PRODUCERS);
+    e8p_lut_init(lut, tables, threadIdx.x - 64, PRODUCERS);
   }
   tc_fence_before();
   __syncthreads();
@@ -222,6 +225,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     bool ok = true;
     if (FMT != 0) {
       const int chunk = t & 7, rbase = t >> 3;          // 64 weight rows per pass
+      const int copy = t & (L::LUT_COPIES - 1);
       for (int kb = 0; kb < kblocks; ++kb) {
         const int s = kb % SB;
         // the codes of this phase are only requested after the tensor core released the
@@ -238,13 +242,13 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
           if (row < rows_valid) {
             if (FMT == 1) {
               const uint2 wd = *reinterpret_cast<const uint2*>(cs + row * 64 + chunk * 8);
-              const uint2 q0 = e8p_decode_q4(wd.x, lut);
-              const uint2 q1 = e8p_decode_q4(wd.y, lut);
+              const uint2 q0 = e8p_decode_q4(wd.x, lut, copy);
+              const uint2 q1 = e8p_decode_q4(wd.y, lut, copy);
               v = make_uint4(q0.x, q0.y, q1.x, q1.y);
             } else {
               const uint32_t wd = *reinterpret_cast<const uint32_t*>(cs + row * 32 + chunk * 4);
-              const uint2 q0 = e8p_decode8(wd & 0xffffu, lut);
-              const uint2 q1 = e8p_decode8(wd >> 16, lut);
+              const uint2 q0 = e8p_decode8<L::LUT_COPIES, 0>(wd, lut, copy);
+              const uint2 q1 = e8p_decode8<L::LUT_COPIES, 1>(wd, lut, copy);
               v = make_uint4(q0.x, q0.y, q1.x, q1.y);
             }
           }
@@ -355,6 +359,435 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   if (po.tp > 0 && partial == nullptr) peer_signal_done(po, gridDim.x * gridDim.y);
 }
 
+// ---------------------------------------------------------------- persistent form
+// One CTA per SM walks the tile list (tile = blockIdx.x + i * gridDim.x; m fastest, so the
+// CTAs running together share a few weight tiles in L2).  What is paid once per CTA instead
+// of once per tile: the decode tables, the TMEM allocation, the barriers and the pipeline
+// fill.  Differences from the one-tile kernel above:
+//   * activation tiles live in a ring of single 16 KiB slots (8 for MT = 4) with a barrier
+//     pair each, so a slot is refilled as soon as its own MMAs retire instead of when the
+//     whole MT-tile stage does; all rings and their phases run on across tiles;
+//   * packed codes and decoded INT8 tiles have rings of their own depth;
+//   * the epilogue of tile i runs while the tensor core already works on tile i+1: the
+//     producer warps first decode the k-blocks of tile i+1 that fit in the ring, then drain
+//     the accumulators of tile i one at a time, and the MMA warp waits per accumulator
+//     (tmem_empty[t]) before it overwrites it;
+//   * M sub-tiles past the last row are neither loaded nor multiplied;
+//   * every wait polls a CTA-wide abort word, so that all roles leave together when one
+//     bounded wait ran out.
+// With peers (fused scatter) the FP16 tile is staged in the operand rings as before, so
+// the loaders wait for the epilogue before they refill the rings (epi_done).
+template <int FMT, int MT, int NB>
+struct PsLayout {
+  static constexpr int ROW_CODE_BYTES = FMT == 1 ? 64 : (FMT == 2 ? 32 : 0);
+  static constexpr int CODE_BYTES = NB * ROW_CODE_BYTES;
+  static constexpr int B_BYTES = NB * BK;
+  static constexpr int NSLOT = MT == 4 ? 8 : (MT == 2 ? 6 : 4);
+  static constexpr int SBD = FMT == 0 ? 4 : 3;          // decoded (or TMA-loaded) weight tiles
+  static constexpr int SC = FMT == 0 ? 0 : 3;           // packed-code slabs
+  static constexpr int LUT_COPIES = 8;
+  static constexpr int LUT_BYTES = FMT == 0 ? 0 : static_cast<int>(sizeof(E8pLut<LUT_COPIES>));
+  static constexpr int A_OFF = 0;
+  static constexpr int B_OFF = A_OFF + NSLOT * TILE_BYTES;
+  static constexpr int CODE_OFF = B_OFF + SBD * B_BYTES;
+  static constexpr int LUT_OFF = CODE_OFF + SC * CODE_BYTES;
+  static constexpr int BAR_OFF = LUT_OFF + LUT_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 512 + 1024;    // barriers + alignment slack
+  static_assert(TOTAL <= 227 * 1024, "exceeds the shared memory of one CTA");
+};
+
+struct PsTile {
+  int n0, m0, m_limit, b_row0, kb0, kblocks, rows_valid, z, mt_act;
+  const unsigned char* w;
+  const __half* w_scale;
+};
+
+template <int FMT, bool OUT_F32, int MT, int NB>
+__global__ void __launch_bounds__(THREADS, 1) qgemm_ps_kernel(
+    const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+    const unsigned char* __restrict__ w, const float* __restrict__ a_scale,
+    const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K,
+    const E8pTables* __restrict__ tables, int* status, PeerOut po, GroupDesc grp, AgIn ag,
+    int* __restrict__ partial, int n_begin, int n_end, int splits) {
+  using L = PsLayout<FMT, MT, NB>;
+  constexpr int NSLOT = L::NSLOT, SBD = L::SBD, SC = L::SC > 0 ? L::SC : 1;
+  constexpr int BN = NB;
+  constexpr int CHUNKS = BN / 32;                      // 32-column chunks per accumulator
+  constexpr uint32_t TMEM_COLS = MT * BN;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* a_s = smem + L::A_OFF;
+  unsigned char* b_s = smem + L::B_OFF;
+  unsigned char* code_s = smem + L::CODE_OFF;
+  using Lut = E8pLut<L::LUT_COPIES>;
+  Lut* lut = reinterpret_cast<Lut*>(smem + L::LUT_OFF);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* a_full = bars;                     // [NSLOT] activation tile landed (TMA)
+  uint64_t* a_empty = a_full + NSLOT;          // [NSLOT] its MMAs retired
+  uint64_t* c_full = a_empty + NSLOT;          // [SC]   packed codes landed (bulk copy)
+  uint64_t* c_empty = c_full + SC;             // [SC]   every producer warp read them
+  uint64_t* b_full = c_empty + SC;             // [SBD]  INT8 weight tile ready (decode or TMA)
+  uint64_t* b_empty = b_full + SBD;            // [SBD]  its MMAs retired
+  uint64_t* tmem_full = b_empty + SBD;         // [1]    all MMAs of the tile retired
+  uint64_t* tmem_empty = tmem_full + 1;        // [MT]   accumulator read out by the epilogue
+  uint64_t* epi_done = tmem_empty + MT;        // [1]    staged tile left for the peers
+  uint64_t* stage_full = epi_done + 1;         // [1]    every producer warp staged its part
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stage_full + 1);
+  volatile int* abort_w = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  static_assert((2 * NSLOT + 2 * SC + 2 * SBD + MT + 3) * 8 + 8 <= 512, "barrier block");
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool peer_stage = po.tp > 0 && partial == nullptr;
+  const int n_tiles = (n_end - n_begin + BN - 1) / BN;
+  const int m_tiles = grp.tiles != nullptr ? grp.meta[0] : (M + BM * MT - 1) / (BM * MT);
+  const int total = n_tiles * m_tiles * splits;
+  const int kb_all = K / BK, kb_per = (kb_all + splits - 1) / splits;
+
+  auto tile_at = [&](int t) {
+    PsTile T;
+    T.z = t / (n_tiles * m_tiles);
+    const int r = t - T.z * (n_tiles * m_tiles);
+    const int nt = r / m_tiles, mi = r - nt * m_tiles;
+    T.n0 = n_begin + nt * BN;
+    T.m0 = mi * BM * MT;
+    T.m_limit = M;
+    T.b_row0 = T.n0;
+    T.w = w;
+    T.w_scale = w_scale;
+    if (grp.tiles != nullptr) {
+      const int expert = grp.tiles[mi * 4];
+      T.m0 = grp.tiles[mi * 4 + 1];
+      T.m_limit = T.m0 + grp.tiles[mi * 4 + 2];
+      T.w = w + static_cast<long long>(expert) * grp.w_stride;
+      T.w_scale = w_scale + static_cast<long long>(expert) * grp.n_per_expert;
+      T.b_row0 = expert * grp.n_per_expert + T.n0;
+    }
+    T.kb0 = T.z * kb_per;
+    T.kblocks = max(0, min(kb_all, T.kb0 + kb_per) - T.kb0);
+    T.rows_valid = min(BN, n_end - T.n0);
+    const int rows = min(T.m_limit, M) - T.m0;
+    T.mt_act = rows <= 0 ? 0 : min(MT, (rows + BM - 1) / BM);
+    return T;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NSLOT; ++s) {
+      mbar_init(&a_full[s], 1);
+      mbar_init(&a_empty[s], 1);
+    }
+    for (int s = 0; s < SC; ++s) {
+      mbar_init(&c_full[s], 1);
+      mbar_init(&c_empty[s], PWARPS);
+    }
+    for (int s = 0; s < SBD; ++s) {
+      mbar_init(&b_full[s], FMT == 0 ? 1 : PWARPS);
+      mbar_init(&b_empty[s], 1);
+    }
+    mbar_init(tmem_full, 1);
+    for (int t = 0; t < MT; ++t) mbar_init(&tmem_empty[t], 4 * CHUNKS);
+    mbar_init(epi_done, PWARPS);
+    mbar_init(stage_full, PWARPS);
+    *abort_w = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmap_a);
+    if (FMT == 0) prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (FMT != 0 && warp >= 2) e8p_lut_init(lut, tables, threadIdx.x - 64, PRODUCERS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr int STAGE_ROW = BN * 2 + 16;
+  static_assert(MT * BM * STAGE_ROW <= L::LUT_OFF, "staged tile must fit in the operand rings");
+
+#define PS_WAIT(bar, par, code, detail) \
+  mbar_wait_abortable((bar), (par), status, (code), (detail), abort_w)
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- activation loader
+      uint32_t ca = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < total; t += gridDim.x, ++it) {
+        const PsTile T = tile_at(t);
+        if (peer_stage && it > 0) ok = PS_WAIT(epi_done, (it - 1) & 1, STATUS_EPILOGUE_WAIT, 1);
+        if (ok && ag.tp > 0 && T.mt_act > 0) {
+          // all-gather fused into the GEMM: the rows of this M tile were pushed by their
+          // owner ranks; wait for exactly those, then order the async-proxy loads after it
+          ok = ag_wait(ag, T.m0, min(T.m0 + MT * BM, M) - 1, status);
+          if (!ok) *abort_w = 1;
+          fence_proxy_async_all();
+        }
+        for (int kb = 0; ok && kb < T.kblocks; ++kb) {
+          for (int s = 0; s < T.mt_act; ++s, ++ca) {
+            const uint32_t slot = ca % NSLOT;
+            ok = PS_WAIT(&a_empty[slot], ((ca / NSLOT) & 1) ^ 1, STATUS_TMA_WAIT, kb);
+            if (!ok) break;
+            mbar_expect_tx(&a_full[slot], TILE_BYTES);
+            tma_load_2d(a_s + slot * TILE_BYTES, &tmap_a, &a_full[slot], (T.kb0 + kb) * BK,
+                        T.m0 + s * BM);
+          }
+        }
+      }
+      // never leave the CTA with a copy of ours in flight
+      for (uint32_t c = ca > NSLOT ? ca - NSLOT : 0; c < ca; ++c)
+        mbar_wait(&a_full[c % NSLOT], (c / NSLOT) & 1, status, STATUS_TMA_WAIT, 0x4000);
+    } else if (lane == 1) {
+      // ---------------- weight loader: INT8 tiles by TMA (W8) or packed codes as bulk copies
+      uint32_t cw = 0;
+      int it = 0;
+      bool ok = true;
+      constexpr int DEPTH = FMT == 0 ? SBD : SC;
+      uint64_t* landed = FMT == 0 ? b_full : c_full;
+      uint64_t* freed = FMT == 0 ? b_empty : c_empty;
+      for (int t = blockIdx.x; ok && t < total; t += gridDim.x, ++it) {
+        const PsTile T = tile_at(t);
+        if (peer_stage && it > 0) ok = PS_WAIT(epi_done, (it - 1) & 1, STATUS_EPILOGUE_WAIT, 2);
+        for (int kb = 0; ok && kb < T.kblocks && T.mt_act > 0; ++kb, ++cw) {
+          const uint32_t s = cw % DEPTH;
+          ok = PS_WAIT(&freed[s], ((cw / DEPTH) & 1) ^ 1, STATUS_TMA_WAIT, 0x1000 | kb);
+          if (!ok) break;
+          if (FMT == 0) {
+            mbar_expect_tx(&b_full[s], L::B_BYTES);
+            tma_load_2d(b_s + s * L::B_BYTES, &tmap_b, &b_full[s], (T.kb0 + kb) * BK, T.b_row0);
+          } else {
+            const unsigned char* src =
+                T.w + (static_cast<size_t>(T.kb0 + kb) * N + T.n0) * L::ROW_CODE_BYTES;
+            mbar_expect_tx(&c_full[s], T.rows_valid * L::ROW_CODE_BYTES);
+            bulk_load(code_s + s * L::CODE_BYTES, src, T.rows_valid * L::ROW_CODE_BYTES,
+                      &c_full[s]);
+          }
+        }
+      }
+      for (uint32_t c = cw > DEPTH ? cw - DEPTH : 0; c < cw; ++c)
+        mbar_wait(&landed[c % DEPTH], (c / DEPTH) & 1, status, STATUS_TMA_WAIT, 0x5000);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer
+      constexpr uint32_t idesc = umma_idesc(2, 1, 1, 0, 0, BM, BN);
+      uint32_t ca = 0, cb = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < total; t += gridDim.x, ++it) {
+        const PsTile T = tile_at(t);
+        const int kbs = T.mt_act > 0 ? T.kblocks : 0;
+        for (int kb = 0; ok && kb < kbs; ++kb, ++cb) {
+          const uint32_t sb = cb % SBD;
+          ok = PS_WAIT(&b_full[sb], (cb / SBD) & 1, STATUS_MMA_WAIT, 0x2000 | kb);
+          if (!ok) break;
+          const uint32_t b_addr = smem_u32(b_s + sb * L::B_BYTES);
+          for (int s = 0; s < T.mt_act; ++s, ++ca) {
+            // the epilogue of the previous tile must have read this accumulator out
+            if (kb == 0 && it > 0)
+              ok = PS_WAIT(&tmem_empty[s], (it - 1) & 1, STATUS_MMA_WAIT, 0x3000 | s);
+            const uint32_t slot = ca % NSLOT;
+            if (ok) ok = PS_WAIT(&a_full[slot], (ca / NSLOT) & 1, STATUS_MMA_WAIT, kb);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(a_s + slot * TILE_BYTES);
+#pragma unroll
+            for (int j = 0; j < BK / 32; ++j)
+              mma_i8_ss(tmem_base + s * BN, umma_desc(a_addr + j * 32, 16, 1024),
+                        umma_desc(b_addr + j * 32, 16, 1024), idesc, (kb | j) != 0 ? 1u : 0u);
+            tc_commit(&a_empty[slot]);
+          }
+          if (ok) tc_commit(&b_empty[sb]);
+        }
+        if (ok) {
+          if (kbs > 0) {
+            tc_commit(tmem_full);
+          } else {
+            // nothing to multiply: still one tmem_full phase per tile, and never ahead of the
+            // previous tile's epilogue (a phase must not complete before its waiters looked)
+            if (it > 0) ok = PS_WAIT(&tmem_empty[0], (it - 1) & 1, STATUS_MMA_WAIT, 0x3800);
+            if (ok) mbar_arrive(tmem_full);
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------- producers (lattice decode) and epilogue
+    const int t512 = threadIdx.x - 64;                  // 0..511
+    const int chunk = t512 & 7, rbase = t512 >> 3;      // 64 weight rows per pass
+    const int copy = t512 & (L::LUT_COPIES - 1);
+    const int quad = warp & 3;                          // TMEM lane quadrant of this warp
+    const int part = (warp - 2) >> 2;                   // 0..3: which 32-column chunks
+    const int row = quad * 32 + lane;
+    bool ok = true;
+
+    auto epilogue = [&](const PsTile& T, int it) {
+      ok = PS_WAIT(tmem_full, it & 1, STATUS_EPILOGUE_WAIT, 0) && ok;
+      ok = __all_sync(0xffffffffu, ok);                 // tcgen05.ld needs the whole warp
+      if (!ok) return;
+      tc_fence_after();
+      const bool have_acc = T.kblocks > 0 && T.mt_act > 0;
+#pragma unroll 1
+      for (int item = part; item < MT * CHUNKS; item += 4) {
+        const int mt = item / CHUNKS, c0 = (item % CHUNKS) * 32;
+        const int m = T.m0 + mt * BM + row;
+        uint32_t r[32];
+        if (have_acc && mt < T.mt_act) {
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + mt * BN + c0, r);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0;        // nothing was accumulated
+        }
+        // this warp's share of accumulator mt is in registers: the tensor core may reuse it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[mt]);
+        // gathered row scales were written by peers: read them past L1
+        const float sa = m < T.m_limit ? (ag.tp > 0 ? __ldcg(a_scale + m) : a_scale[m]) : 0.f;
+        if (partial != nullptr) {
+          if (m < T.m_limit) {
+            // the workspace is compact over this launch's columns
+            const int width = n_end - n_begin;
+            int* dst = partial + (static_cast<size_t>(T.z) * M + m) * width +
+                       (T.n0 - n_begin) + c0;
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              if (T.n0 + c0 + g * 4 + 4 <= n_end)
+                *reinterpret_cast<int4*>(dst + g * 4) =
+                    make_int4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+          }
+          continue;
+        }
+        if (m < T.m_limit) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int n = T.n0 + c0 + g * 8;
+            if (n + 8 <= n_end) {
+              float v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                v[j] = (static_cast<float>(static_cast<int>(r[g * 8 + j])) *
+                        __half2float(T.w_scale[n + j])) * sa;
+              if (peer_stage) {
+                __align__(16) __half h[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
+                *reinterpret_cast<int4*>(smem + static_cast<size_t>(mt * BM + row) * STAGE_ROW +
+                                         (c0 + g * 8) * 2) = *reinterpret_cast<const int4*>(h);
+              } else if (OUT_F32) {
+                float* o = reinterpret_cast<float*>(out) + static_cast<size_t>(m) * N + n;
+                *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+              } else {
+                __align__(16) __half h[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
+                __half* o = reinterpret_cast<__half*>(out) + static_cast<size_t>(m) * N + n;
+                *reinterpret_cast<int4*>(o) = *reinterpret_cast<const int4*>(h);
+              }
+            }
+          }
+        }
+      }
+      if (peer_stage) {
+        // fused scatter, step 2: when every producer warp has staged its part, whole 16-byte
+        // segments of consecutive columns leave lane by lane (a warp writes complete rows per
+        // instruction, which keeps NVLink packets full)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(stage_full);
+        ok = PS_WAIT(stage_full, it & 1, STATUS_EPILOGUE_WAIT, 3);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) return;
+        constexpr int SEGS = BN / 8;
+        for (int idx = t512; idx < MT * BM * SEGS; idx += PRODUCERS) {
+          const int rr = idx / SEGS, seg = idx % SEGS;
+          const int m = T.m0 + rr, n = T.n0 + seg * 8;
+          if (m < T.m_limit && n + 8 <= n_end) {
+            const int4 val = *reinterpret_cast<const int4*>(
+                smem + static_cast<size_t>(rr) * STAGE_ROW + seg * 16);
+            const size_t off = (static_cast<size_t>(po.rank) * po.rows_cap + m) * N + n;
+            if (po.rows_per > 0) {
+              // reduce-scatter: only the owner of row m receives this partial
+              *reinterpret_cast<int4*>(po.inbox[min(m / po.rows_per, po.tp - 1)] + off) = val;
+            } else {
+              for (int d = 0; d < po.tp; ++d) *reinterpret_cast<int4*>(po.inbox[d] + off) = val;
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(epi_done);           // the rings may be refilled
+      }
+    };
+
+    uint32_t cc = 0, cb = 0;
+    int it = 0;
+    bool have_prev = false;
+    PsTile prev{};
+    for (int t = blockIdx.x; ok && t < total; t += gridDim.x, ++it) {
+      const PsTile T = tile_at(t);
+      const int kbs = T.mt_act > 0 ? T.kblocks : 0;
+      bool prev_pending = have_prev;
+      // where the previous tile's epilogue runs: after the k-blocks that fit in the ring
+      // have been decoded (they are all the tensor core can use before it is drained anyway)
+      const int epos = (peer_stage || FMT == 0) ? -1 : min(SBD, kbs) - 1;
+      if (prev_pending && epos < 0) {
+        epilogue(prev, it - 1);
+        prev_pending = false;
+      }
+      if (FMT != 0) {
+        for (int kb = 0; ok && kb < kbs; ++kb, ++cc, ++cb) {
+          const uint32_t sc = cc % SC, sb = cb % SBD;
+          ok = PS_WAIT(&c_full[sc], (cc / SC) & 1, STATUS_DECODE_WAIT, kb);
+          if (ok) ok = PS_WAIT(&b_empty[sb], ((cb / SBD) & 1) ^ 1, STATUS_DECODE_WAIT, 0x800 | kb);
+          if (!ok) break;
+          const unsigned char* cs = code_s + sc * L::CODE_BYTES;
+          unsigned char* bs = b_s + sb * L::B_BYTES;
+#pragma unroll
+          for (int i = 0; i < (BN + 63) / 64; ++i) {
+            const int wrow = rbase + 64 * i;
+            if (BN < 64 && wrow >= BN) break;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (wrow < T.rows_valid) {
+              if (FMT == 1) {
+                const uint2 wd = *reinterpret_cast<const uint2*>(cs + wrow * 64 + chunk * 8);
+                const uint2 q0 = e8p_decode_q4(wd.x, lut, copy);
+                const uint2 q1 = e8p_decode_q4(wd.y, lut, copy);
+                v = make_uint4(q0.x, q0.y, q1.x, q1.y);
+              } else {
+                const uint32_t wd = *reinterpret_cast<const uint32_t*>(cs + wrow * 32 + chunk * 4);
+                const uint2 q0 = e8p_decode8<L::LUT_COPIES, 0>(wd, lut, copy);
+                const uint2 q1 = e8p_decode8<L::LUT_COPIES, 1>(wd, lut, copy);
+                v = make_uint4(q0.x, q0.y, q1.x, q1.y);
+              }
+            }
+            *reinterpret_cast<uint4*>(bs + swz128(wrow, chunk)) = v;
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(&b_full[sb]);
+            mbar_arrive(&c_empty[sc]);
+          }
+          if (prev_pending && kb == epos) {
+            epilogue(prev, it - 1);
+            prev_pending = false;
+          }
+        }
+      }
+      if (ok && prev_pending) epilogue(prev, it - 1);
+      prev = T;
+      have_prev = true;
+    }
+    if (ok && have_prev) epilogue(prev, it - 1);
+  }
+#undef PS_WAIT
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (peer_stage) peer_signal_done(po, gridDim.x);
+}
+
 // out[m][n] = (float(sum_z partial[z][m][n]) * w_scale[n]) * a_scale[m], as FP16 into `out`
 // or, with peers, into the inboxes (all ranks, or the row's owner when rows_per > 0).
 // One thread per 8 columns; the arithmetic is the GEMM epilogue's, so a split GEMM returns
@@ -398,14 +831,16 @@ __global__ void __launch_bounds__(256) splitk_finalize_kernel(
   if (po.tp > 0) peer_signal_done(po, gridDim.x);
 }
 
+// 0: persistent kernel (default); 1: one tile per CTA.  Both give the same bits.
+static int g_impl = 0;
+constexpr int NUM_SMS = 148;
+
 template <int FMT, bool OUT_F32, int MT, int NB>
-int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale, void* out,
-           int M, int N, int K, cudaStream_t stream, const PeerOut& po,
-           const GroupDesc& grp = GroupDesc{nullptr, nullptr, 0, 0}, int experts = 1,
-           int max_tiles = 0, const AgIn& ag = AgIn{nullptr, nullptr, 0, 0}, int splits = 1,
-           int n_begin = 0, int n_end = -1) {
-  using L = Layout<FMT, MT, NB>;
-  if (n_end < 0) n_end = N;
+int launch_ps(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale,
+              void* out, int M, int N, int K, cudaStream_t stream, const PeerOut& po,
+              const GroupDesc& grp, int experts, int max_tiles, const AgIn& ag, int splits,
+              int n_begin, int n_end) {
+  using L = PsLayout<FMT, MT, NB>;
   CUtensorMap ta, tb;
   if (!make_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BM, BK)) return -3;
   if (FMT == 0) {
@@ -416,12 +851,58 @@ int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w
     tb = ta;
     if (reinterpret_cast<uintptr_t>(w) % 16) return -1;
   }
-  static bool attr = false;
-  if (!attr) {
+  static const int slot = runtime_new_slot();
+  if (runtime_first_use(slot)) {
+    cudaError_t e = cudaFuncSetAttribute(qgemm_ps_kernel<FMT, OUT_F32, MT, NB>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  const int width = n_end - n_begin;
+  if (width <= 0) return 0;
+  const long n_tiles = (width + NB - 1) / NB;
+  const long m_tiles = grp.tiles ? max_tiles : (M + BM * MT - 1) / (BM * MT);
+  const long total = n_tiles * m_tiles * splits;
+  const int grid = static_cast<int>(total < NUM_SMS ? total : NUM_SMS);
+  int* partial = splits > 1 ? runtime_splitk_workspace() : nullptr;
+  if (splits > 1 && static_cast<size_t>(splits) * M * width * 4 > SPLITK_WORKSPACE_BYTES) return -1;
+  qgemm_ps_kernel<FMT, OUT_F32, MT, NB><<<grid, THREADS, L::TOTAL, stream>>>(
+      ta, tb, reinterpret_cast<const unsigned char*>(w), a_scale, w_scale, out, M, N, K,
+      runtime_e8p_tables(), runtime_status_ptr(), po, grp, ag, partial, n_begin, n_end, splits);
+  if (splits > 1) {
+    const long long items = static_cast<long long>(M) * (width / 8);
+    splitk_finalize_kernel<<<static_cast<unsigned>((items + 255) / 256), 256, 0, stream>>>(
+        partial, splits, a_scale, w_scale, reinterpret_cast<__half*>(out), M, N, po,
+        ag.tp > 0 ? 1 : 0, n_begin, width);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int FMT, bool OUT_F32, int MT, int NB>
+int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale, void* out,
+           int M, int N, int K, cudaStream_t stream, const PeerOut& po,
+           const GroupDesc& grp = GroupDesc{nullptr, nullptr, 0, 0}, int experts = 1,
+           int max_tiles = 0, const AgIn& ag = AgIn{nullptr, nullptr, 0, 0}, int splits = 1,
+           int n_begin = 0, int n_end = -1) {
+  using L = Layout<FMT, MT, NB>;
+  if (n_end < 0) n_end = N;
+  if (g_impl == 0)
+    return launch_ps<FMT, OUT_F32, MT, NB>(a, a_scale, w, w_scale, out, M, N, K, stream, po, grp,
+                                           experts, max_tiles, ag, splits, n_begin, n_end);
+  CUtensorMap ta, tb;
+  if (!make_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BM, BK)) return -3;
+  if (FMT == 0) {
+    if (!make_tmap_2d(&tb, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1,
+                      static_cast<uint64_t>(N) * experts, K, K, NB, BK))
+      return -3;
+  } else {
+    tb = ta;
+    if (reinterpret_cast<uintptr_t>(w) % 16) return -1;
+  }
+  static const int slot = runtime_new_slot();
+  if (runtime_first_use(slot)) {
     cudaError_t e = cudaFuncSetAttribute(qgemm_tc_kernel<FMT, OUT_F32, MT, NB>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr = true;
   }
   const int width = n_end - n_begin;
   if (width <= 0) return 0;
@@ -656,6 +1137,13 @@ extern "C" int orinfer_qgemm_set_variant(int fmt, int m_lo, int m_hi, int n, int
 }
 
 extern "C" void orinfer_qgemm_clear_variants() { tc::g_variant_count = 0; }
+
+// 0 = persistent kernel (default), 1 = one tile per CTA; for comparisons and tests.
+extern "C" int orinfer_qgemm_set_impl(int impl) {
+  if (impl != 0 && impl != 1) return -1;
+  tc::g_impl = impl;
+  return 0;
+}
 
 // The plan for a shape: out[0..3] = mt, nb, splits, tail_splits.
 extern "C" void orinfer_qgemm_plan(int fmt, int M, int N, int K, int out_f32, int* out) {

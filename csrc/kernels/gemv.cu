@@ -40,213 +40,259 @@ __device__ __forceinline__ void store_row(void* out, int out_f32, int m, int n, 
   else reinterpret_cast<__half*>(out)[static_cast<size_t>(m) * N + n] = __float2half_rn(v);
 }
 
-// FMT 1: Q4 (U32 codes, 8 rows per group, 4 lanes per row); FMT 2: Q2 (U16 codes, 16 rows,
-// 2 lanes).  CTAs are persistent over row groups (decode tables and activations are staged
-// once); inside a group the 8 warps split the k-blocks, and every lane keeps DEPTH 16-byte
-// code loads of the next batch in flight while it decodes the current one.
-// Decode tables replicated COPIES times with the copies interleaved word by word, so that
-// lane l always reads copy l % COPIES.  The lookups of a warp are random in the entry index;
-// with one copy they collide on the 32 banks about 3.5-fold, which made the kernel
-// shared-memory bound.  With 16 interleaved copies only the two lanes sharing a copy can
-// collide (entry parity equal), so a lookup costs ~1.5 wavefronts instead of ~3.5.
-// A single row (MT = 1) keeps one copy: its launch is so short that filling 48 KiB of tables
-// per CTA costs more than the conflicts it removes (measured: 19.9 us vs 22.2 us at
-// N = 19456, K = 2560), while 8 rows gain 20 % (38 us -> 30 us).
-template <int COPIES>
-struct E8pBanked {
-  uint32_t posx[256 * COPIES], posy[256 * COPIES], sel[256 * COPIES];
+// FMT 1: Q4 (U32 codes, 8 output rows per group, 4 lanes per row); FMT 2: Q2 (U16 codes, 16
+// rows, 2 lanes).  One persistent CTA per SM: the decode tables (32 interleaved copies, so a
+// lane's lookups never meet another lane's on a bank) and the activations are staged once.
+// The grid is n_parts x k_parts CTAs; a CTA owns a contiguous range of row groups and one
+// range of k-blocks, its warps take contiguous runs of (group, k-block) units, every lane
+// keeps DEPTH 16-byte code loads in flight, and the partial dot products meet in shared
+// memory (integer atomics: exact, so the result does not depend on the order).
+//
+// The decode never forms the weights.  With v the 4-bit fields of a code (common.cuh), a Q4
+// weight is 8*v0 + 2*v1 - 75, so
+//     sum_k a_k w_k = 2 * sum_k a_k (4*v0 + v1)_k  -  75 * sum_k a_k
+// and the first sum is one dp4a per four weights on bytes built with two masks and one
+// multiply-add; sum_k a_k is computed once per activation row while it is staged.  Q2
+// likewise with 2*v - 15.
+//
+// k_parts > 1 (projections too narrow for one CTA per SM): the CTAs of one n-part add their
+// integers into a zeroed workspace; the last one to finish (ticket) applies the scales,
+// writes the outputs and zeroes what it read.  Launches that use the workspace must not
+// overlap on the device (they are issued on one stream).
+constexpr int GEMV_COPIES = 32;
+constexpr int GEMV_DEPTH = 4;
+
+template <int MT>
+struct GemvThreads {
+  static constexpr int value = MT <= 2 ? 1024 : 512;
 };
 
-template <int COPIES>
-__device__ __forceinline__ void banked_init(E8pBanked<COPIES>* sm,
-                                            const E8pTables* __restrict__ g, int tid,
-                                            int nthreads) {
-  for (int j = tid; j < 256 * COPIES; j += nthreads) {
-    const int i = j / COPIES;
-    const uint2 p = g->pos[i];
-    sm->posx[j] = p.x;
-    sm->posy[j] = p.y;
-    const uint32_t t = static_cast<uint32_t>(i) ^ (__popc(i) & 1u), t2 = t >> 2;
-    const uint32_t lo = 0x3210u | ((t & 0x11u) << 2) | ((t & 0x22u) << 9);
-    const uint32_t hi = 0x3210u | ((t2 & 0x11u) << 2) | ((t2 & 0x22u) << 9);
-    sm->sel[j] = lo | (hi << 16);
-  }
-}
-
-template <int COPIES>
-__device__ __forceinline__ void banked_select(uint32_t code,
-                                              const E8pBanked<COPIES>* __restrict__ sm, int copy,
-                                              uint32_t& lo, uint32_t& hi, uint32_t& par) {
-  const uint32_t s = code & 0xffu;
-  par = __popc(s) & 1u;
-  const uint32_t at = ((code >> 8) & 0xffu) * COPIES + copy;
-  const uint32_t ex = sm->posx[at], ey = sm->posy[at];
-  const uint32_t sl = sm->sel[s * COPIES + copy];
-  lo = __byte_perm(ex, 0x30303030u - ex, sl);
-  hi = __byte_perm(ey, 0x30303030u - ey, sl >> 16);
-}
-
-template <int COPIES>
-__device__ __forceinline__ uint2 banked_decode8(uint32_t code,
-                                                const E8pBanked<COPIES>* __restrict__ sm,
-                                                int copy) {
-  uint32_t lo, hi, par;
-  banked_select(code, sm, copy, lo, hi, par);
-  const uint32_t cw = 0x69696969u - par * 0x02020202u;
-  return make_uint2((lo + cw) ^ 0x80808080u, (hi + cw) ^ 0x80808080u);
-}
-
-template <int COPIES>
-__device__ __forceinline__ uint2 banked_decode_q4(uint32_t word,
-                                                  const E8pBanked<COPIES>* __restrict__ sm,
-                                                  int copy) {
-  uint32_t l0, h0, p0, l1, h1, p1;
-  banked_select(word & 0xffffu, sm, copy, l0, h0, p0);
-  banked_select(word >> 16, sm, copy, l1, h1, p1);
-  const uint32_t cw = 0x0d0d0d0du - p0 * 0x08080808u - p1 * 0x02020202u;
-  return make_uint2(((l0 << 2) + l1 + cw) ^ 0x80808080u, ((h0 << 2) + h1 + cw) ^ 0x80808080u);
-}
-
 template <int FMT, int MT>
-__global__ void __launch_bounds__(GEMV_WARPS * 32) e8p_gemv_kernel(
+__global__ void __launch_bounds__(GemvThreads<MT>::value, 1) e8p_gemv_kernel(
     const int8_t* __restrict__ a, const float* __restrict__ a_scale, const uint4* __restrict__ w,
     const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K, int out_f32,
-    const E8pTables* __restrict__ tables, PeerOut po) {
+    const E8pTables* __restrict__ tables, PeerOut po, int n_parts, int k_parts, int max_groups,
+    int* __restrict__ ws) {
+  constexpr int THREADS = GemvThreads<MT>::value;
   constexpr int ROWS = FMT == 1 ? 8 : 16;
   constexpr int LPR = 32 / ROWS;                 // lanes per row
   constexpr int WPL = 128 / LPR;                 // weights per lane per k-block
-  constexpr int DEPTH = 4;
+  constexpr int DEPTH = GEMV_DEPTH;
+  using Lut = E8pLut<GEMV_COPIES>;
   const PeerOut* peer = po.tp > 0 ? &po : nullptr;
   const bool ll = peer != nullptr && po.rows_per == LL_MODE;
   const int ll_seq = ll ? *reinterpret_cast<volatile int*>(po.sent) + 1 : 0;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  constexpr int COPIES = MT == 1 ? 1 : 16;
-  using Table = E8pBanked<COPIES>;
-  Table* table = reinterpret_cast<Table*>(smem_raw);
-  int8_t* act = reinterpret_cast<int8_t*>(smem_raw) + sizeof(Table);
-  __shared__ int red[2][GEMV_WARPS][ROWS][MT];
+  Lut* lut = reinterpret_cast<Lut*>(smem_raw);
+  int8_t* act = reinterpret_cast<int8_t*>(smem_raw) + sizeof(Lut);
+  int* acc_s = reinterpret_cast<int*>(act + static_cast<size_t>(MT) * K);   // [groups][ROWS][MT]
+  int* asum = acc_s + max_groups * ROWS * MT;                                // [MT]
+  __shared__ int last_flag;
 
-  banked_init(table, tables, threadIdx.x, blockDim.x);
-  const int copy = threadIdx.x & (COPIES - 1);
-  stage_activations<MT>(act, a, M, K);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  e8p_lut_init(lut, tables, tid, THREADS);
+  for (int i = tid; i < max_groups * ROWS * MT + MT; i += THREADS) acc_s[i] = 0;
+  __syncthreads();
+  {
+    // stage the activations; their row sums ride along
+    const int chunks = MT * K / 16;
+    int part_sum[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) part_sum[m] = 0;
+    for (int c = tid; c < chunks; c += THREADS) {
+      const int m = (c * 16) / K;
+      int4 v = make_int4(0, 0, 0, 0);
+      if (m < M) v = *reinterpret_cast<const int4*>(a + static_cast<size_t>(c) * 16);
+      *reinterpret_cast<int4*>(act + static_cast<size_t>(c) * 16) = v;
+      int s = __dp4a(v.x, 0x01010101, 0);
+      s = __dp4a(v.y, 0x01010101, s);
+      s = __dp4a(v.z, 0x01010101, s);
+      s = __dp4a(v.w, 0x01010101, s);
+#pragma unroll
+      for (int mm = 0; mm < MT; ++mm)
+        if (mm == m) part_sum[mm] += s;
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      int s = part_sum[m];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (lane == 0 && s != 0) atomicAdd(&asum[m], s);
+    }
+  }
   __syncthreads();
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = lane / LPR, part = lane % LPR;
-  const int kblocks = K / 128;
+  const int kb_all = K / 128;
   const int groups = (N + ROWS - 1) / ROWS;
+  const int np = blockIdx.x % n_parts, kp = blockIdx.x / n_parts;
+  const int g_lo = static_cast<int>(static_cast<long long>(groups) * np / n_parts);
+  const int g_hi = static_cast<int>(static_cast<long long>(groups) * (np + 1) / n_parts);
+  const int kb_lo = kb_all * kp / k_parts, kb_hi = kb_all * (kp + 1) / k_parts;
+  const int kbs = kb_hi - kb_lo;
+  const int units = (g_hi - g_lo) * kbs;
+  constexpr int NW = THREADS / 32;
+  const int u_lo = static_cast<int>(static_cast<long long>(units) * warp / NW);
+  const int u_hi = static_cast<int>(static_cast<long long>(units) * (warp + 1) / NW);
+
   int acc[MT];
 #pragma unroll
   for (int m = 0; m < MT; ++m) acc[m] = 0;
+  const int copy = lane;                                   // GEMV_COPIES == 32
 
-  // position of this warp in its (group, k-block batch) sequence
-  int g = blockIdx.x, kb0 = warp, parity = 0;
-  auto load_batch = [&](int gg, int kk, uint4 (&dst)[DEPTH]) {
-    const int n = min(gg * ROWS + row, N - 1);
+  if (u_lo < u_hi) {
+    // (group, k-block) of the unit being loaded, and of the unit being consumed
+    int lg = g_lo + u_lo / kbs, lkb = kb_lo + u_lo % kbs;
+    int g = lg, kb = lkb;
+    uint4 buf[DEPTH];
+    auto fetch = [&](int uu) -> uint4 {
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (uu < u_hi) {
+        const int n = min(lg * ROWS + row, N - 1);
+        v = __ldg(w + (static_cast<size_t>(lkb) * N + n) * LPR + part);
+        if (++lkb == kb_hi) {
+          lkb = kb_lo;
+          ++lg;
+        }
+      }
+      return v;
+    };
 #pragma unroll
-    for (int i = 0; i < DEPTH; ++i) {
-      const int kb = kk + GEMV_WARPS * i;
-      dst[i] = make_uint4(0, 0, 0, 0);
-      if (gg < groups && kb < kblocks)
-        dst[i] = __ldg(w + (static_cast<size_t>(kb) * N + n) * LPR + part);
-    }
-  };
-  uint4 cur[DEPTH], nxt[DEPTH];
-  load_batch(g, kb0, cur);
-  while (g < groups) {
-    int ng = g, nkb = kb0 + GEMV_WARPS * DEPTH;
-    if (nkb >= kblocks) {
-      ng = g + gridDim.x;
-      nkb = warp;
-    }
-    load_batch(ng, nkb, nxt);
+    for (int i = 0; i < DEPTH; ++i) buf[i] = fetch(u_lo + i);
+    for (int base = u_lo; base < u_hi; base += DEPTH) {
 #pragma unroll
-    for (int i = 0; i < DEPTH; ++i) {
-      const int kb = kb0 + GEMV_WARPS * i;
-      if (kb < kblocks) {
-        const int8_t* abase = act + kb * 128 + part * WPL;
-        const uint32_t words[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
-        if (FMT == 1) {
+      for (int i = 0; i < DEPTH; ++i) {
+        const uint4 cur = buf[i];
+        buf[i] = fetch(base + i + DEPTH);
+        if (base + i < u_hi) {
+          const int8_t* abase = act + kb * 128 + part * WPL;
+          const uint32_t words[4] = {cur.x, cur.y, cur.z, cur.w};
+          if (FMT == 1) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint2 q = banked_decode_q4(words[j], table, copy);
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t v0 = e8p_fields<GEMV_COPIES, 0>(words[j], lut, copy);
+              const uint32_t v1 = e8p_fields<GEMV_COPIES, 1>(words[j], lut, copy);
+              const int xlo = static_cast<int>((v0 & E8P_NIB) * 4u + (v1 & E8P_NIB));
+              const int xhi = static_cast<int>(((v0 >> 4) & E8P_NIB) * 4u + ((v1 >> 4) & E8P_NIB));
 #pragma unroll
-            for (int m = 0; m < MT; ++m) {
-              const int2 av = *reinterpret_cast<const int2*>(abase + m * K + j * 8);
-              acc[m] = __dp4a(static_cast<int>(q.x), av.x, acc[m]);
-              acc[m] = __dp4a(static_cast<int>(q.y), av.y, acc[m]);
+              for (int m = 0; m < MT; ++m) {
+                const int2 av = *reinterpret_cast<const int2*>(abase + m * K + j * 8);
+                acc[m] = __dp4a(xlo, av.x, acc[m]);
+                acc[m] = __dp4a(xhi, av.y, acc[m]);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t v = (j & 1) ? e8p_fields<GEMV_COPIES, 1>(words[j >> 1], lut, copy)
+                                         : e8p_fields<GEMV_COPIES, 0>(words[j >> 1], lut, copy);
+              const int xlo = static_cast<int>(v & E8P_NIB);
+              const int xhi = static_cast<int>((v >> 4) & E8P_NIB);
+#pragma unroll
+              for (int m = 0; m < MT; ++m) {
+                const int2 av = *reinterpret_cast<const int2*>(abase + m * K + j * 8);
+                acc[m] = __dp4a(xlo, av.x, acc[m]);
+                acc[m] = __dp4a(xhi, av.y, acc[m]);
+              }
             }
           }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t code = (words[j >> 1] >> ((j & 1) * 16)) & 0xffffu;
-            const uint2 q = banked_decode8(code, table, copy);
+          const bool last_of_group = kb + 1 == kb_hi, last_unit = base + i + 1 == u_hi;
+          if (last_of_group || last_unit) {
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
-              const int2 av = *reinterpret_cast<const int2*>(abase + m * K + j * 8);
-              acc[m] = __dp4a(static_cast<int>(q.x), av.x, acc[m]);
-              acc[m] = __dp4a(static_cast<int>(q.y), av.y, acc[m]);
+              int v = acc[m];
+#pragma unroll
+              for (int o = 1; o < LPR; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+              if (part == 0) atomicAdd(&acc_s[((g - g_lo) * ROWS + row) * MT + m], v);
+              acc[m] = 0;
             }
+          }
+          if (last_of_group) {
+            kb = kb_lo;
+            ++g;
+          } else {
+            ++kb;
           }
         }
       }
     }
-    if (ng != g) {
-      // group finished: combine lanes, then warps (double-buffered, one barrier per group)
-#pragma unroll
-      for (int m = 0; m < MT; ++m) {
-#pragma unroll
-        for (int o = 1; o < LPR; o <<= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
-        if (part == 0) red[parity][warp][row][m] = acc[m];
-        acc[m] = 0;
+  }
+  __syncthreads();
+
+  // sum_k a_k w_k from the staged integers: Q4 2*acc - 75*S, Q2 2*acc - 15*S
+  constexpr int BIAS = FMT == 1 ? 75 : 15;
+  const int n_base = g_lo * ROWS;
+  const int n_count = min(g_hi * ROWS, N) - n_base;        // output columns of this n-part
+  bool finalize = true;
+  if (k_parts > 1) {
+    // add this CTA's integers to the workspace; the last CTA of the n-part finishes
+    for (int i = tid; i < n_count * MT; i += THREADS) {
+      const int m = i / n_count, r = i % n_count;
+      const int v = acc_s[r * MT + m];
+      if (m < M && v != 0) atomicAdd(ws + static_cast<size_t>(m) * GEMV_WS_COLS + n_base + r, v);
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      unsigned int* ticket = reinterpret_cast<unsigned int*>(ws + 8 * GEMV_WS_COLS) + np;
+      const unsigned int t = atomicAdd(ticket, 1u);
+      last_flag = t == static_cast<unsigned int>(k_parts - 1);
+      if (last_flag) *ticket = 0;
+    }
+    __syncthreads();
+    finalize = last_flag != 0;
+    if (finalize) {
+      __threadfence();
+      for (int i = tid; i < n_count * MT; i += THREADS) {
+        const int m = i / n_count, r = i % n_count;
+        int v = 0;
+        if (m < M) {
+          int* p = ws + static_cast<size_t>(m) * GEMV_WS_COLS + n_base + r;
+          v = __ldcg(p);
+          *p = 0;
+        }
+        acc_s[r * MT + m] = v;
       }
       __syncthreads();
-      const int n0 = g * ROWS;
-      if (peer != nullptr && n0 + ROWS <= N) {
-        // peers get whole 16-byte segments (8 consecutive outputs of one row per store):
-        // 2-byte remote stores would each become their own NVLink write
-        for (int i = threadIdx.x; i < (ROWS / 8) * MT; i += blockDim.x) {
-          const int m = i % MT, seg = i / MT;
-          if (m < M) {
-            __align__(16) __half h[8];
-            const float sa = a_scale[m];
+    }
+  }
+  if (finalize) {
+    if (peer != nullptr && n_count % 8 == 0) {
+      // peers get whole 16-byte segments (8 consecutive outputs of one row per store):
+      // 2-byte remote stores would each become their own NVLink write
+      const int segs = n_count / 8;
+      for (int i = tid; i < segs * MT; i += THREADS) {
+        const int m = i / segs, seg = i % segs;
+        if (m < M) {
+          __align__(16) __half h[8];
+          const float sa = a_scale[m];
+          const int bias = BIAS * asum[m];
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {
-              int total = 0;
-#pragma unroll
-              for (int wv = 0; wv < GEMV_WARPS; ++wv) total += red[parity][wv][seg * 8 + r][m];
-              h[r] = __float2half_rn(
-                  (static_cast<float>(total) * __half2float(w_scale[n0 + seg * 8 + r])) * sa);
-            }
-            if (ll) {
-              ll_store8(po, ll_seq, m, n0 + seg * 8, N, h);
-            } else {
-              const size_t off =
-                  (static_cast<size_t>(po.rank) * po.rows_cap + m) * N + n0 + seg * 8;
-              for (int d = 0; d < po.tp; ++d)
-                *reinterpret_cast<int4*>(po.inbox[d] + off) = *reinterpret_cast<const int4*>(h);
-            }
+          for (int r = 0; r < 8; ++r) {
+            const int total = 2 * acc_s[(seg * 8 + r) * MT + m] - bias;
+            h[r] = __float2half_rn(
+                (static_cast<float>(total) * __half2float(w_scale[n_base + seg * 8 + r])) * sa);
           }
-        }
-      } else {
-        for (int i = threadIdx.x; i < ROWS * MT; i += blockDim.x) {
-          const int r = i / MT, m = i % MT;
-          if (n0 + r < N && m < M) {
-            int total = 0;
-#pragma unroll
-            for (int wv = 0; wv < GEMV_WARPS; ++wv) total += red[parity][wv][r][m];
-            store_row<MT>(out, out_f32, m, n0 + r, N, total, __half2float(w_scale[n0 + r]),
-                          a_scale[m], peer);
+          if (ll) {
+            ll_store8(po, ll_seq, m, n_base + seg * 8, N, h);
+          } else {
+            const size_t off =
+                (static_cast<size_t>(po.rank) * po.rows_cap + m) * N + n_base + seg * 8;
+            for (int d = 0; d < po.tp; ++d)
+              *reinterpret_cast<int4*>(po.inbox[d] + off) = *reinterpret_cast<const int4*>(h);
           }
         }
       }
-      parity ^= 1;
+    } else {
+      for (int i = tid; i < n_count * MT; i += THREADS) {
+        const int m = i / n_count, r = i % n_count;
+        if (m < M) {
+          const int total = 2 * acc_s[r * MT + m] - BIAS * asum[m];
+          store_row<MT>(out, out_f32, m, n_base + r, N, total, __half2float(w_scale[n_base + r]),
+                        a_scale[m], peer);
+        }
+      }
     }
-    g = ng;
-    kb0 = nkb;
-#pragma unroll
-    for (int i = 0; i < DEPTH; ++i) cur[i] = nxt[i];
   }
   if (ll) ll_done(po, ll_seq, gridDim.x);
   else if (peer != nullptr) peer_signal_done(po, gridDim.x);
@@ -294,24 +340,47 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32) w8_gemv_kernel(
   if (peer != nullptr) peer_signal_done(po, gridDim.x);
 }
 
+// Grid shape of the E8P GEMV: n_parts x k_parts CTAs on the 148 SMs.  K is split (2, 4 or
+// 8 ways, at least 4 k-blocks each) when whole row groups divide badly over the SMs.
+struct GemvGrid {
+  int n_parts, k_parts, max_groups;
+};
+static GemvGrid gemv_grid(int rows_per_group, int N, int K) {
+  const int groups = (N + rows_per_group - 1) / rows_per_group, kb = K / 128;
+  GemvGrid best{groups < 148 ? groups : 148, 1, 0};
+  double best_eff = 0.0;
+  for (int kp = 1; kp <= 8; kp *= 2) {
+    if (kp > 1 && (kb / kp < 4 || N > GEMV_WS_COLS || 148 / kp > GEMV_WS_TICKETS)) break;
+    const int np = groups < 148 / kp ? groups : 148 / kp;
+    const int per = (groups + np - 1) / np;
+    double eff = (static_cast<double>(groups) / np / per) * (static_cast<double>(np) * kp / 148.0);
+    if (kp > 1) eff *= 0.97;                       // the workspace round trip is not free
+    if (eff > best_eff + 1e-9) {
+      best_eff = eff;
+      best = GemvGrid{np, kp, 0};
+    }
+  }
+  best.max_groups = (groups + best.n_parts - 1) / best.n_parts;
+  return best;
+}
+
 template <int FMT, int MT>
 static int launch_e8p(const int8_t* a, const float* as, const void* w, const __half* ws, void* out,
                       int M, int N, int K, int out_f32, cudaStream_t stream, const PeerOut& po) {
   constexpr int ROWS = FMT == 1 ? 8 : 16;
-  const size_t smem = sizeof(E8pBanked<(MT == 1 ? 1 : 16)>) + static_cast<size_t>(MT) * K;
-  if (smem > 200 * 1024) return -1;
-  static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(e8p_gemv_kernel<FMT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         200 * 1024);
-    attr = true;
+  const GemvGrid g = gemv_grid(ROWS, N, K);
+  const size_t smem = sizeof(E8pLut<GEMV_COPIES>) + static_cast<size_t>(MT) * K +
+                      (static_cast<size_t>(g.max_groups) * ROWS * MT + MT) * sizeof(int);
+  if (smem > 220 * 1024) return -1;
+  static const int slot = runtime_new_slot();
+  if (runtime_first_use(slot)) {
+    cudaError_t e = cudaFuncSetAttribute(e8p_gemv_kernel<FMT, MT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
   }
-  const int groups = (N + ROWS - 1) / ROWS;
-  const int per_sm = smem > 110 * 1024 ? 1 : (smem > 72 * 1024 ? 2 : (smem > 54 * 1024 ? 3 : 4));
-  const int grid = groups < 148 * per_sm ? groups : 148 * per_sm;
-  e8p_gemv_kernel<FMT, MT><<<grid, GEMV_WARPS * 32, smem, stream>>>(
+  e8p_gemv_kernel<FMT, MT><<<g.n_parts * g.k_parts, GemvThreads<MT>::value, smem, stream>>>(
       a, as, reinterpret_cast<const uint4*>(w), ws, out, M, N, K, out_f32, runtime_e8p_tables(),
-      po);
+      po, g.n_parts, g.k_parts, g.max_groups, runtime_gemv_workspace());
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -320,12 +389,10 @@ static int launch_w8(const int8_t* a, const float* as, const void* w, const __ha
                      int M, int N, int K, int out_f32, cudaStream_t stream, const PeerOut& po) {
   const size_t smem = static_cast<size_t>(MT) * K;
   if (smem > 200 * 1024) return -1;
-  static bool attr = false;
-  if (!attr) {
+  static const int slot = runtime_new_slot();
+  if (runtime_first_use(slot))
     cudaFuncSetAttribute(w8_gemv_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          200 * 1024);
-    attr = true;
-  }
   w8_gemv_kernel<MT><<<(N + GEMV_WARPS - 1) / GEMV_WARPS, GEMV_WARPS * 32, smem, stream>>>(
       a, as, reinterpret_cast<const int8_t*>(w), ws, out, M, N, K, out_f32, po);
   return static_cast<int>(cudaGetLastError());

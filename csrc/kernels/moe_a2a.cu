@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(256) a2a_recv_prepare_kernel(
     for (int s = 0; s < tp && good; ++s) {
       const long long start = clock64();
       while (ld_acquire_sys(flag + s) < want) {
-        if (clock64() - start > WAIT_LIMIT_CYCLES) {
+        if (clock64() - start > wait_limit(status)) {
           report_status(status, STATUS_PEER_WAIT, 0x200 | s);
           good = 0;
           break;
@@ -126,7 +126,7 @@ __global__ void a2a_wait_kernel(const int* __restrict__ flag, const int* __restr
   for (int s = 0; s < tp; ++s) {
     const long long start = clock64();
     while (ld_acquire_sys(flag + s) < want) {
-      if (clock64() - start > WAIT_LIMIT_CYCLES) {
+      if (clock64() - start > wait_limit(status)) {
         report_status(status, STATUS_PEER_WAIT, 0x300 | s);
         return;
       }

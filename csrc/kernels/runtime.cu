@@ -1,7 +1,10 @@
-// Per-process runtime state of the kernel library: the device status word that
-// bounded waits report into, the E8P decode tables in device memory, and the
-// driver entry point used to encode TMA tensor maps.
+// Runtime state of the kernel library, one set per CUDA device: the status word that
+// bounded waits report into (plus the wait limit they read), the E8P decode tables, the
+// start-up workspaces, and the driver entry point used to encode TMA tensor maps.  Every
+// accessor answers for the device that is current on the calling thread, so a process that
+// drives several GPUs gets separate state on each.
 #include <cuda.h>
+#include <atomic>
 #include <mutex>
 
 #include "api.h"
@@ -12,55 +15,127 @@
 namespace orinfer {
 
 namespace {
-std::mutex g_mutex;
-bool g_ready = false;
-int* g_status = nullptr;
-E8pTables* g_tables = nullptr;
-PFN_encodeTiled g_encode = nullptr;
-int8_t g_basis[256][8];
-int* g_splitk = nullptr;
+constexpr int MAX_DEVICES = 64;
+constexpr int MAX_SLOTS = 256;
 
-uint32_t pack4(int a, int b, int c, int d) {
-  return (static_cast<uint32_t>(a & 0xff)) | (static_cast<uint32_t>(b & 0xff) << 8) |
-         (static_cast<uint32_t>(c & 0xff) << 16) | (static_cast<uint32_t>(d & 0xff) << 24);
+struct DeviceState {
+  bool ready = false;
+  int* status = nullptr;          // int32 [4]: status, -, wait limit / 1024 cycles, -
+  E8pTables* tables = nullptr;
+  int* splitk = nullptr;
+  int* gemv_ws = nullptr;
+  bool used[MAX_SLOTS] = {};
+};
+
+std::mutex g_mutex;
+DeviceState g_dev[MAX_DEVICES];
+PFN_encodeTiled g_encode = nullptr;
+std::atomic<int> g_slots{0};
+
+int current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return -1;
+  return dev;
+}
+
+// Position of coordinate c's 4-bit field inside a table word.
+int field_of(int c) { return c < 4 ? 2 * c : 2 * (c - 4) + 1; }
+
+void build_tables(E8pTables* host) {
+  static const int coord_bit[8] = {0, 4, 1, 5, 2, 6, 3, 7};
+  int8_t basis[256][8];
+  build_e8p_basis(basis);
+  for (int i = 0; i < 256; ++i) {
+    uint32_t e = 0, s = 0;
+    const int par = __builtin_popcount(i) & 1;
+    const int flips = i ^ par;
+    for (int c = 0; c < 8; ++c) {
+      const uint32_t u = static_cast<uint32_t>((basis[i][c] + 14) / 4);       // 1..6
+      e |= (2u * u) << (4 * field_of(c));
+      const uint32_t f = (flips >> coord_bit[c]) & 1;
+      s |= ((f ? 0xEu : 0u) | static_cast<uint32_t>(1 - par)) << (4 * field_of(c));
+    }
+    host->e2[i] = e;
+    host->sg[i] = s;
+  }
 }
 }  // namespace
 
 cudaError_t runtime_ensure_init() {
+  const int dev = current_device();
+  if (dev < 0) return cudaErrorInvalidDevice;
   std::lock_guard<std::mutex> lock(g_mutex);
-  if (g_ready) return cudaSuccess;
-  build_e8p_basis(g_basis);
+  DeviceState& d = g_dev[dev];
+  if (d.ready) return cudaSuccess;
   static E8pTables host;
-  for (int i = 0; i < 256; ++i) {
-    int pos[8];
-    for (int d = 0; d < 8; ++d) pos[d] = g_basis[i][d] + 24;
-    host.pos[i] = make_uint2(pack4(pos[0], pos[1], pos[2], pos[3]),
-                             pack4(pos[4], pos[5], pos[6], pos[7]));
+  build_tables(&host);
+  cudaError_t e = cudaMalloc(&d.status, 4 * sizeof(int));
+  if (e != cudaSuccess) return e;
+  const int init[4] = {0, 0, static_cast<int>(WAIT_LIMIT_CYCLES >> 10), 0};
+  e = cudaMemcpy(d.status, init, sizeof(init), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return e;
+  e = cudaMalloc(&d.tables, sizeof(E8pTables));
+  if (e != cudaSuccess) return e;
+  e = cudaMemcpy(d.tables, &host, sizeof(E8pTables), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return e;
+  e = cudaMalloc(&d.splitk, SPLITK_WORKSPACE_BYTES);
+  if (e != cudaSuccess) return e;
+  const size_t ws = (static_cast<size_t>(8) * GEMV_WS_COLS + GEMV_WS_TICKETS) * sizeof(int);
+  e = cudaMalloc(&d.gemv_ws, ws);
+  if (e != cudaSuccess) return e;
+  e = cudaMemset(d.gemv_ws, 0, ws);
+  if (e != cudaSuccess) return e;
+  if (g_encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess) return e;
+    if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return cudaErrorNotSupported;
+    g_encode = reinterpret_cast<PFN_encodeTiled>(fn);
   }
-  cudaError_t e = cudaMalloc(&g_status, 4 * sizeof(int));
-  if (e != cudaSuccess) return e;
-  e = cudaMemset(g_status, 0, 4 * sizeof(int));
-  if (e != cudaSuccess) return e;
-  e = cudaMalloc(&g_tables, sizeof(E8pTables));
-  if (e != cudaSuccess) return e;
-  e = cudaMemcpy(g_tables, &host, sizeof(E8pTables), cudaMemcpyHostToDevice);
-  if (e != cudaSuccess) return e;
-  e = cudaMalloc(&g_splitk, SPLITK_WORKSPACE_BYTES);
-  if (e != cudaSuccess) return e;
-  void* fn = nullptr;
-  cudaDriverEntryPointQueryResult qres;
-  e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
-  if (e != cudaSuccess) return e;
-  if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return cudaErrorNotSupported;
-  g_encode = reinterpret_cast<PFN_encodeTiled>(fn);
-  g_ready = true;
+  d.ready = true;
   return cudaSuccess;
 }
 
-int* runtime_status_ptr() { return g_status; }
-int* runtime_splitk_workspace() { return g_splitk; }
-const E8pTables* runtime_e8p_tables() { return g_tables; }
+namespace {
+DeviceState* ready_state() {
+  const int dev = current_device();
+  if (dev < 0 || !g_dev[dev].ready) return nullptr;
+  return &g_dev[dev];
+}
+}  // namespace
+
+int* runtime_status_ptr() {
+  DeviceState* d = ready_state();
+  return d ? d->status : nullptr;
+}
+int* runtime_splitk_workspace() {
+  DeviceState* d = ready_state();
+  return d ? d->splitk : nullptr;
+}
+int* runtime_gemv_workspace() {
+  DeviceState* d = ready_state();
+  return d ? d->gemv_ws : nullptr;
+}
+const E8pTables* runtime_e8p_tables() {
+  DeviceState* d = ready_state();
+  return d ? d->tables : nullptr;
+}
 PFN_encodeTiled runtime_tma_encoder() { return g_encode; }
+
+int runtime_new_slot() {
+  const int s = g_slots.fetch_add(1);
+  return s < MAX_SLOTS ? s : -1;
+}
+
+bool runtime_first_use(int slot) {
+  const int dev = current_device();
+  if (dev < 0 || slot < 0 || slot >= MAX_SLOTS) return true;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_dev[dev].used[slot]) return false;
+  g_dev[dev].used[slot] = true;
+  return true;
+}
 
 }  // namespace orinfer
 
@@ -76,10 +151,30 @@ int orinfer_read_status(int* out4) {
                                      cudaMemcpyDeviceToHost));
 }
 
+// Copies the four status ints to (pinned) host memory behind the work already queued on
+// `stream`; no synchronisation.  The caller reads them after its own wait on that stream.
+int orinfer_status_async(int* host_out4, cudaStream_t stream) {
+  if (orinfer::runtime_ensure_init() != cudaSuccess) return -2;
+  return static_cast<int>(cudaMemcpyAsync(host_out4, orinfer::runtime_status_ptr(),
+                                          4 * sizeof(int), cudaMemcpyDeviceToHost, stream));
+}
+
 int orinfer_clear_status(void) {
   if (orinfer::runtime_ensure_init() != cudaSuccess) return -2;
-  return static_cast<int>(cudaMemset(orinfer::runtime_status_ptr(), 0, 4 * sizeof(int)));
+  return static_cast<int>(cudaMemset(orinfer::runtime_status_ptr(), 0, sizeof(int)));
 }
+
+// How long a bounded device wait spins before it gives up, in microseconds of a ~2 GHz clock.
+int orinfer_set_wait_limit_us(long long us) {
+  if (us < 1 || us > 60000000LL) return -1;
+  if (orinfer::runtime_ensure_init() != cudaSuccess) return -2;
+  const int k = static_cast<int>((us * 2000LL) >> 10) + 1;
+  return static_cast<int>(cudaMemcpy(orinfer::runtime_status_ptr() + orinfer::STATUS_LIMIT_WORD,
+                                     &k, sizeof(int), cudaMemcpyHostToDevice));
+}
+
+// Ordinal of the device whose runtime state the calling thread would use, or -1.
+int orinfer_current_device(void) { return orinfer::current_device(); }
 
 const void* orinfer_e8p_tables_device(void) {
   if (orinfer::runtime_ensure_init() != cudaSuccess) return nullptr;

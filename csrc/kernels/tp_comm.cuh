@@ -106,7 +106,7 @@ __device__ __forceinline__ bool ag_wait(const AgIn& in, int m_lo, int m_hi, int*
     if (ld_acquire_sys(in.flag + s) >= want) continue;
     const long long start = clock64();
     while (ld_acquire_sys(in.flag + s) < want) {
-      if (clock64() - start > WAIT_LIMIT_CYCLES) {
+      if (clock64() - start > wait_limit(status)) {
         report_status(status, STATUS_PEER_WAIT, 0x100 | s);
         return false;
       }
@@ -165,7 +165,7 @@ __device__ __forceinline__ bool ll_load4(const uint2* base, int seq, uint32_t& a
       b = v.z;
       return true;
     }
-    if (clock64() - start > WAIT_LIMIT_CYCLES) {
+    if (clock64() - start > wait_limit(status)) {
       report_status(status, STATUS_PEER_WAIT, 0x400 | s);
       a = b = 0;
       return false;
@@ -183,7 +183,7 @@ __device__ __forceinline__ bool inbox_wait(const InboxIn& in, int* status) {
       if (ld_acquire_sys(in.flag + s) >= want) continue;
       const long long start = clock64();
       while (ld_acquire_sys(in.flag + s) < want) {
-        if (clock64() - start > WAIT_LIMIT_CYCLES) {
+        if (clock64() - start > wait_limit(status)) {
           report_status(status, STATUS_PEER_WAIT, s);
           ok = 0;
           break;

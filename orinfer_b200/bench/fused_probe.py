@@ -16,7 +16,7 @@ and (bytes a rank must send over NVLink: (tp-1)/tp * M*H*2 for the reduce-scatte
 Run under torchrun, one rank per GPU::
 
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 \
-        -m orinfer_b200.parallel.fused_probe --rows 8192
+        -m orinfer_b200.bench.fused_probe --rows 8192
 
 Rank 0 prints one JSON line.  Times are CUDA-event times, max over ranks.
 """
@@ -34,10 +34,10 @@ import torch.distributed as dist
 from ..ops import functional as F
 from ..ops import native
 from ..ops.native import FMT, check, ptr, stream
-from ..utils.kernel_probe import peaks
-from . import fused
+from .kernel_probe import peaks
+from ..parallel import fused
 
-NVLINK_GBS = 770.0          # measured peer copy per direction per GPU on this pool
+NVLINK_GBS = 770.0          # measured peer copy per direction per GPU (B200, NVSwitch)
 
 
 def _weights(n, k, dev, seed):

@@ -1,8 +1,10 @@
 """Micro-benchmarks of single kernels with CUDA-event timing and roofline fractions.
 
-    python -m orinfer_b200.utils.kernel_probe gemm --m 512 --n 19456 --k 2560 --fmt q4
-    python -m orinfer_b200.utils.kernel_probe attn --tokens 2048
-    python -m orinfer_b200.utils.kernel_probe gemv --m 1 --n 19456 --k 2560 --fmt q4
+    python -m orinfer_b200.bench.kernel_probe gemm --m 512 --n 19456 --k 2560 --fmt q4
+    python -m orinfer_b200.bench.kernel_probe attn --tokens 2048
+    python -m orinfer_b200.bench.kernel_probe gemm --m 1 --n 19456 --k 2560 --fmt q4
+    python -m orinfer_b200.bench.kernel_probe attn-decode --rows 1 --ctx 512
+    python -m orinfer_b200.bench.kernel_probe act-prep --rows 1 --k 2560
 
 Each run does warm-up launches, then times ``--iters`` launches between two events on
 the launching stream (synchronised on both sides); with ``--rotate`` buffers larger than
@@ -87,12 +89,14 @@ def gemm(args, dev):
     sw = (torch.rand(n, device=dev) * 0.01).half()
     out = torch.empty(m, n, dtype=torch.float16, device=dev)
     path = {"auto": 0, "simt": 1, "tc": 2}[args.path]
+    native.qgemm_set_impl(args.impl)
     t = timed(lambda i: F.qgemm(a, sa, ws[i % copies], sw, args.fmt, n, out=out, path=path),
               args.iters)
     hbm, flops, tag = peaks()
     ops = 2.0 * m * n * k
     byts = wbytes + m * k + m * n * 2
-    print(json.dumps({"kernel": "qgemm", "fmt": args.fmt, "m": m, "n": n, "k": k, "us": t * 1e6,
+    print(json.dumps({"kernel": "qgemm", "impl": args.impl, "fmt": args.fmt, "m": m, "n": n, "k": k,
+                      "us": t * 1e6,
                       "tops": ops / t / 1e12, "gbs": byts / t / 1e9,
                       "frac_int8_peak": ops / t / (2 * flops), "frac_hbm": byts / t / hbm,
                       "peaks": tag, "int8_peak_assumed": "2 x bf16 cuBLAS burst"}))
@@ -116,6 +120,53 @@ def attn(args, dev):
     print(json.dumps({"kernel": "attention_prefill", "tokens": n, "qh": qh, "kvh": kvh, "d": d,
                       "us": t * 1e6, "tflops_causal": ops / t / 1e12,
                       "frac_f16_peak": ops / t / flops, "peaks": tag}))
+
+
+def attn_decode(args, dev):
+    """Row attention (decode steps): ``rows`` requests, each one query row over ``ctx`` keys."""
+    qh, kvh, d, rows, ctx = args.qh, args.kvh, args.d, args.rows, args.ctx
+    per = (ctx + 127) // 128
+    pages = rows * per
+    table = torch.arange(1, pages + 1, dtype=torch.int32, device=dev).view(rows, per)
+    kc = torch.randint(-127, 128, (pages + 1, 128, kvh, d), dtype=torch.int8, device=dev)
+    vc = torch.randint(-127, 128, (pages + 1, 128, kvh, d), dtype=torch.int8, device=dev)
+    ks = (torch.rand(pages + 1, 128, kvh, d // 64, device=dev) * 0.02).half()
+    vs = (torch.rand(pages + 1, 128, kvh, d // 64, device=dev) * 0.02).half()
+    q = torch.randn(rows, qh, d, device=dev).half()
+    out = torch.empty(rows, qh * d, dtype=torch.float16, device=dev)
+    row_req = torch.arange(rows, dtype=torch.int32, device=dev)
+    row_pos = torch.full((rows,), ctx - 1, dtype=torch.int32, device=dev)
+    splits = args.splits or min(F.attention_splits(ctx, rows, kvh), max(512 // rows, 1))
+    need = native.lib().orinfer_attention_scratch_bytes(rows, qh, d, splits)
+    scratch = torch.empty(max(need // 4, 1), dtype=torch.float32, device=dev)
+    t = timed(lambda i: F.attention(q, None, row_req, row_pos, table, kc, vc, ks, vs,
+                                    splits=splits, scratch=scratch, out=out), args.iters)
+    bw, _, tag = peaks()
+    moved = rows * ctx * kvh * (2 * d + 4 * (d // 64))
+    print(json.dumps({"kernel": "attention_rows", "rows": rows, "ctx": ctx, "qh": qh, "kvh": kvh,
+                      "d": d, "splits": splits, "us": t * 1e6, "gbs": moved / t / 1e9,
+                      "frac_hbm": moved / t / bw, "peaks": tag}))
+
+
+def act_prep(args, dev):
+    """Residual add + RMSNorm + rotation + A8 (``--swiglu``: SwiGLU + rotation + A8)."""
+    rows, k = args.rows, args.k
+    g = torch.Generator(device="cpu").manual_seed(0)
+    signs = (1 - 2 * torch.randint(0, 2, (k,), generator=g)).to(torch.int8).to(dev)
+    if args.swiglu:
+        x = torch.randn(rows, 2 * k, device=dev).half()
+        t = timed(lambda i: F.act_prep(x, None, None, signs, swiglu=True), args.iters)
+        moved = rows * (4 * k + k + 4)
+    else:
+        x = torch.randn(rows, k, device=dev).half()
+        resid = torch.randn(rows, k, device=dev)
+        w = torch.ones(k, device=dev).half()
+        t = timed(lambda i: F.act_prep(x, resid, w, signs, eps=1e-6), args.iters)
+        moved = rows * (2 * k + 8 * k + k + 4)
+    bw, _, tag = peaks()
+    print(json.dumps({"kernel": "act_prep", "swiglu": bool(args.swiglu), "rows": rows, "k": k,
+                      "us": t * 1e6, "gbs": moved / t / 1e9, "frac_hbm": moved / t / bw,
+                      "peaks": tag}))
 
 
 def gdn(args, dev):
@@ -153,6 +204,20 @@ def main():
     g.add_argument("--path", default="auto", choices=["auto", "simt", "tc"])
     g.add_argument("--rotate", action="store_true")
     g.add_argument("--iters", type=int, default=20)
+    g.add_argument("--impl", type=int, default=0, help="0 persistent kernel, 1 one tile per CTA")
+    ad = sub.add_parser("attn-decode")
+    ad.add_argument("--rows", type=int, default=1)
+    ad.add_argument("--ctx", type=int, default=512)
+    ad.add_argument("--qh", type=int, default=32)
+    ad.add_argument("--kvh", type=int, default=8)
+    ad.add_argument("--d", type=int, default=128)
+    ad.add_argument("--splits", type=int, default=0)
+    ad.add_argument("--iters", type=int, default=20)
+    pp = sub.add_parser("act-prep")
+    pp.add_argument("--rows", type=int, default=1)
+    pp.add_argument("--k", type=int, default=2560)
+    pp.add_argument("--swiglu", action="store_true")
+    pp.add_argument("--iters", type=int, default=20)
     a = sub.add_parser("attn")
     a.add_argument("--tokens", type=int, default=2048)
     a.add_argument("--qh", type=int, default=32)
@@ -171,7 +236,8 @@ def main():
     GRAPH = args.graph
     dev = torch.device("cuda:0")
     native.init()
-    {"gemm": gemm, "attn": attn, "gdn": gdn}[args.cmd](args, dev)
+    {"gemm": gemm, "attn": attn, "gdn": gdn, "attn-decode": attn_decode,
+     "act-prep": act_prep}[args.cmd](args, dev)
     st = native.read_status()
     if st:
         raise SystemExit(f"kernel status {st:#x}")

@@ -138,7 +138,28 @@ def cmd_serve(a) -> int:
     cfg, name = _model_identity(a)
     name = a.model if a.model != "qwen3.8-27b" or not a.preset else name
 
+    teams = []
+
     def factory():
+        if a.tp > 1:
+            # rank 0 (this process) leads: it starts the follower ranks, joins the process
+            # group, loads its shard and publishes every device command to the followers
+            import dataclasses
+
+            import torch
+            from .parallel.rank_worker import leader_engine
+            if torch.cuda.is_available() and torch.cuda.device_count() < a.tp:
+                raise SystemExit(f"--tp {a.tp} needs {a.tp} GPUs, "
+                                 f"{torch.cuda.device_count()} visible")
+            spec = dict(world=a.tp, device="cuda" if torch.cuda.is_available() else "cpu",
+                        preset=a.preset, model_dir=a.model_dir, max_context=a.max_context,
+                        load={**dataclasses.asdict(load), "cuda_graph": load.cuda_graph.value},
+                        sched={**dataclasses.asdict(sched), "policy": sched.policy.value})
+            engine, team = leader_engine(spec, deadline_s=max(a.step_timeout_ms / 1e3, 30.0))
+            teams.append(team)
+            print(f"MODEL READY {name}; tensor parallel over {a.tp} ranks", file=sys.stderr,
+                  flush=True)
+            return engine
         weights, _ = _weights(a)
         if a.preset:
             print(f"MODEL READY {name}; {weights.nbytes() / 2 ** 20:.0f} MiB of weights",
@@ -175,6 +196,11 @@ def cmd_serve(a) -> int:
         return 1
     service.stop(a.drain_timeout_ms)
     print("SCHEDULER " + json.dumps(service.worker.engine.stats.as_dict()), file=sys.stderr)
+    for team in teams:                                # graphs, peer mappings, followers, group
+        try:
+            service.worker.engine.close()
+        finally:
+            team.close()
     return 1 if service.lifecycle.state == "failed" else 0
 
 

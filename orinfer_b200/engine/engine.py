@@ -103,7 +103,12 @@ class Engine:
     def __init__(self, weights: ModelWeights, *, load: Optional[LoadOptions] = None,
                  sched: Optional[SchedulerOptions] = None, kv_pages: Optional[int] = None,
                  max_context: Optional[int] = None, max_rows: Optional[int] = None,
-                 runner=None):
+                 runner=None, channel=None):
+        # ``channel``: a parallel.rank_channel.LeaderChannel when this engine leads follower
+        # ranks: every device command (page-table row, packet, graph replay, sharded
+        # sampling) is published to them before it runs here, and they replay it through
+        # ``apply`` on an engine of their own that takes no decisions.
+        self.channel = channel
         self.w = weights
         self.cfg: ModelConfig = weights.config
         self.load = load or LoadOptions()
@@ -112,6 +117,18 @@ class Engine:
         self.sched.validate()
         self.device = weights.embed_q.device
         self.on_gpu = self.device.type == "cuda"
+        # The kernel library keeps its status word, decode tables and workspaces per device
+        # and answers for the device that is current on the calling thread: make the model's
+        # device current before anything is launched, and keep a pinned mirror of the status
+        # word that every step's token readback refreshes.
+        self.failed: Optional[Exception] = None
+        self._status = None
+        if self.on_gpu:
+            from ..ops import native
+            torch.cuda.set_device(self.device)
+            native.init()
+            native.expect_device(self.device)
+            self._status = native.StatusReader()
         # Recurrent (GDN) layers keep per-request state that cannot be rebuilt from KV pages.
         # A cached prefix of a hybrid model is therefore usable only at an endpoint where the
         # state was snapshotted (prompt end, periodic checkpoints): prefill chunks are cut at
@@ -231,6 +248,8 @@ class Engine:
         request queue: returns (mean-pooled, L2-normalised final hidden state fp32 [hidden],
         fp32 logits of the last position).  Used by the embeddings and rerank endpoints.
         Needs one free request slot and enough free KV pages (evicting cached prefixes)."""
+        if self.channel is not None:
+            raise ValueError("encoder passes are not supported by a multi-rank engine")
         n = len(tokens)
         if n == 0 or n > min(self.max_context, self.max_rows):
             raise ValueError(f"encoder input of {n} tokens is outside 1..{min(self.max_context, self.max_rows)}")
@@ -267,6 +286,69 @@ class Engine:
             self.pool.release(pages)
             self.free_slots.append(slot)
 
+    def prefill_device(self, ids: torch.Tensor) -> torch.Tensor:
+        """Prefill of one fresh prompt whose token ids are already on the device, up to its
+        first greedy token, without any host synchronisation: returns the device tensor that
+        will hold the token (valid once the stream has run).  The prompt takes a free request
+        slot and KV pages for the duration of the call only (nothing is cached), and runs
+        through the same full-graph prefill path as a queued request.  For device-timed
+        measurements and for callers that keep their own token stream on the GPU."""
+        if not self.on_gpu or self.recurrent or self.channel is not None:
+            raise ValueError("prefill_device needs a single-process CUDA engine of a "
+                             "non-recurrent model")
+        n = int(ids.numel())
+        if n < 1 or n > min(self.max_context, self.max_rows):
+            raise ValueError(f"prompt of {n} tokens is outside 1..{min(self.max_context, self.max_rows)}")
+        need = (n + PAGE_TOKENS - 1) // PAGE_TOKENS
+        if need > self.pool.available:
+            self._reclaim(need)
+        if not self.free_slots or need > self.pool.available:
+            raise MemoryError("no free slot or KV pages")
+        slot = self.free_slots.pop()
+        pages = self.pool.take(need)
+        try:
+            row = self.page_table_host[slot]
+            if list(row[:need]) != list(pages) or row[need:].any():
+                row[:] = 0
+                row[:need] = pages
+                self.page_table_dev[slot].copy_(torch.from_numpy(row), non_blocking=True)
+            cache = self.__dict__.setdefault("_pd_cache", {})
+            fixed = cache.get((n, slot))
+            if fixed is None:
+                dev = self.device
+                fixed = cache[(n, slot)] = (
+                    torch.full((n,), slot, dtype=torch.int32, device=dev),
+                    torch.arange(n, dtype=torch.int32, device=dev),
+                    torch.tensor([n - 1], device=dev),
+                    torch.tensor([[0, n, 0, slot]], dtype=torch.int32, device=dev))
+            req_rows, pos, sel, chunks = fixed
+            packet = Packet(ids.to(torch.int32), req_rows, pos, self.page_table_dev, n, n, sel,
+                            chunks=chunks, max_q_len=n)
+            out = None
+            if (self.cfg.head_dim in (64, 128)
+                    and self.load.cuda_graph.uses_graph(ExecPhase.PREFILL)
+                    and getattr(self.runner, "stage_hook", None) is None):
+                out = self._prefill_graph(packet, (n,), False)
+            if out is None:
+                out = self.runner.greedy(packet, need_logits=False)
+            self.stats.prefill_tokens += n
+            return out[0]
+        finally:
+            self.pool.release(pages)
+            self.free_slots.append(slot)
+
+    def close(self) -> None:
+        """Releases what must go before the process group and the CUDA context do: captured
+        graphs first (they hold the collective and peer-memory work they recorded), then the
+        runner's peer mappings."""
+        self._graphs.clear()
+        self.__dict__.pop("_prefill_graphs", None)
+        if self.on_gpu:
+            torch.cuda.synchronize()
+        closer = getattr(self.runner, "close", None)
+        if closer is not None:
+            closer()
+
     def cancel(self, req: Request) -> None:
         req.cancelled = True
 
@@ -288,6 +370,8 @@ class Engine:
         isolation oracle that batched, chunked, graph-replayed and speculative runs are checked
         against (the reference's crates/orinfer-engine/src/runtime/reference_generation.rs:5-6).
         No prefix cache, no graphs, no speculation; needs an idle engine."""
+        if self.channel is not None:
+            raise ValueError("generate_reference is not supported by a multi-rank engine")
         if self.running or self.waiting:
             raise RuntimeError("generate_reference needs an idle engine")
         prompt = list(map(int, prompt))
@@ -362,6 +446,11 @@ class Engine:
                     self.host_kv.free(h)
             victims = self.prefix.evict(min(short, self.host_kv.available), to_host=True)
             for node, page in victims:
+                # a node that was offloaded before and re-adopted a device page still owns
+                # its old host slot: give it back before the new copy takes one
+                stale = self.prefix.host_handle(node)
+                if stale >= 0:
+                    self.host_kv.free(stale)
                 self.prefix.set_host(node, self.host_kv.save(page))
             if victims:
                 self.host_kv.sync()                 # pages are reused right after this
@@ -445,10 +534,7 @@ class Engine:
                 self.stats.restored_snapshots += 1
             req.phase = Phase.PREFILL
             self._prefix_nodes[req.rid] = node_ids
-            row = self.page_table_host[req.slot]
-            row[:] = 0
-            row[:len(req.pages)] = req.pages
-            self.page_table_dev[req.slot].copy_(torch.from_numpy(row), non_blocking=True)
+            self._set_page_row(req.slot, req.pages)
             self.running.append(req)
             self.stats.admitted += 1
             admitted += 1
@@ -613,8 +699,34 @@ class Engine:
         return getattr(self, "_prefill_tok_s", None)
 
     # ------------------------------------------------------------------ one iteration
+    def _status_enqueue(self) -> None:
+        """Queue the status-word copy behind the step's kernels (no synchronisation)."""
+        if self._status is not None:
+            self._status.enqueue()
+
+    def _status_check(self) -> None:
+        """After the step's readback: a bounded device wait that ran out (peer flag, TMA or
+        MMA barrier) or a rejected index left its code in the status word.  The step's output
+        cannot be trusted and peers' counters may be out of step, so the engine fails closed:
+        this raises a fatal error now and on every later step."""
+        if self._status is None:
+            return
+        word = self._status.value()
+        if word:
+            from ..core.policy import EngineError, ErrorKind
+            code, detail = word >> 16, word & 0xffff
+            kind = ErrorKind.NCCL if code == 5 else ErrorKind.CUDA
+            names = {1: "TMA wait", 2: "MMA wait", 3: "epilogue wait", 4: "decode wait",
+                     5: "peer wait", 6: "rejected index"}
+            self.failed = EngineError(
+                kind, f"device status {word:#x}: {names.get(code, 'code %d' % code)} "
+                      f"(detail {detail:#x}); the engine is failed closed", word)
+            raise self.failed
+
     def step(self) -> List[Request]:
         """Run one packet; returns the requests that produced tokens."""
+        if self.failed is not None:
+            raise self.failed
         for r in list(self.running):
             if r.cancelled:
                 self._finish(r, "cancelled")
@@ -686,6 +798,61 @@ class Engine:
             return host[:n].clone()
         return host[:n].to(self.device, non_blocking=True)
 
+    # ------------------------------------------------------------------ device commands
+    def _publish(self, op: str, payload=None) -> None:
+        if self.channel is not None:
+            self.channel.publish(op, payload)
+
+    def _set_page_row(self, slot: int, pages: Sequence[int]) -> None:
+        pages = [int(p) for p in pages]
+        self._publish("page_row", (slot, pages))
+        row = self.page_table_host[slot]
+        row[:] = 0
+        row[:len(pages)] = pages
+        self.page_table_dev[slot].copy_(torch.from_numpy(row), non_blocking=True)
+
+    def apply(self, op: str, payload) -> None:
+        """Follower side: executes one published device command.  A follower engine takes no
+        decisions of its own and reads nothing back but its status word."""
+        if op == "page_row":
+            self._set_page_row(*payload)
+        elif op == "direct":
+            self._exec_direct(self._build_packet(payload), payload, False)
+        elif op == "decode":
+            self._exec_decode(*payload)
+        elif op == "sharded":
+            rows, options, uniforms = payload
+            self.runner.sample_sharded(rows, options, uniforms)
+        else:
+            raise ValueError(f"unknown device command {op!r}")
+        self._status_enqueue()
+
+    def _build_packet(self, spec: dict) -> Packet:
+        rows = len(spec["ids"])
+        packet = Packet(self._upload("ids", spec["ids"]), self._upload("req", spec["req"]),
+                        self._upload("pos", spec["pos"]), self.page_table_dev, rows,
+                        spec["max_kv"], self._upload("sel", spec["sel"]).long())
+        if self.recurrent:
+            packet.segments = self._upload("segs", spec["segs"]).view(-1, 4)
+            packet.row_first = self._upload("first", spec["first"])
+            packet.n_segments = len(spec["segs"]) // 4
+        if spec["chunks"] and self.on_gpu:
+            packet.chunks = self._upload("chunks", spec["chunks"]).view(-1, 4)
+            packet.max_q_len = max(spec["chunks"][1::4])
+            packet.decode_rows = spec["n_decode"]
+        return packet
+
+    def _exec_direct(self, packet: Packet, spec: dict, has_media: bool):
+        need = spec["need"]
+        graphed = None
+        if (self.on_gpu and spec["n_decode"] == 0 and spec["chunks"] and not self.recurrent
+                and not has_media
+                and getattr(self.runner, "stage_hook", None) is None
+                and self.cfg.head_dim in (64, 128)
+                and self.load.cuda_graph.uses_graph(ExecPhase.PREFILL)):
+            graphed = self._prefill_graph(packet, tuple(spec["chunks"][1::4]), need)
+        return graphed if graphed is not None else self.runner.greedy(packet, need_logits=need)
+
     def _run_direct(self, decoders: List[Request], chunks):
         t0 = time.monotonic()
         ids, req_rows, pos, logit_rows, order, chunk_rows = [], [], [], [], [], []
@@ -714,34 +881,24 @@ class Engine:
             dummy_logits = True
         else:
             dummy_logits = False
-        packet = Packet(self._upload("ids", ids), self._upload("req", req_rows),
-                        self._upload("pos", pos), self.page_table_dev, rows, max_kv,
-                        self._upload("sel", logit_rows).long())
-        has_media = self._attach_media(packet, decoders, chunks, chunk_rows, pos)
+        spec = dict(ids=ids, req=req_rows, pos=pos, sel=logit_rows, max_kv=max_kv,
+                    n_decode=n_decode, chunks=[v for c in chunk_rows for v in c],
+                    need=any(self._needs_logits(r) for r, _n, has in order if has))
         if self.recurrent:
             segs = [[i, 1, 0, 0] for i in range(n_decode)] + [[c[0], c[1], 0, 0] for c in chunk_rows]
-            first = list(range(n_decode)) + [c[0] for c in chunk_rows for _ in range(c[1])]
-            packet.segments = self._upload("segs", [v for g in segs for v in g]).view(-1, 4)
-            packet.row_first = self._upload("first", first)
-            packet.n_segments = len(segs)
-        if chunk_rows and self.on_gpu:
-            flat = [v for c in chunk_rows for v in c]
-            packet.chunks = self._upload("chunks", flat).view(-1, 4)
-            packet.max_q_len = max(c[1] for c in chunk_rows)
-            packet.decode_rows = n_decode
+            spec["segs"] = [v for g in segs for v in g]
+            spec["first"] = list(range(n_decode)) + [c[0] for c in chunk_rows for _ in range(c[1])]
+        self._publish("direct", spec)
+        packet = self._build_packet(spec)
+        has_media = self._attach_media(packet, decoders, chunks, chunk_rows, pos)
+        if has_media and self.channel is not None:
+            raise ValueError("media inputs are not supported by a multi-rank engine")
         t1 = time.monotonic()
         self.stats.batch_inputs_s += t1 - t0
-        need = any(self._needs_logits(r) for r, _n, has in order if has)
-        graphed = None
-        if (self.on_gpu and n_decode == 0 and chunk_rows and not self.recurrent
-                and not has_media
-                and getattr(self.runner, "stage_hook", None) is None
-                and self.cfg.head_dim in (64, 128)
-                and self.load.cuda_graph.uses_graph(ExecPhase.PREFILL)):
-            graphed = self._prefill_graph(packet, tuple(c[1] for c in chunk_rows), need)
-        tok, lg = graphed if graphed is not None else self.runner.greedy(packet,
-                                                                         need_logits=need)
+        tok, lg = self._exec_direct(packet, spec, has_media)
+        self._status_enqueue()
         tokens = tok.cpu()                           # one readback (synchronises)
+        self._status_check()
         if self.spec.enabled and self.runner_has_mtp():
             info, row0 = [], 0
             for r, n, _has in order:
@@ -854,23 +1011,16 @@ class Engine:
         self.stats.graph_hits += 1
         return e["tok"], e["lg"]
 
-    def _run_decode_graph(self, decoders: List[Request]):
-        t0 = time.monotonic()
-        n = len(decoders)
-        bucket = next(b for b in DECODE_BUCKETS if b >= n)
-        need = any(self._needs_logits(r) for r in decoders)
+    def _exec_decode(self, bucket: int, need: bool, ids, slots, pos) -> "_DecodeGraph":
+        """One pure-decode packet of ``bucket`` rows (padded): warm, capture at the second
+        use, replay afterwards.  Returns the graph record holding the output buffers."""
+        t1 = time.monotonic()
         g = self._graphs.get((bucket, need))
         if g is None:
             g = self._graphs[(bucket, need)] = _DecodeGraph(self, bucket)
-        pad = bucket - n
-        ids = [r.pending for r in decoders] + [0] * pad
-        slots = [r.slot for r in decoders] + [self.pad_slot] * pad
-        pos = [r.offset for r in decoders] + [0] * pad
         g.ids.copy_(self._upload("ids", ids), non_blocking=True)
         g.req.copy_(self._upload("req", slots), non_blocking=True)
         g.pos.copy_(self._upload("pos", pos), non_blocking=True)
-        t1 = time.monotonic()
-        self.stats.batch_inputs_s += t1 - t0
         if g.graph is None:
             g.trials += 1
             self.runner.greedy(g.packet, g.logits, g.tokens, need_logits=need)   # warm
@@ -893,7 +1043,24 @@ class Engine:
             from ..ops import native
             native.count_launches(getattr(g, "launches", 0))
             self.stats.graph_hits += 1
+        return g
+
+    def _run_decode_graph(self, decoders: List[Request]):
+        t0 = time.monotonic()
+        n = len(decoders)
+        bucket = next(b for b in DECODE_BUCKETS if b >= n)
+        need = any(self._needs_logits(r) for r in decoders)
+        pad = bucket - n
+        ids = [r.pending for r in decoders] + [0] * pad
+        slots = [r.slot for r in decoders] + [self.pad_slot] * pad
+        pos = [r.offset for r in decoders] + [0] * pad
+        self._publish("decode", (bucket, need, ids, slots, pos))
+        t1 = time.monotonic()
+        self.stats.batch_inputs_s += t1 - t0
+        g = self._exec_decode(bucket, need, ids, slots, pos)
+        self._status_enqueue()
         tokens = g.tokens[:n].cpu()
+        self._status_check()
         if self.spec.enabled and self.runner_has_mtp():
             self.spec.capture([(r, i, 1, r.offset) for i, r in enumerate(decoders)],
                               self.runner.final_hidden(n))
@@ -921,9 +1088,10 @@ class Engine:
             sel += 1
         if not rows:
             return {}
-        toks = self.runner.sample_sharded(
-            rows, [r.sampling for r in reqs],
-            [S.counter_uniform(r.sampling.seed, 0, len(r.generated)) for r in reqs])
+        options = [r.sampling for r in reqs]
+        uniforms = [S.counter_uniform(r.sampling.seed, 0, len(r.generated)) for r in reqs]
+        self._publish("sharded", (rows, options, uniforms))
+        toks = self.runner.sample_sharded(rows, options, uniforms)
         self.stats.sharded_samples += len(rows)
         return dict(zip(rows, toks))
 

@@ -185,7 +185,9 @@ class Speculator:
             packet.tentative = True
         need = any(not eng._plain(r) for r, _ in plans)
         tok_dev, logits = eng.runner.greedy(packet, need_logits=need)
+        eng._status_enqueue()
         tokens = tok_dev.cpu().tolist()
+        eng._status_check()
         produced, row = [], 0
         counts = []
         kept_rows = []

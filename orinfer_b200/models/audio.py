@@ -6,8 +6,8 @@ Contracts follow the reference's crates/orinfer-model-sdk/src/audio.rs (mel is
 ``(frames // 100) * 13 + ceil((frames % 100) / 8)``, i.e. three stride-2 stages over
 100-frame chunks; optional 104-feature attention windows) and
 crates/orinfer-api/src/server/audio.rs (decode -> mono -> 16 kHz -> log-mel on the CPU).
-Only RIFF/WAVE PCM and float containers are decoded here: the build machines carry no
-FLAC / MP3 / AAC / Ogg decoder library, and those uploads are refused with a clear error.
+Only RIFF/WAVE PCM and float containers are decoded here: no FLAC / MP3 / AAC / Ogg decoder
+library is a dependency of this package, and those uploads are refused with a clear error.
 """
 
 from __future__ import annotations

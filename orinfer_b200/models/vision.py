@@ -231,8 +231,8 @@ def mrope_tables(positions: torch.Tensor, head_dim: int, theta: float):
 # ------------------------------------------------------------------ encoder
 class VisionEncoder(torch.nn.Module):
     """Patch projection, 2-D rotary self-attention blocks over one image, and the 2x2 merger
-    projecting to the decoder width.  Weights are random-init from a seed (there are no
-    checkpoints on the build machines); the layout is the one a converted tower would fill."""
+    projecting to the decoder width.  Weights are random-init from a seed (no converter from a
+    checkpoint tower exists yet); the layout is the one a converted tower would fill."""
 
     def __init__(self, spec: VisionSpec, seed: int = 0):
         super().__init__()

@@ -139,11 +139,12 @@ def qgemm(a: torch.Tensor, a_scale: torch.Tensor, codes: torch.Tensor, w_scale: 
 
 
 def attention_splits(max_kv_len: int, rows: int, kvh: int) -> int:
-    """Split the key axis when there are too few (row, kv head) CTAs to fill 148 SMs."""
-    if max_kv_len <= 256:
+    """Split the key axis when there are too few (row, kv head) CTAs to fill 148 SMs: about
+    three CTAs per SM, at least 64 keys per split."""
+    if max_kv_len <= 128:
         return 1
-    want = max(1, (148 * 2) // max(rows * kvh, 1))
-    return int(max(1, min(want, (max_kv_len + 255) // 256, 32)))
+    want = max(1, (148 * 3) // max(rows * kvh, 1))
+    return int(max(1, min(want, (max_kv_len + 63) // 64, 32)))
 
 
 def attention(q: torch.Tensor, gate: Optional[torch.Tensor], row_req: torch.Tensor,

@@ -39,6 +39,10 @@ def _load() -> ctypes.CDLL:
         "orinfer_init": ([], I),
         "orinfer_read_status": ([P], I),
         "orinfer_clear_status": ([], I),
+        "orinfer_status_async": ([P, P], I),
+        "orinfer_set_wait_limit_us": ([c_longlong], I),
+        "orinfer_current_device": ([], I),
+        "orinfer_qgemm_set_impl": ([I], I),
         "orinfer_e8p_basis_host": ([P], I),
         "orinfer_embed_w8": ([P, P, P, P, I, I, I, P], I),
         "orinfer_act_prep": ([P, P, P, P, P, P, P, I, I, c_float, I, I, P], I),
@@ -123,6 +127,18 @@ def init() -> None:
     tables.load_default()
 
 
+def expect_device(device) -> None:
+    """The library answers for the CUDA device that is current on the calling thread; refuse
+    to go on when that is not the device the caller's tensors live on (kernels would run on
+    one GPU with another GPU's pointers)."""
+    want = torch.device(device)
+    index = want.index if want.index is not None else torch.cuda.current_device()
+    have = int(_load().orinfer_current_device())
+    if have != index:
+        raise KernelError(f"kernel library is bound to cuda:{have} on this thread but the "
+                          f"tensors are on cuda:{index}: call torch.cuda.set_device first")
+
+
 def read_status() -> int:
     """Synchronise and return the device status word (0 = no bounded wait ran out)."""
     buf = (c_int * 4)()
@@ -132,6 +148,33 @@ def read_status() -> int:
 
 def clear_status() -> None:
     check(_load().orinfer_clear_status(), "orinfer_clear_status")
+
+
+def set_wait_limit_us(us: int) -> None:
+    """How long a bounded device wait (peer flag, TMA / MMA barrier) spins before it records
+    a status and returns; about one second by default."""
+    check(_load().orinfer_set_wait_limit_us(int(us)), "orinfer_set_wait_limit_us")
+
+
+class StatusReader:
+    """Reads the device status word without a synchronisation of its own: ``enqueue()`` queues
+    a 16-byte copy into pinned memory behind the work already on the current stream, and
+    ``value()`` is valid once the caller has waited for that stream (which it does anyway to
+    read the step's tokens)."""
+
+    def __init__(self):
+        self.buf = torch.zeros(4, dtype=torch.int32).pin_memory()
+
+    def enqueue(self) -> None:
+        check(_load().orinfer_status_async(self.buf.data_ptr(), stream()), "orinfer_status_async")
+
+    def value(self) -> int:
+        return int(self.buf[0])
+
+
+def qgemm_set_impl(impl: int) -> None:
+    """0: persistent tcgen05 GEMM kernel (default); 1: one tile per CTA."""
+    check(_load().orinfer_qgemm_set_impl(int(impl)), "orinfer_qgemm_set_impl")
 
 
 def basis_host() -> torch.Tensor:

@@ -223,6 +223,18 @@ class FusedTPRunner(TPRunner):
         self._sp_rows_per, self._sp_total = 0, 0
         self._ll = os.environ.get("ORINFER_TP_LL", "1") != "0"
 
+    def close(self) -> None:
+        """Unmaps the peers' buffers and frees this rank's (collective: every rank arrives at
+        the barrier first, so nobody unmaps memory a peer's kernel may still write)."""
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        if dist.is_initialized() and self.world > 1:
+            dist.barrier(group=self.group)
+        a2a = getattr(self, "_a2a", None)
+        if a2a is not None and hasattr(a2a, "close"):
+            a2a.close()
+        self.mem.close()
+
     _SLOT = {"o": "o", "gdn_out": "o", "down": "down"}
 
     # a paused forward would leave partial sums in the peers' inboxes while other packets use

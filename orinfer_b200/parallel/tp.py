@@ -177,3 +177,64 @@ def shard_model(weights: ModelWeights, rank: int, world: int) -> ModelWeights:
     out.tp = lay                       # type: ignore[attr-defined]
     out.global_config = cfg            # type: ignore[attr-defined]
     return out
+
+
+def local_config(cfg: ModelConfig, lay: TPLayout) -> ModelConfig:
+    """The geometry one rank computes: its heads, its FFN slice; vocabulary and expert
+    count stay global."""
+    world = lay.world
+    return dataclasses.replace(
+        cfg, q_heads=lay.q_heads, kv_heads=lay.kv_heads,
+        ffn=(lay.ffn[1] - lay.ffn[0]) if cfg.ffn else cfg.ffn,
+        gdn_k_heads=cfg.gdn_k_heads // world if cfg.gdn_k_heads else 0,
+        gdn_v_heads=cfg.gdn_v_heads // world if cfg.gdn_v_heads else 0, mtp_layers=0)
+
+
+def random_shard(cfg: ModelConfig, rank: int, world: int, device, seed: int = 0) -> ModelWeights:
+    """Random-init N(0, 0.02) weights of ONE rank's shard, quantised to the configured
+    formats, created directly in the sharded geometry: no rank ever holds the whole model
+    (``shard_model(random_model(...))`` would need all of an 80B-class model on every GPU).
+
+    Tensors that tensor parallelism replicates (embedding, norms, router, shared expert) come
+    from a generator seeded alike on every rank, so all ranks route and embed identically;
+    sharded tensors come from a rank-specific generator.  The result has the same fields as
+    ``shard_model`` gives (``tp`` layout, ``global_config``)."""
+    from ..models.weights import _Init, quantize_linear
+    lay = layout(cfg, rank, world)
+    local = local_config(cfg, lay)
+    dev = torch.device(device)
+    own = _Init(local, seed + 7919 * (rank + 1), dev, False)
+    shared = _Init(local, seed, dev, False)
+    own.signs = shared.signs                         # one sign vector per width, rank-independent
+    lo, hi = split_blocks(cfg.experts, world)[rank] if cfg.experts else (0, 0)
+    layers: List[LayerWeights] = []
+    for i in range(cfg.layers):
+        dense_cfg = dataclasses.replace(local, experts=0, ffn=local.ffn or 128)
+        own.cfg = dense_cfg if cfg.experts else local
+        lw = own.layer(i, cfg.is_full_attention(i))
+        own.cfg = local
+        if cfg.experts:
+            lw.gate_up = lw.down = None
+            rows = cfg.experts + (1 if cfg.shared_expert_ffn else 0)
+            lw.router = shared.normal(rows, cfg.hidden).to(torch.float16)
+            lw.expert_gate_up = own.bank(hi - lo, 2 * cfg.expert_ffn, cfg.hidden, cfg.expert_format)
+            lw.expert_down = own.bank(hi - lo, cfg.hidden, cfg.expert_ffn, cfg.expert_format)
+            lw.expert_gate_up.base = lw.expert_down.base = lo
+            if cfg.shared_expert_ffn:
+                lw.shared_gate_up = shared.linear(2 * cfg.shared_expert_ffn, cfg.hidden,
+                                                  cfg.proj_format)
+                lw.shared_down = shared.linear(cfg.hidden, cfg.shared_expert_ffn, cfg.proj_format)
+            lw.shared_owner = i % world
+        layers.append(lw)
+    emb = quantize_linear(shared.normal(cfg.vocab, cfg.hidden), "w8", None)
+    v0, v1 = lay.vocab
+    if cfg.tied_embeddings:
+        head = QLinear("w8", v1 - v0, cfg.hidden, emb.codes[v0:v1].contiguous(),
+                       emb.scale[v0:v1].contiguous(), None)
+    else:
+        head = own.linear(v1 - v0, cfg.hidden, cfg.head_format, rotate=False)
+    out = ModelWeights(local, emb.codes, emb.scale, layers, shared.ones(cfg.hidden), head,
+                       shared.signs, None, None)
+    out.tp = lay                       # type: ignore[attr-defined]
+    out.global_config = cfg            # type: ignore[attr-defined]
+    return out

@@ -76,7 +76,7 @@ def tune_shape(fmt: str, n: int, k: int, ranges, iters: int, margin: float, dev,
                ) -> List[GemmVariant]:
     from ..ops import functional as F
     from ..ops import native
-    from ..utils import kernel_probe as KP
+    from ..bench import kernel_probe as KP
     lib = native.lib()
     wbytes = n * k * {"w8": 1.0, "q4": 0.5, "q2": 0.25}[fmt]
     copies = max(2, int(256e6 // wbytes) + 1)

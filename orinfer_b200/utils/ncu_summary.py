@@ -160,7 +160,7 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     text = sys.stdin.read() if a.csv == "-" else open(a.csv).read()
     launches = [l for l in parse(text) if a.kernel in l.kernel]
-    from .kernel_probe import peaks
+    from ..bench.kernel_probe import peaks
     sys.stdout.write(render(launches, a.flops, a.bytes, peaks()))
     return 0
 

@@ -37,12 +37,13 @@ def test_embed_w8(cuda):
     assert torch.equal(out.float(), R.embed_w8(ids, table, scale))
 
 
-@pytest.mark.parametrize("k", [128, 256, 2560])
+@pytest.mark.parametrize("k,m", [(128, 19), (256, 19), (2560, 19), (2560, 3), (5120, 1),
+                                 (1152, 16)])
 @pytest.mark.parametrize("mode", ["norm_rot", "rot", "norm", "plain", "zero"])
-def test_act_prep(cuda, k, mode):
+def test_act_prep(cuda, k, m, mode):
+    """m <= 16 with at least 8 blocks of 128 channels runs as a cluster of CTAs per row."""
     from orinfer_b200.ops import functional as F
     g = torch.Generator().manual_seed(k)
-    m = 19
     x = (torch.randn(m, k, generator=g) * 0.5).half().to(cuda)
     if mode == "zero":
         x.zero_()
@@ -60,10 +61,10 @@ def test_act_prep(cuda, k, mode):
     _codes_close(q, q_ref, 0.02)
 
 
-def test_act_prep_swiglu(cuda):
+@pytest.mark.parametrize("m,f", [(11, 512), (2, 2560), (1, 9728), (40, 1280)])
+def test_act_prep_swiglu(cuda, m, f):
     from orinfer_b200.ops import functional as F
     g = torch.Generator().manual_seed(3)
-    m, f = 11, 512
     gu = torch.randn(m, 2 * f, generator=g).half().to(cuda)
     sg = _signs(f, cuda)
     q, s = F.act_prep(gu, None, None, sg, swiglu=True)
@@ -102,9 +103,15 @@ def _rand_weight(fmt, n, k, dev, seed):
     (512, 2560, 9728, 0), (100, 2560, 4096, 0), (300, 1024, 2560, 0), (512, 6144, 2560, 0),
     # one M tile, a few weight tiles more than SMs: full wave + split-K tail launch
     (512, 19456, 1024, 0), (100, 19968, 1024, 0),
+    # persistent kernel: several tiles per CTA, last M tile with one active sub-tile, 8 k-blocks
+    (1100, 19456, 1024, 0), (2100, 9728, 384, 0),
+    # K-split GEMV shapes (narrow N) and a wide one
+    (1, 2560, 9728, 1), (7, 6144, 2560, 1), (2, 320, 1280, 1), (1, 19456, 2560, 1),
 ])
 def test_qgemm(cuda, fmt, m, n, k, path):
     from orinfer_b200.ops import functional as F
+    from orinfer_b200.ops import native
+    native.qgemm_set_impl(0)
     g = torch.Generator().manual_seed(m * 7 + n)
     a = torch.randint(-127, 128, (m, k), generator=g, dtype=torch.int8).to(cuda)
     sa = (torch.rand(m, generator=g) * 0.05 + 1e-3).to(cuda)
@@ -115,6 +122,26 @@ def test_qgemm(cuda, fmt, m, n, k, path):
         torch.cuda.synchronize()
         assert torch.equal(out.float(), ref), \
             f"max diff {float((out.float() - ref).abs().max())}"
+
+
+@pytest.mark.parametrize("fmt", ["w8", "q4"])
+@pytest.mark.parametrize("m,n,k", [(600, 19456, 256), (512, 2560, 9728), (100, 12800, 256),
+                                   (513, 2560, 1024)])
+def test_qgemm_one_tile_per_cta_form(cuda, fmt, m, n, k):
+    """The non-persistent kernel gives the same bits as the persistent one."""
+    from orinfer_b200.ops import functional as F
+    from orinfer_b200.ops import native
+    g = torch.Generator().manual_seed(m + n)
+    a = torch.randint(-127, 128, (m, k), generator=g, dtype=torch.int8).to(cuda)
+    sa = (torch.rand(m, generator=g) * 0.05 + 1e-3).to(cuda)
+    codes, ws, w_int = _rand_weight(fmt, n, k, cuda, seed=k + n)
+    try:
+        native.qgemm_set_impl(1)
+        out = F.qgemm(a, sa, codes, ws, fmt, n)
+        torch.cuda.synchronize()
+    finally:
+        native.qgemm_set_impl(0)
+    assert torch.equal(out.float(), R.qgemm(a, sa, w_int, ws))
 
 
 def test_qgemm_graph_replay_changed_inputs(cuda):
@@ -165,7 +192,7 @@ def _gather_kv(table, cache, scale, req, length):
 
 
 @pytest.mark.parametrize("qh,kvh,d", [(4, 2, 64), (32, 8, 128), (40, 8, 128), (16, 2, 256)])
-@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("splits", [1, 3, 8])
 def test_attention_rows(cuda, qh, kvh, d, splits):
     from orinfer_b200.ops import functional as F
     lens = [1, 130, 300]

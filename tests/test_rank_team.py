@@ -1,0 +1,120 @@
+"""Leader / follower ranks of a multi-rank engine on CPU (gloo): the leader takes every
+decision, followers replay the published device commands; a follower that stops replying
+fails the leader closed within the deadline.  No GPU is involved."""
+import time
+
+import pytest
+
+SPEC = dict(
+    world=2, device="cpu", preset="tiny", group_timeout_s=20.0, kv_pages=32, max_context=512,
+    max_rows=256,
+    load=dict(cuda_graph="off", prefix_cache_bytes=0, tp=2),
+    sched=dict(policy="latency", max_active=4, prefill_chunk=128),
+)
+
+
+def test_leader_and_follower_generate_like_spmd_ranks():
+    from orinfer_b200.parallel.rank_worker import leader_engine
+    engine, team = leader_engine(dict(SPEC), deadline_s=20.0)
+    try:
+        prompts = [[(7 * i + j) % 1000 + 1 for i in range(40)] for j in range(3)]
+        out = engine.generate(prompts, max_new=6)
+        team.channel.sync(20.0)
+        assert all(len(o) == 6 for o in out)
+        # the same prompts again: same tokens (the follower's KV / page rows stayed in step)
+        again = engine.generate(prompts, max_new=6)
+        assert again == out
+        assert team.channel.failure is None
+    finally:
+        engine.close()
+        team.close()
+    assert all(p.returncode == 0 for p in team.procs)
+
+
+def test_follower_that_stops_replying_fails_the_leader_closed():
+    from orinfer_b200.parallel.rank_channel import RankFailure
+    from orinfer_b200.parallel.rank_worker import leader_engine
+    spec = dict(SPEC, test_stall_after=2, group_timeout_s=6.0)
+    engine, team = leader_engine(spec, deadline_s=3.0)
+    t0 = time.monotonic()
+    try:
+        with pytest.raises((RankFailure, RuntimeError)):
+            for _ in range(50):                       # the follower goes silent after 2 commands
+                engine.generate([[1, 2, 3, 4, 5]], max_new=2)
+                time.sleep(0.2)
+        assert time.monotonic() - t0 < 40.0
+        with pytest.raises((RankFailure, RuntimeError)):
+            engine.generate([[1, 2, 3]], max_new=1)   # sticky
+    finally:
+        team.close(2.0)
+
+
+def _serve_tp2(device_args, timeout_s=300):
+    """`orinfer serve --tp 2` as a subprocess; returns (proc, url) once /health is ready."""
+    import socket
+    import subprocess
+    import sys
+
+    import requests
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    proc = subprocess.Popen([sys.executable, "-m", "orinfer_b200", "serve", "--preset", "tiny",
+                             "--tp", "2", "--listen", f"127.0.0.1:{port}", "--max-context", "512",
+                             "--prefix-cache-mib", "0", *device_args],
+                            stderr=subprocess.PIPE, text=True, start_new_session=True)
+    url = f"http://127.0.0.1:{port}"
+    deadline = time.time() + timeout_s
+    while time.time() < deadline:
+        if proc.poll() is not None:
+            raise AssertionError("serve exited: " + proc.stderr.read()[-2000:])
+        try:
+            if requests.get(url + "/health", timeout=2).status_code == 200:
+                return proc, url
+        except requests.RequestException:
+            pass
+        time.sleep(0.2)
+    proc.kill()
+    raise AssertionError("serve --tp 2 never became ready")
+
+
+def _chat_streams(url):
+    import json
+
+    import requests
+    body = {"messages": [{"role": "user", "content": "hello there"}], "max_tokens": 5,
+            "temperature": 0, "ignore_eos": True, "stream": True,
+            "stream_options": {"include_usage": True}}
+    with requests.post(url + "/v1/chat/completions", json=body, stream=True, timeout=120) as r:
+        assert r.status_code == 200, r.text
+        lines = [l.decode() for l in r.iter_lines() if l.startswith(b"data: ")]
+    assert lines[-1] == "data: [DONE]"
+    assert json.loads(lines[-2][6:])["usage"]["completion_tokens"] == 5
+    plain = requests.post(url + "/v1/chat/completions", json=dict(body, stream=False), timeout=120)
+    assert plain.status_code == 200 and plain.json()["usage"]["completion_tokens"] == 5
+
+
+def test_serve_tp2_streams_a_chat_completion_on_cpu_ranks():
+    import signal
+    proc, url = _serve_tp2(["--device", "cpu", "--cuda-graph", "off"])
+    try:
+        _chat_streams(url)
+    finally:
+        proc.send_signal(signal.SIGTERM)
+        assert proc.wait(timeout=90) == 0
+
+
+@pytest.mark.gpu
+def test_serve_tp2_streams_a_chat_completion_on_two_gpus(cuda):
+    import signal
+
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    proc, url = _serve_tp2([])
+    try:
+        _chat_streams(url)
+        _chat_streams(url)                       # decode graphs captured by now: replay path
+    finally:
+        proc.send_signal(signal.SIGTERM)
+        assert proc.wait(timeout=120) == 0

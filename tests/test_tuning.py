@@ -87,7 +87,7 @@ def test_kernel_library_plan_follows_the_table():
 def test_variants_do_not_change_the_gemm_result(cuda):
     from orinfer_b200.ops import functional as F
     from orinfer_b200.ops import native
-    from orinfer_b200.utils.kernel_probe import weights
+    from orinfer_b200.bench.kernel_probe import weights
     lib = native.lib()
     n, k = 2560, 2560
     w = weights("q4", n, k, cuda, 1)[0]
