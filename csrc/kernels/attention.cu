@@ -81,9 +81,12 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_rows_kernel(
       vsc = __half2float(vs[slot * GROUPS + group]);
     }
   };
-  int key = k_lo + warp * KPW + kslot;
-  fetch(key);
-  for (; key < k_hi; key += ATTN_WARPS * KPW) {
+  // The loop is uniform over the warp (lane groups past the last key idle inside it): the
+  // shuffles below need every lane.
+  fetch(k_lo + warp * KPW + kslot);
+  for (int base = k_lo + warp * KPW; base < k_hi; base += ATTN_WARPS * KPW) {
+    const int key = base + kslot;
+    const bool valid = key < k_hi;
     float kf[16], vf[16];
     unpack16(kraw, kf);
     unpack16(vraw, vf);
@@ -101,14 +104,16 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_rows_kernel(
       d *= kscale;
 #pragma unroll
       for (int o = 1; o < LPK; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-      const float mnew = fmaxf(mx[r], d);
-      const float corr = exp2f(mx[r] - mnew);
-      const float p = exp2f(d - mnew);
-      sum[r] = sum[r] * corr + p;
-      const float pv = p * vscale;
+      if (valid) {
+        const float mnew = fmaxf(mx[r], d);
+        const float corr = exp2f(mx[r] - mnew);
+        const float p = exp2f(d - mnew);
+        sum[r] = sum[r] * corr + p;
+        const float pv = p * vscale;
 #pragma unroll
-      for (int e = 0; e < 16; ++e) acc[r][e] = acc[r][e] * corr + pv * vf[e];
-      mx[r] = mnew;
+        for (int e = 0; e < 16; ++e) acc[r][e] = acc[r][e] * corr + pv * vf[e];
+        mx[r] = mnew;
+      }
     }
   }
   // lanes that only differ in kslot hold states of disjoint key sets: merge them

@@ -71,34 +71,46 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait; false (and a status record) when the phase never completes.
+// Bounded wait; false (and a status record) when the phase never completes.  The clock and
+// the limit (a global load) are only touched every 256 failed polls, so a wait that is
+// satisfied within microseconds costs nothing but the polls.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code,
                                           int detail) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long start = clock64(), limit = wait_limit(status);
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - start > limit) {
-      report_status(status, code, detail);
-      return false;
+  long long start = 0, limit = 0;
+  for (uint32_t spins = 1;; ++spins) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 255u) == 0) {
+      if (limit == 0) {
+        limit = wait_limit(status);
+        start = clock64();
+      } else if (clock64() - start > limit) {
+        report_status(status, code, detail);
+        return false;
+      }
     }
   }
-  return true;
 }
 // Same, for kernels whose roles must all leave when one of them gave up: `abort` is a word
 // in shared memory that the first failed wait sets and every other wait polls.
 __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, int* status,
                                                     int code, int detail, volatile int* abort) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long start = clock64(), limit = wait_limit(status);
-  while (!mbar_try_wait(bar, parity)) {
-    if (*abort != 0) return false;
-    if (clock64() - start > limit) {
-      report_status(status, code, detail);
-      *abort = 1;
-      return false;
+  long long start = 0, limit = 0;
+  for (uint32_t spins = 1;; ++spins) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 63u) == 0) {
+      if (*abort != 0) return false;
+      if ((spins & 255u) == 0) {
+        if (limit == 0) {
+          limit = wait_limit(status);
+          start = clock64();
+        } else if (clock64() - start > limit) {
+          report_status(status, code, detail);
+          *abort = 1;
+          return false;
+        }
+      }
     }
   }
-  return true;
 }
 
 // ---------------------------------------------------------------- TMA
@@ -190,6 +202,77 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t tmem_d, uint64_t adesc, uint
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// ---------------------------------------------------------------- CTA pairs (cta_group::2)
+// Two CTAs of a cluster drive one MMA of 256 rows: each holds its 128 rows of A and its half
+// of the B rows in its own shared memory, the even CTA issues the instruction, and each
+// CTA's TMEM receives its 128 rows of the accumulator.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `local` (a shared::cta address) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(
+                   cluster_addr),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* smem_slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_slot)),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void mma_i8_ss_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Completion of all earlier MMAs of this thread arrives on the barrier at the same offset in
+// every CTA of `cta_mask` (no data moves: this is a barrier signal, not a multicast load).
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;" ::"r"(smem_u32(bar)),
+      "h"(cta_mask)
+      : "memory");
+}
+// TMA tile load of a CTA pair: the data lands in this CTA's shared memory, the bytes are
+// counted on the barrier `bar_cluster_addr` (the even CTA's).  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* tmap,
+                                                 uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(tmap), "r"(bar_cluster_addr), "r"(x), "r"(y)
       : "memory");
 }
 

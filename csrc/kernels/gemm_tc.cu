@@ -32,6 +32,10 @@ constexpr int BM = 128, BK = 128;
 constexpr int TILE_BYTES = 128 * 128;        // one INT8 activation tile (128 rows x 128 k)
 constexpr int PRODUCERS = 512;               // warps 2..17
 constexpr int PWARPS = PRODUCERS / 32;
+constexpr int NUM_SMS = 148;
+// 0: persistent kernel; 1: one tile per CTA; 2: CTA pairs (cta_group::2) where the shape
+// allows, else persistent.  All give the same bits.
+static int g_impl = 0;
 constexpr int THREADS = 64 + PRODUCERS;
 
 template <int FMT, int MT, int NB>
@@ -788,6 +792,441 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_ps_kernel(
   if (peer_stage) peer_signal_done(po, gridDim.x);
 }
 
+// ---------------------------------------------------------------- CTA-pair form
+// Two CTAs (a cluster of 2, neighbouring SMs) share one output tile of 512 rows x 256
+// columns through tcgen05 cta_group::2: every MMA covers 256 rows x 256 columns, CTA r of
+// the pair holds rows [r*128, r*128+128) of each 256-row A sub-tile and weight rows
+// [r*128, r*128+128) of the 256-row B tile in its own shared memory, and its TMEM receives
+// its 128 rows of both accumulators.  Per MAC a CTA therefore streams half the activation
+// bytes and decodes half the weight rows of the one-CTA kernel with the same TMEM budget,
+// which is what the L2-to-SM bandwidth (the limiter of the one-CTA kernel) needed.
+// The even CTA issues the MMAs.  Barriers that the MMA thread waits on live in the even
+// CTA and collect both CTAs' arrivals (TMA bytes through the pair form of the tile load,
+// producer and epilogue warps through cluster-scope arrives); barriers that it signals are
+// signalled in both CTAs at once with tcgen05.commit ... multicast::cluster (a barrier
+// signal; every load in this file is unicast).  Persistent over pair tiles like the kernel
+// above; fused scatter (peers) and fused all-gather wait are kept.
+template <int FMT>
+struct PairLayout {
+  static constexpr int MT = 2, BN = 256, HALF_N = 128;
+  static constexpr int ROW_CODE_BYTES = FMT == 1 ? 64 : (FMT == 2 ? 32 : 0);
+  static constexpr int CODE_BYTES = HALF_N * ROW_CODE_BYTES;
+  static constexpr int B_BYTES = HALF_N * BK;
+  static constexpr int NSLOT = 8;                        // 4 k-blocks of 2 sub-tiles
+  static constexpr int SBD = FMT == 0 ? 4 : 3;
+  static constexpr int SC = FMT == 0 ? 0 : 3;
+  static constexpr int LUT_COPIES = 8;
+  static constexpr int LUT_BYTES = FMT == 0 ? 0 : static_cast<int>(sizeof(E8pLut<LUT_COPIES>));
+  static constexpr int A_OFF = 0;
+  static constexpr int B_OFF = A_OFF + NSLOT * TILE_BYTES;
+  static constexpr int CODE_OFF = B_OFF + SBD * B_BYTES;
+  static constexpr int LUT_OFF = CODE_OFF + SC * CODE_BYTES;
+  static constexpr int BAR_OFF = LUT_OFF + LUT_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 512 + 1024;
+  static_assert(TOTAL <= 227 * 1024, "exceeds the shared memory of one CTA");
+};
+
+template <int FMT, bool OUT_F32>
+__global__ void __launch_bounds__(THREADS, 1) qgemm_pair_kernel(
+    const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+    const unsigned char* __restrict__ w, const float* __restrict__ a_scale,
+    const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K,
+    const E8pTables* __restrict__ tables, int* status, PeerOut po, AgIn ag) {
+  using L = PairLayout<FMT>;
+  constexpr int MT = L::MT, BN = L::BN, HALF_N = L::HALF_N;
+  constexpr int NSLOT = L::NSLOT, SBD = L::SBD, SC = L::SC > 0 ? L::SC : 1;
+  constexpr int CHUNKS = BN / 32;
+  constexpr uint32_t TMEM_COLS = MT * BN;               // 512
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* a_s = smem + L::A_OFF;
+  unsigned char* b_s = smem + L::B_OFF;
+  unsigned char* code_s = smem + L::CODE_OFF;
+  using Lut = E8pLut<L::LUT_COPIES>;
+  Lut* lut = reinterpret_cast<Lut*>(smem + L::LUT_OFF);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* a_full = bars;                     // [NSLOT] even CTA: both halves landed
+  uint64_t* a_empty = a_full + NSLOT;          // [NSLOT] both CTAs: MMAs retired
+  uint64_t* c_full = a_empty + NSLOT;          // [SC]    local: packed codes landed
+  uint64_t* c_empty = c_full + SC;             // [SC]    local: producer warps read them
+  uint64_t* b_full = c_empty + SC;             // [SBD]   even CTA: both halves decoded / landed
+  uint64_t* b_empty = b_full + SBD;            // [SBD]   both CTAs: MMAs retired
+  uint64_t* tmem_full = b_empty + SBD;         // [1]     both CTAs
+  uint64_t* tmem_empty = tmem_full + 1;        // [MT]    even CTA: both epilogues read it out
+  uint64_t* epi_done = tmem_empty + MT;        // [1]     local
+  uint64_t* stage_full = epi_done + 1;         // [1]     local
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stage_full + 1);
+  volatile int* abort_w = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  static_assert((2 * NSLOT + 2 * SC + 2 * SBD + MT + 3) * 8 + 8 <= 512, "barrier block");
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t crank = cluster_ctarank();              // 0: issues the MMAs
+  const bool leader = crank == 0;
+  const bool peer_stage = po.tp > 0;
+  const int n_tiles = (N + BN - 1) / BN;
+  const int m_tiles = (M + 2 * BM * MT - 1) / (2 * BM * MT);       // 512 rows per pair tile
+  const int total = n_tiles * m_tiles;
+  const int kblocks = K / BK;
+  const int pair_id = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+  struct Tile {
+    int n0, m0, mt_act, rows_valid;
+  };
+  auto tile_at = [&](int t) {
+    Tile T;
+    const int nt = t / m_tiles, mi = t - nt * m_tiles;
+    T.n0 = nt * BN;
+    T.m0 = mi * 2 * BM * MT;
+    const int rows = M - T.m0;
+    T.mt_act = rows <= 0 ? 0 : min(MT, (rows + 2 * BM - 1) / (2 * BM));
+    T.rows_valid = max(0, min(HALF_N, N - (T.n0 + static_cast<int>(crank) * HALF_N)));
+    return T;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NSLOT; ++s) {
+      mbar_init(&a_full[s], 1);
+      mbar_init(&a_empty[s], 1);
+    }
+    for (int s = 0; s < SC; ++s) {
+      mbar_init(&c_full[s], 1);
+      mbar_init(&c_empty[s], PWARPS);
+    }
+    for (int s = 0; s < SBD; ++s) {
+      mbar_init(&b_full[s], FMT == 0 ? 1 : 2 * PWARPS);
+      mbar_init(&b_empty[s], 1);
+    }
+    mbar_init(tmem_full, 1);
+    for (int t = 0; t < MT; ++t) mbar_init(&tmem_empty[t], 2 * 4 * CHUNKS);
+    mbar_init(epi_done, PWARPS);
+    mbar_init(stage_full, PWARPS);
+    *abort_w = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmap_a);
+    if (FMT == 0) prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_slot, TMEM_COLS);
+    tmem_relinquish2();
+  }
+  if (FMT != 0 && warp >= 2) e8p_lut_init(lut, tables, threadIdx.x - 64, PRODUCERS);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                          // the peer's barriers exist before anyone signals
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr int STAGE_ROW = BN * 2 + 16;
+  static_assert(MT * BM * STAGE_ROW <= L::LUT_OFF, "staged tile must fit in the operand rings");
+
+#define PR_WAIT(bar, par, code, detail) \
+  mbar_wait_abortable((bar), (par), status, (code), (detail), abort_w)
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- activation loader (both CTAs): this CTA's 128 rows of each sub-tile
+      uint32_t ca = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = pair_id; ok && t < total; t += pairs, ++it) {
+        const Tile T = tile_at(t);
+        if (peer_stage && it > 0) ok = PR_WAIT(epi_done, (it - 1) & 1, STATUS_EPILOGUE_WAIT, 1);
+        if (ok && ag.tp > 0 && T.mt_act > 0) {
+          ok = ag_wait(ag, T.m0, min(T.m0 + 2 * BM * MT, M) - 1, status);
+          if (!ok) *abort_w = 1;
+          fence_proxy_async_all();
+        }
+        for (int kb = 0; ok && kb < kblocks; ++kb) {
+          for (int s = 0; s < T.mt_act; ++s, ++ca) {
+            const uint32_t slot = ca % NSLOT;
+            ok = PR_WAIT(&a_empty[slot], ((ca / NSLOT) & 1) ^ 1, STATUS_TMA_WAIT, kb);
+            if (!ok) break;
+            const uint32_t full0 = mapa_u32(smem_u32(&a_full[slot]), 0);
+            if (leader) mbar_expect_tx(&a_full[slot], 2 * TILE_BYTES);
+            tma_load_2d_pair(a_s + slot * TILE_BYTES, &tmap_a, full0, kb * BK,
+                             T.m0 + s * 2 * BM + static_cast<int>(crank) * BM);
+          }
+        }
+      }
+      // the even CTA's barriers count both CTAs' copies: wait for the last ones before the
+      // pair leaves (the odd CTA is held by the cluster barrier at the end)
+      if (leader)
+        for (uint32_t c = ca > NSLOT ? ca - NSLOT : 0; c < ca; ++c)
+          mbar_wait(&a_full[c % NSLOT], (c / NSLOT) & 1, status, STATUS_TMA_WAIT, 0x4000);
+    } else if (lane == 1) {
+      // ---------------- weight loader (both CTAs): its 128 weight rows
+      uint32_t cw = 0;
+      int it = 0;
+      bool ok = true;
+      constexpr int DEPTH = FMT == 0 ? SBD : SC;
+      uint64_t* freed = FMT == 0 ? b_empty : c_empty;
+      for (int t = pair_id; ok && t < total; t += pairs, ++it) {
+        const Tile T = tile_at(t);
+        const int nrow0 = T.n0 + static_cast<int>(crank) * HALF_N;
+        if (peer_stage && it > 0) ok = PR_WAIT(epi_done, (it - 1) & 1, STATUS_EPILOGUE_WAIT, 2);
+        for (int kb = 0; ok && kb < kblocks && T.mt_act > 0; ++kb, ++cw) {
+          const uint32_t s = cw % DEPTH;
+          ok = PR_WAIT(&freed[s], ((cw / DEPTH) & 1) ^ 1, STATUS_TMA_WAIT, 0x1000 | kb);
+          if (!ok) break;
+          if (FMT == 0) {
+            const uint32_t full0 = mapa_u32(smem_u32(&b_full[s]), 0);
+            if (leader) mbar_expect_tx(&b_full[s], 2 * L::B_BYTES);
+            tma_load_2d_pair(b_s + s * L::B_BYTES, &tmap_b, full0, kb * BK, nrow0);
+          } else {
+            // a slab past the last weight row is not loaded: its waiters get an empty phase
+            const uint32_t bytes = T.rows_valid * L::ROW_CODE_BYTES;
+            mbar_expect_tx(&c_full[s], bytes);
+            if (bytes > 0)
+              bulk_load(code_s + s * L::CODE_BYTES,
+                        w + (static_cast<size_t>(kb) * N + nrow0) * L::ROW_CODE_BYTES, bytes,
+                        &c_full[s]);
+          }
+        }
+      }
+      if (FMT != 0 || leader) {
+        uint64_t* landed = FMT == 0 ? b_full : c_full;
+        for (uint32_t c = cw > DEPTH ? cw - DEPTH : 0; c < cw; ++c)
+          mbar_wait(&landed[c % DEPTH], (c / DEPTH) & 1, status, STATUS_TMA_WAIT, 0x5000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      // ---------------- MMA issuer (even CTA only)
+      constexpr uint32_t idesc = umma_idesc(2, 1, 1, 0, 0, 2 * BM, BN);
+      uint32_t ca = 0, cb = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = pair_id; ok && t < total; t += pairs, ++it) {
+        const Tile T = tile_at(t);
+        const int kbs = T.mt_act > 0 ? kblocks : 0;
+        for (int kb = 0; ok && kb < kbs; ++kb, ++cb) {
+          const uint32_t sb = cb % SBD;
+          ok = PR_WAIT(&b_full[sb], (cb / SBD) & 1, STATUS_MMA_WAIT, 0x2000 | kb);
+          if (!ok) break;
+          const uint32_t b_addr = smem_u32(b_s + sb * L::B_BYTES);
+          for (int s = 0; s < T.mt_act; ++s, ++ca) {
+            if (kb == 0 && it > 0)
+              ok = PR_WAIT(&tmem_empty[s], (it - 1) & 1, STATUS_MMA_WAIT, 0x3000 | s);
+            const uint32_t slot = ca % NSLOT;
+            if (ok) ok = PR_WAIT(&a_full[slot], (ca / NSLOT) & 1, STATUS_MMA_WAIT, kb);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(a_s + slot * TILE_BYTES);
+#pragma unroll
+            for (int j = 0; j < BK / 32; ++j)
+              mma_i8_ss_pair(tmem_base + s * BN, umma_desc(a_addr + j * 32, 16, 1024),
+                             umma_desc(b_addr + j * 32, 16, 1024), idesc, (kb | j) != 0 ? 1u : 0u);
+            tc_commit_pair(&a_empty[slot], 3);
+          }
+          if (ok) tc_commit_pair(&b_empty[sb], 3);
+        }
+        if (ok) {
+          if (kbs > 0) {
+            tc_commit_pair(tmem_full, 3);
+          } else {
+            if (it > 0) ok = PR_WAIT(&tmem_empty[0], (it - 1) & 1, STATUS_MMA_WAIT, 0x3800);
+            if (ok) {
+              mbar_arrive(tmem_full);
+              mbar_arrive_cluster(mapa_u32(smem_u32(tmem_full), 1));
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------- producers (lattice decode of this CTA's weight rows) and epilogue
+    const int t512 = threadIdx.x - 64;
+    const int chunk = t512 & 7, rbase = t512 >> 3;
+    const int copy = t512 & (L::LUT_COPIES - 1);
+    const int quad = warp & 3;
+    const int part = (warp - 2) >> 2;
+    const int row = quad * 32 + lane;
+    bool ok = true;
+
+    auto epilogue = [&](const Tile& T, int it) {
+      ok = PR_WAIT(tmem_full, it & 1, STATUS_EPILOGUE_WAIT, 0) && ok;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) return;
+      tc_fence_after();
+#pragma unroll 1
+      for (int item = part; item < MT * CHUNKS; item += 4) {
+        const int mt = item / CHUNKS, c0 = (item % CHUNKS) * 32;
+        const int m = T.m0 + mt * 2 * BM + static_cast<int>(crank) * BM + row;
+        uint32_t r[32];
+        if (mt < T.mt_act) {
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + mt * BN + c0, r);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty[mt]), 0));
+        const float sa = m < M ? (ag.tp > 0 ? __ldcg(a_scale + m) : a_scale[m]) : 0.f;
+        if (m < M) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int n = T.n0 + c0 + g * 8;
+            if (n + 8 <= N) {
+              float v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                v[j] = (static_cast<float>(static_cast<int>(r[g * 8 + j])) *
+                        __half2float(w_scale[n + j])) * sa;
+              if (peer_stage) {
+                __align__(16) __half h[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
+                *reinterpret_cast<int4*>(smem + static_cast<size_t>(mt * BM + row) * STAGE_ROW +
+                                         (c0 + g * 8) * 2) = *reinterpret_cast<const int4*>(h);
+              } else if (OUT_F32) {
+                float* o = reinterpret_cast<float*>(out) + static_cast<size_t>(m) * N + n;
+                *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+              } else {
+                __align__(16) __half h[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
+                __half* o = reinterpret_cast<__half*>(out) + static_cast<size_t>(m) * N + n;
+                *reinterpret_cast<int4*>(o) = *reinterpret_cast<const int4*>(h);
+              }
+            }
+          }
+        }
+      }
+      if (peer_stage) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(stage_full);
+        ok = PR_WAIT(stage_full, it & 1, STATUS_EPILOGUE_WAIT, 3);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) return;
+        constexpr int SEGS = BN / 8;
+        for (int idx = t512; idx < MT * BM * SEGS; idx += PRODUCERS) {
+          const int rr = idx / SEGS, seg = idx % SEGS;
+          const int m = T.m0 + (rr / BM) * 2 * BM + static_cast<int>(crank) * BM + rr % BM;
+          const int n = T.n0 + seg * 8;
+          if (m < M && n + 8 <= N) {
+            const int4 val = *reinterpret_cast<const int4*>(
+                smem + static_cast<size_t>(rr) * STAGE_ROW + seg * 16);
+            const size_t off = (static_cast<size_t>(po.rank) * po.rows_cap + m) * N + n;
+            if (po.rows_per > 0) {
+              *reinterpret_cast<int4*>(po.inbox[min(m / po.rows_per, po.tp - 1)] + off) = val;
+            } else {
+              for (int d = 0; d < po.tp; ++d) *reinterpret_cast<int4*>(po.inbox[d] + off) = val;
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(epi_done);
+      }
+    };
+
+    uint32_t cc = 0, cb = 0;
+    int it = 0;
+    bool have_prev = false;
+    Tile prev{};
+    for (int t = pair_id; ok && t < total; t += pairs, ++it) {
+      const Tile T = tile_at(t);
+      const int kbs = T.mt_act > 0 ? kblocks : 0;
+      bool prev_pending = have_prev;
+      const int epos = (peer_stage || FMT == 0) ? -1 : min(SBD, kbs) - 1;
+      if (prev_pending && epos < 0) {
+        epilogue(prev, it - 1);
+        prev_pending = false;
+      }
+      if (FMT != 0) {
+        for (int kb = 0; ok && kb < kbs; ++kb, ++cc, ++cb) {
+          const uint32_t sc = cc % SC, sb = cb % SBD;
+          ok = PR_WAIT(&c_full[sc], (cc / SC) & 1, STATUS_DECODE_WAIT, kb);
+          if (ok) ok = PR_WAIT(&b_empty[sb], ((cb / SBD) & 1) ^ 1, STATUS_DECODE_WAIT, 0x800 | kb);
+          if (!ok) break;
+          const unsigned char* cs = code_s + sc * L::CODE_BYTES;
+          unsigned char* bs = b_s + sb * L::B_BYTES;
+#pragma unroll
+          for (int i = 0; i < HALF_N / 64; ++i) {
+            const int wrow = rbase + 64 * i;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (wrow < T.rows_valid) {
+              if (FMT == 1) {
+                const uint2 wd = *reinterpret_cast<const uint2*>(cs + wrow * 64 + chunk * 8);
+                const uint2 q0 = e8p_decode_q4(wd.x, lut, copy);
+                const uint2 q1 = e8p_decode_q4(wd.y, lut, copy);
+                v = make_uint4(q0.x, q0.y, q1.x, q1.y);
+              } else {
+                const uint32_t wd = *reinterpret_cast<const uint32_t*>(cs + wrow * 32 + chunk * 4);
+                const uint2 q0 = e8p_decode8<L::LUT_COPIES, 0>(wd, lut, copy);
+                const uint2 q1 = e8p_decode8<L::LUT_COPIES, 1>(wd, lut, copy);
+                v = make_uint4(q0.x, q0.y, q1.x, q1.y);
+              }
+            }
+            *reinterpret_cast<uint4*>(bs + swz128(wrow, chunk)) = v;
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive_cluster(mapa_u32(smem_u32(&b_full[sb]), 0));
+            mbar_arrive(&c_empty[sc]);
+          }
+          if (prev_pending && kb == epos) {
+            epilogue(prev, it - 1);
+            prev_pending = false;
+          }
+        }
+      }
+      if (ok && prev_pending) epilogue(prev, it - 1);
+      prev = T;
+      have_prev = true;
+    }
+    if (ok && have_prev) epilogue(prev, it - 1);
+  }
+#undef PR_WAIT
+  // nobody leaves while its pair may still signal its barriers or read its shared memory
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) tmem_dealloc2(tmem_base, TMEM_COLS);
+  if (peer_stage) peer_signal_done(po, gridDim.x);
+}
+
+template <int FMT, bool OUT_F32>
+int launch_pair(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale,
+                void* out, int M, int N, int K, cudaStream_t stream, const PeerOut& po,
+                const AgIn& ag) {
+  using L = PairLayout<FMT>;
+  CUtensorMap ta, tb;
+  if (!make_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BM, BK)) return -3;
+  if (FMT == 0) {
+    if (!make_tmap_2d(&tb, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, L::HALF_N, BK)) return -3;
+  } else {
+    tb = ta;
+    if (reinterpret_cast<uintptr_t>(w) % 16) return -1;
+  }
+  static const int slot = runtime_new_slot();
+  if (runtime_first_use(slot)) {
+    cudaError_t e = cudaFuncSetAttribute(qgemm_pair_kernel<FMT, OUT_F32>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  const long tiles = static_cast<long>((N + L::BN - 1) / L::BN) * ((M + 511) / 512);
+  const int pairs = static_cast<int>(tiles < NUM_SMS / 2 ? tiles : NUM_SMS / 2);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = L::TOTAL;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(
+      &cfg, qgemm_pair_kernel<FMT, OUT_F32>, ta, tb, reinterpret_cast<const unsigned char*>(w),
+      a_scale, w_scale, out, M, N, K, runtime_e8p_tables(), runtime_status_ptr(), po, ag);
+  return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
+}
+
 // out[m][n] = (float(sum_z partial[z][m][n]) * w_scale[n]) * a_scale[m], as FP16 into `out`
 // or, with peers, into the inboxes (all ranks, or the row's owner when rows_per > 0).
 // One thread per 8 columns; the arithmetic is the GEMM epilogue's, so a split GEMM returns
@@ -831,9 +1270,6 @@ __global__ void __launch_bounds__(256) splitk_finalize_kernel(
   if (po.tp > 0) peer_signal_done(po, gridDim.x);
 }
 
-// 0: persistent kernel (default); 1: one tile per CTA.  Both give the same bits.
-static int g_impl = 0;
-constexpr int NUM_SMS = 148;
 
 template <int FMT, bool OUT_F32, int MT, int NB>
 int launch_ps(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale,
@@ -885,7 +1321,7 @@ int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w
            int n_begin = 0, int n_end = -1) {
   using L = Layout<FMT, MT, NB>;
   if (n_end < 0) n_end = N;
-  if (g_impl == 0)
+  if (g_impl != 1)
     return launch_ps<FMT, OUT_F32, MT, NB>(a, a_scale, w, w_scale, out, M, N, K, stream, po, grp,
                                            experts, max_tiles, ag, splits, n_begin, n_end);
   CUtensorMap ta, tb;
@@ -1032,6 +1468,10 @@ int launch_fmt(const int8_t* a, const float* a_scale, const void* w, const __hal
                void* out, int M, int N, int K, int out_f32, cudaStream_t stream,
                const PeerOut& po, const AgIn& ag = AgIn{nullptr, nullptr, 0, 0}) {
   const GroupDesc none{nullptr, nullptr, 0, 0};
+  if (g_impl == 2 && M > BM && N >= 256) {
+    if (out_f32) return launch_pair<FMT, true>(a, a_scale, w, w_scale, out, M, N, K, stream, po, ag);
+    return launch_pair<FMT, false>(a, a_scale, w, w_scale, out, M, N, K, stream, po, ag);
+  }
   const Plan plan = make_plan(FMT, M, N, K, out_f32, po.tp != 0);
   const int mt = plan.mt, nb = plan.nb, splits = plan.splits;
   if (plan.tail_splits > 0) {
@@ -1140,7 +1580,7 @@ extern "C" void orinfer_qgemm_clear_variants() { tc::g_variant_count = 0; }
 
 // 0 = persistent kernel (default), 1 = one tile per CTA; for comparisons and tests.
 extern "C" int orinfer_qgemm_set_impl(int impl) {
-  if (impl != 0 && impl != 1) return -1;
+  if (impl < 0 || impl > 2) return -1;
   tc::g_impl = impl;
   return 0;
 }

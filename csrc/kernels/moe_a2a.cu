@@ -79,9 +79,9 @@ __global__ void __launch_bounds__(256) a2a_recv_prepare_kernel(
     const int want = *reinterpret_cast<const volatile int*>(sent);
     int good = 1;
     for (int s = 0; s < tp && good; ++s) {
-      const long long start = clock64();
+      const long long start = clock64(), limit = wait_limit(status);
       while (ld_acquire_sys(flag + s) < want) {
-        if (clock64() - start > wait_limit(status)) {
+        if (clock64() - start > limit) {
           report_status(status, STATUS_PEER_WAIT, 0x200 | s);
           good = 0;
           break;
@@ -124,9 +124,9 @@ __global__ void a2a_wait_kernel(const int* __restrict__ flag, const int* __restr
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
   const int want = *reinterpret_cast<const volatile int*>(sent);
   for (int s = 0; s < tp; ++s) {
-    const long long start = clock64();
+    const long long start = clock64(), limit = wait_limit(status);
     while (ld_acquire_sys(flag + s) < want) {
-      if (clock64() - start > wait_limit(status)) {
+      if (clock64() - start > limit) {
         report_status(status, STATUS_PEER_WAIT, 0x300 | s);
         return;
       }

@@ -104,9 +104,9 @@ __device__ __forceinline__ bool ag_wait(const AgIn& in, int m_lo, int m_hi, int*
   const int s_hi = min(m_hi / in.rows_per, in.tp - 1);
   for (int s = m_lo / in.rows_per; s <= s_hi; ++s) {
     if (ld_acquire_sys(in.flag + s) >= want) continue;
-    const long long start = clock64();
+    const long long start = clock64(), limit = wait_limit(status);
     while (ld_acquire_sys(in.flag + s) < want) {
-      if (clock64() - start > wait_limit(status)) {
+      if (clock64() - start > limit) {
         report_status(status, STATUS_PEER_WAIT, 0x100 | s);
         return false;
       }
@@ -155,8 +155,8 @@ __device__ __forceinline__ void ll_done(const PeerOut& po, int seq, unsigned int
 // Two units (four FP16 values) of source s; spins until both carry `seq` (bounded).
 __device__ __forceinline__ bool ll_load4(const uint2* base, int seq, uint32_t& a, uint32_t& b,
                                          int* status, int s) {
-  const long long start = clock64();
-  for (;;) {
+  long long start = 0, limit = 0;
+  for (uint32_t spins = 1;; ++spins) {
     uint4 v;
     asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(base) : "memory");
@@ -165,10 +165,15 @@ __device__ __forceinline__ bool ll_load4(const uint2* base, int seq, uint32_t& a
       b = v.z;
       return true;
     }
-    if (clock64() - start > wait_limit(status)) {
-      report_status(status, STATUS_PEER_WAIT, 0x400 | s);
-      a = b = 0;
-      return false;
+    if ((spins & 63u) == 0) {             // clock and limit only once the wait is a long one
+      if (limit == 0) {
+        limit = wait_limit(status);
+        start = clock64();
+      } else if (clock64() - start > limit) {
+        report_status(status, STATUS_PEER_WAIT, 0x400 | s);
+        a = b = 0;
+        return false;
+      }
     }
   }
 }
@@ -181,9 +186,9 @@ __device__ __forceinline__ bool inbox_wait(const InboxIn& in, int* status) {
     int ok = 1;
     for (int s = 0; s < in.tp && ok; ++s) {
       if (ld_acquire_sys(in.flag + s) >= want) continue;
-      const long long start = clock64();
+      const long long start = clock64(), limit = wait_limit(status);
       while (ld_acquire_sys(in.flag + s) < want) {
-        if (clock64() - start > wait_limit(status)) {
+        if (clock64() - start > limit) {
           report_status(status, STATUS_PEER_WAIT, s);
           ok = 0;
           break;

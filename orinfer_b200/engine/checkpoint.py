@@ -1,14 +1,20 @@
-"""Checkpoint I/O in the reference's quantised safetensors layout.
+"""Checkpoint I/O of this engine's own model directory, plus dispatch to the reader of
+directories published by the reference's quantiser.
 
-A model directory holds ``model.safetensors`` (one file here; sharded indexes are read
-too), ``config.json`` (geometry) and ``cache/model.json`` - the descriptor with the
-architecture, compute policy, per-tensor SHA-256 digests and frontend-asset hashes
-(crates/orinfer-engine/src/loader.rs:16-35).  Tensor naming follows the reference:
-``<name>.packed`` U32 ``[K/128, N, 16]`` + ``<name>.scale`` FP16 ``[N]`` for E8P Q4
-(layout ``e8p-q4-k128-u32``), ``<name>.packed16`` for Q2, ``<name>.int8`` INT8 ``[N, K]``
-for W8, ``orinfer.rotation.k{K}.signs`` and ``orinfer.e8p_q4.basis``
-(crates/orinfer-models/src/qwen3_5/rows.rs:343-365,405-422;
-python/orinfer_build/quantization/qwen_e8p.py:386-474).
+Own format: ``model.safetensors`` (one file), ``config.json`` (geometry) and
+``cache/model.json`` - the descriptor with the architecture, compute policy, per-tensor
+SHA-256 digests and frontend-asset hashes (the role of crates/orinfer-engine/src/loader.rs:16-35).
+Tensors are stored already fused and tiled for the kernels, under this engine's own names
+(``layers.N.qkv`` ...): ``<name>.packed`` int32 ``[K/128, N, 16]`` + ``<name>.scale`` FP16
+``[N]`` for E8P Q4 (the reference's runtime tiling ``e8p-q4-k128-u32``), ``<name>.packed16``
+for Q2, ``<name>.int8`` INT8 ``[N, K]`` for W8, ``orinfer.rotation.k{K}.signs`` and
+``orinfer.e8p_q4.basis``; the codes themselves are bit-identical to the reference's codec.
+
+A directory written by the reference's quantiser keeps Hugging Face tensor names, one
+projection per tensor in row-major ``[N, K/8]`` U32, shards with an index and a separate
+``quantization.safetensors`` (python/orinfer_build/quantization/qwen_e8p.py:386-474);
+``load_model`` recognises it by its ``quantization_config`` and hands it to
+``ref_checkpoint.load_reference_model``.
 """
 
 from __future__ import annotations
@@ -175,6 +181,9 @@ def load_model(directory, device="cpu", verify: bool = False,
     when the target is a GPU, per-tensor SHA-256 when ``verify``) and uploads it."""
     from .weight_io import WeightReadError, read_tensors
     directory = Path(directory)
+    from .ref_checkpoint import is_reference_layout, load_reference_model
+    if is_reference_layout(directory):           # published by the reference's own quantiser
+        return load_reference_model(directory, device)
     desc = read_descriptor(directory)
     cfg = ModelConfig.from_json((directory / "config.json").read_text())
     from .. import contracts

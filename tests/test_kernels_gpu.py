@@ -144,6 +144,30 @@ def test_qgemm_one_tile_per_cta_form(cuda, fmt, m, n, k):
     assert torch.equal(out.float(), R.qgemm(a, sa, w_int, ws))
 
 
+@pytest.mark.parametrize("fmt", ["w8", "q4", "q2"])
+@pytest.mark.parametrize("m,n,k", [(600, 19456, 256), (512, 2560, 9728), (1100, 9728, 1024),
+                                   (300, 2432, 2560), (513, 2560, 1024), (129, 256, 128),
+                                   (2100, 1000, 384)])
+def test_qgemm_cta_pair_form(cuda, fmt, m, n, k):
+    """cta_group::2: two CTAs share a 512 x 256 tile; ragged M, ragged N (a pair whose odd
+    CTA has no weight rows), several tiles per pair.  Same bits as the oracle."""
+    from orinfer_b200.ops import functional as F
+    from orinfer_b200.ops import native
+    g = torch.Generator().manual_seed(m + n)
+    a = torch.randint(-127, 128, (m, k), generator=g, dtype=torch.int8).to(cuda)
+    sa = (torch.rand(m, generator=g) * 0.05 + 1e-3).to(cuda)
+    codes, ws, w_int = _rand_weight(fmt, n, k, cuda, seed=k + n)
+    try:
+        native.qgemm_set_impl(2)
+        out = F.qgemm(a, sa, codes, ws, fmt, n)
+        out32 = F.qgemm(a, sa, codes, ws, fmt, n, out_f32=True)
+        torch.cuda.synchronize()
+    finally:
+        native.qgemm_set_impl(0)
+    assert torch.equal(out.float(), R.qgemm(a, sa, w_int, ws))
+    assert torch.equal(out32, R.qgemm(a, sa, w_int, ws, out_f32=True))
+
+
 def test_qgemm_graph_replay_changed_inputs(cuda):
     """Capture once, replay with different activation contents."""
     from orinfer_b200.ops import functional as F
