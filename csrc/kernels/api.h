@@ -60,6 +60,16 @@ typedef struct OrinferInbox {
                                // units {2 x fp16, sequence number}; seen / ticket are its counters
 } OrinferInbox;
 
+// Cross-rank merge of a vocabulary-sharded head's greedy token (tp_head.cu).
+typedef struct OrinferHeadMerge {
+  void* table[8];              // every rank's table: uint4 [tp][cap], zero-initialised
+  int* seq;                    // local sequence counter (device memory)
+  int tp, rank, cap;
+} OrinferHeadMerge;
+int orinfer_tp_head_merge(const float* logits, const int* local_tok, int rows, int vocab_local,
+                          int vocab0, const OrinferHeadMerge* h, int* token_out,
+                          cudaStream_t stream);
+
 // Owner rows [rank*rows_per, ...) only: sum the tp partial rows of the inbox, add the
 // residual, normalise, rotate, quantise, store the INT8 row + scale into every rank's
 // activation buffer and publish the all-gather flag.

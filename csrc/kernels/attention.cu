@@ -27,8 +27,13 @@ __device__ __forceinline__ void unpack16(const int4& raw, float (&f)[16]) {
 
 // One CTA per (row, group of RPC query heads sharing a KV head, key split).  A key's D INT8
 // channels are covered by D/16 lanes with one 16-byte load each, so a warp takes 32/(D/16)
-// keys per step (4 at D = 128) and the four warps interleave; every lane group keeps its own
-// online-softmax state, merged by shuffles and then across warps in shared memory.
+// keys per step (4 at D = 128) and the four warps interleave.  Keys are processed in chunks
+// of up to ATTN_CHUNK: pass 1 writes the scores of the chunk to shared memory, the softmax
+// weights are formed there once per (head, key), and pass 2 accumulates weight x V.  No
+// running rescale sits in the inner loops (only one per chunk), so both passes are streams
+// of independent multiply-adds.
+constexpr int ATTN_CHUNK = 512;
+
 template <int D, int RPC>
 __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_rows_kernel(
     const __half* __restrict__ q, const __half* __restrict__ gate, const int* __restrict__ row_req,
@@ -38,12 +43,14 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_rows_kernel(
     float* __restrict__ scratch, int rep) {
   constexpr int LPK = D / 16;                  // lanes per key
   constexpr int KPW = 32 / LPK;                // keys per warp step
+  constexpr int KPI = ATTN_WARPS * KPW;        // keys per CTA step
   constexpr int GROUPS = D / 64;
+  constexpr int THREADS = ATTN_WARPS * 32;
   const int row = blockIdx.x, split = blockIdx.z;
   const int hgroups = rep / RPC;               // CTAs per KV head
   const int h = blockIdx.y / hgroups;          // KV head
   const int head0 = h * rep + (blockIdx.y % hgroups) * RPC;   // first query head of this CTA
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int sub = lane % LPK, kslot = lane / LPK;
   const int req = row_req[row];
   const int kv_len = row_pos[row] + 1;
@@ -55,112 +62,153 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_rows_kernel(
   // query heads (pre-scaled, FP32) in shared memory: every lane group reads the same slice,
   // so the loads are broadcasts, and the registers go to the accumulators
   __shared__ __align__(16) float s_q[RPC][D];
-  for (int i = threadIdx.x; i < RPC * D; i += blockDim.x)
+  __shared__ float s_p[RPC][ATTN_CHUNK];       // scores, then softmax weights, of the chunk
+  __shared__ float s_red[ATTN_WARPS][RPC];
+  __shared__ float s_m[RPC], s_l[RPC], s_corr[RPC];
+  __shared__ float s_o[ATTN_WARPS][RPC][D];
+  for (int i = tid; i < RPC * D; i += THREADS)
     s_q[i / D][i % D] =
         __half2float(q[(static_cast<size_t>(row) * qh + head0 + i / D) * D + i % D]) * qscale;
-  float acc[RPC][16], mx[RPC], sum[RPC];
+  if (tid < RPC) {
+    s_m[tid] = -INFINITY;
+    s_l[tid] = 0.f;
+  }
+  float acc[RPC][16];
 #pragma unroll
-  for (int r = 0; r < RPC; ++r) {
+  for (int r = 0; r < RPC; ++r)
 #pragma unroll
     for (int e = 0; e < 16; ++e) acc[r][e] = 0.f;
-    mx[r] = -INFINITY;
-    sum[r] = 0.f;
-  }
   __syncthreads();
   const int* pages = page_table + static_cast<size_t>(req) * max_pages;
-  // software pipeline: the loads of the next key are in flight while this one is used
-  int4 kraw = make_int4(0, 0, 0, 0), vraw = kraw;
-  float ksc = 0.f, vsc = 0.f;
-  auto fetch = [&](int key) {
-    if (key < k_hi) {
-      const int page = pages[key >> 7];
-      const size_t slot = (static_cast<size_t>(page) * 128 + (key & 127)) * kvh + h;
-      kraw = __ldg(reinterpret_cast<const int4*>(kc + slot * D + sub * 16));
-      vraw = __ldg(reinterpret_cast<const int4*>(vc + slot * D + sub * 16));
-      ksc = __half2float(ks[slot * GROUPS + group]);
-      vsc = __half2float(vs[slot * GROUPS + group]);
+
+  for (int c0 = k_lo; c0 < k_hi; c0 += ATTN_CHUNK) {
+    const int n = min(ATTN_CHUNK, k_hi - c0);
+    // ---- pass 1: scores of the chunk (loop uniform over the warp: the shuffles need every lane)
+    float lmax[RPC];
+#pragma unroll
+    for (int r = 0; r < RPC; ++r) lmax[r] = -INFINITY;
+    for (int base = warp * KPW; base < n; base += KPI) {
+      const int kk = base + kslot;
+      const bool valid = kk < n;
+      float kf[16];
+      float ksc = 0.f;
+      if (valid) {
+        const int key = c0 + kk;
+        const int page = pages[key >> 7];
+        const size_t slot = (static_cast<size_t>(page) * 128 + (key & 127)) * kvh + h;
+        unpack16(__ldg(reinterpret_cast<const int4*>(kc + slot * D + sub * 16)), kf);
+        ksc = __half2float(ks[slot * GROUPS + group]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) kf[e] = 0.f;
+      }
+#pragma unroll
+      for (int r = 0; r < RPC; ++r) {
+        float d = 0.f;
+#pragma unroll
+        for (int e4 = 0; e4 < 4; ++e4) {
+          const float4 qq = *reinterpret_cast<const float4*>(&s_q[r][sub * 16 + e4 * 4]);
+          d += qq.x * kf[e4 * 4] + qq.y * kf[e4 * 4 + 1] + qq.z * kf[e4 * 4 + 2] +
+               qq.w * kf[e4 * 4 + 3];
+        }
+        d *= ksc;
+#pragma unroll
+        for (int o = 1; o < LPK; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        if (valid) {
+          lmax[r] = fmaxf(lmax[r], d);
+          if (sub == 0) s_p[r][kk] = d;
+        }
+      }
     }
-  };
-  // The loop is uniform over the warp (lane groups past the last key idle inside it): the
-  // shuffles below need every lane.
-  fetch(k_lo + warp * KPW + kslot);
-  for (int base = k_lo + warp * KPW; base < k_hi; base += ATTN_WARPS * KPW) {
-    const int key = base + kslot;
-    const bool valid = key < k_hi;
-    float kf[16], vf[16];
-    unpack16(kraw, kf);
-    unpack16(vraw, vf);
-    const float kscale = ksc, vscale = vsc;
-    fetch(key + ATTN_WARPS * KPW);
 #pragma unroll
     for (int r = 0; r < RPC; ++r) {
-      float d = 0.f;
+      const float m = warp_max(lmax[r]);
+      if (lane == 0) s_red[warp][r] = m;
+    }
+    __syncthreads();
+    // ---- new running maximum, rescale factor of what was accumulated so far
+    if (tid < RPC) {
+      float m = s_m[tid];
 #pragma unroll
-      for (int e4 = 0; e4 < 4; ++e4) {
-        const float4 qq = *reinterpret_cast<const float4*>(&s_q[r][sub * 16 + e4 * 4]);
-        d += qq.x * kf[e4 * 4] + qq.y * kf[e4 * 4 + 1] + qq.z * kf[e4 * 4 + 2] +
-             qq.w * kf[e4 * 4 + 3];
+      for (int w = 0; w < ATTN_WARPS; ++w) m = fmaxf(m, s_red[w][tid]);
+      s_corr[tid] = s_m[tid] == -INFINITY ? 0.f : exp2f(s_m[tid] - m);
+      s_m[tid] = m;
+    }
+    __syncthreads();
+    // ---- softmax weights of the chunk, once per (head, key)
+    float lsum[RPC];
+#pragma unroll
+    for (int r = 0; r < RPC; ++r) {
+      const float m = s_m[r];
+      float t = 0.f;
+      for (int kk = tid; kk < n; kk += THREADS) {
+        const float p = exp2f(s_p[r][kk] - m);
+        s_p[r][kk] = p;
+        t += p;
       }
-      d *= kscale;
+      lsum[r] = warp_sum(t);
+    }
+    __syncthreads();                           // every warp is done with s_red's maxima
+    if (lane == 0) {
 #pragma unroll
-      for (int o = 1; o < LPK; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-      if (valid) {
-        const float mnew = fmaxf(mx[r], d);
-        const float corr = exp2f(mx[r] - mnew);
-        const float p = exp2f(d - mnew);
-        sum[r] = sum[r] * corr + p;
-        const float pv = p * vscale;
+      for (int r = 0; r < RPC; ++r) s_red[warp][r] = lsum[r];
+    }
+    __syncthreads();
+    if (tid < RPC) {
+      float l = s_l[tid] * s_corr[tid];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) acc[r][e] = acc[r][e] * corr + pv * vf[e];
-        mx[r] = mnew;
+      for (int w = 0; w < ATTN_WARPS; ++w) l += s_red[w][tid];
+      s_l[tid] = l;
+    }
+    if (c0 > k_lo) {
+#pragma unroll
+      for (int r = 0; r < RPC; ++r) {
+        const float c = s_corr[r];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) acc[r][e] *= c;
       }
     }
+    // ---- pass 2: weight x V
+    for (int base = warp * KPW; base < n; base += KPI) {
+      const int kk = base + kslot;
+      if (kk < n) {
+        const int key = c0 + kk;
+        const int page = pages[key >> 7];
+        const size_t slot = (static_cast<size_t>(page) * 128 + (key & 127)) * kvh + h;
+        float vf[16];
+        unpack16(__ldg(reinterpret_cast<const int4*>(vc + slot * D + sub * 16)), vf);
+        const float vsc = __half2float(vs[slot * GROUPS + group]);
+#pragma unroll
+        for (int r = 0; r < RPC; ++r) {
+          const float pv = s_p[r][kk] * vsc;
+#pragma unroll
+          for (int e = 0; e < 16; ++e) acc[r][e] += pv * vf[e];
+        }
+      }
+    }
+    __syncthreads();                           // s_p is rewritten by the next chunk
   }
-  // lanes that only differ in kslot hold states of disjoint key sets: merge them
+  // lanes that only differ in kslot hold sums over disjoint key sets (same reference maximum)
 #pragma unroll
   for (int o = LPK; o < 32; o <<= 1) {
 #pragma unroll
-    for (int r = 0; r < RPC; ++r) {
-      const float mo = __shfl_xor_sync(0xffffffffu, mx[r], o);
-      const float lo = __shfl_xor_sync(0xffffffffu, sum[r], o);
-      const float mnew = fmaxf(mx[r], mo);
-      const float fa = mx[r] == -INFINITY ? 0.f : exp2f(mx[r] - mnew);
-      const float fb = mo == -INFINITY ? 0.f : exp2f(mo - mnew);
-      sum[r] = sum[r] * fa + lo * fb;
+    for (int r = 0; r < RPC; ++r)
 #pragma unroll
-      for (int e = 0; e < 16; ++e) {
-        const float ao = __shfl_xor_sync(0xffffffffu, acc[r][e], o);
-        acc[r][e] = acc[r][e] * fa + ao * fb;
-      }
-      mx[r] = mnew;
-    }
+      for (int e = 0; e < 16; ++e) acc[r][e] += __shfl_xor_sync(0xffffffffu, acc[r][e], o);
   }
-  __shared__ float s_m[ATTN_WARPS][RPC], s_l[ATTN_WARPS][RPC];
-  __shared__ float s_o[ATTN_WARPS][RPC][D];
   if (kslot == 0) {
 #pragma unroll
-    for (int r = 0; r < RPC; ++r) {
-      if (sub == 0) {
-        s_m[warp][r] = mx[r];
-        s_l[warp][r] = sum[r];
-      }
+    for (int r = 0; r < RPC; ++r)
 #pragma unroll
       for (int e = 0; e < 16; ++e) s_o[warp][r][sub * 16 + e] = acc[r][e];
-    }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < RPC * D; i += blockDim.x) {
+  for (int i = tid; i < RPC * D; i += THREADS) {
     const int r = i / D, d = i % D;
-    float m = -INFINITY;
+    float o = 0.f;
 #pragma unroll
-    for (int w = 0; w < ATTN_WARPS; ++w) m = fmaxf(m, s_m[w][r]);
-    float l = 0.f, o = 0.f;
-#pragma unroll
-    for (int w = 0; w < ATTN_WARPS; ++w) {
-      const float f = s_m[w][r] == -INFINITY ? 0.f : exp2f(s_m[w][r] - m);
-      l += s_l[w][r] * f;
-      o += s_o[w][r][d] * f;
-    }
+    for (int w = 0; w < ATTN_WARPS; ++w) o += s_o[w][r][d];
+    const float m = s_m[r], l = s_l[r];
     const int head = head0 + r;
     if (splits == 1) {
       float v = l > 0.f ? o / l : 0.f;

@@ -440,6 +440,17 @@ __device__ __forceinline__ float warp_max(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
+// Sum of squares of one 128-channel block held as floats: lane l covers channels 4l..4l+3
+// in order, then a butterfly over the warp.  Every kernel that normalises rows uses this
+// function, so the sum does not depend on which kernel (or launch shape) computed it.
+__device__ __forceinline__ float block128_sumsq(const float* block, int lane) {
+  const float4 v = *reinterpret_cast<const float4*>(block + lane * 4);
+  float s = __fmul_rn(v.x, v.x);
+  s = __fmaf_rn(v.y, v.y, s);
+  s = __fmaf_rn(v.z, v.z, s);
+  s = __fmaf_rn(v.w, v.w, s);
+  return warp_sum(s);
+}
 __device__ __forceinline__ float round_f16(float v) { return __half2float(__float2half_rn(v)); }
 
 // Activation scale law: FP16 value of max(amax/127, 2^-24), or 1 for an all-zero row.

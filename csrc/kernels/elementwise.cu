@@ -59,6 +59,8 @@ __device__ __forceinline__ float block_reduce(float v, float* red, bool is_max) 
 // memory, summed in rank order.  The row buffer (this CTA's channels as floats) lives in
 // dynamic shared memory.
 //   SWIGLU: x is [M, 2K] (gate | up);   otherwise x is [M, K] (may be null when resid given).
+constexpr int MAX_NORM_BLOCKS = 128;          // rows that are normalised have K <= 16384
+
 template <int CL>
 __device__ __forceinline__ float cluster_reduce(float v, float* slot, bool is_max) {
   if (CL == 1) return v;
@@ -83,6 +85,7 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
   extern __shared__ float rowbuf_raw[];
   __shared__ float red[32];
   __shared__ float cl_slot[2];
+  __shared__ float blk_sum[MAX_NORM_BLOCKS];
   const int tid = threadIdx.x;
   const int crank = CL > 1 ? static_cast<int>(blockIdx.x) % CL : 0;
   const int nblk = K / 128;
@@ -99,7 +102,6 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
   // a device-side row count (rows routed to this rank's experts) bounds the useful work of a
   // launch that was sized for the worst case
   if (row_limit != nullptr && row >= *row_limit) return;
-  float sumsq = 0.f;
   if (SWIGLU) {
     const __half* g = x + static_cast<size_t>(row) * 2 * K;
     const __half* u = g + K;
@@ -172,13 +174,34 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
         *reinterpret_cast<float4*>(rr + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        rowbuf[i + j] = v[j];
-        sumsq += v[j] * v[j];
-      }
+      for (int j = 0; j < 8; ++j) rowbuf[i + j] = v[j];
     }
     if (norm_w) {
-      const float total = cluster_reduce<CL>(block_reduce(sumsq, red, false), &cl_slot[0], false);
+      // Sum of squares in a launch-independent order: one partial per 128-channel block
+      // (fixed lane pattern), then the blocks added in channel order.  One row therefore
+      // normalises to the same bits whether it runs alone (cluster form), in a large packet
+      // or inside another kernel's prologue.
+      __syncthreads();
+      {
+        const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+        for (int b = k_lo / 128 + warp; b < k_hi / 128; b += nw) {
+          const float s = block128_sumsq(rowbuf + b * 128, lane);
+          if (lane == 0) blk_sum[b - k_lo / 128] = s;
+        }
+      }
+      __syncthreads();
+      float total = 0.f;
+      if (CL == 1) {
+        for (int b = 0; b < nblk; ++b) total = __fadd_rn(total, blk_sum[b]);
+      } else {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        for (int c = 0; c < CL; ++c) {
+          const float* remote = cluster.map_shared_rank(blk_sum, c);
+          const int count = nblk * (c + 1) / CL - nblk * c / CL;
+          for (int b = 0; b < count; ++b) total = __fadd_rn(total, remote[b]);
+        }
+      }
       const float r = rsqrtf(total / static_cast<float>(K) + eps);
       const float add = zero_centered ? 1.f : 0.f;
       for (int i = k_lo + tid * 8; i < k_hi; i += blockDim.x * 8) {
@@ -542,6 +565,7 @@ static int act_prep_launch(const __half* x, float* resid, const __half* norm_w, 
   if (runtime_ensure_init() != cudaSuccess) return -2;
   int* status = runtime_status_ptr();
   if (K % 128) return -1;
+  if (norm_w != nullptr && K / 128 > MAX_NORM_BLOCKS) return -1;
   const size_t smem = static_cast<size_t>(K) * sizeof(float);
   static const int slot = runtime_new_slot();
   if (runtime_first_use(slot)) {

@@ -33,9 +33,9 @@ constexpr int TILE_BYTES = 128 * 128;        // one INT8 activation tile (128 ro
 constexpr int PRODUCERS = 512;               // warps 2..17
 constexpr int PWARPS = PRODUCERS / 32;
 constexpr int NUM_SMS = 148;
-// 0: persistent kernel; 1: one tile per CTA; 2: CTA pairs (cta_group::2) where the shape
-// allows, else persistent.  All give the same bits.
-static int g_impl = 0;
+// 0: persistent kernel; 1: one tile per CTA (default: the fastest measured so far); 2: CTA
+// pairs (cta_group::2) where the shape allows, else persistent.  All give the same bits.
+static int g_impl = 1;
 constexpr int THREADS = 64 + PRODUCERS;
 
 template <int FMT, int MT, int NB>
@@ -586,22 +586,33 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_ps_kernel(
           ok = PS_WAIT(&b_full[sb], (cb / SBD) & 1, STATUS_MMA_WAIT, 0x2000 | kb);
           if (!ok) break;
           const uint32_t b_addr = smem_u32(b_s + sb * L::B_BYTES);
-          for (int s = 0; s < T.mt_act; ++s, ++ca) {
-            // the epilogue of the previous tile must have read this accumulator out
-            if (kb == 0 && it > 0)
-              ok = PS_WAIT(&tmem_empty[s], (it - 1) & 1, STATUS_MMA_WAIT, 0x3000 | s);
-            const uint32_t slot = ca % NSLOT;
-            if (ok) ok = PS_WAIT(&a_full[slot], (ca / NSLOT) & 1, STATUS_MMA_WAIT, kb);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t a_addr = smem_u32(a_s + slot * TILE_BYTES);
+          uint32_t a_addr[MT];
 #pragma unroll
-            for (int j = 0; j < BK / 32; ++j)
-              mma_i8_ss(tmem_base + s * BN, umma_desc(a_addr + j * 32, 16, 1024),
-                        umma_desc(b_addr + j * 32, 16, 1024), idesc, (kb | j) != 0 ? 1u : 0u);
-            tc_commit(&a_empty[slot]);
+          for (int s = 0; s < MT; ++s) {
+            if (s < T.mt_act && ok) {
+              // the epilogue of the previous tile must have read this accumulator out
+              if (kb == 0 && it > 0)
+                ok = PS_WAIT(&tmem_empty[s], (it - 1) & 1, STATUS_MMA_WAIT, 0x3000 | s);
+              const uint32_t slot = (ca + s) % NSLOT;
+              if (ok) ok = PS_WAIT(&a_full[slot], ((ca + s) / NSLOT) & 1, STATUS_MMA_WAIT, kb);
+              a_addr[s] = smem_u32(a_s + slot * TILE_BYTES);
+            }
           }
-          if (ok) tc_commit(&b_empty[sb]);
+          if (!ok) break;
+          tc_fence_after();
+          // consecutive MMAs go to different accumulators: back-to-back accumulation into one
+          // TMEM tile would serialise on it
+#pragma unroll
+          for (int j = 0; j < BK / 32; ++j) {
+            const uint64_t bdesc = umma_desc(b_addr + j * 32, 16, 1024);
+#pragma unroll
+            for (int s = 0; s < MT; ++s)
+              if (s < T.mt_act)
+                mma_i8_ss(tmem_base + s * BN, umma_desc(a_addr[s] + j * 32, 16, 1024), bdesc,
+                          idesc, (kb | j) != 0 ? 1u : 0u);
+          }
+          for (int s = 0; s < T.mt_act; ++s, ++ca) tc_commit(&a_empty[ca % NSLOT]);
+          tc_commit(&b_empty[sb]);
         }
         if (ok) {
           if (kbs > 0) {
@@ -1003,21 +1014,30 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_pair_kernel(
           ok = PR_WAIT(&b_full[sb], (cb / SBD) & 1, STATUS_MMA_WAIT, 0x2000 | kb);
           if (!ok) break;
           const uint32_t b_addr = smem_u32(b_s + sb * L::B_BYTES);
-          for (int s = 0; s < T.mt_act; ++s, ++ca) {
-            if (kb == 0 && it > 0)
-              ok = PR_WAIT(&tmem_empty[s], (it - 1) & 1, STATUS_MMA_WAIT, 0x3000 | s);
-            const uint32_t slot = ca % NSLOT;
-            if (ok) ok = PR_WAIT(&a_full[slot], (ca / NSLOT) & 1, STATUS_MMA_WAIT, kb);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t a_addr = smem_u32(a_s + slot * TILE_BYTES);
+          uint32_t a_addr[MT];
 #pragma unroll
-            for (int j = 0; j < BK / 32; ++j)
-              mma_i8_ss_pair(tmem_base + s * BN, umma_desc(a_addr + j * 32, 16, 1024),
-                             umma_desc(b_addr + j * 32, 16, 1024), idesc, (kb | j) != 0 ? 1u : 0u);
-            tc_commit_pair(&a_empty[slot], 3);
+          for (int s = 0; s < MT; ++s) {
+            if (s < T.mt_act && ok) {
+              if (kb == 0 && it > 0)
+                ok = PR_WAIT(&tmem_empty[s], (it - 1) & 1, STATUS_MMA_WAIT, 0x3000 | s);
+              const uint32_t slot = (ca + s) % NSLOT;
+              if (ok) ok = PR_WAIT(&a_full[slot], ((ca + s) / NSLOT) & 1, STATUS_MMA_WAIT, kb);
+              a_addr[s] = smem_u32(a_s + slot * TILE_BYTES);
+            }
           }
-          if (ok) tc_commit_pair(&b_empty[sb], 3);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int j = 0; j < BK / 32; ++j) {
+            const uint64_t bdesc = umma_desc(b_addr + j * 32, 16, 1024);
+#pragma unroll
+            for (int s = 0; s < MT; ++s)
+              if (s < T.mt_act)
+                mma_i8_ss_pair(tmem_base + s * BN, umma_desc(a_addr[s] + j * 32, 16, 1024), bdesc,
+                               idesc, (kb | j) != 0 ? 1u : 0u);
+          }
+          for (int s = 0; s < T.mt_act; ++s, ++ca) tc_commit_pair(&a_empty[ca % NSLOT], 3);
+          tc_commit_pair(&b_empty[sb], 3);
         }
         if (ok) {
           if (kbs > 0) {

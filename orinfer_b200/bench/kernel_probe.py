@@ -204,7 +204,7 @@ def main():
     g.add_argument("--path", default="auto", choices=["auto", "simt", "tc"])
     g.add_argument("--rotate", action="store_true")
     g.add_argument("--iters", type=int, default=20)
-    g.add_argument("--impl", type=int, default=0, help="0 persistent kernel, 1 one tile per CTA, 2 CTA pairs")
+    g.add_argument("--impl", type=int, default=1, help="0 persistent kernel, 1 one tile per CTA, 2 CTA pairs")
     ad = sub.add_parser("attn-decode")
     ad.add_argument("--rows", type=int, default=1)
     ad.add_argument("--ctx", type=int, default=512)

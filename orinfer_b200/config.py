@@ -149,6 +149,10 @@ PRESETS = {
                                gdn_k_heads=2, gdn_v_heads=4, gdn_head_dim=64, experts=8, top_k=2,
                                expert_ffn=128, shared_expert_ffn=128, ffn=0, gated_attention=True,
                                expert_format="q2"),
+    # mid-size geometry for multi-GPU tests: splits over 2, 4 and 8 ranks, and is large
+    # enough that split-K, tail-peeled and sequence-parallel GEMM launches all occur
+    "mid-dense": ModelConfig(name="mid-dense", layers=4, hidden=1024, q_heads=16, kv_heads=8,
+                             head_dim=64, ffn=4096, vocab=8192),
     "qwen3.5-4b-class": ModelConfig(
         name="qwen3.5-4b-class", layers=36, hidden=2560, q_heads=32, kv_heads=8, head_dim=128,
         ffn=9728, vocab=151936, tied_embeddings=True, mtp_layers=1),

@@ -69,6 +69,7 @@ class EngineStatistics:
     restored_pages: int = 0
     sharded_samples: int = 0                  # rows drawn from a sharded head's candidates
     layered_decode_steps: int = 0             # decode steps taken inside paused prefill packets
+    resident_steps: int = 0                   # decode steps that needed no input upload
     stored_snapshots: int = 0                 # recurrent-state endpoints kept for the prefix cache
     restored_snapshots: int = 0
 
@@ -85,6 +86,14 @@ class _DecodeGraph:
         self.rows = rows
         self.ids, self.req, self.pos = z(rows), z(rows), z(rows)
         self.tokens = z(rows)
+        # Device-resident step control: the captured step ends by writing its own next inputs
+        # (ids <- sampled tokens, pos <- pos + live), so a step over the same requests needs
+        # no upload at all; ``members`` / ``host_pos`` are the host's record of what the
+        # device buffers hold (kernels/cuda/model/control.py:9,27 of the reference keeps
+        # position, length and token on the device in the same way).
+        self.live = z(rows)
+        self.members: Optional[tuple] = None
+        self.host_pos: List[int] = []
         self.logits = torch.zeros(rows, engine.cfg.vocab, dtype=torch.float32, device=dev)
         self.packet = Packet(self.ids, self.req, self.pos, engine.page_table_dev, rows,
                              engine.max_context)
@@ -1011,26 +1020,35 @@ class Engine:
         self.stats.graph_hits += 1
         return e["tok"], e["lg"]
 
-    def _exec_decode(self, bucket: int, need: bool, ids, slots, pos) -> "_DecodeGraph":
+    def _exec_decode(self, bucket: int, need: bool, ids, slots, pos, live) -> "_DecodeGraph":
         """One pure-decode packet of ``bucket`` rows (padded): warm, capture at the second
-        use, replay afterwards.  Returns the graph record holding the output buffers."""
+        use, replay afterwards.  ``ids is None``: the device buffers already hold this step's
+        inputs (written by the previous step).  Returns the record holding the outputs."""
         t1 = time.monotonic()
         g = self._graphs.get((bucket, need))
         if g is None:
             g = self._graphs[(bucket, need)] = _DecodeGraph(self, bucket)
-        g.ids.copy_(self._upload("ids", ids), non_blocking=True)
-        g.req.copy_(self._upload("req", slots), non_blocking=True)
-        g.pos.copy_(self._upload("pos", pos), non_blocking=True)
+        if ids is not None:
+            g.ids.copy_(self._upload("ids", ids), non_blocking=True)
+            g.req.copy_(self._upload("req", slots), non_blocking=True)
+            g.pos.copy_(self._upload("pos", pos), non_blocking=True)
+            g.live.copy_(self._upload("live", live), non_blocking=True)
+
+        def body():
+            self.runner.greedy(g.packet, g.logits, g.tokens, need_logits=need)
+            torch.clamp(g.tokens, min=0, out=g.ids)      # next step's inputs, on the device
+            g.pos.add_(g.live)
+
         if g.graph is None:
             g.trials += 1
-            self.runner.greedy(g.packet, g.logits, g.tokens, need_logits=need)   # warm
+            body()                                       # warm
             if g.trials >= 2:
                 torch.cuda.synchronize()
                 graph = torch.cuda.CUDAGraph()
                 from ..ops import native
                 before = native.launches()
-                with torch.cuda.graph(graph):
-                    self.runner.greedy(g.packet, g.logits, g.tokens, need_logits=need)
+                with torch.cuda.graph(graph):            # records only: nothing runs here
+                    body()
                 g.graph = graph
                 g.local = getattr(self.runner, "_last_local", None)
                 g.launches = native.launches() - before
@@ -1051,13 +1069,25 @@ class Engine:
         bucket = next(b for b in DECODE_BUCKETS if b >= n)
         need = any(self._needs_logits(r) for r in decoders)
         pad = bucket - n
-        ids = [r.pending for r in decoders] + [0] * pad
-        slots = [r.slot for r in decoders] + [self.pad_slot] * pad
-        pos = [r.offset for r in decoders] + [0] * pad
-        self._publish("decode", (bucket, need, ids, slots, pos))
+        g = self._graphs.get((bucket, need))
+        members = tuple(r.slot for r in decoders)
+        resident = (g is not None and g.graph is not None and g.members == members
+                    and all(self._plain(r) for r in decoders)
+                    and all(r.offset == p for r, p in zip(decoders, g.host_pos)))
+        if resident:
+            self._publish("decode", (bucket, need, None, None, None, None))
+            args = (None, None, None, None)
+            self.stats.resident_steps += 1
+        else:
+            args = ([r.pending for r in decoders] + [0] * pad,
+                    [r.slot for r in decoders] + [self.pad_slot] * pad,
+                    [r.offset for r in decoders] + [0] * pad, [1] * n + [0] * pad)
+            self._publish("decode", (bucket, need, *args))
         t1 = time.monotonic()
         self.stats.batch_inputs_s += t1 - t0
-        g = self._exec_decode(bucket, need, ids, slots, pos)
+        g = self._exec_decode(bucket, need, *args)
+        g.members = members
+        g.host_pos = [r.offset + 1 for r in decoders]    # what the device holds after this step
         self._status_enqueue()
         tokens = g.tokens[:n].cpu()
         self._status_check()

@@ -79,6 +79,14 @@ class _Inbox(ctypes.Structure):
                 ("ticket", c_void_p), ("tp", c_int), ("rows_cap", c_int), ("ll", c_void_p)]
 
 
+class _HeadMerge(ctypes.Structure):
+    _fields_ = [("table", c_void_p * 8), ("seq", c_void_p), ("tp", c_int), ("rank", c_int),
+                ("cap", c_int)]
+
+
+HEAD_ROWS = 1024
+
+
 LL_MODE, LL_ROWS = -1, 8
 
 
@@ -111,7 +119,8 @@ class PeerMemory:
         # low-latency regions (decode-sized packets): units of {2 x fp16, sequence number}
         ll_bytes = (self.world * LL_ROWS * (hidden // 2) * 8 + 255) // 256 * 256
         ll_off = ag_off + ag_q_bytes + ag_s_bytes + flag_bytes
-        total = ll_off + len(OPS) * ll_bytes
+        head_off = ll_off + len(OPS) * ll_bytes        # greedy-token merge table [tp][rows][16 B]
+        total = head_off + self.world * HEAD_ROWS * 16
         self.base = lib.orinfer_peer_alloc(total)
         if not self.base:
             raise native.KernelError(f"cannot allocate {total} bytes of peer memory")
@@ -161,6 +170,12 @@ class PeerMemory:
             li = _Inbox(None, None, lp + (40 + 4 * i + 2) * 4, lp + (40 + 4 * i + 3) * 4,
                         self.world, rows_cap, bases[self.rank] + ll_off + i * ll_bytes)
             self.ll_out[op], self.ll_in[op] = lo, li
+        hm = _HeadMerge()
+        for r in range(8):
+            hm.table[r] = bases[r] + head_off if r < self.world else None
+        hm.seq = lp + 56 * 4
+        hm.tp, hm.rank, hm.cap = self.world, self.rank, HEAD_ROWS
+        self.head_merge = hm
         # all-gather activation buffer (INT8 rows + scales) and its flags
         ag = _AgOut()
         for r in range(8):
@@ -209,6 +224,8 @@ def _setup_lib():
     lib.orinfer_qgemm_ag.restype = I
     lib.orinfer_ag_wait.argtypes = [ctypes.POINTER(_AgIn), I, P]
     lib.orinfer_ag_wait.restype = I
+    lib.orinfer_tp_head_merge.argtypes = [P, P, I, I, I, ctypes.POINTER(_HeadMerge), P, P]
+    lib.orinfer_tp_head_merge.restype = I
     return lib
 
 
@@ -234,6 +251,29 @@ class FusedTPRunner(TPRunner):
         if a2a is not None and hasattr(a2a, "close"):
             a2a.close()
         self.mem.close()
+
+    def greedy(self, p, logits_out=None, token_out=None, need_logits: bool = True):
+        """The sharded head's greedy token through the peer tables (one small kernel, no
+        collective call); full logits are still gathered with NCCL when a caller needs them."""
+        from ..ops import functional as F
+        local = self._last_local = self.logits(p)                      # [n_sel, V/tp]
+        rows = local.shape[0]
+        if rows > HEAD_ROWS or os.environ.get("ORINFER_TP_HEAD_MERGE", "1") == "0":
+            return super().greedy(p, logits_out, token_out, need_logits)
+        ltok = F.argmax(local)
+        tok = token_out if token_out is not None else \
+            torch.empty(rows, dtype=torch.int32, device=local.device)
+        check(self.lib.orinfer_tp_head_merge(ptr(local), ptr(ltok), rows, local.shape[1],
+                                             self.vocab0, ctypes.byref(self.mem.head_merge),
+                                             ptr(tok), stream()), "tp_head_merge")
+        count_launches(1)
+        full = None
+        if need_logits:
+            full = self._gather_logits(local)
+            if logits_out is not None:
+                logits_out[:full.shape[0]].copy_(full)
+                full = logits_out
+        return tok, full
 
     _SLOT = {"o": "o", "gdn_out": "o", "down": "down"}
 

@@ -86,8 +86,20 @@ class TPRunner(_TPMixin, ModelRunner):
     def __init__(self, weights: ModelWeights, kv: KVPool, max_rows: int, group=None):
         ModelRunner.__init__(self, weights, kv, max_rows)
         self._init_tp(weights, group)
+        import os
+        self._exact_reduce = os.environ.get("ORINFER_TP_EXACT_REDUCE") == "1"
 
     def _reduce(self, x, rows: int):
+        if self._exact_reduce:
+            # same arithmetic as the fused path's consumer: FP16 partials summed in FP32 in
+            # rank order, rounded once; lets tests compare the two arms bit for bit
+            parts = [torch.empty_like(x[:rows]) for _ in range(self.world)]
+            dist.all_gather(parts, x[:rows].contiguous(), group=self.group)
+            acc = parts[0].float()
+            for p in parts[1:]:
+                acc += p.float()
+            x[:rows].copy_(acc.to(x.dtype))
+            return x
         dist.all_reduce(x[:rows], group=self.group)
         return x
 

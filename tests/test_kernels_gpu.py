@@ -111,7 +111,7 @@ def _rand_weight(fmt, n, k, dev, seed):
 def test_qgemm(cuda, fmt, m, n, k, path):
     from orinfer_b200.ops import functional as F
     from orinfer_b200.ops import native
-    native.qgemm_set_impl(0)
+    native.qgemm_set_impl(1)
     g = torch.Generator().manual_seed(m * 7 + n)
     a = torch.randint(-127, 128, (m, k), generator=g, dtype=torch.int8).to(cuda)
     sa = (torch.rand(m, generator=g) * 0.05 + 1e-3).to(cuda)
@@ -126,9 +126,9 @@ def test_qgemm(cuda, fmt, m, n, k, path):
 
 @pytest.mark.parametrize("fmt", ["w8", "q4"])
 @pytest.mark.parametrize("m,n,k", [(600, 19456, 256), (512, 2560, 9728), (100, 12800, 256),
-                                   (513, 2560, 1024)])
-def test_qgemm_one_tile_per_cta_form(cuda, fmt, m, n, k):
-    """The non-persistent kernel gives the same bits as the persistent one."""
+                                   (513, 2560, 1024), (1100, 19456, 1024), (2100, 9728, 384)])
+def test_qgemm_persistent_form(cuda, fmt, m, n, k):
+    """The persistent kernel gives the same bits as the one-tile-per-CTA one."""
     from orinfer_b200.ops import functional as F
     from orinfer_b200.ops import native
     g = torch.Generator().manual_seed(m + n)
@@ -136,11 +136,11 @@ def test_qgemm_one_tile_per_cta_form(cuda, fmt, m, n, k):
     sa = (torch.rand(m, generator=g) * 0.05 + 1e-3).to(cuda)
     codes, ws, w_int = _rand_weight(fmt, n, k, cuda, seed=k + n)
     try:
-        native.qgemm_set_impl(1)
+        native.qgemm_set_impl(0)
         out = F.qgemm(a, sa, codes, ws, fmt, n)
         torch.cuda.synchronize()
     finally:
-        native.qgemm_set_impl(0)
+        native.qgemm_set_impl(1)
     assert torch.equal(out.float(), R.qgemm(a, sa, w_int, ws))
 
 
@@ -163,7 +163,7 @@ def test_qgemm_cta_pair_form(cuda, fmt, m, n, k):
         out32 = F.qgemm(a, sa, codes, ws, fmt, n, out_f32=True)
         torch.cuda.synchronize()
     finally:
-        native.qgemm_set_impl(0)
+        native.qgemm_set_impl(1)
     assert torch.equal(out.float(), R.qgemm(a, sa, w_int, ws))
     assert torch.equal(out32, R.qgemm(a, sa, w_int, ws, out_f32=True))
 

@@ -16,7 +16,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def _worker(rank, world, port, out_dir, preset, sp=False):
     sys.path.insert(0, ROOT)
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      ORINFER_TP_EXACT_REDUCE="1")
     if sp:       # sequence-parallel prefill (reduce-scatter + all-gather by push) from 64 rows
         os.environ.update(ORINFER_TP_SP_MIN_ROWS="64", ORINFER_TP_SP_WORLD1="1")
     torch.cuda.set_device(rank)
@@ -37,24 +38,24 @@ def _worker(rank, world, port, out_dir, preset, sp=False):
     g = torch.Generator().manual_seed(1)
     res = {}
     for name, cls in (("nccl", TPRunner), ("fused", FusedTPRunner)):
-        runner = cls(shard, KVPool.allocate(shard.config, 6, dev), 256)
+        runner = cls(shard, KVPool.allocate(shard.config, 6, dev), 512)
         outs = []
         gg = torch.Generator().manual_seed(1)
-        n = 150                                          # tensor-core GEMM path
+        n = 150 if cfg.hidden < 1024 else 300             # tensor-core GEMM path
         ids = torch.randint(0, cfg.vocab, (n,), generator=gg, dtype=torch.int32).to(dev)
-        p = Packet(ids, t([0] * n), t(list(range(n))), t([[1, 2]]), n, n,
+        p = Packet(ids, t([0] * n), t(list(range(n))), t([[1, 2, 3]]), n, n,
                    torch.tensor([n - 1], device=dev))
         tok, lg = runner.greedy(p)
         outs.append((tok.cpu(), lg.cpu()))
         for step in range(3):                            # dp4a decode path, twice-used inboxes
-            p = Packet(tok.clone(), t([0]), t([n + step]), t([[1, 2]]), 1, n + step + 1)
+            p = Packet(tok.clone(), t([0]), t([n + step]), t([[1, 2, 3]]), 1, n + step + 1)
             tok, lg = runner.greedy(p)
             outs.append((tok.cpu(), lg.cpu()))
         # graph replay of the decode step with changed inputs (a recurrent model's state
         # advances with every run, so replay-vs-eager equality only holds without GDN layers)
         if name == "fused" and cfg.arch != "hybrid":
             ids1, pos1 = t([5]), t([n + 3])
-            pk = Packet(ids1, t([0]), pos1, t([[1, 2]]), 1, 256)
+            pk = Packet(ids1, t([0]), pos1, t([[1, 2, 3]]), 1, 384)
             lgb = torch.empty(1, cfg.vocab, device=dev)
             tkb = torch.empty(1, dtype=torch.int32, device=dev)
             runner.greedy(pk, lgb, tkb)
@@ -73,11 +74,11 @@ def _worker(rank, world, port, out_dir, preset, sp=False):
         torch.cuda.synchronize()
         assert native.read_status() == 0
     if rank == 0:
-        single = ModelRunner(full, KVPool.allocate(cfg, 6, dev), 256)
-        n = 150
+        single = ModelRunner(full, KVPool.allocate(cfg, 6, dev), 512)
+        n = 150 if cfg.hidden < 1024 else 300
         gg = torch.Generator().manual_seed(1)
         ids = torch.randint(0, cfg.vocab, (n,), generator=gg, dtype=torch.int32).to(dev)
-        p = Packet(ids, t([0] * n), t(list(range(n))), t([[1, 2]]), n, n,
+        p = Packet(ids, t([0] * n), t(list(range(n))), t([[1, 2, 3]]), n, n,
                    torch.tensor([n - 1], device=dev))
         _, lg = single.greedy(p)
         res["single"] = lg.cpu()
@@ -102,6 +103,11 @@ def _check(tmp_path, world, preset="tiny", sp=False):
     for (tn, ln), (tf, lf) in zip(res["nccl"], res["fused"]):
         cos = torch.nn.functional.cosine_similarity(ln.flatten(), lf.flatten(), dim=0)
         assert cos > 0.9995, cos
+        assert torch.equal(tn, tf)
+        if preset in ("tiny", "mid-dense"):
+            # dense models: the NCCL arm reduces with the fused consumer's arithmetic (FP16
+            # partials, FP32 sum in rank order), so the two arms agree bit for bit
+            assert torch.equal(ln, lf), float((ln - lf).abs().max())
     cos = torch.nn.functional.cosine_similarity(res["fused"][0][1].flatten(),
                                                 res["single"].flatten(), dim=0)
     # sharding changes the per-row activation scales (each rank quantises its own slice of
@@ -124,6 +130,16 @@ def test_fused_tp_world2(cuda, tmp_path, preset):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     _check(tmp_path, 2, preset)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("sp", [False, True])
+def test_fused_tp_mid_size_all_worlds(cuda, tmp_path, world, sp):
+    """Mid-size dense model over every rank count the machine has: fused arm equals the NCCL
+    arm bit for bit, decode-sized (all-reduce / low-latency) and sequence-parallel forms."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _check(tmp_path, world, "mid-dense", sp=sp)
 
 
 def test_fused_sequence_parallel_world1(cuda, tmp_path):
