@@ -347,15 +347,23 @@ def main() -> int:
             extra["mtp_random_weights"] = accept
             # a draft head with something to predict (see bigram_like): same GEMMs, same
             # formats, measured acceptance reported beside the rate
-            # pick the branch strength whose fixed-width acceptance is closest to the 0.6-0.8
-            # a trained draft head reaches, then measure with the adaptive controller
-            for strength in (1.0, 0.5, 0.25, 0.12, 0.06):
+            # raise the branch strength until the fixed-width acceptance falls below what a
+            # trained draft head reaches (0.6-0.8), keep the last one above it, then measure
+            # with the adaptive controller
+            chosen, seen = None, {}
+            for strength in (0.0005, 0.001, 0.002, 0.004, 0.008, 0.016, 0.03, 0.06, 0.12, 0.25):
                 bigram_like(engine.w, torch, strength)
                 engine._graphs.clear()            # captured steps hold the old embedding
                 engine.__dict__.pop("_prefill_graphs", None)
                 _, _, probe = decode_rate(1, 512, 64, mtp=True, policy="fixed3")
-                if (probe["acceptance"] or 0.0) >= 0.6:
+                seen[strength] = probe["acceptance"]
+                if (probe["acceptance"] or 0.0) < 0.6:
                     break
+                chosen = strength
+            strength = chosen if chosen is not None else 0.0005
+            bigram_like(engine.w, torch, strength)
+            engine._graphs.clear()
+            extra["mtp_strength_scan"] = seen
             extra["mtp_branch_strength"] = strength
             rate0, _, _ = decode_rate(1, 512, 256)
             rate, ms, accept = decode_rate(1, 512, 256, mtp=True)

@@ -440,6 +440,46 @@ __device__ __forceinline__ float warp_max(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
+// Sum or maximum over the CTA; `red` is 32 floats of shared memory.  Every thread gets the
+// result.  (For maxima of non-negative values.)
+__device__ __forceinline__ float block_reduce(float v, float* red, bool is_max) {
+  v = is_max ? warp_max(v) : warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = (lane < nw) ? red[lane] : 0.f;
+  r = is_max ? warp_max(r) : warp_sum(r);
+  return r;
+}
+
+// Signed block-128 Hadamard rotation of one block held as floats, in place: lane l holds
+// channels 4l..4l+3.  Returns the largest magnitude of the lane's four results.  Shared by
+// every kernel that rotates activations, so the bits do not depend on the kernel.
+__device__ __forceinline__ float hadamard128_inplace(float* block, const int8_t* signs, int lane) {
+  float* p = block + lane * 4;
+  const char4 sg = *reinterpret_cast<const char4*>(signs + lane * 4);
+  float v0 = p[0] * sg.x, v1 = p[1] * sg.y, v2 = p[2] * sg.z, v3 = p[3] * sg.w;
+  float t0 = v0 + v1, t1 = v0 - v1, t2 = v2 + v3, t3 = v2 - v3;      // h = 1
+  v0 = t0 + t2; v2 = t0 - t2; v1 = t1 + t3; v3 = t1 - t3;            // h = 2
+#pragma unroll
+  for (int m = 1; m < 32; m <<= 1) {                                   // h = 4 .. 64
+    const float o0 = __shfl_xor_sync(0xffffffffu, v0, m);
+    const float o1 = __shfl_xor_sync(0xffffffffu, v1, m);
+    const float o2 = __shfl_xor_sync(0xffffffffu, v2, m);
+    const float o3 = __shfl_xor_sync(0xffffffffu, v3, m);
+    const bool hi = (lane & m) != 0;
+    v0 = hi ? o0 - v0 : v0 + o0;
+    v1 = hi ? o1 - v1 : v1 + o1;
+    v2 = hi ? o2 - v2 : v2 + o2;
+    v3 = hi ? o3 - v3 : v3 + o3;
+  }
+  const float c = 0.08838834764831845f;                                // 128^-1/2
+  v0 *= c; v1 *= c; v2 *= c; v3 *= c;
+  p[0] = v0; p[1] = v1; p[2] = v2; p[3] = v3;
+  return fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
+}
+
 // Sum of squares of one 128-channel block held as floats: lane l covers channels 4l..4l+3
 // in order, then a butterfly over the warp.  Every kernel that normalises rows uses this
 // function, so the sum does not depend on which kernel (or launch shape) computed it.

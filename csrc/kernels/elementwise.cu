@@ -42,23 +42,6 @@ __global__ void embed_w8_kernel(const int* __restrict__ ids, const int8_t* __res
 }
 
 // ------------------------------------------------------------------ act_prep
-__device__ __forceinline__ float block_reduce(float v, float* red, bool is_max) {
-  v = is_max ? warp_max(v) : warp_sum(v);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  __syncthreads();
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  float r = (lane < nw) ? red[lane] : (is_max ? 0.f : 0.f);
-  r = is_max ? warp_max(r) : warp_sum(r);
-  return r;
-}
-
-// One CTA per row, or (CL > 1, launches of a few rows) a thread-block cluster of CL CTAs per
-// row: each CTA of the cluster takes a contiguous run of 128-channel blocks, and the two
-// row-wide reductions (sum of squares, absolute maximum) meet through distributed shared
-// memory, summed in rank order.  The row buffer (this CTA's channels as floats) lives in
-// dynamic shared memory.
-//   SWIGLU: x is [M, 2K] (gate | up);   otherwise x is [M, K] (may be null when resid given).
 constexpr int MAX_NORM_BLOCKS = 128;          // rows that are normalised have K <= 16384
 
 template <int CL>
@@ -233,27 +216,7 @@ __global__ void __launch_bounds__(256) act_prep_kernel(
     // Each warp transforms whole 128-blocks; lane holds 4 consecutive values.
     const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
     for (int b = k_lo / 128 + warp; b < k_hi / 128; b += nw) {
-      float* p = rowbuf + b * 128 + lane * 4;
-      const char4 sg = *reinterpret_cast<const char4*>(signs + b * 128 + lane * 4);
-      float v0 = p[0] * sg.x, v1 = p[1] * sg.y, v2 = p[2] * sg.z, v3 = p[3] * sg.w;
-      float t0 = v0 + v1, t1 = v0 - v1, t2 = v2 + v3, t3 = v2 - v3;      // h = 1
-      v0 = t0 + t2; v2 = t0 - t2; v1 = t1 + t3; v3 = t1 - t3;            // h = 2
-#pragma unroll
-      for (int m = 1; m < 32; m <<= 1) {                                   // h = 4 .. 64
-        const float o0 = __shfl_xor_sync(0xffffffffu, v0, m);
-        const float o1 = __shfl_xor_sync(0xffffffffu, v1, m);
-        const float o2 = __shfl_xor_sync(0xffffffffu, v2, m);
-        const float o3 = __shfl_xor_sync(0xffffffffu, v3, m);
-        const bool hi = (lane & m) != 0;
-        v0 = hi ? o0 - v0 : v0 + o0;
-        v1 = hi ? o1 - v1 : v1 + o1;
-        v2 = hi ? o2 - v2 : v2 + o2;
-        v3 = hi ? o3 - v3 : v3 + o3;
-      }
-      const float c = 0.08838834764831845f;                                // 128^-1/2
-      v0 *= c; v1 *= c; v2 *= c; v3 *= c;
-      p[0] = v0; p[1] = v1; p[2] = v2; p[3] = v3;
-      amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3))));
+      amax = fmaxf(amax, hadamard128_inplace(rowbuf + b * 128, signs + b * 128, lane));
     }
   } else {
     for (int i = k_lo + tid; i < k_hi; i += blockDim.x) amax = fmaxf(amax, fabsf(rowbuf[i]));

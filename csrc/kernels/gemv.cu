@@ -62,6 +62,30 @@ __device__ __forceinline__ void store_row(void* out, int out_f32, int m, int n, 
 constexpr int GEMV_COPIES = 32;
 constexpr int GEMV_DEPTH = 4;
 
+// Optional fusion of the decode step's row kernels into the projection (at most 8 rows, no
+// peers).  `pre` builds the INT8 activations inside every CTA instead of reading them:
+//   1: rows = resid (+ x), RMSNorm with norm_w, rotation, A8        (x and norm_w may be null)
+//   2: rows = x (FP16 [M, K]), rotation, A8
+//   3: rows = SwiGLU of x (FP16 [M, 2K]: gate | up), rotation, A8
+// with exactly the arithmetic of act_prep_kernel (same helpers, same order), so a row gives
+// the same bits through either path.  Every CTA repeats the (small) row preparation; CTA 0
+// also stores what other kernels may read (y_out, q_out, scale_out).  `resid_accum` adds the
+// FP16-rounded output into an FP32 matrix: the residual stream then already contains the
+// branch output when the next prologue reads it, so no kernel both reads and writes it.
+struct GemvFuse {
+  int pre;
+  const __half* x;
+  const float* resid;
+  const __half* norm_w;
+  const int8_t* signs;
+  float eps;
+  int zero_centered;
+  int8_t* q_out;
+  float* scale_out;
+  __half* y_out;
+  float* resid_accum;
+};
+
 template <int MT>
 struct GemvThreads {
   static constexpr int value = MT <= 2 ? 1024 : 512;
@@ -72,7 +96,7 @@ __global__ void __launch_bounds__(GemvThreads<MT>::value, 1) e8p_gemv_kernel(
     const int8_t* __restrict__ a, const float* __restrict__ a_scale, const uint4* __restrict__ w,
     const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K, int out_f32,
     const E8pTables* __restrict__ tables, PeerOut po, int n_parts, int k_parts, int max_groups,
-    int* __restrict__ ws) {
+    int* __restrict__ ws, GemvFuse fz) {
   constexpr int THREADS = GemvThreads<MT>::value;
   constexpr int ROWS = FMT == 1 ? 8 : 16;
   constexpr int LPR = 32 / ROWS;                 // lanes per row
@@ -87,13 +111,18 @@ __global__ void __launch_bounds__(GemvThreads<MT>::value, 1) e8p_gemv_kernel(
   int8_t* act = reinterpret_cast<int8_t*>(smem_raw) + sizeof(Lut);
   int* acc_s = reinterpret_cast<int*>(act + static_cast<size_t>(MT) * K);   // [groups][ROWS][MT]
   int* asum = acc_s + max_groups * ROWS * MT;                                // [MT]
+  float* scale_s = reinterpret_cast<float*>(asum + MT);                      // [MT]
+  float* fbuf = reinterpret_cast<float*>(                                    // [MT][K], pre only
+      (reinterpret_cast<uintptr_t>(scale_s + MT) + 15) & ~static_cast<uintptr_t>(15));
   __shared__ int last_flag;
+  __shared__ float red[32];
+  __shared__ float blk_sum[128];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   e8p_lut_init(lut, tables, tid, THREADS);
   for (int i = tid; i < max_groups * ROWS * MT + MT; i += THREADS) acc_s[i] = 0;
   __syncthreads();
-  {
+  if (fz.pre == 0) {
     // stage the activations; their row sums ride along
     const int chunks = MT * K / 16;
     int part_sum[MT];
@@ -118,6 +147,122 @@ __global__ void __launch_bounds__(GemvThreads<MT>::value, 1) e8p_gemv_kernel(
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
       if (lane == 0 && s != 0) atomicAdd(&asum[m], s);
+    }
+    if (tid < MT) scale_s[tid] = tid < M ? a_scale[tid] : 0.f;
+  } else {
+    // build the activations: the row kernels' work, repeated by every CTA
+    constexpr int NWP = THREADS / 32;
+    const bool first_cta = blockIdx.x == 0;
+    for (int m = 0; m < MT; ++m) {
+      int8_t* arow = act + static_cast<size_t>(m) * K;
+      if (m >= M) {
+        for (int i = tid * 16; i < K; i += THREADS * 16)
+          *reinterpret_cast<int4*>(arow + i) = make_int4(0, 0, 0, 0);
+        continue;
+      }
+      float* fb = fbuf + static_cast<size_t>(m) * K;
+      if (fz.pre == 3) {
+        const __half* g = fz.x + static_cast<size_t>(m) * 2 * K;
+        const __half* u = g + K;
+        for (int i = tid * 8; i < K; i += THREADS * 8) {
+          const int4 gr = *reinterpret_cast<const int4*>(g + i);
+          const int4 ur = *reinterpret_cast<const int4*>(u + i);
+          const __half* gh = reinterpret_cast<const __half*>(&gr);
+          const __half* uh = reinterpret_cast<const __half*>(&ur);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float gv = __half2float(gh[j]);
+            const float sg = __fdiv_rn(1.f, 1.f + expf(-gv));
+            fb[i + j] = round_f16(__fmul_rn(__fmul_rn(gv, sg), __half2float(uh[j])));
+          }
+        }
+      } else {
+        const __half* xr = fz.x ? fz.x + static_cast<size_t>(m) * K : nullptr;
+        const float* rr = (fz.pre == 1 && fz.resid) ? fz.resid + static_cast<size_t>(m) * K
+                                                    : nullptr;
+        for (int i = tid * 8; i < K; i += THREADS * 8) {
+          float v[8];
+          if (xr) {
+            const int4 raw = *reinterpret_cast<const int4*>(xr + i);
+            const __half* h = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __half2float(h[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = 0.f;
+          }
+          if (rr) {
+            const float4 r0 = *reinterpret_cast<const float4*>(rr + i);
+            const float4 r1 = *reinterpret_cast<const float4*>(rr + i + 4);
+            v[0] += r0.x; v[1] += r0.y; v[2] += r0.z; v[3] += r0.w;
+            v[4] += r1.x; v[5] += r1.y; v[6] += r1.z; v[7] += r1.w;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) fb[i + j] = v[j];
+        }
+        if (fz.norm_w) {
+          __syncthreads();
+          for (int b = warp; b < K / 128; b += NWP) {
+            const float sq = block128_sumsq(fb + b * 128, lane);
+            if (lane == 0) blk_sum[b] = sq;
+          }
+          __syncthreads();
+          float total = 0.f;
+          for (int b = 0; b < K / 128; ++b) total = __fadd_rn(total, blk_sum[b]);
+          const float r = rsqrtf(total / static_cast<float>(K) + fz.eps);
+          const float add = fz.zero_centered ? 1.f : 0.f;
+          for (int i = tid * 8; i < K; i += THREADS * 8) {
+            const int4 wr = *reinterpret_cast<const int4*>(fz.norm_w + i);
+            const __half* wh = reinterpret_cast<const __half*>(&wr);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              fb[i + j] = round_f16(__fmul_rn(__fmul_rn(fb[i + j], r), __half2float(wh[j]) + add));
+          }
+        } else {
+          for (int i = tid * 8; i < K; i += THREADS * 8)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) fb[i + j] = round_f16(fb[i + j]);
+        }
+      }
+      __syncthreads();
+      if (fz.y_out != nullptr && first_cta) {
+        __half* yr = fz.y_out + static_cast<size_t>(m) * K;
+        for (int i = tid * 8; i < K; i += THREADS * 8) {
+          __align__(16) __half h[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(fb[i + j]);
+          *reinterpret_cast<int4*>(yr + i) = *reinterpret_cast<const int4*>(h);
+        }
+      }
+      float amax = 0.f;
+      if (fz.signs) {
+        for (int b = warp; b < K / 128; b += NWP)
+          amax = fmaxf(amax, hadamard128_inplace(fb + b * 128, fz.signs + b * 128, lane));
+      } else {
+        for (int i = tid; i < K; i += THREADS) amax = fmaxf(amax, fabsf(fb[i]));
+      }
+      amax = block_reduce(amax, red, true);
+      const float scale = a8_scale(amax);
+      int psum = 0;
+      for (int i = tid * 4; i < K; i += THREADS * 4) {
+        char4 c;
+        c.x = static_cast<signed char>(a8_code(fb[i + 0], scale));
+        c.y = static_cast<signed char>(a8_code(fb[i + 1], scale));
+        c.z = static_cast<signed char>(a8_code(fb[i + 2], scale));
+        c.w = static_cast<signed char>(a8_code(fb[i + 3], scale));
+        *reinterpret_cast<char4*>(arow + i) = c;
+        if (fz.q_out != nullptr && first_cta)
+          *reinterpret_cast<char4*>(fz.q_out + static_cast<size_t>(m) * K + i) = c;
+        psum = __dp4a(*reinterpret_cast<const int*>(&c), 0x01010101, psum);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+      if (lane == 0 && psum != 0) atomicAdd(&asum[m], psum);
+      if (tid == 0) {
+        scale_s[m] = scale;
+        if (fz.scale_out != nullptr && first_cta) fz.scale_out[m] = scale;
+      }
+      __syncthreads();
     }
   }
   __syncthreads();
@@ -265,7 +410,7 @@ __global__ void __launch_bounds__(GemvThreads<MT>::value, 1) e8p_gemv_kernel(
         const int m = i / segs, seg = i % segs;
         if (m < M) {
           __align__(16) __half h[8];
-          const float sa = a_scale[m];
+          const float sa = scale_s[m];
           const int bias = BIAS * asum[m];
 #pragma unroll
           for (int r = 0; r < 8; ++r) {
@@ -288,8 +433,16 @@ __global__ void __launch_bounds__(GemvThreads<MT>::value, 1) e8p_gemv_kernel(
         const int m = i / n_count, r = i % n_count;
         if (m < M) {
           const int total = 2 * acc_s[r * MT + m] - BIAS * asum[m];
-          store_row<MT>(out, out_f32, m, n_base + r, N, total, __half2float(w_scale[n_base + r]),
-                        a_scale[m], peer);
+          const float sw = __half2float(w_scale[n_base + r]);
+          if (fz.resid_accum != nullptr) {
+            const __half hv = __float2half_rn((static_cast<float>(total) * sw) * scale_s[m]);
+            float* dst = fz.resid_accum + static_cast<size_t>(m) * N + n_base + r;
+            *dst = *dst + __half2float(hv);
+            if (out != nullptr)
+              reinterpret_cast<__half*>(out)[static_cast<size_t>(m) * N + n_base + r] = hv;
+          } else {
+            store_row<MT>(out, out_f32, m, n_base + r, N, total, sw, scale_s[m], peer);
+          }
         }
       }
     }
@@ -366,11 +519,13 @@ static GemvGrid gemv_grid(int rows_per_group, int N, int K) {
 
 template <int FMT, int MT>
 static int launch_e8p(const int8_t* a, const float* as, const void* w, const __half* ws, void* out,
-                      int M, int N, int K, int out_f32, cudaStream_t stream, const PeerOut& po) {
+                      int M, int N, int K, int out_f32, cudaStream_t stream, const PeerOut& po,
+                      const GemvFuse& fz = GemvFuse{}) {
   constexpr int ROWS = FMT == 1 ? 8 : 16;
   const GemvGrid g = gemv_grid(ROWS, N, K);
-  const size_t smem = sizeof(E8pLut<GEMV_COPIES>) + static_cast<size_t>(MT) * K +
-                      (static_cast<size_t>(g.max_groups) * ROWS * MT + MT) * sizeof(int);
+  size_t smem = sizeof(E8pLut<GEMV_COPIES>) + static_cast<size_t>(MT) * K +
+                (static_cast<size_t>(g.max_groups) * ROWS * MT + 2 * MT) * sizeof(int) + 16;
+  if (fz.pre != 0) smem += static_cast<size_t>(MT) * K * sizeof(float);
   if (smem > 220 * 1024) return -1;
   static const int slot = runtime_new_slot();
   if (runtime_first_use(slot)) {
@@ -380,7 +535,7 @@ static int launch_e8p(const int8_t* a, const float* as, const void* w, const __h
   }
   e8p_gemv_kernel<FMT, MT><<<g.n_parts * g.k_parts, GemvThreads<MT>::value, smem, stream>>>(
       a, as, reinterpret_cast<const uint4*>(w), ws, out, M, N, K, out_f32, runtime_e8p_tables(),
-      po, g.n_parts, g.k_parts, g.max_groups, runtime_gemv_workspace());
+      po, g.n_parts, g.k_parts, g.max_groups, runtime_gemv_workspace(), fz);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -419,4 +574,40 @@ int qgemv_dispatch(int fmt, const int8_t* a, const float* as, const void* w, con
   return -1;
 }
 
+// Projection of at most 8 rows with the row preparation fused in (see GemvFuse); E8P weights.
+int qgemv_fused_dispatch(int fmt, const void* w, const __half* ws, void* out, int M, int N, int K,
+                         cudaStream_t stream, const GemvFuse& fz) {
+  if (M < 1 || M > 8 || K % 128 || fz.pre < 1 || fz.pre > 3 || (fmt != 1 && fmt != 2)) return -1;
+  if (fz.norm_w != nullptr && K / 128 > 128) return -1;
+  const PeerOut po{};
+#define BY_M(F)                                                                                   \
+  (M == 1 ? launch_e8p<F, 1>(nullptr, nullptr, w, ws, out, M, N, K, 0, stream, po, fz)            \
+   : M == 2 ? launch_e8p<F, 2>(nullptr, nullptr, w, ws, out, M, N, K, 0, stream, po, fz)          \
+   : M <= 4 ? launch_e8p<F, 4>(nullptr, nullptr, w, ws, out, M, N, K, 0, stream, po, fz)          \
+            : launch_e8p<F, 8>(nullptr, nullptr, w, ws, out, M, N, K, 0, stream, po, fz))
+  if (fmt == 1) return BY_M(1);
+  return BY_M(2);
+#undef BY_M
+}
+
 }  // namespace orinfer
+
+using namespace orinfer;
+
+// pre: 1 = resid (+ x) -> RMSNorm(norm_w) -> rotate(signs) -> A8; 2 = x -> rotate -> A8;
+// 3 = SwiGLU(x [M, 2K]) -> rotate -> A8.  out: FP16 [M, N] or null; resid_accum: FP32 [M, N]
+// that receives += the FP16-rounded output, or null.  Returns -1 when the shape does not fit
+// the fused kernel (more than 8 rows, W8 weights, too much shared memory): the caller then
+// uses the separate kernels.
+extern "C" int orinfer_qgemv_fused(int fmt, int pre, const __half* x, const float* resid,
+                                   const __half* norm_w, const int8_t* signs, float eps,
+                                   int zero_centered, int8_t* q_out, float* scale_out,
+                                   __half* y_out, const void* w, const __half* w_scale, void* out,
+                                   float* resid_accum, int M, int N, int K, cudaStream_t stream) {
+  if (runtime_ensure_init() != cudaSuccess) return -2;
+  if (pre == 1 && resid == nullptr && x == nullptr) return -1;
+  if ((pre == 2 || pre == 3) && x == nullptr) return -1;
+  const GemvFuse fz{pre, x, resid, norm_w, signs, eps, zero_centered, q_out, scale_out, y_out,
+                    resid_accum};
+  return qgemv_fused_dispatch(fmt, w, w_scale, out, M, N, K, stream, fz);
+}

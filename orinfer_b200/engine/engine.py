@@ -131,6 +131,7 @@ class Engine:
         # device current before anything is launched, and keep a pinned mirror of the status
         # word that every step's token readback refreshes.
         self.failed: Optional[Exception] = None
+        self._step_was_replay = False
         self._status = None
         if self.on_gpu:
             from ..ops import native
@@ -778,6 +779,8 @@ class Engine:
         if pure_decode:
             dt = t2 - t0
             self.tpot_ewma = dt if self.tpot_ewma is None else 0.8 * self.tpot_ewma + 0.2 * dt
+            if not use_graph or self._step_was_replay:     # warm-up / capture steps say nothing
+                self.spec.observe_normal(len(decoders), dt)
         elif chunks:
             toks = sum(n for _, n in chunks)
             rate = toks / max(t2 - t0, 1e-6)
@@ -1039,6 +1042,7 @@ class Engine:
             torch.clamp(g.tokens, min=0, out=g.ids)      # next step's inputs, on the device
             g.pos.add_(g.live)
 
+        self._step_was_replay = g.graph is not None
         if g.graph is None:
             g.trials += 1
             body()                                       # warm

@@ -38,8 +38,13 @@ class Speculator:
         self.lookups: Dict[int, P.PromptLookup] = {}
         self.backlog: Dict[int, list] = {}            # rid -> [(first pos, hidden rows)]
         self.acceptance = P.Acceptance()
-        self.costs: Dict[int, P.Timing] = {}          # verification width -> round cost
-        self.last_used: Dict[int, int] = {}
+        # round cost per (batch bucket, verification width); plain-step cost per batch bucket
+        # (the minimum of the last few: a decode step never gets faster than its kernels, so
+        # outliers are host noise), and the call at which it was last measured
+        self.costs: Dict[tuple, P.Timing] = {}
+        self.last_used: Dict[tuple, int] = {}
+        self.normal: Dict[int, list] = {}
+        self.normal_last: Dict[int, int] = {}
         self.calls = 0
         self.rounds = self.proposed = self.accepted = self.committed = 0
         self.trace = os.environ.get("ORINFER_MTP_TRACE") == "1"
@@ -50,27 +55,46 @@ class Speculator:
         return self.max_drafts > 0 and (self.prompt_lookup or self.engine.runner_has_mtp())
 
     # ------------------------------------------------------------------ width selection
+    @staticmethod
+    def _bucket(batch: int) -> int:
+        b = 1
+        while b < batch:
+            b *= 2
+        return b
+
+    def observe_normal(self, batch: int, seconds: float) -> None:
+        """A plain decode step of ``batch`` requests took ``seconds`` (replayed graph or
+        direct packet, not a warm-up or capture step)."""
+        key = self._bucket(batch)
+        recent = self.normal.setdefault(key, [])
+        recent.append(seconds)
+        del recent[:-8]
+        self.normal_last[key] = self.calls
+
     def choose_width(self, batch: int, remaining: int) -> int:
         """Verification width (rows per speculating request); 1 = plain decode."""
         if self.policy.startswith("fixed"):
             return 1 + min(int(self.policy[5:] or 0), self.max_drafts)
-        normal = self.engine.tpot_ewma
-        if normal is None:
-            return 1
+        key = self._bucket(batch)
+        recent = self.normal.get(key)
+        if not recent or len(recent) < 2:
+            return 1                       # no plain step of this batch size measured yet
+        normal = min(recent)
         cands = []
         for w in WIDTHS:
             if w - 1 > self.max_drafts:
                 break
-            t = self.costs.get(w)
+            t = self.costs.get((key, w))
             exp = self.acceptance.expected(w - 1)
             mean = t.mean if t and t.samples else normal * (1 + 0.05 * (w - 1))
             upper = t.upper if t and t.samples else mean * 1.5
             cands.append(P.Candidate(w, w, exp * batch, w * batch, remaining, mean, upper,
                                      samples=t.samples if t else 0,
-                                     last=self.last_used.get(w)))
+                                     last=self.last_used.get((key, w))))
         cid, exploring, calibrating = P.mtp_select(
             normal, batch, self.engine.sched.target_tpot_ms / 1e3, cands,
-            available_s=normal, calibration_s=4 * normal, calls=self.calls)
+            available_s=normal, calibration_s=4 * normal, calls=self.calls,
+            normal_last=self.normal_last.get(key))
         if self.trace:
             print(f"MTP choose batch={batch} normal={normal:.5f} -> {cid} "
                   f"exploring={exploring} calibrating={calibrating}", flush=True)
@@ -226,8 +250,9 @@ class Speculator:
             self.accepted += sum(c[1] for c in counts)
         self.committed += sum(1 for _ in produced)
         dt = time.monotonic() - t0
-        self.costs.setdefault(width, P.Timing()).observe(dt)
-        self.last_used[width] = self.calls
+        key = (self._bucket(len(decoders)), width)
+        self.costs.setdefault(key, P.Timing()).observe(dt)
+        self.last_used[key] = self.calls
         eng.stats.decode_tokens += len(ids)
         return produced
 

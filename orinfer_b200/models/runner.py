@@ -171,6 +171,16 @@ class ModelRunner:
         self.mtp_kv_index = n
         self._argmax_scratch = None
         self.layer_hooks = {}
+        # Decode steps of at most 8 rows on a dense model with lattice-coded projections run
+        # with the row kernels fused into the projections (four launches fewer per layer).
+        # Runners that reduce across ranks keep the separate kernels.
+        import os
+        e8p = lambda lin: lin is not None and lin.fmt in ("q4", "q2")
+        self._fused_decode = (
+            type(self) is ModelRunner and os.environ.get("ORINFER_FUSED_DECODE", "1") != "0"
+            and self.cfg.arch == "dense" and not self.cfg.experts
+            and all(lw.kind == "attn" and e8p(lw.qkv) and e8p(lw.o) and e8p(lw.gate_up)
+                    and e8p(lw.down) for lw in weights.layers))
 
     # ---------------------------------------------------------------- helpers
     def _signs(self, lin: QLinear):
@@ -183,9 +193,17 @@ class ModelRunner:
     def _attention_block(self, lw: LayerWeights, kv_slot: int, x, p: Packet, rows: int,
                          first: bool):
         cfg, ws = self.cfg, self.ws
-        h = cfg.hidden
         q8, sc = self._prep(x, lw.in_norm, self._signs(lw.qkv), rows)
         qkv = self._linear(lw.qkv, q8, sc, rows, ws.qkv)
+        self._attention_core(lw, kv_slot, qkv, p, rows)
+        qd = cfg.q_heads * cfg.head_dim
+        q8, sc = F.act_prep(ws.attn, None, None, self._signs(lw.o), rows=rows, q_out=ws.q8[qd],
+                            scale_out=ws.scale)
+        return self._row_parallel("o", lw.o, q8, sc, rows)
+
+    def _attention_core(self, lw: LayerWeights, kv_slot: int, qkv, p: Packet, rows: int):
+        """q/k head norm + RoPE + INT8 KV write, then attention into ``ws.attn``."""
+        cfg, ws = self.cfg, self.ws
         F.qk_rope_kv(qkv, lw.q_norm if cfg.qk_norm else None, lw.k_norm if cfg.qk_norm else None,
                      ws.cos, ws.sin, p.row_req, p.row_pos, p.page_table, self.kv.k[kv_slot],
                      self.kv.v[kv_slot], self.kv.ks[kv_slot], self.kv.vs[kv_slot],
@@ -211,10 +229,33 @@ class ModelRunner:
             F.attention(ws.q, gate, p.row_req, see, p.page_table, self.kv.k[kv_slot],
                         self.kv.v[kv_slot], self.kv.ks[kv_slot], self.kv.vs[kv_slot],
                         splits=splits, scratch=scratch, out=ws.attn, rows=row_rows)
+
+    def _fused_layer(self, lw: LayerWeights, kv_slot: int, p: Packet, rows: int) -> bool:
+        """One dense decoder layer of a decode-sized packet with the row kernels fused into
+        the projections.  The residual stream (``ws.resid``) already holds every earlier
+        branch output: each prologue only reads it and the o / down projections add their
+        FP16-rounded results into it.  False when a shape does not fit the fused kernel."""
+        cfg, ws = self.cfg, self.ws
+        h, eps, zc = cfg.hidden, cfg.eps, cfg.zero_centered_norm
+        fuse = F.qgemv_fused
+        if not fuse(F.PRE_NORM, None, ws.resid, lw.in_norm, lw.qkv.signs, lw.qkv.codes,
+                    lw.qkv.scale, lw.qkv.fmt, lw.qkv.n, h, rows, eps=eps, zero_centered=zc,
+                    out=ws.qkv):
+            return False
+        self._attention_core(lw, kv_slot, ws.qkv, p, rows)
         qd = cfg.q_heads * cfg.head_dim
-        q8, sc = F.act_prep(ws.attn, None, None, self._signs(lw.o), rows=rows, q_out=ws.q8[qd],
-                            scale_out=ws.scale)
-        return self._row_parallel("o", lw.o, q8, sc, rows)
+        f = lw.gate_up.n // 2
+        gu = ws.gate_up.view(-1)[: ws.max_rows * 2 * f].view(ws.max_rows, 2 * f)
+        ok = fuse(F.PRE_PLAIN, ws.attn, None, None, lw.o.signs, lw.o.codes, lw.o.scale, lw.o.fmt,
+                  h, qd, rows, resid_accum=ws.resid)
+        ok = ok and fuse(F.PRE_NORM, None, ws.resid, lw.post_norm, lw.gate_up.signs,
+                         lw.gate_up.codes, lw.gate_up.scale, lw.gate_up.fmt, 2 * f, h, rows,
+                         eps=eps, zero_centered=zc, out=gu)
+        ok = ok and fuse(F.PRE_SWIGLU, gu, None, None, lw.down.signs, lw.down.codes,
+                         lw.down.scale, lw.down.fmt, h, f, rows, resid_accum=ws.resid)
+        if not ok:
+            raise RuntimeError("a projection of this model does not fit the fused decode kernel")
+        return True
 
     def _gdn_state(self, slots: int):
         """Recurrent pools, one entry per page-table row: FP32 state [slots, HV, D, D] and the
@@ -351,6 +392,14 @@ class ModelRunner:
         ws.resid[:rows].zero_()
         self._rope(p, rows)
         hook, self.stage_hook = getattr(self, "stage_hook", None), None
+        if (self._fused_decode and rows <= 8 and hook is None and p.attend_pos is None
+                and not self.layer_hooks):
+            ws.resid[:rows].copy_(x[:rows])             # the stream starts as the embedding
+            if self._fused_layer(self.w.layers[0], self._attn_index[0], p, rows):
+                for i, lw in enumerate(self.w.layers[1:], 1):
+                    self._fused_layer(lw, self._attn_index[i], p, rows)
+                return None                             # everything is in ws.resid
+            ws.resid[:rows].zero_()                     # shapes do not fit: separate kernels
         pauses = set()
         if hook is not None:
             n = len(self.w.layers)

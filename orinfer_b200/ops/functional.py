@@ -138,6 +138,35 @@ def qgemm(a: torch.Tensor, a_scale: torch.Tensor, codes: torch.Tensor, w_scale: 
     return out
 
 
+PRE_NORM, PRE_PLAIN, PRE_SWIGLU = 1, 2, 3
+
+
+def qgemv_fused(pre: int, x: Optional[torch.Tensor], resid: Optional[torch.Tensor],
+                norm_w: Optional[torch.Tensor], signs: Optional[torch.Tensor], codes: torch.Tensor,
+                w_scale: torch.Tensor, fmt: str, n: int, k: int, rows: int, *, eps: float = 1e-6,
+                zero_centered: bool = False, out: Optional[torch.Tensor] = None,
+                resid_accum: Optional[torch.Tensor] = None, y_out: Optional[torch.Tensor] = None,
+                q_out: Optional[torch.Tensor] = None,
+                scale_out: Optional[torch.Tensor] = None) -> bool:
+    """Projection of at most 8 rows with the row preparation fused into the kernel
+    (``pre``: PRE_NORM = resid (+ x) -> RMSNorm -> rotation -> A8; PRE_PLAIN = x -> rotation ->
+    A8; PRE_SWIGLU = SwiGLU(x [rows, 2k]) -> rotation -> A8) and, with ``resid_accum``, the
+    FP16-rounded result added into an FP32 matrix.  Same bits as ``act_prep`` followed by
+    ``qgemm``.  Returns False when the shape does not fit (the caller then runs the separate
+    kernels); E8P weights only."""
+    if rows > 8 or fmt not in ("q4", "q2"):
+        return False
+    code = native.lib().orinfer_qgemv_fused(
+        FMT[fmt], pre, ptr(x), ptr(resid), ptr(norm_w), ptr(signs), float(eps),
+        int(zero_centered), ptr(q_out), ptr(scale_out), ptr(y_out), ptr(codes), ptr(w_scale),
+        ptr(out), ptr(resid_accum), rows, n, k, stream())
+    if code == -1:
+        return False
+    check(code, "qgemv_fused")
+    count_launches(1)
+    return True
+
+
 def attention_splits(max_kv_len: int, rows: int, kvh: int) -> int:
     """Split the key axis when there are too few (row, kv head) CTAs to fill 148 SMs: about
     three CTAs per SM, at least 64 keys per split."""

@@ -43,6 +43,7 @@ def _load() -> ctypes.CDLL:
         "orinfer_set_wait_limit_us": ([c_longlong], I),
         "orinfer_current_device": ([], I),
         "orinfer_qgemm_set_impl": ([I], I),
+        "orinfer_qgemv_fused": ([I, I, P, P, P, P, c_float, I, P, P, P, P, P, P, P, I, I, I, P], I),
         "orinfer_e8p_basis_host": ([P], I),
         "orinfer_embed_w8": ([P, P, P, P, I, I, I, P], I),
         "orinfer_act_prep": ([P, P, P, P, P, P, P, I, I, c_float, I, I, P], I),

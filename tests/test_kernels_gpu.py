@@ -168,6 +168,44 @@ def test_qgemm_cta_pair_form(cuda, fmt, m, n, k):
     assert torch.equal(out32, R.qgemm(a, sa, w_int, ws, out_f32=True))
 
 
+@pytest.mark.parametrize("fmt", ["q4", "q2"])
+@pytest.mark.parametrize("m,n,k", [(1, 2560, 2560), (1, 19456, 2560), (3, 6144, 2560),
+                                   (8, 2560, 1024), (1, 2560, 9728), (5, 320, 1280)])
+def test_qgemv_fused_equals_separate_kernels(cuda, fmt, m, n, k):
+    """The projection with the row preparation fused in gives the bits of act_prep + qgemm,
+    for the norm, plain and SwiGLU prologues and for the residual-accumulating epilogue."""
+    from orinfer_b200.ops import functional as F
+    g = torch.Generator().manual_seed(m + n + k)
+    codes, ws, _ = _rand_weight(fmt, n, k, cuda, seed=n + k)
+    sg = _signs(k, cuda)
+    norm_w = (1 + 0.1 * torch.randn(k, generator=g)).half().to(cuda)
+    x = (torch.randn(8, k, generator=g) * 0.5).half().to(cuda)
+    resid = torch.randn(8, k, generator=g).to(cuda)
+    gu = torch.randn(8, 2 * k, generator=g).half().to(cuda)
+    for pre in (F.PRE_NORM, F.PRE_PLAIN, F.PRE_SWIGLU):
+        if pre == F.PRE_NORM:
+            r2 = resid.clone()
+            q8, sc = F.act_prep(x, r2, norm_w, sg, eps=1e-6, rows=m)
+            args = (x, resid, norm_w)
+        elif pre == F.PRE_PLAIN:
+            q8, sc = F.act_prep(x, None, None, sg, rows=m)
+            args = (x, None, None)
+        else:
+            q8, sc = F.act_prep(gu, None, None, sg, swiglu=True, rows=m)
+            args = (gu, None, None)
+        want = F.qgemm(q8, sc, codes, ws, fmt, n, rows=m)
+        out = torch.zeros(8, n, dtype=torch.float16, device=cuda)
+        acc = torch.ones(8, n, device=cuda)
+        qo = torch.zeros(8, k, dtype=torch.int8, device=cuda)
+        so = torch.zeros(8, device=cuda)
+        assert F.qgemv_fused(pre, args[0], args[1], args[2], sg, codes, ws, fmt, n, k, m,
+                             out=out, resid_accum=acc, q_out=qo, scale_out=so)
+        torch.cuda.synchronize()
+        assert torch.equal(qo[:m], q8[:m]) and torch.equal(so[:m], sc[:m]), pre
+        assert torch.equal(out[:m], want[:m]), (pre, float((out[:m].float() - want[:m].float()).abs().max()))
+        assert torch.equal(acc[:m], 1 + want[:m].float())
+
+
 def test_qgemm_graph_replay_changed_inputs(cuda):
     """Capture once, replay with different activation contents."""
     from orinfer_b200.ops import functional as F
