@@ -66,6 +66,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_rows_kernel(
   __shared__ float s_red[ATTN_WARPS][RPC];
   __shared__ float s_m[RPC], s_l[RPC], s_corr[RPC];
   __shared__ float s_o[ATTN_WARPS][RPC][D];
+  __shared__ int s_page[ATTN_CHUNK / 128 + 2];  // page ids covering the chunk
   for (int i = tid; i < RPC * D; i += THREADS)
     s_q[i / D][i % D] =
         __half2float(q[(static_cast<size_t>(row) * qh + head0 + i / D) * D + i % D]) * qscale;
@@ -83,24 +84,37 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_rows_kernel(
 
   for (int c0 = k_lo; c0 < k_hi; c0 += ATTN_CHUNK) {
     const int n = min(ATTN_CHUNK, k_hi - c0);
-    // ---- pass 1: scores of the chunk (loop uniform over the warp: the shuffles need every lane)
+    const int page0 = c0 >> 7;
+    if (tid <= ((c0 + n - 1) >> 7) - page0) s_page[tid] = pages[page0 + tid];
+    __syncthreads();
+    // slot of chunk key kk in the paged cache (page ids come from shared memory, so a key's
+    // address does not wait for a global load)
+    auto slot_of = [&](int kk) {
+      const int key = c0 + kk;
+      return (static_cast<size_t>(s_page[(key >> 7) - page0]) * 128 + (key & 127)) * kvh + h;
+    };
+    // ---- pass 1: scores of the chunk (loop uniform over the warp: the shuffles need every
+    // lane); the loads of the next step are issued before this step's arithmetic
     float lmax[RPC];
 #pragma unroll
     for (int r = 0; r < RPC; ++r) lmax[r] = -INFINITY;
+    int4 raw = make_int4(0, 0, 0, 0);
+    float sc_next = 0.f;
+    if (warp * KPW + kslot < n) {
+      const size_t slot = slot_of(warp * KPW + kslot);
+      raw = __ldg(reinterpret_cast<const int4*>(kc + slot * D + sub * 16));
+      sc_next = __half2float(ks[slot * GROUPS + group]);
+    }
     for (int base = warp * KPW; base < n; base += KPI) {
       const int kk = base + kslot;
       const bool valid = kk < n;
       float kf[16];
-      float ksc = 0.f;
-      if (valid) {
-        const int key = c0 + kk;
-        const int page = pages[key >> 7];
-        const size_t slot = (static_cast<size_t>(page) * 128 + (key & 127)) * kvh + h;
-        unpack16(__ldg(reinterpret_cast<const int4*>(kc + slot * D + sub * 16)), kf);
-        ksc = __half2float(ks[slot * GROUPS + group]);
-      } else {
-#pragma unroll
-        for (int e = 0; e < 16; ++e) kf[e] = 0.f;
+      unpack16(raw, kf);
+      const float ksc = valid ? sc_next : 0.f;
+      if (kk + KPI < n) {
+        const size_t slot = slot_of(kk + KPI);
+        raw = __ldg(reinterpret_cast<const int4*>(kc + slot * D + sub * 16));
+        sc_next = __half2float(ks[slot * GROUPS + group]);
       }
 #pragma unroll
       for (int r = 0; r < RPC; ++r) {
@@ -168,16 +182,23 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_rows_kernel(
         for (int e = 0; e < 16; ++e) acc[r][e] *= c;
       }
     }
-    // ---- pass 2: weight x V
+    // ---- pass 2: weight x V (same one-step-ahead loads)
+    if (warp * KPW + kslot < n) {
+      const size_t slot = slot_of(warp * KPW + kslot);
+      raw = __ldg(reinterpret_cast<const int4*>(vc + slot * D + sub * 16));
+      sc_next = __half2float(vs[slot * GROUPS + group]);
+    }
     for (int base = warp * KPW; base < n; base += KPI) {
       const int kk = base + kslot;
       if (kk < n) {
-        const int key = c0 + kk;
-        const int page = pages[key >> 7];
-        const size_t slot = (static_cast<size_t>(page) * 128 + (key & 127)) * kvh + h;
         float vf[16];
-        unpack16(__ldg(reinterpret_cast<const int4*>(vc + slot * D + sub * 16)), vf);
-        const float vsc = __half2float(vs[slot * GROUPS + group]);
+        unpack16(raw, vf);
+        const float vsc = sc_next;
+        if (kk + KPI < n) {
+          const size_t slot = slot_of(kk + KPI);
+          raw = __ldg(reinterpret_cast<const int4*>(vc + slot * D + sub * 16));
+          sc_next = __half2float(vs[slot * GROUPS + group]);
+        }
 #pragma unroll
         for (int r = 0; r < RPC; ++r) {
           const float pv = s_p[r][kk] * vsc;

@@ -3,11 +3,12 @@
 // One CTA computes a (MT*128) x NB output tile: MT = 1, 2 or 4 accumulators in TMEM share
 // every decoded weight tile (the lattice decode, not the MMA, is the scarce resource, so a
 // weight tile should be decoded once and multiplied against as many rows as the packet has),
-// and NB = 128, 64 or 32 weight rows per CTA spreads narrow projections over the 148 SMs.  Warp 0 streams operand tiles with TMA (activations
-// always; INT8 weights for W8; the packed E8P codes as one contiguous bulk copy per
-// k-block for Q4/Q2).  Warps 2-17 expand the lattice codes into an INT8 weight tile in the
-// 128-byte-swizzled K-major layout the tensor core reads, warp 1 issues tcgen05.mma
-// kind::i8 into TMEM, and warps 2-17 finally read TMEM back, apply the two scales and
+// and NB = 128, 64 or 32 weight rows per CTA spreads narrow projections over the 148 SMs.
+// Warp 0 streams the activation tiles with TMA and warp 2 the weight side (INT8 weights by
+// TMA for W8; the packed E8P codes as one contiguous bulk copy per k-block for Q4/Q2).
+// Warps 3-18 expand the lattice codes into an INT8 weight tile in the 128-byte-swizzled
+// K-major layout the tensor core reads, warp 1 issues tcgen05.mma kind::i8 into TMEM, and
+// warps 3-18 finally read TMEM back, apply the two scales and
 // store FP16/FP32.  INT4 tensor-core MMA (the reference's fastest path,
 // kernels/cuda/model/e8p_core.py:15-33) does not exist on tcgen05, so both E8P formats go
 // through INT8 operands.  Replaces e8p_q4.projection (kernels/cuda/model/e8p_q4.py:144-265),
@@ -30,13 +31,17 @@ namespace tc {
 
 constexpr int BM = 128, BK = 128;
 constexpr int TILE_BYTES = 128 * 128;        // one INT8 activation tile (128 rows x 128 k)
-constexpr int PRODUCERS = 512;               // warps 2..17
+constexpr int PRODUCERS = 512;               // warps 3..18
 constexpr int PWARPS = PRODUCERS / 32;
 constexpr int NUM_SMS = 148;
 // 0: persistent kernel; 1: one tile per CTA (default: the fastest measured so far); 2: CTA
 // pairs (cta_group::2) where the shape allows, else persistent.  All give the same bits.
 static int g_impl = 1;
-constexpr int THREADS = 64 + PRODUCERS;
+// warp 0: activation loader, warp 1: MMA issuer, warp 2: weight loader, warps 3..18: lattice
+// decode and epilogue.  Each role has a warp of its own: two roles that wait on different
+// barriers inside one warp would suspend each other.
+constexpr int ROLE_THREADS = 96;
+constexpr int THREADS = ROLE_THREADS + PRODUCERS;
 
 template <int FMT, int MT, int NB>
 struct Layout {
@@ -139,8 +144,8 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
-  if (FMT != 0 && warp >= 2) {
-    e8p_lut_init(lut, tables, threadIdx.x - 64, PRODUCERS);
+  if (FMT != 0 && warp >= 3) {
+    e8p_lut_init(lut, tables, threadIdx.x - ROLE_THREADS, PRODUCERS);
   }
   tc_fence_before();
   __syncthreads();
@@ -176,7 +181,9 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
       // last copies issued into each stage.
       for (int kb = max(0, issued - SA); kb < issued; ++kb)
         mbar_wait(&a_full[kb % SA], (kb / SA) & 1, status, STATUS_TMA_WAIT, 0x4000 | kb);
-    } else if (lane == 1) {
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {
       // weight loader: INT8 tiles by TMA (W8) or the packed codes as one bulk copy
       int issued = 0;
       uint64_t* landed = FMT == 0 ? b_full : c_full;
@@ -225,7 +232,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
       if (ok && kblocks > 0) tc_commit(tmem_full);
     }
   } else {
-    const int t = threadIdx.x - 64;                     // 0..511
+    const int t = threadIdx.x - ROLE_THREADS;                     // 0..511
     bool ok = true;
     if (FMT != 0) {
       const int chunk = t & 7, rbase = t >> 3;          // 64 weight rows per pass
@@ -267,7 +274,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     if (ok) {
       tc_fence_after();
       const int quad = warp & 3;                          // TMEM lane quadrant of this warp
-      const int part = (warp - 2) >> 2;                   // 0..3: which 32-column chunks
+      const int part = (warp - 3) >> 2;                   // 0..3: which 32-column chunks
       const int row = quad * 32 + lane;
       constexpr int CHUNKS = BN / 32;                     // 32-column chunks per accumulator
 #pragma unroll 1
@@ -333,14 +340,14 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
       }
     }
   }
-  if (warp >= 2 && po.tp > 0 && partial == nullptr) {
+  if (warp >= 3 && po.tp > 0 && partial == nullptr) {
     // fused scatter, step 2: every producer warp joins (also after a failed wait, so that
     // nobody is left at the barrier), then whole 16-byte segments of consecutive columns go
     // out lane by lane: a warp writes two complete 256-byte rows per instruction instead of
     // 32 rows x 16 bytes, which is what keeps NVLink packets full.
     asm volatile("bar.sync 1, %0;" ::"n"(PRODUCERS) : "memory");
     constexpr int SEGS = BN / 8;                          // 16-byte segments per row
-    const int t = threadIdx.x - 64;
+    const int t = threadIdx.x - ROLE_THREADS;
     for (int idx = t; idx < MT * BM * SEGS; idx += PRODUCERS) {
       const int r = idx / SEGS, seg = idx % SEGS;
       const int m = m0 + r, n = n0 + seg * 8;
@@ -500,7 +507,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_ps_kernel(
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
-  if (FMT != 0 && warp >= 2) e8p_lut_init(lut, tables, threadIdx.x - 64, PRODUCERS);
+  if (FMT != 0 && warp >= 3) e8p_lut_init(lut, tables, threadIdx.x - ROLE_THREADS, PRODUCERS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -541,7 +548,9 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_ps_kernel(
       // never leave the CTA with a copy of ours in flight
       for (uint32_t c = ca > NSLOT ? ca - NSLOT : 0; c < ca; ++c)
         mbar_wait(&a_full[c % NSLOT], (c / NSLOT) & 1, status, STATUS_TMA_WAIT, 0x4000);
-    } else if (lane == 1) {
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {
       // ---------------- weight loader: INT8 tiles by TMA (W8) or packed codes as bulk copies
       uint32_t cw = 0;
       int it = 0;
@@ -628,11 +637,11 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_ps_kernel(
     }
   } else {
     // ---------------- producers (lattice decode) and epilogue
-    const int t512 = threadIdx.x - 64;                  // 0..511
+    const int t512 = threadIdx.x - ROLE_THREADS;                  // 0..511
     const int chunk = t512 & 7, rbase = t512 >> 3;      // 64 weight rows per pass
     const int copy = t512 & (L::LUT_COPIES - 1);
     const int quad = warp & 3;                          // TMEM lane quadrant of this warp
-    const int part = (warp - 2) >> 2;                   // 0..3: which 32-column chunks
+    const int part = (warp - 3) >> 2;                   // 0..3: which 32-column chunks
     const int row = quad * 32 + lane;
     bool ok = true;
 
@@ -920,7 +929,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_pair_kernel(
     tmem_alloc2(tmem_slot, TMEM_COLS);
     tmem_relinquish2();
   }
-  if (FMT != 0 && warp >= 2) e8p_lut_init(lut, tables, threadIdx.x - 64, PRODUCERS);
+  if (FMT != 0 && warp >= 3) e8p_lut_init(lut, tables, threadIdx.x - ROLE_THREADS, PRODUCERS);
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();                          // the peer's barriers exist before anyone signals
@@ -963,7 +972,9 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_pair_kernel(
       if (leader)
         for (uint32_t c = ca > NSLOT ? ca - NSLOT : 0; c < ca; ++c)
           mbar_wait(&a_full[c % NSLOT], (c / NSLOT) & 1, status, STATUS_TMA_WAIT, 0x4000);
-    } else if (lane == 1) {
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {
       // ---------------- weight loader (both CTAs): its 128 weight rows
       uint32_t cw = 0;
       int it = 0;
@@ -1054,11 +1065,11 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_pair_kernel(
     }
   } else {
     // ---------------- producers (lattice decode of this CTA's weight rows) and epilogue
-    const int t512 = threadIdx.x - 64;
+    const int t512 = threadIdx.x - ROLE_THREADS;
     const int chunk = t512 & 7, rbase = t512 >> 3;
     const int copy = t512 & (L::LUT_COPIES - 1);
     const int quad = warp & 3;
-    const int part = (warp - 2) >> 2;
+    const int part = (warp - 3) >> 2;
     const int row = quad * 32 + lane;
     bool ok = true;
 

@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(GemvThreads<MT>::value, 1) e8p_gemv_kernel(
   int* acc_s = reinterpret_cast<int*>(act + static_cast<size_t>(MT) * K);   // [groups][ROWS][MT]
   int* asum = acc_s + max_groups * ROWS * MT;                                // [MT]
   float* scale_s = reinterpret_cast<float*>(asum + MT);                      // [MT]
-  float* fbuf = reinterpret_cast<float*>(                                    // [MT][K], pre only
+  float* fbuf = reinterpret_cast<float*>(                                    // [K], pre only
       (reinterpret_cast<uintptr_t>(scale_s + MT) + 15) & ~static_cast<uintptr_t>(15));
   __shared__ int last_flag;
   __shared__ float red[32];
@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(GemvThreads<MT>::value, 1) e8p_gemv_kernel(
           *reinterpret_cast<int4*>(arow + i) = make_int4(0, 0, 0, 0);
         continue;
       }
-      float* fb = fbuf + static_cast<size_t>(m) * K;
+      float* fb = fbuf;                          // one row at a time
       if (fz.pre == 3) {
         const __half* g = fz.x + static_cast<size_t>(m) * 2 * K;
         const __half* u = g + K;
@@ -525,7 +525,7 @@ static int launch_e8p(const int8_t* a, const float* as, const void* w, const __h
   const GemvGrid g = gemv_grid(ROWS, N, K);
   size_t smem = sizeof(E8pLut<GEMV_COPIES>) + static_cast<size_t>(MT) * K +
                 (static_cast<size_t>(g.max_groups) * ROWS * MT + 2 * MT) * sizeof(int) + 16;
-  if (fz.pre != 0) smem += static_cast<size_t>(MT) * K * sizeof(float);
+  if (fz.pre != 0) smem += static_cast<size_t>(K) * sizeof(float);
   if (smem > 220 * 1024) return -1;
   static const int slot = runtime_new_slot();
   if (runtime_first_use(slot)) {

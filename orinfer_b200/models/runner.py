@@ -257,6 +257,14 @@ class ModelRunner:
             raise RuntimeError("a projection of this model does not fit the fused decode kernel")
         return True
 
+    def _fused_fits(self, rows: int) -> bool:
+        """Shared memory of the fused projection kernel: decode tables, the INT8 rows, one
+        FP32 row and the partial sums must fit one CTA for the widest input of a layer."""
+        cfg = self.cfg
+        mt = 1 if rows == 1 else (2 if rows == 2 else (4 if rows <= 4 else 8))
+        k = max(cfg.hidden, cfg.q_heads * cfg.head_dim, cfg.ffn)
+        return 65536 + mt * k + 4 * k + 8192 <= 220 * 1024
+
     def _gdn_state(self, slots: int):
         """Recurrent pools, one entry per page-table row: FP32 state [slots, HV, D, D] and the
         FP16 three-row convolution history [slots, 3, conv_dim] of every GDN layer."""
@@ -393,7 +401,7 @@ class ModelRunner:
         self._rope(p, rows)
         hook, self.stage_hook = getattr(self, "stage_hook", None), None
         if (self._fused_decode and rows <= 8 and hook is None and p.attend_pos is None
-                and not self.layer_hooks):
+                and not self.layer_hooks and self._fused_fits(rows)):
             ws.resid[:rows].copy_(x[:rows])             # the stream starts as the embedding
             if self._fused_layer(self.w.layers[0], self._attn_index[0], p, rows):
                 for i, lw in enumerate(self.w.layers[1:], 1):
