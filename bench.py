@@ -186,6 +186,9 @@ def main() -> int:
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--model", default=MODEL, choices=sorted(BASELINE_PREFILL_512))
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary metrics")
+    ap.add_argument("--profile-step", choices=["prefill", "decode"], default=None,
+                    help="run warm-up, then exactly one step between cudaProfilerStart/Stop "
+                         "and leave (for `ncu --profile-from-start off`); prints no result")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -329,6 +332,27 @@ def main() -> int:
                 "resident_steps": engine.stats.resident_steps}
         return produced / dt, dt / max(steps, 1) * 1e3, info
 
+    if args.profile_step:
+        if args.profile_step == "prefill":
+            prompts = [torch.randint(0, cfg.vocab, (PROMPT,), generator=gen,
+                                     dtype=torch.int32).to(dev) for _ in range(5)]
+            for p in prompts[:4]:
+                engine.prefill_device(p)
+            step = lambda: engine.prefill_device(prompts[4])
+        else:
+            req = engine.submit(torch.randint(0, cfg.vocab, (PROMPT,), generator=gen).tolist(),
+                                64, ignore_eos=True)
+            engine.spec.max_drafts = 0
+            for _ in range(8):
+                engine.step()
+            step = engine.step
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        step()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        engine.close()
+        return 0
     sampler = ClockSampler(local) if rank == 0 else None
     ms_dev, launches, rep_ms = device_prefill(PROMPT, args.steps, args.warmup, args.reps)
     clocks = sampler.stop() if sampler else {}

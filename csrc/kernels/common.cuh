@@ -456,10 +456,9 @@ __device__ __forceinline__ float block_reduce(float v, float* red, bool is_max) 
 // Signed block-128 Hadamard rotation of one block held as floats, in place: lane l holds
 // channels 4l..4l+3.  Returns the largest magnitude of the lane's four results.  Shared by
 // every kernel that rotates activations, so the bits do not depend on the kernel.
-__device__ __forceinline__ float hadamard128_inplace(float* block, const int8_t* signs, int lane) {
-  float* p = block + lane * 4;
-  const char4 sg = *reinterpret_cast<const char4*>(signs + lane * 4);
-  float v0 = p[0] * sg.x, v1 = p[1] * sg.y, v2 = p[2] * sg.z, v3 = p[3] * sg.w;
+__device__ __forceinline__ float hadamard128_regs(float& v0, float& v1, float& v2, float& v3,
+                                                  char4 sg, int lane) {
+  v0 *= sg.x; v1 *= sg.y; v2 *= sg.z; v3 *= sg.w;
   float t0 = v0 + v1, t1 = v0 - v1, t2 = v2 + v3, t3 = v2 - v3;      // h = 1
   v0 = t0 + t2; v2 = t0 - t2; v1 = t1 + t3; v3 = t1 - t3;            // h = 2
 #pragma unroll
@@ -476,8 +475,24 @@ __device__ __forceinline__ float hadamard128_inplace(float* block, const int8_t*
   }
   const float c = 0.08838834764831845f;                                // 128^-1/2
   v0 *= c; v1 *= c; v2 *= c; v3 *= c;
-  p[0] = v0; p[1] = v1; p[2] = v2; p[3] = v3;
   return fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
+}
+__device__ __forceinline__ float hadamard128_inplace(float* block, const int8_t* signs, int lane) {
+  float* p = block + lane * 4;
+  const char4 sg = *reinterpret_cast<const char4*>(signs + lane * 4);
+  float v0 = p[0], v1 = p[1], v2 = p[2], v3 = p[3];
+  const float amax = hadamard128_regs(v0, v1, v2, v3, sg, lane);
+  p[0] = v0; p[1] = v1; p[2] = v2; p[3] = v3;
+  return amax;
+}
+
+// Sum of squares of the lane's four values of a block (same order as block128_sumsq).
+__device__ __forceinline__ float block128_sumsq_regs(float v0, float v1, float v2, float v3) {
+  float s = __fmul_rn(v0, v0);
+  s = __fmaf_rn(v1, v1, s);
+  s = __fmaf_rn(v2, v2, s);
+  s = __fmaf_rn(v3, v3, s);
+  return warp_sum(s);
 }
 
 // Sum of squares of one 128-channel block held as floats: lane l covers channels 4l..4l+3

@@ -37,6 +37,7 @@ constexpr int NUM_SMS = 148;
 // 0: persistent kernel; 1: one tile per CTA (default: the fastest measured so far); 2: CTA
 // pairs (cta_group::2) where the shape allows, else persistent.  All give the same bits.
 static int g_impl = 1;
+static int g_probe = 0;      // timing experiments of the one-tile kernel (see its `probe`)
 // warp 0: activation loader, warp 1: MMA issuer, warp 2: weight loader, warps 3..18: lattice
 // decode and epilogue.  Each role has a warp of its own: two roles that wait on different
 // barriers inside one warp would suspend each other.
@@ -85,7 +86,9 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     const unsigned char* __restrict__ w, const float* __restrict__ a_scale,
     const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K,
     const E8pTables* __restrict__ tables, int* status, PeerOut po, GroupDesc grp, AgIn ag,
-    int* __restrict__ partial, int n_begin, int n_end) {
+    int* __restrict__ partial, int n_begin, int n_end, int probe) {
+  // probe (timing experiments only; results are then meaningless): bit 0 = issue no MMAs,
+  // bit 1 = copy no operands (the loaders only signal), bit 2 = decode nothing
   using L = Layout<FMT, MT, NB>;
   constexpr int SA = L::SA, SB = L::SB;
   constexpr int BN = NB;
@@ -170,11 +173,15 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
       for (int kb = 0; a_ready && kb < kblocks; ++kb) {
         const int s = kb % SA;
         if (!mbar_wait(&a_empty[s], ((kb / SA) & 1) ^ 1, status, STATUS_TMA_WAIT, kb)) break;
-        mbar_expect_tx(&a_full[s], MT * TILE_BYTES);
+        if (probe & 2) {
+          mbar_arrive(&a_full[s]);
+        } else {
+          mbar_expect_tx(&a_full[s], MT * TILE_BYTES);
 #pragma unroll
-        for (int t = 0; t < MT; ++t)
-          tma_load_2d(a_s + (s * MT + t) * TILE_BYTES, &tmap_a, &a_full[s], (kb0 + kb) * BK,
-                      m0 + t * BM);
+          for (int t = 0; t < MT; ++t)
+            tma_load_2d(a_s + (s * MT + t) * TILE_BYTES, &tmap_a, &a_full[s], (kb0 + kb) * BK,
+                        m0 + t * BM);
+        }
         issued = kb + 1;
       }
       // Never leave the CTA with a copy of ours in flight: wait (bounded) for the
@@ -191,7 +198,9 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
         const int s = kb % SB;
         if (!mbar_wait(&b_empty[s], ((kb / SB) & 1) ^ 1, status, STATUS_TMA_WAIT, 0x1000 | kb))
           break;
-        if (FMT == 0) {
+        if (probe & 2) {
+          mbar_arrive(FMT == 0 ? &b_full[s] : &c_full[s]);
+        } else if (FMT == 0) {
           mbar_expect_tx(&b_full[s], L::B_BYTES);
           tma_load_2d(b_s + s * L::B_BYTES, &tmap_b, &b_full[s], (kb0 + kb) * BK, b_row0);
         } else {
@@ -218,6 +227,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
         const uint32_t b_addr = smem_u32(b_s + sb * L::B_BYTES);
 #pragma unroll
         for (int j = 0; j < BK / 32; ++j) {
+          if (probe & 1) break;
           const uint64_t bdesc = umma_desc(b_addr + j * 32, 16, 1024);
 #pragma unroll
           for (int t = 0; t < MT; ++t) {
@@ -248,7 +258,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
 #pragma unroll
         for (int i = 0; i < (BN + 63) / 64; ++i) {
           const int row = rbase + 64 * i;
-          if (BN < 64 && row >= BN) break;
+          if ((BN < 64 && row >= BN) || (probe & 4)) break;
           uint4 v = make_uint4(0, 0, 0, 0);
           if (row < rows_valid) {
             if (FMT == 1) {
@@ -315,9 +325,11 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
               for (int j = 0; j < 8; ++j)
                 v[j] = (static_cast<float>(static_cast<int>(r[g * 8 + j])) *
                         __half2float(w_scale[n + j])) * sa;
-              if (po.tp > 0) {
-                // fused scatter, step 1: the FP16 partial tile is staged in the (now idle)
-                // operand rings so that it can leave for the peers in whole rows
+              if (po.tp > 0 || !OUT_F32) {
+                // step 1: the FP16 tile is staged in the (now idle) operand rings so that it
+                // leaves in whole rows: a warp storing 32 rows x 16 bytes straight from its
+                // registers touches 32 lines per instruction, which made the epilogue cost
+                // more than the main loop; peers get their partial tile the same way
                 __align__(16) __half h[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
@@ -340,11 +352,11 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
       }
     }
   }
-  if (warp >= 3 && po.tp > 0 && partial == nullptr) {
-    // fused scatter, step 2: every producer warp joins (also after a failed wait, so that
-    // nobody is left at the barrier), then whole 16-byte segments of consecutive columns go
-    // out lane by lane: a warp writes two complete 256-byte rows per instruction instead of
-    // 32 rows x 16 bytes, which is what keeps NVLink packets full.
+  if (warp >= 3 && (po.tp > 0 || !OUT_F32) && partial == nullptr) {
+    // step 2: every producer warp joins (also after a failed wait, so that nobody is left at
+    // the barrier), then whole 16-byte segments of consecutive columns go out lane by lane:
+    // a warp writes two complete 256-byte rows per instruction instead of 32 rows x 16
+    // bytes, which keeps memory transactions (and NVLink packets) full.
     asm volatile("bar.sync 1, %0;" ::"n"(PRODUCERS) : "memory");
     constexpr int SEGS = BN / 8;                          // 16-byte segments per row
     const int t = threadIdx.x - ROLE_THREADS;
@@ -354,6 +366,11 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
       if (m < m_limit && n + 8 <= n_end) {
         const int4 val = *reinterpret_cast<const int4*>(smem + static_cast<size_t>(r) * STAGE_ROW +
                                                         seg * 16);
+        if (po.tp == 0) {
+          *reinterpret_cast<int4*>(reinterpret_cast<__half*>(out) + static_cast<size_t>(m) * N +
+                                   n) = val;
+          continue;
+        }
         const size_t off = (static_cast<size_t>(po.rank) * po.rows_cap + m) * N + n;
         if (po.rows_per > 0) {
           // reduce-scatter: only the owner of row m receives this partial
@@ -1378,7 +1395,7 @@ int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w
   if (splits > 1 && static_cast<size_t>(splits) * M * width * 4 > SPLITK_WORKSPACE_BYTES) return -1;
   qgemm_tc_kernel<FMT, OUT_F32, MT, NB><<<grid, THREADS, L::TOTAL, stream>>>(
       ta, tb, reinterpret_cast<const unsigned char*>(w), a_scale, w_scale, out, M, N, K,
-      runtime_e8p_tables(), runtime_status_ptr(), po, grp, ag, partial, n_begin, n_end);
+      runtime_e8p_tables(), runtime_status_ptr(), po, grp, ag, partial, n_begin, n_end, g_probe);
   if (splits > 1) {
     const long long items = static_cast<long long>(M) * (width / 8);
     splitk_finalize_kernel<<<static_cast<unsigned>((items + 255) / 256), 256, 0, stream>>>(
@@ -1610,6 +1627,13 @@ extern "C" int orinfer_qgemm_set_variant(int fmt, int m_lo, int m_hi, int n, int
 extern "C" void orinfer_qgemm_clear_variants() { tc::g_variant_count = 0; }
 
 // 0 = persistent kernel (default), 1 = one tile per CTA; for comparisons and tests.
+// Timing experiments of the one-tile kernel: bit 0 no MMAs, bit 1 no operand copies, bit 2
+// no lattice decode.  Outputs are meaningless while a bit is set.
+extern "C" int orinfer_qgemm_set_probe(int bits) {
+  tc::g_probe = bits & 7;
+  return 0;
+}
+
 extern "C" int orinfer_qgemm_set_impl(int impl) {
   if (impl < 0 || impl > 2) return -1;
   tc::g_impl = impl;

@@ -123,7 +123,9 @@ def main():
     link_bytes = (world - 1) / world * m * h * 3.0
     t_link = link_bytes / (NVLINK_GBS * 1e9)
     bound = max(t_compute, t_link)
-    status = native.read_status()
+    st = torch.tensor([native.read_status()], device=dev)
+    dist.all_reduce(st, op=dist.ReduceOp.MAX)          # any rank's failed wait counts
+    status = int(st[0])
     if rank == 0:
         print(json.dumps({
             "probe": "row-parallel GEMM -> reduce -> norm/quant -> column-parallel GEMM",
@@ -135,7 +137,13 @@ def main():
             "peaks": tag, "int8_peak_assumed": "2 x bf16 cuBLAS burst", "kernel_status": status}))
     dist.barrier()
     torch.cuda.synchronize()
-    os._exit(0)
+    import threading
+    guard = threading.Timer(30.0, lambda: os._exit(0))   # never hang in library teardown
+    guard.daemon = True
+    guard.start()
+    mem.close()
+    dist.destroy_process_group()
+    guard.cancel()
 
 
 if __name__ == "__main__":

@@ -90,12 +90,14 @@ def gemm(args, dev):
     out = torch.empty(m, n, dtype=torch.float16, device=dev)
     path = {"auto": 0, "simt": 1, "tc": 2}[args.path]
     native.qgemm_set_impl(args.impl)
+    if args.probe:
+        native.lib().orinfer_qgemm_set_probe(args.probe)
     t = timed(lambda i: F.qgemm(a, sa, ws[i % copies], sw, args.fmt, n, out=out, path=path),
               args.iters)
     hbm, flops, tag = peaks()
     ops = 2.0 * m * n * k
     byts = wbytes + m * k + m * n * 2
-    print(json.dumps({"kernel": "qgemm", "impl": args.impl, "fmt": args.fmt, "m": m, "n": n, "k": k,
+    print(json.dumps({"kernel": "qgemm", "impl": args.impl, "probe": args.probe, "fmt": args.fmt, "m": m, "n": n, "k": k,
                       "us": t * 1e6,
                       "tops": ops / t / 1e12, "gbs": byts / t / 1e9,
                       "frac_int8_peak": ops / t / (2 * flops), "frac_hbm": byts / t / hbm,
@@ -204,6 +206,9 @@ def main():
     g.add_argument("--path", default="auto", choices=["auto", "simt", "tc"])
     g.add_argument("--rotate", action="store_true")
     g.add_argument("--iters", type=int, default=20)
+    g.add_argument("--probe", type=int, default=0,
+                   help="timing experiment of the one-tile kernel: 1 no MMAs, 2 no operand "
+                        "copies, 4 no decode (bits combine; outputs are then meaningless)")
     g.add_argument("--impl", type=int, default=1, help="0 persistent kernel, 1 one tile per CTA, 2 CTA pairs")
     ad = sub.add_parser("attn-decode")
     ad.add_argument("--rows", type=int, default=1)

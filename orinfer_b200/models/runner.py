@@ -171,8 +171,9 @@ class ModelRunner:
         self.mtp_kv_index = n
         self._argmax_scratch = None
         self.layer_hooks = {}
-        # Decode steps of at most 8 rows on a dense model with lattice-coded projections run
-        # with the row kernels fused into the projections (four launches fewer per layer).
+        # Decode steps of one or two rows on a dense model with lattice-coded projections run
+        # with the row kernels fused into the projections (four launches fewer per layer;
+        # every CTA repeats the row preparation, which stops paying off beyond two rows).
         # Runners that reduce across ranks keep the separate kernels.
         import os
         e8p = lambda lin: lin is not None and lin.fmt in ("q4", "q2")
@@ -400,7 +401,7 @@ class ModelRunner:
         ws.resid[:rows].zero_()
         self._rope(p, rows)
         hook, self.stage_hook = getattr(self, "stage_hook", None), None
-        if (self._fused_decode and rows <= 8 and hook is None and p.attend_pos is None
+        if (self._fused_decode and rows <= 2 and hook is None and p.attend_pos is None
                 and not self.layer_hooks and self._fused_fits(rows)):
             ws.resid[:rows].copy_(x[:rows])             # the stream starts as the embedding
             if self._fused_layer(self.w.layers[0], self._attn_index[0], p, rows):
