@@ -417,6 +417,10 @@ int* runtime_status_ptr();
 // INT32 partial accumulators of split-K GEMMs: [splits][M][N].
 constexpr size_t SPLITK_WORKSPACE_BYTES = 96ull << 20;
 int* runtime_splitk_workspace();
+// One arrival counter per output tile of a split-K GEMM whose last-arriving CTA adds the
+// splits itself; zero between launches (the last arriver clears its counter).
+constexpr int SPLITK_TICKETS = 1 << 14;
+int* runtime_splitk_tickets();
 // Zero-initialised INT32 accumulators [8][GEMV_WS_COLS] + tickets of the K-split GEMV; every
 // launch leaves them zero again.
 constexpr int GEMV_WS_COLS = 1 << 18;

@@ -86,9 +86,10 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     const unsigned char* __restrict__ w, const float* __restrict__ a_scale,
     const __half* __restrict__ w_scale, void* __restrict__ out, int M, int N, int K,
     const E8pTables* __restrict__ tables, int* status, PeerOut po, GroupDesc grp, AgIn ag,
-    int* __restrict__ partial, int n_begin, int n_end, int probe) {
+    int* __restrict__ partial, int* __restrict__ tickets, int n_begin, int n_end, int probe) {
   // probe (timing experiments only; results are then meaningless): bit 0 = issue no MMAs,
-  // bit 1 = copy no operands (the loaders only signal), bit 2 = decode nothing
+  // bit 1 = copy no operands (the loaders only signal), bit 2 = decode nothing, bit 3 = the
+  // epilogue stores nothing to global memory, bit 4 = no epilogue at all, bit 5 = no k-blocks
   using L = Layout<FMT, MT, NB>;
   constexpr int SA = L::SA, SB = L::SB;
   constexpr int BN = NB;
@@ -107,6 +108,8 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   uint64_t* b_empty = c_full + 2 * SB;       // [SB] tensor core done with the weight tile
   uint64_t* tmem_full = c_full + 3 * SB;     // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+  int* ticket_slot = reinterpret_cast<int*>(tmem_slot + 1);
+  bool writes_output = true;                   // false: another split finishes this tile
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = n_begin + blockIdx.x * BN;    // this launch covers columns [n_begin, n_end)
@@ -120,11 +123,13 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     w_scale += static_cast<long long>(expert) * grp.n_per_expert;
     b_row0 = expert * grp.n_per_expert + n0;
   }
-  // split-K: blockIdx.z owns k-blocks [kb0, kb0 + kblocks) and stores raw INT32 accumulators
-  // into partial[z][M][N]; a finalize kernel adds the splits and applies the scales
+  // split-K: blockIdx.z owns k-blocks [kb0, kb0 + kblocks).  Every CTA of a tile stores its raw
+  // INT32 accumulators into partial[z][tile] and takes a ticket; the CTA that arrives last
+  // adds the other splits to its own accumulators and runs the ordinary epilogue, so the
+  // result is bit for bit the unsplit one (integer sums) and no second kernel is needed.
   const int kb_all = K / BK, kb_per = (kb_all + gridDim.z - 1) / gridDim.z;
   const int kb0 = blockIdx.z * kb_per;
-  const int kblocks = max(0, min(kb_all, kb0 + kb_per) - kb0);
+  const int kblocks = (probe & 32) ? 0 : max(0, min(kb_all, kb0 + kb_per) - kb0);
   const int rows_valid = min(BN, n_end - n0);
   constexpr uint32_t TMEM_COLS = MT * BN;
 
@@ -281,12 +286,52 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     }
     if (ok && kblocks > 0) ok = mbar_wait(tmem_full, 0, status, STATUS_EPILOGUE_WAIT, 0);
     ok = __all_sync(0xffffffffu, ok);        // tcgen05.ld needs the whole warp
-    if (ok) {
+    const int quad = warp & 3;                          // TMEM lane quadrant of this warp
+    const int part = (warp - 3) >> 2;                   // 0..3: which 32-column chunks
+    const int row = quad * 32 + lane;
+    constexpr int CHUNKS = BN / 32;                     // 32-column chunks per accumulator
+    constexpr int TILE_INT4 = MT * BM * BN / 4;
+    const size_t tile_id = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
+    const size_t tiles = static_cast<size_t>(gridDim.x) * gridDim.y;
+    if (partial != nullptr) {
+      // Layout inside a tile: [item][group of 4 columns][row] as int4, so a warp instruction
+      // writes (and the last arriver reads back) 512 contiguous bytes.
+      if (ok) {
+        tc_fence_after();
+        int4* mine = reinterpret_cast<int4*>(partial) + (blockIdx.z * tiles + tile_id) * TILE_INT4;
+#pragma unroll 1
+        for (int item = part; item < MT * CHUNKS; item += 4) {
+          const int mt = item / CHUNKS, c0 = (item % CHUNKS) * 32;
+          uint32_t r[32];
+          if (kblocks > 0) {
+            tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + mt * BN + c0, r);
+            tc_wait_ld();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0;         // an empty k range contributes zero
+          }
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            mine[(item * 8 + g) * BM + row] =
+                make_int4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+        }
+      }
+      // every producer warp takes part, also after a failed wait, so that the ticket count
+      // of the tile stays whole and nobody is left at the barrier
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"n"(PRODUCERS) : "memory");
+      if (t == 0) {
+        const int ticket = atomicAdd(tickets + tile_id, 1);
+        if (ticket == static_cast<int>(gridDim.z) - 1) tickets[tile_id] = 0;
+        __threadfence();
+        *ticket_slot = ticket;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(PRODUCERS) : "memory");
+      writes_output = *reinterpret_cast<volatile int*>(ticket_slot) ==
+                      static_cast<int>(gridDim.z) - 1;
+    }
+    if (ok && writes_output && !(probe & 16)) {
       tc_fence_after();
-      const int quad = warp & 3;                          // TMEM lane quadrant of this warp
-      const int part = (warp - 3) >> 2;                   // 0..3: which 32-column chunks
-      const int row = quad * 32 + lane;
-      constexpr int CHUNKS = BN / 32;                     // 32-column chunks per accumulator
 #pragma unroll 1
       for (int item = part; item < MT * CHUNKS; item += 4) {
         const int mt = item / CHUNKS, c0 = (item % CHUNKS) * 32;
@@ -302,18 +347,16 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
           for (int j = 0; j < 32; ++j) r[j] = 0;           // an empty k range contributes zero
         }
         if (partial != nullptr) {
-          if (m < m_limit) {
-            // the workspace is compact over this launch's columns
-            const int width = n_end - n_begin;
-            int* dst = partial + (static_cast<size_t>(blockIdx.z) * M + m) * width +
-                       (n0 - n_begin) + c0;
+          for (int z = 0; z < static_cast<int>(gridDim.z); ++z) {
+            if (z == static_cast<int>(blockIdx.z)) continue;
+            const int4* theirs =
+                reinterpret_cast<const int4*>(partial) + (z * tiles + tile_id) * TILE_INT4;
 #pragma unroll
-            for (int g = 0; g < 8; ++g)
-              if (n0 + c0 + g * 4 + 4 <= n_end)
-                *reinterpret_cast<int4*>(dst + g * 4) =
-                    make_int4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+            for (int g = 0; g < 8; ++g) {
+              const int4 v = __ldcg(theirs + (item * 8 + g) * BM + row);
+              r[g * 4] += v.x; r[g * 4 + 1] += v.y; r[g * 4 + 2] += v.z; r[g * 4 + 3] += v.w;
+            }
           }
-          continue;
         }
         if (m < m_limit) {
 #pragma unroll
@@ -352,7 +395,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
       }
     }
   }
-  if (warp >= 3 && (po.tp > 0 || !OUT_F32) && partial == nullptr) {
+  if (warp >= 3 && (po.tp > 0 || !OUT_F32) && writes_output) {
     // step 2: every producer warp joins (also after a failed wait, so that nobody is left at
     // the barrier), then whole 16-byte segments of consecutive columns go out lane by lane:
     // a warp writes two complete 256-byte rows per instruction instead of 32 rows x 16
@@ -363,7 +406,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     for (int idx = t; idx < MT * BM * SEGS; idx += PRODUCERS) {
       const int r = idx / SEGS, seg = idx % SEGS;
       const int m = m0 + r, n = n0 + seg * 8;
-      if (m < m_limit && n + 8 <= n_end) {
+      if (m < m_limit && n + 8 <= n_end && !(probe & 24)) {
         const int4 val = *reinterpret_cast<const int4*>(smem + static_cast<size_t>(r) * STAGE_ROW +
                                                         seg * 16);
         if (po.tp == 0) {
@@ -384,7 +427,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
-  if (po.tp > 0 && partial == nullptr) peer_signal_done(po, gridDim.x * gridDim.y);
+  if (po.tp > 0) peer_signal_done(po, gridDim.x * gridDim.y * gridDim.z);
 }
 
 // ---------------------------------------------------------------- persistent form
@@ -1392,16 +1435,14 @@ int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w
   if (width <= 0) return 0;
   dim3 grid((width + NB - 1) / NB, grp.tiles ? max_tiles : (M + BM * MT - 1) / (BM * MT), splits);
   int* partial = splits > 1 ? runtime_splitk_workspace() : nullptr;
-  if (splits > 1 && static_cast<size_t>(splits) * M * width * 4 > SPLITK_WORKSPACE_BYTES) return -1;
+  const size_t tiles = static_cast<size_t>(grid.x) * grid.y;
+  if (splits > 1 && (tiles > static_cast<size_t>(SPLITK_TICKETS) ||
+                     tiles * splits * MT * BM * NB * 4 > SPLITK_WORKSPACE_BYTES))
+    return -1;
   qgemm_tc_kernel<FMT, OUT_F32, MT, NB><<<grid, THREADS, L::TOTAL, stream>>>(
       ta, tb, reinterpret_cast<const unsigned char*>(w), a_scale, w_scale, out, M, N, K,
-      runtime_e8p_tables(), runtime_status_ptr(), po, grp, ag, partial, n_begin, n_end, g_probe);
-  if (splits > 1) {
-    const long long items = static_cast<long long>(M) * (width / 8);
-    splitk_finalize_kernel<<<static_cast<unsigned>((items + 255) / 256), 256, 0, stream>>>(
-        partial, splits, a_scale, w_scale, reinterpret_cast<__half*>(out), M, N, po,
-        ag.tp > 0 ? 1 : 0, n_begin, width);
-  }
+      runtime_e8p_tables(), runtime_status_ptr(), po, grp, ag, partial, runtime_splitk_tickets(),
+      n_begin, n_end, g_probe);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -1409,6 +1450,12 @@ int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w
 // then multiplied against up to 512 rows).  Weight rows per CTA: the widest tile that still
 // gives the grid about one CTA per SM, so narrow projections (N = hidden) do not leave most
 // of the machine idle.  FP32 output is only used by the (very wide) vocabulary head.
+// Cells of the split-K workspace one split of an M x N product needs: its tiles are stored
+// whole, so both extents round up to the largest tile.
+inline size_t padded_cells(int M, int N) {
+  return static_cast<size_t>((M + 4 * BM - 1) / (4 * BM)) * (4 * BM) * ((N + 127) / 128) * 128;
+}
+
 inline int plan_splits(int M, int N, int K, int out_f32) {
   const int mt = M > 2 * BM ? 4 : (M > BM ? 2 : 1);
   const long c128 = static_cast<long>((M + BM * mt - 1) / (BM * mt)) * ((N + 127) / 128);
@@ -1417,7 +1464,7 @@ inline int plan_splits(int M, int N, int K, int out_f32) {
     splits = static_cast<int>(148 / c128);
     splits = splits > K / BK / 8 ? K / BK / 8 : splits;          // at least 8 k-blocks each
     splits = splits > 8 ? 8 : splits;
-    while (splits > 1 && static_cast<size_t>(splits) * M * N * 4 > SPLITK_WORKSPACE_BYTES)
+    while (splits > 1 && static_cast<size_t>(splits) * padded_cells(M, N) * 4 > SPLITK_WORKSPACE_BYTES)
       --splits;
   }
   return splits < 1 ? 1 : splits;
@@ -1447,7 +1494,8 @@ inline bool variant_valid(const Variant& v) {
   if (v.nb != 128 && v.nb != 64 && v.nb != 32) return false;
   if (v.splits < 1 || v.splits > 16 || v.splits > v.k / BK) return false;
   if (v.splits > 1 && (v.nb != 128 || v.n % 8)) return false;
-  if (v.splits > 1 && static_cast<size_t>(v.splits) * v.m_hi * v.n * 4 > SPLITK_WORKSPACE_BYTES)
+  if (v.splits > 1 &&
+      static_cast<size_t>(v.splits) * padded_cells(v.m_hi, v.n) * 4 > SPLITK_WORKSPACE_BYTES)
     return false;
   return true;
 }
@@ -1491,7 +1539,7 @@ inline Plan make_plan(int fmt, int M, int N, int K, int out_f32, bool fused) {
     const int per = M <= BM ? 2 : 8;                    // k-blocks a split must keep
     splits = splits > K / BK / per ? K / BK / per : splits;
     splits = splits > 8 ? 8 : splits;
-    while (splits > 1 && static_cast<size_t>(splits) * M * N * 4 > SPLITK_WORKSPACE_BYTES)
+    while (splits > 1 && static_cast<size_t>(splits) * padded_cells(M, N) * 4 > SPLITK_WORKSPACE_BYTES)
       --splits;
     p.splits = splits < 1 ? 1 : splits;
   }
@@ -1604,8 +1652,10 @@ extern "C" int orinfer_qgemm_launches_fmt(int fmt, int M, int N, int K, int out_
                                           int force_path) {
   if (force_path == 1 || (force_path == 0 && M <= 8)) return (M + 7) / 8;
   const tc::Plan p = tc::make_plan(fmt, M, N, K, out_f32, false);
-  if (p.tail_splits > 0) return p.tail_splits > 1 ? 3 : 2;
-  return p.splits > 1 ? 2 : 1;
+  // K splits are added up inside the one-tile kernel; the persistent forms use a second pass
+  const int extra = tc::g_impl == 1 ? 0 : 1;
+  if (p.tail_splits > 0) return p.tail_splits > 1 ? 2 + extra : 2;
+  return p.splits > 1 ? 1 + extra : 1;
 }
 
 extern "C" int orinfer_qgemm_launches(int M, int N, int K, int out_f32, int force_path) {

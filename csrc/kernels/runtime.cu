@@ -23,6 +23,7 @@ struct DeviceState {
   int* status = nullptr;          // int32 [4]: status, -, wait limit / 1024 cycles, -
   E8pTables* tables = nullptr;
   int* splitk = nullptr;
+  int* splitk_tickets = nullptr;  // int32 [SPLITK_TICKETS], zero between launches
   int* gemv_ws = nullptr;
   bool used[MAX_SLOTS] = {};
 };
@@ -80,6 +81,10 @@ cudaError_t runtime_ensure_init() {
   if (e != cudaSuccess) return e;
   e = cudaMalloc(&d.splitk, SPLITK_WORKSPACE_BYTES);
   if (e != cudaSuccess) return e;
+  e = cudaMalloc(&d.splitk_tickets, SPLITK_TICKETS * sizeof(int));
+  if (e != cudaSuccess) return e;
+  e = cudaMemset(d.splitk_tickets, 0, SPLITK_TICKETS * sizeof(int));
+  if (e != cudaSuccess) return e;
   const size_t ws = (static_cast<size_t>(8) * GEMV_WS_COLS + GEMV_WS_TICKETS) * sizeof(int);
   e = cudaMalloc(&d.gemv_ws, ws);
   if (e != cudaSuccess) return e;
@@ -112,6 +117,10 @@ int* runtime_status_ptr() {
 int* runtime_splitk_workspace() {
   DeviceState* d = ready_state();
   return d ? d->splitk : nullptr;
+}
+int* runtime_splitk_tickets() {
+  DeviceState* d = ready_state();
+  return d ? d->splitk_tickets : nullptr;
 }
 int* runtime_gemv_workspace() {
   DeviceState* d = ready_state();

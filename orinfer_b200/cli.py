@@ -196,12 +196,10 @@ def cmd_serve(a) -> int:
         return 1
     service.stop(a.drain_timeout_ms)
     print("SCHEDULER " + json.dumps(service.worker.engine.stats.as_dict()), file=sys.stderr)
+    code = 1 if service.lifecycle.state == "failed" else 0
     for team in teams:                                # graphs, peer mappings, followers, group
-        try:
-            service.worker.engine.close()
-        finally:
-            team.close()
-    return 1 if service.lifecycle.state == "failed" else 0
+        team.close(service.worker.engine)
+    return code
 
 
 def _model_identity(a):

@@ -347,17 +347,23 @@ class Engine:
             self.pool.release(pages)
             self.free_slots.append(slot)
 
-    def close(self) -> None:
+    def close(self, collective: bool = True) -> None:
         """Releases what must go before the process group and the CUDA context do: captured
         graphs first (they hold the collective and peer-memory work they recorded), then the
-        runner's peer mappings."""
+        runner's peer mappings.  With several ranks every rank calls this at the same point
+        (the runner's close meets its peers at a barrier); ``collective=False`` skips that
+        meeting when a rank is known to be gone."""
         self._graphs.clear()
         self.__dict__.pop("_prefill_graphs", None)
         if self.on_gpu:
             torch.cuda.synchronize()
         closer = getattr(self.runner, "close", None)
         if closer is not None:
-            closer()
+            import inspect
+            if "collective" in inspect.signature(closer).parameters:
+                closer(collective=collective)
+            else:
+                closer()
 
     def cancel(self, req: Request) -> None:
         req.cancelled = True

@@ -240,12 +240,14 @@ class FusedTPRunner(TPRunner):
         self._sp_rows_per, self._sp_total = 0, 0
         self._ll = os.environ.get("ORINFER_TP_LL", "1") != "0"
 
-    def close(self) -> None:
+    def close(self, collective: bool = True) -> None:
         """Unmaps the peers' buffers and frees this rank's (collective: every rank arrives at
-        the barrier first, so nobody unmaps memory a peer's kernel may still write)."""
+        the barrier first, so nobody unmaps memory a peer's kernel may still write).
+        ``collective=False`` is for leaving after a peer was lost: no barrier, the peers are
+        not coming."""
         import torch.distributed as dist
         torch.cuda.synchronize()
-        if dist.is_initialized() and self.world > 1:
+        if collective and dist.is_initialized() and self.world > 1:
             dist.barrier(group=self.group)
         a2a = getattr(self, "_a2a", None)
         if a2a is not None and hasattr(a2a, "close"):

@@ -99,12 +99,32 @@ def follower_main(spec: dict) -> int:
             break
         ch.ack(seq)
         done += 1
+    # An orderly close is collective: the leader closes its own engine and destroys the group
+    # at the same point.  After a failure nobody waits for anybody.
     try:
-        engine.close()
+        engine.close(collective=code == 0)
     except Exception:                                   # noqa: BLE001 - leaving anyway
         pass
     ch.close()
+    _leave_group(orderly=code == 0)
     return code
+
+
+def _leave_group(orderly: bool) -> None:
+    """Gives up the process group.  Orderly: every rank destroys it at the same point of the
+    close.  After a failure, destroying an NCCL group would wait for peers that are not coming,
+    so its communicators are aborted instead (gloo has no such wait)."""
+    import torch.distributed as dist
+    if not dist.is_initialized():
+        return
+    try:
+        if orderly or dist.get_backend() != "nccl":
+            dist.destroy_process_group()
+        else:
+            from torch.distributed.distributed_c10d import _abort_process_group
+            _abort_process_group()
+    except Exception:                                   # noqa: BLE001 - peers may be gone
+        pass
 
 
 class RankTeam:
@@ -139,21 +159,30 @@ class RankTeam:
     def admit(self) -> None:
         self.channel.accept_all()
 
-    def close(self, wait_s: float = 20.0) -> None:
+    def close(self, engine=None, wait_s: float = 20.0) -> None:
+        """Ends the team.  Orderly (no failure recorded): the followers get the close command,
+        then every rank, this one included, closes its engine (the runners meet at a barrier
+        before they unmap each other's memory) and destroys the process group, all at the same
+        point.  After a failure the followers are ended and this rank gives up the group
+        without waiting for anybody (an NCCL group is aborted, not destroyed)."""
         self._stop.set()
+        orderly = self.channel.failure is None and all(p.poll() is None for p in self.procs)
         self.channel.close()
+        if engine is not None:
+            try:
+                engine.close(collective=orderly)
+            except Exception:                           # noqa: BLE001 - leaving anyway
+                orderly = False
+        if orderly:
+            _leave_group(True)
         end = time.monotonic() + wait_s
         for p in self.procs:
             try:
                 p.wait(max(0.1, end - time.monotonic()))
             except subprocess.TimeoutExpired:
                 p.kill()
-        import torch.distributed as dist
-        if dist.is_initialized():
-            try:
-                dist.destroy_process_group()
-            except Exception:                           # noqa: BLE001 - peers may be gone
-                pass
+        if not orderly:
+            _leave_group(False)
 
 
 def free_port() -> int:
@@ -177,7 +206,7 @@ def leader_engine(spec: dict, *, deadline_s: float = 30.0):
         weights = load_shard(spec, 0, spec["world"], device)
         engine = build_engine(spec, weights, channel=team.channel)
     except Exception:
-        team.close(1.0)
+        team.close(wait_s=1.0)
         raise
     return engine, team
 

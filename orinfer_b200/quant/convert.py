@@ -148,13 +148,114 @@ def _atomic_json(path: Path, obj) -> None:
     os.replace(tmp, path)
 
 
+def _f16(t: torch.Tensor) -> torch.Tensor:
+    return t.to(torch.float16).contiguous()
+
+
+def build_layer(cfg: ModelConfig, src: "_Source", i: int, lin) -> LayerWeights:
+    """Assembles decoder layer ``i`` from the source tensors; ``lin(weight, fmt)`` quantises
+    one projection.  Formats come from ``cfg`` (``attn_format`` / ``proj_format`` /
+    ``expert_format``)."""
+    f16 = _f16
+    p = f"model.layers.{i}."
+    full = cfg.is_full_attention(i)
+    lw = LayerWeights("attn" if full else "gdn", f16(src.get(p + "input_layernorm.weight")),
+                      f16(src.get(p + "post_attention_layernorm.weight")))
+    if full:
+        d, perm = cfg.head_dim, rotary_permutation(cfg.head_dim, cfg.rotary_dim)
+        q = src.get(p + "self_attn.q_proj.weight")
+        k = src.get(p + "self_attn.k_proj.weight").reshape(cfg.kv_heads, d, -1)[:, perm]
+        if cfg.gated_attention:                # per head: d query rows, then d gate rows
+            q = q.reshape(cfg.q_heads, 2, d, -1)
+            q = torch.cat([q[:, 0][:, perm], q[:, 1]], dim=1)
+        else:
+            q = q.reshape(cfg.q_heads, d, -1)[:, perm]
+        lw.qkv = lin(torch.cat([q.reshape(-1, cfg.hidden), k.reshape(-1, cfg.hidden),
+                                src.get(p + "self_attn.v_proj.weight")]), cfg.attn_format)
+        if cfg.qk_norm:
+            lw.q_norm = f16(src.get(p + "self_attn.q_norm.weight")[perm])
+            lw.k_norm = f16(src.get(p + "self_attn.k_norm.weight")[perm])
+        lw.o = lin(src.get(p + "self_attn.o_proj.weight"), cfg.attn_format)
+    else:
+        hk, hv, gd = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim
+        rep = hv // hk
+        # source rows are grouped per key head: q | k | v of its value heads | z of them
+        w = src.get(p + "linear_attn.in_proj_qkvz.weight").reshape(hk, 2 * gd + 2 * rep * gd, -1)
+        parts = torch.split(w, [gd, gd, rep * gd, rep * gd], dim=1)
+        lw.gdn_qkvz = lin(torch.cat([x.reshape(-1, cfg.hidden) for x in parts]),
+                          cfg.attn_format)
+        ba = src.get(p + "linear_attn.in_proj_ba.weight").reshape(hk, 2 * rep, -1)
+        lw.gdn_ab = f16(torch.cat([ba[:, rep:].reshape(hv, -1), ba[:, :rep].reshape(hv, -1)]))
+        lw.gdn_conv = f16(src.get(p + "linear_attn.conv1d.weight")[:, 0, :])
+        lw.gdn_a_log = src.get(p + "linear_attn.A_log").float().contiguous()
+        lw.gdn_dt_bias = src.get(p + "linear_attn.dt_bias").float().contiguous()
+        lw.gdn_norm = f16(src.get(p + "linear_attn.norm.weight"))
+        lw.gdn_out = lin(src.get(p + "linear_attn.out_proj.weight"), cfg.attn_format)
+    if cfg.experts:
+        router = src.get(p + "mlp.gate.weight")
+        if cfg.shared_expert_ffn:
+            router = torch.cat([router, src.get(p + "mlp.shared_expert_gate.weight")])
+            lw.shared_gate_up = lin(torch.cat([
+                src.get(p + "mlp.shared_expert.gate_proj.weight"),
+                src.get(p + "mlp.shared_expert.up_proj.weight")]), cfg.proj_format)
+            lw.shared_down = lin(src.get(p + "mlp.shared_expert.down_proj.weight"),
+                                 cfg.proj_format)
+        lw.router = f16(router)
+        gu, dn = [], []
+        fused = p + "mlp.experts.gate_up_proj" in src.where     # [E, 2F, H] / [E, H, F]
+        if fused:
+            all_gu, all_dn = src.get(p + "mlp.experts.gate_up_proj"), \
+                src.get(p + "mlp.experts.down_proj")
+        for e in range(cfg.experts):
+            q = p + f"mlp.experts.{e}."
+            if fused:
+                gu.append(lin(all_gu[e], cfg.expert_format))
+                dn.append(lin(all_dn[e], cfg.expert_format))
+                continue
+            gu.append(lin(torch.cat([src.get(q + "gate_proj.weight"),
+                                     src.get(q + "up_proj.weight")]), cfg.expert_format))
+            dn.append(lin(src.get(q + "down_proj.weight"), cfg.expert_format))
+        for bank_name, parts in (("expert_gate_up", gu), ("expert_down", dn)):
+            setattr(lw, bank_name, ExpertBank(
+                parts[0].fmt, cfg.experts, parts[0].n, parts[0].k,
+                torch.stack([x.codes for x in parts]), torch.stack([x.scale for x in parts]),
+                parts[0].signs))
+    else:
+        lw.gate_up = lin(torch.cat([src.get(p + "mlp.gate_proj.weight"),
+                                    src.get(p + "mlp.up_proj.weight")]), cfg.proj_format)
+        lw.down = lin(src.get(p + "mlp.down_proj.weight"), cfg.proj_format)
+    return lw
+
+
+def beam_refine(lin: QLinear, weight: torch.Tensor, device: str = "cpu", rows: int = 128) -> QLinear:
+    """Re-searches the codes of a Q4 projection with the beam-8 refinement (``search.py``),
+    ``rows`` output rows at a time; other formats pass through."""
+    if lin.fmt != "q4":
+        return lin
+    from . import search
+    n, k = lin.n, lin.k
+    packed = lin.codes.cpu().permute(1, 0, 2).reshape(n, k // 8).numpy().view("uint32")
+    scales = lin.scale.cpu().numpy().copy()
+    out = packed.copy()
+    signs = lin.signs.cpu().numpy().astype("int8")
+    for lo in range(0, n, rows):
+        cur = e8p.Q4Weight(packed[lo:lo + rows], scales[lo:lo + rows], signs)
+        new = search.refine_q4(weight[lo:lo + rows].float().cpu().numpy(), cur, device=device)
+        out[lo:lo + rows], scales[lo:lo + rows] = new.packed, new.scales
+    codes = torch.from_numpy(out.view("int32")).reshape(n, k // 128, 16).permute(1, 0, 2)
+    return QLinear("q4", n, k, codes.contiguous(), torch.from_numpy(scales), lin.signs, lin.dense)
+
+
 def convert(source, output, device: str = "cpu", fast: bool = True, name: Optional[str] = None,
             on_layer: Optional[Callable[[int, bool], None]] = None,
-            formats: Optional[Dict[str, str]] = None) -> Path:
+            formats: Optional[Dict[str, str]] = None, search: str = "nearest") -> Path:
     """Returns the model directory.  ``on_layer(i, resumed)`` is called after layer ``i`` is on
     disk (freshly quantised or found in the progress record).  ``formats`` overrides the
     weight formats of the geometry (``attn_format``, ``proj_format``, ``expert_format``,
-    ``head_format``: ``q4`` | ``q2`` | ``w8``)."""
+    ``head_format``: ``q4`` | ``q2`` | ``w8``).  ``search="beam8"`` re-searches every Q4
+    projection with the top-8 coarse-candidate refinement (slower, lower weight error)."""
+    if search not in ("nearest", "beam8"):
+        raise ConvertError("search is nearest or beam8")
     from ..engine.checkpoint import _layer_tensors, _load_layer, save_model
     source, output = Path(source), Path(output)
     config_text = (source / "config.json").read_text()
@@ -169,7 +270,8 @@ def convert(source, output, device: str = "cpu", fast: bool = True, name: Option
     work = output / ".convert"
     work.mkdir(parents=True, exist_ok=True)
     identity = src.identity(config_text + f"|{cfg.attn_format}|{cfg.proj_format}"
-                            f"|{cfg.expert_format}|{cfg.head_format}|{fast}")
+                            f"|{cfg.expert_format}|{cfg.head_format}|{fast}"
+                            + ("" if search == "nearest" else f"|{search}"))
     record_path = work / "progress.json"
     record = {"source": identity, "done": {}}
     if record_path.exists():
@@ -187,10 +289,10 @@ def convert(source, output, device: str = "cpu", fast: bool = True, name: Option
     def lin(weight: torch.Tensor, fmt: str) -> QLinear:
         s = sign(weight.shape[1])
         q = quantize_linear(weight.to(dev), fmt, s.to(dev), fast=fast)
-        return QLinear(q.fmt, q.n, q.k, q.codes.cpu(), q.scale.cpu(), s)
+        q = QLinear(q.fmt, q.n, q.k, q.codes.cpu(), q.scale.cpu(), s)
+        return beam_refine(q, weight, device) if search == "beam8" else q
 
-    def f16(t: torch.Tensor) -> torch.Tensor:
-        return t.to(torch.float16).contiguous()
+    f16 = _f16
 
     for i in range(cfg.layers):
         key, path = f"layer.{i}", work / f"layer_{i:05d}.safetensors"
@@ -199,73 +301,7 @@ def convert(source, output, device: str = "cpu", fast: bool = True, name: Option
             if on_layer:
                 on_layer(i, True)
             continue
-        p = f"model.layers.{i}."
-        full = cfg.is_full_attention(i)
-        lw = LayerWeights("attn" if full else "gdn", f16(src.get(p + "input_layernorm.weight")),
-                          f16(src.get(p + "post_attention_layernorm.weight")))
-        if full:
-            d, perm = cfg.head_dim, rotary_permutation(cfg.head_dim, cfg.rotary_dim)
-            q = src.get(p + "self_attn.q_proj.weight")
-            k = src.get(p + "self_attn.k_proj.weight").reshape(cfg.kv_heads, d, -1)[:, perm]
-            if cfg.gated_attention:                # per head: d query rows, then d gate rows
-                q = q.reshape(cfg.q_heads, 2, d, -1)
-                q = torch.cat([q[:, 0][:, perm], q[:, 1]], dim=1)
-            else:
-                q = q.reshape(cfg.q_heads, d, -1)[:, perm]
-            lw.qkv = lin(torch.cat([q.reshape(-1, cfg.hidden), k.reshape(-1, cfg.hidden),
-                                    src.get(p + "self_attn.v_proj.weight")]), cfg.attn_format)
-            if cfg.qk_norm:
-                lw.q_norm = f16(src.get(p + "self_attn.q_norm.weight")[perm])
-                lw.k_norm = f16(src.get(p + "self_attn.k_norm.weight")[perm])
-            lw.o = lin(src.get(p + "self_attn.o_proj.weight"), cfg.attn_format)
-        else:
-            hk, hv, gd = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim
-            rep = hv // hk
-            # source rows are grouped per key head: q | k | v of its value heads | z of them
-            w = src.get(p + "linear_attn.in_proj_qkvz.weight").reshape(hk, 2 * gd + 2 * rep * gd, -1)
-            parts = torch.split(w, [gd, gd, rep * gd, rep * gd], dim=1)
-            lw.gdn_qkvz = lin(torch.cat([x.reshape(-1, cfg.hidden) for x in parts]),
-                              cfg.attn_format)
-            ba = src.get(p + "linear_attn.in_proj_ba.weight").reshape(hk, 2 * rep, -1)
-            lw.gdn_ab = f16(torch.cat([ba[:, rep:].reshape(hv, -1), ba[:, :rep].reshape(hv, -1)]))
-            lw.gdn_conv = f16(src.get(p + "linear_attn.conv1d.weight")[:, 0, :])
-            lw.gdn_a_log = src.get(p + "linear_attn.A_log").float().contiguous()
-            lw.gdn_dt_bias = src.get(p + "linear_attn.dt_bias").float().contiguous()
-            lw.gdn_norm = f16(src.get(p + "linear_attn.norm.weight"))
-            lw.gdn_out = lin(src.get(p + "linear_attn.out_proj.weight"), cfg.attn_format)
-        if cfg.experts:
-            router = src.get(p + "mlp.gate.weight")
-            if cfg.shared_expert_ffn:
-                router = torch.cat([router, src.get(p + "mlp.shared_expert_gate.weight")])
-                lw.shared_gate_up = lin(torch.cat([
-                    src.get(p + "mlp.shared_expert.gate_proj.weight"),
-                    src.get(p + "mlp.shared_expert.up_proj.weight")]), cfg.proj_format)
-                lw.shared_down = lin(src.get(p + "mlp.shared_expert.down_proj.weight"),
-                                     cfg.proj_format)
-            lw.router = f16(router)
-            gu, dn = [], []
-            fused = p + "mlp.experts.gate_up_proj" in src.where     # [E, 2F, H] / [E, H, F]
-            if fused:
-                all_gu, all_dn = src.get(p + "mlp.experts.gate_up_proj"), \
-                    src.get(p + "mlp.experts.down_proj")
-            for e in range(cfg.experts):
-                q = p + f"mlp.experts.{e}."
-                if fused:
-                    gu.append(lin(all_gu[e], cfg.expert_format))
-                    dn.append(lin(all_dn[e], cfg.expert_format))
-                    continue
-                gu.append(lin(torch.cat([src.get(q + "gate_proj.weight"),
-                                         src.get(q + "up_proj.weight")]), cfg.expert_format))
-                dn.append(lin(src.get(q + "down_proj.weight"), cfg.expert_format))
-            for bank_name, parts in (("expert_gate_up", gu), ("expert_down", dn)):
-                setattr(lw, bank_name, ExpertBank(
-                    parts[0].fmt, cfg.experts, parts[0].n, parts[0].k,
-                    torch.stack([x.codes for x in parts]), torch.stack([x.scale for x in parts]),
-                    parts[0].signs))
-        else:
-            lw.gate_up = lin(torch.cat([src.get(p + "mlp.gate_proj.weight"),
-                                        src.get(p + "mlp.up_proj.weight")]), cfg.proj_format)
-            lw.down = lin(src.get(p + "mlp.down_proj.weight"), cfg.proj_format)
+        lw = build_layer(cfg, src, i, lin)
         tensors = {k: v.detach().cpu().contiguous()
                    for k, v in _layer_tensors(f"layers.{i}", lw).items()}
         tmp = path.with_suffix(".tmp")
@@ -308,11 +344,13 @@ def main(argv=None) -> int:
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--exhaustive", action="store_true", help="slower search, lower error")
     ap.add_argument("--name", default=None)
+    ap.add_argument("--search", default="nearest", choices=["nearest", "beam8"],
+                    help="beam8: top-8 coarse candidates per vector (Q4 projections)")
     ap.add_argument("--format", action="append", default=[], metavar="KEY=FMT",
                     help="e.g. --format attn_format=w8 (q4 | q2 | w8)")
     a = ap.parse_args(argv)
     try:
-        out = convert(a.source, a.output, a.device, fast=not a.exhaustive, name=a.name,
+        out = convert(a.source, a.output, a.device, fast=not a.exhaustive, name=a.name, search=a.search,
                       formats=dict(x.split("=", 1) for x in a.format) or None,
                       on_layer=lambda i, resumed: print(
                           f"layer {i} {'kept' if resumed else 'quantised'}", flush=True))

@@ -26,8 +26,7 @@ def test_leader_and_follower_generate_like_spmd_ranks():
         assert again == out
         assert team.channel.failure is None
     finally:
-        engine.close()
-        team.close()
+        team.close(engine)
     assert all(p.returncode == 0 for p in team.procs)
 
 
@@ -46,7 +45,7 @@ def test_follower_that_stops_replying_fails_the_leader_closed():
         with pytest.raises((RankFailure, RuntimeError)):
             engine.generate([[1, 2, 3]], max_new=1)   # sticky
     finally:
-        team.close(2.0)
+        team.close(wait_s=2.0)
 
 
 def _serve_tp2(device_args, timeout_s=300):

@@ -32,7 +32,7 @@ def _worker(rank, world, port, out_dir, preset, sp=False):
     from orinfer_b200.parallel.tp_runner import TPRunner
     native.init()
     cfg = PRESETS[preset]
-    full = random_model(cfg, seed=0).to(dev)
+    full = random_model(cfg, seed=0, device=dev)
     shard = shard_model(full, rank, world)
     t = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
     g = torch.Generator().manual_seed(1)
