@@ -89,10 +89,12 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     int* __restrict__ partial, int* __restrict__ tickets, int n_begin, int n_end, int probe) {
   // probe (timing experiments only; results are then meaningless): bit 0 = issue no MMAs,
   // bit 1 = copy no operands (the loaders only signal), bit 2 = decode nothing, bit 3 = the
-  // epilogue stores nothing to global memory, bit 4 = no epilogue at all, bit 5 = no k-blocks
+  // epilogue stores nothing to global memory, bit 4 = no epilogue at all, bit 5 = no k-blocks,
+  // bit 6 = leave at once, bit 7 = no TMEM allocation (with bits 0 and 4), bit 8 = no table copy
   using L = Layout<FMT, MT, NB>;
   constexpr int SA = L::SA, SB = L::SB;
   constexpr int BN = NB;
+  if (probe & 64) return;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* a_s = smem + L::A_OFF;
@@ -148,11 +150,11 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     prefetch_tmap(&tmap_a);
     if (FMT == 0) prefetch_tmap(&tmap_b);
   }
-  if (warp == 1) {
+  if (warp == 1 && !(probe & 128)) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
-  if (FMT != 0 && warp >= 3) {
+  if (FMT != 0 && warp >= 3 && !(probe & 256)) {
     e8p_lut_init(lut, tables, threadIdx.x - ROLE_THREADS, PRODUCERS);
   }
   tc_fence_before();
@@ -426,7 +428,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (warp == 1 && !(probe & 128)) tmem_dealloc(tmem_base, TMEM_COLS);
   if (po.tp > 0) peer_signal_done(po, gridDim.x * gridDim.y * gridDim.z);
 }
 

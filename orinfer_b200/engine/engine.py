@@ -338,7 +338,8 @@ class Engine:
             if (self.cfg.head_dim in (64, 128)
                     and self.load.cuda_graph.uses_graph(ExecPhase.PREFILL)
                     and getattr(self.runner, "stage_hook", None) is None):
-                out = self._prefill_graph(packet, (n,), False)
+                plan = self._prefill_pool().plan(((n,), 1, False))
+                out = self._prefill_graph(packet, False, *plan)
             if out is None:
                 out = self.runner.greedy(packet, need_logits=False)
             self.stats.prefill_tokens += n
@@ -354,7 +355,9 @@ class Engine:
         (the runner's close meets its peers at a barrier); ``collective=False`` skips that
         meeting when a rank is known to be gone."""
         self._graphs.clear()
-        self.__dict__.pop("_prefill_graphs", None)
+        pool = self.__dict__.pop("_prefill_graphs", None)
+        if pool is not None:
+            pool.clear()
         if self.on_gpu:
             torch.cuda.synchronize()
         closer = getattr(self.runner, "close", None)
@@ -860,15 +863,59 @@ class Engine:
             packet.decode_rows = spec["n_decode"]
         return packet
 
+    def _graph_eligible(self, spec: dict) -> bool:
+        """A pure-prefill packet of a non-recurrent model in full-graph mode."""
+        return bool(self.on_gpu and spec["n_decode"] == 0 and spec["chunks"]
+                    and not self.recurrent
+                    and getattr(self.runner, "stage_hook", None) is None
+                    and self.cfg.head_dim in (64, 128)
+                    and self.load.cuda_graph.uses_graph(ExecPhase.PREFILL))
+
+    @staticmethod
+    def _geometry(spec: dict) -> tuple:
+        return (tuple(spec["chunks"][1::4]), len(spec["sel"]), bool(spec["need"]))
+
+    def _prefill_pool(self):
+        pool = self.__dict__.get("_prefill_graphs")
+        if pool is None:
+            from ..parallel.graph_registry import GraphPool
+            pool = self._prefill_graphs = GraphPool(self.PREFILL_GRAPHS, 2)
+        return pool
+
+    def _plan_prefill_graph(self, spec: dict):
+        """Leading (or only) rank, before the packet is published: how this packet runs
+        (None = not a graph candidate, else the registry's decision), so that every rank
+        takes the same path.  Geometries a follower could not replay are dropped first: all
+        ranks then capture them again."""
+        if not self._graph_eligible(spec):
+            return None
+        pool = self._prefill_pool()
+        if self.channel is not None:
+            for key in self.channel.take_misses():
+                pool.evict(key)
+        decision, key, held, epoch = pool.plan(self._geometry(spec))
+        self._graph_plan = (decision, key, held, epoch)
+        return decision
+
+    def take_graph_misses(self) -> list:
+        """Follower side: keys of geometries this rank was asked to replay but holds no graph
+        of (it ran them directly); reported to the leader with the acknowledgement."""
+        out, self._graph_misses = getattr(self, "_graph_misses", []), []
+        return out
+
     def _exec_direct(self, packet: Packet, spec: dict, has_media: bool):
         need = spec["need"]
+        plan, self._graph_plan = getattr(self, "_graph_plan", None), None
         graphed = None
-        if (self.on_gpu and spec["n_decode"] == 0 and spec["chunks"] and not self.recurrent
-                and not has_media
-                and getattr(self.runner, "stage_hook", None) is None
-                and self.cfg.head_dim in (64, 128)
-                and self.load.cuda_graph.uses_graph(ExecPhase.PREFILL)):
-            graphed = self._prefill_graph(packet, tuple(spec["chunks"][1::4]), need)
+        if spec.get("graph") is not None and not has_media:
+            if plan is None:                         # follower: carry out the leader's decision
+                from ..parallel.graph_registry import key_of
+                d, key, held, epoch, missed = self._prefill_pool().follow(
+                    self._geometry(spec), spec["graph"])
+                if missed:
+                    self.__dict__.setdefault("_graph_misses", []).append(key)
+                plan = (d, key, held, epoch)
+            graphed = self._prefill_graph(packet, need, *plan)
         return graphed if graphed is not None else self.runner.greedy(packet, need_logits=need)
 
     def _run_direct(self, decoders: List[Request], chunks):
@@ -906,6 +953,8 @@ class Engine:
             segs = [[i, 1, 0, 0] for i in range(n_decode)] + [[c[0], c[1], 0, 0] for c in chunk_rows]
             spec["segs"] = [v for g in segs for v in g]
             spec["first"] = list(range(n_decode)) + [c[0] for c in chunk_rows for _ in range(c[1])]
+        media = self._has_media(decoders, chunks)
+        spec["graph"] = None if media else self._plan_prefill_graph(spec)
         self._publish("direct", spec)
         packet = self._build_packet(spec)
         has_media = self._attach_media(packet, decoders, chunks, chunk_rows, pos)
@@ -930,10 +979,14 @@ class Engine:
             return None, None, order
         return tokens, lg, order
 
+    @staticmethod
+    def _has_media(decoders, chunks) -> bool:
+        return bool(any(r.rope_delta for r in decoders)
+                    or any(r.media or r.rope_positions is not None for r, _ in chunks))
+
     def _attach_media(self, packet: Packet, decoders, chunks, chunk_rows, pos) -> bool:
         """Feature overlay rows and (t, h, w) rotary positions of a direct packet."""
-        if not (any(r.rope_delta for r in decoders)
-                or any(r.media or r.rope_positions is not None for r, _ in chunks)):
+        if not self._has_media(decoders, chunks):
             return False
         rope = torch.tensor([pos, pos, pos], dtype=torch.int32)
         rows_idx, feats = [], []
@@ -984,50 +1037,45 @@ class Engine:
 
     PREFILL_GRAPHS = 16
 
-    def _prefill_graph(self, packet: Packet, chunk_lens: tuple, need: bool):
+    def _prefill_graph(self, packet: Packet, need: bool, decision: int, key: int, held, epoch: int):
         """Full-graph mode: a pure-prefill packet is replayed from a graph keyed by its launch
         geometry (chunk lengths, selected rows); token ids, positions, page-table rows and
-        chunk offsets are data in static buffers.  A geometry is captured at its second use;
-        the least recently used of PREFILL_GRAPHS entries is dropped.  Returns (tokens,
-        logits) or None when this packet ran (or must run) directly."""
-        n_sel = packet.logit_rows.shape[0]
-        key = (chunk_lens, n_sel, need, packet.page_table.data_ptr())
-        cache = self.__dict__.setdefault("_prefill_graphs", {})
-        e = cache.pop(key, None)
-        if e is None:
-            while len(cache) >= self.PREFILL_GRAPHS:
-                cache.pop(next(iter(cache)))
-            cache[key] = {"trials": 1}
-            return None
-        cache[key] = e                               # most recently used goes last
-        if "graph" not in e:
-            e["trials"] += 1
-            if e["trials"] < 2:
-                return None
-            st = Packet(packet.ids.clone(), packet.row_req.clone(), packet.row_pos.clone(),
-                        packet.page_table, packet.rows, packet.max_kv_len,
-                        packet.logit_rows.clone(), chunks=packet.chunks.clone(),
-                        max_q_len=packet.max_q_len, decode_rows=0)
-            self.runner.greedy(st, need_logits=need)                 # warm outside capture
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            from ..ops import native
-            before = native.launches()
-            with torch.cuda.graph(graph):
-                tok, lg = self.runner.greedy(st, need_logits=need)
-            e.update(graph=graph, packet=st, tok=tok, lg=lg, launches=native.launches() - before)
-            self.stats.graph_captures += 1
-        st = e["packet"]
-        st.ids.copy_(packet.ids, non_blocking=True)
-        st.row_req.copy_(packet.row_req, non_blocking=True)
-        st.row_pos.copy_(packet.row_pos, non_blocking=True)
-        st.logit_rows.copy_(packet.logit_rows, non_blocking=True)
-        st.chunks.copy_(packet.chunks, non_blocking=True)
-        e["graph"].replay()
+        chunk offsets are data in static buffers.  The graph registry decides: a geometry is
+        captured at its second use, the least recently used of PREFILL_GRAPHS entries is
+        dropped.  Whatever the decision, the packet's kernels run exactly once in this call,
+        so ranks that decide differently still issue the same collectives.  Returns (tokens,
+        logits), or None when the packet must run directly."""
         from ..ops import native
-        native.count_launches(e["launches"])         # kernels the replay launches
-        self.stats.graph_hits += 1
-        return e["tok"], e["lg"]
+        from ..parallel.graph_registry import CAPTURE, REPLAY
+        if decision == REPLAY:
+            e = held
+            st = e["packet"]
+            st.ids.copy_(packet.ids, non_blocking=True)
+            st.row_req.copy_(packet.row_req, non_blocking=True)
+            st.row_pos.copy_(packet.row_pos, non_blocking=True)
+            st.logit_rows.copy_(packet.logit_rows, non_blocking=True)
+            st.chunks.copy_(packet.chunks, non_blocking=True)
+            e["graph"].replay()
+            native.count_launches(e["launches"])         # kernels the replay launches
+            self.stats.graph_hits += 1
+            return e["tok"], e["lg"]
+        if decision != CAPTURE:
+            return None
+        st = Packet(packet.ids.clone(), packet.row_req.clone(), packet.row_pos.clone(),
+                    packet.page_table, packet.rows, packet.max_kv_len,
+                    packet.logit_rows.clone(), chunks=packet.chunks.clone(),
+                    max_q_len=packet.max_q_len, decode_rows=0)
+        out = self.runner.greedy(st, need_logits=need)       # this step's run, outside capture
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = native.launches()
+        with torch.cuda.graph(graph):                        # records only: nothing runs here
+            tok, lg = self.runner.greedy(st, need_logits=need)
+        entry = dict(graph=graph, packet=st, tok=tok, lg=lg, launches=native.launches() - before)
+        native.count_launches(-entry["launches"])            # recorded, not launched
+        if self._prefill_pool().commit(key, epoch, entry):
+            self.stats.graph_captures += 1
+        return out
 
     def _exec_decode(self, bucket: int, need: bool, ids, slots, pos, live) -> "_DecodeGraph":
         """One pure-decode packet of ``bucket`` rows (padded): warm, capture at the second

@@ -46,6 +46,16 @@ class LeaderChannel:
         # per follower: (sequence number, time sent) of commands not yet acknowledged
         self.pending: List[Deque[Tuple[int, float]]] = [deque() for _ in range(world)]
         self.failure: Optional[RankFailure] = None
+        self.misses: List[int] = []          # graph geometries a follower could not replay
+
+    def take_misses(self) -> List[int]:
+        """Keys reported by followers since the last call (drains their connections first)."""
+        if self.failure is None:
+            for rank in range(1, self.world):
+                if self.conns[rank] is not None:
+                    self._drain(rank)
+        out, self.misses = self.misses, []
+        return out
 
     def accept_all(self) -> None:
         """Waits for every follower's hello (its rank); a missing one is a failure."""
@@ -85,6 +95,8 @@ class LeaderChannel:
                     q = self.pending[rank]
                     while q and q[0][0] <= value:
                         q.popleft()
+                elif kind == "miss":
+                    self.misses.append(int(value))
                 elif kind == "fail":
                     self._fail(rank, f"reported {value}")
         except (EOFError, OSError):
@@ -169,6 +181,13 @@ class FollowerChannel:
     def ack(self, seq: int) -> None:
         try:
             self.conn.send(("ack", seq))
+        except (OSError, ValueError):
+            pass
+
+    def miss(self, key: int) -> None:
+        """A geometry this rank was asked to replay but holds no graph of (it ran directly)."""
+        try:
+            self.conn.send(("miss", int(key)))
         except (OSError, ValueError):
             pass
 

@@ -97,6 +97,8 @@ def follower_main(spec: dict) -> int:
             ch.fail(f"device status {word:#x}")
             code = 1
             break
+        for key in engine.take_graph_misses():
+            ch.miss(key)
         ch.ack(seq)
         done += 1
     # An orderly close is collective: the leader closes its own engine and destroys the group
