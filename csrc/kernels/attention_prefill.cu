@@ -13,6 +13,9 @@
 //     causal mask, keep the running max / sum, rescale O in TMEM when the max moved,
 //     and write P as FP16 into shared memory for the second MMA;
 //   * warp 0 loads the Q tile once with a 3-D TMA (d, head, position).
+// Head size 256 walks the cache in half pages (KT = 64 keys per step): Q (64 KB), two K and
+// two V buffers (32 KB each) and two P buffers then fill the 227 KB of one CTA exactly, and
+// S0 | S1 | O (64 + 64 + 256 columns) still fit in TMEM.
 // Output is O / sum, optionally times sigmoid(gate), in FP16.  Replaces the prefill
 // configurations of causal_attention_int8 and dequantize_attention_kv
 // (kernels/cuda/model/attention_rows.py:61-276, kernels/cuda/model/kv_int8.py:210-247).
@@ -30,14 +33,18 @@ constexpr int TILE = 128;                    // query rows per CTA and keys per 
 
 template <int D>
 struct Smem {
-  static constexpr int SUB = TILE * 128;                 // one [128 x 64 fp16] sub-tile
+  static constexpr int KT = D > 128 ? 64 : 128;          // keys per step
+  static constexpr int SUB = TILE * 128;                 // one [128 x 64 fp16] sub-tile (Q, P)
+  static constexpr int KSUB = KT * 128;                  // one [KT x 64 fp16] sub-tile (K, V)
   static constexpr int NSUB = D / 64;                    // sub-tiles per operand
+  static constexpr int PSUB = KT / 64;                   // sub-tiles of one P buffer
   static constexpr int Q_OFF = 0;
   static constexpr int K_OFF = Q_OFF + NSUB * SUB;       // two K buffers
-  static constexpr int V_OFF = K_OFF + 2 * NSUB * SUB;   // two V buffers
-  static constexpr int P_OFF = V_OFF + 2 * NSUB * SUB;   // two P buffers of 128 x 128 fp16
-  static constexpr int BAR_OFF = P_OFF + 2 * 2 * SUB;
+  static constexpr int V_OFF = K_OFF + 2 * NSUB * KSUB;  // two V buffers
+  static constexpr int P_OFF = V_OFF + 2 * NSUB * KSUB;  // two P buffers of 128 x KT fp16
+  static constexpr int BAR_OFF = P_OFF + 2 * PSUB * SUB;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+  static_assert(TOTAL <= 227 * 1024, "exceeds the shared memory of one CTA");
 };
 
 // Eight INT8 values (two words) -> eight FP16 values times an FP16 scale, exactly
@@ -78,6 +85,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
     int num_pages, int* status) {
   using L = Smem<D>;
   constexpr int NSUB = L::NSUB;
+  constexpr int KT = L::KT;
   constexpr int GROUPS = D / 64;
   constexpr uint32_t TMEM_COLS = 512;          // S0 | S1 (128 columns each) | O (D columns)
   extern __shared__ unsigned char smem_raw[];
@@ -99,7 +107,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
   if (p_first >= ch.q_len) return;
   const int p_count = min(P, ch.q_len - p_first);
   const int last_pos = ch.pos0 + p_first + p_count - 1;
-  const int n_tiles = last_pos / TILE + 1;        // KV pages that any row of the tile can see
+  const int n_tiles = last_pos / KT + 1;          // KV steps that any row of the tile can see
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -136,7 +144,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc(1, 0, 0, 0, 0, TILE, TILE);
+      constexpr uint32_t idesc_s = umma_idesc(1, 0, 0, 0, 0, TILE, KT);
       constexpr uint32_t idesc_o = umma_idesc(1, 0, 0, 0, 1, TILE, D);
       const uint32_t q_addr = smem_u32(smem + L::Q_OFF);
       const uint32_t p_addr = smem_u32(smem + L::P_OFF);
@@ -148,12 +156,13 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
         if (!mbar_wait(&kv_ready[b], (j >> 1) & 1, status, STATUS_MMA_WAIT, 0x100 | j))
           return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(smem + L::K_OFF + b * NSUB * L::SUB);
+        const uint32_t k_addr = smem_u32(smem + L::K_OFF + b * NSUB * L::KSUB);
 #pragma unroll
         for (int i = 0; i < D / 16; ++i) {
-          const uint32_t off = (i / 4) * L::SUB + (i % 4) * 32;
-          mma_f16_ss(tmem_s + 128 * b, umma_desc(q_addr + off, 16, 1024),
-                     umma_desc(k_addr + off, 16, 1024), idesc_s, i != 0 ? 1u : 0u);
+          const uint32_t q_off = (i / 4) * L::SUB + (i % 4) * 32;
+          const uint32_t k_off = (i / 4) * L::KSUB + (i % 4) * 32;
+          mma_f16_ss(tmem_s + 128 * b, umma_desc(q_addr + q_off, 16, 1024),
+                     umma_desc(k_addr + k_off, 16, 1024), idesc_s, i != 0 ? 1u : 0u);
         }
         tc_commit(&s_full[b]);
         return true;
@@ -165,16 +174,16 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
         // waited for before issuing PV(j-1): program order makes the overwrite safe.
         if (j + 1 < n_tiles) ok = issue_qk(j + 1);
         if (!ok) break;
-        const uint32_t v_addr = smem_u32(smem + L::V_OFF + b * NSUB * L::SUB);
-        const uint32_t pj_addr = p_addr + b * 2 * L::SUB;
+        const uint32_t v_addr = smem_u32(smem + L::V_OFF + b * NSUB * L::KSUB);
+        const uint32_t pj_addr = p_addr + b * L::PSUB * L::SUB;
         ok = mbar_wait(&p_ready[b], (j >> 1) & 1, status, STATUS_MMA_WAIT, 0x200 | j);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int i = 0; i < TILE / 16; ++i) {
+        for (int i = 0; i < KT / 16; ++i) {
           const uint32_t a_off = (i / 4) * L::SUB + (i % 4) * 32;
           mma_f16_ss(tmem_o, umma_desc(pj_addr + a_off, 16, 1024),
-                     umma_desc(v_addr + i * 2048, L::SUB, 1024), idesc_o, (j | i) != 0 ? 1u : 0u);
+                     umma_desc(v_addr + i * 2048, L::KSUB, 1024), idesc_o, (j | i) != 0 ? 1u : 0u);
         }
         tc_commit(o_done);
         tc_commit(&kv_free[b]);
@@ -186,15 +195,16 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int b = j & 1;
-      int page = pages[j];
+      int page = pages[j * KT / TILE];
+      const int key_base = j * KT % TILE;            // first key of this step inside the page
       if (page < 0 || page >= num_pages) {
         report_status(status, STATUS_BAD_INDEX, 3);
         page = 0;
       }
-      unsigned char* kb = smem + L::K_OFF + b * NSUB * L::SUB;
-      unsigned char* vb = smem + L::V_OFF + b * NSUB * L::SUB;
+      unsigned char* kb = smem + L::K_OFF + b * NSUB * L::KSUB;
+      unsigned char* vb = smem + L::V_OFF + b * NSUB * L::KSUB;
       constexpr int CPK = D / 16;                    // 16-byte chunks per key
-      constexpr int ITERS = TILE * CPK / 128;
+      constexpr int ITERS = KT * CPK / 128;
       // every load of the page is issued before the first conversion: one memory round trip
       // per page instead of one per pair of chunks (the 128 dequant threads have no other
       // way to hide latency)
@@ -204,7 +214,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
       for (int it = 0; it < ITERS; ++it) {
         const int idx = it * 128 + t;
         const int key = idx / CPK, c = idx % CPK;
-        const size_t slot = (static_cast<size_t>(page) * 128 + key) * kvh + h;
+        const size_t slot = (static_cast<size_t>(page) * 128 + key_base + key) * kvh + h;
         kraw[it] = __ldg(reinterpret_cast<const uint4*>(kc + slot * D + c * 16));
         vraw[it] = __ldg(reinterpret_cast<const uint4*>(vc + slot * D + c * 16));
         ksc[it] = ks[slot * GROUPS + c / 4];
@@ -222,8 +232,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
         const int key = idx / CPK, c = idx % CPK;
         const __half2 k2 = __half2half2(ksc[it]), v2 = __half2half2(vsc[it]);
         const int sub = c / 4, chunk = (c % 4) * 2;
-        unsigned char* kd = kb + sub * L::SUB;
-        unsigned char* vd = vb + sub * L::SUB;
+        unsigned char* kd = kb + sub * L::KSUB;
+        unsigned char* vd = vb + sub * L::KSUB;
         *reinterpret_cast<uint4*>(kd + swz128(key, chunk)) = dequant8(kraw[it].x, kraw[it].y, k2);
         *reinterpret_cast<uint4*>(kd + swz128(key, chunk + 1)) =
             dequant8(kraw[it].z, kraw[it].w, k2);
@@ -248,19 +258,19 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
     for (int j = 0; j < n_tiles; ++j) {
       const int sb = j & 1;
       const uint32_t tmem_sj = tmem_s + 128 * sb;
-      unsigned char* pb = smem + L::P_OFF + sb * 2 * L::SUB;
+      unsigned char* pb = smem + L::P_OFF + sb * L::PSUB * L::SUB;
       ok = mbar_wait(&s_full[sb], (j >> 1) & 1, status, STATUS_EPILOGUE_WAIT, j);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int key0 = j * TILE;
+      const int key0 = j * KT;
       // Only the last page of a row can hold keys beyond its position; every earlier page
       // takes the mask-free path (one FMNMX per score here, FFMA + EX2 per score below).
-      const bool full = key0 + TILE - 1 <= q_pos;
+      const bool full = key0 + KT - 1 <= q_pos;
       // pass 1: row maximum (of the raw scores: the scale is positive)
       float m_raw = -INFINITY;
 #pragma unroll 1
-      for (int c0 = 0; c0 < TILE; c0 += 64) {
+      for (int c0 = 0; c0 < KT; c0 += 64) {
         uint32_t r[32], r2[32];                           // two TMEM loads in flight
         tmem_ld_32x32(tmem_sj + lane_addr + c0, r);
         tmem_ld_32x32(tmem_sj + lane_addr + c0 + 32, r2);
@@ -302,7 +312,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_kernel(
       // pass 2: probabilities -> FP16 P tile, row sum
       float l_tile = 0.f;
 #pragma unroll 1
-      for (int c0 = 0; c0 < TILE; c0 += 32) {
+      for (int c0 = 0; c0 < KT; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(tmem_sj + lane_addr + c0, r);
         tc_wait_ld();
@@ -398,12 +408,11 @@ int launch(const __half* q, const __half* gate, const Chunk* chunks, int n_chunk
           estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return -3;
-  static bool attr = false;
-  if (!attr) {
+  static const int slot = runtime_new_slot();
+  if (runtime_first_use(slot)) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr = true;
   }
   dim3 grid((max_q_len + P - 1) / P, kvh, n_chunks);
   attn_prefill_kernel<D><<<grid, THREADS, L::TOTAL, stream>>>(
@@ -434,5 +443,8 @@ extern "C" int orinfer_attention_prefill(const __half* q, const __half* gate, co
   if (head_dim == 64)
     return fa::launch<64>(q, gate, ch, n_chunks, max_q_len, total_rows, page_table, max_pages, kc,
                           vc, ks, vs, out, qh, kvh, num_pages, stream);
+  if (head_dim == 256)
+    return fa::launch<256>(q, gate, ch, n_chunks, max_q_len, total_rows, page_table, max_pages,
+                           kc, vc, ks, vs, out, qh, kvh, num_pages, stream);
   return -4;          // unsupported head size: caller falls back to the row kernel
 }

@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   // probe (timing experiments only; results are then meaningless): bit 0 = issue no MMAs,
   // bit 1 = copy no operands (the loaders only signal), bit 2 = decode nothing, bit 3 = the
   // epilogue stores nothing to global memory, bit 4 = no epilogue at all, bit 5 = no k-blocks,
-  // bit 6 = leave at once, bit 7 = no TMEM allocation (with bits 0 and 4), bit 8 = no table copy
+  // bit 6 = leave at once, bit 7 = no TMEM allocation (with bits 0 and 4), bit 8 = no table copy, bit 9 = accumulators are reinterpreted, not converted
   using L = Layout<FMT, MT, NB>;
   constexpr int SA = L::SA, SB = L::SB;
   constexpr int BN = NB;
@@ -286,12 +286,32 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
         mbar_arrive(&b_full[s]);
       }
     }
-    if (ok && kblocks > 0) ok = mbar_wait(tmem_full, 0, status, STATUS_EPILOGUE_WAIT, 0);
-    ok = __all_sync(0xffffffffu, ok);        // tcgen05.ld needs the whole warp
     const int quad = warp & 3;                          // TMEM lane quadrant of this warp
     const int part = (warp - 3) >> 2;                   // 0..3: which 32-column chunks
     const int row = quad * 32 + lane;
     constexpr int CHUNKS = BN / 32;                     // 32-column chunks per accumulator
+    // A warp's items all cover the same 32 columns (4 is a multiple of CHUNKS).  Their weight
+    // scales, and the row scales of the warp's rows, are requested before the wait on the
+    // accumulators: fetched one FP16 at a time inside the loop, their latency was most of
+    // the epilogue (10 of 30 us per 512 x 128 tile).
+    const int c_warp = (part % CHUNKS) * 32;
+    uint4 wsv[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const int n = n0 + c_warp + g * 8;
+      wsv[g] = n + 8 <= n_end ? *reinterpret_cast<const uint4*>(w_scale + n)
+                              : make_uint4(0, 0, 0, 0);
+    }
+    float sa_pre[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      const int m = m0 + mt * BM + row;
+      // gathered row scales are written by peers and only complete once the activation
+      // loader has seen their flags: those are read after the accumulators are ready
+      sa_pre[mt] = (ag.tp == 0 && m < m_limit) ? a_scale[m] : 0.f;
+    }
+    if (ok && kblocks > 0) ok = mbar_wait(tmem_full, 0, status, STATUS_EPILOGUE_WAIT, 0);
+    ok = __all_sync(0xffffffffu, ok);        // tcgen05.ld needs the whole warp
     constexpr int TILE_INT4 = MT * BM * BN / 4;
     const size_t tile_id = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
     const size_t tiles = static_cast<size_t>(gridDim.x) * gridDim.y;
@@ -334,12 +354,29 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     }
     if (ok && writes_output && !(probe & 16)) {
       tc_fence_after();
+      // Conversions run at a fraction of the FP32 rate: the 32 weight scales become FP32 once
+      // per thread instead of once per item, and results are packed to FP16 two at a time.
+      float ws[32];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const __half2* h2 = reinterpret_cast<const __half2*>(&wsv[g]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(h2[j]);
+          ws[g * 8 + 2 * j] = f.x;
+          ws[g * 8 + 2 * j + 1] = f.y;
+        }
+      }
 #pragma unroll 1
       for (int item = part; item < MT * CHUNKS; item += 4) {
         const int mt = item / CHUNKS, c0 = (item % CHUNKS) * 32;
         const int m = m0 + mt * BM + row;
         // gathered row scales were written by peers: read them past L1
-        const float sa = m < m_limit ? (ag.tp > 0 ? __ldcg(a_scale + m) : a_scale[m]) : 0.f;
+        float sa = 0.f;
+#pragma unroll
+        for (int q = 0; q < MT; ++q)
+          if (q == mt) sa = sa_pre[q];                     // static indexing keeps it in registers
+        if (ag.tp > 0 && m < m_limit) sa = __ldcg(a_scale + m);
         uint32_t r[32];
         if (kblocks > 0) {
           tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + mt * BN + c0, r);
@@ -368,16 +405,17 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
               float v[8];
 #pragma unroll
               for (int j = 0; j < 8; ++j)
-                v[j] = (static_cast<float>(static_cast<int>(r[g * 8 + j])) *
-                        __half2float(w_scale[n + j])) * sa;
+                v[j] = (((probe & 512) ? __uint_as_float(r[g * 8 + j])
+                                       : static_cast<float>(static_cast<int>(r[g * 8 + j]))) *
+                        ws[g * 8 + j]) * sa;
               if (po.tp > 0 || !OUT_F32) {
                 // step 1: the FP16 tile is staged in the (now idle) operand rings so that it
                 // leaves in whole rows: a warp storing 32 rows x 16 bytes straight from its
                 // registers touches 32 lines per instruction, which made the epilogue cost
                 // more than the main loop; peers get their partial tile the same way
-                __align__(16) __half h[8];
+                __align__(16) __half2 h[4];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
+                for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
                 *reinterpret_cast<int4*>(smem + static_cast<size_t>(mt * BM + row) * STAGE_ROW +
                                          (c0 + g * 8) * 2) = *reinterpret_cast<const int4*>(h);
               } else if (OUT_F32) {
@@ -385,9 +423,9 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
                 *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
                 *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
               } else {
-                __align__(16) __half h[8];
+                __align__(16) __half2 h[4];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
+                for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
                 __half* o = reinterpret_cast<__half*>(out) + static_cast<size_t>(m) * N + n;
                 *reinterpret_cast<int4*>(o) = *reinterpret_cast<const int4*>(h);
               }
@@ -1682,7 +1720,7 @@ extern "C" void orinfer_qgemm_clear_variants() { tc::g_variant_count = 0; }
 // Timing experiments of the one-tile kernel: bit 0 no MMAs, bit 1 no operand copies, bit 2
 // no lattice decode.  Outputs are meaningless while a bit is set.
 extern "C" int orinfer_qgemm_set_probe(int bits) {
-  tc::g_probe = bits & 7;
+  tc::g_probe = bits & 1023;
   return 0;
 }
 

@@ -580,9 +580,20 @@ def build_parser() -> argparse.ArgumentParser:
     cv.add_argument("--exhaustive", action="store_true")
     cv.add_argument("--name", default=None)
     cv.add_argument("--format", action="append", default=[], metavar="KEY=FMT")
+    cv.add_argument("--search", default="nearest", choices=["nearest", "beam8"])
     cv.set_defaults(fn=lambda a: __import__("orinfer_b200.quant.convert", fromlist=["main"]).main(
-        [a.source, a.output, "--device", a.device] + (["--exhaustive"] if a.exhaustive else [])
+        [a.source, a.output, "--device", a.device, "--search", a.search]
+        + (["--exhaustive"] if a.exhaustive else [])
         + (["--name", a.name] if a.name else []) + [x for f in a.format for x in ("--format", f)]))
+    pm = sub.add_parser("promote-model",
+                        help="re-encode chosen layers of a converted model as rotated W8")
+    pm.add_argument("source", help="the original (unquantised) checkpoint directory")
+    pm.add_argument("model_dir")
+    pm.add_argument("output")
+    pm.add_argument("--layers", required=True, help="comma-separated layer numbers")
+    pm.add_argument("--device", default="cpu")
+    pm.set_defaults(fn=lambda a: __import__("orinfer_b200.quant.promotion", fromlist=["main"]).main(
+        [a.source, a.model_dir, a.output, "--layers", a.layers, "--device", a.device]))
     mk = sub.add_parser("make-model")
     mk.add_argument("--preset", required=True, choices=sorted(PRESETS))
     mk.add_argument("--output", required=True)

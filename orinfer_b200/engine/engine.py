@@ -335,7 +335,7 @@ class Engine:
             packet = Packet(ids.to(torch.int32), req_rows, pos, self.page_table_dev, n, n, sel,
                             chunks=chunks, max_q_len=n)
             out = None
-            if (self.cfg.head_dim in (64, 128)
+            if (self.cfg.head_dim in (64, 128, 256)
                     and self.load.cuda_graph.uses_graph(ExecPhase.PREFILL)
                     and getattr(self.runner, "stage_hook", None) is None):
                 plan = self._prefill_pool().plan(((n,), 1, False))
@@ -868,7 +868,7 @@ class Engine:
         return bool(self.on_gpu and spec["n_decode"] == 0 and spec["chunks"]
                     and not self.recurrent
                     and getattr(self.runner, "stage_hook", None) is None
-                    and self.cfg.head_dim in (64, 128)
+                    and self.cfg.head_dim in (64, 128, 256)
                     and self.load.cuda_graph.uses_graph(ExecPhase.PREFILL))
 
     @staticmethod

@@ -215,7 +215,7 @@ class ModelRunner:
         gated = cfg.gated_attention and lw.qkv.n == cfg.q_dim + 2 * cfg.kv_dim
         gate = ws.gate if gated else None
         row_rows = rows
-        if p.chunks is not None and p.attend_pos is None and cfg.head_dim in (64, 128):
+        if p.chunks is not None and p.attend_pos is None and cfg.head_dim in (64, 128, 256):
             done = F.attention_prefill(ws.q, gate, p.chunks, p.max_q_len, p.page_table,
                                        self.kv.k[kv_slot], self.kv.v[kv_slot],
                                        self.kv.ks[kv_slot], self.kv.vs[kv_slot], out=ws.attn,

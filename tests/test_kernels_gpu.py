@@ -344,7 +344,8 @@ def test_e8p_encode_kernel(cuda):
     assert float((codes == ref).float().mean()) > 0.995
 
 
-@pytest.mark.parametrize("qh,kvh,d", [(32, 8, 128), (40, 8, 128), (4, 2, 64), (8, 1, 128)])
+@pytest.mark.parametrize("qh,kvh,d", [(32, 8, 128), (40, 8, 128), (4, 2, 64), (8, 1, 128),
+                                       (16, 2, 256), (2, 2, 256)])
 def test_attention_prefill_tensor_core(cuda, qh, kvh, d):
     """Two chunks: a fresh 300-token prompt and a 130-row continuation at position 200."""
     from orinfer_b200.ops import functional as F
