@@ -315,7 +315,38 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
     constexpr int TILE_INT4 = MT * BM * BN / 4;
     const size_t tile_id = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
     const size_t tiles = static_cast<size_t>(gridDim.x) * gridDim.y;
-    if (partial != nullptr) {
+    if (partial != nullptr && tickets == nullptr) {
+      // Large tiles with many splits: the raw accumulators go to partial[z][M][width]
+      // (compact over this launch's columns) and a second kernel, spread over all SMs, adds
+      // the splits; one CTA reading every other split's tile would take longer than that.
+      if (ok) {
+        tc_fence_after();
+        const int width = n_end - n_begin;
+#pragma unroll 1
+        for (int item = part; item < MT * CHUNKS; item += 4) {
+          const int mt = item / CHUNKS, c0 = (item % CHUNKS) * 32;
+          const int m = m0 + mt * BM + row;
+          uint32_t r[32];
+          if (kblocks > 0) {
+            tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + mt * BN + c0, r);
+            tc_wait_ld();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0;         // an empty k range contributes zero
+          }
+          if (m < m_limit) {
+            int* dst = partial + (static_cast<size_t>(blockIdx.z) * M + m) * width +
+                       (n0 - n_begin) + c0;
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              if (n0 + c0 + g * 4 + 4 <= n_end)
+                *reinterpret_cast<int4*>(dst + g * 4) =
+                    make_int4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+          }
+        }
+      }
+      writes_output = false;
+    } else if (partial != nullptr) {
       // Layout inside a tile: [item][group of 4 columns][row] as int4, so a warp instruction
       // writes (and the last arriver reads back) 512 contiguous bytes.
       if (ok) {
@@ -467,7 +498,9 @@ __global__ void __launch_bounds__(THREADS, 1) qgemm_tc_kernel(
   tc_fence_before();
   __syncthreads();
   if (warp == 1 && !(probe & 128)) tmem_dealloc(tmem_base, TMEM_COLS);
-  if (po.tp > 0) peer_signal_done(po, gridDim.x * gridDim.y * gridDim.z);
+  // (with a second pass adding the splits, that pass pushes to the peers and signals)
+  if (po.tp > 0 && !(partial != nullptr && tickets == nullptr))
+    peer_signal_done(po, gridDim.x * gridDim.y * gridDim.z);
 }
 
 // ---------------------------------------------------------------- persistent form
@@ -1402,6 +1435,12 @@ __global__ void __launch_bounds__(256) splitk_finalize_kernel(
 }
 
 
+// Split-K sums inside the GEMM kernel (one-tile form) when the last arriver has at most
+// 512 KiB of other splits' accumulators to read.
+inline bool splitk_in_kernel(int mt, int nb, int splits) {
+  return splits > 1 && static_cast<long>(splits - 1) * mt * BM * nb * 4 <= 512 * 1024;
+}
+
 template <int FMT, bool OUT_F32, int MT, int NB>
 int launch_ps(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale,
               void* out, int M, int N, int K, cudaStream_t stream, const PeerOut& po,
@@ -1476,13 +1515,22 @@ int launch(const int8_t* a, const float* a_scale, const void* w, const __half* w
   dim3 grid((width + NB - 1) / NB, grp.tiles ? max_tiles : (M + BM * MT - 1) / (BM * MT), splits);
   int* partial = splits > 1 ? runtime_splitk_workspace() : nullptr;
   const size_t tiles = static_cast<size_t>(grid.x) * grid.y;
+  // The CTA that arrives last at a tile adds the other splits itself when that is little to
+  // read; otherwise a second kernel, spread over every SM, adds them.
+  const bool in_kernel = splitk_in_kernel(MT, NB, splits);
   if (splits > 1 && (tiles > static_cast<size_t>(SPLITK_TICKETS) ||
                      tiles * splits * MT * BM * NB * 4 > SPLITK_WORKSPACE_BYTES))
     return -1;
   qgemm_tc_kernel<FMT, OUT_F32, MT, NB><<<grid, THREADS, L::TOTAL, stream>>>(
       ta, tb, reinterpret_cast<const unsigned char*>(w), a_scale, w_scale, out, M, N, K,
-      runtime_e8p_tables(), runtime_status_ptr(), po, grp, ag, partial, runtime_splitk_tickets(),
-      n_begin, n_end, g_probe);
+      runtime_e8p_tables(), runtime_status_ptr(), po, grp, ag, partial,
+      in_kernel ? runtime_splitk_tickets() : nullptr, n_begin, n_end, g_probe);
+  if (splits > 1 && !in_kernel) {
+    const long long items = static_cast<long long>(M) * (width / 8);
+    splitk_finalize_kernel<<<static_cast<unsigned>((items + 255) / 256), 256, 0, stream>>>(
+        partial, splits, a_scale, w_scale, reinterpret_cast<__half*>(out), M, N, po,
+        ag.tp > 0 ? 1 : 0, n_begin, width);
+  }
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -1599,6 +1647,15 @@ inline Plan make_plan(int fmt, int M, int N, int K, int out_f32, bool fused) {
   return p;
 }
 
+// K splits of the tail launch (128-row tiles): fill the machine once, keep at least four
+// k-blocks per split.
+inline int tail_splits_for(int M, int K, int tail_tiles) {
+  const long ctas = static_cast<long>(tail_tiles) * ((M + BM - 1) / BM);
+  long ts = 148 / (ctas > 0 ? ctas : 1);
+  ts = ts > K / BK / 4 ? K / BK / 4 : ts;
+  return static_cast<int>(ts > 8 ? 8 : (ts < 1 ? 1 : ts));
+}
+
 template <int FMT>
 int launch_fmt(const int8_t* a, const float* a_scale, const void* w, const __half* w_scale,
                void* out, int M, int N, int K, int out_f32, cudaStream_t stream,
@@ -1614,14 +1671,16 @@ int launch_fmt(const int8_t* a, const float* a_scale, const void* w, const __hal
     const long ntiles = (N + 127) / 128;
     const int tail_tiles = static_cast<int>(ntiles % 148);
     const int cut = static_cast<int>(ntiles - tail_tiles) * 128;
-    const int ts = plan.tail_splits;
+    // the tail runs as 128-row tiles: more CTAs of less work each, and small accumulator
+    // tiles whose splits are added inside the kernel
+    const int ts = tail_splits_for(M, K, tail_tiles);
 #define ORINFER_TWO(MTV)                                                                        \
   {                                                                                             \
     const int r = launch<FMT, false, MTV, 128>(a, a_scale, w, w_scale, out, M, N, K, stream, po, \
                                                none, 1, 0, ag, 1, 0, cut);                     \
     if (r) return r;                                                                            \
-    return launch<FMT, false, MTV, 128>(a, a_scale, w, w_scale, out, M, N, K, stream, po, none, \
-                                        1, 0, ag, ts, cut, N);                                 \
+    return launch<FMT, false, 1, 128>(a, a_scale, w, w_scale, out, M, N, K, stream, po, none,  \
+                                      1, 0, ag, ts, cut, N);                                   \
   }
     if (mt == 4) ORINFER_TWO(4)
     if (mt == 2) ORINFER_TWO(2)
@@ -1692,10 +1751,17 @@ extern "C" int orinfer_qgemm_launches_fmt(int fmt, int M, int N, int K, int out_
                                           int force_path) {
   if (force_path == 1 || (force_path == 0 && M <= 8)) return (M + 7) / 8;
   const tc::Plan p = tc::make_plan(fmt, M, N, K, out_f32, false);
-  // K splits are added up inside the one-tile kernel; the persistent forms use a second pass
-  const int extra = tc::g_impl == 1 ? 0 : 1;
-  if (p.tail_splits > 0) return p.tail_splits > 1 ? 2 + extra : 2;
-  return p.splits > 1 ? 1 + extra : 1;
+  // K splits are added up inside the one-tile kernel when the tiles are small; otherwise,
+  // and in the persistent forms, a second pass adds them
+  if (p.tail_splits > 0) {
+    const int ts = tc::g_impl == 1
+                       ? tc::tail_splits_for(M, K, static_cast<int>(((N + 127) / 128) % 148))
+                       : p.tail_splits;
+    const bool second = ts > 1 && !(tc::g_impl == 1 && tc::splitk_in_kernel(1, 128, ts));
+    return second ? 3 : 2;
+  }
+  const bool second = p.splits > 1 && !(tc::g_impl == 1 && tc::splitk_in_kernel(p.mt, 128, p.splits));
+  return second ? 2 : 1;
 }
 
 extern "C" int orinfer_qgemm_launches(int M, int N, int K, int out_f32, int force_path) {
