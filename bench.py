@@ -252,8 +252,14 @@ def main() -> int:
         prompts = [torch.randint(0, cfg.vocab, (n_tokens,), generator=gen,
                                  dtype=torch.int32).to(dev)
                    for _ in range(warmup + steps * reps)]
+        run = engine.prefill_device
+        if engine.recurrent:
+            # recurrent (gated-delta-rule) models have no device-resident prefill entry: the
+            # prompt goes through Engine.generate, host round trip included
+            host = {id(p): p.tolist() for p in prompts}
+            run = lambda p: engine.generate([host[id(p)]], max_new=1)
         for p in prompts[:warmup]:
-            engine.prefill_device(p)
+            run(p)
         times, launches = [], 0
         for r in range(reps):
             batch = prompts[warmup + r * steps:warmup + (r + 1) * steps]
@@ -262,7 +268,7 @@ def main() -> int:
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             for p in batch:
-                engine.prefill_device(p)
+                run(p)
             b.record()
             barrier()
             times.append(max_over_ranks(a.elapsed_time(b)) / steps)
@@ -365,7 +371,7 @@ def main() -> int:
             rate, ms, _ = decode_rate(b, 512, 64)
             extra[f"decode_tok_s_bs{b}"] = round(rate, 1)
             extra[f"decode_ms_per_step_bs{b}"] = round(ms, 3)
-        if engine.spec.enabled:
+        if engine.spec.enabled and cfg.ffn and not cfg.experts:     # dense draft layer only
             rate, ms, accept = decode_rate(1, 512, 256, mtp=True)
             extra["decode_tok_s_bs1_mtp_random_weights"] = round(rate, 1)
             extra["mtp_random_weights"] = accept

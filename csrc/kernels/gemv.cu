@@ -517,16 +517,26 @@ static GemvGrid gemv_grid(int rows_per_group, int N, int K) {
   return best;
 }
 
+constexpr size_t GEMV_SMEM_LIMIT = 220 * 1024;
+
+// Dynamic shared memory of the E8P GEMV for `mt` staged activation rows.
+static size_t e8p_gemv_smem(int fmt, int mt, int N, int K, bool fused) {
+  const int rows = fmt == 1 ? 8 : 16;
+  const GemvGrid g = gemv_grid(rows, N, K);
+  size_t smem = sizeof(E8pLut<GEMV_COPIES>) + static_cast<size_t>(mt) * K +
+                (static_cast<size_t>(g.max_groups) * rows * mt + 2 * mt) * sizeof(int) + 16;
+  if (fused) smem += static_cast<size_t>(K) * sizeof(float);
+  return smem;
+}
+
 template <int FMT, int MT>
 static int launch_e8p(const int8_t* a, const float* as, const void* w, const __half* ws, void* out,
                       int M, int N, int K, int out_f32, cudaStream_t stream, const PeerOut& po,
                       const GemvFuse& fz = GemvFuse{}) {
   constexpr int ROWS = FMT == 1 ? 8 : 16;
   const GemvGrid g = gemv_grid(ROWS, N, K);
-  size_t smem = sizeof(E8pLut<GEMV_COPIES>) + static_cast<size_t>(MT) * K +
-                (static_cast<size_t>(g.max_groups) * ROWS * MT + 2 * MT) * sizeof(int) + 16;
-  if (fz.pre != 0) smem += static_cast<size_t>(K) * sizeof(float);
-  if (smem > 220 * 1024) return -1;
+  const size_t smem = e8p_gemv_smem(FMT, MT, N, K, fz.pre != 0);
+  if (smem > GEMV_SMEM_LIMIT) return -1;
   static const int slot = runtime_new_slot();
   if (runtime_first_use(slot)) {
     cudaError_t e = cudaFuncSetAttribute(e8p_gemv_kernel<FMT, MT>,
@@ -559,6 +569,24 @@ int qgemv_dispatch(int fmt, const int8_t* a, const float* as, const void* w, con
   PeerOut po{};
   if (peer != nullptr) po = *peer;
   if (M < 1 || M > 8 || K % 128) return -1;
+  if (fmt != 0) {
+    // Very long rows (K above about 19 000 at eight rows): the staged activations of all
+    // rows do not fit beside the tables, so the rows go in several launches.
+    int fit = 8;
+    while (fit > 1 && e8p_gemv_smem(fmt, fit, N, K, false) > GEMV_SMEM_LIMIT) fit /= 2;
+    if (M > fit) {
+      if (peer != nullptr && peer->tp > 0) return -1;      // row indices of the push would shift
+      const size_t out_row = static_cast<size_t>(N) * (out_f32 ? 4 : 2);
+      for (int m0 = 0; m0 < M; m0 += fit) {
+        const int rows = M - m0 < fit ? M - m0 : fit;
+        const int r = qgemv_dispatch(fmt, a + static_cast<size_t>(m0) * K, as + m0, w, ws,
+                                     static_cast<char*>(out) + m0 * out_row, rows, N, K, out_f32,
+                                     stream, peer);
+        if (r) return r;
+      }
+      return 0;
+    }
+  }
 #define BY_M(FN, ...)                                            \
   (M == 1 ? FN<__VA_ARGS__ 1>(a, as, w, ws, out, M, N, K, out_f32, stream, po)  \
    : M == 2 ? FN<__VA_ARGS__ 2>(a, as, w, ws, out, M, N, K, out_f32, stream, po) \

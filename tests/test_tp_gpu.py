@@ -112,7 +112,8 @@ def _check(tmp_path, world, preset="tiny", sp=False):
                                                 res["single"].flatten(), dim=0)
     # sharding changes the per-row activation scales (each rank quantises its own slice of
     # the channels), so the sharded and the single-GPU logits agree only approximately
-    assert cos > (0.995 if preset == "tiny" else 0.99), cos
+    # (routed models: a token whose top-k set flips under the changed scales moves further)
+    assert cos > {"tiny": 0.995, "mid-dense": 0.99}.get(preset, 0.98), cos
 
 
 PRESET_NAMES = ["tiny", "tiny-moe", "tiny-hybrid"]
