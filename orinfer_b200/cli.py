@@ -93,6 +93,15 @@ def _engine_factory(a, weights, load, sched):
     from .engine.engine import Engine
 
     def factory():
+        # dimensions, sharding and memory are checked before the engine allocates anything
+        from .engine.plan import validate_plan
+        device_bytes = None
+        dev = weights.embed_q.device
+        if dev.type == "cuda":
+            import torch
+            device_bytes = torch.cuda.get_device_properties(dev).total_memory
+        validate_plan(weights.config, load, sched, max_context=a.max_context,
+                      device_bytes=device_bytes)
         return Engine(weights, load=load, sched=sched, max_context=a.max_context)
     return factory
 
@@ -352,7 +361,20 @@ def cmd_plan_model(a) -> int:
         cfg = ModelConfig.from_json((Path(a.model_dir) / "config.json").read_text())
     layers = [{"layer": i, "kind": "attention" if cfg.is_full_attention(i) else "gdn",
                "ffn": "moe" if cfg.experts else "dense"} for i in range(cfg.layers)]
-    print(json.dumps({"model": cfg.name, "target": "sm_100a", "layers": layers,
+    from .config import LoadOptions, SchedulerOptions
+    from .engine.plan import PlanError, validate_plan
+    descriptor = None if a.preset else read_descriptor(a.model_dir)
+    try:
+        plan = validate_plan(cfg, LoadOptions(), SchedulerOptions(),
+                             max_context=getattr(a, "max_context", None),
+                             world=getattr(a, "tp", None) or 1,
+                             device_bytes=(getattr(a, "device_gib", None) or 180) << 30,
+                             descriptor=descriptor, exhaustive=True)
+    except PlanError as e:
+        print(json.dumps({"model": cfg.name, "ok": False, "error": str(e)}))
+        return 2
+    print(json.dumps({"model": cfg.name, "target": "sm_100a", "ok": True,
+                      "memory_plan": plan.as_dict(), "layers": layers,
                       "kv_bytes_per_token": cfg.kv_bytes_per_token(),
                       "kv_bytes_per_page": KVPool.bytes_per_page(cfg, cfg.mtp_layers),
                       "programs": ["prefill", "decode", "mixed", "verify"],
@@ -554,6 +576,9 @@ def build_parser() -> argparse.ArgumentParser:
     pm = sub.add_parser("plan-model")
     pm.add_argument("model_dir", nargs="?")
     pm.add_argument("--preset", choices=sorted(PRESETS))
+    pm.add_argument("--max-context", type=int, default=None)
+    pm.add_argument("--tp", type=int, default=1, help="ranks the model is to be split over")
+    pm.add_argument("--device-gib", type=int, default=180, help="memory of one device")
     pm.set_defaults(fn=cmd_plan_model)
     r = sub.add_parser("run-model")
     _load_args(r)

@@ -239,21 +239,23 @@ class ModelRunner:
         cfg, ws = self.cfg, self.ws
         h, eps, zc = cfg.hidden, cfg.eps, cfg.zero_centered_norm
         fuse = F.qgemv_fused
-        if not fuse(F.PRE_NORM, None, ws.resid, lw.in_norm, lw.qkv.signs, lw.qkv.codes,
-                    lw.qkv.scale, lw.qkv.fmt, lw.qkv.n, h, rows, eps=eps, zero_centered=zc,
-                    out=ws.qkv):
-            return False
-        self._attention_core(lw, kv_slot, ws.qkv, p, rows)
         qd = cfg.q_heads * cfg.head_dim
         f = lw.gate_up.n // 2
         gu = ws.gate_up.view(-1)[: ws.max_rows * 2 * f].view(ws.max_rows, 2 * f)
-        ok = fuse(F.PRE_PLAIN, ws.attn, None, None, lw.o.signs, lw.o.codes, lw.o.scale, lw.o.fmt,
-                  h, qd, rows, resid_accum=ws.resid)
-        ok = ok and fuse(F.PRE_NORM, None, ws.resid, lw.post_norm, lw.gate_up.signs,
-                         lw.gate_up.codes, lw.gate_up.scale, lw.gate_up.fmt, 2 * f, h, rows,
-                         eps=eps, zero_centered=zc, out=gu)
-        ok = ok and fuse(F.PRE_SWIGLU, gu, None, None, lw.down.signs, lw.down.codes,
-                         lw.down.scale, lw.down.fmt, h, f, rows, resid_accum=ws.resid)
+        with trace.span("attn"):
+            if not fuse(F.PRE_NORM, None, ws.resid, lw.in_norm, lw.qkv.signs, lw.qkv.codes,
+                        lw.qkv.scale, lw.qkv.fmt, lw.qkv.n, h, rows, eps=eps, zero_centered=zc,
+                        out=ws.qkv):
+                return False
+            self._attention_core(lw, kv_slot, ws.qkv, p, rows)
+            ok = fuse(F.PRE_PLAIN, ws.attn, None, None, lw.o.signs, lw.o.codes, lw.o.scale,
+                      lw.o.fmt, h, qd, rows, resid_accum=ws.resid)
+        with trace.span("ffn"):
+            ok = ok and fuse(F.PRE_NORM, None, ws.resid, lw.post_norm, lw.gate_up.signs,
+                             lw.gate_up.codes, lw.gate_up.scale, lw.gate_up.fmt, 2 * f, h, rows,
+                             eps=eps, zero_centered=zc, out=gu)
+            ok = ok and fuse(F.PRE_SWIGLU, gu, None, None, lw.down.signs, lw.down.codes,
+                             lw.down.scale, lw.down.fmt, h, f, rows, resid_accum=ws.resid)
         if not ok:
             raise RuntimeError("a projection of this model does not fit the fused decode kernel")
         return True
