@@ -44,7 +44,9 @@ class CheckpointError(ValueError):
 
 
 def _put_linear(out: Dict[str, torch.Tensor], name: str, lin: QLinear) -> None:
-    if lin.fmt == "w8":
+    if lin.fmt == "w8" and lin.rowq4 is not None:
+        out[f"{name}.rowq4"] = lin.rowq4                 # 4-bit level-table rows, expanded on load
+    elif lin.fmt == "w8":
         out[f"{name}.int8"] = lin.codes
     elif lin.fmt == "q4":
         out[f"{name}.packed"] = lin.codes
@@ -57,6 +59,18 @@ def _put_linear(out: Dict[str, torch.Tensor], name: str, lin: QLinear) -> None:
 
 def _get_linear(t: Dict[str, torch.Tensor], name: str, signs: Dict[int, torch.Tensor]) -> QLinear:
     scale = t[f"{name}.scale"]
+    if f"{name}.rowq4" in t:
+        # scalar level-table rows (quant/row_q4.py): the INT8 levels are what the W8 kernels
+        # multiply, so the rows are expanded once here
+        from ..quant.row_q4 import RowQ4Weight
+        packed = t[f"{name}.rowq4"]
+        n, k = packed.shape[0], 2 * packed.shape[1]
+        if k not in signs:
+            raise CheckpointError(f"{name}: no rotation signs for K={k}")
+        ints = RowQ4Weight(packed.cpu().numpy(), scale.cpu().numpy(),
+                           signs[k].cpu().numpy().astype(np.int8)).integers()
+        return QLinear("w8", n, k, torch.from_numpy(ints).to(packed.device), scale, signs[k],
+                       None, packed)
     if f"{name}.int8" in t:
         codes = t[f"{name}.int8"]
         n, k = codes.shape

@@ -148,7 +148,7 @@ def _check_descriptor(cfg: ModelConfig, descriptor: dict, exhaustive: bool) -> N
             continue
         if stem + ".scale" not in tensors:
             raise PlanError(f"descriptor has no scales for {stem}")
-        if not any(stem + suffix in tensors for suffix in (".int8", ".packed", ".packed16")):
+        if not any(stem + suffix in tensors for suffix in (".int8", ".packed", ".packed16", ".rowq4")):
             raise PlanError(f"descriptor has no weight codes for {stem}")
     for name in ("final_norm", "orinfer.e8p_q4.basis"):
         if name not in tensors:

@@ -29,6 +29,9 @@ class QLinear:
     scale: torch.Tensor               # fp16 [N]
     signs: Optional[torch.Tensor]     # int8 [K] when the input is rotated
     dense: Optional[torch.Tensor] = None   # original fp32 weights (kept for tiny models only)
+    # uint8 [N, K/2]: the scalar level-table nibbles these W8 codes were expanded from
+    # (quant/row_q4.py); a checkpoint then stores the nibbles, 4 bits per weight, not the codes
+    rowq4: Optional[torch.Tensor] = None
 
     def integers(self) -> torch.Tensor:
         """INT8 [N, K] integer weights in the (rotated) basis the GEMM multiplies."""
@@ -44,7 +47,7 @@ class QLinear:
     def to(self, device) -> "QLinear":
         mv = lambda t: None if t is None else t.to(device)
         return QLinear(self.fmt, self.n, self.k, mv(self.codes), mv(self.scale), mv(self.signs),
-                       self.dense)
+                       self.dense, self.rowq4)
 
     def nbytes(self) -> int:
         return self.codes.numel() * self.codes.element_size() + self.scale.numel() * 2

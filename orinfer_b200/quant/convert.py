@@ -252,7 +252,9 @@ def convert(source, output, device: str = "cpu", fast: bool = True, name: Option
     """Returns the model directory.  ``on_layer(i, resumed)`` is called after layer ``i`` is on
     disk (freshly quantised or found in the progress record).  ``formats`` overrides the
     weight formats of the geometry (``attn_format``, ``proj_format``, ``expert_format``,
-    ``head_format``: ``q4`` | ``q2`` | ``w8``).  ``search="beam8"`` re-searches every Q4
+    ``head_format``: ``q4`` | ``q2`` | ``w8``; ``attn_format`` and ``proj_format`` also take
+    ``rq4``: scalar level-table rows of ``quant/row_q4.py``, stored as 4-bit nibbles and run as
+    8-bit weights).  ``search="beam8"`` re-searches every Q4
     projection with the top-8 coarse-candidate refinement (slower, lower weight error)."""
     if search not in ("nearest", "beam8"):
         raise ConvertError("search is nearest or beam8")
@@ -263,13 +265,22 @@ def convert(source, output, device: str = "cpu", fast: bool = True, name: Option
     if formats:
         import dataclasses
         unknown = set(formats) - {"attn_format", "proj_format", "expert_format", "head_format"}
-        if unknown or any(v not in ("q4", "q2", "w8") for v in formats.values()):
-            raise ConvertError("formats maps attn / proj / expert / head_format to q4, q2 or w8")
-        cfg = dataclasses.replace(cfg, **formats)
+        if unknown or any(v not in ("q4", "q2", "w8", "rq4") for v in formats.values()):
+            raise ConvertError("formats maps attn / proj / expert / head_format to q4, q2, w8 "
+                               "or rq4")
+        if any(v == "rq4" for k, v in formats.items() if k in ("expert_format", "head_format")):
+            raise ConvertError("rq4 (scalar level-table rows) serves attn_format and proj_format")
+        # rq4 rows run as W8 (their levels are INT8 values); only the stored form differs, so
+        # the saved geometry says w8 and the layer builder is told rq4
+        build_cfg = dataclasses.replace(cfg, **formats)
+        cfg = dataclasses.replace(cfg, **{k: ("w8" if v == "rq4" else v)
+                                          for k, v in formats.items()})
+    else:
+        build_cfg = cfg
     src = _Source(source)
     work = output / ".convert"
     work.mkdir(parents=True, exist_ok=True)
-    identity = src.identity(config_text + f"|{cfg.attn_format}|{cfg.proj_format}"
+    identity = src.identity(config_text + f"|{build_cfg.attn_format}|{build_cfg.proj_format}"
                             f"|{cfg.expert_format}|{cfg.head_format}|{fast}"
                             + ("" if search == "nearest" else f"|{search}"))
     record_path = work / "progress.json"
@@ -288,6 +299,12 @@ def convert(source, output, device: str = "cpu", fast: bool = True, name: Option
 
     def lin(weight: torch.Tensor, fmt: str) -> QLinear:
         s = sign(weight.shape[1])
+        if fmt == "rq4":
+            from . import row_q4
+            q = row_q4.fit(weight.float().cpu().numpy(), s.cpu().numpy().astype("int8"))
+            codes, scale = row_q4.expand_to_w8(q)
+            return QLinear("w8", weight.shape[0], weight.shape[1], torch.from_numpy(codes),
+                           torch.from_numpy(scale), s, None, torch.from_numpy(q.packed))
         q = quantize_linear(weight.to(dev), fmt, s.to(dev), fast=fast)
         q = QLinear(q.fmt, q.n, q.k, q.codes.cpu(), q.scale.cpu(), s)
         return beam_refine(q, weight, device) if search == "beam8" else q
@@ -301,7 +318,7 @@ def convert(source, output, device: str = "cpu", fast: bool = True, name: Option
             if on_layer:
                 on_layer(i, True)
             continue
-        lw = build_layer(cfg, src, i, lin)
+        lw = build_layer(build_cfg, src, i, lin)
         tensors = {k: v.detach().cpu().contiguous()
                    for k, v in _layer_tensors(f"layers.{i}", lw).items()}
         tmp = path.with_suffix(".tmp")
@@ -347,7 +364,7 @@ def main(argv=None) -> int:
     ap.add_argument("--search", default="nearest", choices=["nearest", "beam8"],
                     help="beam8: top-8 coarse candidates per vector (Q4 projections)")
     ap.add_argument("--format", action="append", default=[], metavar="KEY=FMT",
-                    help="e.g. --format attn_format=w8 (q4 | q2 | w8)")
+                    help="e.g. --format attn_format=w8 (q4 | q2 | w8; attn / proj also rq4)")
     a = ap.parse_args(argv)
     try:
         out = convert(a.source, a.output, a.device, fast=not a.exhaustive, name=a.name, search=a.search,

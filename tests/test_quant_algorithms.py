@@ -311,3 +311,27 @@ def test_converter_beam_search_lowers_the_weight_error(tmp_path):
     assert err(beam) < 0.98 * err(plain)
     with pytest.raises(convert.ConvertError):
         convert.convert(src, tmp_path / "x", search="widest")
+
+
+def test_row_q4_projections_are_stored_as_nibbles_and_run_as_w8(tmp_path):
+    from safetensors import safe_open
+
+    from orinfer_b200.engine.checkpoint import load_model
+    from orinfer_b200.quant import convert
+    from orinfer_b200.ref.cpu_forward import generate_greedy
+    src = _tiny_source(tmp_path)
+    out = convert.convert(src, tmp_path / "rq4", formats={"proj_format": "rq4"})
+    with safe_open(str(out / "model.safetensors"), "pt") as f:
+        names = set(f.keys())
+        packed = f.get_tensor("layers.0.down.rowq4")
+    assert "layers.0.down.rowq4" in names and "layers.0.down.int8" not in names
+    assert "layers.0.qkv.packed" in names                      # attention keeps the lattice codes
+    assert packed.dtype == torch.uint8 and packed.shape == (128, 128)
+    model = load_model(out, "cpu", verify=True)
+    down = model.layers[0].down
+    assert down.fmt == "w8" and down.codes.dtype == torch.int8 and down.rowq4 is not None
+    assert set(down.codes.abs().unique().tolist()) <= set(row_q4.LEVELS)
+    assert model.config.proj_format == "w8"
+    assert len(generate_greedy(model, torch.arange(1, 20, dtype=torch.int32), 3)[0]) == 3
+    with pytest.raises(convert.ConvertError):
+        convert.convert(src, tmp_path / "bad", formats={"expert_format": "rq4"})
