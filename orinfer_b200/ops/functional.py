@@ -169,10 +169,13 @@ def qgemv_fused(pre: int, x: Optional[torch.Tensor], resid: Optional[torch.Tenso
 
 def attention_splits(max_kv_len: int, rows: int, kvh: int) -> int:
     """Split the key axis when there are too few (row, kv head) CTAs to fill 148 SMs: about
-    three CTAs per SM, at least 64 keys per split."""
+    three CTAs per SM, at least 64 keys per split.  An ``attention`` entry of the tuning table
+    (``tuning/tables.py``) replaces the first rule for its row and context range."""
     if max_kv_len <= 128:
         return 1
-    want = max(1, (148 * 3) // max(rows * kvh, 1))
+    from ..tuning import tables
+    tuned = tables.attention_lookup(max_kv_len, rows, kvh)      # a tuned table overrides
+    want = tuned if tuned is not None else max(1, (148 * 3) // max(rows * kvh, 1))
     return int(max(1, min(want, (max_kv_len + 63) // 64, 32)))
 
 

@@ -4,10 +4,13 @@ A table is JSON::
 
     {"device": "NVIDIA B200", "schema": 1,
      "gemm": [{"fmt": "q4", "n": 19456, "k": 2560, "m_lo": 257, "m_hi": 512,
-               "mt": 2, "nb": 128, "splits": 1, "us": 61.2, "us_default": 64.0}, ...]}
+               "mt": 2, "nb": 128, "splits": 1, "us": 61.2, "us_default": 64.0}, ...],
+     "attention": [{"rows_lo": 1, "rows_hi": 1, "ctx_lo": 257, "ctx_hi": 1024, "kvh": 8,
+                    "splits": 8, "us": 11.9, "us_default": 12.4}, ...]}
 
 Every entry replaces the launch heuristics of the tensor-core GEMM for rows ``m_lo..m_hi`` of
 one projection shape; shapes and row counts that no entry covers keep the heuristics.  The
+optional ``attention`` list does the same for the key-axis split count of decode attention.  The
 reference selects kernels per row range the same way (``KernelVariant{min_rows, max_rows}``,
 crates/orinfer-model-sdk/src/operators/rows.rs:10-60) from tables written by its offline
 tuners (python/orinfer_build/tuning/); here the tuner is ``orinfer_b200.tuning.gemm_tuner``.
@@ -123,6 +126,82 @@ def merge_ranges(variants: Iterable[GemmVariant]) -> List[GemmVariant]:
     return out
 
 
+# ---------------------------------------------------------------- decode attention splits
+@dataclass(frozen=True)
+class AttentionSplit:
+    """Key-axis split count of the decode / verify attention kernel for packets of
+    ``rows_lo..rows_hi`` rows whose longest context is within ``ctx_lo..ctx_hi`` tokens, on a
+    model with ``kvh`` KV heads.  Replaces the heuristic of ``ops.functional.attention_splits``
+    for that range (written by ``orinfer_b200.tuning.attention_tuner``)."""
+    rows_lo: int
+    rows_hi: int
+    ctx_lo: int
+    ctx_hi: int
+    kvh: int
+    splits: int
+    us: float = 0.0
+    us_default: float = 0.0
+
+    def problems(self) -> List[str]:
+        bad = []
+        if self.rows_lo < 1 or self.rows_hi < self.rows_lo:
+            bad.append("row range must satisfy 1 <= rows_lo <= rows_hi")
+        if self.ctx_lo < 1 or self.ctx_hi < self.ctx_lo:
+            bad.append("context range must satisfy 1 <= ctx_lo <= ctx_hi")
+        if self.kvh < 1:
+            bad.append("kvh must be positive")
+        if not 1 <= self.splits <= 32:
+            bad.append("splits must be within 1..32")
+        return bad
+
+
+ATTENTION: List[AttentionSplit] = []
+
+
+def parse_attention(text: str) -> List[AttentionSplit]:
+    doc = json.loads(text)
+    if not isinstance(doc, dict) or doc.get("schema") != SCHEMA:
+        raise ValueError(f"tuning table: schema {SCHEMA} expected")
+    out: List[AttentionSplit] = []
+    for i, e in enumerate(doc.get("attention", [])):
+        try:
+            v = AttentionSplit(**{k: int(e[k]) for k in ("rows_lo", "rows_hi", "ctx_lo", "ctx_hi",
+                                                         "kvh", "splits")},
+                               us=float(e.get("us", 0.0)),
+                               us_default=float(e.get("us_default", 0.0)))
+        except (KeyError, TypeError, ValueError) as err:
+            raise ValueError(f"tuning table: attention entry {i}: {err}") from None
+        bad = v.problems()
+        if bad:
+            raise ValueError(f"tuning table: attention entry {i}: {'; '.join(bad)}")
+        out.append(v)
+    for a in range(len(out)):
+        for b in range(a + 1, len(out)):
+            x, y = out[a], out[b]
+            if (x.kvh == y.kvh and x.rows_lo <= y.rows_hi and y.rows_lo <= x.rows_hi
+                    and x.ctx_lo <= y.ctx_hi and y.ctx_lo <= x.ctx_hi):
+                raise ValueError(f"tuning table: attention entries {a} and {b} overlap")
+    return out
+
+
+def attention_lookup(max_kv_len: int, rows: int, kvh: int) -> Optional[int]:
+    for v in ATTENTION:
+        if v.kvh == kvh and v.rows_lo <= rows <= v.rows_hi and v.ctx_lo <= max_kv_len <= v.ctx_hi:
+            return v.splits
+    return None
+
+
+def set_attention(entries: Iterable[AttentionSplit]) -> int:
+    ATTENTION[:] = list(entries)
+    return len(ATTENTION)
+
+
+def dump_attention(entries: Iterable[AttentionSplit]) -> List[dict]:
+    return [dict(rows_lo=v.rows_lo, rows_hi=v.rows_hi, ctx_lo=v.ctx_lo, ctx_hi=v.ctx_hi,
+                 kvh=v.kvh, splits=v.splits, us=round(v.us, 2), us_default=round(v.us_default, 2))
+            for v in sorted(entries, key=lambda v: (v.kvh, v.rows_lo, v.ctx_lo))]
+
+
 def apply(variants: Iterable[GemmVariant], lib=None) -> int:
     """Replaces the kernel library's variant table; returns the number of entries set."""
     if lib is None:
@@ -142,10 +221,13 @@ def apply(variants: Iterable[GemmVariant], lib=None) -> int:
 def load_default(lib=None) -> int:
     name = os.environ.get("ORINFER_TUNING_TABLE", "")
     if name == "off":
+        set_attention([])
         return apply([], lib)
     path = Path(name) if name else DEFAULT_PATH
     if not path.exists():
         if name:
             raise FileNotFoundError(f"ORINFER_TUNING_TABLE={name} does not exist")
         return 0
-    return apply(parse(path.read_text()), lib)
+    text = path.read_text()
+    set_attention(parse_attention(text))
+    return apply(parse(text), lib)

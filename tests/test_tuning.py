@@ -136,3 +136,49 @@ def test_launch_plan_is_valid_over_the_whole_row_domain():
                         checked += 1
     lib.orinfer_qgemm_clear_variants()
     assert checked > 40_000
+
+
+def test_attention_split_table_overrides_the_heuristic():
+    from orinfer_b200.ops import functional as F
+    from orinfer_b200.tuning.tables import AttentionSplit
+    saved = list(tables.ATTENTION)
+    try:
+        tables.set_attention([])
+        base = F.attention_splits(512, 1, 8)
+        assert base == 8                                         # 512 keys: at most 8 splits of 64
+        assert F.attention_splits(100, 1, 8) == 1                # one page: never split
+        doc = {"schema": 1, "gemm": [], "attention": [
+            {"rows_lo": 1, "rows_hi": 2, "ctx_lo": 129, "ctx_hi": 1024, "kvh": 8, "splits": 4,
+             "us": 10.0, "us_default": 12.0}]}
+        import json
+        entries = tables.parse_attention(json.dumps(doc))
+        assert tables.set_attention(entries) == 1
+        assert F.attention_splits(512, 1, 8) == 4                # tuned
+        assert F.attention_splits(512, 2, 8) == 4
+        assert F.attention_splits(512, 3, 8) == F.attention_splits(512, 3, 8) != 0   # outside: heuristic
+        assert F.attention_splits(512, 1, 4) == min(148 * 3 // 4, 8)               # other head count
+        assert F.attention_splits(200, 1, 8) == 4                # 200 keys: ceil(200/64) = 4 caps it
+        assert tables.dump_attention(entries)[0]["splits"] == 4
+        doc["attention"].append(dict(doc["attention"][0], rows_lo=2, rows_hi=4))
+        with pytest.raises(ValueError, match="overlap"):
+            tables.parse_attention(json.dumps(doc))
+        doc["attention"] = [dict(doc["attention"][0], splits=64)]
+        with pytest.raises(ValueError, match="splits"):
+            tables.parse_attention(json.dumps(doc))
+        assert AttentionSplit(1, 1, 129, 512, 8, 8).problems() == []
+    finally:
+        tables.set_attention(saved)
+
+
+def test_attention_tuner_cells_and_choice():
+    from orinfer_b200.tuning import attention_tuner as at
+    assert at.candidates(512) == [1, 2, 3, 4, 6, 8]
+    assert at.candidates(130) == [1, 2]                        # 130 keys over 3 splits: 44 each
+    assert 32 in at.candidates(8192)
+    cells = at.buckets([1, 8], [512])
+    assert cells == [((1, 1), (129, 512)), ((5, 8), (129, 512))]
+    assert len(at.buckets([], [])) == len(at.ROW_BUCKETS) * len(at.CTX_BUCKETS)
+    # a candidate must beat the heuristic by more than the margin
+    assert at.choose({4: 10.0, 8: 9.9}, 4, 0.03) == (4, 10.0, 10.0)
+    assert at.choose({4: 10.0, 8: 9.0}, 4, 0.03) == (8, 9.0, 10.0)
+    assert at.main(["--rows", "1", "--ctx", "512"]) == 2         # no GPU here: refuses to guess
