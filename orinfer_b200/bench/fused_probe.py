@@ -48,13 +48,13 @@ def _weights(n, k, dev, seed):
     return codes, scale
 
 
-def main():
+def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--hidden", type=int, default=5120)
     ap.add_argument("--ffn", type=int, default=20480)
     ap.add_argument("--iters", type=int, default=10)
-    args = ap.parse_args()
+    args = ap.parse_args(argv)
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)

@@ -193,7 +193,7 @@ def gdn(args, dev):
                       "gbs": moved / t / 1e9, "frac_hbm": moved / t / bw, "peaks": tag}))
 
 
-def main():
+def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--graph", action="store_true",
                     help="time the launches inside one CUDA graph (no host launch overhead)")
@@ -236,7 +236,7 @@ def main():
     r.add_argument("--hv", type=int, default=32)
     r.add_argument("--d", type=int, default=128)
     r.add_argument("--iters", type=int, default=20)
-    args = ap.parse_args()
+    args = ap.parse_args(argv)
     global GRAPH
     GRAPH = args.graph
     dev = torch.device("cuda:0")

@@ -681,7 +681,8 @@ def build_parser() -> argparse.ArgumentParser:
             c.add_argument("--prompt", default=None)
             c.add_argument("--max-tokens", dest="max_tokens", default=None)
         c.set_defaults(fn=cmd_client, verb=verb)
-    bn = sub.add_parser("bench", help="HTTP benchmark clients against a running server")
+    bn = sub.add_parser("bench", help="HTTP benchmark clients against a running server, and "
+                                       "device-timed kernel probes")
     bn.add_argument("tool", choices=sorted(BENCH_TOOLS))
     bn.add_argument("tool_args", nargs=argparse.REMAINDER)
     bn.set_defaults(fn=cmd_bench)
@@ -784,7 +785,10 @@ def _client_run(a, url: str) -> int:
 
 
 BENCH_TOOLS = {"hf-reference": "hf_reference", "tokens": "token_bench", "quality": "quality", "concurrency": "concurrency", "agentic": "agentic", "startup": "startup",
-               "encoders": "encoders", "scenario": "workloads"}
+               "encoders": "encoders", "scenario": "workloads",
+               # device-timed probes of single kernels and of the fused tensor-parallel step
+               # (the latter under torch.distributed.run, one rank per GPU)
+               "kernel": "kernel_probe", "fused-step": "fused_probe"}
 
 
 def cmd_bench(a) -> int:
