@@ -335,3 +335,109 @@ def test_row_q4_projections_are_stored_as_nibbles_and_run_as_w8(tmp_path):
     assert len(generate_greedy(model, torch.arange(1, 20, dtype=torch.int32), 3)[0]) == 3
     with pytest.raises(convert.ConvertError):
         convert.convert(src, tmp_path / "bad", formats={"expert_format": "rq4"})
+
+
+# ------------------------------------------------------------------ draft calibration
+def _rounds(rng, n, width, true_t):
+    from orinfer_b200.quant import draft_calibration as dc
+    conf = rng.uniform(0.3, 0.99, size=(n, width))
+    step = dc.survival(conf, np.asarray(true_t))
+    cond = np.concatenate([step[:, :1], step[:, 1:] / step[:, :-1]], axis=1)
+    ok = rng.uniform(size=(n, width)) < cond
+    accepted = np.where(ok.all(1), width, (~ok).argmax(1)).astype(np.int64)
+    return conf, accepted
+
+
+def test_draft_calibration_recovers_position_temperatures():
+    from orinfer_b200.quant import draft_calibration as dc
+    rng = np.random.default_rng(13)
+    true_t = [0.5, 1.0, 2.0]
+    conf, accepted = _rounds(rng, 6000, 3, true_t)
+    temps = dc.fit(conf, accepted)
+    assert np.all(np.abs(np.log(temps / np.asarray(true_t))) < 0.35), temps
+    held_c, held_a = _rounds(rng, 3000, 3, true_t)
+    raw = dc.metrics(held_c, held_a, np.ones(3))
+    cal = dc.metrics(held_c, held_a, temps)
+    assert cal["cumulative_brier"] < raw["cumulative_brier"]
+    assert abs(cal["predicted_committed_per_round"] - cal["actual_committed_per_round"]) < 0.05
+    assert max(cal["prefix_ece"]) < 0.05
+    lab = dc.labels(np.array([0, 2, 3]), 3)
+    assert lab.tolist() == [[False] * 3, [True, True, False], [True] * 3]
+    with pytest.raises(ValueError):
+        dc.survival(np.array([[1.2]]), np.array([1.0]))
+    with pytest.raises(ValueError):
+        dc.labels(np.array([4]), 3)
+
+
+def test_draft_calibration_matches_the_reference():
+    ref = _ref("orinfer_build.quantization.speculative")
+    from orinfer_b200.quant import draft_calibration as dc
+    rng = np.random.default_rng(14)
+    conf, accepted = _rounds(rng, 400, 4, [0.7, 1.0, 1.5, 1.0])
+    temps = dc.fit(conf, accepted)
+    assert np.allclose(temps, ref.fit_temperatures(conf, accepted))
+    assert np.allclose(dc.survival(conf, temps), ref.calibrated_survival(conf, temps))
+    mine, theirs = dc.metrics(conf, accepted, temps), ref.calibration_metrics(conf, accepted, temps)
+    assert np.isclose(mine["cumulative_brier"], theirs["cumulative_brier"])
+    assert np.allclose(mine["prefix_ece"], theirs["prefix_ece"])
+
+
+# ------------------------------------------------------------------ precision screening
+def test_screening_separates_weight_and_activation_error():
+    from orinfer_b200.quant import screening as sc
+    rng = np.random.default_rng(15)
+    w = rng.standard_normal((48, 64)).astype(np.float32) * 0.05
+    mix = rng.standard_normal((64, 64)).astype(np.float32) * 0.3 + np.eye(64, dtype=np.float32)
+    train = rng.standard_normal((300, 64)).astype(np.float32) @ mix
+    hold = rng.standard_normal((200, 64)).astype(np.float32) @ mix
+    r8 = sc.screen_linear(w, train, hold, bits=8)
+    r4 = sc.screen_linear(w, train, hold, bits=4)
+    assert r8["holdout_nmse"] < 1e-3 < r4["holdout_nmse"] < 0.1
+    assert r8["activation_only_nmse"] == 0.0 and r8["weight_only_nmse"] == r8["holdout_nmse"]
+    joint = sc.screen_linear(w, train, hold, bits=8, quantize_activation=True)
+    assert joint["activation_only_nmse"] > 0 and joint["holdout_nmse"] >= joint["weight_only_nmse"]
+    assert r4["clip"] in (0.8, 0.9, 0.95, 1.0)
+    st = sc.statistics(train)
+    assert st["rows"] == 300 and 0 < st["max_channel_energy_fraction"] < 0.2
+    with pytest.raises(ValueError):
+        sc.quantize_rows(w, bits=5)
+
+
+def test_integer_refinement_and_scale_fit_lower_the_output_error():
+    from orinfer_b200.quant import screening as sc
+    rng = np.random.default_rng(16)
+    x = rng.standard_normal((256, 32)).astype(np.float32)
+    w = rng.standard_normal((12, 32)).astype(np.float32)
+    scales = (np.abs(w).max(1) / 7).astype(np.float32)
+    codes = np.clip(np.rint(w / scales[:, None]), -8, 7).astype(np.int8)
+    want = x @ w.T
+    weights = np.ones_like(want)
+    err = lambda q, s: float(np.square(want - (x @ q.astype(np.float32).T) * s).sum())
+    better = sc.refine_integer_codes(x, want, codes, scales, weights, steps=8)
+    assert better.min() >= -8 and better.max() <= 7
+    assert err(better, scales) <= err(codes, scales)
+    fitted = sc.fit_output_scales(x @ better.astype(np.float32).T, want, scales)
+    assert np.all(np.abs(fitted / scales - 1) <= 0.05 + 1e-6)
+    assert err(better, fitted) <= err(better, scales) + 1e-6
+    with pytest.raises(ValueError):
+        sc.refine_integer_codes(x, want, codes.astype(np.int32) * 3, scales, weights)
+
+
+def test_screening_matches_the_reference():
+    ref = _ref("orinfer_build.quantization.activation")
+    from orinfer_b200.quant import screening as sc
+    rng = np.random.default_rng(17)
+    x = rng.standard_normal((128, 32)).astype(np.float32)
+    w = rng.standard_normal((10, 32)).astype(np.float32)
+    assert np.array_equal(sc.quantize_rows(w, 4, 0.9), ref.quantize_rows(w, 4, 0.9))
+    a, b = sc.screen_linear(w, x[:64], x[64:], bits=4), ref.screen_linear(w, x[:64], x[64:], bits=4)
+    assert a == b
+    scales = (np.abs(w).max(1) / 7).astype(np.float32)
+    codes = np.clip(np.rint(w / scales[:, None]), -8, 7).astype(np.int8)
+    want = x @ w.T
+    weights = rng.uniform(0.5, 1.5, size=want.shape).astype(np.float32)
+    assert np.array_equal(sc.refine_integer_codes(x, want, codes, scales, weights),
+                          ref.refine_integer_codes(x, want, codes, scales, weights))
+    prod = x @ codes.astype(np.float32).T
+    assert np.allclose(sc.fit_output_scales(prod, want, scales, weights),
+                       ref.fit_output_scales(prod, want, scales, weights))
