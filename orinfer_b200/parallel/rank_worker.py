@@ -59,9 +59,16 @@ def build_engine(spec: dict, weights, channel=None):
     from ..engine.engine import Engine
     load = LoadOptions(**{**spec["load"], "cuda_graph": GraphMode(spec["load"]["cuda_graph"])})
     sched = SchedulerOptions(**{**spec["sched"], "policy": Policy(spec["sched"]["policy"])})
-    # what multi-rank serving does not carry yet is switched off on every rank alike
-    load = dataclasses.replace(load, prefix_cache_bytes=0, kv_offload_bytes=0, mtp_drafts=0,
-                               prompt_lookup=False)
+    # What multi-rank serving does not carry yet is switched off on every rank alike: host KV
+    # offload, speculation and the recurrent-state snapshots of hybrid models move device data
+    # that the published command stream does not describe.  The prefix cache of an
+    # attention-only model is host bookkeeping plus page-table rows, which are published, so
+    # the leader keeps it; followers take no decisions and need none.
+    leader = channel is not None
+    recurrent = weights.config.arch == "hybrid"
+    load = dataclasses.replace(
+        load, prefix_cache_bytes=load.prefix_cache_bytes if leader and not recurrent else 0,
+        kv_offload_bytes=0, mtp_drafts=0, prompt_lookup=False)
     return Engine(weights, load=load, sched=sched, max_context=spec.get("max_context"),
                   kv_pages=spec.get("kv_pages"), max_rows=spec.get("max_rows"), channel=channel)
 

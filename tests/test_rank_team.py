@@ -30,6 +30,26 @@ def test_leader_and_follower_generate_like_spmd_ranks():
     assert all(p.returncode == 0 for p in team.procs)
 
 
+def test_leader_keeps_the_prefix_cache_and_followers_follow_its_page_rows():
+    from orinfer_b200.parallel.rank_worker import leader_engine
+    spec = dict(SPEC, load=dict(SPEC["load"], prefix_cache_bytes=64 << 20))
+    engine, team = leader_engine(spec, deadline_s=20.0)
+    try:
+        assert engine.prefix is not None
+        shared = [(11 * i) % 997 + 1 for i in range(300)]           # two full pages and a bit
+        first = engine.generate([shared + [5, 6, 7]], max_new=4)
+        reqs = [engine.submit(shared + [8, 9], 4), engine.submit(shared + [5, 6, 7], 4)]
+        while any(not r.finished for r in reqs):
+            engine.step()
+        team.channel.sync(20.0)
+        assert all(r.cached_tokens >= 256 for r in reqs)            # both reuse the cached pages
+        assert reqs[1].generated == first[0]                        # and the follower kept in step
+        assert team.channel.failure is None
+    finally:
+        team.close(engine)
+    assert all(p.returncode == 0 for p in team.procs)
+
+
 def test_follower_that_stops_replying_fails_the_leader_closed():
     from orinfer_b200.parallel.rank_channel import RankFailure
     from orinfer_b200.parallel.rank_worker import leader_engine
