@@ -15,6 +15,7 @@
 // integer_vq (kernels/cuda/model/integer_vq.py:263) and int8_projection
 // (kernels/cuda/model/int8_projection.py:15).
 #include <cuda.h>
+#include <mutex>
 
 #include "api.h"
 #include "common.cuh"
@@ -1575,6 +1576,7 @@ struct Variant {
 constexpr int MAX_VARIANTS = 512;
 static Variant g_variants[MAX_VARIANTS];
 static int g_variant_count = 0;
+static std::mutex g_variant_mutex;            // the table may change while other threads launch
 
 inline bool variant_valid(const Variant& v) {
   if (v.fmt < 0 || v.fmt > 2 || v.m_lo < 1 || v.m_hi < v.m_lo || v.n < 8 || v.k < BK) return false;
@@ -1592,6 +1594,7 @@ inline Plan make_plan(int fmt, int M, int N, int K, int out_f32, bool fused) {
   Plan p{};
   p.mt = M > 2 * BM ? 4 : (M > BM ? 2 : 1);
   if (!out_f32) {
+    std::lock_guard<std::mutex> lock(g_variant_mutex);
     for (int i = 0; i < g_variant_count; ++i) {
       const Variant& v = g_variants[i];
       if (v.fmt == fmt && v.n == N && v.k == K && M >= v.m_lo && M <= v.m_hi) {
@@ -1770,19 +1773,23 @@ extern "C" int orinfer_qgemm_launches(int M, int N, int K, int out_f32, int forc
 
 // Tuned launch variants: rows m_lo..m_hi of projection (fmt, N, K) run with M-tile factor mt
 // (1, 2, 4), weight-tile width nb (128, 64, 32) and `splits` K splits.  Earlier entries win.
-// Not thread-safe against concurrent launches: set the table before serving.
+// The table is guarded by a mutex: launches on other threads read a consistent table.
 extern "C" int orinfer_qgemm_set_variant(int fmt, int m_lo, int m_hi, int n, int k, int mt,
                                          int nb, int splits) {
   const tc::Variant v{fmt, m_lo, m_hi, n, k, mt, nb, splits};
   if (!tc::variant_valid(v)) return -1;
+  std::lock_guard<std::mutex> lock(tc::g_variant_mutex);
   if (tc::g_variant_count >= tc::MAX_VARIANTS) return -2;
   tc::g_variants[tc::g_variant_count++] = v;
   return 0;
 }
 
-extern "C" void orinfer_qgemm_clear_variants() { tc::g_variant_count = 0; }
+extern "C" void orinfer_qgemm_clear_variants() {
+  std::lock_guard<std::mutex> lock(tc::g_variant_mutex);
+  tc::g_variant_count = 0;
+}
 
-// 0 = persistent kernel (default), 1 = one tile per CTA; for comparisons and tests.
+// 0 = persistent kernel, 1 = one tile per CTA (default), 2 = CTA pairs; for comparisons and tests.
 // Timing experiments of the one-tile kernel: bit 0 no MMAs, bit 1 no operand copies, bit 2
 // no lattice decode.  Outputs are meaningless while a bit is set.
 extern "C" int orinfer_qgemm_set_probe(int bits) {
