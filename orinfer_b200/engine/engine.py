@@ -462,17 +462,17 @@ class Engine:
             # move the least useful pages to pinned host memory; their nodes stay indexed
             if self.host_kv.available < short:
                 for h in self.prefix.drop_host(short - self.host_kv.available):
-                    self.host_kv.free(h)
+                    self._host_kv("free", h)
             victims = self.prefix.evict(min(short, self.host_kv.available), to_host=True)
             for node, page in victims:
                 # a node that was offloaded before and re-adopted a device page still owns
                 # its old host slot: give it back before the new copy takes one
                 stale = self.prefix.host_handle(node)
                 if stale >= 0:
-                    self.host_kv.free(stale)
-                self.prefix.set_host(node, self.host_kv.save(page))
+                    self._host_kv("free", stale)
+                self.prefix.set_host(node, self._host_kv("save", page))
             if victims:
-                self.host_kv.sync()                 # pages are reused right after this
+                self._host_kv("sync")               # pages are reused right after this
             self.pool.release([p for _, p in victims])
             self.stats.evicted_pages += len(victims)
             self.stats.offloaded_pages += len(victims)
@@ -482,6 +482,18 @@ class Engine:
         victims = self.prefix.evict(short, to_host=False)
         self.pool.release([p for _, p in victims])
         self.stats.evicted_pages += len(victims)
+
+    def _host_kv(self, op: str, *args):
+        """One operation of the host KV tier, published first: every rank moves its own shard
+        of the page between its own device pool and its own host slab.  The stores hand out
+        slots in the same order on every rank, so a handle means the same slot everywhere;
+        ``save`` carries the leader's handle so that a follower can check that."""
+        if op == "save":
+            handle = self.host_kv.save(*args)
+            self._publish("host_kv", (op, *args, handle))
+            return handle
+        self._publish("host_kv", (op, *args))
+        return getattr(self.host_kv, op)(*args)
 
     def _restore_host_pages(self, node_ids: List[int], pages: List[int]) -> int:
         """Brings the host-resident nodes of a matched prefix back into device pages, in
@@ -499,12 +511,12 @@ class Engine:
             if handle < 0:
                 return i
             new = self.pool.take(1)[0]
-            self.host_kv.load(handle, new)
+            self._host_kv("load", handle, new)
             if not self.prefix.restore(node, new):
                 self.pool.release([new])
                 return i
             self.prefix.set_host(node, -1)
-            self.host_kv.free(handle)
+            self._host_kv("free", handle)
             pages[i] = new
             self.stats.restored_pages += 1
         return len(pages)
@@ -841,6 +853,16 @@ class Engine:
             self._exec_direct(self._build_packet(payload), payload, False)
         elif op == "decode":
             self._exec_decode(*payload)
+        elif op == "host_kv":
+            kind, *args = payload
+            if self.host_kv is None:
+                raise ValueError("host KV command without a host KV store on this rank")
+            if kind == "save":
+                page, expected = args
+                if self.host_kv.save(page) != expected:
+                    raise ValueError("host KV slots of this rank are out of step with the leader")
+            else:
+                getattr(self.host_kv, kind)(*args)
         elif op == "sharded":
             rows, options, uniforms = payload
             self.runner.sample_sharded(rows, options, uniforms)

@@ -59,18 +59,25 @@ def build_engine(spec: dict, weights, channel=None):
     from ..engine.engine import Engine
     load = LoadOptions(**{**spec["load"], "cuda_graph": GraphMode(spec["load"]["cuda_graph"])})
     sched = SchedulerOptions(**{**spec["sched"], "policy": Policy(spec["sched"]["policy"])})
-    # What multi-rank serving does not carry yet is switched off on every rank alike: host KV
-    # offload, speculation and the recurrent-state snapshots of hybrid models move device data
-    # that the published command stream does not describe.  The prefix cache of an
-    # attention-only model is host bookkeeping plus page-table rows, which are published, so
-    # the leader keeps it; followers take no decisions and need none.
+    # What multi-rank serving does not carry yet is switched off on every rank alike:
+    # speculation and the recurrent-state snapshots of hybrid models move device data that the
+    # published command stream does not describe.  The prefix cache of an attention-only model
+    # is host bookkeeping plus page-table rows, which are published, so the leader keeps it;
+    # followers take no decisions and need none.  Its host tier is a published command per
+    # page move, carried out by every rank on its own shard.
     leader = channel is not None
     recurrent = weights.config.arch == "hybrid"
+    offload = 0 if recurrent else load.kv_offload_bytes
     load = dataclasses.replace(
         load, prefix_cache_bytes=load.prefix_cache_bytes if leader and not recurrent else 0,
-        kv_offload_bytes=0, mtp_drafts=0, prompt_lookup=False)
-    return Engine(weights, load=load, sched=sched, max_context=spec.get("max_context"),
-                  kv_pages=spec.get("kv_pages"), max_rows=spec.get("max_rows"), channel=channel)
+        kv_offload_bytes=offload if leader else 0, mtp_drafts=0, prompt_lookup=False)
+    engine = Engine(weights, load=load, sched=sched, max_context=spec.get("max_context"),
+                    kv_pages=spec.get("kv_pages"), max_rows=spec.get("max_rows"),
+                    channel=channel)
+    if not leader and offload > 0 and spec["load"].get("prefix_cache_bytes", 0) > 0:
+        from ..engine.offload import HostKvStore
+        engine.host_kv = HostKvStore(engine.kv, offload)
+    return engine
 
 
 def follower_main(spec: dict) -> int:

@@ -6,7 +6,7 @@ import time
 import pytest
 
 SPEC = dict(
-    world=2, device="cpu", preset="tiny", group_timeout_s=20.0, kv_pages=32, max_context=512,
+    world=2, device="cpu", preset="tiny", group_timeout_s=120.0, kv_pages=32, max_context=512,
     max_rows=256,
     load=dict(cuda_graph="off", prefix_cache_bytes=0, tp=2),
     sched=dict(policy="latency", max_active=4, prefill_chunk=128),
@@ -15,11 +15,11 @@ SPEC = dict(
 
 def test_leader_and_follower_generate_like_spmd_ranks():
     from orinfer_b200.parallel.rank_worker import leader_engine
-    engine, team = leader_engine(dict(SPEC), deadline_s=20.0)
+    engine, team = leader_engine(dict(SPEC), deadline_s=90.0)
     try:
         prompts = [[(7 * i + j) % 1000 + 1 for i in range(40)] for j in range(3)]
         out = engine.generate(prompts, max_new=6)
-        team.channel.sync(20.0)
+        team.channel.sync(90.0)
         assert all(len(o) == 6 for o in out)
         # the same prompts again: same tokens (the follower's KV / page rows stayed in step)
         again = engine.generate(prompts, max_new=6)
@@ -33,7 +33,7 @@ def test_leader_and_follower_generate_like_spmd_ranks():
 def test_leader_keeps_the_prefix_cache_and_followers_follow_its_page_rows():
     from orinfer_b200.parallel.rank_worker import leader_engine
     spec = dict(SPEC, load=dict(SPEC["load"], prefix_cache_bytes=64 << 20))
-    engine, team = leader_engine(spec, deadline_s=20.0)
+    engine, team = leader_engine(spec, deadline_s=90.0)
     try:
         assert engine.prefix is not None
         shared = [(11 * i) % 997 + 1 for i in range(300)]           # two full pages and a bit
@@ -41,9 +41,34 @@ def test_leader_keeps_the_prefix_cache_and_followers_follow_its_page_rows():
         reqs = [engine.submit(shared + [8, 9], 4), engine.submit(shared + [5, 6, 7], 4)]
         while any(not r.finished for r in reqs):
             engine.step()
-        team.channel.sync(20.0)
+        team.channel.sync(90.0)
         assert all(r.cached_tokens >= 256 for r in reqs)            # both reuse the cached pages
         assert reqs[1].generated == first[0]                        # and the follower kept in step
+        assert team.channel.failure is None
+    finally:
+        team.close(engine)
+    assert all(p.returncode == 0 for p in team.procs)
+
+
+def test_host_kv_tier_moves_pages_on_every_rank():
+    """Page pressure sends cached prefixes to the host tier and a later hit brings them back:
+    every rank saves and restores its own shard of the page on the leader's published commands,
+    and the restored KV gives the same tokens."""
+    from orinfer_b200.parallel.rank_worker import leader_engine
+    spec = dict(SPEC, kv_pages=4, max_context=256,
+                load=dict(SPEC["load"], prefix_cache_bytes=64 << 20, kv_offload_bytes=64 << 20),
+                sched=dict(SPEC["sched"], max_active=1, prefill_chunk=256))
+    engine, team = leader_engine(spec, deadline_s=90.0)
+    try:
+        base = [[(13 * i + 7 * j) % 997 + 1 for i in range(130)] for j in range(3)]
+        first = [engine.generate([p], max_new=4)[0] for p in base]   # 3 usable pages: must evict
+        assert engine.stats.offloaded_pages >= 1
+        r = engine.submit(base[0], 4)
+        while not r.finished:
+            engine.step()
+        team.channel.sync(90.0)
+        assert engine.stats.restored_pages >= 1 and r.cached_tokens == 128
+        assert r.generated == first[0]
         assert team.channel.failure is None
     finally:
         team.close(engine)
