@@ -853,6 +853,11 @@ class Engine:
             self._exec_direct(self._build_packet(payload), payload, False)
         elif op == "decode":
             self._exec_decode(*payload)
+        elif op == "verify":
+            ids, rows_req, pos, max_kv, need = payload
+            packet = Packet(self._upload("ids", ids), self._upload("req", rows_req),
+                            self._upload("pos", pos), self.page_table_dev, len(ids), max_kv)
+            self.runner.greedy(packet, need_logits=need)
         elif op == "host_kv":
             kind, *args = payload
             if self.host_kv is None:
@@ -869,6 +874,18 @@ class Engine:
         else:
             raise ValueError(f"unknown device command {op!r}")
         self._status_enqueue()
+
+    def _verify_packet(self, ids, rows_req, pos, max_kv: int, need: bool) -> Packet:
+        """Packet of a verification round (every row's token is read back).  With follower
+        ranks the round is published first; they run the same packet through ``apply`` and
+        take part in its collectives.  Recurrent models add their segment table afterwards and
+        are not served by several ranks with speculation."""
+        if self.channel is not None:
+            if self.recurrent:
+                raise ValueError("speculation on a recurrent model is not published to ranks")
+            self._publish("verify", (list(ids), list(rows_req), list(pos), int(max_kv), bool(need)))
+        return Packet(self._upload("ids", ids), self._upload("req", rows_req),
+                      self._upload("pos", pos), self.page_table_dev, len(ids), max_kv)
 
     def _build_packet(self, spec: dict) -> Packet:
         rows = len(spec["ids"])

@@ -192,9 +192,8 @@ class Speculator:
             rows_req += [r.slot] * len(toks)
             pos += list(range(r.offset, r.offset + len(toks)))
             max_kv = max(max_kv, r.offset + len(toks))
-        from ..models.runner import Packet
-        packet = Packet(eng._upload("ids", ids), eng._upload("req", rows_req),
-                        eng._upload("pos", pos), eng.page_table_dev, len(ids), max_kv)
+        need = any(not eng._plain(r) for r, _ in plans)
+        packet = eng._verify_packet(ids, rows_req, pos, max_kv, need)
         if eng.recurrent:
             # recurrent layers must only keep the accepted prefix of each request's rows
             segs, first, start = [], [], 0
@@ -207,7 +206,6 @@ class Speculator:
             packet.row_first = eng._upload("first", first)
             packet.n_segments = len(plans)
             packet.tentative = True
-        need = any(not eng._plain(r) for r, _ in plans)
         tok_dev, logits = eng.runner.greedy(packet, need_logits=need)
         eng._status_enqueue()
         tokens = tok_dev.cpu().tolist()

@@ -59,9 +59,10 @@ def build_engine(spec: dict, weights, channel=None):
     from ..engine.engine import Engine
     load = LoadOptions(**{**spec["load"], "cuda_graph": GraphMode(spec["load"]["cuda_graph"])})
     sched = SchedulerOptions(**{**spec["sched"], "policy": Policy(spec["sched"]["policy"])})
-    # What multi-rank serving does not carry yet is switched off on every rank alike:
-    # speculation and the recurrent-state snapshots of hybrid models move device data that the
-    # published command stream does not describe.  The prefix cache of an attention-only model
+    # What multi-rank serving does not carry yet is switched off on every rank alike: draft
+    # heads and the recurrent-state snapshots of hybrid models move device data that the
+    # published command stream does not describe.  Prompt-lookup speculation only adds
+    # verification packets, which are published like any other packet.  The prefix cache of an attention-only model
     # is host bookkeeping plus page-table rows, which are published, so the leader keeps it;
     # followers take no decisions and need none.  Its host tier is a published command per
     # page move, carried out by every rank on its own shard.
@@ -70,7 +71,10 @@ def build_engine(spec: dict, weights, channel=None):
     offload = 0 if recurrent else load.kv_offload_bytes
     load = dataclasses.replace(
         load, prefix_cache_bytes=load.prefix_cache_bytes if leader and not recurrent else 0,
-        kv_offload_bytes=offload if leader else 0, mtp_drafts=0, prompt_lookup=False)
+        kv_offload_bytes=offload if leader else 0,
+        # the draft budget stays (prompt lookup uses it); sharded weights carry no draft head
+        mtp_drafts=load.mtp_drafts if leader and not recurrent else 0,
+        prompt_lookup=load.prompt_lookup and leader and not recurrent)
     engine = Engine(weights, load=load, sched=sched, max_context=spec.get("max_context"),
                     kv_pages=spec.get("kv_pages"), max_rows=spec.get("max_rows"),
                     channel=channel)

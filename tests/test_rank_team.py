@@ -50,6 +50,34 @@ def test_leader_keeps_the_prefix_cache_and_followers_follow_its_page_rows():
     assert all(p.returncode == 0 for p in team.procs)
 
 
+def test_prompt_lookup_speculation_publishes_its_verification_packets(monkeypatch):
+    """Drafts copied from earlier n-grams are verified in packets that the followers run too;
+    the greedy text is what plain decoding gives."""
+    from orinfer_b200.parallel.rank_worker import leader_engine
+    monkeypatch.setenv("ORINFER_SINGLE_MTP_POLICY", "fixed3")
+    prompt = [3, 1, 4, 1, 5, 9, 2, 6] * 6
+    plain_engine, plain_team = leader_engine(dict(SPEC), deadline_s=90.0)
+    try:
+        plain = plain_engine.generate([prompt], max_new=16)[0]
+    finally:
+        plain_team.close(plain_engine)
+    spec = dict(SPEC, load=dict(SPEC["load"], prompt_lookup=True, mtp_drafts=3))
+    engine, team = leader_engine(spec, deadline_s=90.0)
+    try:
+        assert engine.spec.enabled and not engine.runner_has_mtp()
+        # an oracle draft source makes every round propose (and accept) something
+        engine.spec.drafts_for = lambda r, c: plain[len(r.generated):len(r.generated) + c]
+        out = engine.generate([prompt], max_new=16)[0]
+        team.channel.sync(90.0)
+        st = engine.spec.statistics()
+        assert out == plain
+        assert st["rounds"] > 0 and st["accepted_draft_tokens"] > 0
+        assert team.channel.failure is None
+    finally:
+        team.close(engine)
+    assert all(p.returncode == 0 for p in team.procs)
+
+
 def test_host_kv_tier_moves_pages_on_every_rank():
     """Page pressure sends cached prefixes to the host tier and a later hit brings them back:
     every rank saves and restores its own shard of the page on the leader's published commands,
