@@ -138,6 +138,64 @@ class GdnPolicy:
                                 "gated-delta-rule layers")
 
 
+# ------------------------------------------------------------------ speculation contract
+@dataclass(frozen=True)
+class MtpSpec:
+    """What speculative decoding may do for a model.
+
+    ``verification_widths``: row counts of one request's verification (verified token plus
+    drafts) that the engine may choose from, ascending; ``batch_verification_tokens``: most
+    rows of a verification packet over all requests; ``batch_draft_profiles``: request counts
+    the draft head runs in one batched pass, ascending (a batch is padded up to the next
+    profile and split when it exceeds the last); ``commit_always``: recurrent layers need a
+    commit pass even when every draft was accepted; ``hidden_ring``: the draft head consumes
+    the target's hidden rows of every prefill chunk before the ring is reused.
+    (crates/orinfer-model-sdk/src/mtp.rs:20-70,280-300 of the reference.)"""
+    max_drafts: int = 3
+    verification_widths: Tuple[int, ...] = (2, 3, 4)
+    batch_verification_tokens: int = 512
+    batch_draft_profiles: Tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64, 128)
+    commit_always: bool = False
+    hidden_ring: bool = True
+
+    def __post_init__(self):
+        if not 0 <= self.max_drafts <= 31:
+            raise ContractError("max_drafts must be within 0..31")
+        w = self.verification_widths
+        if any(a >= b for a, b in zip(w, w[1:])) or any(not 2 <= x <= 32 for x in w):
+            raise ContractError("verification widths must ascend within 2..32")
+        if w and w[-1] > self.max_drafts + 1 and self.max_drafts:
+            raise ContractError("a verification width exceeds max_drafts + 1")
+        p = self.batch_draft_profiles
+        if not p or p[0] < 1 or any(a >= b for a, b in zip(p, p[1:])):
+            raise ContractError("batch draft profiles must be positive and strictly ascending")
+        if self.batch_verification_tokens < (w[-1] if w else 1):
+            raise ContractError("batch_verification_tokens cannot hold one request's round")
+
+    @staticmethod
+    def for_config(cfg, max_drafts: int, max_active: int, max_rows: int) -> "MtpSpec":
+        """The contract the engine derives for a geometry and its serving options."""
+        drafts = max(0, min(int(max_drafts), 31))
+        widths = tuple(range(2, drafts + 2))
+        profiles = tuple(b for b in (1, 2, 4, 8, 16, 32, 64, 128) if b < max_active) + (max_active,)
+        return MtpSpec(max_drafts=drafts, verification_widths=widths,
+                       batch_verification_tokens=max(max_rows, widths[-1] if widths else 1),
+                       batch_draft_profiles=profiles,
+                       commit_always=getattr(cfg, "arch", "") == "hybrid")
+
+    def draft_capacity(self, requests: int) -> int:
+        """Profile that holds ``requests`` draft rows, or the largest one when none does (the
+        caller then drafts in several passes)."""
+        for p in self.batch_draft_profiles:
+            if p >= requests:
+                return p
+        return self.batch_draft_profiles[-1]
+
+    def width_allowed(self, width: int, requests: int) -> bool:
+        return (width in self.verification_widths
+                and width * requests <= self.batch_verification_tokens)
+
+
 # ------------------------------------------------------------------ pooled-encoder specs
 @dataclass(frozen=True)
 class EmbeddingSpec:

@@ -35,6 +35,10 @@ class Speculator:
         if max_drafts is None:
             self.max_drafts = 3                        # "auto": up to three drafts
         self.prompt_lookup = prompt_lookup
+        # the contract: which widths and batch shapes speculation may use for this model
+        from ..contracts import MtpSpec
+        self.contract = MtpSpec.for_config(engine.cfg, self.max_drafts, engine.sched.max_active,
+                                           engine.max_rows)
         self.lookups: Dict[int, P.PromptLookup] = {}
         self.backlog: Dict[int, list] = {}            # rid -> [(first pos, hidden rows)]
         self.acceptance = P.Acceptance()
@@ -134,6 +138,12 @@ class Speculator:
         live = [r for r in reqs if self.backlog.get(r.rid)]
         if not live or count <= 0:
             return {}
+        cap = self.contract.draft_capacity(len(live))
+        if len(live) > cap:                              # more requests than the largest profile
+            out: Dict[int, List[int]] = {}
+            for lo in range(0, len(live), cap):
+                out.update(self.mtp_drafts(live[lo:lo + cap], count))
+            return out
         toks, hids, rreq, rpos, last = [], [], [], [], []
         for r in live:
             hist = r.history

@@ -78,3 +78,25 @@ def test_registry_guards_the_loader(tmp_path):
         path.write_text(json.dumps(dict(desc, **{key: value})))
         with pytest.raises(CheckpointError, match=why):
             load_model(tmp_path)
+
+
+def test_mtp_spec_contract():
+    from orinfer_b200.config import PRESETS
+    from orinfer_b200.contracts import ContractError, MtpSpec
+    spec = MtpSpec.for_config(PRESETS["tiny"], 3, 32, 4128)
+    assert spec.verification_widths == (2, 3, 4) and spec.max_drafts == 3
+    assert spec.batch_draft_profiles == (1, 2, 4, 8, 16, 32) and not spec.commit_always
+    assert spec.draft_capacity(3) == 4 and spec.draft_capacity(33) == 32
+    assert spec.width_allowed(4, 100) and not spec.width_allowed(5, 1)
+    assert not spec.width_allowed(4, 2000)                      # 8000 rows exceed the packet bound
+    assert MtpSpec.for_config(PRESETS["tiny-hybrid"], 2, 4, 256).commit_always
+    off = MtpSpec.for_config(PRESETS["tiny"], 0, 8, 256)
+    assert off.verification_widths == () and off.max_drafts == 0
+    with pytest.raises(ContractError):
+        MtpSpec(verification_widths=(3, 2))
+    with pytest.raises(ContractError):
+        MtpSpec(batch_draft_profiles=(4, 4))
+    with pytest.raises(ContractError):
+        MtpSpec(max_drafts=2, verification_widths=(2, 3, 4))
+    with pytest.raises(ContractError):
+        MtpSpec(batch_verification_tokens=2)

@@ -181,6 +181,12 @@ def test_mtp_head_speculation_preserves_greedy_output():
         eng = _engine(w, load=LoadOptions(mtp_drafts=2))
         assert eng.runner_has_mtp() and eng.spec.enabled
         out = eng.generate(prompts, max_new=10)
+        # a contract whose largest draft profile is one request: the draft head runs once per
+        # request instead of once per batch, with the same result
+        split = _engine(w, load=LoadOptions(mtp_drafts=2))
+        split.spec.contract = dataclasses.replace(split.spec.contract, batch_draft_profiles=(1,))
+        assert split.generate(prompts, max_new=10) == plain
+        assert split.spec.statistics()["rounds"] > 0
     finally:
         del os.environ["ORINFER_SINGLE_MTP_POLICY"]
     assert out == plain
