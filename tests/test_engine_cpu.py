@@ -231,3 +231,24 @@ def test_layered_prefill_lets_decoders_step_inside_a_long_prompt(weights):
     while eng.has_work():
         eng.step()
     assert [a.generated, b.generated] == want
+
+
+def test_follower_commands_check_what_they_can(weights):
+    """``Engine.apply`` is what a follower rank runs: a host-tier save must land in the slot
+    the leader announced, a host-tier command needs a store, unknown commands are refused."""
+    from orinfer_b200.engine.offload import HostKvStore
+    eng = _engine(weights, load=LoadOptions(prefix_cache_bytes=0))
+    with pytest.raises(ValueError, match="without a host KV store"):
+        eng.apply("host_kv", ("save", 1, 0))
+    eng.host_kv = HostKvStore(eng.kv, 8 << 20)
+    first = eng.host_kv._free[-1]
+    eng.apply("host_kv", ("save", 1, first))                  # the slot the store hands out next
+    with pytest.raises(ValueError, match="out of step"):
+        eng.apply("host_kv", ("save", 2, first))              # the leader says an occupied slot
+    eng.apply("host_kv", ("load", first, 3))
+    eng.apply("host_kv", ("free", first))
+    eng.apply("host_kv", ("sync",))
+    eng.apply("page_row", (0, [1, 2]))
+    eng.apply("verify", ([5, 6, 7], [0, 0, 0], [0, 1, 2], 3, False))      # runs, returns nothing
+    with pytest.raises(ValueError, match="unknown device command"):
+        eng.apply("reboot", None)
