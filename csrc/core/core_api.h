@@ -115,6 +115,7 @@ int orinfer_prefix_match(void* handle, const uint32_t* tokens, int n, const uint
 int orinfer_prefix_insert(void* handle, const uint32_t* tokens, int n, const uint64_t* media,
                           const int32_t* pages, int n_pages, int32_t* adopted, int32_t* node_ids);
 void orinfer_prefix_release(void* handle, const int32_t* node_ids, int n);
+void orinfer_prefix_abandon(void* handle, const int32_t* node_ids, int n);
 int orinfer_prefix_evict(void* handle, int want, int to_host, int32_t* node_ids, int32_t* pages);
 int orinfer_prefix_set_host(void* handle, int32_t node_id, int64_t host_handle);
 int64_t orinfer_prefix_host_handle(void* handle, int32_t node_id);

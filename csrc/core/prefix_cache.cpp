@@ -182,6 +182,19 @@ void orinfer_prefix_release(void* handle, const int32_t* node_ids, int n) {
   }
 }
 
+// Release of a match that was never used (the request could not be admitted and will match
+// again on its next attempt): the users go, and so do the hits the match counted, so that a
+// request waiting for pages does not inflate the utility of its prefix with every retry.
+void orinfer_prefix_abandon(void* handle, const int32_t* node_ids, int n) {
+  Cache* c = static_cast<Cache*>(handle);
+  for (int i = 0; i < n; ++i) {
+    auto it = c->nodes.find(node_ids[i]);
+    if (it == c->nodes.end()) continue;
+    if (it->second->users > 0) --it->second->users;
+    if (it->second->hits > 0) --it->second->hits;
+  }
+}
+
 // Choose up to `want` evictable device pages (leaf-first, no users), lowest utility
 // first.  With to_host != 0 the nodes stay indexed as host-resident (the caller copies
 // the page out and later reports the host handle); otherwise they are removed.

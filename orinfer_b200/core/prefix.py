@@ -43,6 +43,7 @@ class RadixPrefixCache:
                                             POINTER(c_int32), c_int, POINTER(c_int32),
                                             POINTER(c_int32)]
         l.orinfer_prefix_release.argtypes = [c_void_p, POINTER(c_int32), c_int]
+        l.orinfer_prefix_abandon.argtypes = [c_void_p, POINTER(c_int32), c_int]
         l.orinfer_prefix_evict.argtypes = [c_void_p, c_int, c_int, POINTER(c_int32),
                                            POINTER(c_int32)]
         l.orinfer_prefix_set_host.argtypes = [c_void_p, c_int32, c_int64]
@@ -100,6 +101,14 @@ class RadixPrefixCache:
             return
         a = np.ascontiguousarray(node_ids, dtype=np.int32)
         self._l.orinfer_prefix_release(self._h, a.ctypes.data_as(POINTER(c_int32)), len(a))
+
+    def abandon(self, node_ids: Sequence[int]) -> None:
+        """Release of a match that was not used (deferred admission): also takes back the
+        hits it counted."""
+        if not node_ids:
+            return
+        a = np.ascontiguousarray(node_ids, dtype=np.int32)
+        self._l.orinfer_prefix_abandon(self._h, a.ctypes.data_as(POINTER(c_int32)), len(a))
 
     def evict(self, want: int, to_host: bool = False) -> List[Tuple[int, int]]:
         ids = np.empty(max(want, 1), np.int32)

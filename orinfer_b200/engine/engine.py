@@ -148,6 +148,11 @@ class Engine:
         self.recurrent = self.cfg.arch == "hybrid"
         self._snapshots: "collections.OrderedDict[int, tuple]" = collections.OrderedDict()
         self._snapshot_bytes = 0
+        # the copies themselves: handle -> this rank's tensors (every rank of a multi-rank
+        # engine keeps its own shard under the handle the leader chose)
+        self._state_copies: Dict[int, tuple] = {}
+        self._state_handles = 0
+        self._tentative: Optional[Packet] = None     # verification packet awaiting its commit
         self.max_context = max_context or min(self.cfg.max_context, 32768)
         self.max_pages_per_req = (self.max_context + PAGE_TOKENS - 1) // PAGE_TOKENS
         self.max_rows = max_rows or max(self.sched.prefill_chunk + self.sched.max_active, 256)
@@ -551,7 +556,7 @@ class Engine:
                 self._reclaim(need)
             if not self.free_slots or need > self.pool.available:
                 if node_ids:
-                    self.prefix.release(node_ids)
+                    self.prefix.abandon(node_ids)        # the retry will match (and count) again
                 self.stats.deferred_admissions += 1
                 break
             self.waiting.popleft()
@@ -561,7 +566,7 @@ class Engine:
             req.slot = self.free_slots.pop()
             req.offset = req.cached_tokens = len(pages) * PAGE_TOKENS
             if self.recurrent and pages:
-                self.runner.gdn_restore(req.slot, snapshot, self.page_table_dev.shape[0])
+                self._state_copy("restore", snapshot, req.slot)
                 self.stats.restored_snapshots += 1
             req.phase = Phase.PREFILL
             self._prefix_nodes[req.rid] = node_ids
@@ -592,12 +597,22 @@ class Engine:
                 adopted, ids = self.prefix.insert(
                     toks, req.pages[:len(toks) // PAGE_TOKENS],
                     media=req.page_media(PAGE_TOKENS, len(toks) // PAGE_TOKENS + 1))
-                for pg, took in zip(req.pages, adopted):
+                for pg, took, node in zip(req.pages, adopted, ids):
                     if took:
                         self.pool.share(pg)
-                for at, snap in req.snapshots.items():
+                        # a host-resident node that adopts a fresh device page needs its host
+                        # copy no longer: give the slot back now (an eviction that removes
+                        # the node later would lose it)
+                        stale = self.prefix.host_handle(node) if self.host_kv is not None else -1
+                        if stale >= 0:
+                            self.prefix.set_host(node, -1)
+                            self._host_kv("free", stale)
+                for at in sorted(req.snapshots):
                     if at // PAGE_TOKENS <= len(ids):
-                        self._store_snapshot(ids[at // PAGE_TOKENS - 1], toks[:at], snap)
+                        self._store_snapshot(ids[at // PAGE_TOKENS - 1], toks[:at],
+                                             req.snapshots.pop(at))
+            for handle in req.snapshots.values():            # endpoints that were not indexed
+                self._state_copy("drop", handle)
             req.snapshots = {}
             if self.prefix is not None:
                 self.prefix.release(self._prefix_nodes.pop(req.rid, []))
@@ -677,7 +692,26 @@ class Engine:
         for r, _n in chunks:
             if r.cache_prompt and r.slot >= 0 and r.offset in self._endpoints(len(r.prompt)) \
                     and r.offset > r.cached_tokens:
-                r.snapshots[r.offset] = self.runner.gdn_snapshot(r.slot)
+                self._state_handles += 1
+                r.snapshots[r.offset] = self._state_copy("take", self._state_handles, r.slot)
+
+    def _state_copy(self, op: str, handle: int, slot: int = -1) -> int:
+        """Recurrent-state copies live on each rank under a handle that the leader chose:
+        ``take`` copies the state of one request slot (every recurrent layer), ``restore``
+        writes a copy back into a slot, ``drop`` forgets it.  The command is published, so
+        every rank does the same to its own shard of the state."""
+        self._publish("state_copy", (op, int(handle), int(slot)))
+        if op == "take":
+            self._state_copies[handle] = self.runner.gdn_snapshot(slot)
+        elif op == "restore":
+            if handle not in self._state_copies:
+                raise ValueError(f"no recurrent-state copy under handle {handle} on this rank")
+            self.runner.gdn_restore(slot, self._state_copies[handle], self.page_table_dev.shape[0])
+        elif op == "drop":
+            self._state_copies.pop(handle, None)
+        else:
+            raise ValueError(f"unknown state-copy operation {op!r}")
+        return handle
 
     @staticmethod
     def _token_digest(tokens) -> bytes:
@@ -695,25 +729,29 @@ class Engine:
                     total += t.numel() * t.element_size()
         return total
 
-    def _store_snapshot(self, node: int, tokens, snap) -> None:
-        """Keeps ``snap`` for the radix node ``node`` (the last page of ``tokens``); the token
-        digest guards against a node id that the tree has recycled since.  The store is an LRU
-        bounded by a quarter of the prefix-cache budget."""
+    def _store_snapshot(self, node: int, tokens, handle: int) -> None:
+        """Keeps the state copy ``handle`` for the radix node ``node`` (the last page of
+        ``tokens``); the token digest guards against a node id that the tree has recycled
+        since.  The store is an LRU bounded by a quarter of the prefix-cache budget (counted in
+        this rank's bytes; shards are equal)."""
         digest = self._token_digest(tokens)
         old = self._snapshots.pop(node, None)
         if old is not None:
             self._snapshot_bytes -= old[2]
-        size = self._nbytes(snap)
-        self._snapshots[node] = (digest, snap, size)
+            self._state_copy("drop", old[1])
+        size = self._nbytes(self._state_copies[handle])
+        self._snapshots[node] = (digest, handle, size)
         self._snapshot_bytes += size
         self.stats.stored_snapshots += 1
         limit = max(self.load.prefix_cache_bytes // 4, size)
         while self._snapshot_bytes > limit and len(self._snapshots) > 1:
-            _node, (_d, _s, sz) = self._snapshots.popitem(last=False)
+            _node, (_d, gone, sz) = self._snapshots.popitem(last=False)
             self._snapshot_bytes -= sz
+            self._state_copy("drop", gone)
 
     def _snapshot_for(self, prompt, node_ids):
-        """-> (pages of the matched prefix that can be used, snapshot at that endpoint)."""
+        """-> (pages of the matched prefix that can be used, handle of the state copy at that
+        endpoint)."""
         for i in range(len(node_ids) - 1, -1, -1):
             hit = self._snapshots.get(node_ids[i])
             if hit is None:
@@ -721,6 +759,7 @@ class Engine:
             if hit[0] != self._token_digest(prompt[:(i + 1) * PAGE_TOKENS]):
                 self._snapshot_bytes -= hit[2]                # recycled node id: stale entry
                 del self._snapshots[node_ids[i]]
+                self._state_copy("drop", hit[1])
                 continue
             self._snapshots.move_to_end(node_ids[i])
             return i + 1, hit[1]
@@ -854,10 +893,12 @@ class Engine:
         elif op == "decode":
             self._exec_decode(*payload)
         elif op == "verify":
-            ids, rows_req, pos, max_kv, need = payload
-            packet = Packet(self._upload("ids", ids), self._upload("req", rows_req),
-                            self._upload("pos", pos), self.page_table_dev, len(ids), max_kv)
-            self.runner.greedy(packet, need_logits=need)
+            packet = self._verify_packet(*payload)
+            self.runner.greedy(packet, need_logits=bool(payload[4]))
+        elif op == "verify_commit":
+            self._verify_commit(payload)
+        elif op == "state_copy":
+            self._state_copy(*payload)
         elif op == "host_kv":
             kind, *args = payload
             if self.host_kv is None:
@@ -875,17 +916,44 @@ class Engine:
             raise ValueError(f"unknown device command {op!r}")
         self._status_enqueue()
 
-    def _verify_packet(self, ids, rows_req, pos, max_kv: int, need: bool) -> Packet:
+    def _verify_packet(self, ids, rows_req, pos, max_kv: int, need: bool,
+                       seg_lens: Optional[Sequence[int]] = None) -> Packet:
         """Packet of a verification round (every row's token is read back).  With follower
         ranks the round is published first; they run the same packet through ``apply`` and
-        take part in its collectives.  Recurrent models add their segment table afterwards and
-        are not served by several ranks with speculation."""
-        if self.channel is not None:
-            if self.recurrent:
-                raise ValueError("speculation on a recurrent model is not published to ranks")
-            self._publish("verify", (list(ids), list(rows_req), list(pos), int(max_kv), bool(need)))
-        return Packet(self._upload("ids", ids), self._upload("req", rows_req),
-                      self._upload("pos", pos), self.page_table_dev, len(ids), max_kv)
+        take part in its collectives.  ``seg_lens`` (recurrent models): rows per request; the
+        packet then runs tentatively, recurrent layers journal their rows, and
+        ``_verify_commit`` keeps the accepted prefix of every request."""
+        seg_lens = [int(n) for n in seg_lens] if seg_lens else None
+        if seg_lens and sum(seg_lens) != len(ids):
+            raise ValueError("segment lengths do not add up to the packet's rows")
+        self._publish("verify", (list(ids), list(rows_req), list(pos), int(max_kv), bool(need),
+                                 seg_lens))
+        packet = Packet(self._upload("ids", ids), self._upload("req", rows_req),
+                        self._upload("pos", pos), self.page_table_dev, len(ids), max_kv)
+        if seg_lens:
+            segs, first, start = [], [], 0
+            for n in seg_lens:
+                segs += [start, n, 0, 0]
+                first += [start] * n
+                start += n
+            packet.segments = self._upload("segs", segs).view(-1, 4)
+            packet.row_first = self._upload("first", first)
+            packet.n_segments = len(seg_lens)
+            packet.tentative = True
+            self._tentative = packet
+        return packet
+
+    def _verify_commit(self, kept_rows: Sequence[int]) -> None:
+        """Keeps the first ``kept_rows[i]`` rows of request ``i`` of the tentative packet in
+        every recurrent layer, on every rank."""
+        packet, self._tentative = self._tentative, None
+        if packet is None:
+            raise ValueError("commit without a tentative verification packet")
+        kept_rows = [int(k) for k in kept_rows]
+        if len(kept_rows) != packet.n_segments:
+            raise ValueError("one kept-row count per request of the tentative packet")
+        self._publish("verify_commit", kept_rows)
+        self.runner.gdn_commit(packet, kept_rows)
 
     def _build_packet(self, spec: dict) -> Packet:
         rows = len(spec["ids"])

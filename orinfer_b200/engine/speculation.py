@@ -203,19 +203,9 @@ class Speculator:
             pos += list(range(r.offset, r.offset + len(toks)))
             max_kv = max(max_kv, r.offset + len(toks))
         need = any(not eng._plain(r) for r, _ in plans)
-        packet = eng._verify_packet(ids, rows_req, pos, max_kv, need)
-        if eng.recurrent:
-            # recurrent layers must only keep the accepted prefix of each request's rows
-            segs, first, start = [], [], 0
-            for _r, drafts in plans:
-                n = 1 + len(drafts)
-                segs += [start, n, 0, 0]
-                first += [start] * n
-                start += n
-            packet.segments = eng._upload("segs", segs).view(-1, 4)
-            packet.row_first = eng._upload("first", first)
-            packet.n_segments = len(plans)
-            packet.tentative = True
+        # recurrent layers must only keep the accepted prefix of each request's rows
+        seg_lens = [1 + len(d) for _r, d in plans] if eng.recurrent else None
+        packet = eng._verify_packet(ids, rows_req, pos, max_kv, need, seg_lens)
         tok_dev, logits = eng.runner.greedy(packet, need_logits=need)
         eng._status_enqueue()
         tokens = tok_dev.cpu().tolist()
@@ -250,7 +240,7 @@ class Speculator:
             produced.append(r)
             row += n
         if packet.tentative:
-            eng.runner.gdn_commit(packet, kept_rows)
+            eng._verify_commit(kept_rows)
         if counts:
             self.acceptance.observe(counts)
             self.rounds += 1

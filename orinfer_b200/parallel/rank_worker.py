@@ -59,22 +59,21 @@ def build_engine(spec: dict, weights, channel=None):
     from ..engine.engine import Engine
     load = LoadOptions(**{**spec["load"], "cuda_graph": GraphMode(spec["load"]["cuda_graph"])})
     sched = SchedulerOptions(**{**spec["sched"], "policy": Policy(spec["sched"]["policy"])})
-    # What multi-rank serving does not carry yet is switched off on every rank alike: draft
-    # heads and the recurrent-state snapshots of hybrid models move device data that the
-    # published command stream does not describe.  Prompt-lookup speculation only adds
-    # verification packets, which are published like any other packet.  The prefix cache of an attention-only model
-    # is host bookkeeping plus page-table rows, which are published, so the leader keeps it;
-    # followers take no decisions and need none.  Its host tier is a published command per
-    # page move, carried out by every rank on its own shard.
+    # Every device-side effect of a leader's decision is a published command, so the leader
+    # keeps the host-side machinery and followers, which take no decisions, need none of it:
+    # the radix prefix cache (page-table rows are published), its host tier (one command per
+    # page move, carried out by every rank on its own shard), the recurrent-state copies of
+    # hybrid models (taken, restored and dropped under handles the leader chooses) and
+    # prompt-lookup speculation (verification packets and, for recurrent layers, the commit of
+    # the accepted rows).  Sharded weights carry no draft head, so the draft budget serves
+    # prompt lookup only.
     leader = channel is not None
-    recurrent = weights.config.arch == "hybrid"
-    offload = 0 if recurrent else load.kv_offload_bytes
+    offload = load.kv_offload_bytes
     load = dataclasses.replace(
-        load, prefix_cache_bytes=load.prefix_cache_bytes if leader and not recurrent else 0,
+        load, prefix_cache_bytes=load.prefix_cache_bytes if leader else 0,
         kv_offload_bytes=offload if leader else 0,
-        # the draft budget stays (prompt lookup uses it); sharded weights carry no draft head
-        mtp_drafts=load.mtp_drafts if leader and not recurrent else 0,
-        prompt_lookup=load.prompt_lookup and leader and not recurrent)
+        mtp_drafts=load.mtp_drafts if leader else 0,
+        prompt_lookup=load.prompt_lookup and leader)
     engine = Engine(weights, load=load, sched=sched, max_context=spec.get("max_context"),
                     kv_pages=spec.get("kv_pages"), max_rows=spec.get("max_rows"),
                     channel=channel)
@@ -87,6 +86,11 @@ def build_engine(spec: dict, weights, channel=None):
 def follower_main(spec: dict) -> int:
     rank, world = spec["rank"], spec["world"]
     device = init_group(rank, world, spec["port"], spec["device"], spec["group_timeout_s"])
+    if device.type == "cpu":
+        # CPU ranks share the host's cores: every rank spinning up a full-width thread pool
+        # for each small operator costs far more than it gives
+        import torch
+        torch.set_num_threads(max(1, (os.cpu_count() or 1) // (2 * world)))
     # join the channel before building the engine: the leader builds its own engine after it
     # has admitted every follower, and a fused runner's constructor is collective
     ch = FollowerChannel(spec["address"], bytes.fromhex(spec["authkey"]), rank)

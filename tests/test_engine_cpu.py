@@ -211,6 +211,26 @@ def test_host_kv_offload_restores_evicted_prefix(weights):
     assert cold.generate([base[0]], max_new=4)[0] == first[0]
 
 
+def test_host_tier_slots_are_all_accounted_for_under_traffic(weights):
+    """Prompt families that share pages, far more of them than device pages: pages go to the
+    host tier, come back, are re-adopted by recomputed prompts and dropped.  Every slot of the
+    host slab is then either free or owned by a node the tree still indexes."""
+    import random
+    rng = random.Random(3)
+    load = LoadOptions(kv_offload_bytes=8 * 4 * 2 * 128 * 2 * 32 * 2)      # a handful of slots
+    eng = _engine(weights, kv_pages=5, max_active=1, prefill_chunk=256, load=load)
+    assert 2 <= eng.host_kv.slots <= 64
+    stems = [_prompts(1, 128, seed=20 + i)[0] for i in range(3)]
+    tails = [_prompts(1, 130, seed=40 + i)[0] for i in range(4)]
+    for _ in range(40):
+        stem = rng.choice(stems)
+        prompt = stem + rng.choice(tails) if rng.random() < 0.6 else stem + [7, 8, 9]
+        eng.generate([prompt], max_new=2)
+        live = eng.prefix.statistics().host_pages
+        assert eng.host_kv.available + live == eng.host_kv.slots
+    assert eng.stats.offloaded_pages > 0 and eng.stats.restored_pages > 0
+
+
 def test_layered_prefill_lets_decoders_step_inside_a_long_prompt(weights):
     """A prompt that joins while another request decodes is run as a paused packet: the
     decoder takes a step at every layer-boundary pause and both texts stay what they were."""
@@ -250,5 +270,12 @@ def test_follower_commands_check_what_they_can(weights):
     eng.apply("host_kv", ("sync",))
     eng.apply("page_row", (0, [1, 2]))
     eng.apply("verify", ([5, 6, 7], [0, 0, 0], [0, 1, 2], 3, False))      # runs, returns nothing
+    with pytest.raises(ValueError, match="do not add up"):
+        eng.apply("verify", ([5, 6, 7], [0, 0, 0], [0, 1, 2], 3, False, [2, 2]))
+    with pytest.raises(ValueError, match="without a tentative"):
+        eng.apply("verify_commit", [1])
+    with pytest.raises(ValueError, match="no recurrent-state copy"):
+        eng.apply("state_copy", ("restore", 7, 0))
+    eng.apply("state_copy", ("drop", 7, -1))                  # dropping twice is harmless
     with pytest.raises(ValueError, match="unknown device command"):
         eng.apply("reboot", None)

@@ -49,6 +49,28 @@ def test_utility_prefers_popular_and_recent():
     assert c.evict(1) == [(1, 1)]
 
 
+def test_abandoned_matches_do_not_count_as_hits():
+    # a request that waits for pages matches on every admission attempt; those matches must
+    # not make its prefix look more popular than one that was really used
+    c = RadixPrefixCache(page_tokens=4)
+    c.insert(_toks(1), [1])
+    c.insert(_toks(2), [2])
+    c.insert(_toks(3), [3])
+    for _ in range(3):
+        ids, _ = c.match(_toks(1))
+        c.release(ids)                           # prefix 1: three real uses
+    for _ in range(6):
+        ids, _ = c.match(_toks(2))
+        c.abandon(ids)                           # prefix 2: six retries, never used
+    held, _ = c.match(_toks(3))                  # prefix 3 stays in use: not evictable
+    for _ in range(90):                          # time passes, so that age no longer decides
+        c.match(_toks(3), acquire=False)
+    assert c.evict(1) == [(2, 2)]                # with the retries counted, 1 would go first
+    assert c.evict(1) == [(1, 1)]                # abandon dropped the users as well
+    assert c.evict(1) == []
+    c.release(held)
+
+
 def test_host_tier_roundtrip():
     c = RadixPrefixCache(page_tokens=4)
     c.insert(_toks(1, 2), [5, 6])

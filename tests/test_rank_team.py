@@ -5,6 +5,17 @@ import time
 
 import pytest
 
+@pytest.fixture(autouse=True)
+def _few_threads():
+    """The leader rank lives in the test process: like the follower processes it should not
+    claim every core for each small operator."""
+    import torch
+    before = torch.get_num_threads()
+    torch.set_num_threads(2)
+    yield
+    torch.set_num_threads(before)
+
+
 SPEC = dict(
     world=2, device="cpu", preset="tiny", group_timeout_s=120.0, kv_pages=32, max_context=512,
     max_rows=256,
@@ -97,6 +108,55 @@ def test_host_kv_tier_moves_pages_on_every_rank():
         team.channel.sync(90.0)
         assert engine.stats.restored_pages >= 1 and r.cached_tokens == 128
         assert r.generated == first[0]
+        assert team.channel.failure is None
+    finally:
+        team.close(engine)
+    assert all(p.returncode == 0 for p in team.procs)
+
+
+def test_hybrid_model_keeps_prefix_cache_and_speculation_across_ranks(monkeypatch):
+    """Recurrent state is per-rank device data: its copies are taken, restored and dropped by
+    published commands under the leader's handles, and a verification round's accepted rows are
+    committed on every rank.  Texts equal those of a plain multi-rank engine."""
+    from orinfer_b200.parallel.rank_worker import leader_engine
+    monkeypatch.setenv("ORINFER_SINGLE_MTP_POLICY", "fixed3")
+    base = dict(SPEC, preset="tiny-hybrid")
+    shared = [(11 * i) % 251 + 1 for i in range(128)]
+    prompts = [shared + [5, 6, 7, 8, 5, 6, 7, 8, 5, 6], shared + [9, 8, 7]]
+    plain_engine, plain_team = leader_engine(dict(base), deadline_s=90.0)
+    try:
+        assert plain_engine.recurrent
+        plain = [plain_engine.generate([p], max_new=8)[0] for p in prompts]
+    finally:
+        plain_team.close(plain_engine)
+    spec = dict(base, load=dict(SPEC["load"], prefix_cache_bytes=64 << 20, prompt_lookup=True,
+                                mtp_drafts=3))
+    engine, team = leader_engine(spec, deadline_s=90.0)
+    try:
+        assert engine.prefix is not None and engine.spec.enabled
+        text = {}
+
+        def drafts(r, c):                          # half-right drafts: accept one, reject the rest
+            d = list(text[r.rid][len(r.generated):len(r.generated) + c])
+            if len(d) > 1:
+                d[1:] = [(t + 1) % 251 for t in d[1:]]
+            return d
+
+        engine.spec.drafts_for = drafts
+        got = []
+        for p, want in zip(prompts + prompts[:1], plain + plain[:1]):
+            r = engine.submit(p, 8)
+            text[r.rid] = want
+            while not r.finished:
+                engine.step()
+            got.append(r)
+        team.channel.sync(90.0)
+        assert [r.generated for r in got] == plain + plain[:1]
+        assert got[0].cached_tokens == 0 and got[1].cached_tokens == 128
+        assert got[2].cached_tokens == 128
+        st = engine.spec.statistics()
+        assert 0 < st["accepted_draft_tokens"] < st["proposed_tokens"]
+        assert engine.stats.stored_snapshots >= 1 and engine.stats.restored_snapshots == 2
         assert team.channel.failure is None
     finally:
         team.close(engine)
