@@ -51,6 +51,9 @@ def _load_args(p: argparse.ArgumentParser, batch: bool = False) -> None:
                         "decoding requests step in between (1 = off)")
     p.add_argument("--max-context", type=int, default=None)
     p.add_argument("--tp", type=int, default=1)
+    p.add_argument("--tp-draft-head", action="store_true",
+                   help="with --tp: shard the model's draft head too and speculate with it "
+                        "(verified on CPU ranks only so far)")
     p.add_argument("--device", default="cuda")
 
 
@@ -162,6 +165,7 @@ def cmd_serve(a) -> int:
                                  f"{torch.cuda.device_count()} visible")
             spec = dict(world=a.tp, device="cuda" if torch.cuda.is_available() else "cpu",
                         preset=a.preset, model_dir=a.model_dir, max_context=a.max_context,
+                        draft_head=bool(getattr(a, "tp_draft_head", False)),
                         load={**dataclasses.asdict(load), "cuda_graph": load.cuda_graph.value},
                         sched={**dataclasses.asdict(sched), "policy": sched.policy.value})
             engine, team = leader_engine(spec, deadline_s=max(a.step_timeout_ms / 1e3, 30.0))

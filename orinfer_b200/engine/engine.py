@@ -153,6 +153,8 @@ class Engine:
         self._state_copies: Dict[int, tuple] = {}
         self._state_handles = 0
         self._tentative: Optional[Packet] = None     # verification packet awaiting its commit
+        # hidden rows the draft head has not seen yet: rid -> [(first position, rows)]
+        self._mtp_backlog: Dict[int, list] = {}
         self.max_context = max_context or min(self.cfg.max_context, 32768)
         self.max_pages_per_req = (self.max_context + PAGE_TOKENS - 1) // PAGE_TOKENS
         self.max_rows = max_rows or max(self.sched.prefill_chunk + self.sched.max_active, 256)
@@ -899,6 +901,12 @@ class Engine:
             self._verify_commit(payload)
         elif op == "state_copy":
             self._state_copy(*payload)
+        elif op == "mtp_capture":
+            self._mtp_capture(payload)
+        elif op == "mtp_draft":
+            self._mtp_draft(payload)
+        elif op == "mtp_forget":
+            self._mtp_forget(payload)
         elif op == "host_kv":
             kind, *args = payload
             if self.host_kv is None:
@@ -942,6 +950,53 @@ class Engine:
             packet.tentative = True
             self._tentative = packet
         return packet
+
+    # Draft head: the hidden rows it consumes and the KV it writes are per-rank device data, so
+    # the three things that touch them are published like packets.
+    def _mtp_capture(self, keep, hidden=None) -> None:
+        """``keep``: [(rid, first row, rows, first position)] of the packet that just ran; the
+        rows' final hidden states are copied into the draft backlog."""
+        keep = [tuple(int(v) for v in item) for item in keep]
+        self._publish("mtp_capture", keep)
+        if hidden is None:
+            hidden = self.runner.final_hidden(max(row0 + n for _rid, row0, n, _pos in keep))
+        for rid, row0, n, pos0 in keep:
+            self._mtp_backlog.setdefault(rid, []).append((pos0, hidden[row0:row0 + n].clone()))
+
+    def _mtp_forget(self, rid: int) -> None:
+        if rid in self._mtp_backlog:
+            self._publish("mtp_forget", int(rid))
+            del self._mtp_backlog[rid]
+
+    def _mtp_draft(self, plan: dict) -> List[torch.Tensor]:
+        """One batched draft round: a head pass over the backlog rows of ``plan["rids"]``
+        (catch-up plus the first draft, read at row ``last[i]`` of request i), then
+        ``count - 1`` single-row passes that feed the head's own hidden state back.  Returns
+        one token tensor [requests] per draft position."""
+        self._publish("mtp_draft", plan)
+        hids = []
+        for rid in plan["rids"]:
+            if rid not in self._mtp_backlog:
+                raise ValueError(f"no draft backlog for request {rid} on this rank")
+            hids += [h for _pos0, h in self._mtp_backlog.pop(rid)]
+        rows = len(plan["toks"])
+        if sum(h.shape[0] for h in hids) != rows:
+            raise ValueError("the draft backlog of this rank is out of step with the leader")
+        p = Packet(self._upload("mids", plan["toks"]), self._upload("mreq", plan["rreq"]),
+                   self._upload("mpos", plan["rpos"]), self.page_table_dev, rows,
+                   max(plan["rpos"]) + 1)
+        dtok, dhid = self.runner.mtp_rows(p.ids, torch.cat(hids, dim=0), p)
+        sel = torch.tensor(plan["last"], device=dtok.device)
+        cur_tok, cur_hid = dtok[sel], dhid[sel]
+        out = [cur_tok]
+        live = len(plan["slots"])
+        for j in range(1, plan["count"]):
+            pos = [o - 1 + j for o in plan["offsets"]]
+            p = Packet(cur_tok.to(torch.int32).contiguous(), self._upload("mreq", plan["slots"]),
+                       self._upload("mpos", pos), self.page_table_dev, live, max(pos) + 1)
+            cur_tok, cur_hid = self.runner.mtp_rows(p.ids, cur_hid, p)
+            out.append(cur_tok)
+        return out
 
     def _verify_commit(self, kept_rows: Sequence[int]) -> None:
         """Keeps the first ``kept_rows[i]`` rows of request ``i`` of the tentative packet in
@@ -1362,7 +1417,7 @@ class Engine:
 
     def runner_has_mtp(self) -> bool:
         return (self.w.mtp is not None and hasattr(self.runner, "mtp_rows")
-                and self.load.mtp_drafts != 0 and getattr(self.w, "tp", None) is None)
+                and self.load.mtp_drafts != 0)
 
     @staticmethod
     def _plain(r: Request) -> bool:

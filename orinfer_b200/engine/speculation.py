@@ -40,7 +40,6 @@ class Speculator:
         self.contract = MtpSpec.for_config(engine.cfg, self.max_drafts, engine.sched.max_active,
                                            engine.max_rows)
         self.lookups: Dict[int, P.PromptLookup] = {}
-        self.backlog: Dict[int, list] = {}            # rid -> [(first pos, hidden rows)]
         self.acceptance = P.Acceptance()
         # round cost per (batch bucket, verification width); plain-step cost per batch bucket
         # (the minimum of the last few: a decode step never gets faster than its kernels, so
@@ -53,6 +52,12 @@ class Speculator:
         self.rounds = self.proposed = self.accepted = self.committed = 0
         self.trace = os.environ.get("ORINFER_MTP_TRACE") == "1"
         self.policy = os.environ.get("ORINFER_SINGLE_MTP_POLICY", "auto")
+
+    @property
+    def backlog(self) -> Dict[int, list]:
+        """rid -> [(first position, hidden rows)] not yet seen by the draft head.  The rows are
+        device data, so the engine keeps them (on every rank of a multi-rank engine)."""
+        return self.engine._mtp_backlog
 
     @property
     def enabled(self) -> bool:
@@ -117,7 +122,7 @@ class Speculator:
 
     def forget(self, r: Request) -> None:
         self.lookups.pop(r.rid, None)
-        self.backlog.pop(r.rid, None)
+        self.engine._mtp_forget(r.rid)
 
     # ------------------------------------------------------------------ MTP draft head
     def capture(self, rows_info, hidden) -> None:
@@ -125,15 +130,14 @@ class Speculator:
         see (next token, hidden) of every position before it can draft past it."""
         if not self.engine.runner_has_mtp() or self.max_drafts <= 0:
             return
-        for r, row0, n, pos0 in rows_info:
-            if n > 0 and not r.finished and r.constraint is None:
-                self.backlog.setdefault(r.rid, []).append((pos0, hidden[row0:row0 + n].clone()))
+        keep = [(r.rid, int(row0), int(n), int(pos0)) for r, row0, n, pos0 in rows_info
+                if n > 0 and not r.finished and r.constraint is None]
+        if keep:
+            self.engine._mtp_capture(keep, hidden)
 
     def mtp_drafts(self, reqs: List[Request], count: int) -> Dict[int, List[int]]:
         """Batched draft loop: one head pass over the backlog rows (catch-up + first draft),
         then ``count - 1`` single-row passes feeding the head's own hidden state back."""
-        import torch
-        from ..models.runner import Packet
         eng = self.engine
         live = [r for r in reqs if self.backlog.get(r.rid)]
         if not live or count <= 0:
@@ -144,32 +148,25 @@ class Speculator:
             for lo in range(0, len(live), cap):
                 out.update(self.mtp_drafts(live[lo:lo + cap], count))
             return out
-        toks, hids, rreq, rpos, last = [], [], [], [], []
+        toks, rreq, rpos, last = [], [], [], []
         for r in live:
             hist = r.history
-            for pos0, h in self.backlog.pop(r.rid):
+            for pos0, h in self.backlog[r.rid]:
                 n = h.shape[0]
                 toks += [hist[pos0 + i + 1] for i in range(n)]
-                hids.append(h)
                 rreq += [r.slot] * n
                 rpos += list(range(pos0, pos0 + n))
             last.append(len(toks) - 1)
-        rows = len(toks)
-        if rows > eng.max_rows:
+        if len(toks) > eng.max_rows:
+            for r in live:
+                eng._mtp_forget(r.rid)
             return {}
-        p = Packet(eng._upload("mids", toks), eng._upload("mreq", rreq), eng._upload("mpos", rpos),
-                   eng.page_table_dev, rows, max(rpos) + 1)
-        dtok, dhid = eng.runner.mtp_rows(p.ids, torch.cat(hids, dim=0), p)
-        sel = torch.tensor(last, device=dtok.device)
-        cur_tok, cur_hid = dtok[sel], dhid[sel]
-        out = {r.rid: [int(t)] for r, t in zip(live, cur_tok.cpu().tolist())}
-        for j in range(1, count):
-            pos = [r.offset - 1 + j for r in live]
-            p = Packet(cur_tok.to(torch.int32).contiguous(),
-                       eng._upload("mreq", [r.slot for r in live]), eng._upload("mpos", pos),
-                       eng.page_table_dev, len(live), max(pos) + 1)
-            cur_tok, cur_hid = eng.runner.mtp_rows(p.ids, cur_hid, p)
-            for r, t in zip(live, cur_tok.cpu().tolist()):
+        plan = dict(rids=[r.rid for r in live], slots=[r.slot for r in live], toks=toks,
+                    rreq=rreq, rpos=rpos, last=last, count=int(count),
+                    offsets=[r.offset for r in live])
+        out: Dict[int, List[int]] = {r.rid: [] for r in live}
+        for step in eng._mtp_draft(plan):                # one device tensor per draft position
+            for r, t in zip(live, step.cpu().tolist()):
                 out[r.rid].append(int(t))
         return out
 

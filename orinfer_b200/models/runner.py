@@ -604,4 +604,9 @@ class ModelRunner:
             hid = ws.resid[:rows].clone()
         finally:
             ws.resid = saved
-        return F.argmax(lg[:rows]), hid
+        return self._draft_tokens(lg[:rows]), hid
+
+    def _draft_tokens(self, logits: torch.Tensor) -> torch.Tensor:
+        """Greedy draft tokens from the head's logits (tensor-parallel runners merge the
+        ranks' vocabulary shards here)."""
+        return F.argmax(logits)

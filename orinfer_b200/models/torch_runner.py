@@ -236,10 +236,15 @@ class TorchRunner:
         resid = x
         y = R.rms_norm(resid, m.layer.in_norm, cfg.eps, zc)
         mix = self._attention(m.layer, self.mtp_kv_index, y, p, cos, sin)
-        x = self._linear(m.layer.o, mix)
+        x = self._reduce(self._linear(m.layer.o, mix))
         resid = resid + x
         y = R.rms_norm(resid, m.layer.post_norm, cfg.eps, zc)
         x = self._ffn(m.layer, y)
         final = resid + x
         lg = self._linear(self.w.head, R.rms_norm(final, m.final_norm, cfg.eps, zc), out_f32=True)
-        return R.argmax_lowest(lg), final
+        return self._draft_tokens(lg), final
+
+    def _draft_tokens(self, logits: torch.Tensor) -> torch.Tensor:
+        """Greedy draft tokens from the head's logits (tensor-parallel runners merge the
+        ranks' vocabulary shards here)."""
+        return R.argmax_lowest(logits)

@@ -361,7 +361,20 @@ class FusedTPRunner(TPRunner):
         count_launches(1)
         return "down"
 
+    def mtp_rows(self, tokens, hidden, p):
+        """The draft layer's two row-parallel projections are reduced with plain all-reduces
+        (the peer inboxes belong to the model's own layers and their sequence counters)."""
+        self._plain_reduce = True
+        try:
+            return super().mtp_rows(tokens, hidden, p)
+        finally:
+            self._plain_reduce = False
+
+    _plain_reduce = False
+
     def _row_parallel(self, name: str, lin: QLinear, q8, sc, rows: int):
+        if self._plain_reduce:
+            return TPRunner._row_parallel(self, name, lin, q8, sc, rows)
         name = self._SLOT[name]
         if rows <= LL_ROWS and lin.fmt != "w8" and lin.n % 16 == 0 and self._ll:
             # decode-sized: data and readiness travel in the same 8-byte units

@@ -45,12 +45,20 @@ def init_group(rank: int, world: int, port: int, device: str, timeout_s: float):
 def load_shard(spec: dict, rank: int, world: int, device):
     """This rank's weights: a preset is created directly in the sharded geometry; a model
     directory is loaded and cut down to the shard."""
+    import dataclasses
     from ..config import PRESETS
     from .tp import random_shard, shard_model
+    # ``draft_head``: shard the model's draft head too (speculation with it then runs on every
+    # rank through published commands); off unless asked for
+    draft = bool(spec.get("draft_head", False))
     if spec.get("preset"):
-        return random_shard(PRESETS[spec["preset"]], rank, world, device, seed=0)
+        cfg = PRESETS[spec["preset"]]
+        if spec.get("mtp_layers") is not None:
+            cfg = dataclasses.replace(cfg, mtp_layers=int(spec["mtp_layers"]))
+        return random_shard(cfg, rank, world, device, seed=0, draft_head=draft)
     from ..engine.checkpoint import load_model
-    return shard_model(load_model(spec["model_dir"], device, verify=False), rank, world)
+    return shard_model(load_model(spec["model_dir"], device, verify=False), rank, world,
+                       draft_head=draft)
 
 
 def build_engine(spec: dict, weights, channel=None):
@@ -65,8 +73,8 @@ def build_engine(spec: dict, weights, channel=None):
     # page move, carried out by every rank on its own shard), the recurrent-state copies of
     # hybrid models (taken, restored and dropped under handles the leader chooses) and
     # prompt-lookup speculation (verification packets and, for recurrent layers, the commit of
-    # the accepted rows).  Sharded weights carry no draft head, so the draft budget serves
-    # prompt lookup only.
+    # the accepted rows) and, when the shards carry a draft head, its captures, draft rounds
+    # and backlog clean-up.
     leader = channel is not None
     offload = load.kv_offload_bytes
     load = dataclasses.replace(

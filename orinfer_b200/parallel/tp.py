@@ -147,9 +147,31 @@ def _shard_moe(cfg: ModelConfig, lw: LayerWeights, layer: int, lay: TPLayout, de
     lw.shared_owner = layer % w
 
 
-def shard_model(weights: ModelWeights, rank: int, world: int) -> ModelWeights:
+def _draft_ffn_slice(width: int, lay: TPLayout) -> Tuple[int, int]:
+    """This rank's channels of the draft layer's FFN (its width is the model's FFN width for
+    dense models and a width of its own for expert models)."""
+    if width % 128 or width // 128 < lay.world:
+        raise ValueError(f"a draft FFN of {width} channels does not split over {lay.world} ranks")
+    lo, hi = split_blocks(width // 128, lay.world)[lay.rank]
+    return lo * 128, hi * 128
+
+
+def _shard_draft_head(cfg: ModelConfig, mtp, lay: TPLayout, dev):
+    """The draft head's decoder layer is sharded like any full-attention layer (heads, FFN
+    channels); its input projection and norms are small and stay whole on every rank; the
+    vocabulary head it shares with the model is sharded already."""
+    from ..models.weights import MtpWeights
+    lw = dataclasses.replace(mtp.layer)
+    _shard_attention(cfg, lw, lay, dev)
+    _shard_ffn(lw, dataclasses.replace(lay, ffn=_draft_ffn_slice(lw.gate_up.n // 2, lay)), dev)
+    return MtpWeights(mtp.norm_e, mtp.norm_h, mtp.fc, lw, mtp.final_norm)
+
+
+def shard_model(weights: ModelWeights, rank: int, world: int,
+                draft_head: bool = False) -> ModelWeights:
     """Returns this rank's shard; ``weights.config`` becomes the *local* geometry
-    (local head counts, local FFN width) while ``vocab`` and the expert count stay global."""
+    (local head counts, local FFN width) while ``vocab`` and the expert count stay global.
+    ``draft_head``: keep (and shard) the model's draft head; without it the shard has none."""
     cfg = weights.config
     lay = layout(cfg, rank, world)
     dev = weights.embed_q.device
@@ -172,8 +194,12 @@ def shard_model(weights: ModelWeights, rank: int, world: int) -> ModelWeights:
                                 gdn_k_heads=cfg.gdn_k_heads // world if cfg.gdn_k_heads else 0,
                                 gdn_v_heads=cfg.gdn_v_heads // world if cfg.gdn_v_heads else 0,
                                 mtp_layers=0)
+    mtp = None
+    if draft_head and weights.mtp is not None:
+        mtp = _shard_draft_head(cfg, weights.mtp, lay, dev)
+        local = dataclasses.replace(local, mtp_layers=cfg.mtp_layers)
     out = ModelWeights(local, weights.embed_q, weights.embed_s, layers, weights.final_norm, head,
-                       weights.signs, None, weights.embed_dense)
+                       weights.signs, mtp, weights.embed_dense)
     out.tp = lay                       # type: ignore[attr-defined]
     out.global_config = cfg            # type: ignore[attr-defined]
     return out
@@ -190,7 +216,8 @@ def local_config(cfg: ModelConfig, lay: TPLayout) -> ModelConfig:
         gdn_v_heads=cfg.gdn_v_heads // world if cfg.gdn_v_heads else 0, mtp_layers=0)
 
 
-def random_shard(cfg: ModelConfig, rank: int, world: int, device, seed: int = 0) -> ModelWeights:
+def random_shard(cfg: ModelConfig, rank: int, world: int, device, seed: int = 0,
+                 draft_head: bool = False) -> ModelWeights:
     """Random-init N(0, 0.02) weights of ONE rank's shard, quantised to the configured
     formats, created directly in the sharded geometry: no rank ever holds the whole model
     (``shard_model(random_model(...))`` would need all of an 80B-class model on every GPU).
@@ -198,8 +225,9 @@ def random_shard(cfg: ModelConfig, rank: int, world: int, device, seed: int = 0)
     Tensors that tensor parallelism replicates (embedding, norms, router, shared expert) come
     from a generator seeded alike on every rank, so all ranks route and embed identically;
     sharded tensors come from a rank-specific generator.  The result has the same fields as
-    ``shard_model`` gives (``tp`` layout, ``global_config``)."""
-    from ..models.weights import _Init, quantize_linear
+    ``shard_model`` gives (``tp`` layout, ``global_config``).  ``draft_head``: also create this
+    rank's shard of the draft head when the geometry has one."""
+    from ..models.weights import MtpWeights, _Init, _mtp_layer, quantize_linear
     lay = layout(cfg, rank, world)
     local = local_config(cfg, lay)
     dev = torch.device(device)
@@ -233,8 +261,18 @@ def random_shard(cfg: ModelConfig, rank: int, world: int, device, seed: int = 0)
                        emb.scale[v0:v1].contiguous(), None)
     else:
         head = own.linear(v1 - v0, cfg.hidden, cfg.head_format, rotate=False)
+    mtp = None
+    if draft_head and cfg.mtp_layers:
+        full_f = cfg.ffn or max(cfg.expert_ffn * 4, 512)
+        f0, f1 = _draft_ffn_slice(full_f, lay)
+        own.cfg = dataclasses.replace(local, experts=0, ffn=f1 - f0)
+        mtp = MtpWeights(shared.ones(cfg.hidden), shared.ones(cfg.hidden),
+                         shared.linear(cfg.hidden, 2 * cfg.hidden, "w8", rotate=False),
+                         _mtp_layer(own), shared.ones(cfg.hidden))
+        own.cfg = local
+        local = dataclasses.replace(local, mtp_layers=cfg.mtp_layers)
     out = ModelWeights(local, emb.codes, emb.scale, layers, shared.ones(cfg.hidden), head,
-                       shared.signs, None, None)
+                       shared.signs, mtp, None)
     out.tp = lay                       # type: ignore[attr-defined]
     out.global_config = cfg            # type: ignore[attr-defined]
     return out

@@ -81,6 +81,9 @@ class _TPMixin:
 
 
 class TPRunner(_TPMixin, ModelRunner):
+    # NOTE: the draft head (``mtp_rows``) of a sharded model runs the inherited code: its
+    # row-parallel projections end in ``_reduce`` and its tokens go through ``_draft_tokens``.
+
     """NCCL-only tensor-parallel runner (baseline arm)."""
 
     def __init__(self, weights: ModelWeights, kv: KVPool, max_rows: int, group=None):
@@ -102,6 +105,9 @@ class TPRunner(_TPMixin, ModelRunner):
             return x
         dist.all_reduce(x[:rows], group=self.group)
         return x
+
+    def _draft_tokens(self, logits: torch.Tensor) -> torch.Tensor:
+        return self._merge_tokens(logits, F.argmax(logits))
 
     def greedy(self, p: Packet, logits_out=None, token_out=None, need_logits: bool = True):
         local = self._last_local = self.logits(p)                      # [n_sel, V/tp]
@@ -130,6 +136,9 @@ class TPTorchRunner(_TPMixin, TorchRunner):
         y = x.float().contiguous()
         dist.all_reduce(y, group=self.group)
         return R.f16(y)
+
+    def _draft_tokens(self, logits: torch.Tensor) -> torch.Tensor:
+        return self._merge_tokens(logits, R.argmax_lowest(logits))
 
     def greedy(self, p: Packet, logits_out=None, token_out=None, need_logits: bool = True):
         local = self._last_local = self.logits(p)

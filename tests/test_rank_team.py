@@ -163,6 +163,38 @@ def test_hybrid_model_keeps_prefix_cache_and_speculation_across_ranks(monkeypatc
     assert all(p.returncode == 0 for p in team.procs)
 
 
+def test_draft_head_speculation_runs_sharded_on_every_rank(monkeypatch):
+    """With ``draft_head`` the shards carry the draft head (heads and FFN channels split like a
+    decoder layer): the hidden rows it consumes are captured on every rank, its draft rounds
+    are collective, and the text equals that of the same ranks without speculation."""
+    from orinfer_b200.parallel.rank_worker import leader_engine
+    monkeypatch.setenv("ORINFER_SINGLE_MTP_POLICY", "fixed2")
+    base = dict(SPEC, mtp_layers=1, draft_head=True)
+    prompts = [[(7 * i + 3 * j) % 500 + 1 for i in range(24)] for j in range(2)]
+    plain_engine, plain_team = leader_engine(
+        dict(base, load=dict(SPEC["load"], mtp_drafts=0)), deadline_s=90.0)
+    try:
+        assert not plain_engine.spec.enabled
+        plain = plain_engine.generate(prompts, max_new=10)
+    finally:
+        plain_team.close(plain_engine)
+    engine, team = leader_engine(dict(base, load=dict(SPEC["load"], mtp_drafts=2)),
+                                 deadline_s=90.0)
+    try:
+        assert engine.runner_has_mtp() and engine.spec.enabled
+        assert engine.w.mtp.layer.qkv.n < 2 * engine.w.global_config.q_heads * 64   # a shard
+        out = engine.generate(prompts, max_new=10)
+        team.channel.sync(90.0)
+        assert out == plain
+        st = engine.spec.statistics()
+        assert st["rounds"] > 0 and st["proposed_tokens"] > 0
+        assert not engine._mtp_backlog or all(r.finished for r in engine.running)
+        assert team.channel.failure is None
+    finally:
+        team.close(engine)
+    assert all(p.returncode == 0 for p in team.procs)
+
+
 def test_follower_that_stops_replying_fails_the_leader_closed():
     from orinfer_b200.parallel.rank_channel import RankFailure
     from orinfer_b200.parallel.rank_worker import leader_engine

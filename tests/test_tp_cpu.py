@@ -146,3 +146,57 @@ def test_tp2_engine_samples_from_sharded_candidates(tmp_path):
     assert r0["out"] == r1["out"]
     assert all(len(o) == 10 for o in r0["out"])
     assert r0["sharded"] == 20                       # two sampled requests x 10 tokens
+
+
+def _draft_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import dataclasses
+    torch.set_num_threads(2)
+    from orinfer_b200.config import PRESETS
+    from orinfer_b200.models.runner import KVPool, Packet
+    from orinfer_b200.models.weights import random_model
+    from orinfer_b200.parallel.tp import shard_model
+    from orinfer_b200.parallel.tp_runner import TPTorchRunner
+    cfg = dataclasses.replace(PRESETS["tiny"], mtp_layers=1)
+    shard = shard_model(random_model(cfg, seed=0), rank, world, draft_head=True)
+    assert shard.config.mtp_layers == 1 and shard.mtp.layer.gate_up.n == cfg.ffn * 2 // world
+    assert shard.mtp.layer.o.k == cfg.q_heads * cfg.head_dim // world
+    runner = TPTorchRunner(shard, KVPool.allocate(shard.config, 4, "cpu", 1), 64)
+    ids, p = _draft_inputs(cfg, Packet)
+    runner.greedy(p)
+    tok, hid = runner.mtp_rows(torch.roll(ids, -1), runner.final_hidden(p.rows), p)
+    torch.save({"tok": tok, "hid": hid}, os.path.join(out_dir, f"d{rank}.pt"))
+    dist.destroy_process_group()
+
+
+def _draft_inputs(cfg, Packet):
+    g = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, cfg.vocab, (16,), generator=g, dtype=torch.int32)
+    t = lambda v: torch.tensor(v, dtype=torch.int32)
+    return ids, Packet(ids, t([0] * 16), t(list(range(16))), t([[1]]), 16, 16)
+
+
+def test_sharded_draft_head_matches_the_whole_one(tmp_path):
+    """The draft head split over two ranks (heads, FFN channels, vocabulary) gives the hidden
+    rows and draft tokens of the unsplit head, up to the per-shard activation scales."""
+    import dataclasses
+    from orinfer_b200.config import PRESETS
+    from orinfer_b200.models.runner import KVPool, Packet
+    from orinfer_b200.models.torch_runner import TorchRunner
+    from orinfer_b200.models.weights import random_model
+    port = 31500 + os.getpid() % 2000
+    mp.spawn(_draft_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = torch.load(tmp_path / "d0.pt"), torch.load(tmp_path / "d1.pt")
+    assert torch.equal(r0["tok"], r1["tok"]) and torch.equal(r0["hid"], r1["hid"])
+    cfg = dataclasses.replace(PRESETS["tiny"], mtp_layers=1)
+    full = random_model(cfg, seed=0)
+    runner = TorchRunner(full, KVPool.allocate(cfg, 4, "cpu", 1), 64)
+    ids, p = _draft_inputs(cfg, Packet)
+    runner.greedy(p)
+    tok, hid = runner.mtp_rows(torch.roll(ids, -1), runner.final_hidden(p.rows), p)
+    cos = torch.nn.functional.cosine_similarity(r0["hid"].float(), hid.float(), dim=1)
+    assert cos.min() > 0.995, cos
+    assert (r0["tok"].long() == tok.long()).float().mean() >= 0.75
