@@ -92,6 +92,11 @@ class ModelConfig:
     gdn_conv: int = 4
     # MTP draft head (number of extra decoder layers, 0 = none)
     mtp_layers: int = 0
+    # shape of the draft layer: "dense" = plain attention + dense FFN in W8 whatever the model
+    # is; "model" = the shape of the model's own full-attention layers (gated attention where
+    # the model has it, routed experts where the model has them), which is what checkpoints
+    # of the expert and hybrid families carry
+    draft_layer: str = "dense"
     max_context: int = 32768
     # Encoder families (embedding models): every token attends to the whole input.  Such a
     # model serves /v1/embeddings through ``Engine.encode``; it does not generate.

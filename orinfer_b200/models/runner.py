@@ -597,7 +597,10 @@ class ModelRunner:
             ws.resid[:rows].zero_()
             self._rope(p, rows)
             x = self._attention_block(m.layer, self.mtp_kv_index, x, p, rows, True)
-            x = self._dense_ffn(m.layer, x, rows)
+            if m.layer.router is not None:       # a draft layer with routed experts
+                x = self._moe_ffn(m.layer, x, rows)
+            else:
+                x = self._dense_ffn(m.layer, x, rows)
             q8, sc = self._prep(x, m.final_norm, self.w.head.signs, rows)
             lg = F.qgemm(q8, sc, self.w.head.codes, self.w.head.scale, self.w.head.fmt,
                          self.w.head.n, out_f32=True, rows=rows)

@@ -239,7 +239,13 @@ class TorchRunner:
         x = self._reduce(self._linear(m.layer.o, mix))
         resid = resid + x
         y = R.rms_norm(resid, m.layer.post_norm, cfg.eps, zc)
-        x = self._ffn(m.layer, y)
+        if m.layer.router is not None:           # a draft layer with routed experts
+            from ..ref.cpu_forward import moe_ffn
+            tp = getattr(self.w, "tp", None)
+            m.layer._add_shared = tp is None or m.layer.shared_owner in (-1, tp.rank)
+            x = self._reduce(moe_ffn(cfg, m.layer, y, True))
+        else:
+            x = self._ffn(m.layer, y)
         final = resid + x
         lg = self._linear(self.w.head, R.rms_norm(final, m.final_norm, cfg.eps, zc), out_f32=True)
         return self._draft_tokens(lg), final

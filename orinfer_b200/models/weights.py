@@ -279,6 +279,8 @@ def _mtp_layer(init: _Init) -> LayerWeights:
     """The draft layer is a dense full-attention decoder layer in W8
     (python/orinfer_build/models/qwen35/mtp.py: one W8 layer + shared head)."""
     c = init.cfg
+    if c.draft_layer == "model":           # a full-attention layer shaped like the model's own
+        return init.layer(c.layers, True)
     lw = LayerWeights("attn", init.ones(c.hidden), init.ones(c.hidden))
     qd = c.q_heads * c.head_dim
     lw.qkv = init.linear(qd + 2 * c.kv_dim, c.hidden, "w8", rotate=False)

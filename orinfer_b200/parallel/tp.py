@@ -163,7 +163,11 @@ def _shard_draft_head(cfg: ModelConfig, mtp, lay: TPLayout, dev):
     from ..models.weights import MtpWeights
     lw = dataclasses.replace(mtp.layer)
     _shard_attention(cfg, lw, lay, dev)
-    _shard_ffn(lw, dataclasses.replace(lay, ffn=_draft_ffn_slice(lw.gate_up.n // 2, lay)), dev)
+    if lw.router is not None:
+        _shard_moe(cfg, lw, 0, lay, dev)
+    else:
+        _shard_ffn(lw, dataclasses.replace(lay, ffn=_draft_ffn_slice(lw.gate_up.n // 2, lay)),
+                   dev)
     return MtpWeights(mtp.norm_e, mtp.norm_h, mtp.fc, lw, mtp.final_norm)
 
 
@@ -235,11 +239,11 @@ def random_shard(cfg: ModelConfig, rank: int, world: int, device, seed: int = 0,
     shared = _Init(local, seed, dev, False)
     own.signs = shared.signs                         # one sign vector per width, rank-independent
     lo, hi = split_blocks(cfg.experts, world)[rank] if cfg.experts else (0, 0)
-    layers: List[LayerWeights] = []
-    for i in range(cfg.layers):
+
+    def make_layer(i: int, full_attention: bool) -> LayerWeights:
         dense_cfg = dataclasses.replace(local, experts=0, ffn=local.ffn or 128)
         own.cfg = dense_cfg if cfg.experts else local
-        lw = own.layer(i, cfg.is_full_attention(i))
+        lw = own.layer(i, full_attention)
         own.cfg = local
         if cfg.experts:
             lw.gate_up = lw.down = None
@@ -253,7 +257,10 @@ def random_shard(cfg: ModelConfig, rank: int, world: int, device, seed: int = 0,
                                                   cfg.proj_format)
                 lw.shared_down = shared.linear(cfg.hidden, cfg.shared_expert_ffn, cfg.proj_format)
             lw.shared_owner = i % world
-        layers.append(lw)
+        return lw
+
+    layers: List[LayerWeights] = [make_layer(i, cfg.is_full_attention(i))
+                                  for i in range(cfg.layers)]
     emb = quantize_linear(shared.normal(cfg.vocab, cfg.hidden), "w8", None)
     v0, v1 = lay.vocab
     if cfg.tied_embeddings:
@@ -263,13 +270,17 @@ def random_shard(cfg: ModelConfig, rank: int, world: int, device, seed: int = 0,
         head = own.linear(v1 - v0, cfg.hidden, cfg.head_format, rotate=False)
     mtp = None
     if draft_head and cfg.mtp_layers:
-        full_f = cfg.ffn or max(cfg.expert_ffn * 4, 512)
-        f0, f1 = _draft_ffn_slice(full_f, lay)
-        own.cfg = dataclasses.replace(local, experts=0, ffn=f1 - f0)
+        if cfg.draft_layer == "model":
+            draft = make_layer(cfg.layers, True)
+        else:
+            full_f = cfg.ffn or max(cfg.expert_ffn * 4, 512)
+            f0, f1 = _draft_ffn_slice(full_f, lay)
+            own.cfg = dataclasses.replace(local, experts=0, ffn=f1 - f0)
+            draft = _mtp_layer(own)
+            own.cfg = local
         mtp = MtpWeights(shared.ones(cfg.hidden), shared.ones(cfg.hidden),
                          shared.linear(cfg.hidden, 2 * cfg.hidden, "w8", rotate=False),
-                         _mtp_layer(own), shared.ones(cfg.hidden))
-        own.cfg = local
+                         draft, shared.ones(cfg.hidden))
         local = dataclasses.replace(local, mtp_layers=cfg.mtp_layers)
     out = ModelWeights(local, emb.codes, emb.scale, layers, shared.ones(cfg.hidden), head,
                        shared.signs, mtp, None)

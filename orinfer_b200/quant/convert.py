@@ -152,13 +152,37 @@ def _f16(t: torch.Tensor) -> torch.Tensor:
     return t.to(torch.float16).contiguous()
 
 
-def build_layer(cfg: ModelConfig, src: "_Source", i: int, lin) -> LayerWeights:
+DRAFT_PREFIX = "mtp."
+
+
+def has_draft_head(src: "_Source") -> bool:
+    return DRAFT_PREFIX + "fc.weight" in src.where
+
+
+def build_draft_head(cfg: ModelConfig, src: "_Source", lin):
+    """The checkpoint's draft head (``mtp.*`` tensors of the Qwen3-Next / Qwen3.5 families):
+    norms of the token embedding and of the target's hidden state, the [H, 2H] projection of
+    their concatenation (embedding half first), one full-attention decoder layer shaped like
+    the model's own, and the norm before the shared vocabulary head."""
+    from ..models.weights import MtpWeights
+    p = DRAFT_PREFIX
+    layer = build_layer(cfg, src, 0, lin, prefix=p + "layers.0.", full=True)
+    fc = quantize_linear(src.get(p + "fc.weight"), "w8", None)
+    fc = QLinear(fc.fmt, fc.n, fc.k, fc.codes.cpu(), fc.scale.cpu(), None)
+    return MtpWeights(_f16(src.get(p + "pre_fc_norm_embedding.weight")),
+                      _f16(src.get(p + "pre_fc_norm_hidden.weight")), fc, layer,
+                      _f16(src.get(p + "norm.weight")))
+
+
+def build_layer(cfg: ModelConfig, src: "_Source", i: int, lin, prefix: Optional[str] = None,
+                full: Optional[bool] = None) -> LayerWeights:
     """Assembles decoder layer ``i`` from the source tensors; ``lin(weight, fmt)`` quantises
     one projection.  Formats come from ``cfg`` (``attn_format`` / ``proj_format`` /
-    ``expert_format``)."""
+    ``expert_format``).  ``prefix`` / ``full``: a layer that lives elsewhere in the checkpoint
+    (the draft head's)."""
     f16 = _f16
-    p = f"model.layers.{i}."
-    full = cfg.is_full_attention(i)
+    p = prefix or f"model.layers.{i}."
+    full = cfg.is_full_attention(i) if full is None else full
     lw = LayerWeights("attn" if full else "gdn", f16(src.get(p + "input_layernorm.weight")),
                       f16(src.get(p + "post_attention_layernorm.weight")))
     if full:
@@ -278,6 +302,10 @@ def convert(source, output, device: str = "cpu", fast: bool = True, name: Option
     else:
         build_cfg = cfg
     src = _Source(source)
+    if has_draft_head(src):
+        import dataclasses
+        cfg = dataclasses.replace(cfg, mtp_layers=1, draft_layer="model")
+        build_cfg = dataclasses.replace(build_cfg, mtp_layers=1, draft_layer="model")
     work = output / ".convert"
     work.mkdir(parents=True, exist_ok=True)
     identity = src.identity(config_text + f"|{build_cfg.attn_format}|{build_cfg.proj_format}"
@@ -344,8 +372,28 @@ def convert(source, output, device: str = "cpu", fast: bool = True, name: Option
     else:
         hq = quantize_linear(src.get("lm_head.weight").to(dev), cfg.head_format, None, fast=fast)
         head = QLinear(hq.fmt, hq.n, hq.k, hq.codes.cpu(), hq.scale.cpu(), None)
+    mtp = None
+    if cfg.mtp_layers:
+        from ..models.weights import MtpWeights
+        dpath = work / "draft.safetensors"
+        done = record["done"].get("draft")
+        if not (done and dpath.exists() and dpath.stat().st_size == done):
+            m = build_draft_head(build_cfg, src, lin)
+            t = {"norm_e": m.norm_e, "norm_h": m.norm_h, "final_norm": m.final_norm,
+                 "fc.int8": m.fc.codes, "fc.scale": m.fc.scale}
+            t.update(_layer_tensors("layer", m.layer))
+            tmp = dpath.with_suffix(".tmp")
+            save_file({k: v.detach().cpu().contiguous() for k, v in t.items()}, str(tmp))
+            os.replace(tmp, dpath)
+            record["done"]["draft"] = dpath.stat().st_size
+            _atomic_json(record_path, record)
+        t = load_file(str(dpath))
+        fc = QLinear("w8", t["fc.int8"].shape[0], t["fc.int8"].shape[1], t["fc.int8"],
+                     t["fc.scale"], None)
+        mtp = MtpWeights(t["norm_e"], t["norm_h"], fc, _load_layer(t, "layer", "attn", signs),
+                         t["final_norm"])
     weights = ModelWeights(cfg, emb.codes, emb.scale, layers, f16(src.get("model.norm.weight")),
-                           head, signs)
+                           head, signs, mtp)
     for asset in ASSETS:
         if (source / asset).exists():
             shutil.copyfile(source / asset, output / asset)

@@ -225,6 +225,66 @@ def test_hybrid_family_reproduces_the_transformers_implementation(tmp_path):
     assert perm.tolist() == [0, 1, 4, 5, 2, 3, 6, 7] and C.rotary_permutation(8, 0).tolist() == list(range(8))
 
 
+def test_draft_head_of_a_hybrid_checkpoint_is_converted(tmp_path, monkeypatch):
+    """``mtp.*`` tensors become the draft head: a full-attention layer shaped like the model's
+    own (gated attention, routed experts, shared expert), the [H, 2H] projection and the three
+    norms.  The draft layer here is a copy of the model's last layer, so its converted form
+    must equal that layer's; the engine then speculates with the head and keeps the text."""
+    transformers = pytest.importorskip("transformers")
+    if not hasattr(transformers, "Qwen3NextForCausalLM"):
+        pytest.skip("this transformers has no Qwen3-Next")
+    from safetensors.torch import load_file
+    from orinfer_b200.config import LoadOptions, SchedulerOptions
+    from orinfer_b200.engine.checkpoint import load_model
+    from orinfer_b200.engine.engine import Engine
+    torch.manual_seed(0)
+    cfg = transformers.Qwen3NextConfig(
+        hidden_size=H, num_hidden_layers=4, num_attention_heads=HEADS, num_key_value_heads=KV,
+        head_dim=D, vocab_size=V, intermediate_size=FFN, moe_intermediate_size=128,
+        shared_expert_intermediate_size=128, num_experts=4, num_experts_per_tok=2,
+        linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=64,
+        linear_value_head_dim=64, partial_rotary_factor=0.25, rope_theta=10000.0,
+        tie_word_embeddings=False, max_position_embeddings=512)
+    transformers.Qwen3NextForCausalLM(cfg).float().eval().save_pretrained(
+        tmp_path / "hf", safe_serialization=True)
+    have = {}
+    for f in (tmp_path / "hf").glob("*.safetensors"):
+        have.update(load_file(str(f)))
+    g = torch.Generator().manual_seed(3)
+    extra = {k.replace("model.layers.3.", "mtp.layers.0."): v.clone()
+             for k, v in have.items() if k.startswith("model.layers.3.")}
+    extra["mtp.fc.weight"] = torch.randn(H, 2 * H, generator=g) * 0.05
+    extra["mtp.pre_fc_norm_embedding.weight"] = 0.2 * torch.randn(H, generator=g)
+    extra["mtp.pre_fc_norm_hidden.weight"] = 0.2 * torch.randn(H, generator=g)
+    extra["mtp.norm.weight"] = 0.2 * torch.randn(H, generator=g)
+    save_file({k: v.contiguous() for k, v in extra.items()}, str(tmp_path / "hf/mtp.safetensors"))
+    fmts = {"attn_format": "w8", "proj_format": "w8", "expert_format": "w8"}
+    w = load_model(C.convert(tmp_path / "hf", tmp_path / "out", formats=fmts))
+    c, m = w.config, w.mtp
+    assert c.mtp_layers == 1 and c.draft_layer == "model" and m is not None
+    last = w.layers[3]
+    assert torch.equal(m.layer.qkv.codes, last.qkv.codes) and m.layer.qkv.n == last.qkv.n
+    assert torch.equal(m.layer.expert_down.codes, last.expert_down.codes)
+    assert torch.equal(m.layer.router, last.router)
+    assert torch.equal(m.layer.shared_gate_up.codes, last.shared_gate_up.codes)
+    assert m.fc.signs is None and m.fc.n == H and m.fc.k == 2 * H
+    got = m.fc.integers().float() * m.fc.scale.float()[:, None]
+    assert float((got - extra["mtp.fc.weight"]).norm() / extra["mtp.fc.weight"].norm()) < 0.02
+    assert torch.allclose(m.norm_e.float(), extra["mtp.pre_fc_norm_embedding.weight"], atol=1e-3)
+    assert torch.allclose(m.final_norm.float(), extra["mtp.norm.weight"], atol=1e-3)
+    # speculation with the converted head never changes the text
+    monkeypatch.setenv("ORINFER_SINGLE_MTP_POLICY", "fixed2")
+    ids = torch.randint(0, V, (20,), generator=torch.Generator().manual_seed(1)).tolist()
+    mk = lambda drafts: Engine(w, load=LoadOptions(mtp_drafts=drafts, prefix_cache_bytes=0),
+                               sched=SchedulerOptions(max_active=2, prefill_chunk=16),
+                               kv_pages=8, max_context=256)
+    plain = mk(0).generate([ids], max_new=8)[0]
+    eng = mk(2)
+    assert eng.runner_has_mtp() and eng.spec.enabled
+    assert eng.generate([ids], max_new=8)[0] == plain
+    assert eng.spec.statistics()["proposed_tokens"] > 0
+
+
 def test_llama_style_checkpoints_convert_too(tmp_path):
     """The same decoder without per-head q / k norms (Llama, Mistral)."""
     transformers = pytest.importorskip("transformers")

@@ -148,21 +148,30 @@ def test_tp2_engine_samples_from_sharded_candidates(tmp_path):
     assert r0["sharded"] == 20                       # two sampled requests x 10 tokens
 
 
-def _draft_worker(rank, world, port, out_dir):
+def _draft_cfg(preset):
+    import dataclasses
+    from orinfer_b200.config import PRESETS
+    return dataclasses.replace(PRESETS[preset], mtp_layers=1,
+                               draft_layer="dense" if preset == "tiny" else "model")
+
+
+def _draft_worker(rank, world, port, out_dir, preset):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    import dataclasses
     torch.set_num_threads(2)
-    from orinfer_b200.config import PRESETS
     from orinfer_b200.models.runner import KVPool, Packet
     from orinfer_b200.models.weights import random_model
     from orinfer_b200.parallel.tp import shard_model
     from orinfer_b200.parallel.tp_runner import TPTorchRunner
-    cfg = dataclasses.replace(PRESETS["tiny"], mtp_layers=1)
+    cfg = _draft_cfg(preset)
     shard = shard_model(random_model(cfg, seed=0), rank, world, draft_head=True)
-    assert shard.config.mtp_layers == 1 and shard.mtp.layer.gate_up.n == cfg.ffn * 2 // world
+    assert shard.config.mtp_layers == 1
+    if cfg.experts:
+        assert shard.mtp.layer.expert_down.experts == cfg.experts // world
+    else:
+        assert shard.mtp.layer.gate_up.n == cfg.ffn * 2 // world
     assert shard.mtp.layer.o.k == cfg.q_heads * cfg.head_dim // world
     runner = TPTorchRunner(shard, KVPool.allocate(shard.config, 4, "cpu", 1), 64)
     ids, p = _draft_inputs(cfg, Packet)
@@ -179,19 +188,19 @@ def _draft_inputs(cfg, Packet):
     return ids, Packet(ids, t([0] * 16), t(list(range(16))), t([[1]]), 16, 16)
 
 
-def test_sharded_draft_head_matches_the_whole_one(tmp_path):
-    """The draft head split over two ranks (heads, FFN channels, vocabulary) gives the hidden
-    rows and draft tokens of the unsplit head, up to the per-shard activation scales."""
-    import dataclasses
-    from orinfer_b200.config import PRESETS
+@pytest.mark.parametrize("preset", ["tiny", "tiny-moe"])
+def test_sharded_draft_head_matches_the_whole_one(tmp_path, preset):
+    """The draft head split over two ranks (heads, FFN channels or experts, vocabulary) gives
+    the hidden rows and draft tokens of the unsplit head, up to the per-shard activation
+    scales."""
     from orinfer_b200.models.runner import KVPool, Packet
     from orinfer_b200.models.torch_runner import TorchRunner
     from orinfer_b200.models.weights import random_model
     port = 31500 + os.getpid() % 2000
-    mp.spawn(_draft_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_draft_worker, args=(2, port, str(tmp_path), preset), nprocs=2, join=True)
     r0, r1 = torch.load(tmp_path / "d0.pt"), torch.load(tmp_path / "d1.pt")
     assert torch.equal(r0["tok"], r1["tok"]) and torch.equal(r0["hid"], r1["hid"])
-    cfg = dataclasses.replace(PRESETS["tiny"], mtp_layers=1)
+    cfg = _draft_cfg(preset)
     full = random_model(cfg, seed=0)
     runner = TorchRunner(full, KVPool.allocate(cfg, 4, "cpu", 1), 64)
     ids, p = _draft_inputs(cfg, Packet)
@@ -200,3 +209,20 @@ def test_sharded_draft_head_matches_the_whole_one(tmp_path):
     cos = torch.nn.functional.cosine_similarity(r0["hid"].float(), hid.float(), dim=1)
     assert cos.min() > 0.995, cos
     assert (r0["tok"].long() == tok.long()).float().mean() >= 0.75
+
+
+def test_random_shards_carry_a_draft_head_only_when_asked():
+    from orinfer_b200.parallel.tp import random_shard
+    for preset in ("tiny", "tiny-moe"):
+        cfg = _draft_cfg(preset)
+        assert random_shard(cfg, 0, 2, "cpu").mtp is None
+        shards = [random_shard(cfg, r, 2, "cpu", draft_head=True) for r in range(2)]
+        for r, s in enumerate(shards):
+            assert s.config.mtp_layers == 1 and s.mtp.fc.k == 2 * cfg.hidden
+            assert s.mtp.layer.o.k == cfg.q_heads * cfg.head_dim // 2
+            if cfg.experts:
+                assert s.mtp.layer.expert_down.base == r * cfg.experts // 2
+                assert torch.equal(s.mtp.layer.router, shards[0].mtp.layer.router)
+            else:
+                assert s.mtp.layer.gate_up.n == cfg.ffn
+        assert torch.equal(shards[0].mtp.fc.codes, shards[1].mtp.fc.codes)     # replicated
