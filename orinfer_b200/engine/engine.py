@@ -24,7 +24,7 @@ from __future__ import annotations
 
 import collections
 import dataclasses
-
+import os
 import time
 from collections import deque
 from dataclasses import dataclass, field
@@ -54,6 +54,7 @@ class EngineStatistics:
     graph_hits: int = 0
     graph_captures: int = 0
     direct_packets: int = 0
+    packed_uploads: int = 0                   # packets whose index arrays went up in one copy
     admitted: int = 0
     deferred_admissions: int = 0
     finished: int = 0
@@ -214,6 +215,8 @@ class Engine:
         self._graphs: Dict[int, _DecodeGraph] = {}
         self._next_rid = 1
         self._pin = {}
+        self._stage = None                       # pinned staging ring of ``_upload_many``
+        self._packed_uploads = os.environ.get("ORINFER_PACKED_UPLOAD", "1") != "0"
         from .speculation import Speculator
         self.spec = Speculator(self, self.load.mtp_drafts, self.load.prompt_lookup)
         self.tpot_ewma: Optional[float] = None
@@ -872,6 +875,67 @@ class Engine:
             return host[:n].clone()
         return host[:n].to(self.device, non_blocking=True)
 
+    STAGE_BYTES = 4 << 20
+
+    def _upload_many(self, parts: Dict[str, Optional[List[int]]]) -> Dict[str, torch.Tensor]:
+        """All index arrays of one packet in ONE host-to-device copy: the arrays are written
+        at 128-byte aligned offsets into a region of a pinned staging ring (regions are handed
+        out in submission order and reused only after the copy that read them has completed),
+        copied as one block, and returned as int32 views of that block.  ``None`` entries are
+        skipped.  Packets too large for the ring, and engines started with
+        ``ORINFER_PACKED_UPLOAD=0``, upload every array on its own."""
+        names = [k for k, v in parts.items() if v is not None]
+        offs, total = {}, 0
+        for k in names:
+            offs[k] = total
+            total += (4 * len(parts[k]) + 127) // 128 * 128
+        if not self._packed_uploads or total == 0 or total > self.STAGE_BYTES // 4:
+            return {k: self._upload(k, parts[k]) for k in names}
+        from ..core import transfers
+        if self._stage is None:
+            self._stage = torch.empty(self.STAGE_BYTES, dtype=torch.uint8)
+            if self.on_gpu:
+                self._stage = self._stage.pin_memory()
+            self._stage_np = self._stage.numpy()
+            self._stage_ring = transfers.StagingRing(self.STAGE_BYTES, 256)
+            self._stage_inflight: Deque[tuple] = collections.deque()
+        while self._stage_inflight and self._stage_inflight[0][1].query():
+            self._stage_ring.retire_through(self._stage_inflight.popleft()[0])
+        got = self._stage_ring.acquire(total)
+        if got is None:                          # ring full: wait for the copies in flight
+            while self._stage_inflight:
+                ticket, event = self._stage_inflight.popleft()
+                event.synchronize()
+                self._stage_ring.retire_through(ticket)
+            got = self._stage_ring.acquire(total)
+            if got is None:
+                return {k: self._upload(k, parts[k]) for k in names}
+        ticket, base = got
+        image = self._stage_np[base:base + total]
+        ranges = transfers.pack_inputs(
+            image, [(offs[k], np.asarray(parts[k], dtype=np.int32)) for k in names],
+            merge_gap=128)
+        if not ranges:
+            self._stage_ring.retire_through(ticket)
+            return {k: self._upload(k, parts[k]) for k in names}
+        lo, hi = ranges[0][0], ranges[-1][0] + ranges[-1][1]
+        block = self._stage[base + lo:base + hi]
+        if self.on_gpu:
+            dev = block.to(self.device, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record()
+            self._stage_inflight.append((ticket, event))
+        else:
+            dev = block.clone()
+            self._stage_ring.retire_through(ticket)
+        self.stats.packed_uploads += 1
+        out = {}
+        for k in names:
+            o, n = offs[k] - lo, 4 * len(parts[k])
+            out[k] = dev[o:o + n].view(torch.int32) if n else \
+                torch.empty(0, dtype=torch.int32, device=dev.device)
+        return out
+
     # ------------------------------------------------------------------ device commands
     def _publish(self, op: str, payload=None) -> None:
         if self.channel is not None:
@@ -936,16 +1000,18 @@ class Engine:
             raise ValueError("segment lengths do not add up to the packet's rows")
         self._publish("verify", (list(ids), list(rows_req), list(pos), int(max_kv), bool(need),
                                  seg_lens))
-        packet = Packet(self._upload("ids", ids), self._upload("req", rows_req),
-                        self._upload("pos", pos), self.page_table_dev, len(ids), max_kv)
+        segs, first, start = [], [], 0
+        for n in seg_lens or ():
+            segs += [start, n, 0, 0]
+            first += [start] * n
+            start += n
+        dev = self._upload_many({"ids": list(ids), "req": list(rows_req), "pos": list(pos),
+                                 "segs": segs if seg_lens else None,
+                                 "first": first if seg_lens else None})
+        packet = Packet(dev["ids"], dev["req"], dev["pos"], self.page_table_dev, len(ids), max_kv)
         if seg_lens:
-            segs, first, start = [], [], 0
-            for n in seg_lens:
-                segs += [start, n, 0, 0]
-                first += [start] * n
-                start += n
-            packet.segments = self._upload("segs", segs).view(-1, 4)
-            packet.row_first = self._upload("first", first)
+            packet.segments = dev["segs"].view(-1, 4)
+            packet.row_first = dev["first"]
             packet.n_segments = len(seg_lens)
             packet.tentative = True
             self._tentative = packet
@@ -1012,15 +1078,20 @@ class Engine:
 
     def _build_packet(self, spec: dict) -> Packet:
         rows = len(spec["ids"])
-        packet = Packet(self._upload("ids", spec["ids"]), self._upload("req", spec["req"]),
-                        self._upload("pos", spec["pos"]), self.page_table_dev, rows,
-                        spec["max_kv"], self._upload("sel", spec["sel"]).long())
+        chunked = bool(spec["chunks"] and self.on_gpu)
+        dev = self._upload_many({
+            "ids": spec["ids"], "req": spec["req"], "pos": spec["pos"], "sel": spec["sel"],
+            "segs": spec["segs"] if self.recurrent else None,
+            "first": spec["first"] if self.recurrent else None,
+            "chunks": spec["chunks"] if chunked else None})
+        packet = Packet(dev["ids"], dev["req"], dev["pos"], self.page_table_dev, rows,
+                        spec["max_kv"], dev["sel"].long())
         if self.recurrent:
-            packet.segments = self._upload("segs", spec["segs"]).view(-1, 4)
-            packet.row_first = self._upload("first", spec["first"])
+            packet.segments = dev["segs"].view(-1, 4)
+            packet.row_first = dev["first"]
             packet.n_segments = len(spec["segs"]) // 4
-        if spec["chunks"] and self.on_gpu:
-            packet.chunks = self._upload("chunks", spec["chunks"]).view(-1, 4)
+        if chunked:
+            packet.chunks = dev["chunks"].view(-1, 4)
             packet.max_q_len = max(spec["chunks"][1::4])
             packet.decode_rows = spec["n_decode"]
         return packet

@@ -253,6 +253,40 @@ def test_layered_prefill_lets_decoders_step_inside_a_long_prompt(weights):
     assert [a.generated, b.generated] == want
 
 
+def test_packed_uploads_equal_single_uploads_and_reuse_the_ring(weights, monkeypatch):
+    """All index arrays of a packet travel in one staged copy; the views must hold what
+    separate uploads hold, through many wrap-arounds of the ring, with empty arrays, and fall
+    back for a packet that is too large for a region."""
+    import random
+    eng = _engine(weights)
+    rng = random.Random(0)
+    for step in range(300):
+        parts = {"ids": [rng.randrange(1000) for _ in range(rng.randrange(0, 700))],
+                 "req": [rng.randrange(4) for _ in range(rng.randrange(0, 700))],
+                 "none": None, "sel": [rng.randrange(9)], "empty": []}
+        got = eng._upload_many(parts)
+        assert set(got) == {"ids", "req", "sel", "empty"}
+        for k, v in got.items():
+            assert v.dtype == torch.int32 and v.tolist() == parts[k] and v.is_contiguous()
+    assert eng.stats.packed_uploads == 300
+    big = {"ids": list(range(eng.STAGE_BYTES // 8))}          # over a quarter of the ring
+    assert eng._upload_many(big)["ids"].tolist() == big["ids"]
+    assert eng.stats.packed_uploads == 300
+    # a ring much smaller than the traffic: regions are reused only after they were retired
+    monkeypatch.setattr(type(eng), "STAGE_BYTES", 1 << 14)
+    small = _engine(weights)
+    for step in range(200):
+        parts = {"a": [step] * 500, "b": [step + 1] * 300}
+        got = small._upload_many(parts)
+        assert got["a"].tolist() == parts["a"] and got["b"].tolist() == parts["b"]
+    st = small._stage_ring.stats()
+    assert st["live"] == 0 and st["peak"] <= 1 << 14 and small.stats.packed_uploads == 200
+    monkeypatch.setenv("ORINFER_PACKED_UPLOAD", "0")
+    plain = _engine(weights)
+    assert plain._upload_many({"a": [1, 2, 3]})["a"].tolist() == [1, 2, 3]
+    assert plain.stats.packed_uploads == 0 and plain._stage is None
+
+
 def test_follower_commands_check_what_they_can(weights):
     """``Engine.apply`` is what a follower rank runs: a host-tier save must land in the slot
     the leader announced, a host-tier command needs a store, unknown commands are refused."""
