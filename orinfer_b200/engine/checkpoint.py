@@ -209,7 +209,7 @@ def load_model(directory, device="cpu", verify: bool = False,
         raise CheckpointError(str(e)) from e
     to_gpu = torch.device(device).type == "cuda"
     try:
-        t, meta = read_tensors(directory / "model.safetensors", workers=workers, pin=to_gpu,
+        t, meta = read_tensors(directory / "model.safetensors", workers=workers, device=device,
                                digests=desc["tensors"] if verify else None)
     except WeightReadError as e:
         raise CheckpointError(str(e)) from e
@@ -218,7 +218,7 @@ def load_model(directory, device="cpu", verify: bool = False,
             raise CheckpointError(f"quantisation contract mismatch on {key}")
     if verify and set(desc["tensors"]) - set(t):
         raise CheckpointError(f"tensors missing: {sorted(set(desc['tensors']) - set(t))[:3]}")
-    if not np.array_equal(t["orinfer.e8p_q4.basis"].numpy(), np.array(e8p.basis())):
+    if not np.array_equal(t["orinfer.e8p_q4.basis"].cpu().numpy(), np.array(e8p.basis())):
         raise CheckpointError("E8P basis in the checkpoint differs from the codec's")
     t = {k: v.to(device, non_blocking=to_gpu) for k, v in t.items()}
     if to_gpu:

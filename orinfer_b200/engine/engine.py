@@ -70,6 +70,7 @@ class EngineStatistics:
     restored_pages: int = 0
     sharded_samples: int = 0                  # rows drawn from a sharded head's candidates
     layered_decode_steps: int = 0             # decode steps taken inside paused prefill packets
+    mixed_verify_packets: int = 0             # prefill packets that also verified drafts
     resident_steps: int = 0                   # decode steps that needed no input upload
     stored_snapshots: int = 0                 # recurrent-state endpoints kept for the prefix cache
     restored_snapshots: int = 0
@@ -156,6 +157,9 @@ class Engine:
         self._tentative: Optional[Packet] = None     # verification packet awaiting its commit
         # hidden rows the draft head has not seen yet: rid -> [(first position, rows)]
         self._mtp_backlog: Dict[int, list] = {}
+        # decoders of the current direct packet that verify drafts: rid -> (drafts, first row)
+        self._verify: Dict[int, tuple] = {}
+        self._direct_rows = 0
         self.max_context = max_context or min(self.cfg.max_context, 32768)
         self.max_pages_per_req = (self.max_context + PAGE_TOKENS - 1) // PAGE_TOKENS
         self.max_rows = max_rows or max(self.sched.prefill_chunk + self.sched.max_active, 256)
@@ -802,6 +806,7 @@ class Engine:
         """Run one packet; returns the requests that produced tokens."""
         if self.failed is not None:
             raise self.failed
+        self._verify = {}
         for r in list(self.running):
             if r.cancelled:
                 self._finish(r, "cancelled")
@@ -835,7 +840,13 @@ class Engine:
               and getattr(self.runner, "supports_stages", False)):
             tokens, logits, order = self._run_layered(decoders, chunks, early)
         else:
-            tokens, logits, order = self._run_direct(decoders, chunks)
+            # prompt chunks do not stop speculation: greedy decoders bring their drafts into
+            # the same packet as verification rows (attention-only models)
+            drafts = None
+            if chunks and decoders and self.spec.enabled and not self.recurrent:
+                room = min(self.max_rows, self.row_cap) - len(decoders) - sum(n for _, n in chunks)
+                drafts = self.spec.plan_mixed(decoders, room)
+            tokens, logits, order = self._run_direct(decoders, chunks, drafts)
         t1 = time.monotonic()
         produced = early + [r for r in self._commit(order, tokens, logits) if r not in early]
         self._capture_snapshots(chunks)
@@ -1151,18 +1162,28 @@ class Engine:
             graphed = self._prefill_graph(packet, need, *plan)
         return graphed if graphed is not None else self.runner.greedy(packet, need_logits=need)
 
-    def _run_direct(self, decoders: List[Request], chunks):
+    def _run_direct(self, decoders: List[Request], chunks, drafts: Optional[dict] = None):
+        """``drafts``: rid -> draft tokens of decoders that verify them in this packet (their
+        rows are ``[pending, d1, ..]`` at consecutive positions, every row's token is read
+        back, and ``_commit`` keeps the accepted prefix)."""
         t0 = time.monotonic()
         ids, req_rows, pos, logit_rows, order, chunk_rows = [], [], [], [], [], []
         max_kv = 1
+        self._verify = {}
         for r in decoders:
-            ids.append(r.pending)
-            req_rows.append(r.slot)
-            pos.append(r.offset)
-            logit_rows.append(len(ids) - 1)
-            order.append((r, 1, True))
-            max_kv = max(max_kv, r.offset + 1)
+            toks = [r.pending] + list((drafts or {}).get(r.rid, ()))
+            first = len(ids)
+            ids += toks
+            req_rows += [r.slot] * len(toks)
+            pos += list(range(r.offset, r.offset + len(toks)))
+            logit_rows += list(range(first, first + len(toks)))
+            order.append((r, len(toks), True))
+            if len(toks) > 1:
+                self._verify[r.rid] = (toks[1:], first)
+            max_kv = max(max_kv, r.offset + len(toks))
         n_decode = len(ids)
+        if self._verify:
+            self.stats.mixed_verify_packets += 1
         for r, n in chunks:
             chunk_rows.append([len(ids), n, r.offset, r.slot])
             ids += r.prompt[r.offset:r.offset + n]
@@ -1199,10 +1220,12 @@ class Engine:
         self._status_enqueue()
         tokens = tok.cpu()                           # one readback (synchronises)
         self._status_check()
+        self._direct_rows = rows
         if self.spec.enabled and self.runner_has_mtp():
             info, row0 = [], 0
             for r, n, _has in order:
-                info.append((r, row0, n, r.offset))
+                if r.rid not in self._verify:       # verified rows: captured once accepted
+                    info.append((r, row0, n, r.offset))
                 row0 += n
             self.spec.capture(info, self.runner.final_hidden(rows))
         self.stats.direct_packets += 1
@@ -1400,13 +1423,13 @@ class Engine:
 
     def _sharded_samples(self, order) -> Dict[int, int]:
         rows, reqs, sel = [], [], 0
-        for r, _n, has_logits in order:
+        for r, n, has_logits in order:
             if not has_logits:
                 continue
             if self._sharded(r):
                 rows.append(sel)
                 reqs.append(r)
-            sel += 1
+            sel += self._logit_rows(r, n)
         if not rows:
             return {}
         options = [r.sampling for r in reqs]
@@ -1423,14 +1446,14 @@ class Engine:
         if not self.on_gpu or logits is None or not logits.is_cuda:
             return {}
         rows, reqs, sel = [], [], 0
-        for r, _n, has_logits in order:
+        for r, n, has_logits in order:
             if not has_logits:
                 continue
             if (not self._plain(r) and not self._sharded(r) and r.constraint is None
                     and not r.want_logprobs and r.sampling.device_topk):
                 rows.append(sel)
                 reqs.append(r)
-            sel += 1
+            sel += self._logit_rows(r, n)
         if not rows:
             return {}
         from ..ops import functional as F
@@ -1446,6 +1469,28 @@ class Engine:
         self.stats.device_samples += len(rows)
         return {row: t for row, t, f in zip(rows, tok, flag) if not f}
 
+    def _logit_rows(self, r: Request, n: int) -> int:
+        """Rows of the logit selection that belong to an entry with logits: every row of a
+        decoder that verifies drafts, else one."""
+        return n if r.rid in self._verify else 1
+
+    def _commit_verified(self, r: Request, n: int, tokens, sel: int) -> None:
+        """A greedy decoder's verification rows inside a mixed packet: keep the longest draft
+        prefix the model agrees with plus its own next token."""
+        drafts, first = self._verify[r.rid]
+        commit = S.greedy_commit(drafts, tokens[sel:sel + n])
+        accepted = len(commit) - 1
+        self.spec.observe_mixed(r, drafts, accepted)
+        if self.runner_has_mtp():
+            self.spec.capture([(r, first, 1 + accepted, r.offset)],
+                              self.runner.final_hidden(self._direct_rows))
+        r.offset += 1 + accepted
+        self.stats.decode_tokens += n
+        for tok in commit:
+            if r.finished:
+                break
+            self._deliver(r, int(tok))
+
     def _commit(self, order, tokens, logits) -> List[Request]:
         produced = []
         sel = 0
@@ -1456,6 +1501,11 @@ class Engine:
             tokens = tokens.tolist()
         for r, n, has_logits in order:
             was_decode = r.phase is Phase.DECODE
+            if was_decode and r.rid in self._verify:
+                self._commit_verified(r, n, tokens, sel)
+                sel += n
+                produced.append(r)
+                continue
             r.offset += n
             if not was_decode:
                 r.last_prefill_at = now
@@ -1468,6 +1518,7 @@ class Engine:
             tok = drawn[row] if row in drawn else self._sample(r, tokens, logits, row)
             self._deliver(r, tok)
             produced.append(r)
+        self._verify = {}
         return produced
 
     def _deliver(self, r: Request, tok: int) -> None:

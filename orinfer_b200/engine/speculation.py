@@ -170,6 +170,47 @@ class Speculator:
                 out[r.rid].append(int(t))
         return out
 
+    # ------------------------------------------------------------------ inside prefill packets
+    def plan_mixed(self, decoders: List[Request], room: int) -> Optional[Dict[int, List[int]]]:
+        """Drafts of the greedy decoders for a packet that also carries prompt chunks:
+        rid -> drafts, at most ``room`` draft rows in all; None when nobody drafts.  The
+        width is the controller's choice for this many decoders (its round costs are learnt
+        from pure verification rounds only)."""
+        eng = self.engine
+        if room <= 0 or not decoders:
+            return None
+        remaining = min(r.max_new - len(r.generated) for r in decoders)
+        width = self.choose_width(len(decoders), remaining)
+        self.calls += 1
+        if width < 2:
+            return None
+        plain = [r for r in decoders if eng._plain(r)]
+        plans: Dict[int, List[int]] = {}
+        for r in plain:
+            plans[r.rid] = self.drafts_for(r, min(width - 1, r.max_new - len(r.generated) - 1))
+        if eng.runner_has_mtp():
+            need = [r for r in plain if not plans[r.rid]]
+            cap = min([r.max_new - len(r.generated) - 1 for r in need], default=0)
+            for rid, d in self.mtp_drafts(need, min(width - 1, cap)).items():
+                plans[rid] = d
+        out: Dict[int, List[int]] = {}
+        for r in plain:
+            d = plans.get(r.rid) or []
+            d = d[:max(room, 0)]
+            if d:
+                out[r.rid] = d
+                room -= len(d)
+        return out or None
+
+    def observe_mixed(self, r: Request, drafts: List[int], accepted: int) -> None:
+        self.acceptance.observe([(len(drafts), accepted)])
+        self.rounds += 1
+        self.proposed += len(drafts)
+        self.accepted += accepted
+        self.committed += 1
+        if r.rid in self.lookups:
+            self.lookups[r.rid].observe(accepted, len(drafts), len(r.history))
+
     # ------------------------------------------------------------------ one round
     def run(self, decoders: List[Request]) -> Optional[List[Request]]:
         """Runs one verification packet; None when no request had a draft (caller falls

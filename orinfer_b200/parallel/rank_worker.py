@@ -57,8 +57,13 @@ def load_shard(spec: dict, rank: int, world: int, device):
             cfg = dataclasses.replace(cfg, mtp_layers=int(spec["mtp_layers"]))
         return random_shard(cfg, rank, world, device, seed=0, draft_head=draft)
     from ..engine.checkpoint import load_model
-    return shard_model(load_model(spec["model_dir"], device, verify=False), rank, world,
-                       draft_head=draft)
+    # cut the shard out on the host and upload only that: no rank holds the whole model on
+    # its device (and the loader's arena of the whole model is released with the host copy)
+    shard = shard_model(load_model(spec["model_dir"], "cpu", verify=False), rank, world,
+                        draft_head=draft)
+    out = shard.to(device)
+    out.tp, out.global_config = shard.tp, shard.global_config
+    return out
 
 
 def build_engine(spec: dict, weights, channel=None):

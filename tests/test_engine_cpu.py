@@ -194,6 +194,58 @@ def test_mtp_head_speculation_preserves_greedy_output():
     assert st["rounds"] > 0 and st["proposed_tokens"] >= 2 * st["rounds"]
 
 
+def test_drafts_are_verified_inside_packets_that_carry_prompt_chunks(monkeypatch):
+    """A prompt that arrives while others decode does not stop their speculation: the greedy
+    decoders' verification rows travel in the same packets as its chunks.  Texts equal plain
+    decoding for right, wrong and half-right drafts and for the draft head; a sampled decoder
+    rides along with one row."""
+    import dataclasses
+    monkeypatch.setenv("ORINFER_SINGLE_MTP_POLICY", "fixed3")
+    cfg = dataclasses.replace(PRESETS["tiny"], mtp_layers=1)
+    w = random_model(cfg, seed=4)
+    early = _prompts(2, 12, seed=5)
+    late = _prompts(1, 150, seed=6)[0]
+    sampled = SamplingOptions(temperature=0.7, seed=9)
+
+    def run(load, drafts=None, sampler=None):
+        eng = _engine(w, load=load, prefill_chunk=32, max_active=4)
+        if drafts is not None:
+            eng.spec.drafts_for = lambda r, c: drafts(r, c)
+        reqs = [eng.submit(early[0], 40), eng.submit(early[1], 40, sampling=sampler)]
+        for _ in range(2):
+            eng.step()
+        reqs.append(eng.submit(late, 6))              # five 32-row chunks beside the decoders
+        while eng.has_work():
+            eng.step()
+        return eng, reqs
+
+    _, want = run(LoadOptions(mtp_drafts=0))
+    text = {tuple(r.prompt): r.generated for r in want}
+    oracle = lambda r, c: text[tuple(r.prompt)][len(r.generated):len(r.generated) + c]
+    wrong = lambda r, c: [(t + 1) % cfg.vocab for t in oracle(r, c)]
+    half = lambda r, c: oracle(r, c)[:1] + wrong(r, c)[1:]
+    for name, drafts in (("oracle", oracle), ("wrong", wrong), ("half", half)):
+        eng, got = run(LoadOptions(prompt_lookup=True, mtp_drafts=3), drafts)
+        assert [r.generated for r in got] == [r.generated for r in want], name
+        assert eng.stats.mixed_verify_packets >= 2, name
+        st = eng.spec.statistics()
+        if name == "oracle":
+            assert st["acceptance_rate"] == 1.0
+        if name == "wrong":
+            assert st["accepted_draft_tokens"] == 0 and st["proposed_tokens"] > 0
+    # the draft head proposes (its backlog stays whole across mixed packets)
+    eng, got = run(LoadOptions(mtp_drafts=2))
+    assert eng.runner_has_mtp() and eng.stats.mixed_verify_packets >= 2
+    assert [r.generated for r in got] == [r.generated for r in want]
+    # a sampled decoder keeps its sample path: it never drafts inside a mixed packet
+    _, want_s = run(LoadOptions(mtp_drafts=0), sampler=sampled)
+    eng, got_s = run(LoadOptions(prompt_lookup=True, mtp_drafts=3), oracle_s := (
+        lambda r, c: {tuple(q.prompt): q.generated for q in want_s}[tuple(r.prompt)]
+        [len(r.generated):len(r.generated) + c]), sampler=sampled)
+    assert got_s[0].generated == want_s[0].generated and got_s[2].generated == want_s[2].generated
+    assert len(got_s[1].generated) == 40
+
+
 def test_host_kv_offload_restores_evicted_prefix(weights):
     """With a host tier, prefixes evicted under page pressure come back from pinned host memory
     instead of being recomputed, and the restored KV gives the same tokens."""

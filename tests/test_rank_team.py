@@ -195,6 +195,32 @@ def test_draft_head_speculation_runs_sharded_on_every_rank(monkeypatch):
     assert all(p.returncode == 0 for p in team.procs)
 
 
+def test_ranks_cut_their_shards_out_of_a_model_directory(tmp_path):
+    """A saved model served by two ranks: every rank reads the checkpoint on the host, keeps
+    its shard and uploads that; the text is the unsharded model's up to the shard scales."""
+    from orinfer_b200.config import PRESETS
+    from orinfer_b200.engine.checkpoint import save_model
+    from orinfer_b200.engine.engine import Engine
+    from orinfer_b200.models.weights import random_model
+    from orinfer_b200.parallel.rank_worker import leader_engine
+    w = random_model(PRESETS["tiny"], seed=3)
+    save_model(w, tmp_path / "m", "tiny")
+    prompts = [[(5 * i + j) % 700 + 1 for i in range(30)] for j in range(2)]
+    whole = Engine(w, kv_pages=16, max_context=512).generate(prompts, max_new=4)
+    engine, team = leader_engine(dict(SPEC, preset=None, model_dir=str(tmp_path / "m")),
+                                 deadline_s=90.0)
+    try:
+        assert engine.w.tp.world == 2 and engine.w.config.q_heads == PRESETS["tiny"].q_heads // 2
+        out = engine.generate(prompts, max_new=4)
+        team.channel.sync(90.0)
+        same = sum(a == b for o, v in zip(out, whole) for a, b in zip(o, v))
+        assert same >= 6, (out, whole)             # random weights: near-ties may flip a token
+        assert team.channel.failure is None
+    finally:
+        team.close(engine)
+    assert all(p.returncode == 0 for p in team.procs)
+
+
 def test_follower_that_stops_replying_fails_the_leader_closed():
     from orinfer_b200.parallel.rank_channel import RankFailure
     from orinfer_b200.parallel.rank_worker import leader_engine
