@@ -98,6 +98,8 @@ void orinfer_acceptance_observe(void* h, const int* proposed, const int* accepte
 double orinfer_acceptance_rate(void* h, int position, double prior);
 double orinfer_acceptance_expected(void* h, int drafts);
 double orinfer_mtp_progress(const double* yields, int n, int batch, int latency);
+int orinfer_mtp_allocate(const double* rate, const int* cap, int n, int budget, double floor,
+                         int* counts);
 int orinfer_mtp_select(const OrinferMtpSelection* in, const OrinferMtpCandidate* cands, int n,
                        int* flags);
 void* orinfer_lookup_create(void);

@@ -138,6 +138,41 @@ double orinfer_mtp_progress(const double* yields, int n, int batch, int latency)
   return latency ? static_cast<double>(batch) * batch / acc : acc;
 }
 
+// Places `budget` draft rows of one verification packet on `n` requests.  Request r accepts
+// each of its drafts with probability rate[r] given that the one before was accepted, so its
+// j-th draft is worth rate[r]^j committed tokens: rows go one at a time to the request whose
+// next draft is worth most (optimal for this separable, concave gain), never more than cap[r]
+// per request, and not at all once the next draft is worth less than `floor`.  Ties go to the
+// request with fewer rows, then the lower index, so equal requests get equal shares.  Returns
+// the rows placed.  Role of the reference's per-request draft selection under a
+// verification-row budget (models/deepseek_v41/provider/dspark.rs:55-100, dspark/policy.rs).
+int orinfer_mtp_allocate(const double* rate, const int* cap, int n, int budget, double floor,
+                         int* counts) {
+  if (n <= 0) return 0;
+  std::vector<double> next(n);
+  for (int r = 0; r < n; ++r) {
+    counts[r] = 0;
+    const double a = std::min(std::max(rate[r], 0.0), 1.0);
+    next[r] = cap[r] > 0 ? a : -1.0;
+  }
+  int placed = 0;
+  while (placed < budget) {
+    int best = -1;
+    for (int r = 0; r < n; ++r) {
+      if (next[r] < 0.0 || next[r] < floor) continue;
+      if (best < 0 || next[r] > next[best] + 1e-12 ||
+          (std::fabs(next[r] - next[best]) <= 1e-12 && counts[r] < counts[best]))
+        best = r;
+    }
+    if (best < 0) break;
+    ++counts[best];
+    ++placed;
+    const double a = std::min(std::max(rate[best], 0.0), 1.0);
+    next[best] = counts[best] < cap[best] ? next[best] * a : -1.0;
+  }
+  return placed;
+}
+
 // Returns the chosen candidate id or -1 (plain decode); flags: bit0 exploring, bit1 calibrating.
 int orinfer_mtp_select(const OrinferMtpSelection* in, const OrinferMtpCandidate* cands, int n,
                        int* flags) {

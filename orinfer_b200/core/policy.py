@@ -90,6 +90,8 @@ def _L():
     l.orinfer_acceptance_rate.argtypes = [c_void_p, c_int, c_double]
     l.orinfer_acceptance_expected.restype = c_double
     l.orinfer_acceptance_expected.argtypes = [c_void_p, c_int]
+    l.orinfer_mtp_allocate.argtypes = [POINTER(c_double), POINTER(c_int), c_int, c_int, c_double,
+                                       POINTER(c_int)]
     l.orinfer_mtp_progress.restype = c_double
     l.orinfer_mtp_progress.argtypes = [POINTER(c_double), c_int, c_int, c_int]
     l.orinfer_lookup_propose.argtypes = [c_void_p, POINTER(c_uint32), c_int, c_int, c_int,
@@ -263,6 +265,22 @@ def mtp_select(normal_s: float, batch: int, slack_s: float, candidates: Sequence
     l.orinfer_mtp_select.argtypes = [POINTER(_Sel), POINTER(_Cand), c_int, POINTER(c_int)]
     cid = l.orinfer_mtp_select(ctypes.byref(sel), arr, len(candidates), ctypes.byref(flags))
     return (None if cid < 0 else cid), bool(flags.value & 1), bool(flags.value & 2)
+
+
+def mtp_allocate(rates: Sequence[float], caps: Sequence[int], budget: int,
+                 floor: float = 0.0) -> List[int]:
+    """Draft rows per request for one verification packet of ``budget`` draft rows: request r
+    accepts each draft with probability ``rates[r]`` given the previous one, may take at most
+    ``caps[r]``, and a row is placed only while its expected yield is at least ``floor``."""
+    n = len(rates)
+    if n != len(caps):
+        raise ValueError("one cap per request")
+    if n == 0:
+        return []
+    out = (c_int * n)()
+    _L().orinfer_mtp_allocate((c_double * n)(*rates), (c_int * n)(*caps), n, int(budget),
+                              float(floor), out)
+    return list(out)
 
 
 def mtp_progress(yields: Sequence[float], batch: int, latency: bool) -> float:

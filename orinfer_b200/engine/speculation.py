@@ -52,6 +52,11 @@ class Speculator:
         self.rounds = self.proposed = self.accepted = self.committed = 0
         self.trace = os.environ.get("ORINFER_MTP_TRACE") == "1"
         self.policy = os.environ.get("ORINFER_SINGLE_MTP_POLICY", "auto")
+        # how a round's draft rows are placed on its requests: "adaptive" gives the rows of a
+        # width-w round (batch x (w - 1)) to the requests whose drafts survive most often,
+        # "uniform" gives every request w - 1
+        self.allocation = os.environ.get("ORINFER_MTP_ALLOCATION", "adaptive")
+        self.local: Dict[int, List[float]] = {}       # rid -> [draft positions tested, accepted]
 
     @property
     def backlog(self) -> Dict[int, list]:
@@ -122,6 +127,7 @@ class Speculator:
 
     def forget(self, r: Request) -> None:
         self.lookups.pop(r.rid, None)
+        self.local.pop(r.rid, None)
         self.engine._mtp_forget(r.rid)
 
     # ------------------------------------------------------------------ MTP draft head
@@ -170,6 +176,44 @@ class Speculator:
                 out[r.rid].append(int(t))
         return out
 
+    # ------------------------------------------------------------------ draft rows per request
+    LOCAL_PRIOR = 4.0            # draft positions' worth of weight of the engine-wide rate
+    MIN_YIELD = 0.05             # a draft row expected to commit fewer tokens is not spent
+
+    def local_rate(self, r: Request) -> float:
+        """Probability that a draft of this request is accepted given the one before was:
+        its own history, started from the engine-wide first-position rate."""
+        tested, accepted = self.local.get(r.rid, (0.0, 0.0))
+        prior = self.acceptance.rate(0, 0.7)
+        return (self.LOCAL_PRIOR * prior + accepted) / (self.LOCAL_PRIOR + tested)
+
+    def allocate(self, decoders: List[Request], width: int) -> Dict[int, int]:
+        """rid -> draft rows of a width-``width`` round.  One request, fixed-width policies'
+        first rounds and ``ORINFER_MTP_ALLOCATION=uniform`` give everyone ``width - 1``; else
+        the same total is placed where it is expected to commit most tokens (a request whose
+        drafts keep failing decodes plainly inside the packet, one that keeps being right
+        gets up to the draft limit)."""
+        uniform = {r.rid: width - 1 for r in decoders}
+        if len(decoders) < 2 or self.allocation != "adaptive":
+            return uniform
+        caps = [0 if r.constraint is not None else
+                max(min(self.max_drafts, r.max_new - len(r.generated) - 1), 0) for r in decoders]
+        counts = P.mtp_allocate([self.local_rate(r) for r in decoders], caps,
+                                len(decoders) * (width - 1), self.MIN_YIELD)
+        return {r.rid: c for r, c in zip(decoders, counts)}
+
+    def observe_local(self, r: Request, proposed: int, accepted: int) -> None:
+        """``proposed`` drafts of ``r`` were verified and ``accepted`` of them kept; a round in
+        which the request was given none lets its history fade towards the prior, so a text
+        that turns predictable is tried again."""
+        loc = self.local.setdefault(r.rid, [0.0, 0.0])
+        if proposed <= 0:
+            loc[0] *= 0.9
+            loc[1] *= 0.9
+            return
+        loc[0] += min(accepted + 1, proposed)
+        loc[1] += accepted
+
     # ------------------------------------------------------------------ inside prefill packets
     def plan_mixed(self, decoders: List[Request], room: int) -> Optional[Dict[int, List[int]]]:
         """Drafts of the greedy decoders for a packet that also carries prompt chunks:
@@ -203,6 +247,7 @@ class Speculator:
         return out or None
 
     def observe_mixed(self, r: Request, drafts: List[int], accepted: int) -> None:
+        self.observe_local(r, len(drafts), accepted)
         self.acceptance.observe([(len(drafts), accepted)])
         self.rounds += 1
         self.proposed += len(drafts)
@@ -221,15 +266,17 @@ class Speculator:
         self.calls += 1
         if width < 2:
             return None
+        share = self.allocate(decoders, width)
         plans: List[Tuple[Request, List[int]]] = []
         for r in decoders:
             room = r.max_new - len(r.generated) - 1
-            plans.append((r, self.drafts_for(r, min(width - 1, room))))
+            plans.append((r, self.drafts_for(r, min(share[r.rid], room))))
         if eng.runner_has_mtp():
-            need = [r for r, d in plans if not d and r.constraint is None]
+            need = [r for r, d in plans if not d and r.constraint is None and share[r.rid] > 0]
             room = min([r.max_new - len(r.generated) - 1 for r in need], default=0)
-            got = self.mtp_drafts(need, min(width - 1, room))
-            plans = [(r, d or got.get(r.rid, [])) for r, d in plans]
+            most = max([share[r.rid] for r in need], default=0)
+            got = self.mtp_drafts(need, min(most, room))
+            plans = [(r, d or got.get(r.rid, [])[:share[r.rid]]) for r, d in plans]
         if not any(d for _, d in plans):
             return None
         t0 = time.monotonic()
@@ -264,6 +311,7 @@ class Speculator:
                 commit = [eng._sample(r, tokens, logits, row)]
             accepted = len(commit) - 1
             kept_rows.append(1 + accepted)
+            self.observe_local(r, len(drafts), accepted)
             if drafts:
                 counts.append((len(drafts), accepted))
                 if r.rid in self.lookups:

@@ -168,6 +168,38 @@ def test_speculation_preserves_output(weights):
     assert eng.generate([base], max_new=24)[0] == greedy
 
 
+def test_draft_rows_go_to_the_requests_whose_drafts_survive(weights, monkeypatch):
+    """A round's draft rows are placed by each request's own acceptance history: with two
+    requests whose drafts are always right and two whose drafts are always wrong, the same row
+    budget commits more tokens than equal shares do, and every text stays the plain one."""
+    from orinfer_b200.core import policy as P
+    assert P.mtp_allocate([0.9, 0.9, 0.1, 0.5], [3, 3, 3, 3], 6) == [3, 3, 0, 0]
+    assert P.mtp_allocate([0.7, 0.7, 0.7], [3, 3, 3], 4) == [2, 1, 1]      # ties: fewest rows first
+    assert P.mtp_allocate([0.9, 0.2], [3, 3], 6, 0.1) == [3, 1]            # 0.2^2 is under the floor
+    assert P.mtp_allocate([0.9, 0.8], [2, 0], 6) == [2, 0]                 # caps
+    assert P.mtp_allocate([], [], 4) == []
+    monkeypatch.setenv("ORINFER_SINGLE_MTP_POLICY", "fixed2")
+    prompts = _prompts(4, 16, seed=21)
+    plain = _engine(weights).generate(prompts, max_new=24)
+    text = {tuple(p): t for p, t in zip(prompts, plain)}
+
+    def drafts(r, c):
+        d = list(text[tuple(r.prompt)][len(r.generated):len(r.generated) + c])
+        return d if tuple(r.prompt) in (tuple(prompts[0]), tuple(prompts[1])) else \
+            [(t + 1) % 1024 for t in d]
+
+    stats = {}
+    for mode in ("uniform", "adaptive"):
+        monkeypatch.setenv("ORINFER_MTP_ALLOCATION", mode)
+        eng = _engine(weights, load=LoadOptions(prompt_lookup=True, mtp_drafts=3))
+        eng.spec.drafts_for = drafts
+        assert eng.generate(prompts, max_new=24) == plain, mode
+        stats[mode] = eng.spec.statistics()
+    uni, ada = stats["uniform"], stats["adaptive"]
+    assert ada["acceptance_rate"] > uni["acceptance_rate"] + 0.15
+    assert ada["rounds"] <= uni["rounds"]
+
+
 def test_mtp_head_speculation_preserves_greedy_output():
     """Draft-head rounds (catch-up over the prompt, draft loop, verify, commit) leave the
     greedy text unchanged; the head of a random-init model rarely guesses right."""
