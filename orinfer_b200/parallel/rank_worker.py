@@ -98,6 +98,8 @@ def build_engine(spec: dict, weights, channel=None):
 
 def follower_main(spec: dict) -> int:
     rank, world = spec["rank"], spec["world"]
+    from . import affinity
+    affinity.bind_rank(rank, world)          # before the device context and reader threads
     device = init_group(rank, world, spec["port"], spec["device"], spec["group_timeout_s"])
     if device.type == "cpu":
         # CPU ranks share the host's cores: every rank spinning up a full-width thread pool
@@ -235,8 +237,11 @@ def leader_engine(spec: dict, *, deadline_s: float = 30.0):
     spec = dict(spec, rank=0)
     spec.setdefault("port", free_port())
     spec.setdefault("group_timeout_s", 120.0)
+    from . import affinity
+    affinity.configured(spec["world"])       # a bad placement fails before any rank starts
     team = RankTeam(spec, deadline_s=deadline_s)
     try:
+        affinity.bind_rank(0, spec["world"])
         device = init_group(0, spec["world"], spec["port"], spec["device"],
                             spec["group_timeout_s"])
         team.admit()

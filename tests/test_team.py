@@ -112,3 +112,30 @@ def test_preflight_gate():
     assert T.preflight([lambda: True] * 3, timeout_s=1.0)
     assert not T.preflight([lambda: True, lambda: False], timeout_s=1.0)
     assert not T.preflight([lambda: True, lambda: time.sleep(0.5) or True], timeout_s=0.1)
+
+
+def test_worker_cpu_sets_are_parsed_checked_and_applied(monkeypatch):
+    """``ORINFER_WORKER_CPUS``: one CPU set per rank; malformed, overlapping or unavailable
+    sets are refused; a rank pins itself to its set."""
+    import os
+    from orinfer_b200.parallel import affinity as A
+    assert A.parse("0-2,5;3,4", 2) == [[0, 1, 2, 5], [3, 4]]
+    assert A.parse(" 7 ", 1) == [[7]]
+    for bad, ranks in (("0-1", 2), ("0;0", 2), ("0-1,1;2", 2), ("3-1;4", 2), ("a;1", 2),
+                       ("0,;1", 2), (";1", 2), ("0;99999", 2), ("-1;2", 2)):
+        with pytest.raises(A.AffinityError):
+            A.parse(bad, ranks)
+    assert A.configured(2, "") is None
+    monkeypatch.delenv(A.VARIABLE, raising=False)
+    assert A.bind_rank(0, 2) is None
+    allowed = sorted(os.sched_getaffinity(0))
+    outside = max(allowed) + 1
+    with pytest.raises(A.AffinityError, match="not available"):
+        A.configured(2, f"{allowed[0]};{outside}")
+    if len(allowed) >= 2:
+        monkeypatch.setenv(A.VARIABLE, f"{allowed[0]};{allowed[1]}")
+        try:
+            assert A.bind_rank(1, 2) == [allowed[1]]
+            assert os.sched_getaffinity(0) == {allowed[1]}
+        finally:
+            os.sched_setaffinity(0, allowed)
