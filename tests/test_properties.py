@@ -230,3 +230,71 @@ def test_prefix_cache_never_evicts_a_page_in_use_and_matches_what_it_indexed(ops
                 page_of = {k: v for k, v in page_of.items() if v != pg}
     st_ = cache.statistics()
     assert st_.device_pages == len(page_of) and st_.evicted == len(evicted)
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.lists(st.tuples(st.sampled_from(["insert", "offload", "restore", "drop", "evict"]),
+                          st.integers(0, 5), st.integers(1, 4)), min_size=1, max_size=80))
+def test_host_tier_slots_are_never_lost_or_shared(ops):
+    """Random traffic that moves pages between the device and a host slab of eight slots the
+    way the engine does (offload = evict to host + record the slot; a hit restores and frees
+    it; re-adoption of a host-resident node frees its stale slot; pressure drops host-only
+    leaves): every slot is always either free or owned by exactly one indexed node."""
+    from orinfer_b200.core.prefix import RadixPrefixCache
+    cache = RadixPrefixCache(page_tokens=4)
+    family = lambda f, pages: [(f % 3) * 100 + i // 4 if i < 4 else f * 1000 + i // 4
+                               for i in range(pages * 4)]
+    free = list(range(8))
+    owner = {}                        # slot -> node id
+    next_page = [1]
+
+    def check():
+        assert len(free) + len(owner) == 8 and not set(free) & set(owner)
+        assert cache.statistics().host_pages == len(owner)
+        for slot, node in owner.items():
+            assert cache.host_handle(node) == slot
+
+    for op, f, pages in ops:
+        toks = family(f, pages)
+        if op == "insert":
+            ids = list(range(next_page[0], next_page[0] + pages))
+            next_page[0] += pages
+            adopted, nodes = cache.insert(toks, ids)
+            for took, node in zip(adopted, nodes):
+                stale = cache.host_handle(node) if took else -1
+                if stale >= 0:                         # re-adopted: the host copy is redundant
+                    cache.set_host(node, -1)
+                    free.append(owner_pop(owner, stale, node))
+        elif op == "offload":
+            if not free:
+                for slot in cache.drop_host(pages):
+                    del owner[slot]
+                    free.append(slot)
+            for node, _page in cache.evict(min(pages, len(free)), to_host=True):
+                slot = free.pop()
+                cache.set_host(node, slot)
+                owner[slot] = node
+        elif op == "restore":
+            nodes, got = cache.match(toks, acquire=False)
+            for node, page in zip(nodes, got):
+                if page >= 0:
+                    continue
+                slot = cache.host_handle(node)
+                if slot < 0 or not cache.restore(node, next_page[0]):
+                    break
+                next_page[0] += 1
+                cache.set_host(node, -1)
+                free.append(owner_pop(owner, slot, node))
+        elif op == "drop":
+            for slot in cache.drop_host(pages):
+                del owner[slot]
+                free.append(slot)
+        elif op == "evict":
+            for node, _page in cache.evict(pages):
+                assert cache.host_handle(node) < 0 and node not in owner.values()
+        check()
+
+
+def owner_pop(owner, slot, node):
+    assert owner.pop(slot) == node
+    return slot
