@@ -81,6 +81,28 @@ def weight_shapes(cfg: ModelConfig) -> Dict[str, tuple]:
         else:
             out[p + "gate_up"] = (2 * cfg.ffn, h, cfg.proj_format)
             out[p + "down"] = (h, cfg.ffn, cfg.proj_format)
+    if cfg.mtp_layers:
+        # the draft head: its [H, 2H] input projection and one full-attention layer, shaped
+        # like the model's own layers or (the presets) a dense W8 layer
+        p = "mtp.layer."
+        out["mtp.fc"] = (h, 2 * h, "w8")
+        own = cfg.draft_layer == "model"
+        gated = 2 if own and cfg.gated_attention else 1
+        attn_fmt = cfg.attn_format if own else "w8"
+        out[p + "qkv"] = (cfg.q_heads * cfg.head_dim * gated + 2 * cfg.kv_heads * cfg.head_dim,
+                          h, attn_fmt)
+        out[p + "o"] = (h, cfg.q_heads * cfg.head_dim, attn_fmt)
+        if own and cfg.experts:
+            out[p + "expert_gate_up"] = (cfg.experts * 2 * cfg.expert_ffn, h, cfg.expert_format)
+            out[p + "expert_down"] = (cfg.experts * h, cfg.expert_ffn, cfg.expert_format)
+            if cfg.shared_expert_ffn:
+                out[p + "shared_gate_up"] = (2 * cfg.shared_expert_ffn, h, cfg.proj_format)
+                out[p + "shared_down"] = (h, cfg.shared_expert_ffn, cfg.proj_format)
+        else:
+            f = cfg.ffn or max(cfg.expert_ffn * 4, 512)
+            fmt = cfg.proj_format if own else "w8"
+            out[p + "gate_up"] = (2 * f, h, fmt)
+            out[p + "down"] = (h, f, fmt)
     out["embed"] = (cfg.vocab, h, "w8")
     if not cfg.tied_embeddings:
         out["head"] = (cfg.vocab, h, cfg.head_format)

@@ -73,3 +73,28 @@ def test_plan_model_cli_reports_the_plan_and_refusals(capsys):
     assert cli.main(["plan-model", "--preset", "80b-a3b-class", "--device-gib", "8"]) == 2
     out = json.loads(capsys.readouterr().out)
     assert not out["ok"] and "GiB" in out["error"]
+
+
+def test_the_draft_head_is_part_of_the_plan(tmp_path):
+    import dataclasses
+
+    from orinfer_b200.engine.checkpoint import read_descriptor, save_model
+    from orinfer_b200.models.weights import random_model
+    for preset, kind in (("tiny", "dense"), ("tiny-moe", "model")):
+        base = PRESETS[preset]
+        cfg = dataclasses.replace(base, mtp_layers=1, draft_layer=kind)
+        stems = weight_shapes(cfg)
+        assert stems["mtp.fc"] == (cfg.hidden, 2 * cfg.hidden, "w8")
+        assert ("mtp.layer.expert_down" in stems) == (kind == "model")
+        with_head = validate_plan(cfg, L, S, max_context=256)
+        without = validate_plan(base, L, S, max_context=256)
+        assert with_head.weight_bytes > without.weight_bytes
+        assert with_head.kv_bytes_per_page > without.kv_bytes_per_page       # its own KV layer
+        out = tmp_path / preset
+        save_model(random_model(cfg, seed=0), out)
+        desc = read_descriptor(out)
+        validate_plan(cfg, L, S, max_context=256, descriptor=desc, exhaustive=True)
+        broken = json.loads(json.dumps(desc))
+        del broken["tensors"]["mtp.fc.scale"]
+        with pytest.raises(PlanError, match="mtp.fc"):
+            validate_plan(cfg, L, S, max_context=256, descriptor=broken)
