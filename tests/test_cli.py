@@ -61,3 +61,27 @@ def test_models_registry_verbs(tmp_path, capsys):
     assert names == ["tiny", "tiny2"]
     assert main(["models", *st, "rm", "tiny"]) == 0
     assert main(["models", *st, "show", "tiny"]) == 2
+
+
+def test_shipped_examples_run(tmp_path, capsys):
+    """The files under examples/ are valid inputs of the verbs they document."""
+    import json
+    from pathlib import Path
+    from orinfer_b200.api.chat_codec import ChatCodec  # noqa: F401  (the request schema lives there)
+    from orinfer_b200.cli import main
+    root = Path(__file__).resolve().parents[1] / "examples"
+    common = ["--device", "cpu", "--cuda-graph", "off", "--prefix-cache-mib", "0"]
+    assert main(["run-model", "--preset", "tiny", "--requests", str(root / "requests.json")]
+                + common) == 0
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert [r["id"] for r in rep["requests"]] == ["short", "two-chunks"]
+    assert [len(r["tokens"]) for r in rep["requests"]] == [8, 4]
+    out = tmp_path / "out.jsonl"
+    assert main(["batch", "--preset", "tiny", "--input", str(root / "batch.jsonl"), "--output",
+                 str(out)] + common) == 0
+    rows = [json.loads(x) for x in out.read_text().splitlines()]
+    assert sorted(r.get("id", r.get("custom_id")) for r in rows) == ["a", "b"]
+    body = json.loads((root / "chat-request.json").read_text())
+    assert body["tools"][0]["function"]["strict"] and body["stream"]
+    json.loads((root / "opencode.json").read_text())
+    compile((root / "openai-python.py").read_text(), "openai-python.py", "exec")
