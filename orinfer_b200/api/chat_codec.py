@@ -251,13 +251,13 @@ class ChatCodec:
         if unknown:
             raise RequestError(f"unknown field `{unknown[0]}`", param=unknown[0])
         req = merge_defaults(body, deployment_defaults or {})
-        messages = req.get("messages")
-        if not isinstance(messages, list) or not messages:
-            raise RequestError("`messages` must be a non-empty array", param="messages")
-        for i, m in enumerate(messages):
-            if not isinstance(m, dict) or m.get("role") not in ("system", "user", "assistant",
-                                                                "tool", "developer"):
-                raise RequestError("invalid message role", param=f"messages[{i}].role")
+        from .messages import MessageError, normalize
+        try:
+            # one shape for every wire form: text parts joined, ``null`` content empty, tool
+            # call arguments parsed, developer folded into system, calls answered
+            messages = normalize(req.get("messages"), self.tool_format)
+        except MessageError as e:
+            raise RequestError(str(e), param=e.param)
         if req.get("n", 1) != 1:
             raise RequestError("only n = 1 is supported", param="n")
         if req.get("store") is True:

@@ -84,6 +84,44 @@ def _content(text, images):
     return parts
 
 
+def _link_tool_messages(messages: list) -> list:
+    """Ollama histories carry tool calls without ids and tool results named by ``tool_name``;
+    the native history wants every call identified and every result bound to its call.  Calls
+    without an id get ``call_N``; a result without ``tool_call_id`` answers the oldest open
+    call of its ``tool_name`` (or the oldest open call when it names none)."""
+    out, open_calls, made = [], [], 0
+    for m in messages:
+        if not isinstance(m, dict):
+            out.append(m)
+            continue
+        m = dict(m)
+        if m.get("role") == "assistant" and isinstance(m.get("tool_calls"), list):
+            calls = []
+            for c in m["tool_calls"]:
+                if isinstance(c, dict):
+                    c = dict(c)
+                    if not c.get("id"):
+                        made += 1
+                        c["id"] = f"call_{made}"
+                    c.setdefault("type", "function")
+                    fn = c.get("function")
+                    open_calls.append((c["id"], fn.get("name") if isinstance(fn, dict) else None))
+                calls.append(c)
+            m["tool_calls"] = calls
+        elif m.get("role") == "tool":
+            if m.get("tool_call_id"):
+                open_calls = [c for c in open_calls if c[0] != m["tool_call_id"]]
+            else:
+                name = m.get("tool_name") or m.get("name")
+                pick = next((c for c in open_calls if name and c[1] == name), None) \
+                    or (open_calls[0] if open_calls else None)
+                if pick is not None:
+                    open_calls.remove(pick)
+                    m["tool_call_id"] = pick[0]
+        out.append(m)
+    return out
+
+
 def translate(body: Dict[str, Any], generate: bool) -> Dict[str, Any]:
     """Ollama request -> native chat request."""
     if not isinstance(body, dict):
@@ -103,10 +141,11 @@ def translate(body: Dict[str, Any], generate: bool) -> Dict[str, Any]:
             raise RequestError("suffix is not supported", param="suffix")
         out["messages"] = msgs
     else:
-        out["messages"] = [dict({k: v for k, v in m.items() if k != "images"},
-                                content=_content(m.get("content", ""), m["images"]))
-                           if isinstance(m, dict) and m.get("images") else m
-                           for m in body.get("messages") or []]
+        out["messages"] = _link_tool_messages(
+            [dict({k: v for k, v in m.items() if k != "images"},
+                  content=_content(m.get("content", ""), m["images"]))
+             if isinstance(m, dict) and m.get("images") else m
+             for m in body.get("messages") or []])
     opts = body.get("options") or {}
     for k, v in opts.items():
         if k in OPTION_MAP:

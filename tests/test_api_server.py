@@ -124,6 +124,32 @@ def test_ollama_routes(client):
     assert client.post("/api/generate", json={"model": "tiny"}).json()["done_reason"] == "load"
 
 
+def test_ollama_tool_histories_reach_the_native_form(client):
+    """Ollama tool calls have no ids and results are named by tool: the gateway numbers the
+    calls and binds each result to the oldest open call of its tool."""
+    from orinfer_b200.api.ollama import translate
+    fn = lambda name, **args: {"function": {"name": name, "arguments": args}}
+    history = [
+        {"role": "user", "content": "weather and time in Paris?"},
+        {"role": "assistant", "content": "", "tool_calls": [fn("get_weather", city="Paris"),
+                                                             fn("get_time", zone="CET")]},
+        {"role": "tool", "tool_name": "get_time", "content": "12:00"},
+        {"role": "tool", "tool_name": "get_weather", "content": "sunny"},
+        {"role": "user", "content": "thanks, once more for Rome"},
+    ]
+    out = translate({"model": "tiny", "messages": history}, generate=False)["messages"]
+    ids = [c["id"] for c in out[1]["tool_calls"]]
+    assert ids == ["call_1", "call_2"] and all(c["type"] == "function" for c in out[1]["tool_calls"])
+    assert [m.get("tool_call_id") for m in out[2:4]] == ["call_2", "call_1"]
+    r = client.post("/api/chat", json={"model": "tiny", "messages": history, "stream": False,
+                                       "options": {"num_predict": 3, "temperature": 0}})
+    assert r.status_code == 200 and r.json()["done"]
+    # a result nobody asked for is a client error, not a template failure
+    orphan = history[:1] + [{"role": "tool", "tool_name": "get_time", "content": "12:00"}]
+    assert client.post("/api/chat", json={"model": "tiny", "messages": orphan,
+                                          "stream": False}).status_code == 400
+
+
 def test_keep_alive_forms():
     from orinfer_b200.api.ollama import parse_keep_alive
     assert parse_keep_alive("1h30m") == 5400 and parse_keep_alive(-1) == -1

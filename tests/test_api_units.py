@@ -112,10 +112,118 @@ def test_codec_loads_templates_kept_in_the_tokenizer_configuration(tmp_path):
     text = codec.prepare({"messages": msgs}).prompt_text
     assert text == "<|im_start|>user: 0<|im_end|><|im_start|>user: 1<|im_end|>"     # break honoured
     try:
-        codec.prepare({"messages": [{"role": "tool", "content": "x"}]})
+        codec.prepare({"messages": [
+            {"role": "user", "content": "q"},
+            {"role": "assistant", "content": None, "tool_calls": [
+                {"id": "c1", "type": "function", "function": {"name": "f", "arguments": "{}"}}]},
+            {"role": "tool", "tool_call_id": "c1", "content": "x"}]})
     except RequestError as e:
         assert "no tools" in e.message
     else:
         raise AssertionError("the template's own refusal must surface as a request error")
     (tmp_path / "chat_template.jinja").write_text("{{ messages[0].content }}!")
     assert ChatCodec.load(tmp_path, 1024, 512, "m").prepare({"messages": msgs}).prompt_text == "0!"
+
+
+def test_histories_are_normalised_before_the_template_sees_them():
+    """Wire shapes of one conversation (text parts, null content, JSON-string arguments,
+    developer beside system) reach the template in one form; malformed histories are refused."""
+    import json
+
+    import pytest
+    from orinfer_b200.api.messages import RAW_ARGUMENTS, MessageError, normalize
+    call = lambda cid, args: {"id": cid, "type": "function",
+                              "function": {"name": "get_weather", "arguments": args}}
+    user = {"role": "user", "content": "What is the weather?"}
+    # a tool result sent as text parts is the concatenation of the parts; no parts is ""
+    got = normalize([user, {"role": "assistant", "content": None, "tool_calls": [call("c1", "{}")]},
+                     {"role": "tool", "tool_call_id": "c1",
+                      "content": [{"type": "text", "text": "sunny [img]"},
+                                  {"type": "text", "text": ", 72F [img-99]"}]}])
+    assert got[1]["content"] == "" and got[1]["tool_calls"][0]["function"]["arguments"] == {}
+    assert got[2]["content"] == "sunny [img], 72F [img-99]"
+    got = normalize([user, {"role": "assistant", "tool_calls": [call("c1", '{"city":"Paris"}')]},
+                     {"role": "tool", "tool_call_id": "c1", "content": []}])
+    assert got[2]["content"] == "" and \
+        got[1]["tool_calls"][0]["function"]["arguments"] == {"city": "Paris"}
+    # system and developer instructions become one system message
+    got = normalize([{"role": "system", "content": "Be brief."},
+                     {"role": "developer", "content": "Call tools when asked."},
+                     {"role": "user", "content": [{"type": "text", "text": "Hi"}]}])
+    assert got == [{"role": "system", "content": "Be brief.\n\nCall tools when asked."},
+                   {"role": "user", "content": "Hi"}]
+    # arguments that are not a JSON object are kept for the model to see, not guessed
+    got = normalize([user, {"role": "assistant", "tool_calls": [call("c1", '{"city": "Par')]},
+                     {"role": "tool", "tool_call_id": "c1", "content": "error: bad arguments"}])
+    assert got[1]["tool_calls"][0]["function"]["arguments"] == {RAW_ARGUMENTS: '{"city": "Par'}
+    # an image part keeps the part list for the image front end
+    parts = [{"type": "text", "text": "look"}, {"type": "image_url", "image_url": {"url": "x"}}]
+    assert normalize([{"role": "user", "content": parts}])[0]["content"] == parts
+    # dsml histories: parts joined by a blank line, system messages stay where they are,
+    # doubly encoded arguments are unwrapped
+    got = normalize([user, {"role": "system", "content": "late"},
+                     {"role": "assistant", "tool_calls": [call("c1", json.dumps(json.dumps({"a": 1})))]},
+                     {"role": "tool", "tool_call_id": "c1",
+                      "content": [{"type": "text", "text": "a"}, {"type": "text", "text": "b"}]}],
+                    "dsml")
+    assert got[1]["role"] == "system" and got[3]["content"] == "a\n\nb"
+    assert got[2]["tool_calls"][0]["function"]["arguments"] == {"a": 1}
+    bad = [
+        ([], "non-empty"),
+        ([{"role": "system", "content": "only instructions"}], "user message"),
+        ([user, {"role": "system", "content": "late"}], "precede"),
+        ([user, {"role": "narrator", "content": "x"}], "role"),
+        ([user, {"role": "tool", "tool_call_id": "nope", "content": "x"}], "tool_call_id"),
+        ([user, {"role": "assistant", "tool_calls": [call("c1", "{}")]}, user], "answering"),
+        ([user, {"role": "assistant", "tool_calls": [call("c1", "{}")]}], "answering"),
+        ([user, {"role": "assistant", "tool_calls": [call("c1", "{}"), call("c1", "{}")]}], "unique"),
+        ([user, {"role": "assistant", "tool_calls": [call("", "{}")]}], "unique"),
+        ([user, {"role": "user", "tool_calls": [call("c1", "{}")], "content": "x"}], "assistant"),
+        ([user, {"role": "assistant", "tool_calls": [
+            {"id": "c1", "type": "function", "function": {"name": "bad name!", "arguments": "{}"}}]}],
+         "invalid assistant tool call"),
+        ([user, {"role": "assistant", "tool_calls": [call("c1", 5)]}], "JSON string"),
+        ([{"role": "user", "content": 7}], "content"),
+        ([{"role": "user", "content": [{"type": "text"}]}], "text"),
+    ]
+    for history, word in bad:
+        with pytest.raises(MessageError, match=word):
+            normalize(history)
+
+
+def test_parser_and_finish_reason_follow_the_protocol_table():
+    """Raw model text -> (reasoning, content, calls) for every way of cutting it into two
+    pieces, and the finish reason: running out of tokens wins over a finished tool call."""
+    import json
+    from orinfer_b200.api.output_parser import OutputParser
+    call = '<tool_call>{"name":"get_time","arguments":{"timezone":"UTC"}}</tool_call>'
+    cases = [
+        ("<think>step-by-step</think>final answer", "step-by-step", "final answer", []),
+        ("<think>need a tool</think>" + call, "need a tool", "",
+         [("get_time", {"timezone": "UTC"})]),
+        ("<think>pondering", "pondering", "", []),
+        ("hello", "", "hello", []),
+        (call, "", "", [("get_time", {"timezone": "UTC"})]),
+        ("", "", "", []),
+    ]
+    for raw, reasoning, content, calls in cases:
+        for cut in range(len(raw) + 1):
+            p = OutputParser(thinking=False)
+            got_r = got_c = ""
+            got_calls = {}
+            for piece, final in ((raw[:cut], False), (raw[cut:], True)):
+                d = p.feed(piece, final=final)
+                got_r, got_c = got_r + d.reasoning, got_c + d.content
+                for c in d.tool_calls:
+                    e = got_calls.setdefault(c["index"], ["", ""])
+                    e[0] += c.get("function", {}).get("name") or ""
+                    e[1] += c.get("function", {}).get("arguments") or ""
+            assert (got_r.strip(), got_c.strip()) == (reasoning, content), (raw, cut)
+            assert [(n, json.loads(a or "{}")) for n, a in
+                    (got_calls[i] for i in sorted(got_calls))] == calls, (raw, cut)
+    for exhausted, has_tool, want in ((False, False, "stop"), (True, False, "length"),
+                                      (False, True, "tool_calls"), (True, True, "length")):
+        p = OutputParser()
+        if has_tool:
+            p.feed(call, final=True)
+        assert p.finish_reason("length" if exhausted else "stop") == want
