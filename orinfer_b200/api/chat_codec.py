@@ -133,7 +133,10 @@ ALLOWED_FIELDS = {
     "tool_choice", "parallel_tool_calls", "response_format", "enable_thinking",
     "chat_template_kwargs", "reasoning_effort", "thinking_token_budget", "prompt_cache_key",
     "prompt_cache_retention", "ignore_eos", "image_processing", "store", "metadata",
-    "min_tokens", "cache_prompt",
+    "min_tokens", "cache_prompt", "service_tier",
+    # "clamp": an output limit that does not fit the context is shortened instead of refused
+    # (what the Ollama routes ask for: `num_predict` is a wish there, not a contract)
+    "output_limit",
 }
 GROUPS = [("enable_thinking", "reasoning_effort"), ("max_tokens", "max_completion_tokens")]
 
@@ -219,6 +222,8 @@ class ChatCodec:
         self.model_name = model_name
         self.images = None            # api.images.ImageFrontend of a vision-capable model
         self.tool_format = "xml"      # "dsml": DeepSeek-style call blocks (api/dsml.py)
+        # an explicit output limit that does not fit the context is refused, not shortened
+        self.strict_context = True
 
     @classmethod
     def load(cls, model_dir: Path, vocab: int, context: int, model_name: str) -> "ChatCodec":
@@ -258,6 +263,26 @@ class ChatCodec:
             messages = normalize(req.get("messages"), self.tool_format)
         except MessageError as e:
             raise RequestError(str(e), param=e.param)
+        for name in ("stream", "logprobs", "enable_thinking", "ignore_eos", "store",
+                     "parallel_tool_calls", "cache_prompt"):
+            if req.get(name) is not None and not isinstance(req[name], bool):
+                raise RequestError(f"`{name}` must be true, false or null", param=name)
+        if body.get("max_tokens") is not None and body.get("max_completion_tokens") is not None:
+            raise RequestError("specify only one output-token limit",
+                               param="max_completion_tokens")
+        if req.get("reasoning_effort") is not None and req["reasoning_effort"] not in EFFORTS:
+            raise RequestError("`reasoning_effort` is one of " + "/".join(EFFORTS),
+                               param="reasoning_effort")
+        if req.get("reasoning_effort") == "none" and req.get("enable_thinking") is True:
+            raise RequestError("`enable_thinking` conflicts with reasoning_effort=none",
+                               param="enable_thinking")
+        key = req.get("prompt_cache_key")
+        if key is not None and (not isinstance(key, str) or not 1 <= len(key) <= 64):
+            raise RequestError("`prompt_cache_key` takes 1 to 64 characters",
+                               param="prompt_cache_key")
+        if req.get("prompt_cache_retention") not in (None, "in-memory", "24h"):
+            raise RequestError("`prompt_cache_retention` is in-memory or 24h",
+                               param="prompt_cache_retention")
         if req.get("n", 1) != 1:
             raise RequestError("only n = 1 is supported", param="n")
         if req.get("store") is True:
@@ -297,8 +322,13 @@ class ChatCodec:
         bias_in = req.get("logit_bias") or {}
         try:
             bias = {int(k): float(v) for k, v in bias_in.items()}
-        except (TypeError, ValueError):
+        except (TypeError, ValueError, AttributeError):
             raise RequestError("`logit_bias` maps token ids to numbers", param="logit_bias")
+        vocab = getattr(self.tokenizer, "vocab", None)
+        for tok in bias:
+            if tok < 0 or (vocab is not None and tok >= vocab):
+                raise RequestError(f"token {tok} is not in the vocabulary",
+                                   param=f"logit_bias.{tok}")
         want_lp = bool(req.get("logprobs", False))
         top_lp = req.get("top_logprobs")
         if top_lp is not None and not want_lp:
@@ -322,10 +352,10 @@ class ChatCodec:
         if rf.get("type") == "json_schema":
             js = rf.get("json_schema") or {}
             schema = js.get("schema")
-            if not isinstance(schema, dict):
+            if not isinstance(schema, (dict, bool)):
                 raise RequestError("`json_schema.schema` must be an object",
-                                   param="response_format")
-            _check_depth(schema)
+                                   param="response_format.json_schema.schema")
+            _check_schema(schema)
         elif rf.get("type") == "json_object":
             json_object = True
         elif rf.get("type") != "text":
@@ -371,14 +401,31 @@ class ChatCodec:
             bound = self.images.bind(ids, decoded, opts)
             ids = bound.prompt_ids
             bound = bound if bound.images else None
-        max_new = req.get("max_completion_tokens", req.get("max_tokens", d.max_tokens))
-        if not isinstance(max_new, int) or max_new < 1:
-            raise RequestError("`max_tokens` must be a positive integer", param="max_tokens")
+        limit = req.get("max_completion_tokens")
+        limit_name = "max_completion_tokens" if limit is not None else "max_tokens"
+        if limit is None:
+            limit = req.get("max_tokens")
+        # explicit: the client itself named a limit (deployment defaults are shortened to fit)
+        explicit = (body.get("max_completion_tokens") is not None
+                    or body.get("max_tokens") is not None) \
+            and req.get("output_limit", "strict") != "clamp"
+        max_new = limit if limit is not None else d.max_tokens
+        if not isinstance(max_new, int) or isinstance(max_new, bool) or max_new < 1:
+            raise RequestError(f"`{limit_name}` must be a positive integer", param=limit_name)
         if len(ids) >= self.context:
             raise RequestError(
                 f"the prompt of {len(ids)} tokens exceeds the context window of "
                 f"{self.context} tokens", param="messages", code="context_length_exceeded")
+        if explicit and len(ids) + max_new > self.context and self.strict_context:
+            # a limit the client asked for is kept or refused, never silently shortened
+            raise RequestError(
+                f"the request exceeds the context window of {self.context} tokens: "
+                f"{len(ids)} prompt tokens + {max_new} output tokens", param=limit_name,
+                code="context_length_exceeded")
         max_new = min(max_new, self.context - len(ids))
+        if thinking and budget is not None and max_new < 2:
+            raise RequestError("a thinking budget needs room for the end of thinking and an "
+                               "answer token", param=limit_name)
         stream_opts = req.get("stream_options") or {}
         return Prepared(
             prompt_ids=ids, sampling=sampling, max_new=max_new, stream=bool(req.get("stream")),
@@ -413,12 +460,37 @@ class ChatCodec:
             raise RequestError(f"chat template failed: {e}", param="messages")
 
 
-def _check_depth(schema, depth: int = 0, limit: int = 64) -> None:
+EFFORTS = ("none", "minimal", "low", "medium", "high", "xhigh", "max")
+SCHEMA_PARAM = "response_format.json_schema.schema"
+
+
+def _check_schema(schema, depth: int = 0, limit: int = 64, param: str = SCHEMA_PARAM) -> None:
+    """What the constraint compiler will not be given: schemas nested deeper than ``limit``,
+    references that leave the document, vendor extensions, malformed containers."""
     if depth > limit:
-        raise RequestError("JSON schema nests too deeply", param="response_format")
-    if isinstance(schema, dict):
-        for v in schema.values():
-            _check_depth(v, depth + 1, limit)
-    elif isinstance(schema, list):
-        for v in schema:
-            _check_depth(v, depth + 1, limit)
+        raise RequestError("JSON schema nests too deeply", param=param)
+    if isinstance(schema, bool):
+        return
+    if not isinstance(schema, dict):
+        raise RequestError("a JSON schema is an object or a boolean", param=param)
+    ref = schema.get("$ref")
+    if isinstance(ref, str) and not ref.startswith("#"):
+        raise RequestError("only local schema references are supported", param=param)
+    if "x-guidance" in schema:
+        raise RequestError("x-guidance schema extensions are not supported", param=param)
+    for key in ("properties", "$defs", "definitions", "patternProperties"):
+        if key in schema:
+            if not isinstance(schema[key], dict):
+                raise RequestError(f"schema `{key}` must be an object", param=param)
+            for child in schema[key].values():
+                _check_schema(child, depth + 1, limit, param)
+    for key in ("items", "additionalProperties", "not", "if", "then", "else"):
+        if key in schema:
+            _check_schema(schema[key], depth + 1, limit, param)
+    for key in ("anyOf", "allOf", "oneOf", "prefixItems"):
+        if key in schema:
+            if not isinstance(schema[key], list):
+                raise RequestError(f"schema `{key}` must be an array", param=param)
+            for child in schema[key]:
+                _check_schema(child, depth + 1, limit, param)
+

@@ -146,6 +146,7 @@ def translate(body: Dict[str, Any], generate: bool) -> Dict[str, Any]:
                   content=_content(m.get("content", ""), m["images"]))
              if isinstance(m, dict) and m.get("images") else m
              for m in body.get("messages") or []])
+    out["output_limit"] = "clamp"
     opts = body.get("options") or {}
     for k, v in opts.items():
         if k in OPTION_MAP:

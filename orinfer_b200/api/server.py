@@ -107,7 +107,7 @@ class Service:
             out["queued"] = len(eng.waiting) + self.worker.jobs.qsize()
             if eng.prefix is not None:
                 out["prefix_cache"] = eng.prefix.statistics().__dict__
-            out["context"] = eng.max_context
+            out["context"] = out["max_context"] = eng.max_context
             pager = getattr(eng.runner, "pager", None)
             if pager is not None:
                 out["expert_pager"] = pager.stats.as_dict()
@@ -159,6 +159,15 @@ def create_app(service: Service) -> FastAPI:
             resp = await call_next(request)
         resp.headers["x-request-id"] = rid
         return resp
+
+    @app.exception_handler(404)
+    async def not_found(request: HttpRequest, exc):
+        return _error(404, f"no route {request.method} {request.url.path}", code="not_found")
+
+    @app.exception_handler(405)
+    async def wrong_method(request: HttpRequest, exc):
+        return _error(405, f"{request.method} is not allowed on {request.url.path}",
+                      code="method_not_allowed")
 
     @app.get("/health")
     async def health():

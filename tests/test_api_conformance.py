@@ -110,3 +110,59 @@ def test_unicode_token_bytes_in_logprobs(client):
         assert e["logprob"] <= 0 and len(e["top_logprobs"]) == 2
     raw = bytes(b for e in entries for b in e["bytes"])
     assert raw.decode("utf-8", errors="replace") is not None
+
+
+def test_validation_errors_name_their_parameter(client):
+    """Each malformed field is refused with 400, a request id and ``error.param`` naming it."""
+    base = dict(messages=MSG, temperature=0, seed=-20261002, max_completion_tokens=16)
+    schema_ref = {"type": "json_schema", "json_schema": {
+        "name": "remote", "schema": {"$ref": "https://example.com/schema"}}}
+    table = [
+        ({"stream": "yes"}, "stream"),
+        ({"top_logprobs": 3}, "top_logprobs"),
+        ({"logprobs": True, "top_logprobs": 21}, "top_logprobs"),
+        ({"store": True}, "store"),
+        ({"temperature": -1}, "temperature"),
+        ({"reasoning_effort": "invalid"}, "reasoning_effort"),
+        ({"reasoning_effort": "none", "enable_thinking": True}, "enable_thinking"),
+        ({"thinking_token_budget": -1}, "thinking_token_budget"),
+        ({"prompt_cache_key": "x" * 65}, "prompt_cache_key"),
+        ({"prompt_cache_key": ""}, "prompt_cache_key"),
+        ({"prompt_cache_retention": "forever"}, "prompt_cache_retention"),
+        ({"enable_thinking": True, "thinking_token_budget": 0, "max_completion_tokens": 1},
+         "max_completion_tokens"),
+        ({"max_tokens": 4}, "max_completion_tokens"),                 # two limits at once
+        ({"logit_bias": {"999999999": 1}}, "logit_bias.999999999"),
+        ({"response_format": schema_ref}, "response_format.json_schema.schema"),
+        ({"response_format": {"type": "json_schema", "json_schema": {
+            "name": "x", "schema": {"properties": {"a": {"x-guidance": {}}}}}}},
+         "response_format.json_schema.schema"),
+    ]
+    for fields, param in table:
+        r = client.post("/v1/chat/completions", json=dict(base, **fields))
+        assert r.status_code == 400, (fields, r.text)
+        assert r.headers.get("x-request-id")
+        assert r.json()["error"]["param"] == param, (fields, r.json())
+    # the accepted spellings of the same fields
+    ok = dict(base, stream=None, tools=None, store=False, metadata={"t": "c"}, service_tier="auto",
+              prompt_cache_key="pi-session-probe", prompt_cache_retention="24h",
+              reasoning_effort="xhigh", logit_bias={"42": -100})
+    assert client.post("/v1/chat/completions", json=ok).status_code == 200
+
+
+def test_recognizable_context_overflow(client):
+    """An output limit the client named is kept or refused, never silently shortened; the
+    refusal carries the code clients look for."""
+    limit = client.get("/health").json()["max_context"]
+    r = client.post("/v1/chat/completions", json=dict(messages=MSG, max_completion_tokens=limit))
+    err = r.json()["error"]
+    assert r.status_code == 400 and err["code"] == "context_length_exceeded"
+    assert "exceeds the context window" in err["message"] and err["param"] == "max_completion_tokens"
+    # without a limit of its own a request gets what fits
+    assert client.post("/v1/chat/completions", json=dict(messages=MSG)).status_code == 200
+
+
+def test_unknown_routes_answer_in_the_error_shape(client):
+    for path, code in (("/v1/missing", 404), ("/v1/chat/completions", 405)):
+        r = client.get(path)
+        assert r.status_code == code and r.json()["error"]["message"]
