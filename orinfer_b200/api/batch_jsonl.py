@@ -149,7 +149,8 @@ def run_batch(engine, codec: ChatCodec, input_path, output_path, *, resume: bool
             if d.reasoning:
                 msg["reasoning_content"] = d.reasoning
             if d.tool_calls:
-                msg["tool_calls"] = d.tool_calls
+                from .output_parser import merge_tool_calls
+                msg["tool_calls"] = merge_tool_calls(d.tool_calls)      # fragments -> calls
             writer.q.put({"id": rid, "response": {
                 "choices": [{"index": 0, "message": msg,
                              "finish_reason": parser.finish_reason(req.finish_reason or "stop")}],

@@ -30,18 +30,22 @@ class _TokTable:
         eos = list(getattr(tokenizer, "eos_ids", ()) or ())
         self.eos_token_id = eos[0] if eos else vocab - 1
         self.bos_token_id = None
-        specials = []
-        if hasattr(tokenizer, "special_ids"):
-            specials = list(tokenizer.special_ids.values())
-            for i in specials:
-                self.tokens[i] = b"\xff" + self.tokens[i]          # never matched as text
+        from .token_boundary import BoundaryError, control_vocabulary, plain_encoder
+        specials = [i for i in control_vocabulary(tokenizer).values() if 0 <= i < vocab]
+        for i in specials:
+            self.tokens[i] = b"\xff" + self.tokens[i]              # never matched as text
         self.special_token_ids = specials
-        self._tk = tokenizer
+        # text the grammar forces (constants, keys) is tokenised as plain characters: a
+        # constant that spells a control token must not come back as that token
+        try:
+            self._encode = plain_encoder(tokenizer)
+        except BoundaryError:
+            self._encode = tokenizer.encode
 
     def __call__(self, s):
         if isinstance(s, bytes):
             s = s.decode("utf-8", errors="replace")
-        return self._tk.encode(s)
+        return self._encode(s)
 
 
 _TOKENIZERS = {}

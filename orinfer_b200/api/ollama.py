@@ -122,6 +122,41 @@ def _link_tool_messages(messages: list) -> list:
     return out
 
 
+class CallAssembler:
+    """The native stream delivers a tool call as fragments (name first, then pieces of the
+    argument text); this protocol shows a call once, whole, with its arguments as an object.
+    ``feed`` returns the calls that became complete; ``flush`` what was cut off."""
+
+    def __init__(self):
+        self.open: Dict[int, Dict[str, str]] = {}
+
+    def feed(self, fragments) -> list:
+        for c in fragments:
+            e = self.open.setdefault(c.get("index", 0), {"name": "", "arguments": ""})
+            fn = c.get("function") or {}
+            e["name"] += fn.get("name") or ""
+            e["arguments"] += fn.get("arguments") or ""
+        done = []
+        for index in sorted(self.open):
+            e = self.open[index]
+            try:                                   # a proper prefix of an object never parses
+                args = json.loads(e["arguments"]) if e["arguments"] else None
+            except ValueError:
+                continue
+            if isinstance(args, dict):
+                done.append({"function": {"name": e["name"], "arguments": args}})
+                del self.open[index]
+        return done
+
+    def flush(self) -> list:
+        from .messages import RAW_ARGUMENTS
+        out = [{"function": {"name": e["name"],
+                             "arguments": {RAW_ARGUMENTS: e["arguments"]} if e["arguments"] else {}}}
+               for _i, e in sorted(self.open.items())]
+        self.open = {}
+        return out
+
+
 def translate(body: Dict[str, Any], generate: bool) -> Dict[str, Any]:
     """Ollama request -> native chat request."""
     if not isinstance(body, dict):
@@ -259,10 +294,7 @@ def install(app: FastAPI, service) -> None:
                 if thinking:
                     msg["thinking"] = thinking
                 if calls:
-                    msg["tool_calls"] = [{"function": {
-                        "name": c["function"]["name"],
-                        "arguments": json.loads(c["function"]["arguments"] or "{}")}}
-                        for c in calls]
+                    msg["tool_calls"] = calls              # whole calls (CallAssembler)
                 out["message"] = msg
             out["done"] = done
             if final:
@@ -279,6 +311,7 @@ def install(app: FastAPI, service) -> None:
                     "prompt_eval_duration": first - started,
                     "eval_count": u["completion_tokens"], "eval_duration": now - first}
 
+        assembler = CallAssembler()
         if stream:
             async def ndjson():
                 nonlocal first_token_ns
@@ -287,10 +320,13 @@ def install(app: FastAPI, service) -> None:
                         if ev["type"] == "delta":
                             first_token_ns = first_token_ns or time.perf_counter_ns()
                             d = ev["delta"]
-                            yield json.dumps(frame(d.content, d.reasoning, d.tool_calls),
-                                             ensure_ascii=False) + "\n"
+                            whole = assembler.feed(d.tool_calls)
+                            if d.content or d.reasoning or whole:
+                                yield json.dumps(frame(d.content, d.reasoning, whole),
+                                                 ensure_ascii=False) + "\n"
                         elif ev["type"] == "done":
-                            yield json.dumps(frame(done=True, final=finals(ev))) + "\n"
+                            yield json.dumps(frame(calls=assembler.flush(), done=True,
+                                                   final=finals(ev))) + "\n"
                         elif ev["type"] == "error":
                             yield json.dumps({"error": ev["message"]}) + "\n"
                 finally:
@@ -302,11 +338,11 @@ def install(app: FastAPI, service) -> None:
                 first_token_ns = first_token_ns or time.perf_counter_ns()
                 content += ev["delta"].content
                 thinking += ev["delta"].reasoning
-                calls += ev["delta"].tool_calls
+                calls += assembler.feed(ev["delta"].tool_calls)
             elif ev["type"] == "error":
                 return JSONResponse({"error": ev["message"]}, status_code=ev.get("status", 500))
             elif ev["type"] == "done":
-                return frame(content, thinking, calls, True, finals(ev))
+                return frame(content, thinking, calls + assembler.flush(), True, finals(ev))
         return JSONResponse({"error": "request ended without a result"}, status_code=500)
 
     @app.post("/api/chat")

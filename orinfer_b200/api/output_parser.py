@@ -98,6 +98,12 @@ class OutputParser:
         self.in_tool = False
         self.tool_text = ""
         self.tool_index = 0
+        # a JSON call body `{"name": ..., "arguments": {...}}` is streamed: the name as soon
+        # as it is complete, the arguments as raw fragments while they are generated
+        self.call_stage = 0                 # 0 header, 1 inside the arguments, 2 after them
+        self.call_seen = 0                  # characters of tool_text already scanned
+        self.call_depth = 0
+        self.call_string = self.call_escape = False
         self.stopped = False
         self.saw_tool_call = False
         self.reasoning_chars = 0
@@ -148,8 +154,13 @@ class OutputParser:
                 self.dsml = DsmlCalls()
             elif hit == TOOL_OPEN:
                 self.in_tool, self.tool_text = True, ""
+                self.call_stage = self.call_seen = self.call_depth = 0
+                self.call_string = self.call_escape = False
             elif hit == TOOL_CLOSE:
                 self.in_tool = False
+                if self.call_stage:         # streamed: name and arguments are out already
+                    self.tool_index += 1
+                    continue
                 call = parse_tool_call(self.tool_text)
                 if call is not None:
                     self.saw_tool_call = True
@@ -164,10 +175,59 @@ class OutputParser:
                 self.buffer = ""
                 break
         if final and self.in_tool:
-            # an unfinished call at the end of generation is returned as plain text
-            delta.content += TOOL_OPEN + self.tool_text
+            # an unfinished call at the end of generation is returned as plain text, unless
+            # its name went out already: then it stays a call with truncated arguments
+            if self.call_stage:
+                self.tool_index += 1
+            else:
+                delta.content += TOOL_OPEN + self.tool_text
             self.in_tool = False
         return delta
+
+    _CALL_HEAD = re.compile(r'\s*\{\s*"name"\s*:\s*("(?:[^"\\]|\\.)*")\s*,\s*"arguments"\s*:\s*(?=\S)')
+
+    def _stream_call(self, delta: Delta) -> None:
+        """Advance the streamed form of the call body collected in ``tool_text``."""
+        if self.call_stage == 0:
+            m = self._CALL_HEAD.match(self.tool_text)
+            if m is None or self.tool_text[m.end()] != "{":
+                return                      # not (yet) `{"name": "...", "arguments": {`
+            try:
+                name = json.loads(m.group(1))
+            except json.JSONDecodeError:
+                return
+            self.saw_tool_call = True
+            delta.tool_calls.append({"index": self.tool_index, "id": f"call_{self.tool_index}",
+                                     "type": "function",
+                                     "function": {"name": str(name), "arguments": ""}})
+            self.call_stage, self.call_seen = 1, m.end()
+        if self.call_stage != 1:
+            return
+        start = i = self.call_seen
+        text = self.tool_text
+        while i < len(text):
+            ch = text[i]
+            i += 1
+            if self.call_string:
+                if self.call_escape:
+                    self.call_escape = False
+                elif ch == "\\":
+                    self.call_escape = True
+                elif ch == '"':
+                    self.call_string = False
+            elif ch == '"':
+                self.call_string = True
+            elif ch == "{":
+                self.call_depth += 1
+            elif ch == "}":
+                self.call_depth -= 1
+                if self.call_depth == 0:
+                    self.call_stage = 2
+                    break
+        self.call_seen = i
+        if i > start:
+            delta.tool_calls.append({"index": self.tool_index,
+                                     "function": {"arguments": text[start:i]}})
 
     def _feed_dsml(self, delta: Delta) -> bool:
         """Run the buffered text through the DSML state machine; True when the block closed
@@ -202,6 +262,7 @@ class OutputParser:
             return
         if self.in_tool:
             self.tool_text += text
+            self._stream_call(delta)
         elif self.in_think:
             delta.reasoning += text
             self.reasoning_chars += len(text)

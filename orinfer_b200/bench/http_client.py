@@ -105,6 +105,10 @@ def stream_chat(base_url: str, body: dict, timeout: float = 600.0, session=None,
                         res.tool_calls.append(call)
                     if choice.get("finish_reason"):
                         res.finish_reason = choice["finish_reason"]
+            if res.tool_calls:                       # streamed fragments -> whole calls
+                from ..api.output_parser import merge_tool_calls
+                res.tool_calls = merge_tool_calls([dict(c, index=c.get("index", 0))
+                                                   for c in res.tool_calls])
             res.ok = not res.error
     except requests.RequestException as exc:
         res.error = f"{type(exc).__name__}: {exc}"[:500]

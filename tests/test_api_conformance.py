@@ -166,3 +166,118 @@ def test_unknown_routes_answer_in_the_error_shape(client):
     for path, code in (("/v1/missing", 404), ("/v1/chat/completions", 405)):
         r = client.get(path)
         assert r.status_code == code and r.json()["error"]["message"]
+
+
+@pytest.fixture(scope="module")
+def roomy():
+    """A server with room for tool prompts (2048-token context)."""
+    weights = random_model(PRESETS["tiny"], seed=0)
+    svc = Service(lambda: Engine(weights, sched=SchedulerOptions(max_active=4, prefill_chunk=64),
+                                 kv_pages=64, max_context=2048),
+                  ChatCodec(ByteTokenizer(1024), context=2048, model_name="tiny"), "tiny")
+    svc.start()
+    with TestClient(create_app(svc)) as c:
+        yield c
+    svc.stop(1000)
+
+
+def _sse(client, body):
+    out = []
+    with client.stream("POST", "/v1/chat/completions",
+                       json=dict(body, stream=True, stream_options={"include_usage": True})) as r:
+        for line in r.iter_lines():
+            if line.startswith("data: ") and line != "data: [DONE]":
+                out.append(json.loads(line[6:]))
+    return out
+
+
+def _check_scores(content, scores, count):
+    import math
+    assert b"".join(bytes(s["bytes"]) for s in scores).decode() == content
+    for s in scores:
+        assert math.isfinite(s["logprob"]) and s["logprob"] <= 0
+        tops = [t["logprob"] for t in s["top_logprobs"]]
+        assert len(tops) <= count and tops == sorted(tops, reverse=True)
+        assert all(math.isfinite(t) and t <= 0 for t in tops)
+
+
+COMMON = dict(temperature=0, seed=-20261002, max_completion_tokens=200,
+              messages=[{"role": "user", "content": "2+3?"}])
+LITERAL = "<think>中文</think><tool_call>literal</tool_call>"
+LITERAL_FORMAT = {"type": "json_schema", "json_schema": {"name": "literal", "strict": True, "schema": {
+    "type": "object", "properties": {"text": {"type": "string", "const": LITERAL}},
+    "required": ["text"], "additionalProperties": False}}}
+
+
+def test_json_literal_protocol_tags_and_probabilities_over_sse(roomy):
+    """A schema constant that spells the protocol's own tags is content, character for
+    character: it is neither parsed as reasoning or a tool call nor emitted as control tokens;
+    streamed text and probabilities equal the non-streamed ones; usage rides only the last
+    chunk; one token of budget ends with `length`."""
+    body = dict(COMMON, logprobs=True, top_logprobs=3, response_format=LITERAL_FORMAT)
+    full = roomy.post("/v1/chat/completions", json=body).json()
+    choice = full["choices"][0]
+    assert choice["finish_reason"] == "stop"
+    assert json.loads(choice["message"]["content"]) == {"text": LITERAL}
+    assert not choice["message"].get("tool_calls") and not choice["message"].get("reasoning_content")
+    _check_scores(choice["message"]["content"], choice["logprobs"]["content"], 3)
+    chunks = _sse(roomy, body)
+    text = "".join(c["choices"][0]["delta"].get("content") or "" for c in chunks if c["choices"])
+    scores = [s for c in chunks if c["choices"]
+              for s in (c["choices"][0].get("logprobs") or {}).get("content", [])]
+    assert text == choice["message"]["content"] and scores == choice["logprobs"]["content"]
+    assert all(c.get("usage") is None for c in chunks[:-1]) and chunks[-1]["usage"]
+    assert chunks[-2]["choices"][0]["finish_reason"] == "stop"
+    cut = roomy.post("/v1/chat/completions", json=dict(body, max_completion_tokens=1)).json()
+    assert cut["choices"][0]["finish_reason"] == "length"
+    # sampling under the constraint is reproducible for a seed
+    sampled = dict(body, temperature=0.7, top_p=0.9)
+    a = roomy.post("/v1/chat/completions", json=sampled).json()
+    b = roomy.post("/v1/chat/completions", json=sampled).json()
+    assert a["choices"] == b["choices"]
+
+
+def test_strict_tools_local_references_histories_and_thinking_budgets(roomy):
+    tools = [{"type": "function", "function": {
+        "name": "read_verification", "strict": True, "description": "Read a local code.",
+        "parameters": {"type": "object",
+                       "$defs": {"filename": {"type": "string", "enum": ["input.txt"]}},
+                       "properties": {"filename": {"$ref": "#/$defs/filename"},
+                                      "count": {"type": "integer", "const": 2}},
+                       "required": ["filename", "count"], "additionalProperties": False}}}]
+    ask = dict(COMMON, tools=tools, parallel_tool_calls=False, tool_choice="required",
+               messages=[{"role": "user", "content": "Call read_verification."}])
+    want = {"filename": "input.txt", "count": 2}
+    first = roomy.post("/v1/chat/completions", json=ask).json()["choices"][0]
+    call = first["message"]["tool_calls"][0]
+    assert first["finish_reason"] == "tool_calls" and json.loads(call["function"]["arguments"]) == want
+    # the call and its result as history (arguments travel as a JSON string), tools switched off
+    done = roomy.post("/v1/chat/completions", json=dict(
+        ask, tool_choice="none", max_completion_tokens=8, messages=ask["messages"] + [
+            {"role": "assistant", "content": None, "tool_calls": [call]},
+            {"role": "tool", "tool_call_id": call["id"], "content": '{"code":"CHECK_5824"}'}]))
+    assert done.status_code == 200 and not done.json()["choices"][0]["message"].get("tool_calls")
+    # a call whose arguments were cut off stays in the history for the model to recover from
+    broken = json.loads(json.dumps(call))
+    broken["function"]["arguments"] = '{"filename":'
+    again = roomy.post("/v1/chat/completions", json=dict(ask, messages=ask["messages"] + [
+        {"role": "assistant", "content": None, "tool_calls": [broken]},
+        {"role": "tool", "tool_call_id": broken["id"], "content": "Invalid arguments. Retry."}]))
+    assert again.status_code == 200, again.text
+    retry = again.json()["choices"][0]["message"]["tool_calls"][0]
+    assert json.loads(retry["function"]["arguments"]) == want
+    # thinking budgets hold beside a forced tool call and beside a schema
+    capped = roomy.post("/v1/chat/completions", json=dict(
+        ask, enable_thinking=True, thinking_token_budget=8)).json()
+    assert capped["choices"][0]["message"]["tool_calls"]
+    assert capped["usage"]["completion_tokens_details"]["reasoning_tokens"] <= 8
+    capped = roomy.post("/v1/chat/completions", json=dict(
+        COMMON, response_format=LITERAL_FORMAT, enable_thinking=True, thinking_token_budget=8)).json()
+    assert json.loads(capped["choices"][0]["message"]["content"]) == {"text": LITERAL}
+    assert capped["usage"]["completion_tokens_details"]["reasoning_tokens"] <= 8
+    # streamed forced call: several argument fragments, finish reason on the chunk before usage
+    chunks = _sse(roomy, ask)
+    deltas = [d for c in chunks if c["choices"] for d in c["choices"][0]["delta"].get("tool_calls", [])]
+    args = "".join(d["function"].get("arguments") or "" for d in deltas)
+    assert len(deltas) > 1 and json.loads(args) == want
+    assert chunks[-2]["choices"][0]["finish_reason"] == "tool_calls"

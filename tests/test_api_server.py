@@ -156,3 +156,21 @@ def test_keep_alive_forms():
     assert parse_keep_alive("60s") == 60 and parse_keep_alive("0") == 0
     with pytest.raises(ValueError):
         parse_keep_alive("soon")
+
+
+def test_ollama_shows_tool_calls_whole():
+    """The native stream cuts a call into fragments; the Ollama frames carry it once, with its
+    arguments as an object; a call that was cut off keeps its raw text."""
+    from orinfer_b200.api.messages import RAW_ARGUMENTS
+    from orinfer_b200.api.ollama import CallAssembler
+    from orinfer_b200.api.output_parser import OutputParser
+    raw = ('<tool_call>\n{"name": "get_time", "arguments": {"zone": "U}TC", "n": {"k": [1]}}}\n'
+           '</tool_call><tool_call>{"name": "second", "arguments": {"a"')
+    parser, asm, whole = OutputParser(), CallAssembler(), []
+    for ch in raw:
+        whole += asm.feed(parser.feed(ch).tool_calls)
+    whole += asm.feed(parser.feed("", final=True).tool_calls)
+    assert whole == [{"function": {"name": "get_time",
+                                   "arguments": {"zone": "U}TC", "n": {"k": [1]}}}}]
+    assert asm.flush() == [{"function": {"name": "second", "arguments": {RAW_ARGUMENTS: '{"a"'}}}]
+    assert parser.finish_reason("stop") == "tool_calls"

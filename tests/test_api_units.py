@@ -48,8 +48,13 @@ def test_parser_thinking_tools_and_withholding_every_split():
     for cut in range(1, len(text)):
         p = OutputParser(thinking=True, stops=["STOP"])
         parts = [p.feed(text[:cut]), p.feed(text[cut:], final=True)]
+        calls = {}
+        for c in (c for d in parts for c in d.tool_calls):       # fragments of a streamed call
+            e = calls.setdefault(c["index"], {"name": "", "arguments": ""})
+            e["name"] += c["function"].get("name") or ""
+            e["arguments"] += c["function"].get("arguments") or ""
         got = ("".join(d.reasoning for d in parts), "".join(d.content for d in parts),
-               [c["function"] for d in parts for c in d.tool_calls], p.stopped)
+               [calls[i] for i in sorted(calls)], p.stopped)
         want = want or got
         assert got == want, cut
     assert want[0] == "plan" and want[1] == "Hello  bye " and want[3]
