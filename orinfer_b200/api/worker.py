@@ -485,6 +485,13 @@ class EngineWorker(threading.Thread):
         tail = job.parser.feed(job.pending_bytes.decode("utf-8", errors="replace"), final=True)
         if not tail.empty() or job.logprob_entries:
             sink(job, {"type": "delta", "delta": tail, "logprobs": self._take_logprobs(job)})
+        if req.error:
+            # the request failed on its own (a constraint that cannot go on, logits that are
+            # not finite): its client gets the reason, nobody else notices
+            self.metrics.add("requests_failed_total")
+            sink(job, {"type": "error", "status": 500, "message": req.error,
+                       "code": "generation_failed"})
+            return
         reason = req.finish_reason or "stop"
         if reason == "cancelled" or job.parser.stopped:
             reason = "stop"

@@ -71,6 +71,7 @@ class EngineStatistics:
     sharded_samples: int = 0                  # rows drawn from a sharded head's candidates
     layered_decode_steps: int = 0             # decode steps taken inside paused prefill packets
     mixed_verify_packets: int = 0             # prefill packets that also verified drafts
+    failed_requests: int = 0                  # requests ended by an error of their own
     resident_steps: int = 0                   # decode steps that needed no input upload
     stored_snapshots: int = 0                 # recurrent-state endpoints kept for the prefix cache
     restored_snapshots: int = 0
@@ -1515,8 +1516,9 @@ class Engine:
             sel += 1
             if was_decode:
                 self.stats.decode_tokens += 1
-            tok = drawn[row] if row in drawn else self._sample(r, tokens, logits, row)
-            self._deliver(r, tok)
+            tok = drawn[row] if row in drawn else self._sample_or_fail(r, tokens, logits, row)
+            if tok is not None:
+                self._deliver(r, tok)
             produced.append(r)
         self._verify = {}
         return produced
@@ -1547,12 +1549,28 @@ class Engine:
         return (r.sampling.is_greedy and r.constraint is None and not r.want_logprobs
                 and r.sampling.top_logprobs is None)
 
+    def _sample_or_fail(self, r: Request, tokens, logits, row: int) -> Optional[int]:
+        """The next token of ``r``, or None after the request was failed: what goes wrong
+        while one request's token is chosen (its constraint rejects every token or cannot
+        follow the grammar, its logits are not finite) ends that request with an error its
+        client sees; the engine and the other requests carry on."""
+        try:
+            return self._sample(r, tokens, logits, row)
+        except Exception as exc:                       # noqa: BLE001 - any failure of this row
+            first = (str(exc).strip().splitlines() or [""])[0]
+            self._fail_request(r, f"{type(exc).__name__}: {first}")
+            return None
+
+    def _fail_request(self, r: Request, message: str) -> None:
+        r.error = message[:300]
+        self.stats.failed_requests += 1
+        self._finish(r, "error")
+
     def _sample(self, r: Request, tokens, logits, row: int) -> int:
         if self._plain(r):
             tok = int(tokens[row])
             if tok < 0:
-                r.error = "non-finite logits"
-                return 0
+                raise FloatingPointError("non-finite logits")
             return tok
         lg = logits[row].float().cpu().numpy()
         mask = None

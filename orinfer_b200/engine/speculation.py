@@ -308,8 +308,12 @@ class Speculator:
                 commit = S.sampled_commit(drafts, None, lg, r.history, r.sampling,
                                           len(r.generated))
             else:
-                commit = [eng._sample(r, tokens, logits, row)]
-            accepted = len(commit) - 1
+                tok = eng._sample_or_fail(r, tokens, logits, row)
+                commit = [] if tok is None else [tok]
+            if any(int(t) < 0 for t in commit):          # the device found no finite logit
+                eng._fail_request(r, "FloatingPointError: non-finite logits")
+                commit = []
+            accepted = max(len(commit) - 1, 0)
             kept_rows.append(1 + accepted)
             self.observe_local(r, len(drafts), accepted)
             if drafts:

@@ -281,3 +281,26 @@ def test_strict_tools_local_references_histories_and_thinking_budgets(roomy):
     args = "".join(d["function"].get("arguments") or "" for d in deltas)
     assert len(deltas) > 1 and json.loads(args) == want
     assert chunks[-2]["choices"][0]["finish_reason"] == "tool_calls"
+
+
+def test_a_failing_constraint_fails_one_request_not_the_server(roomy, monkeypatch):
+    from orinfer_b200.api import grammar
+    real = grammar.GrammarConstraint.consume
+    calls = {"n": 0}
+
+    def flaky(self, token):
+        calls["n"] += 1
+        if calls["n"] == 4:
+            raise grammar.GrammarError("parser too complex\nstate dump")
+        return real(self, token)
+
+    monkeypatch.setattr(grammar.GrammarConstraint, "consume", flaky)
+    body = dict(COMMON, response_format=LITERAL_FORMAT)
+    r = roomy.post("/v1/chat/completions", json=body)
+    assert r.status_code == 500 and r.json()["error"]["code"] == "generation_failed"
+    assert "parser too complex" in r.json()["error"]["message"]
+    assert "state dump" not in r.json()["error"]["message"]
+    assert roomy.get("/health").status_code == 200                   # still serving
+    ok = roomy.post("/v1/chat/completions", json=body)
+    assert ok.status_code == 200
+    assert json.loads(ok.json()["choices"][0]["message"]["content"]) == {"text": LITERAL}

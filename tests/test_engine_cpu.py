@@ -397,3 +397,37 @@ def test_follower_commands_check_what_they_can(weights):
     eng.apply("state_copy", ("drop", 7, -1))                  # dropping twice is harmless
     with pytest.raises(ValueError, match="unknown device command"):
         eng.apply("reboot", None)
+
+
+def test_a_request_whose_constraint_breaks_fails_alone(weights):
+    """What goes wrong while one request's token is chosen ends that request with an error;
+    the engine keeps serving the others and the text of a bystander is unchanged."""
+    class Breaks:
+        def __init__(self, after):
+            self.left = after
+
+        def mask(self, vocab):
+            return None
+
+        def consume(self, token):
+            self.left -= 1
+            if self.left < 0:
+                raise ValueError("grammar cannot follow this token\nlong state dump")
+
+        def finished(self):
+            return False
+
+    prompts = _prompts(2, 20, seed=31)
+    want = _engine(weights).generate([prompts[1]], max_new=8)[0]
+    eng = _engine(weights)
+    bad = eng.submit(prompts[0], 8)
+    bad.constraint = Breaks(after=3)
+    good = eng.submit(prompts[1], 8)
+    while eng.has_work():
+        eng.step()                                        # never raises
+    assert bad.finished and bad.finish_reason == "error" and len(bad.generated) == 3
+    assert bad.error == "ValueError: grammar cannot follow this token"
+    assert good.generated == want and good.error is None
+    assert eng.stats.failed_requests == 1 and eng.failed is None
+    again = eng.generate([prompts[0]], max_new=4)         # its slot and pages came back
+    assert len(again[0]) == 4
