@@ -68,11 +68,13 @@ def prepare_completion(codec, body: Dict[str, Any], defaults=None) -> Prepared:
 
 
 def install(app: FastAPI, service) -> None:
-    def chunk(rid, model, text, finish=None, usage=None, choices=True, token=None):
+    def plain_chunk(rid, model, text, finish=None, usage=None, choices=True, token=None,
+                    created=None):
         choice = {"index": 0, "text": text, "finish_reason": finish}
         if token is not None:
             choice["token_ids"] = [token]
-        body = {"id": rid, "object": "text_completion", "created": int(time.time()),
+        body = {"id": rid, "object": "text_completion",
+                "created": int(time.time()) if created is None else created,
                 "model": model, "choices": [choice] if choices else []}
         if usage is not None:
             body["usage"] = usage
@@ -96,6 +98,9 @@ def install(app: FastAPI, service) -> None:
         rid = "cmpl-" + uuid.uuid4().hex[:24]
         model = prepared.model
         if prepared.stream:
+            import functools
+            chunk = functools.partial(plain_chunk, created=job.created_unix)   # one per stream
+
             async def sse():
                 try:
                     async for ev in service.events(job):

@@ -128,7 +128,7 @@ def _chunk(job: Job, model: str, delta: dict, finish: Optional[str] = None,
     choice: Dict[str, Any] = {"index": 0, "delta": delta, "finish_reason": finish}
     if logprobs:
         choice["logprobs"] = {"content": logprobs}
-    body = {"id": job.rid, "object": "chat.completion.chunk", "created": int(time.time()),
+    body = {"id": job.rid, "object": "chat.completion.chunk", "created": job.created_unix,
             "model": model, "choices": [choice] if delta is not None else []}
     if usage is not None:
         body["usage"] = usage

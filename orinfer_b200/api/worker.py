@@ -50,6 +50,7 @@ class Job:
     loop: Optional[asyncio.AbstractEventLoop] = None
     events: Any = None                           # asyncio.Queue or queue.Queue
     created: float = field(default_factory=time.monotonic)
+    created_unix: int = field(default_factory=lambda: int(time.time()))   # `created` of every chunk
     cancelled: bool = False
     stop_requested: bool = False                 # the output side saw a stop string
     started_at: Optional[float] = None           # handed to the engine (end of queueing)

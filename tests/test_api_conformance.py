@@ -304,3 +304,33 @@ def test_a_failing_constraint_fails_one_request_not_the_server(roomy, monkeypatc
     ok = roomy.post("/v1/chat/completions", json=body)
     assert ok.status_code == 200
     assert json.loads(ok.json()["choices"][0]["message"]["content"]) == {"text": LITERAL}
+
+
+def test_stream_chunks_keep_one_identity_and_one_field_per_delta(roomy):
+    """Every chunk of a stream carries the same id / created / model / object; the role comes
+    once; the finish reason rides an empty delta; usage only the last chunk; a delta carries
+    content, reasoning or tool-call fragments, never two of them; text parts and a plain
+    string give the same result."""
+    tools = [{"type": "function", "function": {"name": "get_weather", "strict": True, "parameters": {
+        "type": "object", "properties": {"location": {"type": "string", "enum": ["Boston"]}},
+        "required": ["location"], "additionalProperties": False}}}]
+    body = dict(messages=[{"role": "user", "content": "Call it"}], tools=tools, tool_choice="required",
+                parallel_tool_calls=False, max_completion_tokens=80, temperature=0, seed=1)
+    chunks = _sse(roomy, body)
+    assert len(chunks) > 5
+    for name in ("id", "created", "model", "object"):
+        assert all(c[name] == chunks[0][name] for c in chunks), name
+    deltas = [c["choices"][0]["delta"] for c in chunks if c["choices"]]
+    assert [d["role"] for d in deltas if "role" in d] == ["assistant"] and deltas[-1] == {}
+    assert all(c["choices"][0]["finish_reason"] is None for c in chunks[:-2])
+    assert chunks[-2]["choices"][0]["finish_reason"] == "tool_calls" and chunks[-1]["choices"] == []
+    for d in deltas:
+        assert sum(bool(d.get(f)) for f in ("content", "reasoning_content", "tool_calls")) <= 1
+    usage = chunks[-1]["usage"]
+    assert usage["total_tokens"] == usage["prompt_tokens"] + usage["completion_tokens"]
+    parts = dict(COMMON, max_completion_tokens=8, messages=[{"role": "user", "content": [
+        {"type": "text", "text": "Say"}, {"type": "text", "text": " hi"}]}])
+    text = dict(parts, messages=[{"role": "user", "content": "Say hi"}])
+    a = roomy.post("/v1/chat/completions", json=parts).json()
+    b = roomy.post("/v1/chat/completions", json=text).json()
+    assert a["choices"] == b["choices"] and a["usage"] == b["usage"]
