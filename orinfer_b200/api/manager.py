@@ -58,20 +58,35 @@ class Runner:
 class ModelManager:
     """``start(entry) -> (service, bytes)`` builds and starts a runner; ``stop(service)``
     retires it.  Both run under the transition lock, so starts and stops are serialised while
-    models that are already up keep serving."""
+    models that are already up keep serving (their requests take only the table lock).
+
+    ``estimate(entry) -> bytes`` (optional) sizes a model before it is started, so that room
+    is made under the memory budget first; ``alive(service) -> bool`` (optional, default the
+    service's own ``alive()``) lets a runner that died be noticed and started again by the
+    next request.  When the budget is held by models in use, a request waits up to
+    ``capacity_wait_s`` for one of them to go idle (a waiter whose client left is not loaded
+    afterwards).  A start that failed is remembered for a short while and shared by everyone
+    who was waiting for it."""
 
     def __init__(self, state_dir, start: Callable[[Entry], tuple], stop: Callable[[object], None],
-                 memory_budget_bytes: int = 0, clock: Callable[[], float] = time.monotonic):
+                 memory_budget_bytes: int = 0, clock: Callable[[], float] = time.monotonic,
+                 estimate: Optional[Callable[[Entry], int]] = None,
+                 alive: Optional[Callable[[object], bool]] = None,
+                 capacity_wait_s: float = 0.0):
         self.state = Path(state_dir)
         self.state.mkdir(parents=True, exist_ok=True)
         self._start, self._stop = start, stop
+        self._estimate, self._alive = estimate, alive
+        self.capacity_wait_s = capacity_wait_s
         self.budget = memory_budget_bytes
         self.clock = clock
         self._lock = threading.Lock()              # registry + runner table
+        self._idle = threading.Condition(self._lock)   # a lease was returned / a runner left
         self._transition = threading.Lock()        # serialises starts / stops
         self.entries: Dict[str, Entry] = {}
         self.runners: Dict[str, Runner] = {}
         self._failed: Dict[str, tuple] = {}        # runner key -> (time, message)
+        self.restarts = 0                          # runners found dead and started again
         self._load()
 
     # ------------------------------------------------------------------ registry
@@ -129,35 +144,70 @@ class ModelManager:
             return self.entries[name]
 
     # ------------------------------------------------------------------ runners
-    def acquire(self, name: str, keep_alive_s: Optional[float] = None) -> Runner:
-        """Lease on the runner serving ``name`` (started if needed).  Pair with ``release``."""
+    def _is_alive(self, service) -> bool:
+        if self._alive is not None:
+            return bool(self._alive(service))
+        probe = getattr(getattr(service, "service", service), "alive", None)
+        return bool(probe()) if callable(probe) else True
+
+    def _lease(self, key: str, keep_alive_s: Optional[float]) -> Optional[Runner]:
+        """Under the table lock: a lease on the live runner of ``key``, or None (a runner
+        that died is taken out of the table here; its successor is started by the caller)."""
+        r = self.runners.get(key)
+        if r is None:
+            return None
+        if not self._is_alive(r.service):
+            del self.runners[key]
+            self.restarts += 1
+            self._idle.notify_all()
+            threading.Thread(target=self._stop, args=(r.service,), daemon=True).start()
+            return None
+        r.leases += 1
+        r.last_used = self.clock()
+        if keep_alive_s is not None:
+            r.keep_alive_s = keep_alive_s
+        return r
+
+    def _check_failed(self, name: str, key: str) -> None:
+        failed = self._failed.get(key)
+        if failed and self.clock() - failed[0] < NEGATIVE_CACHE_S:
+            raise ManagerError(f"model '{name}' failed to start: {failed[1]}", 503)
+
+    def acquire(self, name: str, keep_alive_s: Optional[float] = None,
+                cancelled: Optional[Callable[[], bool]] = None) -> Runner:
+        """Lease on the runner serving ``name`` (started if needed).  Pair with ``release``.
+        ``cancelled``: polled while waiting; a caller that has left gets no runner started."""
         entry = self.show(name)
         key = entry.runner_key()
+        gone = cancelled or (lambda: False)
         with self._lock:
-            r = self.runners.get(key)
+            r = self._lease(key, keep_alive_s)
             if r is not None:
-                r.leases += 1
-                r.last_used = self.clock()
-                if keep_alive_s is not None:
-                    r.keep_alive_s = keep_alive_s
                 return r
-            failed = self._failed.get(key)
-            if failed and self.clock() - failed[0] < NEGATIVE_CACHE_S:
-                raise ManagerError(f"model '{name}' failed to start: {failed[1]}", 503)
+            self._check_failed(name, key)
         with self._transition:
+            if gone():
+                raise ManagerError("the request was cancelled while waiting to start", 499)
             with self._lock:                        # someone else may have started it meanwhile
-                r = self.runners.get(key)
+                r = self._lease(key, keep_alive_s)
                 if r is not None:
-                    r.leases += 1
-                    r.last_used = self.clock()
                     return r
+                self._check_failed(name, key)       # ... or failed to: the failure is shared
             try:
+                if self._estimate is not None:
+                    self._make_room(int(self._estimate(entry)), gone)   # before it takes memory
                 service, nbytes = self._start(entry)
+            except ManagerError:
+                raise
             except Exception as exc:                # noqa: BLE001 - reported to the client
                 with self._lock:
                     self._failed[key] = (self.clock(), str(exc))
                 raise ManagerError(f"model '{name}' failed to start: {exc}", 503) from exc
-            self._make_room(nbytes)
+            try:
+                self._make_room(nbytes, gone)
+            except ManagerError:
+                self._stop(service)                 # it does not fit after all
+                raise
             r = Runner(key, service, nbytes, leases=1, last_used=self.clock(),
                        keep_alive_s=DEFAULT_KEEP_ALIVE_S if keep_alive_s is None else keep_alive_s)
             with self._lock:
@@ -169,11 +219,15 @@ class ModelManager:
         with self._lock:
             runner.leases = max(runner.leases - 1, 0)
             runner.last_used = self.clock()
+            self._idle.notify_all()
 
-    def _make_room(self, nbytes: int) -> None:
-        """Idle eviction under the memory budget: least recently used idle runners go first."""
+    def _make_room(self, nbytes: int, cancelled: Callable[[], bool] = lambda: False) -> None:
+        """Idle eviction under the memory budget: least recently used idle runners go first
+        (whatever their keep-alive).  With every runner in use the caller waits up to
+        ``capacity_wait_s`` for a lease to come back."""
         if self.budget <= 0:
             return
+        deadline = time.monotonic() + self.capacity_wait_s
         while True:
             with self._lock:
                 used = sum(r.bytes for r in self.runners.values())
@@ -182,7 +236,14 @@ class ModelManager:
                 idle = sorted((r for r in self.runners.values() if r.leases == 0),
                               key=lambda r: r.last_used)
                 if not idle:
-                    raise ManagerError("memory budget exhausted by models in use", 503)
+                    left = deadline - time.monotonic()
+                    if left <= 0 or nbytes > self.budget:
+                        raise ManagerError("memory budget exhausted by models in use", 503)
+                    self._idle.wait(min(left, 0.05))
+                    if cancelled():
+                        raise ManagerError("the request was cancelled while waiting for "
+                                           "memory", 499)
+                    continue
                 victim = idle[0].key
             self._retire(victim, force=True, locked=True)
 
@@ -195,6 +256,7 @@ class ModelManager:
                 if r.leases > 0:
                     return False
                 del self.runners[key]
+                self._idle.notify_all()
             self._stop(r.service)
             return True
         if locked:

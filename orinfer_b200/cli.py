@@ -239,6 +239,7 @@ def _serve_manager(a, host: str, port: int, load, sched) -> int:
     import copy
 
     import uvicorn
+    from .api.child_runner import weight_bytes
     from .api.manager import ModelManager, RunnerHandle, create_gateway_app
     from .api.server import Service, create_app
 
@@ -274,7 +275,9 @@ def _serve_manager(a, host: str, port: int, load, sched) -> int:
         handle.service.stop(a.drain_timeout_ms / 1e3 if process else a.drain_timeout_ms)
 
     manager = ModelManager(_state_dir(a), start_process if process else start, stop,
-                           memory_budget_bytes=getattr(a, "memory_budget_mib", 0) << 20)
+                           memory_budget_bytes=getattr(a, "memory_budget_mib", 0) << 20,
+                           estimate=lambda entry: weight_bytes(entry.path),
+                           capacity_wait_s=getattr(a, "capacity_wait_ms", 30000) / 1e3)
     print(f"API READY http://{a.listen}/v1; manager with {len(manager.list())} models",
           file=sys.stderr)
     uvicorn.Server(uvicorn.Config(create_gateway_app(manager), host=host, port=port,
@@ -566,6 +569,9 @@ def build_parser() -> argparse.ArgumentParser:
                         "on retirement) or as services inside the gateway process")
     s.add_argument("--memory-budget-mib", type=int, default=0,
                    help="manager mode: evict idle models beyond this many MiB of weights")
+    s.add_argument("--capacity-wait-ms", type=int, default=30000,
+                   help="manager mode: how long a request waits for a model in use to go idle "
+                        "when the memory budget leaves no room for its own model")
     s.set_defaults(fn=cmd_serve)
     b = sub.add_parser("batch")
     _load_args(b, batch=True)

@@ -54,12 +54,19 @@ def test_gateway_streams_through_a_child_process(model_dir, tmp_path):
         assert any(l.startswith("API READY") for l in lines)
         assert any(l.startswith("MODEL READY") for l in lines)
         assert c.get("/api/logs", params={"model": "ghost"}).status_code == 404
-        # a runner that died answers 502 in the OpenAI error shape, the gateway stays up
+        # a runner that died is noticed by the next request and started again
         started[0].stop(30)
+        back = c.post("/v1/chat/completions", json=body)
+        assert back.status_code == 200 and back.json()["usage"]["completion_tokens"] == 4
+        assert len(started) == 2 and m.restarts == 1 and started[1].alive()
+        # one that dies between the liveness check and the relay answers 502 in the OpenAI
+        # error shape, and the gateway stays up
+        m._alive = lambda service: True
+        started[1].stop(30)
         dead = c.post("/v1/chat/completions", json=body)
         assert dead.status_code == 502 and dead.json()["error"]["code"] == "runner_unavailable"
         assert c.get("/health").status_code == 200
-    assert stopped == ["tiny"] and not started[0].alive()
+    assert stopped.count("tiny") == 2 and not started[0].alive() and not started[1].alive()
 
 
 def test_child_that_cannot_start_reports_its_stderr(tmp_path):

@@ -59,10 +59,86 @@ def test_budget_evicts_idle_lru_and_refuses_when_all_in_use(tmp_path):
     with pytest.raises(M.ManagerError) as err:
         m.acquire("c")                                            # 300 > 250, nothing idle
     assert err.value.status == 503
+    assert stopped == ["svc:/models/c"]                           # what did not fit was stopped again
     m.release(ra); clock.t = 3
     m.acquire("c")
-    assert stopped == ["svc:/models/a"] and {r["names"][0] for r in m.running()} == {"b", "c"}
+    assert stopped[1:] == ["svc:/models/a"] and {r["names"][0] for r in m.running()} == {"b", "c"}
     m.release(rb)
+
+
+def test_lifecycle_under_pressure_failures_and_dead_runners(tmp_path):
+    """Room is made before a sized model starts; a request waits for capacity and a waiter
+    that left is never loaded; concurrent requests share one start and one failure, and a
+    later retry recovers; a runner that died is started again by the next request; memory
+    pressure ignores a keep-alive of forever."""
+    import threading
+    import time
+    starts, stopped, alive = [], [], {}
+    fail = {"on": False}
+
+    def start(entry):
+        starts.append(entry.name)
+        time.sleep(0.05)
+        if fail["on"]:
+            raise RuntimeError("boom")
+        svc = f"svc:{entry.name}:{len(starts)}"
+        alive[svc] = True
+        return svc, 100
+
+    m = M.ModelManager(tmp_path, start, stopped.append, 250, estimate=lambda e: 100,
+                       alive=lambda s: alive.get(s, False), capacity_wait_s=2.0)
+    for n in "abc":
+        m.register(n, f"/models/{n}")
+    ra, rb = m.acquire("a", keep_alive_s=-1), m.acquire("b", keep_alive_s=-1)
+    # c waits for capacity; it is loaded once a lease comes back, evicting the idle model
+    got = {}
+    waiter = threading.Thread(target=lambda: got.setdefault("c", m.acquire("c")))
+    waiter.start()
+    time.sleep(0.2)
+    assert starts == ["a", "b"] and waiter.is_alive()            # sized first: not started yet
+    m.release(ra)
+    waiter.join(5)
+    assert got["c"].leases == 1 and stopped == ["svc:a:1"] and starts == ["a", "b", "c"]
+    # a waiter whose client left is not loaded when space appears
+    left = {"flag": False}
+    err = {}
+
+    def leaver():
+        try:
+            m.acquire("a", cancelled=lambda: left["flag"])
+        except M.ManagerError as e:
+            err["e"] = e
+    t = threading.Thread(target=leaver)
+    t.start()
+    time.sleep(0.2)
+    left["flag"] = True
+    t.join(5)
+    assert err["e"].status == 499 and starts == ["a", "b", "c"]
+    m.release(rb); m.release(got["c"])
+    # two requests for a model that cannot start share one attempt and one failure
+    fail["on"] = True
+    errors = []
+
+    def want_a():
+        try:
+            m.acquire("a")
+        except M.ManagerError as e:
+            errors.append(e.status)
+    pair = [threading.Thread(target=want_a) for _ in range(2)]
+    [p.start() for p in pair]
+    [p.join(5) for p in pair]
+    assert errors == [503, 503] and starts.count("a") == 2        # the first load and this one
+    fail["on"] = False
+    m._failed.clear()                                             # the negative cache ran out
+    ra = m.acquire("a")
+    assert ra.leases == 1
+    m.release(ra)
+    # a runner that died is noticed by the next request and started again
+    alive[ra.service] = False
+    again = m.acquire("a")
+    assert again.service != ra.service and m.restarts == 1 and alive[again.service]
+    m.release(again)
+    m.shutdown()
 
 
 def test_keep_alive_sweep_and_negative_cache(tmp_path):
