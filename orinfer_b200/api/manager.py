@@ -22,7 +22,7 @@ from pathlib import Path
 from typing import Callable, Dict, List, Optional
 
 from fastapi import Request as HttpRequest
-from fastapi.responses import JSONResponse, Response
+from fastapi.responses import JSONResponse, PlainTextResponse, Response
 
 NEGATIVE_CACHE_S = 10.0
 DEFAULT_KEEP_ALIVE_S = 300.0
@@ -303,6 +303,19 @@ class ModelManager:
             self._stop(r.service)
             return True
 
+    def unload_or_expire(self, name: str) -> bool:
+        """Unload now when idle; a model with requests in flight gets a keep-alive of zero, so
+        it goes as soon as they end.  False when it was not loaded."""
+        try:
+            return self.unload(name, force=False)
+        except ManagerError:
+            key = self.show(name).runner_key()
+            with self._lock:
+                r = self.runners.get(key)
+                if r is not None:
+                    r.keep_alive_s = 0.0
+            return r is not None
+
     def logs(self, name: str) -> List[str]:
         """Recent stderr lines of the runner serving ``name`` (child-process runners keep a
         tail; in-process ones have none); 409 when the model is not loaded."""
@@ -322,10 +335,75 @@ class ModelManager:
                 self._stop(r.service)
 
 
+def describe(entry: Entry) -> dict:
+    """What `/api/show` says about a registered model, read from its files alone: no runner is
+    started and nothing touches a GPU.  Geometry from ``config.json``, the chat template from
+    ``chat_template.jinja`` or ``tokenizer_config.json``, capabilities from the geometry (an
+    encoder embeds, a decoder completes, calls tools and thinks; a vision section adds
+    ``vision``)."""
+    root = Path(entry.path)
+
+    def read(name):
+        try:
+            return json.loads((root / name).read_text())
+        except (OSError, ValueError):
+            return {}
+    cfg = read("config.json")
+    text = cfg.get("text_config") if isinstance(cfg.get("text_config"), dict) else cfg
+    arch = str(cfg.get("arch") or (cfg.get("architectures") or ["orinfer"])[0])
+    template = ""
+    if (root / "chat_template.jinja").exists():
+        template = (root / "chat_template.jinja").read_text()
+    else:
+        template = str(read("tokenizer_config.json").get("chat_template") or "")
+    encoder = bool(cfg.get("bidirectional"))
+    caps = ["embedding"] if encoder else ["completion", "tools", "thinking"]
+    if "vision_config" in cfg or entry.options.get("vision"):
+        caps.append("vision")
+    info = {"general.architecture": arch}
+    for key, field_ in (("context_length", "max_context"), ("embedding_length", "hidden"),
+                        ("block_count", "layers"), ("vocab_size", "vocab")):
+        value = text.get(field_)
+        if value is None:
+            value = {"max_context": text.get("max_position_embeddings"),
+                     "hidden": text.get("hidden_size"),
+                     "layers": text.get("num_hidden_layers"),
+                     "vocab": text.get("vocab_size")}[field_]
+        if value is not None:
+            info[f"{arch}.{key}"] = value
+    limit = entry.options.get("max_context")
+    if limit:
+        info[f"{arch}.context_length"] = limit
+    return {"details": {"family": arch, "format": "safetensors", "path": entry.path,
+                        "quantization_level": "E8P-Q4A8"},
+            "model_info": info, "capabilities": caps, "template": template,
+            "parameters": "\n".join(f"{k} {v}" for k, v in sorted(entry.defaults.items()))}
+
+
 def install(app, manager: ModelManager) -> None:
     """Registry routes of the Ollama surface on a gateway app."""
     def fail(e: ManagerError):
         return JSONResponse({"error": str(e)}, status_code=e.status)
+
+    @app.get("/")
+    async def root():
+        return PlainTextResponse("Orinfer is running")
+
+    @app.get("/api/version")
+    async def version():
+        from .. import __version__
+        return {"version": __version__}
+
+    @app.post("/api/show")
+    async def show(request: HttpRequest):
+        try:
+            body = json.loads(await request.body() or b"{}")
+        except ValueError:
+            return JSONResponse({"error": "invalid JSON"}, status_code=400)
+        try:
+            return describe(manager.show(body.get("model") or body.get("name") or ""))
+        except ManagerError as e:
+            return fail(e)
 
     @app.get("/api/tags")
     async def tags():
@@ -334,7 +412,17 @@ def install(app, manager: ModelManager) -> None:
 
     @app.get("/api/ps")
     async def ps():
-        return {"models": [{"name": n, "size": r["bytes"], "leases": r["leases"]}
+        import datetime
+        now = datetime.datetime.now(datetime.timezone.utc)
+
+        def expires(r):
+            if r["keep_alive_s"] < 0:
+                return "9999-12-31T23:59:59Z"                # kept until told otherwise
+            left = r["keep_alive_s"] - (r["idle_s"] if r["leases"] == 0 else 0.0)
+            return (now + datetime.timedelta(seconds=max(left, 0.0))).strftime(
+                "%Y-%m-%dT%H:%M:%SZ")
+        return {"models": [{"name": n, "model": n, "size": r["bytes"], "size_vram": r["bytes"],
+                            "leases": r["leases"], "expires_at": expires(r)}
                            for r in manager.running() for n in r["names"]]}
 
     @app.post("/api/copy")
@@ -460,11 +548,36 @@ def create_gateway_app(manager: ModelManager, sweep_s: float = 5.0):
             return fail_ollama(err) if ollama else openai_error(err)
         keep = None
         if ollama and "keep_alive" in payload:
+            from .chat_codec import RequestError
             from .ollama import parse_keep_alive
-            keep = parse_keep_alive(payload["keep_alive"])
+            try:
+                keep = parse_keep_alive(payload["keep_alive"])
+            except RequestError as e:
+                return JSONResponse({"error": e.message}, status_code=400)
+        run = asyncio.get_running_loop().run_in_executor
+        generate = request.url.path == "/api/generate"
+        if ollama and request.url.path in ("/api/generate", "/api/chat") \
+                and not payload.get("prompt" if generate else "messages"):
+            # no prompt: the request only loads the model or, with keep_alive 0, unloads it;
+            # nothing is generated and an unload starts nothing
+            import datetime
+            try:
+                if keep == 0:
+                    manager.show(name)
+                    await run(None, manager.unload_or_expire, name)
+                    reason = "unload"
+                else:
+                    await run(None, manager.load, name, keep)
+                    reason = "load"
+            except ManagerError as e:
+                return fail_ollama(e)
+            stamp = datetime.datetime.now(datetime.timezone.utc).strftime("%Y-%m-%dT%H:%M:%SZ")
+            empty = {"response": ""} if generate else {"message": {"role": "assistant",
+                                                                   "content": ""}}
+            return JSONResponse(dict(empty, model=name, created_at=stamp, done=True,
+                                     done_reason=reason))
         try:
-            runner = await asyncio.get_running_loop().run_in_executor(
-                None, manager.acquire, name, keep)
+            runner = await run(None, manager.acquire, name, keep)
         except ManagerError as e:
             return fail_ollama(e) if ollama else openai_error(e)
         return _Forward(runner.service.app, body, lambda: manager.release(runner))
@@ -481,7 +594,7 @@ def create_gateway_app(manager: ModelManager, sweep_s: float = 5.0):
                  "/v1/embeddings",
                  "/v1/rerank", "/rerank", "/v1/audio/transcriptions"):
         app.add_api_route(path, handler(False), methods=["POST"])
-    for path in ("/api/chat", "/api/generate", "/api/show", "/api/embed", "/api/embeddings"):
+    for path in ("/api/chat", "/api/generate", "/api/embed", "/api/embeddings"):
         app.add_api_route(path, handler(True), methods=["POST"])
 
     @app.get("/health")

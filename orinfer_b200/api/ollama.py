@@ -315,8 +315,10 @@ def install(app: FastAPI, service) -> None:
         if stream:
             async def ndjson():
                 nonlocal first_token_ns
+                ended = False
                 try:
                     async for ev in service.events(job):
+                        ended = ended or ev["type"] in ("done", "error")
                         if ev["type"] == "delta":
                             first_token_ns = first_token_ns or time.perf_counter_ns()
                             d = ev["delta"]
@@ -329,6 +331,9 @@ def install(app: FastAPI, service) -> None:
                                                    final=finals(ev))) + "\n"
                         elif ev["type"] == "error":
                             yield json.dumps({"error": ev["message"]}) + "\n"
+                    if not ended:
+                        # a stream that just stops is an error, not a short success
+                        yield json.dumps({"error": "the response ended without a result"}) + "\n"
                 finally:
                     job.cancelled = True
             return StreamingResponse(ndjson(), media_type="application/x-ndjson")

@@ -278,3 +278,69 @@ def test_gateway_forwards_by_model_and_releases_leases(tmp_path):
         assert c.post("/api/generate", json={"model": "nope", "prompt": "x"}).status_code == 404
         assert [x["name"] for x in c.get("/api/ps").json()["models"]] == ["tiny", "tiny-alias"]
     assert stopped == ["tiny-alias"]                                # shutdown retired the runner
+
+
+def test_discovery_reads_files_and_starts_nothing(tmp_path):
+    """`/`, `/api/version`, `/api/tags`, `/api/ps` and `/api/show` of the gateway are answered
+    from the registry and the model's files; no runner is started for them."""
+    import json
+    from fastapi.testclient import TestClient
+    root = tmp_path / "model"
+    root.mkdir()
+    (root / "config.json").write_text(json.dumps(
+        {"architectures": ["TestForCausalLM"],
+         "text_config": {"hidden_size": 256, "num_hidden_layers": 4,
+                         "max_position_embeddings": 8192}, "vision_config": {}}))
+    (root / "tokenizer_config.json").write_text(json.dumps({"chat_template": "native jinja"}))
+    starts = []
+    m = M.ModelManager(tmp_path / "state", lambda e: starts.append(e.name), lambda s: None)
+    m.register("fixture:2b", str(root), defaults={"temperature": 0.2})
+    with TestClient(M.create_gateway_app(m, sweep_s=3600)) as c:
+        for route in ("/", "/api/version", "/api/tags", "/api/ps"):
+            assert c.get(route).status_code == 200, route
+        assert c.get("/api/tags").json()["models"][0]["name"] == "fixture:2b"
+        shown = c.post("/api/show", json={"model": "fixture:2b"}).json()
+        assert shown["model_info"]["TestForCausalLM.context_length"] == 8192
+        assert shown["model_info"]["TestForCausalLM.block_count"] == 4
+        assert shown["template"] == "native jinja" and "vision" in shown["capabilities"]
+        assert "temperature 0.2" in shown["parameters"]
+        assert c.post("/api/show", json={"model": "absent"}).status_code == 404
+        bad = c.post("/api/chat", content="{")
+        assert bad.status_code == 400 and isinstance(bad.json()["error"], str)
+    assert starts == []
+
+
+def test_gateway_load_and_unload_requests_generate_nothing(tmp_path):
+    """An Ollama request without a prompt loads the model (or, with keep_alive 0, unloads it)
+    at the gateway: nothing is generated, an unload starts nothing, `/api/ps` shows when a
+    model goes, malformed keep-alives are client errors."""
+    from fastapi.testclient import TestClient
+    starts, stops, seen = [], [], []
+
+    class App:                                                   # a runner that must not be asked
+        async def __call__(self, scope, receive, send):
+            seen.append(scope["path"])
+            raise AssertionError("no request may reach the runner")
+
+    def start(entry):
+        starts.append(entry.name)
+        return M.RunnerHandle(object(), App()), 100
+
+    m = M.ModelManager(tmp_path, start, lambda h: stops.append(1))
+    m.register("fixture:2b", "/models/x")
+    with TestClient(M.create_gateway_app(m, sweep_s=3600)) as c:
+        gone = c.post("/api/generate", json={"model": "fixture:2b", "keep_alive": 0})
+        assert gone.status_code == 200 and gone.json()["done_reason"] == "unload" and starts == []
+        up = c.post("/api/generate", json={"model": "fixture:2b", "keep_alive": -1, "stream": False})
+        assert up.json()["done_reason"] == "load" and up.json()["response"] == "" and starts == ["fixture:2b"]
+        ps = c.get("/api/ps").json()["models"][0]
+        assert ps["name"] == "fixture:2b" and ps["expires_at"] == "9999-12-31T23:59:59Z"
+        chat = c.post("/api/chat", json={"model": "fixture:2b", "keep_alive": "5m"})
+        assert chat.json()["done_reason"] == "load" and chat.json()["message"]["content"] == ""
+        assert c.get("/api/ps").json()["models"][0]["expires_at"].startswith("20")
+        down = c.post("/api/chat", json={"model": "fixture:2b", "messages": [], "keep_alive": 0})
+        assert down.json()["done_reason"] == "unload" and stops == [1] and m.running() == []
+        assert c.post("/api/generate", json={"model": "absent"}).status_code == 404
+        bad = c.post("/api/generate", json={"model": "fixture:2b", "prompt": "hi", "keep_alive": {}})
+        assert bad.status_code == 400 and isinstance(bad.json()["error"], str)
+    assert seen == [] and starts == ["fixture:2b"]
