@@ -335,6 +335,32 @@ class ModelManager:
                 self._stop(r.service)
 
 
+def apply_entry_defaults(payload: dict, defaults: Dict[str, object], ollama: bool) -> dict:
+    """The request with the sampling defaults of the name it was sent to underneath it (the
+    request's own fields win).  Names that share a runner keep their own defaults this way.
+    Ollama bodies take them through ``options`` / ``think``; defaults without an Ollama
+    spelling are left to the native routes."""
+    if not defaults:
+        return payload
+    if not ollama:
+        from .chat_codec import merge_defaults
+        return merge_defaults(payload, defaults)
+    from .ollama import OPTION_MAP
+    spelling = {native: name for name, native in OPTION_MAP.items()}
+    out = dict(payload)
+    options = dict(out.get("options") or {})
+    for key, value in defaults.items():
+        if key in spelling:
+            options.setdefault(spelling[key], value)
+        elif key == "max_completion_tokens":
+            options.setdefault("num_predict", value)
+        elif key in ("enable_thinking", "reasoning_effort"):
+            out.setdefault("think", value)
+    if options:
+        out["options"] = options
+    return out
+
+
 def describe(entry: Entry) -> dict:
     """What `/api/show` says about a registered model, read from its files alone: no runner is
     started and nothing touches a GPU.  Geometry from ``config.json``, the chat template from
@@ -576,6 +602,13 @@ def create_gateway_app(manager: ModelManager, sweep_s: float = 5.0):
                                                                    "content": ""}}
             return JSONResponse(dict(empty, model=name, created_at=stamp, done=True,
                                      done_reason=reason))
+        if payload:
+            try:                                     # the addressed name's own defaults
+                merged = apply_entry_defaults(payload, manager.show(name).defaults, ollama)
+            except ManagerError as e:
+                return fail_ollama(e) if ollama else openai_error(e)
+            if merged is not payload:
+                body = _json.dumps(merged, ensure_ascii=False).encode()
         try:
             runner = await run(None, manager.acquire, name, keep)
         except ManagerError as e:

@@ -248,7 +248,7 @@ def _serve_manager(a, host: str, port: int, load, sched) -> int:
         args.model_dir, args.preset = entry.path, None
         weights, name = _weights(args)
         svc = Service(_engine_factory(args, weights, load, sched), _codec(args, weights, entry.name),
-                      entry.name, dict(json.loads(a.default_request_params), **entry.defaults),
+                      entry.name, json.loads(a.default_request_params),   # per-name defaults: gateway
                       a.queue_timeout_ms, a.output_timeout_ms, a.preparation_workers,
                       a.preparation_memory_mib)
         svc.start()
@@ -263,7 +263,7 @@ def _serve_manager(a, host: str, port: int, load, sched) -> int:
                  "--max-active-requests", str(a.max_active_requests),
                  "--prefix-cache-mib", str(a.prefix_cache_mib), "--tp", str(a.tp),
                  "--default-request-params",
-                 json.dumps(dict(json.loads(a.default_request_params), **entry.defaults))]
+                 a.default_request_params]           # per-name defaults are applied by the gateway
         if a.max_context:
             extra += ["--max-context", str(a.max_context)]
         child = ChildRunner(entry.path, entry.name, extra).start()

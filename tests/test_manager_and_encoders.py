@@ -344,3 +344,43 @@ def test_gateway_load_and_unload_requests_generate_nothing(tmp_path):
         bad = c.post("/api/generate", json={"model": "fixture:2b", "prompt": "hi", "keep_alive": {}})
         assert bad.status_code == 400 and isinstance(bad.json()["error"], str)
     assert seen == [] and starts == ["fixture:2b"]
+
+
+def test_names_that_share_a_runner_keep_their_own_defaults(tmp_path):
+    """An alias's sampling defaults are laid under each request at the gateway (the request's
+    own fields win, alternative spellings of one limit are respected); Ollama bodies get them
+    through `options` / `think`."""
+    import json
+    from fastapi.testclient import TestClient
+    from starlette.responses import JSONResponse as Echo
+
+    class App:
+        async def __call__(self, scope, receive, send):
+            body = (await receive())["body"]
+            await Echo(json.loads(body))(scope, receive, send)
+
+    starts = []
+
+    def start(entry):
+        starts.append(entry.name)
+        return M.RunnerHandle(object(), App()), 1
+
+    m = M.ModelManager(tmp_path, start, lambda h: None)
+    m.register("base", "/models/x")
+    m.register("warm", "/models/x", defaults={"temperature": 0.7, "max_tokens": 64,
+                                              "enable_thinking": True})
+    msgs = [{"role": "user", "content": "hi"}]
+    with TestClient(M.create_gateway_app(m, sweep_s=3600)) as c:
+        plain = c.post("/v1/chat/completions", json={"model": "base", "messages": msgs}).json()
+        assert plain == {"model": "base", "messages": msgs}
+        warm = c.post("/v1/chat/completions", json={"model": "warm", "messages": msgs}).json()
+        assert warm["temperature"] == 0.7 and warm["max_tokens"] == 64 and warm["enable_thinking"]
+        own = c.post("/v1/chat/completions", json={"model": "warm", "messages": msgs,
+                                                   "temperature": 0, "max_completion_tokens": 8}).json()
+        assert own["temperature"] == 0 and own["max_completion_tokens"] == 8
+        assert "max_tokens" not in own                       # one limit, the request's spelling
+        oll = c.post("/api/chat", json={"model": "warm", "messages": msgs,
+                                        "options": {"top_p": 0.5}}).json()
+        assert oll["options"] == {"top_p": 0.5, "temperature": 0.7, "num_predict": 64}
+        assert oll["think"] is True
+    assert starts == ["base"]                                # same files, same options: one runner
