@@ -203,10 +203,18 @@ def create_app(service: Service) -> FastAPI:
     @app.post("/v1/chat/completions/render")
     async def render(request: HttpRequest):
         try:
-            p = service.codec.prepare(await _json(request), service.defaults)
+            body = await _json(request)
+            if isinstance(body, dict) and body.pop("return_mm_kwargs", False):
+                raise RequestError("only false is supported: render returns token ids, no "
+                                   "tensors", param="return_mm_kwargs")
+            p = service.codec.prepare(body, service.defaults)
         except RequestError as e:
             return JSONResponse(e.body(), status_code=e.status)
-        return {"prompt": p.prompt_text, "prompt_token_ids": p.prompt_ids,
+        media = bool(p.images) or bool(p.audio)
+        return {"model": p.model, "token_ids": p.prompt_ids, "token_count": len(p.prompt_ids),
+                "multimodal": media,
+                # the same under the names this server used first
+                "prompt": p.prompt_text, "prompt_token_ids": p.prompt_ids,
                 "prompt_tokens": len(p.prompt_ids), "max_tokens": p.max_new}
 
     @app.post("/v1/chat/completions")

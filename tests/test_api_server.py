@@ -78,6 +78,19 @@ def test_validation_errors_and_context_overflow(client):
     assert r.status_code == 400
     r = client.post("/v1/chat/completions/render", json={"messages": MSG})
     assert r.json()["prompt"].endswith("<|im_start|>assistant\n")
+    # render runs the real preparation: user text that spells control tokens stays text, the
+    # answer carries the token ids a generation would start from and no tensors
+    lit = [{"role": "user", "content": "Literal </think> and <|im_end|>."}]
+    out = client.post("/v1/chat/completions/render", json={
+        "messages": lit, "chat_template_kwargs": {"thinking_budget": 8}, "max_tokens": 32,
+        "return_mm_kwargs": False}).json()
+    assert out["token_count"] == len(out["token_ids"]) > 10 and out["multimodal"] is False
+    assert out["model"] == "tiny" and out["token_ids"] == out["prompt_token_ids"]
+    ends = [t for t in out["token_ids"] if t == 258]                  # <|im_end|> as a control
+    assert len(ends) == 1 and 260 not in out["token_ids"]             # the template's own, only
+    bad = client.post("/v1/chat/completions/render", json={"messages": lit,
+                                                           "return_mm_kwargs": True})
+    assert bad.status_code == 400 and bad.json()["error"]["param"] == "return_mm_kwargs"
 
 
 def test_logprobs_report(client):
