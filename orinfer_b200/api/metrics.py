@@ -20,9 +20,24 @@ class Metrics:
         self.counters: Dict[str, float] = {
             "prompt_tokens_total": 0, "completion_tokens_total": 0, "cached_tokens_total": 0,
             "requests_total": 0, "request_errors_total": 0, "compute_seconds_total": 0.0,
-            "admission_seconds_total": 0.0}
+            "admission_seconds_total": 0.0,
+            # the reference's spellings of the token counters and of its failure, planning,
+            # cache and reclaim counters (server/metrics.rs:90-235)
+            "generated_tokens_total": 0, "cached_prompt_tokens_total": 0,
+            "sampling_request_failures_total": 0, "batch_plan_seconds_total": 0.0,
+            "prefix_cache_evictions_total": 0, "prefix_cache_host_evictions_total": 0,
+            "prefix_restore_seconds_total": 0.0, "program_reclaims_total": 0}
         self.gauges: Dict[str, float] = {"requests_running": 0, "requests_waiting": 0,
-                                         "backend_healthy": 1}
+                                         "backend_healthy": 1,
+                                         "prefix_cache_device_entries": 0,
+                                         "prefix_cache_device_bytes": 0,
+                                         "prefix_cache_host_entries": 0,
+                                         "prefix_cache_host_bytes": 0}
+
+    def level(self, name: str, value: float) -> None:
+        """A counter whose source keeps the running total itself (engine statistics)."""
+        with self._lock:
+            self.counters[name] = max(self.counters.get(name, 0), value)
 
     def observe(self, name: str, seconds: float) -> None:
         with self._lock:

@@ -245,11 +245,29 @@ class EngineWorker(threading.Thread):
         spec = eng.spec.statistics()
         m.set("speculation_acceptance_rate", spec.get("acceptance_rate", 0.0))
         m.set("speculation_rounds_total", spec.get("rounds", 0))
+        m.level("batch_plan_seconds_total", eng.stats.batch_inputs_s)
+        m.level("sampling_request_failures_total", eng.stats.failed_requests)
+        pool = getattr(eng, "_prefill_graphs", None)
+        if pool is not None and hasattr(pool, "evictions"):
+            m.level("program_reclaims_total", pool.evictions)
+        if eng.on_gpu:
+            import torch
+            free = torch.cuda.mem_get_info(eng.device)[0]
+            m.set("device_rank_free_bytes_min", free)      # one rank per process
+            m.set("device_rank_free_bytes_max", free)
         if eng.prefix is not None:
             st = eng.prefix.statistics()
+            page = eng.kv.bytes_per_page(eng.cfg, eng.cfg.mtp_layers)
             m.set("prefix_cache_hit_rate", st.hit_rate)
             m.set("prefix_cache_device_pages", st.device_pages)
             m.set("prefix_cache_host_pages", st.host_pages)
+            m.set("prefix_cache_device_entries", st.device_pages)
+            m.set("prefix_cache_device_bytes", st.device_pages * page)
+            m.set("prefix_cache_host_entries", st.host_pages)
+            m.set("prefix_cache_host_bytes", st.host_pages * page)
+            m.level("prefix_cache_evictions_total", st.evicted)
+            dropped = max(st.offloaded - st.restored - st.host_pages, 0)
+            m.level("prefix_cache_host_evictions_total", dropped)
 
     def _instrument(self) -> None:
         """Time the engine's admission pass and its prefix-cache store / host restore calls for
@@ -269,7 +287,9 @@ class EngineWorker(threading.Thread):
             "admission_seconds_total", dt) if dt > 1e-5 else None)
         eng._restore_host_pages = timed(
             eng._restore_host_pages,
-            lambda dt, a, out: metrics.observe("prefix_restore", dt) if dt > 1e-5 else None)
+            lambda dt, a, out: (metrics.observe("prefix_restore", dt),
+                                metrics.add("prefix_restore_seconds_total", dt))
+            if dt > 1e-5 else None)
         if eng.prefix is not None:
             eng.prefix.insert = timed(eng.prefix.insert,
                                       lambda dt, a, out: metrics.observe("prefix_store", dt))
@@ -505,7 +525,9 @@ class EngineWorker(threading.Thread):
         self.metrics.add("requests_total")
         self.metrics.add("prompt_tokens_total", len(req.prompt))
         self.metrics.add("completion_tokens_total", len(req.generated))
+        self.metrics.add("generated_tokens_total", len(req.generated))
         self.metrics.add("cached_tokens_total", req.cached_tokens)
+        self.metrics.add("cached_prompt_tokens_total", req.cached_tokens)
         reasoning = 0
         if job.prepared.thinking:
             close = self.codec.tokenizer.encode("</think>")

@@ -38,9 +38,26 @@ def test_health_models_metrics(client):
     assert client.get("/v1/models/tiny").json()["object"] == "model"
     gone = client.get("/v1/models/other")
     assert gone.status_code == 404 and gone.json()["error"]["code"] == "model_not_found"
+    client.post("/v1/chat/completions", json={"messages": MSG, "max_tokens": 3,
+                                              "ignore_eos": True})
     r = client.get("/metrics")
     assert "orinfer_request_latency_seconds_bucket" in r.text
     assert "x-request-id" in r.headers
+    values = dict(line.split(" ", 1) for line in r.text.splitlines()
+                  if line and not line.startswith("#") and "{" not in line)
+    for name in ("orinfer_generated_tokens_total", "orinfer_prompt_tokens_total",
+                 "orinfer_cached_prompt_tokens_total", "orinfer_compute_seconds_total",
+                 "orinfer_admission_seconds_total", "orinfer_batch_plan_seconds_total",
+                 "orinfer_sampling_request_failures_total", "orinfer_program_reclaims_total",
+                 "orinfer_prefix_cache_evictions_total", "orinfer_prefix_cache_host_evictions_total",
+                 "orinfer_prefix_restore_seconds_total", "orinfer_prefix_cache_device_entries",
+                 "orinfer_prefix_cache_device_bytes", "orinfer_prefix_cache_host_entries",
+                 "orinfer_prefix_cache_host_bytes", "orinfer_requests_running",
+                 "orinfer_requests_waiting"):
+        assert name in values, name
+    assert float(values["orinfer_generated_tokens_total"]) >= 3
+    assert float(values["orinfer_generated_tokens_total"]) == \
+        float(values["orinfer_completion_tokens_total"])
 
 
 def test_chat_completion_json_and_determinism(client):
