@@ -549,6 +549,14 @@ def create_gateway_app(manager: ModelManager, sweep_s: float = 5.0):
     from fastapi import FastAPI
 
     app = FastAPI(title="orinfer-b200 gateway", docs_url=None, redoc_url=None)
+    from .server import api_key, refuse_unauthorized
+    key = api_key()
+
+    @app.middleware("http")
+    async def authorise(request: HttpRequest, call_next):
+        refused = refuse_unauthorized(key, request)
+        return refused if refused is not None else await call_next(request)
+
     install(app, manager)
 
     def openai_error(e: ManagerError):

@@ -32,6 +32,30 @@ def _error(status: int, message: str, code: Optional[str] = None, param: Optiona
                                    "code": code}}, status_code=status, headers=headers)
 
 
+OPEN_PATHS = ("/health", "/", "/api/version")
+
+
+def api_key() -> Optional[str]:
+    """``ORINFER_API_KEY``: when set (and not empty) every route but the liveness ones wants
+    ``Authorization: Bearer <key>`` (crates/orinfer-api/src/server/mod.rs:232-249)."""
+    import os
+    return os.environ.get("ORINFER_API_KEY") or None
+
+
+def bearer_authorized(key: Optional[str], headers) -> bool:
+    if key is None:
+        return True
+    import hmac
+    value = headers.get("authorization") or ""
+    return value.startswith("Bearer ") and hmac.compare_digest(value[7:].encode(), key.encode())
+
+
+def refuse_unauthorized(key: Optional[str], request) -> Optional[JSONResponse]:
+    if request.url.path in OPEN_PATHS or bearer_authorized(key, request.headers):
+        return None
+    return _error(401, "Invalid API key", code="invalid_api_key", err_type="authentication_error")
+
+
 class Service:
     def __init__(self, engine_factory: Callable, codec: ChatCodec, model_name: str,
                  default_request_params: Optional[dict] = None, queue_timeout_ms: int = 0,
@@ -97,8 +121,20 @@ class Service:
         out = {"status": self.lifecycle.state, "model": self.model_name,
                "uptime_s": round(time.time() - self.started, 3),
                "continuous_batching": True,
-               "chat_capabilities": {"chat_template_kwargs": True, "tools": True,
-                                     "json_schema": True, "logprobs": True}}
+               "chat_capabilities": {
+                   "chat_template_kwargs": True, "json_schema": True, "logprobs": True,
+                   "streaming": True, "default_stream": bool(self.defaults.get("stream", False)),
+                   "max_choices": 1, "response_formats": ["text", "json_object", "json_schema"],
+                   "constraint_backend": "llguidance",
+                   "tools": {"function": True, "strict": True, "required": True,
+                             "incremental_arguments": True},
+                   "max_top_logprobs": 20, "logit_bias": True, "stored_completions": False,
+                   "images": False, "video": False,
+                   "audio": getattr(self.codec, "audio", None) is not None,
+                   "thinking_token_budget": True,
+                   "prompt_cache": {"key": True, "retention": ["in-memory", "24h"],
+                                    "persistent": False, "ttl_guaranteed": False}},
+               "default_request_params": self.defaults}
         if self.lifecycle.reason:
             out["reason"] = self.lifecycle.reason
         if eng is not None:
@@ -108,6 +144,10 @@ class Service:
             if eng.prefix is not None:
                 out["prefix_cache"] = eng.prefix.statistics().__dict__
             out["context"] = out["max_context"] = eng.max_context
+            out["mtp"] = {"enabled": eng.runner_has_mtp() and eng.spec.enabled,
+                          "max_drafts": eng.spec.max_drafts}
+            out["prompt_lookup"] = {"enabled": bool(eng.spec.prompt_lookup and eng.spec.enabled)}
+            out["active_requests"], out["queued_requests"] = out["active"], out["queued"]
             pager = getattr(eng.runner, "pager", None)
             if pager is not None:
                 out["expert_pager"] = pager.stats.as_dict()
@@ -148,12 +188,16 @@ def _delta_dict(d) -> dict:
 
 def create_app(service: Service) -> FastAPI:
     app = FastAPI(title="orinfer-b200", docs_url=None, redoc_url=None)
+    key = api_key()
 
     @app.middleware("http")
     async def request_id(request: HttpRequest, call_next):
         rid = request.headers.get("x-request-id") or uuid.uuid4().hex
         size = int(request.headers.get("content-length") or 0)
-        if size > BODY_LIMIT:
+        resp = refuse_unauthorized(key, request)
+        if resp is not None:
+            pass
+        elif size > BODY_LIMIT:
             resp = _error(413, "request body too large", code="body_too_large")
         else:
             resp = await call_next(request)

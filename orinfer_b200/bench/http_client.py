@@ -67,8 +67,11 @@ def stream_chat(base_url: str, body: dict, timeout: float = 600.0, session=None,
         release.wait()
     res.start = time.perf_counter()
     try:
+        import os
+        key = os.environ.get("ORINFER_API_KEY")
         with http.post(base_url.rstrip("/") + "/v1/chat/completions", json=body, stream=True,
-                       timeout=timeout) as r:
+                       timeout=timeout,
+                       headers={"Authorization": "Bearer " + key} if key else None) as r:
             res.status = r.status_code
             if r.status_code != 200:
                 res.error = r.text[:500]

@@ -309,7 +309,8 @@ def cmd_models(a) -> int:
             print(json.dumps(m.register(a.name, str(snap)).__dict__))
         elif a.models_cmd == "logs":
             import requests
-            r = requests.get(a.url.rstrip("/") + "/api/logs", params={"model": a.name}, timeout=10)
+            r = _session().get(a.url.rstrip("/") + "/api/logs", params={"model": a.name},
+                               timeout=10)
             if r.status_code != 200:
                 print(r.text, file=sys.stderr)
                 return 2
@@ -699,11 +700,23 @@ def build_parser() -> argparse.ArgumentParser:
     return ap
 
 
+def _session():
+    """HTTP session of the client verbs; carries ``ORINFER_API_KEY`` as a bearer token."""
+    import os
+
+    import requests
+    http = requests.Session()
+    if os.environ.get("ORINFER_API_KEY"):
+        http.headers["Authorization"] = "Bearer " + os.environ["ORINFER_API_KEY"]
+    return http
+
+
 def cmd_client(a) -> int:
     """Verbs that talk to a running server or manager over HTTP: ``ps``, ``load``, ``stop``,
     ``run`` (one prompt, piped stdin, or an interactive chat) and ``transcribe``."""
     import requests
     url = a.url.rstrip("/")
+    http = _session()
 
     def fail(r) -> int:
         print(r.text.strip(), file=sys.stderr)
@@ -711,7 +724,7 @@ def cmd_client(a) -> int:
 
     try:
         if a.verb == "ps":
-            r = requests.get(url + "/api/ps", timeout=10)
+            r = http.get(url + "/api/ps", timeout=10)
             if r.status_code != 200:
                 return fail(r)
             print(json.dumps(r.json()["models"], indent=1))
@@ -719,12 +732,12 @@ def cmd_client(a) -> int:
             body = {"model": a.name}
             if a.keep_alive is not None:
                 body["keep_alive"] = a.keep_alive
-            r = requests.post(url + "/api/load", json=body, timeout=3600)
+            r = http.post(url + "/api/load", json=body, timeout=3600)
             if r.status_code != 200:
                 return fail(r)
             print(json.dumps(r.json()))
         elif a.verb == "stop":
-            r = requests.post(url + "/api/stop", json={"model": a.name, "force": a.force},
+            r = http.post(url + "/api/stop", json={"model": a.name, "force": a.force},
                               timeout=600)
             if r.status_code != 200:
                 return fail(r)
@@ -735,7 +748,7 @@ def cmd_client(a) -> int:
                 if getattr(a, key):
                     data[key] = getattr(a, key)
             with open(a.input, "rb") as f:
-                r = requests.post(url + "/v1/audio/transcriptions", data=data, timeout=3600,
+                r = http.post(url + "/v1/audio/transcriptions", data=data, timeout=3600,
                                   files={"file": (Path(a.input).name, f)})
             if r.status_code != 200:
                 return fail(r)

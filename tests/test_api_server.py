@@ -204,3 +204,31 @@ def test_ollama_shows_tool_calls_whole():
                                    "arguments": {"zone": "U}TC", "n": {"k": [1]}}}}]
     assert asm.flush() == [{"function": {"name": "second", "arguments": {RAW_ARGUMENTS: '{"a"'}}}]
     assert parser.finish_reason("stop") == "tool_calls"
+
+
+def test_api_key_guards_everything_but_liveness(monkeypatch):
+    """With ORINFER_API_KEY set, routes want `Authorization: Bearer <key>`; `/health` stays
+    open; the refusal is a 401 in the error shape with a request id."""
+    monkeypatch.setenv("ORINFER_API_KEY", "s3cret")
+    weights = random_model(PRESETS["tiny"], seed=0)
+    svc = Service(lambda: Engine(weights, sched=SchedulerOptions(max_active=2, prefill_chunk=64),
+                                 kv_pages=16, max_context=256),
+                  ChatCodec(ByteTokenizer(1024), context=256, model_name="tiny"), "tiny")
+    svc.start()
+    try:
+        with TestClient(create_app(svc)) as c:
+            assert c.get("/health").status_code == 200
+            for method, path in (("get", "/v1/models"), ("get", "/metrics"),
+                                 ("post", "/v1/chat/completions"), ("post", "/api/chat")):
+                r = getattr(c, method)(path)
+                assert r.status_code == 401 and r.json()["error"]["code"] == "invalid_api_key"
+                assert r.headers.get("x-request-id")
+            wrong = c.get("/v1/models", headers={"Authorization": "Bearer nope"})
+            assert wrong.status_code == 401
+            ok = {"Authorization": "Bearer s3cret"}
+            assert c.get("/v1/models", headers=ok).status_code == 200
+            r = c.post("/v1/chat/completions", headers=ok,
+                       json={"messages": MSG, "max_tokens": 2, "ignore_eos": True})
+            assert r.status_code == 200
+    finally:
+        svc.stop(1000)
