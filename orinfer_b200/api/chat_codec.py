@@ -460,6 +460,28 @@ class ChatCodec:
             raise RequestError(f"chat template failed: {e}", param="messages")
 
 
+def validate_defaults(codec: "ChatCodec", defaults: Dict[str, Any]) -> None:
+    """Deployment defaults are checked when the service starts, not when the first request
+    trips over them: they may not name what only a client can (`model`, `messages`), and the
+    request they make with a one-line conversation must itself be valid
+    (crates/orinfer-api/src/server/defaults.rs:6-21)."""
+    if not isinstance(defaults, dict):
+        raise ValueError("default_request_params must be a JSON object")
+    for name in ("model", "messages"):
+        if name in defaults:
+            raise ValueError(f"default_request_params.{name}: must be supplied by the client")
+    unknown = sorted(set(defaults) - ALLOWED_FIELDS)
+    if unknown:
+        raise ValueError(f"default_request_params.{unknown[0]}: unknown field")
+    if not defaults:
+        return
+    try:
+        codec.prepare({"messages": [{"role": "user", "content": "Hello"}]}, defaults)
+    except RequestError as e:
+        where = f".{e.param}" if e.param else ""
+        raise ValueError(f"default_request_params{where}: {e.message}") from e
+
+
 EFFORTS = ("none", "minimal", "low", "medium", "high", "xhigh", "max")
 SCHEMA_PARAM = "response_format.json_schema.schema"
 

@@ -65,6 +65,8 @@ class Service:
         self.codec = codec
         self.model_name = model_name
         self.defaults = default_request_params or {}
+        from .chat_codec import validate_defaults
+        validate_defaults(codec, self.defaults)          # a bad default fails the start
         self.metrics = Metrics()
         self.lifecycle = Lifecycle()
         self.worker = EngineWorker(engine_factory, codec, self.metrics, self.lifecycle,

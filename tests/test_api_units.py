@@ -232,3 +232,21 @@ def test_parser_and_finish_reason_follow_the_protocol_table():
         if has_tool:
             p.feed(call, final=True)
         assert p.finish_reason("length" if exhausted else "stop") == want
+
+
+def test_deployment_defaults_are_checked_at_start():
+    import pytest
+    from orinfer_b200.api.chat_codec import ByteTokenizer, ChatCodec, validate_defaults
+    codec = ChatCodec(ByteTokenizer(1024), context=512, model_name="m")
+    validate_defaults(codec, {})
+    validate_defaults(codec, {"temperature": 0.3, "max_tokens": 64, "enable_thinking": True})
+    for bad, word in (({"model": "x"}, "default_request_params.model"),
+                      ({"messages": []}, "default_request_params.messages"),
+                      ({"temperature": -1}, "default_request_params.temperature"),
+                      ({"bogus": 1}, "default_request_params.bogus"),
+                      ({"reasoning_effort": "much"}, "default_request_params.reasoning_effort")):
+        with pytest.raises(ValueError, match=word):
+            validate_defaults(codec, bad)
+    # a default limit is shortened to fit, an explicit one is kept or refused
+    p = codec.prepare({"messages": [{"role": "user", "content": "x" * 400}]}, {"max_tokens": 4096})
+    assert p.max_new < 4096
