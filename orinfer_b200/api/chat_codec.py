@@ -138,23 +138,73 @@ ALLOWED_FIELDS = {
     # (what the Ollama routes ask for: `num_predict` is a wish there, not a contract)
     "output_limit",
 }
-GROUPS = [("enable_thinking", "reasoning_effort"), ("max_tokens", "max_completion_tokens")]
+
+
+
+THINKING_FIELDS = ("enable_thinking", "thinking", "reasoning_effort")     # in template kwargs
+BUDGET_FIELDS = ("thinking_budget", "thinking_token_budget")
 
 
 def merge_defaults(request: Dict[str, Any], deployment: Dict[str, Any]) -> Dict[str, Any]:
-    """request > deployment; an explicit null in the request clears the deployment
-    default; grouped fields override as a group."""
-    out = dict(deployment)
-    for group in GROUPS:
-        if any(k in request for k in group):
-            for k in group:
-                out.pop(k, None)
-    for k, v in request.items():
-        if v is None:
-            out.pop(k, None)
-        else:
-            out[k] = v
-    return out
+    """request > deployment.  A field the request names (even as ``false``, ``[]`` or
+    ``null``) is the request's; ``null`` then means "not set".  Related controls override as
+    one group, so a default can neither contradict nor defeat the spelling the client chose:
+    the two output limits; the thinking switches (top level or inside
+    ``chat_template_kwargs``); the two spellings of the thinking budget.  ``stream`` off takes
+    a default ``stream_options`` with it and ``logprobs`` off a default ``top_logprobs``.
+    ``chat_template_kwargs`` merge key by key (crates/orinfer-api/src/server/defaults.rs:40-104)."""
+    kwargs = request.get("chat_template_kwargs")
+    kwargs = kwargs if isinstance(kwargs, dict) else {}
+    output_override = "max_tokens" in request or "max_completion_tokens" in request
+    thinking_override = ("enable_thinking" in request or "reasoning_effort" in request
+                         or any(k in kwargs for k in THINKING_FIELDS))
+    budget_override = ("thinking_token_budget" in request
+                       or any(k in kwargs for k in BUDGET_FIELDS))
+    stream_off = "stream" in request and not request["stream"]
+    logprobs_off = "logprobs" in request and not request["logprobs"]
+    out = dict(request)
+    for name, value in deployment.items():
+        if name == "chat_template_kwargs" and isinstance(value, dict):
+            if "chat_template_kwargs" in request and not isinstance(
+                    request["chat_template_kwargs"], dict):
+                continue                              # an explicit null clears the whole map
+            merged = dict(kwargs)
+            for key, v in value.items():
+                if thinking_override and key in THINKING_FIELDS \
+                        or budget_override and key in BUDGET_FIELDS:
+                    continue
+                merged.setdefault(key, v)
+            out["chat_template_kwargs"] = merged
+            continue
+        if (name in request
+                or output_override and name in ("max_tokens", "max_completion_tokens")
+                or thinking_override and name in ("enable_thinking", "reasoning_effort")
+                or budget_override and name == "thinking_token_budget"
+                or stream_off and name == "stream_options"
+                or logprobs_off and name == "top_logprobs"):
+            continue
+        out[name] = value
+    return {k: v for k, v in out.items() if v is not None}
+
+
+def thinking_budget_of(req: Dict[str, Any]) -> Optional[int]:
+    """The thinking budget a request asks for: the top-level field wins over the template
+    variables; the two spellings inside ``chat_template_kwargs`` may not disagree; a budget is
+    a non-negative integer (not a boolean, a fraction or a string)."""
+    kwargs = req.get("chat_template_kwargs") or {}
+    inner = [kwargs[k] for k in BUDGET_FIELDS if k in kwargs and kwargs[k] is not None]
+    for value, where in [(req.get("thinking_token_budget"), "thinking_token_budget")] + \
+            [(v, "chat_template_kwargs.thinking_budget") for v in inner]:
+        if value is not None and (isinstance(value, bool) or not isinstance(value, int)
+                                  or value < 0):
+            raise RequestError("a thinking budget is a non-negative integer",
+                               param="thinking_token_budget" if "." not in where else where)
+    if len(inner) == 2 and inner[0] != inner[1]:
+        raise RequestError("`thinking_budget` and `thinking_token_budget` disagree",
+                           param="chat_template_kwargs.thinking_budget")
+    if req.get("thinking_token_budget") is not None:
+        return req["thinking_token_budget"]
+    return inner[0] if inner else None
 
 
 @dataclass
@@ -305,10 +355,7 @@ class ChatCodec:
         if thinking is None:
             thinking = (effort not in (None, "none")) if effort is not None \
                 else self.defaults.thinking
-        budget = req.get("thinking_token_budget", kwargs.get("thinking_budget"))
-        if budget is not None and (not isinstance(budget, int) or budget < 0):
-            raise RequestError("`thinking_token_budget` must be >= 0",
-                               param="thinking_token_budget")
+        budget = thinking_budget_of(req)
 
         d = self.defaults
         seed = req.get("seed")

@@ -250,3 +250,56 @@ def test_deployment_defaults_are_checked_at_start():
     # a default limit is shortened to fit, an explicit one is kept or refused
     p = codec.prepare({"messages": [{"role": "user", "content": "x" * 400}]}, {"max_tokens": 4096})
     assert p.max_new < 4096
+
+
+def test_defaults_only_fill_what_the_request_left_open():
+    """The merge rules of deployment defaults, case by case."""
+    import pytest
+    from orinfer_b200.api.chat_codec import (ByteTokenizer, ChatCodec, RequestError,
+                                             merge_defaults, thinking_budget_of)
+    d = {"enable_thinking": True, "temperature": 0.7, "stream": True, "stop": ["END"]}
+    assert merge_defaults({}, d) == d
+    own = {"enable_thinking": False, "temperature": 0, "stream": False, "stop": []}
+    assert merge_defaults(own, d) == own                      # false, 0 and [] are answers
+    assert merge_defaults({"enable_thinking": None, "temperature": None, "stream": None}, d) \
+        == {"stop": ["END"]}                                  # null: not set, default cleared
+    # one group, one spelling
+    assert merge_defaults({"max_completion_tokens": 8}, {"max_tokens": 64}) == \
+        {"max_completion_tokens": 8}
+    assert merge_defaults({"reasoning_effort": "none"}, {"enable_thinking": True}) == \
+        {"reasoning_effort": "none"}
+    assert merge_defaults({"chat_template_kwargs": {"enable_thinking": False}},
+                          {"enable_thinking": True, "reasoning_effort": "high"}) == \
+        {"chat_template_kwargs": {"enable_thinking": False}}
+    # switching a feature off takes its dependent default with it
+    assert merge_defaults({"stream": False}, {"stream_options": {"include_usage": True}}) == \
+        {"stream": False}
+    assert merge_defaults({"logprobs": False}, {"top_logprobs": 5, "logprobs": True}) == \
+        {"logprobs": False}
+    # template variables merge key by key; null clears the map
+    assert merge_defaults({"chat_template_kwargs": {"a": 1}},
+                          {"chat_template_kwargs": {"a": 0, "b": 2}}) == \
+        {"chat_template_kwargs": {"a": 1, "b": 2}}
+    assert merge_defaults({"chat_template_kwargs": None},
+                          {"chat_template_kwargs": {"b": 2}}) == {}
+    # every spelling of a default budget yields to either spelling in the request
+    for default in ({"thinking_token_budget": 512},
+                    {"chat_template_kwargs": {"thinking_token_budget": 512}},
+                    {"chat_template_kwargs": {"thinking_budget": 512}}):
+        for name in ("thinking_budget", "thinking_token_budget"):
+            merged = merge_defaults({"chat_template_kwargs": {name: 0}}, default)
+            assert thinking_budget_of(merged) == 0, (default, name)
+    both = {"thinking_token_budget": 4,
+            "chat_template_kwargs": {"thinking_budget": 16, "thinking_token_budget": 16}}
+    assert thinking_budget_of(both) == 4                      # the top-level field wins
+    for bad in (-1, True, 1.5, "8"):
+        with pytest.raises(RequestError):
+            thinking_budget_of({"chat_template_kwargs": {"thinking_budget": bad}})
+    with pytest.raises(RequestError, match="disagree"):
+        thinking_budget_of({"chat_template_kwargs": {"thinking_budget": 8,
+                                                     "thinking_token_budget": 4}})
+    codec = ChatCodec(ByteTokenizer(1024), context=512, model_name="m")
+    p = codec.prepare({"messages": [{"role": "user", "content": "hi"}], "enable_thinking": True,
+                       "chat_template_kwargs": {"thinking_budget": 0}},
+                      {"thinking_token_budget": 512})
+    assert p.thinking_budget == 0
