@@ -474,6 +474,11 @@ class ChatCodec:
             raise RequestError("a thinking budget needs room for the end of thinking and an "
                                "answer token", param=limit_name)
         stream_opts = req.get("stream_options") or {}
+        if not isinstance(stream_opts, dict):
+            raise RequestError("`stream_options` must be an object", param="stream_options")
+        if stream_opts.get("include_obfuscation"):
+            raise RequestError("only false is supported",
+                               param="stream_options.include_obfuscation")
         return Prepared(
             prompt_ids=ids, sampling=sampling, max_new=max_new, stream=bool(req.get("stream")),
             include_usage=bool(stream_opts.get("include_usage")),
