@@ -72,12 +72,13 @@ class ModelManager:
                  memory_budget_bytes: int = 0, clock: Callable[[], float] = time.monotonic,
                  estimate: Optional[Callable[[Entry], int]] = None,
                  alive: Optional[Callable[[object], bool]] = None,
-                 capacity_wait_s: float = 0.0):
+                 capacity_wait_s: float = 0.0, max_loaded: int = 0):
         self.state = Path(state_dir)
         self.state.mkdir(parents=True, exist_ok=True)
         self._start, self._stop = start, stop
         self._estimate, self._alive = estimate, alive
         self.capacity_wait_s = capacity_wait_s
+        self.max_loaded = max_loaded               # 0: no limit on the number of runners
         self.budget = memory_budget_bytes
         self.clock = clock
         self._lock = threading.Lock()              # registry + runner table
@@ -225,19 +226,20 @@ class ModelManager:
         """Idle eviction under the memory budget: least recently used idle runners go first
         (whatever their keep-alive).  With every runner in use the caller waits up to
         ``capacity_wait_s`` for a lease to come back."""
-        if self.budget <= 0:
+        if self.budget <= 0 and self.max_loaded <= 0:
             return
         deadline = time.monotonic() + self.capacity_wait_s
         while True:
             with self._lock:
                 used = sum(r.bytes for r in self.runners.values())
-                if used + nbytes <= self.budget:
+                fits = self.budget <= 0 or used + nbytes <= self.budget
+                if fits and (self.max_loaded <= 0 or len(self.runners) < self.max_loaded):
                     return
                 idle = sorted((r for r in self.runners.values() if r.leases == 0),
                               key=lambda r: r.last_used)
                 if not idle:
                     left = deadline - time.monotonic()
-                    if left <= 0 or nbytes > self.budget:
+                    if left <= 0 or 0 < self.budget < nbytes:
                         raise ManagerError("memory budget exhausted by models in use", 503)
                     self._idle.wait(min(left, 0.05))
                     if cancelled():

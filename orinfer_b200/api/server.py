@@ -188,7 +188,7 @@ def _delta_dict(d) -> dict:
     return out
 
 
-def create_app(service: Service) -> FastAPI:
+def create_app(service: Service, body_limit: int = BODY_LIMIT) -> FastAPI:
     app = FastAPI(title="orinfer-b200", docs_url=None, redoc_url=None)
     key = api_key()
 
@@ -199,7 +199,7 @@ def create_app(service: Service) -> FastAPI:
         resp = refuse_unauthorized(key, request)
         if resp is not None:
             pass
-        elif size > BODY_LIMIT:
+        elif size > body_limit:
             resp = _error(413, "request body too large", code="body_too_large")
         else:
             resp = await call_next(request)

@@ -142,6 +142,16 @@ def cmd_serve(a) -> int:
     probe.close()
     if not a.model_dir and not a.preset:
         return _serve_manager(a, host, int(port), load, sched)
+    if getattr(a, "gpu_lock", None):
+        # one holder per device: a second server (or a measurement) on the same GPU is
+        # refused at once instead of sharing it unnoticed
+        from .bench.telemetry import GpuBusy, GpuLock
+        index = int(str(a.device).partition(":")[2] or 0)
+        try:
+            a._gpu_lock = GpuLock(index, a.gpu_lock).acquire()      # held for the process's life
+        except GpuBusy as e:
+            print(str(e), file=sys.stderr)
+            return 2
     # Listen first, load behind: /health answers `starting` (503) while the weights load, a
     # port conflict shows at once, and clients that retry on 503 need no separate readiness poll
     # (the reference binds before loading too, crates/orinfer-api/src/server/startup.rs:44-160).
@@ -183,8 +193,9 @@ def cmd_serve(a) -> int:
                       json.loads(a.default_request_params), a.queue_timeout_ms,
                       a.output_timeout_ms, a.preparation_workers, a.preparation_memory_mib,
                       a.step_timeout_ms, exit_on_stall=True)
-    server = uvicorn.Server(uvicorn.Config(create_app(service), host=host, port=int(port),
-                                           log_level="warning"))
+    server = uvicorn.Server(uvicorn.Config(
+        create_app(service, body_limit=getattr(a, "request_body_mib", 32) << 20),
+        host=host, port=int(port), log_level="warning"))
     service.start(wait=False)
 
     def announce():
@@ -266,7 +277,8 @@ def _serve_manager(a, host: str, port: int, load, sched) -> int:
                  a.default_request_params]           # per-name defaults are applied by the gateway
         if a.max_context:
             extra += ["--max-context", str(a.max_context)]
-        child = ChildRunner(entry.path, entry.name, extra).start()
+        child = ChildRunner(entry.path, entry.name, extra,
+                            start_timeout_s=getattr(a, "load_timeout_s", 600.0)).start()
         return RunnerHandle(child, ProxyApp(child.base_url)), weight_bytes(entry.path)
 
     process = getattr(a, "runners", "process") == "process"
@@ -277,6 +289,7 @@ def _serve_manager(a, host: str, port: int, load, sched) -> int:
     manager = ModelManager(_state_dir(a), start_process if process else start, stop,
                            memory_budget_bytes=getattr(a, "memory_budget_mib", 0) << 20,
                            estimate=lambda entry: weight_bytes(entry.path),
+                           max_loaded=getattr(a, "max_loaded_models", 0),
                            capacity_wait_s=getattr(a, "capacity_wait_ms", 30000) / 1e3)
     print(f"API READY http://{a.listen}/v1; manager with {len(manager.list())} models",
           file=sys.stderr)
@@ -549,10 +562,22 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--listen", default="[::]:8088")
     s.add_argument("--queue-timeout-ms", type=int, default=0)
     s.add_argument("--output-timeout-ms", type=int, default=60000)
-    s.add_argument("--preparation-workers", type=int, default=4,
+    s.add_argument("--preparation-workers", "--preprocess-workers", dest="preparation_workers",
+                   type=int, default=4,
                    help="threads that render, tokenise and compile grammars for new requests")
-    s.add_argument("--preparation-memory-mib", type=int, default=1024,
+    s.add_argument("--preparation-memory-mib", "--preprocess-memory-mib",
+                   dest="preparation_memory_mib", type=int, default=1024,
                    help="host memory that requests being prepared may hold at once")
+    s.add_argument("--request-body-mib", type=int, default=32,
+                   help="largest HTTP request body that is read (413 beyond it)")
+    s.add_argument("--max-loaded-models", type=int, default=0,
+                   help="manager mode: at most this many models loaded at once (0 = as many "
+                        "as the memory budget allows)")
+    s.add_argument("--load-timeout-s", type=float, default=600.0,
+                   help="manager mode: how long a model's runner process may take to start")
+    s.add_argument("--gpu-lock", default=None,
+                   help="directory of the per-GPU advisory locks; with it `serve` takes the "
+                        "lock of its device and refuses to start while another holder has it")
     s.add_argument("--drain-timeout-ms", type=int, default=30000)
     s.add_argument("--step-timeout-ms", type=int, default=120000,
                    help="an engine step running longer fails the server closed and exits 70 "

@@ -384,3 +384,29 @@ def test_names_that_share_a_runner_keep_their_own_defaults(tmp_path):
         assert oll["options"] == {"top_p": 0.5, "temperature": 0.7, "num_predict": 64}
         assert oll["think"] is True
     assert starts == ["base"]                                # same files, same options: one runner
+
+
+def test_max_loaded_models_caps_the_number_of_runners(tmp_path):
+    starts, stopped = [], []
+    m = M.ModelManager(tmp_path, lambda e: (starts.append(e.name) or f"svc:{e.name}", 1),
+                       stopped.append, max_loaded=2)
+    for n in "abc":
+        m.register(n, f"/models/{n}")
+    ra, rb = m.acquire("a"), m.acquire("b")
+    with pytest.raises(M.ManagerError) as err:
+        m.acquire("c")                                       # both in use, no waiting configured
+    assert err.value.status == 503
+    m.release(ra)
+    m.acquire("c")
+    assert "svc:a" in stopped and len(m.running()) == 2
+    m.release(rb)
+
+
+def test_serve_flags_of_the_reference_are_accepted():
+    from orinfer_b200.cli import build_parser
+    a = build_parser().parse_args([
+        "serve", "--preset", "tiny", "--preprocess-workers", "3", "--preprocess-memory-mib",
+        "512", "--request-body-mib", "8", "--max-loaded-models", "2", "--load-timeout-s", "120",
+        "--gpu-lock", "/tmp/locks"])
+    assert (a.preparation_workers, a.preparation_memory_mib, a.request_body_mib,
+            a.max_loaded_models, a.load_timeout_s, a.gpu_lock) == (3, 512, 8, 2, 120.0, "/tmp/locks")
