@@ -215,6 +215,28 @@ class ModelDefaults:
     top_k: int = 0
     presence_penalty: float = 0.0
     max_tokens: int = 1024
+    frequency_penalty: float = 0.0
+    repetition_penalty: float = 1.0
+
+    @classmethod
+    def from_generation_config(cls, gen: Dict[str, Any]) -> "ModelDefaults":
+        """Sampling defaults a checkpoint ships in ``generation_config.json`` (the model
+        card's recommendation); requests and deployment defaults are applied on top
+        (crates/orinfer-api/src/server/chat/generation_defaults.rs:41-60).  ``do_sample:
+        false`` means greedy whatever temperature is written beside it."""
+        d = cls()
+        number = lambda key, old: float(gen[key]) if isinstance(gen.get(key), (int, float)) \
+            and not isinstance(gen.get(key), bool) else old
+        if gen.get("do_sample") is not False:
+            d.temperature = number("temperature", d.temperature)
+        d.top_p = number("top_p", d.top_p)
+        top_k = gen.get("top_k")
+        if isinstance(top_k, int) and not isinstance(top_k, bool):
+            d.top_k = 0 if top_k < 0 else top_k
+        d.presence_penalty = number("presence_penalty", d.presence_penalty)
+        d.frequency_penalty = number("frequency_penalty", d.frequency_penalty)
+        d.repetition_penalty = number("repetition_penalty", d.repetition_penalty)
+        return d
 
 
 @dataclass
@@ -288,15 +310,18 @@ class ChatCodec:
             if isinstance(held, str) and held.strip():
                 template = held
         eos: List[int] = []
+        defaults = None
         gen = model_dir / "generation_config.json"
         if gen.exists():
-            e = json.loads(gen.read_text()).get("eos_token_id", [])
-            eos = [e] if isinstance(e, int) else list(e)
+            held = json.loads(gen.read_text())
+            e = held.get("eos_token_id", [])
+            eos = [e] if isinstance(e, int) else list(e or [])
+            defaults = ModelDefaults.from_generation_config(held)
         tok_file = model_dir / "tokenizer.json"
         tokenizer = HFTokenizer(tok_file, eos) if tok_file.exists() else ByteTokenizer(vocab)
         if tokenizer.vocab > vocab:
             raise ValueError("tokenizer vocabulary exceeds the model vocabulary")
-        return cls(tokenizer, template, None, context, model_name)
+        return cls(tokenizer, template, defaults, context, model_name)
 
     # ----------------------------------------------------------------- validation
     def prepare(self, body: Dict[str, Any], deployment_defaults: Optional[dict] = None) -> Prepared:
@@ -384,8 +409,8 @@ class ChatCodec:
             temperature=float(req.get("temperature", d.temperature)),
             top_p=float(req.get("top_p", d.top_p)), top_k=int(top_k),
             presence_penalty=float(req.get("presence_penalty", d.presence_penalty)),
-            frequency_penalty=float(req.get("frequency_penalty", 0.0)),
-            repetition_penalty=float(req.get("repetition_penalty", 1.0)),
+            frequency_penalty=float(req.get("frequency_penalty", d.frequency_penalty)),
+            repetition_penalty=float(req.get("repetition_penalty", d.repetition_penalty)),
             seed=seed & (2 ** 64 - 1), logit_bias=bias,
             top_logprobs=(top_lp if top_lp is not None else (0 if want_lp else None)))
         try:

@@ -303,3 +303,23 @@ def test_defaults_only_fill_what_the_request_left_open():
                        "chat_template_kwargs": {"thinking_budget": 0}},
                       {"thinking_token_budget": 512})
     assert p.thinking_budget == 0
+
+
+def test_generation_config_supplies_the_sampling_defaults(tmp_path):
+    import json
+    from orinfer_b200.api.chat_codec import ChatCodec
+    (tmp_path / "generation_config.json").write_text(json.dumps(
+        {"eos_token_id": [258, 256], "do_sample": True, "temperature": 0.6, "top_p": 0.95,
+         "top_k": 20, "repetition_penalty": 1.05}))
+    codec = ChatCodec.load(tmp_path, 1024, 512, "m")
+    msgs = [{"role": "user", "content": "hi"}]
+    s = codec.prepare({"messages": msgs}).sampling
+    assert (s.temperature, s.top_p, s.top_k, s.repetition_penalty) == (0.6, 0.95, 20, 1.05)
+    s = codec.prepare({"messages": msgs, "temperature": 0, "top_k": -1}).sampling
+    assert s.temperature == 0 and s.top_k == 0 and s.top_p == 0.95       # the request wins
+    s = codec.prepare({"messages": msgs}, {"temperature": 0.2}).sampling
+    assert s.temperature == 0.2                                          # then the deployment
+    (tmp_path / "generation_config.json").write_text(json.dumps(
+        {"do_sample": False, "temperature": 0.6, "top_k": 50}))
+    s = ChatCodec.load(tmp_path, 1024, 512, "m").prepare({"messages": msgs}).sampling
+    assert s.temperature == 0 and s.top_k == 50                          # greedy as shipped
