@@ -273,8 +273,10 @@ def create_app(service: Service, body_limit: int = BODY_LIMIT) -> FastAPI:
         model = job.prepared.model
         if job.prepared.stream:
             async def sse():
+                ended = False
                 try:
                     async for ev in service.events(job):
+                        ended = ended or ev["type"] in ("done", "error")
                         if ev["type"] == "start":
                             yield _chunk(job, model, {"role": "assistant", "content": ""})
                         elif ev["type"] == "delta":
@@ -290,6 +292,13 @@ def create_app(service: Service, body_limit: int = BODY_LIMIT) -> FastAPI:
                                 "message": ev["message"], "type": "server_error", "param": None,
                                 "code": ev.get("code")}}) + "\n\n"
                             yield "data: [DONE]\n\n"
+                    if not ended:
+                        # a stream that just stops is an error, not a short success
+                        yield "data: " + json.dumps({"error": {
+                            "message": "the response ended without a result",
+                            "type": "server_error", "param": None,
+                            "code": "incomplete_response"}}) + "\n\n"
+                        yield "data: [DONE]\n\n"
                 finally:
                     job.cancelled = True          # client went away or stream ended
             return StreamingResponse(sse(), media_type="text/event-stream")
