@@ -897,11 +897,22 @@ class Engine:
         skipped.  Packets too large for the ring, and engines started with
         ``ORINFER_PACKED_UPLOAD=0``, upload every array on its own."""
         names = [k for k, v in parts.items() if v is not None]
+        if self._packed_uploads:
+            try:
+                return self._upload_packed(parts, names)
+            except Exception as exc:               # noqa: BLE001 - the plain path always works
+                import sys
+                print(f"packed uploads switched off after {type(exc).__name__}: {exc}",
+                      file=sys.stderr, flush=True)
+                self._packed_uploads = False
+        return {k: self._upload(k, parts[k]) for k in names}
+
+    def _upload_packed(self, parts, names) -> Dict[str, torch.Tensor]:
         offs, total = {}, 0
         for k in names:
             offs[k] = total
             total += (4 * len(parts[k]) + 127) // 128 * 128
-        if not self._packed_uploads or total == 0 or total > self.STAGE_BYTES // 4:
+        if total == 0 or total > self.STAGE_BYTES // 4:
             return {k: self._upload(k, parts[k]) for k in names}
         from ..core import transfers
         if self._stage is None:

@@ -365,6 +365,13 @@ def test_packed_uploads_equal_single_uploads_and_reuse_the_ring(weights, monkeyp
         assert got["a"].tolist() == parts["a"] and got["b"].tolist() == parts["b"]
     st = small._stage_ring.stats()
     assert st["live"] == 0 and st["peak"] <= 1 << 14 and small.stats.packed_uploads == 200
+    # a failure inside the packed path switches it off and the plain path carries on
+    from orinfer_b200.core import transfers
+    broken = _engine(weights)
+    monkeypatch.setattr(transfers, "pack_inputs", lambda *a, **k: 1 / 0)
+    assert broken._upload_many({"a": [4, 5], "b": [6]})["b"].tolist() == [6]
+    assert broken._packed_uploads is False
+    monkeypatch.undo()
     monkeypatch.setenv("ORINFER_PACKED_UPLOAD", "0")
     plain = _engine(weights)
     assert plain._upload_many({"a": [1, 2, 3]})["a"].tolist() == [1, 2, 3]
