@@ -222,6 +222,9 @@ class Engine:
         self._pin = {}
         self._stage = None                       # pinned staging ring of ``_upload_many``
         self._packed_uploads = os.environ.get("ORINFER_PACKED_UPLOAD", "1") != "0"
+        # verification rows inside prompt packets (ORINFER_MIXED_VERIFY=0: decoders take plain
+        # single rows while prompts are being prefilled)
+        self._mixed_verify = os.environ.get("ORINFER_MIXED_VERIFY", "1") != "0"
         from .speculation import Speculator
         self.spec = Speculator(self, self.load.mtp_drafts, self.load.prompt_lookup)
         self.tpot_ewma: Optional[float] = None
@@ -844,7 +847,8 @@ class Engine:
             # prompt chunks do not stop speculation: greedy decoders bring their drafts into
             # the same packet as verification rows (attention-only models)
             drafts = None
-            if chunks and decoders and self.spec.enabled and not self.recurrent:
+            if chunks and decoders and self.spec.enabled and not self.recurrent \
+                    and self._mixed_verify:
                 room = min(self.max_rows, self.row_cap) - len(decoders) - sum(n for _, n in chunks)
                 drafts = self.spec.plan_mixed(decoders, room)
             tokens, logits, order = self._run_direct(decoders, chunks, drafts)
